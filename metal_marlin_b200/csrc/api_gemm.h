@@ -1,0 +1,55 @@
+// C ABI of the tcgen05 (sm_100a) GEMM kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// out[M, N] = x[M, Kx] * W^T with W in the FP4 device tile layout (see api.h).
+// Grouped mode (MoE): tile_* describe, per token tile, which expert bank to use and which rows of
+// the (expert-sorted) x / out it covers; all three arrays and n_tiles live in device memory so the
+// host never waits for the routing result.
+typedef struct {
+  const void* x;            // bf16 [M, Kx] row major (16-byte aligned rows)
+  const void* qw;           // tile-layout weights [(E,) N/16, K/64, 32, 4] int32
+  const void* sc;           // tile-layout scales  [(E,) N/16, K/gs, 8, 2] fp16
+  void* out;                // bf16 [M, ldo]
+  int M, N, K, Kx, ldo;
+  int gs_shift;
+  int act;                  // 0 none; 1: rows [0,N/2) gate and [N/2,N) up are interleaved per 64-row half tile -> silu(g)*u
+  int* status;              // device int[4]: [0] != 0 after a wait timed out (1 = producer, 2 = mma, 3 = dequant, 4 = epilogue)
+  // grouped mode (all null/0 for a plain GEMM)
+  const int* tile_expert;   // [max_tiles]
+  const int* tile_row0;     // [max_tiles] first row of the tile in x / out
+  const int* tile_rows;     // [max_tiles] valid rows in the tile (<= token tile)
+  const int* n_tiles;       // device scalar
+  int max_tiles;
+  long long expert_stride_q;   // 16-byte units
+  long long expert_stride_s;   // 4-byte units
+  const float* row_scale;   // optional fp32 [M]: out row multiplied by it (routing weight)
+  int token_tile;           // 0 = auto; else 32 / 64 / 128 / 256
+} MmbFp4GemmParams;
+
+int mmb_fp4_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
+
+// out[M, N] = x[M, K] * W[N, K]^T, both bf16 row major (TMA for both operands), fp32 accumulate in TMEM.
+// Batched over `batch` independent problems with element strides (0 = shared operand).
+typedef struct {
+  const void* x;
+  const void* w;
+  void* out;                // bf16 or fp32
+  int M, N, K, ldo;
+  int out_f32;
+  int batch;
+  long long x_batch_stride, w_batch_stride, out_batch_stride;   // elements
+  int ldx, ldw;             // row strides in elements (multiples of 8)
+  int* status;
+} MmbBf16GemmParams;
+
+int mmb_bf16_gemm(const MmbBf16GemmParams* p, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,375 @@
+// torch.ops.mmb200.* : thin argument-checking shims over the extern "C" kernel launchers.
+// Every op writes into caller-provided output tensors (no allocation here), runs on the current
+// CUDA stream and is therefore capturable in a CUDA graph.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/torch.h>
+
+#include "api.h"
+#include "api_gemm.h"
+
+namespace {
+
+using torch::Tensor;
+using OptT = c10::optional<Tensor>;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+inline const void* cptr(const OptT& t) { return (t.has_value() && t->defined()) ? t->data_ptr() : nullptr; }
+inline void* mptr(const OptT& t) { return (t.has_value() && t->defined()) ? t->data_ptr() : nullptr; }
+
+inline void check(int err, const char* what) {
+  TORCH_CHECK(err == 0, what, " failed: ", cudaGetErrorString((cudaError_t)err), " (", err, ")");
+}
+inline void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, name, " must be a CUDA bf16 tensor");
+}
+inline int log2i(int64_t v) {
+  int s = 0;
+  while ((1LL << s) < v) ++s;
+  TORCH_CHECK((1LL << s) == v, "group size must be a power of two, got ", v);
+  return s;
+}
+
+void fp4_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t Kx, int64_t gs,
+              const OptT& delta, const OptT& norm_w, const OptT& resid_out, double eps, int64_t act, const OptT& bias,
+              const OptT& out_add) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1);
+  TORCH_CHECK(qw.dim() == 4 && qw.is_contiguous() && sc.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbFp4GemvParams p{};
+  p.qw = qw.data_ptr();
+  p.sc = sc.data_ptr();
+  p.x = x.data_ptr();
+  p.delta = cptr(delta);
+  p.norm_w = cptr(norm_w);
+  p.resid_out = mptr(resid_out);
+  p.out = out.data_ptr();
+  p.bias = cptr(bias);
+  p.out_add = cptr(out_add);
+  p.M = (int)x.size(0);
+  p.N = (int)N;
+  p.K = (int)qw.size(1) * 64;
+  p.Kx = (int)Kx;
+  p.ldx = (int)x.stride(0);
+  p.ldo = (int)out.stride(0);
+  p.gs_shift = log2i(gs);
+  p.eps = (float)eps;
+  p.act = (int)act;
+  p.mode = 0;
+  TORCH_CHECK(qw.size(0) * 16 >= N && x.size(1) >= Kx);
+  if (delta.has_value() && delta->defined()) TORCH_CHECK(delta->stride(0) == x.stride(0));
+  check(mmb_fp4_gemv(&p, cur_stream()), "fp4_gemv");
+}
+
+// mode 1: gate-up for every (token, slot); x [T, Kx]; out [T * S, N or N/2].
+// mode 2: down; x [T * S, Kx]; out [T, N].
+void fp4_moe_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t Kx, int64_t gs,
+                  int64_t mode, const Tensor& ids, const OptT& weights, int64_t n_shared, int64_t shared_base,
+                  const OptT& norm_w, double eps, int64_t act, const OptT& out_add) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(qw.dim() == 5 && qw.is_contiguous() && sc.is_contiguous(), "expert bank must be [E, N/16, K/64, 32, 4]");
+  TORCH_CHECK(ids.scalar_type() == at::kInt && ids.dim() == 2 && ids.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbFp4GemvParams p{};
+  p.qw = qw.data_ptr();
+  p.sc = sc.data_ptr();
+  p.x = x.data_ptr();
+  p.norm_w = cptr(norm_w);
+  p.out = out.data_ptr();
+  p.out_add = cptr(out_add);
+  p.M = (int)ids.size(0);
+  p.N = (int)N;
+  p.K = (int)qw.size(2) * 64;
+  p.Kx = (int)Kx;
+  p.ldx = (int)x.stride(0);
+  p.ldo = (int)out.stride(0);
+  p.gs_shift = log2i(gs);
+  p.eps = (float)eps;
+  p.act = (int)act;
+  p.mode = (int)mode;
+  p.expert_ids = ids.data_ptr<int>();
+  if (weights.has_value() && weights->defined()) {
+    TORCH_CHECK(weights->scalar_type() == at::kFloat && weights->is_contiguous());
+    p.expert_w = weights->data_ptr<float>();
+  }
+  p.topk = (int)ids.size(1);
+  p.n_shared = (int)n_shared;
+  p.shared_base = (int)shared_base;
+  p.expert_stride_q = qw.stride(0) / 4;     // int32 elements -> 16-byte units
+  p.expert_stride_s = sc.stride(0) / 2;     // fp16 elements -> 4-byte units
+  TORCH_CHECK(mode == 1 || mode == 2);
+  TORCH_CHECK(mode != 2 || p.expert_w != nullptr, "down projection needs routing weights");
+  const int S = p.topk + p.n_shared;
+  if (mode == 1) {
+    TORCH_CHECK(x.size(0) == p.M && out.size(0) == (int64_t)p.M * S);
+  } else {
+    TORCH_CHECK(x.size(0) == (int64_t)p.M * S && out.size(0) == p.M);
+  }
+  check(mmb_fp4_gemv(&p, cur_stream()), "fp4_moe_gemv");
+}
+
+void bf16_gemv(const Tensor& x, const Tensor& w, Tensor out, const OptT& delta, const OptT& norm_w, double eps) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  TORCH_CHECK(w.is_contiguous() && x.stride(1) == 1 && out.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbBf16GemvParams p{};
+  p.w = w.data_ptr();
+  p.x = x.data_ptr();
+  p.delta = cptr(delta);
+  p.norm_w = cptr(norm_w);
+  p.out = out.data_ptr();
+  p.M = (int)x.size(0);
+  p.N = (int)w.size(0);
+  p.K = (int)w.size(1);
+  p.ldx = (int)x.stride(0);
+  p.ldo = (int)out.stride(0);
+  p.eps = (float)eps;
+  p.out_f32 = out.scalar_type() == at::kFloat;
+  TORCH_CHECK(p.out_f32 || out.scalar_type() == at::kBFloat16);
+  check(mmb_bf16_gemv(&p, cur_stream()), "bf16_gemv");
+}
+
+void rmsnorm(const Tensor& x, const OptT& delta, const OptT& w, Tensor out, const OptT& resid_out, double eps) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(mmb_rmsnorm(x.data_ptr(), cptr(delta), cptr(w), out.data_ptr(), mptr(resid_out), (int)x.size(0), (int)x.size(1),
+                    (int)x.stride(0), (int)out.stride(0), (float)eps, cur_stream()),
+        "rmsnorm");
+}
+
+void silu_mul(const Tensor& gate_up, Tensor out) {
+  check_bf16(gate_up, "gate_up");
+  TORCH_CHECK(gate_up.is_contiguous() && out.is_contiguous());
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  check(mmb_silu_mul(gate_up.data_ptr(), out.data_ptr(), (int)gate_up.size(0), (int)gate_up.size(1) / 2, cur_stream()),
+        "silu_mul");
+}
+
+void add(const Tensor& a, const Tensor& b, Tensor out) {
+  check_bf16(a, "a");
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && out.is_contiguous());
+  c10::cuda::CUDAGuard guard(a.device());
+  check(mmb_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), cur_stream()), "add");
+}
+
+void embedding(const Tensor& table, const Tensor& ids, Tensor out) {
+  check_bf16(table, "table");
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && table.is_contiguous() && out.is_contiguous());
+  c10::cuda::CUDAGuard guard(table.device());
+  check(mmb_embedding(table.data_ptr(), ids.data_ptr<int64_t>(), out.data_ptr(), (int)ids.numel(), (int)table.size(1),
+                      cur_stream()),
+        "embedding");
+}
+
+void rope(Tensor q, const OptT& k, const Tensor& positions, const Tensor& inv_freq, int64_t Hq, int64_t Hk, int64_t D,
+          int64_t rot_dim, bool interleaved, double mscale) {
+  check_bf16(q, "q");
+  TORCH_CHECK(positions.scalar_type() == at::kInt && inv_freq.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(q.device());
+  const int T = (int)positions.numel();
+  check(mmb_rope(q.data_ptr(), mptr(k), positions.data_ptr<int>(), inv_freq.data_ptr<float>(), T, (int)Hq, (int)Hk, (int)D,
+                 (int)rot_dim, (int)q.stride(0), k.has_value() && k->defined() ? (int)k->stride(0) : 0, interleaved ? 1 : 0,
+                 (float)mscale, cur_stream()),
+        "rope");
+}
+
+void qk_norm_rope_cache(Tensor q, const Tensor& k, const Tensor& v, const OptT& qn_w, const OptT& kn_w,
+                        const Tensor& positions, const Tensor& inv_freq, const Tensor& slots, Tensor k_pool, Tensor v_pool,
+                        int64_t Hq, int64_t Hk, int64_t D, double eps, bool interleaved) {
+  check_bf16(q, "q");
+  TORCH_CHECK(q.stride(0) == k.stride(0) && q.stride(0) == v.stride(0));
+  TORCH_CHECK(positions.scalar_type() == at::kInt && slots.scalar_type() == at::kLong);
+  c10::cuda::CUDAGuard guard(q.device());
+  check(mmb_qk_norm_rope_cache(q.data_ptr(), k.data_ptr(), v.data_ptr(), cptr(qn_w), cptr(kn_w), positions.data_ptr<int>(),
+                               inv_freq.data_ptr<float>(), slots.data_ptr<int64_t>(), k_pool.data_ptr(), v_pool.data_ptr(),
+                               (int)positions.numel(), (int)Hq, (int)Hk, (int)D, (int)q.stride(0), (float)eps,
+                               interleaved ? 1 : 0, cur_stream()),
+        "qk_norm_rope_cache");
+}
+
+void mla_prep(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
+              const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, int64_t H, int64_t dn, int64_t dr,
+              int64_t R, double eps, double mscale, bool interleaved) {
+  check_bf16(q, "q");
+  check_bf16(kva, "kva");
+  check_bf16(w_ukT, "w_ukT");
+  TORCH_CHECK(w_ukT.is_contiguous() && q_full.is_contiguous() && cache.is_contiguous());
+  TORCH_CHECK(positions.scalar_type() == at::kInt && slots.scalar_type() == at::kLong);
+  c10::cuda::CUDAGuard guard(q.device());
+  MmbMlaPrepParams p{};
+  p.q = q.data_ptr();
+  p.kva = kva.data_ptr();
+  p.w_ukT = w_ukT.data_ptr();
+  p.kv_norm_w = kv_norm_w.data_ptr();
+  p.positions = positions.data_ptr<int>();
+  p.inv_freq = inv_freq.data_ptr<float>();
+  p.slots = slots.data_ptr<int64_t>();
+  p.q_full = q_full.data_ptr();
+  p.cache = cache.data_ptr();
+  p.T = (int)positions.numel();
+  p.H = (int)H;
+  p.dn = (int)dn;
+  p.dr = (int)dr;
+  p.R = (int)R;
+  p.ld_q = (int)q.stride(0);
+  p.ld_kva = (int)kva.stride(0);
+  p.eps = (float)eps;
+  p.mscale = (float)mscale;
+  p.interleaved = interleaved ? 1 : 0;
+  check(mmb_mla_prep(&p, cur_stream()), "mla_prep");
+}
+
+void paged_decode(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& block_tables,
+                  const Tensor& ctx_lens, Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk, int64_t dv,
+                  int64_t block_size, int64_t splits, double scale, int64_t window) {
+  check_bf16(q, "q");
+  check_bf16(k_pool, "k_pool");
+  TORCH_CHECK(q.is_contiguous() && k_pool.is_contiguous() && block_tables.is_contiguous() && block_tables.dim() == 2);
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && ctx_lens.scalar_type() == at::kInt);
+  TORCH_CHECK(part_o.scalar_type() == at::kFloat && part_ml.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(q.device());
+  MmbPagedDecodeParams p{};
+  p.q = q.data_ptr();
+  p.k_pool = k_pool.data_ptr();
+  p.v_pool = cptr(v_pool);
+  p.block_tables = block_tables.data_ptr<int>();
+  p.ctx_lens = ctx_lens.data_ptr<int>();
+  p.part_o = part_o.data_ptr<float>();
+  p.part_ml = part_ml.data_ptr<float>();
+  p.B = (int)ctx_lens.numel();
+  p.Hq = (int)Hq;
+  p.Hkv = (int)Hkv;
+  p.dqk = (int)dqk;
+  p.dv = (int)dv;
+  p.block_size = (int)block_size;
+  p.max_blocks = (int)block_tables.size(1);
+  p.splits = (int)splits;
+  p.scale = (float)scale;
+  p.window = (int)window;
+  TORCH_CHECK(part_o.numel() >= (int64_t)p.B * Hq * splits * dv && part_ml.numel() >= (int64_t)p.B * Hq * splits * 2);
+  check(mmb_paged_decode(&p, cur_stream()), "paged_decode");
+}
+
+void decode_merge(const Tensor& part_o, const Tensor& part_ml, const OptT& w_uv, Tensor out, int64_t B, int64_t Hq,
+                  int64_t dv, int64_t dvo, int64_t splits) {
+  c10::cuda::CUDAGuard guard(part_o.device());
+  check(mmb_decode_merge(part_o.data_ptr<float>(), part_ml.data_ptr<float>(), cptr(w_uv), out.data_ptr(), (int)B, (int)Hq,
+                         (int)dv, (int)dvo, (int)splits, cur_stream()),
+        "decode_merge");
+}
+
+void moe_router(const Tensor& x, const Tensor& w, const OptT& delta, const OptT& norm_w, const OptT& resid_out,
+                const OptT& bias, Tensor ids, Tensor weights, const OptT& logits_out, const OptT& counts, int64_t topk,
+                double eps, int64_t scoring, bool renorm, double routed_scale, int64_t n_group, int64_t topk_group) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous() && ids.is_contiguous() && weights.is_contiguous());
+  TORCH_CHECK(ids.scalar_type() == at::kInt && weights.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbRouterParams p{};
+  p.w = w.data_ptr();
+  p.x = x.data_ptr();
+  p.delta = cptr(delta);
+  p.norm_w = cptr(norm_w);
+  p.resid_out = mptr(resid_out);
+  p.bias = (bias.has_value() && bias->defined()) ? bias->data_ptr<float>() : nullptr;
+  p.ids = ids.data_ptr<int>();
+  p.weights = weights.data_ptr<float>();
+  p.logits_out = (logits_out.has_value() && logits_out->defined()) ? logits_out->data_ptr<float>() : nullptr;
+  p.counts = (counts.has_value() && counts->defined()) ? counts->data_ptr<int>() : nullptr;
+  p.T = (int)x.size(0);
+  p.E = (int)w.size(0);
+  p.K = (int)w.size(1);
+  p.topk = (int)topk;
+  p.eps = (float)eps;
+  p.scoring = (int)scoring;
+  p.renorm = renorm ? 1 : 0;
+  p.routed_scale = (float)routed_scale;
+  p.n_group = (int)n_group;
+  p.topk_group = (int)topk_group;
+  check(mmb_moe_router(&p, cur_stream()), "moe_router");
+}
+
+void sample(const Tensor& logits, Tensor out_ids, const OptT& out_logprob, const OptT& temperature, const OptT& top_k,
+            const OptT& top_p, const OptT& min_p, const OptT& history, const OptT& rep_penalty, int64_t seed,
+            int64_t offset) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.is_contiguous() && logits.dim() == 2);
+  TORCH_CHECK(out_ids.scalar_type() == at::kLong);
+  c10::cuda::CUDAGuard guard(logits.device());
+  MmbSampleParams p{};
+  p.logits = logits.data_ptr<float>();
+  p.out_ids = out_ids.data_ptr<int64_t>();
+  auto fp = [](const OptT& t) -> const float* { return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr; };
+  p.out_logprob = (out_logprob.has_value() && out_logprob->defined()) ? out_logprob->data_ptr<float>() : nullptr;
+  p.temperature = fp(temperature);
+  p.top_k = (top_k.has_value() && top_k->defined()) ? top_k->data_ptr<int>() : nullptr;
+  p.top_p = fp(top_p);
+  p.min_p = fp(min_p);
+  p.rep_penalty = fp(rep_penalty);
+  if (history.has_value() && history->defined()) {
+    TORCH_CHECK(history->scalar_type() == at::kLong && history->is_contiguous() && history->dim() == 2);
+    p.history = history->data_ptr<int64_t>();
+    p.hist_len = (int)history->size(1);
+  }
+  p.B = (int)logits.size(0);
+  p.V = (int)logits.size(1);
+  p.seed = (unsigned long long)seed;
+  p.offset = (unsigned long long)offset;
+  check(mmb_sample(&p, cur_stream()), "sample");
+}
+
+void argmax(const Tensor& logits, Tensor out) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.is_contiguous() && logits.dim() == 2);
+  c10::cuda::CUDAGuard guard(logits.device());
+  check(mmb_argmax(logits.data_ptr<float>(), out.data_ptr<int64_t>(), (int)logits.size(0), (int)logits.size(1), cur_stream()),
+        "argmax");
+}
+
+// ---- tcgen05 GEMM (prefill / large M)
+void fp4_gemm(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && qw.is_contiguous() && sc.is_contiguous());
+  TORCH_CHECK(status.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbFp4GemmParams p{};
+  p.x = x.data_ptr();
+  p.qw = qw.data_ptr();
+  p.sc = sc.data_ptr();
+  p.out = out.data_ptr();
+  p.M = (int)x.size(0);
+  p.N = (int)N;
+  p.K = (int)qw.size(1) * 64;
+  p.Kx = (int)x.size(1);
+  p.ldo = (int)out.stride(0);
+  p.gs_shift = log2i(gs);
+  p.status = status.data_ptr<int>();
+  check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm");
+}
+
+}  // namespace
+
+TORCH_LIBRARY(mmb200, m) {
+  m.def("fp4_gemv", &fp4_gemv);
+  m.def("fp4_moe_gemv", &fp4_moe_gemv);
+  m.def("bf16_gemv", &bf16_gemv);
+  m.def("rmsnorm", &rmsnorm);
+  m.def("silu_mul", &silu_mul);
+  m.def("add", &add);
+  m.def("embedding", &embedding);
+  m.def("rope", &rope);
+  m.def("qk_norm_rope_cache", &qk_norm_rope_cache);
+  m.def("mla_prep", &mla_prep);
+  m.def("paged_decode", &paged_decode);
+  m.def("decode_merge", &decode_merge);
+  m.def("moe_router", &moe_router);
+  m.def("sample", &sample);
+  m.def("argmax", &argmax);
+  m.def("fp4_gemm", &fp4_gemm);
+}

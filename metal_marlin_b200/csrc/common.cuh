@@ -1,0 +1,108 @@
+// Shared device helpers for the sm_100a kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MMB_API extern "C" __attribute__((visibility("default")))
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+namespace mmb {
+
+constexpr int kWarp = 32;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; `red` is >= 32 floats of shared memory.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+// 16-byte streaming load that does not pollute L1 (weights are read once per step).
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t hi16) { return __uint_as_float(hi16 << 16); }
+
+// m16n8k16, fp16 inputs, fp32 accumulate.
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// m16n8k16, bf16 inputs, fp32 accumulate.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Expand the eight E2M1 nibbles of a tile-layout word into the four fp16x2 registers of an
+// m16n8k16 A fragment.  The fp16 values equal e2m1 * 2^-14 (the exponent field is used
+// as-is, so code 1 lands on an fp16 subnormal); the caller folds 2^14 into the group scale.
+__device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t q, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) {
+  a0 = (q & 0x80008000u) | ((q & 0x70007000u) >> 3);
+  q <<= 4;
+  a1 = (q & 0x80008000u) | ((q & 0x70007000u) >> 3);
+  q <<= 4;
+  a2 = (q & 0x80008000u) | ((q & 0x70007000u) >> 3);
+  q <<= 4;
+  a3 = (q & 0x80008000u) | ((q & 0x70007000u) >> 3);
+}
+constexpr float kE2M1F16Rescale = 16384.0f;  // 2^14
+
+// Same nibbles to bf16x2 holding e2m1 * 2^-126 (bf16 subnormal trick).
+__device__ __forceinline__ void e2m1x8_to_bf16x2_raw(uint32_t q, uint32_t& a0, uint32_t& a1, uint32_t& a2,
+                                                     uint32_t& a3) {
+  a0 = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+  q <<= 4;
+  a1 = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+  q <<= 4;
+  a2 = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+  q <<= 4;
+  a3 = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+}  // namespace mmb

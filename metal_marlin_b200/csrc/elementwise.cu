@@ -1,0 +1,208 @@
+// Memory-bound elementwise / normalisation kernels: RMSNorm (+residual), SwiGLU, RoPE, the fused
+// per-head q/k norm + RoPE + paged K/V scatter, embedding gather.  One CTA per row, 16-byte
+// accesses where the row length allows, fp32 math, bf16 storage.
+#include "api.h"
+#include "common.cuh"
+
+namespace mmb {
+
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta,
+                                                      const bf16* __restrict__ w, bf16* __restrict__ out,
+                                                      bf16* __restrict__ resid_out, int dim, int ldx, int ldo,
+                                                      float eps) {
+  __shared__ float red[32];
+  extern __shared__ float row_s[];   // dim floats
+  const long long r = blockIdx.x;
+  const bf16* xr = x + r * ldx;
+  const bf16* dr = delta ? delta + r * ldx : nullptr;
+  float ss = 0.f;
+  for (int k = threadIdx.x * 2; k < dim; k += blockDim.x * 2) {
+    float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
+    if (dr) {
+      float2 d = __bfloat1622float2(*reinterpret_cast<const bf162*>(dr + k));
+      bf162 s2 = __floats2bfloat162_rn(v.x + d.x, v.y + d.y);
+      v = __bfloat1622float2(s2);
+      if (resid_out) *reinterpret_cast<bf162*>(resid_out + r * dim + k) = s2;
+    }
+    row_s[k] = v.x;
+    row_s[k + 1] = v.y;
+    ss += v.x * v.x + v.y * v.y;
+  }
+  ss = block_sum(ss, red);
+  const float rs = rsqrtf(ss / (float)dim + eps);
+  for (int k = threadIdx.x * 2; k < dim; k += blockDim.x * 2) {
+    float2 wv = w ? __bfloat1622float2(*reinterpret_cast<const bf162*>(w + k)) : make_float2(1.f, 1.f);
+    *reinterpret_cast<bf162*>(out + r * ldo + k) = __floats2bfloat162_rn(row_s[k] * rs * wv.x, row_s[k + 1] * rs * wv.y);
+  }
+}
+
+__global__ void silu_mul_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int inter) {
+  const long long r = blockIdx.y;
+  const int k = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (k >= inter) return;
+  float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(gu + r * 2 * inter + k));
+  float2 u = __bfloat1622float2(*reinterpret_cast<const bf162*>(gu + r * 2 * inter + inter + k));
+  *reinterpret_cast<bf162*>(out + r * inter + k) = __floats2bfloat162_rn(silu(g.x) * u.x, silu(g.y) * u.y);
+}
+
+__global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ out, long long n) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (i + 1 < n) {
+    float2 x = __bfloat1622float2(*reinterpret_cast<const bf162*>(a + i));
+    float2 y = __bfloat1622float2(*reinterpret_cast<const bf162*>(b + i));
+    *reinterpret_cast<bf162*>(out + i) = __floats2bfloat162_rn(x.x + y.x, x.y + y.y);
+  } else if (i < n) {
+    out[i] = __float2bfloat16(__bfloat162float(a[i]) + __bfloat162float(b[i]));
+  }
+}
+
+__global__ void embedding_kernel(const bf16* __restrict__ table, const int64_t* __restrict__ ids, bf16* __restrict__ out,
+                                 int dim) {
+  const long long r = blockIdx.x;
+  const long long id = ids[r];
+  const uint4* src = reinterpret_cast<const uint4*>(table + id * dim);
+  uint4* dst = reinterpret_cast<uint4*>(out + r * dim);
+  for (int k = threadIdx.x; k < dim / 8; k += blockDim.x) dst[k] = src[k];
+}
+
+__device__ __forceinline__ void rope_pair(float& a, float& b, float c, float s) {
+  const float x = a * c - b * s, y = b * c + a * s;
+  a = x;
+  b = y;
+}
+
+// One CTA per token; threads loop over (head, pair).
+__global__ void rope_kernel(bf16* __restrict__ q, bf16* __restrict__ k, const int* __restrict__ positions,
+                            const float* __restrict__ inv_freq, int Hq, int Hk, int D, int rot_dim, int ldq, int ldk,
+                            int interleaved, float mscale) {
+  const long long tkn = blockIdx.x;
+  const float pos = (float)positions[tkn];
+  const int half = rot_dim / 2;
+  const int total = (Hq + Hk) * half;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int h = i / half, j = i % half;
+    bf16* base = (h < Hq) ? (q + tkn * ldq + (long long)h * D) : (k + tkn * ldk + (long long)(h - Hq) * D);
+    float sn, cs;
+    sincosf(pos * inv_freq[j], &sn, &cs);
+    sn *= mscale;
+    cs *= mscale;
+    const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+    float a = __bfloat162float(base[ia]), b = __bfloat162float(base[ib]);
+    rope_pair(a, b, cs, sn);
+    base[ia] = __float2bfloat16(a);
+    base[ib] = __float2bfloat16(b);
+  }
+}
+
+// Qwen3-style attention prologue: per-head RMSNorm of q and k (optional), RoPE, K/V scatter to a paged
+// pool [num_slots, Hk, D].  grid = (T, Hq + Hk); one warp-sized CTA per (token, head); D <= 256.
+__global__ void __launch_bounds__(128) qk_norm_rope_cache_kernel(bf16* __restrict__ q, const bf16* __restrict__ k,
+                                                                 const bf16* __restrict__ v, const bf16* __restrict__ qn_w,
+                                                                 const bf16* __restrict__ kn_w,
+                                                                 const int* __restrict__ positions,
+                                                                 const float* __restrict__ inv_freq,
+                                                                 const int64_t* __restrict__ slots, bf16* __restrict__ k_pool,
+                                                                 bf16* __restrict__ v_pool, int Hq, int Hk, int D, int ldqkv,
+                                                                 float eps, int interleaved) {
+  __shared__ float red[32];
+  __shared__ float vals[256];
+  const long long tkn = blockIdx.x;
+  const int h = blockIdx.y;
+  const bool is_q = h < Hq;
+  const bf16* src = is_q ? (q + tkn * ldqkv + (long long)h * D) : (k + tkn * ldqkv + (long long)(h - Hq) * D);
+  const bf16* nw = is_q ? qn_w : kn_w;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float x = __bfloat162float(src[i]);
+    vals[i] = x;
+    ss += x * x;
+  }
+  ss = block_sum(ss, red);
+  if (nw != nullptr) {
+    const float rs = rsqrtf(ss / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x)
+      vals[i] = __bfloat162float(__float2bfloat16(vals[i] * rs * __bfloat162float(nw[i])));
+  }
+  __syncthreads();
+  const float pos = (float)positions[tkn];
+  const int half = D / 2;
+  const long long slot = slots ? slots[tkn] : -1;
+  bf16* dst;
+  if (is_q) dst = q + tkn * ldqkv + (long long)h * D;
+  else dst = (slot >= 0) ? k_pool + (slot * Hk + (h - Hq)) * (long long)D : nullptr;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float sn, cs;
+    sincosf(pos * inv_freq[j], &sn, &cs);
+    const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+    float a = vals[ia], b = vals[ib];
+    rope_pair(a, b, cs, sn);
+    if (dst) {
+      dst[ia] = __float2bfloat16(a);
+      dst[ib] = __float2bfloat16(b);
+    }
+  }
+  if (!is_q && slot >= 0 && v != nullptr) {
+    const bf16* vs = v + tkn * ldqkv + (long long)(h - Hq) * D;
+    bf16* vd = v_pool + (slot * Hk + (h - Hq)) * (long long)D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) vd[i] = vs[i];
+  }
+}
+
+}  // namespace mmb
+
+MMB_API int mmb_rmsnorm(const void* x, const void* delta, const void* w, void* out, void* resid_out, int rows, int dim,
+                        int ldx, int ldo, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dim % 2 != 0 || dim * 4 > 160 * 1024) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)dim * 4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(mmb::rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  mmb::rmsnorm_kernel<<<rows, 256, smem, stream>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w, (bf16*)out,
+                                                   (bf16*)resid_out, dim, ldx, ldo, eps);
+  return (int)cudaGetLastError();
+}
+
+MMB_API int mmb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (inter % 2 != 0) return (int)cudaErrorInvalidValue;
+  dim3 grid((inter / 2 + 255) / 256, rows);
+  mmb::silu_mul_kernel<<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
+  return (int)cudaGetLastError();
+}
+
+MMB_API int mmb_add(const void* a, const void* b, void* out, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const long long pairs = (n + 1) / 2;
+  mmb::add_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, stream>>>((const bf16*)a, (const bf16*)b, (bf16*)out, n);
+  return (int)cudaGetLastError();
+}
+
+MMB_API int mmb_embedding(const void* table, const int64_t* ids, void* out, int n, int dim, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dim % 8 != 0) return (int)cudaErrorInvalidValue;
+  mmb::embedding_kernel<<<n, 128, 0, stream>>>((const bf16*)table, ids, (bf16*)out, dim);
+  return (int)cudaGetLastError();
+}
+
+MMB_API int mmb_rope(void* q, void* k, const int* positions, const float* inv_freq, int T, int Hq, int Hk, int D,
+                     int rot_dim, int ldq, int ldk, int interleaved, float mscale, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  mmb::rope_kernel<<<T, 256, 0, stream>>>((bf16*)q, (bf16*)k, positions, inv_freq, Hq, k ? Hk : 0, D, rot_dim, ldq, ldk,
+                                          interleaved, mscale);
+  return (int)cudaGetLastError();
+}
+
+MMB_API int mmb_qk_norm_rope_cache(void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
+                                   const int* positions, const float* inv_freq, const int64_t* slots, void* k_pool,
+                                   void* v_pool, int T, int Hq, int Hk, int D, int ldqkv, float eps, int interleaved,
+                                   cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D > 256 || D % 2) return (int)cudaErrorInvalidValue;
+  dim3 grid(T, Hq + Hk);
+  mmb::qk_norm_rope_cache_kernel<<<grid, 128, 0, stream>>>((bf16*)q, (const bf16*)k, (const bf16*)v, (const bf16*)qn_w,
+                                                           (const bf16*)kn_w, positions, inv_freq, slots, (bf16*)k_pool,
+                                                           (bf16*)v_pool, Hq, Hk, D, ldqkv, eps, interleaved);
+  return (int)cudaGetLastError();
+}

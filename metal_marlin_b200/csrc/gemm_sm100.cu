@@ -1,0 +1,490 @@
+// tcgen05 GEMM for sm_100a: out[M, N] = x[M, K] * W^T with fp32 accumulators in tensor memory.
+//
+// Orientation: the weight tile is the MMA "A" operand (128 output features = 128 TMEM lanes) and
+// the token tile is the "B" operand (TN = 32..256 tokens = TMEM columns), so the same kernel serves
+// batch-32 decode (TN = 32) and long prefill (TN = 256) without wasting the M = 128 instruction shape.
+//
+// CTA = 6 warps:
+//   warp 0      TMA producer: x tile [TN x 64] bf16, 128-byte swizzle, one bulk tensor copy per stage
+//               (bf16-weight variant: also the W tile)
+//   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits stages back to the
+//               producers through mbarriers
+//   warps 2..5  FP4 variant: stream tile-layout weight blocks from global memory (one 16-byte load per
+//               lane per 16x64 block), expand E2M1 -> bf16 with the group scale in registers and
+//               store them into the 128-byte-swizzled K-major A tile; afterwards the same four warps
+//               run the epilogue (tcgen05.ld of their 32-lane TMEM quarter, bf16 stores).
+// Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records a code in
+// status[0], skips the remaining work, still frees its TMEM and returns.
+#include <cuda.h>
+
+#include "api_gemm.h"
+#include "common.cuh"
+
+namespace mmb {
+
+constexpr int kBK = 64;                 // K elements per stage (one 128-byte swizzle row of bf16)
+constexpr int kTileRows = 128;          // output features per CTA
+constexpr int kGemmThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
+
+// ------------------------------------------------------------------------------------------ PTX
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when the limit expired or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    }
+  }
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
+      "[%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte swizzle shared-memory matrix descriptor: rows are 128 bytes, 8-row groups are
+// 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell), layout type 2.
+__device__ __forceinline__ uint64_t make_sw128_desc(const void* smem_tile) {
+  const uint64_t addr = (uint64_t)((smem_u32(smem_tile) & 0x3FFFFu) >> 4);
+  return addr | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = tn.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int tn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
+}
+
+template <int TN>
+struct GemmCfg {
+  static constexpr int kStages = (TN <= 128) ? 6 : 4;
+  static constexpr int a_bytes = kTileRows * kBK * 2;      // 16 KB
+  static constexpr int b_bytes = TN * kBK * 2;
+  static constexpr int stage_bytes = a_bytes + b_bytes;
+  static constexpr int tmem_cols = (TN < 32) ? 32 : TN;
+  static constexpr size_t smem_bytes = (size_t)kStages * stage_bytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+struct PipeShared {
+  uint64_t full_a[6];
+  uint64_t full_b[6];
+  uint64_t empty[6];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// WFMT 0: FP4 tile-layout weights expanded by warps 2..5.  WFMT 1: bf16 weights fetched by TMA.
+template <int TN, int WFMT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+            const MmbFp4GemmParams p, const MmbBf16GemmParams pb) {
+  using Cfg = GemmCfg<TN>;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  PipeShared* ps = reinterpret_cast<PipeShared*>(tiles + (size_t)Cfg::kStages * Cfg::stage_bytes);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- problem decode
+  const int M = WFMT == 0 ? p.M : pb.M, N = WFMT == 0 ? p.N : pb.N, K = WFMT == 0 ? p.K : pb.K;
+  int* status = WFMT == 0 ? p.status : pb.status;
+  const int n0 = blockIdx.x * kTileRows;
+  int tok0 = blockIdx.y * TN, tok_rows = TN, expert = 0;
+  const int batch = blockIdx.z;
+  if (WFMT == 0 && p.tile_expert != nullptr) {
+    if ((int)blockIdx.y >= *p.n_tiles) return;
+    expert = p.tile_expert[blockIdx.y];
+    tok0 = p.tile_row0[blockIdx.y];
+    tok_rows = p.tile_rows[blockIdx.y];
+  }
+  const int KB = K / kBK;
+
+  if (tid == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&ps->full_a[s], WFMT == 0 ? 4 : 1);
+      mbar_init(&ps->full_b[s], 1);
+      mbar_init(&ps->empty[s], 1);
+    }
+    mbar_init(&ps->acc_full, 1);
+    ps->abort_flag = 0;
+    fence_proxy_async_smem();
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&ps->tmem_base, Cfg::tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ps->tmem_base;
+  volatile int* abort_flag = &ps->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int i = 0; i < KB; ++i) {
+        const int s = i % Cfg::kStages;
+        const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
+        if (!mbar_wait(&ps->empty[s], ph ^ 1u, abort_flag)) {
+          if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 1);
+          break;
+        }
+        unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
+        unsigned char* b_tile = a_tile + Cfg::a_bytes;
+        if (WFMT == 0) {
+          mbar_expect_tx(&ps->full_b[s], Cfg::b_bytes);
+          tma_load_2d(b_tile, &tmap_x, &ps->full_b[s], i * kBK, tok0);
+        } else {
+          mbar_expect_tx(&ps->full_b[s], Cfg::b_bytes);
+          tma_load_3d(b_tile, &tmap_x, &ps->full_b[s], i * kBK, tok0, pb.x_batch_stride ? batch : 0);
+          mbar_expect_tx(&ps->full_a[s], Cfg::a_bytes);
+          tma_load_3d(a_tile, &tmap_w, &ps->full_a[s], i * kBK, n0, pb.w_batch_stride ? batch : 0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TN < 16 ? 16 : TN);
+      bool ok = true;
+      for (int i = 0; i < KB && ok; ++i) {
+        const int s = i % Cfg::kStages;
+        const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
+        ok = mbar_wait(&ps->full_a[s], ph, abort_flag) && mbar_wait(&ps->full_b[s], ph, abort_flag);
+        if (!ok) {
+          if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 2);
+          break;
+        }
+        tc_fence_after();
+        unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
+        const uint64_t adesc = make_sw128_desc(a_tile);
+        const uint64_t bdesc = make_sw128_desc(a_tile + Cfg::a_bytes);
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k)
+          umma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (uint32_t)((i | k) != 0));
+        umma_commit(&ps->empty[s]);     // frees the stage once these MMAs have read it
+      }
+      if (ok) umma_commit(&ps->acc_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ weight expansion (FP4) + epilogue
+    const int dw = warp - 2;            // 0..3
+    bool ok = true;
+    if (WFMT == 0) {
+      const int g = lane >> 2, t = lane & 3;
+      const int KC = K >> 6;
+      const int NG = K >> p.gs_shift;
+      const int n_rt = (N + 15) >> 4;
+      const uint4* qw = reinterpret_cast<const uint4*>(p.qw) + (long long)expert * p.expert_stride_q;
+      const uint32_t* sc = reinterpret_cast<const uint32_t*>(p.sc) + (long long)expert * p.expert_stride_s;
+      const int rt_base = (n0 >> 4) + dw * 2;
+      uint4 wnext[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int rt = rt_base + j;
+        wnext[j] = (rt < n_rt && KB > 0) ? ldg_stream(qw + ((long long)rt * KC) * 32 + lane) : make_uint4(0, 0, 0, 0);
+      }
+      for (int i = 0; i < KB; ++i) {
+        const int s = i % Cfg::kStages;
+        const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
+        uint4 wcur[2] = {wnext[0], wnext[1]};
+        if (i + 1 < KB) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int rt = rt_base + j;
+            if (rt < n_rt) wnext[j] = ldg_stream(qw + ((long long)rt * KC + (i + 1)) * 32 + lane);
+          }
+        }
+        if (!mbar_wait(&ps->empty[s], ph ^ 1u, abort_flag)) {
+          if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 3);
+          ok = false;
+          break;
+        }
+        unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int rt = rt_base + j;
+          const uint32_t qq[4] = {wcur[j].x, wcur[j].y, wcur[j].z, wcur[j].w};
+          const int row_lo = (dw * 2 + j) * 16 + g;           // row inside the 128-row tile (and row_lo + 8)
+          unsigned char* r0 = a_tile + row_lo * 128;
+          unsigned char* r1 = r0 + 8 * 128;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const int kabs = i * kBK + ks * 16;
+            const int grp = kabs >> p.gs_shift;
+            uint32_t sw = 0u;     // (scale row g, scale row g+8) as half2; L1-resident reload per k16 step
+            if (rt < n_rt) sw = __ldg(sc + ((long long)rt * NG + grp) * 8 + g);
+            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sw));
+            // fold the 2^126 subnormal rescale into the scale when it cannot overflow bf16
+            uint32_t a0, a1, a2, a3;
+            e2m1x8_to_bf16x2_raw(qq[ks], a0, a1, a2, a3);
+            const bool fold = (fabsf(sf.x) < 2.f) && (fabsf(sf.y) < 2.f);
+            bf162 m_lo, m_hi;
+            if (fold) {
+              m_lo = __float2bfloat162_rn(sf.x * 8.507059173023462e37f);   // 2^126
+              m_hi = __float2bfloat162_rn(sf.y * 8.507059173023462e37f);
+            } else {
+              const bf162 big = __float2bfloat162_rn(8.507059173023462e37f);
+              *reinterpret_cast<bf162*>(&a0) = __hmul2(*reinterpret_cast<bf162*>(&a0), big);
+              *reinterpret_cast<bf162*>(&a1) = __hmul2(*reinterpret_cast<bf162*>(&a1), big);
+              *reinterpret_cast<bf162*>(&a2) = __hmul2(*reinterpret_cast<bf162*>(&a2), big);
+              *reinterpret_cast<bf162*>(&a3) = __hmul2(*reinterpret_cast<bf162*>(&a3), big);
+              m_lo = __float2bfloat162_rn(sf.x);
+              m_hi = __float2bfloat162_rn(sf.y);
+            }
+            // fragment registers: a0 = (row g, k 2t..), a1 = (row g+8, same k), a2 = (row g, k+8), a3 = (row g+8, k+8)
+            *reinterpret_cast<bf162*>(&a0) = __hmul2(*reinterpret_cast<bf162*>(&a0), m_lo);
+            *reinterpret_cast<bf162*>(&a1) = __hmul2(*reinterpret_cast<bf162*>(&a1), m_hi);
+            *reinterpret_cast<bf162*>(&a2) = __hmul2(*reinterpret_cast<bf162*>(&a2), m_lo);
+            *reinterpret_cast<bf162*>(&a3) = __hmul2(*reinterpret_cast<bf162*>(&a3), m_hi);
+            // 128-byte swizzle: 16-byte chunk index XOR (row % 8); row % 8 == g for both halves
+            const int c_lo = ((ks * 2) ^ g) * 16 + 4 * t;
+            const int c_hi = ((ks * 2 + 1) ^ g) * 16 + 4 * t;
+            *reinterpret_cast<uint32_t*>(r0 + c_lo) = a0;
+            *reinterpret_cast<uint32_t*>(r1 + c_lo) = a1;
+            *reinterpret_cast<uint32_t*>(r0 + c_hi) = a2;
+            *reinterpret_cast<uint32_t*>(r1 + c_hi) = a3;
+          }
+        }
+        fence_proxy_async_smem();       // generic-proxy stores -> visible to the tensor core (async proxy)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ps->full_a[s]);
+      }
+    }
+    // ---- epilogue: TMEM -> registers -> global
+    if (ok) ok = mbar_wait(&ps->acc_full, 0u, abort_flag);
+    if (!ok) {
+      if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 4);
+    } else {
+      tc_fence_after();
+      const int q = warp & 3;                    // TMEM lane quarter this warp may access
+      const int n = n0 + q * 32 + lane;
+      const int ldo = WFMT == 0 ? p.ldo : pb.ldo;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld_wait();
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int r = c0 + j;
+            if (r < tok_rows && tok0 + r < M) {
+              float f = __uint_as_float(v[j]);
+              if (WFMT == 0) {
+                if (p.row_scale) f *= p.row_scale[tok0 + r];
+                reinterpret_cast<bf16*>(p.out)[(long long)(tok0 + r) * ldo + n] = __float2bfloat16(f);
+              } else {
+                const long long o = (long long)batch * pb.out_batch_stride + (long long)(tok0 + r) * ldo + n;
+                if (pb.out_f32) reinterpret_cast<float*>(pb.out)[o] = f;
+                else reinterpret_cast<bf16*>(pb.out)[o] = __float2bfloat16(f);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  // ---- teardown: if something timed out give in-flight bulk copies time to land, then free TMEM
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// bf16 [batch, rows, cols] with row stride ld (elements); box = {64, box_rows, 1}, 128-byte swizzle, zero fill.
+static int make_tmap(CUtensorMap* map, const void* base, long long cols, long long rows, long long batch, long long ld,
+                     long long batch_stride, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16 != 0) return (int)cudaErrorInvalidValue;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(batch > 0 ? batch : 1)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch_stride > 0 ? batch_stride : rows * ld) * 2};
+  if (strides[1] % 16 != 0) return (int)cudaErrorInvalidValue;
+  cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+static int make_tmap_2d(CUtensorMap* map, const void* base, long long cols, long long rows, long long ld, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16 != 0) return (int)cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int TN, int WFMT>
+static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const MmbFp4GemmParams& p, const MmbBf16GemmParams& pb,
+                       dim3 grid, cudaStream_t stream) {
+  auto kern = gemm_kernel<TN, WFMT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<TN>::smem_bytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, GemmCfg<TN>::smem_bytes, stream>>>(mx, mw, p, pb);
+  return (int)cudaGetLastError();
+}
+
+static int pick_tn(int M, int forced) {
+  if (forced == 32 || forced == 64 || forced == 128 || forced == 256) return forced;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 1024) return 128;
+  return 256;
+}
+
+}  // namespace mmb
+
+MMB_API int mmb_fp4_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
+  using namespace mmb;
+  MmbFp4GemmParams p = *pp;
+  if (p.M <= 0 || p.N <= 0) return 0;
+  if (p.K % 64 != 0 || p.Kx % 8 != 0 || p.Kx > p.K || p.act != 0) return (int)cudaErrorInvalidValue;
+  const bool grouped = p.tile_expert != nullptr;
+  const int TN = pick_tn(grouped ? (p.token_tile ? p.token_tile : 128) : p.M, p.token_tile);
+  CUtensorMap mx;
+  int e = make_tmap_2d(&mx, p.x, p.Kx, p.M, p.Kx, TN);
+  if (e) return e;
+  MmbBf16GemmParams pb{};
+  dim3 grid((p.N + kTileRows - 1) / kTileRows, grouped ? p.max_tiles : (p.M + TN - 1) / TN, 1);
+  switch (TN) {
+    case 32: return launch_gemm<32, 0>(mx, mx, p, pb, grid, stream);
+    case 64: return launch_gemm<64, 0>(mx, mx, p, pb, grid, stream);
+    case 128: return launch_gemm<128, 0>(mx, mx, p, pb, grid, stream);
+    default: return launch_gemm<256, 0>(mx, mx, p, pb, grid, stream);
+  }
+}
+
+MMB_API int mmb_bf16_gemm(const MmbBf16GemmParams* pp, cudaStream_t stream) {
+  using namespace mmb;
+  MmbBf16GemmParams pb = *pp;
+  if (pb.M <= 0 || pb.N <= 0) return 0;
+  if (pb.K % 64 != 0 || pb.ldx % 8 != 0 || pb.ldw % 8 != 0) return (int)cudaErrorInvalidValue;
+  const int nb = pb.batch > 0 ? pb.batch : 1;
+  const int TN = pick_tn(pb.M, 0);
+  CUtensorMap mx, mw;
+  int e = make_tmap(&mx, pb.x, pb.K, pb.M, pb.x_batch_stride ? nb : 1, pb.ldx, pb.x_batch_stride, TN);
+  if (e) return e;
+  e = make_tmap(&mw, pb.w, pb.K, pb.N, pb.w_batch_stride ? nb : 1, pb.ldw, pb.w_batch_stride, kTileRows);
+  if (e) return e;
+  MmbFp4GemmParams p{};
+  dim3 grid((pb.N + kTileRows - 1) / kTileRows, (pb.M + TN - 1) / TN, nb);
+  switch (TN) {
+    case 32: return launch_gemm<32, 1>(mx, mw, p, pb, grid, stream);
+    case 64: return launch_gemm<64, 1>(mx, mw, p, pb, grid, stream);
+    case 128: return launch_gemm<128, 1>(mx, mw, p, pb, grid, stream);
+    default: return launch_gemm<256, 1>(mx, mw, p, pb, grid, stream);
+  }
+}
