@@ -1,0 +1,255 @@
+#!/usr/bin/env python
+"""Headline benchmark: GLM-4.7-Flash-architecture MMFP4 decode throughput on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--batch B] [--prompt-len P] [--impl ours|reference|eager]
+
+Workload (the reference's headline, ``README.md:23-24`` of RESMP-DEV/metal-marlin: GLM-4.7-Flash
+MMFP4 decode, 35.2 tok/s at batch 1): random-init weights of the GLM-4.7-Flash architecture
+RTN-quantized to MMFP4 (group 128), paged latent KV cache with 16-token blocks, a uniform-random
+prompt of ``--prompt-len`` tokens (default 4096) prefilled through the engine, then greedy decode.
+A step = one decode iteration of the whole batch (all layers, head, sampler).
+
+Timing: W untimed warm-up steps, then exactly K steps between CUDA events on the launching stream
+with a barrier + synchronize on both sides, max over ranks.  Each step streams ~2.3 GB of weights,
+far more than the 126 MB L2, so no explicit flush is needed (stated in ``config``).
+The ``e2e`` number drives the same steps through the public session API with, per step, a
+host->device copy of the step's input ids from pinned memory and a device->host read of the sampled ids.
+
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+BASELINE_TOK_S = 35.2   # reference headline (Apple M4 Max), README.md:23
+
+
+def _args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=1, help="sequences per model replica")
+    ap.add_argument("--prompt-len", type=int, default=4096)
+    ap.add_argument("--model", default="glm-4.7-flash")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "eager"])
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "tp", "dp"])
+    ap.add_argument("--extra", action="store_true", help="also measure batch 32 and prefill (TTFT)")
+    ap.add_argument("--seed", type=int, default=0)
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_arm(args):
+    """The reference package is Metal-only: its quantized kernels need Apple GPUs and its flagship model class
+    (metal_marlin/models/mmfp4_causal_lm.py) is absent from its own tree, so MMFP4Pipeline.from_pretrained cannot
+    construct the GLM-4.7-Flash model on this platform."""
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "reference is Apple-Metal only: MMFP4Pipeline.from_pretrained imports metal_marlin.models.mmfp4_causal_lm, "
+                      "which is missing from the reference tree, and its kernels are Metal shaders (no CUDA path)"}))
+    return 0
+
+
+def main():
+    args = _args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.engine.session import DecodeSession, SamplingParams
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM, prefill
+
+    cfg = get_preset(args.model)
+    block_size = 16
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    eager = args.impl == "eager"
+    t_build = time.time()
+    lm = MMFP4ForCausalLM.from_config(cfg, device=str(dev), seed=args.seed)
+    build_s = time.time() - t_build
+    if eager:
+        from metal_marlin_b200.baseline_eager import EagerBF16Model
+        eager_model = EagerBF16Model(lm.model)
+
+    def run_config(batch: int, steps: int, warmup: int, e2e: bool):
+        total_len = args.prompt_len + warmup + steps * (2 if e2e else 1) + 8
+        nb = (total_len + block_size - 1) // block_size
+        kv = lm.new_cache(batch * nb, block_size)
+        g = torch.Generator().manual_seed(args.seed + rank)
+        prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(batch)]
+        bt = torch.arange(batch * nb, dtype=torch.int32).view(batch, nb)
+        torch.cuda.synchronize(dev)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        if eager:
+            logits = eager_model.prefill(kv, prompts, bt)
+        else:
+            logits = prefill(lm.model, kv, prompts, bt)
+        ev1.record()
+        torch.cuda.synchronize(dev)
+        ttft_ms = ev0.elapsed_time(ev1)
+        model = eager_model if eager else lm.model
+        sess = DecodeSession(model, kv, batch, nb, max_new_tokens=0, max_ctx=total_len, use_graph=not eager)
+        sess.set_sampling([SamplingParams()] * batch)
+        sess.set_state(logits.argmax(-1), [args.prompt_len] * batch, bt)
+        l0 = ops.launch_count()
+        sess._step_body() if eager else sess.capture()
+        launches_per_step = (ops.launch_count() - l0) // (1 if eager else 3)
+        if eager:
+            sess.set_state(logits.argmax(-1), [args.prompt_len] * batch, bt)
+        for _ in range(warmup):
+            sess.step()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        time.sleep(0.3)
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        s0.record()
+        for _ in range(steps):
+            sess.step()
+        s1.record()
+        barrier()
+        ms = max_over_ranks(s0.elapsed_time(s1))
+        clocks = sampler.stop()
+        res = {"ms_per_step": ms / steps, "ttft_ms": max_over_ranks(ttft_ms), "launches_per_step": launches_per_step,
+               "clocks": clocks}
+        if e2e:
+            # public-API loop: pinned-host ids in, sampled ids out, every step
+            h_in = torch.empty(batch, dtype=torch.int64).pin_memory()
+            h_out = torch.empty(batch, dtype=torch.int64).pin_memory()
+            h_in.copy_(sess.out_ids.cpu())
+            barrier()
+            t0 = time.perf_counter()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                sess.ids.copy_(h_in, non_blocking=True)          # H2D: this step's input token ids
+                sess.step()
+                h_out.copy_(sess.out_ids, non_blocking=True)     # D2H: the step's result
+                torch.cuda.current_stream(dev).synchronize()
+                h_in.copy_(h_out)
+            e1.record()
+            barrier()
+            wall_ms = (time.perf_counter() - t0) * 1e3
+            res["e2e_ms_per_step"] = max_over_ranks(max(wall_ms, e0.elapsed_time(e1))) / steps
+            res["h2d_bytes_per_step"] = batch * 8
+            res["d2h_bytes_per_step"] = batch * 8
+        del sess, kv
+        torch.cuda.empty_cache()
+        return res
+
+    replicas = world      # data-parallel replicas of the model; each decodes its own batch
+    r = run_config(args.batch, args.steps, args.warmup, e2e=True)
+    tok_s = replicas * args.batch * 1e3 / r["ms_per_step"]
+    e2e_tok_s = replicas * args.batch * 1e3 / r["e2e_ms_per_step"]
+    out = {
+        "metric": f"glm47_flash_mmfp4_decode_tok_s_bs{args.batch}",
+        "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(tok_s / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
+        "impl": args.impl,
+        "config": {"model": f"{args.model} (random-init, RTN MMFP4 group 128)", "global_batch": replicas * args.batch,
+                   "seq_len": args.prompt_len, "parallelism": f"dp{world}" if world > 1 else "single",
+                   "kv": "paged latent MLA, 16-token blocks", "decode": "greedy, CUDA graph per step",
+                   "l2_policy": "inputs larger than L2 (each step streams >2 GB of weights)",
+                   "weights_gb": round(lm.model.weight_bytes() / 1e9, 2), "build_s": round(build_s, 1)},
+        "clocks": r["clocks"],
+        "e2e": {"value": round(e2e_tok_s, 2), "unit": "tok/s", "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": r["d2h_bytes_per_step"], "ms_per_step": round(r["e2e_ms_per_step"], 4)},
+        "gpu_launches": int(r["launches_per_step"] * args.steps),
+        "ttft_ms_p50": round(r["ttft_ms"], 2),
+    }
+    if args.extra:
+        r32 = run_config(32, max(8, args.steps // 2), max(3, args.warmup // 2), e2e=False)
+        out["extra"] = {"bs32_tok_s": round(replicas * 32 * 1e3 / r32["ms_per_step"], 1),
+                        "bs32_ms_per_step": round(r32["ms_per_step"], 4), "bs32_ttft_ms": round(r32["ttft_ms"], 1),
+                        "bs32_launches_per_step": r32["launches_per_step"]}
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -298,7 +298,7 @@ void moe_router(const Tensor& x, const Tensor& w, const OptT& delta, const OptT&
 
 void sample(const Tensor& logits, Tensor out_ids, const OptT& out_logprob, const OptT& temperature, const OptT& top_k,
             const OptT& top_p, const OptT& min_p, const OptT& history, const OptT& rep_penalty, int64_t seed,
-            int64_t offset) {
+            int64_t offset, const OptT& offset_dev) {
   TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.is_contiguous() && logits.dim() == 2);
   TORCH_CHECK(out_ids.scalar_type() == at::kLong);
   c10::cuda::CUDAGuard guard(logits.device());
@@ -321,6 +321,10 @@ void sample(const Tensor& logits, Tensor out_ids, const OptT& out_logprob, const
   p.V = (int)logits.size(1);
   p.seed = (unsigned long long)seed;
   p.offset = (unsigned long long)offset;
+  if (offset_dev.has_value() && offset_dev->defined()) {
+    TORCH_CHECK(offset_dev->scalar_type() == at::kLong);
+    p.offset_dev = offset_dev->data_ptr<int64_t>();
+  }
   check(mmb_sample(&p, cur_stream()), "sample");
 }
 
@@ -353,9 +357,74 @@ void fp4_gemm(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, i
   check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm");
 }
 
+// Grouped (MoE) GEMM: x rows are sorted by expert; the tile list lives on the device.
+void fp4_gemm_grouped(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
+                      const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
+                      int64_t token_tile, const OptT& row_scale, Tensor status) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && qw.dim() == 5 && qw.is_contiguous() &&
+              sc.is_contiguous());
+  TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_row0.scalar_type() == at::kInt &&
+              tile_rows.scalar_type() == at::kInt && n_tiles.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbFp4GemmParams p{};
+  p.x = x.data_ptr();
+  p.qw = qw.data_ptr();
+  p.sc = sc.data_ptr();
+  p.out = out.data_ptr();
+  p.M = (int)x.size(0);
+  p.N = (int)N;
+  p.K = (int)qw.size(2) * 64;
+  p.Kx = (int)x.size(1);
+  p.ldo = (int)out.stride(0);
+  p.gs_shift = log2i(gs);
+  p.status = status.data_ptr<int>();
+  p.tile_expert = tile_expert.data_ptr<int>();
+  p.tile_row0 = tile_row0.data_ptr<int>();
+  p.tile_rows = tile_rows.data_ptr<int>();
+  p.n_tiles = n_tiles.data_ptr<int>();
+  p.max_tiles = (int)tile_expert.numel();
+  p.expert_stride_q = qw.stride(0) / 4;
+  p.expert_stride_s = sc.stride(0) / 2;
+  p.token_tile = (int)token_tile;
+  if (row_scale.has_value() && row_scale->defined()) {
+    TORCH_CHECK(row_scale->scalar_type() == at::kFloat && row_scale->is_contiguous());
+    p.row_scale = row_scale->data_ptr<float>();
+  }
+  check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm_grouped");
+}
+
+void bf16_gemm(const Tensor& x, const Tensor& w, Tensor out, Tensor status) {
+  // x [B?, M, K], w [B?, N, K] -> out [B?, M, N]; 2-D operands are shared across the batch
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  TORCH_CHECK(x.stride(-1) == 1 && w.stride(-1) == 1 && out.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbBf16GemmParams p{};
+  p.x = x.data_ptr();
+  p.w = w.data_ptr();
+  p.out = out.data_ptr();
+  p.M = (int)x.size(-2);
+  p.N = (int)w.size(-2);
+  p.K = (int)x.size(-1);
+  p.ldx = (int)x.stride(-2);
+  p.ldw = (int)w.stride(-2);
+  p.ldo = (int)out.size(-1);
+  p.out_f32 = out.scalar_type() == at::kFloat;
+  p.batch = out.dim() == 3 ? (int)out.size(0) : 1;
+  p.x_batch_stride = x.dim() == 3 ? x.stride(0) : 0;
+  p.w_batch_stride = w.dim() == 3 ? w.stride(0) : 0;
+  p.out_batch_stride = out.dim() == 3 ? out.stride(0) : 0;
+  p.status = status.data_ptr<int>();
+  check(mmb_bf16_gemm(&p, cur_stream()), "bf16_gemm");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(mmb200, m) {
+  m.def("fp4_gemm_grouped", &fp4_gemm_grouped);
+  m.def("bf16_gemm", &bf16_gemm);
   m.def("fp4_gemv", &fp4_gemv);
   m.def("fp4_moe_gemv", &fp4_moe_gemv);
   m.def("bf16_gemv", &bf16_gemv);

@@ -1,0 +1,343 @@
+"""Decoder-only transformer over the op layer: dense GQA (Llama / Qwen3), MLA + MoE
+(GLM-4.7-Flash / DeepSeek) and GQA + MoE (Qwen3-MoE), always on a *paged* KV cache.
+
+Parity: the reference's flagship model class ``MMFP4ForCausalLM`` is imported at
+``metal_marlin/inference/mmfp4_pipeline.py:1843`` but absent from its tree; its layers are
+``metal_marlin/layers/mmfp4_mla.py:149`` (MLA), ``metal_marlin/layers/mmfp4_moe.py:352`` (MoE),
+``metal_marlin/layers/mmfp4_linear.py:600`` (linear) and, for dense models,
+``metal_marlin/inference/pipeline.py:277-830`` (``MetalMarlinModel``).
+
+Blackwell-first choices that differ from the reference:
+
+* the residual stream is carried as ``(hidden, pending delta)``; the add and the RMSNorm that
+  follow every sub-layer are fused into the *prologue* of the next weight-streaming kernel, so a
+  decode layer is 9 launches (MLA + MoE) instead of ~40 dispatches;
+* MLA decode uses the absorbed formulation on a post-norm / post-RoPE latent cache: the cache
+  row is exactly what attention consumes (576 values), W_uk is applied to the query and W_uv to
+  the merged output, so nothing is re-normalised or up-projected per cached token;
+* the whole decode step (all layers, head, sampler) is captured in one CUDA graph.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from ..ops import FP4ExpertBank, FP4Weight
+from .config import ModelConfig
+
+
+# ---------------------------------------------------------------------------------------------
+# rotary frequencies (plain + YaRN)
+# ---------------------------------------------------------------------------------------------
+def rope_inv_freq(cfg: ModelConfig, rot_dim: int, device) -> Tuple[torch.Tensor, float]:
+    """Returns (inv_freq fp32 [rot_dim/2], attention/mscale factor applied to cos and sin).
+    YaRN follows the published NTK-by-parts rule.  Parity: reference ``metal_marlin/rope.py:44-250``."""
+    base = float(cfg.rope_theta)
+    idx = torch.arange(0, rot_dim, 2, dtype=torch.float32, device=device)
+    inv = 1.0 / (base ** (idx / rot_dim))
+    rs = cfg.rope_scaling or {}
+    kind = rs.get("rope_type", rs.get("type"))
+    mscale = 1.0
+    if kind == "linear":
+        inv = inv / float(rs.get("factor", 1.0))
+    elif kind == "yarn":
+        factor = float(rs.get("factor", 1.0))
+        orig = float(rs.get("original_max_position_embeddings", cfg.max_position_embeddings))
+        beta_fast, beta_slow = float(rs.get("beta_fast", 32)), float(rs.get("beta_slow", 1))
+
+        def corr_dim(n_rot):
+            return (rot_dim * math.log(orig / (n_rot * 2 * math.pi))) / (2 * math.log(base))
+
+        low = max(math.floor(corr_dim(beta_fast)), 0)
+        high = min(math.ceil(corr_dim(beta_slow)), rot_dim - 1)
+        ramp = ((torch.arange(rot_dim // 2, dtype=torch.float32, device=device) - low) / max(high - low, 1e-3)).clamp(0, 1)
+        inv = inv / factor * ramp + inv * (1 - ramp)
+        m, m_all = float(rs.get("mscale", 1.0)), float(rs.get("mscale_all_dim", 0.0))
+
+        def ms(scale, mm):
+            return 1.0 if scale <= 1 else 0.1 * mm * math.log(scale) + 1.0
+
+        mscale = ms(factor, m) / ms(factor, m_all) if m_all else ms(factor, m)
+    return inv.contiguous(), mscale
+
+
+# ---------------------------------------------------------------------------------------------
+# weights
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class LayerWeights:
+    input_norm: torch.Tensor
+    post_norm: torch.Tensor
+    # GQA attention
+    qkv: Optional[FP4Weight] = None
+    qkv_bias: Optional[torch.Tensor] = None
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    # MLA
+    qa_kva: Optional[FP4Weight] = None        # rows [q_a (q_lora) | kv_a (kv_lora + rope)]  (or [q | kv_a] without q_lora)
+    q_a_norm: Optional[torch.Tensor] = None
+    q_b: Optional[FP4Weight] = None
+    kv_a_norm: Optional[torch.Tensor] = None
+    kv_b: Optional[FP4Weight] = None          # kept for prefill (non-absorbed) attention
+    w_ukT: Optional[torch.Tensor] = None      # bf16 [H, R, dn]
+    w_uv: Optional[torch.Tensor] = None       # bf16 [H, dv, R]
+    o: Optional[FP4Weight] = None
+    # dense MLP
+    gate_up: Optional[FP4Weight] = None
+    down: Optional[FP4Weight] = None
+    # MoE
+    router_w: Optional[torch.Tensor] = None
+    router_bias: Optional[torch.Tensor] = None
+    gate_up_bank: Optional[FP4ExpertBank] = None
+    down_bank: Optional[FP4ExpertBank] = None
+
+
+def absorb_kv_b(kv_b: FP4Weight, H: int, dn: int, dv: int, R: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Split the dequantized kv_b projection ``[H * (dn + dv), R]`` into ``W_uk^T [H, R, dn]`` and
+    ``W_uv [H, dv, R]`` (bf16) for absorbed-MLA decode.  Parity: reference
+    ``metal_marlin/paged/mmfp4_paged_adapter.py:236-345``."""
+    w = kv_b.dequantize(torch.float32).view(H, dn + dv, R)
+    w_uk = w[:, :dn, :]
+    return w_uk.transpose(1, 2).contiguous().to(torch.bfloat16), w[:, dn:, :].contiguous().to(torch.bfloat16)
+
+
+# ---------------------------------------------------------------------------------------------
+# paged KV storage
+# ---------------------------------------------------------------------------------------------
+class PagedKVStorage:
+    """Device pools, one per layer.  MLA: ``[num_slots, R + dr]`` latent rows.  GQA: separate K and V
+    pools ``[num_slots, Hkv, D]``.  A slot is ``block * block_size + offset``; block tables and slot
+    mappings come from the host-side allocator (``kv/paged.py``)."""
+
+    def __init__(self, cfg: ModelConfig, num_blocks: int, block_size: int, device, dtype=torch.bfloat16):
+        self.cfg, self.num_blocks, self.block_size = cfg, num_blocks, block_size
+        n_slots = num_blocks * block_size
+        L = cfg.num_hidden_layers
+        if cfg.is_mla:
+            self.k = [torch.zeros(n_slots, cfg.latent_dim, dtype=dtype, device=device) for _ in range(L)]
+            self.v = [None] * L
+        else:
+            self.k = [torch.zeros(n_slots, cfg.num_key_value_heads, cfg.dh, dtype=dtype, device=device) for _ in range(L)]
+            self.v = [torch.zeros(n_slots, cfg.num_key_value_heads, cfg.dh, dtype=dtype, device=device) for _ in range(L)]
+
+    def bytes_per_token(self) -> int:
+        cfg = self.cfg
+        per = cfg.latent_dim if cfg.is_mla else 2 * cfg.num_key_value_heads * cfg.dh
+        return per * 2 * cfg.num_hidden_layers
+
+
+@dataclass
+class BatchMeta:
+    """Per-step batch description (all tensors on the model's device).
+
+    ``positions [T] int32``, ``slots [T] int64`` (cache slot of every token, -1 = do not cache),
+    ``block_tables [B, max_blocks] int32``, ``ctx_lens [B] int32`` (tokens visible to each sequence
+    *including* this step's), ``cu_seqlens``: list of python ints delimiting the sequences inside
+    the flattened token axis (prefill only), ``decode``: one token per sequence."""
+    positions: torch.Tensor
+    slots: torch.Tensor
+    block_tables: torch.Tensor
+    ctx_lens: torch.Tensor
+    decode: bool = True
+    cu_seqlens: Optional[List[int]] = None
+    max_ctx: Optional[int] = None
+    splits: Optional[int] = None
+    ctx_lens_host: Optional[List[int]] = None
+
+
+# ---------------------------------------------------------------------------------------------
+# the model
+# ---------------------------------------------------------------------------------------------
+class Transformer:
+    def __init__(self, cfg: ModelConfig, layers: List[LayerWeights], embed: torch.Tensor, final_norm: torch.Tensor,
+                 lm_head: torch.Tensor):
+        self.cfg = cfg
+        self.layers = layers
+        self.embed = embed
+        self.final_norm = final_norm
+        self.lm_head = lm_head
+        self.device = embed.device
+        rot = cfg.qk_rope_head_dim if cfg.is_mla else cfg.dh
+        self.inv_freq, self.rope_mscale = rope_inv_freq(cfg, rot, self.device)
+        self.scale = cfg.softmax_scale()
+        self.mtp = None      # optional multi-token-prediction head (spec/mtp.py)
+
+    # ------------------------------------------------------------------ attention blocks
+    def _attn_gqa(self, L: LayerWeights, li: int, h, d, kv: PagedKVStorage, meta: BatchMeta):
+        cfg = self.cfg
+        Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.dh
+        T = h.shape[0]
+        new_h = torch.empty_like(h) if d is not None else None
+        qkv = ops.linear(h, L.qkv, delta=d, norm_w=L.input_norm, eps=cfg.rms_norm_eps, resid_out=new_h, bias=L.qkv_bias)
+        if new_h is not None:
+            h = new_h
+        q = qkv[:, : Hq * D]
+        k = qkv[:, Hq * D: (Hq + Hk) * D]
+        v = qkv[:, (Hq + Hk) * D:]
+        ops.qk_norm_rope_cache(q, k, v, L.q_norm, L.k_norm, meta.positions, self.inv_freq, meta.slots, kv.k[li], kv.v[li],
+                               Hq, Hk, D, cfg.rms_norm_eps, cfg.rope_interleave)
+        if meta.decode:
+            qc = q.contiguous().view(T, Hq, D)
+            o = ops.paged_attention(qc, kv.k[li], kv.v[li], meta.block_tables, meta.ctx_lens, Hq=Hq, Hkv=Hk, dqk=D, dv=D,
+                                    block_size=kv.block_size, scale=self.scale, window=cfg.sliding_window,
+                                    splits=meta.splits, max_ctx=meta.max_ctx)
+            o = o.reshape(T, Hq * D)
+        else:
+            o = self._prefill_attention_gqa(q.reshape(T, Hq, D), kv, li, meta)
+        d = ops.linear(o, L.o)
+        return h, d
+
+    def _prefill_attention_gqa(self, q, kv: PagedKVStorage, li: int, meta: BatchMeta):
+        """Causal attention of every prompt chunk against its sequence's cached keys (which already
+        include this chunk).  Runs per sequence over gathered K/V."""
+        cfg = self.cfg
+        Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.dh
+        out = torch.empty(q.shape[0], Hq * D, dtype=torch.bfloat16, device=q.device)
+        bs = kv.block_size
+        for b in range(len(meta.cu_seqlens) - 1):
+            s, e = meta.cu_seqlens[b], meta.cu_seqlens[b + 1]
+            n_ctx = int(meta.ctx_lens_host[b])
+            tok = torch.arange(n_ctx, device=q.device)
+            slots = meta.block_tables[b, tok // bs].long() * bs + tok % bs
+            K = kv.k[li][slots].transpose(0, 1).unsqueeze(0)       # [1, Hk, n, D]
+            V = kv.v[li][slots].transpose(0, 1).unsqueeze(0)
+            Q = q[s:e].transpose(0, 1).unsqueeze(0)                # [1, Hq, t, D]
+            t = e - s
+            mask = None
+            if n_ctx != t or cfg.sliding_window:
+                qpos = torch.arange(n_ctx - t, n_ctx, device=q.device).unsqueeze(1)
+                kpos = tok.unsqueeze(0)
+                mask = kpos <= qpos
+                if cfg.sliding_window:
+                    mask &= kpos > qpos - cfg.sliding_window
+            o = F.scaled_dot_product_attention(Q, K, V, attn_mask=mask, is_causal=(mask is None), scale=self.scale,
+                                               enable_gqa=(Hq != Hk))
+            out[s:e] = o.squeeze(0).transpose(0, 1).reshape(t, Hq * D)
+        return out
+
+    def _attn_mla(self, L: LayerWeights, li: int, h, d, kv: PagedKVStorage, meta: BatchMeta):
+        cfg = self.cfg
+        H, dn, dr, dv, R = cfg.num_attention_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        T = h.shape[0]
+        new_h = torch.empty_like(h) if d is not None else None
+        a = ops.linear(h, L.qa_kva, delta=d, norm_w=L.input_norm, eps=cfg.rms_norm_eps, resid_out=new_h)
+        if new_h is not None:
+            h = new_h
+        if L.q_b is not None:
+            ql = cfg.q_lora_rank
+            q = ops.linear(a[:, :ql], L.q_b, norm_w=L.q_a_norm, eps=cfg.rms_norm_eps)
+            kva = a[:, ql:]
+        else:
+            ql = H * (dn + dr)
+            q = a[:, :ql]
+            kva = a[:, ql:]
+        q_full = torch.empty(T, H, R + dr, dtype=torch.bfloat16, device=h.device)
+        ops.mla_prep(q, kva, L.w_ukT, L.kv_a_norm, meta.positions, self.inv_freq, meta.slots, q_full, kv.k[li], H, dn, dr,
+                     R, cfg.rms_norm_eps, self.rope_mscale, cfg.rope_interleave)
+        if meta.decode:
+            o = ops.paged_attention(q_full, kv.k[li], None, meta.block_tables, meta.ctx_lens, Hq=H, Hkv=1, dqk=R + dr, dv=R,
+                                    block_size=kv.block_size, scale=self.scale, splits=meta.splits, w_uv=L.w_uv,
+                                    max_ctx=meta.max_ctx)
+            o = o.reshape(T, H * dv)
+        else:
+            o = self._prefill_attention_mla(L, q_full, kv, li, meta)
+        d = ops.linear(o, L.o)
+        return h, d
+
+    def _prefill_attention_mla(self, L: LayerWeights, q_full, kv: PagedKVStorage, li: int, meta: BatchMeta):
+        """Absorbed-form causal prefill: scores and values live in the 576/512-d latent space, all heads
+        share the latent keys (an MQA problem), then W_uv lifts the result to v_head_dim per head."""
+        cfg = self.cfg
+        H, dr, dv, R = cfg.num_attention_heads, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        out = torch.empty(q_full.shape[0], H * dv, dtype=torch.bfloat16, device=q_full.device)
+        bs = kv.block_size
+        for b in range(len(meta.cu_seqlens) - 1):
+            s, e = meta.cu_seqlens[b], meta.cu_seqlens[b + 1]
+            n_ctx = int(meta.ctx_lens_host[b])
+            t = e - s
+            tok = torch.arange(n_ctx, device=q_full.device)
+            slots = meta.block_tables[b, tok // bs].long() * bs + tok % bs
+            lat = kv.k[li][slots]                                   # [n, R + dr]
+            Q = q_full[s:e].transpose(0, 1).unsqueeze(0)            # [1, H, t, R + dr]
+            Kt = lat.view(1, 1, n_ctx, R + dr)
+            Vt = lat[:, :R].reshape(1, 1, n_ctx, R)
+            mask = None
+            if n_ctx != t:
+                qpos = torch.arange(n_ctx - t, n_ctx, device=q_full.device).unsqueeze(1)
+                mask = tok.unsqueeze(0) <= qpos
+            o = F.scaled_dot_product_attention(Q, Kt.expand(1, H, n_ctx, R + dr), Vt.expand(1, H, n_ctx, R), attn_mask=mask,
+                                               is_causal=(mask is None), scale=self.scale)
+            o_lat = o.squeeze(0).transpose(0, 1).contiguous()       # [t, H, R]
+            out[s:e] = torch.einsum("thr,hvr->thv", o_lat, L.w_uv).reshape(t, H * dv)
+        return out
+
+    # ------------------------------------------------------------------ MLP blocks
+    def _mlp_dense(self, L: LayerWeights, h, d):
+        cfg = self.cfg
+        new_h = torch.empty_like(h)
+        x = ops.linear(h, L.gate_up, delta=d, norm_w=L.post_norm, eps=cfg.rms_norm_eps, resid_out=new_h, act=1)
+        return new_h, ops.linear(x, L.down)
+
+    def _mlp_moe(self, L: LayerWeights, h, d, counts=None):
+        cfg = self.cfg
+        new_h = torch.empty_like(h)
+        ids, wts = ops.moe_router(h, L.router_w, delta=d, norm_w=L.post_norm, eps=cfg.rms_norm_eps, resid_out=new_h,
+                                  bias=L.router_bias, topk=cfg.num_experts_per_tok,
+                                  scoring=1 if cfg.scoring_func == "sigmoid" else 0, renorm=cfg.norm_topk_prob,
+                                  routed_scale=cfg.routed_scaling_factor, n_group=cfg.n_group, topk_group=cfg.topk_group,
+                                  counts=counts)
+        out = ops.moe_forward(new_h, L.gate_up_bank, L.down_bank, ids, wts, n_shared=cfg.n_shared_experts,
+                              shared_base=cfg.num_experts, norm_w=L.post_norm, eps=cfg.rms_norm_eps)
+        return new_h, out
+
+    # ------------------------------------------------------------------ full forward
+    def forward_hidden(self, input_ids: torch.Tensor, kv: PagedKVStorage, meta: BatchMeta) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Runs all layers.  Returns (hidden, pending delta): the final residual add + norm is fused
+        into the head projection."""
+        h = ops.embedding(self.embed, input_ids)
+        d = None
+        for li, L in enumerate(self.layers):
+            if self.cfg.is_mla:
+                h, d = self._attn_mla(L, li, h, d, kv, meta)
+            else:
+                h, d = self._attn_gqa(L, li, h, d, kv, meta)
+            if L.gate_up_bank is not None:
+                h, d = self._mlp_moe(L, h, d)
+            else:
+                h, d = self._mlp_dense(L, h, d)
+        return h, d
+
+    def logits(self, h, d, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """fp32 logits of the selected rows (default: all)."""
+        if rows is not None:
+            h = h.index_select(0, rows)
+            d = d.index_select(0, rows) if d is not None else None
+        return ops.bf16_linear(h, self.lm_head, delta=d, norm_w=self.final_norm, eps=self.cfg.rms_norm_eps,
+                               out_dtype=torch.float32)
+
+    def final_hidden(self, h, d) -> torch.Tensor:
+        """Normalised last hidden state (input of the head / of MTP modules)."""
+        return ops.rmsnorm(h, self.final_norm, self.cfg.rms_norm_eps, delta=d)
+
+    def forward(self, input_ids, kv: PagedKVStorage, meta: BatchMeta, last_only: bool = True) -> torch.Tensor:
+        h, d = self.forward_hidden(input_ids, kv, meta)
+        rows = None
+        if not meta.decode and last_only and meta.cu_seqlens is not None:
+            rows = torch.tensor([e - 1 for e in meta.cu_seqlens[1:]], device=h.device, dtype=torch.long)
+        return self.logits(h, d, rows)
+
+    # ------------------------------------------------------------------ accounting
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() * 2 + (0 if self.lm_head is self.embed else self.lm_head.numel() * 2)
+        for L in self.layers:
+            for v in vars(L).values():
+                if isinstance(v, (FP4Weight, FP4ExpertBank)):
+                    n += v.nbytes()
+                elif isinstance(v, torch.Tensor):
+                    n += v.numel() * v.element_size()
+        return n

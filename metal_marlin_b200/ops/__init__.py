@@ -1,0 +1,407 @@
+"""Op layer: one functional API, two implementations.
+
+CUDA tensors run the hand-written sm_100a kernels in ``_C.so`` (loaded eagerly and
+*required* whenever a GPU is present: a missing or stale library raises instead of
+falling back).  CPU tensors — and any call made under ``force_reference()`` — run the
+PyTorch restatement in ``ops/reference.py``.  Parity: reference
+``metal_marlin/kernels_core.py:1830-5370`` (flat python wrappers around Metal
+dispatches) and the try/except fallbacks around them.
+"""
+from __future__ import annotations
+
+import contextlib
+import os
+from typing import Optional
+
+import torch
+
+from .. import _build
+from . import reference as ref
+from .weights import FP4ExpertBank, FP4Weight  # noqa: F401
+
+_FORCE_REF = os.environ.get("MMB200_FORCE_TORCH", "0") == "1"
+_native_ok = False
+GEMV_MAX_M = 16          # at or below this many tokens the weight-streaming GEMV path is used
+
+
+def native_available() -> bool:
+    global _native_ok
+    if _native_ok:
+        return True
+    if not torch.cuda.is_available():
+        return False
+    _build.load(require=True)
+    _native_ok = True
+    return True
+
+
+@contextlib.contextmanager
+def force_reference(flag: bool = True):
+    """Run ops through the PyTorch restatement even on CUDA tensors (tests, baselines)."""
+    global _FORCE_REF
+    old = _FORCE_REF
+    _FORCE_REF = flag
+    try:
+        yield
+    finally:
+        _FORCE_REF = old
+
+
+def _use_native(t: torch.Tensor) -> bool:
+    return t.is_cuda and not _FORCE_REF and native_available()
+
+
+_status = {}
+
+
+def gemm_status(device) -> torch.Tensor:
+    """Per-device int32[4] status word written by kernels whose bounded waits expire."""
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> int:
+    """Host read of the status word (synchronises).  0 = no wait timed out."""
+    return int(gemm_status(device)[0].item())
+
+
+class _NativeOps:
+    """``K.mmb200.<op>(...)`` forwards to ``torch.ops.mmb200.<op>`` and counts kernel launches, so
+    benchmarks can report how many of this library's kernels ran inside a timed region."""
+    KERNELS_PER_CALL = {"paged_decode": 1, "decode_merge": 1}
+
+    def __init__(self):
+        self.launches = 0
+        self._cache = {}
+
+    def __getattr__(self, name):
+        if name.startswith("_") or name in ("launches", "mmb200"):
+            raise AttributeError(name)
+        fn = getattr(torch.ops.mmb200, name)
+        n = self.KERNELS_PER_CALL.get(name, 1)
+
+        def call(*args):
+            self.launches += n
+            return fn(*args)
+
+        self.__dict__[name] = call
+        return call
+
+
+class _K:
+    mmb200 = _NativeOps()
+
+
+K = _K()
+
+
+def launch_count() -> int:
+    """Number of native kernel launches issued through this module so far."""
+    return K.mmb200.launches
+
+
+def rmsnorm(x, w, eps=1e-6, *, delta=None, resid_out=None, out=None):
+    if not _use_native(x):
+        return ref.rmsnorm(x, w, eps, delta, resid_out, out)
+    if out is None:
+        out = torch.empty_like(x)
+    K.mmb200.rmsnorm(x, delta, w, out, resid_out, eps)
+    return out
+
+
+def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bias=None, out_add=None,
+           out=None, token_tile=0):
+    """``out = epilogue( prologue(x) @ dequant(W)^T )``; prologue = optional residual add + RMSNorm,
+    epilogue = optional bias, SwiGLU over the two row halves (``act=1``), residual add."""
+    if not _use_native(x):
+        return ref.linear(x, W, delta=delta, norm_w=norm_w, eps=eps, resid_out=resid_out, act=act, bias=bias,
+                          out_add=out_add, out=out)
+    M = x.shape[0]
+    n_out = W.out_features // 2 if act == 1 else W.out_features
+    if out is None:
+        out = torch.empty(M, n_out, dtype=torch.bfloat16, device=x.device)
+    if M <= GEMV_MAX_M:
+        K.mmb200.fp4_gemv(x, W.qtile, W.stile, out, W.out_features, W.in_features, W.group_size, delta, norm_w,
+                          resid_out, eps, act, bias, out_add)
+        return out
+    # tensor-core path: prologue/epilogue pieces run as their own (memory-bound) kernels
+    xin = x
+    if norm_w is not None or delta is not None:
+        xin = torch.empty(M, W.in_features, dtype=torch.bfloat16, device=x.device)
+        if norm_w is not None:
+            K.mmb200.rmsnorm(x, delta, norm_w, xin, resid_out, eps)
+        else:
+            K.mmb200.add(x.contiguous(), delta.contiguous(), xin)
+            if resid_out is not None:
+                resid_out.copy_(xin)
+    elif not xin.is_contiguous() or xin.shape[1] != W.in_features:
+        xin = xin[:, : W.in_features].contiguous()
+    y = out if act == 0 else torch.empty(M, W.out_features, dtype=torch.bfloat16, device=x.device)
+    K.mmb200.fp4_gemm(xin, W.qtile, W.stile, y, W.out_features, W.group_size, gemm_status(x.device))
+    if bias is not None:
+        y += bias
+    if act == 1:
+        K.mmb200.silu_mul(y, out)
+    if out_add is not None:
+        out += out_add
+    return out
+
+
+def bf16_linear(x, w, *, delta=None, norm_w=None, eps=1e-6, out_dtype=torch.bfloat16, out=None):
+    if not _use_native(x):
+        return ref.bf16_linear(x, w, delta=delta, norm_w=norm_w, eps=eps, out_dtype=out_dtype, out=out)
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty(M, w.shape[0], dtype=out_dtype, device=x.device)
+    if M <= 64:
+        K.mmb200.bf16_gemv(x, w, out, delta, norm_w, eps)
+        return out
+    xin = x
+    if norm_w is not None:
+        xin = torch.empty_like(x)
+        K.mmb200.rmsnorm(x, delta, norm_w, xin, None, eps)
+    # large-M unquantized projections (lm_head over a whole prompt) are plain library GEMMs
+    y = torch.matmul(xin, w.t())
+    out.copy_(y.to(out_dtype))
+    return out
+
+
+def silu_mul(gu, out=None):
+    if not _use_native(gu):
+        return ref.silu_mul(gu, out)
+    if out is None:
+        out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=gu.dtype, device=gu.device)
+    K.mmb200.silu_mul(gu, out)
+    return out
+
+
+def embedding(table, ids, out=None):
+    if not _use_native(table):
+        return ref.embedding(table, ids, out)
+    ids = ids.reshape(-1).contiguous()
+    if out is None:
+        out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    K.mmb200.embedding(table, ids, out)
+    return out
+
+
+def rope(q, k, positions, inv_freq, Hq, Hk, D, rot_dim, interleaved=False, mscale=1.0):
+    if not _use_native(q):
+        return ref.rope(q, k, positions, inv_freq, Hq, Hk, D, rot_dim, interleaved, mscale)
+    K.mmb200.rope(q, k, positions, inv_freq, Hq, Hk, D, rot_dim, interleaved, mscale)
+    return q, k
+
+
+def qk_norm_rope_cache(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool, v_pool, Hq, Hk, D, eps, interleaved=False):
+    if not _use_native(q):
+        return ref.qk_norm_rope_cache(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool, v_pool, Hq, Hk, D, eps,
+                                      interleaved)
+    K.mmb200.qk_norm_rope_cache(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool, v_pool, Hq, Hk, D, eps, interleaved)
+    return q
+
+
+def mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps, mscale=1.0,
+             interleaved=True):
+    if not _use_native(q):
+        return ref.mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps,
+                            mscale, interleaved)
+    K.mmb200.mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps, mscale,
+                      interleaved)
+    return q_full
+
+
+def default_splits(batch: int, n_kv_heads: int, max_ctx: int, sm_count: int = 148) -> int:
+    """Split-KV factor so that batch * kv_heads * splits covers the SMs, each split >= 2 tiles of 64."""
+    tiles = max(1, (max_ctx + 63) // 64)
+    want = max(1, sm_count // max(1, batch * n_kv_heads))
+    return int(max(1, min(want, (tiles + 1) // 2, 64)))
+
+
+def paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, *, Hq, Hkv, dqk, dv, block_size, scale, window=0,
+                    splits=None, w_uv=None, workspace=None, out=None, max_ctx=None):
+    """Decode attention over a paged pool.  With ``w_uv [Hq, dvo, dv]`` the merged latent output is
+    up-projected per head (MLA).  Returns bf16 ``[B, Hq, dvo or dv]``."""
+    B = ctx_lens.numel()
+    dvo = w_uv.shape[1] if w_uv is not None else dv
+    if not _use_native(q):
+        o = ref.paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, Hq, Hkv, dqk, dv, block_size, scale, window)
+        if w_uv is not None:
+            o = ref.mla_up(o, w_uv)
+        if out is not None:
+            out.copy_(o.view_as(out))
+            return out
+        return o
+    if splits is None:
+        if max_ctx is None:
+            max_ctx = block_tables.shape[1] * block_size
+        splits = default_splits(B, Hkv, max_ctx)
+    if workspace is None:
+        part_o = torch.empty(B * Hq * splits * dv, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=q.device)
+    else:
+        part_o, part_ml = workspace
+    if out is None:
+        out = torch.empty(B, Hq, dvo, dtype=torch.bfloat16, device=q.device)
+    K.mmb200.paged_decode(q, k_pool, v_pool, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv, block_size,
+                          splits, scale, window)
+    K.mmb200.decode_merge(part_o, part_ml, w_uv, out, B, Hq, dv, dvo, splits)
+    return out
+
+
+def moe_router(x, w, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, bias=None, topk=4, scoring=0, renorm=True,
+               routed_scale=1.0, n_group=1, topk_group=1, ids=None, weights=None, logits_out=None, counts=None):
+    if not _use_native(x):
+        i, wt, lg = ref.moe_router(x, w, delta=delta, norm_w=norm_w, eps=eps, resid_out=resid_out, bias=bias, topk=topk,
+                                   scoring=scoring, renorm=renorm, routed_scale=routed_scale, n_group=n_group,
+                                   topk_group=topk_group)
+        if ids is not None:
+            ids.copy_(i)
+            weights.copy_(wt)
+            i, wt = ids, weights
+        if logits_out is not None:
+            logits_out.copy_(lg)
+        if counts is not None:
+            counts += torch.bincount(i.reshape(-1).long(), minlength=counts.numel()).to(counts.dtype)
+        return i, wt
+    T = x.shape[0]
+    if ids is None:
+        ids = torch.empty(T, topk, dtype=torch.int32, device=x.device)
+        weights = torch.empty(T, topk, dtype=torch.float32, device=x.device)
+    K.mmb200.moe_router(x, w, delta, norm_w, resid_out, bias, ids, weights, logits_out, counts, topk, eps, scoring,
+                        renorm, routed_scale, n_group, topk_group)
+    return ids, weights
+
+
+def moe_gate_up(x, bank: FP4ExpertBank, ids, *, n_shared=0, shared_base=0, norm_w=None, eps=1e-6, out=None):
+    if not _use_native(x):
+        return ref.moe_gate_up(x, bank, ids, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps, out=out)
+    T, topk = ids.shape
+    S = topk + n_shared
+    if out is None:
+        out = torch.empty(T * S, bank.out_features // 2, dtype=torch.bfloat16, device=x.device)
+    K.mmb200.fp4_moe_gemv(x, bank.qtile, bank.stile, out, bank.out_features, bank.in_features, bank.group_size, 1, ids,
+                          None, n_shared, shared_base, norm_w, eps, 1, None)
+    return out
+
+
+def moe_down(h, bank: FP4ExpertBank, ids, weights, *, n_shared=0, shared_base=0, out_add=None, out=None):
+    if not _use_native(h):
+        return ref.moe_down(h, bank, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add, out=out)
+    T = ids.shape[0]
+    if out is None:
+        out = torch.empty(T, bank.out_features, dtype=torch.bfloat16, device=h.device)
+    K.mmb200.fp4_moe_gemv(h, bank.qtile, bank.stile, out, bank.out_features, bank.in_features, bank.group_size, 2, ids,
+                          weights, n_shared, shared_base, None, 0.0, 0, out_add)
+    return out
+
+
+def argmax(logits, out=None):
+    if not _use_native(logits):
+        r = logits.argmax(-1)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    K.mmb200.argmax(logits, out)
+    return out
+
+
+def sample(logits, *, temperature=None, top_k=None, top_p=None, min_p=None, history=None, rep_penalty=None, seed=0,
+           offset=0, out=None, out_logprob=None, generator=None, offset_dev=None):
+    """Per-row parameters are tensors on the logits' device (None = feature off)."""
+    if not _use_native(logits):
+        ids, lp = ref.sample(logits, temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p, history=history,
+                             rep_penalty=rep_penalty, generator=generator)
+        if out is not None:
+            out.copy_(ids)
+            ids = out
+        if out_logprob is not None:
+            out_logprob.copy_(lp)
+        return ids
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    K.mmb200.sample(logits, out, out_logprob, temperature, top_k, top_p, min_p, history, rep_penalty, int(seed), int(offset),
+                    offset_dev)
+    return out
+
+
+def bf16_gemm(x, w, out=None, out_dtype=torch.bfloat16):
+    """tcgen05 GEMM ``out[.., M, N] = x[.., M, K] @ w[.., N, K]^T`` (bf16 operands by TMA, fp32 in TMEM)."""
+    if not _use_native(x):
+        y = torch.matmul(x.to(torch.float32), w.to(torch.float32).transpose(-1, -2)).to(out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    batched = x.dim() == 3 or w.dim() == 3
+    nb = x.shape[0] if x.dim() == 3 else (w.shape[0] if w.dim() == 3 else 1)
+    shape = (nb, x.shape[-2], w.shape[-2]) if batched else (x.shape[-2], w.shape[-2])
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=x.device)
+    K.mmb200.bf16_gemm(x, w, out, gemm_status(x.device))
+    return out
+
+
+def _build_tile_list(flat_ids: torch.Tensor, num_experts: int, token_tile: int):
+    """Device-side (no host sync) construction of the grouped-GEMM work list.
+    Returns (order, tile_expert, tile_row0, tile_rows, n_tiles)."""
+    n = flat_ids.numel()
+    order = torch.argsort(flat_ids, stable=True)
+    counts = torch.bincount(flat_ids, minlength=num_experts)[:num_experts]
+    offs = torch.cumsum(counts, 0) - counts
+    tiles_per = (counts + token_tile - 1) // token_tile
+    tile_end = torch.cumsum(tiles_per, 0)
+    tile_start = tile_end - tiles_per
+    max_tiles = (n + token_tile - 1) // token_tile + num_experts
+    j = torch.arange(max_tiles, device=flat_ids.device)
+    e = torch.searchsorted(tile_end, j, right=True).clamp_(max=num_experts - 1)
+    local = j - tile_start[e]
+    row0 = offs[e] + local * token_tile
+    rows = (counts[e] - local * token_tile).clamp_(0, token_tile)
+    n_tiles = tile_end[-1:].to(torch.int32)
+    return order, e.to(torch.int32), row0.to(torch.int32), rows.to(torch.int32), n_tiles
+
+
+def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *, n_shared=0, shared_base=0,
+                norm_w=None, eps=1e-6, out_add=None, token_tile=128):
+    """Whole expert MLP: ``sum_s w_s * down_e(silu(gate_e(x)) * up_e(x))`` over routed + shared experts.
+
+    Few tokens: per-(token, slot) weight-streaming kernels (experts read from device memory ids).
+    Many tokens: counting-sort tokens by expert, grouped tcgen05 GEMMs over a device-built tile list."""
+    T, topk = ids.shape
+    if (not _use_native(x)) or T <= GEMV_MAX_M:
+        h = moe_gate_up(x, gate_up, ids, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps)
+        return moe_down(h, down, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add)
+    xin = x
+    if norm_w is not None:
+        xin = torch.empty_like(x)
+        K.mmb200.rmsnorm(x, None, norm_w, xin, None, eps)
+    st = gemm_status(x.device)
+    inter = gate_up.out_features // 2
+    flat = ids.reshape(-1).long()
+    order, t_e, t_r0, t_rows, n_tiles = _build_tile_list(flat, gate_up.num_experts, token_tile)
+    tok = torch.div(order, topk, rounding_mode="floor")
+    xs = xin.index_select(0, tok)
+    gu = torch.empty(xs.shape[0], gate_up.out_features, dtype=torch.bfloat16, device=x.device)
+    K.mmb200.fp4_gemm_grouped(xs, gate_up.qtile, gate_up.stile, gu, gate_up.out_features, gate_up.group_size,
+                              t_e, t_r0, t_rows, n_tiles, token_tile, None, st)
+    h = torch.empty(xs.shape[0], inter, dtype=torch.bfloat16, device=x.device)
+    K.mmb200.silu_mul(gu, h)
+    y = torch.empty(xs.shape[0], down.out_features, dtype=torch.bfloat16, device=x.device)
+    rs = weights.reshape(-1).index_select(0, order).contiguous()
+    K.mmb200.fp4_gemm_grouped(h, down.qtile, down.stile, y, down.out_features, down.group_size,
+                              t_e, t_r0, t_rows, n_tiles, token_tile, rs, st)
+    unsorted = torch.empty_like(y)
+    unsorted.index_copy_(0, order, y)
+    acc = unsorted.view(T, topk, -1).to(torch.float32).sum(1)
+    for j in range(n_shared):
+        e = shared_base + j
+        hs = linear(xin, gate_up.expert(e), act=1)
+        acc += linear(hs, down.expert(e)).to(torch.float32)
+    if out_add is not None:
+        acc += out_add.to(torch.float32)
+    return acc.to(torch.bfloat16)

@@ -1,0 +1,143 @@
+"""Device-resident quantized weight containers.
+
+``FP4Weight`` / ``FP4ExpertBank`` hold a matrix (or a stacked bank of expert
+matrices) in the device tile layout the sm_100a kernels read (see
+``formats/fp4.py``).  They are built once at load time from any checkpoint
+layout — the "repack at load" step; the checkpoint bytes themselves are never
+changed.  Parity: reference ``metal_marlin/layers/mmfp4_linear.py:414``
+(``_rowpacked_to_gpu_layout``) and ``metal_marlin/glm4_moe_experts.py:140-215``
+(stacked expert buffers).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..formats import fp4 as fp4fmt
+
+
+class FP4Weight:
+    __slots__ = ("qtile", "stile", "out_features", "in_features", "group_size", "_deq")
+
+    def __init__(self, qtile, stile, out_features, in_features, group_size):
+        self.qtile = qtile
+        self.stile = stile
+        self.out_features = int(out_features)
+        self.in_features = int(in_features)
+        self.group_size = int(group_size)
+        self._deq = None
+
+    # ------------------------------------------------------------------ constructors
+    @classmethod
+    def from_codes(cls, codes: torch.Tensor, scales: torch.Tensor, device=None) -> "FP4Weight":
+        out_f, in_f = codes.shape
+        if device is not None:
+            codes, scales = codes.to(device), scales.to(device)
+        qtile, stile, gs = fp4fmt.to_tile_layout(codes, scales)
+        return cls(qtile, stile, out_f, in_f, gs)
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor, group_size: int = 128, device=None) -> "FP4Weight":
+        gs = fp4fmt.pick_group_size(w.shape[1], group_size)
+        if device is not None:
+            w = w.to(device)
+        codes, scales = fp4fmt.quantize_codes(w, gs)
+        return cls.from_codes(codes, scales)
+
+    @classmethod
+    def from_mmfp4(cls, packed: torch.Tensor, scales: torch.Tensor, device=None) -> "FP4Weight":
+        if device is not None:
+            packed, scales = packed.to(device), scales.to(device)
+        codes, sc = fp4fmt.unpack_mmfp4(packed, scales)
+        return cls.from_codes(codes, sc)
+
+    @classmethod
+    def from_marlin_fp4(cls, packed: torch.Tensor, scales: torch.Tensor, device=None) -> "FP4Weight":
+        if device is not None:
+            packed, scales = packed.to(device), scales.to(device)
+        codes, sc = fp4fmt.unpack_marlin_fp4(packed, scales)
+        return cls.from_codes(codes, sc)
+
+    @classmethod
+    def concat_rows(cls, parts: Sequence["FP4Weight"]) -> "FP4Weight":
+        """Stack matrices that share the input dimension along the output axis
+        (fused q_a|kv_a, q|k|v, gate|up).  Each part must have a multiple of 16 rows."""
+        p0 = parts[0]
+        for p in parts:
+            assert p.in_features == p0.in_features and p.group_size == p0.group_size
+            assert p.out_features % 16 == 0, "row-concat needs 16-row aligned parts"
+        q = torch.cat([p.qtile for p in parts], 0)
+        s = torch.cat([p.stile for p in parts], 0)
+        return cls(q, s, sum(p.out_features for p in parts), p0.in_features, p0.group_size)
+
+    # ------------------------------------------------------------------ views
+    @property
+    def device(self):
+        return self.qtile.device
+
+    @property
+    def padded_in(self) -> int:
+        return self.qtile.shape[1] * 64
+
+    def to(self, device) -> "FP4Weight":
+        return FP4Weight(self.qtile.to(device), self.stile.to(device), self.out_features, self.in_features,
+                         self.group_size)
+
+    def codes_scales(self):
+        return fp4fmt.from_tile_layout(self.qtile, self.stile, self.out_features, self.in_features, self.group_size)
+
+    def dequantize(self, dtype=torch.float32, cache: bool = False) -> torch.Tensor:
+        if self._deq is not None and self._deq.dtype == dtype:
+            return self._deq
+        codes, scales = self.codes_scales()
+        w = fp4fmt.dequantize_codes(codes, scales, dtype)
+        if cache:
+            self._deq = w
+        return w
+
+    def nbytes(self) -> int:
+        return self.qtile.numel() * 4 + self.stile.numel() * 2
+
+
+class FP4ExpertBank:
+    """``E`` (+ shared) expert matrices of identical shape stacked on a leading axis."""
+    __slots__ = ("qtile", "stile", "num_experts", "out_features", "in_features", "group_size", "_deq")
+
+    def __init__(self, qtile, stile, out_features, in_features, group_size):
+        self.qtile = qtile            # [E, N/16, K/64, 32, 4] int32
+        self.stile = stile            # [E, N/16, K/gs, 8, 2] fp16
+        self.num_experts = qtile.shape[0]
+        self.out_features = int(out_features)
+        self.in_features = int(in_features)
+        self.group_size = int(group_size)
+        self._deq = None
+
+    @classmethod
+    def from_weights(cls, ws: List[FP4Weight]) -> "FP4ExpertBank":
+        w0 = ws[0]
+        return cls(torch.stack([w.qtile for w in ws]), torch.stack([w.stile for w in ws]),
+                   w0.out_features, w0.in_features, w0.group_size)
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor, group_size: int = 128) -> "FP4ExpertBank":
+        """``w [E, out, in]`` float -> quantized bank, one expert at a time (bounded memory)."""
+        return cls.from_weights([FP4Weight.from_float(w[e], group_size) for e in range(w.shape[0])])
+
+    @property
+    def device(self):
+        return self.qtile.device
+
+    def expert(self, e: int) -> FP4Weight:
+        return FP4Weight(self.qtile[e], self.stile[e], self.out_features, self.in_features, self.group_size)
+
+    def dequantize(self, dtype=torch.float32, cache: bool = False) -> torch.Tensor:
+        if self._deq is not None and self._deq.dtype == dtype:
+            return self._deq
+        w = torch.stack([self.expert(e).dequantize(dtype) for e in range(self.num_experts)])
+        if cache:
+            self._deq = w
+        return w
+
+    def nbytes(self) -> int:
+        return self.qtile.numel() * 4 + self.stile.numel() * 2

@@ -1,0 +1,83 @@
+"""tcgen05 / TMA / TMEM GEMM kernels against fp32 PyTorch matmuls (tile-boundary shapes, every token
+tile, grouped MoE mode, batched bf16 mode).  Also asserts the bounded-wait status word stays 0."""
+import pytest
+import torch
+
+from metal_marlin_b200 import ops
+from metal_marlin_b200.ops import FP4ExpertBank, FP4Weight
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _check(y, ref, tol=2e-2):
+    err = (y.float() - ref.float()).abs().max() / ref.float().abs().max().clamp_min(1e-6)
+    assert float(err) < tol, float(err)
+
+
+@pytest.mark.parametrize("M", [17, 32, 33, 64, 100, 128, 257, 1024, 2500])
+@pytest.mark.parametrize("N,K,gs", [(128, 64, 64), (256, 512, 128), (2048, 2048, 128), (576, 768, 128), (1000, 1536, 128),
+                                    (48, 192, 64)])
+def test_fp4_gemm_tcgen05(M, N, K, gs):
+    torch.manual_seed(M + N)
+    W = FP4Weight.from_float(torch.randn(N, K, device=DEV) * 0.03, gs)
+    x = (torch.randn(M, K, device=DEV)).to(torch.bfloat16)
+    y = ops.linear(x, W)
+    assert ops.check_status(DEV) == 0
+    ref = x.float() @ W.dequantize().t()
+    _check(y, ref)
+
+
+def test_fp4_gemm_large_scale_values_use_two_step_rescale():
+    N, K = 128, 256
+    codes = torch.randint(0, 16, (N, K), dtype=torch.uint8, device=DEV)
+    scales = torch.full((N, K // 128), 8.0, dtype=torch.float16, device=DEV)     # >= 2: no folding of 2^126
+    W = FP4Weight.from_codes(codes, scales)
+    x = torch.randint(-2, 3, (40, K), device=DEV).to(torch.bfloat16)
+    y = ops.linear(x, W)
+    _check(y, x.float() @ W.dequantize().t(), tol=1e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(40, 128, 64), (300, 1000, 512), (128, 256, 2048)])
+def test_bf16_gemm_tcgen05(M, N, K):
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = torch.randn(N, K, device=DEV).to(torch.bfloat16)
+    y = ops.bf16_gemm(x, w, out_dtype=torch.float32)
+    assert ops.check_status(DEV) == 0
+    _check(y, x.float() @ w.float().t(), tol=1e-2)
+
+
+def test_bf16_gemm_batched_shared_x():
+    x = torch.randn(70, 128, device=DEV).to(torch.bfloat16)
+    w = torch.randn(5, 192, 128, device=DEV).to(torch.bfloat16)
+    y = ops.bf16_gemm(x, w)
+    _check(y, torch.einsum("mk,bnk->bmn", x.float(), w.float()), tol=1e-2)
+
+
+@pytest.mark.parametrize("T,E,topk,ns", [(64, 8, 2, 1), (300, 64, 4, 1), (1000, 16, 8, 0)])
+def test_moe_grouped_gemm_path(T, E, topk, ns):
+    torch.manual_seed(T)
+    H, I = 256, 128
+    gu = FP4ExpertBank.from_float(torch.randn(E + ns, 2 * I, H, device=DEV) * 0.05, 64)
+    dn = FP4ExpertBank.from_float(torch.randn(E + ns, H, I, device=DEV) * 0.05, 64)
+    x = torch.randn(T, H, device=DEV).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, device=DEV)[:topk] for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, topk, device=DEV)
+    y = ops.moe_forward(x, gu, dn, ids, wts, n_shared=ns, shared_base=E, norm_w=nw)
+    assert ops.check_status(DEV) == 0
+    with ops.force_reference():
+        y_ref = ops.moe_forward(x, gu, dn, ids, wts, n_shared=ns, shared_base=E, norm_w=nw)
+    _check(y, y_ref, tol=4e-2)
+
+
+def test_prefill_through_tensor_core_path_matches_reference():
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM, prefill
+    lm = MMFP4ForCausalLM.from_config("tiny-mla-moe", device="cuda", seed=5)
+    prompts = [torch.randint(0, 512, (200,)).tolist(), torch.randint(0, 512, (90,)).tolist()]
+    bt = torch.arange(32, dtype=torch.int32).view(2, 16)
+    a = prefill(lm.model, lm.new_cache(32, 16), prompts, bt)
+    with ops.force_reference():
+        b = prefill(lm.model, lm.new_cache(32, 16), prompts, bt)
+    assert ops.check_status(DEV) == 0
+    assert float((a - b).abs().max() / b.abs().max()) < 4e-2
