@@ -22,6 +22,8 @@ from .weights import FP4ExpertBank, FP4Weight  # noqa: F401
 _FORCE_REF = os.environ.get("MMB200_FORCE_TORCH", "0") == "1"
 _native_ok = False
 GEMV_MAX_M = 16          # at or below this many tokens the weight-streaming GEMV path is used
+# Diagnostic switch: route every shape through the weight-streaming kernels (no tcgen05 GEMM).
+NO_TCGEN05 = os.environ.get("MMB200_NO_TCGEN05", "0") == "1"
 
 
 def native_available() -> bool:
@@ -122,7 +124,7 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
     n_out = W.out_features // 2 if act == 1 else W.out_features
     if out is None:
         out = torch.empty(M, n_out, dtype=torch.bfloat16, device=x.device)
-    if M <= GEMV_MAX_M:
+    if M <= GEMV_MAX_M or NO_TCGEN05:
         K.mmb200.fp4_gemv(x, W.qtile, W.stile, out, W.out_features, W.in_features, W.group_size, delta, norm_w,
                           resid_out, eps, act, bias, out_add)
         return out
@@ -373,7 +375,7 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
     Few tokens: per-(token, slot) weight-streaming kernels (experts read from device memory ids).
     Many tokens: counting-sort tokens by expert, grouped tcgen05 GEMMs over a device-built tile list."""
     T, topk = ids.shape
-    if (not _use_native(x)) or T <= GEMV_MAX_M:
+    if (not _use_native(x)) or T <= GEMV_MAX_M or NO_TCGEN05:
         h = moe_gate_up(x, gate_up, ids, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps)
         return moe_down(h, down, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add)
     xin = x
