@@ -1,0 +1,307 @@
+"""Serving engine: scheduler + paged cache + model runner, driven by ``step()`` (synchronously or
+from a background thread).
+
+Parity: the loop the reference sketches but never wires to its HTTP server
+(``metal_marlin/serving/continuous_batch.py:550,614`` + ``metal_marlin/serving/runner.py:157``
+``BatchedModelRunner.execute`` + ``metal_marlin/serving/continuous_engine.py:129``).  Differences by
+design: the KV scatter is one kernel instead of a per-token python loop (runner.py:562); decode
+batches replay a CUDA graph per batch-size bucket with inputs staged through pinned host buffers;
+sampling happens on the device and only token ids cross PCIe.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..kv.paged import PagedKVCache
+from ..models.transformer import BatchMeta, PagedKVStorage, Transformer
+from .request import GenerationRequest, RequestStatus, RunningRequest, SchedulerOutput
+from .scheduler import BatchScheduler, SchedulerConfig
+from .session import SamplingParams
+
+
+@dataclass
+class EngineConfig:
+    num_kv_blocks: int = 512
+    block_size: int = 16
+    max_model_len: int = 4096
+    max_num_seqs: int = 64
+    max_num_batched_tokens: int = 2048
+    max_prefill_tokens: int = 1024
+    max_chunk: int = 512
+    enable_prefix_cache: bool = True
+    use_cuda_graphs: bool = True
+    request_timeout_s: float = 60.0
+    graph_buckets: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)
+
+
+class _DecodeBucket:
+    """Static buffers (+ optional CUDA graph) for decode batches padded to ``B`` rows."""
+
+    def __init__(self, model: Transformer, kv: PagedKVStorage, B: int, max_blocks: int, use_graph: bool):
+        dev = model.device
+        self.model, self.kv, self.B, self.dev = model, kv, B, dev
+        pin = dev.type == "cuda"
+        self.h_ids = torch.zeros(B, dtype=torch.int64, pin_memory=pin)
+        self.h_pos = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
+        self.h_slots = torch.full((B,), -1, dtype=torch.int64, pin_memory=pin)
+        self.h_ctx = torch.ones(B, dtype=torch.int32, pin_memory=pin)
+        self.h_bt = torch.zeros(B, max_blocks, dtype=torch.int32, pin_memory=pin)
+        self.h_f = torch.zeros(4, B, dtype=torch.float32, pin_memory=pin)      # temperature, top_p, min_p, rep_penalty
+        self.h_topk = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
+        self.h_out = torch.zeros(B, dtype=torch.int64, pin_memory=pin)
+        self.ids = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.slots = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.ctx = torch.ones(B, dtype=torch.int32, device=dev)
+        self.bt = torch.zeros(B, max_blocks, dtype=torch.int32, device=dev)
+        self.f = torch.zeros(4, B, dtype=torch.float32, device=dev)
+        self.topk = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.out = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.step_no = torch.zeros(1, dtype=torch.int64, device=dev)
+        cfg = model.cfg
+        self.max_ctx = max_blocks * kv.block_size
+        self.splits = ops.default_splits(B, 1 if cfg.is_mla else cfg.num_key_value_heads, self.max_ctx)
+        self.use_graph = use_graph and dev.type == "cuda"
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.seed = 0
+
+    def _body(self):
+        meta = BatchMeta(positions=self.pos, slots=self.slots, block_tables=self.bt, ctx_lens=self.ctx, decode=True,
+                         max_ctx=self.max_ctx, splits=self.splits)
+        logits = self.model.forward(self.ids, self.kv, meta)
+        ops.sample(logits, temperature=self.f[0], top_k=self.topk, top_p=self.f[1], min_p=self.f[2], seed=self.seed,
+                   offset_dev=self.step_no, out=self.out)
+        self.step_no += 1
+
+    def run(self) -> torch.Tensor:
+        for d, h in ((self.ids, self.h_ids), (self.pos, self.h_pos), (self.slots, self.h_slots), (self.ctx, self.h_ctx),
+                     (self.bt, self.h_bt), (self.f, self.h_f), (self.topk, self.h_topk)):
+            d.copy_(h, non_blocking=True)
+        if self.use_graph:
+            if self.graph is None:
+                s = torch.cuda.Stream(device=self.dev)
+                s.wait_stream(torch.cuda.current_stream(self.dev))
+                with torch.cuda.stream(s):
+                    self._body()
+                torch.cuda.current_stream(self.dev).wait_stream(s)
+                torch.cuda.synchronize(self.dev)
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph):
+                    self._body()
+            self.graph.replay()
+        else:
+            self._body()
+        self.h_out.copy_(self.out, non_blocking=True)
+        if self.dev.type == "cuda":
+            torch.cuda.current_stream(self.dev).synchronize()
+        return self.h_out
+
+
+class LLMEngine:
+    def __init__(self, model: Transformer, config: Optional[EngineConfig] = None):
+        self.model = model
+        self.cfg = config or EngineConfig()
+        c = self.cfg
+        self.kv = PagedKVStorage(model.cfg, c.num_kv_blocks, c.block_size, model.device)
+        self.cache = PagedKVCache(c.num_kv_blocks, c.block_size, enable_prefix_cache=c.enable_prefix_cache,
+                                  copy_fn=self._copy_block)
+        self.scheduler = BatchScheduler(SchedulerConfig(max_num_seqs=c.max_num_seqs,
+                                                        max_num_batched_tokens=c.max_num_batched_tokens,
+                                                        max_prefill_tokens=c.max_prefill_tokens, block_size=c.block_size,
+                                                        max_chunk=c.max_chunk, max_model_len=c.max_model_len), self.cache)
+        self.max_blocks = -(-c.max_model_len // c.block_size)
+        self._buckets: Dict[int, _DecodeBucket] = {}
+        self._lock = threading.RLock()
+        self._thread: Optional[threading.Thread] = None
+        self._stop = threading.Event()
+        self._wake = threading.Event()
+        self.iterations = 0
+        self.tokens_generated = 0
+        self.last_error: Optional[str] = None
+
+    # ------------------------------------------------------------------ cache plumbing
+    def _copy_block(self, src: int, dst: int) -> None:
+        bs = self.cfg.block_size
+        for pool in (self.kv.k, self.kv.v):
+            for t in pool:
+                if t is not None:
+                    t[dst * bs:(dst + 1) * bs].copy_(t[src * bs:(src + 1) * bs])
+
+    # ------------------------------------------------------------------ public API
+    def add_request(self, req: GenerationRequest) -> RunningRequest:
+        if req.timeout_s is None:
+            req.timeout_s = self.cfg.request_timeout_s
+        with self._lock:
+            rr = self.scheduler.add_request(req)
+        self._wake.set()
+        return rr
+
+    def abort(self, request_id: str) -> bool:
+        with self._lock:
+            return self.scheduler.abort(request_id)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    @torch.no_grad()
+    def step(self) -> List[RunningRequest]:
+        """One engine iteration.  Returns the requests that finished in it."""
+        with self._lock:
+            out = self.scheduler.schedule()
+            if out.is_empty:
+                return []
+            sampled: Dict[str, int] = {}
+            if out.prefill:
+                sampled.update(self._run_prefill(out))
+            if out.decode:
+                sampled.update(self._run_decode(out.decode))
+            finished = self.scheduler.step(out, sampled)
+            self.iterations += 1
+            self.tokens_generated += len(sampled)
+            return finished
+
+    def run_until_done(self, max_iters: int = 1 << 30) -> None:
+        it = 0
+        while self.has_work() and it < max_iters:
+            self.step()
+            it += 1
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 16,
+                 sampling: Optional[SamplingParams] = None, eos_ids: Sequence[int] = ()) -> List[List[int]]:
+        rrs = [self.add_request(GenerationRequest(list(p), max_new_tokens, sampling or SamplingParams(), eos_ids))
+               for p in prompts]
+        if self._thread is None:
+            self.run_until_done()
+        else:
+            for rr in rrs:
+                rr.done.wait()
+        return [rr.output_ids for rr in rrs]
+
+    # ------------------------------------------------------------------ background loop
+    def start(self) -> None:
+        if self._thread is not None:
+            return
+        self._stop.clear()
+        self._thread = threading.Thread(target=self._loop, name="mmb200-engine", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        self._wake.set()
+        if self._thread is not None:
+            self._thread.join(timeout=10)
+            self._thread = None
+
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            if not self.has_work():
+                self._wake.wait(timeout=0.05)
+                self._wake.clear()
+                continue
+            try:
+                self.step()
+            except Exception as e:      # fail every in-flight request rather than wedging the server
+                self.last_error = repr(e)
+                with self._lock:
+                    for rr in list(self.scheduler.running):
+                        rr.error = repr(e)
+                        self.scheduler.running.remove(rr)
+                        self.cache.release(rr.id)
+                        rr.transition(RequestStatus.FAILED)
+
+    # ------------------------------------------------------------------ model execution
+    def _run_prefill(self, out: SchedulerOutput) -> Dict[str, int]:
+        dev = self.model.device
+        bs = self.cfg.block_size
+        ids: List[int] = []
+        pos: List[int] = []
+        slots: List[int] = []
+        cu = [0]
+        ctx = []
+        tables = []
+        for ch in out.prefill:
+            rr = ch.request
+            toks = rr.all_ids[ch.start:ch.start + ch.length]
+            ids.extend(toks)
+            pos.extend(range(ch.start, ch.start + ch.length))
+            slots.extend(self.cache.table.slot_mapping(rr.id, ch.start, ch.length))
+            cu.append(cu[-1] + ch.length)
+            ctx.append(ch.start + ch.length)
+            tables.append(self.cache.table.block_table(rr.id))
+        width = max(len(t) for t in tables)
+        bt = torch.tensor([t + [0] * (width - len(t)) for t in tables], dtype=torch.int32, device=dev)
+        meta = BatchMeta(positions=torch.tensor(pos, dtype=torch.int32, device=dev),
+                         slots=torch.tensor(slots, dtype=torch.int64, device=dev), block_tables=bt,
+                         ctx_lens=torch.tensor(ctx, dtype=torch.int32, device=dev), decode=False, cu_seqlens=cu,
+                         ctx_lens_host=ctx)
+        logits = self.model.forward(torch.tensor(ids, dtype=torch.int64, device=dev), self.kv, meta, last_only=True)
+        # sample a first token only for requests whose prefill completes now and that have no output yet
+        rows, reqs = [], []
+        for j, ch in enumerate(out.prefill):
+            rr = ch.request
+            if ch.start + ch.length >= rr.prefill_target and not rr.output_ids:
+                rows.append(j)
+                reqs.append(rr)
+        if not rows:
+            return {}
+        lg = logits[rows].contiguous()
+        toks = self._sample(lg, reqs)
+        return {rr.id: int(t) for rr, t in zip(reqs, toks)}
+
+    def _sample(self, logits: torch.Tensor, reqs: List[RunningRequest]) -> List[int]:
+        dev = logits.device
+        sp = [r.req.sampling for r in reqs]
+        if all(p.temperature <= 0 for p in sp):
+            return ops.argmax(logits).tolist()
+        t = torch.tensor([p.temperature for p in sp], dtype=torch.float32, device=dev)
+        k = torch.tensor([p.top_k for p in sp], dtype=torch.int32, device=dev)
+        tp = torch.tensor([p.top_p for p in sp], dtype=torch.float32, device=dev)
+        mp = torch.tensor([p.min_p for p in sp], dtype=torch.float32, device=dev)
+        return ops.sample(logits, temperature=t, top_k=k, top_p=tp, min_p=mp, seed=sp[0].seed,
+                          offset=(1 << 32) + self.iterations).tolist()
+
+    def _bucket(self, n: int) -> _DecodeBucket:
+        B = next((b for b in self.cfg.graph_buckets if b >= n), n)
+        bk = self._buckets.get(B)
+        if bk is None:
+            bk = _DecodeBucket(self.model, self.kv, B, self.max_blocks, self.cfg.use_cuda_graphs)
+            self._buckets[B] = bk
+        return bk
+
+    def _run_decode(self, reqs: List[RunningRequest]) -> Dict[str, int]:
+        bk = self._bucket(len(reqs))
+        bs = self.cfg.block_size
+        bk.h_slots.fill_(-1)
+        bk.h_ctx.fill_(1)
+        bk.h_pos.zero_()
+        bk.h_ids.zero_()
+        bk.h_f.zero_()
+        bk.h_f[1].fill_(1.0)
+        bk.h_f[3].fill_(1.0)
+        bk.h_topk.zero_()
+        for i, rr in enumerate(reqs):
+            n = self.cache.table.num_tokens(rr.id)         # includes the slot appended for this step's input
+            blocks = self.cache.table.block_table(rr.id)
+            bk.h_ids[i] = rr.output_ids[-1]
+            bk.h_pos[i] = n - 1
+            bk.h_ctx[i] = n
+            bk.h_slots[i] = blocks[(n - 1) // bs] * bs + (n - 1) % bs
+            bk.h_bt[i, : len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
+            sp = rr.req.sampling
+            bk.h_f[0, i], bk.h_f[1, i], bk.h_f[2, i], bk.h_f[3, i] = sp.temperature, sp.top_p, sp.min_p, sp.repetition_penalty
+            bk.h_topk[i] = sp.top_k
+            bk.seed = sp.seed
+        out = bk.run()
+        return {rr.id: int(out[i]) for i, rr in enumerate(reqs)}
+
+    # ------------------------------------------------------------------ introspection
+    def stats(self) -> dict:
+        s = self.scheduler.stats()
+        s.update(iterations=self.iterations, tokens_generated=self.tokens_generated, last_error=self.last_error)
+        return s

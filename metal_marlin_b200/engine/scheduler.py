@@ -1,0 +1,246 @@
+"""Continuous-batching scheduler: per-iteration token budgets, decode-first planning, chunked
+prefill, priorities with starvation promotion, preemption by recompute, FCFS variant.
+
+Parity: reference ``metal_marlin/serving/continuous_batch.py``: ``SchedulerConfig`` (max_num_seqs 64,
+max_num_batched_tokens 2048, max_prefill_tokens 1024, chunk 512, starvation 30 s), ``PreemptionPolicy``,
+``IterationPlanner.plan_iteration`` ``:374`` (phase 1: one decode token per running sequence, phase 2:
+prefill chunks inside the remaining budget), ``BatchScheduler.schedule`` ``:550`` / ``step`` ``:614`` /
+``_preempt`` ``:663`` / ``_check_starvation`` ``:698``; ``metal_marlin/serving/scheduler.py:329``
+(``FCFSScheduler``, queue-full error, insertion policies).
+"""
+from __future__ import annotations
+
+import enum
+import heapq
+import itertools
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+from ..kv.paged import OutOfBlocks, PagedKVCache
+from .request import (GenerationRequest, PrefillChunk, RequestPriority, RequestStatus, RunningRequest,
+                      SchedulerOutput)
+
+
+class PreemptionPolicy(enum.Enum):
+    MOST_TOKENS = "most_tokens"
+    LEAST_TOKENS = "least_tokens"
+    OLDEST = "oldest"
+    LOWEST_PRIORITY = "lowest_priority"
+
+
+class QueueFullError(RuntimeError):
+    pass
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_seqs: int = 64
+    max_num_batched_tokens: int = 2048
+    max_prefill_tokens: int = 1024
+    block_size: int = 16
+    enable_chunked_prefill: bool = True
+    max_chunk: int = 512
+    starvation_s: float = 30.0
+    preemption_policy: PreemptionPolicy = PreemptionPolicy.LOWEST_PRIORITY
+    max_waiting: int = 4096
+    max_model_len: int = 1 << 20
+    fcfs: bool = False                     # ignore priorities: strict arrival order
+
+
+class BatchScheduler:
+    def __init__(self, config: SchedulerConfig, cache: PagedKVCache):
+        self.cfg, self.cache = config, cache
+        self._heap: List = []
+        self._seq = itertools.count()
+        self.running: List[RunningRequest] = []
+        self.requests: Dict[str, RunningRequest] = {}
+        self.num_preemptions = 0
+        self.num_finished = 0
+
+    # ------------------------------------------------------------------ queue
+    def add_request(self, req: GenerationRequest) -> RunningRequest:
+        if len(self._heap) >= self.cfg.max_waiting:
+            raise QueueFullError(f"waiting queue is full ({self.cfg.max_waiting})")
+        if len(req.prompt_ids) + req.max_new_tokens > self.cfg.max_model_len:
+            raise ValueError("context_length_exceeded")
+        rr = RunningRequest(req)
+        self.requests[rr.id] = rr
+        self._push(rr)
+        return rr
+
+    def _push(self, rr: RunningRequest) -> None:
+        pr = 0 if self.cfg.fcfs else -rr.effective_priority
+        heapq.heappush(self._heap, (pr, rr.arrival, next(self._seq), rr))
+
+    @property
+    def num_waiting(self) -> int:
+        return len(self._heap)
+
+    def has_work(self) -> bool:
+        return bool(self._heap or self.running)
+
+    def abort(self, request_id: str) -> bool:
+        rr = self.requests.get(request_id)
+        if rr is None or rr.status in (RequestStatus.FINISHED, RequestStatus.ABORTED, RequestStatus.FAILED):
+            return False
+        if rr in self.running:
+            self.running.remove(rr)
+            self.cache.release(rr.id)
+        else:
+            self._heap = [e for e in self._heap if e[3] is not rr]
+            heapq.heapify(self._heap)
+            if self.cache.table.has(rr.id):
+                self.cache.release(rr.id)
+        rr.finish_reason = "abort"
+        rr.transition(RequestStatus.ABORTED)
+        return True
+
+    # ------------------------------------------------------------------ policy helpers
+    def _check_starvation(self) -> None:
+        if self.cfg.fcfs:
+            return
+        now = time.monotonic()
+        changed = False
+        for i, (pr, arr, seq, rr) in enumerate(self._heap):
+            if now - arr > self.cfg.starvation_s and rr.effective_priority < int(RequestPriority.REALTIME):
+                rr.effective_priority += 1
+                self._heap[i] = (-rr.effective_priority, now, seq, rr)     # restart its clock after a promotion
+                changed = True
+        if changed:
+            heapq.heapify(self._heap)
+
+    def _pick_victim(self, exclude=()) -> Optional[RunningRequest]:
+        cands = [r for r in self.running if r not in exclude]
+        if not cands:
+            return None
+        pol = self.cfg.preemption_policy
+        if pol is PreemptionPolicy.MOST_TOKENS:
+            return max(cands, key=lambda r: len(r.all_ids))
+        if pol is PreemptionPolicy.LEAST_TOKENS:
+            return min(cands, key=lambda r: len(r.all_ids))
+        if pol is PreemptionPolicy.OLDEST:
+            return min(cands, key=lambda r: r.arrival)
+        return min(cands, key=lambda r: (r.effective_priority, -r.arrival))
+
+    def _preempt(self, rr: RunningRequest) -> None:
+        """Free the sequence's KV and queue it again; its cache is recomputed on resume."""
+        self.running.remove(rr)
+        self.cache.release(rr.id)
+        rr.prefill_progress = 0
+        rr.cached_prefix = 0
+        rr.num_preemptions += 1
+        self.num_preemptions += 1
+        rr.transition(RequestStatus.PREEMPTED)
+        self._push(rr)
+
+    # ------------------------------------------------------------------ planning
+    def schedule(self) -> SchedulerOutput:
+        out = SchedulerOutput()
+        self._check_starvation()
+        budget = self.cfg.max_num_batched_tokens
+        # phase 1: every fully prefilled running sequence decodes one token; grow its KV by one slot
+        order = sorted(self.running, key=lambda r: (-r.effective_priority, r.arrival))
+        for rr in order:
+            if rr not in self.running or rr.status is not RequestStatus.RUNNING:
+                continue
+            if budget <= 0:
+                break
+            while True:
+                try:
+                    self.cache.append(rr.id, 1)
+                    break
+                except OutOfBlocks:
+                    victim = self._pick_victim(exclude=(rr,))
+                    if victim is None or victim.effective_priority > rr.effective_priority:
+                        victim = rr
+                    out.preempted.append(victim)
+                    if victim in out.decode:
+                        out.decode.remove(victim)
+                        budget += 1
+                    self._preempt(victim)
+                    if victim is rr:
+                        break
+            if rr in self.running:
+                out.decode.append(rr)
+                budget -= 1
+        # phase 2: prefill chunks (sequences mid-prefill first, then new admissions)
+        prefill_budget = min(budget, self.cfg.max_prefill_tokens)
+        for rr in [r for r in self.running if r.status is RequestStatus.PREFILLING]:
+            if prefill_budget <= 0:
+                break
+            n = self._chunk_len(rr, prefill_budget)
+            if n > 0:
+                out.prefill.append(PrefillChunk(rr, rr.prefill_progress, n))
+                prefill_budget -= n
+        while self._heap and prefill_budget > 0 and len(self.running) < self.cfg.max_num_seqs:
+            rr = self._heap[0][3]
+            tokens = rr.all_ids[: rr.prefill_target] if rr.output_ids else rr.req.prompt_ids
+            if not self.cfg.enable_chunked_prefill and len(tokens) > prefill_budget and out.prefill:
+                break
+            # room for the whole context plus the first decode slot
+            if not self.cache.can_admit(len(tokens) + 1):
+                break
+            heapq.heappop(self._heap)
+            try:
+                cached = self.cache.admit(rr.id, tokens)
+            except OutOfBlocks:
+                self._push(rr)
+                break
+            rr.cached_prefix = cached
+            rr.prefill_progress = cached
+            rr.transition(RequestStatus.PREFILLING)
+            self.running.append(rr)
+            n = self._chunk_len(rr, prefill_budget)
+            if n > 0:
+                out.prefill.append(PrefillChunk(rr, rr.prefill_progress, n))
+                prefill_budget -= n
+        return out
+
+    def _chunk_len(self, rr: RunningRequest, budget: int) -> int:
+        n = min(rr.remaining_prefill, budget)
+        if self.cfg.enable_chunked_prefill:
+            n = min(n, self.cfg.max_chunk)
+        elif n < rr.remaining_prefill:
+            return 0
+        return n
+
+    # ------------------------------------------------------------------ after the model ran
+    def step(self, out: SchedulerOutput, sampled: Dict[str, int]) -> List[RunningRequest]:
+        """Account for an executed iteration.  ``sampled`` maps request id -> new token for every
+        decode request and for every request whose prefill completed in this iteration."""
+        finished = []
+        for ch in out.prefill:
+            rr = ch.request
+            rr.prefill_progress += ch.length
+            if rr.remaining_prefill == 0 and rr.status is RequestStatus.PREFILLING:
+                self.cache.publish(rr.id, rr.req.prompt_ids)
+                rr.transition(RequestStatus.RUNNING)
+        for rid, tok in sampled.items():
+            rr = self.requests[rid]
+            if rr.status is not RequestStatus.RUNNING:
+                continue
+            rr.append_token(tok)
+            reason = rr.should_stop()
+            if reason is None and rr.req.timeout_s is not None and time.monotonic() - rr.arrival > rr.req.timeout_s:
+                reason = "timeout"
+            if reason is not None:
+                rr.finish_reason = reason
+                self.running.remove(rr)
+                self.cache.release(rr.id)
+                rr.transition(RequestStatus.FINISHED)
+                self.num_finished += 1
+                finished.append(rr)
+        return finished
+
+    def stats(self) -> dict:
+        return {"waiting": self.num_waiting, "running": len(self.running), "preemptions": self.num_preemptions,
+                "finished": self.num_finished, "kv": self.cache.stats()}
+
+
+class FCFSScheduler(BatchScheduler):
+    """Strict first-come-first-served variant (no priorities, no starvation promotion)."""
+
+    def __init__(self, config: SchedulerConfig, cache: PagedKVCache):
+        config.fcfs = True
+        super().__init__(config, cache)

@@ -1,0 +1,227 @@
+"""Paged-cache bookkeeping, scheduler policies and the engine loop (CPU).  Behavioural specs taken from the
+reference's tests/test_paged.py, test_cow_cache_manager.py, test_batch_scheduler.py and test_continuous_batch*.py."""
+import pytest
+import torch
+
+from metal_marlin_b200.engine.engine import EngineConfig, LLMEngine
+from metal_marlin_b200.engine.request import (GenerationRequest, IllegalTransition, RequestPriority, RequestStatus,
+                                              RunningRequest)
+from metal_marlin_b200.engine.scheduler import BatchScheduler, PreemptionPolicy, QueueFullError, SchedulerConfig
+from metal_marlin_b200.engine.session import SamplingParams
+from metal_marlin_b200.kv.paged import (BlockAllocator, EvictionPolicy, MultimodalBlockAllocator, OutOfBlocks, PagedKVCache,
+                                        PageTable, PrefixCache)
+from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM
+
+
+# ---------------------------------------------------------------- allocator / page table
+def test_allocator_refcount_and_free():
+    a = BlockAllocator(4, 16)
+    b0, b1 = a.allocate(), a.allocate()
+    assert (b0, b1) == (0, 1) and a.num_free == 2
+    a.incref(b0)
+    a.free(b0)
+    assert a.num_free == 2 and a.ref_count(b0) == 1
+    a.free(b0)
+    assert a.num_free == 3
+    with pytest.raises(AssertionError):
+        a.free(b0)
+    a.allocate_many(3)
+    with pytest.raises(OutOfBlocks):
+        a.allocate()
+
+
+def test_allocator_contiguous_best_fit_and_fragmentation():
+    a = BlockAllocator(12, 16)
+    ids = a.allocate_many(12)
+    for b in (1, 2, 5, 6, 7, 8, 10):
+        a.free(b)
+    assert a.free_runs() == [(1, 2), (5, 4), (10, 1)]
+    assert a.allocate_contiguous(2) == [1, 2]          # smallest run that fits, not the first 4-run
+    assert a.allocate_contiguous(3) == [5, 6, 7]
+    assert 0.0 < a.fragmentation() <= 0.5
+    with pytest.raises(OutOfBlocks):
+        a.allocate_contiguous(3)
+
+
+def test_copy_on_write():
+    a = BlockAllocator(4, 16)
+    copies = []
+    b = a.allocate()
+    assert a.cow(b, lambda s, d: copies.append((s, d))) == b and not copies
+    a.incref(b)
+    nb = a.cow(b, lambda s, d: copies.append((s, d)))
+    assert nb != b and copies == [(b, nb)] and a.ref_count(b) == 1 and a.cow_copies == 1
+
+
+def test_page_table_append_fork_truncate():
+    a = BlockAllocator(8, 4)
+    pt = PageTable(a)
+    pt.add_sequence("a", 6)
+    assert len(pt.block_table("a")) == 2
+    assert pt.slot_mapping("a", 0, 6) == [0, 1, 2, 3, 4, 5]
+    pt.fork("a", "b")
+    assert a.ref_count(pt.block_table("a")[1]) == 2
+    slots = pt.append_tokens("b", 1)                      # writes into the shared half-full block -> COW
+    assert pt.block_table("b")[1] != pt.block_table("a")[1] and slots == [pt.block_table("b")[1] * 4 + 2]
+    pt.append_tokens("a", 3)
+    assert pt.num_tokens("a") == 9 and len(pt.block_table("a")) == 3
+    pt.truncate("a", 5)
+    assert pt.num_tokens("a") == 5 and len(pt.block_table("a")) == 2
+    pt.remove("a"), pt.remove("b")
+    assert a.num_free == 8
+
+
+def test_prefix_cache_match_insert_evict():
+    a = BlockAllocator(16, 4)
+    pc = PrefixCache(a, max_blocks=3, policy=EvictionPolicy.LRU)
+    toks = list(range(10))
+    blocks = a.allocate_many(3)
+    assert pc.insert(toks, blocks) == 2                   # only full blocks are cached
+    assert pc.match(toks) == blocks[:2] and a.ref_count(blocks[0]) == 3
+    assert pc.match([0, 1, 2, 3, 99, 5, 6, 7]) == blocks[:1]
+    assert pc.match([9, 9, 9, 9]) == []
+    pc.insert(list(range(100, 108)), a.allocate_many(2))  # exceeds max_blocks -> LRU eviction
+    assert len(pc.table) == 3 and pc.evictions == 1
+
+
+def test_paged_cache_admit_uses_prefix_and_never_the_last_block():
+    kv = PagedKVCache(16, 4)
+    toks = list(range(12))
+    assert kv.admit("a", toks) == 0
+    kv.publish("a", toks)
+    assert kv.admit("b", toks) == 8                       # 12 tokens = 3 full blocks, last one recomputed
+    assert kv.table.block_table("b")[:2] == kv.table.block_table("a")[:2]
+    kv.release("a"), kv.release("b")
+    assert kv.alloc.num_free == 16 - len(kv.prefix.table)
+
+
+def test_multimodal_allocator_shares_image_blocks():
+    a = MultimodalBlockAllocator(16, 4, vision_fraction=0.5)
+    x = a.allocate_image("img", 10)
+    y = a.allocate_image("img", 10)
+    assert x == y and a.ref_count(x[0]) == 2
+    with pytest.raises(OutOfBlocks):
+        a.allocate_image("big", 40)
+    a.release_image("img"), a.release_image("img")
+    assert a.num_free == 16
+
+
+# ---------------------------------------------------------------- request FSM
+def test_request_state_machine():
+    rr = RunningRequest(GenerationRequest([1, 2, 3], 4))
+    with pytest.raises(IllegalTransition):
+        rr.transition(RequestStatus.RUNNING)
+    rr.transition(RequestStatus.PREFILLING)
+    rr.transition(RequestStatus.RUNNING)
+    rr.append_token(7)
+    assert rr.ttft is not None and rr.should_stop() is None
+    rr.transition(RequestStatus.PREEMPTED)
+    assert rr.prefill_target == 3
+    rr.transition(RequestStatus.PREFILLING)
+    rr.transition(RequestStatus.FINISHED)
+    assert rr.done.is_set()
+    with pytest.raises(IllegalTransition):
+        rr.transition(RequestStatus.RUNNING)
+
+
+# ---------------------------------------------------------------- scheduler
+def _sched(blocks=64, **kw):
+    cfg = SchedulerConfig(block_size=4, **kw)
+    return BatchScheduler(cfg, PagedKVCache(blocks, 4, enable_prefix_cache=False))
+
+
+def _drive(s, out, tok=5):
+    sampled = {}
+    for ch in out.prefill:
+        if ch.start + ch.length >= ch.request.prefill_target and not ch.request.output_ids:
+            sampled[ch.request.id] = tok
+    for rr in out.decode:
+        sampled[rr.id] = tok
+    return s.step(out, sampled)
+
+
+def test_chunked_prefill_then_decode_and_budgets():
+    s = _sched(max_num_batched_tokens=16, max_prefill_tokens=8, max_chunk=6)
+    a = s.add_request(GenerationRequest(list(range(10)), 3))
+    o = s.schedule()
+    assert [(c.start, c.length) for c in o.prefill] == [(0, 6)] and not o.decode
+    _drive(s, o)
+    o = s.schedule()
+    assert [(c.start, c.length) for c in o.prefill] == [(6, 4)]
+    _drive(s, o)
+    assert a.status is RequestStatus.RUNNING and a.output_ids == [5]
+    b = s.add_request(GenerationRequest(list(range(20)), 2))
+    o = s.schedule()
+    assert o.decode == [a] and o.prefill[0].request is b and o.prefill[0].length == 6      # decode first, prefill after
+    assert o.num_tokens <= 16
+
+
+def test_priority_order_and_starvation_promotion():
+    s = _sched(max_num_seqs=1, starvation_s=0.0)
+    lo = s.add_request(GenerationRequest([1, 2], 1, priority=RequestPriority.LOW))
+    hi = s.add_request(GenerationRequest([3, 4], 1, priority=RequestPriority.HIGH))
+    o = s.schedule()
+    assert o.prefill[0].request is hi
+    assert lo.effective_priority > int(RequestPriority.LOW)       # promoted while it waited
+
+
+def test_preemption_by_recompute_when_blocks_run_out():
+    s = _sched(blocks=4, preemption_policy=PreemptionPolicy.LOWEST_PRIORITY)
+    a = s.add_request(GenerationRequest(list(range(7)), 8, priority=RequestPriority.HIGH))
+    b = s.add_request(GenerationRequest(list(range(7)), 8, priority=RequestPriority.LOW))
+    _drive(s, s.schedule())
+    assert a.status is RequestStatus.RUNNING and b.status is RequestStatus.RUNNING and s.cache.alloc.num_free == 0
+    _drive(s, s.schedule())                              # both decode into their half-empty second block
+    o = s.schedule()                                     # now each needs a third block: the low-priority one is evicted
+    assert b in o.preempted and b.status is RequestStatus.PREEMPTED and b.prefill_progress == 0
+    assert a in o.decode and s.num_preemptions == 1
+    _drive(s, o)
+    while a.status is not RequestStatus.FINISHED:
+        _drive(s, s.schedule())
+    while b.status is not RequestStatus.FINISHED:
+        _drive(s, s.schedule())
+    assert len(b.output_ids) == 8 and b.num_preemptions >= 1
+    assert s.cache.alloc.num_free == 4
+
+
+def test_queue_full_and_abort():
+    s = _sched(max_waiting=1)
+    a = s.add_request(GenerationRequest([1], 1))
+    with pytest.raises(QueueFullError):
+        s.add_request(GenerationRequest([1], 1))
+    assert s.abort(a.id) and a.status is RequestStatus.ABORTED and not s.has_work()
+
+
+# ---------------------------------------------------------------- engine
+def test_engine_matches_plain_generate_and_reuses_prefixes():
+    lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    prompts = [list(range(1, 40)), list(range(1, 40)) + [77, 78], [9, 8, 7]]
+    want = [lm.generate([p], max_new_tokens=6)[0] for p in prompts]
+    eng = LLMEngine(lm.model, EngineConfig(num_kv_blocks=64, block_size=16, max_model_len=128, max_chunk=16,
+                                           max_prefill_tokens=32, use_cuda_graphs=False))
+    got = eng.generate(prompts, max_new_tokens=6)
+    assert got == want
+    assert eng.cache.alloc.num_free == 64 - len(eng.cache.prefix.table)
+    got2 = eng.generate([prompts[0]], max_new_tokens=6)       # second pass hits the prefix cache
+    assert got2[0] == want[0] and eng.cache.prefix.hits >= 1
+
+
+def test_engine_background_thread_streams_tokens():
+    lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    eng = LLMEngine(lm.model, EngineConfig(num_kv_blocks=32, max_model_len=64, use_cuda_graphs=False))
+    eng.start()
+    seen = []
+    rr = eng.add_request(GenerationRequest([1, 2, 3], 5, on_token=lambda rid, t: seen.append(t)))
+    assert rr.done.wait(30)
+    eng.stop()
+    assert rr.status is RequestStatus.FINISHED and seen == rr.output_ids and len(seen) == 5
+
+
+def test_engine_survives_preemption_with_identical_output():
+    lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    prompts = [list(range(1, 30)), list(range(40, 70))]
+    want = [lm.generate([p], max_new_tokens=10)[0] for p in prompts]
+    eng = LLMEngine(lm.model, EngineConfig(num_kv_blocks=5, block_size=16, max_model_len=64, enable_prefix_cache=False,
+                                           use_cuda_graphs=False))
+    got = eng.generate(prompts, max_new_tokens=10)
+    assert got == want and eng.scheduler.num_preemptions >= 1
