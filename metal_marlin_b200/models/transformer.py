@@ -148,6 +148,7 @@ class BatchMeta:
     max_ctx: Optional[int] = None
     splits: Optional[int] = None
     ctx_lens_host: Optional[List[int]] = None
+    attn_mask: Optional[torch.Tensor] = None     # [T, n_ctx] bool, single-sequence prefill only (tree verification)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -215,6 +216,8 @@ class Transformer:
                 mask = kpos <= qpos
                 if cfg.sliding_window:
                     mask &= kpos > qpos - cfg.sliding_window
+            if meta.attn_mask is not None:
+                mask = meta.attn_mask
             o = F.scaled_dot_product_attention(Q, K, V, attn_mask=mask, is_causal=(mask is None), scale=self.scale,
                                                enable_gqa=(Hq != Hk))
             out[s:e] = o.squeeze(0).transpose(0, 1).reshape(t, Hq * D)
@@ -270,6 +273,8 @@ class Transformer:
             if n_ctx != t:
                 qpos = torch.arange(n_ctx - t, n_ctx, device=q_full.device).unsqueeze(1)
                 mask = tok.unsqueeze(0) <= qpos
+            if meta.attn_mask is not None:
+                mask = meta.attn_mask
             o = F.scaled_dot_product_attention(Q, Kt.expand(1, H, n_ctx, R + dr), Vt.expand(1, H, n_ctx, R), attn_mask=mask,
                                                is_causal=(mask is None), scale=self.scale)
             o_lat = o.squeeze(0).transpose(0, 1).contiguous()       # [t, H, R]

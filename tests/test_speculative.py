@@ -1,0 +1,113 @@
+"""Speculative decoding: verification rules, drafts, adaptive depth, and end-to-end equivalence with
+plain greedy decoding (CPU).  Specs from the reference's tests/test_speculative.py,
+test_token_acceptance.py, test_adaptive_depth.py and test_verify_kernel*.py."""
+import pytest
+import torch
+
+from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM
+from metal_marlin_b200.spec.adaptive import AdaptiveSpeculationController, TokenAcceptanceTracker
+from metal_marlin_b200.spec.draft import EagleDraft, MTPDraft, NGramDraft, SmallModelDraft
+from metal_marlin_b200.spec.engine import SpeculativeEngine
+from metal_marlin_b200.spec.verify import (tree_attention_mask, verify_batch_greedy, verify_greedy, verify_speculative,
+                                           verify_tree_greedy)
+
+
+def test_verify_greedy_prefix_and_bonus():
+    lg = torch.full((4, 10), -5.0)
+    for i, t in enumerate([3, 7, 2, 9]):
+        lg[i, t] = 5.0
+    r = verify_greedy(lg, [3, 7, 1])
+    assert r.num_accepted == 2 and r.next_token == 2
+    r = verify_greedy(lg, [3, 7, 2])
+    assert r.num_accepted == 3 and r.next_token == 9
+    n, nxt = verify_batch_greedy(lg.unsqueeze(0), torch.tensor([[3, 7, 1]]))
+    assert int(n) == 2 and int(nxt) == 2
+
+
+def test_rejection_sampling_preserves_target_distribution():
+    torch.manual_seed(0)
+    V = 6
+    p = torch.softmax(torch.randn(V), -1)
+    q = torch.softmax(torch.randn(V), -1)
+    g = torch.Generator().manual_seed(1)
+    counts = torch.zeros(V)
+    N = 20000
+    for _ in range(N):
+        d = int(torch.multinomial(q, 1, generator=g))
+        r = verify_speculative(torch.stack([p, p]), q.unsqueeze(0), [d], g)
+        counts[d if r.num_accepted == 1 else r.next_token] += 1
+    assert float((counts / N - p).abs().max()) < 0.015
+
+
+def test_deterministic_draft_rejection_excludes_draft_token():
+    p = torch.tensor([[0.0, 1.0, 0.0], [0.2, 0.3, 0.5]])
+    r = verify_speculative(p, None, [0], torch.Generator().manual_seed(0))
+    assert r.num_accepted == 0 and r.next_token == 1
+
+
+def test_tree_mask_and_tree_verify():
+    parents = [-1, -1, 0, 0, 2]
+    m = tree_attention_mask(parents)
+    assert m[4].tolist() == [True, False, True, False, True] and m[1].tolist() == [False, True, False, False, False]
+    V = 8
+    root = torch.zeros(V); root[5] = 1
+    nodes = torch.zeros(5, V)
+    nodes[0, 6] = 1; nodes[2, 7] = 1; nodes[4, 1] = 1
+    path, nxt = verify_tree_greedy(root, nodes, tokens=[5, 4, 6, 3, 7], parents=parents)
+    assert path == [0, 2, 4] and nxt == 1
+
+
+def test_adaptive_depth_and_tracker():
+    c = AdaptiveSpeculationController(depth=4)
+    for _ in range(20):
+        c.update(4, 4)
+    assert c.depth == 8
+    for _ in range(40):
+        c.update(4, 0)
+    assert c.depth == 1
+    t = TokenAcceptanceTracker()
+    t.record([1, 2, 3], 2)
+    t.record([1, 2, 3], 3)
+    assert abs(t.acceptance_rate - 5 / 6) < 1e-9 and t.position_rates()[2] == 0.5
+    assert 2.0 < t.expected_tokens_per_step() < 4.0
+
+
+def test_ngram_draft_learns_repetition():
+    d = NGramDraft(max_n=3)
+    ctx = [1, 2, 3, 4, 1, 2, 3, 4, 1, 2]
+    assert d.propose(ctx, 4).tokens == [3, 4, 1, 2]
+
+
+@pytest.fixture(scope="module")
+def lm():
+    return MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+
+
+@pytest.mark.parametrize("kind", ["ngram", "mtp", "eagle", "self"])
+def test_speculative_greedy_equals_plain_greedy(lm, kind):
+    prompt = [5, 9, 2, 7, 5, 9, 2, 7, 5, 9]
+    want = lm.generate([prompt], max_new_tokens=24)[0]
+    draft = {"ngram": lambda: NGramDraft(), "mtp": lambda: MTPDraft(lm.model, depth=3),
+             "eagle": lambda: EagleDraft(lm.model, width=2, depth=2), "self": lambda: SmallModelDraft(lm, max_len=256)}[kind]()
+    eng = SpeculativeEngine(lm, draft, num_speculative_tokens=3, max_len=256)
+    got, stats = eng.generate(prompt, 24)
+    assert got == want
+    if kind == "self":                      # the target drafting for itself must be accepted every time
+        assert stats.acceptance_rate == 1.0 and stats.tokens_per_step > 2.0
+
+
+def test_speculative_sampling_runs_and_is_seeded(lm):
+    eng = SpeculativeEngine(lm, NGramDraft(), num_speculative_tokens=3, max_len=256)
+    a, _ = eng.generate([1, 2, 3, 1, 2, 3], 16, temperature=0.9, seed=3)
+    b, _ = eng.generate([1, 2, 3, 1, 2, 3], 16, temperature=0.9, seed=3)
+    assert a == b and len(a) == 16
+
+
+def test_pipeline_speculative_api():
+    from metal_marlin_b200.inference.pipeline import MMFP4Pipeline
+    pipe = MMFP4Pipeline.from_config("tiny-llama", device="cpu")
+    plain = pipe("hello hello hello", max_new_tokens=12)
+    pipe.enable_speculative_decoding("ngram", 4)
+    text, stats = pipe.speculative_generate("hello hello hello", max_new_tokens=12)
+    assert text == plain and stats.tokens == 12
+    pipe.close()
