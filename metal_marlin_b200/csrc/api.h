@@ -9,6 +9,22 @@
 extern "C" {
 #endif
 
+// ----------------------------------------------------------------------------- tensor-parallel exchange
+// Optional in-kernel exchange of row-parallel partial sums over NVLink peer memory (see tp_comm.cuh).
+// `in`: this kernel consumes the sum of tp partial slots as its residual delta.
+// `out`: this kernel produces a partial and pushes it into every peer's receive buffer.
+typedef struct {
+  const float* in_buf;              // local fp32 [tp][in_slot_stride] (null = no consumption)
+  const unsigned* in_flags;         // local [tp]
+  long long in_slot_stride;
+  float* const* out_peer_slots;     // device array [tp] (null = no production)
+  unsigned* const* out_peer_flags;  // device array [tp]
+  unsigned* out_counter;            // local, zero between launches
+  const unsigned* step;             // device scalar, incremented once per decode step
+  int* status;                      // optional error word
+  int tp;
+} MmbTpExchange;
+
 // ----------------------------------------------------------------------------- FP4 small-M GEMV
 // Weights are in the device tile layout: int32 [N/16][K/64][32][4]; scales fp16 [N/16][K/gs][8][2].
 typedef struct {
@@ -33,6 +49,7 @@ typedef struct {
   int shared_base;
   long long expert_stride_q; // distance between experts in 16-byte units
   long long expert_stride_s; // distance between experts in 4-byte units
+  MmbTpExchange tpx;         // all-zero = single GPU
 } MmbFp4GemvParams;
 
 int mmb_fp4_gemv(const MmbFp4GemvParams* p, cudaStream_t stream);
@@ -47,6 +64,7 @@ typedef struct {
   int M, N, K, ldx, ldo;
   float eps;
   int out_f32;
+  MmbTpExchange tpx;         // consumer side only
 } MmbBf16GemvParams;
 int mmb_bf16_gemv(const MmbBf16GemvParams* p, cudaStream_t stream);
 
@@ -120,6 +138,7 @@ typedef struct {
   int renorm;
   float routed_scale;
   int n_group, topk_group;   // grouped top-k (DeepSeek/GLM); n_group <= 1 disables
+  MmbTpExchange tpx;         // consumer side only
 } MmbRouterParams;
 int mmb_moe_router(const MmbRouterParams* p, cudaStream_t stream);
 
@@ -140,6 +159,9 @@ typedef struct {
 } MmbSampleParams;
 int mmb_sample(const MmbSampleParams* p, cudaStream_t stream);
 int mmb_argmax(const float* logits, int64_t* out, int B, int V, cudaStream_t stream);
+// Vocab-parallel greedy head (tensor parallel): logits [B, Vloc] is this rank's vocabulary shard.
+int mmb_tp_argmax(const float* logits, int64_t* out, int B, int Vloc, int vocab_offset, const MmbTpExchange* x,
+                  cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -5,17 +5,27 @@
 //  * paged_decode: split-KV flash-decoding.  All query heads that share a KV head form the M
 //                  dimension of the MMA (MLA: every head shares the single 576-d latent, and V is
 //                  its first 512 columns, so one KV tile in shared memory feeds both QK^T and PV).
-//                  KV tiles (64 tokens) arrive through a 2-stage cp.async pipeline.
+//                  KV tiles (64 tokens) arrive through a 2-stage cp.async pipeline; tiles that cannot
+//                  contain this step's token are requested before the kernel waits for its producer.
 //  * decode_merge: log-sum-exp merge of the split partials, optionally followed by the per-head
-//                  MLA value up-projection W_uv.
+//                  MLA value up-projection W_uv.  One thread-block cluster per head: each CTA merges a
+//                  slice of the latent and the slices are exchanged through distributed shared memory.
+#include <cooperative_groups.h>
+
 #include "api.h"
 #include "common.cuh"
+#include "launch.h"
+
+namespace cg = cooperative_groups;
 
 namespace mmb {
 
 // ------------------------------------------------------------------------------------------------
-// mla_prep: grid (H * 4 + 1, ceil(T / 8)), 256 threads.
+// mla_prep: grid (H * ceil(R / 32) + 1, ceil(T / 8)), 256 threads.  Each CTA of the first group owns 32
+// rows of one head's W_uk^T (4 per warp); the weight rows are requested before the query is staged so the
+// DRAM round trip overlaps it.  The last CTA writes the new latent into the paged cache.
 constexpr int kPrepTok = 8;
+constexpr int kPrepRows = 32;
 __global__ void __launch_bounds__(256) mla_prep_kernel(const MmbMlaPrepParams p) {
   __shared__ float red[32];
   extern __shared__ float sm[];   // [kPrepTok][max(dn, R + dr)]
@@ -25,32 +35,46 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const MmbMlaPrepParams p)
   const bf16* q = reinterpret_cast<const bf16*>(p.q);
   bf16* qf = reinterpret_cast<bf16*>(p.q_full);
   const int dq = p.dn + p.dr, dl = p.R + p.dr;
-  if ((int)blockIdx.x < p.H * 4) {
-    const int h = blockIdx.x >> 2, chunk = blockIdx.x & 3;
-    // stage q_nope of the tile's tokens
+  const int n_chunks = (p.R + kPrepRows - 1) / kPrepRows;
+  if ((int)blockIdx.x < p.H * n_chunks) {
+    const int h = blockIdx.x / n_chunks, chunk = blockIdx.x % n_chunks;
+    const bf16* W = reinterpret_cast<const bf16*>(p.w_ukT) + (long long)h * p.R * p.dn;
+    // this warp's four rows; one 16-byte load per lane per row (dn <= 256)
+    uint4 wv[4];
+    int crow[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      crow[r] = chunk * kPrepRows + warp * 4 + r;
+      wv[r] = make_uint4(0, 0, 0, 0);
+      if (crow[r] < p.R && lane * 8 < p.dn) wv[r] = ldg_stream(reinterpret_cast<const uint4*>(W + (long long)crow[r] * p.dn + lane * 8));
+    }
+    pdl_launch_dependents();
+    pdl_wait();
     for (int j = 0; j < nt; ++j)
       for (int d = tid; d < p.dn; d += 256)
         sm[j * p.dn + d] = __bfloat162float(q[(long long)(t0 + j) * p.ld_q + h * dq + d]);
     __syncthreads();
-    const bf16* W = reinterpret_cast<const bf16*>(p.w_ukT) + (long long)h * p.R * p.dn;
-    const int rows_per_chunk = (p.R + 3) / 4;
-    const int c_lo = chunk * rows_per_chunk, c_hi = min(p.R, c_lo + rows_per_chunk);
-    for (int c = c_lo + warp; c < c_hi; c += 8) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      if (crow[r] >= p.R) continue;
+      const uint32_t ww[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
       float acc[kPrepTok];
 #pragma unroll
       for (int j = 0; j < kPrepTok; ++j) acc[j] = 0.f;
-      const bf16* wr = W + (long long)c * p.dn;
-      for (int d = lane * 2; d < p.dn; d += 64) {
-        const float2 wv = __bfloat1622float2(*reinterpret_cast<const bf162*>(wr + d));
+      if (lane * 8 < p.dn) {
 #pragma unroll
-        for (int j = 0; j < kPrepTok; ++j)
-          if (j < nt) acc[j] = fmaf(wv.x, sm[j * p.dn + d], fmaf(wv.y, sm[j * p.dn + d + 1], acc[j]));
+        for (int e = 0; e < 4; ++e) {
+          const float w0 = __uint_as_float(ww[e] << 16), w1 = __uint_as_float(ww[e] & 0xffff0000u);
+#pragma unroll
+          for (int j = 0; j < kPrepTok; ++j)
+            if (j < nt) acc[j] = fmaf(w0, sm[j * p.dn + lane * 8 + 2 * e], fmaf(w1, sm[j * p.dn + lane * 8 + 2 * e + 1], acc[j]));
+        }
       }
 #pragma unroll
       for (int j = 0; j < kPrepTok; ++j) {
         if (j < nt) {
           const float v = warp_sum(acc[j]);
-          if (lane == 0) qf[((long long)(t0 + j) * p.H + h) * dl + c] = __float2bfloat16(v);
+          if (lane == 0) qf[((long long)(t0 + j) * p.H + h) * dl + crow[r]] = __float2bfloat16(v);
         }
       }
     }
@@ -72,6 +96,8 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const MmbMlaPrepParams p)
     }
   } else {
     // latent cache write: RMSNorm(c_kv) | RoPE(k_rope)
+    pdl_launch_dependents();
+    pdl_wait();
     const bf16* kva = reinterpret_cast<const bf16*>(p.kva);
     const bf16* nw = reinterpret_cast<const bf16*>(p.kv_norm_w);
     bf16* cache = reinterpret_cast<bf16*>(p.cache);
@@ -128,31 +154,35 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
 
 constexpr int kTileTok = 64;
 
-template <int DQK, int DV, int MT, bool SHARED_V>
+// NW warps: in QK^T each warp owns 64 / NW token columns, in PV it owns DV / NW value columns.
+template <int DQK, int DV, int MT, bool SHARED_V, int NW>
 struct DecodeSmem {
   static constexpr int KS = DQK + 8;                     // row strides in elements (16-byte skew)
   static constexpr int VS = DV + 8;
   static constexpr int PS = kTileTok + 8;
+  static constexpr int SS = kTileTok + 4;                // fp32 score row stride
   static constexpr size_t q_bytes = (size_t)MT * 16 * KS * 2;
   static constexpr size_t k_bytes = (size_t)kTileTok * KS * 2;
   static constexpr size_t v_bytes = SHARED_V ? 0 : (size_t)kTileTok * VS * 2;
-  static constexpr size_t s_bytes = (size_t)MT * 16 * kTileTok * 4;
+  static constexpr size_t s_bytes = (size_t)MT * 16 * SS * 4;
   static constexpr size_t p_bytes = (size_t)MT * 16 * PS * 2;
   static constexpr size_t total = q_bytes + 2 * (k_bytes + v_bytes) + s_bytes + p_bytes + 3 * MT * 16 * 4;
+  static_assert((64 / NW) % 8 == 0 && (DV / NW) % 16 == 0, "each warp needs whole n8 tiles (pairs of them in PV)");
 };
 
-// grid (splits, Hkv, B), 128 threads.
-template <int DQK, int DV, int MT, bool SHARED_V>
-__global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeParams p) {
-  using L = DecodeSmem<DQK, DV, MT, SHARED_V>;
+// grid (splits, Hkv, B), NW * 32 threads.
+template <int DQK, int DV, int MT, bool SHARED_V, int NW>
+__global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDecodeParams p) {
+  using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW>;
+  constexpr int NT = NW * 32;
+  constexpr int NQ = 64 / NW / 8;       // n8 tiles of token columns per warp in QK^T
+  constexpr int NVT = DV / NW / 8;      // n8 tiles of value columns per warp in PV
   extern __shared__ __align__(128) unsigned char smem[];
   bf16* q_s = reinterpret_cast<bf16*>(smem);
-  bf16* k_s[2];
-  bf16* v_s[2];
-  k_s[0] = reinterpret_cast<bf16*>(smem + L::q_bytes);
-  k_s[1] = reinterpret_cast<bf16*>(smem + L::q_bytes + L::k_bytes + L::v_bytes);
-  v_s[0] = SHARED_V ? k_s[0] : reinterpret_cast<bf16*>(smem + L::q_bytes + L::k_bytes);
-  v_s[1] = SHARED_V ? k_s[1] : reinterpret_cast<bf16*>(smem + L::q_bytes + 2 * L::k_bytes + L::v_bytes);
+  bf16* const k_s0 = reinterpret_cast<bf16*>(smem + L::q_bytes);
+  bf16* const k_s1 = reinterpret_cast<bf16*>(smem + L::q_bytes + L::k_bytes + L::v_bytes);
+  bf16* const v_s0 = SHARED_V ? k_s0 : reinterpret_cast<bf16*>(smem + L::q_bytes + L::k_bytes);
+  bf16* const v_s1 = SHARED_V ? k_s1 : reinterpret_cast<bf16*>(smem + L::q_bytes + 2 * L::k_bytes + L::v_bytes);
   float* s_s = reinterpret_cast<float*>(smem + L::q_bytes + 2 * (L::k_bytes + L::v_bytes));
   bf16* p_s = reinterpret_cast<bf16*>(reinterpret_cast<unsigned char*>(s_s) + L::s_bytes);
   float* row_m = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p_s) + L::p_bytes);
@@ -163,6 +193,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int Gh = p.Hq / p.Hkv;                  // query heads per KV head (<= MT * 16)
+  // ctx_lens / block_tables were written long before the producer of q started, so they may be read now
   const int ctx = p.ctx_lens[b];
   const int lo = (p.window > 0) ? max(0, ctx - p.window) : 0;
   const int lo_al = lo & ~(kTileTok - 1);
@@ -180,8 +211,10 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
   float* pml = p.part_ml + (((long long)b * p.Hq + (long long)hkv * Gh) * p.splits + split) * 2;
 
   if (tile_begin >= tile_end) {   // empty split: neutral partial
+    pdl_launch_dependents();
+    pdl_wait();
     for (int r = 0; r < Gh; ++r) {
-      for (int d = tid; d < DV; d += 128) po[(long long)r * p.splits * DV + d] = 0.f;
+      for (int d = tid; d < DV; d += NT) po[(long long)r * p.splits * DV + d] = 0.f;
       if (tid == 0) {
         pml[(long long)r * p.splits * 2] = -INFINITY;
         pml[(long long)r * p.splits * 2 + 1] = 0.f;
@@ -190,8 +223,43 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
     return;
   }
 
+  auto load_tile = [&](int tile, int buf) {
+    const int tok0 = lo_al + tile * kTileTok;
+    bf16* kd = buf ? k_s1 : k_s0;
+    constexpr int KCH = DQK / 8;
+    for (int i = tid; i < kTileTok * KCH; i += NT) {
+      const int r = i / KCH, c = i % KCH;
+      const int tok = tok0 + r;
+      const bool valid = tok < ctx;
+      long long slot = 0;
+      if (valid) slot = (long long)bt[tok / p.block_size] * p.block_size + (tok % p.block_size);
+      cp_async16(kd + r * L::KS + c * 8, kp + (slot * p.Hkv + hkv) * DQK + c * 8, valid);
+    }
+    if (!SHARED_V) {
+      bf16* vd = buf ? v_s1 : v_s0;
+      constexpr int VCH = DV / 8;
+      for (int i = tid; i < kTileTok * VCH; i += NT) {
+        const int r = i / VCH, c = i % VCH;
+        const int tok = tok0 + r;
+        const bool valid = tok < ctx;
+        long long slot = 0;
+        if (valid) slot = (long long)bt[tok / p.block_size] * p.block_size + (tok % p.block_size);
+        cp_async16(vd + r * L::VS + c * 8, vp + (slot * p.Hkv + hkv) * DV + c * 8, valid);
+      }
+    }
+    cp_async_commit();
+  };
+
+  // The cache row of this step's token (position ctx - 1) is written by the previous kernel; every other
+  // row is older.  A first tile that does not contain it can be requested before waiting.
+  const bool first_is_old = (lo_al + (tile_begin + 1) * kTileTok) <= ctx - 1;
+  if (first_is_old) load_tile(tile_begin, 0);
+  pdl_launch_dependents();
+  pdl_wait();
+  if (!first_is_old) load_tile(tile_begin, 0);
+
   // ---- stage Q (zero padded to MT*16 rows)
-  for (int i = tid; i < MT * 16 * (DQK / 8); i += 128) {
+  for (int i = tid; i < MT * 16 * (DQK / 8); i += NT) {
     const int r = i / (DQK / 8), c = i % (DQK / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < Gh) v = *reinterpret_cast<const uint4*>(q + (long long)r * DQK + c * 8);
@@ -202,32 +270,6 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
     row_l[tid] = 0.f;
   }
 
-  auto load_tile = [&](int tile, int buf) {
-    const int tok0 = lo_al + tile * kTileTok;
-    constexpr int KCH = DQK / 8;
-    for (int i = tid; i < kTileTok * KCH; i += 128) {
-      const int r = i / KCH, c = i % KCH;
-      const int tok = tok0 + r;
-      const bool valid = tok < ctx;
-      long long slot = 0;
-      if (valid) slot = (long long)bt[tok / p.block_size] * p.block_size + (tok % p.block_size);
-      cp_async16(k_s[buf] + r * L::KS + c * 8, kp + (slot * p.Hkv + hkv) * DQK + c * 8, valid);
-    }
-    if (!SHARED_V) {
-      constexpr int VCH = DV / 8;
-      for (int i = tid; i < kTileTok * VCH; i += 128) {
-        const int r = i / VCH, c = i % VCH;
-        const int tok = tok0 + r;
-        const bool valid = tok < ctx;
-        long long slot = 0;
-        if (valid) slot = (long long)bt[tok / p.block_size] * p.block_size + (tok % p.block_size);
-        cp_async16(v_s[buf] + r * L::VS + c * 8, vp + (slot * p.Hkv + hkv) * DV + c * 8, valid);
-      }
-    }
-    cp_async_commit();
-  };
-
-  constexpr int NVT = DV / 4 / 8;   // n8 tiles of V columns per warp
   float o[MT][NVT][4];
 #pragma unroll
   for (int m = 0; m < MT; ++m)
@@ -236,7 +278,6 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[m][n][e] = 0.f;
 
-  load_tile(tile_begin, 0);
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int buf = (tile - tile_begin) & 1;
     if (tile + 1 < tile_end) {
@@ -246,22 +287,24 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
       cp_async_wait<0>();
     }
     __syncthreads();   // tile `buf` (and, first time, Q) visible to all warps
+    const bf16* kt = buf ? k_s1 : k_s0;
+    const bf16* vt = buf ? v_s1 : v_s0;
 
-    // ---- S = Q K^T for this warp's 16 token columns
+    // ---- S = Q K^T for this warp's token columns
     {
-      float s[MT][2][4];
+      float s[MT][NQ][4];
 #pragma unroll
       for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
+        for (int n = 0; n < NQ; ++n)
 #pragma unroll
           for (int e = 0; e < 4; ++e) s[m][n][e] = 0.f;
-      const bf16* kb = k_s[buf] + (warp * 16 + g) * L::KS + 2 * t;
+      const bf16* kb = kt + (warp * (64 / NW) + g) * L::KS + 2 * t;
 #pragma unroll 4
       for (int k0 = 0; k0 < DQK; k0 += 16) {
-        uint32_t bfr[2][2];
+        uint32_t bfr[NQ][2];
 #pragma unroll
-        for (int n = 0; n < 2; ++n) {
+        for (int n = 0; n < NQ; ++n) {
           bfr[n][0] = *reinterpret_cast<const uint32_t*>(kb + n * 8 * L::KS + k0);
           bfr[n][1] = *reinterpret_cast<const uint32_t*>(kb + n * 8 * L::KS + k0 + 8);
         }
@@ -270,21 +313,21 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
           uint32_t a0, a1, a2, a3;
           ldmatrix_x4(a0, a1, a2, a3, q_s + (m * 16 + (lane & 15)) * L::KS + k0 + (lane >> 4) * 8);
 #pragma unroll
-          for (int n = 0; n < 2; ++n) mma_bf16_16816(s[m][n], a0, a1, a2, a3, bfr[n][0], bfr[n][1]);
+          for (int n = 0; n < NQ; ++n) mma_bf16_16816(s[m][n], a0, a1, a2, a3, bfr[n][0], bfr[n][1]);
         }
       }
       const int tok0 = lo_al + tile * kTileTok;
 #pragma unroll
       for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
+        for (int n = 0; n < NQ; ++n)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int r = m * 16 + g + ((e >> 1) << 3);
-            const int c = warp * 16 + n * 8 + 2 * t + (e & 1);
+            const int c = warp * (64 / NW) + n * 8 + 2 * t + (e & 1);
             const int tok = tok0 + c;
             const bool ok = (tok < ctx) && (tok >= lo);
-            s_s[r * kTileTok + c] = ok ? s[m][n][e] * p.scale : -INFINITY;
+            s_s[r * L::SS + c] = ok ? s[m][n][e] * p.scale : -INFINITY;
           }
     }
     __syncthreads();
@@ -292,7 +335,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
     // ---- online softmax: 4 threads per row, 16 columns each
     if (tid < MT * 16 * 4) {
       const int r = tid >> 2, part = tid & 3;
-      const float* sr = s_s + r * kTileTok + part * 16;
+      const float* sr = s_s + r * L::SS + part * 16;
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 16; ++c) mx = fmaxf(mx, sr[c]);
@@ -320,7 +363,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
     }
     __syncthreads();
 
-    // ---- O = O * corr + P V for this warp's DV/4 value columns
+    // ---- O = O * corr + P V for this warp's value columns
     {
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
@@ -333,7 +376,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
           o[m][n][3] *= c1;
         }
       }
-      const bf16* vb = v_s[buf] + warp * (DV / 4);
+      const bf16* vb = vt + warp * (DV / NW);
 #pragma unroll
       for (int k0 = 0; k0 < kTileTok; k0 += 16) {
         uint32_t a[MT][4];
@@ -364,10 +407,10 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
 #pragma unroll
     for (int n = 0; n < NVT; ++n)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
+      for (int e = 0; e < 4; e += 2) {
         const int r = m * 16 + g + ((e >> 1) << 3);
-        const int c = warp * (DV / 4) + n * 8 + 2 * t + (e & 1);
-        if (r < Gh) po[(long long)r * p.splits * DV + c] = o[m][n][e];
+        const int c = warp * (DV / NW) + n * 8 + 2 * t;
+        if (r < Gh) *reinterpret_cast<float2*>(po + (long long)r * p.splits * DV + c) = make_float2(o[m][n][e], o[m][n][e + 1]);
       }
   if (tid < Gh) {
     pml[(long long)tid * p.splits * 2] = row_m[tid];
@@ -376,16 +419,43 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const MmbPagedDecodeP
 }
 
 // ------------------------------------------------------------------------------------------------
-// decode_merge: grid (Hq, ceil(B / 8)), 256 threads.
+// decode_merge: grid (Hq * CL, ceil(B / 8)) in clusters of CL CTAs (one cluster per head), 256 threads.
+// CTA c of a cluster merges latent columns [c * dv / CL, (c + 1) * dv / CL) of every token of the tile and
+// writes them into the shared memory of all CTAs of the cluster (DSMEM); after the cluster barrier each CTA
+// applies its 32-row slab of W_uv (requested before anything else) to the full merged latent.
 constexpr int kMergeTok = 8;
+constexpr int kMergeRows = 32;
 __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restrict__ part_o,
                                                            const float* __restrict__ part_ml,
                                                            const bf16* __restrict__ w_uv, bf16* __restrict__ out, int B,
-                                                           int Hq, int dv, int dvo, int splits) {
+                                                           int Hq, int dv, int dvo, int splits, int CL) {
   extern __shared__ float o_s[];   // [kMergeTok][dv]
-  const int h = blockIdx.x, b0 = blockIdx.y * kMergeTok;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = (CL > 1) ? (int)cluster.block_rank() : 0;
+  const int h = blockIdx.x / CL, b0 = blockIdx.y * kMergeTok;
   const int nb = min(kMergeTok, B - b0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // weight rows of this warp: slabs of 32 rows, slab index = crank, crank + CL, ...; the first slab's rows are
+  // requested now (up to two 16-byte loads per lane per row, dv <= 512)
+  uint4 wv[4][2];
+  const bf16* W = (w_uv != nullptr) ? w_uv + (long long)h * dvo * dv : nullptr;
+  if (W != nullptr) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int row = crank * kMergeRows + warp * 4 + r;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int d = u * 256 + lane * 8;
+        wv[r][u] = (row < dvo && d < dv) ? ldg_stream(reinterpret_cast<const uint4*>(W + (long long)row * dv + d))
+                                         : make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  // ---- merge this CTA's column slice
+  const int per = (dv + CL - 1) / CL;
+  const int d_lo = crank * per, d_hi = min(dv, d_lo + per);
   for (int j = 0; j < nb; ++j) {
     const long long base = ((long long)(b0 + j) * Hq + h) * splits;
     float M = -INFINITY;
@@ -396,55 +466,66 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
       if (ls > 0.f) Lsum += ls * __expf(ms - M);
     }
     const float inv = (Lsum > 0.f) ? 1.f / Lsum : 0.f;
-    for (int d = tid; d < dv; d += 256) {
+    for (int d = d_lo + tid; d < d_hi; d += 256) {
       float acc = 0.f;
       for (int s = 0; s < splits; ++s) {
         const float ms = part_ml[(base + s) * 2], ls = part_ml[(base + s) * 2 + 1];
         if (ls > 0.f) acc += part_o[(base + s) * dv + d] * __expf(ms - M);
       }
-      o_s[j * dv + d] = acc * inv;
-    }
-  }
-  __syncthreads();
-  if (w_uv == nullptr) {
-    for (int j = 0; j < nb; ++j)
-      for (int d = tid; d < dv; d += 256) out[((long long)(b0 + j) * Hq + h) * dv + d] = __float2bfloat16(o_s[j * dv + d]);
-    return;
-  }
-  // round the merged latent to bf16 first (matches an unfused pipeline that stores it)
-  for (int i = tid; i < nb * dv; i += 256) o_s[i] = __bfloat162float(__float2bfloat16(o_s[i]));
-  __syncthreads();
-  const bf16* W = w_uv + (long long)h * dvo * dv;
-  for (int r = warp; r < dvo; r += 8) {
-    float acc[kMergeTok];
-#pragma unroll
-    for (int j = 0; j < kMergeTok; ++j) acc[j] = 0.f;
-    const bf16* wr = W + (long long)r * dv;
-    for (int d = lane * 8; d < dv; d += 256) {
-      const uint4 wv = *reinterpret_cast<const uint4*>(wr + d);
-      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float w0 = __uint_as_float(ww[e] << 16), w1 = __uint_as_float(ww[e] & 0xffff0000u);
-#pragma unroll
-        for (int j = 0; j < kMergeTok; ++j)
-          if (j < nb) acc[j] = fmaf(w0, o_s[j * dv + d + 2 * e], fmaf(w1, o_s[j * dv + d + 2 * e + 1], acc[j]));
+      // round the merged latent to bf16 (an unfused pipeline would store it in bf16)
+      const float v = __bfloat162float(__float2bfloat16(acc * inv));
+      if (CL > 1) {
+        for (int c = 0; c < CL; ++c) cluster.map_shared_rank(o_s, c)[j * dv + d] = v;
+      } else {
+        o_s[j * dv + d] = v;
       }
     }
+  }
+  if (CL > 1) cluster.sync();
+  else __syncthreads();
+  if (W == nullptr) {
+    for (int j = 0; j < nb; ++j)
+      for (int d = d_lo + tid; d < d_hi; d += 256) out[((long long)(b0 + j) * Hq + h) * dv + d] = __float2bfloat16(o_s[j * dv + d]);
+    return;
+  }
+  for (int slab = crank; slab * kMergeRows < dvo; slab += CL) {
 #pragma unroll
-    for (int j = 0; j < kMergeTok; ++j) {
-      if (j < nb) {
-        const float v = warp_sum(acc[j]);
-        if (lane == 0) out[((long long)(b0 + j) * Hq + h) * dvo + r] = __float2bfloat16(v);
+    for (int r = 0; r < 4; ++r) {
+      const int row = slab * kMergeRows + warp * 4 + r;
+      if (row >= dvo) continue;
+      float acc[kMergeTok];
+#pragma unroll
+      for (int j = 0; j < kMergeTok; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int d = u * 256 + lane * 8;
+        if (d < dv) {
+          const uint4 w4 = (slab == crank) ? wv[r][u] : ldg_stream(reinterpret_cast<const uint4*>(W + (long long)row * dv + d));
+          const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float w0 = __uint_as_float(ww[e] << 16), w1 = __uint_as_float(ww[e] & 0xffff0000u);
+#pragma unroll
+            for (int j = 0; j < kMergeTok; ++j)
+              if (j < nb) acc[j] = fmaf(w0, o_s[j * dv + d + 2 * e], fmaf(w1, o_s[j * dv + d + 2 * e + 1], acc[j]));
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kMergeTok; ++j) {
+        if (j < nb) {
+          const float v = warp_sum(acc[j]);
+          if (lane == 0) out[((long long)(b0 + j) * Hq + h) * dvo + row] = __float2bfloat16(v);
+        }
       }
     }
   }
 }
 
-template <int DQK, int DV, int MT, bool SHARED_V>
+template <int DQK, int DV, int MT, bool SHARED_V, int NW>
 static int launch_decode(const MmbPagedDecodeParams& p, cudaStream_t stream) {
-  using L = DecodeSmem<DQK, DV, MT, SHARED_V>;
-  auto kern = paged_decode_kernel<DQK, DV, MT, SHARED_V>;
+  using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW>;
+  auto kern = paged_decode_kernel<DQK, DV, MT, SHARED_V, NW>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::total);
@@ -452,8 +533,7 @@ static int launch_decode(const MmbPagedDecodeParams& p, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(p.splits, p.Hkv, p.B);
-  kern<<<grid, 128, L::total, stream>>>(p);
-  return (int)cudaGetLastError();
+  return launch(kern, grid, dim3(NW * 32), L::total, stream, 1, p);
 }
 
 }  // namespace mmb
@@ -461,13 +541,12 @@ static int launch_decode(const MmbPagedDecodeParams& p, cudaStream_t stream) {
 MMB_API int mmb_mla_prep(const MmbMlaPrepParams* pp, cudaStream_t stream) {
   const MmbMlaPrepParams& p = *pp;
   if (p.T <= 0) return 0;
-  if ((p.dn & 1) || (p.dr & 1)) return (int)cudaErrorInvalidValue;
+  if ((p.dn & 7) || (p.dr & 1) || p.dn > 256) return (int)cudaErrorInvalidValue;
   const int width = (p.dn > p.R + p.dr) ? p.dn : (p.R + p.dr);
   const size_t smem = (size_t)mmb::kPrepTok * width * 4;
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-  dim3 grid(p.H * 4 + 1, (p.T + mmb::kPrepTok - 1) / mmb::kPrepTok);
-  mmb::mla_prep_kernel<<<grid, 256, smem, stream>>>(p);
-  return (int)cudaGetLastError();
+  dim3 grid(p.H * ((p.R + mmb::kPrepRows - 1) / mmb::kPrepRows) + 1, (p.T + mmb::kPrepTok - 1) / mmb::kPrepTok);
+  return mmb::launch(mmb::mla_prep_kernel, grid, dim3(256), smem, stream, 1, p);
 }
 
 MMB_API int mmb_paged_decode(const MmbPagedDecodeParams* pp, cudaStream_t stream) {
@@ -477,22 +556,27 @@ MMB_API int mmb_paged_decode(const MmbPagedDecodeParams* pp, cudaStream_t stream
   if (p.Hq % p.Hkv != 0 || p.splits < 1) return (int)cudaErrorInvalidValue;
   const int Gh = p.Hq / p.Hkv;
   const bool shared = (p.v_pool == nullptr);
-  if (shared && p.dqk == 576 && p.dv == 512 && Gh <= 32) return launch_decode<576, 512, 2, true>(p, stream);
-  if (shared && p.dqk == 96 && p.dv == 64 && Gh <= 16) return launch_decode<96, 64, 1, true>(p, stream);   // tiny MLA (tests)
-  if (!shared && p.dqk == 128 && p.dv == 128 && Gh <= 16) return launch_decode<128, 128, 1, false>(p, stream);
-  if (!shared && p.dqk == 64 && p.dv == 64 && Gh <= 16) return launch_decode<64, 64, 1, false>(p, stream);
-  if (!shared && p.dqk == 256 && p.dv == 256 && Gh <= 16) return launch_decode<256, 256, 1, false>(p, stream);
+  if (shared && p.dqk == 576 && p.dv == 512 && Gh <= 32) return launch_decode<576, 512, 2, true, 8>(p, stream);
+  if (shared && p.dqk == 96 && p.dv == 64 && Gh <= 16) return launch_decode<96, 64, 1, true, 4>(p, stream);   // tiny MLA (tests)
+  if (!shared && p.dqk == 128 && p.dv == 128 && Gh <= 16) return launch_decode<128, 128, 1, false, 8>(p, stream);
+  if (!shared && p.dqk == 64 && p.dv == 64 && Gh <= 16) return launch_decode<64, 64, 1, false, 4>(p, stream);
+  if (!shared && p.dqk == 256 && p.dv == 256 && Gh <= 16) return launch_decode<256, 256, 1, false, 8>(p, stream);
   return (int)cudaErrorNotSupported;
 }
 
 MMB_API int mmb_decode_merge(const float* part_o, const float* part_ml, const void* w_uv, void* out, int B, int Hq, int dv,
                              int dvo, int splits, cudaStream_t stream) {
   if (B <= 0) return 0;
-  if (dv % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (dv % 8 != 0 || dv > 512) return (int)cudaErrorInvalidValue;
   const size_t smem = (size_t)mmb::kMergeTok * dv * 4;
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-  dim3 grid(Hq, (B + mmb::kMergeTok - 1) / mmb::kMergeTok);
-  mmb::decode_merge_kernel<<<grid, 256, smem, stream>>>(part_o, part_ml, (const bf16*)w_uv, (bf16*)out, B, Hq, dv, dvo,
-                                                        splits);
-  return (int)cudaGetLastError();
+  // cluster size: one CTA per 32-row slab of the up-projection, at most 8 (portable cluster size)
+  int cl = 1;
+  if (w_uv != nullptr) {
+    const int slabs = (dvo + mmb::kMergeRows - 1) / mmb::kMergeRows;
+    while (cl < 8 && cl < slabs) cl *= 2;
+  }
+  dim3 grid(Hq * cl, (B + mmb::kMergeTok - 1) / mmb::kMergeTok);
+  return mmb::launch(mmb::decode_merge_kernel, grid, dim3(256), smem, stream, cl, part_o, part_ml, (const bf16*)w_uv,
+                     (bf16*)out, B, Hq, dv, dvo, splits, cl);
 }

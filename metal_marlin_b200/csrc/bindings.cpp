@@ -31,9 +31,26 @@ inline int log2i(int64_t v) {
   return s;
 }
 
+// Tensor-parallel exchange descriptor: a CPU int64[9] tensor
+// [in_buf, in_flags, in_slot_stride, out_peer_slots, out_peer_flags, out_counter, step, status, tp] (raw addresses).
+inline void fill_tpx(const OptT& t, MmbTpExchange& x) {
+  if (!t.has_value() || !t->defined()) return;
+  TORCH_CHECK(!t->is_cuda() && t->scalar_type() == at::kLong && t->numel() == 9, "tpx must be a CPU int64[9] tensor");
+  const int64_t* v = t->data_ptr<int64_t>();
+  x.in_buf = reinterpret_cast<const float*>(v[0]);
+  x.in_flags = reinterpret_cast<const unsigned*>(v[1]);
+  x.in_slot_stride = v[2];
+  x.out_peer_slots = reinterpret_cast<float* const*>(v[3]);
+  x.out_peer_flags = reinterpret_cast<unsigned* const*>(v[4]);
+  x.out_counter = reinterpret_cast<unsigned*>(v[5]);
+  x.step = reinterpret_cast<const unsigned*>(v[6]);
+  x.status = reinterpret_cast<int*>(v[7]);
+  x.tp = (int)v[8];
+}
+
 void fp4_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t Kx, int64_t gs,
               const OptT& delta, const OptT& norm_w, const OptT& resid_out, double eps, int64_t act, const OptT& bias,
-              const OptT& out_add) {
+              const OptT& out_add, const OptT& tpx) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1);
@@ -59,6 +76,7 @@ void fp4_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, i
   p.eps = (float)eps;
   p.act = (int)act;
   p.mode = 0;
+  fill_tpx(tpx, p.tpx);
   TORCH_CHECK(qw.size(0) * 16 >= N && x.size(1) >= Kx);
   if (delta.has_value() && delta->defined()) TORCH_CHECK(delta->stride(0) == x.stride(0));
   check(mmb_fp4_gemv(&p, cur_stream()), "fp4_gemv");
@@ -68,7 +86,7 @@ void fp4_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, i
 // mode 2: down; x [T * S, Kx]; out [T, N].
 void fp4_moe_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t Kx, int64_t gs,
                   int64_t mode, const Tensor& ids, const OptT& weights, int64_t n_shared, int64_t shared_base,
-                  const OptT& norm_w, double eps, int64_t act, const OptT& out_add) {
+                  const OptT& norm_w, double eps, int64_t act, const OptT& out_add, const OptT& tpx) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(qw.dim() == 5 && qw.is_contiguous() && sc.is_contiguous(), "expert bank must be [E, N/16, K/64, 32, 4]");
@@ -99,6 +117,7 @@ void fp4_moe_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor ou
   p.topk = (int)ids.size(1);
   p.n_shared = (int)n_shared;
   p.shared_base = (int)shared_base;
+  fill_tpx(tpx, p.tpx);
   p.expert_stride_q = qw.stride(0) / 4;     // int32 elements -> 16-byte units
   p.expert_stride_s = sc.stride(0) / 2;     // fp16 elements -> 4-byte units
   TORCH_CHECK(mode == 1 || mode == 2);
@@ -112,7 +131,8 @@ void fp4_moe_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor ou
   check(mmb_fp4_gemv(&p, cur_stream()), "fp4_moe_gemv");
 }
 
-void bf16_gemv(const Tensor& x, const Tensor& w, Tensor out, const OptT& delta, const OptT& norm_w, double eps) {
+void bf16_gemv(const Tensor& x, const Tensor& w, Tensor out, const OptT& delta, const OptT& norm_w, double eps,
+               const OptT& tpx) {
   check_bf16(x, "x");
   check_bf16(w, "w");
   TORCH_CHECK(w.is_contiguous() && x.stride(1) == 1 && out.stride(1) == 1);
@@ -130,6 +150,7 @@ void bf16_gemv(const Tensor& x, const Tensor& w, Tensor out, const OptT& delta, 
   p.ldo = (int)out.stride(0);
   p.eps = (float)eps;
   p.out_f32 = out.scalar_type() == at::kFloat;
+  fill_tpx(tpx, p.tpx);
   TORCH_CHECK(p.out_f32 || out.scalar_type() == at::kBFloat16);
   check(mmb_bf16_gemv(&p, cur_stream()), "bf16_gemv");
 }
@@ -266,7 +287,8 @@ void decode_merge(const Tensor& part_o, const Tensor& part_ml, const OptT& w_uv,
 
 void moe_router(const Tensor& x, const Tensor& w, const OptT& delta, const OptT& norm_w, const OptT& resid_out,
                 const OptT& bias, Tensor ids, Tensor weights, const OptT& logits_out, const OptT& counts, int64_t topk,
-                double eps, int64_t scoring, bool renorm, double routed_scale, int64_t n_group, int64_t topk_group) {
+                double eps, int64_t scoring, bool renorm, double routed_scale, int64_t n_group, int64_t topk_group,
+                const OptT& tpx) {
   check_bf16(x, "x");
   check_bf16(w, "w");
   TORCH_CHECK(x.is_contiguous() && w.is_contiguous() && ids.is_contiguous() && weights.is_contiguous());
@@ -293,6 +315,7 @@ void moe_router(const Tensor& x, const Tensor& w, const OptT& delta, const OptT&
   p.routed_scale = (float)routed_scale;
   p.n_group = (int)n_group;
   p.topk_group = (int)topk_group;
+  fill_tpx(tpx, p.tpx);
   check(mmb_moe_router(&p, cur_stream()), "moe_router");
 }
 
@@ -333,6 +356,16 @@ void argmax(const Tensor& logits, Tensor out) {
   c10::cuda::CUDAGuard guard(logits.device());
   check(mmb_argmax(logits.data_ptr<float>(), out.data_ptr<int64_t>(), (int)logits.size(0), (int)logits.size(1), cur_stream()),
         "argmax");
+}
+
+void tp_argmax(const Tensor& logits, Tensor out, int64_t vocab_offset, const Tensor& tpx) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.is_contiguous() && logits.dim() == 2);
+  c10::cuda::CUDAGuard guard(logits.device());
+  MmbTpExchange x{};
+  fill_tpx(tpx, x);
+  check(mmb_tp_argmax(logits.data_ptr<float>(), out.data_ptr<int64_t>(), (int)logits.size(0), (int)logits.size(1),
+                      (int)vocab_offset, &x, cur_stream()),
+        "tp_argmax");
 }
 
 // ---- tcgen05 GEMM (prefill / large M)
@@ -440,5 +473,6 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("moe_router", &moe_router);
   m.def("sample", &sample);
   m.def("argmax", &argmax);
+  m.def("tp_argmax", &tp_argmax);
   m.def("fp4_gemm", &fp4_gemm);
 }

@@ -101,6 +101,12 @@ __device__ __forceinline__ void e2m1x8_to_bf16x2_raw(uint32_t q, uint32_t& a0, u
   a3 = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
 }
 
+// Programmatic dependent launch: pdl_launch_dependents() lets the next kernel of the stream start its
+// independent prologue; pdl_wait() blocks until the previous kernel has completed and its writes are visible.
+// Both are no-ops for kernels launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

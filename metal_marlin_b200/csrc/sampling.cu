@@ -11,6 +11,7 @@
 // Randomness: Philox-4x32-10 keyed by (seed), counter (offset, row, index).
 #include "api.h"
 #include "common.cuh"
+#include "tp_comm.cuh"
 
 namespace mmb {
 
@@ -283,7 +284,66 @@ __global__ void __launch_bounds__(kSampThreads) argmax_kernel(const float* __res
   if (threadIdx.x == 0) out[row] = am.i;
 }
 
+// Vocab-parallel greedy head: each rank arg-maxes its vocabulary shard, pushes (value, global index) for
+// every row to all peers, waits for the tp pairs and picks the winner (ties -> lowest index), so all ranks
+// end the step with the same token without moving the logits.  One CTA; B rows are handled in turn.
+__global__ void __launch_bounds__(kSampThreads) tp_argmax_kernel(const float* __restrict__ logits, int64_t* __restrict__ out,
+                                                                 int B, int Vloc, int vocab_offset, const MmbTpExchange x) {
+  __shared__ ArgMax red_am[32];
+  const int tid = threadIdx.x;
+  for (int b = 0; b < B; ++b) {
+    const float* lg = logits + (long long)b * Vloc;
+    ArgMax am;
+    am.v = -INFINITY;
+    am.i = 0x7fffffff;
+    for (int i = tid; i < Vloc; i += kSampThreads) {
+      ArgMax c;
+      c.v = lg[i];
+      c.i = i;
+      am = argmax_combine(am, c);
+    }
+    am = block_argmax(am, red_am);
+    if (tid < x.tp) {
+      float* dst = x.out_peer_slots[tid] + 2 * b;
+      dst[0] = am.v;
+      dst[1] = __int_as_float(am.i + vocab_offset);
+    }
+    __syncthreads();
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < x.tp) st_release_sys(x.out_peer_flags[tid], *x.step);
+  TpIn tin;
+  tin.buf = x.in_buf;
+  tin.flags = x.in_flags;
+  tin.step = x.step;
+  tin.status = x.status;
+  tin.tp = x.tp;
+  tin.slot_stride = x.in_slot_stride;
+  tp_wait(tin);
+  for (int b = tid; b < B; b += kSampThreads) {
+    ArgMax best;
+    best.v = -INFINITY;
+    best.i = 0x7fffffff;
+    for (int r = 0; r < x.tp; ++r) {
+      ArgMax c;
+      c.v = __ldcg(x.in_buf + r * x.in_slot_stride + 2 * b);
+      c.i = __float_as_int(__ldcg(x.in_buf + r * x.in_slot_stride + 2 * b + 1));
+      best = argmax_combine(best, c);
+    }
+    out[b] = best.i;
+  }
+}
+
 }  // namespace mmb
+
+MMB_API int mmb_tp_argmax(const float* logits, int64_t* out, int B, int Vloc, int vocab_offset, const MmbTpExchange* x,
+                          cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (x->tp < 1 || x->tp > 32 || x->out_peer_slots == nullptr || x->in_buf == nullptr) return (int)cudaErrorInvalidValue;
+  mmb::tp_argmax_kernel<<<1, mmb::kSampThreads, 0, stream>>>(logits, out, B, Vloc, vocab_offset, *x);
+  return (int)cudaGetLastError();
+}
 
 MMB_API int mmb_sample(const MmbSampleParams* pp, cudaStream_t stream) {
   const MmbSampleParams& p = *pp;

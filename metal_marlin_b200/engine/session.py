@@ -103,15 +103,18 @@ class DecodeSession:
     def _step_body(self) -> None:
         meta = BatchMeta(positions=self.positions, slots=self.slots, block_tables=self.block_tables,
                          ctx_lens=self.ctx_lens, decode=True, max_ctx=self.max_ctx, splits=self.splits)
+        if getattr(self.model, "tp", None) is not None:
+            self.model.tp.begin_step()
         logits = self.model.forward(self.ids, self.kv, meta)
         self.logits = logits
         if self.use_sampler_filters or self.use_history_penalty:
+            logits = self.model.full_logits(logits)
             ops.sample(logits, temperature=self.temperature, top_k=self.top_k, top_p=self.top_p, min_p=self.min_p,
                        history=self.history if self.use_history_penalty else None,
                        rep_penalty=self.rep_penalty if self.use_history_penalty else None,
                        seed=self.seed, offset=0, offset_dev=self.step_idx, out=self.out_ids, out_logprob=self.logprob)
         else:
-            ops.argmax(logits, out=self.out_ids)
+            self.model.greedy(logits, out=self.out_ids)
         # bookkeeping on device: next token, position, cache slot, history
         bs = self.kv.block_size
         self.ids.copy_(self.out_ids)

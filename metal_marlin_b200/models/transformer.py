@@ -167,14 +167,32 @@ class Transformer:
         self.inv_freq, self.rope_mscale = rope_inv_freq(cfg, rot, self.device)
         self.scale = cfg.softmax_scale()
         self.mtp = None      # optional multi-token-prediction head (spec/mtp.py)
+        # tensor parallelism (parallel/tp.py): a shard keeps only its local heads / vocabulary rows
+        self.tp = None
+        self.n_heads_local = cfg.num_attention_heads
+        self.n_kv_heads_local = cfg.num_key_value_heads
+        self.vocab_range = (0, cfg.vocab_size)
+
+    # ------------------------------------------------------------------ tensor-parallel plumbing
+    def _dargs(self, d) -> dict:
+        """kwargs carrying the pending residual delta into the next op (tensor, or in-kernel exchange)."""
+        if self.tp is not None:
+            return self.tp.consume(d)
+        return {"delta": d}
+
+    def _row_parallel(self, x, W, site: int):
+        if self.tp is not None:
+            return self.tp.row_parallel(x, W, site)
+        return ops.linear(x, W)
 
     # ------------------------------------------------------------------ attention blocks
     def _attn_gqa(self, L: LayerWeights, li: int, h, d, kv: PagedKVStorage, meta: BatchMeta):
         cfg = self.cfg
-        Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.dh
+        Hq, Hk, D = self.n_heads_local, self.n_kv_heads_local, cfg.dh
         T = h.shape[0]
         new_h = torch.empty_like(h) if d is not None else None
-        qkv = ops.linear(h, L.qkv, delta=d, norm_w=L.input_norm, eps=cfg.rms_norm_eps, resid_out=new_h, bias=L.qkv_bias)
+        qkv = ops.linear(h, L.qkv, norm_w=L.input_norm, eps=cfg.rms_norm_eps, resid_out=new_h, bias=L.qkv_bias,
+                         **self._dargs(d))
         if new_h is not None:
             h = new_h
         q = qkv[:, : Hq * D]
@@ -190,14 +208,14 @@ class Transformer:
             o = o.reshape(T, Hq * D)
         else:
             o = self._prefill_attention_gqa(q.reshape(T, Hq, D), kv, li, meta)
-        d = ops.linear(o, L.o)
+        d = self._row_parallel(o, L.o, 2 * li)
         return h, d
 
     def _prefill_attention_gqa(self, q, kv: PagedKVStorage, li: int, meta: BatchMeta):
         """Causal attention of every prompt chunk against its sequence's cached keys (which already
         include this chunk).  Runs per sequence over gathered K/V."""
         cfg = self.cfg
-        Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.dh
+        Hq, Hk, D = self.n_heads_local, self.n_kv_heads_local, cfg.dh
         out = torch.empty(q.shape[0], Hq * D, dtype=torch.bfloat16, device=q.device)
         bs = kv.block_size
         for b in range(len(meta.cu_seqlens) - 1):
@@ -225,10 +243,10 @@ class Transformer:
 
     def _attn_mla(self, L: LayerWeights, li: int, h, d, kv: PagedKVStorage, meta: BatchMeta):
         cfg = self.cfg
-        H, dn, dr, dv, R = cfg.num_attention_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        H, dn, dr, dv, R = self.n_heads_local, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         T = h.shape[0]
         new_h = torch.empty_like(h) if d is not None else None
-        a = ops.linear(h, L.qa_kva, delta=d, norm_w=L.input_norm, eps=cfg.rms_norm_eps, resid_out=new_h)
+        a = ops.linear(h, L.qa_kva, norm_w=L.input_norm, eps=cfg.rms_norm_eps, resid_out=new_h, **self._dargs(d))
         if new_h is not None:
             h = new_h
         if L.q_b is not None:
@@ -249,14 +267,14 @@ class Transformer:
             o = o.reshape(T, H * dv)
         else:
             o = self._prefill_attention_mla(L, q_full, kv, li, meta)
-        d = ops.linear(o, L.o)
+        d = self._row_parallel(o, L.o, 2 * li)
         return h, d
 
     def _prefill_attention_mla(self, L: LayerWeights, q_full, kv: PagedKVStorage, li: int, meta: BatchMeta):
         """Absorbed-form causal prefill: scores and values live in the 576/512-d latent space, all heads
         share the latent keys (an MQA problem), then W_uv lifts the result to v_head_dim per head."""
         cfg = self.cfg
-        H, dr, dv, R = cfg.num_attention_heads, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        H, dr, dv, R = self.n_heads_local, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         out = torch.empty(q_full.shape[0], H * dv, dtype=torch.bfloat16, device=q_full.device)
         bs = kv.block_size
         for b in range(len(meta.cu_seqlens) - 1):
@@ -282,20 +300,23 @@ class Transformer:
         return out
 
     # ------------------------------------------------------------------ MLP blocks
-    def _mlp_dense(self, L: LayerWeights, h, d):
+    def _mlp_dense(self, L: LayerWeights, li: int, h, d):
         cfg = self.cfg
         new_h = torch.empty_like(h)
-        x = ops.linear(h, L.gate_up, delta=d, norm_w=L.post_norm, eps=cfg.rms_norm_eps, resid_out=new_h, act=1)
-        return new_h, ops.linear(x, L.down)
+        x = ops.linear(h, L.gate_up, norm_w=L.post_norm, eps=cfg.rms_norm_eps, resid_out=new_h, act=1, **self._dargs(d))
+        return new_h, self._row_parallel(x, L.down, 2 * li + 1)
 
-    def _mlp_moe(self, L: LayerWeights, h, d, counts=None):
+    def _mlp_moe(self, L: LayerWeights, li: int, h, d, counts=None):
         cfg = self.cfg
         new_h = torch.empty_like(h)
-        ids, wts = ops.moe_router(h, L.router_w, delta=d, norm_w=L.post_norm, eps=cfg.rms_norm_eps, resid_out=new_h,
+        ids, wts = ops.moe_router(h, L.router_w, norm_w=L.post_norm, eps=cfg.rms_norm_eps, resid_out=new_h, **self._dargs(d),
                                   bias=L.router_bias, topk=cfg.num_experts_per_tok,
                                   scoring=1 if cfg.scoring_func == "sigmoid" else 0, renorm=cfg.norm_topk_prob,
                                   routed_scale=cfg.routed_scaling_factor, n_group=cfg.n_group, topk_group=cfg.topk_group,
                                   counts=counts)
+        if self.tp is not None:
+            return new_h, self.tp.moe_row_parallel(new_h, {"norm_w": L.post_norm, "eps": cfg.rms_norm_eps}, L, ids, wts, cfg,
+                                                   2 * li + 1)
         out = ops.moe_forward(new_h, L.gate_up_bank, L.down_bank, ids, wts, n_shared=cfg.n_shared_experts,
                               shared_base=cfg.num_experts, norm_w=L.post_norm, eps=cfg.rms_norm_eps)
         return new_h, out
@@ -311,10 +332,10 @@ class Transformer:
                 h, d = self._attn_mla(L, li, h, d, kv, meta)
             else:
                 h, d = self._attn_gqa(L, li, h, d, kv, meta)
-            if L.gate_up_bank is not None:
-                h, d = self._mlp_moe(L, h, d)
+            if L.router_w is not None:
+                h, d = self._mlp_moe(L, li, h, d)
             else:
-                h, d = self._mlp_dense(L, h, d)
+                h, d = self._mlp_dense(L, li, h, d)
         return h, d
 
     def logits(self, h, d, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -322,12 +343,23 @@ class Transformer:
         if rows is not None:
             h = h.index_select(0, rows)
             d = d.index_select(0, rows) if d is not None else None
-        return ops.bf16_linear(h, self.lm_head, delta=d, norm_w=self.final_norm, eps=self.cfg.rms_norm_eps,
-                               out_dtype=torch.float32)
+        return ops.bf16_linear(h, self.lm_head, norm_w=self.final_norm, eps=self.cfg.rms_norm_eps,
+                               out_dtype=torch.float32, **self._dargs(d))
 
     def final_hidden(self, h, d) -> torch.Tensor:
         """Normalised last hidden state (input of the head / of MTP modules)."""
         return ops.rmsnorm(h, self.final_norm, self.cfg.rms_norm_eps, delta=d)
+
+    def greedy(self, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Arg-max token ids; with a vocabulary-sharded head the shards exchange (max, index) pairs."""
+        if self.tp is not None and self.tp.tp > 1:
+            return self.tp.greedy(logits, self.vocab_range[0], out=out)
+        return ops.argmax(logits, out=out)
+
+    def full_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None and self.tp.tp > 1:
+            return self.tp.gather_logits(logits)
+        return logits
 
     def forward(self, input_ids, kv: PagedKVStorage, meta: BatchMeta, last_only: bool = True) -> torch.Tensor:
         h, d = self.forward_hidden(input_ids, kv, meta)

@@ -114,7 +114,7 @@ def rmsnorm(x, w, eps=1e-6, *, delta=None, resid_out=None, out=None):
 
 
 def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bias=None, out_add=None,
-           out=None, token_tile=0):
+           out=None, token_tile=0, tpx=None):
     """``out = epilogue( prologue(x) @ dequant(W)^T )``; prologue = optional residual add + RMSNorm,
     epilogue = optional bias, SwiGLU over the two row halves (``act=1``), residual add."""
     if not _use_native(x):
@@ -125,9 +125,14 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
     if out is None:
         out = torch.empty(M, n_out, dtype=torch.bfloat16, device=x.device)
     if M <= GEMV_MAX_M or NO_TCGEN05:
+        if (x.data_ptr() & 15) or (x.stride(0) & 7) or (W.in_features & 7):
+            x = x[:, : W.in_features].contiguous()      # the kernel stages activations with 16-byte loads
+            if delta is not None:
+                delta = delta[:, : W.in_features].contiguous()
         K.mmb200.fp4_gemv(x, W.qtile, W.stile, out, W.out_features, W.in_features, W.group_size, delta, norm_w,
-                          resid_out, eps, act, bias, out_add)
+                          resid_out, eps, act, bias, out_add, tpx)
         return out
+    assert tpx is None, "the in-kernel tensor-parallel exchange is a decode (small-M) path"
     # tensor-core path: prologue/epilogue pieces run as their own (memory-bound) kernels
     xin = x
     if norm_w is not None or delta is not None:
@@ -151,15 +156,16 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
     return out
 
 
-def bf16_linear(x, w, *, delta=None, norm_w=None, eps=1e-6, out_dtype=torch.bfloat16, out=None):
+def bf16_linear(x, w, *, delta=None, norm_w=None, eps=1e-6, out_dtype=torch.bfloat16, out=None, tpx=None):
     if not _use_native(x):
         return ref.bf16_linear(x, w, delta=delta, norm_w=norm_w, eps=eps, out_dtype=out_dtype, out=out)
     M = x.shape[0]
     if out is None:
         out = torch.empty(M, w.shape[0], dtype=out_dtype, device=x.device)
     if M <= 64:
-        K.mmb200.bf16_gemv(x, w, out, delta, norm_w, eps)
+        K.mmb200.bf16_gemv(x, w, out, delta, norm_w, eps, tpx)
         return out
+    assert tpx is None
     xin = x
     if norm_w is not None:
         xin = torch.empty_like(x)
@@ -215,10 +221,10 @@ def mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache
 
 
 def default_splits(batch: int, n_kv_heads: int, max_ctx: int, sm_count: int = 148) -> int:
-    """Split-KV factor so that batch * kv_heads * splits covers the SMs, each split >= 2 tiles of 64."""
+    """Split-KV factor so that batch * kv_heads * splits covers the SMs (at least one 64-token tile per split)."""
     tiles = max(1, (max_ctx + 63) // 64)
     want = max(1, sm_count // max(1, batch * n_kv_heads))
-    return int(max(1, min(want, (tiles + 1) // 2, 64)))
+    return int(max(1, min(want, tiles, 64)))
 
 
 def paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, *, Hq, Hkv, dqk, dv, block_size, scale, window=0,
@@ -253,7 +259,8 @@ def paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, *, Hq, Hkv, dqk, 
 
 
 def moe_router(x, w, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, bias=None, topk=4, scoring=0, renorm=True,
-               routed_scale=1.0, n_group=1, topk_group=1, ids=None, weights=None, logits_out=None, counts=None):
+               routed_scale=1.0, n_group=1, topk_group=1, ids=None, weights=None, logits_out=None, counts=None,
+               tpx=None):
     if not _use_native(x):
         i, wt, lg = ref.moe_router(x, w, delta=delta, norm_w=norm_w, eps=eps, resid_out=resid_out, bias=bias, topk=topk,
                                    scoring=scoring, renorm=renorm, routed_scale=routed_scale, n_group=n_group,
@@ -272,7 +279,7 @@ def moe_router(x, w, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, bias=
         ids = torch.empty(T, topk, dtype=torch.int32, device=x.device)
         weights = torch.empty(T, topk, dtype=torch.float32, device=x.device)
     K.mmb200.moe_router(x, w, delta, norm_w, resid_out, bias, ids, weights, logits_out, counts, topk, eps, scoring,
-                        renorm, routed_scale, n_group, topk_group)
+                        renorm, routed_scale, n_group, topk_group, tpx)
     return ids, weights
 
 
@@ -284,18 +291,26 @@ def moe_gate_up(x, bank: FP4ExpertBank, ids, *, n_shared=0, shared_base=0, norm_
     if out is None:
         out = torch.empty(T * S, bank.out_features // 2, dtype=torch.bfloat16, device=x.device)
     K.mmb200.fp4_moe_gemv(x, bank.qtile, bank.stile, out, bank.out_features, bank.in_features, bank.group_size, 1, ids,
-                          None, n_shared, shared_base, norm_w, eps, 1, None)
+                          None, n_shared, shared_base, norm_w, eps, 1, None, None)
     return out
 
 
-def moe_down(h, bank: FP4ExpertBank, ids, weights, *, n_shared=0, shared_base=0, out_add=None, out=None):
+def moe_down(h, bank: FP4ExpertBank, ids, weights, *, n_shared=0, shared_base=0, out_add=None, out=None, tpx=None):
     if not _use_native(h):
         return ref.moe_down(h, bank, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add, out=out)
     T = ids.shape[0]
     if out is None:
         out = torch.empty(T, bank.out_features, dtype=torch.bfloat16, device=h.device)
     K.mmb200.fp4_moe_gemv(h, bank.qtile, bank.stile, out, bank.out_features, bank.in_features, bank.group_size, 2, ids,
-                          weights, n_shared, shared_base, None, 0.0, 0, out_add)
+                          weights, n_shared, shared_base, None, 0.0, 0, out_add, tpx)
+    return out
+
+
+def tp_argmax(logits, vocab_offset: int, tpx, out=None):
+    """Vocab-parallel greedy head: every rank ends with the global arg-max (native path only)."""
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    K.mmb200.tp_argmax(logits, out, int(vocab_offset), tpx)
     return out
 
 
@@ -353,7 +368,9 @@ def _build_tile_list(flat_ids: torch.Tensor, num_experts: int, token_tile: int):
     Returns (order, tile_expert, tile_row0, tile_rows, n_tiles)."""
     n = flat_ids.numel()
     order = torch.argsort(flat_ids, stable=True)
-    counts = torch.bincount(flat_ids, minlength=num_experts)[:num_experts]
+    # scatter_add instead of bincount: no host sync, so the whole routine is CUDA-graph capturable
+    counts = torch.zeros(num_experts, dtype=torch.int64, device=flat_ids.device).scatter_add_(
+        0, flat_ids, torch.ones_like(flat_ids))
     offs = torch.cumsum(counts, 0) - counts
     tiles_per = (counts + token_tile - 1) // token_tile
     tile_end = torch.cumsum(tiles_per, 0)
@@ -369,7 +386,7 @@ def _build_tile_list(flat_ids: torch.Tensor, num_experts: int, token_tile: int):
 
 
 def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *, n_shared=0, shared_base=0,
-                norm_w=None, eps=1e-6, out_add=None, token_tile=128):
+                norm_w=None, eps=1e-6, out_add=None, token_tile=0, tpx=None):
     """Whole expert MLP: ``sum_s w_s * down_e(silu(gate_e(x)) * up_e(x))`` over routed + shared experts.
 
     Few tokens: per-(token, slot) weight-streaming kernels (experts read from device memory ids).
@@ -377,12 +394,16 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
     T, topk = ids.shape
     if (not _use_native(x)) or T <= GEMV_MAX_M or NO_TCGEN05:
         h = moe_gate_up(x, gate_up, ids, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps)
-        return moe_down(h, down, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add)
+        return moe_down(h, down, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add, tpx=tpx)
+    assert tpx is None
     xin = x
     if norm_w is not None:
         xin = torch.empty_like(x)
         K.mmb200.rmsnorm(x, None, norm_w, xin, None, eps)
     st = gemm_status(x.device)
+    if not token_tile:      # smallest MMA N tile that holds the average expert load
+        avg = T * topk / max(1, gate_up.num_experts - n_shared)
+        token_tile = 32 if avg <= 24 else (64 if avg <= 48 else 128)
     inter = gate_up.out_features // 2
     flat = ids.reshape(-1).long()
     order, t_e, t_r0, t_rows, n_tiles = _build_tile_list(flat, gate_up.num_experts, token_tile)

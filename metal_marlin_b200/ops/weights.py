@@ -71,6 +71,21 @@ class FP4Weight:
         s = torch.cat([p.stile for p in parts], 0)
         return cls(q, s, sum(p.out_features for p in parts), p0.in_features, p0.group_size)
 
+    # ------------------------------------------------------------------ tensor-parallel shards
+    def slice_rows(self, r0: int, r1: int) -> "FP4Weight":
+        """Output rows ``[r0, r1)`` (column-parallel shard); bounds must be multiples of 16."""
+        assert r0 % 16 == 0 and (r1 % 16 == 0 or r1 == self.out_features)
+        return FP4Weight(self.qtile[r0 // 16: (r1 + 15) // 16].contiguous(), self.stile[r0 // 16: (r1 + 15) // 16].contiguous(),
+                         r1 - r0, self.in_features, self.group_size)
+
+    def slice_cols(self, k0: int, k1: int) -> "FP4Weight":
+        """Input columns ``[k0, k1)`` (row-parallel shard); bounds must be multiples of max(64, group size)."""
+        unit = max(64, self.group_size)
+        assert k0 % unit == 0 and (k1 % unit == 0 or k1 == self.in_features), (k0, k1, unit)
+        gs = self.group_size
+        return FP4Weight(self.qtile[:, k0 // 64: (k1 + 63) // 64].contiguous(),
+                         self.stile[:, k0 // gs: (k1 + gs - 1) // gs].contiguous(), self.out_features, k1 - k0, gs)
+
     # ------------------------------------------------------------------ views
     @property
     def device(self):
@@ -127,6 +142,19 @@ class FP4ExpertBank:
     @property
     def device(self):
         return self.qtile.device
+
+    def slice_rows(self, ranges) -> "FP4ExpertBank":
+        """Keep the output-row ranges ``[(r0, r1), ...]`` (multiples of 16) of every expert, concatenated."""
+        q = torch.cat([self.qtile[:, r0 // 16: r1 // 16] for r0, r1 in ranges], 1).contiguous()
+        s = torch.cat([self.stile[:, r0 // 16: r1 // 16] for r0, r1 in ranges], 1).contiguous()
+        return FP4ExpertBank(q, s, sum(r1 - r0 for r0, r1 in ranges), self.in_features, self.group_size)
+
+    def slice_cols(self, k0: int, k1: int) -> "FP4ExpertBank":
+        unit = max(64, self.group_size)
+        assert k0 % unit == 0 and (k1 % unit == 0 or k1 == self.in_features), (k0, k1, unit)
+        gs = self.group_size
+        return FP4ExpertBank(self.qtile[:, :, k0 // 64: (k1 + 63) // 64].contiguous(),
+                             self.stile[:, :, k0 // gs: (k1 + gs - 1) // gs].contiguous(), self.out_features, k1 - k0, gs)
 
     def expert(self, e: int) -> FP4Weight:
         return FP4Weight(self.qtile[e], self.stile[e], self.out_features, self.in_features, self.group_size)

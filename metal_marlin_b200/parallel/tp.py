@@ -1,0 +1,272 @@
+"""Tensor parallelism over the GPUs of one node.
+
+Sharding (per layer): attention heads are split across ranks (q_b / q / k / v rows, W_uk / W_uv, o_proj columns);
+MLP and expert intermediate dimensions are split on quantization-group boundaries (gate/up rows, down columns);
+the vocabulary is split for the LM head; small matrices (q_a | kv_a, router, norms, embeddings) are replicated so
+no collective is needed for them, and the MLA latent cache is replicated (it is 576 values per token).
+
+Two ways to combine the row-parallel partial sums:
+
+* ``fused`` (decode, <= 16 tokens): the producing GEMV stores its partial directly into every peer's receive
+  buffer over NVLink and the next kernel sums the tp slots while staging its input (``csrc/tp_comm.cuh``);
+  no collective kernel is launched at all.  The LM head is vocabulary-parallel with an in-kernel exchange of
+  (max, argmax) pairs.
+* ``nccl`` (prefill / large batches and the baseline): ``torch.distributed.all_reduce`` on the partial.
+
+Parity: reference ``metal_marlin/distributed/tensor_parallel.py:61-276`` (``ParallelMode``, ``shard_tensor``,
+``TensorParallelLinear.from_marlin_linear`` ``:341``, column ``:515`` / row ``:546`` forward, simulated
+collectives) and ``metal_marlin/distributed/verification.py:85-509`` (sharded-vs-unsharded equality).
+"""
+from __future__ import annotations
+
+import copy
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..models.transformer import LayerWeights, Transformer
+from .symm import SymmetricBuffer
+
+FUSED_MAX_TOKENS = 16
+
+
+def even_split(n: int, parts: int, unit: int = 1) -> List[Tuple[int, int]]:
+    """Split ``n`` into ``parts`` contiguous ranges whose inner boundaries are multiples of ``unit``; a ragged
+    tail (``n % unit``) goes to the last range."""
+    u = n // unit
+    assert u >= parts, (n, parts, unit)
+    out = [((r * u) // parts * unit, ((r + 1) * u) // parts * unit) for r in range(parts)]
+    out[-1] = (out[-1][0], n)
+    return out
+
+
+@dataclass
+class TPPartial:
+    """Handle for "the sum over ranks of the partials of site ``site``" (not yet materialised)."""
+    site: int
+    rows: int
+
+
+class TPContext:
+    def __init__(self, rank: int, tp: int, device: torch.device, n_sites: int, hidden: int, group=None,
+                 max_tokens: int = FUSED_MAX_TOKENS, mode: str = "fused"):
+        self.rank, self.tp, self.device, self.mode = rank, tp, device, mode
+        self.group = group
+        self.hidden, self.max_tokens, self.n_sites = hidden, max_tokens, n_sites
+        self.fused_ok = mode == "fused" and device.type == "cuda" and ops.native_available()
+        self.slot = max_tokens * hidden                     # fp32 elements per (site, source rank)
+        self.site_bytes = tp * self.slot * 4
+        pair_bytes = tp * max_tokens * 2 * 4
+        flags_off = n_sites * self.site_bytes + pair_bytes
+        self.n_flag_sites = n_sites + 1
+        total = flags_off + self.n_flag_sites * tp * 4
+        self._desc_cache: Dict[Tuple[str, int, int], torch.Tensor] = {}
+        if not self.fused_ok:
+            self.buf = None
+            return
+        self.buf = SymmetricBuffer(total, device, group)
+        self.pairs_off = n_sites * self.site_bytes
+        self.flags_off = flags_off
+        self.step = torch.zeros(1, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(self.n_flag_sites, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        # per site: device arrays of peer addresses (my slot in every peer's buffer, my flag on every peer)
+        slots = torch.empty(self.n_flag_sites, tp, dtype=torch.int64)
+        flags = torch.empty(self.n_flag_sites, tp, dtype=torch.int64)
+        for s in range(self.n_flag_sites):
+            for r in range(tp):
+                if s < n_sites:
+                    slots[s, r] = self.buf.peer_addr(r, s * self.site_bytes + rank * self.slot * 4)
+                else:
+                    slots[s, r] = self.buf.peer_addr(r, self.pairs_off + rank * max_tokens * 2 * 4)
+                flags[s, r] = self.buf.peer_addr(r, flags_off + (s * tp + rank) * 4)
+        self.peer_slots = slots.to(device)
+        self.peer_flags = flags.to(device)
+
+    # ------------------------------------------------------------------ descriptors (CPU int64[9])
+    def _desc(self, kind: str, site: int, rows: int) -> torch.Tensor:
+        key = (kind, site, rows)
+        d = self._desc_cache.get(key)
+        if d is None:
+            base = self.buf.local.data_ptr()
+            v = [0] * 9
+            if kind == "in":
+                v[0] = base + site * self.site_bytes
+                v[1] = base + self.flags_off + site * self.tp * 4
+                v[2] = self.slot
+            elif kind == "out":
+                v[3] = self.peer_slots[site].data_ptr()
+                v[4] = self.peer_flags[site].data_ptr()
+                v[5] = self.counters[site:].data_ptr()
+            else:       # "pairs": vocabulary-parallel arg-max exchange (both directions)
+                v[0] = base + self.pairs_off
+                v[1] = base + self.flags_off + site * self.tp * 4
+                v[2] = self.max_tokens * 2
+                v[3] = self.peer_slots[site].data_ptr()
+                v[4] = self.peer_flags[site].data_ptr()
+            v[6] = self.step.data_ptr()
+            v[7] = self.status.data_ptr()
+            v[8] = self.tp
+            d = torch.tensor(v, dtype=torch.int64)
+            self._desc_cache[key] = d
+        return d
+
+    # ------------------------------------------------------------------ step bookkeeping
+    def begin_step(self) -> None:
+        """Advance the exchange epoch; must run (on every rank) once before each decode step's kernels."""
+        if self.fused_ok:
+            self.step += 1
+
+    def use_fused(self, n_tokens: int) -> bool:
+        return self.fused_ok and n_tokens <= self.max_tokens
+
+    # ------------------------------------------------------------------ producers / consumers
+    def row_parallel(self, x, W, site: int):
+        """Row-parallel linear: returns a :class:`TPPartial` (fused) or the all-reduced tensor (nccl)."""
+        M = x.shape[0]
+        if self.use_fused(M):
+            ops.linear(x, W, tpx=self._desc("out", site, M), out=self._dummy(M, W.out_features))
+            return TPPartial(site, M)
+        y = ops.linear(x, W)
+        return self.all_reduce(y)
+
+    def moe_row_parallel(self, h, x_normed_args, L, ids, wts, cfg, site: int):
+        T = ids.shape[0]
+        if self.use_fused(T):
+            hmid = ops.moe_gate_up(h, L.gate_up_bank, ids, n_shared=cfg.n_shared_experts, shared_base=cfg.num_experts,
+                                   **x_normed_args)
+            ops.moe_down(hmid, L.down_bank, ids, wts, n_shared=cfg.n_shared_experts, shared_base=cfg.num_experts,
+                         tpx=self._desc("out", site, T), out=self._dummy(T, L.down_bank.out_features))
+            return TPPartial(site, T)
+        y = ops.moe_forward(h, L.gate_up_bank, L.down_bank, ids, wts, n_shared=cfg.n_shared_experts,
+                            shared_base=cfg.num_experts, **x_normed_args)
+        return self.all_reduce(y)
+
+    def _dummy(self, m: int, n: int) -> torch.Tensor:
+        key = ("dummy", m, n)
+        t = self._desc_cache.get(key)
+        if t is None:
+            t = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
+            self._desc_cache[key] = t
+        return t
+
+    def consume(self, d) -> dict:
+        """kwargs for the consuming op: either a plain ``delta`` tensor or the in-kernel exchange descriptor."""
+        if isinstance(d, TPPartial):
+            return {"delta": None, "tpx": self._desc("in", d.site, d.rows)}
+        return {"delta": d}
+
+    def all_reduce(self, y: torch.Tensor) -> torch.Tensor:
+        if self.tp > 1:
+            yf = y.to(torch.float32)
+            dist.all_reduce(yf, group=self.group)
+            return yf.to(y.dtype)
+        return y
+
+    def greedy(self, logits_local: torch.Tensor, vocab_offset: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Global arg-max of vocabulary-sharded logits."""
+        B = logits_local.shape[0]
+        if self.use_fused(B):
+            return ops.tp_argmax(logits_local, vocab_offset, self._desc("pairs", self.n_sites, B), out=out)
+        full = self.gather_logits(logits_local)
+        r = full.argmax(-1)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+
+    def gather_logits(self, logits_local: torch.Tensor) -> torch.Tensor:
+        parts = [torch.empty_like(logits_local) for _ in range(self.tp)]
+        dist.all_gather(parts, logits_local.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+    def check(self) -> int:
+        return int(self.status[0].item()) if self.fused_ok else 0
+
+
+# ---------------------------------------------------------------------------------------------
+# sharding
+# ---------------------------------------------------------------------------------------------
+def shard_layer(cfg, L: LayerWeights, rank: int, tp: int) -> Tuple[LayerWeights, dict]:
+    """Returns the rank's shard of one layer and its local dimensions."""
+    S = copy.copy(L)
+    info = {}
+    if cfg.is_mla:
+        H, dn, dr, dv = cfg.num_attention_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        h0, h1 = even_split(H, tp)[rank]
+        info["heads"] = h1 - h0
+        dq = dn + dr
+        if L.q_b is not None:
+            S.q_b = L.q_b.slice_rows(h0 * dq, h1 * dq)
+        else:
+            # direct q projection fused with kv_a: keep q rows of the local heads + all kv_a rows
+            nq = H * dq
+            q = L.qa_kva.slice_rows(h0 * dq, h1 * dq)
+            kv = L.qa_kva.slice_rows(nq, L.qa_kva.out_features)
+            from ..ops import FP4Weight
+            S.qa_kva = FP4Weight.concat_rows([q, kv])
+        S.w_ukT = L.w_ukT[h0:h1].contiguous()
+        S.w_uv = L.w_uv[h0:h1].contiguous()
+        S.o = L.o.slice_cols(h0 * dv, h1 * dv)
+    else:
+        Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.dh
+        assert Hk % tp == 0 or tp % Hk == 0, "kv heads must divide (or be divided by) the tensor-parallel degree"
+        kv_per = max(1, Hk // tp)
+        k0 = (rank * Hk) // tp
+        g = Hq // Hk
+        q0, q1 = (rank * Hq) // tp, ((rank + 1) * Hq) // tp
+        info["heads"], info["kv_heads"] = q1 - q0, kv_per
+        from ..ops import FP4Weight
+        S.qkv = FP4Weight.concat_rows([L.qkv.slice_rows(q0 * D, q1 * D),
+                                       L.qkv.slice_rows((Hq + k0) * D, (Hq + k0 + kv_per) * D),
+                                       L.qkv.slice_rows((Hq + Hk + k0) * D, (Hq + Hk + k0 + kv_per) * D)])
+        if L.qkv_bias is not None:
+            b = L.qkv_bias
+            S.qkv_bias = torch.cat([b[q0 * D:q1 * D], b[(Hq + k0) * D:(Hq + k0 + kv_per) * D],
+                                    b[(Hq + Hk + k0) * D:(Hq + Hk + k0 + kv_per) * D]]).contiguous()
+        S.o = L.o.slice_cols(q0 * D, q1 * D)
+        assert g >= 1
+    if L.gate_up_bank is not None:
+        I = L.gate_up_bank.out_features // 2
+        unit = max(64, L.down_bank.group_size)
+        i0, i1 = even_split(I, tp, unit)[rank]
+        info["moe_inter"] = i1 - i0
+        assert i1 > i0, "tensor-parallel degree exceeds the number of quantization groups of the expert width"
+        S.gate_up_bank = L.gate_up_bank.slice_rows([(i0, i1), (I + i0, I + i1)])
+        S.down_bank = L.down_bank.slice_cols(i0, i1)
+    else:
+        I = L.gate_up.out_features // 2
+        unit = max(64, L.down.group_size)
+        i0, i1 = even_split(I, tp, unit)[rank]
+        from ..ops import FP4Weight
+        S.gate_up = FP4Weight.concat_rows([L.gate_up.slice_rows(i0, i1), L.gate_up.slice_rows(I + i0, I + i1)])
+        S.down = L.down.slice_cols(i0, i1)
+    return S, info
+
+
+def shard_transformer(model: Transformer, rank: int, tp: int, ctx: Optional[TPContext] = None) -> Transformer:
+    """Build the rank's tensor-parallel shard of ``model`` (weights are sliced, not re-quantized)."""
+    cfg = model.cfg
+    layers, infos = [], []
+    for L in model.layers:
+        S, info = shard_layer(cfg, L, rank, tp)
+        layers.append(S)
+        infos.append(info)
+    v0, v1 = even_split(cfg.vocab_size, tp)[rank]
+    head = model.lm_head[v0:v1].contiguous()
+    m = Transformer(cfg, layers, model.embed, model.final_norm, head)
+    m.tp = ctx
+    m.tp_rank, m.tp_size = rank, tp
+    m.vocab_range = (v0, v1)
+    m.n_heads_local = infos[0]["heads"]
+    m.n_kv_heads_local = infos[0].get("kv_heads", 1)
+    return m
+
+
+def make_context(model_cfg, device, group=None, mode: str = "fused", max_tokens: int = FUSED_MAX_TOKENS) -> TPContext:
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    tp = dist.get_world_size(group) if dist.is_initialized() else 1
+    return TPContext(rank, tp, device, 2 * model_cfg.num_hidden_layers, model_cfg.hidden_size, group, max_tokens, mode)

@@ -1,0 +1,151 @@
+"""Per-kernel micro-benchmarks at the flagship model's shapes (GLM-4.7-Flash decode), the target of the
+``ncu`` captures summarised under ``profiles/``.
+
+    python -m metal_marlin_b200.profiling.kernel_bench --op all --iters 20
+    python -m metal_marlin_b200.profiling.kernel_bench --op moe_gate_up --iters 3 --warmup 1      # small: for ncu
+
+Every op is timed with CUDA events on the launching stream after warm-up, with a write of a 256 MB buffer
+between iterations so the 126 MB L2 is cold, and reported with its algorithmic bytes and the fraction of the
+measured copy bandwidth (``MEASURED_PEAKS.json``; 6.65 TB/s fallback).
+
+Parity: the reference's ``benchmarks/`` drivers and ``metal_marlin/profiling/roofline.py:223``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from .. import ops
+from ..ops import FP4ExpertBank, FP4Weight
+
+
+def _peak_gbs() -> float:
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(here, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f).get("hbm_gbs", 6650.0))
+    return 6650.0
+
+
+def _rand_w(n, k, dev):
+    return FP4Weight.from_float(torch.randn(n, k, device=dev) * 0.02, 128)
+
+
+def build_cases(dev, batch: int, ctx: int):
+    H, R, dr, dn, dv, NH = 2048, 512, 64, 192, 256, 20
+    E, I, topk = 64, 1536, 4
+    bf = lambda *s: (torch.randn(*s, device=dev) * 0.5).to(torch.bfloat16)
+    cases = {}
+    x = bf(batch, H)
+    delta = bf(batch, H)
+    nw = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    w_qa = _rand_w(768 + 576, H, dev)
+    cases["qa_kva_gemv"] = (lambda: ops.linear(x, w_qa, delta=delta, norm_w=nw, resid_out=torch.empty_like(x)), w_qa.nbytes())
+    w_qb = _rand_w(NH * 256, 768, dev)
+    a = bf(batch, 1344)
+    nq = torch.ones(768, device=dev, dtype=torch.bfloat16)
+    cases["q_b_gemv"] = (lambda: ops.linear(a[:, :768], w_qb, norm_w=nq), w_qb.nbytes())
+    w_o = _rand_w(H, NH * dv, dev)
+    ao = bf(batch, NH * dv)
+    cases["o_proj_gemv"] = (lambda: ops.linear(ao, w_o), w_o.nbytes())
+    # MLA prologue / attention / epilogue
+    q = bf(batch, NH * (dn + dr))
+    kva = bf(batch, R + dr)
+    w_ukT, w_uv = bf(NH, R, dn), bf(NH, dv, R)
+    nkv = torch.ones(R, device=dev, dtype=torch.bfloat16)
+    bs = 16
+    nb = (ctx + bs) // bs + 1
+    cache = bf(batch * nb * bs, R + dr)
+    bt = torch.arange(batch * nb, dtype=torch.int32, device=dev).view(batch, nb)
+    cl = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
+    pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device=dev)
+    slots = (bt[:, (ctx - 1) // bs].long() * bs + (ctx - 1) % bs)
+    inv = 1.0 / (1e6 ** (torch.arange(0, dr, 2, device=dev).float() / dr))
+    qf = torch.empty(batch, NH, R + dr, dtype=torch.bfloat16, device=dev)
+    cases["mla_prep"] = (lambda: ops.mla_prep(q, kva, w_ukT, nkv, pos, inv, slots, qf, cache, NH, dn, dr, R, 1e-5, 1.0, True),
+                         w_ukT.numel() * 2)
+    splits = ops.default_splits(batch, 1, ctx)
+    cases["mla_decode_attn"] = (lambda: ops.paged_attention(qf, cache, None, bt, cl, Hq=NH, Hkv=1, dqk=R + dr, dv=R, block_size=bs,
+                                                            scale=1 / 16.0, splits=splits, w_uv=w_uv),
+                                batch * ctx * (R + dr) * 2 + w_uv.numel() * 2)
+    # MoE
+    rw = bf(E, H)
+    rb = torch.zeros(E, device=dev)
+    ids = torch.stack([torch.randperm(E, device=dev)[:topk] for _ in range(batch)]).to(torch.int32)
+    wts = torch.rand(batch, topk, device=dev)
+    cases["moe_router"] = (lambda: ops.moe_router(x, rw, delta=delta, norm_w=nw, resid_out=torch.empty_like(x), bias=rb, topk=topk,
+                                                  scoring=1, renorm=True, routed_scale=1.8), rw.numel() * 2)
+    gu = FP4ExpertBank(torch.randint(-2 ** 31, 2 ** 31 - 1, (E + 1, 2 * I // 16, H // 64, 32, 4), dtype=torch.int32, device=dev),
+                       (torch.rand(E + 1, 2 * I // 16, H // 128, 8, 2, device=dev) * 0.01).half(), 2 * I, H, 128)
+    dn_b = FP4ExpertBank(torch.randint(-2 ** 31, 2 ** 31 - 1, (E + 1, H // 16, I // 64, 32, 4), dtype=torch.int32, device=dev),
+                         (torch.rand(E + 1, H // 16, I // 128, 8, 2, device=dev) * 0.01).half(), H, I, 128)
+    slots_per_tok = topk + 1
+    active = min(E, batch * topk) + 1
+    per_exp_gu = 2 * I * H // 2 + 2 * I * (H // 128) * 2
+    per_exp_dn = H * I // 2 + H * (I // 128) * 2
+    cases["moe_gate_up"] = (lambda: ops.moe_gate_up(x, gu, ids, n_shared=1, shared_base=E, norm_w=nw),
+                            (batch * slots_per_tok if batch <= 16 else active) * per_exp_gu)
+    hi = bf(batch * slots_per_tok, I)
+    cases["moe_down"] = (lambda: ops.moe_down(hi, dn_b, ids, wts, n_shared=1, shared_base=E),
+                         (batch * slots_per_tok if batch <= 16 else active) * per_exp_dn)
+    cases["moe_forward"] = (lambda: ops.moe_forward(x, gu, dn_b, ids, wts, n_shared=1, shared_base=E, norm_w=nw),
+                            (batch * slots_per_tok if batch <= 16 else active) * (per_exp_gu + per_exp_dn))
+    head = bf(154880, H)
+    cases["lm_head"] = (lambda: ops.bf16_linear(x, head, delta=delta, norm_w=nw, out_dtype=torch.float32), head.numel() * 2)
+    lg = torch.randn(batch, 154880, device=dev)
+    cases["argmax"] = (lambda: ops.argmax(lg), lg.numel() * 4)
+    # prefill-size GEMMs on the tensor-core path
+    xp = bf(4096, H)
+    w_gu = _rand_w(2 * I, H, dev)
+    cases["gemm_4096x3072x2048"] = (lambda: ops.linear(xp, w_gu), 2.0 * 4096 * 2 * I * H)
+    return cases
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all")
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    assert ops.native_available()
+    cases = build_cases(dev, args.batch, args.ctx)
+    names = list(cases) if args.op == "all" else args.op.split(",")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    peak = _peak_gbs()
+    out = {}
+    for n in names:
+        fn, nbytes = cases[n]
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(args.iters):
+            if not args.no_flush:
+                flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        med = ts[len(ts) // 2]
+        if n.startswith("gemm_"):
+            out[n] = {"us": round(med, 2), "tflops": round(nbytes / med / 1e6, 1)}
+        else:
+            gbs = nbytes / med / 1e3
+            out[n] = {"us": round(med, 2), "MB": round(nbytes / 1e6, 3), "GBps": round(gbs, 1), "frac_of_measured_copy": round(gbs / peak, 3)}
+        print(n, out[n], flush=True)
+    print(json.dumps({"batch": args.batch, "ctx": args.ctx, "results": out}))
+
+
+if __name__ == "__main__":
+    main()

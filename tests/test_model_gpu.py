@@ -16,6 +16,9 @@ def test_decode_logits_match_reference_path(preset):
     torch.manual_seed(0)
     lm = MMFP4ForCausalLM.from_config(preset, device="cuda", seed=1)
     cfg = lm.config
+    for L in lm.model.layers:          # decisive routing: bf16-level noise must not flip an expert choice
+        if L.router_w is not None:
+            L.router_w.mul_(16.0)
     prompts = [torch.randint(0, cfg.vocab_size, (n,)).tolist() for n in (37, 5, 64)]
     bt = torch.arange(3 * 8, dtype=torch.int32).view(3, 8)
 
@@ -31,10 +34,10 @@ def test_decode_logits_match_reference_path(preset):
     lg0, lg1, ids = run()
     with ops.force_reference():
         r0, r1, rids = run()
-    for a, b in ((lg0, r0), (lg1, r1)):
+    for name, a, b in (("prefill", lg0, r0), ("decode", lg1, r1)):
         assert torch.isfinite(a).all()
-        err = (a - b).abs().max() / b.abs().max()
-        assert float(err) < 3e-2, float(err)
+        err = (a - b).abs().amax(-1) / b.abs().amax(-1)
+        assert float(err.max()) < 3e-2, (name, err.tolist())
 
 
 @pytest.mark.parametrize("preset", ["tiny-llama", "tiny-mla-moe"])
