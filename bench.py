@@ -158,6 +158,15 @@ def main():
     eager = args.impl == "eager"
     t_build = time.time()
     lm = MMFP4ForCausalLM.from_config(cfg, device=str(dev), seed=args.seed)
+    use_tp = world > 1 and args.parallelism in ("auto", "tp")
+    run_model = lm.model
+    if use_tp:
+        # every rank built the same weights (per-tensor seeds); keep only this rank's tensor-parallel shard
+        from metal_marlin_b200.parallel.tp import make_context, shard_transformer
+        tp_ctx = make_context(cfg, dev, mode="fused")
+        run_model = shard_transformer(lm.model, rank, world, tp_ctx)
+        lm.model.layers = []
+        torch.cuda.empty_cache()
     build_s = time.time() - t_build
     if eager:
         from metal_marlin_b200.baseline_eager import EagerBF16Model
@@ -167,7 +176,7 @@ def main():
         total_len = args.prompt_len + warmup + steps * (2 if e2e else 1) + 8
         nb = (total_len + block_size - 1) // block_size
         kv = lm.new_cache(batch * nb, block_size)
-        g = torch.Generator().manual_seed(args.seed + rank)
+        g = torch.Generator().manual_seed(args.seed + (0 if use_tp else rank))     # tensor-parallel ranks share the batch
         prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(batch)]
         bt = torch.arange(batch * nb, dtype=torch.int32).view(batch, nb)
         torch.cuda.synchronize(dev)
@@ -176,19 +185,20 @@ def main():
         if eager:
             logits = eager_model.prefill(kv, prompts, bt)
         else:
-            logits = prefill(lm.model, kv, prompts, bt)
+            logits = prefill(run_model, kv, prompts, bt)
         ev1.record()
         torch.cuda.synchronize(dev)
         ttft_ms = ev0.elapsed_time(ev1)
-        model = eager_model if eager else lm.model
+        model = eager_model if eager else run_model
         sess = DecodeSession(model, kv, batch, nb, max_new_tokens=0, max_ctx=total_len, use_graph=not (eager or args.no_graph))
         sess.set_sampling([SamplingParams()] * batch)
-        sess.set_state(logits.argmax(-1), [args.prompt_len] * batch, bt)
+        first = run_model.greedy(logits) if not eager else logits.argmax(-1)
+        sess.set_state(first, [args.prompt_len] * batch, bt)
         l0 = ops.launch_count()
         sess._step_body() if (eager or args.no_graph) else sess.capture()
         launches_per_step = (ops.launch_count() - l0) // (1 if (eager or args.no_graph) else 3)
         if eager or args.no_graph:
-            sess.set_state(logits.argmax(-1), [args.prompt_len] * batch, bt)
+            sess.set_state(first, [args.prompt_len] * batch, bt)
         for _ in range(warmup):
             sess.step()
         barrier()
@@ -231,21 +241,24 @@ def main():
         torch.cuda.empty_cache()
         return res
 
-    replicas = world      # data-parallel replicas of the model; each decodes its own batch
+    # tensor parallel: one model instance over all GPUs (strong scaling, global batch fixed);
+    # data parallel: one replica per GPU, each decoding its own batch (weak scaling)
+    replicas = 1 if use_tp else world
     r = run_config(args.batch, args.steps, args.warmup, e2e=True)
     tok_s = replicas * args.batch * 1e3 / r["ms_per_step"]
     e2e_tok_s = replicas * args.batch * 1e3 / r["e2e_ms_per_step"]
     out = {
         "metric": f"glm47_flash_mmfp4_decode_tok_s_bs{args.batch}",
         "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True, "scaling": "strong" if use_tp else "weak",
         "vs_baseline": round(tok_s / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
         "impl": args.impl,
         "config": {"model": f"{args.model} (random-init, RTN MMFP4 group 128)", "global_batch": replicas * args.batch,
-                   "seq_len": args.prompt_len, "parallelism": f"dp{world}" if world > 1 else "single",
+                   "seq_len": args.prompt_len, "parallelism": (f"tp{world} (in-kernel NVLink exchange)" if use_tp else f"dp{world}") if world > 1 else "single",
                    "kv": "paged latent MLA, 16-token blocks", "decode": "greedy, CUDA graph per step",
                    "l2_policy": "inputs larger than L2 (each step streams >2 GB of weights)",
-                   "weights_gb": round(lm.model.weight_bytes() / 1e9, 2), "build_s": round(build_s, 1)},
+                   "weights_gb_per_gpu": round(run_model.weight_bytes() / 1e9, 2), "build_s": round(build_s, 1),
+                   "exchange_status": tp_ctx.check() if use_tp else 0},
         "clocks": r["clocks"],
         "e2e": {"value": round(e2e_tok_s, 2), "unit": "tok/s", "h2d_bytes_per_step": r["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": r["d2h_bytes_per_step"], "ms_per_step": round(r["e2e_ms_per_step"], 4)},

@@ -28,7 +28,7 @@ def prefill(model: Transformer, kv: PagedKVStorage, seqs: Sequence[Sequence[int]
     bs = kv.block_size
     B = len(seqs)
     done = list(start) if start is not None else [0] * B
-    last_logits = torch.zeros(B, model.cfg.vocab_size, dtype=torch.float32, device=dev)
+    last_logits = None       # [B, vocab] (or the rank's vocabulary shard under tensor parallelism)
     pending = [b for b in range(B) if done[b] < len(seqs[b])]
     while pending:
         batch, ntok = [], 0
@@ -57,6 +57,8 @@ def prefill(model: Transformer, kv: PagedKVStorage, seqs: Sequence[Sequence[int]
                          ctx_lens=torch.tensor(ctx, dtype=torch.int32, device=dev), decode=False, cu_seqlens=cu,
                          ctx_lens_host=ctx)
         lg = model.forward(ids_t, kv, meta, last_only=True)
+        if last_logits is None:
+            last_logits = torch.zeros(B, lg.shape[1], dtype=torch.float32, device=dev)
         for j, (b, s, n) in enumerate(batch):
             done[b] = s + n
             if done[b] >= len(seqs[b]):

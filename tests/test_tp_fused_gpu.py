@@ -1,0 +1,88 @@
+"""Fused tensor-parallel decode on real GPUs: the in-kernel NVLink exchange (partials pushed from the GEMV
+epilogue, summed in the next kernel's prologue, vocabulary-parallel arg-max) must reproduce the unsharded model.
+Runs as child processes, one per GPU; skipped when fewer than two GPUs are visible."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+_CHILD = r"""
+import os, sys, json, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["MMB_REPO"])
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from metal_marlin_b200.engine.session import DecodeSession, SamplingParams
+from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM, prefill
+from metal_marlin_b200.models.transformer import PagedKVStorage
+from metal_marlin_b200.parallel.tp import make_context, shard_transformer
+preset = os.environ["MMB_PRESET"]
+lm = MMFP4ForCausalLM.from_config(preset, device=str(dev), seed=5)
+for L in lm.model.layers:
+    if L.router_w is not None:
+        L.router_w.mul_(16.0)
+ctx = make_context(lm.config, dev, mode="fused")
+shard = shard_transformer(lm.model, rank, world, ctx)
+prompts = [list(range(3, 40)), list(range(50, 58))]
+bt = torch.arange(16, dtype=torch.int32).view(2, 8)
+
+def run(model, graph):
+    kv = PagedKVStorage(model.cfg, 16, 16, dev)
+    lg = model.full_logits(prefill(model, kv, prompts, bt))
+    sess = DecodeSession(model, kv, 2, 8, max_new_tokens=6, use_graph=graph)
+    sess.set_sampling([SamplingParams()] * 2)
+    sess.set_state(lg.argmax(-1), [len(p) for p in prompts], bt)
+    toks = [sess.step().clone() for _ in range(6)]
+    return lg, torch.stack(toks)
+
+lg_ref, tok_ref = run(lm.model, False)
+lg_tp, tok_tp = run(shard, False)
+lg_g, tok_g = run(shard, True)
+err = float((lg_tp - lg_ref).abs().max() / lg_ref.abs().max())
+res = {"rank": rank, "err": err, "eager_equal": bool(torch.equal(tok_tp, tok_ref)), "graph_equal": bool(torch.equal(tok_g, tok_ref)),
+       "status": ctx.check(), "backend": ctx.buf.backend}
+print("RESULT " + json.dumps(res), flush=True)
+dist.barrier()
+dist.destroy_process_group()
+"""
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.mark.parametrize("preset", ["tiny-mla-moe"])
+def test_fused_tp_decode_matches_unsharded(preset, tmp_path):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = 2
+    port = _free_port()
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD)
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(r), WORLD_SIZE=str(world),
+                   LOCAL_RANK=str(r), MMB_PRESET=preset, MMB_REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                   NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                                      text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {r} failed:\n{o[-3000:]}"
+        line = [l for l in o.splitlines() if l.startswith("RESULT ")][-1]
+        import json
+        res = json.loads(line[7:])
+        assert res["status"] == 0, res
+        assert res["err"] < 4e-2, res
+        assert res["eager_equal"] and res["graph_equal"], res
