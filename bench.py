@@ -158,15 +158,24 @@ def main():
     eager = args.impl == "eager"
     t_build = time.time()
     lm = MMFP4ForCausalLM.from_config(cfg, device=str(dev), seed=args.seed)
-    use_tp = world > 1 and args.parallelism in ("auto", "tp")
-    run_model = lm.model
-    if use_tp:
+    # N > 1: the headline is data parallel (one replica per GPU, each decoding its own stream: weak scaling);
+    # the same run then times the tensor-parallel latency mode (one model over all GPUs, partial sums exchanged
+    # inside the kernels over NVLink) and reports it under "tp".  --parallelism tp makes that the headline.
+    headline_tp = world > 1 and args.parallelism == "tp"
+    also_tp = world > 1 and args.parallelism == "auto" and not (args.impl == "eager")
+    state = {"model": lm.model, "tp": False, "ctx": None}
+
+    def to_tensor_parallel():
         # every rank built the same weights (per-tensor seeds); keep only this rank's tensor-parallel shard
         from metal_marlin_b200.parallel.tp import make_context, shard_transformer
-        tp_ctx = make_context(cfg, dev, mode="fused")
-        run_model = shard_transformer(lm.model, rank, world, tp_ctx)
+        state["ctx"] = make_context(cfg, dev, mode="fused")
+        state["model"] = shard_transformer(lm.model, rank, world, state["ctx"])
+        state["tp"] = True
         lm.model.layers = []
         torch.cuda.empty_cache()
+
+    if headline_tp:
+        to_tensor_parallel()
     build_s = time.time() - t_build
     if eager:
         from metal_marlin_b200.baseline_eager import EagerBF16Model
@@ -176,6 +185,7 @@ def main():
         total_len = args.prompt_len + warmup + steps * (2 if e2e else 1) + 8
         nb = (total_len + block_size - 1) // block_size
         kv = lm.new_cache(batch * nb, block_size)
+        use_tp, run_model = state["tp"], state["model"]
         g = torch.Generator().manual_seed(args.seed + (0 if use_tp else rank))     # tensor-parallel ranks share the batch
         prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(batch)]
         bt = torch.arange(batch * nb, dtype=torch.int32).view(batch, nb)
@@ -241,8 +251,7 @@ def main():
         torch.cuda.empty_cache()
         return res
 
-    # tensor parallel: one model instance over all GPUs (strong scaling, global batch fixed);
-    # data parallel: one replica per GPU, each decoding its own batch (weak scaling)
+    use_tp = state["tp"]
     replicas = 1 if use_tp else world
     r = run_config(args.batch, args.steps, args.warmup, e2e=True)
     tok_s = replicas * args.batch * 1e3 / r["ms_per_step"]
@@ -254,25 +263,38 @@ def main():
         "vs_baseline": round(tok_s / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
         "impl": args.impl,
         "config": {"model": f"{args.model} (random-init, RTN MMFP4 group 128)", "global_batch": replicas * args.batch,
-                   "seq_len": args.prompt_len, "parallelism": (f"tp{world} (in-kernel NVLink exchange)" if use_tp else f"dp{world}") if world > 1 else "single",
+                   "seq_len": args.prompt_len,
+                   "parallelism": (f"tp{world} (in-kernel NVLink exchange)" if use_tp else f"dp{world}") if world > 1 else "single",
                    "kv": "paged latent MLA, 16-token blocks", "decode": "greedy, CUDA graph per step",
                    "l2_policy": "inputs larger than L2 (each step streams >2 GB of weights)",
-                   "weights_gb_per_gpu": round(run_model.weight_bytes() / 1e9, 2), "build_s": round(build_s, 1),
-                   "exchange_status": tp_ctx.check() if use_tp else 0},
+                   "weights_gb_per_gpu": round(state["model"].weight_bytes() / 1e9, 2), "build_s": round(build_s, 1)},
         "clocks": r["clocks"],
         "e2e": {"value": round(e2e_tok_s, 2), "unit": "tok/s", "h2d_bytes_per_step": r["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": r["d2h_bytes_per_step"], "ms_per_step": round(r["e2e_ms_per_step"], 4)},
         "gpu_launches": int(r["launches_per_step"] * args.steps),
         "ttft_ms_p50": round(r["ttft_ms"], 2),
     }
+    if use_tp:
+        out["config"]["exchange_status"] = state["ctx"].check()
     if args.extra:
         try:
             r32 = run_config(32, max(8, args.steps // 2), max(3, args.warmup // 2), e2e=False)
-            out["extra"] = {"bs32_tok_s": round(replicas * 32 * 1e3 / r32["ms_per_step"], 1),
+            out["extra"] = {"bs32_tok_s": round((1 if state["tp"] else world) * 32 * 1e3 / r32["ms_per_step"], 1),
                             "bs32_ms_per_step": round(r32["ms_per_step"], 4), "bs32_ttft_ms": round(r32["ttft_ms"], 1),
                             "bs32_launches_per_step": r32["launches_per_step"]}
         except Exception as e:      # the headline line must still be printed
             out["extra"] = {"error": repr(e)[:300]}
+    if also_tp:
+        # latency mode on the same GPUs: one stream, every matrix split over the ranks
+        try:
+            to_tensor_parallel()
+            rt = run_config(args.batch, args.steps, args.warmup, e2e=False)
+            out["tp"] = {"parallelism": f"tp{world} (in-kernel NVLink exchange)", "global_batch": args.batch,
+                         "ms_per_step": round(rt["ms_per_step"], 4), "tok_s": round(args.batch * 1e3 / rt["ms_per_step"], 2),
+                         "launches_per_step": rt["launches_per_step"], "exchange_status": state["ctx"].check(),
+                         "weights_gb_per_gpu": round(state["model"].weight_bytes() / 1e9, 2)}
+        except Exception as e:
+            out["tp"] = {"error": repr(e)[:300]}
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

@@ -223,27 +223,47 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
     return;
   }
 
+  // Block-table entries of a 64-token tile are fetched once per tile (four independent loads for 16-token
+  // blocks) instead of once per copied row, so no copy waits on a table lookup of its own.
+  const bool pow2_blocks = (p.block_size & (p.block_size - 1)) == 0 && p.block_size >= 16;
+  const int bs_shift = pow2_blocks ? (31 - __clz(p.block_size)) : 0;
   auto load_tile = [&](int tile, int buf) {
     const int tok0 = lo_al + tile * kTileTok;
+    int blk[4] = {0, 0, 0, 0};
+    if (pow2_blocks) {
+      const int last_blk = (ctx - 1) >> bs_shift;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int bi = (tok0 >> bs_shift) + j;
+        if ((j << bs_shift) < kTileTok && bi <= last_blk) blk[j] = __ldg(bt + bi);
+      }
+    }
+    auto slot_of = [&](int r) -> long long {
+      const int tok = tok0 + r;
+      if (pow2_blocks) {
+        const int j = (tok >> bs_shift) - (tok0 >> bs_shift);
+        const int bsel = (j == 0) ? blk[0] : ((j == 1) ? blk[1] : ((j == 2) ? blk[2] : blk[3]));
+        return ((long long)bsel << bs_shift) + (tok & (p.block_size - 1));
+      }
+      return (long long)bt[tok / p.block_size] * p.block_size + (tok % p.block_size);
+    };
     bf16* kd = buf ? k_s1 : k_s0;
     constexpr int KCH = DQK / 8;
+#pragma unroll 4
     for (int i = tid; i < kTileTok * KCH; i += NT) {
       const int r = i / KCH, c = i % KCH;
-      const int tok = tok0 + r;
-      const bool valid = tok < ctx;
-      long long slot = 0;
-      if (valid) slot = (long long)bt[tok / p.block_size] * p.block_size + (tok % p.block_size);
+      const bool valid = tok0 + r < ctx;
+      const long long slot = valid ? slot_of(r) : 0;
       cp_async16(kd + r * L::KS + c * 8, kp + (slot * p.Hkv + hkv) * DQK + c * 8, valid);
     }
     if (!SHARED_V) {
       bf16* vd = buf ? v_s1 : v_s0;
       constexpr int VCH = DV / 8;
+#pragma unroll 4
       for (int i = tid; i < kTileTok * VCH; i += NT) {
         const int r = i / VCH, c = i % VCH;
-        const int tok = tok0 + r;
-        const bool valid = tok < ctx;
-        long long slot = 0;
-        if (valid) slot = (long long)bt[tok / p.block_size] * p.block_size + (tok % p.block_size);
+        const bool valid = tok0 + r < ctx;
+        const long long slot = valid ? slot_of(r) : 0;
         cp_async16(vd + r * L::VS + c * 8, vp + (slot * p.Hkv + hkv) * DV + c * 8, valid);
       }
     }
@@ -432,6 +452,7 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
   extern __shared__ float o_s[];   // [kMergeTok][dv]
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = (CL > 1) ? (int)cluster.block_rank() : 0;
+  if (CL > 1) cluster_arrive();   // matched by cluster_wait() before the first remote shared-memory store
   const int h = blockIdx.x / CL, b0 = blockIdx.y * kMergeTok;
   const int nb = min(kMergeTok, B - b0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -453,32 +474,71 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
   }
   pdl_launch_dependents();
   pdl_wait();
-  // ---- merge this CTA's column slice
+  // ---- merge this CTA's column slice.  Split weights first (one warp per token: lanes cover the splits),
+  // then the weighted sum with the splits spread over thread groups so every partial is requested at once.
+  float* wgt = o_s + kMergeTok * dv;               // [kMergeTok][splits]: exp(m_s - M) / L, 0 for empty splits
+  float* red = wgt + kMergeTok * splits;           // [groups][per] partial sums of one token
   const int per = (dv + CL - 1) / CL;
   const int d_lo = crank * per, d_hi = min(dv, d_lo + per);
-  for (int j = 0; j < nb; ++j) {
-    const long long base = ((long long)(b0 + j) * Hq + h) * splits;
+  if (warp < nb) {
+    const long long base = ((long long)(b0 + warp) * Hq + h) * splits;
     float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    float Lsum = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = part_ml[(base + s) * 2], ls = part_ml[(base + s) * 2 + 1];
-      if (ls > 0.f) Lsum += ls * __expf(ms - M);
+    for (int s = lane; s < splits; s += 32) {
+      const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
+      if (ml.y > 0.f) M = fmaxf(M, ml.x);
     }
+    M = warp_max(M);
+    float Lsum = 0.f;
+    for (int s = lane; s < splits; s += 32) {
+      const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
+      const float w = (ml.y > 0.f) ? __expf(ml.x - M) : 0.f;
+      wgt[warp * splits + s] = w;
+      Lsum += ml.y * w;
+    }
+    Lsum = warp_sum(Lsum);
     const float inv = (Lsum > 0.f) ? 1.f / Lsum : 0.f;
-    for (int d = d_lo + tid; d < d_hi; d += 256) {
-      float acc = 0.f;
-      for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[(base + s) * 2], ls = part_ml[(base + s) * 2 + 1];
-        if (ls > 0.f) acc += part_o[(base + s) * dv + d] * __expf(ms - M);
+    __syncwarp();
+    for (int s = lane; s < splits; s += 32) wgt[warp * splits + s] *= inv;
+  }
+  __syncthreads();
+  {
+    const int quads = (d_hi - d_lo + 3) >> 2;      // float4 columns of the slice (dv and per are multiples of 8)
+    int groups = 256 / quads;
+    if (groups < 1) groups = 1;
+    if (groups > splits) groups = splits;
+    const int cq = tid % quads, sg = tid / quads;
+    const bool worker = sg < groups;
+    if (CL > 1) cluster_wait();
+    for (int j = 0; j < nb; ++j) {
+      const long long base = ((long long)(b0 + j) * Hq + h) * splits;
+      if (worker) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int s = sg; s < splits; s += groups) {
+          const float w = wgt[j * splits + s];
+          if (w != 0.f) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * dv + d_lo + cq * 4));
+            acc.x = fmaf(v.x, w, acc.x);
+            acc.y = fmaf(v.y, w, acc.y);
+            acc.z = fmaf(v.z, w, acc.z);
+            acc.w = fmaf(v.w, w, acc.w);
+          }
+        }
+        *reinterpret_cast<float4*>(red + sg * per + cq * 4) = acc;
       }
-      // round the merged latent to bf16 (an unfused pipeline would store it in bf16)
-      const float v = __bfloat162float(__float2bfloat16(acc * inv));
-      if (CL > 1) {
-        for (int c = 0; c < CL; ++c) cluster.map_shared_rank(o_s, c)[j * dv + d] = v;
-      } else {
-        o_s[j * dv + d] = v;
+      __syncthreads();
+      for (int d = tid; d < d_hi - d_lo; d += 256) {
+        float a = 0.f;
+        for (int gI = 0; gI < groups; ++gI) a += red[gI * per + d];
+        // round the merged latent to bf16 (an unfused pipeline would store it in bf16)
+        const float v = __bfloat162float(__float2bfloat16(a));
+        if (CL > 1) {
+          for (int c = 0; c < CL; ++c) cluster.map_shared_rank(o_s, c)[j * dv + d_lo + d] = v;
+        } else {
+          o_s[j * dv + d_lo + d] = v;
+        }
       }
+      __syncthreads();
     }
   }
   if (CL > 1) cluster.sync();
@@ -568,14 +628,20 @@ MMB_API int mmb_decode_merge(const float* part_o, const float* part_ml, const vo
                              int dvo, int splits, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (dv % 8 != 0 || dv > 512) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)mmb::kMergeTok * dv * 4;
-  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   // cluster size: one CTA per 32-row slab of the up-projection, at most 8 (portable cluster size)
   int cl = 1;
   if (w_uv != nullptr) {
     const int slabs = (dvo + mmb::kMergeRows - 1) / mmb::kMergeRows;
     while (cl < 8 && cl < slabs) cl *= 2;
   }
+  // shared memory: merged latent [8][dv], split weights [8][splits], per-group partial sums [groups][dv / cl]
+  const int per = (dv + cl - 1) / cl;
+  if (per % 4 != 0 || splits < 1) return (int)cudaErrorInvalidValue;
+  int groups = 256 / (per / 4);
+  if (groups < 1) groups = 1;
+  if (groups > splits) groups = splits;
+  const size_t smem = ((size_t)mmb::kMergeTok * dv + (size_t)mmb::kMergeTok * splits + (size_t)groups * per) * 4;
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   dim3 grid(Hq * cl, (B + mmb::kMergeTok - 1) / mmb::kMergeTok);
   return mmb::launch(mmb::decode_merge_kernel, grid, dim3(256), smem, stream, cl, part_o, part_ml, (const bf16*)w_uv,
                      (bf16*)out, B, Hq, dv, dvo, splits, cl);

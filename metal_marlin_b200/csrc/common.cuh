@@ -14,6 +14,12 @@ namespace mmb {
 
 constexpr int kWarp = 32;
 
+// Split cluster barrier.  A CTA may only touch another CTA's shared memory once that CTA has started; arriving
+// at kernel entry and waiting right before the first remote access gives that guarantee without exposing the
+// barrier latency.  Both must be executed by every thread of every CTA of the cluster.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -1,9 +1,9 @@
 // Weight-streaming small-M kernels (decode): FP4 tile-layout GEMV on mma.sync with fp32
 // accumulation and exact per-group scaling, plus a bf16 GEMV for unquantized matrices.
 //
-// FP4 kernel design (sm_100a, HBM-bound):
-//  * one CTA owns R row tiles (16 rows each); its 8 warps split the (virtual) K axis, every
-//    warp streaming whole 512-byte tile blocks with one 16-byte load per lane;
+// FP4 kernel design (sm_100a; decode GEMVs are bound by latency and instruction fetch before bandwidth):
+//  * warp groups own 16-row tiles (or gate/up tile pairs) and split the (virtual) K axis; each warp streams
+//    whole 512-byte tile blocks through a private cp.async ring in shared memory, 16 bytes per lane per block;
 //  * the eight nibbles of a word are turned into an fp16 A fragment with 3 integer ops per
 //    register (no multiply): the fp16 value is e2m1 * 2^-14 and the factor is folded into the
 //    group scale, which is applied in fp32 to a per-group accumulator -> exact W4A16 math;
@@ -51,33 +51,91 @@ __device__ __forceinline__ SegPtr seg_lookup(const MmbFp4GemvParams& p, int toke
   return r;
 }
 
-constexpr int kDepth = 4;   // 16-byte weight loads kept in flight per lane
+constexpr int kRing = 8;    // weight chunks (512 B per warp) kept in flight per warp through cp.async
 
-// NWARPS warps per CTA (8 or 16), R row tiles per CTA.  Decode GEMVs are latency bound: the launcher picks
-// NWARPS so that a warp owns only about two 64-wide chunks, which keeps the dependent instruction chain of
-// every warp short.
-template <int R, bool BIG_GROUPS, int NWARPS>
-__global__ void __launch_bounds__(NWARPS * 32, 1) fp4_gemv_kernel(const MmbFp4GemvParams p) {
+// Barrier over one warp group of the CTA (ids 1..15; id 0 is __syncthreads).
+__device__ __forceinline__ void group_bar(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Where ring position (it, v) of a warp lives: v counts the chunks of one unit in the order the warp walks
+// them (tile 0 of the unit, then tile 1 when the SwiGLU epilogue is fused).  A "run" is the stretch of
+// consecutive positions that stay inside one row tile and one expert segment: inside a run the weight address
+// just advances by one 512-byte block per chunk, so this lookup is only needed at run starts.
+struct GemvLoc {
+  const uint4* q;        // this lane's 16 bytes of the first chunk (null: expert id < 0 -> zeros)
+  const uint32_t* s;     // scale words of the row tile for this lane's row pair (null like q)
+  float mult;            // routing weight of the segment (mode 2) or 1
+  int slot, rt0;         // unit: MoE slot (mode 1) and first row tile
+  int tsel;              // tile of the unit (0 / 1)
+  int sidx, cc;          // segment and chunk inside the segment
+  int run;               // chunks in the run, starting with this one
+};
+
+struct GemvGeom {
+  int gi, TG, tiles_per_slot, n_rt, cpw, c_begin, KC, NG, nseg, token, lane, g;
+};
+
+__device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const GemvGeom& ge, int it, int v) {
+  GemvLoc L;
+  const int u = ge.gi + it * ge.TG;
+  if (p.mode == 1) {
+    L.slot = u / ge.tiles_per_slot;
+    L.rt0 = u - L.slot * ge.tiles_per_slot;
+  } else {
+    L.slot = 0;
+    L.rt0 = u;
+  }
+  L.tsel = (v >= ge.cpw) ? 1 : 0;
+  const int off = v - L.tsel * ge.cpw;
+  const int ci = ge.c_begin + off;
+  const int rt = L.rt0 + L.tsel * (ge.n_rt >> 1);
+  L.sidx = 0;
+  L.cc = ci;
+  if (ge.nseg > 1) {
+    L.sidx = ci / ge.KC;
+    L.cc = ci - L.sidx * ge.KC;
+  }
+  const SegPtr sp = seg_lookup(p, ge.token, (p.mode == 1) ? L.slot : L.sidx);
+  L.mult = sp.mult;
+  L.q = (sp.q != nullptr) ? sp.q + ((long long)rt * ge.KC + L.cc) * 32 + ge.lane : nullptr;
+  L.s = (sp.s != nullptr) ? sp.s + (long long)rt * ge.NG * 8 + ge.g : nullptr;
+  L.run = min(ge.cpw - off, ge.KC - L.cc);
+  return L;
+}
+
+// NWARPS warps per CTA (8: two CTAs per SM, so the next kernel's CTAs become resident and prefetch while this
+// one drains; 16: one CTA per SM).  The warps form groups of `wpt`; a group owns one unit of work at a time - a
+// 16-row tile, or a gate/up tile pair when the SwiGLU epilogue is fused - and splits its K axis; the groups of
+// the whole grid walk the units round-robin, so the activation is staged once per CTA however many tiles it
+// ends up processing.  Every warp streams its weights through a private ring of kRing 512-byte blocks in
+// shared memory filled by cp.async, which runs on across tile and unit boundaries; the code of the loop exists
+// once (no unrolled register ring), which matters because these kernels are short enough to be bound by
+// instruction fetch.
+template <bool BIG_GROUPS, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ float red[NWARPS * 128];
+  __shared__ float red[2][NWARPS][2][128];
   __shared__ float ss_red[NWARPS][8];
   __shared__ float rstd_s[8];
   constexpr int kGemvThreads = NWARPS * 32;
-  constexpr int kGemvWarps = NWARPS;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  constexpr int WPT = kGemvWarps / R;
 
   const int S = (p.mode == 0) ? 1 : (p.topk + p.n_shared);
-  int m0, mt, token = 0, slot = 0;
+  int m0, mt, token = 0;
   if (p.mode == 0) {
     m0 = blockIdx.y * 8;
     mt = min(8, p.M - m0);
-  } else if (p.mode == 1) {
-    token = blockIdx.y / S;
-    slot = blockIdx.y % S;
-    m0 = token;
-    mt = 1;
   } else {
     token = blockIdx.y;
     m0 = token;
@@ -87,66 +145,72 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) fp4_gemv_kernel(const MmbFp4Ge
   const int Kv = nseg * p.K;   // virtual K
   const int XS = Kv + 32;      // smem row stride in halves: rows are 64 bytes apart mod 128 -> 16-byte loads of a
                                // quarter warp (2 rows x 4 lanes) touch distinct banks
+  const int rows_to_stage = (p.mode == 2) ? 1 : mt;     // mode 2 stages its S segments as one row of S * K
   __half* xs = reinterpret_cast<__half*>(smem_raw);
+  const uint32_t ring_q = smem_u32(smem_raw) + (uint32_t)((((size_t)rows_to_stage * XS * 2) + 127) & ~(size_t)127) +
+                          (uint32_t)warp * (kRing * 512) + (uint32_t)lane * 16;
+  const uint32_t ring_s = smem_u32(smem_raw) + (uint32_t)((((size_t)rows_to_stage * XS * 2) + 127) & ~(size_t)127) +
+                          (uint32_t)NWARPS * (kRing * 512) + (uint32_t)warp * (kRing * 128) + (uint32_t)lane * 4;
 
   // ---- work assignment of this warp (depends on launch parameters only)
-  const int n_rt = (p.N + 15) >> 4;
-  const int ti = warp / WPT, wi = warp % WPT;
-  int rt;
-  if (p.act == 1) {
-    rt = (ti == 0) ? (int)blockIdx.x : (int)blockIdx.x + (n_rt >> 1);   // R == 2 enforced by the launcher
-  } else {
-    rt = blockIdx.x * R + ti;
-  }
-  const int KC = p.K >> 6;                 // chunks per segment
-  const int NG = p.K >> p.gs_shift;        // groups per segment
+  GemvGeom ge;
+  ge.n_rt = (p.N + 15) >> 4;
+  const int NT = (p.act == 1) ? 2 : 1;                                   // tiles per unit
+  ge.tiles_per_slot = (p.act == 1) ? (ge.n_rt >> 1) : ge.n_rt;
+  const int n_units = ((p.mode == 1) ? S : 1) * ge.tiles_per_slot;
+  const int G = NWARPS / wpt;                                            // groups per CTA
+  ge.TG = gridDim.x * G;                                                 // groups in the grid (per blockIdx.y)
+  const int grp = warp / wpt, wi = warp - grp * wpt;
+  ge.gi = blockIdx.x * G + grp;
+  const int n_iter = (ge.gi < n_units) ? (n_units - ge.gi + ge.TG - 1) / ge.TG : 0;   // units of this group
+  ge.KC = p.K >> 6;                        // chunks per segment
+  ge.NG = p.K >> p.gs_shift;               // groups per segment
+  ge.nseg = nseg;
+  ge.token = token;
+  ge.lane = lane;
+  ge.g = g;
   const int gs = 1 << p.gs_shift;
-  const int unit_chunks = (gs >= 64) ? (gs >> 6) : 1;
-  const int total_units = (nseg * KC) / unit_chunks;
-  int c_begin = (int)(((long long)wi * total_units) / WPT) * unit_chunks;
-  int c_end = (int)(((long long)(wi + 1) * total_units) / WPT) * unit_chunks;
-  if (rt >= n_rt) c_end = c_begin;
+  {
+    const int unit_chunks = (gs >= 64) ? (gs >> 6) : 1;
+    const int total_units = (nseg * ge.KC) / unit_chunks;
+    ge.c_begin = (int)(((long long)wi * total_units) / wpt) * unit_chunks;
+    ge.cpw = (int)(((long long)(wi + 1) * total_units) / wpt) * unit_chunks - ge.c_begin;   // chunks per tile
+  }
+  const int cv = NT * ge.cpw;                                            // chunks of this warp per unit
+  const int cpg_shift = BIG_GROUPS ? (p.gs_shift - 6) : 0;               // log2(chunks per quantization group)
 
-  // ---- issue the first weight loads before anything else: their DRAM latency overlaps the x staging
-  uint4 w[kDepth];
-  uint32_t sw[kDepth];      // group scale word travelling with each chunk (BIG_GROUPS)
-  int ld_seg = -1;
-  SegPtr lseg;
-  lseg.q = nullptr;
-  lseg.s = nullptr;
-  lseg.mult = 0.f;
-  const int cpg_shift_ld = p.gs_shift - 6;      // log2(chunks per group) when the group spans whole chunks
-  auto load_chunk = [&](int ci, uint32_t& scale_word) -> uint4 {
-    int sidx = 0, cc = ci;
-    if (nseg > 1) {
-      sidx = ci / KC;
-      cc = ci - sidx * KC;
+  // ---- loader: one cp.async (16 bytes per lane) per chunk, plus the 4-byte scale word of the lane's row pair
+  int l_it = (cv > 0) ? 0 : n_iter, l_v = 0, l_cnt = 0, l_run = 0, l_cc = 0;
+  const uint4* l_q = nullptr;
+  const uint32_t* l_s = nullptr;
+  auto issue = [&]() {
+    if (l_it < n_iter) {
+      if (l_run == 0) {
+        const GemvLoc L = gemv_locate(p, ge, l_it, l_v);
+        l_q = L.q;
+        l_s = L.s;
+        l_cc = L.cc;
+        l_run = L.run;
+      }
+      const uint32_t slot = (uint32_t)l_cnt & (kRing - 1);
+      cp_async_16(ring_q + slot * 512, (l_q != nullptr) ? (const void*)l_q : p.qw, (l_q != nullptr) ? 16 : 0);
+      if (BIG_GROUPS)
+        cp_async_4(ring_s + slot * 128, (l_s != nullptr) ? (const void*)(l_s + (l_cc >> cpg_shift) * 8) : p.sc,
+                   (l_s != nullptr) ? 4 : 0);
+      if (l_q != nullptr) l_q += 32;
+      ++l_cc;
+      --l_run;
+      if (++l_v == cv) {
+        l_v = 0;
+        ++l_it;
+      }
     }
-    if (sidx != ld_seg) {
-      lseg = seg_lookup(p, token, (p.mode == 1) ? slot : sidx);
-      ld_seg = sidx;
-    }
-    if (lseg.q == nullptr) {
-      scale_word = 0u;
-      return make_uint4(0, 0, 0, 0);
-    }
-    if (BIG_GROUPS) scale_word = __ldg(lseg.s + ((long long)rt * NG + (cc >> cpg_shift_ld)) * 8 + g);
-    return ldg_stream(lseg.q + ((long long)rt * KC + cc) * 32 + lane);
+    cp_async_commit_group();
+    ++l_cnt;
   };
-  // Dense weights never change, so their first fetches are issued before waiting for the previous kernel;
-  // MoE fetches depend on the router's expert ids and must come after the wait.
-#pragma unroll
-  for (int i = 0; i < kDepth; ++i) {
-    w[i] = make_uint4(0, 0, 0, 0);
-    sw[i] = 0u;
-  }
-  if (p.mode == 0) {
-#pragma unroll
-    for (int i = 0; i < kDepth; ++i)
-      if (c_begin + i < c_end) w[i] = load_chunk(c_begin + i, sw[i]);
-  }
-  // the RMSNorm weight is static as well: fetch this thread's first slices now (the rest, for K > 4096, is
-  // read where it is used)
+
+  // the RMSNorm weight is static: fetch this thread's first slices before waiting (the rest, for K beyond two
+  // trips of the CTA, is read where it is used)
   const bf16* nw = reinterpret_cast<const bf16*>(p.norm_w);
   constexpr int kNormCh = 2;
   uint4 nwv[kNormCh];
@@ -157,19 +221,24 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) fp4_gemv_kernel(const MmbFp4Ge
       nwv[j] = (k < p.Kx) ? *reinterpret_cast<const uint4*>(nw + k) : make_uint4(0, 0, 0, 0);
     }
   }
-  pdl_launch_dependents();
-  pdl_wait();
-  if (p.mode != 0) {
-#pragma unroll
-    for (int i = 0; i < kDepth; ++i)
-      if (c_begin + i < c_end) w[i] = load_chunk(c_begin + i, sw[i]);
+  // Dense weights never change, so the ring is filled before waiting for the previous kernel; MoE fetches depend
+  // on the router's expert ids and must come after the wait.
+#pragma unroll 1
+  for (int phase = 0; phase < 2; ++phase) {
+    if (phase == 1) {
+      pdl_launch_dependents();
+      pdl_wait();
+    }
+    if ((p.mode == 0) == (phase == 0)) {
+#pragma unroll 1
+      for (int i = 0; i < kRing; ++i) issue();
+    }
   }
 
   // ---- stage activations as fp16 (optional residual add + RMSNorm), 8 elements per thread per trip
   const bf16* xg = reinterpret_cast<const bf16*>(p.x);
   const bf16* dg = reinterpret_cast<const bf16*>(p.delta);
   bf16* ro = reinterpret_cast<bf16*>(p.resid_out);
-  const int rows_to_stage = (p.mode == 2) ? nseg : mt;
   // tensor-parallel consumer: the residual delta is the sum of the tp partials peers pushed into the local buffer
   const bool has_tin = p.tpx.in_buf != nullptr;
   TpIn tin;
@@ -181,86 +250,54 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) fp4_gemv_kernel(const MmbFp4Ge
   tin.slot_stride = p.tpx.in_slot_stride;
   if (has_tin) tp_wait(tin);
 
-  // value of (x + delta) for 8 consecutive elements of row j, rounded to bf16 like an unfused add would
-  auto load8 = [&](int j, long long row, int k, float (&v)[8]) {
-    const uint4 xv = *reinterpret_cast<const uint4*>(xg + row + k);
-    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      v[2 * e] = __uint_as_float(xw[e] << 16);
-      v[2 * e + 1] = __uint_as_float(xw[e] & 0xffff0000u);
-    }
-    if (has_tin) {
-      const long long idx = (long long)(m0 + j) * p.Kx + k;
-      float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int r = 0; r < tin.tp; ++r) {
-        const float4 a = __ldcg(reinterpret_cast<const float4*>(tin.buf + r * tin.slot_stride + idx));
-        const float4 b = __ldcg(reinterpret_cast<const float4*>(tin.buf + r * tin.slot_stride + idx + 4));
-        d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
-        d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
-      }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = __bfloat162float(__float2bfloat16(v[e] + d[e]));
-    } else if (dg != nullptr) {
-      const uint4 dv = *reinterpret_cast<const uint4*>(dg + row + k);
-      const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        v[2 * e] = __bfloat162float(__float2bfloat16(v[2 * e] + __uint_as_float(dw[e] << 16)));
-        v[2 * e + 1] = __bfloat162float(__float2bfloat16(v[2 * e + 1] + __uint_as_float(dw[e] & 0xffff0000u)));
-      }
-    }
-  };
-
-  if (nw != nullptr) {
-    // pass 1: sum of squares per token row; one combined block reduction for all rows
-    float ss[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) ss[j] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (j < rows_to_stage) {
-        const long long row = (long long)(m0 + j) * p.ldx;
-        for (int k = tid * 8; k < p.Kx; k += kGemvThreads * 8) {
-          float v[8];
-          load8(j, row, k, v);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) ss[j] = fmaf(v[e], v[e], ss[j]);
-        }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (j < rows_to_stage) {
-        const float sred = warp_sum(ss[j]);
-        if (lane == 0) ss_red[warp][j] = sred;
-      }
-    }
-    __syncthreads();
-    if (tid < rows_to_stage) {
-      float tot = 0.f;
-#pragma unroll
-      for (int w2 = 0; w2 < kGemvWarps; ++w2) tot += ss_red[w2][tid];
-      rstd_s[tid] = rsqrtf(tot / (float)p.Kx + p.eps);
-    }
-    __syncthreads();
-  }
+  // Pass A reads global memory once: x (+ delta or the tp partial sums), rounded to bf16 like an unfused add;
+  // writes the new residual; without a norm it stores the final fp16 value, with a norm it parks the bf16 bits
+  // in the same shared-memory slots (fragment order) and accumulates the sum of squares.  Pass B (norm only)
+  // has every thread rewrite its own slots with bf16(v * rstd * w) as fp16.
+  const int stage_k = (p.mode == 2) ? Kv : p.K;          // staged width of a row (columns beyond Kx are zero)
+#pragma unroll 1
   for (int j = 0; j < rows_to_stage; ++j) {
-    long long row;
-    __half* dst;
-    if (p.mode == 2) {
-      row = (long long)(token * S + j) * p.ldx;
-      dst = xs + (long long)j * p.K;
-    } else {
-      row = (long long)(m0 + j) * p.ldx;
-      dst = xs + (long long)j * XS;
-    }
-    const float rs = (nw != nullptr) ? rstd_s[j] : 1.f;
-    for (int jj = 0, k = tid * 8; k < p.K; ++jj, k += kGemvThreads * 8) {
+    float ss = 0.f;
+    __half* dst = xs + (long long)j * XS;
+#pragma unroll 1
+    for (int k = tid * 8; k < stage_k; k += kGemvThreads * 8) {
       float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (k < p.Kx) {
-        load8(j, row, k, v);
-        if ((dg != nullptr || has_tin) && ro != nullptr && blockIdx.x == 0 && (p.mode != 1 || slot == 0)) {
+      bool valid = k < p.Kx;
+      long long src = (long long)(m0 + j) * p.ldx + k;
+      if (p.mode == 2) {
+        const int sg = k / p.K, off = k - sg * p.K;       // segment rows of h are ldx apart
+        valid = off < p.Kx;
+        src = (long long)(token * S + sg) * p.ldx + off;
+      }
+      if (valid) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xg + src);
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[2 * e] = __uint_as_float(xw[e] << 16);
+          v[2 * e + 1] = __uint_as_float(xw[e] & 0xffff0000u);
+        }
+        if (has_tin) {
+          const long long idx = (long long)(m0 + j) * p.Kx + k;
+          float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int r = 0; r < tin.tp; ++r) {
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(tin.buf + r * tin.slot_stride + idx));
+            const float4 b = __ldcg(reinterpret_cast<const float4*>(tin.buf + r * tin.slot_stride + idx + 4));
+            d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
+            d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = __bfloat162float(__float2bfloat16(v[e] + d[e]));
+        } else if (dg != nullptr) {
+          const uint4 dv = *reinterpret_cast<const uint4*>(dg + src);
+          const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            v[2 * e] = __bfloat162float(__float2bfloat16(v[2 * e] + __uint_as_float(dw[e] << 16)));
+            v[2 * e + 1] = __bfloat162float(__float2bfloat16(v[2 * e + 1] + __uint_as_float(dw[e] & 0xffff0000u)));
+          }
+        }
+        if ((dg != nullptr || has_tin) && ro != nullptr && blockIdx.x == 0) {
           uint4 o;
           o.x = (__float_as_uint(v[0]) >> 16) | (__float_as_uint(v[1]) & 0xffff0000u);
           o.y = (__float_as_uint(v[2]) >> 16) | (__float_as_uint(v[3]) & 0xffff0000u);
@@ -268,154 +305,199 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) fp4_gemv_kernel(const MmbFp4Ge
           o.w = (__float_as_uint(v[6]) >> 16) | (__float_as_uint(v[7]) & 0xffff0000u);
           *reinterpret_cast<uint4*>(ro + (long long)(m0 + j) * p.Kx + k) = o;
         }
-        if (nw != nullptr) {
-          const uint4 nv = (jj == 0) ? nwv[0] : ((jj == 1) ? nwv[1] : *reinterpret_cast<const uint4*>(nw + k));
-          const uint32_t nww[4] = {nv.x, nv.y, nv.z, nv.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            // round to bf16 like an unfused norm kernel would, so fused and unfused paths agree
-            v[2 * e] = __bfloat162float(__float2bfloat16(v[2 * e] * rs * __uint_as_float(nww[e] << 16)));
-            v[2 * e + 1] = __bfloat162float(__float2bfloat16(v[2 * e + 1] * rs * __uint_as_float(nww[e] & 0xffff0000u)));
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = fminf(fmaxf(v[e], -65504.f), 65504.f);
       }
       // fragment order inside each 32-wide block: lane t finds (b0, b1) of both k16 steps in 16 contiguous bytes
       __half* blk = dst + (k & ~31) + ((k >> 4) & 1) * 4 + ((k >> 3) & 1) * 2;
+      if (nw != nullptr) {
 #pragma unroll
-      for (int tt = 0; tt < 4; ++tt)
-        *reinterpret_cast<__half2*>(blk + tt * 8) = __floats2half2_rn(v[2 * tt], v[2 * tt + 1]);
+        for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt)    // bf16 bits parked in the fp16 slots until pass B
+          *reinterpret_cast<uint32_t*>(blk + tt * 8) = (__float_as_uint(v[2 * tt]) >> 16) | (__float_as_uint(v[2 * tt + 1]) & 0xffff0000u);
+      } else {
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt)
+          *reinterpret_cast<__half2*>(blk + tt * 8) = __floats2half2_rn(fminf(fmaxf(v[2 * tt], -65504.f), 65504.f),
+                                                                        fminf(fmaxf(v[2 * tt + 1], -65504.f), 65504.f));
+      }
+    }
+    if (nw != nullptr) {
+      ss = warp_sum(ss);
+      if (lane == 0) ss_red[warp][j] = ss;
+    }
+  }
+  if (nw != nullptr) {
+    __syncthreads();
+    if (tid < rows_to_stage) {
+      float tot = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < NWARPS; ++w2) tot += ss_red[w2][tid];
+      rstd_s[tid] = rsqrtf(tot / (float)p.Kx + p.eps);
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int j = 0; j < rows_to_stage; ++j) {
+      const float rs = rstd_s[j];
+      __half* dst = xs + (long long)j * XS;
+#pragma unroll 1
+      for (int jj = 0, k = tid * 8; k < p.Kx; ++jj, k += kGemvThreads * 8) {
+        const uint4 nv = (jj == 0) ? nwv[0] : ((jj == 1) ? nwv[1] : *reinterpret_cast<const uint4*>(nw + k));
+        const uint32_t nww[4] = {nv.x, nv.y, nv.z, nv.w};
+        __half* blk = dst + (k & ~31) + ((k >> 4) & 1) * 4 + ((k >> 3) & 1) * 2;
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt) {
+          const uint32_t bits = *reinterpret_cast<const uint32_t*>(blk + tt * 8);
+          // round to bf16 like an unfused norm kernel would, so fused and unfused paths agree
+          float a = __bfloat162float(__float2bfloat16(__uint_as_float(bits << 16) * rs * __uint_as_float(nww[tt] << 16)));
+          float b = __bfloat162float(__float2bfloat16(__uint_as_float(bits & 0xffff0000u) * rs * __uint_as_float(nww[tt] & 0xffff0000u)));
+          a = fminf(fmaxf(a, -65504.f), 65504.f);
+          b = fminf(fmaxf(b, -65504.f), 65504.f);
+          *reinterpret_cast<__half2*>(blk + tt * 8) = __floats2half2_rn(a, b);
+        }
+      }
     }
   }
   __syncthreads();
 
-  // ---- main loop: kDepth loads stay in flight per lane.  Per 64-wide chunk: two 16-byte shared loads give
-  // the B fragments of its four k16 steps (the staging above stored x in fragment order), 4 x (12 integer
-  // ops + 1 MMA), and once per quantization group the scale is applied to the group accumulator in fp32.
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  // ---- main loop.  Per 64-wide chunk: one 16-byte shared load of the lane's weight words, two 16-byte shared
+  // loads with the B fragments of its four k16 steps (the staging above stored x in fragment order),
+  // 4 x (12 integer ops + 1 MMA), and once per quantization group the scale applied to the group accumulator
+  // in fp32.
+  const bool tp_out = p.tpx.out_peer_slots != nullptr;
+  TpOut tout;
+  tout.peer_slots = p.tpx.out_peer_slots;
+  tout.peer_flags = p.tpx.out_peer_flags;
+  tout.counter = p.tpx.out_counter;
+  tout.step = p.tpx.step;
+  tout.tp = p.tpx.tp;
+  bf16* const out = reinterpret_cast<bf16*>(p.out);
   {
     const int gmask = gs - 1;
-    const int cpg_shift = p.gs_shift - 6;                 // log2(chunks per group), valid when BIG_GROUPS
-    const int cpg_mask = BIG_GROUPS ? ((1 << cpg_shift) - 1) : 0;
+    const int cpg_mask = (1 << cpg_shift) - 1;
     const __half* xbase = xs + min(g, mt - 1) * ((p.mode == 2) ? 0 : XS) + t * 8;
-    float gacc[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t s2 = 0;
-    int pr_seg = -1;
-    SegPtr pseg;
-    pseg.q = nullptr;
-    pseg.s = nullptr;
-    pseg.mult = 0.f;
-    const uint32_t* sbase = nullptr;
+    const unsigned char* ring_q_gen = smem_raw + (ring_q - smem_u32(smem_raw));
+    const unsigned char* ring_s_gen = smem_raw + (ring_s - smem_u32(smem_raw));
+    int c_cnt = 0, c_run = 0, c_cc = 0, c_tsel = 0, c_slot = 0, c_rt0 = 0;
     float mult = 0.f;
-    for (int c = c_begin; c < c_end; c += kDepth) {
-#pragma unroll
-      for (int i = 0; i < kDepth; ++i) {
-        const int ci = c + i;
-        if (ci >= c_end) break;
-        int sidx = 0, cc = ci;
-        if (nseg > 1) {
-          sidx = ci / KC;
-          cc = ci - sidx * KC;
+    const __half* xp = xbase;
+    const uint32_t* c_s = nullptr;
+#pragma unroll 1
+    for (int it = 0; it < n_iter; ++it) {
+      float accg[4] = {0.f, 0.f, 0.f, 0.f};    // tile 0 of the unit
+      float accu[4] = {0.f, 0.f, 0.f, 0.f};    // tile 1 (the up half when the SwiGLU epilogue is fused)
+      float gacc[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t s2 = 0;
+#pragma unroll 1
+      for (int v = 0; v < cv; ++v) {
+        if (c_run == 0) {
+          const GemvLoc L = gemv_locate(p, ge, it, v);
+          c_run = L.run;
+          c_cc = L.cc;
+          c_tsel = L.tsel;
+          c_slot = L.slot;
+          c_rt0 = L.rt0;
+          c_s = L.s;
+          mult = L.mult * kE2M1F16Rescale;
+          xp = xbase + (long long)L.sidx * p.K + L.cc * 64;
         }
-        if (sidx != pr_seg) {
-          pseg = seg_lookup(p, token, (p.mode == 1) ? slot : sidx);
-          pr_seg = sidx;
-          sbase = (pseg.s != nullptr) ? pseg.s + (long long)rt * NG * 8 + g : nullptr;
-          mult = pseg.mult * kE2M1F16Rescale;
-        }
-        const uint32_t qq[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
-        const uint32_t s_cur = sw[i];
-        if (ci + kDepth < c_end) w[i] = load_chunk(ci + kDepth, sw[i]);
-        const __half* xp = xbase + (long long)sidx * p.K + cc * 64;
+        cp_async_wait_group<kRing - 1>();
+        const uint32_t slot = (uint32_t)c_cnt & (kRing - 1);
+        const uint4 wq = *reinterpret_cast<const uint4*>(ring_q_gen + slot * 512);
+        const uint32_t s_cur = BIG_GROUPS ? *reinterpret_cast<const uint32_t*>(ring_s_gen + slot * 128) : 0u;
+        issue();   // refill the slot just read
+        const uint32_t qq[4] = {wq.x, wq.y, wq.z, wq.w};
         const uint4 xv0 = *reinterpret_cast<const uint4*>(xp);
         const uint4 xv1 = *reinterpret_cast<const uint4*>(xp + 32);
         const uint32_t bb[8] = {xv0.x, xv0.y, xv0.z, xv0.w, xv1.x, xv1.y, xv1.z, xv1.w};
         if (BIG_GROUPS) s2 = s_cur;
+        bool flush = false;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           if (!BIG_GROUPS) {
-            const int kabs = cc * 64 + ks * 16;
-            if ((kabs & gmask) == 0) s2 = (sbase != nullptr) ? __ldg(sbase + (kabs >> p.gs_shift) * 8) : 0u;
+            const int kabs = c_cc * 64 + ks * 16;
+            if ((kabs & gmask) == 0) s2 = (c_s != nullptr) ? __ldg(c_s + (kabs >> p.gs_shift) * 8) : 0u;
           }
           uint32_t a0, a1, a2, a3;
           e2m1x8_to_f16x2(qq[ks], a0, a1, a2, a3);
           mma_f16_16816(gacc, a0, a1, a2, a3, bb[2 * ks], bb[2 * ks + 1]);
-          if (!BIG_GROUPS) {
-            const int kabs = cc * 64 + ks * 16;
-            if (((kabs + 16) & gmask) == 0) {
-              const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&s2));
-              const float slo = sf.x * mult, shi = sf.y * mult;
-              acc[0] = fmaf(gacc[0], slo, acc[0]);
-              acc[1] = fmaf(gacc[1], slo, acc[1]);
-              acc[2] = fmaf(gacc[2], shi, acc[2]);
-              acc[3] = fmaf(gacc[3], shi, acc[3]);
-              gacc[0] = gacc[1] = gacc[2] = gacc[3] = 0.f;
-            }
-          }
-        }
-        if (BIG_GROUPS) {
-          if (((cc + 1) & cpg_mask) == 0) {
+          if (BIG_GROUPS) flush = (ks == 3) && (((c_cc + 1) & cpg_mask) == 0);
+          else flush = (((c_cc * 64 + ks * 16 + 16) & gmask) == 0);
+          if (flush) {
             const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&s2));
             const float slo = sf.x * mult, shi = sf.y * mult;
-            acc[0] = fmaf(gacc[0], slo, acc[0]);
-            acc[1] = fmaf(gacc[1], slo, acc[1]);
-            acc[2] = fmaf(gacc[2], shi, acc[2]);
-            acc[3] = fmaf(gacc[3], shi, acc[3]);
+            if (c_tsel == 0) {
+              accg[0] = fmaf(gacc[0], slo, accg[0]);
+              accg[1] = fmaf(gacc[1], slo, accg[1]);
+              accg[2] = fmaf(gacc[2], shi, accg[2]);
+              accg[3] = fmaf(gacc[3], shi, accg[3]);
+            } else {
+              accu[0] = fmaf(gacc[0], slo, accu[0]);
+              accu[1] = fmaf(gacc[1], slo, accu[1]);
+              accu[2] = fmaf(gacc[2], shi, accu[2]);
+              accu[3] = fmaf(gacc[3], shi, accu[3]);
+            }
             gacc[0] = gacc[1] = gacc[2] = gacc[3] = 0.f;
+          }
+        }
+        xp += 64;
+        ++c_cc;
+        --c_run;
+        ++c_cnt;
+      }
+      // ---- reduction over the warps of the group and epilogue of this unit.  `red` is double buffered by unit
+      // parity, so one group barrier per unit is enough: a warp can only overwrite a buffer after passing the
+      // barrier of the unit in between, which the readers of that buffer reach after they are done with it.
+      const int buf = it & 1;
+      {
+        float* r = &red[buf][warp][0][0];
+        r[g * 8 + 2 * t] = accg[0];
+        r[g * 8 + 2 * t + 1] = accg[1];
+        r[(g + 8) * 8 + 2 * t] = accg[2];
+        r[(g + 8) * 8 + 2 * t + 1] = accg[3];
+        if (NT == 2) {
+          r += 128;
+          r[g * 8 + 2 * t] = accu[0];
+          r[g * 8 + 2 * t + 1] = accu[1];
+          r[(g + 8) * 8 + 2 * t] = accu[2];
+          r[(g + 8) * 8 + 2 * t + 1] = accu[3];
+        }
+      }
+      if (wpt > 1) group_bar(1 + grp, wpt * 32);
+      else __syncwarp();
+      if (cv == 0) {   // a warp without chunks of its own still needs the unit of its group for the epilogue
+        const GemvLoc L = gemv_locate(p, ge, it, 0);
+        c_slot = L.slot;
+        c_rt0 = L.rt0;
+      }
+      const int w0 = grp * wpt;
+      for (int o = wi * 32 + lane; o < 16 * 8; o += wpt * 32) {
+        const int row = o >> 3, col = o & 7;
+        if (col >= mt) continue;
+        float v = 0.f;
+#pragma unroll 4
+        for (int w2 = 0; w2 < wpt; ++w2) v += red[buf][w0 + w2][0][o];
+        const long long orow = (p.mode == 1) ? (long long)token * S + c_slot : (long long)(m0 + col);
+        const int n = c_rt0 * 16 + row;
+        if (p.act == 1) {
+          float u = 0.f;
+#pragma unroll 4
+          for (int w2 = 0; w2 < wpt; ++w2) u += red[buf][w0 + w2][1][o];
+          if (n < (p.N >> 1)) out[orow * p.ldo + n] = __float2bfloat16(silu(v) * u);
+        } else if (n < p.N) {
+          if (tp_out) {
+            // tensor-parallel producer: this rank's partial goes straight into every peer's receive buffer
+            tp_push(tout, orow * p.N + n, v);
+          } else {
+            if (p.bias) v += __bfloat162float(reinterpret_cast<const bf16*>(p.bias)[n]);
+            if (p.out_add) v += __bfloat162float(reinterpret_cast<const bf16*>(p.out_add)[orow * p.ldo + n]);
+            out[orow * p.ldo + n] = __float2bfloat16(v);
           }
         }
       }
     }
   }
-  // ---- cross-warp reduction and epilogue
-  {
-    float* r = red + warp * 128;
-    r[g * 8 + 2 * t] = acc[0];
-    r[g * 8 + 2 * t + 1] = acc[1];
-    r[(g + 8) * 8 + 2 * t] = acc[2];
-    r[(g + 8) * 8 + 2 * t + 1] = acc[3];
-  }
-  __syncthreads();
-  const int et = tid >> 7;            // epilogue tile (threads beyond R * 128 only take part in the barriers)
-  const int row = (tid & 127) >> 3, col = tid & 7;
-  const bool active = (et < R) && (col < mt);
-  float v = 0.f;
-  if (active) {
-#pragma unroll
-    for (int w2 = 0; w2 < WPT; ++w2) v += red[(et * WPT + w2) * 128 + row * 8 + col];
-  }
-  const long long orow = (p.mode == 1) ? (long long)blockIdx.y : (long long)(m0 + col);
-  if (p.tpx.out_peer_slots != nullptr) {
-    // tensor-parallel producer: this rank's partial goes straight into every peer's receive buffer
-    TpOut tout;
-    tout.peer_slots = p.tpx.out_peer_slots;
-    tout.peer_flags = p.tpx.out_peer_flags;
-    tout.counter = p.tpx.out_counter;
-    tout.step = p.tpx.step;
-    tout.tp = p.tpx.tp;
-    const int n = (blockIdx.x * R + et) * 16 + row;
-    if (active && n < p.N) tp_push(tout, orow * p.N + n, v);
-    tp_signal(tout, gridDim.x * gridDim.y);
-    return;
-  }
-  if (!active) return;
-  bf16* out = reinterpret_cast<bf16*>(p.out);
-  if (p.act == 1) {
-    if (et != 0) return;
-    float u = 0.f;
-#pragma unroll
-    for (int w2 = 0; w2 < WPT; ++w2) u += red[(WPT + w2) * 128 + row * 8 + col];
-    const int n = blockIdx.x * 16 + row;
-    if (n < (p.N >> 1)) out[orow * p.ldo + n] = __float2bfloat16(silu(v) * u);
-  } else {
-    const int n = (blockIdx.x * R + et) * 16 + row;
-    if (n < p.N) {
-      if (p.bias) v += __bfloat162float(reinterpret_cast<const bf16*>(p.bias)[n]);
-      if (p.out_add) v += __bfloat162float(reinterpret_cast<const bf16*>(p.out_add)[orow * p.ldo + n]);
-      out[orow * p.ldo + n] = __float2bfloat16(v);
-    }
-  }
+  cp_async_wait_group<0>();
+  if (tp_out) tp_signal(tout, gridDim.x * gridDim.y);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -532,9 +614,10 @@ __global__ void __launch_bounds__(256) bf16_gemv_kernel(const MmbBf16GemvParams 
   }
 }
 
+// `static_bytes`: the kernel's statically declared shared memory, which counts against the same 48 KB default.
 template <typename K>
-static int set_smem(K kernel, size_t bytes) {
-  if (bytes > 48 * 1024) {
+static int set_smem(K kernel, size_t bytes, size_t static_bytes = 0) {
+  if (bytes + static_bytes > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return (int)e;
   }
@@ -557,53 +640,51 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   const int n_rt = (p.N + 15) / 16;
   size_t smem;
   dim3 grid;
-  int R;
   if (p.mode == 0) {
     const int mt = p.M < 8 ? p.M : 8;
     smem = (size_t)mt * (p.K + 32) * 2;
     grid.y = (p.M + 7) / 8;
   } else if (p.mode == 1) {
     smem = (size_t)(p.K + 32) * 2;
-    grid.y = p.M * S;
+    grid.y = p.M;
   } else {
     smem = (size_t)(S * p.K + 32) * 2;
     grid.y = p.M;
   }
-  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (p.tpx.out_peer_slots != nullptr && (p.act != 0 || p.mode == 1)) return (int)cudaErrorInvalidValue;
-  if (p.act == 1) {
-    if (n_rt % 2 != 0) return (int)cudaErrorInvalidValue;
-    R = 2;
-    grid.x = n_rt / 2;
-  } else {
-    R = 1;
-    grid.x = (n_rt + R - 1) / R;
-  }
+  if (p.act == 1 && n_rt % 2 != 0) return (int)cudaErrorInvalidValue;
   grid.z = 1;
-  int e;
   const bool big = p.gs_shift >= 6;
-  // warps per row tile so that a warp owns ~2 chunks; CTA = R tiles x that many warps, 8..32 warps in total
+  // Work units per token tile: row tiles (tile pairs with the fused SwiGLU), times the MoE slots in mode 1.
+  const int n_units = ((p.mode == 1) ? S : 1) * ((p.act == 1) ? n_rt / 2 : n_rt);
   const int chunks = ((p.mode == 2) ? S : 1) * (p.K / 64);
-  int wpt = 1;
-  while (wpt * 2 < chunks && wpt * R < 16) wpt *= 2;
-  int nw = wpt * R;
-  if (nw < 8) nw = 8;
-  if (nw > 16) nw = 16;     // 32 warps would cap a thread at 64 registers and spill
-#define MMB_LAUNCH_GEMV(RR, BG, NW)                                                         \
-  do {                                                                                      \
-    if ((e = set_smem(fp4_gemv_kernel<RR, BG, NW>, smem))) return e;                         \
-    return launch(fp4_gemv_kernel<RR, BG, NW>, grid, dim3(NW * 32), smem, stream, 1, p);     \
+  const int gs = 1 << p.gs_shift;
+  const int k_units = chunks / ((gs >= 64) ? (gs >> 6) : 1);      // indivisible pieces of the K axis
+  // Warps per unit: as many as keep every warp of the machine busy (148 SMs x 16 warps) while a warp still owns
+  // at least two 64-wide chunks of a tile.
+  const int warp_slots = 148 * 16 / (int)grid.y;
+  int wpt = 16;
+  while (wpt > 1 && ((long long)n_units * wpt > warp_slots || k_units < wpt || chunks < 2 * wpt)) wpt >>= 1;
+  const int nw = (wpt == 16) ? 16 : 8;
+  const int G = nw / wpt;
+  const int cta_units = (n_units + G - 1) / G;                   // CTAs needed for one unit per group
+  int cap = ((nw == 8) ? 296 : 148) / (int)grid.y;               // CTAs of one wave
+  if (cap < 1) cap = 1;
+  const int passes = (cta_units + cap - 1) / cap;
+  grid.x = (cta_units + passes - 1) / passes;
+  // dynamic shared memory: the staged activation rows, then every warp's weight ring (512 + 128 bytes per slot)
+  smem = ((smem + 127) & ~(size_t)127) + (size_t)nw * kRing * (512 + 128);
+  if (smem > 180 * 1024) return (int)cudaErrorInvalidValue;
+  int e;
+#define MMB_LAUNCH_GEMV(BG, NW)                                                                \
+  do {                                                                                         \
+    if ((e = set_smem(fp4_gemv_kernel<BG, NW>, smem, 34 * 1024))) return e;                              \
+    return launch(fp4_gemv_kernel<BG, NW>, grid, dim3(NW * 32), smem, stream, 1, p, wpt);       \
   } while (0)
-#define MMB_DISPATCH_NW(RR, BG)             \
-  do {                                      \
-    if (nw == 8) MMB_LAUNCH_GEMV(RR, BG, 8);  \
-    MMB_LAUNCH_GEMV(RR, BG, 16);            \
-  } while (0)
-  if (R == 2 && big) MMB_DISPATCH_NW(2, true);
-  if (R == 2) MMB_DISPATCH_NW(2, false);
-  if (big) MMB_DISPATCH_NW(1, true);
-  MMB_DISPATCH_NW(1, false);
-#undef MMB_DISPATCH_NW
+  if (big && nw == 8) MMB_LAUNCH_GEMV(true, 8);
+  if (big) MMB_LAUNCH_GEMV(true, 16);
+  if (nw == 8) MMB_LAUNCH_GEMV(false, 8);
+  MMB_LAUNCH_GEMV(false, 16);
 #undef MMB_LAUNCH_GEMV
 }
 

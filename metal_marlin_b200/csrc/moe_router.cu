@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const MmbRouterParams p
   __shared__ float group_s[64];
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = (cluster_size > 1) ? (int)cluster.block_rank() : 0;
+  if (cluster_size > 1) cluster_arrive();   // matched by cluster_wait() before the first store into the leader's table
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const long long tk = blockIdx.x / cluster_size;
   const bf16* W = reinterpret_cast<const bf16*>(p.w);
@@ -106,6 +107,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const MmbRouterParams p
   __syncthreads();
 
   // ---- gate GEMV for this CTA's experts; results go to the leader's logit table
+  if (cluster_size > 1) cluster_wait();
   float* leader_logits = (cluster_size > 1) ? cluster.map_shared_rank(logit_s, 0) : logit_s;
   for (int e = e_first; e < e_hi; e += 8) {
     float acc = 0.f;

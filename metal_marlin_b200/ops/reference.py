@@ -16,6 +16,18 @@ import torch
 import torch.nn.functional as F
 
 
+# Dtype of the dequantized weight copies and of the matrix products.  fp32 is the numerics oracle; the eager
+# baseline (``baseline_eager.py``) switches to bf16 so its matrix products run as library bf16 GEMMs.
+MATMUL_DTYPE = torch.float32
+
+
+def _mm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` in ``MATMUL_DTYPE``, returned as fp32."""
+    if MATMUL_DTYPE == torch.float32:
+        return x.to(torch.float32) @ w.to(torch.float32).t()
+    return F.linear(x.to(MATMUL_DTYPE), w.to(MATMUL_DTYPE)).to(torch.float32)
+
+
 def _bf(x: torch.Tensor) -> torch.Tensor:
     """Round to bf16 and come back to fp32."""
     return x.to(torch.bfloat16).to(torch.float32)
@@ -45,8 +57,8 @@ def rmsnorm(x, w, eps, delta=None, resid_out=None, out=None):
 
 def linear(x, W, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bias=None, out_add=None, out=None):
     xin = add_norm(x[:, : W.in_features], None if delta is None else delta[:, : W.in_features], norm_w, eps, resid_out)
-    wd = W.dequantize(torch.float32, cache=True)
-    y = xin @ wd.t()
+    wd = W.dequantize(MATMUL_DTYPE, cache=True)
+    y = _mm(xin, wd)
     if bias is not None:
         y = y + bias.to(torch.float32)
     if act == 1:
@@ -63,7 +75,7 @@ def linear(x, W, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bi
 
 def bf16_linear(x, w, *, delta=None, norm_w=None, eps=1e-6, out_dtype=torch.bfloat16, out=None):
     xin = add_norm(x, delta, norm_w, eps)
-    y = (xin @ w.to(torch.float32).t()).to(out_dtype)
+    y = _mm(xin, w).to(out_dtype)
     if out is not None:
         out.copy_(y)
         return out
@@ -216,7 +228,7 @@ def moe_gate_up(x, bank, ids, *, n_shared=0, shared_base=0, norm_w=None, eps=1e-
     T, topk = ids.shape
     S = topk + n_shared
     xin = add_norm(x[:, : bank.in_features], None, norm_w, eps)
-    W = bank.dequantize(torch.float32, cache=True)                     # [E, 2I, K]
+    W = bank.dequantize(MATMUL_DTYPE, cache=True)                     # [E, 2I, K]
     inter = bank.out_features // 2
     e_all = torch.cat([ids.long(), torch.arange(shared_base, shared_base + n_shared, device=x.device)
                        .expand(T, n_shared)], 1) if n_shared else ids.long()
@@ -225,7 +237,7 @@ def moe_gate_up(x, bank, ids, *, n_shared=0, shared_base=0, norm_w=None, eps=1e-
         if e < 0:
             continue
         tt, ss = (e_all == e).nonzero(as_tuple=True)
-        y = xin[tt] @ W[e].t()
+        y = _mm(xin[tt], W[e])
         res[tt, ss] = F.silu(y[:, :inter]) * y[:, inter:]
     res = res.to(torch.bfloat16).view(T * S, inter)
     if out is not None:
@@ -238,7 +250,7 @@ def moe_down(h, bank, ids, weights, *, n_shared=0, shared_base=0, out_add=None, 
     """h [T * S, I] -> [T, H] = sum_s w[t, s] * (W_d[e(t, s)] h[t, s])."""
     T, topk = ids.shape
     S = topk + n_shared
-    W = bank.dequantize(torch.float32, cache=True)
+    W = bank.dequantize(MATMUL_DTYPE, cache=True)
     hv = h.view(T, S, -1)[..., : bank.in_features].to(torch.float32)
     e_all = torch.cat([ids.long(), torch.arange(shared_base, shared_base + n_shared, device=h.device)
                        .expand(T, n_shared)], 1) if n_shared else ids.long()
@@ -249,7 +261,7 @@ def moe_down(h, bank, ids, weights, *, n_shared=0, shared_base=0, out_add=None, 
         if e < 0:
             continue
         tt, ss = (e_all == e).nonzero(as_tuple=True)
-        y.index_add_(0, tt, (hv[tt, ss] @ W[e].t()) * w_all[tt, ss].unsqueeze(-1))
+        y.index_add_(0, tt, _mm(hv[tt, ss], W[e]) * w_all[tt, ss].unsqueeze(-1))
     if out_add is not None:
         y = y + out_add.to(torch.float32)
     y = y.to(torch.bfloat16)

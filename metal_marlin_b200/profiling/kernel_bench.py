@@ -35,50 +35,59 @@ def _rand_w(n, k, dev):
     return FP4Weight.from_float(torch.randn(n, k, device=dev) * 0.02, 128)
 
 
-def build_cases(dev, batch: int, ctx: int):
+def build_cases(dev, batch: int, ctx: int, variants: int = 1):
+    """Returns ``{name: (fn, algorithmic_bytes)}``.  ``fn(i)`` runs the op on weight set ``i % variants`` so a
+    chain of calls streams distinct weights like consecutive layers of a model do."""
     H, R, dr, dn, dv, NH = 2048, 512, 64, 192, 256, 20
     E, I, topk = 64, 1536, 4
+    V = max(1, variants)
     bf = lambda *s: (torch.randn(*s, device=dev) * 0.5).to(torch.bfloat16)
     cases = {}
     x = bf(batch, H)
     delta = bf(batch, H)
     nw = torch.ones(H, device=dev, dtype=torch.bfloat16)
-    w_qa = _rand_w(768 + 576, H, dev)
-    cases["qa_kva_gemv"] = (lambda: ops.linear(x, w_qa, delta=delta, norm_w=nw, resid_out=torch.empty_like(x)), w_qa.nbytes())
-    w_qb = _rand_w(NH * 256, 768, dev)
+    ro = torch.empty_like(x)
+
+    def clones(w):
+        return [w] + [FP4Weight(w.qtile.clone(), w.stile.clone(), w.out_features, w.in_features, w.group_size) for _ in range(V - 1)]
+
+    w_qa = clones(_rand_w(768 + 576, H, dev))
+    cases["qa_kva_gemv"] = (lambda i=0: ops.linear(x, w_qa[i % V], delta=delta, norm_w=nw, resid_out=ro), w_qa[0].nbytes())
+    w_qb = clones(_rand_w(NH * 256, 768, dev))
     a = bf(batch, 1344)
     nq = torch.ones(768, device=dev, dtype=torch.bfloat16)
-    cases["q_b_gemv"] = (lambda: ops.linear(a[:, :768], w_qb, norm_w=nq), w_qb.nbytes())
-    w_o = _rand_w(H, NH * dv, dev)
+    cases["q_b_gemv"] = (lambda i=0: ops.linear(a[:, :768], w_qb[i % V], norm_w=nq), w_qb[0].nbytes())
+    w_o = clones(_rand_w(H, NH * dv, dev))
     ao = bf(batch, NH * dv)
-    cases["o_proj_gemv"] = (lambda: ops.linear(ao, w_o), w_o.nbytes())
+    cases["o_proj_gemv"] = (lambda i=0: ops.linear(ao, w_o[i % V]), w_o[0].nbytes())
     # MLA prologue / attention / epilogue
     q = bf(batch, NH * (dn + dr))
     kva = bf(batch, R + dr)
-    w_ukT, w_uv = bf(NH, R, dn), bf(NH, dv, R)
+    w_ukT = [bf(NH, R, dn) for _ in range(V)]
+    w_uv = [bf(NH, dv, R) for _ in range(V)]
     nkv = torch.ones(R, device=dev, dtype=torch.bfloat16)
     bs = 16
     nb = (ctx + bs) // bs + 1
-    cache = bf(batch * nb * bs, R + dr)
+    cache = [bf(batch * nb * bs, R + dr) for _ in range(V)]
     bt = torch.arange(batch * nb, dtype=torch.int32, device=dev).view(batch, nb)
     cl = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
     pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device=dev)
     slots = (bt[:, (ctx - 1) // bs].long() * bs + (ctx - 1) % bs)
     inv = 1.0 / (1e6 ** (torch.arange(0, dr, 2, device=dev).float() / dr))
     qf = torch.empty(batch, NH, R + dr, dtype=torch.bfloat16, device=dev)
-    cases["mla_prep"] = (lambda: ops.mla_prep(q, kva, w_ukT, nkv, pos, inv, slots, qf, cache, NH, dn, dr, R, 1e-5, 1.0, True),
-                         w_ukT.numel() * 2)
+    cases["mla_prep"] = (lambda i=0: ops.mla_prep(q, kva, w_ukT[i % V], nkv, pos, inv, slots, qf, cache[i % V], NH, dn, dr, R, 1e-5,
+                                                  1.0, True), w_ukT[0].numel() * 2)
     splits = ops.default_splits(batch, 1, ctx)
-    cases["mla_decode_attn"] = (lambda: ops.paged_attention(qf, cache, None, bt, cl, Hq=NH, Hkv=1, dqk=R + dr, dv=R, block_size=bs,
-                                                            scale=1 / 16.0, splits=splits, w_uv=w_uv),
-                                batch * ctx * (R + dr) * 2 + w_uv.numel() * 2)
+    cases["mla_decode_attn"] = (lambda i=0: ops.paged_attention(qf, cache[i % V], None, bt, cl, Hq=NH, Hkv=1, dqk=R + dr, dv=R,
+                                                                block_size=bs, scale=1 / 16.0, splits=splits, w_uv=w_uv[i % V]),
+                                batch * ctx * (R + dr) * 2 + w_uv[0].numel() * 2)
     # MoE
-    rw = bf(E, H)
+    rw = [bf(E, H) for _ in range(V)]
     rb = torch.zeros(E, device=dev)
-    ids = torch.stack([torch.randperm(E, device=dev)[:topk] for _ in range(batch)]).to(torch.int32)
+    ids = [torch.stack([torch.randperm(E, device=dev)[:topk] for _ in range(batch)]).to(torch.int32) for _ in range(V)]
     wts = torch.rand(batch, topk, device=dev)
-    cases["moe_router"] = (lambda: ops.moe_router(x, rw, delta=delta, norm_w=nw, resid_out=torch.empty_like(x), bias=rb, topk=topk,
-                                                  scoring=1, renorm=True, routed_scale=1.8), rw.numel() * 2)
+    cases["moe_router"] = (lambda i=0: ops.moe_router(x, rw[i % V], delta=delta, norm_w=nw, resid_out=ro, bias=rb, topk=topk,
+                                                      scoring=1, renorm=True, routed_scale=1.8), rw[0].numel() * 2)
     gu = FP4ExpertBank(torch.randint(-2 ** 31, 2 ** 31 - 1, (E + 1, 2 * I // 16, H // 64, 32, 4), dtype=torch.int32, device=dev),
                        (torch.rand(E + 1, 2 * I // 16, H // 128, 8, 2, device=dev) * 0.01).half(), 2 * I, H, 128)
     dn_b = FP4ExpertBank(torch.randint(-2 ** 31, 2 ** 31 - 1, (E + 1, H // 16, I // 64, 32, 4), dtype=torch.int32, device=dev),
@@ -87,21 +96,21 @@ def build_cases(dev, batch: int, ctx: int):
     active = min(E, batch * topk) + 1
     per_exp_gu = 2 * I * H // 2 + 2 * I * (H // 128) * 2
     per_exp_dn = H * I // 2 + H * (I // 128) * 2
-    cases["moe_gate_up"] = (lambda: ops.moe_gate_up(x, gu, ids, n_shared=1, shared_base=E, norm_w=nw),
+    cases["moe_gate_up"] = (lambda i=0: ops.moe_gate_up(x, gu, ids[i % V], n_shared=1, shared_base=E, norm_w=nw),
                             (batch * slots_per_tok if batch <= 16 else active) * per_exp_gu)
     hi = bf(batch * slots_per_tok, I)
-    cases["moe_down"] = (lambda: ops.moe_down(hi, dn_b, ids, wts, n_shared=1, shared_base=E),
+    cases["moe_down"] = (lambda i=0: ops.moe_down(hi, dn_b, ids[i % V], wts, n_shared=1, shared_base=E),
                          (batch * slots_per_tok if batch <= 16 else active) * per_exp_dn)
-    cases["moe_forward"] = (lambda: ops.moe_forward(x, gu, dn_b, ids, wts, n_shared=1, shared_base=E, norm_w=nw),
+    cases["moe_forward"] = (lambda i=0: ops.moe_forward(x, gu, dn_b, ids[i % V], wts, n_shared=1, shared_base=E, norm_w=nw),
                             (batch * slots_per_tok if batch <= 16 else active) * (per_exp_gu + per_exp_dn))
     head = bf(154880, H)
-    cases["lm_head"] = (lambda: ops.bf16_linear(x, head, delta=delta, norm_w=nw, out_dtype=torch.float32), head.numel() * 2)
+    cases["lm_head"] = (lambda i=0: ops.bf16_linear(x, head, delta=delta, norm_w=nw, out_dtype=torch.float32), head.numel() * 2)
     lg = torch.randn(batch, 154880, device=dev)
-    cases["argmax"] = (lambda: ops.argmax(lg), lg.numel() * 4)
+    cases["argmax"] = (lambda i=0: ops.argmax(lg), lg.numel() * 4)
     # prefill-size GEMMs on the tensor-core path
     xp = bf(4096, H)
     w_gu = _rand_w(2 * I, H, dev)
-    cases["gemm_4096x3072x2048"] = (lambda: ops.linear(xp, w_gu), 2.0 * 4096 * 2 * I * H)
+    cases["gemm_4096x3072x2048"] = (lambda i=0: ops.linear(xp, w_gu), 2.0 * 4096 * 2 * I * H)
     return cases
 
 
@@ -113,10 +122,13 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--chain", type=int, default=0,
+                    help="time a CUDA graph of this many dependent launches of the op on distinct weight sets "
+                         "(in-graph cost per launch, as inside a decode step) instead of isolated cold launches")
     args = ap.parse_args()
     dev = torch.device("cuda")
     assert ops.native_available()
-    cases = build_cases(dev, args.batch, args.ctx)
+    cases = build_cases(dev, args.batch, args.ctx, variants=max(1, args.chain))
     names = list(cases) if args.op == "all" else args.op.split(",")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     peak = _peak_gbs()
@@ -127,6 +139,33 @@ def main():
             fn()
         torch.cuda.synchronize()
         ts = []
+        if args.chain > 0:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(args.chain):
+                    fn(i)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(args.chain):
+                        fn(i)
+            torch.cuda.current_stream().wait_stream(side)
+            graph.replay()
+            torch.cuda.synchronize()
+            for _ in range(args.iters):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1e3 / args.chain)
+            ts.sort()
+            med = ts[len(ts) // 2]
+            gbs = nbytes / med / 1e3
+            out[n] = {"us_per_launch_in_graph": round(med, 2), "chain": args.chain, "MB": round(nbytes / 1e6, 3), "GBps": round(gbs, 1)}
+            print(n, out[n], flush=True)
+            del graph
+            continue
         for _ in range(args.iters):
             if not args.no_flush:
                 flush.fill_(1)

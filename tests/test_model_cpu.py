@@ -54,3 +54,23 @@ def test_config_from_hf_dict_aliases(tmp_path):
     cfg = ModelConfig.from_pretrained(str(tmp_path))
     assert cfg.num_experts == 8 and cfg.is_mla and cfg.group_size == 32 and cfg.quant_format == "mmfp4"
     assert cfg.scoring_func == "sigmoid" and cfg.rope_interleave
+
+
+def test_eager_bf16_baseline_tracks_the_model():
+    """The eager bf16 baseline wrapper runs prefill + decode and stays close to the fp32-restatement logits."""
+    from metal_marlin_b200.baseline_eager import EagerBF16Model
+    from metal_marlin_b200.engine.session import DecodeSession, SamplingParams
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM, prefill
+    lm = MMFP4ForCausalLM.from_config("tiny-mla-moe", device="cpu", seed=2)
+    em = EagerBF16Model(lm.model)
+    prompts = [list(range(5, 30))]
+    bt = torch.arange(4, dtype=torch.int32).view(1, 4)
+    kv_a, kv_b = lm.new_cache(4, 16), lm.new_cache(4, 16)
+    lg_ref = prefill(lm.model, kv_a, prompts, bt)
+    lg_eager = em.prefill(kv_b, prompts, bt)
+    assert (lg_ref - lg_eager).abs().max() / lg_ref.abs().max() < 0.1
+    sess = DecodeSession(em, kv_b, 1, 4, max_new_tokens=4, use_graph=False)
+    sess.set_sampling([SamplingParams()])
+    sess.set_state(lg_eager.argmax(-1), [25], bt)
+    toks = [int(sess.step()[0]) for _ in range(3)]
+    assert all(0 <= t < lm.config.vocab_size for t in toks)
