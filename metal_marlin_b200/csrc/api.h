@@ -114,6 +114,7 @@ typedef struct {
   int B, Hq, Hkv, dqk, dv, block_size, max_blocks, splits;
   float scale;
   int window;               // 0 = full; >0 = attend to the last `window` tokens only
+  int* status;              // optional device word: set non-zero when a bounded wait inside the kernel expired
 } MmbPagedDecodeParams;
 int mmb_paged_decode(const MmbPagedDecodeParams* p, cudaStream_t stream);
 // Merge the split partials; optional per-head up projection W_uv [Hq, dvo, dv] (MLA), output bf16 [B, Hq, dvo or dv].

@@ -223,68 +223,57 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
     return;
   }
 
-  // Block-table entries of a 64-token tile are fetched once per tile (four independent loads for 16-token
-  // blocks) instead of once per copied row, so no copy waits on a table lookup of its own.
-  const bool pow2_blocks = (p.block_size & (p.block_size - 1)) == 0 && p.block_size >= 16;
+  // K / V rows of a tile and the query rows arrive by bulk copies (one per row, issued by one lane each) that
+  // signal an mbarrier per buffer; rows past the end of the sequence are zero-filled with plain stores.
+  __shared__ __align__(8) uint64_t bar_kv[2];
+  __shared__ __align__(8) uint64_t bar_q;
+  __shared__ int abort_s;
+  if (tid == 0) {
+    mbar_init(&bar_kv[0], 1);
+    mbar_init(&bar_kv[1], 1);
+    mbar_init(&bar_q, 1);
+    abort_s = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const bool pow2_blocks = (p.block_size & (p.block_size - 1)) == 0;
   const int bs_shift = pow2_blocks ? (31 - __clz(p.block_size)) : 0;
   auto load_tile = [&](int tile, int buf) {
     const int tok0 = lo_al + tile * kTileTok;
-    int blk[4] = {0, 0, 0, 0};
-    if (pow2_blocks) {
-      const int last_blk = (ctx - 1) >> bs_shift;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int bi = (tok0 >> bs_shift) + j;
-        if ((j << bs_shift) < kTileTok && bi <= last_blk) blk[j] = __ldg(bt + bi);
-      }
-    }
-    auto slot_of = [&](int r) -> long long {
-      const int tok = tok0 + r;
-      if (pow2_blocks) {
-        const int j = (tok >> bs_shift) - (tok0 >> bs_shift);
-        const int bsel = (j == 0) ? blk[0] : ((j == 1) ? blk[1] : ((j == 2) ? blk[2] : blk[3]));
-        return ((long long)bsel << bs_shift) + (tok & (p.block_size - 1));
-      }
-      return (long long)bt[tok / p.block_size] * p.block_size + (tok % p.block_size);
-    };
+    const int nvalid = min(kTileTok, ctx - tok0);
     bf16* kd = buf ? k_s1 : k_s0;
-    constexpr int KCH = DQK / 8;
-#pragma unroll 4
-    for (int i = tid; i < kTileTok * KCH; i += NT) {
-      const int r = i / KCH, c = i % KCH;
-      const bool valid = tok0 + r < ctx;
-      const long long slot = valid ? slot_of(r) : 0;
-      cp_async16(kd + r * L::KS + c * 8, kp + (slot * p.Hkv + hkv) * DQK + c * 8, valid);
+    bf16* vd = buf ? v_s1 : v_s0;
+    if (tid == 0) mbar_expect_tx(&bar_kv[buf], (uint32_t)nvalid * (uint32_t)((DQK + (SHARED_V ? 0 : DV)) * 2));
+    if (tid < nvalid) {
+      const int tok = tok0 + tid;
+      const long long slot = pow2_blocks ? (((long long)__ldg(bt + (tok >> bs_shift)) << bs_shift) + (tok & (p.block_size - 1)))
+                                         : ((long long)__ldg(bt + tok / p.block_size) * p.block_size + (tok % p.block_size));
+      bulk_g2s(kd + tid * L::KS, kp + (slot * p.Hkv + hkv) * DQK, DQK * 2, &bar_kv[buf]);
+      if (!SHARED_V) bulk_g2s(vd + tid * L::VS, vp + (slot * p.Hkv + hkv) * DV, DV * 2, &bar_kv[buf]);
     }
-    if (!SHARED_V) {
-      bf16* vd = buf ? v_s1 : v_s0;
-      constexpr int VCH = DV / 8;
-#pragma unroll 4
-      for (int i = tid; i < kTileTok * VCH; i += NT) {
-        const int r = i / VCH, c = i % VCH;
-        const bool valid = tok0 + r < ctx;
-        const long long slot = valid ? slot_of(r) : 0;
-        cp_async16(vd + r * L::VS + c * 8, vp + (slot * p.Hkv + hkv) * DV + c * 8, valid);
-      }
+    if (nvalid < kTileTok) {
+      constexpr int KCH = DQK / 8, VCH = DV / 8;
+      for (int i = tid; i < (kTileTok - nvalid) * KCH; i += NT)
+        *reinterpret_cast<uint4*>(kd + (nvalid + i / KCH) * L::KS + (i % KCH) * 8) = make_uint4(0, 0, 0, 0);
+      if (!SHARED_V)
+        for (int i = tid; i < (kTileTok - nvalid) * VCH; i += NT)
+          *reinterpret_cast<uint4*>(vd + (nvalid + i / VCH) * L::VS + (i % VCH) * 8) = make_uint4(0, 0, 0, 0);
     }
-    cp_async_commit();
   };
 
   // The cache row of this step's token (position ctx - 1) is written by the previous kernel; every other
   // row is older.  A first tile that does not contain it can be requested before waiting.
   const bool first_is_old = (lo_al + (tile_begin + 1) * kTileTok) <= ctx - 1;
   if (first_is_old) load_tile(tile_begin, 0);
+  // query rows beyond the group are zero and never change
+  for (int i = tid; i < (MT * 16 - Gh) * (DQK / 8); i += NT)
+    *reinterpret_cast<uint4*>(q_s + (Gh + i / (DQK / 8)) * L::KS + (i % (DQK / 8)) * 8) = make_uint4(0, 0, 0, 0);
   pdl_launch_dependents();
   pdl_wait();
+  if (tid == 0) mbar_expect_tx(&bar_q, (uint32_t)Gh * (uint32_t)(DQK * 2));
+  if (tid >= 64 && tid < 64 + Gh) bulk_g2s(q_s + (tid - 64) * L::KS, q + (long long)(tid - 64) * DQK, DQK * 2, &bar_q);
   if (!first_is_old) load_tile(tile_begin, 0);
 
-  // ---- stage Q (zero padded to MT*16 rows)
-  for (int i = tid; i < MT * 16 * (DQK / 8); i += NT) {
-    const int r = i / (DQK / 8), c = i % (DQK / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < Gh) v = *reinterpret_cast<const uint4*>(q + (long long)r * DQK + c * 8);
-    *reinterpret_cast<uint4*>(q_s + r * L::KS + c * 8) = v;
-  }
   if (tid < MT * 16) {
     row_m[tid] = -INFINITY;
     row_l[tid] = 0.f;
@@ -300,42 +289,60 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int buf = (tile - tile_begin) & 1;
-    if (tile + 1 < tile_end) {
-      load_tile(tile + 1, buf ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    if (tile + 1 < tile_end) load_tile(tile + 1, buf ^ 1);
+    bool landed = mbar_wait(&bar_kv[buf], (uint32_t)((tile - tile_begin) >> 1) & 1u, &abort_s);
+    if (tile == tile_begin) landed = mbar_wait(&bar_q, 0u, &abort_s) && landed;
+    if (!landed) abort_s = 1;
+    // tile `buf` (and, first time, Q and the zero rows) visible to all warps; a wait that expired ends the loop
+    // for the whole CTA at once
+    if (!__syncthreads_and(landed ? 1 : 0)) {
+      if (tid == 0 && p.status != nullptr) atomicExch(p.status, 200);
+      break;
     }
-    __syncthreads();   // tile `buf` (and, first time, Q) visible to all warps
     const bf16* kt = buf ? k_s1 : k_s0;
     const bf16* vt = buf ? v_s1 : v_s0;
 
     // ---- S = Q K^T for this warp's token columns
     {
-      float s[MT][NQ][4];
+      // two accumulator sets (even / odd k16 steps) halve the dependent MMA chain of this latency-bound loop
+      float s[MT][NQ][4], s_odd[MT][NQ][4];
 #pragma unroll
       for (int m = 0; m < MT; ++m)
 #pragma unroll
         for (int n = 0; n < NQ; ++n)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) s[m][n][e] = 0.f;
+          for (int e = 0; e < 4; ++e) s[m][n][e] = s_odd[m][n][e] = 0.f;
       const bf16* kb = kt + (warp * (64 / NW) + g) * L::KS + 2 * t;
-#pragma unroll 4
-      for (int k0 = 0; k0 < DQK; k0 += 16) {
-        uint32_t bfr[NQ][2];
+      static_assert(DQK % 32 == 0, "the QK^T loop consumes two k16 steps per trip");
+#pragma unroll 2
+      for (int k0 = 0; k0 < DQK; k0 += 32) {
 #pragma unroll
-        for (int n = 0; n < NQ; ++n) {
-          bfr[n][0] = *reinterpret_cast<const uint32_t*>(kb + n * 8 * L::KS + k0);
-          bfr[n][1] = *reinterpret_cast<const uint32_t*>(kb + n * 8 * L::KS + k0 + 8);
-        }
+        for (int half = 0; half < 2; ++half) {
+          const int kk = k0 + half * 16;
+          uint32_t bfr[NQ][2];
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          uint32_t a0, a1, a2, a3;
-          ldmatrix_x4(a0, a1, a2, a3, q_s + (m * 16 + (lane & 15)) * L::KS + k0 + (lane >> 4) * 8);
+          for (int n = 0; n < NQ; ++n) {
+            bfr[n][0] = *reinterpret_cast<const uint32_t*>(kb + n * 8 * L::KS + kk);
+            bfr[n][1] = *reinterpret_cast<const uint32_t*>(kb + n * 8 * L::KS + kk + 8);
+          }
 #pragma unroll
-          for (int n = 0; n < NQ; ++n) mma_bf16_16816(s[m][n], a0, a1, a2, a3, bfr[n][0], bfr[n][1]);
+          for (int m = 0; m < MT; ++m) {
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(a0, a1, a2, a3, q_s + (m * 16 + (lane & 15)) * L::KS + kk + (lane >> 4) * 8);
+#pragma unroll
+            for (int n = 0; n < NQ; ++n) {
+              if (half == 0) mma_bf16_16816(s[m][n], a0, a1, a2, a3, bfr[n][0], bfr[n][1]);
+              else mma_bf16_16816(s_odd[m][n], a0, a1, a2, a3, bfr[n][0], bfr[n][1]);
+            }
+          }
         }
       }
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int n = 0; n < NQ; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[m][n][e] += s_odd[m][n][e];
       const int tok0 = lo_al + tile * kTileTok;
 #pragma unroll
       for (int m = 0; m < MT; ++m)
@@ -445,11 +452,13 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
 // applies its 32-row slab of W_uv (requested before anything else) to the full merged latent.
 constexpr int kMergeTok = 8;
 constexpr int kMergeRows = 32;
+// position of latent element d inside a token's row of the merged-latent tile: [d / 256][(d / 4) % 2][(d / 8) % 32][d % 4]
+__device__ __forceinline__ int merge_perm(int d) { return (((d >> 8) * 2 + ((d >> 2) & 1)) << 7) + (((d >> 3) & 31) << 2) + (d & 3); }
 __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restrict__ part_o,
                                                            const float* __restrict__ part_ml,
                                                            const bf16* __restrict__ w_uv, bf16* __restrict__ out, int B,
                                                            int Hq, int dv, int dvo, int splits, int CL) {
-  extern __shared__ float o_s[];   // [kMergeTok][dv]
+  extern __shared__ __align__(16) float o_s[];   // [kMergeTok][DS] merged latent (permuted), then weights and partial sums
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = (CL > 1) ? (int)cluster.block_rank() : 0;
   if (CL > 1) cluster_arrive();   // matched by cluster_wait() before the first remote shared-memory store
@@ -474,23 +483,56 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
   }
   pdl_launch_dependents();
   pdl_wait();
-  // ---- merge this CTA's column slice.  Split weights first (one warp per token: lanes cover the splits),
-  // then the weighted sum with the splits spread over thread groups so every partial is requested at once.
-  float* wgt = o_s + kMergeTok * dv;               // [kMergeTok][splits]: exp(m_s - M) / L, 0 for empty splits
+  // ---- merge this CTA's column slice.  The partial outputs of the first token are requested first, then the
+  // split weights are computed (one warp per token: lanes cover the splits) while those loads are in flight.
+  // Merged latent layout in shared memory: element d of a token sits at merge_perm(d), which puts the eight
+  // values a lane multiplies with one 16-byte weight word into two lane-contiguous float4 (no bank conflicts).
+  const int DS = (dv <= 256) ? 256 : 512;          // row stride of o_s
+  float* wgt = o_s + kMergeTok * DS;               // [kMergeTok][splits]: exp(m_s - M) / L, 0 for empty splits
   float* red = wgt + kMergeTok * splits;           // [groups][per] partial sums of one token
   const int per = (dv + CL - 1) / CL;
   const int d_lo = crank * per, d_hi = min(dv, d_lo + per);
+  const int quads = (d_hi - d_lo + 3) >> 2;        // float4 columns of the slice (dv and per are multiples of 4)
+  int groups = 256 / quads;
+  if (groups < 1) groups = 1;
+  if (groups > splits) groups = splits;
+  const int cq = tid % quads, sg = tid / quads;
+  const bool worker = sg < groups;
+  float4 pre[4];
+  if (worker) {
+    const long long base = ((long long)b0 * Hq + h) * splits;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int s = sg + i * groups;
+      pre[i] = (s < splits) ? __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * dv + d_lo + cq * 4))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   if (warp < nb) {
     const long long base = ((long long)(b0 + warp) * Hq + h) * splits;
+    float2 mlr[2];
     float M = -INFINITY;
-    for (int s = lane; s < splits; s += 32) {
-      const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int s = lane + 32 * i;
+      mlr[i] = (s < splits) ? __ldcg(reinterpret_cast<const float2*>(part_ml + (base + s) * 2)) : make_float2(-INFINITY, 0.f);
+      if (mlr[i].y > 0.f) M = fmaxf(M, mlr[i].x);
+    }
+    for (int s = lane + 64; s < splits; s += 32) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (base + s) * 2));
       if (ml.y > 0.f) M = fmaxf(M, ml.x);
     }
     M = warp_max(M);
     float Lsum = 0.f;
-    for (int s = lane; s < splits; s += 32) {
-      const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int s = lane + 32 * i;
+      const float w = (mlr[i].y > 0.f) ? __expf(mlr[i].x - M) : 0.f;
+      if (s < splits) wgt[warp * splits + s] = w;
+      Lsum += mlr[i].y * w;
+    }
+    for (int s = lane + 64; s < splits; s += 32) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (base + s) * 2));
       const float w = (ml.y > 0.f) ? __expf(ml.x - M) : 0.f;
       wgt[warp * splits + s] = w;
       Lsum += ml.y * w;
@@ -501,51 +543,55 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
     for (int s = lane; s < splits; s += 32) wgt[warp * splits + s] *= inv;
   }
   __syncthreads();
-  {
-    const int quads = (d_hi - d_lo + 3) >> 2;      // float4 columns of the slice (dv and per are multiples of 8)
-    int groups = 256 / quads;
-    if (groups < 1) groups = 1;
-    if (groups > splits) groups = splits;
-    const int cq = tid % quads, sg = tid / quads;
-    const bool worker = sg < groups;
-    if (CL > 1) cluster_wait();
-    for (int j = 0; j < nb; ++j) {
-      const long long base = ((long long)(b0 + j) * Hq + h) * splits;
-      if (worker) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int s = sg; s < splits; s += groups) {
-          const float w = wgt[j * splits + s];
+  if (CL > 1) cluster_wait();
+  for (int j = 0; j < nb; ++j) {
+    const long long base = ((long long)(b0 + j) * Hq + h) * splits;
+    if (worker) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s0 = sg, round = 0; s0 < splits; s0 += 4 * groups, ++round) {
+        float4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int s = s0 + i * groups;
+          if (j == 0 && round == 0) v[i] = pre[i];
+          else v[i] = (s < splits) ? __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * dv + d_lo + cq * 4))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int s = s0 + i * groups;
+          const float w = (s < splits) ? wgt[j * splits + s] : 0.f;
           if (w != 0.f) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * dv + d_lo + cq * 4));
-            acc.x = fmaf(v.x, w, acc.x);
-            acc.y = fmaf(v.y, w, acc.y);
-            acc.z = fmaf(v.z, w, acc.z);
-            acc.w = fmaf(v.w, w, acc.w);
+            acc.x = fmaf(v[i].x, w, acc.x);
+            acc.y = fmaf(v[i].y, w, acc.y);
+            acc.z = fmaf(v[i].z, w, acc.z);
+            acc.w = fmaf(v[i].w, w, acc.w);
           }
         }
-        *reinterpret_cast<float4*>(red + sg * per + cq * 4) = acc;
       }
-      __syncthreads();
-      for (int d = tid; d < d_hi - d_lo; d += 256) {
-        float a = 0.f;
-        for (int gI = 0; gI < groups; ++gI) a += red[gI * per + d];
-        // round the merged latent to bf16 (an unfused pipeline would store it in bf16)
-        const float v = __bfloat162float(__float2bfloat16(a));
-        if (CL > 1) {
-          for (int c = 0; c < CL; ++c) cluster.map_shared_rank(o_s, c)[j * dv + d_lo + d] = v;
-        } else {
-          o_s[j * dv + d_lo + d] = v;
-        }
-      }
-      __syncthreads();
+      *reinterpret_cast<float4*>(red + sg * per + cq * 4) = acc;
     }
+    __syncthreads();
+    for (int d = tid; d < d_hi - d_lo; d += 256) {
+      float a = 0.f;
+      for (int gI = 0; gI < groups; ++gI) a += red[gI * per + d];
+      // round the merged latent to bf16 (an unfused pipeline would store it in bf16)
+      const float v = __bfloat162float(__float2bfloat16(a));
+      const int pd = j * DS + merge_perm(d_lo + d);
+      if (CL > 1) {
+        for (int c = 0; c < CL; ++c) cluster.map_shared_rank(o_s, c)[pd] = v;
+      } else {
+        o_s[pd] = v;
+      }
+    }
+    __syncthreads();
   }
   if (CL > 1) cluster.sync();
   else __syncthreads();
   if (W == nullptr) {
     for (int j = 0; j < nb; ++j)
-      for (int d = d_lo + tid; d < d_hi; d += 256) out[((long long)(b0 + j) * Hq + h) * dv + d] = __float2bfloat16(o_s[j * dv + d]);
+      for (int d = d_lo + tid; d < d_hi; d += 256)
+        out[((long long)(b0 + j) * Hq + h) * dv + d] = __float2bfloat16(o_s[j * DS + merge_perm(d)]);
     return;
   }
   for (int slab = crank; slab * kMergeRows < dvo; slab += CL) {
@@ -561,13 +607,18 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
         const int d = u * 256 + lane * 8;
         if (d < dv) {
           const uint4 w4 = (slab == crank) ? wv[r][u] : ldg_stream(reinterpret_cast<const uint4*>(W + (long long)row * dv + d));
-          const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+          const float wf[8] = {__uint_as_float(w4.x << 16), __uint_as_float(w4.x & 0xffff0000u),
+                               __uint_as_float(w4.y << 16), __uint_as_float(w4.y & 0xffff0000u),
+                               __uint_as_float(w4.z << 16), __uint_as_float(w4.z & 0xffff0000u),
+                               __uint_as_float(w4.w << 16), __uint_as_float(w4.w & 0xffff0000u)};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float w0 = __uint_as_float(ww[e] << 16), w1 = __uint_as_float(ww[e] & 0xffff0000u);
-#pragma unroll
-            for (int j = 0; j < kMergeTok; ++j)
-              if (j < nb) acc[j] = fmaf(w0, o_s[j * dv + d + 2 * e], fmaf(w1, o_s[j * dv + d + 2 * e + 1], acc[j]));
+          for (int j = 0; j < kMergeTok; ++j) {
+            if (j < nb) {
+              const float4 x0 = *reinterpret_cast<const float4*>(o_s + j * DS + (u * 2) * 128 + lane * 4);
+              const float4 x1 = *reinterpret_cast<const float4*>(o_s + j * DS + (u * 2 + 1) * 128 + lane * 4);
+              acc[j] = fmaf(wf[0], x0.x, fmaf(wf[1], x0.y, fmaf(wf[2], x0.z, fmaf(wf[3], x0.w, acc[j]))));
+              acc[j] = fmaf(wf[4], x1.x, fmaf(wf[5], x1.y, fmaf(wf[6], x1.z, fmaf(wf[7], x1.w, acc[j]))));
+            }
           }
         }
       }
@@ -640,7 +691,8 @@ MMB_API int mmb_decode_merge(const float* part_o, const float* part_ml, const vo
   int groups = 256 / (per / 4);
   if (groups < 1) groups = 1;
   if (groups > splits) groups = splits;
-  const size_t smem = ((size_t)mmb::kMergeTok * dv + (size_t)mmb::kMergeTok * splits + (size_t)groups * per) * 4;
+  const int ds = (dv <= 256) ? 256 : 512;
+  const size_t smem = ((size_t)mmb::kMergeTok * ds + (size_t)mmb::kMergeTok * splits + (size_t)groups * per) * 4;
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   dim3 grid(Hq * cl, (B + mmb::kMergeTok - 1) / mmb::kMergeTok);
   return mmb::launch(mmb::decode_merge_kernel, grid, dim3(256), smem, stream, cl, part_o, part_ml, (const bf16*)w_uv,

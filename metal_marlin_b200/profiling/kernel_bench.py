@@ -81,6 +81,18 @@ def build_cases(dev, batch: int, ctx: int, variants: int = 1):
     cases["mla_decode_attn"] = (lambda i=0: ops.paged_attention(qf, cache[i % V], None, bt, cl, Hq=NH, Hkv=1, dqk=R + dr, dv=R,
                                                                 block_size=bs, scale=1 / 16.0, splits=splits, w_uv=w_uv[i % V]),
                                 batch * ctx * (R + dr) * 2 + w_uv[0].numel() * 2)
+    part_o = torch.empty(batch * NH * splits * R, dtype=torch.float32, device=dev)
+    part_ml = torch.empty(batch * NH * splits * 2, dtype=torch.float32, device=dev)
+    o_att = torch.empty(batch, NH, dv, dtype=torch.bfloat16, device=dev)
+    ops.paged_attention(qf, cache[0], None, bt, cl, Hq=NH, Hkv=1, dqk=R + dr, dv=R, block_size=bs, scale=1 / 16.0, splits=splits,
+                        w_uv=w_uv[0], workspace=(part_o, part_ml), out=o_att)          # fills the partials for the merge-only case
+    cases["paged_decode_only"] = (lambda i=0: ops.K.mmb200.paged_decode(qf, cache[i % V], None, bt, cl, part_o, part_ml, NH, 1, R + dr, R,
+                                                                        bs, splits, 1 / 16.0, 0),
+                                  batch * ctx * (R + dr) * 2)
+    cases["decode_merge_only"] = (lambda i=0: ops.K.mmb200.decode_merge(part_o, part_ml, w_uv[i % V], o_att, batch, NH, R, dv, splits),
+                                  w_uv[0].numel() * 2 + part_o.numel() * 4)
+    tiny = bf(batch, H)
+    cases["launch_floor_add"] = (lambda i=0: ops.K.mmb200.add(tiny, delta, ro), 3 * tiny.numel() * 2)
     # MoE
     rw = [bf(E, H) for _ in range(V)]
     rb = torch.zeros(E, device=dev)
