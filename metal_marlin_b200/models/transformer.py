@@ -169,6 +169,7 @@ class Transformer:
         self.mtp = None      # optional multi-token-prediction head (spec/mtp.py)
         # tensor parallelism (parallel/tp.py): a shard keeps only its local heads / vocabulary rows
         self.tp = None
+        self.routing_hook = None     # optional callable(layer, expert_ids, router_probs)
         self.n_heads_local = cfg.num_attention_heads
         self.n_kv_heads_local = cfg.num_key_value_heads
         self.vocab_range = (0, cfg.vocab_size)
@@ -314,6 +315,8 @@ class Transformer:
                                   scoring=1 if cfg.scoring_func == "sigmoid" else 0, renorm=cfg.norm_topk_prob,
                                   routed_scale=cfg.routed_scaling_factor, n_group=cfg.n_group, topk_group=cfg.topk_group,
                                   counts=counts)
+        if self.routing_hook is not None:
+            self.routing_hook(li, ids, None)       # analysis tools (expert-usage profiler); forces no sync by itself
         if self.tp is not None:
             return new_h, self.tp.moe_row_parallel(new_h, {"norm_w": L.post_norm, "eps": cfg.rms_norm_eps}, L, ids, wts, cfg,
                                                    2 * li + 1)
