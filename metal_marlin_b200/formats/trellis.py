@@ -291,3 +291,36 @@ class TrellisModelLoader:
         for e in self.meta.values():
             h[e["bits"]] = h.get(e["bits"], 0) + 1
         return dict(sorted(h.items()))
+
+
+def quantize_model_trellis(model_dir: str, out_dir: str, bits: int = 4, group_size: int = 128, device: str = "cpu",
+                           container: str = "v3", bit_allocation: Optional[Dict[str, int]] = None) -> dict:
+    """Quantize a float HF checkpoint into a trellis container.  Linear weights (2-D, not embeddings / norms /
+    routers) become trellis tensors at ``bits`` (or ``bit_allocation[name]``); everything else is kept as is."""
+    from ..quant.convert import iter_safetensors_weights, should_quantize_tensor
+    weights: Dict[str, TrellisWeight] = {}
+    base: Dict[str, torch.Tensor] = {}
+    errs = []
+    for name, t in iter_safetensors_weights(model_dir):
+        if should_quantize_tensor(name, t):
+            b = (bit_allocation or {}).get(name, bits)
+            tw = quantize_trellis(t.to(device=device, dtype=torch.float32), b, group_size, seed=len(weights))
+            tw.name = name
+            weights[name] = tw
+            w = t.float()
+            errs.append(float((tw.dequantize().to(w.device) - w).pow(2).mean().sqrt() / w.pow(2).mean().sqrt().clamp_min(1e-12)))
+        else:
+            base[name] = t
+    cfg = None
+    cp = os.path.join(model_dir, "config.json")
+    if os.path.exists(cp):
+        with open(cp) as f:
+            cfg = json.load(f)
+        cfg["quantization_config"] = {"format": "trellis_" + container, "bits": bits, "group_size": group_size}
+    (save_trellis_v3 if container == "v3" else save_trellis_v2)(weights, base, out_dir, config=cfg)
+    for fn in ("tokenizer.json", "tokenizer_config.json", "generation_config.json", "special_tokens_map.json"):
+        if os.path.exists(os.path.join(model_dir, fn)):
+            import shutil
+            shutil.copy(os.path.join(model_dir, fn), os.path.join(out_dir, fn))
+    return {"quantized": len(weights), "tensors": len(weights) + len(base), "bits": bits,
+            "mean_rel_rmse": sum(errs) / max(1, len(errs)), "format": "trellis_" + container}

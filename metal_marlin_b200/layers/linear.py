@@ -79,6 +79,8 @@ def _lut_for(fmt: str, device) -> torch.Tensor:
 
 class QuantizedLinear:
     """Group-quantized linear for the non-FP4 formats."""
+    is_generic = True
+    names = None
 
     def __init__(self, q: rtn.QuantizedTensor, bias: Optional[torch.Tensor] = None, device=None):
         device = torch.device(device) if device is not None else q.codes.device
@@ -125,6 +127,9 @@ class QuantizedLinear:
 
 
 class TrellisLinear:
+    is_generic = True
+    names = None
+
     def __init__(self, tw: trfmt.TrellisWeight, device=None, bias: Optional[torch.Tensor] = None):
         device = torch.device(device) if device is not None else tw.indices.device
         self.out_features, self.in_features = tw.shape
@@ -167,6 +172,8 @@ class TrellisLinear:
 
 class HadamardLinear:
     """``y = inner(block_hadamard(x))`` for a weight stored in the rotated basis."""
+    is_generic = True
+    names = None
 
     def __init__(self, inner, block: int = 128):
         self.inner, self.block = inner, block

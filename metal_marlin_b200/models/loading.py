@@ -145,6 +145,8 @@ def build_layer(cfg: ModelConfig, src, i: int) -> LayerWeights:
         if isinstance(src, RandomSource):
             L.gate_up_bank = src.bank(f"{m}.experts.gate_up", E + ns, I, H, parts=2)
             L.down_bank = src.bank(f"{m}.experts.down", E + ns, H, I)
+        elif hasattr(src, "expert_banks"):
+            L.gate_up_bank, L.down_bank = src.expert_banks(m, E, I, H, ns)
         else:
             gus, dws = [], []
             for e in range(E):

@@ -127,6 +127,10 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
            out=None, token_tile=0, tpx=None):
     """``out = epilogue( prologue(x) @ dequant(W)^T )``; prologue = optional residual add + RMSNorm,
     epilogue = optional bias, SwiGLU over the two row halves (``act=1``), residual add."""
+    if getattr(W, "is_generic", False):
+        from . import generic
+        return generic.linear(x, W, delta=delta, norm_w=norm_w, eps=eps, resid_out=resid_out, act=act, bias=bias,
+                              out_add=out_add, out=out)
     if _capture is not None:
         _capture("linear", W, ref.add_norm(x[:, : W.in_features], None if delta is None else delta[:, : W.in_features], norm_w, eps), None)
     if not _use_native(x):
@@ -404,6 +408,10 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
     Few tokens: per-(token, slot) weight-streaming kernels (experts read from device memory ids).
     Many tokens: counting-sort tokens by expert, grouped tcgen05 GEMMs over a device-built tile list."""
     T, topk = ids.shape
+    if getattr(gate_up, "is_generic", False):
+        from . import generic
+        return generic.moe_forward(x, gate_up, ids, weights, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps,
+                                   out_add=out_add)
     if _capture is not None:
         # calibration: expose the inputs of both expert projections with the expert of every (token, slot)
         e_all = ids.long()

@@ -1,0 +1,98 @@
+"""Weights that are not in the FP4 tile layout (trellis, INT4 / INT8 / FP8 / NF4 layers): the op layer runs them
+through their own matmul with the fused prologue / epilogue pieces as separate steps.
+
+A generic weight is any object with ``in_features``, ``out_features``, ``__call__(x2d) -> bf16 [M, out]`` and
+``dequantize(dtype)``.  ``CatWeight`` stacks such weights along the output axis (fused q_a|kv_a, q|k|v, gate|up);
+``GenericExpertBank`` holds per-expert gate|up and down projections (routed experts first, shared experts last).
+Parity: the reference's trellis model runs on exactly this kind of layer object (``metal_marlin/trellis/linear.py:50``
+``TrellisLinear``, ``metal_marlin/trellis/moe.py:131``).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+
+class CatWeight:
+    is_generic = True
+
+    def __init__(self, parts: Sequence):
+        self.parts = list(parts)
+        self.in_features = parts[0].in_features
+        self.out_features = sum(p.out_features for p in parts)
+        self.names = None
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return torch.cat([p(x) for p in self.parts], -1)
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        return torch.cat([p.dequantize(dtype) for p in self.parts], 0)
+
+
+class GenericExpertBank:
+    """``gate_up[e]`` maps ``[M, H] -> [M, 2 * I_e]`` (gate rows then up rows), ``down[e]`` maps ``[M, I_e] -> [M, H]``."""
+    is_generic = True
+
+    def __init__(self, gate_up: List, down: List):
+        self.gate_up, self.down = gate_up, down
+        self.num_experts = len(gate_up)
+        self.in_features = gate_up[0].in_features
+        self.out_features = gate_up[0].out_features
+        self.names = None
+
+
+def is_generic(w) -> bool:
+    return getattr(w, "is_generic", False)
+
+
+def linear(x, W, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bias=None, out_add=None, out=None):
+    from . import rmsnorm
+    xin = x[:, : W.in_features]
+    if norm_w is not None:
+        xin = rmsnorm(xin, norm_w, eps, delta=None if delta is None else delta[:, : W.in_features], resid_out=resid_out)
+    elif delta is not None:
+        xin = (xin.to(torch.float32) + delta[:, : W.in_features].to(torch.float32)).to(torch.bfloat16)
+        if resid_out is not None:
+            resid_out.copy_(xin)
+    y = W(xin.contiguous()).to(torch.float32)
+    if bias is not None:
+        y = y + bias.to(torch.float32)
+    if act == 1:
+        half = W.out_features // 2
+        y = F.silu(y[:, :half]) * y[:, half:]
+    if out_add is not None:
+        y = y + out_add.to(torch.float32)
+    y = y.to(torch.bfloat16)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def moe_forward(x, bank: GenericExpertBank, ids, weights, *, n_shared=0, shared_base=0, norm_w=None, eps=1e-6, out_add=None):
+    """Loop over the experts that received tokens (host-side grouping; the trellis path is not graph captured)."""
+    from . import rmsnorm
+    xin = rmsnorm(x, norm_w, eps) if norm_w is not None else x
+    T = x.shape[0]
+    acc = torch.zeros(T, bank.down[0].out_features, dtype=torch.float32, device=x.device)
+    ids_l = ids.long()
+    for e in ids_l.unique().tolist():
+        if e < 0:
+            continue
+        tt, ss = (ids_l == e).nonzero(as_tuple=True)
+        gu = bank.gate_up[e](xin[tt].contiguous()).to(torch.float32)
+        half = gu.shape[1] // 2
+        h = (F.silu(gu[:, :half]) * gu[:, half:]).to(torch.bfloat16)
+        acc.index_add_(0, tt, bank.down[e](h).to(torch.float32) * weights[tt, ss].to(torch.float32).unsqueeze(-1))
+    for j in range(n_shared):
+        e = shared_base + j
+        if bank.gate_up[e] is None:          # a multi-expert shared MLP kept as one matrix occupies the first slot only
+            continue
+        gu = bank.gate_up[e](xin.contiguous()).to(torch.float32)
+        half = gu.shape[1] // 2
+        acc += bank.down[e]((F.silu(gu[:, :half]) * gu[:, half:]).to(torch.bfloat16)).to(torch.float32)
+    if out_add is not None:
+        acc += out_add.to(torch.float32)
+    return acc.to(torch.bfloat16)
