@@ -162,10 +162,14 @@ def build_layer(cfg: ModelConfig, src, i: int) -> LayerWeights:
                 for j in range(ns):
                     gcs, ucs = sg.codes_scales(), su.codes_scales()
                     sl = slice(j * I, (j + 1) * I)
-                    gus.append(FP4Weight.concat_rows([FP4Weight.from_codes(gcs[0][sl], gcs[1][sl]),
-                                                      FP4Weight.from_codes(ucs[0][sl], ucs[1][sl])]))
+                    gu = FP4Weight.concat_rows([FP4Weight.from_codes(gcs[0][sl], gcs[1][sl]),
+                                                FP4Weight.from_codes(ucs[0][sl], ucs[1][sl])])
+                    gu.names = (sg.names or []) + (su.names or [])        # calibration: same input as the whole shared MLP
+                    gus.append(gu)
                     gper = I // sd.group_size
-                    dws.append(FP4Weight.from_codes(sdc[:, sl].contiguous(), sds[:, j * gper:(j + 1) * gper].contiguous()))
+                    dw = FP4Weight.from_codes(sdc[:, sl].contiguous(), sds[:, j * gper:(j + 1) * gper].contiguous())
+                    dw.names = sd.names if ns == 1 else None            # a column slice of the shared down matrix has no Hessian of its own
+                    dws.append(dw)
             L.gate_up_bank = FP4ExpertBank.from_weights(gus)
             L.down_bank = FP4ExpertBank.from_weights(dws)
     else:

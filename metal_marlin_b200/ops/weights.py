@@ -138,8 +138,8 @@ class FP4ExpertBank:
         w0 = ws[0]
         bank = cls(torch.stack([w.qtile for w in ws]), torch.stack([w.stile for w in ws]),
                    w0.out_features, w0.in_features, w0.group_size)
-        if all(w.names for w in ws):
-            bank.names = [w.names for w in ws]
+        if any(w.names for w in ws):
+            bank.names = [w.names or [] for w in ws]
         return bank
 
     @classmethod
