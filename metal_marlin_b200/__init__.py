@@ -1,2 +1,102 @@
-"""B200-native quantized LLM inference engine."""
+"""B200-native quantized LLM inference engine: the capabilities, public API and checkpoint formats of metal-marlin on
+NVIDIA B200 (sm_100a) - PyTorch for the framework layer, hand-written CUDA kernels (``metal_marlin_b200/_C.so``) for
+every hot op, in-kernel NVLink exchange for tensor / expert parallel decode.
+
+Parity: reference ``metal_marlin/__init__.py:19-518`` (package facade re-exporting ~150 names with optional-import
+guards).  Names are resolved lazily on first access so importing the package stays cheap and never needs a GPU.
+"""
+from __future__ import annotations
+
+import importlib
+from typing import Dict, Tuple
+
 __version__ = "0.1.0"
+
+# public name -> (module, attribute)
+_EXPORTS: Dict[str, Tuple[str, str]] = {}
+
+
+def _reg(module: str, *names: str, **aliases: str) -> None:
+    for n in names:
+        _EXPORTS[n] = (module, n)
+    for alias, target in aliases.items():
+        _EXPORTS[alias] = (module, target)
+
+
+_reg("._compat", "E2M1_VALUES", "NF4_VALUES")
+_reg(".dtypes", "DTypeConfig", "get_dtype_config", "to_torch_dtype")
+_reg(".inference.pipeline", "MMFP4Pipeline", "StreamingOutput", MarlinPipeline="MMFP4Pipeline")
+_reg(".models.mmfp4_causal_lm", "MMFP4ForCausalLM", "prefill")
+_reg(".models.config", "ModelConfig", "get_preset")
+_reg(".models.transformer", "Transformer", "PagedKVStorage", "BatchMeta")
+_reg(".engine.session", "DecodeSession", "SamplingParams")
+_reg(".engine.engine", "LLMEngine")
+_reg(".engine.scheduler", "BatchScheduler", "FCFSScheduler", "SchedulerConfig", "PreemptionPolicy")
+_reg(".engine.request", "GenerationRequest", "RequestStatus", "RunningRequest", "RequestPriority")
+_reg(".sampler", "SamplingConfig", "Sampler", "sample_next_token", MetalSampler="Sampler")
+_reg(".rope", "YaRNConfig", "RotaryEmbedding", "apply_rope", "rope_inv_freq", "yarn_inv_freq")
+_reg(".kv.contiguous", "KVCache", "KVCacheTorch", "MLAKVCache", "PersistentKVCache", "CacheConfig", "quantize_kv", "dequantize_kv")
+_reg(".kv.paged", "BlockAllocator", "MultimodalBlockAllocator", "PageTable", "PrefixCache", "PagedKVCache")
+_reg(".layers", "MMFP4Linear", "QuantizedLinear", "TrellisLinear", "HadamardLinear")
+_reg(".ops.weights", "FP4Weight", "FP4ExpertBank")
+_reg(".trellis", "TrellisForCausalLM", "TrellisGenerator", "TrellisModelConfig", "GenerationConfig")
+_reg(".formats.mmfp4_loader", "MMFP4ModelLoader")
+_reg(".formats.trellis", "TrellisModelLoader", "TrellisWeight", "quantize_trellis", "quantize_model_trellis")
+_reg(".formats.fp4", "quantize_fp4", "pack_mmfp4", "pack_marlin_fp4", "unpack_mmfp4", "unpack_marlin_fp4")
+_reg(".quant.rtn", "quantize", "dequantize", "QuantizedTensor", "pack_bits", "unpack_bits")
+_reg(".quant.convert", "convert_model", "convert_model_to_fp4", "convert_model_to_mmfp4", "save_random_checkpoint")
+_reg(".quant.gptq", "GPTQConfig", "MRGPTQConfig", "gptq_quantize", "mr_gptq_quantize")
+_reg(".quant.awq", "awq_quantize", "awq_search")
+_reg(".quant.hadamard", "hadamard_matrix", "block_hadamard", "fwht")
+_reg(".quant.calibration", "HessianCollector", "load_calibration_tokens")
+_reg(".quant.mixed_precision", "policy_for", "allocate_bits", "TensorPolicy")
+_reg(".quant.pipeline", "quantize_checkpoint", "collect_hessians")
+_reg(".converters", "convert_checkpoint", "MixedFormatPack")
+_reg(".converters.gguf", "GGUFReader", "write_gguf")
+_reg(".spec.engine", "SpeculativeEngine")
+_reg(".spec.draft", "NGramDraft", "SmallModelDraft", "MTPDraft", "MTPHead", "EagleDraft", "DraftModel")
+_reg(".spec.verify", "verify_greedy", "verify_speculative", "verify_batch_greedy", "verify_tree_greedy", "tree_attention_mask")
+_reg(".spec.adaptive", "AdaptiveSpeculationController", "TokenAcceptanceTracker")
+_reg(".serving.engine", "ServingEngine", "EngineConfig")
+_reg(".serving.server", "run_server")
+_reg(".serving.metrics", "MetricsCollector", "MoEMetrics", "PerplexityTracker")
+_reg(".eval", "compute_perplexity", "kl_divergence", "quality_report", "ExpertUsageProfiler", "load_balancing_loss")
+_reg(".inference.long_context", "LongContextConfig", "LongContextModel", "StreamingAttention", "chunked_attention", "sliding_window_mask")
+_reg(".attention", "block_sparse_attention", "sliding_window_attention", "tree_attention", "differential_attention")
+_reg(".arch", "MambaBlock", "MambaConfig", "selective_scan", "gated_delta_rule_chunked", "gated_delta_step", "wkv5", "wkv6", "layout_from_config")
+_reg(".vision", "ImagePreprocessor", "PreprocessConfig", "LlavaProjector", "PatchMergerProjector", "VisionEncoderCache")
+_reg(".hf", "replace_linear_layers", "find_linear_layers", "find_moe_layers", "load_prequantized_mmfp4_model")
+_reg(".memory", "Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "PinnedPool", "WeightStreamer", "MemoryPressureMonitor")
+_reg(".parallel.tp", "TPContext", "shard_transformer", "make_context")
+_reg(".parallel.mesh", "DeviceMesh", "MeshShape", "plan_mesh")
+_reg(".parallel.ep", "ExpertParallelMoE")
+_reg(".parallel.pp", "PipelineStage", "pipeline_prefill")
+_reg(".parallel.cp", "ring_attention")
+_reg(".parallel.symm", "SymmetricBuffer")
+_reg(".profiling", "KernelTimer", "RooflinePoint", "load_peaks", "trace_scope", "write_trace", "launch_tracer", "profile_kernel")
+_reg(".utils", "NaNGuard", "LazyCheckpoint", "load_checkpoint", "save_checkpoint", "remap_weight_keys", "filter_weights")
+_reg(".baseline_eager", "EagerBF16Model")
+
+
+def __getattr__(name: str):
+    try:
+        module, attr = _EXPORTS[name]
+    except KeyError:
+        raise AttributeError(f"module 'metal_marlin_b200' has no attribute {name!r}") from None
+    val = getattr(importlib.import_module(module, __name__), attr)
+    globals()[name] = val
+    return val
+
+
+def __dir__():
+    return sorted(list(globals()) + list(_EXPORTS))
+
+
+def has_cuda_kernels() -> bool:
+    """True when a GPU is present and the native library is loaded (the CUDA path is the one that will run)."""
+    from . import ops
+    return ops.native_available()
+
+
+HAS_TORCH = True
+__all__ = sorted(_EXPORTS) + ["__version__", "has_cuda_kernels", "HAS_TORCH"]

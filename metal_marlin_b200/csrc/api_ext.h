@@ -45,6 +45,15 @@ int mmb_vision_preprocess(const uint8_t* images, void* out, int B, int H, int W,
 int mmb_spec_verify(const float* p_target, const float* p_draft, const int64_t* draft, const float* u, const float* u_resample,
                     int64_t* out_tokens, int* out_accepted, int B, int K, int V, cudaStream_t stream);
 
+// Recurrent layers, one decode step.  Gated delta rule: q, k bf16 [B, H, dk], v bf16 [B, H, dv], g (log decay) and beta fp32
+// [B, H], state fp32 [B, H, dk, dv] updated in place, out bf16 [B, H, dv].
+int mmb_gated_delta_step(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state, void* out,
+                         int B, int H, int dk, int dv, float scale, cudaStream_t stream);
+// Mamba selective scan: x bf16 [B, D], dt fp32 [B, D] (after softplus), A fp32 [D, N] (negative), Bm / Cm fp32 [B, N], optional
+// skip Dskip fp32 [D], state fp32 [B, D, N] updated in place, y bf16 [B, D].
+int mmb_selective_scan_step(const void* x, const float* dt, const float* A, const float* Bm, const float* Cm, const float* Dskip,
+                            float* state, void* y, int B, int D, int N, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

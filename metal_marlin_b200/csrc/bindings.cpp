@@ -534,6 +534,35 @@ void spec_verify(const Tensor& p_target, const Tensor& p_draft, const Tensor& dr
         "spec_verify");
 }
 
+void gated_delta_step(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, Tensor state, Tensor out,
+                      double scale) {
+  check_bf16(q, "q");
+  check_bf16(k, "k");
+  check_bf16(v, "v");
+  TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && state.is_contiguous() && out.is_contiguous());
+  TORCH_CHECK(g.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat && state.scalar_type() == at::kFloat);
+  const int B = (int)q.size(0), H = (int)q.size(1), dk = (int)q.size(2), dv = (int)v.size(2);
+  TORCH_CHECK(state.numel() == (int64_t)B * H * dk * dv && g.numel() == (int64_t)B * H && beta.numel() == (int64_t)B * H);
+  c10::cuda::CUDAGuard guard(q.device());
+  check(mmb_gated_delta_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr<float>(), beta.data_ptr<float>(), state.data_ptr<float>(),
+                             out.data_ptr(), B, H, dk, dv, (float)scale, cur_stream()),
+        "gated_delta_step");
+}
+
+void selective_scan_step(const Tensor& x, const Tensor& dt, const Tensor& A, const Tensor& Bm, const Tensor& Cm, const OptT& Dskip,
+                         Tensor state, Tensor y) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.is_contiguous() && dt.is_contiguous() && A.is_contiguous() && Bm.is_contiguous() && Cm.is_contiguous() && state.is_contiguous());
+  TORCH_CHECK(dt.scalar_type() == at::kFloat && A.scalar_type() == at::kFloat && Bm.scalar_type() == at::kFloat && Cm.scalar_type() == at::kFloat &&
+              state.scalar_type() == at::kFloat);
+  const int B = (int)x.size(0), D = (int)x.size(1), N = (int)A.size(1);
+  TORCH_CHECK(state.numel() == (int64_t)B * D * N && A.size(0) == D && Bm.numel() == (int64_t)B * N);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(mmb_selective_scan_step(x.data_ptr(), dt.data_ptr<float>(), A.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
+                                (const float*)cptr(Dskip), state.data_ptr<float>(), y.data_ptr(), B, D, N, cur_stream()),
+        "selective_scan_step");
+}
+
 TORCH_LIBRARY(mmb200, m) {
   m.def("fp4_gemm_grouped", &fp4_gemm_grouped);
   m.def("bf16_gemm", &bf16_gemm);
@@ -560,4 +589,6 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("codebook_gemv", &codebook_gemv);
   m.def("vision_preprocess", &vision_preprocess);
   m.def("spec_verify", &spec_verify);
+  m.def("gated_delta_step", &gated_delta_step);
+  m.def("selective_scan_step", &selective_scan_step);
 }
