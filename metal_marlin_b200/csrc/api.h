@@ -99,6 +99,7 @@ typedef struct {
   int T, H, dn, dr, R, ld_q, ld_kva;
   float eps, mscale;
   int interleaved;
+  int skip_absorb;          // 1: leave q_full[:, :, :R] untouched (prefill uses the non-absorbed form), only RoPE + cache write
 } MmbMlaPrepParams;
 int mmb_mla_prep(const MmbMlaPrepParams* p, cudaStream_t stream);
 

@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const MmbMlaPrepParams p)
   const bf16* q = reinterpret_cast<const bf16*>(p.q);
   bf16* qf = reinterpret_cast<bf16*>(p.q_full);
   const int dq = p.dn + p.dr, dl = p.R + p.dr;
-  const int n_chunks = (p.R + kPrepRows - 1) / kPrepRows;
+  const int n_chunks = p.skip_absorb ? 1 : (p.R + kPrepRows - 1) / kPrepRows;
   if ((int)blockIdx.x < p.H * n_chunks) {
     const int h = blockIdx.x / n_chunks, chunk = blockIdx.x % n_chunks;
     const bf16* W = reinterpret_cast<const bf16*>(p.w_ukT) + (long long)h * p.R * p.dn;
@@ -46,17 +46,19 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const MmbMlaPrepParams p)
     for (int r = 0; r < 4; ++r) {
       crow[r] = chunk * kPrepRows + warp * 4 + r;
       wv[r] = make_uint4(0, 0, 0, 0);
-      if (crow[r] < p.R && lane * 8 < p.dn) wv[r] = ldg_stream(reinterpret_cast<const uint4*>(W + (long long)crow[r] * p.dn + lane * 8));
+      if (!p.skip_absorb && crow[r] < p.R && lane * 8 < p.dn) wv[r] = ldg_stream(reinterpret_cast<const uint4*>(W + (long long)crow[r] * p.dn + lane * 8));
     }
     pdl_launch_dependents();
     pdl_wait();
-    for (int j = 0; j < nt; ++j)
-      for (int d = tid; d < p.dn; d += 256)
-        sm[j * p.dn + d] = __bfloat162float(q[(long long)(t0 + j) * p.ld_q + h * dq + d]);
+    if (!p.skip_absorb) {
+      for (int j = 0; j < nt; ++j)
+        for (int d = tid; d < p.dn; d += 256)
+          sm[j * p.dn + d] = __bfloat162float(q[(long long)(t0 + j) * p.ld_q + h * dq + d]);
+    }
     __syncthreads();
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      if (crow[r] >= p.R) continue;
+      if (p.skip_absorb || crow[r] >= p.R) continue;
       const uint32_t ww[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
       float acc[kPrepTok];
 #pragma unroll
@@ -656,7 +658,7 @@ MMB_API int mmb_mla_prep(const MmbMlaPrepParams* pp, cudaStream_t stream) {
   const int width = (p.dn > p.R + p.dr) ? p.dn : (p.R + p.dr);
   const size_t smem = (size_t)mmb::kPrepTok * width * 4;
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-  dim3 grid(p.H * ((p.R + mmb::kPrepRows - 1) / mmb::kPrepRows) + 1, (p.T + mmb::kPrepTok - 1) / mmb::kPrepTok);
+  dim3 grid(p.H * (p.skip_absorb ? 1 : (p.R + mmb::kPrepRows - 1) / mmb::kPrepRows) + 1, (p.T + mmb::kPrepTok - 1) / mmb::kPrepTok);
   return mmb::launch(mmb::mla_prep_kernel, grid, dim3(256), smem, stream, 1, p);
 }
 

@@ -217,7 +217,7 @@ void qk_norm_rope_cache(Tensor q, const Tensor& k, const Tensor& v, const OptT& 
 
 void mla_prep(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
               const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, int64_t H, int64_t dn, int64_t dr,
-              int64_t R, double eps, double mscale, bool interleaved) {
+              int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb) {
   check_bf16(q, "q");
   check_bf16(kva, "kva");
   check_bf16(w_ukT, "w_ukT");
@@ -244,6 +244,7 @@ void mla_prep(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Ten
   p.eps = (float)eps;
   p.mscale = (float)mscale;
   p.interleaved = interleaved ? 1 : 0;
+  p.skip_absorb = skip_absorb ? 1 : 0;
   check(mmb_mla_prep(&p, cur_stream()), "mla_prep");
 }
 

@@ -4,15 +4,17 @@
 // the token tile is the "B" operand (TN = 32..256 tokens = TMEM columns), so the same kernel serves
 // batch-32 decode (TN = 32) and long prefill (TN = 256) without wasting the M = 128 instruction shape.
 //
-// CTA = 6 warps:
+// CTA = 10 warps:
 //   warp 0      TMA producer: x tile [TN x 64] bf16, 128-byte swizzle, one bulk tensor copy per stage
 //               (bf16-weight variant: also the W tile)
 //   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits stages back to the
 //               producers through mbarriers
-//   warps 2..5  FP4 variant: stream tile-layout weight blocks from global memory (one 16-byte load per
-//               lane per 16x64 block), expand E2M1 -> bf16 with the group scale in registers and
-//               store them into the 128-byte-swizzled K-major A tile; afterwards the same four warps
-//               run the epilogue (tcgen05.ld of their 32-lane TMEM quarter, bf16 stores).
+//   warps 2..9  FP4 variant: stream tile-layout weight blocks from global memory (one 16-byte load per
+//               lane per 16x64 block, one block per warp per stage), expand E2M1 -> bf16 with the group
+//               scale in registers and store them into the 128-byte-swizzled K-major A tile (weight
+//               expansion is what bounds this kernel at small token counts, hence eight warps of it);
+//               afterwards the same warps run the epilogue: tcgen05.ld of their 32-lane TMEM quarter
+//               (warp % 4), the two warps of a quarter taking alternate 32-column chunks.
 // Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records a code in
 // status[0], skips the remaining work, still frees its TMEM and returns.
 #include <cuda.h>
@@ -24,7 +26,8 @@ namespace mmb {
 
 constexpr int kBK = 64;                 // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr int kTileRows = 128;          // output features per CTA
-constexpr int kGemmThreads = 192;
+constexpr int kExpandWarps = 8;           // warps that expand FP4 weights (one 16-row block each per stage)
+constexpr int kGemmThreads = (2 + kExpandWarps) * 32;
 
 // ------------------------------------------------------------------------------------------ PTX
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
@@ -137,7 +140,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
 
   if (tid == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
-      mbar_init(&ps->full_a[s], WFMT == 0 ? 4 : 1);
+      mbar_init(&ps->full_a[s], WFMT == 0 ? kExpandWarps : 1);
       mbar_init(&ps->full_b[s], 1);
       mbar_init(&ps->empty[s], 1);
     }
@@ -205,7 +208,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------------------------------ weight expansion (FP4) + epilogue
-    const int dw = warp - 2;            // 0..3
+    const int dw = warp - 2;            // 0..7
     bool ok = true;
     if (WFMT == 0) {
       const int g = lane >> 2, t = lane & 3;
@@ -214,20 +217,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       const int n_rt = (N + 15) >> 4;
       const uint4* qw = reinterpret_cast<const uint4*>(p.qw) + (long long)expert * p.expert_stride_q;
       const uint32_t* sc = reinterpret_cast<const uint32_t*>(p.sc) + (long long)expert * p.expert_stride_s;
-      const int rt_base = (n0 >> 4) + dw * 2;
-      uint4 wnext[2];
+      const int rt_base = (n0 >> 4) + dw;
+      uint4 wnext[1];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < 1; ++j) {
         const int rt = rt_base + j;
         wnext[j] = (rt < n_rt && KB > 0) ? ldg_stream(qw + ((long long)rt * KC) * 32 + lane) : make_uint4(0, 0, 0, 0);
       }
       for (int i = 0; i < KB; ++i) {
         const int s = i % Cfg::kStages;
         const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
-        uint4 wcur[2] = {wnext[0], wnext[1]};
+        uint4 wcur[1] = {wnext[0]};
         if (i + 1 < KB) {
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
+          for (int j = 0; j < 1; ++j) {
             const int rt = rt_base + j;
             if (rt < n_rt) wnext[j] = ldg_stream(qw + ((long long)rt * KC + (i + 1)) * 32 + lane);
           }
@@ -239,10 +242,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < 1; ++j) {
           const int rt = rt_base + j;
           const uint32_t qq[4] = {wcur[j].x, wcur[j].y, wcur[j].z, wcur[j].w};
-          const int row_lo = (dw * 2 + j) * 16 + g;           // row inside the 128-row tile (and row_lo + 8)
+          const int row_lo = (dw + j) * 16 + g;           // row inside the 128-row tile (and row_lo + 8)
           unsigned char* r0 = a_tile + row_lo * 128;
           unsigned char* r1 = r0 + 8 * 128;
 #pragma unroll
@@ -297,8 +300,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       const int q = warp & 3;                    // TMEM lane quarter this warp may access
       const int n = n0 + q * 32 + lane;
       const int ldo = WFMT == 0 ? p.ldo : pb.ldo;
+      const int c_first = ((warp - 2) >> 2) * 32; // the two warps of a quarter alternate over 32-column chunks
 #pragma unroll 1
-      for (int c0 = 0; c0 < TN; c0 += 32) {
+      for (int c0 = c_first; c0 < TN; c0 += 64) {
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
         tmem_ld_wait();

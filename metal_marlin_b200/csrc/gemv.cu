@@ -122,7 +122,7 @@ __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const 
 // once (no unrolled register ring), which matters because these kernels are short enough to be bound by
 // instruction fetch.
 template <bool BIG_GROUPS, int NWARPS>
-__global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt) {
+__global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt, const int mrows) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float red[2][NWARPS][2][128];
   __shared__ float ss_red[NWARPS][8];
@@ -134,8 +134,8 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
   const int S = (p.mode == 0) ? 1 : (p.topk + p.n_shared);
   int m0, mt, token = 0;
   if (p.mode == 0) {
-    m0 = blockIdx.y * 8;
-    mt = min(8, p.M - m0);
+    m0 = blockIdx.y * mrows;            // mrows <= 8 token rows per CTA (fewer when K is so large that 8 rows do not fit)
+    mt = min(mrows, p.M - m0);
   } else {
     token = blockIdx.y;
     m0 = token;
@@ -640,10 +640,15 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   const int n_rt = (p.N + 15) / 16;
   size_t smem;
   dim3 grid;
+  int mrows = 8;
   if (p.mode == 0) {
-    const int mt = p.M < 8 ? p.M : 8;
-    smem = (size_t)mt * (p.K + 32) * 2;
-    grid.y = (p.M + 7) / 8;
+    // token rows staged per CTA: up to 8, fewer when 8 rows of this K would not leave room for the weight rings
+    const size_t row_bytes = (size_t)(p.K + 32) * 2;
+    const size_t budget = 170 * 1024 - (size_t)16 * kRing * (512 + 128);
+    while (mrows > 1 && (size_t)mrows * row_bytes > budget) mrows >>= 1;
+    const int mt = p.M < mrows ? p.M : mrows;
+    smem = (size_t)mt * row_bytes;
+    grid.y = (p.M + mrows - 1) / mrows;
   } else if (p.mode == 1) {
     smem = (size_t)(p.K + 32) * 2;
     grid.y = p.M;
@@ -679,7 +684,7 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
 #define MMB_LAUNCH_GEMV(BG, NW)                                                                \
   do {                                                                                         \
     if ((e = set_smem(fp4_gemv_kernel<BG, NW>, smem, 34 * 1024))) return e;                              \
-    return launch(fp4_gemv_kernel<BG, NW>, grid, dim3(NW * 32), smem, stream, 1, p, wpt);       \
+    return launch(fp4_gemv_kernel<BG, NW>, grid, dim3(NW * 32), smem, stream, 1, p, wpt, mrows);       \
   } while (0)
   if (big && nw == 8) MMB_LAUNCH_GEMV(true, 8);
   if (big) MMB_LAUNCH_GEMV(true, 16);

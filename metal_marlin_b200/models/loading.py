@@ -124,7 +124,8 @@ def build_layer(cfg: ModelConfig, src, i: int) -> LayerWeights:
         L.kv_a_norm = src.norm(f"{a}.kv_a_layernorm.weight", R)
         L.kv_b = src.linear(f"{a}.kv_b_proj", nh * (dn + dv), R)
         L.w_ukT, L.w_uv = absorb_kv_b(L.kv_b, nh, dn, dv, R)
-        L.kv_b = None      # the absorbed copies serve decode and prefill
+        L.kv_b_dense = L.kv_b.dequantize(torch.bfloat16).contiguous()      # prefill lifts latent rows to per-head K / V with it
+        L.kv_b = None      # the absorbed copies serve decode
         L.o = src.linear(f"{a}.o_proj", H, nh * dv)
     else:
         Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.dh

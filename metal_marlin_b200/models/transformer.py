@@ -86,6 +86,7 @@ class LayerWeights:
     kv_b: Optional[FP4Weight] = None          # kept for prefill (non-absorbed) attention
     w_ukT: Optional[torch.Tensor] = None      # bf16 [H, R, dn]
     w_uv: Optional[torch.Tensor] = None       # bf16 [H, dv, R]
+    kv_b_dense: Optional[torch.Tensor] = None  # bf16 [H * (dn + dv), R]: latent -> (k_nope | v) per head, for prefill
     o: Optional[FP4Weight] = None
     # dense MLP
     gate_up: Optional[FP4Weight] = None
@@ -259,17 +260,49 @@ class Transformer:
             q = a[:, :ql]
             kva = a[:, ql:]
         q_full = torch.empty(T, H, R + dr, dtype=torch.bfloat16, device=h.device)
+        nonabsorbed = (not meta.decode) and L.kv_b_dense is not None and meta.attn_mask is None
         ops.mla_prep(q, kva, L.w_ukT, L.kv_a_norm, meta.positions, self.inv_freq, meta.slots, q_full, kv.k[li], H, dn, dr,
-                     R, cfg.rms_norm_eps, self.rope_mscale, cfg.rope_interleave)
+                     R, cfg.rms_norm_eps, self.rope_mscale, cfg.rope_interleave, skip_absorb=nonabsorbed)
         if meta.decode:
             o = ops.paged_attention(q_full, kv.k[li], None, meta.block_tables, meta.ctx_lens, Hq=H, Hkv=1, dqk=R + dr, dv=R,
                                     block_size=kv.block_size, scale=self.scale, splits=meta.splits, w_uv=L.w_uv,
                                     max_ctx=meta.max_ctx)
             o = o.reshape(T, H * dv)
+        elif nonabsorbed:
+            o = self._prefill_attention_mla_expanded(L, q.view(T, H, dn + dr), q_full, kv, li, meta)
         else:
             o = self._prefill_attention_mla(L, q_full, kv, li, meta)
         d = self._row_parallel(o, L.o, 2 * li)
         return h, d
+
+    def _prefill_attention_mla_expanded(self, L: LayerWeights, q, q_full, kv: PagedKVStorage, li: int, meta: BatchMeta):
+        """Non-absorbed causal prefill: the cached latent rows are lifted to per-head keys / values with one GEMM
+        (``kv_b``), so attention runs with 256-wide heads instead of the 576 / 512-wide latent form - less than half
+        the attention FLOPs and a head size the fused attention kernels support."""
+        cfg = self.cfg
+        H, dn, dr, dv, R = self.n_heads_local, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        out = torch.empty(q.shape[0], H * dv, dtype=torch.bfloat16, device=q.device)
+        bs = kv.block_size
+        for b in range(len(meta.cu_seqlens) - 1):
+            s, e = meta.cu_seqlens[b], meta.cu_seqlens[b + 1]
+            n_ctx = int(meta.ctx_lens_host[b])
+            t = e - s
+            tok = torch.arange(n_ctx, device=q.device)
+            slots = meta.block_tables[b, tok // bs].long() * bs + tok % bs
+            lat = kv.k[li][slots]                                           # [n, R + dr] post-norm | post-RoPE
+            c = lat[:, :R].contiguous()
+            kvx = (ops.bf16_gemm(c, L.kv_b_dense) if R % 64 == 0 else torch.matmul(c, L.kv_b_dense.t())).view(n_ctx, H, dn + dv)
+            k = torch.cat([kvx[..., :dn], lat[:, None, R:].expand(n_ctx, H, dr)], -1)
+            qq = torch.cat([q[s:e, :, :dn], q_full[s:e, :, R:]], -1)
+            mask = None
+            if n_ctx != t:
+                qpos = torch.arange(n_ctx - t, n_ctx, device=q.device).unsqueeze(1)
+                mask = tok.unsqueeze(0) <= qpos
+            o = F.scaled_dot_product_attention(qq.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
+                                               kvx[..., dn:].transpose(0, 1).unsqueeze(0), attn_mask=mask, is_causal=(mask is None),
+                                               scale=self.scale)
+            out[s:e] = o.squeeze(0).transpose(0, 1).reshape(t, H * dv)
+        return out
 
     def _prefill_attention_mla(self, L: LayerWeights, q_full, kv: PagedKVStorage, li: int, meta: BatchMeta):
         """Absorbed-form causal prefill: scores and values live in the 576/512-d latent space, all heads

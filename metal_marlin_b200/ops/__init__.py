@@ -21,7 +21,8 @@ from .weights import FP4ExpertBank, FP4Weight  # noqa: F401
 
 _FORCE_REF = os.environ.get("MMB200_FORCE_TORCH", "0") == "1"
 _native_ok = False
-GEMV_MAX_M = 16          # at or below this many tokens the weight-streaming GEMV path is used
+GEMV_MAX_M = 32          # dense projections: at or below this many tokens the weight-streaming GEMV path is used
+MOE_GEMV_MAX_T = 16      # MoE: per-(token, slot) streaming up to this many tokens, grouped tcgen05 GEMMs above
 # Diagnostic switch: route every shape through the weight-streaming kernels (no tcgen05 GEMM).
 NO_TCGEN05 = os.environ.get("MMB200_NO_TCGEN05", "0") == "1"
 
@@ -178,17 +179,20 @@ def bf16_linear(x, w, *, delta=None, norm_w=None, eps=1e-6, out_dtype=torch.bflo
     M = x.shape[0]
     if out is None:
         out = torch.empty(M, w.shape[0], dtype=out_dtype, device=x.device)
-    if M <= 64:
-        K.mmb200.bf16_gemv(x, w, out, delta, norm_w, eps, tpx)
+    if M <= 8 or tpx is not None or w.shape[1] % 64 != 0:
+        K.mmb200.bf16_gemv(x, w, out, delta, norm_w, eps, tpx)      # weight-streaming: every weight row read once per 4 tokens
         return out
-    assert tpx is None
+    # more tokens: the tcgen05 GEMM streams the weight once for all of them (A operand by TMA, fp32 in TMEM)
     xin = x
-    if norm_w is not None:
+    if norm_w is not None or delta is not None:
         xin = torch.empty_like(x)
-        K.mmb200.rmsnorm(x, delta, norm_w, xin, None, eps)
-    # large-M unquantized projections (lm_head over a whole prompt) are plain library GEMMs
-    y = torch.matmul(xin, w.t())
-    out.copy_(y.to(out_dtype))
+        if norm_w is not None:
+            K.mmb200.rmsnorm(x, delta, norm_w, xin, None, eps)
+        else:
+            K.mmb200.add(x.contiguous(), delta.contiguous(), xin)
+    elif not xin.is_contiguous():
+        xin = xin.contiguous()
+    K.mmb200.bf16_gemm(xin, w, out, gemm_status(x.device))
     return out
 
 
@@ -227,12 +231,14 @@ def qk_norm_rope_cache(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool, 
 
 
 def mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps, mscale=1.0,
-             interleaved=True):
+             interleaved=True, skip_absorb=False):
+    """``skip_absorb``: only RoPE the query's rope slice into ``q_full[..., R:]`` and write the new latent rows (prefill
+    attends in the non-absorbed form and never needs ``q_full[..., :R]``)."""
     if not _use_native(q):
         return ref.mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps,
                             mscale, interleaved)
     K.mmb200.mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps, mscale,
-                      interleaved)
+                      interleaved, skip_absorb)
     return q_full
 
 
@@ -421,7 +427,7 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
         h = moe_gate_up(x, gate_up, ids, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps)
         _capture("moe_down", down, h.view(T, e_all.shape[1], -1)[..., : down.in_features].to(torch.float32), e_all)
         return moe_down(h, down, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add, tpx=tpx)
-    if (not _use_native(x)) or T <= GEMV_MAX_M or NO_TCGEN05:
+    if (not _use_native(x)) or T <= MOE_GEMV_MAX_T or NO_TCGEN05:
         h = moe_gate_up(x, gate_up, ids, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps)
         return moe_down(h, down, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add, tpx=tpx)
     assert tpx is None

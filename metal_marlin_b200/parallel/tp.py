@@ -210,6 +210,9 @@ def shard_layer(cfg, L: LayerWeights, rank: int, tp: int) -> Tuple[LayerWeights,
             S.qa_kva = FP4Weight.concat_rows([q, kv])
         S.w_ukT = L.w_ukT[h0:h1].contiguous()
         S.w_uv = L.w_uv[h0:h1].contiguous()
+        if L.kv_b_dense is not None:
+            per = cfg.qk_nope_head_dim + cfg.v_head_dim
+            S.kv_b_dense = L.kv_b_dense[h0 * per: h1 * per].contiguous()
         S.o = L.o.slice_cols(h0 * dv, h1 * dv)
     else:
         Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.dh
