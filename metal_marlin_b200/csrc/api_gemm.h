@@ -30,6 +30,15 @@ typedef struct {
   long long expert_stride_s;   // 4-byte units
   const float* row_scale;   // optional fp32 [M]: out row multiplied by it (routing weight)
   int token_tile;           // 0 = auto; else 32 / 64 / 128 / 256
+  // Tensor-parallel reduce-scatter epilogue (row-parallel projection; all null / 0 on one GPU).  Token row t belongs
+  // to rank t / rs_rows; this rank's fp32 partial of the row goes straight from the epilogue into slot `rs_rank` of
+  // the owner's receive buffer fp32 [tp][rs_rows][N] (NVLink peer stores); the last CTA publishes the step number in
+  // flag[rs_rank] on every peer.  `out` is not written in this mode.
+  float* const* rs_peer_bufs;       // device array [tp]: base of rank r's receive buffer
+  unsigned* const* rs_peer_flags;   // device array [tp]: flag[rs_rank] on rank r
+  unsigned* rs_counter;             // local CTA completion counter (0 before and after the launch)
+  const unsigned* rs_step;          // device scalar: current step number
+  int rs_tp, rs_rank, rs_rows;
 } MmbFp4GemmParams;
 
 int mmb_fp4_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
@@ -49,6 +58,24 @@ typedef struct {
 } MmbBf16GemmParams;
 
 int mmb_bf16_gemm(const MmbBf16GemmParams* p, cudaStream_t stream);
+
+// Second half of the fused all-reduce of a row-parallel projection.  Waits (bounded) until every rank's partial of
+// this rank's token rows has arrived, sums the tp slots in rank order, optionally adds a bf16 residual of the local
+// rows, rounds to bf16 and stores the reduced rows into EVERY peer's gathered buffer bf16 [M, N] (all-gather by peer
+// stores); the last CTA publishes the step in ag flag[rank] on every peer.
+typedef struct {
+  const float* in_buf;              // local fp32 [tp][rows][N]
+  const unsigned* in_flags;         // local [tp]
+  void* const* ag_peer_bufs;        // device array [tp]: base of rank r's gathered buffer
+  unsigned* const* ag_peer_flags;   // device array [tp]: ag flag[rank] on rank r
+  unsigned* counter;
+  const unsigned* step;
+  int* status;
+  int tp, rank, rows, N, M;
+} MmbRsFinishParams;
+int mmb_tp_rs_finish(const MmbRsFinishParams* p, cudaStream_t stream);
+// Wait (bounded) until all tp ranks published `step` in `flags`; on expiry writes a code to `status`.
+int mmb_tp_wait(const unsigned* flags, const unsigned* step, int* status, int tp, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -392,6 +392,66 @@ void fp4_gemm(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, i
   check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm");
 }
 
+// Row-parallel projection with the reduce-scatter epilogue: `rs` is a CPU int64[7] descriptor
+// (peer buffer table, peer flag table, counter, step, tp, rank, rows per rank); nothing is written locally.
+void fp4_gemm_rs(const Tensor& x, const Tensor& qw, const Tensor& sc, int64_t N, int64_t gs, Tensor status, const Tensor& rs) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && qw.is_contiguous() && sc.is_contiguous());
+  TORCH_CHECK(!rs.is_cuda() && rs.scalar_type() == at::kLong && rs.numel() == 7, "rs must be a CPU int64[7] tensor");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t* v = rs.data_ptr<int64_t>();
+  MmbFp4GemmParams p{};
+  p.x = x.data_ptr();
+  p.qw = qw.data_ptr();
+  p.sc = sc.data_ptr();
+  p.out = nullptr;
+  p.M = (int)x.size(0);
+  p.N = (int)N;
+  p.K = (int)qw.size(1) * 64;
+  p.Kx = (int)x.size(1);
+  p.ldo = (int)N;
+  p.gs_shift = log2i(gs);
+  p.status = status.data_ptr<int>();
+  p.rs_peer_bufs = reinterpret_cast<float* const*>(v[0]);
+  p.rs_peer_flags = reinterpret_cast<unsigned* const*>(v[1]);
+  p.rs_counter = reinterpret_cast<unsigned*>(v[2]);
+  p.rs_step = reinterpret_cast<const unsigned*>(v[3]);
+  p.rs_tp = (int)v[4];
+  p.rs_rank = (int)v[5];
+  p.rs_rows = (int)v[6];
+  TORCH_CHECK(p.rs_rows > 0 && (int64_t)p.rs_rows * p.rs_tp >= p.M);
+  check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm_rs");
+}
+
+// desc: CPU int64[12] = in_buf, in_flags, ag_peer_bufs, ag_peer_flags, counter, step, status, tp, rank, rows, N, M
+void tp_rs_finish(const Tensor& desc) {
+  TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kLong && desc.numel() == 12);
+  const int64_t* v = desc.data_ptr<int64_t>();
+  MmbRsFinishParams p{};
+  p.in_buf = reinterpret_cast<const float*>(v[0]);
+  p.in_flags = reinterpret_cast<const unsigned*>(v[1]);
+  p.ag_peer_bufs = reinterpret_cast<void* const*>(v[2]);
+  p.ag_peer_flags = reinterpret_cast<unsigned* const*>(v[3]);
+  p.counter = reinterpret_cast<unsigned*>(v[4]);
+  p.step = reinterpret_cast<const unsigned*>(v[5]);
+  p.status = reinterpret_cast<int*>(v[6]);
+  p.tp = (int)v[7];
+  p.rank = (int)v[8];
+  p.rows = (int)v[9];
+  p.N = (int)v[10];
+  p.M = (int)v[11];
+  check(mmb_tp_rs_finish(&p, cur_stream()), "tp_rs_finish");
+}
+
+// desc: CPU int64[4] = flags, step, status, tp
+void tp_wait(const Tensor& desc) {
+  TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kLong && desc.numel() == 4);
+  const int64_t* v = desc.data_ptr<int64_t>();
+  check(mmb_tp_wait(reinterpret_cast<const unsigned*>(v[0]), reinterpret_cast<const unsigned*>(v[1]), reinterpret_cast<int*>(v[2]), (int)v[3],
+                    cur_stream()),
+        "tp_wait");
+}
+
 // Grouped (MoE) GEMM: x rows are sorted by expert; the tile list lives on the device.
 void fp4_gemm_grouped(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
                       const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
@@ -584,6 +644,9 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("argmax", &argmax);
   m.def("tp_argmax", &tp_argmax);
   m.def("fp4_gemm", &fp4_gemm);
+  m.def("fp4_gemm_rs", &fp4_gemm_rs);
+  m.def("tp_rs_finish", &tp_rs_finish);
+  m.def("tp_wait", &tp_wait);
   m.def("hadamard", &hadamard);
   m.def("trellis_dequant", &trellis_dequant);
   m.def("trellis_gemv", &trellis_gemv);

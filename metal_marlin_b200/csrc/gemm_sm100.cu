@@ -21,6 +21,7 @@
 
 #include "api_gemm.h"
 #include "common.cuh"
+#include "tp_comm.cuh"
 
 namespace mmb {
 
@@ -312,7 +313,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             const int r = c0 + j;
             if (r < tok_rows && tok0 + r < M) {
               float f = __uint_as_float(v[j]);
-              if (WFMT == 0) {
+              if (WFMT == 0 && p.rs_peer_bufs != nullptr) {
+                // reduce-scatter epilogue: the partial goes to the rank that owns this token row
+                const int row = tok0 + r, owner = row / p.rs_rows;
+                p.rs_peer_bufs[owner][((long long)p.rs_rank * p.rs_rows + (row - owner * p.rs_rows)) * N + n] = f;
+              } else if (WFMT == 0) {
                 if (p.row_scale) f *= p.row_scale[tok0 + r];
                 reinterpret_cast<bf16*>(p.out)[(long long)(tok0 + r) * ldo + n] = __float2bfloat16(f);
               } else {
@@ -325,6 +330,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
       }
     }
+  }
+  if (WFMT == 0 && p.rs_peer_bufs != nullptr) {
+    // all threads: make the peer stores visible system wide, then the last CTA of the grid raises the flags
+    TpOut tout;
+    tout.peer_slots = nullptr;
+    tout.peer_flags = p.rs_peer_flags;
+    tout.counter = p.rs_counter;
+    tout.step = p.rs_step;
+    tout.tp = p.rs_tp;
+    tp_signal(tout, gridDim.x * gridDim.y * gridDim.z);
   }
   // ---- teardown: if something timed out give in-flight bulk copies time to land, then free TMEM
   if (*abort_flag) {

@@ -103,9 +103,7 @@ class DecodeSession:
     def _step_body(self) -> None:
         meta = BatchMeta(positions=self.positions, slots=self.slots, block_tables=self.block_tables,
                          ctx_lens=self.ctx_lens, decode=True, max_ctx=self.max_ctx, splits=self.splits)
-        if getattr(self.model, "tp", None) is not None:
-            self.model.tp.begin_step()
-        logits = self.model.forward(self.ids, self.kv, meta)
+        logits = self.model.forward(self.ids, self.kv, meta)      # (a tensor-parallel model opens its exchange epoch itself)
         self.logits = logits
         if self.use_sampler_filters or self.use_history_penalty:
             logits = self.model.full_logits(logits)

@@ -361,6 +361,8 @@ class Transformer:
     def forward_hidden(self, input_ids: torch.Tensor, kv: PagedKVStorage, meta: BatchMeta) -> Tuple[torch.Tensor, torch.Tensor]:
         """Runs all layers.  Returns (hidden, pending delta): the final residual add + norm is fused
         into the head projection."""
+        if self.tp is not None:
+            self.tp.begin_step()          # new exchange epoch: every in-kernel exchange site is used once per forward pass
         h = ops.embedding(self.embed, input_ids)
         d = None
         for li, L in enumerate(self.layers):

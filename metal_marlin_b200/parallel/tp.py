@@ -31,6 +31,7 @@ from ..models.transformer import LayerWeights, Transformer
 from .symm import SymmetricBuffer
 
 FUSED_MAX_TOKENS = 16
+FUSED_GEMM_MAX_TOKENS = 8192      # prefill chunks up to this many tokens use the GEMM -> reduce-scatter epilogue
 
 
 def even_split(n: int, parts: int, unit: int = 1) -> List[Tuple[int, int]]:
@@ -85,6 +86,70 @@ class TPContext:
                 flags[s, r] = self.buf.peer_addr(r, flags_off + (s * tp + rank) * 4)
         self.peer_slots = slots.to(device)
         self.peer_flags = flags.to(device)
+        self._big = None       # prefill-size exchange buffers, created on first use
+
+    # ------------------------------------------------------------------ prefill-size exchange (GEMM -> RS, then AG)
+    def _big_buffers(self):
+        """Two (ping-pong by site parity) receive buffers fp32 [tp][rows][hidden] and gathered buffers bf16
+        [M][hidden], their flag words and the per-peer address tables.  Site s + 2 may reuse the buffers of site s:
+        no rank can produce site s + 2 before it consumed site s + 1, which needs every rank's site s + 1 partial,
+        which a rank only produces after it consumed site s."""
+        if self._big is not None:
+            return self._big
+        tp, H, M = self.tp, self.hidden, FUSED_GEMM_MAX_TOKENS
+        rows = (M + tp - 1) // tp
+        rs_bytes = tp * rows * H * 4
+        ag_bytes = M * H * 2
+        flag_bytes = self.n_sites * 2 * tp * 4                   # [site][rs | ag][tp]: flags are per site, buffers ping-pong
+        buf = SymmetricBuffer(2 * (rs_bytes + ag_bytes) + flag_bytes, self.device, self.group)
+        self._big = {"buf": buf, "rows_max": rows, "rs_bytes": rs_bytes, "ag_bytes": ag_bytes, "flags_off": 2 * (rs_bytes + ag_bytes),
+                     "tabs": {}, "counters": torch.zeros(2 * self.n_sites, dtype=torch.int32, device=self.device)}
+        return self._big
+
+    def _big_tables(self, site: int):
+        big = self._big_buffers()
+        t = big["tabs"].get(site)
+        if t is None:
+            buf, tp = big["buf"], self.tp
+            par = site & 1
+            rs_off = par * (big["rs_bytes"] + big["ag_bytes"])
+            ag_off = rs_off + big["rs_bytes"]
+            f_rs = big["flags_off"] + (site * 2 + 0) * tp * 4
+            f_ag = big["flags_off"] + (site * 2 + 1) * tp * 4
+            dev = self.device
+            t = {
+                "rs_bufs": torch.tensor([buf.peer_addr(r, rs_off) for r in range(tp)], dtype=torch.int64).to(dev),
+                "rs_flags": torch.tensor([buf.peer_addr(r, f_rs + self.rank * 4) for r in range(tp)], dtype=torch.int64).to(dev),
+                "ag_bufs": torch.tensor([buf.peer_addr(r, ag_off) for r in range(tp)], dtype=torch.int64).to(dev),
+                "ag_flags": torch.tensor([buf.peer_addr(r, f_ag + self.rank * 4) for r in range(tp)], dtype=torch.int64).to(dev),
+                "rs_local": buf.local.data_ptr() + rs_off, "ag_local_off": ag_off,
+                "rs_flags_local": buf.local.data_ptr() + f_rs, "ag_flags_local": buf.local.data_ptr() + f_ag,
+            }
+            big["tabs"][site] = t
+        return big, t
+
+    def use_fused_gemm(self, n_tokens: int, W) -> bool:
+        return (self.fused_ok and self.tp > 1 and ops.GEMV_MAX_M < n_tokens <= FUSED_GEMM_MAX_TOKENS and isinstance(W, ops.FP4Weight)
+                and W.out_features == self.hidden and W.in_features % 64 == 0)
+
+    def fused_gemm_all_reduce(self, x, W, site: int) -> torch.Tensor:
+        """``all_reduce(x @ W^T)`` in three launches and no collective call: the tcgen05 GEMM whose epilogue scatters
+        the fp32 partials to the owners of the token rows, the owners' reduce + all-gather-by-peer-stores, and a
+        bounded wait for the gathered rows.  Returns a bf16 ``[M, hidden]`` view of the gathered buffer."""
+        big, t = self._big_tables(site)
+        M, H, tp = x.shape[0], self.hidden, self.tp
+        rows = (M + tp - 1) // tp
+        cnt = big["counters"]
+        rs = torch.tensor([t["rs_bufs"].data_ptr(), t["rs_flags"].data_ptr(), cnt[site * 2:].data_ptr(), self.step.data_ptr(), tp, self.rank, rows],
+                          dtype=torch.int64)
+        xin = x if x.is_contiguous() and x.shape[1] == W.in_features else x[:, : W.in_features].contiguous()
+        ops.K.mmb200.fp4_gemm_rs(xin, W.qtile, W.stile, W.out_features, W.group_size, ops.gemm_status(x.device), rs)
+        fin = torch.tensor([t["rs_local"], t["rs_flags_local"], t["ag_bufs"].data_ptr(), t["ag_flags"].data_ptr(), cnt[site * 2 + 1:].data_ptr(),
+                            self.step.data_ptr(), self.status.data_ptr(), tp, self.rank, rows, H, M], dtype=torch.int64)
+        ops.K.mmb200.tp_rs_finish(fin)
+        ops.K.mmb200.tp_wait(torch.tensor([t["ag_flags_local"], self.step.data_ptr(), self.status.data_ptr(), tp], dtype=torch.int64))
+        off = t["ag_local_off"]
+        return big["buf"].local[off: off + M * H * 2].view(torch.bfloat16).view(M, H)
 
     # ------------------------------------------------------------------ descriptors (CPU int64[9])
     def _desc(self, kind: str, site: int, rows: int) -> torch.Tensor:
@@ -130,6 +195,8 @@ class TPContext:
         if self.use_fused(M):
             ops.linear(x, W, tpx=self._desc("out", site, M), out=self._dummy(M, W.out_features))
             return TPPartial(site, M)
+        if self.use_fused_gemm(M, W):
+            return self.fused_gemm_all_reduce(x, W, site)
         y = ops.linear(x, W)
         return self.all_reduce(y)
 
