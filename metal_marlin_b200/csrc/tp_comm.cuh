@@ -91,17 +91,19 @@ __device__ __forceinline__ void tp_push(const TpOut& t, long long idx, float v) 
   for (int r = 0; r < t.tp; ++r) t.peer_slots[r][idx] = v;
 }
 
-// Called by all threads of every CTA of the producer grid after their tp_push calls.
+// Called by all threads of every CTA of the producer grid after their tp_push calls.  The CTA barrier orders every
+// thread's peer stores before thread 0's system-scope fence (fences are cumulative over writes observed through the
+// barrier), so one fence per CTA - not one per thread - publishes them; the CTA that finds the counter complete
+// raises the flags.
 __device__ __forceinline__ void tp_signal(const TpOut& t, unsigned total_ctas) {
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned old = atomicAdd(t.counter, 1u);
     if (old == total_ctas - 1u) {
       __threadfence();
       atomicExch(t.counter, 0u);
       const unsigned step = *t.step;
-      __threadfence_system();
       for (int r = 0; r < t.tp; ++r) st_release_sys(t.peer_flags[r], step);
     }
   }
