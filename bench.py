@@ -189,6 +189,12 @@ def main():
         g = torch.Generator().manual_seed(args.seed + (0 if use_tp else rank))     # tensor-parallel ranks share the batch
         prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(batch)]
         bt = torch.arange(batch * nb, dtype=torch.int32).view(batch, nb)
+        # one untimed prefill of the first sequence: one-time library / attribute initialisation is not time-to-first-token
+        # (the timed prefill below rewrites the same cache blocks)
+        if eager:
+            eager_model.prefill(kv, prompts[:1], bt[:1])
+        else:
+            prefill(run_model, kv, prompts[:1], bt[:1])
         torch.cuda.synchronize(dev)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
@@ -257,7 +263,7 @@ def main():
     tok_s = replicas * args.batch * 1e3 / r["ms_per_step"]
     e2e_tok_s = replicas * args.batch * 1e3 / r["e2e_ms_per_step"]
     out = {
-        "metric": f"glm47_flash_mmfp4_decode_tok_s_bs{args.batch}",
+        "metric": f"{args.model.replace('-', '_').replace('.', '')}_mmfp4_decode_tok_s_bs{args.batch}".replace("glm_47_flash", "glm47_flash"),
         "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True, "scaling": "strong" if use_tp else "weak",
         "vs_baseline": round(tok_s / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",

@@ -37,8 +37,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const bf16* __restrict__ x
 }
 
 __global__ void silu_mul_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int inter) {
-  const long long r = blockIdx.y;
-  const int k = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  const long long r = blockIdx.x;            // rows on the x axis: prefill row counts exceed the 65535 limit of y
+  const int k = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
   if (k >= inter) return;
   float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(gu + r * 2 * inter + k));
   float2 u = __bfloat1622float2(*reinterpret_cast<const bf162*>(gu + r * 2 * inter + inter + k));
@@ -167,7 +167,7 @@ MMB_API int mmb_rmsnorm(const void* x, const void* delta, const void* w, void* o
 MMB_API int mmb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (inter % 2 != 0) return (int)cudaErrorInvalidValue;
-  dim3 grid((inter / 2 + 255) / 256, rows);
+  dim3 grid(rows, (inter / 2 + 255) / 256);
   mmb::silu_mul_kernel<<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
   return (int)cudaGetLastError();
 }
