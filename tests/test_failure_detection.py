@@ -1,0 +1,96 @@
+"""Rank-failure detection on CPU processes: a rank that leaves between steps, a rank that goes silent, and the
+device-status path of the step guard with a fake exchange context.  Failures are made on the host only."""
+import os
+import socket
+import time
+from datetime import timedelta
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from metal_marlin_b200.parallel.health import Heartbeat, PeerFailure, StepGuard
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, mode, q):
+    store = dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=timedelta(seconds=30))
+    hb = Heartbeat(store, rank, world, interval_s=0.05, timeout_s=0.6).start()
+    guard = StepGuard(hb)
+    steps, err = 0, None
+    store.add("ready", 1)                       # start together: process start-up times differ by seconds
+    while int(store.add("ready", 0)) < world:
+        time.sleep(0.01)
+    try:
+        for i in range(200):
+            if rank == 1 and i == 3:
+                if mode == "leave":
+                    hb.leave()                  # orderly: between steps, nothing in flight
+                else:
+                    hb.stop()                   # silent: the heartbeat thread dies, the process lingers
+                    time.sleep(3.0)
+                break
+            guard.run(lambda: time.sleep(0.02))
+            steps += 1
+    except PeerFailure as e:
+        err = (e.ranks, e.reason)
+    q.put((rank, steps, err))
+    if rank == 0:
+        time.sleep(0.5)                         # keep the store alive until the others reported
+    hb.stop()
+
+
+@pytest.mark.parametrize("mode", ["leave", "silent"])
+def test_survivors_detect_a_lost_rank_before_the_next_step(mode):
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, mode, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(world):
+        r, steps, err = q.get(timeout=60)
+        res[r] = (steps, err)
+    for p in procs:
+        p.join(timeout=30)
+    assert res[1] == (3, None)
+    for r in (0, 2):
+        steps, err = res[r]
+        assert err is not None and err[0] == [1], res
+        assert 2 <= steps < 200
+        assert ("left the job" in err[1]) if mode == "leave" else ("no heartbeat" in err[1])
+
+
+def test_step_guard_reports_device_wait_expiry():
+    class FakeStore(dict):
+        def set(self, k, v):
+            self[k] = v.encode() if isinstance(v, str) else v
+
+        def get(self, k):
+            return self[k]
+
+    class FakeCtx:
+        code = 0
+
+        def check(self):
+            return self.code
+
+    store = FakeStore()
+    hb = Heartbeat(store, 0, 1)
+    ctx = FakeCtx()
+    guard = StepGuard(hb, ctx)
+    assert guard.run(lambda: 7) == 7
+    ctx.code = 101                              # the bounded wait on source rank 1 expired
+    with pytest.raises(PeerFailure) as e:
+        guard.run(lambda: 7)
+    assert e.value.ranks == [1] and "status 101" in str(e.value)

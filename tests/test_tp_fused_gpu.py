@@ -44,9 +44,30 @@ def run(model, graph):
 lg_ref, tok_ref = run(lm.model, False)
 lg_tp, tok_tp = run(shard, False)
 lg_g, tok_g = run(shard, True)
+# expert parallel decode: every rank runs its own experts on the replicated tokens, the partial outputs meet through the
+# same in-kernel exchange (site 0 of a fresh epoch); the sum over the receive slots must equal the unsharded MoE
+from metal_marlin_b200 import ops
+from metal_marlin_b200.parallel.ep import ExpertParallelMoE
+cfg = lm.config
+Lm = next(l for l in lm.model.layers if l.router_w is not None)
+torch.manual_seed(1)
+T = 5
+xe = (torch.randn(T, cfg.hidden_size, device=dev) * 0.5).to(torch.bfloat16)
+ide = torch.stack([torch.randperm(cfg.num_experts, device=dev)[: cfg.num_experts_per_tok] for _ in range(T)]).to(torch.int32)
+wte = torch.rand(T, cfg.num_experts_per_tok, device=dev)
+full = ops.moe_forward(xe, Lm.gate_up_bank, Lm.down_bank, ide, wte, n_shared=cfg.n_shared_experts, shared_base=cfg.num_experts,
+                       norm_w=Lm.post_norm).float()
+ep = ExpertParallelMoE(Lm.gate_up_bank, Lm.down_bank, cfg.num_experts, cfg.n_shared_experts, rank, world)
+ctx.begin_step()
+ep.partial(xe, ide, wte, norm_w=Lm.post_norm, tpx=ctx._desc("out", 0, T))
+d_in = ctx._desc("in", 0, T)
+ops.K.mmb200.tp_wait(torch.tensor([int(d_in[1]), ctx.step.data_ptr(), ctx.status.data_ptr(), world], dtype=torch.int64))
+torch.cuda.synchronize()
+slots = ctx.buf.local[: world * ctx.slot * 4].view(torch.float32).view(world, ctx.slot)[:, : T * cfg.hidden_size]
+ep_err = float((slots.sum(0).view(T, cfg.hidden_size) - full).abs().max() / full.abs().max())
 err = float((lg_tp - lg_ref).abs().max() / lg_ref.abs().max())
 res = {"rank": rank, "err": err, "eager_equal": bool(torch.equal(tok_tp, tok_ref)), "graph_equal": bool(torch.equal(tok_g, tok_ref)),
-       "status": ctx.check(), "backend": ctx.buf.backend}
+       "status": ctx.check(), "backend": ctx.buf.backend, "ep_err": ep_err}
 print("RESULT " + json.dumps(res), flush=True)
 dist.barrier()
 dist.destroy_process_group()
@@ -86,3 +107,4 @@ def test_fused_tp_decode_matches_unsharded(preset, tmp_path):
         assert res["status"] == 0, res
         assert res["err"] < 4e-2, res
         assert res["eager_equal"] and res["graph_equal"], res
+        assert res["ep_err"] < 2e-2, res
