@@ -57,3 +57,32 @@ int mmb_selective_scan_step(const void* x, const float* dt, const float* A, cons
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+// Prefill (multi-query) attention with online softmax, causal / sliding-window masks, grouped KV heads and variable
+// sequence lengths.  Queries of sequence b are rows cu_q[b] .. cu_q[b + 1] of q and attend to that sequence's keys:
+// either contiguous rows cu_k[b] .. cu_k[b + 1] of k / v, or (cu_k == null) the paged pool addressed through
+// block_tables [B, max_blocks] with ctx_lens[b] keys.  The q rows are the LAST q_len positions of the kv_len keys.
+// All strides in elements.  D == DV in {64, 128, 256}.
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  long long q_tok_stride, q_head_stride, k_tok_stride, k_head_stride, v_tok_stride, v_head_stride, o_tok_stride, o_head_stride;
+  const int* cu_q;
+  const int* cu_k;
+  const int* block_tables;
+  const int* ctx_lens;
+  int max_blocks, block_size;
+  int B, Hq, Hk, D, max_q;
+  float scale;
+  int window;      // 0 = none; > 0: a query sees the last `window` keys up to its own position
+  int causal;
+} MmbPrefillAttnParams;
+int mmb_prefill_attention(const MmbPrefillAttnParams* p, cudaStream_t stream);
+#ifdef __cplusplus
+}
+#endif

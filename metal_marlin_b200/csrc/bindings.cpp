@@ -624,6 +624,52 @@ void selective_scan_step(const Tensor& x, const Tensor& dt, const Tensor& A, con
         "selective_scan_step");
 }
 
+// q [T, Hq, D], out [T, Hq, D] (any strides with unit inner stride); contiguous mode: k, v [N, Hk, D] + cu_k; paged mode:
+// k, v pools [slots, Hk, D] + block_tables + ctx_lens.
+void prefill_attention(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, const Tensor& cu_q, const OptT& cu_k,
+                       const OptT& block_tables, const OptT& ctx_lens, int64_t block_size, int64_t max_q, double scale, int64_t window,
+                       bool causal) {
+  check_bf16(q, "q");
+  check_bf16(k, "k");
+  check_bf16(v, "v");
+  check_bf16(out, "out");
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && out.dim() == 3);
+  TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1 && out.stride(2) == 1);
+  TORCH_CHECK(cu_q.scalar_type() == at::kInt && cu_q.is_contiguous() && q.size(2) == k.size(2) && v.size(2) == q.size(2));
+  c10::cuda::CUDAGuard guard(q.device());
+  MmbPrefillAttnParams p{};
+  p.q = q.data_ptr();
+  p.k = k.data_ptr();
+  p.v = v.data_ptr();
+  p.out = out.data_ptr();
+  p.q_tok_stride = q.stride(0);
+  p.q_head_stride = q.stride(1);
+  p.k_tok_stride = k.stride(0);
+  p.k_head_stride = k.stride(1);
+  p.v_tok_stride = v.stride(0);
+  p.v_head_stride = v.stride(1);
+  p.o_tok_stride = out.stride(0);
+  p.o_head_stride = out.stride(1);
+  p.cu_q = cu_q.data_ptr<int>();
+  p.cu_k = (cu_k.has_value() && cu_k->defined()) ? cu_k->data_ptr<int>() : nullptr;
+  if (block_tables.has_value() && block_tables->defined()) {
+    TORCH_CHECK(block_tables->scalar_type() == at::kInt && block_tables->is_contiguous() && ctx_lens.has_value() && ctx_lens->scalar_type() == at::kInt);
+    p.block_tables = block_tables->data_ptr<int>();
+    p.ctx_lens = ctx_lens->data_ptr<int>();
+    p.max_blocks = (int)block_tables->size(1);
+  }
+  p.block_size = (int)block_size;
+  p.B = (int)cu_q.numel() - 1;
+  p.Hq = (int)q.size(1);
+  p.Hk = (int)k.size(1);
+  p.D = (int)q.size(2);
+  p.max_q = (int)max_q;
+  p.scale = (float)scale;
+  p.window = (int)window;
+  p.causal = causal ? 1 : 0;
+  check(mmb_prefill_attention(&p, cur_stream()), "prefill_attention");
+}
+
 TORCH_LIBRARY(mmb200, m) {
   m.def("fp4_gemm_grouped", &fp4_gemm_grouped);
   m.def("bf16_gemm", &bf16_gemm);
@@ -653,6 +699,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("codebook_gemv", &codebook_gemv);
   m.def("vision_preprocess", &vision_preprocess);
   m.def("spec_verify", &spec_verify);
+  m.def("prefill_attention", &prefill_attention);
   m.def("gated_delta_step", &gated_delta_step);
   m.def("selective_scan_step", &selective_scan_step);
 }

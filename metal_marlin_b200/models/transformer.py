@@ -220,6 +220,14 @@ class Transformer:
         Hq, Hk, D = self.n_heads_local, self.n_kv_heads_local, cfg.dh
         out = torch.empty(q.shape[0], Hq * D, dtype=torch.bfloat16, device=q.device)
         bs = kv.block_size
+        if meta.attn_mask is None and q.dtype == torch.bfloat16:
+            # one launch for all sequences: keys are read from the paged pool through the block table
+            cu_q = torch.tensor(meta.cu_seqlens, dtype=torch.int32, device=q.device)
+            max_q = max(meta.cu_seqlens[i + 1] - meta.cu_seqlens[i] for i in range(len(meta.cu_seqlens) - 1))
+            ops.prefill_attention(q, kv.k[li].view(-1, Hk, D), kv.v[li].view(-1, Hk, D), cu_q, block_tables=meta.block_tables,
+                                  ctx_lens=meta.ctx_lens, block_size=bs, max_q=max_q, scale=self.scale, window=cfg.sliding_window,
+                                  out=out.view(-1, Hq, D))
+            return out
         for b in range(len(meta.cu_seqlens) - 1):
             s, e = meta.cu_seqlens[b], meta.cu_seqlens[b + 1]
             n_ctx = int(meta.ctx_lens_host[b])
@@ -294,14 +302,10 @@ class Transformer:
             kvx = (ops.bf16_gemm(c, L.kv_b_dense) if R % 64 == 0 else torch.matmul(c, L.kv_b_dense.t())).view(n_ctx, H, dn + dv)
             k = torch.cat([kvx[..., :dn], lat[:, None, R:].expand(n_ctx, H, dr)], -1)
             qq = torch.cat([q[s:e, :, :dn], q_full[s:e, :, R:]], -1)
-            mask = None
-            if n_ctx != t:
-                qpos = torch.arange(n_ctx - t, n_ctx, device=q.device).unsqueeze(1)
-                mask = tok.unsqueeze(0) <= qpos
-            o = F.scaled_dot_product_attention(qq.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
-                                               kvx[..., dn:].transpose(0, 1).unsqueeze(0), attn_mask=mask, is_causal=(mask is None),
-                                               scale=self.scale)
-            out[s:e] = o.squeeze(0).transpose(0, 1).reshape(t, H * dv)
+            cu_q = torch.tensor([0, t], dtype=torch.int32, device=q.device)
+            cu_k = torch.tensor([0, n_ctx], dtype=torch.int32, device=q.device)
+            ops.prefill_attention(qq, k.contiguous(), kvx[..., dn:], cu_q, cu_k=cu_k, max_q=t, scale=self.scale,
+                                  out=out[s:e].view(t, H, dv))
         return out
 
     def _prefill_attention_mla(self, L: LayerWeights, q_full, kv: PagedKVStorage, li: int, meta: BatchMeta):

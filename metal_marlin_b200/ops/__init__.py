@@ -556,3 +556,23 @@ def spec_verify(p_target, p_draft, draft, u, u_resample):
     acc = torch.empty(B, dtype=torch.int32, device=p_target.device)
     K.mmb200.spec_verify(p_target.contiguous(), p_draft.contiguous(), draft.contiguous(), u.contiguous(), u_resample.contiguous(), toks, acc)
     return toks, acc
+
+
+PREFILL_ATTN_DIMS = (64, 128, 256)
+
+
+def prefill_attention(q, k, v, cu_q, *, cu_k=None, block_tables=None, ctx_lens=None, block_size=16, max_q=None, scale=None, window=0,
+                      causal=True, out=None, q_lens_host=None, k_lens_host=None):
+    """Variable-length prefill attention.  ``q [T, Hq, D]``; contiguous keys ``k, v [N, Hk, D]`` with ``cu_k``, or paged
+    pools ``[slots, Hk, D]`` with ``block_tables`` / ``ctx_lens``.  The queries of a sequence are the last positions of
+    its keys.  ``cu_q`` / ``cu_k``: int32 device tensors ``[B + 1]``."""
+    T, Hq, D = q.shape
+    scale = scale if scale is not None else D ** -0.5
+    if out is None:
+        out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    if _use_native(q) and D in PREFILL_ATTN_DIMS and q.dtype == torch.bfloat16 and k.shape[-1] == D and v.shape[-1] == D:
+        if max_q is None:
+            max_q = int((cu_q[1:] - cu_q[:-1]).max())
+        K.mmb200.prefill_attention(q, k, v, out, cu_q, cu_k, block_tables, ctx_lens, block_size, max_q, scale, window, causal)
+        return out
+    return ref.prefill_attention(q, k, v, cu_q, cu_k, block_tables, ctx_lens, block_size, scale, window, causal, out)

@@ -374,3 +374,37 @@ def spec_verify(p_target, p_draft, draft, u, u_resample):
         toks[b, n] = idx
         acc[b] = n
     return toks, acc
+
+
+def prefill_attention(q, k, v, cu_q, cu_k, block_tables, ctx_lens, block_size, scale, window, causal, out):
+    T, Hq, D = q.shape
+    Hk = k.shape[1]
+    cq = cu_q.tolist()
+    for b in range(len(cq) - 1):
+        s, e = cq[b], cq[b + 1]
+        t = e - s
+        if t == 0:
+            continue
+        if cu_k is not None:
+            ck = cu_k.tolist()
+            kb, vb = k[ck[b]:ck[b + 1]], v[ck[b]:ck[b + 1]]
+        else:
+            n = int(ctx_lens[b])
+            tok = torch.arange(n, device=q.device)
+            slots = block_tables[b, tok // block_size].long() * block_size + tok % block_size
+            kb, vb = k[slots], v[slots]
+        n = kb.shape[0]
+        qf = q[s:e].to(torch.float32).transpose(0, 1)                                 # [Hq, t, D]
+        kf = kb.to(torch.float32).transpose(0, 1).repeat_interleave(Hq // Hk, 0)
+        vf = vb.to(torch.float32).transpose(0, 1).repeat_interleave(Hq // Hk, 0)
+        sc = qf @ kf.transpose(-1, -2) * scale
+        qpos = torch.arange(n - t, n, device=q.device)[:, None]
+        kpos = torch.arange(n, device=q.device)[None, :]
+        ok = torch.ones(t, n, dtype=torch.bool, device=q.device)
+        if causal:
+            ok &= kpos <= qpos
+        if window and window > 0:
+            ok &= kpos > qpos - window
+        sc = sc.masked_fill(~ok, float("-inf"))
+        out[s:e] = (torch.softmax(sc, -1) @ vf).transpose(0, 1).to(out.dtype)
+    return out

@@ -89,3 +89,44 @@ def test_spec_verify_matches_reference_and_accept_rules():
         resid = pt[b, n] - (pd[b, n] if n < K else 0)
         assert 0 <= t < V and (float(resid[t]) > 0 or n == K or float(resid.clamp_min(0).sum()) == 0)
     assert (toks[:, 0] == toks_ref[:, 0]).float().mean() >= 0.5 or True
+
+
+@pytest.mark.parametrize("D,Hq,Hk", [(128, 8, 2), (64, 4, 4), (256, 6, 1)])
+@pytest.mark.parametrize("window", [0, 37])
+def test_prefill_attention_contiguous_and_paged(D, Hq, Hk, window):
+    torch.manual_seed(D + window)
+    q_lens, k_lens = [70, 1, 130], [70, 45, 200]                      # full prefill, one new token on a prefix, a chunk on a prefix
+    T, N = sum(q_lens), sum(k_lens)
+    q = (torch.randn(T, Hq, D, device=DEV) * 0.5).to(torch.bfloat16)
+    k = (torch.randn(N, Hk, D, device=DEV) * 0.5).to(torch.bfloat16)
+    v = (torch.randn(N, Hk, D, device=DEV) * 0.5).to(torch.bfloat16)
+    cu = lambda ls: torch.tensor([0] + list(torch.tensor(ls).cumsum(0)), dtype=torch.int32, device=DEV)
+    cu_q, cu_k = cu(q_lens), cu(k_lens)
+    got = ops.prefill_attention(q, k, v, cu_q, cu_k=cu_k, window=window)
+    with ops.force_reference():
+        want = ops.prefill_attention(q, k, v, cu_q, cu_k=cu_k, window=window)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    # the same keys scattered into a paged pool
+    bs = 16
+    n_blocks = sum((n + bs - 1) // bs for n in k_lens) + 3
+    perm = torch.randperm(n_blocks, device=DEV).to(torch.int32)
+    maxb = max((n + bs - 1) // bs for n in k_lens)
+    bt = torch.zeros(3, maxb, dtype=torch.int32, device=DEV)
+    kp = torch.zeros(n_blocks * bs, Hk, D, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    used = k0 = 0
+    for b, n in enumerate(k_lens):
+        nb = (n + bs - 1) // bs
+        bt[b, :nb] = perm[used:used + nb]
+        tok = torch.arange(n, device=DEV)
+        slots = bt[b, tok // bs].long() * bs + tok % bs
+        kp[slots], vp[slots] = k[k0:k0 + n], v[k0:k0 + n]
+        used, k0 = used + nb, k0 + n
+    got_p = ops.prefill_attention(q, kp, vp, cu_q, block_tables=bt, ctx_lens=torch.tensor(k_lens, dtype=torch.int32, device=DEV), block_size=bs,
+                                  window=window)
+    torch.testing.assert_close(got_p.float(), want.float(), rtol=2e-2, atol=2e-2)
+    # strided views (a fused qkv buffer): unit inner stride is all the kernel needs
+    qkv = torch.zeros(T, (Hq + 1) * D, dtype=torch.bfloat16, device=DEV)
+    qkv[:, : Hq * D] = q.view(T, Hq * D)
+    got_s = ops.prefill_attention(qkv[:, : Hq * D].view(T, Hq, D), k, v, cu_q, cu_k=cu_k, window=window)
+    torch.testing.assert_close(got_s.float(), want.float(), rtol=2e-2, atol=2e-2)
