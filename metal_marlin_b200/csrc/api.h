@@ -143,6 +143,8 @@ typedef struct {
   MmbTpExchange tpx;         // consumer side only
 } MmbRouterParams;
 int mmb_moe_router(const MmbRouterParams* p, cudaStream_t stream);
+// Selection only: gate logits fp32 [T, E] are given (computed by a GEMM); uses the scoring / top-k fields of `p`.
+int mmb_moe_select(const MmbRouterParams* p, const float* logits_in, cudaStream_t stream);
 
 // ----------------------------------------------------------------------------- sampling
 typedef struct {

@@ -321,6 +321,27 @@ void moe_router(const Tensor& x, const Tensor& w, const OptT& delta, const OptT&
   check(mmb_moe_router(&p, cur_stream()), "moe_router");
 }
 
+void moe_select(const Tensor& logits, const OptT& bias, Tensor ids, Tensor weights, const OptT& counts, int64_t topk, int64_t scoring,
+                bool renorm, double routed_scale, int64_t n_group, int64_t topk_group) {
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.is_contiguous() && logits.dim() == 2);
+  TORCH_CHECK(ids.scalar_type() == at::kInt && weights.scalar_type() == at::kFloat && ids.is_contiguous() && weights.is_contiguous());
+  c10::cuda::CUDAGuard guard(logits.device());
+  MmbRouterParams p{};
+  p.bias = (bias.has_value() && bias->defined()) ? bias->data_ptr<float>() : nullptr;
+  p.ids = ids.data_ptr<int>();
+  p.weights = weights.data_ptr<float>();
+  p.counts = (counts.has_value() && counts->defined()) ? counts->data_ptr<int>() : nullptr;
+  p.T = (int)logits.size(0);
+  p.E = (int)logits.size(1);
+  p.topk = (int)topk;
+  p.scoring = (int)scoring;
+  p.renorm = renorm ? 1 : 0;
+  p.routed_scale = (float)routed_scale;
+  p.n_group = (int)n_group;
+  p.topk_group = (int)topk_group;
+  check(mmb_moe_select(&p, logits.data_ptr<float>(), cur_stream()), "moe_select");
+}
+
 void sample(const Tensor& logits, Tensor out_ids, const OptT& out_logprob, const OptT& temperature, const OptT& top_k,
             const OptT& top_p, const OptT& min_p, const OptT& history, const OptT& rep_penalty, int64_t seed,
             int64_t offset, const OptT& offset_dev) {
@@ -686,6 +707,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("paged_decode", &paged_decode);
   m.def("decode_merge", &decode_merge);
   m.def("moe_router", &moe_router);
+  m.def("moe_select", &moe_select);
   m.def("sample", &sample);
   m.def("argmax", &argmax);
   m.def("tp_argmax", &tp_argmax);

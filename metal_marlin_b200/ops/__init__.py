@@ -22,6 +22,7 @@ from .weights import FP4ExpertBank, FP4Weight  # noqa: F401
 _FORCE_REF = os.environ.get("MMB200_FORCE_TORCH", "0") == "1"
 _native_ok = False
 GEMV_MAX_M = 32          # dense projections: at or below this many tokens the weight-streaming GEMV path is used
+ROUTER_GEMM_MIN_T = 64   # above this many tokens the gate logits come from the bf16 tcgen05 GEMM
 MOE_GEMV_MAX_T = 16      # MoE: per-(token, slot) streaming up to this many tokens, grouped tcgen05 GEMMs above
 # Diagnostic switch: route every shape through the weight-streaming kernels (no tcgen05 GEMM).
 NO_TCGEN05 = os.environ.get("MMB200_NO_TCGEN05", "0") == "1"
@@ -300,6 +301,21 @@ def moe_router(x, w, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, bias=
     if ids is None:
         ids = torch.empty(T, topk, dtype=torch.int32, device=x.device)
         weights = torch.empty(T, topk, dtype=torch.float32, device=x.device)
+    if T > ROUTER_GEMM_MIN_T and tpx is None and w.shape[1] % 64 == 0 and x.is_contiguous():
+        # prefill: add + norm kernel, gate logits on the tensor cores, then one warp per token scores and selects
+        xin = torch.empty_like(x)
+        if norm_w is not None:
+            K.mmb200.rmsnorm(x, delta, norm_w, xin, resid_out, eps)
+        elif delta is not None:
+            K.mmb200.add(x, delta.contiguous(), xin)
+            if resid_out is not None:
+                resid_out.copy_(xin)
+        else:
+            xin = x
+        lg = logits_out if logits_out is not None else torch.empty(T, w.shape[0], dtype=torch.float32, device=x.device)
+        K.mmb200.bf16_gemm(xin, w, lg, gemm_status(x.device))
+        K.mmb200.moe_select(lg, bias, ids, weights, counts, topk, scoring, renorm, routed_scale, n_group, topk_group)
+        return ids, weights
     K.mmb200.moe_router(x, w, delta, norm_w, resid_out, bias, ids, weights, logits_out, counts, topk, eps, scoring,
                         renorm, routed_scale, n_group, topk_group, tpx)
     return ids, weights

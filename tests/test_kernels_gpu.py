@@ -252,9 +252,10 @@ def test_mla_prep(T):
 
 @pytest.mark.parametrize("scoring,E,topk,ng,tg", [(0, 64, 4, 1, 1), (1, 64, 4, 1, 1), (1, 64, 8, 8, 4), (0, 128, 8, 1, 1),
                                                   (1, 8, 2, 1, 1)])
-def test_moe_router(scoring, E, topk, ng, tg):
+@pytest.mark.parametrize("T", [6, 200])      # 200 tokens: gate logits from the tensor-core GEMM + select kernel
+def test_moe_router(scoring, E, topk, ng, tg, T):
     torch.manual_seed(3)
-    T, K = 6, 512
+    K = 512
     x, d, w = _bf(T, K), _bf(T, K, scale=0.2), _bf(E, K, scale=0.2)
     nw = (1 + 0.1 * torch.randn(K, device=DEV)).to(torch.bfloat16)
     bias = torch.randn(E, device=DEV) * 0.1 if scoring == 1 else None
