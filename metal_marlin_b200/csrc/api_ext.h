@@ -86,3 +86,15 @@ int mmb_prefill_attention(const MmbPrefillAttnParams* p, cudaStream_t stream);
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+// MoE dispatch helpers (see moe_dispatch.cu).  ids int32 [n = T * topk]; order / inv int32 [n]; tile arrays int32 [max_tiles].
+int mmb_moe_group(const int* ids, int n, int E, int token_tile, int max_tiles, int* order, int* inv, int* tile_expert, int* tile_row0,
+                  int* tile_rows, int* n_tiles, cudaStream_t stream);
+int mmb_moe_gather(const void* x, const int* order, void* xs, int n, int topk, int K, int ldx, cudaStream_t stream);
+int mmb_moe_combine(const void* y, const int* inv, const void* add0, const void* add1, void* out, int T, int topk, int N, cudaStream_t stream);
+#ifdef __cplusplus
+}
+#endif

@@ -691,6 +691,42 @@ void prefill_attention(const Tensor& q, const Tensor& k, const Tensor& v, Tensor
   check(mmb_prefill_attention(&p, cur_stream()), "prefill_attention");
 }
 
+void moe_group(const Tensor& ids, int64_t E, int64_t token_tile, Tensor order, Tensor inv, Tensor tile_expert, Tensor tile_row0,
+               Tensor tile_rows, Tensor n_tiles) {
+  TORCH_CHECK(ids.scalar_type() == at::kInt && ids.is_contiguous() && order.scalar_type() == at::kInt && inv.scalar_type() == at::kInt);
+  TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_row0.scalar_type() == at::kInt && tile_rows.scalar_type() == at::kInt &&
+              n_tiles.scalar_type() == at::kInt);
+  TORCH_CHECK(order.numel() == ids.numel() && inv.numel() == ids.numel() && tile_row0.numel() == tile_expert.numel() &&
+              tile_rows.numel() == tile_expert.numel());
+  c10::cuda::CUDAGuard guard(ids.device());
+  check(mmb_moe_group(ids.data_ptr<int>(), (int)ids.numel(), (int)E, (int)token_tile, (int)tile_expert.numel(), order.data_ptr<int>(),
+                      inv.data_ptr<int>(), tile_expert.data_ptr<int>(), tile_row0.data_ptr<int>(), tile_rows.data_ptr<int>(),
+                      n_tiles.data_ptr<int>(), cur_stream()),
+        "moe_group");
+}
+
+void moe_gather(const Tensor& x, const Tensor& order, Tensor xs, int64_t topk) {
+  check_bf16(x, "x");
+  check_bf16(xs, "xs");
+  TORCH_CHECK(x.stride(1) == 1 && xs.is_contiguous() && order.scalar_type() == at::kInt && xs.size(0) == order.numel() && xs.size(1) <= x.size(1));
+  c10::cuda::CUDAGuard guard(x.device());
+  check(mmb_moe_gather(x.data_ptr(), order.data_ptr<int>(), xs.data_ptr(), (int)order.numel(), (int)topk, (int)xs.size(1), (int)x.stride(0),
+                       cur_stream()),
+        "moe_gather");
+}
+
+void moe_combine(const Tensor& y, const Tensor& inv, const OptT& add0, const OptT& add1, Tensor out, int64_t topk) {
+  check_bf16(y, "y");
+  check_bf16(out, "out");
+  TORCH_CHECK(y.is_contiguous() && out.is_contiguous() && inv.scalar_type() == at::kInt && inv.numel() == out.size(0) * topk);
+  if (add0.has_value() && add0->defined()) TORCH_CHECK(add0->is_contiguous() && add0->scalar_type() == at::kBFloat16);
+  if (add1.has_value() && add1->defined()) TORCH_CHECK(add1->is_contiguous() && add1->scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(y.device());
+  check(mmb_moe_combine(y.data_ptr(), inv.data_ptr<int>(), cptr(add0), cptr(add1), out.data_ptr(), (int)out.size(0), (int)topk, (int)out.size(1),
+                        cur_stream()),
+        "moe_combine");
+}
+
 TORCH_LIBRARY(mmb200, m) {
   m.def("fp4_gemm_grouped", &fp4_gemm_grouped);
   m.def("bf16_gemm", &bf16_gemm);
@@ -721,6 +757,9 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("codebook_gemv", &codebook_gemv);
   m.def("vision_preprocess", &vision_preprocess);
   m.def("spec_verify", &spec_verify);
+  m.def("moe_group", &moe_group);
+  m.def("moe_gather", &moe_gather);
+  m.def("moe_combine", &moe_combine);
   m.def("prefill_attention", &prefill_attention);
   m.def("gated_delta_step", &gated_delta_step);
   m.def("selective_scan_step", &selective_scan_step);

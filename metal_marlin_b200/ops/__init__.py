@@ -452,33 +452,43 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
         xin = torch.empty_like(x)
         K.mmb200.rmsnorm(x, None, norm_w, xin, None, eps)
     st = gemm_status(x.device)
+    E_routed = gate_up.num_experts - n_shared
     if not token_tile:      # smallest MMA N tile that holds the average expert load
-        avg = T * topk / max(1, gate_up.num_experts - n_shared)
+        avg = T * topk / max(1, E_routed)
         token_tile = 32 if avg <= 24 else (64 if avg <= 48 else 128)
     inter = gate_up.out_features // 2
-    flat = ids.reshape(-1).long()
-    order, t_e, t_r0, t_rows, n_tiles = _build_tile_list(flat, gate_up.num_experts, token_tile)
-    tok = torch.div(order, topk, rounding_mode="floor")
-    xs = xin.index_select(0, tok)
-    gu = torch.empty(xs.shape[0], gate_up.out_features, dtype=torch.bfloat16, device=x.device)
+    n = T * topk
+    dev = x.device
+    # device-side dispatch: counting sort by expert + tile list (one launch), gather in expert order (one launch)
+    max_tiles = (n + token_tile - 1) // token_tile + gate_up.num_experts
+    order = torch.empty(n, dtype=torch.int32, device=dev)
+    inv = torch.empty(n, dtype=torch.int32, device=dev)
+    t_e = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    t_r0, t_rows = torch.empty_like(t_e), torch.empty_like(t_e)
+    n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    K.mmb200.moe_group(ids.reshape(-1).contiguous(), gate_up.num_experts, token_tile, order, inv, t_e, t_r0, t_rows, n_tiles)
+    xs = torch.empty(n, gate_up.in_features, dtype=torch.bfloat16, device=dev)
+    K.mmb200.moe_gather(xin, order, xs, topk)
+    gu = torch.empty(n, gate_up.out_features, dtype=torch.bfloat16, device=dev)
     K.mmb200.fp4_gemm_grouped(xs, gate_up.qtile, gate_up.stile, gu, gate_up.out_features, gate_up.group_size,
                               t_e, t_r0, t_rows, n_tiles, token_tile, None, st)
-    h = torch.empty(xs.shape[0], inter, dtype=torch.bfloat16, device=x.device)
+    h = torch.empty(n, inter, dtype=torch.bfloat16, device=dev)
     K.mmb200.silu_mul(gu, h)
-    y = torch.empty(xs.shape[0], down.out_features, dtype=torch.bfloat16, device=x.device)
-    rs = weights.reshape(-1).index_select(0, order).contiguous()
+    y = torch.empty(n, down.out_features, dtype=torch.bfloat16, device=dev)
+    # routing weight of every sorted row (dropped pairs, id < 0, are never read by a tile)
+    rs = weights.reshape(-1).to(torch.float32).index_select(0, order.clamp_min(0).long()).contiguous()
     K.mmb200.fp4_gemm_grouped(h, down.qtile, down.stile, y, down.out_features, down.group_size,
                               t_e, t_r0, t_rows, n_tiles, token_tile, rs, st)
-    unsorted = torch.empty_like(y)
-    unsorted.index_copy_(0, order, y)
-    acc = unsorted.view(T, topk, -1).to(torch.float32).sum(1)
+    shared = None
     for j in range(n_shared):
         e = shared_base + j
         hs = linear(xin, gate_up.expert(e), act=1)
-        acc += linear(hs, down.expert(e)).to(torch.float32)
-    if out_add is not None:
-        acc += out_add.to(torch.float32)
-    return acc.to(torch.bfloat16)
+        sj = linear(hs, down.expert(e))
+        shared = sj if shared is None else shared + sj
+    out = torch.empty(T, down.out_features, dtype=torch.bfloat16, device=dev)
+    # combine: un-sort, sum over the token's slots, add the shared expert and the residual input (one launch)
+    K.mmb200.moe_combine(y, inv, shared, None if out_add is None else out_add.contiguous(), out, topk)
+    return out
 
 
 # ----------------------------------------------------------------------------------------------------------------
