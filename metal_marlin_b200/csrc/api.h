@@ -42,7 +42,7 @@ typedef struct {
   int gs_shift;              // log2(group size); group size is a power of two >= 16
   float eps;
   int act;                   // 0 = none, 1 = rows [0,N/2) are gate, [N/2,N) are up: out[:, n] = silu(g) * u
-  int mode;                  // 0 dense, 1 MoE gate-up (one CTA column per (token, slot)), 2 MoE down
+  int mode;                  // 0 dense, 1 MoE gate-up (one CTA column per (token, slot)), 2 MoE down, 3 grouped MoE (tile list)
   const int* expert_ids;     // [M, topk] routed expert per slot (negative = skip)
   const float* expert_w;     // [M, topk] routing weights (mode 2)
   int topk, n_shared;        // slots per token = topk + n_shared; shared expert j has index shared_base + j
@@ -50,6 +50,19 @@ typedef struct {
   long long expert_stride_q; // distance between experts in 16-byte units
   long long expert_stride_s; // distance between experts in 4-byte units
   MmbTpExchange tpx;         // all-zero = single GPU
+  // mode 3: grouped MoE over a device-built tile list (rows of the work are sorted by expert).  Tile j covers sorted rows
+  // tile_row0[j] .. + tile_rows[j] (<= 8) of expert tile_expert[j]; *n_tiles tiles are valid.  x is used as is (no add /
+  // norm).  row_order (optional) holds the flat (token * order_div + slot) pair of every sorted row: with order_div > 0
+  // the input row is gathered from x[pair / order_div], and with expert_w set the output row is scaled by
+  // expert_w[pair] (routing weight of the down projection).
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* n_tiles;
+  const int* row_order;
+  int order_div;
+  int max_tiles;
+  int grouped_wpt, grouped_upi;   // 0 = chosen by the launcher; warps per unit (1, 2, 4, 8) and units per item and group
 } MmbFp4GemvParams;
 
 int mmb_fp4_gemv(const MmbFp4GemvParams* p, cudaStream_t stream);

@@ -132,6 +132,54 @@ void fp4_moe_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor ou
   check(mmb_fp4_gemv(&p, cur_stream()), "fp4_moe_gemv");
 }
 
+// Grouped MoE weight-streaming kernel over a device-built tile list (tiles of at most 8 sorted rows).
+void fp4_grouped_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, int64_t act,
+                      const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
+                      const OptT& row_order, int64_t order_div, const OptT& weights, int64_t wpt, int64_t upi) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(qw.dim() == 5 && qw.is_contiguous() && sc.is_contiguous(), "expert bank must be [E, N/16, K/64, 32, 4]");
+  TORCH_CHECK(x.stride(1) == 1 && out.stride(1) == 1);
+  for (const Tensor* t : {&tile_expert, &tile_row0, &tile_rows, &n_tiles})
+    TORCH_CHECK(t->scalar_type() == at::kInt && t->is_contiguous() && t->is_cuda());
+  TORCH_CHECK(tile_row0.numel() == tile_expert.numel() && tile_rows.numel() == tile_expert.numel() && n_tiles.numel() == 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbFp4GemvParams p{};
+  p.qw = qw.data_ptr();
+  p.sc = sc.data_ptr();
+  p.x = x.data_ptr();
+  p.out = out.data_ptr();
+  p.M = (int)out.size(0);
+  p.N = (int)N;
+  p.K = (int)qw.size(2) * 64;
+  p.Kx = p.K;
+  TORCH_CHECK(x.size(1) >= p.K, "grouped kernel needs rows of the padded width");
+  p.ldx = (int)x.stride(0);
+  p.ldo = (int)out.stride(0);
+  p.gs_shift = log2i(gs);
+  p.act = (int)act;
+  p.mode = 3;
+  p.expert_stride_q = qw.stride(0) / 4;
+  p.expert_stride_s = sc.stride(0) / 2;
+  p.tile_expert = tile_expert.data_ptr<int>();
+  p.tile_row0 = tile_row0.data_ptr<int>();
+  p.tile_rows = tile_rows.data_ptr<int>();
+  p.n_tiles = n_tiles.data_ptr<int>();
+  p.max_tiles = (int)tile_expert.numel();
+  if (row_order.has_value() && row_order->defined()) {
+    TORCH_CHECK(row_order->scalar_type() == at::kInt && row_order->is_contiguous() && row_order->numel() >= out.size(0));
+    p.row_order = row_order->data_ptr<int>();
+  }
+  p.order_div = (int)order_div;
+  if (weights.has_value() && weights->defined()) {
+    TORCH_CHECK(weights->scalar_type() == at::kFloat && weights->is_contiguous());
+    p.expert_w = weights->data_ptr<float>();
+  }
+  p.grouped_wpt = (int)wpt;
+  p.grouped_upi = (int)upi;
+  check(mmb_fp4_gemv(&p, cur_stream()), "fp4_grouped_gemv");
+}
+
 void bf16_gemv(const Tensor& x, const Tensor& w, Tensor out, const OptT& delta, const OptT& norm_w, double eps,
                const OptT& tpx) {
   check_bf16(x, "x");
@@ -732,6 +780,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("bf16_gemm", &bf16_gemm);
   m.def("fp4_gemv", &fp4_gemv);
   m.def("fp4_moe_gemv", &fp4_moe_gemv);
+  m.def("fp4_grouped_gemv", &fp4_grouped_gemv);
   m.def("bf16_gemv", &bf16_gemv);
   m.def("rmsnorm", &rmsnorm);
   m.def("silu_mul", &silu_mul);

@@ -32,7 +32,9 @@ __device__ __forceinline__ SegPtr seg_lookup(const MmbFp4GemvParams& p, int toke
   SegPtr r;
   int e = 0;
   r.mult = 1.f;
-  if (p.mode != 0) {
+  if (p.mode == 3) {
+    e = __ldg(p.tile_expert + sl);
+  } else if (p.mode != 0) {
     if (sl < p.topk) {
       e = __ldg(p.expert_ids + token * p.topk + sl);
       if (p.mode == 2) r.mult = __ldg(p.expert_w + token * p.topk + sl);
@@ -83,12 +85,17 @@ struct GemvLoc {
 
 struct GemvGeom {
   int gi, TG, tiles_per_slot, n_rt, cpw, c_begin, KC, NG, nseg, token, lane, g;
+  int upi, UB, grp, G, item0, item_stride;   // grouped mode: the CTA walks items of UB units, upi units per group
 };
 
 __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const GemvGeom& ge, int it, int v) {
   GemvLoc L;
-  const int u = ge.gi + it * ge.TG;
-  if (p.mode == 1) {
+  int u = ge.gi + it * ge.TG;
+  if (p.mode == 3) {
+    const int n = it / ge.upi;
+    u = (ge.item0 + n * ge.item_stride) * ge.UB + ge.grp + (it - n * ge.upi) * ge.G;
+  }
+  if (p.mode == 1 || p.mode == 3) {       // slot = MoE slot (mode 1) or tile-list entry (mode 3)
     L.slot = u / ge.tiles_per_slot;
     L.rt0 = u - L.slot * ge.tiles_per_slot;
   } else {
@@ -105,7 +112,7 @@ __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const 
     L.sidx = ci / ge.KC;
     L.cc = ci - L.sidx * ge.KC;
   }
-  const SegPtr sp = seg_lookup(p, ge.token, (p.mode == 1) ? L.slot : L.sidx);
+  const SegPtr sp = seg_lookup(p, ge.token, (p.mode == 1 || p.mode == 3) ? L.slot : L.sidx);
   L.mult = sp.mult;
   L.q = (sp.q != nullptr) ? sp.q + ((long long)rt * ge.KC + L.cc) * 32 + ge.lane : nullptr;
   L.s = (sp.s != nullptr) ? sp.s + (long long)rt * ge.NG * 8 + ge.g : nullptr;
@@ -121,7 +128,11 @@ __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const 
 // shared memory filled by cp.async, which runs on across tile and unit boundaries; the code of the loop exists
 // once (no unrolled register ring), which matters because these kernels are short enough to be bound by
 // instruction fetch.
-template <bool BIG_GROUPS, int NWARPS>
+//
+// GROUPED (mode 3) serves a batch routed through a mixture of experts: rows are sorted by expert and cut into
+// tiles of at most 8 rows by a device-built list.  A CTA walks work items - (tile, block of UB units) - stages
+// the tile's rows once per item, and its groups take `upi` units each; the weight rings run on across items.
+template <bool BIG_GROUPS, int NWARPS, bool GROUPED>
 __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt, const int mrows) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float red[2][NWARPS][2][128];
@@ -131,9 +142,13 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
 
-  const int S = (p.mode == 0) ? 1 : (p.topk + p.n_shared);
+  constexpr bool grouped = GROUPED;
+  const int S = (p.mode == 0 || grouped) ? 1 : (p.topk + p.n_shared);
   int m0, mt, token = 0;
-  if (p.mode == 0) {
+  if (grouped) {
+    m0 = 0;
+    mt = 8;                             // per unit: the tile's row count
+  } else if (p.mode == 0) {
     m0 = blockIdx.y * mrows;            // mrows <= 8 token rows per CTA (fewer when K is so large that 8 rows do not fit)
     mt = min(mrows, p.M - m0);
   } else {
@@ -145,7 +160,8 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
   const int Kv = nseg * p.K;   // virtual K
   const int XS = Kv + 32;      // smem row stride in halves: rows are 64 bytes apart mod 128 -> 16-byte loads of a
                                // quarter warp (2 rows x 4 lanes) touch distinct banks
-  const int rows_to_stage = (p.mode == 2) ? 1 : mt;     // mode 2 stages its S segments as one row of S * K
+  // rows of the staging area: mode 2 stages its S segments as one row of S * K; grouped mode restages up to 8 rows per item
+  const int rows_to_stage = (p.mode == 2) ? 1 : mt;
   __half* xs = reinterpret_cast<__half*>(smem_raw);
   const uint32_t ring_q = smem_u32(smem_raw) + (uint32_t)((((size_t)rows_to_stage * XS * 2) + 127) & ~(size_t)127) +
                           (uint32_t)warp * (kRing * 512) + (uint32_t)lane * 16;
@@ -162,13 +178,20 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
   ge.TG = gridDim.x * G;                                                 // groups in the grid (per blockIdx.y)
   const int grp = warp / wpt, wi = warp - grp * wpt;
   ge.gi = blockIdx.x * G + grp;
-  const int n_iter = (ge.gi < n_units) ? (n_units - ge.gi + ge.TG - 1) / ge.TG : 0;   // units of this group
+  // units of this group (grouped mode: known after the wait, the tile count lives on the device)
+  int n_iter = (!grouped && ge.gi < n_units) ? (n_units - ge.gi + ge.TG - 1) / ge.TG : 0;
   ge.KC = p.K >> 6;                        // chunks per segment
   ge.NG = p.K >> p.gs_shift;               // groups per segment
   ge.nseg = nseg;
   ge.token = token;
   ge.lane = lane;
   ge.g = g;
+  ge.G = G;
+  ge.grp = grp;
+  ge.upi = grouped ? mrows : 1;            // grouped launches pass the units per item and group in this argument
+  ge.UB = G * ge.upi;
+  ge.item0 = blockIdx.x;
+  ge.item_stride = gridDim.x;
   const int gs = 1 << p.gs_shift;
   {
     const int unit_chunks = (gs >= 64) ? (gs >> 6) : 1;
@@ -180,11 +203,11 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
   const int cpg_shift = BIG_GROUPS ? (p.gs_shift - 6) : 0;               // log2(chunks per quantization group)
 
   // ---- loader: one cp.async (16 bytes per lane) per chunk, plus the 4-byte scale word of the lane's row pair
-  int l_it = (cv > 0) ? 0 : n_iter, l_v = 0, l_cnt = 0, l_run = 0, l_cc = 0;
+  int l_it = 0, l_v = 0, l_cnt = 0, l_run = 0, l_cc = 0;
   const uint4* l_q = nullptr;
   const uint32_t* l_s = nullptr;
   auto issue = [&]() {
-    if (l_it < n_iter) {
+    if (cv > 0 && l_it < n_iter) {
       if (l_run == 0) {
         const GemvLoc L = gemv_locate(p, ge, l_it, l_v);
         l_q = L.q;
@@ -228,6 +251,10 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
     if (phase == 1) {
       pdl_launch_dependents();
       pdl_wait();
+      if (grouped) {
+        const int n_items = min(*p.n_tiles, p.max_tiles) * (ge.tiles_per_slot / ge.UB);
+        n_iter = ((int)blockIdx.x < n_items) ? ((n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * ge.upi : 0;
+      }
     }
     if ((p.mode == 0) == (phase == 0)) {
 #pragma unroll 1
@@ -256,7 +283,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
   // has every thread rewrite its own slots with bf16(v * rstd * w) as fp16.
   const int stage_k = (p.mode == 2) ? Kv : p.K;          // staged width of a row (columns beyond Kx are zero)
 #pragma unroll 1
-  for (int j = 0; j < rows_to_stage; ++j) {
+  for (int j = 0; j < (grouped ? 0 : rows_to_stage); ++j) {
     float ss = 0.f;
     __half* dst = xs + (long long)j * XS;
 #pragma unroll 1
@@ -326,7 +353,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
       if (lane == 0) ss_red[warp][j] = ss;
     }
   }
-  if (nw != nullptr) {
+  if (!grouped && nw != nullptr) {
     __syncthreads();
     if (tid < rows_to_stage) {
       float tot = 0.f;
@@ -375,6 +402,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
     const int gmask = gs - 1;
     const int cpg_mask = (1 << cpg_shift) - 1;
     const __half* xbase = xs + min(g, mt - 1) * ((p.mode == 2) ? 0 : XS) + t * 8;
+    const int k8 = p.K >> 3;
     const unsigned char* ring_q_gen = smem_raw + (ring_q - smem_u32(smem_raw));
     const unsigned char* ring_s_gen = smem_raw + (ring_s - smem_u32(smem_raw));
     int c_cnt = 0, c_run = 0, c_cc = 0, c_tsel = 0, c_slot = 0, c_rt0 = 0;
@@ -383,6 +411,34 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
     const uint32_t* c_s = nullptr;
 #pragma unroll 1
     for (int it = 0; it < n_iter; ++it) {
+      if (grouped && (it % ge.upi) == 0) {
+        // new item: every group is done with the previous rows; stage the rows of this item's tile (already
+        // normalized bf16, clamped into fp16, fragment order as above)
+        const int item = ge.item0 + (it / ge.upi) * ge.item_stride;
+        const int tj = (item * ge.UB) / ge.tiles_per_slot;
+        __syncthreads();
+        m0 = __ldg(p.tile_row0 + tj);
+        mt = min(__ldg(p.tile_rows + tj), 8);
+#pragma unroll 1
+        for (int idx = tid; idx < mt * k8; idx += kGemvThreads) {
+          const int r = idx / k8, k = (idx - r * k8) << 3;
+          int srow = m0 + r;
+          if (p.order_div > 0) {
+            const int pair = __ldg(p.row_order + srow);
+            srow = (pair >= 0) ? pair / p.order_div : -1;
+          }
+          const uint4 xv = (srow >= 0) ? *reinterpret_cast<const uint4*>(xg + (long long)srow * p.ldx + k) : make_uint4(0, 0, 0, 0);
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+          __half* blk = xs + (long long)r * XS + (k & ~31) + ((k >> 4) & 1) * 4 + ((k >> 3) & 1) * 2;
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt)
+            *reinterpret_cast<__half2*>(blk + tt * 8) =
+                __floats2half2_rn(fminf(fmaxf(__uint_as_float(xw[tt] << 16), -65504.f), 65504.f),
+                                  fminf(fmaxf(__uint_as_float(xw[tt] & 0xffff0000u), -65504.f), 65504.f));
+        }
+        __syncthreads();
+        xbase = xs + min(g, mt - 1) * XS + t * 8;
+      }
       float accg[4] = {0.f, 0.f, 0.f, 0.f};    // tile 0 of the unit
       float accu[4] = {0.f, 0.f, 0.f, 0.f};    // tile 1 (the up half when the SwiGLU epilogue is fused)
       float gacc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -477,6 +533,10 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
 #pragma unroll 4
         for (int w2 = 0; w2 < wpt; ++w2) v += red[buf][w0 + w2][0][o];
         const long long orow = (p.mode == 1) ? (long long)token * S + c_slot : (long long)(m0 + col);
+        if (grouped && p.expert_w != nullptr) {
+          const int pair = __ldg(p.row_order + orow);
+          v *= (pair >= 0) ? __ldg(p.expert_w + pair) : 0.f;
+        }
         const int n = c_rt0 * 16 + row;
         if (p.act == 1) {
           float u = 0.f;
@@ -634,8 +694,12 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
       (reinterpret_cast<uintptr_t>(p.norm_w) & 15) || (reinterpret_cast<uintptr_t>(p.resid_out) & 15))
     return (int)cudaErrorInvalidValue;
   if ((1 << p.gs_shift) < 16) return (int)cudaErrorInvalidValue;
-  const int S = (p.mode == 0) ? 1 : (p.topk + p.n_shared);
+  const int S = (p.mode == 0 || p.mode == 3) ? 1 : (p.topk + p.n_shared);
   if (S > kMaxSeg) return (int)cudaErrorInvalidValue;
+  if (p.mode == 3 && (p.norm_w != nullptr || p.delta != nullptr || p.tpx.in_buf != nullptr || p.tpx.out_peer_slots != nullptr ||
+                      p.tile_expert == nullptr || p.tile_row0 == nullptr || p.tile_rows == nullptr || p.n_tiles == nullptr ||
+                      p.max_tiles <= 0 || p.Kx != p.K || ((p.order_div > 0 || p.expert_w != nullptr) && p.row_order == nullptr)))
+    return (int)cudaErrorInvalidValue;
   if (p.mode == 2 && (p.norm_w != nullptr || p.delta != nullptr)) return (int)cudaErrorInvalidValue;
   const int n_rt = (p.N + 15) / 16;
   size_t smem;
@@ -649,6 +713,9 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
     const int mt = p.M < mrows ? p.M : mrows;
     smem = (size_t)mt * row_bytes;
     grid.y = (p.M + mrows - 1) / mrows;
+  } else if (p.mode == 3) {
+    smem = (size_t)8 * (p.K + 32) * 2;
+    grid.y = 1;
   } else if (p.mode == 1) {
     smem = (size_t)(p.K + 32) * 2;
     grid.y = p.M;
@@ -670,6 +737,25 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   const int warp_slots = 148 * 16 / (int)grid.y;
   int wpt = 16;
   while (wpt > 1 && ((long long)n_units * wpt > warp_slots || k_units < wpt || chunks < 2 * wpt)) wpt >>= 1;
+  if (p.mode == 3) {
+    // many units per CTA: a warp should own at least a ring's worth of chunks per unit; 8-warp CTAs, two per SM
+    const int tps = (p.act == 1) ? n_rt / 2 : n_rt;
+    const int unit_chunks = ((p.act == 1) ? 2 : 1) * chunks;
+    wpt = 8;
+    while (wpt > 1 && (unit_chunks < 2 * kRing * wpt || k_units < wpt)) wpt >>= 1;
+    while (wpt < 8 && tps % (8 / wpt) != 0) wpt <<= 1;      // the groups of a CTA share the units of an item evenly
+    if (p.grouped_wpt > 0) wpt = p.grouped_wpt;
+    if (wpt > 8 || (wpt & (wpt - 1)) || k_units < wpt) return (int)cudaErrorInvalidValue;
+    const int Gg = 8 / wpt;
+    if (tps % Gg != 0) return (int)cudaErrorInvalidValue;
+    // units per item and group: items of about a quarter of a wave each, so the tail stays short, but as many units
+    // per staging of the rows as that allows
+    int upi = 8;
+    while (upi > 1 && (tps % (Gg * upi) != 0 || (long long)p.max_tiles * tps / (Gg * upi) < 4 * 296)) upi >>= 1;
+    if (p.grouped_upi > 0) upi = p.grouped_upi;
+    if (tps % (Gg * upi) != 0) return (int)cudaErrorInvalidValue;
+    mrows = upi;
+  }
   const int nw = (wpt == 16) ? 16 : 8;
   const int G = nw / wpt;
   const int cta_units = (n_units + G - 1) / G;                   // CTAs needed for one unit per group
@@ -677,19 +763,27 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   if (cap < 1) cap = 1;
   const int passes = (cta_units + cap - 1) / cap;
   grid.x = (cta_units + passes - 1) / passes;
+  if (p.mode == 3) {
+    const long long items = (long long)p.max_tiles * (((p.act == 1) ? n_rt / 2 : n_rt) / (G * mrows));
+    grid.x = (unsigned)(items < 296 ? items : 296);
+  }
   // dynamic shared memory: the staged activation rows, then every warp's weight ring (512 + 128 bytes per slot)
   smem = ((smem + 127) & ~(size_t)127) + (size_t)nw * kRing * (512 + 128);
   if (smem > 180 * 1024) return (int)cudaErrorInvalidValue;
   int e;
-#define MMB_LAUNCH_GEMV(BG, NW)                                                                \
-  do {                                                                                         \
-    if ((e = set_smem(fp4_gemv_kernel<BG, NW>, smem, 34 * 1024))) return e;                              \
-    return launch(fp4_gemv_kernel<BG, NW>, grid, dim3(NW * 32), smem, stream, 1, p, wpt, mrows);       \
+#define MMB_LAUNCH_GEMV(BG, NW, GR)                                                                \
+  do {                                                                                             \
+    if ((e = set_smem(fp4_gemv_kernel<BG, NW, GR>, smem, 34 * 1024))) return e;                              \
+    return launch(fp4_gemv_kernel<BG, NW, GR>, grid, dim3(NW * 32), smem, stream, 1, p, wpt, mrows);       \
   } while (0)
-  if (big && nw == 8) MMB_LAUNCH_GEMV(true, 8);
-  if (big) MMB_LAUNCH_GEMV(true, 16);
-  if (nw == 8) MMB_LAUNCH_GEMV(false, 8);
-  MMB_LAUNCH_GEMV(false, 16);
+  if (p.mode == 3) {
+    if (big) MMB_LAUNCH_GEMV(true, 8, true);
+    MMB_LAUNCH_GEMV(false, 8, true);
+  }
+  if (big && nw == 8) MMB_LAUNCH_GEMV(true, 8, false);
+  if (big) MMB_LAUNCH_GEMV(true, 16, false);
+  if (nw == 8) MMB_LAUNCH_GEMV(false, 8, false);
+  MMB_LAUNCH_GEMV(false, 16, false);
 #undef MMB_LAUNCH_GEMV
 }
 

@@ -23,7 +23,9 @@ _FORCE_REF = os.environ.get("MMB200_FORCE_TORCH", "0") == "1"
 _native_ok = False
 GEMV_MAX_M = 32          # dense projections: at or below this many tokens the weight-streaming GEMV path is used
 ROUTER_GEMM_MIN_T = 64   # above this many tokens the gate logits come from the bf16 tcgen05 GEMM
-MOE_GEMV_MAX_T = 16      # MoE: per-(token, slot) streaming up to this many tokens, grouped tcgen05 GEMMs above
+MOE_GEMV_MAX_T = 16      # MoE: per-(token, slot) streaming up to this many tokens
+MOE_GROUPED_GEMV_MAX_T = 128   # ... expert-sorted 8-row tiles on the streaming kernel up to here, grouped tcgen05 GEMMs above
+GROUPED_GEMV_TUNE = [0, 0, 0, 0]   # (wpt, units per item) of the gate-up and the down launch; 0 = launcher's choice
 # Diagnostic switch: route every shape through the weight-streaming kernels (no tcgen05 GEMM).
 NO_TCGEN05 = os.environ.get("MMB200_NO_TCGEN05", "0") == "1"
 
@@ -423,6 +425,53 @@ def _build_tile_list(flat_ids: torch.Tensor, num_experts: int, token_tile: int):
     return order, e.to(torch.int32), row0.to(torch.int32), rows.to(torch.int32), n_tiles
 
 
+def _shared_experts(xin, gate_up, down, n_shared, shared_base):
+    shared = None
+    for j in range(n_shared):
+        e = shared_base + j
+        hs = linear(xin, gate_up.expert(e), act=1)
+        sj = linear(hs, down.expert(e))
+        shared = sj if shared is None else shared + sj
+    return shared
+
+
+def _grouped_gemv_ok(bank, act: int) -> bool:
+    """Whether the streaming kernel can split this bank's row tiles evenly over the warp groups of a CTA."""
+    k = bank.qtile.shape[2] * 64
+    k_units = k // max(bank.group_size, 64)
+    tps = bank.out_features // (32 if act else 16)
+    if bank.out_features % (32 if act else 16):
+        return False
+    return any(k_units >= w and tps % (8 // w) == 0 for w in (1, 2, 4, 8))
+
+
+def _moe_forward_grouped_gemv(xin, gate_up, down, ids, weights, n_shared, shared_base, out_add):
+    """Medium batches: still bound by weight bytes, but most experts are hit, so tokens are sorted by expert and
+    every expert's weights stream once for up to 8 of its rows per tile (gather and routing weight fused into the
+    two launches)."""
+    T, topk = ids.shape
+    n = T * topk
+    dev = xin.device
+    max_tiles = (n + 7) // 8 + gate_up.num_experts
+    order = torch.empty(n, dtype=torch.int32, device=dev)
+    inv = torch.empty(n, dtype=torch.int32, device=dev)
+    t_e = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    t_r0, t_rows = torch.empty_like(t_e), torch.empty_like(t_e)
+    n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    K.mmb200.moe_group(ids.reshape(-1).contiguous(), gate_up.num_experts, 8, order, inv, t_e, t_r0, t_rows, n_tiles)
+    h = torch.empty(n, gate_up.out_features // 2, dtype=torch.bfloat16, device=dev)
+    K.mmb200.fp4_grouped_gemv(xin, gate_up.qtile, gate_up.stile, h, gate_up.out_features, gate_up.group_size, 1,
+                              t_e, t_r0, t_rows, n_tiles, order, topk, None, GROUPED_GEMV_TUNE[0], GROUPED_GEMV_TUNE[1])
+    y = torch.empty(n, down.out_features, dtype=torch.bfloat16, device=dev)
+    K.mmb200.fp4_grouped_gemv(h, down.qtile, down.stile, y, down.out_features, down.group_size, 0,
+                              t_e, t_r0, t_rows, n_tiles, order, 0, weights.reshape(-1).contiguous(),
+                              GROUPED_GEMV_TUNE[2], GROUPED_GEMV_TUNE[3])
+    shared = _shared_experts(xin, gate_up, down, n_shared, shared_base)
+    out = torch.empty(T, down.out_features, dtype=torch.bfloat16, device=dev)
+    K.mmb200.moe_combine(y, inv, shared, None if out_add is None else out_add.contiguous(), out, topk)
+    return out
+
+
 def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *, n_shared=0, shared_base=0,
                 norm_w=None, eps=1e-6, out_add=None, token_tile=0, tpx=None):
     """Whole expert MLP: ``sum_s w_s * down_e(silu(gate_e(x)) * up_e(x))`` over routed + shared experts.
@@ -451,6 +500,10 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
     if norm_w is not None:
         xin = torch.empty_like(x)
         K.mmb200.rmsnorm(x, None, norm_w, xin, None, eps)
+    if (T <= MOE_GROUPED_GEMV_MAX_T and xin.shape[1] >= gate_up.qtile.shape[2] * 64
+            and gate_up.out_features // 2 == down.qtile.shape[2] * 64 and _grouped_gemv_ok(gate_up, 1)
+            and _grouped_gemv_ok(down, 0)):
+        return _moe_forward_grouped_gemv(xin, gate_up, down, ids, weights, n_shared, shared_base, out_add)
     st = gemm_status(x.device)
     E_routed = gate_up.num_experts - n_shared
     if not token_tile:      # smallest MMA N tile that holds the average expert load
@@ -479,12 +532,7 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
     rs = weights.reshape(-1).to(torch.float32).index_select(0, order.clamp_min(0).long()).contiguous()
     K.mmb200.fp4_gemm_grouped(h, down.qtile, down.stile, y, down.out_features, down.group_size,
                               t_e, t_r0, t_rows, n_tiles, token_tile, rs, st)
-    shared = None
-    for j in range(n_shared):
-        e = shared_base + j
-        hs = linear(xin, gate_up.expert(e), act=1)
-        sj = linear(hs, down.expert(e))
-        shared = sj if shared is None else shared + sj
+    shared = _shared_experts(xin, gate_up, down, n_shared, shared_base)
     out = torch.empty(T, down.out_features, dtype=torch.bfloat16, device=dev)
     # combine: un-sort, sum over the token's slots, add the shared expert and the residual input (one launch)
     K.mmb200.moe_combine(y, inv, shared, None if out_add is None else out_add.contiguous(), out, topk)

@@ -137,9 +137,13 @@ def main():
     ap.add_argument("--chain", type=int, default=0,
                     help="time a CUDA graph of this many dependent launches of the op on distinct weight sets "
                          "(in-graph cost per launch, as inside a decode step) instead of isolated cold launches")
+    ap.add_argument("--grouped-tune", default="",
+                    help="wpt,upi,wpt,upi of the expert-sorted streaming MoE launches (gate-up, down); 0 = launcher's choice")
     args = ap.parse_args()
     dev = torch.device("cuda")
     assert ops.native_available()
+    if args.grouped_tune:
+        ops.GROUPED_GEMV_TUNE[:] = [int(v) for v in args.grouped_tune.split(",")]
     cases = build_cases(dev, args.batch, args.ctx, variants=max(1, args.chain))
     names = list(cases) if args.op == "all" else args.op.split(",")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)

@@ -55,8 +55,9 @@ def test_bf16_gemm_batched_shared_x():
 
 
 @pytest.mark.parametrize("T,E,topk,ns", [(64, 8, 2, 1), (300, 64, 4, 1), (1000, 16, 8, 0)])
-def test_moe_grouped_gemm_path(T, E, topk, ns):
+def test_moe_grouped_gemm_path(T, E, topk, ns, monkeypatch):
     torch.manual_seed(T)
+    monkeypatch.setattr(ops, "MOE_GROUPED_GEMV_MAX_T", 0)      # 64 tokens would otherwise take the streaming kernel
     H, I = 256, 128
     gu = FP4ExpertBank.from_float(torch.randn(E + ns, 2 * I, H, device=DEV) * 0.05, 64)
     dn = FP4ExpertBank.from_float(torch.randn(E + ns, H, I, device=DEV) * 0.05, 64)
@@ -68,6 +69,29 @@ def test_moe_grouped_gemm_path(T, E, topk, ns):
     assert ops.check_status(DEV) == 0
     with ops.force_reference():
         y_ref = ops.moe_forward(x, gu, dn, ids, wts, n_shared=ns, shared_base=E, norm_w=nw)
+    _check(y, y_ref, tol=4e-2)
+
+
+@pytest.mark.parametrize("T,E,topk,ns,H,I,gs", [(17, 8, 2, 1, 256, 128, 64), (32, 64, 8, 1, 2048, 512, 128), (64, 16, 4, 0, 1024, 256, 32),
+                                                (128, 32, 8, 2, 512, 192, 64), (40, 64, 6, 1, 2048, 1536, 128)])
+def test_moe_grouped_streaming_path(T, E, topk, ns, H, I, gs):
+    """17 to 128 tokens: tokens sorted by expert, 8-row tiles on the weight-streaming kernel (gather and routing
+    weight fused)."""
+    torch.manual_seed(T)
+    gu = FP4ExpertBank.from_float(torch.randn(E + ns, 2 * I, H, device=DEV) * 0.05, gs)
+    dn = FP4ExpertBank.from_float(torch.randn(E + ns, H, I, device=DEV) * 0.05, gs)
+    x = torch.randn(T, H, device=DEV).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16)
+    # skewed routing: expert 0 gets far more than one tile of rows, some experts none
+    ids = torch.stack([torch.randperm(E, device=DEV)[:topk] for _ in range(T)]).to(torch.int32)
+    ids[: T // 2, 0] = 0
+    ids[: T // 2, 1:] = torch.stack([1 + torch.randperm(E - 1, device=DEV)[: topk - 1] for _ in range(T // 2)]).to(torch.int32)
+    wts = torch.rand(T, topk, device=DEV)
+    add = torch.randn(T, H, device=DEV).to(torch.bfloat16)
+    assert ops.MOE_GEMV_MAX_T < T <= ops.MOE_GROUPED_GEMV_MAX_T
+    y = ops.moe_forward(x, gu, dn, ids, wts, n_shared=ns, shared_base=E, norm_w=nw, out_add=add)
+    with ops.force_reference():
+        y_ref = ops.moe_forward(x, gu, dn, ids, wts, n_shared=ns, shared_base=E, norm_w=nw, out_add=add)
     _check(y, y_ref, tol=4e-2)
 
 
