@@ -7,6 +7,17 @@
 extern "C" {
 #endif
 
+// All-gather fused into the GEMM's activation load: token row t of x is written into this GPU's memory by rank
+// t / rows (peer stores of that rank's reduce kernel, see MmbRsFinishParams), which then publishes *step in flags[rank].
+// The TMA producer of every CTA waits (bounded; on expiry the CTA aborts and status gets a code) for the owners of its
+// token tile only, and token tiles are walked starting with this rank's own rows, so the transfer of the other
+// ranks' rows overlaps the tiles that are already complete.
+typedef struct {
+  const unsigned* flags;    // local [tp] or null
+  const unsigned* step;
+  int tp, rank, rows;
+} MmbAgWait;
+
 // out[M, N] = x[M, Kx] * W^T with W in the FP4 device tile layout (see api.h).
 // Grouped mode (MoE): tile_* describe, per token tile, which expert bank to use and which rows of
 // the (expert-sorted) x / out it covers; all three arrays and n_tiles live in device memory so the
@@ -39,6 +50,7 @@ typedef struct {
   unsigned* rs_counter;             // local CTA completion counter (0 before and after the launch)
   const unsigned* rs_step;          // device scalar: current step number
   int rs_tp, rs_rank, rs_rows;
+  MmbAgWait ag;                     // all-zero: x is complete when the kernel starts
 } MmbFp4GemmParams;
 
 int mmb_fp4_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
@@ -55,6 +67,7 @@ typedef struct {
   long long x_batch_stride, w_batch_stride, out_batch_stride;   // elements
   int ldx, ldw;             // row strides in elements (multiples of 8)
   int* status;
+  MmbAgWait ag;             // all-zero: x is complete when the kernel starts
 } MmbBf16GemmParams;
 
 int mmb_bf16_gemm(const MmbBf16GemmParams* p, cudaStream_t stream);
@@ -72,6 +85,13 @@ typedef struct {
   const unsigned* step;
   int* status;
   int tp, rank, rows, N, M;
+  // Optional fused residual add + RMSNorm of the owned rows (sequence-parallel form of the layer boundary): with
+  // norm_w set, h_new = bf16(resid + bf16(sum)) goes to every peer's ag_peer_bufs (the new residual stream) and
+  // bf16(h_new * rstd * norm_w) to every peer's ag2_peer_bufs (the input of the next projection).
+  const void* resid;                // bf16 [M, N] (only the owned rows are read) or null
+  const void* norm_w;               // bf16 [N] or null
+  void* const* ag2_peer_bufs;       // device array [tp] or null
+  float eps;
 } MmbRsFinishParams;
 int mmb_tp_rs_finish(const MmbRsFinishParams* p, cudaStream_t stream);
 // Wait (bounded) until all tp ranks published `step` in `flags`; on expiry writes a code to `status`.

@@ -24,11 +24,35 @@ namespace mmb {
 // mla_prep: grid (H * ceil(R / 32) + 1, ceil(T / 8)), 256 threads.  Each CTA of the first group owns 32
 // rows of one head's W_uk^T (4 per warp); the weight rows are requested before the query is staged so the
 // DRAM round trip overlaps it.  The last CTA writes the new latent into the paged cache.
+// Sums of 8 per-lane values over the 32 lanes of a warp in 9 shuffles: halve the value count while halving the lane
+// span (xor 16, 8, 4), then finish the 4-lane groups.  Lane 4 * j returns the sum of value j (other lanes: partial
+// garbage of no use).
+__device__ __forceinline__ float warp_sum8(const float (&acc)[8], int lane) {
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+  float v4[4], v2[2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float send = b4 ? acc[i] : acc[i + 4];
+    const float keep = b4 ? acc[i + 4] : acc[i];
+    v4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float send = b3 ? v4[i] : v4[i + 2];
+    const float keep = b3 ? v4[i + 2] : v4[i];
+    v2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+  float v1 = (b2 ? v2[1] : v2[0]) + __shfl_xor_sync(0xffffffffu, b2 ? v2[0] : v2[1], 4);
+  v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+  v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+  return v1;
+}
+
 constexpr int kPrepTok = 8;
 constexpr int kPrepRows = 32;
 __global__ void __launch_bounds__(256) mla_prep_kernel(const MmbMlaPrepParams p) {
   __shared__ float red[32];
-  extern __shared__ float sm[];   // [kPrepTok][max(dn, R + dr)]
+  extern __shared__ __align__(16) float sm[];   // [kPrepTok][max(256, R + dr)]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t0 = blockIdx.y * kPrepTok;
   const int nt = min(kPrepTok, p.T - t0);
@@ -50,35 +74,34 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const MmbMlaPrepParams p)
     }
     pdl_launch_dependents();
     pdl_wait();
+    // query rows in shared memory, 256 floats per token, element d at [(d / 4) % 2][d / 8][d % 4]: the eight values a
+    // lane multiplies with its weight word are two lane-contiguous float4 (no bank conflicts)
     if (!p.skip_absorb) {
-      for (int j = 0; j < nt; ++j)
-        for (int d = tid; d < p.dn; d += 256)
-          sm[j * p.dn + d] = __bfloat162float(q[(long long)(t0 + j) * p.ld_q + h * dq + d]);
+      for (int i = tid; i < kPrepTok * 256; i += 256) {
+        const int j = i >> 8, pos = i & 255;
+        const int d = ((pos >> 2) & 31) * 8 + (pos >> 7) * 4 + (pos & 3);
+        sm[i] = (j < nt && d < p.dn) ? __bfloat162float(q[(long long)(t0 + j) * p.ld_q + h * dq + d]) : 0.f;
+      }
     }
     __syncthreads();
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       if (p.skip_absorb || crow[r] >= p.R) continue;
-      const uint32_t ww[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+      const float wf[8] = {__uint_as_float(wv[r].x << 16), __uint_as_float(wv[r].x & 0xffff0000u),
+                           __uint_as_float(wv[r].y << 16), __uint_as_float(wv[r].y & 0xffff0000u),
+                           __uint_as_float(wv[r].z << 16), __uint_as_float(wv[r].z & 0xffff0000u),
+                           __uint_as_float(wv[r].w << 16), __uint_as_float(wv[r].w & 0xffff0000u)};
       float acc[kPrepTok];
 #pragma unroll
-      for (int j = 0; j < kPrepTok; ++j) acc[j] = 0.f;
-      if (lane * 8 < p.dn) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float w0 = __uint_as_float(ww[e] << 16), w1 = __uint_as_float(ww[e] & 0xffff0000u);
-#pragma unroll
-          for (int j = 0; j < kPrepTok; ++j)
-            if (j < nt) acc[j] = fmaf(w0, sm[j * p.dn + lane * 8 + 2 * e], fmaf(w1, sm[j * p.dn + lane * 8 + 2 * e + 1], acc[j]));
-        }
-      }
-#pragma unroll
       for (int j = 0; j < kPrepTok; ++j) {
-        if (j < nt) {
-          const float v = warp_sum(acc[j]);
-          if (lane == 0) qf[((long long)(t0 + j) * p.H + h) * dl + crow[r]] = __float2bfloat16(v);
-        }
+        const float4 x0 = *reinterpret_cast<const float4*>(sm + j * 256 + lane * 4);
+        const float4 x1 = *reinterpret_cast<const float4*>(sm + j * 256 + 128 + lane * 4);
+        acc[j] = fmaf(wf[0], x0.x, fmaf(wf[1], x0.y, fmaf(wf[2], x0.z, wf[3] * x0.w)));
+        acc[j] = fmaf(wf[4], x1.x, fmaf(wf[5], x1.y, fmaf(wf[6], x1.z, fmaf(wf[7], x1.w, acc[j]))));
       }
+      const float v1 = warp_sum8(acc, lane);
+      const int j = lane >> 2;
+      if ((lane & 3) == 0 && j < nt) qf[((long long)(t0 + j) * p.H + h) * dl + crow[r]] = __float2bfloat16(v1);
     }
     if (chunk == 0) {
       // RoPE on the rope part of q
@@ -624,13 +647,9 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
           }
         }
       }
-#pragma unroll
-      for (int j = 0; j < kMergeTok; ++j) {
-        if (j < nb) {
-          const float v = warp_sum(acc[j]);
-          if (lane == 0) out[((long long)(b0 + j) * Hq + h) * dvo + row] = __float2bfloat16(v);
-        }
-      }
+      static_assert(kMergeTok == 8, "warp_sum8 reduces eight tokens at once");
+      const float v = warp_sum8(acc, lane);
+      if ((lane & 3) == 0 && (lane >> 2) < nb) out[((long long)(b0 + (lane >> 2)) * Hq + h) * dvo + row] = __float2bfloat16(v);
     }
   }
 }
@@ -655,7 +674,7 @@ MMB_API int mmb_mla_prep(const MmbMlaPrepParams* pp, cudaStream_t stream) {
   const MmbMlaPrepParams& p = *pp;
   if (p.T <= 0) return 0;
   if ((p.dn & 7) || (p.dr & 1) || p.dn > 256) return (int)cudaErrorInvalidValue;
-  const int width = (p.dn > p.R + p.dr) ? p.dn : (p.R + p.dr);
+  const int width = (256 > p.R + p.dr) ? 256 : (p.R + p.dr);      // absorb CTAs: 256 floats per token; latent CTA: one row
   const size_t smem = (size_t)mmb::kPrepTok * width * 4;
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   dim3 grid(p.H * (p.skip_absorb ? 1 : (p.R + mmb::kPrepRows - 1) / mmb::kPrepRows) + 1, (p.T + mmb::kPrepTok - 1) / mmb::kPrepTok);

@@ -440,7 +440,28 @@ void tp_argmax(const Tensor& logits, Tensor out, int64_t vocab_offset, const Ten
 }
 
 // ---- tcgen05 GEMM (prefill / large M)
+// ag: CPU int64[5] = flags, step, tp, rank, rows per rank (all-gather fused into the load of x)
+MmbAgWait ag_from(const Tensor& ag) {
+  TORCH_CHECK(!ag.is_cuda() && ag.scalar_type() == at::kLong && ag.numel() == 5, "ag must be a CPU int64[5] tensor");
+  const int64_t* v = ag.data_ptr<int64_t>();
+  MmbAgWait a{};
+  a.flags = reinterpret_cast<const unsigned*>(v[0]);
+  a.step = reinterpret_cast<const unsigned*>(v[1]);
+  a.tp = (int)v[2];
+  a.rank = (int)v[3];
+  a.rows = (int)v[4];
+  TORCH_CHECK(a.tp >= 1 && a.rows > 0 && a.rank >= 0 && a.rank < a.tp);
+  return a;
+}
+
+void fp4_gemm_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status, const Tensor* ag);
 void fp4_gemm(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status) {
+  fp4_gemm_impl(x, qw, sc, out, N, gs, status, nullptr);
+}
+void fp4_gemm_ag(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status, const Tensor& ag) {
+  fp4_gemm_impl(x, qw, sc, out, N, gs, status, &ag);
+}
+void fp4_gemm_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status, const Tensor* ag) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && qw.is_contiguous() && sc.is_contiguous());
@@ -458,6 +479,7 @@ void fp4_gemm(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, i
   p.ldo = (int)out.stride(0);
   p.gs_shift = log2i(gs);
   p.status = status.data_ptr<int>();
+  if (ag != nullptr) p.ag = ag_from(*ag);
   check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm");
 }
 
@@ -492,8 +514,15 @@ void fp4_gemm_rs(const Tensor& x, const Tensor& qw, const Tensor& sc, int64_t N,
   check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm_rs");
 }
 
-// desc: CPU int64[12] = in_buf, in_flags, ag_peer_bufs, ag_peer_flags, counter, step, status, tp, rank, rows, N, M
-void tp_rs_finish(const Tensor& desc) {
+// desc: CPU int64[12] = in_buf, in_flags, ag_peer_bufs, ag_peer_flags, counter, step, status, tp, rank, rows, N, M;
+// with resid / norm_w the owned rows get the residual add and the RMSNorm, and the normalized rows go to the
+// second gathered buffer (ag2: device address of the peer table).
+void tp_rs_finish_impl(const Tensor& desc, const OptT& resid, const OptT& norm_w, int64_t ag2, double eps);
+void tp_rs_finish(const Tensor& desc) { tp_rs_finish_impl(desc, c10::nullopt, c10::nullopt, 0, 0.0); }
+void tp_rs_finish_norm(const Tensor& desc, const OptT& resid, const Tensor& norm_w, int64_t ag2, double eps) {
+  tp_rs_finish_impl(desc, resid, norm_w, ag2, eps);
+}
+void tp_rs_finish_impl(const Tensor& desc, const OptT& resid, const OptT& norm_w, int64_t ag2, double eps) {
   TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kLong && desc.numel() == 12);
   const int64_t* v = desc.data_ptr<int64_t>();
   MmbRsFinishParams p{};
@@ -509,6 +538,18 @@ void tp_rs_finish(const Tensor& desc) {
   p.rows = (int)v[9];
   p.N = (int)v[10];
   p.M = (int)v[11];
+  if (resid.has_value() && resid->defined()) {
+    check_bf16(*resid, "resid");
+    TORCH_CHECK(resid->is_contiguous() && resid->dim() == 2 && resid->size(0) >= p.M && resid->size(1) == p.N);
+    p.resid = resid->data_ptr();
+  }
+  if (norm_w.has_value() && norm_w->defined()) {
+    check_bf16(*norm_w, "norm_w");
+    TORCH_CHECK(norm_w->is_contiguous() && norm_w->numel() == p.N && ag2 != 0);
+    p.norm_w = norm_w->data_ptr();
+    p.ag2_peer_bufs = reinterpret_cast<void* const*>(ag2);
+    p.eps = (float)eps;
+  }
   check(mmb_tp_rs_finish(&p, cur_stream()), "tp_rs_finish");
 }
 
@@ -559,7 +600,13 @@ void fp4_gemm_grouped(const Tensor& x, const Tensor& qw, const Tensor& sc, Tenso
   check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm_grouped");
 }
 
-void bf16_gemm(const Tensor& x, const Tensor& w, Tensor out, Tensor status) {
+void bf16_gemm_impl(const Tensor& x, const Tensor& w, Tensor out, Tensor status, const Tensor* ag);
+void bf16_gemm(const Tensor& x, const Tensor& w, Tensor out, Tensor status) { bf16_gemm_impl(x, w, out, status, nullptr); }
+void bf16_gemm_ag(const Tensor& x, const Tensor& w, Tensor out, Tensor status, const Tensor& ag) {
+  TORCH_CHECK(out.dim() == 2, "the fused all-gather covers unbatched problems");
+  bf16_gemm_impl(x, w, out, status, &ag);
+}
+void bf16_gemm_impl(const Tensor& x, const Tensor& w, Tensor out, Tensor status, const Tensor* ag) {
   // x [B?, M, K], w [B?, N, K] -> out [B?, M, N]; 2-D operands are shared across the batch
   check_bf16(x, "x");
   check_bf16(w, "w");
@@ -581,6 +628,7 @@ void bf16_gemm(const Tensor& x, const Tensor& w, Tensor out, Tensor status) {
   p.w_batch_stride = w.dim() == 3 ? w.stride(0) : 0;
   p.out_batch_stride = out.dim() == 3 ? out.stride(0) : 0;
   p.status = status.data_ptr<int>();
+  if (ag != nullptr) p.ag = ag_from(*ag);
   check(mmb_bf16_gemm(&p, cur_stream()), "bf16_gemm");
 }
 
@@ -799,6 +847,9 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("fp4_gemm", &fp4_gemm);
   m.def("fp4_gemm_rs", &fp4_gemm_rs);
   m.def("tp_rs_finish", &tp_rs_finish);
+  m.def("tp_rs_finish_norm", &tp_rs_finish_norm);
+  m.def("fp4_gemm_ag", &fp4_gemm_ag);
+  m.def("bf16_gemm_ag", &bf16_gemm_ag);
   m.def("tp_wait", &tp_wait);
   m.def("hadamard", &hadamard);
   m.def("trellis_dequant", &trellis_dequant);

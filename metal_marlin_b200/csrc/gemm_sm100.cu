@@ -129,7 +129,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   const int M = WFMT == 0 ? p.M : pb.M, N = WFMT == 0 ? p.N : pb.N, K = WFMT == 0 ? p.K : pb.K;
   int* status = WFMT == 0 ? p.status : pb.status;
   const int n0 = blockIdx.x * kTileRows;
-  int tok0 = blockIdx.y * TN, tok_rows = TN, expert = 0;
+  const MmbAgWait& ag = WFMT == 0 ? p.ag : pb.ag;
+  int tile_y = blockIdx.y;
+  if (ag.flags != nullptr)      // all-gather fused into the load of x: start with the token tiles of this rank's own rows
+    tile_y = (int)((blockIdx.y + (unsigned)((ag.rank * ag.rows) / TN)) % gridDim.y);
+  int tok0 = tile_y * TN, tok_rows = TN, expert = 0;
   const int batch = blockIdx.z;
   if (WFMT == 0 && p.tile_expert != nullptr) {
     if ((int)blockIdx.y >= *p.n_tiles) return;
@@ -163,7 +167,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int i = 0; i < KB; ++i) {
+      bool x_ready = true;
+      if (ag.flags != nullptr) {
+        // rows tok0 .. tok0 + TN - 1 arrive from their owners by peer stores; wait (bounded) for those ranks only
+        const unsigned want = *ag.step;
+        const int last_row = min(tok0 + TN, M) - 1;
+        const int r_hi = min(last_row / ag.rows, ag.tp - 1);
+        for (int r = tok0 / ag.rows; r <= r_hi && x_ready; ++r) {
+          const unsigned* f = ag.flags + r;
+          if (ld_acquire_sys(f) >= want) continue;
+          const unsigned long long t0 = tp_now_ns();
+          unsigned spins = 0;
+          while (ld_acquire_sys(f) < want) {
+            if ((++spins & 63u) == 0u && tp_now_ns() - t0 > kTpWaitNs) {
+              x_ready = false;
+              break;
+            }
+          }
+        }
+        if (!x_ready) {
+          if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 110);
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");      // the rows are read through the async proxy (TMA)
+      }
+      for (int i = 0; i < KB && x_ready; ++i) {
         const int s = i % Cfg::kStages;
         const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
         if (!mbar_wait(&ps->empty[s], ph ^ 1u, abort_flag)) {
@@ -431,6 +458,7 @@ MMB_API int mmb_fp4_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
   if (p.M <= 0 || p.N <= 0) return 0;
   if (p.K % 64 != 0 || p.Kx % 8 != 0 || p.Kx > p.K || p.act != 0) return (int)cudaErrorInvalidValue;
   const bool grouped = p.tile_expert != nullptr;
+  if (p.ag.flags != nullptr && (grouped || p.ag.step == nullptr || p.ag.rows <= 0 || p.ag.tp < 1)) return (int)cudaErrorInvalidValue;
   const int TN = pick_tn(grouped ? (p.token_tile ? p.token_tile : 128) : p.M, p.token_tile);
   CUtensorMap mx;
   int e = make_tmap_2d(&mx, p.x, p.Kx, p.M, p.Kx, TN);
@@ -451,6 +479,7 @@ MMB_API int mmb_bf16_gemm(const MmbBf16GemmParams* pp, cudaStream_t stream) {
   if (pb.M <= 0 || pb.N <= 0) return 0;
   if (pb.K % 64 != 0 || pb.ldx % 8 != 0 || pb.ldw % 8 != 0) return (int)cudaErrorInvalidValue;
   const int nb = pb.batch > 0 ? pb.batch : 1;
+  if (pb.ag.flags != nullptr && (nb != 1 || pb.ag.step == nullptr || pb.ag.rows <= 0 || pb.ag.tp < 1)) return (int)cudaErrorInvalidValue;
   const int TN = pick_tn(pb.M, 0);
   CUtensorMap mx, mw;
   int e = make_tmap(&mx, pb.x, pb.K, pb.M, pb.x_batch_stride ? nb : 1, pb.ldx, pb.x_batch_stride, TN);

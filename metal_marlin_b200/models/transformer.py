@@ -182,6 +182,18 @@ class Transformer:
             return self.tp.consume(d)
         return {"delta": d}
 
+    def _norm_linear(self, h, d, W, norm_w, **kw):
+        """``W(norm(h + d))`` and the new residual stream.  When ``d`` is a row-parallel projection whose partials sit
+        with the row owners, the add and the norm run there on the owned rows only and the GEMM gathers while it
+        loads (see ``parallel/tp.py``)."""
+        eps = self.cfg.rms_norm_eps
+        if self.tp is not None and getattr(d, "pending_rs", False):
+            g = self.tp.finish_norm(d, h, norm_w, eps)
+            return ops.linear(g.x, W, ag_wait=g, **kw), g.h
+        new_h = torch.empty_like(h) if d is not None else None
+        y = ops.linear(h, W, norm_w=norm_w, eps=eps, resid_out=new_h, **kw, **self._dargs(d))
+        return y, (h if new_h is None else new_h)
+
     def _row_parallel(self, x, W, site: int):
         if self.tp is not None:
             return self.tp.row_parallel(x, W, site)
@@ -192,11 +204,7 @@ class Transformer:
         cfg = self.cfg
         Hq, Hk, D = self.n_heads_local, self.n_kv_heads_local, cfg.dh
         T = h.shape[0]
-        new_h = torch.empty_like(h) if d is not None else None
-        qkv = ops.linear(h, L.qkv, norm_w=L.input_norm, eps=cfg.rms_norm_eps, resid_out=new_h, bias=L.qkv_bias,
-                         **self._dargs(d))
-        if new_h is not None:
-            h = new_h
+        qkv, h = self._norm_linear(h, d, L.qkv, L.input_norm, bias=L.qkv_bias)
         q = qkv[:, : Hq * D]
         k = qkv[:, Hq * D: (Hq + Hk) * D]
         v = qkv[:, (Hq + Hk) * D:]
@@ -255,10 +263,7 @@ class Transformer:
         cfg = self.cfg
         H, dn, dr, dv, R = self.n_heads_local, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         T = h.shape[0]
-        new_h = torch.empty_like(h) if d is not None else None
-        a = ops.linear(h, L.qa_kva, norm_w=L.input_norm, eps=cfg.rms_norm_eps, resid_out=new_h, **self._dargs(d))
-        if new_h is not None:
-            h = new_h
+        a, h = self._norm_linear(h, d, L.qa_kva, L.input_norm)
         if L.q_b is not None:
             ql = cfg.q_lora_rank
             q = ops.linear(a[:, :ql], L.q_b, norm_w=L.q_a_norm, eps=cfg.rms_norm_eps)
@@ -340,18 +345,23 @@ class Transformer:
     # ------------------------------------------------------------------ MLP blocks
     def _mlp_dense(self, L: LayerWeights, li: int, h, d):
         cfg = self.cfg
-        new_h = torch.empty_like(h)
-        x = ops.linear(h, L.gate_up, norm_w=L.post_norm, eps=cfg.rms_norm_eps, resid_out=new_h, act=1, **self._dargs(d))
+        x, new_h = self._norm_linear(h, d, L.gate_up, L.post_norm, act=1)
         return new_h, self._row_parallel(x, L.down, 2 * li + 1)
 
     def _mlp_moe(self, L: LayerWeights, li: int, h, d, counts=None):
         cfg = self.cfg
+        rkw = dict(bias=L.router_bias, topk=cfg.num_experts_per_tok, scoring=1 if cfg.scoring_func == "sigmoid" else 0,
+                   renorm=cfg.norm_topk_prob, routed_scale=cfg.routed_scaling_factor, n_group=cfg.n_group,
+                   topk_group=cfg.topk_group, counts=counts)
+        if self.tp is not None and getattr(d, "pending_rs", False):
+            # sequence-parallel boundary: add + norm on the owned rows inside the reduce kernel; the gate GEMM gathers
+            g = self.tp.finish_norm(d, h, L.post_norm, cfg.rms_norm_eps)
+            ids, wts = ops.moe_router(g.x, L.router_w, ag_wait=g, **rkw)
+            if self.routing_hook is not None:
+                self.routing_hook(li, ids, None)
+            return g.h, self.tp.moe_row_parallel(g.x, {}, L, ids, wts, cfg, 2 * li + 1)
         new_h = torch.empty_like(h)
-        ids, wts = ops.moe_router(h, L.router_w, norm_w=L.post_norm, eps=cfg.rms_norm_eps, resid_out=new_h, **self._dargs(d),
-                                  bias=L.router_bias, topk=cfg.num_experts_per_tok,
-                                  scoring=1 if cfg.scoring_func == "sigmoid" else 0, renorm=cfg.norm_topk_prob,
-                                  routed_scale=cfg.routed_scaling_factor, n_group=cfg.n_group, topk_group=cfg.topk_group,
-                                  counts=counts)
+        ids, wts = ops.moe_router(h, L.router_w, norm_w=L.post_norm, eps=cfg.rms_norm_eps, resid_out=new_h, **self._dargs(d), **rkw)
         if self.routing_hook is not None:
             self.routing_hook(li, ids, None)       # analysis tools (expert-usage profiler); forces no sync by itself
         if self.tp is not None:
@@ -378,6 +388,8 @@ class Transformer:
                 h, d = self._mlp_moe(L, li, h, d)
             else:
                 h, d = self._mlp_dense(L, li, h, d)
+        if getattr(d, "pending_rs", False):     # callers get a tensor (or a decode-path handle)
+            d = self.tp.finish_plain(d)
         return h, d
 
     def logits(self, h, d, rows: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -128,9 +128,18 @@ def rmsnorm(x, w, eps=1e-6, *, delta=None, resid_out=None, out=None):
 
 
 def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bias=None, out_add=None,
-           out=None, token_tile=0, tpx=None):
+           out=None, token_tile=0, tpx=None, ag_wait=None):
     """``out = epilogue( prologue(x) @ dequant(W)^T )``; prologue = optional residual add + RMSNorm,
-    epilogue = optional bias, SwiGLU over the two row halves (``act=1``), residual add."""
+    epilogue = optional bias, SwiGLU over the two row halves (``act=1``), residual add.
+
+    ``ag_wait``: ``x`` is a gathered buffer whose rows are still arriving from the tensor-parallel peers; the GEMM
+    waits per token tile for the owners of the rows (an object with ``.wait`` descriptor and ``.ensure()``)."""
+    if ag_wait is not None:
+        direct = (delta is None and norm_w is None and _use_native(x) and not getattr(W, "is_generic", False) and _capture is None
+                  and x.shape[0] > GEMV_MAX_M and not NO_TCGEN05 and x.is_contiguous() and x.shape[1] == W.in_features)
+        if not direct:
+            ag_wait.ensure()
+            ag_wait = None
     if getattr(W, "is_generic", False):
         from . import generic
         return generic.linear(x, W, delta=delta, norm_w=norm_w, eps=eps, resid_out=resid_out, act=act, bias=bias,
@@ -166,7 +175,10 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
     elif not xin.is_contiguous() or xin.shape[1] != W.in_features:
         xin = xin[:, : W.in_features].contiguous()
     y = out if act == 0 else torch.empty(M, W.out_features, dtype=torch.bfloat16, device=x.device)
-    K.mmb200.fp4_gemm(xin, W.qtile, W.stile, y, W.out_features, W.group_size, gemm_status(x.device))
+    if ag_wait is not None:
+        K.mmb200.fp4_gemm_ag(xin, W.qtile, W.stile, y, W.out_features, W.group_size, gemm_status(x.device), ag_wait.wait)
+    else:
+        K.mmb200.fp4_gemm(xin, W.qtile, W.stile, y, W.out_features, W.group_size, gemm_status(x.device))
     if bias is not None:
         y += bias
     if act == 1:
@@ -285,7 +297,13 @@ def paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, *, Hq, Hkv, dqk, 
 
 def moe_router(x, w, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, bias=None, topk=4, scoring=0, renorm=True,
                routed_scale=1.0, n_group=1, topk_group=1, ids=None, weights=None, logits_out=None, counts=None,
-               tpx=None):
+               tpx=None, ag_wait=None):
+    if ag_wait is not None:
+        direct = (_use_native(x) and x.shape[0] > ROUTER_GEMM_MIN_T and tpx is None and w.shape[1] % 64 == 0 and x.is_contiguous()
+                  and norm_w is None and delta is None)
+        if not direct:
+            ag_wait.ensure()
+            ag_wait = None
     if not _use_native(x):
         i, wt, lg = ref.moe_router(x, w, delta=delta, norm_w=norm_w, eps=eps, resid_out=resid_out, bias=bias, topk=topk,
                                    scoring=scoring, renorm=renorm, routed_scale=routed_scale, n_group=n_group,
@@ -315,7 +333,10 @@ def moe_router(x, w, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, bias=
         else:
             xin = x
         lg = logits_out if logits_out is not None else torch.empty(T, w.shape[0], dtype=torch.float32, device=x.device)
-        K.mmb200.bf16_gemm(xin, w, lg, gemm_status(x.device))
+        if ag_wait is not None:      # gathered rows still arriving: the GEMM waits per token tile
+            K.mmb200.bf16_gemm_ag(xin, w, lg, gemm_status(x.device), ag_wait.wait)
+        else:
+            K.mmb200.bf16_gemm(xin, w, lg, gemm_status(x.device))
         K.mmb200.moe_select(lg, bias, ids, weights, counts, topk, scoring, renorm, routed_scale, n_group, topk_group)
         return ids, weights
     K.mmb200.moe_router(x, w, delta, norm_w, resid_out, bias, ids, weights, logits_out, counts, topk, eps, scoring,

@@ -11,7 +11,12 @@ Two ways to combine the row-parallel partial sums:
   buffer over NVLink and the next kernel sums the tp slots while staging its input (``csrc/tp_comm.cuh``);
   no collective kernel is launched at all.  The LM head is vocabulary-parallel with an in-kernel exchange of
   (max, argmax) pairs.
-* ``nccl`` (prefill / large batches and the baseline): ``torch.distributed.all_reduce`` on the partial.
+* prefill (33 .. 8192 tokens): GEMM -> reduce-scatter -> all-gather -> GEMM without a collective call.  The tcgen05
+  GEMM's epilogue scatters fp32 partials to the owners of the token rows; the owners' reduce kernel adds the
+  residual, applies the next RMSNorm to its rows only (sequence-parallel layer boundary) and stores residual and
+  normalized rows into every peer's gathered buffers; the next projection's GEMM waits per token tile, inside its
+  TMA producer, for the owners of that tile and starts with this rank's own rows, so the gather overlaps the math.
+* ``nccl`` (large batches and the baseline): ``torch.distributed.all_reduce`` on the partial.
 
 Parity: reference ``metal_marlin/distributed/tensor_parallel.py:61-276`` (``ParallelMode``, ``shard_tensor``,
 ``TensorParallelLinear.from_marlin_linear`` ``:341``, column ``:515`` / row ``:546`` forward, simulated
@@ -42,6 +47,29 @@ def even_split(n: int, parts: int, unit: int = 1) -> List[Tuple[int, int]]:
     out = [((r * u) // parts * unit, ((r + 1) * u) // parts * unit) for r in range(parts)]
     out[-1] = (out[-1][0], n)
     return out
+
+
+@dataclass
+class TPPendingRS:
+    """A row-parallel projection whose partials were scattered to the row owners by the GEMM epilogue; the reduce +
+    gather kernel has not run yet, so the consumer can have its residual add and RMSNorm fused into it."""
+    site: int
+    rows: int
+    pending_rs = True
+
+
+@dataclass
+class TPGathered:
+    """Gathered (normalized activation, new residual) of a prefill site; ``wait`` is the CPU descriptor for the GEMM
+    that consumes ``x`` first (per-tile wait inside its TMA producer)."""
+    x: torch.Tensor
+    h: torch.Tensor
+    wait: torch.Tensor
+    flags_desc: torch.Tensor
+
+    def ensure(self):
+        """Stand-alone bounded wait, for a first consumer that is not one of the GEMM kernels."""
+        ops.K.mmb200.tp_wait(self.flags_desc)
 
 
 @dataclass
@@ -99,7 +127,7 @@ class TPContext:
         tp, H, M = self.tp, self.hidden, FUSED_GEMM_MAX_TOKENS
         rows = (M + tp - 1) // tp
         rs_bytes = tp * rows * H * 4
-        ag_bytes = M * H * 2
+        ag_bytes = 2 * M * H * 2                                  # reduced rows / new residual, and normalized rows
         flag_bytes = self.n_sites * 2 * tp * 4                   # [site][rs | ag][tp]: flags are per site, buffers ping-pong
         buf = SymmetricBuffer(2 * (rs_bytes + ag_bytes) + flag_bytes, self.device, self.group)
         self._big = {"buf": buf, "rows_max": rows, "rs_bytes": rs_bytes, "ag_bytes": ag_bytes, "flags_off": 2 * (rs_bytes + ag_bytes),
@@ -122,7 +150,8 @@ class TPContext:
                 "rs_flags": torch.tensor([buf.peer_addr(r, f_rs + self.rank * 4) for r in range(tp)], dtype=torch.int64).to(dev),
                 "ag_bufs": torch.tensor([buf.peer_addr(r, ag_off) for r in range(tp)], dtype=torch.int64).to(dev),
                 "ag_flags": torch.tensor([buf.peer_addr(r, f_ag + self.rank * 4) for r in range(tp)], dtype=torch.int64).to(dev),
-                "rs_local": buf.local.data_ptr() + rs_off, "ag_local_off": ag_off,
+                "ag2_bufs": torch.tensor([buf.peer_addr(r, ag_off + big["ag_bytes"] // 2) for r in range(tp)], dtype=torch.int64).to(dev),
+                "rs_local": buf.local.data_ptr() + rs_off, "ag_local_off": ag_off, "ag2_local_off": ag_off + big["ag_bytes"] // 2,
                 "rs_flags_local": buf.local.data_ptr() + f_rs, "ag_flags_local": buf.local.data_ptr() + f_ag,
             }
             big["tabs"][site] = t
@@ -132,24 +161,55 @@ class TPContext:
         return (self.fused_ok and self.tp > 1 and ops.GEMV_MAX_M < n_tokens <= FUSED_GEMM_MAX_TOKENS and isinstance(W, ops.FP4Weight)
                 and W.out_features == self.hidden and W.in_features % 64 == 0)
 
-    def fused_gemm_all_reduce(self, x, W, site: int) -> torch.Tensor:
-        """``all_reduce(x @ W^T)`` in three launches and no collective call: the tcgen05 GEMM whose epilogue scatters
-        the fp32 partials to the owners of the token rows, the owners' reduce + all-gather-by-peer-stores, and a
-        bounded wait for the gathered rows.  Returns a bf16 ``[M, hidden]`` view of the gathered buffer."""
+    def fused_gemm_rs(self, x, W, site: int) -> TPPendingRS:
+        """First launch of the fused all-reduce: the tcgen05 GEMM whose epilogue scatters the fp32 partials to the
+        owners of the token rows."""
         big, t = self._big_tables(site)
-        M, H, tp = x.shape[0], self.hidden, self.tp
+        M, tp = x.shape[0], self.tp
         rows = (M + tp - 1) // tp
         cnt = big["counters"]
         rs = torch.tensor([t["rs_bufs"].data_ptr(), t["rs_flags"].data_ptr(), cnt[site * 2:].data_ptr(), self.step.data_ptr(), tp, self.rank, rows],
                           dtype=torch.int64)
         xin = x if x.is_contiguous() and x.shape[1] == W.in_features else x[:, : W.in_features].contiguous()
         ops.K.mmb200.fp4_gemm_rs(xin, W.qtile, W.stile, W.out_features, W.group_size, ops.gemm_status(x.device), rs)
+        return TPPendingRS(site, M)
+
+    def _finish_desc(self, site: int, M: int):
+        big, t = self._big_tables(site)
+        tp, H = self.tp, self.hidden
+        rows = (M + tp - 1) // tp
+        cnt = big["counters"]
         fin = torch.tensor([t["rs_local"], t["rs_flags_local"], t["ag_bufs"].data_ptr(), t["ag_flags"].data_ptr(), cnt[site * 2 + 1:].data_ptr(),
                             self.step.data_ptr(), self.status.data_ptr(), tp, self.rank, rows, H, M], dtype=torch.int64)
+        flags_desc = torch.tensor([t["ag_flags_local"], self.step.data_ptr(), self.status.data_ptr(), tp], dtype=torch.int64)
+        return big, t, rows, fin, flags_desc
+
+    def finish_plain(self, d: TPPendingRS) -> torch.Tensor:
+        """Reduce + all-gather by peer stores + a bounded wait; returns the all-reduced projection output as a bf16
+        ``[M, hidden]`` view of the gathered buffer."""
+        M, H = d.rows, self.hidden
+        big, t, rows, fin, flags_desc = self._finish_desc(d.site, M)
         ops.K.mmb200.tp_rs_finish(fin)
-        ops.K.mmb200.tp_wait(torch.tensor([t["ag_flags_local"], self.step.data_ptr(), self.status.data_ptr(), tp], dtype=torch.int64))
+        ops.K.mmb200.tp_wait(flags_desc)
         off = t["ag_local_off"]
         return big["buf"].local[off: off + M * H * 2].view(torch.bfloat16).view(M, H)
+
+    def finish_norm(self, d: TPPendingRS, h: torch.Tensor, norm_w: torch.Tensor, eps: float) -> TPGathered:
+        """Reduce with the residual add and the next RMSNorm fused on the owned rows; residual and normalized rows are
+        gathered by peer stores.  Nothing waits here: the first consumer does (see :class:`TPGathered`)."""
+        M, H = d.rows, self.hidden
+        big, t, rows, fin, flags_desc = self._finish_desc(d.site, M)
+        ops.K.mmb200.tp_rs_finish_norm(fin, h.contiguous(), norm_w, t["ag2_bufs"].data_ptr(), eps)
+        off, off2 = t["ag_local_off"], t["ag2_local_off"]
+        loc = big["buf"].local
+        wait = torch.tensor([t["ag_flags_local"], self.step.data_ptr(), self.tp, self.rank, rows], dtype=torch.int64)
+        return TPGathered(x=loc[off2: off2 + M * H * 2].view(torch.bfloat16).view(M, H),
+                          h=loc[off: off + M * H * 2].view(torch.bfloat16).view(M, H), wait=wait, flags_desc=flags_desc)
+
+    def fused_gemm_all_reduce(self, x, W, site: int) -> torch.Tensor:
+        """``all_reduce(x @ W^T)`` in three launches and no collective call (GEMM with scatter epilogue, reduce +
+        gather, bounded wait)."""
+        return self.finish_plain(self.fused_gemm_rs(x, W, site))
 
     # ------------------------------------------------------------------ descriptors (CPU int64[9])
     def _desc(self, kind: str, site: int, rows: int) -> torch.Tensor:
@@ -196,7 +256,7 @@ class TPContext:
             ops.linear(x, W, tpx=self._desc("out", site, M), out=self._dummy(M, W.out_features))
             return TPPartial(site, M)
         if self.use_fused_gemm(M, W):
-            return self.fused_gemm_all_reduce(x, W, site)
+            return self.fused_gemm_rs(x, W, site)
         y = ops.linear(x, W)
         return self.all_reduce(y)
 
@@ -224,6 +284,8 @@ class TPContext:
         """kwargs for the consuming op: either a plain ``delta`` tensor or the in-kernel exchange descriptor."""
         if isinstance(d, TPPartial):
             return {"delta": None, "tpx": self._desc("in", d.site, d.rows)}
+        if isinstance(d, TPPendingRS):
+            return {"delta": self.finish_plain(d)}
         return {"delta": d}
 
     def all_reduce(self, y: torch.Tensor) -> torch.Tensor:

@@ -26,3 +26,16 @@ def test_config_runner_and_reference_arm():
     assert r.returncode == 0 and "[5]" in r.stdout
     ref = _run(["bench.py", "--impl", "reference"])
     assert ref["impl"] == "reference" and "unavailable" in ref
+
+
+import pytest
+
+
+@pytest.mark.gpu
+def test_tp_gemm_chain_emulated_on_one_gpu():
+    """GEMM with scatter epilogue -> reduce with fused residual add + RMSNorm -> GEMM with the gather wait in its TMA
+    producer, ranks emulated as buffers of one GPU: numerics of every stage against fp32 PyTorch, status word clean."""
+    out = _run(["-m", "metal_marlin_b200.profiling.tp_gemm_bench", "--tokens", "300", "--out", "512", "--inner", "1024", "--tp", "2",
+                "--iters", "2"])
+    assert out["status"] == 0
+    assert out["rel_err"] < 2e-2 and out["rel_err_norm"] < 2e-2 and out["rel_err_ag_gemm"] < 2e-2
