@@ -573,12 +573,26 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
     const long long base = ((long long)(b0 + j) * Hq + h) * splits;
     if (worker) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      // the first four partials of this token were requested one token ago; request the next token's now, so their
+      // latency hides behind this token's barriers and remote stores
+      float4 cur[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cur[i] = pre[i];
+      if (j + 1 < nb) {
+        const long long nbase = base + (long long)Hq * splits;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int s = sg + i * groups;
+          pre[i] = (s < splits) ? __ldcg(reinterpret_cast<const float4*>(part_o + (nbase + s) * dv + d_lo + cq * 4))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
       for (int s0 = sg, round = 0; s0 < splits; s0 += 4 * groups, ++round) {
         float4 v[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int s = s0 + i * groups;
-          if (j == 0 && round == 0) v[i] = pre[i];
+          if (round == 0) v[i] = cur[i];
           else v[i] = (s < splits) ? __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * dv + d_lo + cq * 4))
                                    : make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -597,16 +611,22 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
       *reinterpret_cast<float4*>(red + sg * per + cq * 4) = acc;
     }
     __syncthreads();
-    for (int d = tid; d < d_hi - d_lo; d += 256) {
-      float a = 0.f;
-      for (int gI = 0; gI < groups; ++gI) a += red[gI * per + d];
+    for (int qd = tid; qd < quads; qd += 256) {     // four consecutive latent elements per thread: one 16-byte store per CTA of the cluster
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int gI = 0; gI < groups; ++gI) {
+        const float4 r4 = *reinterpret_cast<const float4*>(red + gI * per + qd * 4);
+        a.x += r4.x; a.y += r4.y; a.z += r4.z; a.w += r4.w;
+      }
       // round the merged latent to bf16 (an unfused pipeline would store it in bf16)
-      const float v = __bfloat162float(__float2bfloat16(a));
-      const int pd = j * DS + merge_perm(d_lo + d);
+      a.x = __bfloat162float(__float2bfloat16(a.x));
+      a.y = __bfloat162float(__float2bfloat16(a.y));
+      a.z = __bfloat162float(__float2bfloat16(a.z));
+      a.w = __bfloat162float(__float2bfloat16(a.w));
+      const int pd = j * DS + merge_perm(d_lo + qd * 4);      // d_lo and the quad start are multiples of 4: contiguous
       if (CL > 1) {
-        for (int c = 0; c < CL; ++c) cluster.map_shared_rank(o_s, c)[pd] = v;
+        for (int c = 0; c < CL; ++c) *reinterpret_cast<float4*>(cluster.map_shared_rank(o_s, c) + pd) = a;
       } else {
-        o_s[pd] = v;
+        *reinterpret_cast<float4*>(o_s + pd) = a;
       }
     }
     __syncthreads();
