@@ -54,15 +54,47 @@ def expand_block_mask(block_mask: torch.Tensor, block: int, seq_len: int, causal
     return m
 
 
+def _kernel_ok(q, k, v) -> bool:
+    """Whether the varlen prefill kernel serves these ``[B, H, S, D]`` operands (bf16 on a GPU, supported head size)."""
+    from . import ops
+    return (q.is_cuda and ops.native_available() and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+            and q.shape[-1] in ops.PREFILL_ATTN_DIMS and k.shape[-1] == q.shape[-1] == v.shape[-1] and q.shape[1] % k.shape[1] == 0)
+
+
+def _kernel_call(q, k, v, scale, **mask_kw):
+    """``[B, H, S, D]`` operands through ``ops.prefill_attention`` (token-major varlen layout, equal lengths)."""
+    from . import ops
+    B, H, S, D = q.shape
+    N = k.shape[2]
+    tm = lambda x: x.transpose(1, 2).reshape(B * x.shape[2], x.shape[1], D)
+    cu_q = torch.arange(B + 1, dtype=torch.int32, device=q.device) * S
+    cu_k = torch.arange(B + 1, dtype=torch.int32, device=q.device) * N
+    o = ops.prefill_attention(tm(q), tm(k), tm(v), cu_q, cu_k=cu_k, max_q=S, scale=scale, **mask_kw)
+    return o.view(B, S, H, D).transpose(1, 2)
+
+
 def block_sparse_attention(q, k, v, block_mask: torch.Tensor, block: int = 64, causal: bool = True, scale=None):
-    """``[B, H, S, D]`` attention restricted to the allowed blocks."""
+    """``[B, H, S, D]`` attention restricted to the allowed blocks.  On the GPU the prefill kernel skips key tiles whose
+    128-query x 64-key block is empty; masks finer than that ride along as an element mask."""
     S = q.shape[2]
+    if _kernel_ok(q, k, v) and k.shape[2] == S:
+        bm = block_mask.to(q.device).bool()
+        el = bm.repeat_interleave(block, 0).repeat_interleave(block, 1)[:S, :S]          # element level, before causal
+        nq, nk = (S + 127) // 128, (S + 63) // 64
+        pad = torch.zeros(nq * 128, nk * 64, dtype=torch.bool, device=q.device)
+        pad[:S, :S] = el
+        coarse = pad.view(nq, 128, nk, 64).any(3).any(1).to(torch.uint8).unsqueeze(0).contiguous()
+        exact = block % 128 == 0
+        tree = None if exact else el.to(torch.uint8).repeat(q.shape[0], 1).contiguous()
+        return _kernel_call(q, k, v, scale, causal=causal, block_mask=coarse, tree_mask=tree)
     m = expand_block_mask(block_mask.to(q.device), block, S, causal)
     return F.scaled_dot_product_attention(q, k, v, attn_mask=m, scale=scale)
 
 
 def sliding_window_attention(q, k, v, window: int, global_tokens: int = 0, scale=None):
     from .inference.long_context import sliding_window_mask
+    if _kernel_ok(q, k, v):
+        return _kernel_call(q, k, v, scale, causal=True, window=window, sinks=global_tokens)
     m = sliding_window_mask(q.shape[2], k.shape[2], window, global_tokens, q.device)
     if k.shape[1] != q.shape[1]:
         k, v = k.repeat_interleave(q.shape[1] // k.shape[1], 1), v.repeat_interleave(q.shape[1] // v.shape[1], 1)
@@ -87,9 +119,12 @@ def tree_attention(q, k_ctx, v_ctx, k_tree, v_tree, parents: Sequence[int], scal
     """Queries are the N tree nodes ``[B, H, N, D]``; keys are the committed context (fully visible) followed by
     the tree nodes (ancestor-visible)."""
     N, C = q.shape[2], k_ctx.shape[2]
-    mask = torch.cat([torch.ones(N, C, dtype=torch.bool), tree_mask_from_parents(parents)], 1).to(q.device)
     k = torch.cat([k_ctx, k_tree], 2)
     v = torch.cat([v_ctx, v_tree], 2)
+    if _kernel_ok(q, k, v):
+        tm = tree_mask_from_parents(parents).to(device=q.device, dtype=torch.uint8).repeat(q.shape[0], 1).contiguous()
+        return _kernel_call(q, k, v, scale, causal=False, tree_mask=tm)
+    mask = torch.cat([torch.ones(N, C, dtype=torch.bool), tree_mask_from_parents(parents)], 1).to(q.device)
     return F.scaled_dot_product_attention(q, k, v, attn_mask=mask, scale=scale)
 
 

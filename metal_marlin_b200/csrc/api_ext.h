@@ -61,7 +61,8 @@ int mmb_selective_scan_step(const void* x, const float* dt, const float* A, cons
 #ifdef __cplusplus
 extern "C" {
 #endif
-// Prefill (multi-query) attention with online softmax, causal / sliding-window masks, grouped KV heads and variable
+// Prefill (multi-query) attention with online softmax, causal / sliding-window (+ global tokens) / tree / block-sparse
+// masks, grouped KV heads and variable
 // sequence lengths.  Queries of sequence b are rows cu_q[b] .. cu_q[b + 1] of q and attend to that sequence's keys:
 // either contiguous rows cu_k[b] .. cu_k[b + 1] of k / v, or (cu_k == null) the paged pool addressed through
 // block_tables [B, max_blocks] with ctx_lens[b] keys.  The q rows are the LAST q_len positions of the kv_len keys.
@@ -81,6 +82,12 @@ typedef struct {
   float scale;
   int window;      // 0 = none; > 0: a query sees the last `window` keys up to its own position
   int causal;
+  // further mask modes (all optional, combined with the above by AND):
+  int sinks;                        // with a window: the first `sinks` keys stay visible to every query (global tokens)
+  const unsigned char* tree_mask;   // [total q rows][tree_ld]: query row i sees key q_off + j iff tree_mask[i][j] != 0; keys
+  int tree_ld;                      //   before q_off (the committed context) stay visible (speculative token trees)
+  const unsigned char* block_mask;  // [block_heads (1 or Hq)][ceil(max_q / 128)][n_kblocks]: 128-query x 64-key blocks
+  int block_heads, n_kblocks;       //   with a zero byte are skipped entirely (block-sparse attention)
 } MmbPrefillAttnParams;
 int mmb_prefill_attention(const MmbPrefillAttnParams* p, cudaStream_t stream);
 #ifdef __cplusplus

@@ -514,18 +514,21 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
   // values a lane multiplies with one 16-byte weight word into two lane-contiguous float4 (no bank conflicts).
   const int DS = (dv <= 256) ? 256 : 512;          // row stride of o_s
   float* wgt = o_s + kMergeTok * DS;               // [kMergeTok][splits]: exp(m_s - M) / L, 0 for empty splits
-  float* red = wgt + kMergeTok * splits;           // [groups][per] partial sums of one token
+  float* red = wgt + kMergeTok * splits;           // [tokens in flight][groups][per] partial sums
   const int per = (dv + CL - 1) / CL;
   const int d_lo = crank * per, d_hi = min(dv, d_lo + per);
   const int quads = (d_hi - d_lo + 3) >> 2;        // float4 columns of the slice (dv and per are multiples of 4)
-  int groups = 256 / quads;
-  if (groups < 1) groups = 1;
-  if (groups > splits) groups = splits;
-  const int cq = tid % quads, sg = tid / quads;
-  const bool worker = sg < groups;
+  // thread rows of `quads` threads: tok_par tokens are merged at once, each by `groups` rows that split the splits
+  const int pq = per >> 2;                         // thread-row width (the last CTA's slice may be shorter: quads <= pq)
+  const int TG = max(1, 256 / pq);
+  const int tok_par = min(nb, TG);
+  const int groups = max(1, min(splits, TG / tok_par));
+  const int cq = tid % pq, trow = tid / pq;
+  const int tj = trow % tok_par, sg = trow / tok_par;
+  const bool worker = trow < tok_par * groups && cq < quads;
   float4 pre[4];
   if (worker) {
-    const long long base = ((long long)b0 * Hq + h) * splits;
+    const long long base = ((long long)(b0 + tj) * Hq + h) * splits;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int s = sg + i * groups;
@@ -569,30 +572,17 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
   }
   __syncthreads();
   if (CL > 1) cluster_wait();
-  for (int j = 0; j < nb; ++j) {
-    const long long base = ((long long)(b0 + j) * Hq + h) * splits;
-    if (worker) {
+  for (int j0 = 0; j0 < nb; j0 += tok_par) {
+    const int j = j0 + tj;
+    if (worker && j < nb) {
+      const long long base = ((long long)(b0 + j) * Hq + h) * splits;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      // the first four partials of this token were requested one token ago; request the next token's now, so their
-      // latency hides behind this token's barriers and remote stores
-      float4 cur[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) cur[i] = pre[i];
-      if (j + 1 < nb) {
-        const long long nbase = base + (long long)Hq * splits;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int s = sg + i * groups;
-          pre[i] = (s < splits) ? __ldcg(reinterpret_cast<const float4*>(part_o + (nbase + s) * dv + d_lo + cq * 4))
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-      }
       for (int s0 = sg, round = 0; s0 < splits; s0 += 4 * groups, ++round) {
         float4 v[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int s = s0 + i * groups;
-          if (round == 0) v[i] = cur[i];
+          if (j0 == 0 && round == 0) v[i] = pre[i];
           else v[i] = (s < splits) ? __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * dv + d_lo + cq * 4))
                                    : make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -608,13 +598,16 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
           }
         }
       }
-      *reinterpret_cast<float4*>(red + sg * per + cq * 4) = acc;
+      *reinterpret_cast<float4*>(red + (tj * groups + sg) * per + cq * 4) = acc;
     }
     __syncthreads();
-    for (int qd = tid; qd < quads; qd += 256) {     // four consecutive latent elements per thread: one 16-byte store per CTA of the cluster
+    // four consecutive latent elements per thread: one 16-byte store per CTA of the cluster
+    for (int idx = tid; idx < tok_par * pq; idx += 256) {
+      const int t2 = idx / pq, qd = idx - t2 * pq;
+      if (j0 + t2 >= nb || qd >= quads) continue;
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int gI = 0; gI < groups; ++gI) {
-        const float4 r4 = *reinterpret_cast<const float4*>(red + gI * per + qd * 4);
+        const float4 r4 = *reinterpret_cast<const float4*>(red + (t2 * groups + gI) * per + qd * 4);
         a.x += r4.x; a.y += r4.y; a.z += r4.z; a.w += r4.w;
       }
       // round the merged latent to bf16 (an unfused pipeline would store it in bf16)
@@ -622,7 +615,7 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
       a.y = __bfloat162float(__float2bfloat16(a.y));
       a.z = __bfloat162float(__float2bfloat16(a.z));
       a.w = __bfloat162float(__float2bfloat16(a.w));
-      const int pd = j * DS + merge_perm(d_lo + qd * 4);      // d_lo and the quad start are multiples of 4: contiguous
+      const int pd = (j0 + t2) * DS + merge_perm(d_lo + qd * 4);      // d_lo and the quad start are multiples of 4: contiguous
       if (CL > 1) {
         for (int c = 0; c < CL; ++c) *reinterpret_cast<float4*>(cluster.map_shared_rank(o_s, c) + pd) = a;
       } else {
@@ -639,37 +632,49 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
         out[((long long)(b0 + j) * Hq + h) * dv + d] = __float2bfloat16(o_s[j * DS + merge_perm(d)]);
     return;
   }
+  // Up-projection: the warp's four rows against the eight tokens; every 16-byte pair of the merged latent is read once
+  // per token and used for all four rows.
   for (int slab = crank; slab * kMergeRows < dvo; slab += CL) {
+    const int row0 = slab * kMergeRows + warp * 4;
+    float acc[4][kMergeTok];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int row = slab * kMergeRows + warp * 4 + r;
-      if (row >= dvo) continue;
-      float acc[kMergeTok];
+    for (int r = 0; r < 4; ++r)
 #pragma unroll
-      for (int j = 0; j < kMergeTok; ++j) acc[j] = 0.f;
+      for (int j = 0; j < kMergeTok; ++j) acc[r][j] = 0.f;
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int d = u * 256 + lane * 8;
-        if (d < dv) {
-          const uint4 w4 = (slab == crank) ? wv[r][u] : ldg_stream(reinterpret_cast<const uint4*>(W + (long long)row * dv + d));
-          const float wf[8] = {__uint_as_float(w4.x << 16), __uint_as_float(w4.x & 0xffff0000u),
-                               __uint_as_float(w4.y << 16), __uint_as_float(w4.y & 0xffff0000u),
-                               __uint_as_float(w4.z << 16), __uint_as_float(w4.z & 0xffff0000u),
-                               __uint_as_float(w4.w << 16), __uint_as_float(w4.w & 0xffff0000u)};
+    for (int u = 0; u < 2; ++u) {
+      const int d = u * 256 + lane * 8;
+      if (d >= dv) continue;
+      float wf[4][8];
 #pragma unroll
-          for (int j = 0; j < kMergeTok; ++j) {
-            if (j < nb) {
-              const float4 x0 = *reinterpret_cast<const float4*>(o_s + j * DS + (u * 2) * 128 + lane * 4);
-              const float4 x1 = *reinterpret_cast<const float4*>(o_s + j * DS + (u * 2 + 1) * 128 + lane * 4);
-              acc[j] = fmaf(wf[0], x0.x, fmaf(wf[1], x0.y, fmaf(wf[2], x0.z, fmaf(wf[3], x0.w, acc[j]))));
-              acc[j] = fmaf(wf[4], x1.x, fmaf(wf[5], x1.y, fmaf(wf[6], x1.z, fmaf(wf[7], x1.w, acc[j]))));
-            }
+      for (int r = 0; r < 4; ++r) {
+        uint4 w4 = make_uint4(0, 0, 0, 0);
+        if (slab == crank) w4 = wv[r][u];
+        else if (row0 + r < dvo) w4 = ldg_stream(reinterpret_cast<const uint4*>(W + (long long)(row0 + r) * dv + d));
+        wf[r][0] = __uint_as_float(w4.x << 16); wf[r][1] = __uint_as_float(w4.x & 0xffff0000u);
+        wf[r][2] = __uint_as_float(w4.y << 16); wf[r][3] = __uint_as_float(w4.y & 0xffff0000u);
+        wf[r][4] = __uint_as_float(w4.z << 16); wf[r][5] = __uint_as_float(w4.z & 0xffff0000u);
+        wf[r][6] = __uint_as_float(w4.w << 16); wf[r][7] = __uint_as_float(w4.w & 0xffff0000u);
+      }
+#pragma unroll
+      for (int j = 0; j < kMergeTok; ++j) {
+        if (j < nb) {
+          const float4 x0 = *reinterpret_cast<const float4*>(o_s + j * DS + (u * 2) * 128 + lane * 4);
+          const float4 x1 = *reinterpret_cast<const float4*>(o_s + j * DS + (u * 2 + 1) * 128 + lane * 4);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            acc[r][j] = fmaf(wf[r][0], x0.x, fmaf(wf[r][1], x0.y, fmaf(wf[r][2], x0.z, fmaf(wf[r][3], x0.w, acc[r][j]))));
+            acc[r][j] = fmaf(wf[r][4], x1.x, fmaf(wf[r][5], x1.y, fmaf(wf[r][6], x1.z, fmaf(wf[r][7], x1.w, acc[r][j]))));
           }
         }
       }
-      static_assert(kMergeTok == 8, "warp_sum8 reduces eight tokens at once");
-      const float v = warp_sum8(acc, lane);
-      if ((lane & 3) == 0 && (lane >> 2) < nb) out[((long long)(b0 + (lane >> 2)) * Hq + h) * dvo + row] = __float2bfloat16(v);
+    }
+    static_assert(kMergeTok == 8, "warp_sum8 reduces eight tokens at once");
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float v = warp_sum8(acc[r], lane);
+      if (row0 + r < dvo && (lane & 3) == 0 && (lane >> 2) < nb)
+        out[((long long)(b0 + (lane >> 2)) * Hq + h) * dvo + row0 + r] = __float2bfloat16(v);
     }
   }
 }
@@ -729,11 +734,10 @@ MMB_API int mmb_decode_merge(const float* part_o, const float* part_ml, const vo
   // shared memory: merged latent [8][dv], split weights [8][splits], per-group partial sums [groups][dv / cl]
   const int per = (dv + cl - 1) / cl;
   if (per % 4 != 0 || splits < 1) return (int)cudaErrorInvalidValue;
-  int groups = 256 / (per / 4);
-  if (groups < 1) groups = 1;
-  if (groups > splits) groups = splits;
+  int trows = 256 / (per / 4);          // thread rows of the merge; the partial-sum area holds one slice per row
+  if (trows < 1) trows = 1;
   const int ds = (dv <= 256) ? 256 : 512;
-  const size_t smem = ((size_t)mmb::kMergeTok * ds + (size_t)mmb::kMergeTok * splits + (size_t)groups * per) * 4;
+  const size_t smem = ((size_t)mmb::kMergeTok * ds + (size_t)mmb::kMergeTok * splits + (size_t)trows * per) * 4;
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   dim3 grid(Hq * cl, (B + mmb::kMergeTok - 1) / mmb::kMergeTok);
   return mmb::launch(mmb::decode_merge_kernel, grid, dim3(256), smem, stream, cl, part_o, part_ml, (const bf16*)w_uv,

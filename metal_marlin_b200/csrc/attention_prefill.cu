@@ -59,8 +59,24 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const Mmb
   // key range of this query tile
   const int qpos_hi = q_off + min(q0 + kPfM, q_len) - 1;
   const int k_hi = p.causal ? min(kv_len, qpos_hi + 1) : kv_len;
-  const int k_lo = (p.window > 0) ? max(0, q_off + q0 - p.window + 1) : 0;
-  const int tile_lo = k_lo / kPfN, tile_hi = (k_hi + kPfN - 1) / kPfN;
+  const int k_lo_win = (p.window > 0) ? max(0, q_off + q0 - p.window + 1) : 0;
+  const int sinks = (p.window > 0) ? p.sinks : 0;
+  const int tile_lo = (sinks > 0) ? 0 : k_lo_win / kPfN, tile_hi = (k_hi + kPfN - 1) / kPfN;
+  const unsigned char* bmask = p.block_mask
+      ? p.block_mask + ((long long)(p.block_heads > 1 ? h : 0) * ((p.max_q + kPfM - 1) / kPfM) + blockIdx.x) * p.n_kblocks
+      : nullptr;
+  const unsigned char* tmask = p.tree_mask ? p.tree_mask + (long long)q_begin * p.tree_ld : nullptr;
+  // key tiles nobody in this query tile can see are skipped: block-sparse zeros, and the gap between the global tokens
+  // and the start of the window
+  auto next_tile = [&](int tl) {
+    while (tl < tile_hi) {
+      const bool in_gap = sinks > 0 && tl * kPfN >= sinks && (tl + 1) * kPfN <= k_lo_win;
+      const bool off = bmask != nullptr && (tl >= p.n_kblocks || bmask[tl] == 0);
+      if (!in_gap && !off) break;
+      ++tl;
+    }
+    return tl;
+  };
 
   auto load_kv = [&](int tile, int buf) {
     bf16* kd = Ks + buf * kPfN * LD;
@@ -79,7 +95,8 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const Mmb
     const int r = i / CH, c = i % CH;
     pf_cp16(Qs + r * LD + c * 8, qg + (long long)r * p.q_tok_stride + c * 8, q0 + r < q_len);
   }
-  if (tile_lo < tile_hi) load_kv(tile_lo, 0);
+  const int tile_first = next_tile(tile_lo);
+  if (tile_first < tile_hi) load_kv(tile_first, 0);
   pf_commit();
 
   float o[D / 8][4];
@@ -89,9 +106,10 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const Mmb
   const float sl2 = p.scale * 1.4426950408889634f;
   const int qrow0 = q0 + warp * 16 + g;        // this thread's rows: qrow0 and qrow0 + 8 (relative to the sequence's queries)
 
-  for (int tile = tile_lo; tile < tile_hi; ++tile) {
-    const int buf = (tile - tile_lo) & 1;
-    if (tile + 1 < tile_hi) load_kv(tile + 1, buf ^ 1);
+  int buf = 0;
+  for (int tile = tile_first, tile_next; tile < tile_hi; tile = tile_next, buf ^= 1) {
+    tile_next = next_tile(tile + 1);
+    if (tile_next < tile_hi) load_kv(tile_next, buf ^ 1);
     pf_commit();
     pf_wait<1>();
     __syncthreads();
@@ -116,7 +134,8 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const Mmb
     // ---- mask + online soft-max (rows g and g + 8)
     const int key0 = tile * kPfN;
     const bool need_mask = (key0 + kPfN > kv_len) || (p.causal && key0 + kPfN - 1 > q_off + q0 + warp * 16) ||
-                           (p.window > 0 && key0 < q_off + q0 + warp * 16 + 16 - p.window + 1);
+                           (p.window > 0 && key0 < q_off + q0 + warp * 16 + 16 - p.window + 1) ||
+                           (tmask != nullptr && key0 + kPfN > q_off);
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < kPfN / 8; ++n) {
@@ -126,7 +145,11 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const Mmb
         if (need_mask) {
           const int key = key0 + n * 8 + 2 * t + (e & 1);
           const int qpos = q_off + qrow0 + ((e >> 1) << 3);
-          const bool ok = key < kv_len && (!p.causal || key <= qpos) && (p.window <= 0 || key > qpos - p.window);
+          bool ok = key < kv_len && (!p.causal || key <= qpos) && (p.window <= 0 || key > qpos - p.window || key < sinks);
+          if (ok && tmask != nullptr && key >= q_off) {
+            const int qr = qpos - q_off;
+            ok = qr < q_len && tmask[(long long)qr * p.tree_ld + (key - q_off)] != 0;
+          }
           if (!ok) v = -INFINITY;
         }
         s[n][e] = v;

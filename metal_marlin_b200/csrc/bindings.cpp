@@ -745,7 +745,7 @@ void selective_scan_step(const Tensor& x, const Tensor& dt, const Tensor& A, con
 // k, v pools [slots, Hk, D] + block_tables + ctx_lens.
 void prefill_attention(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, const Tensor& cu_q, const OptT& cu_k,
                        const OptT& block_tables, const OptT& ctx_lens, int64_t block_size, int64_t max_q, double scale, int64_t window,
-                       bool causal) {
+                       bool causal, int64_t sinks, const OptT& tree_mask, const OptT& block_mask) {
   check_bf16(q, "q");
   check_bf16(k, "k");
   check_bf16(v, "v");
@@ -784,6 +784,20 @@ void prefill_attention(const Tensor& q, const Tensor& k, const Tensor& v, Tensor
   p.scale = (float)scale;
   p.window = (int)window;
   p.causal = causal ? 1 : 0;
+  p.sinks = (int)sinks;
+  if (tree_mask.has_value() && tree_mask->defined()) {
+    TORCH_CHECK(tree_mask->scalar_type() == at::kByte && tree_mask->dim() == 2 && tree_mask->is_contiguous() && tree_mask->is_cuda() &&
+                tree_mask->size(0) == q.size(0) && tree_mask->size(1) >= max_q);
+    p.tree_mask = tree_mask->data_ptr<unsigned char>();
+    p.tree_ld = (int)tree_mask->size(1);
+  }
+  if (block_mask.has_value() && block_mask->defined()) {
+    TORCH_CHECK(block_mask->scalar_type() == at::kByte && block_mask->dim() == 3 && block_mask->is_contiguous() && block_mask->is_cuda() &&
+                (block_mask->size(0) == 1 || block_mask->size(0) == q.size(1)) && block_mask->size(1) == (max_q + 127) / 128);
+    p.block_mask = block_mask->data_ptr<unsigned char>();
+    p.block_heads = (int)block_mask->size(0);
+    p.n_kblocks = (int)block_mask->size(2);
+  }
   check(mmb_prefill_attention(&p, cur_stream()), "prefill_attention");
 }
 

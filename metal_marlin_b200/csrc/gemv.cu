@@ -132,8 +132,16 @@ __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const 
 // GROUPED (mode 3) serves a batch routed through a mixture of experts: rows are sorted by expert and cut into
 // tiles of at most 8 rows by a device-built list.  A CTA walks work items - (tile, block of UB units) - stages
 // the tile's rows once per item, and its groups take `upi` units each; the weight rings run on across items.
-template <bool BIG_GROUPS, int NWARPS, bool GROUPED>
+//
+// GM selects the loop shape by quantization group size: 0 - groups below 64 (scale word fetched per k16 step), 1 - groups
+// of 64 (one 64-wide chunk per trip), 2 - groups of 128 and more (two chunks and one scale word per trip: the per-trip
+// bookkeeping of loader and consumer is paid once per 1 KB of weights, which matters because the fully loaded kernel
+// is bound by instruction issue, not by DRAM).
+template <int GM, int NWARPS, bool GROUPED>
 __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt, const int mrows) {
+  constexpr bool BIG_GROUPS = GM > 0;
+  constexpr int CPI = (GM == 2) ? 2 : 1;       // chunks per trip
+  constexpr int kRingIt = kRing / CPI;         // ring slots (one trip's weights each)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float red[2][NWARPS][2][128];
   __shared__ float ss_red[NWARPS][8];
@@ -215,15 +223,18 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
         l_cc = L.cc;
         l_run = L.run;
       }
-      const uint32_t slot = (uint32_t)l_cnt & (kRing - 1);
-      cp_async_16(ring_q + slot * 512, (l_q != nullptr) ? (const void*)l_q : p.qw, (l_q != nullptr) ? 16 : 0);
-      if (BIG_GROUPS)
+      const uint32_t slot = (uint32_t)l_cnt & (kRingIt - 1);
+#pragma unroll
+      for (int c = 0; c < CPI; ++c)
+        cp_async_16(ring_q + slot * (CPI * 512) + c * 512, (l_q != nullptr) ? (const void*)(l_q + c * 32) : p.qw, (l_q != nullptr) ? 16 : 0);
+      if (BIG_GROUPS)       // the chunks of a trip share their quantization group
         cp_async_4(ring_s + slot * 128, (l_s != nullptr) ? (const void*)(l_s + (l_cc >> cpg_shift) * 8) : p.sc,
                    (l_s != nullptr) ? 4 : 0);
-      if (l_q != nullptr) l_q += 32;
-      ++l_cc;
-      --l_run;
-      if (++l_v == cv) {
+      if (l_q != nullptr) l_q += 32 * CPI;
+      l_cc += CPI;
+      l_run -= CPI;
+      l_v += CPI;
+      if (l_v == cv) {
         l_v = 0;
         ++l_it;
       }
@@ -258,7 +269,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
     }
     if ((p.mode == 0) == (phase == 0)) {
 #pragma unroll 1
-      for (int i = 0; i < kRing; ++i) issue();
+      for (int i = 0; i < kRingIt; ++i) issue();
     }
   }
 
@@ -444,7 +455,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
       float gacc[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t s2 = 0;
 #pragma unroll 1
-      for (int v = 0; v < cv; ++v) {
+      for (int v = 0; v < cv; v += CPI) {
         if (c_run == 0) {
           const GemvLoc L = gemv_locate(p, ge, it, v);
           c_run = L.run;
@@ -456,48 +467,53 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
           mult = L.mult * kE2M1F16Rescale;
           xp = xbase + (long long)L.sidx * p.K + L.cc * 64;
         }
-        cp_async_wait_group<kRing - 1>();
-        const uint32_t slot = (uint32_t)c_cnt & (kRing - 1);
-        const uint4 wq = *reinterpret_cast<const uint4*>(ring_q_gen + slot * 512);
+        cp_async_wait_group<kRingIt - 1>();
+        const uint32_t slot = (uint32_t)c_cnt & (kRingIt - 1);
+        uint4 wq[CPI];
+#pragma unroll
+        for (int c = 0; c < CPI; ++c) wq[c] = *reinterpret_cast<const uint4*>(ring_q_gen + slot * (CPI * 512) + c * 512);
         const uint32_t s_cur = BIG_GROUPS ? *reinterpret_cast<const uint32_t*>(ring_s_gen + slot * 128) : 0u;
         issue();   // refill the slot just read
-        const uint32_t qq[4] = {wq.x, wq.y, wq.z, wq.w};
-        const uint4 xv0 = *reinterpret_cast<const uint4*>(xp);
-        const uint4 xv1 = *reinterpret_cast<const uint4*>(xp + 32);
-        const uint32_t bb[8] = {xv0.x, xv0.y, xv0.z, xv0.w, xv1.x, xv1.y, xv1.z, xv1.w};
         if (BIG_GROUPS) s2 = s_cur;
-        bool flush = false;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          if (!BIG_GROUPS) {
-            const int kabs = c_cc * 64 + ks * 16;
-            if ((kabs & gmask) == 0) s2 = (c_s != nullptr) ? __ldg(c_s + (kabs >> p.gs_shift) * 8) : 0u;
-          }
-          uint32_t a0, a1, a2, a3;
-          e2m1x8_to_f16x2(qq[ks], a0, a1, a2, a3);
-          mma_f16_16816(gacc, a0, a1, a2, a3, bb[2 * ks], bb[2 * ks + 1]);
-          if (BIG_GROUPS) flush = (ks == 3) && (((c_cc + 1) & cpg_mask) == 0);
-          else flush = (((c_cc * 64 + ks * 16 + 16) & gmask) == 0);
-          if (flush) {
-            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&s2));
-            const float slo = sf.x * mult, shi = sf.y * mult;
-            if (c_tsel == 0) {
-              accg[0] = fmaf(gacc[0], slo, accg[0]);
-              accg[1] = fmaf(gacc[1], slo, accg[1]);
-              accg[2] = fmaf(gacc[2], shi, accg[2]);
-              accg[3] = fmaf(gacc[3], shi, accg[3]);
-            } else {
-              accu[0] = fmaf(gacc[0], slo, accu[0]);
-              accu[1] = fmaf(gacc[1], slo, accu[1]);
-              accu[2] = fmaf(gacc[2], shi, accu[2]);
-              accu[3] = fmaf(gacc[3], shi, accu[3]);
+        for (int c = 0; c < CPI; ++c) {
+          const uint32_t qq[4] = {wq[c].x, wq[c].y, wq[c].z, wq[c].w};
+          const uint4 xv0 = *reinterpret_cast<const uint4*>(xp + c * 64);
+          const uint4 xv1 = *reinterpret_cast<const uint4*>(xp + c * 64 + 32);
+          const uint32_t bb[8] = {xv0.x, xv0.y, xv0.z, xv0.w, xv1.x, xv1.y, xv1.z, xv1.w};
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            if (!BIG_GROUPS) {
+              const int kabs = c_cc * 64 + ks * 16;
+              if ((kabs & gmask) == 0) s2 = (c_s != nullptr) ? __ldg(c_s + (kabs >> p.gs_shift) * 8) : 0u;
             }
-            gacc[0] = gacc[1] = gacc[2] = gacc[3] = 0.f;
+            uint32_t a0, a1, a2, a3;
+            e2m1x8_to_f16x2(qq[ks], a0, a1, a2, a3);
+            mma_f16_16816(gacc, a0, a1, a2, a3, bb[2 * ks], bb[2 * ks + 1]);
+            // group complete: apply its scale to the group accumulator in fp32 (big groups: once per trip at most)
+            const bool flush = BIG_GROUPS ? (c == CPI - 1 && ks == 3 && (((c_cc + CPI) & cpg_mask) == 0))
+                                          : (((c_cc * 64 + ks * 16 + 16) & gmask) == 0);
+            if (flush) {
+              const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&s2));
+              const float slo = sf.x * mult, shi = sf.y * mult;
+              if (c_tsel == 0) {
+                accg[0] = fmaf(gacc[0], slo, accg[0]);
+                accg[1] = fmaf(gacc[1], slo, accg[1]);
+                accg[2] = fmaf(gacc[2], shi, accg[2]);
+                accg[3] = fmaf(gacc[3], shi, accg[3]);
+              } else {
+                accu[0] = fmaf(gacc[0], slo, accu[0]);
+                accu[1] = fmaf(gacc[1], slo, accu[1]);
+                accu[2] = fmaf(gacc[2], shi, accu[2]);
+                accu[3] = fmaf(gacc[3], shi, accu[3]);
+              }
+              gacc[0] = gacc[1] = gacc[2] = gacc[3] = 0.f;
+            }
           }
         }
-        xp += 64;
-        ++c_cc;
-        --c_run;
+        xp += 64 * CPI;
+        c_cc += CPI;
+        c_run -= CPI;
         ++c_cnt;
       }
       // ---- reduction over the warps of the group and epilogue of this unit.  `red` is double buffered by unit
@@ -726,7 +742,7 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   if (p.tpx.out_peer_slots != nullptr && (p.act != 0 || p.mode == 1)) return (int)cudaErrorInvalidValue;
   if (p.act == 1 && n_rt % 2 != 0) return (int)cudaErrorInvalidValue;
   grid.z = 1;
-  const bool big = p.gs_shift >= 6;
+  const int gm = p.gs_shift >= 7 ? 2 : (p.gs_shift == 6 ? 1 : 0);
   // Work units per token tile: row tiles (tile pairs with the fused SwiGLU), times the MoE slots in mode 1.
   const int n_units = ((p.mode == 1) ? S : 1) * ((p.act == 1) ? n_rt / 2 : n_rt);
   const int chunks = ((p.mode == 2) ? S : 1) * (p.K / 64);
@@ -771,19 +787,21 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   smem = ((smem + 127) & ~(size_t)127) + (size_t)nw * kRing * (512 + 128);
   if (smem > 180 * 1024) return (int)cudaErrorInvalidValue;
   int e;
-#define MMB_LAUNCH_GEMV(BG, NW, GR)                                                                \
-  do {                                                                                             \
-    if ((e = set_smem(fp4_gemv_kernel<BG, NW, GR>, smem, 34 * 1024))) return e;                              \
-    return launch(fp4_gemv_kernel<BG, NW, GR>, grid, dim3(NW * 32), smem, stream, 1, p, wpt, mrows);       \
+#define MMB_LAUNCH_GEMV(GM_, NW, GR)                                                                \
+  do {                                                                                              \
+    if ((e = set_smem(fp4_gemv_kernel<GM_, NW, GR>, smem, 34 * 1024))) return e;                              \
+    return launch(fp4_gemv_kernel<GM_, NW, GR>, grid, dim3(NW * 32), smem, stream, 1, p, wpt, mrows);       \
   } while (0)
-  if (p.mode == 3) {
-    if (big) MMB_LAUNCH_GEMV(true, 8, true);
-    MMB_LAUNCH_GEMV(false, 8, true);
-  }
-  if (big && nw == 8) MMB_LAUNCH_GEMV(true, 8, false);
-  if (big) MMB_LAUNCH_GEMV(true, 16, false);
-  if (nw == 8) MMB_LAUNCH_GEMV(false, 8, false);
-  MMB_LAUNCH_GEMV(false, 16, false);
+#define MMB_LAUNCH_GEMV_GM(NW, GR)                 \
+  do {                                             \
+    if (gm == 2) MMB_LAUNCH_GEMV(2, NW, GR);       \
+    if (gm == 1) MMB_LAUNCH_GEMV(1, NW, GR);       \
+    MMB_LAUNCH_GEMV(0, NW, GR);                    \
+  } while (0)
+  if (p.mode == 3) MMB_LAUNCH_GEMV_GM(8, true);
+  if (nw == 8) MMB_LAUNCH_GEMV_GM(8, false);
+  MMB_LAUNCH_GEMV_GM(16, false);
+#undef MMB_LAUNCH_GEMV_GM
 #undef MMB_LAUNCH_GEMV
 }
 

@@ -236,6 +236,17 @@ class Transformer:
                                   ctx_lens=meta.ctx_lens, block_size=bs, max_q=max_q, scale=self.scale, window=cfg.sliding_window,
                                   out=out.view(-1, Hq, D))
             return out
+        if (meta.attn_mask is not None and q.dtype == torch.bfloat16 and len(meta.cu_seqlens) == 2 and q.is_cuda
+                and D in ops.PREFILL_ATTN_DIMS and ops.native_available()):
+            # token-tree verification: the committed context is fully visible, the last T keys through the given mask
+            T = q.shape[0]
+            n_ctx = int(meta.ctx_lens_host[0])
+            tm = meta.attn_mask[:, n_ctx - T:].to(torch.uint8).contiguous()
+            cu_q = torch.tensor(meta.cu_seqlens, dtype=torch.int32, device=q.device)
+            ops.prefill_attention(q, kv.k[li].view(-1, Hk, D), kv.v[li].view(-1, Hk, D), cu_q, block_tables=meta.block_tables,
+                                  ctx_lens=meta.ctx_lens, block_size=bs, max_q=T, scale=self.scale, causal=False, tree_mask=tm,
+                                  out=out.view(-1, Hq, D))
+            return out
         for b in range(len(meta.cu_seqlens) - 1):
             s, e = meta.cu_seqlens[b], meta.cu_seqlens[b + 1]
             n_ctx = int(meta.ctx_lens_host[b])

@@ -657,17 +657,24 @@ PREFILL_ATTN_DIMS = (64, 128, 256)
 
 
 def prefill_attention(q, k, v, cu_q, *, cu_k=None, block_tables=None, ctx_lens=None, block_size=16, max_q=None, scale=None, window=0,
-                      causal=True, out=None, q_lens_host=None, k_lens_host=None):
+                      causal=True, out=None, q_lens_host=None, k_lens_host=None, sinks=0, tree_mask=None, block_mask=None):
     """Variable-length prefill attention.  ``q [T, Hq, D]``; contiguous keys ``k, v [N, Hk, D]`` with ``cu_k``, or paged
     pools ``[slots, Hk, D]`` with ``block_tables`` / ``ctx_lens``.  The queries of a sequence are the last positions of
-    its keys.  ``cu_q`` / ``cu_k``: int32 device tensors ``[B + 1]``."""
+    its keys.  ``cu_q`` / ``cu_k``: int32 device tensors ``[B + 1]``.
+
+    Mask modes (combined by AND): ``causal``; ``window`` (+ ``sinks`` always-visible first keys); ``tree_mask`` uint8
+    ``[T, >= max_q]`` - query row i sees the j-th of its sequence's last ``q_len`` keys iff ``tree_mask[i, j]`` (earlier keys
+    stay visible; pass ``causal=False`` for a token tree); ``block_mask`` uint8 ``[1 | Hq, ceil(max_q / 128), n_kblocks]`` -
+    128-query x 64-key blocks with a zero byte are skipped."""
     T, Hq, D = q.shape
     scale = scale if scale is not None else D ** -0.5
     if out is None:
         out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    if max_q is None and (block_mask is not None or (_use_native(q) and D in PREFILL_ATTN_DIMS)):
+        max_q = int((cu_q[1:] - cu_q[:-1]).max())
     if _use_native(q) and D in PREFILL_ATTN_DIMS and q.dtype == torch.bfloat16 and k.shape[-1] == D and v.shape[-1] == D:
-        if max_q is None:
-            max_q = int((cu_q[1:] - cu_q[:-1]).max())
-        K.mmb200.prefill_attention(q, k, v, out, cu_q, cu_k, block_tables, ctx_lens, block_size, max_q, scale, window, causal)
+        K.mmb200.prefill_attention(q, k, v, out, cu_q, cu_k, block_tables, ctx_lens, block_size, max_q, scale, window, causal,
+                                   int(sinks), tree_mask, block_mask)
         return out
-    return ref.prefill_attention(q, k, v, cu_q, cu_k, block_tables, ctx_lens, block_size, scale, window, causal, out)
+    return ref.prefill_attention(q, k, v, cu_q, cu_k, block_tables, ctx_lens, block_size, scale, window, causal, out,
+                                 sinks=sinks, tree_mask=tree_mask, block_mask=block_mask)

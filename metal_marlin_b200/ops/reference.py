@@ -376,7 +376,8 @@ def spec_verify(p_target, p_draft, draft, u, u_resample):
     return toks, acc
 
 
-def prefill_attention(q, k, v, cu_q, cu_k, block_tables, ctx_lens, block_size, scale, window, causal, out):
+def prefill_attention(q, k, v, cu_q, cu_k, block_tables, ctx_lens, block_size, scale, window, causal, out, sinks=0, tree_mask=None,
+                      block_mask=None):
     T, Hq, D = q.shape
     Hk = k.shape[1]
     cq = cu_q.tolist()
@@ -404,7 +405,21 @@ def prefill_attention(q, k, v, cu_q, cu_k, block_tables, ctx_lens, block_size, s
         if causal:
             ok &= kpos <= qpos
         if window and window > 0:
-            ok &= kpos > qpos - window
+            ok &= (kpos > qpos - window) | (kpos < (sinks or 0))
+        if tree_mask is not None:
+            tm = torch.ones(t, n, dtype=torch.bool, device=q.device)
+            tm[:, n - t:] = tree_mask[s:e, :t].bool()
+            ok &= tm
+        ok = ok.unsqueeze(0).expand(Hq, t, n)
+        if block_mask is not None:
+            qb = torch.arange(t, device=q.device) // 128
+            kb_i = torch.arange(n, device=q.device) // 64
+            bm = block_mask.bool()
+            inside = kb_i < bm.shape[2]
+            sel = bm[:, qb][:, :, kb_i.clamp_max(bm.shape[2] - 1)] & inside[None, None, :]
+            ok = ok & sel.expand(Hq, t, n)
         sc = sc.masked_fill(~ok, float("-inf"))
-        out[s:e] = (torch.softmax(sc, -1) @ vf).transpose(0, 1).to(out.dtype)
+        pr = torch.softmax(sc, -1)
+        pr = torch.where(ok.any(-1, keepdim=True), pr, torch.zeros_like(pr))       # rows that see nothing give zeros
+        out[s:e] = (pr @ vf).transpose(0, 1).to(out.dtype)
     return out

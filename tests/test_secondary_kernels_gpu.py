@@ -130,3 +130,42 @@ def test_prefill_attention_contiguous_and_paged(D, Hq, Hk, window):
     qkv[:, : Hq * D] = q.view(T, Hq * D)
     got_s = ops.prefill_attention(qkv[:, : Hq * D].view(T, Hq, D), k, v, cu_q, cu_k=cu_k, window=window)
     torch.testing.assert_close(got_s.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+def _bhsd(B, H, S, D, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(B, H, S, D, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+
+
+def test_prefill_attention_mask_modes_match_dense_masks():
+    """Window + global tokens, token-tree mask and block-sparse skipping against dense-mask fp32 attention."""
+    import torch.nn.functional as F
+    from metal_marlin_b200 import attention as A
+    from metal_marlin_b200.inference.long_context import sliding_window_mask
+    B, H, Hk, S, D = 2, 4, 2, 300, 64
+    q, k, v = _bhsd(B, H, S, D, 1), _bhsd(B, Hk, S, D, 2), _bhsd(B, Hk, S, D, 3)
+    kx, vx = k.repeat_interleave(H // Hk, 1).float(), v.repeat_interleave(H // Hk, 1).float()
+    # sliding window with global tokens (keys between the sinks and the window are skipped tile-wise)
+    got = A.sliding_window_attention(q, k, v, window=70, global_tokens=5)
+    m = sliding_window_mask(S, S, 70, 5, DEV)
+    want = F.scaled_dot_product_attention(q.float(), kx, vx, attn_mask=m)
+    torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2)
+    # block-sparse, 64-blocks (finer than the kernel's 128-row skip granularity) and 128-blocks (exact skip only)
+    for block in (64, 128):
+        nb = (S + block - 1) // block
+        bm = A.block_mask_bigbird(nb, window_blocks=1, global_blocks=1, random_blocks=1, seed=3)
+        got = A.block_sparse_attention(q, k, v, bm, block=block, causal=True)
+        dm = A.expand_block_mask(bm.to(DEV), block, S, True)
+        want = F.scaled_dot_product_attention(q.float(), kx, vx, attn_mask=dm)
+        torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2)
+    # token tree on top of a committed context
+    parents = [-1, 0, 0, 1, 1, 2, 5, 6]
+    N, C = len(parents), 150
+    qt = _bhsd(1, H, N, D, 4)
+    kc, vc, kt, vt = _bhsd(1, Hk, C, D, 5), _bhsd(1, Hk, C, D, 6), _bhsd(1, Hk, N, D, 7), _bhsd(1, Hk, N, D, 8)
+    got = A.tree_attention(qt, kc, vc, kt, vt, parents)
+    mask = torch.cat([torch.ones(N, C, dtype=torch.bool), A.tree_mask_from_parents(parents)], 1).to(DEV)
+    kk = torch.cat([kc, kt], 2).repeat_interleave(H // Hk, 1).float()
+    vv = torch.cat([vc, vt], 2).repeat_interleave(H // Hk, 1).float()
+    want = F.scaled_dot_product_attention(qt.float(), kk, vv, attn_mask=mask)
+    torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2)
