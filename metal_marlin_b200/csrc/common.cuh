@@ -81,30 +81,28 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Expand the eight E2M1 nibbles of a tile-layout word into the four fp16x2 registers of an
-// m16n8k16 A fragment.  The fp16 values equal e2m1 * 2^-14 (the exponent field is used
+// Expand the eight E2M1 codes of a tile-layout word into the four fp16x2 registers of an m16n8k16 A fragment.  In each
+// 16-bit half the word holds the signs of registers 0..3 in bits 15..12 and their 3-bit magnitudes in bits 11..9, 8..6,
+// 5..3, 2..0, so every register is an independent (shift, mask) pair of the same word: no serial shift chain, and the
+// shifts can run as multiplies beside the logic ops.  The fp16 values equal e2m1 * 2^-14 (the exponent field is used
 // as-is, so code 1 lands on an fp16 subnormal); the caller folds 2^14 into the group scale.
 __device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t q, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) {
-  a0 = (q & 0x80008000u) | ((q & 0x70007000u) >> 3);
-  q <<= 4;
-  a1 = (q & 0x80008000u) | ((q & 0x70007000u) >> 3);
-  q <<= 4;
-  a2 = (q & 0x80008000u) | ((q & 0x70007000u) >> 3);
-  q <<= 4;
-  a3 = (q & 0x80008000u) | ((q & 0x70007000u) >> 3);
+  const uint32_t q3 = q << 3;
+  a0 = q & 0x8E008E00u;
+  a1 = ((q << 1) & 0x80008000u) | (q3 & 0x0E000E00u);
+  a2 = ((q << 2) & 0x80008000u) | ((q << 6) & 0x0E000E00u);
+  a3 = (q3 & 0x80008000u) | ((q << 9) & 0x0E000E00u);
 }
 constexpr float kE2M1F16Rescale = 16384.0f;  // 2^14
 
-// Same nibbles to bf16x2 holding e2m1 * 2^-126 (bf16 subnormal trick).
+// Same codes to bf16x2 holding e2m1 * 2^-126 (bf16 subnormal trick): magnitudes go to bits 8..6.
 __device__ __forceinline__ void e2m1x8_to_bf16x2_raw(uint32_t q, uint32_t& a0, uint32_t& a1, uint32_t& a2,
                                                      uint32_t& a3) {
-  a0 = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
-  q <<= 4;
-  a1 = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
-  q <<= 4;
-  a2 = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
-  q <<= 4;
-  a3 = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+  const uint32_t q3 = q << 3;
+  a0 = (q & 0x80008000u) | ((q >> 3) & 0x01C001C0u);
+  a1 = ((q << 1) & 0x80008000u) | (q & 0x01C001C0u);
+  a2 = ((q << 2) & 0x80008000u) | (q3 & 0x01C001C0u);
+  a3 = (q3 & 0x80008000u) | ((q << 6) & 0x01C001C0u);
 }
 
 // Programmatic dependent launch: pdl_launch_dependents() lets the next kernel of the stream start its

@@ -16,10 +16,13 @@ Device tile layout (what the sm_100a kernels read; built once at load time):
 * weights ``int32 [out/16, in/64, 32, 4]``.  Block ``(rt, kc)`` holds rows
   ``16*rt .. 16*rt+15`` and input columns ``64*kc .. 64*kc+63``; the four words of
   lane ``l = 4*g + t`` are the four k16 steps of that block, and the eight nibbles
-  of each word are exactly the lane's A-fragment of an ``m16n8k16`` MMA, ordered
-  so that ``(w & 0x80008000) | ((w & 0x70007000) >> s)`` followed by ``w <<= 4``
-  produces the four fragment registers in turn.  A warp therefore reads one block
-  with a single coalesced 512-byte load and needs no shuffles.
+  of each word are exactly the lane's A-fragment of an ``m16n8k16`` MMA.  Inside each
+  16-bit half the four sign bits sit in bits 15..12 (fragment register 0..3) and the
+  four 3-bit magnitudes in bits 11..9, 8..6, 5..3, 2..0, so register ``j`` is
+  ``((w << j) & 0x80008000) | ((w << 3j) & 0x0E000E00)``: four independent
+  extractions from the same word (no serial shift chain), register 0 with a single
+  AND.  A warp reads one block with a single coalesced 512-byte load and needs no
+  shuffles.
 * scales ``fp16 [out/16, in/gs, 8, 2]``: the two scales a lane needs (rows ``g`` and
   ``g+8``) sit in one 32-bit word.
 """
@@ -175,8 +178,8 @@ def to_tile_layout(codes: torch.Tensor, scales: torch.Tensor) -> Tuple[torch.Ten
     h = torch.arange(2, device=codes.device).view(1, 2, 1, 1, 1, 1, 1, 1)
     kh = torch.arange(2, device=codes.device).view(1, 1, 1, 1, 1, 2, 1, 1)
     e = torch.arange(2, device=codes.device).view(1, 1, 1, 1, 1, 1, 1, 2)
-    nib_pos = 3 - h - 2 * kh + 4 * e
-    word = (c << (4 * nib_pos)).sum(dim=(1, 5, 7))          # [rt, g, kc, ks, t]
+    j = h + 2 * kh                                           # fragment register of the element
+    word = (((c >> 3) << (16 * e + 15 - j)) + ((c & 7) << (16 * e + 9 - 3 * j))).sum(dim=(1, 5, 7))     # [rt, g, kc, ks, t]
     word = torch.where(word >= 2 ** 31, word - 2 ** 32, word).to(torch.int32)
     qtile = word.permute(0, 2, 1, 4, 3).contiguous().view(out_p // 16, in_p // 64, 32, 4)
     stile = s.view(out_p // 16, 2, 8, ng_p).permute(0, 3, 2, 1).contiguous()   # [rt, grp, g, h]
@@ -192,8 +195,9 @@ def from_tile_layout(qtile: torch.Tensor, stile: torch.Tensor, out_f: int, in_f:
     h = torch.arange(2, device=dev).view(2, 1, 1)
     kh = torch.arange(2, device=dev).view(1, 2, 1)
     e = torch.arange(2, device=dev).view(1, 1, 2)
-    nib_pos = (3 - h - 2 * kh + 4 * e)                                        # [h, kh, e]
-    nib = (w.view(n_rt, n_kc, 8, 4, 4, 1, 1, 1) >> (4 * nib_pos)) & 0xF       # [rt,kc,g,t,ks,h,kh,e]
+    j = h + 2 * kh                                                             # [h, kh, 1]
+    w8 = w.view(n_rt, n_kc, 8, 4, 4, 1, 1, 1)
+    nib = (((w8 >> (16 * e + 15 - j)) & 1) << 3) | ((w8 >> (16 * e + 9 - 3 * j)) & 7)      # [rt,kc,g,t,ks,h,kh,e]
     codes = nib.permute(0, 5, 2, 1, 4, 6, 3, 7).contiguous().view(n_rt * 16, n_kc * 64).to(torch.uint8)
     ng = stile.shape[1]
     scales = stile.permute(0, 3, 2, 1).contiguous().view(n_rt * 16, ng)

@@ -61,9 +61,10 @@ def test_tile_word_is_mma_fragment():
         for ks in range(4):
             w = int(q[0, 0, lane, ks]) & 0xFFFFFFFF
             frags = []
-            for _ in range(4):
-                frags.append(((w >> 12) & 0xF, (w >> 28) & 0xF))
-                w = (w << 4) & 0xFFFFFFFF
+            for j in range(4):       # register j = ((w << j) & 0x80008000) | ((w << 3j) & 0x0E000E00): sign bit 15, magnitude 11..9
+                r = (((w << j) & 0x80008000) | ((w << (3 * j)) & 0x0E000E00)) & 0xFFFFFFFF
+                code = lambda half: (((half >> 15) & 1) << 3) | ((half >> 9) & 7)
+                frags.append((code(r & 0xFFFF), code(r >> 16)))
             k0 = ks * 16 + 2 * t
             exp = [(codes[g, k0], codes[g, k0 + 1]), (codes[g + 8, k0], codes[g + 8, k0 + 1]),
                    (codes[g, k0 + 8], codes[g, k0 + 9]), (codes[g + 8, k0 + 8], codes[g + 8, k0 + 9])]
