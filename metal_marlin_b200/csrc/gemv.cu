@@ -83,20 +83,37 @@ struct GemvLoc {
   int run;               // chunks in the run, starting with this one
 };
 
+// Division by a value fixed for the launch as one multiply-high: exact while dividend * divisor < 2^32 (unit and chunk
+// counts here are far below that).
+struct FastDiv {
+  uint32_t magic;      // ceil(2^32 / d); unused for d == 1
+  int d;
+  __host__ __device__ void set(int div) {
+    d = div;
+    magic = (div > 1) ? 0xFFFFFFFFu / (unsigned)div + 1u : 0u;
+  }
+  __device__ __forceinline__ int div(int u) const { return (d > 1) ? (int)__umulhi((uint32_t)u, magic) : u; }
+};
+// The divisors of a launch (row tiles per slot, chunks per segment, slots per token), prepared on the host.
+struct GemvDivs {
+  FastDiv tps, kc, od;
+};
+
 struct GemvGeom {
   int gi, TG, tiles_per_slot, n_rt, cpw, c_begin, KC, NG, nseg, token, lane, g;
-  int upi, UB, grp, G, item0, item_stride;   // grouped mode: the CTA walks items of UB units, upi units per group
+  int upi, upi_shift, UB, grp, G, item0, item_stride;   // grouped mode: the CTA walks items of UB units, upi (a power of two) per group
+  FastDiv tps_div, kc_div;
 };
 
 __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const GemvGeom& ge, int it, int v) {
   GemvLoc L;
   int u = ge.gi + it * ge.TG;
   if (p.mode == 3) {
-    const int n = it / ge.upi;
-    u = (ge.item0 + n * ge.item_stride) * ge.UB + ge.grp + (it - n * ge.upi) * ge.G;
+    const int n = it >> ge.upi_shift;
+    u = (ge.item0 + n * ge.item_stride) * ge.UB + ge.grp + (it - (n << ge.upi_shift)) * ge.G;
   }
   if (p.mode == 1 || p.mode == 3) {       // slot = MoE slot (mode 1) or tile-list entry (mode 3)
-    L.slot = u / ge.tiles_per_slot;
+    L.slot = ge.tps_div.div(u);
     L.rt0 = u - L.slot * ge.tiles_per_slot;
   } else {
     L.slot = 0;
@@ -109,7 +126,7 @@ __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const 
   L.sidx = 0;
   L.cc = ci;
   if (ge.nseg > 1) {
-    L.sidx = ci / ge.KC;
+    L.sidx = ge.kc_div.div(ci);
     L.cc = ci - L.sidx * ge.KC;
   }
   const SegPtr sp = seg_lookup(p, ge.token, (p.mode == 1 || p.mode == 3) ? L.slot : L.sidx);
@@ -138,7 +155,7 @@ __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const 
 // bookkeeping of loader and consumer is paid once per 1 KB of weights, which matters because the fully loaded kernel
 // is bound by instruction issue, not by DRAM).
 template <int GM, int NWARPS, bool GROUPED>
-__global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt, const int mrows) {
+__global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt, const int mrows, const GemvDivs divs) {
   constexpr bool BIG_GROUPS = GM > 0;
   constexpr int CPI = (GM == 2) ? 2 : 1;       // chunks per trip
   constexpr int kRingIt = kRing / CPI;         // ring slots (one trip's weights each)
@@ -189,6 +206,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
   // units of this group (grouped mode: known after the wait, the tile count lives on the device)
   int n_iter = (!grouped && ge.gi < n_units) ? (n_units - ge.gi + ge.TG - 1) / ge.TG : 0;
   ge.KC = p.K >> 6;                        // chunks per segment
+  ge.kc_div = divs.kc;
   ge.NG = p.K >> p.gs_shift;               // groups per segment
   ge.nseg = nseg;
   ge.token = token;
@@ -197,6 +215,8 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
   ge.G = G;
   ge.grp = grp;
   ge.upi = grouped ? mrows : 1;            // grouped launches pass the units per item and group in this argument
+  ge.upi_shift = 31 - __clz(ge.upi);
+  ge.tps_div = divs.tps;
   ge.UB = G * ge.upi;
   ge.item0 = blockIdx.x;
   ge.item_stride = gridDim.x;
@@ -211,26 +231,27 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
   const int cpg_shift = BIG_GROUPS ? (p.gs_shift - 6) : 0;               // log2(chunks per quantization group)
 
   // ---- loader: one cp.async (16 bytes per lane) per chunk, plus the 4-byte scale word of the lane's row pair
-  int l_it = 0, l_v = 0, l_cnt = 0, l_run = 0, l_cc = 0;
-  const uint4* l_q = nullptr;
-  const uint32_t* l_s = nullptr;
+  int l_it = 0, l_v = 0, l_cnt = 0, l_run = 0, l_cc = 0, l_qb = 0, l_sb = 0;     // l_qb / l_sb: bytes to copy (0 = zero fill: no expert)
+  const uint4* l_q = reinterpret_cast<const uint4*>(p.qw);
+  const uint32_t* l_s = reinterpret_cast<const uint32_t*>(p.sc);
   auto issue = [&]() {
     if (cv > 0 && l_it < n_iter) {
       if (l_run == 0) {
         const GemvLoc L = gemv_locate(p, ge, l_it, l_v);
-        l_q = L.q;
-        l_s = L.s;
+        l_qb = (L.q != nullptr) ? 16 : 0;
+        l_sb = (L.s != nullptr) ? 4 : 0;
+        l_q = (L.q != nullptr) ? L.q : reinterpret_cast<const uint4*>(p.qw);
+        l_s = (L.s != nullptr) ? L.s : reinterpret_cast<const uint32_t*>(p.sc);
         l_cc = L.cc;
         l_run = L.run;
       }
       const uint32_t slot = (uint32_t)l_cnt & (kRingIt - 1);
 #pragma unroll
       for (int c = 0; c < CPI; ++c)
-        cp_async_16(ring_q + slot * (CPI * 512) + c * 512, (l_q != nullptr) ? (const void*)(l_q + c * 32) : p.qw, (l_q != nullptr) ? 16 : 0);
+        cp_async_16(ring_q + slot * (CPI * 512) + c * 512, l_q + c * 32, l_qb);
       if (BIG_GROUPS)       // the chunks of a trip share their quantization group
-        cp_async_4(ring_s + slot * 128, (l_s != nullptr) ? (const void*)(l_s + (l_cc >> cpg_shift) * 8) : p.sc,
-                   (l_s != nullptr) ? 4 : 0);
-      if (l_q != nullptr) l_q += 32 * CPI;
+        cp_async_4(ring_s + slot * 128, l_sb ? (const void*)(l_s + (l_cc >> cpg_shift) * 8) : (const void*)l_s, l_sb);
+      if (l_qb) l_q += 32 * CPI;
       l_cc += CPI;
       l_run -= CPI;
       l_v += CPI;
@@ -413,7 +434,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
     const int gmask = gs - 1;
     const int cpg_mask = (1 << cpg_shift) - 1;
     const __half* xbase = xs + min(g, mt - 1) * ((p.mode == 2) ? 0 : XS) + t * 8;
-    const int k8 = p.K >> 3;
+    const FastDiv od_div = divs.od;
     const unsigned char* ring_q_gen = smem_raw + (ring_q - smem_u32(smem_raw));
     const unsigned char* ring_s_gen = smem_raw + (ring_s - smem_u32(smem_raw));
     int c_cnt = 0, c_run = 0, c_cc = 0, c_tsel = 0, c_slot = 0, c_rt0 = 0;
@@ -422,30 +443,45 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
     const uint32_t* c_s = nullptr;
 #pragma unroll 1
     for (int it = 0; it < n_iter; ++it) {
-      if (grouped && (it % ge.upi) == 0) {
+      if (grouped && (it & (ge.upi - 1)) == 0) {
         // new item: every group is done with the previous rows; stage the rows of this item's tile (already
         // normalized bf16, clamped into fp16, fragment order as above)
-        const int item = ge.item0 + (it / ge.upi) * ge.item_stride;
-        const int tj = (item * ge.UB) / ge.tiles_per_slot;
+        const int item = ge.item0 + (it >> ge.upi_shift) * ge.item_stride;
+        const int tj = ge.tps_div.div(item * ge.UB);
         __syncthreads();
         m0 = __ldg(p.tile_row0 + tj);
         mt = min(__ldg(p.tile_rows + tj), 8);
-#pragma unroll 1
-        for (int idx = tid; idx < mt * k8; idx += kGemvThreads) {
-          const int r = idx / k8, k = (idx - r * k8) << 3;
-          int srow = m0 + r;
-          if (p.order_div > 0) {
-            const int pair = __ldg(p.row_order + srow);
-            srow = (pair >= 0) ? pair / p.order_div : -1;
-          }
-          const uint4 xv = (srow >= 0) ? *reinterpret_cast<const uint4*>(xg + (long long)srow * p.ldx + k) : make_uint4(0, 0, 0, 0);
-          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-          __half* blk = xs + (long long)r * XS + (k & ~31) + ((k >> 4) & 1) * 4 + ((k >> 3) & 1) * 2;
+        // source rows first (eight independent loads), then one 16-byte load per row and trip, all in flight together
+        int srows[8];
 #pragma unroll
-          for (int tt = 0; tt < 4; ++tt)
-            *reinterpret_cast<__half2*>(blk + tt * 8) =
-                __floats2half2_rn(fminf(fmaxf(__uint_as_float(xw[tt] << 16), -65504.f), 65504.f),
-                                  fminf(fmaxf(__uint_as_float(xw[tt] & 0xffff0000u), -65504.f), 65504.f));
+        for (int r = 0; r < 8; ++r) {
+          srows[r] = -1;
+          if (r < mt) {
+            srows[r] = m0 + r;
+            if (p.order_div > 0) {
+              const int pair = __ldg(p.row_order + m0 + r);
+              srows[r] = (pair >= 0) ? od_div.div(pair) : -1;
+            }
+          }
+        }
+#pragma unroll 1
+        for (int k = tid * 8; k < p.K; k += kGemvThreads * 8) {
+          uint4 xv[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            xv[r] = (srows[r] >= 0) ? *reinterpret_cast<const uint4*>(xg + (long long)srows[r] * p.ldx + k) : make_uint4(0, 0, 0, 0);
+          __half* blk0 = xs + (k & ~31) + ((k >> 4) & 1) * 4 + ((k >> 3) & 1) * 2;
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            if (r >= mt) break;
+            const uint32_t xw[4] = {xv[r].x, xv[r].y, xv[r].z, xv[r].w};
+            __half* blk = blk0 + (long long)r * XS;
+#pragma unroll
+            for (int tt = 0; tt < 4; ++tt)
+              *reinterpret_cast<__half2*>(blk + tt * 8) =
+                  __floats2half2_rn(fminf(fmaxf(__uint_as_float(xw[tt] << 16), -65504.f), 65504.f),
+                                    fminf(fmaxf(__uint_as_float(xw[tt] & 0xffff0000u), -65504.f), 65504.f));
+          }
         }
         __syncthreads();
         xbase = xs + min(g, mt - 1) * XS + t * 8;
@@ -758,7 +794,7 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
     const int tps = (p.act == 1) ? n_rt / 2 : n_rt;
     const int unit_chunks = ((p.act == 1) ? 2 : 1) * chunks;
     wpt = 8;
-    while (wpt > 1 && (unit_chunks < 2 * kRing * wpt || k_units < wpt)) wpt >>= 1;
+    while (wpt > 1 && (unit_chunks < 4 * kRing * wpt || k_units < wpt)) wpt >>= 1;
     while (wpt < 8 && tps % (8 / wpt) != 0) wpt <<= 1;      // the groups of a CTA share the units of an item evenly
     if (p.grouped_wpt > 0) wpt = p.grouped_wpt;
     if (wpt > 8 || (wpt & (wpt - 1)) || k_units < wpt) return (int)cudaErrorInvalidValue;
@@ -769,7 +805,7 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
     int upi = 8;
     while (upi > 1 && (tps % (Gg * upi) != 0 || (long long)p.max_tiles * tps / (Gg * upi) < 4 * 296)) upi >>= 1;
     if (p.grouped_upi > 0) upi = p.grouped_upi;
-    if (tps % (Gg * upi) != 0) return (int)cudaErrorInvalidValue;
+    if (tps % (Gg * upi) != 0 || (upi & (upi - 1))) return (int)cudaErrorInvalidValue;
     mrows = upi;
   }
   const int nw = (wpt == 16) ? 16 : 8;
@@ -786,11 +822,15 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   // dynamic shared memory: the staged activation rows, then every warp's weight ring (512 + 128 bytes per slot)
   smem = ((smem + 127) & ~(size_t)127) + (size_t)nw * kRing * (512 + 128);
   if (smem > 180 * 1024) return (int)cudaErrorInvalidValue;
+  GemvDivs divs;
+  divs.tps.set((p.act == 1) ? n_rt / 2 : n_rt);
+  divs.kc.set(p.K / 64);
+  divs.od.set(p.order_div > 0 ? p.order_div : 1);
   int e;
 #define MMB_LAUNCH_GEMV(GM_, NW, GR)                                                                \
   do {                                                                                              \
     if ((e = set_smem(fp4_gemv_kernel<GM_, NW, GR>, smem, 34 * 1024))) return e;                              \
-    return launch(fp4_gemv_kernel<GM_, NW, GR>, grid, dim3(NW * 32), smem, stream, 1, p, wpt, mrows);       \
+    return launch(fp4_gemv_kernel<GM_, NW, GR>, grid, dim3(NW * 32), smem, stream, 1, p, wpt, mrows, divs);  \
   } while (0)
 #define MMB_LAUNCH_GEMV_GM(NW, GR)                 \
   do {                                             \
