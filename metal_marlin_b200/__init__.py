@@ -53,6 +53,8 @@ _reg(".quant.mixed_precision", "policy_for", "allocate_bits", "TensorPolicy")
 _reg(".quant.pipeline", "quantize_checkpoint", "collect_hessians")
 _reg(".converters", "convert_checkpoint", "MixedFormatPack")
 _reg(".converters.gguf", "GGUFReader", "write_gguf")
+_reg(".converters.onnx", "ONNXExecutor", "ONNXGraph", "ONNXOp", "load_onnx", "save_onnx", "parse_onnx_graph", "summarize_graph",
+     "detect_architecture")
 _reg(".spec.engine", "SpeculativeEngine")
 _reg(".spec.draft", "NGramDraft", "SmallModelDraft", "MTPDraft", "MTPHead", "EagleDraft", "DraftModel")
 _reg(".spec.verify", "verify_greedy", "verify_speculative", "verify_batch_greedy", "verify_tree_greedy", "tree_attention_mask")

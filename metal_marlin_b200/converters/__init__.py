@@ -1,5 +1,6 @@
 """Checkpoint importers / converters: GGUF (de-quantize + re-quantize), PyTorch ``.bin`` / ``.pt`` state dicts, HF
-safetensors, GPTQ (AutoGPTQ-style int4) and EXL3-style trellis tensors, plus the mixed-format packer.
+safetensors, GPTQ (AutoGPTQ-style int4), EXL3-style trellis tensors and ONNX graphs (``onnx.py``: own protobuf reader,
+graph summary, executor with quantized MatMul / Gemm), plus the mixed-format packer.
 
 Parity: reference ``metal_marlin/converters/*``, ``gguf_to_marlin.py``, ``hf_exl3_loader.py``,
 ``quantization/exl3_to_marlin.py``, ``packing/mixed_format.py`` and the ``convert`` command (``cli.py:307-345``).
@@ -26,6 +27,8 @@ def detect_format(path: str) -> str:
         ext = os.path.splitext(path)[1].lower()
         if ext == ".gguf":
             return "gguf"
+        if ext == ".onnx":
+            return "onnx"
         if ext in (".bin", ".pt", ".pth"):
             return "pytorch"
         if ext == ".safetensors":
@@ -47,6 +50,16 @@ def _iter_source(src: str, fmt: str) -> Iterator[Tuple[str, torch.Tensor]]:
         with gguf.GGUFReader(p) as r:
             for name in r.tensor_names():
                 yield gguf.gguf_name_to_hf(name), r.load_tensor(name)
+    elif fmt == "onnx":
+        # the linear weights of the graph (as [out, in]) plus every other float initializer under its own name
+        from . import onnx as _onnx
+        g = _onnx.load_onnx(src)
+        lin = _onnx.extract_linear_weights(g)
+        for k, arr in g.initializers.items():
+            if k in lin:
+                yield k + ".weight", lin[k]
+            elif arr.dtype.kind == "f":
+                yield k, torch.from_numpy(arr.astype("float32"))
     elif fmt == "pytorch":
         files = [src] if os.path.isfile(src) else [os.path.join(src, f) for f in sorted(os.listdir(src)) if f.endswith((".bin", ".pt", ".pth"))]
         for fp in files:
@@ -92,4 +105,4 @@ def convert_checkpoint(src: str, dst: str, from_format: str = "auto", to_format:
             shutil.rmtree(stage, ignore_errors=True)
 
 
-__all__ = ["convert_checkpoint", "detect_format", "gguf", "dequantize_gptq_int4", "import_gptq_state", "MixedFormatPack"]
+__all__ = ["convert_checkpoint", "detect_format", "gguf", "onnx", "dequantize_gptq_int4", "import_gptq_state", "MixedFormatPack"]
