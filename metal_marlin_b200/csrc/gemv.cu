@@ -154,15 +154,20 @@ __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const 
 // of 64 (one 64-wide chunk per trip), 2 - groups of 128 and more (two chunks and one scale word per trip: the per-trip
 // bookkeeping of loader and consumer is paid once per 1 KB of weights, which matters because the fully loaded kernel
 // is bound by instruction issue, not by DRAM).
-template <int GM, int NWARPS, bool GROUPED>
-__global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt, const int mrows, const GemvDivs divs) {
+//
+// MB row blocks (dense mode only): a CTA holds 8 * MB token rows and every expanded weight fragment feeds MB MMAs, one per
+// block of 8 rows, so the expansion - the bulk of the instructions - is paid once for up to 32 tokens.  The accumulators
+// of MB = 2 / 4 need more registers than two resident 8-warp CTAs leave, so those variants run one CTA per SM.
+template <int GM, int NWARPS, bool GROUPED, int MB>
+__global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8 && MB == 1) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt, const int mrows, const GemvDivs divs) {
+  static_assert(MB == 1 || (!GROUPED && NWARPS == 8), "row blocks exist for the dense 8-warp kernel");
   constexpr bool BIG_GROUPS = GM > 0;
   constexpr int CPI = (GM == 2) ? 2 : 1;       // chunks per trip
   constexpr int kRingIt = kRing / CPI;         // ring slots (one trip's weights each)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float red[2][NWARPS][2][128];
-  __shared__ float ss_red[NWARPS][8];
-  __shared__ float rstd_s[8];
+  __shared__ float ss_red[NWARPS][8 * MB];
+  __shared__ float rstd_s[8 * MB];
   constexpr int kGemvThreads = NWARPS * 32;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -174,7 +179,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
     m0 = 0;
     mt = 8;                             // per unit: the tile's row count
   } else if (p.mode == 0) {
-    m0 = blockIdx.y * mrows;            // mrows <= 8 token rows per CTA (fewer when K is so large that 8 rows do not fit)
+    m0 = blockIdx.y * mrows;            // mrows <= 8 * MB token rows per CTA (fewer when K is so large that they do not fit)
     mt = min(mrows, p.M - m0);
   } else {
     token = blockIdx.y;
@@ -314,8 +319,79 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
   // in the same shared-memory slots (fragment order) and accumulates the sum of squares.  Pass B (norm only)
   // has every thread rewrite its own slots with bf16(v * rstd * w) as fp16.
   const int stage_k = (p.mode == 2) ? Kv : p.K;          // staged width of a row (columns beyond Kx are zero)
+  if (MB > 1) {
+    // Many rows (dense mode, no exchange): one warp per row, so a row's loads are all in flight together, its sum of
+    // squares needs one warp reduction, and pass B touches only slots the same lane wrote - no CTA barrier per row.
 #pragma unroll 1
-  for (int j = 0; j < (grouped ? 0 : rows_to_stage); ++j) {
+    for (int j = warp; j < rows_to_stage; j += NWARPS) {
+      __half* dst = xs + (long long)j * XS;
+      float ss = 0.f;
+#pragma unroll 4
+      for (int k = lane * 8; k < stage_k; k += 256) {
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (k < p.Kx) {
+          const long long src = (long long)(m0 + j) * p.ldx + k;
+          const uint4 xv = *reinterpret_cast<const uint4*>(xg + src);
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            v[2 * e] = __uint_as_float(xw[e] << 16);
+            v[2 * e + 1] = __uint_as_float(xw[e] & 0xffff0000u);
+          }
+          if (dg != nullptr) {
+            const uint4 dv = *reinterpret_cast<const uint4*>(dg + src);
+            const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              v[2 * e] = __bfloat162float(__float2bfloat16(v[2 * e] + __uint_as_float(dw[e] << 16)));
+              v[2 * e + 1] = __bfloat162float(__float2bfloat16(v[2 * e + 1] + __uint_as_float(dw[e] & 0xffff0000u)));
+            }
+            if (ro != nullptr && blockIdx.x == 0) {
+              uint4 o;
+              o.x = (__float_as_uint(v[0]) >> 16) | (__float_as_uint(v[1]) & 0xffff0000u);
+              o.y = (__float_as_uint(v[2]) >> 16) | (__float_as_uint(v[3]) & 0xffff0000u);
+              o.z = (__float_as_uint(v[4]) >> 16) | (__float_as_uint(v[5]) & 0xffff0000u);
+              o.w = (__float_as_uint(v[6]) >> 16) | (__float_as_uint(v[7]) & 0xffff0000u);
+              *reinterpret_cast<uint4*>(ro + (long long)(m0 + j) * p.Kx + k) = o;
+            }
+          }
+        }
+        __half* blk = dst + (k & ~31) + ((k >> 4) & 1) * 4 + ((k >> 3) & 1) * 2;
+        if (nw != nullptr) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt)
+            *reinterpret_cast<uint32_t*>(blk + tt * 8) = (__float_as_uint(v[2 * tt]) >> 16) | (__float_as_uint(v[2 * tt + 1]) & 0xffff0000u);
+        } else {
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt)
+            *reinterpret_cast<__half2*>(blk + tt * 8) = __floats2half2_rn(fminf(fmaxf(v[2 * tt], -65504.f), 65504.f),
+                                                                          fminf(fmaxf(v[2 * tt + 1], -65504.f), 65504.f));
+        }
+      }
+      if (nw != nullptr) {
+        const float rs = rsqrtf(warp_sum(ss) / (float)p.Kx + p.eps);
+#pragma unroll 4
+        for (int k = lane * 8; k < p.Kx; k += 256) {
+          const uint4 nv = *reinterpret_cast<const uint4*>(nw + k);
+          const uint32_t nww[4] = {nv.x, nv.y, nv.z, nv.w};
+          __half* blk = dst + (k & ~31) + ((k >> 4) & 1) * 4 + ((k >> 3) & 1) * 2;
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt) {
+            const uint32_t bits = *reinterpret_cast<const uint32_t*>(blk + tt * 8);
+            float a = __bfloat162float(__float2bfloat16(__uint_as_float(bits << 16) * rs * __uint_as_float(nww[tt] << 16)));
+            float b = __bfloat162float(__float2bfloat16(__uint_as_float(bits & 0xffff0000u) * rs * __uint_as_float(nww[tt] & 0xffff0000u)));
+            a = fminf(fmaxf(a, -65504.f), 65504.f);
+            b = fminf(fmaxf(b, -65504.f), 65504.f);
+            *reinterpret_cast<__half2*>(blk + tt * 8) = __floats2half2_rn(a, b);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll 1
+  for (int j = 0; j < ((grouped || MB > 1) ? 0 : rows_to_stage); ++j) {
     float ss = 0.f;
     __half* dst = xs + (long long)j * XS;
 #pragma unroll 1
@@ -385,7 +461,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
       if (lane == 0) ss_red[warp][j] = ss;
     }
   }
-  if (!grouped && nw != nullptr) {
+  if (!grouped && MB == 1 && nw != nullptr) {
     __syncthreads();
     if (tid < rows_to_stage) {
       float tot = 0.f;
@@ -434,10 +510,14 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
     const int gmask = gs - 1;
     const int cpg_mask = (1 << cpg_shift) - 1;
     const __half* xbase = xs + min(g, mt - 1) * ((p.mode == 2) ? 0 : XS) + t * 8;
+    // row blocks beyond the first: element offset of this lane's row (clamped to the last staged row) from xbase
+    int xoff[MB];
+#pragma unroll
+    for (int b = 0; b < MB; ++b) xoff[b] = (min(b * 8 + g, mt - 1) - min(g, mt - 1)) * XS;
     const FastDiv od_div = divs.od;
     const unsigned char* ring_q_gen = smem_raw + (ring_q - smem_u32(smem_raw));
     const unsigned char* ring_s_gen = smem_raw + (ring_s - smem_u32(smem_raw));
-    int c_cnt = 0, c_run = 0, c_cc = 0, c_tsel = 0, c_slot = 0, c_rt0 = 0;
+    int c_cnt = 0, c_run = 0, c_cc = 0, c_tsel = 0, c_slot = 0, c_rt0 = 0, ebuf = 0;
     float mult = 0.f;
     const __half* xp = xbase;
     const uint32_t* c_s = nullptr;
@@ -486,9 +566,13 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
         __syncthreads();
         xbase = xs + min(g, mt - 1) * XS + t * 8;
       }
-      float accg[4] = {0.f, 0.f, 0.f, 0.f};    // tile 0 of the unit
-      float accu[4] = {0.f, 0.f, 0.f, 0.f};    // tile 1 (the up half when the SwiGLU epilogue is fused)
-      float gacc[4] = {0.f, 0.f, 0.f, 0.f};
+      float accg[MB][4];    // tile 0 of the unit
+      float accu[MB][4];    // tile 1 (the up half when the SwiGLU epilogue is fused)
+      float gacc[MB][4];
+#pragma unroll
+      for (int b = 0; b < MB; ++b)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) accg[b][e] = accu[b][e] = gacc[b][e] = 0.f;
       uint32_t s2 = 0;
 #pragma unroll 1
       for (int v = 0; v < cv; v += CPI) {
@@ -514,9 +598,14 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
 #pragma unroll
         for (int c = 0; c < CPI; ++c) {
           const uint32_t qq[4] = {wq[c].x, wq[c].y, wq[c].z, wq[c].w};
-          const uint4 xv0 = *reinterpret_cast<const uint4*>(xp + c * 64);
-          const uint4 xv1 = *reinterpret_cast<const uint4*>(xp + c * 64 + 32);
-          const uint32_t bb[8] = {xv0.x, xv0.y, xv0.z, xv0.w, xv1.x, xv1.y, xv1.z, xv1.w};
+          uint32_t bb[MB][8];
+#pragma unroll
+          for (int b = 0; b < MB; ++b) {
+            const uint4 xv0 = *reinterpret_cast<const uint4*>(xp + xoff[b] + c * 64);
+            const uint4 xv1 = *reinterpret_cast<const uint4*>(xp + xoff[b] + c * 64 + 32);
+            bb[b][0] = xv0.x; bb[b][1] = xv0.y; bb[b][2] = xv0.z; bb[b][3] = xv0.w;
+            bb[b][4] = xv1.x; bb[b][5] = xv1.y; bb[b][6] = xv1.z; bb[b][7] = xv1.w;
+          }
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
             if (!BIG_GROUPS) {
@@ -525,25 +614,29 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
             }
             uint32_t a0, a1, a2, a3;
             e2m1x8_to_f16x2(qq[ks], a0, a1, a2, a3);
-            mma_f16_16816(gacc, a0, a1, a2, a3, bb[2 * ks], bb[2 * ks + 1]);
+#pragma unroll
+            for (int b = 0; b < MB; ++b) mma_f16_16816(gacc[b], a0, a1, a2, a3, bb[b][2 * ks], bb[b][2 * ks + 1]);
             // group complete: apply its scale to the group accumulator in fp32 (big groups: once per trip at most)
             const bool flush = BIG_GROUPS ? (c == CPI - 1 && ks == 3 && (((c_cc + CPI) & cpg_mask) == 0))
                                           : (((c_cc * 64 + ks * 16 + 16) & gmask) == 0);
             if (flush) {
               const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&s2));
               const float slo = sf.x * mult, shi = sf.y * mult;
-              if (c_tsel == 0) {
-                accg[0] = fmaf(gacc[0], slo, accg[0]);
-                accg[1] = fmaf(gacc[1], slo, accg[1]);
-                accg[2] = fmaf(gacc[2], shi, accg[2]);
-                accg[3] = fmaf(gacc[3], shi, accg[3]);
-              } else {
-                accu[0] = fmaf(gacc[0], slo, accu[0]);
-                accu[1] = fmaf(gacc[1], slo, accu[1]);
-                accu[2] = fmaf(gacc[2], shi, accu[2]);
-                accu[3] = fmaf(gacc[3], shi, accu[3]);
+#pragma unroll
+              for (int b = 0; b < MB; ++b) {
+                if (c_tsel == 0) {
+                  accg[b][0] = fmaf(gacc[b][0], slo, accg[b][0]);
+                  accg[b][1] = fmaf(gacc[b][1], slo, accg[b][1]);
+                  accg[b][2] = fmaf(gacc[b][2], shi, accg[b][2]);
+                  accg[b][3] = fmaf(gacc[b][3], shi, accg[b][3]);
+                } else {
+                  accu[b][0] = fmaf(gacc[b][0], slo, accu[b][0]);
+                  accu[b][1] = fmaf(gacc[b][1], slo, accu[b][1]);
+                  accu[b][2] = fmaf(gacc[b][2], shi, accu[b][2]);
+                  accu[b][3] = fmaf(gacc[b][3], shi, accu[b][3]);
+                }
+                gacc[b][0] = gacc[b][1] = gacc[b][2] = gacc[b][3] = 0.f;
               }
-              gacc[0] = gacc[1] = gacc[2] = gacc[3] = 0.f;
             }
           }
         }
@@ -555,54 +648,59 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8) ? 2 : 1) fp4_gemv_k
       // ---- reduction over the warps of the group and epilogue of this unit.  `red` is double buffered by unit
       // parity, so one group barrier per unit is enough: a warp can only overwrite a buffer after passing the
       // barrier of the unit in between, which the readers of that buffer reach after they are done with it.
-      const int buf = it & 1;
-      {
-        float* r = &red[buf][warp][0][0];
-        r[g * 8 + 2 * t] = accg[0];
-        r[g * 8 + 2 * t + 1] = accg[1];
-        r[(g + 8) * 8 + 2 * t] = accg[2];
-        r[(g + 8) * 8 + 2 * t + 1] = accg[3];
-        if (NT == 2) {
-          r += 128;
-          r[g * 8 + 2 * t] = accu[0];
-          r[g * 8 + 2 * t + 1] = accu[1];
-          r[(g + 8) * 8 + 2 * t] = accu[2];
-          r[(g + 8) * 8 + 2 * t + 1] = accu[3];
-        }
-      }
-      if (wpt > 1) group_bar(1 + grp, wpt * 32);
-      else __syncwarp();
       if (cv == 0) {   // a warp without chunks of its own still needs the unit of its group for the epilogue
         const GemvLoc L = gemv_locate(p, ge, it, 0);
         c_slot = L.slot;
         c_rt0 = L.rt0;
       }
       const int w0 = grp * wpt;
-      for (int o = wi * 32 + lane; o < 16 * 8; o += wpt * 32) {
-        const int row = o >> 3, col = o & 7;
-        if (col >= mt) continue;
-        float v = 0.f;
-#pragma unroll 4
-        for (int w2 = 0; w2 < wpt; ++w2) v += red[buf][w0 + w2][0][o];
-        const long long orow = (p.mode == 1) ? (long long)token * S + c_slot : (long long)(m0 + col);
-        if (grouped && p.expert_w != nullptr) {
-          const int pair = __ldg(p.row_order + orow);
-          v *= (pair >= 0) ? __ldg(p.expert_w + pair) : 0.f;
+#pragma unroll
+      for (int b = 0; b < MB; ++b) {
+        if (b * 8 >= mt) break;
+        const int buf = ebuf;         // alternates per executed block epilogue (see the note on `red` above)
+        ebuf ^= 1;
+        {
+          float* r = &red[buf][warp][0][0];
+          r[g * 8 + 2 * t] = accg[b][0];
+          r[g * 8 + 2 * t + 1] = accg[b][1];
+          r[(g + 8) * 8 + 2 * t] = accg[b][2];
+          r[(g + 8) * 8 + 2 * t + 1] = accg[b][3];
+          if (NT == 2) {
+            r += 128;
+            r[g * 8 + 2 * t] = accu[b][0];
+            r[g * 8 + 2 * t + 1] = accu[b][1];
+            r[(g + 8) * 8 + 2 * t] = accu[b][2];
+            r[(g + 8) * 8 + 2 * t + 1] = accu[b][3];
+          }
         }
-        const int n = c_rt0 * 16 + row;
-        if (p.act == 1) {
-          float u = 0.f;
+        if (wpt > 1) group_bar(1 + grp, wpt * 32);
+        else __syncwarp();
+        for (int o = wi * 32 + lane; o < 16 * 8; o += wpt * 32) {
+          const int row = o >> 3, col = b * 8 + (o & 7);
+          if (col >= mt) continue;
+          float v = 0.f;
 #pragma unroll 4
-          for (int w2 = 0; w2 < wpt; ++w2) u += red[buf][w0 + w2][1][o];
-          if (n < (p.N >> 1)) out[orow * p.ldo + n] = __float2bfloat16(silu(v) * u);
-        } else if (n < p.N) {
-          if (tp_out) {
-            // tensor-parallel producer: this rank's partial goes straight into every peer's receive buffer
-            tp_push(tout, orow * p.N + n, v);
-          } else {
-            if (p.bias) v += __bfloat162float(reinterpret_cast<const bf16*>(p.bias)[n]);
-            if (p.out_add) v += __bfloat162float(reinterpret_cast<const bf16*>(p.out_add)[orow * p.ldo + n]);
-            out[orow * p.ldo + n] = __float2bfloat16(v);
+          for (int w2 = 0; w2 < wpt; ++w2) v += red[buf][w0 + w2][0][o];
+          const long long orow = (p.mode == 1) ? (long long)token * S + c_slot : (long long)(m0 + col);
+          if (grouped && p.expert_w != nullptr) {
+            const int pair = __ldg(p.row_order + orow);
+            v *= (pair >= 0) ? __ldg(p.expert_w + pair) : 0.f;
+          }
+          const int n = c_rt0 * 16 + row;
+          if (p.act == 1) {
+            float u = 0.f;
+#pragma unroll 4
+            for (int w2 = 0; w2 < wpt; ++w2) u += red[buf][w0 + w2][1][o];
+            if (n < (p.N >> 1)) out[orow * p.ldo + n] = __float2bfloat16(silu(v) * u);
+          } else if (n < p.N) {
+            if (tp_out) {
+              // tensor-parallel producer: this rank's partial goes straight into every peer's receive buffer
+              tp_push(tout, orow * p.N + n, v);
+            } else {
+              if (p.bias) v += __bfloat162float(reinterpret_cast<const bf16*>(p.bias)[n]);
+              if (p.out_add) v += __bfloat162float(reinterpret_cast<const bf16*>(p.out_add)[orow * p.ldo + n]);
+              out[orow * p.ldo + n] = __float2bfloat16(v);
+            }
           }
         }
       }
@@ -756,12 +854,17 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   const int n_rt = (p.N + 15) / 16;
   size_t smem;
   dim3 grid;
-  int mrows = 8;
+  int mrows = 8, mb = 1;
   if (p.mode == 0) {
-    // token rows staged per CTA: up to 8, fewer when 8 rows of this K would not leave room for the weight rings
+    // token rows staged per CTA: up to 8 per row block; 2 or 4 row blocks (one CTA per SM) when more than 8 tokens come
+    // and their rows fit beside the weight rings; fewer than 8 rows when K is so large that 8 do not fit
     const size_t row_bytes = (size_t)(p.K + 32) * 2;
+    const size_t ring_bytes = (size_t)8 * kRing * (512 + 128);
+    if (p.M > 8 && 16 * row_bytes + ring_bytes <= 204 * 1024) mb = 2;
+    if (p.tpx.in_buf != nullptr || p.tpx.out_peer_slots != nullptr) mb = 1;       // the exchange paths are decode-size
+    mrows = 8 * mb;
     const size_t budget = 170 * 1024 - (size_t)16 * kRing * (512 + 128);
-    while (mrows > 1 && (size_t)mrows * row_bytes > budget) mrows >>= 1;
+    while (mb == 1 && mrows > 1 && (size_t)mrows * row_bytes > budget) mrows >>= 1;
     const int mt = p.M < mrows ? p.M : mrows;
     smem = (size_t)mt * row_bytes;
     grid.y = (p.M + mrows - 1) / mrows;
@@ -786,8 +889,8 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   const int k_units = chunks / ((gs >= 64) ? (gs >> 6) : 1);      // indivisible pieces of the K axis
   // Warps per unit: as many as keep every warp of the machine busy (148 SMs x 16 warps) while a warp still owns
   // at least two 64-wide chunks of a tile.
-  const int warp_slots = 148 * 16 / (int)grid.y;
-  int wpt = 16;
+  const int warp_slots = 148 * ((mb > 1) ? 8 : 16) / (int)grid.y;
+  int wpt = (mb > 1) ? 8 : 16;
   while (wpt > 1 && ((long long)n_units * wpt > warp_slots || k_units < wpt || chunks < 2 * wpt)) wpt >>= 1;
   if (p.mode == 3) {
     // many units per CTA: a warp should own at least a ring's worth of chunks per unit; 8-warp CTAs, two per SM
@@ -811,7 +914,7 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   const int nw = (wpt == 16) ? 16 : 8;
   const int G = nw / wpt;
   const int cta_units = (n_units + G - 1) / G;                   // CTAs needed for one unit per group
-  int cap = ((nw == 8) ? 296 : 148) / (int)grid.y;               // CTAs of one wave
+  int cap = ((nw == 8 && mb == 1) ? 296 : 148) / (int)grid.y;    // CTAs of one wave
   if (cap < 1) cap = 1;
   const int passes = (cta_units + cap - 1) / cap;
   grid.x = (cta_units + passes - 1) / passes;
@@ -821,26 +924,28 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   }
   // dynamic shared memory: the staged activation rows, then every warp's weight ring (512 + 128 bytes per slot)
   smem = ((smem + 127) & ~(size_t)127) + (size_t)nw * kRing * (512 + 128);
-  if (smem > 180 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > (size_t)((mb > 1) ? 206 : 180) * 1024) return (int)cudaErrorInvalidValue;
   GemvDivs divs;
   divs.tps.set((p.act == 1) ? n_rt / 2 : n_rt);
   divs.kc.set(p.K / 64);
   divs.od.set(p.order_div > 0 ? p.order_div : 1);
   int e;
-#define MMB_LAUNCH_GEMV(GM_, NW, GR)                                                                \
-  do {                                                                                              \
-    if ((e = set_smem(fp4_gemv_kernel<GM_, NW, GR>, smem, 34 * 1024))) return e;                              \
-    return launch(fp4_gemv_kernel<GM_, NW, GR>, grid, dim3(NW * 32), smem, stream, 1, p, wpt, mrows, divs);  \
+#define MMB_LAUNCH_GEMV(GM_, NW, GR, MB_)                                                                     \
+  do {                                                                                                        \
+    if ((e = set_smem(fp4_gemv_kernel<GM_, NW, GR, MB_>, smem, 34 * 1024))) return e;                                   \
+    return launch(fp4_gemv_kernel<GM_, NW, GR, MB_>, grid, dim3(NW * 32), smem, stream, 1, p, wpt, mrows, divs);  \
   } while (0)
-#define MMB_LAUNCH_GEMV_GM(NW, GR)                 \
-  do {                                             \
-    if (gm == 2) MMB_LAUNCH_GEMV(2, NW, GR);       \
-    if (gm == 1) MMB_LAUNCH_GEMV(1, NW, GR);       \
-    MMB_LAUNCH_GEMV(0, NW, GR);                    \
+#define MMB_LAUNCH_GEMV_GM(NW, GR, MB_)                 \
+  do {                                                  \
+    if (gm == 2) MMB_LAUNCH_GEMV(2, NW, GR, MB_);       \
+    if (gm == 1) MMB_LAUNCH_GEMV(1, NW, GR, MB_);       \
+    MMB_LAUNCH_GEMV(0, NW, GR, MB_);                    \
   } while (0)
-  if (p.mode == 3) MMB_LAUNCH_GEMV_GM(8, true);
-  if (nw == 8) MMB_LAUNCH_GEMV_GM(8, false);
-  MMB_LAUNCH_GEMV_GM(16, false);
+  if (p.mode == 3) MMB_LAUNCH_GEMV_GM(8, true, 1);
+  if (mb == 4) MMB_LAUNCH_GEMV_GM(8, false, 4);
+  if (mb == 2) MMB_LAUNCH_GEMV_GM(8, false, 2);
+  if (nw == 8) MMB_LAUNCH_GEMV_GM(8, false, 1);
+  MMB_LAUNCH_GEMV_GM(16, false, 1);
 #undef MMB_LAUNCH_GEMV_GM
 #undef MMB_LAUNCH_GEMV
 }

@@ -22,6 +22,7 @@ from .weights import FP4ExpertBank, FP4Weight  # noqa: F401
 _FORCE_REF = os.environ.get("MMB200_FORCE_TORCH", "0") == "1"
 _native_ok = False
 GEMV_MAX_M = 32          # dense projections: at or below this many tokens the weight-streaming GEMV path is used
+GEMV_FUSED_PROLOGUE_MAX_M = 8   # ... with the residual add + RMSNorm fused into its staging up to this many tokens
 ROUTER_GEMM_MIN_T = 64   # above this many tokens the gate logits come from the bf16 tcgen05 GEMM
 MOE_GEMV_MAX_T = 16      # MoE: per-(token, slot) streaming up to this many tokens
 MOE_GROUPED_GEMV_MAX_T = 128   # ... expert-sorted 8-row tiles on the streaming kernel up to here, grouped tcgen05 GEMMs above
@@ -154,6 +155,17 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
     if out is None:
         out = torch.empty(M, n_out, dtype=torch.bfloat16, device=x.device)
     if M <= GEMV_MAX_M or NO_TCGEN05:
+        if M > GEMV_FUSED_PROLOGUE_MAX_M and tpx is None and delta is not None:
+            # every CTA of the streaming kernel stages all its token rows: with many rows the residual add (+ norm, + the
+            # residual write) is cheaper done once in its own launch than repeated by every CTA; a norm alone stays fused
+            xin = torch.empty(M, x.shape[1], dtype=torch.bfloat16, device=x.device)
+            if norm_w is not None:
+                K.mmb200.rmsnorm(x, delta, norm_w, xin, resid_out, eps)
+            else:
+                K.mmb200.add(x.contiguous(), delta.contiguous(), xin)
+                if resid_out is not None:
+                    resid_out.copy_(xin)
+            x, delta, norm_w, resid_out = xin, None, None, None
         if (x.data_ptr() & 15) or (x.stride(0) & 7) or (W.in_features & 7):
             x = x[:, : W.in_features].contiguous()      # the kernel stages activations with 16-byte loads
             if delta is not None:

@@ -30,7 +30,7 @@ def test_native_library_loaded():
     assert hasattr(torch.ops.mmb200, "fp4_gemv")
 
 
-@pytest.mark.parametrize("M", [1, 2, 7, 8, 11, 16])
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 11, 16, 17, 25, 32])        # above 8 tokens: 2 / 4 row blocks per CTA
 @pytest.mark.parametrize("N,K,gs", [(768, 2048, 128), (2048, 5120, 128), (576, 768, 128), (48, 192, 64), (16, 64, 32),
                                     (1344, 2048, 128), (9472, 2048, 128)])
 def test_fp4_gemv_matches_reference(M, N, K, gs):
@@ -62,7 +62,7 @@ def test_fp4_gemv_zero_input_and_determinism():
     assert torch.equal(ops.linear(x, W), ops.linear(x, W))
 
 
-@pytest.mark.parametrize("M", [1, 5, 16])
+@pytest.mark.parametrize("M", [1, 5, 16, 27, 32])
 def test_fp4_gemv_fused_prologue_epilogue(M):
     K, N = 1024, 512
     W = FP4Weight.from_float(torch.randn(N, K, device=DEV) * 0.03, 128)
