@@ -156,8 +156,9 @@ __device__ __forceinline__ GemvLoc gemv_locate(const MmbFp4GemvParams& p, const 
 // is bound by instruction issue, not by DRAM).
 //
 // MB row blocks (dense mode only): a CTA holds 8 * MB token rows and every expanded weight fragment feeds MB MMAs, one per
-// block of 8 rows, so the expansion - the bulk of the instructions - is paid once for up to 32 tokens.  The accumulators
-// of MB = 2 / 4 need more registers than two resident 8-warp CTAs leave, so those variants run one CTA per SM.
+// block of 8 rows, so the expansion - the bulk of the instructions - is paid once for 16 tokens (MB = 2; four blocks
+// measured slower: staging 32 rows per CTA costs more than the expansion saved).  The extra accumulators need more
+// registers than two resident 8-warp CTAs leave, so that variant runs one CTA per SM.
 template <int GM, int NWARPS, bool GROUPED, int MB>
 __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8 && MB == 1) ? 2 : 1) fp4_gemv_kernel(const MmbFp4GemvParams p, const int wpt, const int mrows, const GemvDivs divs) {
   static_assert(MB == 1 || (!GROUPED && NWARPS == 8), "row blocks exist for the dense 8-warp kernel");
@@ -856,8 +857,8 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
   dim3 grid;
   int mrows = 8, mb = 1;
   if (p.mode == 0) {
-    // token rows staged per CTA: up to 8 per row block; 2 or 4 row blocks (one CTA per SM) when more than 8 tokens come
-    // and their rows fit beside the weight rings; fewer than 8 rows when K is so large that 8 do not fit
+    // token rows staged per CTA: up to 8 per row block; 2 row blocks (one CTA per SM) when more than 8 tokens come and
+    // their rows fit beside the weight rings; fewer than 8 rows when K is so large that 8 do not fit
     const size_t row_bytes = (size_t)(p.K + 32) * 2;
     const size_t ring_bytes = (size_t)8 * kRing * (512 + 128);
     if (p.M > 8 && 16 * row_bytes + ring_bytes <= 204 * 1024) mb = 2;
@@ -942,7 +943,6 @@ MMB_API int mmb_fp4_gemv(const MmbFp4GemvParams* pp, cudaStream_t stream) {
     MMB_LAUNCH_GEMV(0, NW, GR, MB_);                    \
   } while (0)
   if (p.mode == 3) MMB_LAUNCH_GEMV_GM(8, true, 1);
-  if (mb == 4) MMB_LAUNCH_GEMV_GM(8, false, 4);
   if (mb == 2) MMB_LAUNCH_GEMV_GM(8, false, 2);
   if (nw == 8) MMB_LAUNCH_GEMV_GM(8, false, 1);
   MMB_LAUNCH_GEMV_GM(16, false, 1);
