@@ -43,6 +43,7 @@ def _args():
     ap.add_argument("--parallelism", default="auto", choices=["auto", "tp", "dp"])
     ap.add_argument("--extra", action="store_true", help="also measure batch 32 and prefill (TTFT)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"], help="paged KV cache element type (fp8: E4M3 + per-row scale)")
     ap.add_argument("--no-graph", action="store_true", help="launch the decode step kernel by kernel (profiling)")
     return ap.parse_args()
 
@@ -184,7 +185,7 @@ def main():
     def run_config(batch: int, steps: int, warmup: int, e2e: bool):
         total_len = args.prompt_len + warmup + steps * (2 if e2e else 1) + 8
         nb = (total_len + block_size - 1) // block_size
-        kv = lm.new_cache(batch * nb, block_size)
+        kv = lm.new_cache(batch * nb, block_size, kv_dtype=args.kv_dtype)
         use_tp, run_model = state["tp"], state["model"]
         g = torch.Generator().manual_seed(args.seed + (0 if use_tp else rank))     # tensor-parallel ranks share the batch
         prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(batch)]
@@ -271,7 +272,7 @@ def main():
         "config": {"model": f"{args.model} (random-init, RTN MMFP4 group 128)", "global_batch": replicas * args.batch,
                    "seq_len": args.prompt_len,
                    "parallelism": (f"tp{world} (in-kernel NVLink exchange)" if use_tp else f"dp{world}") if world > 1 else "single",
-                   "kv": "paged latent MLA, 16-token blocks", "decode": "greedy, CUDA graph per step",
+                   "kv": f"paged, 16-token blocks, {args.kv_dtype}", "decode": "greedy, CUDA graph per step",
                    "l2_policy": "inputs larger than L2 (each step streams >2 GB of weights)",
                    "weights_gb_per_gpu": round(state["model"].weight_bytes() / 1e9, 2), "build_s": round(build_s, 1)},
         "clocks": r["clocks"],

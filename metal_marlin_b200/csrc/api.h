@@ -91,6 +91,15 @@ int mmb_embedding(const void* table, const int64_t* ids, void* out, int n, int d
 int mmb_rope(void* q, void* k, const int* positions, const float* inv_freq, int T, int Hq, int Hk, int D,
              int rot_dim, int ldq, int ldk, int interleaved, float mscale, cudaStream_t stream);
 // Per-head RMSNorm (Qwen3 q/k norm) fused with RoPE, then K/V scatter into a paged pool.
+// FP8 variant of the K / V scatter: pools of E4M3 bytes plus one fp32 scale (row amax / 448) per (slot, head).
+int mmb_qk_norm_rope_cache_fp8(void* q, const void* k, const void* v, const void* qn_w, const void* kn_w, const int* positions,
+                               const float* inv_freq, const int64_t* slots, void* k_pool, void* v_pool, float* k_scale,
+                               float* v_scale, int T, int Hq, int Hk, int D, int ldqkv, float eps, int interleaved,
+                               cudaStream_t stream);
+// Paged FP8 rows -> contiguous bf16 rows (prompt passes over a quantized cache): out[cu_k[b] + t, h, :] = pool row of token t
+// of sequence b times its scale.
+int mmb_kv_fp8_gather(const void* pool, const float* scale, const int* block_tables, const int* ctx_lens, const int* cu_k,
+                      void* out, int B, int Hkv, int D, int block_size, int max_blocks, int max_ctx, cudaStream_t stream);
 int mmb_qk_norm_rope_cache(void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
                            const int* positions, const float* inv_freq, const int64_t* slots, void* k_pool,
                            void* v_pool, int T, int Hq, int Hk, int D, int ldqkv, float eps, int interleaved,
@@ -113,6 +122,7 @@ typedef struct {
   float eps, mscale;
   int interleaved;
   int skip_absorb;          // 1: leave q_full[:, :, :R] untouched (prefill uses the non-absorbed form), only RoPE + cache write
+  float* cache_scale;       // FP8 cache: cache holds E4M3 bytes [num_slots, R + dr], cache_scale fp32 [num_slots] the row's scale
 } MmbMlaPrepParams;
 int mmb_mla_prep(const MmbMlaPrepParams* p, cudaStream_t stream);
 
@@ -129,6 +139,10 @@ typedef struct {
   float scale;
   int window;               // 0 = full; >0 = attend to the last `window` tokens only
   int* status;              // optional device word: set non-zero when a bounded wait inside the kernel expired
+  // FP8 (E4M3) pools: k_pool / v_pool hold one byte per element and k_scale / v_scale fp32 [num_slots, Hkv] the scale of
+  // every (token, head) row; rows are expanded to bf16 in shared memory after they land.  Null scales = bf16 pools.
+  const float* k_scale;
+  const float* v_scale;
 } MmbPagedDecodeParams;
 int mmb_paged_decode(const MmbPagedDecodeParams* p, cudaStream_t stream);
 // Merge the split partials; optional per-head up projection W_uv [Hq, dvo, dv] (MLA), output bf16 [B, Hq, dvo or dv].

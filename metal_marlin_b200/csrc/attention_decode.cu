@@ -138,7 +138,35 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const MmbMlaPrepParams p)
       }
       ss = block_sum(ss, red);
       const float rs = rsqrtf(ss / (float)p.R + p.eps);
-      if (slot >= 0) {
+      if (p.cache_scale != nullptr) {
+        // FP8 cache: the finished row (bf16-rounded like the bf16 cache would hold it) goes back to shared memory, its
+        // amax gives the scale, then E4M3 bytes.  All threads take this branch together (slot is per token).
+        float amax = 0.f;
+        for (int d = tid; d < p.R; d += 256) {
+          const float v = __bfloat162float(__float2bfloat16(sm[d] * rs * __bfloat162float(nw[d])));
+          sm[d] = v;
+          amax = fmaxf(amax, fabsf(v));
+        }
+        const int half = p.dr / 2;
+        for (int f = tid; f < half; f += 256) {
+          float sn, cs;
+          sincosf((float)p.positions[tk] * p.inv_freq[f], &sn, &cs);
+          const int ia = p.interleaved ? 2 * f : f, ib = p.interleaved ? 2 * f + 1 : f + half;
+          const float a = __bfloat162float(src[p.R + ia]), b = __bfloat162float(src[p.R + ib]);
+          const float ra = __bfloat162float(__float2bfloat16((a * cs - b * sn) * p.mscale));
+          const float rb = __bfloat162float(__float2bfloat16((b * cs + a * sn) * p.mscale));
+          sm[p.R + ia] = ra;
+          sm[p.R + ib] = rb;
+          amax = fmaxf(amax, fmaxf(fabsf(ra), fabsf(rb)));
+        }
+        amax = block_max(amax, red);
+        if (slot >= 0) {
+          const float sc = amax > 0.f ? amax / 448.f : 1.f, inv = 1.f / sc;
+          unsigned char* dst8 = reinterpret_cast<unsigned char*>(p.cache) + slot * dl;
+          for (int d = tid; d < dl; d += 256) dst8[d] = (unsigned char)__nv_cvt_float_to_fp8(sm[d] * inv, __NV_SATFINITE, __NV_E4M3);
+          if (tid == 0) p.cache_scale[slot] = sc;
+        }
+      } else if (slot >= 0) {
         bf16* dst = cache + slot * dl;
         for (int d = tid; d < p.R; d += 256) dst[d] = __float2bfloat16(sm[d] * rs * __bfloat162float(nw[d]));
         const int half = p.dr / 2;
@@ -179,6 +207,46 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
 
 constexpr int kTileTok = 64;
 
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem));
+}
+
+// In-place expansion of a tile of E4M3 rows (D bytes each, sitting in the upper half of bf16 rows of stride RS elements)
+// to bf16 x row scale.  Called by all NT threads of the CTA: every thread first reads its 16-byte pieces, the CTA
+// synchronizes, then the 32-byte results are written (a piece's result overlaps other pieces' source bytes).
+template <int D, int RS, int NT>
+__device__ __forceinline__ void expand_fp8_rows(bf16* rows, const float* row_scale, int nvalid, int tid) {
+  constexpr int UPR = D / 16;                               // pieces per row
+  constexpr int PER = (kTileTok * UPR + NT - 1) / NT;        // pieces per thread
+  uint4 raw[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int u = tid + i * NT, r = u / UPR, c = u - r * UPR;
+    raw[i] = make_uint4(0, 0, 0, 0);
+    if (r < nvalid) raw[i] = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(rows + r * RS) + D + c * 16);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int u = tid + i * NT, r = u / UPR, c = u - r * UPR;
+    if (r >= nvalid) continue;
+    const float sc = row_scale[r];
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+    uint32_t o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w[e >> 1] >> ((e & 1) * 16)) & 0xffffu), __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      const bf162 b2 = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+      o[e] = *reinterpret_cast<const uint32_t*>(&b2);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(rows + r * RS + c * 16);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+  __syncthreads();
+}
+
 // NW warps: in QK^T each warp owns 64 / NW token columns, in PV it owns DV / NW value columns.
 template <int DQK, int DV, int MT, bool SHARED_V, int NW>
 struct DecodeSmem {
@@ -195,8 +263,9 @@ struct DecodeSmem {
   static_assert((64 / NW) % 8 == 0 && (DV / NW) % 16 == 0, "each warp needs whole n8 tiles (pairs of them in PV)");
 };
 
-// grid (splits, Hkv, B), NW * 32 threads.
-template <int DQK, int DV, int MT, bool SHARED_V, int NW>
+// grid (splits, Hkv, B), NW * 32 threads.  FP8: the pools hold E4M3 bytes and a scale per (slot, head); a row's bytes land
+// in the upper half of its bf16 row in shared memory and are expanded in place (all reads, a barrier, all writes).
+template <int DQK, int DV, int MT, bool SHARED_V, int NW, bool FP8>
 __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDecodeParams p) {
   using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW>;
   constexpr int NT = NW * 32;
@@ -253,6 +322,7 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
   __shared__ __align__(8) uint64_t bar_kv[2];
   __shared__ __align__(8) uint64_t bar_q;
   __shared__ int abort_s;
+  __shared__ float scale_s[2][2][kTileTok];     // [buffer][K | V][row]
   if (tid == 0) {
     mbar_init(&bar_kv[0], 1);
     mbar_init(&bar_kv[1], 1);
@@ -268,14 +338,27 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
     const int nvalid = min(kTileTok, ctx - tok0);
     bf16* kd = buf ? k_s1 : k_s0;
     bf16* vd = buf ? v_s1 : v_s0;
-    if (tid == 0) mbar_expect_tx(&bar_kv[buf], (uint32_t)nvalid * (uint32_t)((DQK + (SHARED_V ? 0 : DV)) * 2));
+    if (tid == 0) mbar_expect_tx(&bar_kv[buf], (uint32_t)nvalid * (uint32_t)((DQK + (SHARED_V ? 0 : DV)) * (FP8 ? 1 : 2)));
     if (tid < nvalid) {
       const int tok = tok0 + tid;
       const long long slot = pow2_blocks ? (((long long)__ldg(bt + (tok >> bs_shift)) << bs_shift) + (tok & (p.block_size - 1)))
                                          : ((long long)__ldg(bt + tok / p.block_size) * p.block_size + (tok % p.block_size));
-      bulk_g2s(kd + tid * L::KS, kp + (slot * p.Hkv + hkv) * DQK, DQK * 2, &bar_kv[buf]);
-      if (!SHARED_V) bulk_g2s(vd + tid * L::VS, vp + (slot * p.Hkv + hkv) * DV, DV * 2, &bar_kv[buf]);
+      if (FP8) {
+        const long long row = slot * p.Hkv + hkv;
+        bulk_g2s(reinterpret_cast<unsigned char*>(kd + tid * L::KS) + DQK, reinterpret_cast<const unsigned char*>(p.k_pool) + row * DQK, DQK,
+                 &bar_kv[buf]);
+        cp_async_4(&scale_s[buf][0][tid], p.k_scale + row);
+        if (!SHARED_V) {
+          bulk_g2s(reinterpret_cast<unsigned char*>(vd + tid * L::VS) + DV, reinterpret_cast<const unsigned char*>(p.v_pool) + row * DV, DV,
+                   &bar_kv[buf]);
+          cp_async_4(&scale_s[buf][1][tid], p.v_scale + row);
+        }
+      } else {
+        bulk_g2s(kd + tid * L::KS, kp + (slot * p.Hkv + hkv) * DQK, DQK * 2, &bar_kv[buf]);
+        if (!SHARED_V) bulk_g2s(vd + tid * L::VS, vp + (slot * p.Hkv + hkv) * DV, DV * 2, &bar_kv[buf]);
+      }
     }
+    if (FP8) cp_async_commit();      // one group per tile from every thread, so the waits below can count groups
     if (nvalid < kTileTok) {
       constexpr int KCH = DQK / 8, VCH = DV / 8;
       for (int i = tid; i < (kTileTok - nvalid) * KCH; i += NT)
@@ -315,6 +398,10 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int buf = (tile - tile_begin) & 1;
     if (tile + 1 < tile_end) load_tile(tile + 1, buf ^ 1);
+    if (FP8) {      // this tile's scales (the group before the one just committed, if any)
+      if (tile + 1 < tile_end) cp_async_wait<1>();
+      else cp_async_wait<0>();
+    }
     bool landed = mbar_wait(&bar_kv[buf], (uint32_t)((tile - tile_begin) >> 1) & 1u, &abort_s);
     if (tile == tile_begin) landed = mbar_wait(&bar_q, 0u, &abort_s) && landed;
     if (!landed) abort_s = 1;
@@ -326,6 +413,11 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
     }
     const bf16* kt = buf ? k_s1 : k_s0;
     const bf16* vt = buf ? v_s1 : v_s0;
+    if (FP8) {
+      const int nvalid = min(kTileTok, ctx - (lo_al + tile * kTileTok));
+      expand_fp8_rows<DQK, L::KS, NT>(buf ? k_s1 : k_s0, scale_s[buf][0], nvalid, tid);
+      if (!SHARED_V) expand_fp8_rows<DV, L::VS, NT>(buf ? v_s1 : v_s0, scale_s[buf][1], nvalid, tid);
+    }
 
     // ---- S = Q K^T for this warp's token columns
     {
@@ -679,10 +771,10 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
   }
 }
 
-template <int DQK, int DV, int MT, bool SHARED_V, int NW>
-static int launch_decode(const MmbPagedDecodeParams& p, cudaStream_t stream) {
+template <int DQK, int DV, int MT, bool SHARED_V, int NW, bool FP8>
+static int launch_decode_impl(const MmbPagedDecodeParams& p, cudaStream_t stream) {
   using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW>;
-  auto kern = paged_decode_kernel<DQK, DV, MT, SHARED_V, NW>;
+  auto kern = paged_decode_kernel<DQK, DV, MT, SHARED_V, NW, FP8>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::total);
@@ -691,6 +783,14 @@ static int launch_decode(const MmbPagedDecodeParams& p, cudaStream_t stream) {
   }
   dim3 grid(p.splits, p.Hkv, p.B);
   return launch(kern, grid, dim3(NW * 32), L::total, stream, 1, p);
+}
+template <int DQK, int DV, int MT, bool SHARED_V, int NW>
+static int launch_decode(const MmbPagedDecodeParams& p, cudaStream_t stream) {
+  if (p.k_scale != nullptr) {
+    if (!SHARED_V && p.v_scale == nullptr) return (int)cudaErrorInvalidValue;
+    return launch_decode_impl<DQK, DV, MT, SHARED_V, NW, true>(p, stream);
+  }
+  return launch_decode_impl<DQK, DV, MT, SHARED_V, NW, false>(p, stream);
 }
 
 }  // namespace mmb

@@ -263,9 +263,58 @@ void qk_norm_rope_cache(Tensor q, const Tensor& k, const Tensor& v, const OptT& 
         "qk_norm_rope_cache");
 }
 
+void qk_norm_rope_cache_fp8(Tensor q, const Tensor& k, const Tensor& v, const OptT& qn_w, const OptT& kn_w, const Tensor& positions,
+                            const Tensor& inv_freq, const Tensor& slots, Tensor k_pool, Tensor v_pool, Tensor k_scale, Tensor v_scale,
+                            int64_t Hq, int64_t Hk, int64_t D, double eps, bool interleaved) {
+  check_bf16(q, "q");
+  TORCH_CHECK(q.stride(0) == k.stride(0) && q.stride(0) == v.stride(0));
+  TORCH_CHECK(positions.scalar_type() == at::kInt && slots.scalar_type() == at::kLong);
+  TORCH_CHECK(k_pool.scalar_type() == at::kByte && v_pool.scalar_type() == at::kByte && k_scale.scalar_type() == at::kFloat &&
+              v_scale.scalar_type() == at::kFloat && k_pool.is_contiguous() && v_pool.is_contiguous());
+  c10::cuda::CUDAGuard guard(q.device());
+  check(mmb_qk_norm_rope_cache_fp8(q.data_ptr(), k.data_ptr(), v.data_ptr(), cptr(qn_w), cptr(kn_w), positions.data_ptr<int>(),
+                                   inv_freq.data_ptr<float>(), slots.data_ptr<int64_t>(), k_pool.data_ptr(), v_pool.data_ptr(),
+                                   k_scale.data_ptr<float>(), v_scale.data_ptr<float>(), (int)positions.numel(), (int)Hq, (int)Hk, (int)D,
+                                   (int)q.stride(0), (float)eps, interleaved ? 1 : 0, cur_stream()),
+        "qk_norm_rope_cache_fp8");
+}
+
+// pool uint8 [num_slots, Hkv, D] + scale fp32 [num_slots, Hkv] -> out bf16 [sum ctx, Hkv, D] (rows cu_k[b] .. of sequence b)
+void kv_fp8_gather(const Tensor& pool, const Tensor& scale, const Tensor& block_tables, const Tensor& ctx_lens, const Tensor& cu_k, Tensor out,
+                   int64_t Hkv, int64_t D, int64_t block_size, int64_t max_ctx) {
+  check_bf16(out, "out");
+  TORCH_CHECK(pool.scalar_type() == at::kByte && pool.is_contiguous() && scale.scalar_type() == at::kFloat && out.is_contiguous());
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 && block_tables.is_contiguous() &&
+              ctx_lens.scalar_type() == at::kInt && cu_k.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(pool.device());
+  check(mmb_kv_fp8_gather(pool.data_ptr(), scale.data_ptr<float>(), block_tables.data_ptr<int>(), ctx_lens.data_ptr<int>(),
+                          cu_k.data_ptr<int>(), out.data_ptr(), (int)ctx_lens.numel(), (int)Hkv, (int)D, (int)block_size,
+                          (int)block_tables.size(1), (int)max_ctx, cur_stream()),
+        "kv_fp8_gather");
+}
+
+void mla_prep_impl(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
+                   const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, int64_t H, int64_t dn, int64_t dr,
+                   int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb, Tensor* cache_scale);
 void mla_prep(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
               const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, int64_t H, int64_t dn, int64_t dr,
               int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb) {
+  TORCH_CHECK(cache.scalar_type() == at::kBFloat16);
+  mla_prep_impl(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps, mscale, interleaved, skip_absorb,
+                nullptr);
+}
+// FP8 latent cache: `cache` uint8 [num_slots, R + dr] (E4M3), `cache_scale` fp32 [num_slots].
+void mla_prep_fp8(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
+                  const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, Tensor cache_scale, int64_t H, int64_t dn,
+                  int64_t dr, int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb) {
+  TORCH_CHECK(cache.scalar_type() == at::kByte && cache_scale.scalar_type() == at::kFloat && cache_scale.is_contiguous() &&
+              cache_scale.numel() == cache.size(0));
+  mla_prep_impl(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps, mscale, interleaved, skip_absorb,
+                &cache_scale);
+}
+void mla_prep_impl(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
+                   const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, int64_t H, int64_t dn, int64_t dr,
+                   int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb, Tensor* cache_scale) {
   check_bf16(q, "q");
   check_bf16(kva, "kva");
   check_bf16(w_ukT, "w_ukT");
@@ -293,14 +342,35 @@ void mla_prep(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Ten
   p.mscale = (float)mscale;
   p.interleaved = interleaved ? 1 : 0;
   p.skip_absorb = skip_absorb ? 1 : 0;
+  p.cache_scale = cache_scale ? cache_scale->data_ptr<float>() : nullptr;
   check(mmb_mla_prep(&p, cur_stream()), "mla_prep");
 }
 
+void paged_decode_impl(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& block_tables, const Tensor& ctx_lens,
+                       Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk, int64_t dv, int64_t block_size, int64_t splits,
+                       double scale, int64_t window, const Tensor* k_scale, const OptT* v_scale);
 void paged_decode(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& block_tables,
                   const Tensor& ctx_lens, Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk, int64_t dv,
                   int64_t block_size, int64_t splits, double scale, int64_t window) {
-  check_bf16(q, "q");
   check_bf16(k_pool, "k_pool");
+  paged_decode_impl(q, k_pool, v_pool, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv, block_size, splits, scale, window, nullptr,
+                    nullptr);
+}
+// FP8 pools: uint8 (E4M3) K / V pools with fp32 scales [num_slots, Hkv].
+void paged_decode_fp8(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& k_scale, const OptT& v_scale,
+                      const Tensor& block_tables, const Tensor& ctx_lens, Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk,
+                      int64_t dv, int64_t block_size, int64_t splits, double scale, int64_t window) {
+  TORCH_CHECK(k_pool.scalar_type() == at::kByte && k_scale.scalar_type() == at::kFloat && k_scale.is_contiguous());
+  TORCH_CHECK(dqk % 16 == 0 && dv % 16 == 0, "FP8 rows are copied in 16-byte pieces");
+  if (v_pool.has_value() && v_pool->defined())
+    TORCH_CHECK(v_pool->scalar_type() == at::kByte && v_scale.has_value() && v_scale->defined() && v_scale->scalar_type() == at::kFloat);
+  paged_decode_impl(q, k_pool, v_pool, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv, block_size, splits, scale, window, &k_scale,
+                    &v_scale);
+}
+void paged_decode_impl(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& block_tables, const Tensor& ctx_lens,
+                       Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk, int64_t dv, int64_t block_size, int64_t splits,
+                       double scale, int64_t window, const Tensor* k_scale, const OptT* v_scale) {
+  check_bf16(q, "q");
   TORCH_CHECK(q.is_contiguous() && k_pool.is_contiguous() && block_tables.is_contiguous() && block_tables.dim() == 2);
   TORCH_CHECK(block_tables.scalar_type() == at::kInt && ctx_lens.scalar_type() == at::kInt);
   TORCH_CHECK(part_o.scalar_type() == at::kFloat && part_ml.scalar_type() == at::kFloat);
@@ -323,6 +393,10 @@ void paged_decode(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, con
   p.splits = (int)splits;
   p.scale = (float)scale;
   p.window = (int)window;
+  if (k_scale != nullptr) {
+    p.k_scale = k_scale->data_ptr<float>();
+    if (v_scale != nullptr && v_scale->has_value() && (*v_scale)->defined()) p.v_scale = (*v_scale)->data_ptr<float>();
+  }
   TORCH_CHECK(part_o.numel() >= (int64_t)p.B * Hq * splits * dv && part_ml.numel() >= (int64_t)p.B * Hq * splits * 2);
   check(mmb_paged_decode(&p, cur_stream()), "paged_decode");
 }
@@ -875,6 +949,10 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("moe_gather", &moe_gather);
   m.def("moe_combine", &moe_combine);
   m.def("prefill_attention", &prefill_attention);
+  m.def("qk_norm_rope_cache_fp8", &qk_norm_rope_cache_fp8);
+  m.def("kv_fp8_gather", &kv_fp8_gather);
+  m.def("mla_prep_fp8", &mla_prep_fp8);
+  m.def("paged_decode_fp8", &paged_decode_fp8);
   m.def("gated_delta_step", &gated_delta_step);
   m.def("selective_scan_step", &selective_scan_step);
 }

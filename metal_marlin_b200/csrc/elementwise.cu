@@ -96,6 +96,106 @@ __global__ void rope_kernel(bf16* __restrict__ q, bf16* __restrict__ k, const in
 
 // Qwen3-style attention prologue: per-head RMSNorm of q and k (optional), RoPE, K/V scatter to a paged
 // pool [num_slots, Hk, D].  grid = (T, Hq + Hk); one warp-sized CTA per (token, head); D <= 256.
+// E4M3 byte of v / scale (saturating).
+__device__ __forceinline__ unsigned char to_e4m3(float v) {
+  return (unsigned char)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+// FP8 cache variant of the kernel below: same prologue; the K row (after norm + RoPE) and the V row are quantized to
+// E4M3 with one scale per row (amax / 448) written beside them.
+__global__ void __launch_bounds__(128) qk_norm_rope_cache_fp8_kernel(bf16* __restrict__ q, const bf16* __restrict__ k,
+                                                                     const bf16* __restrict__ v, const bf16* __restrict__ qn_w,
+                                                                     const bf16* __restrict__ kn_w, const int* __restrict__ positions,
+                                                                     const float* __restrict__ inv_freq, const int64_t* __restrict__ slots,
+                                                                     unsigned char* __restrict__ k_pool, unsigned char* __restrict__ v_pool,
+                                                                     float* __restrict__ k_scale, float* __restrict__ v_scale, int Hq,
+                                                                     int Hk, int D, int ldqkv, float eps, int interleaved) {
+  __shared__ float red[32];
+  __shared__ float vals[256];
+  const long long tkn = blockIdx.x;
+  const int h = blockIdx.y;
+  const bool is_q = h < Hq;
+  const bf16* src = is_q ? (q + tkn * ldqkv + (long long)h * D) : (k + tkn * ldqkv + (long long)(h - Hq) * D);
+  const bf16* nw = is_q ? qn_w : kn_w;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float x = __bfloat162float(src[i]);
+    vals[i] = x;
+    ss += x * x;
+  }
+  ss = block_sum(ss, red);
+  if (nw != nullptr) {
+    const float rs = rsqrtf(ss / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x)
+      vals[i] = __bfloat162float(__float2bfloat16(vals[i] * rs * __bfloat162float(nw[i])));
+  }
+  __syncthreads();
+  const float pos = (float)positions[tkn];
+  const int half = D / 2;
+  const long long slot = slots ? slots[tkn] : -1;
+  float amax = 0.f;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float sn, cs;
+    sincosf(pos * inv_freq[j], &sn, &cs);
+    const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+    float a = vals[ia], b = vals[ib];
+    rope_pair(a, b, cs, sn);
+    a = __bfloat162float(__float2bfloat16(a));
+    b = __bfloat162float(__float2bfloat16(b));
+    if (is_q) {
+      bf16* dst = q + tkn * ldqkv + (long long)h * D;
+      dst[ia] = __float2bfloat16(a);
+      dst[ib] = __float2bfloat16(b);
+    } else {
+      vals[ia] = a;      // every pair is owned by one thread: in place
+      vals[ib] = b;
+      amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+    }
+  }
+  if (is_q || slot < 0) return;
+  const long long row = slot * Hk + (h - Hq);
+  amax = block_max(amax, red);
+  {
+    const float sc = amax > 0.f ? amax / 448.f : 1.f, inv = 1.f / sc;
+    unsigned char* kd = k_pool + row * (long long)D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) kd[i] = to_e4m3(vals[i] * inv);
+    if (threadIdx.x == 0) k_scale[row] = sc;
+  }
+  if (v != nullptr) {
+    const bf16* vs = v + tkn * ldqkv + (long long)(h - Hq) * D;
+    float vmax = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) vmax = fmaxf(vmax, fabsf(__bfloat162float(vs[i])));
+    vmax = block_max(vmax, red);
+    const float sc = vmax > 0.f ? vmax / 448.f : 1.f, inv = 1.f / sc;
+    unsigned char* vd = v_pool + row * (long long)D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) vd[i] = to_e4m3(__bfloat162float(vs[i]) * inv);
+    if (threadIdx.x == 0) v_scale[row] = sc;
+  }
+}
+
+// Paged FP8 rows to contiguous bf16: grid (max_ctx, Hkv, B), one row per CTA of 64 threads (4 bytes per thread and trip).
+__global__ void __launch_bounds__(64) kv_fp8_gather_kernel(const unsigned char* __restrict__ pool, const float* __restrict__ scale,
+                                                           const int* __restrict__ block_tables, const int* __restrict__ ctx_lens,
+                                                           const int* __restrict__ cu_k, bf16* __restrict__ out, int Hkv, int D,
+                                                           int block_size, int max_blocks) {
+  const int t = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  if (t >= ctx_lens[b]) return;
+  const long long slot = (long long)block_tables[(long long)b * max_blocks + t / block_size] * block_size + t % block_size;
+  const long long row = slot * Hkv + h;
+  const float sc = scale[row];
+  const unsigned char* src = pool + row * (long long)D;
+  bf16* dst = out + ((long long)(cu_k[b] + t) * Hkv + h) * D;
+  for (int i = threadIdx.x * 4; i < D; i += 64 * 4) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(src + i);
+#pragma unroll
+    for (int e = 0; e < 4; e += 2) {
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w >> (8 * e)) & 0xffffu), __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      *reinterpret_cast<bf162*>(dst + i + e) = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(128) qk_norm_rope_cache_kernel(bf16* __restrict__ q, const bf16* __restrict__ k,
                                                                  const bf16* __restrict__ v, const bf16* __restrict__ qn_w,
                                                                  const bf16* __restrict__ kn_w,
@@ -204,5 +304,29 @@ MMB_API int mmb_qk_norm_rope_cache(void* q, const void* k, const void* v, const 
   mmb::qk_norm_rope_cache_kernel<<<grid, 128, 0, stream>>>((bf16*)q, (const bf16*)k, (const bf16*)v, (const bf16*)qn_w,
                                                            (const bf16*)kn_w, positions, inv_freq, slots, (bf16*)k_pool,
                                                            (bf16*)v_pool, Hq, Hk, D, ldqkv, eps, interleaved);
+  return (int)cudaGetLastError();
+}
+
+MMB_API int mmb_qk_norm_rope_cache_fp8(void* q, const void* k, const void* v, const void* qn_w, const void* kn_w, const int* positions,
+                                       const float* inv_freq, const int64_t* slots, void* k_pool, void* v_pool, float* k_scale,
+                                       float* v_scale, int T, int Hq, int Hk, int D, int ldqkv, float eps, int interleaved,
+                                       cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D > 256 || D % 4 || k_scale == nullptr || (v != nullptr && v_scale == nullptr)) return (int)cudaErrorInvalidValue;
+  dim3 grid(T, Hq + Hk);
+  mmb::qk_norm_rope_cache_fp8_kernel<<<grid, 128, 0, stream>>>((bf16*)q, (const bf16*)k, (const bf16*)v, (const bf16*)qn_w,
+                                                               (const bf16*)kn_w, positions, inv_freq, slots, (unsigned char*)k_pool,
+                                                               (unsigned char*)v_pool, k_scale, v_scale, Hq, Hk, D, ldqkv, eps,
+                                                               interleaved);
+  return (int)cudaGetLastError();
+}
+
+MMB_API int mmb_kv_fp8_gather(const void* pool, const float* scale, const int* block_tables, const int* ctx_lens, const int* cu_k,
+                              void* out, int B, int Hkv, int D, int block_size, int max_blocks, int max_ctx, cudaStream_t stream) {
+  if (B <= 0 || max_ctx <= 0) return 0;
+  if (D % 4 != 0 || Hkv > 65535 || B > 65535) return (int)cudaErrorInvalidValue;
+  dim3 grid(max_ctx, Hkv, B);
+  mmb::kv_fp8_gather_kernel<<<grid, 64, 0, stream>>>((const unsigned char*)pool, scale, block_tables, ctx_lens, cu_k, (bf16*)out, Hkv, D,
+                                                     block_size, max_blocks);
   return (int)cudaGetLastError();
 }

@@ -29,6 +29,7 @@ from .session import SamplingParams
 class EngineConfig:
     num_kv_blocks: int = 512
     block_size: int = 16
+    kv_cache_dtype: str = "bf16"       # "fp8": E4M3 pools with per-row scales (half the cache bytes)
     max_model_len: int = 4096
     max_num_seqs: int = 64
     max_num_batched_tokens: int = 2048
@@ -108,7 +109,7 @@ class LLMEngine:
         self.model = model
         self.cfg = config or EngineConfig()
         c = self.cfg
-        self.kv = PagedKVStorage(model.cfg, c.num_kv_blocks, c.block_size, model.device)
+        self.kv = PagedKVStorage(model.cfg, c.num_kv_blocks, c.block_size, model.device, kv_dtype=c.kv_cache_dtype)
         self.cache = PagedKVCache(c.num_kv_blocks, c.block_size, enable_prefix_cache=c.enable_prefix_cache,
                                   copy_fn=self._copy_block)
         self.scheduler = BatchScheduler(SchedulerConfig(max_num_seqs=c.max_num_seqs,
@@ -131,7 +132,7 @@ class LLMEngine:
         for pool in (self.kv.k, self.kv.v):
             for t in pool:
                 if t is not None:
-                    t[dst * bs:(dst + 1) * bs].copy_(t[src * bs:(src + 1) * bs])
+                    ops.kv_copy_rows(t, slice(dst * bs, (dst + 1) * bs), slice(src * bs, (src + 1) * bs))
 
     # ------------------------------------------------------------------ public API
     def add_request(self, req: GenerationRequest) -> RunningRequest:

@@ -89,8 +89,8 @@ class MMFP4ForCausalLM:
         return cls(build_transformer(cfg, RandomSource(cfg, device, seed)))
 
     # ------------------------------------------------------------------ cache helpers
-    def new_cache(self, num_blocks: int, block_size: int = 16) -> PagedKVStorage:
-        return PagedKVStorage(self.config, num_blocks, block_size, self.device)
+    def new_cache(self, num_blocks: int, block_size: int = 16, kv_dtype: str = "bf16") -> PagedKVStorage:
+        return PagedKVStorage(self.config, num_blocks, block_size, self.device, kv_dtype=kv_dtype)
 
     # ------------------------------------------------------------------ generation
     @torch.no_grad()

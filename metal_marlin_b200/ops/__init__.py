@@ -249,7 +249,81 @@ def rope(q, k, positions, inv_freq, Hq, Hk, D, rot_dim, interleaved=False, mscal
     return q, k
 
 
+class FP8KV:
+    """Paged KV pool in FP8 (E4M3) with one fp32 scale per cached row: ``data`` uint8 ``[num_slots, Hkv, D]`` (GQA) or
+    ``[num_slots, latent_dim]`` (MLA latent), ``scale`` fp32 ``[num_slots, Hkv | 1]`` = row amax / 448.  Indexing with slot
+    ids returns the de-quantized bf16 rows, so code that gathers rows from a bf16 pool works unchanged.
+
+    Parity: reference ``metal_marlin/kv_cache.py`` (fp8 cache mode) and ``paged_attention_v1_fp8`` / ``_v2_fp8``
+    (``src/paged_attention.metal``)."""
+
+    def __init__(self, num_slots: int, row_shape, device):
+        row_shape = tuple(row_shape)
+        self.data = torch.zeros(num_slots, *row_shape, dtype=torch.uint8, device=device)
+        self.scale = torch.ones(num_slots, row_shape[0] if len(row_shape) == 2 else 1, dtype=torch.float32, device=device)
+
+    shape = property(lambda self: self.data.shape)
+    device = property(lambda self: self.data.device)
+    dtype = torch.uint8
+
+    def view(self, *shape):
+        return self
+
+    def numel(self):
+        return self.data.numel()
+
+    def element_size(self):
+        return 1
+
+    def store(self, slots, rows):
+        """PyTorch restatement of the kernels' quantizer (rows: float ``[n, ...row_shape]``, bf16-rounded first)."""
+        r = rows.to(torch.bfloat16).float()
+        amax = r.abs().amax(-1)
+        sc = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+        q = (r * (1.0 / sc).unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+        self.data[slots] = q.view(torch.uint8)
+        self.scale[slots] = sc.reshape(sc.shape[0], -1)
+
+    def __getitem__(self, idx):
+        d = self.data[idx].view(torch.float8_e4m3fn).float()
+        sc = self.scale[idx]
+        return (d * (sc.unsqueeze(-1) if d.dim() == sc.dim() + 1 else sc)).to(torch.bfloat16)
+
+    def dequantize(self):
+        return self[torch.arange(self.data.shape[0], device=self.data.device)]
+
+
+def kv_copy_rows(pool, dst, src) -> None:
+    """``pool[dst] = pool[src]`` (slices or index tensors) for bf16 pools and FP8 pools alike (copy-on-write of cache
+    blocks, compaction of accepted speculative rows)."""
+    if isinstance(pool, FP8KV):
+        pool.data[dst] = pool.data[src].clone()
+        pool.scale[dst] = pool.scale[src].clone()
+    else:
+        pool[dst] = pool[src].clone()
+
+
+def _ref_cache_write(fn, pool_pairs, slots, n_tok):
+    """Runs a reference cache-writing op against scratch bf16 pools with identity slots, then quantizes the written rows
+    into the FP8 pools."""
+    ident = torch.where(slots >= 0, torch.arange(n_tok, device=slots.device), torch.full_like(slots, -1))
+    tmps = [torch.zeros(n_tok, *p.data.shape[1:], dtype=torch.bfloat16, device=p.data.device) for p in pool_pairs]
+    r = fn(ident, tmps)
+    ok = slots >= 0
+    for p, t in zip(pool_pairs, tmps):
+        p.store(slots[ok], t[ok])
+    return r
+
+
 def qk_norm_rope_cache(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool, v_pool, Hq, Hk, D, eps, interleaved=False):
+    if isinstance(k_pool, FP8KV):
+        if not _use_native(q):
+            _ref_cache_write(lambda sl, t: ref.qk_norm_rope_cache(q, k, v, qn_w, kn_w, positions, inv_freq, sl, t[0], t[1], Hq, Hk, D, eps,
+                                                                  interleaved), [k_pool, v_pool], slots, q.shape[0])
+            return q
+        K.mmb200.qk_norm_rope_cache_fp8(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool.data, v_pool.data, k_pool.scale,
+                                        v_pool.scale, Hq, Hk, D, eps, interleaved)
+        return q
     if not _use_native(q):
         return ref.qk_norm_rope_cache(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool, v_pool, Hq, Hk, D, eps,
                                       interleaved)
@@ -261,12 +335,35 @@ def mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache
              interleaved=True, skip_absorb=False):
     """``skip_absorb``: only RoPE the query's rope slice into ``q_full[..., R:]`` and write the new latent rows (prefill
     attends in the non-absorbed form and never needs ``q_full[..., :R]``)."""
+    if isinstance(cache, FP8KV):
+        if not _use_native(q):
+            _ref_cache_write(lambda sl, t: ref.mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, sl, q_full, t[0], H, dn, dr, R, eps,
+                                                        mscale, interleaved), [cache], slots, q.shape[0])
+            return q_full
+        K.mmb200.mla_prep_fp8(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache.data, cache.scale.view(-1), H, dn, dr, R,
+                              eps, mscale, interleaved, skip_absorb)
+        return q_full
     if not _use_native(q):
         return ref.mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps,
                             mscale, interleaved)
     K.mmb200.mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps, mscale,
                       interleaved, skip_absorb)
     return q_full
+
+
+def kv_fp8_rows(pool: "FP8KV", block_tables, ctx_lens, cu_k, total: int, max_ctx: int, block_size: int):
+    """Contiguous bf16 ``[total, Hkv, D]`` rows of the sequences described by ``block_tables`` / ``ctx_lens``."""
+    Hkv, D = (pool.data.shape[1], pool.data.shape[2]) if pool.data.dim() == 3 else (1, pool.data.shape[1])
+    out = torch.empty(total, Hkv, D, dtype=torch.bfloat16, device=pool.data.device)
+    if _use_native(pool.data) and D % 4 == 0:
+        K.mmb200.kv_fp8_gather(pool.data, pool.scale, block_tables, ctx_lens, cu_k, out, Hkv, D, block_size, max_ctx)
+        return out
+    cl, ck = ctx_lens.tolist(), cu_k.tolist()
+    for b, n in enumerate(cl):
+        tok = torch.arange(n, device=pool.data.device)
+        slots = block_tables[b, tok // block_size].long() * block_size + tok % block_size
+        out[ck[b]: ck[b] + n] = pool[slots].view(n, Hkv, D)
+    return out
 
 
 def default_splits(batch: int, n_kv_heads: int, max_ctx: int, sm_count: int = 148) -> int:
@@ -282,7 +379,10 @@ def paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, *, Hq, Hkv, dqk, 
     up-projected per head (MLA).  Returns bf16 ``[B, Hq, dvo or dv]``."""
     B = ctx_lens.numel()
     dvo = w_uv.shape[1] if w_uv is not None else dv
+    fp8 = isinstance(k_pool, FP8KV)
     if not _use_native(q):
+        if fp8:      # the oracle attends over the de-quantized pools
+            k_pool, v_pool = k_pool.dequantize(), (v_pool.dequantize() if v_pool is not None else None)
         o = ref.paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, Hq, Hkv, dqk, dv, block_size, scale, window)
         if w_uv is not None:
             o = ref.mla_up(o, w_uv)
@@ -301,8 +401,13 @@ def paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, *, Hq, Hkv, dqk, 
         part_o, part_ml = workspace
     if out is None:
         out = torch.empty(B, Hq, dvo, dtype=torch.bfloat16, device=q.device)
-    K.mmb200.paged_decode(q, k_pool, v_pool, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv, block_size,
-                          splits, scale, window)
+    if fp8:
+        K.mmb200.paged_decode_fp8(q, k_pool.data, None if v_pool is None else v_pool.data, k_pool.scale,
+                                  None if v_pool is None else v_pool.scale, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv,
+                                  block_size, splits, scale, window)
+    else:
+        K.mmb200.paged_decode(q, k_pool, v_pool, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv, block_size,
+                              splits, scale, window)
     K.mmb200.decode_merge(part_o, part_ml, w_uv, out, B, Hq, dv, dvo, splits)
     return out
 
@@ -682,6 +787,15 @@ def prefill_attention(q, k, v, cu_q, *, cu_k=None, block_tables=None, ctx_lens=N
     scale = scale if scale is not None else D ** -0.5
     if out is None:
         out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    if isinstance(k, FP8KV):
+        # prompt pass over a quantized cache: the sequences' rows are de-quantized into contiguous bf16 keys / values once
+        # (one gather launch per pool) and the kernel runs in its contiguous mode
+        lens = ctx_lens.to(torch.int64)
+        cu_k = torch.zeros(lens.numel() + 1, dtype=torch.int32, device=q.device)
+        cu_k[1:] = torch.cumsum(lens, 0)
+        total, mx = int(cu_k[-1]), int(lens.max())
+        k, v = (kv_fp8_rows(pl, block_tables, ctx_lens, cu_k, total, mx, block_size) for pl in (k, v))
+        block_tables = ctx_lens = None
     if max_q is None and (block_mask is not None or (_use_native(q) and D in PREFILL_ATTN_DIMS)):
         max_q = int((cu_q[1:] - cu_q[:-1]).max())
     if _use_native(q) and D in PREFILL_ATTN_DIMS and q.dtype == torch.bfloat16 and k.shape[-1] == D and v.shape[-1] == D:

@@ -81,6 +81,14 @@ def build_cases(dev, batch: int, ctx: int, variants: int = 1):
     cases["mla_decode_attn"] = (lambda i=0: ops.paged_attention(qf, cache[i % V], None, bt, cl, Hq=NH, Hkv=1, dqk=R + dr, dv=R,
                                                                 block_size=bs, scale=1 / 16.0, splits=splits, w_uv=w_uv[i % V]),
                                 batch * ctx * (R + dr) * 2 + w_uv[0].numel() * 2)
+    cache8 = []
+    for c in cache:       # the same latent rows in an FP8 pool (E4M3 + per-row scale)
+        p8 = ops.FP8KV(c.shape[0], (R + dr,), dev)
+        p8.store(torch.arange(c.shape[0], device=dev), c.float())
+        cache8.append(p8)
+    cases["mla_decode_attn_fp8kv"] = (lambda i=0: ops.paged_attention(qf, cache8[i % V], None, bt, cl, Hq=NH, Hkv=1, dqk=R + dr, dv=R,
+                                                                      block_size=bs, scale=1 / 16.0, splits=splits, w_uv=w_uv[i % V]),
+                                      batch * ctx * (R + dr + 4) + w_uv[0].numel() * 2)
     part_o = torch.empty(batch * NH * splits * R, dtype=torch.float32, device=dev)
     part_ml = torch.empty(batch * NH * splits * 2, dtype=torch.float32, device=dev)
     o_att = torch.empty(batch, NH, dv, dtype=torch.bfloat16, device=dev)

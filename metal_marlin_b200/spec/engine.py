@@ -13,6 +13,7 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
+from .. import ops
 from ..models.transformer import BatchMeta
 from .adaptive import AdaptiveSpeculationController, TokenAcceptanceTracker
 from .draft import DraftModel, DraftOutput, EagleDraft, MTPDraft, NGramDraft, SmallModelDraft
@@ -108,7 +109,7 @@ class SpeculativeEngine:
         for pool in (self.kv.k, self.kv.v):
             for t in pool:
                 if t is not None:
-                    t[dst] = t[src].clone()
+                    ops.kv_copy_rows(t, dst, src)
 
     # ------------------------------------------------------------------ generation
     @torch.no_grad()
