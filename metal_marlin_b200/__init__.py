@@ -53,6 +53,12 @@ _reg(".quant.mixed_precision", "policy_for", "allocate_bits", "TensorPolicy")
 _reg(".quant.pipeline", "quantize_checkpoint", "collect_hessians")
 _reg(".converters", "convert_checkpoint", "MixedFormatPack")
 _reg(".converters.gguf", "GGUFReader", "write_gguf")
+_reg(".converters.nemo", "load_nemo")
+_reg(".kv.prompt_cache", "TieredPrefixCache", "RadixPrefixCache", "PrefixCacheConfig", "StorageTier")
+_reg(".serving.batching", "RequestBatcher", "BatchConfig", "KVCacheSharing")
+_reg(".profiling.wandb_helper", "WandbHelper", "get_wandb")
+_reg(".profiling.benchmark_report", "aggregate_results", "generate_markdown_report")
+_reg(".inference.early_exit", "EarlyExitModel", "EarlyExitOutput")
 _reg(".converters.onnx", "ONNXExecutor", "ONNXGraph", "ONNXOp", "load_onnx", "save_onnx", "parse_onnx_graph", "summarize_graph",
      "detect_architecture")
 _reg(".spec.engine", "SpeculativeEngine")

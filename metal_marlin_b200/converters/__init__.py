@@ -29,6 +29,8 @@ def detect_format(path: str) -> str:
             return "gguf"
         if ext == ".onnx":
             return "onnx"
+        if ext == ".nemo":
+            return "nemo"
         if ext in (".bin", ".pt", ".pth"):
             return "pytorch"
         if ext == ".safetensors":
@@ -50,6 +52,10 @@ def _iter_source(src: str, fmt: str) -> Iterator[Tuple[str, torch.Tensor]]:
         with gguf.GGUFReader(p) as r:
             for name in r.tensor_names():
                 yield gguf.gguf_name_to_hf(name), r.load_tensor(name)
+    elif fmt == "nemo":
+        from . import nemo as _nemo
+        sd, _ = _nemo.load_nemo(src)
+        yield from sd.items()
     elif fmt == "onnx":
         # the linear weights of the graph (as [out, in]) plus every other float initializer under its own name
         from . import onnx as _onnx

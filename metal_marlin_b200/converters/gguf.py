@@ -1,7 +1,7 @@
 """GGUF reader / writer and block de-quantizers.
 
 Parity: reference ``metal_marlin/gguf_loader.py`` (header + metadata + tensor-info parsing, de-quantization of
-Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0 / Q4_K / Q6_K blocks, F16 / BF16 / F32) and ``metal_marlin/gguf_to_marlin.py``
+Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0 / Q2_K / Q4_K / Q5_K / Q6_K / IQ4_NL / IQ4_XS blocks, F16 / BF16 / F32) and ``metal_marlin/gguf_to_marlin.py``
 (GGUF -> marlin FP4 incl. MXFP4 blocks with ``e8m0`` scales).  Files are memory-mapped; tensors are de-quantized on
 demand with vectorised numpy and can then be re-quantized into this engine's formats.
 """
@@ -17,11 +17,14 @@ import torch
 GGUF_MAGIC = 0x46554747      # "GGUF" little endian
 # ggml tensor types
 F32, F16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q4_K, Q6_K, BF16, MXFP4 = 0, 1, 2, 3, 6, 7, 8, 12, 14, 30, 39
+Q2_K, Q5_K, IQ4_NL, IQ4_XS = 10, 13, 20, 23
 TYPE_NAMES = {F32: "F32", F16: "F16", Q4_0: "Q4_0", Q4_1: "Q4_1", Q5_0: "Q5_0", Q5_1: "Q5_1", Q8_0: "Q8_0", Q4_K: "Q4_K",
-              Q6_K: "Q6_K", BF16: "BF16", MXFP4: "MXFP4"}
+              Q6_K: "Q6_K", BF16: "BF16", MXFP4: "MXFP4", Q2_K: "Q2_K", Q5_K: "Q5_K", IQ4_NL: "IQ4_NL", IQ4_XS: "IQ4_XS"}
 # (elements per block, bytes per block)
 BLOCK = {F32: (1, 4), F16: (1, 2), BF16: (1, 2), Q4_0: (32, 18), Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q8_0: (32, 34),
-         Q4_K: (256, 144), Q6_K: (256, 210), MXFP4: (32, 17)}
+         Q4_K: (256, 144), Q6_K: (256, 210), MXFP4: (32, 17), Q2_K: (256, 84), Q5_K: (256, 176), IQ4_NL: (32, 18), IQ4_XS: (256, 136)}
+# non-linear 4-bit code book of the IQ4 types
+IQ4_VALUES = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.float32)
 _VT = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
 E2M1 = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6, -0.0, -0.5, -1, -1.5, -2, -3, -4, -6], dtype=np.float32)
 
@@ -94,6 +97,66 @@ def dequant_q4_k(raw: np.ndarray) -> np.ndarray:
     return (q * (d * sc)[:, :, None] - (dmin * mn)[:, :, None]).reshape(-1)
 
 
+def _k_scales(s: np.ndarray):
+    """The eight 6-bit (scale, min) pairs packed in the 12 scale bytes of a Q4_K / Q5_K super-block."""
+    sc = np.empty((s.shape[0], 8), dtype=np.float32)
+    mn = np.empty((s.shape[0], 8), dtype=np.float32)
+    for j in range(8):
+        if j < 4:
+            sc[:, j], mn[:, j] = s[:, j] & 63, s[:, j + 4] & 63
+        else:
+            sc[:, j] = (s[:, j + 4] & 0xF) | ((s[:, j - 4] >> 6) << 4)
+            mn[:, j] = (s[:, j + 4] >> 4) | ((s[:, j] >> 6) << 4)
+    return sc, mn
+
+
+def dequant_q5_k(raw: np.ndarray) -> np.ndarray:
+    blk = raw.reshape(-1, 176)
+    d, dmin = _f16(blk[:, :2].copy()).reshape(-1, 1), _f16(blk[:, 2:4].copy()).reshape(-1, 1)
+    sc, mn = _k_scales(blk[:, 4:16].astype(np.uint8))
+    qh = blk[:, 16:48]                                       # bit 2c / 2c + 1 of byte l: fifth bit of chunk c, low / high nibble
+    qs = blk[:, 48:].reshape(-1, 4, 32)
+    bits = np.stack([(qh >> k) & 1 for k in range(8)], 1).reshape(-1, 4, 2, 32)       # [blk, chunk, lo|hi, l]
+    lo = (qs & 0xF) + 16 * bits[:, :, 0]
+    hi = (qs >> 4) + 16 * bits[:, :, 1]
+    q = np.stack([lo, hi], 2).reshape(-1, 8, 32).astype(np.float32)
+    return (q * (d * sc)[:, :, None] - (dmin * mn)[:, :, None]).reshape(-1)
+
+
+def dequant_q2_k(raw: np.ndarray) -> np.ndarray:
+    blk = raw.reshape(-1, 84)
+    scales = blk[:, :16]
+    qs = blk[:, 16:80].reshape(-1, 2, 32)                    # two halves of 128 elements
+    d, dmin = _f16(blk[:, 80:82].copy()).reshape(-1, 1), _f16(blk[:, 82:84].copy()).reshape(-1, 1)
+    dl = d * (scales & 0xF).astype(np.float32)               # [blk, 16] sub-blocks of 16 elements
+    ml = dmin * (scales >> 4).astype(np.float32)
+    # element order inside a half: shift 0: q[0..31], shift 2: q[0..31], ... ; every 16 elements own one (scale, min)
+    q = np.stack([(qs >> sh) & 3 for sh in (0, 2, 4, 6)], 2).astype(np.float32)       # [blk, half, shift, 32]
+    q = q.reshape(-1, 16, 16)
+    return (q * dl[:, :, None] - ml[:, :, None]).reshape(-1)
+
+
+def dequant_iq4_nl(raw: np.ndarray) -> np.ndarray:
+    blk = raw.reshape(-1, 18)
+    d = _f16(blk[:, :2].copy()).reshape(-1, 1)
+    qs = blk[:, 2:]
+    idx = np.concatenate([qs & 0xF, qs >> 4], 1)
+    return (IQ4_VALUES[idx] * d).reshape(-1)
+
+
+def dequant_iq4_xs(raw: np.ndarray) -> np.ndarray:
+    blk = raw.reshape(-1, 136)
+    d = _f16(blk[:, :2].copy()).reshape(-1, 1)
+    sh = blk[:, 2:4].copy().view(np.uint16).astype(np.int32).reshape(-1, 1)
+    sl = blk[:, 4:8].astype(np.int32)
+    ib = np.arange(8)
+    ls = ((sl[:, ib // 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)     # [blk, 8] 6-bit sub-block scales
+    dl = d * (ls - 32).astype(np.float32)
+    qs = blk[:, 8:].reshape(-1, 8, 16)
+    idx = np.concatenate([qs & 0xF, qs >> 4], 2)             # [blk, 8, 32]
+    return (IQ4_VALUES[idx] * dl[:, :, None]).reshape(-1)
+
+
 def dequant_q6_k(raw: np.ndarray) -> np.ndarray:
     blk = raw.reshape(-1, 210)
     ql, qh = blk[:, :128].reshape(-1, 2, 64), blk[:, 128:192].reshape(-1, 2, 32)
@@ -120,7 +183,8 @@ def dequant_mxfp4(raw: np.ndarray) -> np.ndarray:
 
 
 _DEQUANT = {Q4_0: dequant_q4_0, Q4_1: dequant_q4_1, Q5_0: dequant_q5_0, Q5_1: dequant_q5_1, Q8_0: dequant_q8_0, Q4_K: dequant_q4_k,
-            Q6_K: dequant_q6_k, MXFP4: dequant_mxfp4}
+            Q6_K: dequant_q6_k, MXFP4: dequant_mxfp4, Q2_K: dequant_q2_k, Q5_K: dequant_q5_k, IQ4_NL: dequant_iq4_nl,
+            IQ4_XS: dequant_iq4_xs}
 
 
 def dequantize_blocks(raw: np.ndarray, ggml_type: int, n_elements: int) -> np.ndarray:
