@@ -18,6 +18,19 @@ int mmb_hadamard(const void* x, void* out, int rows, int dim, int block, cudaStr
 int mmb_trellis_dequant(const uint8_t* codes, const float* scales, const float* su, const float* sv, void* out_bf16,
                         int out_f, int in_f, int bits, int group_size, cudaStream_t stream);
 // y bf16 [M, out] = x bf16 [M, in] W^T for M <= 4 (decode), straight from the bit stream.
+// One trellis matrix as the MoE kernels see it (device pointers; 48 bytes, built once per expert bank).
+typedef struct {
+  const uint8_t* codes;     // header-less tile bit stream
+  const float* scales;      // [in / gs, out]
+  const float* su;          // [in]
+  const float* sv;          // [out]
+  int out_f, in_f, bits, gs;
+} MmbTrellisMat;
+// Routed experts of a trellis MoE layer for T <= a few tokens: mats[e * 3 + {0, 1, 2}] = gate, up, down of expert e (any
+// bits 2..8 per matrix); ids int32 [T, topk] (negative = skip), wts fp32 [T, topk]; h bf16 [T * topk, inter] scratch;
+// y fp32 [T * topk, hidden] receives w * down(silu(gate(x)) * up(x)) per slot (x already normalized).
+int mmb_trellis_moe(const void* x, const MmbTrellisMat* mats, const int* ids, const float* wts, void* h, float* y, int T, int topk,
+                    int hidden, int inter, int ldx, cudaStream_t stream);
 int mmb_trellis_gemv(const void* x, const uint8_t* codes, const float* scales, const float* su, const float* sv, void* y,
                      int M, int out_f, int in_f, int bits, int group_size, int ldx, int ldy, cudaStream_t stream);
 

@@ -747,6 +747,26 @@ void trellis_gemv(const Tensor& x, const Tensor& codes, const Tensor& scales, co
   }
 }
 
+// mats: int64 CUDA tensor [n_experts * 3, 6] laid out like MmbTrellisMat (4 pointers, then out | in << 32, bits | gs << 32)
+void trellis_moe(const Tensor& x, const Tensor& mats, const Tensor& ids, const Tensor& wts, Tensor h, Tensor y, int64_t hidden,
+                 int64_t inter) {
+  check_bf16(x, "x");
+  check_bf16(h, "h");
+  static_assert(sizeof(MmbTrellisMat) == 48, "descriptor rows are six 64-bit words");
+  TORCH_CHECK(mats.is_cuda() && mats.scalar_type() == at::kLong && mats.is_contiguous() && mats.dim() == 2 && mats.size(1) == 6);
+  TORCH_CHECK(ids.scalar_type() == at::kInt && ids.is_contiguous() && ids.dim() == 2 && wts.scalar_type() == at::kFloat && wts.is_contiguous() &&
+              wts.numel() == ids.numel());
+  const int T = (int)ids.size(0), topk = (int)ids.size(1);
+  TORCH_CHECK(x.size(0) == T && x.stride(1) == 1 && x.size(1) >= hidden);
+  TORCH_CHECK(h.is_contiguous() && h.size(0) == (int64_t)T * topk && h.size(1) == inter);
+  TORCH_CHECK(y.scalar_type() == at::kFloat && y.is_contiguous() && y.size(0) == (int64_t)T * topk && y.size(1) == hidden);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(mmb_trellis_moe(x.data_ptr(), reinterpret_cast<const MmbTrellisMat*>(mats.data_ptr<int64_t>()), ids.data_ptr<int>(),
+                        wts.data_ptr<float>(), h.data_ptr(), y.data_ptr<float>(), T, topk, (int)hidden, (int)inter, (int)x.stride(0),
+                        cur_stream()),
+        "trellis_moe");
+}
+
 void codebook_gemv(const Tensor& x, const Tensor& codes, const Tensor& scales, const OptT& zeros, const Tensor& lut, Tensor y,
                    int64_t in_f, int64_t group_size, int64_t bits) {
   check_bf16(x, "x");
@@ -942,6 +962,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("hadamard", &hadamard);
   m.def("trellis_dequant", &trellis_dequant);
   m.def("trellis_gemv", &trellis_gemv);
+  m.def("trellis_moe", &trellis_moe);
   m.def("codebook_gemv", &codebook_gemv);
   m.def("vision_preprocess", &vision_preprocess);
   m.def("spec_verify", &spec_verify);

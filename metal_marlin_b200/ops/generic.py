@@ -71,11 +71,64 @@ def linear(x, W, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bi
     return y
 
 
+TRELLIS_MOE_MAX_T = 16      # decode-size batches run the routed experts in two device-side launches
+
+
+def _trellis_parts(bank: GenericExpertBank, n_routed: int):
+    """(gate, up, down) TrellisLinear triples of the routed experts, or None if the bank is not uniformly trellis."""
+    out = []
+    for e in range(n_routed):
+        gu, dn = bank.gate_up[e], bank.down[e]
+        parts = getattr(gu, "parts", None)
+        if parts is None or len(parts) != 2 or not all(hasattr(p, "codes") and hasattr(p, "su") for p in (*parts, dn)):
+            return None
+        if any(p.bias is not None or p.group_size % 16 for p in (*parts, dn)):
+            return None
+        out.append((parts[0], parts[1], dn))
+    return out
+
+
+def _trellis_desc(bank: GenericExpertBank, n_routed: int, device):
+    """Device table ``int64 [n_routed * 3, 6]`` of the experts' matrices in the layout of ``MmbTrellisMat``."""
+    cached = getattr(bank, "_trellis_desc", None)
+    if cached is not None and cached[0] == n_routed:
+        return cached[1]
+    trip = _trellis_parts(bank, n_routed)
+    desc = None
+    if trip is not None:
+        I, H = trip[0][0].out_features, trip[0][0].in_features
+        ok = all(g.out_features == I and u.out_features == I and d.in_features == I and d.out_features == H and g.in_features == H
+                 for g, u, d in trip) and I % 16 == 0 and H % 16 == 0
+        if ok:
+            rows = []
+            for tr in trip:
+                for m in tr:
+                    rows.append([m.codes.data_ptr(), m.scales.data_ptr(), m.su.data_ptr(), m.sv.data_ptr(),
+                                 m.out_features | (m.in_features << 32), m.bits | (m.group_size << 32)])
+            desc = (torch.tensor(rows, dtype=torch.int64).to(device), H, I)
+    bank._trellis_desc = (n_routed, desc)
+    return desc
+
+
 def moe_forward(x, bank: GenericExpertBank, ids, weights, *, n_shared=0, shared_base=0, norm_w=None, eps=1e-6, out_add=None):
-    """Loop over the experts that received tokens (host-side grouping; the trellis path is not graph captured)."""
-    from . import rmsnorm
+    """Routed + shared experts on generic (trellis, codebook, dense) weights.  Decode-size batches on trellis banks run the
+    routed experts in two launches that read the expert ids from device memory (mixed bits per expert and matrix; no
+    host synchronization, so the step can be graph captured); otherwise the experts that received tokens are looped over on
+    the host."""
+    from . import K, _use_native, rmsnorm
     xin = rmsnorm(x, norm_w, eps) if norm_w is not None else x
     T = x.shape[0]
+    n_routed = shared_base if n_shared else bank.num_experts
+    desc = _trellis_desc(bank, n_routed, x.device) if (_use_native(x) and T <= TRELLIS_MOE_MAX_T and x.dtype == torch.bfloat16) else None
+    if desc is not None:
+        mats, H, I = desc
+        topk = ids.shape[1]
+        h = torch.empty(T * topk, I, dtype=torch.bfloat16, device=x.device)
+        y = torch.empty(T * topk, H, dtype=torch.float32, device=x.device)
+        K.mmb200.trellis_moe(xin if xin.stride(1) == 1 else xin.contiguous(), mats, ids.to(torch.int32).contiguous(),
+                             weights.to(torch.float32).contiguous(), h, y, H, I)
+        acc = y.view(T, topk, H).sum(1)
+        return _finish_shared(acc, xin, bank, n_shared, shared_base, out_add)
     acc = torch.zeros(T, bank.down[0].out_features, dtype=torch.float32, device=x.device)
     ids_l = ids.long()
     for e in ids_l.unique().tolist():
@@ -86,6 +139,10 @@ def moe_forward(x, bank: GenericExpertBank, ids, weights, *, n_shared=0, shared_
         half = gu.shape[1] // 2
         h = (F.silu(gu[:, :half]) * gu[:, half:]).to(torch.bfloat16)
         acc.index_add_(0, tt, bank.down[e](h).to(torch.float32) * weights[tt, ss].to(torch.float32).unsqueeze(-1))
+    return _finish_shared(acc, xin, bank, n_shared, shared_base, out_add)
+
+
+def _finish_shared(acc, xin, bank, n_shared, shared_base, out_add):
     for j in range(n_shared):
         e = shared_base + j
         if bank.gate_up[e] is None:          # a multi-expert shared MLP kept as one matrix occupies the first slot only

@@ -169,3 +169,36 @@ def test_prefill_attention_mask_modes_match_dense_masks():
     vv = torch.cat([vc, vt], 2).repeat_interleave(H // Hk, 1).float()
     want = F.scaled_dot_product_attention(qt.float(), kk, vv, attn_mask=mask)
     torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("T,topk", [(1, 2), (5, 4)])
+def test_trellis_moe_device_path_matches_host_loop(T, topk, monkeypatch):
+    """Routed trellis experts in two device-side launches (mixed bits per expert / matrix) against the host loop over
+    experts that uses the per-matrix GEMV."""
+    from metal_marlin_b200.layers import TrellisLinear
+    from metal_marlin_b200.ops import generic
+    torch.manual_seed(T)
+    E, H, I = 6, 256, 128
+    bits = [2, 3, 4, 5, 6, 8]
+    gus, dws = [], []
+    for e in range(E):
+        g = TrellisLinear.from_float(torch.randn(I, H) * 0.05, bits=bits[e], group_size=64, device=DEV)
+        u = TrellisLinear.from_float(torch.randn(I, H) * 0.05, bits=bits[(e + 1) % E], group_size=64, device=DEV)
+        gus.append(generic.CatWeight([g, u]))
+        dws.append(TrellisLinear.from_float(torch.randn(H, I) * 0.05, bits=bits[(e + 2) % E], group_size=64, device=DEV))
+    sg = TrellisLinear.from_float(torch.randn(I, H) * 0.05, bits=4, group_size=64, device=DEV)
+    su = TrellisLinear.from_float(torch.randn(I, H) * 0.05, bits=4, group_size=64, device=DEV)
+    gus.append(generic.CatWeight([sg, su]))
+    dws.append(TrellisLinear.from_float(torch.randn(H, I) * 0.05, bits=4, group_size=64, device=DEV))
+    bank = generic.GenericExpertBank(gus, dws)
+    x = (torch.randn(T, H, device=DEV) * 0.5).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, device=DEV)[:topk] for _ in range(T)]).to(torch.int32)
+    ids[0, 0] = -1                                   # a dropped slot
+    wts = torch.rand(T, topk, device=DEV)
+    add = (torch.randn(T, H, device=DEV) * 0.1).to(torch.bfloat16)
+    got = generic.moe_forward(x, bank, ids, wts, n_shared=1, shared_base=E, norm_w=nw, out_add=add)
+    assert bank._trellis_desc[1] is not None          # the device path was taken
+    monkeypatch.setattr(generic, "TRELLIS_MOE_MAX_T", 0)
+    want = generic.moe_forward(x, bank, ids, wts, n_shared=1, shared_base=E, norm_w=nw, out_add=add)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
