@@ -4,17 +4,19 @@
 // the token tile is the "B" operand (TN = 32..256 tokens = TMEM columns), so the same kernel serves
 // batch-32 decode (TN = 32) and long prefill (TN = 256) without wasting the M = 128 instruction shape.
 //
-// CTA = 10 warps:
+// CTA = 18 warps:
 //   warp 0      TMA producer: x tile [TN x 64] bf16, 128-byte swizzle, one bulk tensor copy per stage
 //               (bf16-weight variant: also the W tile)
 //   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits stages back to the
 //               producers through mbarriers
-//   warps 2..9  FP4 variant: stream tile-layout weight blocks from global memory (one 16-byte load per
-//               lane per 16x64 block, one block per warp per stage), expand E2M1 -> bf16 with the group
-//               scale in registers and store them into the 128-byte-swizzled K-major A tile (weight
-//               expansion is what bounds this kernel at small token counts, hence eight warps of it);
-//               afterwards the same warps run the epilogue: tcgen05.ld of their 32-lane TMEM quarter
-//               (warp % 4), the two warps of a quarter taking alternate 32-column chunks.
+//   warps 2..17 FP4 variant: stream tile-layout weight blocks from global memory (two warps per 16x64
+//               block and stage, an 8-byte load per lane = two of the block's four k16 steps, four k
+//               blocks in flight), expand E2M1 -> bf16 with the group scale in registers and store them
+//               into the 128-byte-swizzled K-major A tile.  Weight expansion bounds this kernel and is
+//               latency bound per warp, hence sixteen warps of it (eight measured 390 TFLOP/s on
+//               4096 x 3072 x 2048, sixteen 547).  Afterwards the same warps run the epilogue:
+//               tcgen05.ld of their 32-lane TMEM quarter (warp % 4), the four warps of a quarter taking
+//               the 32-column chunks round-robin.
 // Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records a code in
 // status[0], skips the remaining work, still frees its TMEM and returns.
 #include <cuda.h>
@@ -27,7 +29,7 @@ namespace mmb {
 
 constexpr int kBK = 64;                 // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr int kTileRows = 128;          // output features per CTA
-constexpr int kExpandWarps = 8;           // warps that expand FP4 weights (one 16-row block each per stage)
+constexpr int kExpandWarps = 16;          // warps that expand FP4 weights: two per 16-row block and stage, two k16 steps each
 constexpr int kGemmThreads = (2 + kExpandWarps) * 32;
 
 // ------------------------------------------------------------------------------------------ PTX
@@ -236,7 +238,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------------------------------ weight expansion (FP4) + epilogue
-    const int dw = warp - 2;            // 0..7
+    const int dw = (warp - 2) >> 1;     // 16-row block of the 128-row tile (0..7)
+    const int kh = (warp - 2) & 1;      // which half of a block's four k16 steps this warp expands
     bool ok = true;
     if (WFMT == 0) {
       const int g = lane >> 2, t = lane & 3;
@@ -246,38 +249,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       const uint4* qw = reinterpret_cast<const uint4*>(p.qw) + (long long)expert * p.expert_stride_q;
       const uint32_t* sc = reinterpret_cast<const uint32_t*>(p.sc) + (long long)expert * p.expert_stride_s;
       const int rt_base = (n0 >> 4) + dw;
-      uint4 wnext[1];
-#pragma unroll
-      for (int j = 0; j < 1; ++j) {
-        const int rt = rt_base + j;
-        wnext[j] = (rt < n_rt && KB > 0) ? ldg_stream(qw + ((long long)rt * KC) * 32 + lane) : make_uint4(0, 0, 0, 0);
-      }
+      // This warp's 16 weight rows: one 16-byte word per lane and k block.  The words of the next four k blocks are kept
+      // in flight (the loads do not depend on the pipeline barriers, only the shared-memory stores do), so the L2 round
+      // trip is off the per-stage critical path.
+      const bool rt_ok = rt_base < n_rt;
+      const uint2* wsrc = reinterpret_cast<const uint2*>(qw + ((long long)rt_base * KC) * 32 + lane) + kh;     // words 2 kh, 2 kh + 1
+      auto wload = [&](int kb) { return (rt_ok && kb < KB) ? __ldg(wsrc + (long long)kb * 64) : make_uint2(0, 0); };
+      uint2 w0 = wload(0), w1 = wload(1), w2 = wload(2), w3 = wload(3);
       for (int i = 0; i < KB; ++i) {
         const int s = i % Cfg::kStages;
         const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
-        uint4 wcur[1] = {wnext[0]};
-        if (i + 1 < KB) {
-#pragma unroll
-          for (int j = 0; j < 1; ++j) {
-            const int rt = rt_base + j;
-            if (rt < n_rt) wnext[j] = ldg_stream(qw + ((long long)rt * KC + (i + 1)) * 32 + lane);
-          }
-        }
+        const uint2 wcur = w0;
+        w0 = w1;
+        w1 = w2;
+        w2 = w3;
+        w3 = wload(i + 4);
         if (!mbar_wait(&ps->empty[s], ph ^ 1u, abort_flag)) {
           if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 3);
           ok = false;
           break;
         }
         unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
-#pragma unroll
-        for (int j = 0; j < 1; ++j) {
-          const int rt = rt_base + j;
-          const uint32_t qq[4] = {wcur[j].x, wcur[j].y, wcur[j].z, wcur[j].w};
-          const int row_lo = (dw + j) * 16 + g;           // row inside the 128-row tile (and row_lo + 8)
+        {
+          const int rt = rt_base;
+          const uint32_t qq[2] = {wcur.x, wcur.y};
+          const int row_lo = dw * 16 + g;                 // row inside the 128-row tile (and row_lo + 8)
           unsigned char* r0 = a_tile + row_lo * 128;
           unsigned char* r1 = r0 + 8 * 128;
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
+          for (int kq = 0; kq < 2; ++kq) {
+            const int ks = kh * 2 + kq;
             const int kabs = i * kBK + ks * 16;
             const int grp = kabs >> p.gs_shift;
             uint32_t sw = 0u;     // (scale row g, scale row g+8) as half2; L1-resident reload per k16 step
@@ -285,7 +286,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sw));
             // fold the 2^126 subnormal rescale into the scale when it cannot overflow bf16
             uint32_t a0, a1, a2, a3;
-            e2m1x8_to_bf16x2_raw(qq[ks], a0, a1, a2, a3);
+            e2m1x8_to_bf16x2_raw(qq[kq], a0, a1, a2, a3);
             const bool fold = (fabsf(sf.x) < 2.f) && (fabsf(sf.y) < 2.f);
             bf162 m_lo, m_hi;
             if (fold) {
@@ -328,9 +329,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       const int q = warp & 3;                    // TMEM lane quarter this warp may access
       const int n = n0 + q * 32 + lane;
       const int ldo = WFMT == 0 ? p.ldo : pb.ldo;
-      const int c_first = ((warp - 2) >> 2) * 32; // the two warps of a quarter alternate over 32-column chunks
+      const int c_first = ((warp - 2) >> 2) * 32; // the warps of a quarter take the 32-column chunks round-robin
 #pragma unroll 1
-      for (int c0 = c_first; c0 < TN; c0 += 64) {
+      for (int c0 = c_first; c0 < TN; c0 += (kExpandWarps / 4) * 32) {
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
         tmem_ld_wait();
