@@ -9,14 +9,15 @@
 //               (bf16-weight variant: also the W tile)
 //   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits stages back to the
 //               producers through mbarriers
-//   warps 2..17 FP4 variant: stream tile-layout weight blocks from global memory (two warps per 16x64
-//               block and stage, an 8-byte load per lane = two of the block's four k16 steps, four k
-//               blocks in flight), expand E2M1 -> bf16 with the group scale in registers and store them
-//               into the 128-byte-swizzled K-major A tile.  Weight expansion bounds this kernel and is
-//               latency bound per warp, hence sixteen warps of it (eight measured 390 TFLOP/s on
-//               4096 x 3072 x 2048, sixteen 547).  Afterwards the same warps run the epilogue:
-//               tcgen05.ld of their 32-lane TMEM quarter (warp % 4), the four warps of a quarter taking
-//               the 32-column chunks round-robin.
+//   warps 2..17 FP4 variant: stream tile-layout weight blocks from global memory and expand E2M1 -> bf16 with
+//               the group scale in registers into the 128-byte-swizzled K-major A tile.  The two warps of a
+//               16-row block take alternate k blocks (a 16-byte load per lane and block, two blocks in
+//               flight).  The kernel is bound by the latency of a warp's (barrier wait -> expand -> store ->
+//               fence -> arrive) round trip, not by instruction count, L2 or the tensor pipe, so what counts
+//               is warps in flight and few, fat trips: 8 warps measured 390 TFLOP/s on 4096 x 3072 x 2048,
+//               16 warps splitting the k16 steps 547, 16 warps alternating k blocks 593.  Afterwards the
+//               same warps run the epilogue: tcgen05.ld of their 32-lane TMEM quarter (warp % 4), the four
+//               warps of a quarter taking the 32-column chunks round-robin.
 // Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records a code in
 // status[0], skips the remaining work, still frees its TMEM and returns.
 #include <cuda.h>
@@ -30,6 +31,7 @@ namespace mmb {
 constexpr int kBK = 64;                 // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr int kTileRows = 128;          // output features per CTA
 constexpr int kExpandWarps = 16;          // warps that expand FP4 weights: two per 16-row block and stage, two k16 steps each
+constexpr int kExpandSplit = 2;           // stage classes: a k block is expanded by kExpandWarps / kExpandSplit warps
 constexpr int kGemmThreads = (2 + kExpandWarps) * 32;
 
 // ------------------------------------------------------------------------------------------ PTX
@@ -147,7 +149,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
 
   if (tid == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
-      mbar_init(&ps->full_a[s], WFMT == 0 ? kExpandWarps : 1);
+      mbar_init(&ps->full_a[s], WFMT == 0 ? kExpandWarps / kExpandSplit : 1);      // the warps of one stage class (see the expansion loop)
       mbar_init(&ps->full_b[s], 1);
       mbar_init(&ps->empty[s], 1);
     }
@@ -238,8 +240,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------------------------------ weight expansion (FP4) + epilogue
-    const int dw = (warp - 2) >> 1;     // 16-row block of the 128-row tile (0..7)
-    const int kh = (warp - 2) & 1;      // which half of a block's four k16 steps this warp expands
+    // Expansion work split: the k blocks (pipeline stages) are dealt round-robin to kSplit classes of warps; a warp
+    // expands kRB 16-row blocks (all four k16 steps each) of every k block of its class.  Fewer, fatter trips per warp:
+    // a trip is a serial (barrier wait -> expand -> store -> fence -> arrive) round trip whose latency, not the
+    // instruction count, bounds the kernel, and the independent chains inside a trip overlap.
+    constexpr int kSplit = kExpandSplit;      // 2; (4 classes x 2 row blocks measured slower: with 4 stages a class is then tied to one buffer)
+    constexpr int kRB = kSplit * 8 / kExpandWarps;        // row blocks per warp (8 per 128-row tile)
+    const int kh = (warp - 2) % kSplit;                   // stage class of this warp
+    const int dw0 = ((warp - 2) / kSplit) * kRB;          // first 16-row block of this warp
     bool ok = true;
     if (WFMT == 0) {
       const int g = lane >> 2, t = lane & 3;
@@ -248,71 +256,92 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       const int n_rt = (N + 15) >> 4;
       const uint4* qw = reinterpret_cast<const uint4*>(p.qw) + (long long)expert * p.expert_stride_q;
       const uint32_t* sc = reinterpret_cast<const uint32_t*>(p.sc) + (long long)expert * p.expert_stride_s;
-      const int rt_base = (n0 >> 4) + dw;
-      // This warp's 16 weight rows: one 16-byte word per lane and k block.  The words of the next four k blocks are kept
-      // in flight (the loads do not depend on the pipeline barriers, only the shared-memory stores do), so the L2 round
-      // trip is off the per-stage critical path.
-      const bool rt_ok = rt_base < n_rt;
-      const uint2* wsrc = reinterpret_cast<const uint2*>(qw + ((long long)rt_base * KC) * 32 + lane) + kh;     // words 2 kh, 2 kh + 1
-      auto wload = [&](int kb) { return (rt_ok && kb < KB) ? __ldg(wsrc + (long long)kb * 64) : make_uint2(0, 0); };
-      uint2 w0 = wload(0), w1 = wload(1), w2 = wload(2), w3 = wload(3);
-      for (int i = 0; i < KB; ++i) {
+      const bool big_groups = p.gs_shift >= 6;
+      // per row block: weight words (one 16-byte word per lane and k block; the next two k blocks of the class are kept
+      // in flight - the loads do not depend on the pipeline barriers), scale words of this lane's row pair, store row
+      bool rt_ok[kRB];
+      const uint4* wsrc[kRB];
+      const uint32_t* sc_row[kRB];
+      int st_row[kRB];
+      uint4 w0[kRB], w1[kRB];
+#pragma unroll
+      for (int j = 0; j < kRB; ++j) {
+        const int rt = (n0 >> 4) + dw0 + j;
+        rt_ok[j] = rt < n_rt;
+        wsrc[j] = qw + ((long long)rt * KC) * 32 + lane;
+        sc_row[j] = sc + (long long)rt * NG * 8 + g;
+        st_row[j] = ((dw0 + j) * 16 + g) * 128;
+        w0[j] = (rt_ok[j] && kh < KB) ? ldg_stream(wsrc[j] + (long long)kh * 32) : make_uint4(0, 0, 0, 0);
+        w1[j] = (rt_ok[j] && kh + kSplit < KB) ? ldg_stream(wsrc[j] + (long long)(kh + kSplit) * 32) : make_uint4(0, 0, 0, 0);
+      }
+      // store offsets inside a row of the A tile (128-byte swizzle: 16-byte chunk index XOR (row % 8); row % 8 == g)
+      int st_col[4][2];
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        st_col[ks][0] = ((ks * 2) ^ g) * 16 + 4 * t;
+        st_col[ks][1] = ((ks * 2 + 1) ^ g) * 16 + 4 * t;
+      }
+      for (int i = kh; i < KB; i += kSplit) {
         const int s = i % Cfg::kStages;
         const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
-        const uint2 wcur = w0;
-        w0 = w1;
-        w1 = w2;
-        w2 = w3;
-        w3 = wload(i + 4);
+        uint4 wcur[kRB];
+#pragma unroll
+        for (int j = 0; j < kRB; ++j) {
+          wcur[j] = w0[j];
+          w0[j] = w1[j];
+          w1[j] = (rt_ok[j] && i + 2 * kSplit < KB) ? ldg_stream(wsrc[j] + (long long)(i + 2 * kSplit) * 32) : make_uint4(0, 0, 0, 0);
+        }
         if (!mbar_wait(&ps->empty[s], ph ^ 1u, abort_flag)) {
           if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 3);
           ok = false;
           break;
         }
         unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
-        {
-          const int rt = rt_base;
-          const uint32_t qq[2] = {wcur.x, wcur.y};
-          const int row_lo = dw * 16 + g;                 // row inside the 128-row tile (and row_lo + 8)
-          unsigned char* r0 = a_tile + row_lo * 128;
-          unsigned char* r1 = r0 + 8 * 128;
 #pragma unroll
-          for (int kq = 0; kq < 2; ++kq) {
-            const int ks = kh * 2 + kq;
-            const int kabs = i * kBK + ks * 16;
-            const int grp = kabs >> p.gs_shift;
-            uint32_t sw = 0u;     // (scale row g, scale row g+8) as half2; L1-resident reload per k16 step
-            if (rt < n_rt) sw = __ldg(sc + ((long long)rt * NG + grp) * 8 + g);
+        for (int j = 0; j < kRB; ++j) {
+          const uint32_t qq[4] = {wcur[j].x, wcur[j].y, wcur[j].z, wcur[j].w};
+          unsigned char* r0 = a_tile + st_row[j];         // rows g and g + 8 of the 16-row block
+          unsigned char* r1 = r0 + 8 * 128;
+          // groups of 64 and more: the four k16 steps of a k block share its group, so the scale word is fetched and
+          // turned into the bf16 multipliers once per block
+          bf162 m_lo, m_hi;
+          bool fold = true;
+          if (big_groups) {
+            const uint32_t sw = rt_ok[j] ? __ldg(sc_row[j] + (long long)((i * kBK) >> p.gs_shift) * 8) : 0u;
             const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sw));
             // fold the 2^126 subnormal rescale into the scale when it cannot overflow bf16
+            fold = (fabsf(sf.x) < 2.f) && (fabsf(sf.y) < 2.f);
+            m_lo = __float2bfloat162_rn(fold ? sf.x * 8.507059173023462e37f : sf.x);   // 2^126
+            m_hi = __float2bfloat162_rn(fold ? sf.y * 8.507059173023462e37f : sf.y);
+          }
+#pragma unroll
+          for (int kq = 0; kq < 4; ++kq) {
+            if (!big_groups) {
+              const int kabs = i * kBK + kq * 16;
+              const uint32_t sw = rt_ok[j] ? __ldg(sc_row[j] + (long long)(kabs >> p.gs_shift) * 8) : 0u;
+              const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sw));
+              fold = (fabsf(sf.x) < 2.f) && (fabsf(sf.y) < 2.f);
+              m_lo = __float2bfloat162_rn(fold ? sf.x * 8.507059173023462e37f : sf.x);
+              m_hi = __float2bfloat162_rn(fold ? sf.y * 8.507059173023462e37f : sf.y);
+            }
             uint32_t a0, a1, a2, a3;
             e2m1x8_to_bf16x2_raw(qq[kq], a0, a1, a2, a3);
-            const bool fold = (fabsf(sf.x) < 2.f) && (fabsf(sf.y) < 2.f);
-            bf162 m_lo, m_hi;
-            if (fold) {
-              m_lo = __float2bfloat162_rn(sf.x * 8.507059173023462e37f);   // 2^126
-              m_hi = __float2bfloat162_rn(sf.y * 8.507059173023462e37f);
-            } else {
+            if (!fold) {
               const bf162 big = __float2bfloat162_rn(8.507059173023462e37f);
               *reinterpret_cast<bf162*>(&a0) = __hmul2(*reinterpret_cast<bf162*>(&a0), big);
               *reinterpret_cast<bf162*>(&a1) = __hmul2(*reinterpret_cast<bf162*>(&a1), big);
               *reinterpret_cast<bf162*>(&a2) = __hmul2(*reinterpret_cast<bf162*>(&a2), big);
               *reinterpret_cast<bf162*>(&a3) = __hmul2(*reinterpret_cast<bf162*>(&a3), big);
-              m_lo = __float2bfloat162_rn(sf.x);
-              m_hi = __float2bfloat162_rn(sf.y);
             }
             // fragment registers: a0 = (row g, k 2t..), a1 = (row g+8, same k), a2 = (row g, k+8), a3 = (row g+8, k+8)
             *reinterpret_cast<bf162*>(&a0) = __hmul2(*reinterpret_cast<bf162*>(&a0), m_lo);
             *reinterpret_cast<bf162*>(&a1) = __hmul2(*reinterpret_cast<bf162*>(&a1), m_hi);
             *reinterpret_cast<bf162*>(&a2) = __hmul2(*reinterpret_cast<bf162*>(&a2), m_lo);
             *reinterpret_cast<bf162*>(&a3) = __hmul2(*reinterpret_cast<bf162*>(&a3), m_hi);
-            // 128-byte swizzle: 16-byte chunk index XOR (row % 8); row % 8 == g for both halves
-            const int c_lo = ((ks * 2) ^ g) * 16 + 4 * t;
-            const int c_hi = ((ks * 2 + 1) ^ g) * 16 + 4 * t;
-            *reinterpret_cast<uint32_t*>(r0 + c_lo) = a0;
-            *reinterpret_cast<uint32_t*>(r1 + c_lo) = a1;
-            *reinterpret_cast<uint32_t*>(r0 + c_hi) = a2;
-            *reinterpret_cast<uint32_t*>(r1 + c_hi) = a3;
+            *reinterpret_cast<uint32_t*>(r0 + st_col[kq][0]) = a0;
+            *reinterpret_cast<uint32_t*>(r1 + st_col[kq][0]) = a1;
+            *reinterpret_cast<uint32_t*>(r0 + st_col[kq][1]) = a2;
+            *reinterpret_cast<uint32_t*>(r1 + st_col[kq][1]) = a3;
           }
         }
         fence_proxy_async_smem();       // generic-proxy stores -> visible to the tensor core (async proxy)
