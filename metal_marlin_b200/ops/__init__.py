@@ -646,7 +646,7 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
     E_routed = gate_up.num_experts - n_shared
     if not token_tile:      # smallest MMA N tile that holds the average expert load
         avg = T * topk / max(1, E_routed)
-        token_tile = 32 if avg <= 24 else (64 if avg <= 48 else 128)
+        token_tile = 32 if avg <= 24 else (64 if avg <= 48 else (128 if avg <= 160 else 256))
     inter = gate_up.out_features // 2
     n = T * topk
     dev = x.device
