@@ -299,7 +299,7 @@ def main():
             out["tp"] = {"parallelism": f"tp{world} (in-kernel NVLink exchange)", "global_batch": args.batch,
                          "ms_per_step": round(rt["ms_per_step"], 4), "tok_s": round(args.batch * 1e3 / rt["ms_per_step"], 2),
                          "ttft_ms": round(rt["ttft_ms"], 2),      # prompt split over the ranks: GEMM -> reduce-scatter -> gather -> GEMM in-kernel
-                         "launches_per_step": rt["launches_per_step"], "exchange_status": state["ctx"].check(),
+                         "launches_per_step": rt["launches_per_step"], "exchange_status": state["ctx"].check(), "multimem": bool(getattr(state["ctx"], "use_multimem", False)),
                          "weights_gb_per_gpu": round(state["model"].weight_bytes() / 1e9, 2)}
         except Exception as e:
             out["tp"] = {"error": repr(e)[:300]}

@@ -23,6 +23,8 @@ typedef struct {
   const unsigned* step;             // device scalar, incremented once per decode step
   int* status;                      // optional error word
   int tp;
+  float* out_mc_slot;               // optional: this rank's slot through the multicast (NVLS) mapping of the receive buffers;
+                                    // when set, one multimem store per value replaces the tp peer stores
 } MmbTpExchange;
 
 // ----------------------------------------------------------------------------- FP4 small-M GEMV

@@ -36,7 +36,7 @@ inline int log2i(int64_t v) {
 // [in_buf, in_flags, in_slot_stride, out_peer_slots, out_peer_flags, out_counter, step, status, tp] (raw addresses).
 inline void fill_tpx(const OptT& t, MmbTpExchange& x) {
   if (!t.has_value() || !t->defined()) return;
-  TORCH_CHECK(!t->is_cuda() && t->scalar_type() == at::kLong && t->numel() == 9, "tpx must be a CPU int64[9] tensor");
+  TORCH_CHECK(!t->is_cuda() && t->scalar_type() == at::kLong && (t->numel() == 9 || t->numel() == 10), "tpx must be a CPU int64[9 | 10] tensor");
   const int64_t* v = t->data_ptr<int64_t>();
   x.in_buf = reinterpret_cast<const float*>(v[0]);
   x.in_flags = reinterpret_cast<const unsigned*>(v[1]);
@@ -47,6 +47,7 @@ inline void fill_tpx(const OptT& t, MmbTpExchange& x) {
   x.step = reinterpret_cast<const unsigned*>(v[6]);
   x.status = reinterpret_cast<int*>(v[7]);
   x.tp = (int)v[8];
+  if (t->numel() == 10) x.out_mc_slot = reinterpret_cast<float*>(v[9]);
 }
 
 void fp4_gemv(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t Kx, int64_t gs,

@@ -506,6 +506,7 @@ __global__ void __launch_bounds__(NWARPS * 32, (NWARPS == 8 && MB == 1) ? 2 : 1)
   tout.counter = p.tpx.out_counter;
   tout.step = p.tpx.step;
   tout.tp = p.tpx.tp;
+  tout.mc_slot = p.tpx.out_mc_slot;
   bf16* const out = reinterpret_cast<bf16*>(p.out);
   {
     const int gmask = gs - 1;

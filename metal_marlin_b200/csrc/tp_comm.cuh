@@ -48,6 +48,7 @@ struct TpOut {
   unsigned* counter;             // local CTA completion counter (starts at 0, left at 0)
   const unsigned* step;
   int tp;
+  float* mc_slot = nullptr;      // optional: my slot addressed through the NVSwitch multicast mapping of the buffers
 };
 
 // All threads of the CTA call this before reading the receive buffer.
@@ -86,8 +87,13 @@ __device__ __forceinline__ float2 tp_sum2(const TpIn& t, long long idx) {
   return s;
 }
 
-// Store one value of this rank's partial into every peer.
+// Store one value of this rank's partial into every peer: one multimem store that the NVSwitch replicates into all
+// ranks' buffers when the buffers are bound to a multicast object, else tp plain peer stores.
 __device__ __forceinline__ void tp_push(const TpOut& t, long long idx, float v) {
+  if (t.mc_slot != nullptr) {
+    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(t.mc_slot + idx), "f"(v) : "memory");
+    return;
+  }
   for (int r = 0; r < t.tp; ++r) t.peer_slots[r][idx] = v;
 }
 

@@ -4,7 +4,8 @@ One allocation per rank with the same layout on every rank; after the rendezvous
 device address of every peer's copy, so kernels can store into / load from peer memory directly.
 
 Primary path: ``torch.distributed._symmetric_memory`` (CUDA VMM allocations exported to the peers of the
-process group; no multicast object is requested here, kernels use plain peer stores).  Fallback: CUDA IPC
+process group; where the fabric supports it the allocation is also bound to an NVSwitch multicast object, whose address
+``multicast_ptr`` lets a kernel reach all ranks' copies with one ``multimem`` store).  Fallback: CUDA IPC
 handles of a regular torch allocation exchanged through the process group.
 
 Parity: nothing comparable exists in the reference (its "collectives" are numpy concatenations inside one
@@ -30,6 +31,7 @@ class SymmetricBuffer:
         self.nbytes = (nbytes + 255) // 256 * 256
         self.backend = None
         self._handle = None
+        self.multicast_ptr = 0
         self._peer_tensors: List[torch.Tensor] = []
         err = None
         try:
@@ -52,6 +54,9 @@ class SymmetricBuffer:
         self.local = t
         self._handle = hdl
         self.peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
+        # address of the same allocation through the NVSwitch multicast object (0 when the fabric or the driver has none):
+        # a multimem store there lands in every rank's copy
+        self.multicast_ptr = int(getattr(hdl, "multicast_ptr", 0) or 0)
         assert len(self.peer_ptrs) == self.world and self.peer_ptrs[self.rank] == t.data_ptr()
 
     def _init_ipc(self) -> None:

@@ -25,6 +25,7 @@ collectives) and ``metal_marlin/distributed/verification.py:85-509`` (sharded-vs
 from __future__ import annotations
 
 import copy
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -93,10 +94,15 @@ class TPContext:
         self.n_flag_sites = n_sites + 1
         total = flags_off + self.n_flag_sites * tp * 4
         self._desc_cache: Dict[Tuple[str, int, int], torch.Tensor] = {}
+        self.use_multimem = False
         if not self.fused_ok:
             self.buf = None
             return
         self.buf = SymmetricBuffer(total, device, group)
+        # NVSwitch multicast for the decode exchange (off when NVLS is switched off for the process, as the multi-rank failure
+        # tests do: their ranks may leave while others still run)
+        self.use_multimem = bool(self.buf.multicast_ptr) and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0" \
+            and os.environ.get("MMB_TP_MULTIMEM", "1") != "0"
         self.pairs_off = n_sites * self.site_bytes
         self.flags_off = flags_off
         self.step = torch.zeros(1, dtype=torch.int32, device=device)
@@ -217,7 +223,7 @@ class TPContext:
         d = self._desc_cache.get(key)
         if d is None:
             base = self.buf.local.data_ptr()
-            v = [0] * 9
+            v = [0] * 10
             if kind == "in":
                 v[0] = base + site * self.site_bytes
                 v[1] = base + self.flags_off + site * self.tp * 4
@@ -226,6 +232,9 @@ class TPContext:
                 v[3] = self.peer_slots[site].data_ptr()
                 v[4] = self.peer_flags[site].data_ptr()
                 v[5] = self.counters[site:].data_ptr()
+                if self.use_multimem and site < self.n_sites:
+                    # my slot of this site in EVERY rank's buffer through the multicast mapping: one multimem store per value
+                    v[9] = self.buf.multicast_ptr + site * self.site_bytes + self.rank * self.slot * 4
             else:       # "pairs": vocabulary-parallel arg-max exchange (both directions)
                 v[0] = base + self.pairs_off
                 v[1] = base + self.flags_off + site * self.tp * 4
