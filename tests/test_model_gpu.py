@@ -67,3 +67,24 @@ def test_chunked_prefill_equals_single_pass():
     a = prefill(lm.model, kv1, prompt, bt, chunk_tokens=4096)
     b = prefill(lm.model, kv2, prompt, bt, chunk_tokens=64)
     assert float((a - b).abs().max() / a.abs().max()) < 3e-2
+
+
+@pytest.mark.parametrize("preset,per_layer", [("tiny-mla-moe", 9), ("tiny-llama", 7)])
+def test_decode_step_launch_budget(preset, per_layer):
+    """Launch-count budget of one decode step (a step is latency bound: every extra launch costs ~1.3 us per layer).
+    MLA + MoE layer: q_a|kv_a, q_b, prologue, paged decode, merge, o_proj, router, gate|up, down; GQA + dense layer:
+    qkv, prologue (q/k norm + RoPE + cache write), paged decode, merge, o_proj, gate|up, down.  Head: LM head + arg-max (+ embedding)."""
+    lm = MMFP4ForCausalLM.from_config(preset, device="cuda", seed=4)
+    prompts = [list(range(1, 12))]
+    bt = torch.arange(8, dtype=torch.int32).view(1, 8)
+    kv = lm.new_cache(8, 16)
+    lg0 = prefill(lm.model, kv, prompts, bt)
+    sess = DecodeSession(lm.model, kv, 1, 8, max_new_tokens=4, use_graph=False)
+    sess.set_sampling([SamplingParams()])
+    sess.set_state(lg0.argmax(-1), [11], bt)
+    sess.step()                                  # first step may initialise lazily built descriptors
+    n0 = ops.launch_count()
+    sess.step()
+    launches = ops.launch_count() - n0
+    n_layers = len(lm.model.layers)
+    assert launches <= n_layers * per_layer + 4, (launches, n_layers)
