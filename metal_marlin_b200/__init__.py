@@ -54,6 +54,8 @@ _reg(".quant.pipeline", "quantize_checkpoint", "collect_hessians")
 _reg(".converters", "convert_checkpoint", "MixedFormatPack")
 _reg(".converters.gguf", "GGUFReader", "write_gguf")
 _reg(".converters.nemo", "load_nemo")
+_reg(".memory.streams", "StreamPool", "EventPool", "AsyncEvent", "discover_devices", "get_stream")
+_reg(".quant.psd", "gershgorin_is_psd", "project_psd", "damp_until_cholesky")
 _reg(".kv.prompt_cache", "TieredPrefixCache", "RadixPrefixCache", "PrefixCacheConfig", "StorageTier")
 _reg(".serving.batching", "RequestBatcher", "BatchConfig", "KVCacheSharing")
 _reg(".profiling.wandb_helper", "WandbHelper", "get_wandb")

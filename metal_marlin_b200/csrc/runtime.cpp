@@ -104,6 +104,38 @@ struct Arena {
     return off;
   }
 
+  // Slide every movable (unpinned) live block towards offset 0, closing the holes in front of it; pinned blocks stay
+  // where they are and split the arena into segments that are compacted separately.  Returns (old offset, new offset,
+  // size) triples in ascending order of the old offset: moving the bytes in that order with memmove semantics is safe.
+  std::vector<int64_t> compact() {
+    std::vector<int64_t> moves;
+    std::map<int64_t, Block> out;
+    int64_t cursor = 0;      // next free byte of the current segment
+    auto flush_gap = [&](int64_t upto) {
+      if (upto > cursor) out[cursor] = Block{upto - cursor, true, false, 0, 0};
+    };
+    for (auto& kv : blocks) {
+      const Block& b = kv.second;
+      if (b.free) continue;
+      if (b.pinned) {
+        flush_gap(kv.first);
+        out[kv.first] = b;
+        cursor = kv.first + b.size;
+      } else {
+        if (kv.first != cursor) {
+          moves.push_back(kv.first);
+          moves.push_back(cursor);
+          moves.push_back(b.size);
+        }
+        out[cursor] = b;
+        cursor += b.size;
+      }
+    }
+    flush_gap(capacity);
+    blocks.swap(out);
+    return moves;
+  }
+
   double fragmentation() const {
     int64_t free_total = 0, largest = 0;
     for (auto& kv : blocks)
@@ -160,6 +192,10 @@ void arena_touch(int64_t h, int64_t off) {
   if (it != a.blocks.end() && !it->second.free) it->second.last_use = ++a.clock;
 }
 // [capacity, used, peak, n_alloc, n_evict, n_blocks, largest_free, fragmentation * 1e6]
+std::vector<int64_t> arena_compact(int64_t h) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  return arena_get(h).compact();
+}
 std::vector<int64_t> arena_stats(int64_t h) {
   std::lock_guard<std::mutex> lock(g_mu);
   auto& a = arena_get(h);
@@ -383,6 +419,7 @@ TORCH_LIBRARY_FRAGMENT(mmb200, m) {
   m.def("arena_pin", &arena_pin);
   m.def("arena_touch", &arena_touch);
   m.def("arena_stats", &arena_stats);
+  m.def("arena_compact", &arena_compact);
   m.def("cpu_group_tokens", &cpu_group_tokens);
   m.def("plan_grouped_gemm", &plan_grouped_gemm);
   m.def("cpu_dequant_fp4", &cpu_dequant_fp4);

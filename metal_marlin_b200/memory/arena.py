@@ -60,6 +60,26 @@ class Arena:
     def touch(self, t: torch.Tensor) -> None:
         _native().arena_touch(self._h, self.offset_of(t))
 
+    def compact(self) -> Dict[int, int]:
+        """Close the holes between live blocks (pinned blocks stay in place).  The bytes are moved inside the slab; views
+        handed out earlier for moved blocks are stale afterwards, the returned ``{old offset: new offset}`` map tells the
+        owner where each block went (``view_at`` gives a fresh view)."""
+        moves = list(_native().arena_compact(self._h))
+        remap: Dict[int, int] = {}
+        for i in range(0, len(moves), 3):
+            old, new, size = moves[i], moves[i + 1], moves[i + 2]
+            if new + size <= old:
+                self.slab[new: new + size].copy_(self.slab[old: old + size])
+            else:                                   # overlapping slide to lower addresses: go through a temporary
+                self.slab[new: new + size].copy_(self.slab[old: old + size].clone())
+            remap[old] = new
+        self._live = {remap.get(off, off): v for off, v in self._live.items()}
+        return remap
+
+    def view_at(self, offset: int, shape: Sequence[int], dtype=torch.bfloat16) -> torch.Tensor:
+        n = int(math.prod(shape)) * _ELT[dtype]
+        return self.slab[offset: offset + n].view(dtype).view(*shape)
+
     def stats(self) -> Dict[str, float]:
         cap, used, peak, n_alloc, n_evict, n_blocks, largest, frag = _native().arena_stats(self._h)
         return {"capacity": cap, "used": used, "peak": peak, "allocs": n_alloc, "evictions": n_evict, "blocks": n_blocks,

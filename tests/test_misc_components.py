@@ -183,3 +183,68 @@ def test_early_exit_stops_when_confident_and_matches_full_depth_otherwise():
     ee = EarlyExitModel(lm.model, exit_threshold=0.0)
     always = ee(ids, lm.new_cache(2, 16), meta(), rows=torch.tensor([T - 1]))
     assert always.exit_layer == 0 and always.logits.shape == full.shape and ee.average_exit_layer() == 0.0
+
+
+def test_arena_compaction_moves_live_blocks_and_keeps_pinned_ones():
+    from metal_marlin_b200.memory.arena import Arena
+    a = Arena(4096, alignment=256)
+    t = [a.alloc((256,), torch.uint8, tag=str(i)) for i in range(8)]            # eight 256-byte blocks
+    for i, x in enumerate(t):
+        x.fill_(i + 1)
+    a.pin(t[5])
+    for i in (0, 2, 4, 6):
+        a.free(t[i])
+    assert a.stats()["largest_free"] == 2048 and a.stats()["fragmentation"] > 0      # four holes + the tail
+    remap = a.compact()
+    # block 1 -> 0, block 3 -> 256; block 5 is pinned at 1280 and stays; block 7 follows it at 1536 (it moves from 1792)
+    assert remap == {256: 0, 768: 256, 1792: 1536}
+    for old, val in ((256, 2), (768, 4), (1792, 8)):
+        assert torch.all(a.view_at(remap[old], (256,), torch.uint8) == val)
+    assert torch.all(a.view_at(1280, (256,), torch.uint8) == 6)
+    big = a.alloc((2304,), torch.uint8)                                          # the tail is one hole now
+    assert a.offset_of(big) == 1792
+
+
+def test_stream_pool_event_pool_and_discovery_degrade_without_cuda():
+    from metal_marlin_b200.memory import streams
+    pool = streams.StreamPool()
+    try:
+        pool.get("bogus")
+        assert False
+    except ValueError:
+        pass
+    ev = streams.EventPool().record()
+    if not torch.cuda.is_available():
+        assert pool.get("copy") is None and ev.wait(0.01) and streams.discover_devices() == []
+    devs = [streams.DeviceInfo(i, "B200", 148, 180 << 30, (10, 0), [j for j in range(4) if j != i], 18) for i in range(4)]
+    assert streams.multicast_plausible(devs)
+    devs[0].peers.pop()
+    assert not streams.multicast_plausible(devs)
+
+    class FakeNvml:
+        def nvmlDeviceGetHandleByIndex(self, i):
+            return i
+
+        def nvmlDeviceGetNvLinkState(self, h, link):
+            if link >= 6:
+                raise RuntimeError("no such link")
+            return link % 2 == 0
+    assert streams._nvml_links(0, FakeNvml()) == 3
+
+
+def test_psd_helpers():
+    from metal_marlin_b200.quant import psd
+    torch.manual_seed(0)
+    X = torch.randn(64, 16)
+    H = X.t() @ X
+    assert psd.min_eigenvalue(H) > 0 and psd.gershgorin_is_psd(torch.eye(4) * 3 + 0.5)
+    bad = H - 50 * torch.eye(16)
+    assert psd.min_eigenvalue(bad) < 0 and not psd.gershgorin_is_psd(bad)
+    P = psd.project_psd(bad, eps=1e-3)
+    assert psd.min_eigenvalue(P) > 0 and torch.allclose(P, P.t(), atol=1e-5)
+    Hd, L, lam = psd.damp_until_cholesky(H)
+    assert lam > 0 and torch.allclose(L @ L.t(), Hd, atol=1e-3)
+    sing = torch.zeros(8, 8)
+    sing[0, 0] = 1.0
+    Hd, L, lam = psd.damp_until_cholesky(sing)
+    assert torch.isfinite(L).all()
