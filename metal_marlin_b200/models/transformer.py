@@ -163,6 +163,22 @@ class BatchMeta:
     splits: Optional[int] = None
     ctx_lens_host: Optional[List[int]] = None
     attn_mask: Optional[torch.Tensor] = None     # [T, n_ctx] bool, single-sequence prefill only (tree verification)
+    _dev_cache: Optional[dict] = None            # small device tensors derived from the host lists, built once per batch
+
+    def dev_ints(self, key, values, device) -> torch.Tensor:
+        """int32 device tensor of ``values``, cached under ``key``: a host list becomes a device tensor through a
+        synchronous copy that drains the stream, so it must happen once per batch, not once per layer."""
+        return self.cached(key, lambda: torch.tensor(list(values), dtype=torch.int32, device=device))
+
+    def cached(self, key, make):
+        """Per-batch memo for tensors every layer would otherwise rebuild (cache slots of a sequence, cumulative lengths)."""
+        if self._dev_cache is None:
+            self._dev_cache = {}
+        t = self._dev_cache.get(key)
+        if t is None:
+            t = make()
+            self._dev_cache[key] = t
+        return t
 
 
 # ---------------------------------------------------------------------------------------------
@@ -243,7 +259,7 @@ class Transformer:
         bs = kv.block_size
         if meta.attn_mask is None and q.dtype == torch.bfloat16:
             # one launch for all sequences: keys are read from the paged pool through the block table
-            cu_q = torch.tensor(meta.cu_seqlens, dtype=torch.int32, device=q.device)
+            cu_q = meta.dev_ints("cu_q", meta.cu_seqlens, q.device)
             max_q = max(meta.cu_seqlens[i + 1] - meta.cu_seqlens[i] for i in range(len(meta.cu_seqlens) - 1))
             ops.prefill_attention(q, kv.k[li].view(-1, Hk, D), kv.v[li].view(-1, Hk, D), cu_q, block_tables=meta.block_tables,
                                   ctx_lens=meta.ctx_lens, block_size=bs, max_q=max_q, scale=self.scale, window=cfg.sliding_window,
@@ -255,7 +271,7 @@ class Transformer:
             T = q.shape[0]
             n_ctx = int(meta.ctx_lens_host[0])
             tm = meta.attn_mask[:, n_ctx - T:].to(torch.uint8).contiguous()
-            cu_q = torch.tensor(meta.cu_seqlens, dtype=torch.int32, device=q.device)
+            cu_q = meta.dev_ints("cu_q", meta.cu_seqlens, q.device)
             ops.prefill_attention(q, kv.k[li].view(-1, Hk, D), kv.v[li].view(-1, Hk, D), cu_q, block_tables=meta.block_tables,
                                   ctx_lens=meta.ctx_lens, block_size=bs, max_q=T, scale=self.scale, causal=False, tree_mask=tm,
                                   out=out.view(-1, Hq, D))
@@ -324,15 +340,17 @@ class Transformer:
             s, e = meta.cu_seqlens[b], meta.cu_seqlens[b + 1]
             n_ctx = int(meta.ctx_lens_host[b])
             t = e - s
-            tok = torch.arange(n_ctx, device=q.device)
-            slots = meta.block_tables[b, tok // bs].long() * bs + tok % bs
+            def _slots(b=b, n_ctx=n_ctx):
+                tok = torch.arange(n_ctx, device=q.device)
+                return meta.block_tables[b, tok // bs].long() * bs + tok % bs
+            slots = meta.cached(("slots", b, n_ctx), _slots)
             lat = kv.k[li][slots]                                           # [n, R + dr] post-norm | post-RoPE
             c = lat[:, :R].contiguous()
             kvx = (ops.bf16_gemm(c, L.kv_b_dense) if R % 64 == 0 else torch.matmul(c, L.kv_b_dense.t())).view(n_ctx, H, dn + dv)
             k = torch.cat([kvx[..., :dn], lat[:, None, R:].expand(n_ctx, H, dr)], -1)
             qq = torch.cat([q[s:e, :, :dn], q_full[s:e, :, R:]], -1)
-            cu_q = torch.tensor([0, t], dtype=torch.int32, device=q.device)
-            cu_k = torch.tensor([0, n_ctx], dtype=torch.int32, device=q.device)
+            cu_q = meta.dev_ints(("cu_q1", b), [0, t], q.device)
+            cu_k = meta.dev_ints(("cu_k1", b), [0, n_ctx], q.device)
             ops.prefill_attention(qq, k.contiguous(), kvx[..., dn:], cu_q, cu_k=cu_k, max_q=t, scale=self.scale,
                                   out=out[s:e].view(t, H, dv))
         return out
