@@ -214,10 +214,10 @@ __device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem) {
 // In-place expansion of a tile of E4M3 rows (D bytes each, sitting in the upper half of bf16 rows of stride RS elements)
 // to bf16 x row scale.  Called by all NT threads of the CTA: every thread first reads its 16-byte pieces, the CTA
 // synchronizes, then the 32-byte results are written (a piece's result overlaps other pieces' source bytes).
-template <int D, int RS, int NT>
+template <int D, int RS, int NT, int TT>
 __device__ __forceinline__ void expand_fp8_rows(bf16* rows, const float* row_scale, int nvalid, int tid) {
   constexpr int UPR = D / 16;                               // pieces per row
-  constexpr int PER = (kTileTok * UPR + NT - 1) / NT;        // pieces per thread
+  constexpr int PER = (TT * UPR + NT - 1) / NT;              // pieces per thread
   uint4 raw[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
@@ -248,28 +248,35 @@ __device__ __forceinline__ void expand_fp8_rows(bf16* rows, const float* row_sca
 }
 
 // NW warps: in QK^T each warp owns 64 / NW token columns, in PV it owns DV / NW value columns.
-template <int DQK, int DV, int MT, bool SHARED_V, int NW>
+// TT tokens per tile.  TT = 64: one CTA per SM (the two K/V buffers fill the shared memory).  TT = 32 (MLA shape only): half
+// the tile, query rows stored compactly (the rows beyond the head group share one zero row) -> two CTAs per SM, so one
+// CTA's barrier-separated phases (QK^T, soft-max, PV) overlap the other's; used when the grid has more CTAs than SMs.
+template <int DQK, int DV, int MT, bool SHARED_V, int NW, int TT>
 struct DecodeSmem {
   static constexpr int KS = DQK + 8;                     // row strides in elements (16-byte skew)
   static constexpr int VS = DV + 8;
-  static constexpr int PS = kTileTok + 8;
-  static constexpr int SS = kTileTok + 4;                // fp32 score row stride
-  static constexpr size_t q_bytes = (size_t)MT * 16 * KS * 2;
-  static constexpr size_t k_bytes = (size_t)kTileTok * KS * 2;
-  static constexpr size_t v_bytes = SHARED_V ? 0 : (size_t)kTileTok * VS * 2;
+  static constexpr int PS = TT + 8;
+  static constexpr int SS = TT + 4;                      // fp32 score row stride
+  static constexpr int QR = (TT == 32) ? 24 : MT * 16;   // query rows held (compact form: up to 23 heads + the zero row)
+  static constexpr size_t q_bytes = (size_t)QR * KS * 2;
+  static constexpr size_t k_bytes = (size_t)TT * KS * 2;
+  static constexpr size_t v_bytes = SHARED_V ? 0 : (size_t)TT * VS * 2;
   static constexpr size_t s_bytes = (size_t)MT * 16 * SS * 4;
   static constexpr size_t p_bytes = (size_t)MT * 16 * PS * 2;
   static constexpr size_t total = q_bytes + 2 * (k_bytes + v_bytes) + s_bytes + p_bytes + 3 * MT * 16 * 4;
-  static_assert((64 / NW) % 8 == 0 && (DV / NW) % 16 == 0, "each warp needs whole n8 tiles (pairs of them in PV)");
+  static_assert(TT == 32 || ((64 / NW) % 8 == 0), "each warp needs whole n8 tiles of token columns");
+  static_assert(TT == 64 || (MT * (TT / 8) == NW), "compact form: one 16 x 8 score tile per warp");
+  static_assert((DV / NW) % 16 == 0, "each warp needs pairs of n8 tiles of value columns");
 };
 
 // grid (splits, Hkv, B), NW * 32 threads.  FP8: the pools hold E4M3 bytes and a scale per (slot, head); a row's bytes land
 // in the upper half of its bf16 row in shared memory and are expanded in place (all reads, a barrier, all writes).
-template <int DQK, int DV, int MT, bool SHARED_V, int NW, bool FP8>
-__global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDecodeParams p) {
-  using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW>;
+template <int DQK, int DV, int MT, bool SHARED_V, int NW, bool FP8, int TT>
+__global__ void __launch_bounds__(NW * 32, (TT == 32) ? 2 : 1) paged_decode_kernel(const MmbPagedDecodeParams p) {
+  using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW, TT>;
   constexpr int NT = NW * 32;
-  constexpr int NQ = 64 / NW / 8;       // n8 tiles of token columns per warp in QK^T
+  constexpr int kTileTok = TT;          // shadows the file-level default inside this kernel
+  constexpr int NQ = (TT == 64) ? 64 / NW / 8 : 1;       // n8 tiles of token columns per warp in QK^T
   constexpr int NVT = DV / NW / 8;      // n8 tiles of value columns per warp in PV
   extern __shared__ __align__(128) unsigned char smem[];
   bf16* q_s = reinterpret_cast<bf16*>(smem);
@@ -374,7 +381,7 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
   const bool first_is_old = (lo_al + (tile_begin + 1) * kTileTok) <= ctx - 1;
   if (first_is_old) load_tile(tile_begin, 0);
   // query rows beyond the group are zero and never change
-  for (int i = tid; i < (MT * 16 - Gh) * (DQK / 8); i += NT)
+  for (int i = tid; i < (L::QR - Gh) * (DQK / 8); i += NT)
     *reinterpret_cast<uint4*>(q_s + (Gh + i / (DQK / 8)) * L::KS + (i % (DQK / 8)) * 8) = make_uint4(0, 0, 0, 0);
   pdl_launch_dependents();
   pdl_wait();
@@ -415,21 +422,25 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
     const bf16* vt = buf ? v_s1 : v_s0;
     if (FP8) {
       const int nvalid = min(kTileTok, ctx - (lo_al + tile * kTileTok));
-      expand_fp8_rows<DQK, L::KS, NT>(buf ? k_s1 : k_s0, scale_s[buf][0], nvalid, tid);
-      if (!SHARED_V) expand_fp8_rows<DV, L::VS, NT>(buf ? v_s1 : v_s0, scale_s[buf][1], nvalid, tid);
+      expand_fp8_rows<DQK, L::KS, NT, TT>(buf ? k_s1 : k_s0, scale_s[buf][0], nvalid, tid);
+      if (!SHARED_V) expand_fp8_rows<DV, L::VS, NT, TT>(buf ? v_s1 : v_s0, scale_s[buf][1], nvalid, tid);
     }
 
     // ---- S = Q K^T for this warp's token columns
     {
       // two accumulator sets (even / odd k16 steps) halve the dependent MMA chain of this latency-bound loop
-      float s[MT][NQ][4], s_odd[MT][NQ][4];
+      // this warp's part of S: all MT row tiles x its NQ column tiles (64-token tiles), or one 16 x 8 tile (32-token tiles)
+      constexpr int MQ = (TT == 64) ? MT : 1;
+      const int m_first = (TT == 64) ? 0 : warp / (TT / 8);
+      const int col_base = (TT == 64) ? warp * (64 / NW) : (warp % (TT / 8)) * 8;
+      float s[MQ][NQ][4], s_odd[MQ][NQ][4];
 #pragma unroll
-      for (int m = 0; m < MT; ++m)
+      for (int m = 0; m < MQ; ++m)
 #pragma unroll
         for (int n = 0; n < NQ; ++n)
 #pragma unroll
           for (int e = 0; e < 4; ++e) s[m][n][e] = s_odd[m][n][e] = 0.f;
-      const bf16* kb = kt + (warp * (64 / NW) + g) * L::KS + 2 * t;
+      const bf16* kb = kt + (col_base + g) * L::KS + 2 * t;
       static_assert(DQK % 32 == 0, "the QK^T loop consumes two k16 steps per trip");
 #pragma unroll 2
       for (int k0 = 0; k0 < DQK; k0 += 32) {
@@ -443,9 +454,11 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
             bfr[n][1] = *reinterpret_cast<const uint32_t*>(kb + n * 8 * L::KS + kk + 8);
           }
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
+          for (int m = 0; m < MQ; ++m) {
             uint32_t a0, a1, a2, a3;
-            ldmatrix_x4(a0, a1, a2, a3, q_s + (m * 16 + (lane & 15)) * L::KS + kk + (lane >> 4) * 8);
+            // compact query rows: rows beyond the head group read the zero row kept at the end
+            const int qrow = min((m_first + m) * 16 + (lane & 15), L::QR - 1);
+            ldmatrix_x4(a0, a1, a2, a3, q_s + qrow * L::KS + kk + (lane >> 4) * 8);
 #pragma unroll
             for (int n = 0; n < NQ; ++n) {
               if (half == 0) mma_bf16_16816(s[m][n], a0, a1, a2, a3, bfr[n][0], bfr[n][1]);
@@ -455,20 +468,20 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
         }
       }
 #pragma unroll
-      for (int m = 0; m < MT; ++m)
+      for (int m = 0; m < MQ; ++m)
 #pragma unroll
         for (int n = 0; n < NQ; ++n)
 #pragma unroll
           for (int e = 0; e < 4; ++e) s[m][n][e] += s_odd[m][n][e];
       const int tok0 = lo_al + tile * kTileTok;
 #pragma unroll
-      for (int m = 0; m < MT; ++m)
+      for (int m = 0; m < MQ; ++m)
 #pragma unroll
         for (int n = 0; n < NQ; ++n)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int r = m * 16 + g + ((e >> 1) << 3);
-            const int c = warp * (64 / NW) + n * 8 + 2 * t + (e & 1);
+            const int r = (m_first + m) * 16 + g + ((e >> 1) << 3);
+            const int c = col_base + n * 8 + 2 * t + (e & 1);
             const int tok = tok0 + c;
             const bool ok = (tok < ctx) && (tok >= lo);
             s_s[r * L::SS + c] = ok ? s[m][n][e] * p.scale : -INFINITY;
@@ -476,21 +489,22 @@ __global__ void __launch_bounds__(NW * 32) paged_decode_kernel(const MmbPagedDec
     }
     __syncthreads();
 
-    // ---- online softmax: 4 threads per row, 16 columns each
+    // ---- online softmax: 4 threads per row, a quarter of the tile's columns each
     if (tid < MT * 16 * 4) {
+      constexpr int CPT = TT / 4;
       const int r = tid >> 2, part = tid & 3;
-      const float* sr = s_s + r * L::SS + part * 16;
+      const float* sr = s_s + r * L::SS + part * CPT;
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) mx = fmaxf(mx, sr[c]);
+      for (int c = 0; c < CPT; ++c) mx = fmaxf(mx, sr[c]);
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_old = row_m[r];
       const float m_new = fmaxf(m_old, mx);
       float sum = 0.f;
-      bf16* pr = p_s + r * L::PS + part * 16;
+      bf16* pr = p_s + r * L::PS + part * CPT;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = 0; c < CPT; ++c) {
         const float e = (m_new == -INFINITY) ? 0.f : __expf(sr[c] - m_new);
         const bf16 eb = __float2bfloat16(e);
         pr[c] = eb;
@@ -771,10 +785,10 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
   }
 }
 
-template <int DQK, int DV, int MT, bool SHARED_V, int NW, bool FP8>
+template <int DQK, int DV, int MT, bool SHARED_V, int NW, bool FP8, int TT = 64>
 static int launch_decode_impl(const MmbPagedDecodeParams& p, cudaStream_t stream) {
-  using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW>;
-  auto kern = paged_decode_kernel<DQK, DV, MT, SHARED_V, NW, FP8>;
+  using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW, TT>;
+  auto kern = paged_decode_kernel<DQK, DV, MT, SHARED_V, NW, FP8, TT>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::total);
@@ -813,6 +827,8 @@ MMB_API int mmb_paged_decode(const MmbPagedDecodeParams* pp, cudaStream_t stream
   if (p.Hq % p.Hkv != 0 || p.splits < 1) return (int)cudaErrorInvalidValue;
   const int Gh = p.Hq / p.Hkv;
   const bool shared = (p.v_pool == nullptr);
+  if (shared && p.dqk == 576 && p.dv == 512 && Gh <= 23 && (long long)p.B * p.Hkv * p.splits > 148 && p.k_scale == nullptr)
+    return launch_decode_impl<576, 512, 2, true, 8, false, 32>(p, stream);      // more CTAs than SMs: two smaller CTAs per SM
   if (shared && p.dqk == 576 && p.dv == 512 && Gh <= 32) return launch_decode<576, 512, 2, true, 8>(p, stream);
   if (shared && p.dqk == 96 && p.dv == 64 && Gh <= 16) return launch_decode<96, 64, 1, true, 4>(p, stream);   // tiny MLA (tests)
   if (!shared && p.dqk == 128 && p.dv == 128 && Gh <= 16) return launch_decode<128, 128, 1, false, 8>(p, stream);

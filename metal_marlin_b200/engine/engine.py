@@ -67,7 +67,8 @@ class _DecodeBucket:
         self.step_no = torch.zeros(1, dtype=torch.int64, device=dev)
         cfg = model.cfg
         self.max_ctx = max_blocks * kv.block_size
-        self.splits = ops.default_splits(B, 1 if cfg.is_mla else cfg.num_key_value_heads, self.max_ctx)
+        self.splits = ops.default_splits(B, 1 if cfg.is_mla else cfg.num_key_value_heads, self.max_ctx,
+                                         mla_latent=cfg.is_mla and cfg.latent_dim == 576 and getattr(self.kv, "kv_dtype", "bf16") == "bf16")
         self.use_graph = use_graph and dev.type == "cuda"
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.seed = 0

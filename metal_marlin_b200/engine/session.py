@@ -63,7 +63,8 @@ class DecodeSession:
         self.use_history_penalty = False
         self.max_ctx = max_ctx or max_blocks_per_seq * kv.block_size
         cfg = model.cfg
-        self.splits = ops.default_splits(batch, 1 if cfg.is_mla else cfg.num_key_value_heads, self.max_ctx)
+        self.splits = ops.default_splits(batch, 1 if cfg.is_mla else cfg.num_key_value_heads, self.max_ctx,
+                                         mla_latent=cfg.is_mla and cfg.latent_dim == 576 and getattr(kv, "kv_dtype", "bf16") == "bf16")
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.use_graph = (dev.type == "cuda") if use_graph is None else use_graph
         self.launches_per_step = 0

@@ -366,10 +366,16 @@ def kv_fp8_rows(pool: "FP8KV", block_tables, ctx_lens, cu_k, total: int, max_ctx
     return out
 
 
-def default_splits(batch: int, n_kv_heads: int, max_ctx: int, sm_count: int = 148) -> int:
-    """Split-KV factor so that batch * kv_heads * splits covers the SMs (at least one 64-token tile per split)."""
+def default_splits(batch: int, n_kv_heads: int, max_ctx: int, sm_count: int = 148, mla_latent: bool = False) -> int:
+    """Split-KV factor so that batch * kv_heads * splits covers the SMs (at least one 64-token tile per split).
+    ``mla_latent``: the 576 / 512 latent shape has a two-CTAs-per-SM kernel variant (32-token tiles) that the launcher
+    picks when the grid exceeds the SM count, so once a batch leaves four splits per sequence or fewer the target is two
+    CTAs per SM."""
     tiles = max(1, (max_ctx + 63) // 64)
-    want = max(1, sm_count // max(1, batch * n_kv_heads))
+    bh = max(1, batch * n_kv_heads)
+    want = max(1, sm_count // bh)
+    if mla_latent and want <= 4 and bh <= 2 * sm_count:
+        want = max(1, (2 * sm_count) // bh)
     return int(max(1, min(want, tiles, 64)))
 
 
@@ -393,7 +399,7 @@ def paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, *, Hq, Hkv, dqk, 
     if splits is None:
         if max_ctx is None:
             max_ctx = block_tables.shape[1] * block_size
-        splits = default_splits(B, Hkv, max_ctx)
+        splits = default_splits(B, Hkv, max_ctx, mla_latent=(v_pool is None and dqk == 576 and dv == 512 and not fp8))
     if workspace is None:
         part_o = torch.empty(B * Hq * splits * dv, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=q.device)

@@ -77,7 +77,7 @@ def build_cases(dev, batch: int, ctx: int, variants: int = 1):
     qf = torch.empty(batch, NH, R + dr, dtype=torch.bfloat16, device=dev)
     cases["mla_prep"] = (lambda i=0: ops.mla_prep(q, kva, w_ukT[i % V], nkv, pos, inv, slots, qf, cache[i % V], NH, dn, dr, R, 1e-5,
                                                   1.0, True), w_ukT[0].numel() * 2)
-    splits = ops.default_splits(batch, 1, ctx)
+    splits = ops.default_splits(batch, 1, ctx, mla_latent=True)
     cases["mla_decode_attn"] = (lambda i=0: ops.paged_attention(qf, cache[i % V], None, bt, cl, Hq=NH, Hkv=1, dqk=R + dr, dv=R,
                                                                 block_size=bs, scale=1 / 16.0, splits=splits, w_uv=w_uv[i % V]),
                                 batch * ctx * (R + dr) * 2 + w_uv[0].numel() * 2)

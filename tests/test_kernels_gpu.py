@@ -231,6 +231,29 @@ def test_mla_decode_with_value_up_projection(H, R, dr, dvo, ctxs):
     _close(o, o_ref, rtol=3e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("window", [0, 300])
+def test_mla_decode_two_ctas_per_sm_variant(window):
+    """More (sequence, split) CTAs than SMs: the launcher takes the 32-token-tile kernel with compact query rows."""
+    torch.manual_seed(7)
+    H, R, dr, dvo, bs = 20, 512, 64, 256, 16
+    ctxs = [1, 31, 32, 33, 65, 700, 1000, 4096] * 3                     # 24 sequences
+    B = len(ctxs)
+    n_blocks = sum((c + bs - 1) // bs for c in ctxs) + 4
+    bt, cl = _paged_setup(B, ctxs, bs, n_blocks)
+    cache = _bf(n_blocks * bs, R + dr, scale=0.5)
+    q = _bf(B, H, R + dr, scale=0.3)
+    w_uv = _bf(H, dvo, R, scale=0.05)
+    scale = 1.0 / math.sqrt(192 + 64)
+    for splits in (7, 12):                                               # 168 and 288 CTAs
+        o = ops.paged_attention(q, cache, None, bt, cl, Hq=H, Hkv=1, dqk=R + dr, dv=R, block_size=bs, scale=scale, w_uv=w_uv,
+                                splits=splits, window=window)
+        with ops.force_reference():
+            o_ref = ops.paged_attention(q, cache, None, bt, cl, Hq=H, Hkv=1, dqk=R + dr, dv=R, block_size=bs, scale=scale, w_uv=w_uv,
+                                        window=window)
+        _close(o, o_ref, rtol=3e-2, atol=1e-2)
+    assert ops.default_splits(32, 1, 4096, mla_latent=True) == 9 and ops.default_splits(1, 1, 4096, mla_latent=True) == 64
+
+
 @pytest.mark.parametrize("T", [1, 5, 11])
 def test_mla_prep(T):
     H, dn, dr, R = 20, 192, 64, 512
