@@ -118,3 +118,67 @@ int mmb_moe_combine(const void* y, const int* inv, const void* add0, const void*
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+// Expert-parallel token exchange over peer memory (see ep_comm.cu).  Every rank owns, in memory all peers can address:
+//   recv_x    bf16 [ep][cap][H]   rows sent by rank src land in region src
+//   recv_meta int  [ep][cap][2]   (local expert id, pair index t * topk + slot at the sender)
+//   recv_cnt  int  [ep]           rows rank src sent this step
+//   ret_y     bf16 [cap][H]       expert outputs of this rank's own pairs, written by the expert owners
+//   flags     u32  [2][ep]        [0][src] dispatch of src arrived, [1][dst] returns of dst arrived (step numbers)
+typedef struct {
+  const void* x;                   // bf16 [T, H] local tokens (already normalized)
+  int ldx;
+  const int* ids;                  // int32 [T, topk] global expert ids, negative = dropped
+  int T, topk, H;
+  int experts_per_rank, ep, rank, cap;
+  void* const* peer_recv_x;        // device arrays [ep]: bases on rank d
+  int* const* peer_recv_meta;
+  int* const* peer_recv_cnt;
+  unsigned* const* peer_flags;     // flags[0][rank] on rank d
+  int* send_cnt;                   // local int [ep], zero before and after the launch
+  unsigned* counter;               // local CTA completion counter, zero before and after
+  const unsigned* step;
+  int* status;                     // 120: more than cap rows for one destination
+} MmbEpDispatchParams;
+int mmb_ep_dispatch(const MmbEpDispatchParams* p, cudaStream_t stream);
+
+typedef struct {
+  const int* recv_meta;            // local
+  const int* recv_cnt;
+  const unsigned* flags;           // local flags[0][*]
+  const unsigned* step;
+  int* status;                     // 121 + src: dispatch of rank src did not arrive within the limit
+  int ep, cap, H, E_local, token_tile, max_tiles;
+  const long long* ret_peer;       // device [ep]: address of ret_y on rank src
+  int* order;                      // [ep * cap]: sorted position -> row of recv_x (-1 padded)
+  long long* row_dst;              // [ep * cap]: sorted position -> address of the row's slot in the sender's ret_y (0 padded)
+  int* tile_expert;
+  int* tile_row0;
+  int* tile_rows;
+  int* n_tiles;
+} MmbEpRecvParams;
+int mmb_ep_recv_group(const MmbEpRecvParams* p, cudaStream_t stream);
+
+// Publishes `step` in flags[1][rank] of every peer after everything earlier in the stream (the down projection whose
+// epilogue stored into the peers' ret_y) is complete.
+int mmb_ep_signal(unsigned* const* peer_flags, const unsigned* step, int ep, cudaStream_t stream);
+
+typedef struct {
+  const void* ret_y;               // local bf16 [T * topk, N]
+  const int* ids;                  // [T, topk] (negative = dropped)
+  const float* weights;            // fp32 [T, topk]
+  const void* add0;                // optional bf16 [T, N]
+  const void* add1;
+  void* out;                       // bf16 [T, N]
+  int T, topk, N, ep;
+  const unsigned* flags;           // local flags[1][*]
+  const unsigned* step;
+  int* status;                     // 140 + dst: returns of rank dst did not arrive within the limit
+} MmbEpCombineParams;
+int mmb_ep_combine(const MmbEpCombineParams* p, cudaStream_t stream);
+#ifdef __cplusplus
+}
+#endif

@@ -51,6 +51,10 @@ typedef struct {
   const unsigned* rs_step;          // device scalar: current step number
   int rs_tp, rs_rank, rs_rows;
   MmbAgWait ag;                     // all-zero: x is complete when the kernel starts
+  // Optional scatter epilogue (expert-parallel combine): row r of the result is stored as bf16 [N] at the address
+  // out_rows[r] instead of out + r * ldo (0 = row not stored).  The addresses may lie in peer memory: the expert
+  // outputs go straight from the epilogue into the token owners' return buffers over NVLink.
+  const long long* out_rows;
 } MmbFp4GemmParams;
 
 int mmb_fp4_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);

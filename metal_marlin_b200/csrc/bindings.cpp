@@ -638,9 +638,25 @@ void tp_wait(const Tensor& desc) {
 }
 
 // Grouped (MoE) GEMM: x rows are sorted by expert; the tile list lives on the device.
+static void fp4_gemm_grouped_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
+                                  const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
+                                  int64_t token_tile, const OptT& row_scale, Tensor status, const Tensor* out_rows);
 void fp4_gemm_grouped(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
                       const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
                       int64_t token_tile, const OptT& row_scale, Tensor status) {
+  fp4_gemm_grouped_impl(x, qw, sc, out, N, gs, tile_expert, tile_row0, tile_rows, n_tiles, token_tile, row_scale, status, nullptr);
+}
+// Same GEMM with the scatter epilogue: row r of the result goes to the address out_rows[r] (int64 [M] on the device, 0 = skip;
+// the addresses may be peer memory).  `out` only supplies the row width.
+void fp4_gemm_grouped_scatter(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
+                              const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
+                              int64_t token_tile, Tensor status, const Tensor& out_rows) {
+  TORCH_CHECK(out_rows.is_cuda() && out_rows.scalar_type() == at::kLong && out_rows.is_contiguous() && out_rows.numel() >= x.size(0));
+  fp4_gemm_grouped_impl(x, qw, sc, out, N, gs, tile_expert, tile_row0, tile_rows, n_tiles, token_tile, c10::nullopt, status, &out_rows);
+}
+static void fp4_gemm_grouped_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
+                                  const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
+                                  int64_t token_tile, const OptT& row_scale, Tensor status, const Tensor* out_rows) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && qw.dim() == 5 && qw.is_contiguous() &&
@@ -672,7 +688,106 @@ void fp4_gemm_grouped(const Tensor& x, const Tensor& qw, const Tensor& sc, Tenso
     TORCH_CHECK(row_scale->scalar_type() == at::kFloat && row_scale->is_contiguous());
     p.row_scale = row_scale->data_ptr<float>();
   }
+  if (out_rows != nullptr) p.out_rows = reinterpret_cast<const long long*>(out_rows->data_ptr<int64_t>());
   check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm_grouped");
+}
+
+// ---- expert-parallel exchange (ep_comm.cu).  Descriptors are CPU int64 tensors of device addresses.
+// desc [8] = tables (device arrays of ep pointers) peer_recv_x, peer_recv_meta, peer_recv_cnt, peer_flags; then the local
+// send_cnt, counter, step, status
+void ep_dispatch(const Tensor& x, const Tensor& ids, const Tensor& desc, int64_t experts_per_rank, int64_t ep, int64_t rank, int64_t cap) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && ids.scalar_type() == at::kInt && ids.is_contiguous() && ids.dim() == 2 &&
+              ids.size(0) == x.size(0));
+  TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kLong && desc.numel() == 8);
+  const int64_t* v = desc.data_ptr<int64_t>();
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbEpDispatchParams p{};
+  p.x = x.data_ptr();
+  p.ldx = (int)x.stride(0);
+  p.ids = ids.data_ptr<int>();
+  p.T = (int)x.size(0);
+  p.topk = (int)ids.size(1);
+  p.H = (int)x.size(1);
+  p.experts_per_rank = (int)experts_per_rank;
+  p.ep = (int)ep;
+  p.rank = (int)rank;
+  p.cap = (int)cap;
+  p.peer_recv_x = reinterpret_cast<void* const*>(v[0]);
+  p.peer_recv_meta = reinterpret_cast<int* const*>(v[1]);
+  p.peer_recv_cnt = reinterpret_cast<int* const*>(v[2]);
+  p.peer_flags = reinterpret_cast<unsigned* const*>(v[3]);
+  p.send_cnt = reinterpret_cast<int*>(v[4]);
+  p.counter = reinterpret_cast<unsigned*>(v[5]);
+  p.step = reinterpret_cast<const unsigned*>(v[6]);
+  p.status = reinterpret_cast<int*>(v[7]);
+  check(mmb_ep_dispatch(&p, cur_stream()), "ep_dispatch");
+}
+
+// desc [6] = recv_meta, recv_cnt, flags, step, status, ret_peer table (device int64 [ep])
+void ep_recv_group(const Tensor& desc, int64_t ep, int64_t cap, int64_t H, int64_t E_local, int64_t token_tile, Tensor order, Tensor row_dst,
+                   Tensor tile_expert, Tensor tile_row0, Tensor tile_rows, Tensor n_tiles) {
+  TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kLong && desc.numel() == 6);
+  TORCH_CHECK(order.is_cuda() && order.scalar_type() == at::kInt && order.numel() == ep * cap && row_dst.scalar_type() == at::kLong &&
+              row_dst.numel() == ep * cap && order.is_contiguous() && row_dst.is_contiguous());
+  TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_row0.scalar_type() == at::kInt && tile_rows.scalar_type() == at::kInt &&
+              n_tiles.scalar_type() == at::kInt && tile_row0.numel() == tile_expert.numel() && tile_rows.numel() == tile_expert.numel());
+  const int64_t* v = desc.data_ptr<int64_t>();
+  c10::cuda::CUDAGuard guard(order.device());
+  MmbEpRecvParams p{};
+  p.recv_meta = reinterpret_cast<const int*>(v[0]);
+  p.recv_cnt = reinterpret_cast<const int*>(v[1]);
+  p.flags = reinterpret_cast<const unsigned*>(v[2]);
+  p.step = reinterpret_cast<const unsigned*>(v[3]);
+  p.status = reinterpret_cast<int*>(v[4]);
+  p.ret_peer = reinterpret_cast<const long long*>(v[5]);
+  p.ep = (int)ep;
+  p.cap = (int)cap;
+  p.H = (int)H;
+  p.E_local = (int)E_local;
+  p.token_tile = (int)token_tile;
+  p.max_tiles = (int)tile_expert.numel();
+  p.order = order.data_ptr<int>();
+  p.row_dst = reinterpret_cast<long long*>(row_dst.data_ptr<int64_t>());
+  p.tile_expert = tile_expert.data_ptr<int>();
+  p.tile_row0 = tile_row0.data_ptr<int>();
+  p.tile_rows = tile_rows.data_ptr<int>();
+  p.n_tiles = n_tiles.data_ptr<int>();
+  check(mmb_ep_recv_group(&p, cur_stream()), "ep_recv_group");
+}
+
+// desc [2] = peer_flags table (device array of ep pointers), step
+void ep_signal(const Tensor& desc, int64_t ep) {
+  TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kLong && desc.numel() == 2);
+  const int64_t* v = desc.data_ptr<int64_t>();
+  check(mmb_ep_signal(reinterpret_cast<unsigned* const*>(v[0]), reinterpret_cast<const unsigned*>(v[1]), (int)ep, cur_stream()), "ep_signal");
+}
+
+// desc [4] = ret_y, flags, step, status
+void ep_combine(const Tensor& desc, const Tensor& ids, const Tensor& weights, const OptT& add0, const OptT& add1, Tensor out, int64_t ep) {
+  check_bf16(out, "out");
+  TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kLong && desc.numel() == 4);
+  TORCH_CHECK(out.dim() == 2 && out.is_contiguous() && ids.scalar_type() == at::kInt && ids.is_contiguous() && ids.dim() == 2 &&
+              ids.size(0) == out.size(0) && weights.scalar_type() == at::kFloat && weights.is_contiguous() && weights.numel() == ids.numel());
+  if (add0.has_value() && add0->defined()) TORCH_CHECK(add0->is_contiguous() && add0->scalar_type() == at::kBFloat16 && add0->numel() == out.numel());
+  if (add1.has_value() && add1->defined()) TORCH_CHECK(add1->is_contiguous() && add1->scalar_type() == at::kBFloat16 && add1->numel() == out.numel());
+  const int64_t* v = desc.data_ptr<int64_t>();
+  c10::cuda::CUDAGuard guard(out.device());
+  MmbEpCombineParams p{};
+  p.ret_y = reinterpret_cast<const void*>(v[0]);
+  p.flags = reinterpret_cast<const unsigned*>(v[1]);
+  p.step = reinterpret_cast<const unsigned*>(v[2]);
+  p.status = reinterpret_cast<int*>(v[3]);
+  p.ids = ids.data_ptr<int>();
+  p.weights = weights.data_ptr<float>();
+  p.add0 = cptr(add0);
+  p.add1 = cptr(add1);
+  p.out = out.data_ptr();
+  p.T = (int)out.size(0);
+  p.topk = (int)ids.size(1);
+  p.N = (int)out.size(1);
+  p.ep = (int)ep;
+  check(mmb_ep_combine(&p, cur_stream()), "ep_combine");
 }
 
 void bf16_gemm_impl(const Tensor& x, const Tensor& w, Tensor out, Tensor status, const Tensor* ag);
@@ -967,6 +1082,11 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("codebook_gemv", &codebook_gemv);
   m.def("vision_preprocess", &vision_preprocess);
   m.def("spec_verify", &spec_verify);
+  m.def("fp4_gemm_grouped_scatter", &fp4_gemm_grouped_scatter);
+  m.def("ep_dispatch", &ep_dispatch);
+  m.def("ep_recv_group", &ep_recv_group);
+  m.def("ep_signal", &ep_signal);
+  m.def("ep_combine", &ep_combine);
   m.def("moe_group", &moe_group);
   m.def("moe_gather", &moe_gather);
   m.def("moe_combine", &moe_combine);

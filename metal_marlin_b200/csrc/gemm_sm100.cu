@@ -374,6 +374,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
                 // reduce-scatter epilogue: the partial goes to the rank that owns this token row
                 const int row = tok0 + r, owner = row / p.rs_rows;
                 p.rs_peer_bufs[owner][((long long)p.rs_rank * p.rs_rows + (row - owner * p.rs_rows)) * N + n] = f;
+              } else if (WFMT == 0 && p.out_rows != nullptr) {
+                // scatter epilogue: the row's destination (possibly in a peer's memory) comes from a device table
+                bf16* dst = reinterpret_cast<bf16*>(p.out_rows[tok0 + r]);
+                if (dst != nullptr) dst[n] = __float2bfloat16(f);
               } else if (WFMT == 0) {
                 if (p.row_scale) f *= p.row_scale[tok0 + r];
                 reinterpret_cast<bf16*>(p.out)[(long long)(tok0 + r) * ldo + n] = __float2bfloat16(f);
@@ -386,6 +390,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           }
         }
       }
+      if (WFMT == 0 && p.out_rows != nullptr) __threadfence_system();     // peer stores ordered before the grid completes
     }
   }
   if (WFMT == 0 && p.rs_peer_bufs != nullptr) {

@@ -7,14 +7,18 @@ Two regimes:
   which the MoE kernels skip - and the partial outputs are summed with the same in-kernel NVLink exchange the
   tensor-parallel row projections use (``csrc/tp_comm.cuh``): dispatch is implicit, combine is fused into the
   down-projection epilogue.
-* prefill / large batches: tokens are sent to the ranks owning their experts (all-to-all), run through the grouped
-  tcgen05 expert GEMM there and returned (all-to-all), the NCCL baseline.
+* prefill / large batches, every rank holding different tokens: tokens travel to the ranks owning their experts, run
+  through the grouped tcgen05 expert GEMM there and come back.  ``forward_fused`` does the whole exchange inside our own
+  kernels over NVLink peer memory (``csrc/ep_comm.cu``): sender warps store token rows straight into the owners' receive
+  regions, the owner builds the GEMM tile list on the device once the senders' flags arrive, and the down projection's
+  epilogue stores every output row directly into the token owner's return buffer; no collective call, no host
+  synchronisation on the routing result.  ``forward_dispatch`` is the NCCL all-to-all baseline of the same thing.
 
 Parity: reference ``metal_marlin/distributed/expert_parallel.py`` (simulated expert placement + dispatch / combine).
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -96,3 +100,146 @@ class ExpertParallelMoE:
         out = torch.zeros(T, self.down.out_features, dtype=torch.float32, device=dev)
         out.index_add_(0, tok, back.to(torch.float32) * w_sorted.unsqueeze(-1))
         return out.to(torch.bfloat16)
+
+
+    def forward_fused(self, ex: "EPExchange", x_local, ids_local, weights_local, *, norm_w=None, eps=1e-6, add0=None, add1=None,
+                      token_tile: int = 0):
+        """Same result as :meth:`forward_dispatch` (+ ``add0`` + ``add1``, e.g. the shared expert and the residual input)
+        with the dispatch, the expert GEMMs and the combine chained on the device over peer memory."""
+        if not (x_local.is_cuda and ops.native_available()):
+            out = self.forward_dispatch(x_local, ids_local, weights_local, norm_w=norm_w, eps=eps).to(torch.float32)
+            for a in (add0, add1):
+                if a is not None:
+                    out = out + a.to(torch.float32)
+            return out.to(torch.bfloat16)
+        st = self.fused_dispatch(ex, x_local, ids_local, weights_local, norm_w=norm_w, eps=eps)
+        self.fused_experts(ex, expected_rows=ids_local.numel(), token_tile=token_tile)
+        return self.fused_combine(ex, st, add0=add0, add1=add1)
+
+    # The three phases of forward_fused, separately callable so that several emulated ranks on one GPU can be stepped phase
+    # by phase (a kernel must never wait for a launch that comes after it in the same stream).
+    def fused_dispatch(self, ex: "EPExchange", x_local, ids_local, weights_local, *, norm_w=None, eps=1e-6):
+        """Phase 1 (token owner): normalise, then store every (token, slot) row into the expert owner's receive region."""
+        T, k = ids_local.shape
+        assert ex.ep == self.ep and ex.rank == self.rank and T * k <= ex.cap and x_local.shape[1] == ex.hidden
+        xin = ops.rmsnorm(x_local, norm_w, eps) if norm_w is not None else x_local
+        ids32 = ids_local.to(torch.int32).contiguous()
+        ex.begin()
+        per = (self.num_routed + self.ep - 1) // self.ep
+        ops.K.mmb200.ep_dispatch(xin, ids32, ex.desc_dispatch, per, self.ep, self.rank, ex.cap)
+        return ids32, weights_local.to(torch.float32).contiguous()
+
+    def fused_experts(self, ex: "EPExchange", *, expected_rows: int, token_tile: int = 0) -> None:
+        """Phase 2 (expert owner): wait for the senders, group the received rows, run the experts, return the rows."""
+        K = ops.K.mmb200
+        dev = ex.local.device
+        gu_b, dn_b = self.gate_up, self.down
+        n = self.ep * ex.cap
+        if not token_tile:      # rows arrive from every rank: a local expert expects about expected_rows / n_local of them
+            avg = expected_rows / max(1, self.n_local)
+            token_tile = 32 if avg <= 24 else (64 if avg <= 48 else (128 if avg <= 160 else 256))
+        max_tiles = n // token_tile + self.n_local + 1
+        order = torch.empty(n, dtype=torch.int32, device=dev)
+        row_dst = torch.empty(n, dtype=torch.int64, device=dev)
+        t_e = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+        t_r0, t_rows = torch.empty_like(t_e), torch.empty_like(t_e)
+        n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+        K.ep_recv_group(ex.desc_recv, self.ep, ex.cap, dn_b.out_features, max(1, self.n_local), token_tile, order, row_dst, t_e, t_r0,
+                        t_rows, n_tiles)
+        st = ops.gemm_status(dev)
+        xs = torch.empty(n, gu_b.in_features, dtype=torch.bfloat16, device=dev)
+        K.moe_gather(ex.recv_x, order, xs, 1)
+        gu = torch.empty(n, gu_b.out_features, dtype=torch.bfloat16, device=dev)
+        K.fp4_gemm_grouped(xs, gu_b.qtile, gu_b.stile, gu, gu_b.out_features, gu_b.group_size, t_e, t_r0, t_rows, n_tiles, token_tile,
+                           None, st)
+        h = torch.empty(n, gu_b.out_features // 2, dtype=torch.bfloat16, device=dev)
+        K.silu_mul(gu, h)
+        # down projection: every output row goes from the epilogue into its token owner's return buffer
+        K.fp4_gemm_grouped_scatter(h, dn_b.qtile, dn_b.stile, ex.ret_y[:1], dn_b.out_features, dn_b.group_size, t_e, t_r0, t_rows,
+                                   n_tiles, token_tile, st, row_dst)
+        K.ep_signal(ex.desc_signal, self.ep)
+
+    def fused_combine(self, ex: "EPExchange", state, *, add0=None, add1=None):
+        """Phase 3 (token owner): wait for the owners' returns, routing-weighted sum over the slots (+ adds)."""
+        ids32, w32 = state
+        out = torch.empty(ids32.shape[0], self.down.out_features, dtype=torch.bfloat16, device=ids32.device)
+        ops.K.mmb200.ep_combine(ex.desc_combine, ids32, w32, None if add0 is None else add0.contiguous(),
+                                None if add1 is None else add1.contiguous(), out, self.ep)
+        return out
+
+
+class EPExchange:
+    """One rank's peer-addressable buffers for :meth:`ExpertParallelMoE.forward_fused` and the descriptors the kernels take.
+
+    Layout of the allocation (identical on every rank): flag words ``u32 [2][ep]``, received row counts ``int [ep]``, local
+    scratch words (send counters, CTA counter, step, status), ``recv_meta int [ep][cap][2]``, ``recv_x bf16 [ep][cap][H]``,
+    ``ret_y bf16 [cap][H]`` with ``cap = max_tokens * topk`` (the worst case: every pair of a rank goes to one owner).
+    One buffer serves every layer: a rank can only start the next layer's dispatch after its combine saw all return
+    flags, i.e. after every owner finished reading the previous layer's rows."""
+
+    OFF_FLAGS, OFF_CNT, OFF_SEND, OFF_COUNTER, OFF_STEP, OFF_STATUS, OFF_META = 0, 256, 512, 640, 644, 648, 1024
+
+    @staticmethod
+    def layout(ep: int, cap: int, hidden: int) -> Dict[str, int]:
+        assert ep <= 32 and hidden % 8 == 0
+        meta = EPExchange.OFF_META
+        rx = (meta + ep * cap * 8 + 255) // 256 * 256
+        ry = (rx + ep * cap * hidden * 2 + 255) // 256 * 256
+        return {"meta": meta, "recv_x": rx, "ret_y": ry, "bytes": ry + cap * hidden * 2}
+
+    def __init__(self, rank: int, ep: int, hidden: int, max_tokens: int, topk: int, local: torch.Tensor, peer_ptrs: Sequence[int]):
+        self.rank, self.ep, self.hidden, self.cap = rank, ep, hidden, max_tokens * topk
+        self.local, self.peer_ptrs = local, [int(p) for p in peer_ptrs]
+        lay = self.layout(ep, self.cap, hidden)
+        assert local.numel() >= lay["bytes"] and local.dtype == torch.uint8 and self.peer_ptrs[rank] == local.data_ptr()
+        dev = local.device
+        base = local.data_ptr()
+        self.recv_x = local[lay["recv_x"]: lay["recv_x"] + ep * self.cap * hidden * 2].view(torch.bfloat16).view(ep * self.cap, hidden)
+        self.ret_y = local[lay["ret_y"]: lay["ret_y"] + self.cap * hidden * 2].view(torch.bfloat16).view(self.cap, hidden)
+        self.step = local[self.OFF_STEP: self.OFF_STEP + 4].view(torch.int32)
+        self.status = local[self.OFF_STATUS: self.OFF_STATUS + 4].view(torch.int32)
+        tbl = torch.tensor([[p + lay["recv_x"] for p in self.peer_ptrs],
+                            [p + lay["meta"] for p in self.peer_ptrs],
+                            [p + self.OFF_CNT for p in self.peer_ptrs],
+                            [p + self.OFF_FLAGS + 4 * rank for p in self.peer_ptrs],                 # dispatch flag [0][rank] on d
+                            [p + lay["ret_y"] for p in self.peer_ptrs],
+                            [p + self.OFF_FLAGS + 4 * (ep + rank) for p in self.peer_ptrs]],        # return flag [1][rank] on s
+                           dtype=torch.int64).to(dev)
+        self._tbl = tbl
+        row = lambda i: tbl.data_ptr() + i * ep * 8
+        i64 = lambda *v: torch.tensor(list(v), dtype=torch.int64)
+        self.desc_dispatch = i64(row(0), row(1), row(2), row(3), base + self.OFF_SEND, base + self.OFF_COUNTER, base + self.OFF_STEP,
+                                 base + self.OFF_STATUS)
+        self.desc_recv = i64(base + lay["meta"], base + self.OFF_CNT, base + self.OFF_FLAGS, base + self.OFF_STEP, base + self.OFF_STATUS,
+                             row(4))
+        self.desc_signal = i64(row(5), base + self.OFF_STEP)
+        self.desc_combine = i64(base + lay["ret_y"], base + self.OFF_FLAGS + 4 * ep, base + self.OFF_STEP, base + self.OFF_STATUS)
+
+    def begin(self) -> None:
+        """Advance the exchange epoch (every rank, once per exchanged layer)."""
+        self.step += 1
+
+    def check(self) -> int:
+        """0, or the code of the wait that gave up / the overflow (reads the device: call between steps)."""
+        return int(self.status.item())
+
+    @classmethod
+    def create(cls, hidden: int, max_tokens: int, topk: int, device, group=None) -> "EPExchange":
+        """Allocates the buffers in symmetric memory of ``group`` (one rank per GPU)."""
+        from .symm import SymmetricBuffer
+        g = group if group is not None else dist.group.WORLD
+        ep, rank = dist.get_world_size(g), dist.get_rank(g)
+        buf = SymmetricBuffer(cls.layout(ep, max_tokens * topk, hidden)["bytes"], torch.device(device), g)
+        ex = cls(rank, ep, hidden, max_tokens, topk, buf.local, buf.peer_ptrs)
+        ex._buf = buf
+        return ex
+
+    @classmethod
+    def emulated(cls, ep: int, hidden: int, max_tokens: int, topk: int, device) -> List["EPExchange"]:
+        """All ``ep`` ranks' buffers on ONE device (tests, single-GPU bring-up).  The kernels of the emulated ranks must be
+        launched phase by phase - every rank's dispatch, then every rank's expert pass, then every rank's combine - so
+        that no launch ever waits for a later one."""
+        nbytes = cls.layout(ep, max_tokens * topk, hidden)["bytes"]
+        bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(ep)]
+        ptrs = [b.data_ptr() for b in bufs]
+        return [cls(r, ep, hidden, max_tokens, topk, bufs[r], ptrs) for r in range(ep)]

@@ -63,6 +63,10 @@ def _worker(rank, world, port, q):
         routed = ops.moe_forward(x, L.gate_up_bank, L.down_bank, ids, wts, n_shared=0, shared_base=cfg.num_experts, norm_w=L.post_norm).float()
         got_d = ep.forward_dispatch(x[half], ids[half], wts[half], norm_w=L.post_norm).float()
         res["ep_dispatch"] = float((got_d - routed[half]).abs().max() / routed.abs().max())
+        # the fused entry point falls back to the collective path off the GPU (and adds what the caller passes)
+        got_f = ep.forward_fused(None, x[half], ids[half], wts[half], norm_w=L.post_norm, add0=x[half]).float()
+        want_f = routed[half] + x[half].float()
+        res["ep_fused_cpu"] = float((got_f - want_f).abs().max() / want_f.abs().max())
         # pipeline: 2 stages vs the whole model
         toks = list(range(3, 19))
         ref_logits = lm.forward_logits(toks)
@@ -106,5 +110,6 @@ def test_ep_pp_cp_on_two_cpu_ranks():
         assert res["mesh"]
         assert res["ep_replicated"] < 2e-2, res
         assert res["ep_dispatch"] < 2e-2, res
+        assert res["ep_fused_cpu"] < 3e-2, res
         assert res["cp"] < 1e-4, res
     assert results[world - 1]["pp"] < 1e-2, results
