@@ -182,3 +182,24 @@ int mmb_ep_combine(const MmbEpCombineParams* p, cudaStream_t stream);
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+// Causal prefill attention of ONE sequence on the tcgen05 tensor cores (see attention_fmha_sm100.cu).
+// q [t, Hq, D], k [n, Hk, D] (element strides given), vt [Hk, D, n_pad] = V transposed per head with n_pad % 8 == 0 and
+// zeros behind column n; out [t, Hq, D] bf16.  Query row i sits at key position n - t + i.  D is 128 or 256.
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* vt;
+  void* out;
+  int t, n, n_pad, Hq, Hk, D;
+  long long q_tok_stride, q_head_stride, k_tok_stride, k_head_stride, o_tok_stride, o_head_stride;
+  float scale;
+  int* status;            // device int: 31..36 after a bounded wait expired (producer, mma, softmax stages)
+} MmbFmhaPrefillParams;
+int mmb_fmha_prefill(const MmbFmhaPrefillParams* p, cudaStream_t stream);
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,345 @@
+// Causal prefill attention on the tcgen05 tensor cores.
+//
+// One CTA owns 128 query rows of one head and walks the keys in tiles of 128:
+//   warp 0      TMA producer: Q once, then per tile the K rows [128 keys x D] and the V^T block [D x 128 keys]
+//               (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers);
+//   warp 1      one elected thread issues the MMAs: S = Q K^T (M 128, N 128, K = D) into one of two S buffers in TMEM,
+//               O += P V (M 128, N = D, K 128) into the O accumulator in TMEM; tcgen05.commit signals the mbarriers.
+//               S of tile j + 1 is issued before P V of tile j, so it runs under the soft-max of tile j;
+//   warps 2-5   soft-max, one query row per thread (its TMEM lane): tcgen05.ld of the 128 scores, scale, causal mask,
+//               running maximum with LAZY rescaling (the reference maximum only moves when a row's maximum grew by more
+//               than 2^8, decided per warp; then the O rows are rescaled in TMEM with tcgen05.ld / tcgen05.st), exp2,
+//               P rounded to bf16 and stored as the K-major swizzled A operand of the P V MMA; finally O / l -> global.
+// TMEM: O in columns [0, D), S buffers at D and D + 128 (512 columns for D = 256).
+// Shared memory (D = 256): Q 64 KB, K 64 KB, V^T 64 KB, P 32 KB - single buffers; the load of K(j+1) starts when S(j) is
+// complete and the load of V(j+1) when P V(j) is complete, both under the soft-max.
+// Every mbarrier wait is bounded; on expiry a code goes to the status word, the roles stop, TMEM is freed.
+#include "api_ext.h"
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace mmb {
+
+constexpr int kFmThreads = 192;
+constexpr float kFmLazyLog2 = 8.f;      // rescale O only when a row maximum grew by more than this (log2 units)
+
+struct FmhaShared {
+  uint64_t q_full, k_full, v_full, s_full[2], p_full, o_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int D>
+struct FmhaCfg {
+  static constexpr int KB = D / 64;                 // 64-wide k blocks of the head dimension
+  static constexpr int q_bytes = KB * 16384;
+  static constexpr int k_bytes = KB * 16384;
+  static constexpr int v_half = D * 128;            // V^T rows [D] x 64 keys
+  static constexpr int v_bytes = 2 * v_half;
+  static constexpr int p_bytes = 2 * 16384;
+  static constexpr size_t smem_bytes = (size_t)q_bytes + k_bytes + v_bytes + p_bytes + 1024 + 256;
+};
+
+// kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t fm_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ float fm_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t fm_pack(float a, float b) {
+  const bf162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kFmThreads, 1)
+fmha_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const MmbFmhaPrefillParams p) {
+  using Cfg = FmhaCfg<D>;
+  extern __shared__ unsigned char smem_fm[];
+  unsigned char* Qs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_fm) + 1023) & ~(uintptr_t)1023);
+  unsigned char* Ks = Qs + Cfg::q_bytes;
+  unsigned char* Vs = Ks + Cfg::k_bytes;
+  unsigned char* Ps = Vs + Cfg::v_bytes;
+  FmhaShared* sh = reinterpret_cast<FmhaShared*>(Ps + Cfg::p_bytes);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;       // the tiles with the most keys start first
+  const int q0 = qt * 128, h = blockIdx.y, hk = h / (p.Hq / p.Hk);
+  const int q_off = p.n - p.t;
+  const int nt = (q_off + min(q0 + 127, p.t - 1)) / 128 + 1;   // key tiles this query tile can see
+  int* status = p.status;
+
+  if (tid == 0) {
+    mbar_init(&sh->q_full, 1);
+    mbar_init(&sh->k_full, 1);
+    mbar_init(&sh->v_full, 1);
+    mbar_init(&sh->s_full[0], 1);
+    mbar_init(&sh->s_full[1], 1);
+    mbar_init(&sh->p_full, 4);
+    mbar_init(&sh->o_done, 1);
+    sh->abort_flag = 0;
+    fence_proxy_async_smem();
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+  volatile int* abort_flag = &sh->abort_flag;
+  auto fail = [&](int code) {
+    if (atomicExch(&sh->abort_flag, 1) == 0 && status) atomicExch(status, code);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&sh->q_full, Cfg::q_bytes);
+      for (int kb = 0; kb < Cfg::KB; ++kb) tma_load_3d(Qs + kb * 16384, &tm_q, &sh->q_full, kb * 64, h, q0);
+      for (int j = 0; j < nt; ++j) {
+        if (j > 0 && !mbar_wait(&sh->s_full[(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1u, abort_flag)) {   // K buffer read by S(j-1)
+          fail(31);
+          break;
+        }
+        mbar_expect_tx(&sh->k_full, Cfg::k_bytes);
+        for (int kb = 0; kb < Cfg::KB; ++kb) tma_load_3d(Ks + kb * 16384, &tm_k, &sh->k_full, kb * 64, hk, j * 128);
+        if (j > 0 && !mbar_wait(&sh->o_done, (uint32_t)(j - 1) & 1u, abort_flag)) {                         // V buffer read by PV(j-1)
+          fail(32);
+          break;
+        }
+        mbar_expect_tx(&sh->v_full, Cfg::v_bytes);
+        for (int kb = 0; kb < 2; ++kb) tma_load_3d(Vs + kb * Cfg::v_half, &tm_v, &sh->v_full, j * 128 + kb * 64, 0, hk);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t id_s = fm_idesc(128), id_o = fm_idesc(D);
+      bool ok = mbar_wait(&sh->q_full, 0u, abort_flag);
+      if (!ok) fail(33);
+      auto issue_s = [&](int j) -> bool {
+        if (!mbar_wait(&sh->k_full, (uint32_t)j & 1u, abort_flag)) {
+          fail(34);
+          return false;
+        }
+        tc_fence_after();
+        const uint32_t ts = tmem_base + (uint32_t)(D + (j & 1) * 128);
+#pragma unroll
+        for (int kb = 0; kb < Cfg::KB; ++kb) {
+          const uint64_t ad = make_sw128_desc(Qs + kb * 16384), bd = make_sw128_desc(Ks + kb * 16384);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_bf16(ts, ad + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), id_s, (uint32_t)((kb | k) != 0));
+        }
+        umma_commit(&sh->s_full[j & 1]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < nt && ok; ++j) {
+        if (j + 1 < nt) ok = issue_s(j + 1);       // runs under the soft-max of tile j
+        if (!ok) break;
+        if (!mbar_wait(&sh->p_full, (uint32_t)j & 1u, abort_flag) || !mbar_wait(&sh->v_full, (uint32_t)j & 1u, abort_flag)) {
+          fail(35);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t ad = make_sw128_desc(Ps + kb * 16384), bd = make_sw128_desc(Vs + kb * Cfg::v_half);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base, ad + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), id_o, (uint32_t)((j | kb | k) != 0));
+        }
+        umma_commit(&sh->o_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ soft-max: one query row per thread
+    const int quarter = warp & 3;                     // TMEM lane quarter this warp may access
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float c = p.scale * 1.4426950408889634f;
+    const int my_pos = q_off + q0 + row;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nt; ++j) {
+      if (!mbar_wait(&sh->s_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) {
+        fail(36);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t ts = tmem_base + lane_addr + (uint32_t)(D + (j & 1) * 128);
+      uint32_t v[4][32];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) tmem_ld32(ts + (uint32_t)(cc * 32), v[cc]);
+      tmem_ld_wait();
+      const int key0 = j * 128;
+      const bool need_mask = (key0 + 127 > q_off + q0) || (key0 + 128 > p.n);
+      float mt = -INFINITY;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(v[cc][i]) * c;
+          if (need_mask) {
+            const int key = key0 + cc * 32 + i;
+            if (key > my_pos || key >= p.n) x = -INFINITY;
+          }
+          v[cc][i] = __float_as_uint(x);
+          mt = fmaxf(mt, x);
+        }
+      float alpha = 1.f;
+      bool resc = false;
+      if (j == 0) {
+        m_ref = mt;
+      } else {
+        resc = __any_sync(0xffffffffu, mt > m_ref + kFmLazyLog2) != 0;
+        if (resc) {
+          const float mn = fmaxf(m_ref, mt);
+          alpha = (m_ref == -INFINITY) ? 0.f : fm_exp2(m_ref - mn);
+          m_ref = mn;
+        }
+      }
+      const float mr = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float sum = 0.f;
+      // probabilities, rounded to bf16 and packed in place: v[cc][0..15] hold the 32 keys of chunk cc
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fm_exp2(__uint_as_float(v[cc][i]) - mr), p1 = fm_exp2(__uint_as_float(v[cc][i + 1]) - mr);
+          sum += p0 + p1;
+          v[cc][i >> 1] = fm_pack(p0, p1);
+        }
+      // the P buffer and the O accumulator belong to P V of the previous tile until it has completed
+      if (j > 0) {
+        if (!mbar_wait(&sh->o_done, (uint32_t)(j - 1) & 1u, abort_flag)) {
+          fail(37);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (resc) {
+#pragma unroll 1
+          for (int c8 = 0; c8 < D / 32; ++c8) {
+            uint32_t o[32];
+            tmem_ld32(tmem_base + lane_addr + (uint32_t)(c8 * 32), o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tmem_base + lane_addr + (uint32_t)(c8 * 32), o);
+          }
+          tmem_st_wait();
+        }
+      }
+      l = l * alpha + sum;
+      // P as the A operand of the next MMA: two [128 rows x 64 keys] K-major tiles, 16-byte chunk index XOR (row % 8)
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        unsigned char* dst = Ps + (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) * 16);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(v[ch >> 2][(ch & 3) * 4], v[ch >> 2][(ch & 3) * 4 + 1], v[ch >> 2][(ch & 3) * 4 + 2],
+                                                    v[ch >> 2][(ch & 3) * 4 + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->p_full);
+    }
+    // ---- epilogue: O / l -> global
+    if (ok) ok = mbar_wait(&sh->o_done, (uint32_t)(nt - 1) & 1u, abort_flag);
+    if (!ok) {
+      fail(38);
+    } else {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool store = q0 + row < p.t;
+      bf16* dst = reinterpret_cast<bf16*>(p.out) + (long long)(q0 + row) * p.o_tok_stride + (long long)h * p.o_head_stride;
+#pragma unroll 1
+      for (int c8 = 0; c8 < D / 32; ++c8) {
+        uint32_t o[32];
+        tmem_ld32(tmem_base + lane_addr + (uint32_t)(c8 * 32), o);
+        tmem_ld_wait();
+        if (store) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = fm_pack(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            w.y = fm_pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            w.z = fm_pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            w.w = fm_pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c8 * 32 + i) = w;
+          }
+        }
+      }
+    }
+  }
+  // ---- teardown: if something timed out give in-flight bulk copies time to land, then free TMEM
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// bf16 tensor map with 128-byte swizzle; dims / strides innermost first (strides in elements, for dims 1 and 2).
+static int fm_tmap(CUtensorMap* map, const void* base, long long d0, long long d1, long long d2, long long s1, long long s2, int b0, int b1,
+                   int b2) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (s1 * 2) % 16 != 0 || (s2 * 2) % 16 != 0) return (int)cudaErrorInvalidValue;
+  cuuint64_t dims[3] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)d2};
+  cuuint64_t strides[2] = {(cuuint64_t)s1 * 2, (cuuint64_t)s2 * 2};
+  cuuint32_t box[3] = {(cuuint32_t)b0, (cuuint32_t)b1, (cuuint32_t)b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int D>
+static int launch_fmha(const MmbFmhaPrefillParams& p, cudaStream_t stream) {
+  CUtensorMap mq, mk, mv;
+  // q / k as (d, head, token): the head stride is the smaller one in [token, head, d] tensors
+  int e = fm_tmap(&mq, p.q, D, p.Hq, p.t, p.q_head_stride, p.q_tok_stride, 64, 1, 128);
+  if (e) return e;
+  e = fm_tmap(&mk, p.k, D, p.Hk, p.n, p.k_head_stride, p.k_tok_stride, 64, 1, 128);
+  if (e) return e;
+  e = fm_tmap(&mv, p.vt, p.n_pad, D, p.Hk, p.n_pad, (long long)D * p.n_pad, 64, D, 1);
+  if (e) return e;
+  auto kern = fmha_prefill_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FmhaCfg<D>::smem_bytes);
+    if (ce != cudaSuccess) return (int)ce;
+    configured = true;
+  }
+  dim3 grid((p.t + 127) / 128, p.Hq, 1);
+  kern<<<grid, kFmThreads, FmhaCfg<D>::smem_bytes, stream>>>(mq, mk, mv, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace mmb
+
+MMB_API int mmb_fmha_prefill(const MmbFmhaPrefillParams* pp, cudaStream_t stream) {
+  const MmbFmhaPrefillParams& p = *pp;
+  if (p.t <= 0) return 0;
+  if (p.n < p.t || p.n_pad < p.n || p.n_pad % 8 != 0 || p.Hk < 1 || p.Hq % p.Hk != 0 || (p.D != 128 && p.D != 256)) return (int)cudaErrorInvalidValue;
+  if (p.q_tok_stride % 8 || p.q_head_stride % 8 || p.k_tok_stride % 8 || p.k_head_stride % 8 || p.o_tok_stride % 8 || p.o_head_stride % 8 ||
+      (reinterpret_cast<uintptr_t>(p.out) & 15))
+    return (int)cudaErrorInvalidValue;
+  // the tensor maps need strides that grow with the dimension: head stride <= token stride
+  if (p.q_head_stride > p.q_tok_stride || p.k_head_stride > p.k_tok_stride) return (int)cudaErrorInvalidValue;
+  return p.D == 128 ? mmb::launch_fmha<128>(p, stream) : mmb::launch_fmha<256>(p, stream);
+}

@@ -1047,7 +1047,43 @@ void moe_combine(const Tensor& y, const Tensor& inv, const OptT& add0, const Opt
         "moe_combine");
 }
 
+// Causal prefill attention of one sequence on the tcgen05 path.  q [t, Hq, D], k [n, Hk, D] (last dim contiguous),
+// vt [Hk, D, n_pad] contiguous, out [t, Hq, D]; status: device int tensor (first word receives a code after a timeout).
+void fmha_prefill(const Tensor& q, const Tensor& k, const Tensor& vt, Tensor out, int64_t n, double scale, Tensor status) {
+  check_bf16(q, "q");
+  check_bf16(k, "k");
+  check_bf16(vt, "vt");
+  check_bf16(out, "out");
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && vt.dim() == 3 && out.dim() == 3 && q.stride(2) == 1 && k.stride(2) == 1 && out.stride(2) == 1 &&
+              vt.is_contiguous());
+  TORCH_CHECK(k.size(2) == q.size(2) && vt.size(1) == q.size(2) && vt.size(0) == k.size(1) && out.size(0) == q.size(0) &&
+              out.size(1) == q.size(1) && out.size(2) == q.size(2) && k.size(0) >= n && vt.size(2) >= n);
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(q.device());
+  MmbFmhaPrefillParams p{};
+  p.q = q.data_ptr();
+  p.k = k.data_ptr();
+  p.vt = vt.data_ptr();
+  p.out = out.data_ptr();
+  p.t = (int)q.size(0);
+  p.n = (int)n;
+  p.n_pad = (int)vt.size(2);
+  p.Hq = (int)q.size(1);
+  p.Hk = (int)k.size(1);
+  p.D = (int)q.size(2);
+  p.q_tok_stride = q.stride(0);
+  p.q_head_stride = q.stride(1);
+  p.k_tok_stride = k.stride(0);
+  p.k_head_stride = k.stride(1);
+  p.o_tok_stride = out.stride(0);
+  p.o_head_stride = out.stride(1);
+  p.scale = (float)scale;
+  p.status = status.data_ptr<int>();
+  check(mmb_fmha_prefill(&p, cur_stream()), "fmha_prefill");
+}
+
 TORCH_LIBRARY(mmb200, m) {
+  m.def("fmha_prefill", &fmha_prefill);
   m.def("fp4_gemm_grouped", &fp4_gemm_grouped);
   m.def("bf16_gemm", &bf16_gemm);
   m.def("fp4_gemv", &fp4_gemv);

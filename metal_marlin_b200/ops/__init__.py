@@ -779,6 +779,25 @@ def spec_verify(p_target, p_draft, draft, u, u_resample):
 PREFILL_ATTN_DIMS = (64, 128, 256)
 
 
+FMHA_TCGEN05 = os.environ.get("MMB200_FMHA", "1") != "0"      # single-sequence causal prompts take the tcgen05 attention kernel
+FMHA_MIN_T = 256
+
+
+def fmha_prefill(q, k, v, out, scale):
+    """Causal attention of ONE sequence on the tcgen05 kernel (``csrc/attention_fmha_sm100.cu``): ``q [t, Hq, D]`` are the last
+    ``t`` positions of the keys ``k, v [n, Hk, D]``; ``D`` 128 or 256.  The kernel takes V transposed per head (the B operand
+    of its P V MMA is K-major like every other operand), built here with one strided copy."""
+    assert native_available(), "the tcgen05 attention kernel needs the CUDA extension"
+    n, Hk, D = k.shape
+    n_pad = (n + 7) // 8 * 8
+    vt = torch.empty(Hk, D, n_pad, dtype=torch.bfloat16, device=q.device)
+    vt[:, :, :n].copy_(v.permute(1, 2, 0))
+    if n_pad > n:
+        vt[:, :, n:].zero_()
+    K.mmb200.fmha_prefill(q, k, vt, out, n, float(scale), gemm_status(q.device))
+    return out
+
+
 def prefill_attention(q, k, v, cu_q, *, cu_k=None, block_tables=None, ctx_lens=None, block_size=16, max_q=None, scale=None, window=0,
                       causal=True, out=None, q_lens_host=None, k_lens_host=None, sinks=0, tree_mask=None, block_mask=None):
     """Variable-length prefill attention.  ``q [T, Hq, D]``; contiguous keys ``k, v [N, Hk, D]`` with ``cu_k``, or paged
@@ -804,6 +823,11 @@ def prefill_attention(q, k, v, cu_q, *, cu_k=None, block_tables=None, ctx_lens=N
         block_tables = ctx_lens = None
     if max_q is None and (block_mask is not None or (_use_native(q) and D in PREFILL_ATTN_DIMS)):
         max_q = int((cu_q[1:] - cu_q[:-1]).max())
+    if (FMHA_TCGEN05 and _use_native(q) and not NO_TCGEN05 and D in (128, 256) and q.dtype == torch.bfloat16 and cu_k is not None
+            and cu_q.numel() == 2 and causal and not window and not sinks and tree_mask is None and block_mask is None
+            and T >= FMHA_MIN_T and k.shape[-1] == D and v.shape[-1] == D and k.shape[0] >= T and q.stride(2) == 1
+            and k.stride(2) == 1 and out.stride(2) == 1 and k.stride(1) <= k.stride(0) and q.stride(1) <= q.stride(0)):
+        return fmha_prefill(q, k, v, out, scale)
     if _use_native(q) and D in PREFILL_ATTN_DIMS and q.dtype == torch.bfloat16 and k.shape[-1] == D and v.shape[-1] == D:
         K.mmb200.prefill_attention(q, k, v, out, cu_q, cu_k, block_tables, ctx_lens, block_size, max_q, scale, window, causal,
                                    int(sinks), tree_mask, block_mask)

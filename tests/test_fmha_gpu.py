@@ -1,0 +1,55 @@
+"""Causal prefill attention on the tcgen05 kernel (``csrc/attention_fmha_sm100.cu``) against an fp32 PyTorch reference:
+full prompts, ragged lengths, chunked prompts (queries are the last positions of the keys), grouped heads, strided
+values, both head sizes, and score ranges that force the lazily deferred rescaling of the accumulator in tensor memory."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _ref(q, k, v, scale):
+    t, Hq, D = q.shape
+    n, Hk, _ = k.shape
+    g = Hq // Hk
+    qf, kf, vf = q.float(), k.float().repeat_interleave(g, 1), v.float().repeat_interleave(g, 1)
+    s = torch.einsum("thd,nhd->htn", qf, kf) * scale
+    pos = torch.arange(n - t, n, device=q.device).view(1, t, 1)
+    s = s.masked_fill(torch.arange(n, device=q.device).view(1, 1, n) > pos, float("-inf"))
+    return torch.einsum("htn,nhd->thd", torch.softmax(s, -1), vf)
+
+
+@pytest.mark.parametrize("t,n,Hq,Hk,D,boost", [(512, 512, 4, 4, 256, 1.0), (300, 300, 8, 2, 256, 1.0), (256, 1000, 4, 1, 128, 1.0),
+                                               (640, 640, 2, 2, 256, 8.0), (384, 900, 4, 2, 128, 8.0), (129, 129, 2, 2, 256, 1.0)])
+def test_fmha_prefill_matches_reference(t, n, Hq, Hk, D, boost):
+    from metal_marlin_b200 import ops
+    torch.manual_seed(t + n)
+    q = torch.randn(t, Hq, D, device=DEV).to(torch.bfloat16)
+    k = torch.randn(n, Hk, D, device=DEV).to(torch.bfloat16)
+    if boost != 1.0:          # later keys score far higher: the running maximum jumps by more than the lazy threshold
+        k[n // 2:] *= boost
+    kv = torch.randn(n, Hk, 2 * D, device=DEV).to(torch.bfloat16)
+    v = kv[..., D:]           # strided rows, as the per-head values of the MLA prompt path are
+    out = torch.empty(t, Hq, D, dtype=torch.bfloat16, device=DEV)
+    scale = D ** -0.5
+    ops.fmha_prefill(q, k, v, out, scale)
+    torch.cuda.synchronize()
+    assert ops.check_status(torch.device(DEV)) == 0
+    ref = _ref(q, k, v, scale)
+    err = float((out.float() - ref).abs().max() / ref.abs().max())
+    assert err < 2e-2, err
+
+
+def test_prefill_attention_routes_single_sequences_to_the_tensor_core_kernel():
+    from metal_marlin_b200 import ops
+    torch.manual_seed(0)
+    t, H, D = 512, 4, 256
+    q, k, v = (torch.randn(t, H, D, device=DEV).to(torch.bfloat16) for _ in range(3))
+    cu = torch.tensor([0, t], dtype=torch.int32, device=DEV)
+    before = ops.launch_count()
+    a = ops.prefill_attention(q, k, v, cu, cu_k=cu, max_q=t)
+    with ops.force_reference():
+        b = ops.prefill_attention(q, k, v, cu, cu_k=cu, max_q=t)
+    assert float((a.float() - b.float()).abs().max() / b.float().abs().max()) < 2e-2
+    assert ops.launch_count() > before
