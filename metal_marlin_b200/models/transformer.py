@@ -257,6 +257,18 @@ class Transformer:
         Hq, Hk, D = self.n_heads_local, self.n_kv_heads_local, cfg.dh
         out = torch.empty(q.shape[0], Hq * D, dtype=torch.bfloat16, device=q.device)
         bs = kv.block_size
+        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and len(meta.cu_seqlens) == 2 and not cfg.sliding_window
+                and not isinstance(kv.k[li], ops.FP8KV) and q.stride(2) == 1
+                and ops.fmha_ok(q.shape[0], int(meta.ctx_lens_host[0]), D, D, q.device)):
+            # one long sequence: its cache rows (this chunk included) gathered once, then the tcgen05 attention kernel
+            n_ctx = int(meta.ctx_lens_host[0])
+
+            def _slots(n_ctx=n_ctx):
+                tok = torch.arange(n_ctx, device=q.device)
+                return meta.block_tables[0, tok // bs].long() * bs + tok % bs
+            slots = meta.cached(("slots", 0, n_ctx), _slots)
+            ops.fmha_prefill(q, kv.k[li].view(-1, Hk, D)[slots], kv.v[li].view(-1, Hk, D)[slots], out.view(-1, Hq, D), self.scale)
+            return out
         if meta.attn_mask is None and q.dtype == torch.bfloat16:
             # one launch for all sequences: keys are read from the paged pool through the block table
             cu_q = meta.dev_ints("cu_q", meta.cu_seqlens, q.device)
@@ -345,6 +357,22 @@ class Transformer:
                 return meta.block_tables[b, tok // bs].long() * bs + tok % bs
             slots = meta.cached(("slots", b, n_ctx), _slots)
             lat = kv.k[li][slots]                                           # [n, R + dr] post-norm | post-RoPE
+            if R % 64 == 0 and ops.fmha_ok(t, n_ctx, dn + dr, dv, q.device):
+                # tensor-core attention: keys per head from one GEMM, V^T per head straight from a second GEMM with the
+                # operands swapped (W_v x c^T), so no transposition pass is needed
+                n_pad = (n_ctx + 7) // 8 * 8
+                c = torch.empty(n_pad, R, dtype=torch.bfloat16, device=q.device)
+                c[:n_ctx].copy_(lat[:, :R])
+                if n_pad > n_ctx:
+                    c[n_ctx:].zero_()
+                w_k, w_v = self._kv_b_split(L)
+                k = torch.empty(n_ctx, H, dn + dr, dtype=torch.bfloat16, device=q.device)
+                k[..., :dn].copy_(ops.bf16_gemm(c[:n_ctx], w_k).view(n_ctx, H, dn))
+                k[..., dn:].copy_(lat[:, None, R:].expand(n_ctx, H, dr))
+                vt = ops.bf16_gemm(w_v, c)                                  # [H, dv, n_pad]
+                qq = torch.cat([q[s:e, :, :dn], q_full[s:e, :, R:]], -1)
+                ops.fmha_prefill(qq, k, None, out[s:e].view(t, H, dv), self.scale, vt=vt)
+                continue
             c = lat[:, :R].contiguous()
             kvx = (ops.bf16_gemm(c, L.kv_b_dense) if R % 64 == 0 else torch.matmul(c, L.kv_b_dense.t())).view(n_ctx, H, dn + dv)
             k = torch.cat([kvx[..., :dn], lat[:, None, R:].expand(n_ctx, H, dr)], -1)
@@ -354,6 +382,20 @@ class Transformer:
             ops.prefill_attention(qq, k.contiguous(), kvx[..., dn:], cu_q, cu_k=cu_k, max_q=t, scale=self.scale,
                                   out=out[s:e].view(t, H, dv))
         return out
+
+    def _kv_b_split(self, L: LayerWeights):
+        """``kv_b`` split for the tensor-core prompt path: ``w_k [H * dn, R]`` (contiguous copy, made once per layer) and
+        ``w_v [H, dv, R]`` (a strided view of the same matrix, the batched GEMM takes it as it is)."""
+        sp = getattr(L, "_kv_b_split_cache", None)
+        if sp is not None and sp[2] != L.kv_b_dense.data_ptr():        # a (sharded) copy of the layer carries another matrix
+            sp = None
+        if sp is None:
+            cfg = self.cfg
+            H, dn, dv, R = self.n_heads_local, cfg.qk_nope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+            w = L.kv_b_dense.view(H, dn + dv, R)
+            sp = (w[:, :dn, :].reshape(H * dn, R).contiguous(), w[:, dn:, :], L.kv_b_dense.data_ptr())
+            L._kv_b_split_cache = sp
+        return sp[0], sp[1]
 
     def _prefill_attention_mla(self, L: LayerWeights, q_full, kv: PagedKVStorage, li: int, meta: BatchMeta):
         """Absorbed-form causal prefill: scores and values live in the 576/512-d latent space, all heads

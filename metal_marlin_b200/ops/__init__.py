@@ -783,17 +783,26 @@ FMHA_TCGEN05 = os.environ.get("MMB200_FMHA", "1") != "0"      # single-sequence 
 FMHA_MIN_T = 256
 
 
-def fmha_prefill(q, k, v, out, scale):
+def fmha_ok(t: int, n: int, D: int, Dv: int, device) -> bool:
+    """True when a single causal sequence of ``t`` queries over ``n`` keys takes the tcgen05 attention kernel."""
+    return bool(FMHA_TCGEN05 and not NO_TCGEN05 and D == Dv and D in (128, 256) and t >= FMHA_MIN_T and n >= t
+                and torch.device(device).type == "cuda" and native_available() and not _FORCE_REF)
+
+
+def fmha_prefill(q, k, v, out, scale, vt=None):
     """Causal attention of ONE sequence on the tcgen05 kernel (``csrc/attention_fmha_sm100.cu``): ``q [t, Hq, D]`` are the last
-    ``t`` positions of the keys ``k, v [n, Hk, D]``; ``D`` 128 or 256.  The kernel takes V transposed per head (the B operand
-    of its P V MMA is K-major like every other operand), built here with one strided copy."""
+    ``t`` positions of the keys ``k, v [n, Hk, D]``; ``D`` 128 or 256.  The kernel takes V transposed per head, ``vt [Hk, D,
+    n_pad]`` with ``n_pad % 8 == 0`` and zeros behind column ``n`` (the B operand of its P V MMA is K-major like every other
+    operand); callers that can produce it directly (a GEMM with swapped operands) pass ``vt``, else it is built here with
+    one strided copy of ``v``."""
     assert native_available(), "the tcgen05 attention kernel needs the CUDA extension"
     n, Hk, D = k.shape
-    n_pad = (n + 7) // 8 * 8
-    vt = torch.empty(Hk, D, n_pad, dtype=torch.bfloat16, device=q.device)
-    vt[:, :, :n].copy_(v.permute(1, 2, 0))
-    if n_pad > n:
-        vt[:, :, n:].zero_()
+    if vt is None:
+        n_pad = (n + 7) // 8 * 8
+        vt = torch.empty(Hk, D, n_pad, dtype=torch.bfloat16, device=q.device)
+        vt[:, :, :n].copy_(v.permute(1, 2, 0))
+        if n_pad > n:
+            vt[:, :, n:].zero_()
     K.mmb200.fmha_prefill(q, k, vt, out, n, float(scale), gemm_status(q.device))
     return out
 

@@ -53,3 +53,62 @@ def test_prefill_attention_routes_single_sequences_to_the_tensor_core_kernel():
         b = ops.prefill_attention(q, k, v, cu, cu_k=cu, max_q=t)
     assert float((a.float() - b.float()).abs().max() / b.float().abs().max()) < 2e-2
     assert ops.launch_count() > before
+
+
+def test_mla_prompt_pass_with_tensor_core_attention_matches_reference():
+    """A small MLA + MoE model with the head sizes of GLM-4.7-Flash (192 + 64 query / key, 256 value, latent 512): prompts
+    of 256 and more tokens run keys-from-GEMM, V^T-from-GEMM and the tcgen05 attention kernel; a second, chunked pass
+    attends over the cached first chunk."""
+    import dataclasses
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM, prefill
+    cfg = dataclasses.replace(get_preset("tiny-mla-moe"), hidden_size=512, num_hidden_layers=2, kv_lora_rank=512, q_lora_rank=256,
+                              qk_nope_head_dim=192, qk_rope_head_dim=64, v_head_dim=256)
+    lm = MMFP4ForCausalLM.from_config(cfg, device="cuda", seed=3)
+    prompts = [torch.randint(0, 512, (700,)).tolist(), torch.randint(0, 512, (301,)).tolist()]
+    bt = torch.arange(2 * 48, dtype=torch.int32).view(2, 48)
+    calls = {"n": 0}
+    real = ops.fmha_prefill
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+    ops.fmha_prefill = counting
+    try:
+        a = prefill(lm.model, lm.new_cache(96, 16), prompts, bt)
+    finally:
+        ops.fmha_prefill = real
+    assert calls["n"] == 2 * cfg.num_hidden_layers
+    with ops.force_reference():
+        b = prefill(lm.model, lm.new_cache(96, 16), prompts, bt)
+    assert ops.check_status(torch.device(DEV)) == 0
+    assert float((a - b).abs().max() / b.abs().max()) < 4e-2
+
+
+def test_gqa_prompt_pass_with_tensor_core_attention_matches_reference():
+    """Grouped-query model with 128-wide heads: one 600-token prompt, then a second chunk over the cached first one."""
+    import dataclasses
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM, prefill
+    cfg = dataclasses.replace(get_preset("tiny-qwen3-moe"), head_dim=128, num_attention_heads=4, num_key_value_heads=2, hidden_size=512)
+    lm = MMFP4ForCausalLM.from_config(cfg, device="cuda", seed=4)
+    prompts = [torch.randint(0, 512, (600,)).tolist()]
+    bt = torch.arange(48, dtype=torch.int32).view(1, 48)
+    calls = {"n": 0}
+    real = ops.fmha_prefill
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+    ops.fmha_prefill = counting
+    try:
+        a = prefill(lm.model, lm.new_cache(48, 16), prompts, bt)
+    finally:
+        ops.fmha_prefill = real
+    assert calls["n"] == cfg.num_hidden_layers
+    with ops.force_reference():
+        b = prefill(lm.model, lm.new_cache(48, 16), prompts, bt)
+    assert ops.check_status(torch.device(DEV)) == 0
+    assert float((a - b).abs().max() / b.abs().max()) < 4e-2
