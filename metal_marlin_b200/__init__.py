@@ -79,7 +79,7 @@ _reg(".hf", "replace_linear_layers", "find_linear_layers", "find_moe_layers", "l
 _reg(".memory", "Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "PinnedPool", "WeightStreamer", "MemoryPressureMonitor")
 _reg(".parallel.tp", "TPContext", "shard_transformer", "make_context")
 _reg(".parallel.mesh", "DeviceMesh", "MeshShape", "plan_mesh")
-_reg(".parallel.ep", "ExpertParallelMoE")
+_reg(".parallel.ep", "ExpertParallelMoE", "EPExchange")
 _reg(".parallel.pp", "PipelineStage", "pipeline_prefill")
 _reg(".parallel.cp", "ring_attention")
 _reg(".parallel.symm", "SymmetricBuffer")

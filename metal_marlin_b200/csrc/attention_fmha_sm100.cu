@@ -1,18 +1,19 @@
 // Causal prefill attention on the tcgen05 tensor cores.
 //
-// One CTA owns 128 query rows of one head and walks the keys in tiles of 128:
-//   warp 0      TMA producer: Q once, then per tile the K rows [128 keys x D] and the V^T block [D x 128 keys]
-//               (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers);
-//   warp 1      one elected thread issues the MMAs: S = Q K^T (M 128, N 128, K = D) into one of two S buffers in TMEM,
-//               O += P V (M 128, N = D, K 128) into the O accumulator in TMEM; tcgen05.commit signals the mbarriers.
+// One CTA owns 128 query rows of one head and walks the keys in tiles of KT (64 at head size 256, 128 at head size 128):
+//   warp 0      TMA producer: Q once, then per tile the K rows [KT keys x D] and the V^T block [D x KT keys] into a
+//               two-stage ring (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers);
+//   warp 1      one elected thread issues the MMAs: S = Q K^T (M 128, N KT, K = D) into one of two S buffers in TMEM,
+//               O += P V (M 128, N = D, K = KT) into the O accumulator in TMEM; tcgen05.commit signals the mbarriers.
 //               S of tile j + 1 is issued before P V of tile j, so it runs under the soft-max of tile j;
-//   warps 2-5   soft-max, one query row per thread (its TMEM lane): tcgen05.ld of the 128 scores, scale, causal mask,
-//               running maximum with LAZY rescaling (the reference maximum only moves when a row's maximum grew by more
-//               than 2^8, decided per warp; then the O rows are rescaled in TMEM with tcgen05.ld / tcgen05.st), exp2,
-//               P rounded to bf16 and stored as the K-major swizzled A operand of the P V MMA; finally O / l -> global.
-// TMEM: O in columns [0, D), S buffers at D and D + 128 (512 columns for D = 256).
-// Shared memory (D = 256): Q 64 KB, K 64 KB, V^T 64 KB, P 32 KB - single buffers; the load of K(j+1) starts when S(j) is
-// complete and the load of V(j+1) when P V(j) is complete, both under the soft-max.
+//   warps 2-9   soft-max, two threads per query row (its TMEM lane; each takes half of the tile's keys and half of the O
+//               columns, row maxima exchanged through shared memory): tcgen05.ld of the scores, scale, causal mask (diagonal
+//               tiles only), running maximum with LAZY rescaling (the reference maximum only moves when a row's maximum
+//               grew by more than 2^8, decided per warp; only then does the warp wait for the previous P V and rescale
+//               its O rows in TMEM with tcgen05.ld / tcgen05.st), exp2, P rounded to bf16 and stored as the K-major
+//               swizzled A operand of the P V MMA (two P buffers); finally O / l -> global.
+// TMEM: O in columns [0, D), S buffers at D and D + 128.
+// Shared memory: Q 64 KB + 2 x (K 32 KB + V^T 32 KB + P 16 KB) at D = 256; 32 + 2 x (32 + 32 + 32) KB at D = 128.
 // Every mbarrier wait is bounded; on expiry a code goes to the status word, the roles stop, TMEM is freed.
 #include "api_ext.h"
 #include "common.cuh"
@@ -20,24 +21,31 @@
 
 namespace mmb {
 
-constexpr int kFmThreads = 192;
+constexpr int kFmThreads = 320;         // warp 0 TMA, warp 1 MMA, warps 2-9 soft-max (two per TMEM lane quarter)
 constexpr float kFmLazyLog2 = 8.f;      // rescale O only when a row maximum grew by more than this (log2 units)
 
 struct FmhaShared {
-  uint64_t q_full, k_full, v_full, s_full[2], p_full, o_done;
+  uint64_t q_full, k_full[2], v_full[2], s_full[2], p_full[2], pv_done[2];
+  uint64_t pair_bar[4];       // the two soft-max warps of a lane quarter meet here (64 arrivals), bounded like every wait
   uint32_t tmem_base;
   int abort_flag;
+  float xmax[2][2][128];      // [tile parity][column half][row]: row maxima exchanged between the two warps of a row (the row
+                              // sums take the idle parity once at the end)
 };
 
-template <int D>
+// D: head size; KT: keys per tile (64 at D = 256, 128 at D = 128, so that K, V^T and P all fit twice).
+template <int D, int KT>
 struct FmhaCfg {
-  static constexpr int KB = D / 64;                 // 64-wide k blocks of the head dimension
+  static constexpr int KB = D / 64;                 // 64-wide k blocks of the head dimension (S = Q K^T)
+  static constexpr int NKB = KT / 64;               // 64-key k blocks of a tile (O += P V)
   static constexpr int q_bytes = KB * 16384;
-  static constexpr int k_bytes = KB * 16384;
-  static constexpr int v_half = D * 128;            // V^T rows [D] x 64 keys
-  static constexpr int v_bytes = 2 * v_half;
-  static constexpr int p_bytes = 2 * 16384;
-  static constexpr size_t smem_bytes = (size_t)q_bytes + k_bytes + v_bytes + p_bytes + 1024 + 256;
+  static constexpr int k_blk = KT * 128;            // one k block of the K tile: KT rows x 128 B
+  static constexpr int k_bytes = KB * k_blk;
+  static constexpr int v_blk = D * 128;             // one 64-key block of V^T: D rows x 128 B
+  static constexpr int v_bytes = NKB * v_blk;
+  static constexpr int p_bytes = NKB * 16384;
+  static constexpr size_t smem_bytes = (size_t)q_bytes + 2 * (k_bytes + v_bytes + p_bytes) + sizeof(FmhaShared);
+  static_assert(smem_bytes <= 232448, "shared memory of one CTA");
 };
 
 // kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
@@ -54,32 +62,38 @@ __device__ __forceinline__ uint32_t fm_pack(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int D>
+template <int D, int KT>
 __global__ void __launch_bounds__(kFmThreads, 1)
 fmha_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const MmbFmhaPrefillParams p) {
-  using Cfg = FmhaCfg<D>;
-  extern __shared__ unsigned char smem_fm[];
-  unsigned char* Qs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_fm) + 1023) & ~(uintptr_t)1023);
-  unsigned char* Ks = Qs + Cfg::q_bytes;
-  unsigned char* Vs = Ks + Cfg::k_bytes;
-  unsigned char* Ps = Vs + Cfg::v_bytes;
-  FmhaShared* sh = reinterpret_cast<FmhaShared*>(Ps + Cfg::p_bytes);
+  using Cfg = FmhaCfg<D, KT>;
+  extern __shared__ __align__(1024) unsigned char smem_fm[];      // the swizzled tiles need 1024-byte alignment
+  unsigned char* Qs = smem_fm;
+  unsigned char* Ks = Qs + Cfg::q_bytes;            // [2][k_bytes]
+  unsigned char* Vs = Ks + 2 * Cfg::k_bytes;        // [2][v_bytes]
+  unsigned char* Ps = Vs + 2 * Cfg::v_bytes;        // [2][p_bytes]
+  FmhaShared* sh = reinterpret_cast<FmhaShared*>(Ps + 2 * Cfg::p_bytes);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;       // the tiles with the most keys start first
-  const int q0 = qt * 128, h = blockIdx.y, hk = h / (p.Hq / p.Hk);
+  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;       // all heads' tiles with the most keys start first
+  const int q0 = qt * 128, h = blockIdx.x, hk = h / (p.Hq / p.Hk);
   const int q_off = p.n - p.t;
-  const int nt = (q_off + min(q0 + 127, p.t - 1)) / 128 + 1;   // key tiles this query tile can see
+  const int nt = (q_off + min(q0 + 127, p.t - 1)) / KT + 1;    // key tiles this query tile can see
   int* status = p.status;
+  if ((smem_u32(smem_fm) & 1023u) != 0u) {      // no room for alignment slack: refuse rather than mis-address the tiles
+    if (tid == 0 && status) atomicExch(status, 42);
+    return;
+  }
 
   if (tid == 0) {
     mbar_init(&sh->q_full, 1);
-    mbar_init(&sh->k_full, 1);
-    mbar_init(&sh->v_full, 1);
-    mbar_init(&sh->s_full[0], 1);
-    mbar_init(&sh->s_full[1], 1);
-    mbar_init(&sh->p_full, 4);
-    mbar_init(&sh->o_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh->k_full[i], 1);
+      mbar_init(&sh->v_full[i], 1);
+      mbar_init(&sh->s_full[i], 1);
+      mbar_init(&sh->p_full[i], 8);
+      mbar_init(&sh->pv_done[i], 1);
+    }
+    for (int i = 0; i < 4; ++i) mbar_init(&sh->pair_bar[i], 64);
     sh->abort_flag = 0;
     fence_proxy_async_smem();
     fence_barrier_init();
@@ -96,6 +110,8 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   auto fail = [&](int code) {
     if (atomicExch(&sh->abort_flag, 1) == 0 && status) atomicExch(status, code);
   };
+  // tile j uses stage / buffer j & 1; its barriers are in phase (j >> 1) & 1
+  auto ph = [](int j) { return (uint32_t)(j >> 1) & 1u; };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -103,98 +119,122 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_expect_tx(&sh->q_full, Cfg::q_bytes);
       for (int kb = 0; kb < Cfg::KB; ++kb) tma_load_3d(Qs + kb * 16384, &tm_q, &sh->q_full, kb * 64, h, q0);
       for (int j = 0; j < nt; ++j) {
-        if (j > 0 && !mbar_wait(&sh->s_full[(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1u, abort_flag)) {   // K buffer read by S(j-1)
+        const int s = j & 1;
+        if (j >= 2 && !mbar_wait(&sh->s_full[s], ph(j - 2), abort_flag)) {      // K stage read by S(j-2)
           fail(31);
           break;
         }
-        mbar_expect_tx(&sh->k_full, Cfg::k_bytes);
-        for (int kb = 0; kb < Cfg::KB; ++kb) tma_load_3d(Ks + kb * 16384, &tm_k, &sh->k_full, kb * 64, hk, j * 128);
-        if (j > 0 && !mbar_wait(&sh->o_done, (uint32_t)(j - 1) & 1u, abort_flag)) {                         // V buffer read by PV(j-1)
+        mbar_expect_tx(&sh->k_full[s], Cfg::k_bytes);
+        for (int kb = 0; kb < Cfg::KB; ++kb)
+          tma_load_3d(Ks + s * Cfg::k_bytes + kb * Cfg::k_blk, &tm_k, &sh->k_full[s], kb * 64, hk, j * KT);
+        if (j >= 2 && !mbar_wait(&sh->pv_done[s], ph(j - 2), abort_flag)) {     // V stage read by PV(j-2)
           fail(32);
           break;
         }
-        mbar_expect_tx(&sh->v_full, Cfg::v_bytes);
-        for (int kb = 0; kb < 2; ++kb) tma_load_3d(Vs + kb * Cfg::v_half, &tm_v, &sh->v_full, j * 128 + kb * 64, 0, hk);
+        mbar_expect_tx(&sh->v_full[s], Cfg::v_bytes);
+        for (int kb = 0; kb < Cfg::NKB; ++kb)
+          tma_load_3d(Vs + s * Cfg::v_bytes + kb * Cfg::v_blk, &tm_v, &sh->v_full[s], j * KT + kb * 64, 0, hk);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t id_s = fm_idesc(128), id_o = fm_idesc(D);
+      constexpr uint32_t id_s = fm_idesc(KT), id_o = fm_idesc(D);
       bool ok = mbar_wait(&sh->q_full, 0u, abort_flag);
       if (!ok) fail(33);
       auto issue_s = [&](int j) -> bool {
-        if (!mbar_wait(&sh->k_full, (uint32_t)j & 1u, abort_flag)) {
+        const int s = j & 1;
+        if (!mbar_wait(&sh->k_full[s], ph(j), abort_flag)) {
           fail(34);
           return false;
         }
         tc_fence_after();
-        const uint32_t ts = tmem_base + (uint32_t)(D + (j & 1) * 128);
+        const uint32_t ts = tmem_base + (uint32_t)(D + s * 128);
 #pragma unroll
         for (int kb = 0; kb < Cfg::KB; ++kb) {
-          const uint64_t ad = make_sw128_desc(Qs + kb * 16384), bd = make_sw128_desc(Ks + kb * 16384);
+          const uint64_t ad = make_sw128_desc(Qs + kb * 16384), bd = make_sw128_desc(Ks + s * Cfg::k_bytes + kb * Cfg::k_blk);
 #pragma unroll
           for (int k = 0; k < 4; ++k) umma_bf16(ts, ad + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), id_s, (uint32_t)((kb | k) != 0));
         }
-        umma_commit(&sh->s_full[j & 1]);
+        umma_commit(&sh->s_full[s]);
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < nt && ok; ++j) {
+        const int s = j & 1;
         if (j + 1 < nt) ok = issue_s(j + 1);       // runs under the soft-max of tile j
         if (!ok) break;
-        if (!mbar_wait(&sh->p_full, (uint32_t)j & 1u, abort_flag) || !mbar_wait(&sh->v_full, (uint32_t)j & 1u, abort_flag)) {
+        if (!mbar_wait(&sh->p_full[s], ph(j), abort_flag) || !mbar_wait(&sh->v_full[s], ph(j), abort_flag)) {
           fail(35);
           ok = false;
           break;
         }
         tc_fence_after();
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb) {
-          const uint64_t ad = make_sw128_desc(Ps + kb * 16384), bd = make_sw128_desc(Vs + kb * Cfg::v_half);
+        for (int kb = 0; kb < Cfg::NKB; ++kb) {
+          const uint64_t ad = make_sw128_desc(Ps + s * Cfg::p_bytes + kb * 16384), bd = make_sw128_desc(Vs + s * Cfg::v_bytes + kb * Cfg::v_blk);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_bf16(tmem_base, ad + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), id_o, (uint32_t)((j | kb | k) != 0));
         }
-        umma_commit(&sh->o_done);
+        umma_commit(&sh->pv_done[s]);
       }
     }
   } else {
-    // ------------------------------------------------------------------ soft-max: one query row per thread
+    // ------------------------------------------------------------------ soft-max: two threads (of two warps) per query row
+    constexpr int HC = KT / 2;                        // score columns per thread
+    constexpr int NC = HC / 32;                       // 32-column chunks per thread
     const int quarter = warp & 3;                     // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;                 // which half of the columns (and of the O columns) this warp owns
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float c = p.scale * 1.4426950408889634f;
     const int my_pos = q_off + q0 + row;
+    uint32_t pair_phase = 0;
+    auto pair_sync = [&]() -> bool {                  // rendezvous of the two warps that share these rows
+      mbar_arrive(&sh->pair_bar[quarter]);
+      const bool r = mbar_wait(&sh->pair_bar[quarter], pair_phase, abort_flag);
+      pair_phase ^= 1u;
+      return r;
+    };
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nt; ++j) {
-      if (!mbar_wait(&sh->s_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) {
+      const int s = j & 1;
+      if (!mbar_wait(&sh->s_full[s], ph(j), abort_flag)) {
         fail(36);
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t ts = tmem_base + lane_addr + (uint32_t)(D + (j & 1) * 128);
-      uint32_t v[4][32];
+      const uint32_t ts = tmem_base + lane_addr + (uint32_t)(D + s * 128 + half * HC);
+      uint32_t v[NC][32];
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) tmem_ld32(ts + (uint32_t)(cc * 32), v[cc]);
+      for (int cc = 0; cc < NC; ++cc) tmem_ld32(ts + (uint32_t)(cc * 32), v[cc]);
       tmem_ld_wait();
-      const int key0 = j * 128;
-      const bool need_mask = (key0 + 127 > q_off + q0) || (key0 + 128 > p.n);
+      const int key0 = j * KT;
+      const bool need_mask = (key0 + KT - 1 > q_off + q0) || (key0 + KT > p.n);
       float mt = -INFINITY;
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc)
+      for (int cc = 0; cc < NC; ++cc)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float x = __uint_as_float(v[cc][i]) * c;
           if (need_mask) {
-            const int key = key0 + cc * 32 + i;
+            const int key = key0 + half * HC + cc * 32 + i;
             if (key > my_pos || key >= p.n) x = -INFINITY;
           }
           v[cc][i] = __float_as_uint(x);
           mt = fmaxf(mt, x);
         }
+      // the row maximum over both halves: both threads of a row reach the same decisions below
+      sh->xmax[s][half][row] = mt;
+      if (!pair_sync()) {
+        fail(40);
+        ok = false;
+        break;
+      }
+      mt = fmaxf(mt, sh->xmax[s][half ^ 1][row]);
       float alpha = 1.f;
       bool resc = false;
       if (j == 0) {
@@ -211,60 +251,71 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       float sum = 0.f;
       // probabilities, rounded to bf16 and packed in place: v[cc][0..15] hold the 32 keys of chunk cc
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc)
+      for (int cc = 0; cc < NC; ++cc)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float p0 = fm_exp2(__uint_as_float(v[cc][i]) - mr), p1 = fm_exp2(__uint_as_float(v[cc][i + 1]) - mr);
           sum += p0 + p1;
           v[cc][i >> 1] = fm_pack(p0, p1);
         }
-      // the P buffer and the O accumulator belong to P V of the previous tile until it has completed
-      if (j > 0) {
-        if (!mbar_wait(&sh->o_done, (uint32_t)(j - 1) & 1u, abort_flag)) {
-          fail(37);
+      // P buffer s was the A operand of PV(j-2)
+      if (j >= 2 && !mbar_wait(&sh->pv_done[s], ph(j - 2), abort_flag)) {
+        fail(37);
+        ok = false;
+        break;
+      }
+      if (resc) {
+        // the O accumulator may only be touched between PV(j-1) and PV(j); this warp rescales its half of the columns
+        if (!mbar_wait(&sh->pv_done[(j - 1) & 1], ph(j - 1), abort_flag)) {
+          fail(39);
           ok = false;
           break;
         }
         tc_fence_after();
-        if (resc) {
 #pragma unroll 1
-          for (int c8 = 0; c8 < D / 32; ++c8) {
-            uint32_t o[32];
-            tmem_ld32(tmem_base + lane_addr + (uint32_t)(c8 * 32), o);
-            tmem_ld_wait();
+        for (int c8 = 0; c8 < D / 64; ++c8) {
+          uint32_t o[32];
+          const uint32_t ta = tmem_base + lane_addr + (uint32_t)(half * (D / 2) + c8 * 32);
+          tmem_ld32(ta, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tmem_base + lane_addr + (uint32_t)(c8 * 32), o);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(ta, o);
         }
+        tmem_st_wait();
       }
       l = l * alpha + sum;
-      // P as the A operand of the next MMA: two [128 rows x 64 keys] K-major tiles, 16-byte chunk index XOR (row % 8)
+      // P as the A operand of the next MMA: [128 rows x 64 keys] K-major tiles, 16-byte chunk index XOR (row % 8)
+      unsigned char* pb = Ps + s * Cfg::p_bytes;
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        unsigned char* dst = Ps + (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) * 16);
-        *reinterpret_cast<uint4*>(dst) = make_uint4(v[ch >> 2][(ch & 3) * 4], v[ch >> 2][(ch & 3) * 4 + 1], v[ch >> 2][(ch & 3) * 4 + 2],
-                                                    v[ch >> 2][(ch & 3) * 4 + 3]);
+      for (int cch = 0; cch < HC / 8; ++cch) {
+        const int ch = half * (HC / 8) + cch;
+        unsigned char* dst = pb + (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) * 16);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(v[cch >> 2][(cch & 3) * 4], v[cch >> 2][(cch & 3) * 4 + 1], v[cch >> 2][(cch & 3) * 4 + 2],
+                                                    v[cch >> 2][(cch & 3) * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->p_full);
+      if (lane == 0) mbar_arrive(&sh->p_full[s]);
     }
-    // ---- epilogue: O / l -> global
-    if (ok) ok = mbar_wait(&sh->o_done, (uint32_t)(nt - 1) & 1u, abort_flag);
+    // ---- epilogue: O / l -> global, each warp its half of the columns
+    if (ok) ok = mbar_wait(&sh->pv_done[(nt - 1) & 1], ph(nt - 1), abort_flag);
     if (!ok) {
       fail(38);
     } else {
       tc_fence_after();
+      float (*xl)[128] = sh->xmax[nt & 1];           // the parity the last tile did not use
+      xl[half][row] = l;
+      if (!pair_sync()) fail(41);
+      l += xl[half ^ 1][row];
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const bool store = q0 + row < p.t;
-      bf16* dst = reinterpret_cast<bf16*>(p.out) + (long long)(q0 + row) * p.o_tok_stride + (long long)h * p.o_head_stride;
+      bf16* dst = reinterpret_cast<bf16*>(p.out) + (long long)(q0 + row) * p.o_tok_stride + (long long)h * p.o_head_stride + half * (D / 2);
 #pragma unroll 1
-      for (int c8 = 0; c8 < D / 32; ++c8) {
+      for (int c8 = 0; c8 < D / 64; ++c8) {
         uint32_t o[32];
-        tmem_ld32(tmem_base + lane_addr + (uint32_t)(c8 * 32), o);
+        tmem_ld32(tmem_base + lane_addr + (uint32_t)(half * (D / 2) + c8 * 32), o);
         tmem_ld_wait();
         if (store) {
 #pragma unroll
@@ -308,25 +359,25 @@ static int fm_tmap(CUtensorMap* map, const void* base, long long d0, long long d
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int D>
+template <int D, int KT>
 static int launch_fmha(const MmbFmhaPrefillParams& p, cudaStream_t stream) {
   CUtensorMap mq, mk, mv;
   // q / k as (d, head, token): the head stride is the smaller one in [token, head, d] tensors
   int e = fm_tmap(&mq, p.q, D, p.Hq, p.t, p.q_head_stride, p.q_tok_stride, 64, 1, 128);
   if (e) return e;
-  e = fm_tmap(&mk, p.k, D, p.Hk, p.n, p.k_head_stride, p.k_tok_stride, 64, 1, 128);
+  e = fm_tmap(&mk, p.k, D, p.Hk, p.n, p.k_head_stride, p.k_tok_stride, 64, 1, KT);
   if (e) return e;
   e = fm_tmap(&mv, p.vt, p.n_pad, D, p.Hk, p.n_pad, (long long)D * p.n_pad, 64, D, 1);
   if (e) return e;
-  auto kern = fmha_prefill_kernel<D>;
+  auto kern = fmha_prefill_kernel<D, KT>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FmhaCfg<D>::smem_bytes);
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FmhaCfg<D, KT>::smem_bytes);
     if (ce != cudaSuccess) return (int)ce;
     configured = true;
   }
-  dim3 grid((p.t + 127) / 128, p.Hq, 1);
-  kern<<<grid, kFmThreads, FmhaCfg<D>::smem_bytes, stream>>>(mq, mk, mv, p);
+  dim3 grid(p.Hq, (p.t + 127) / 128, 1);
+  kern<<<grid, kFmThreads, FmhaCfg<D, KT>::smem_bytes, stream>>>(mq, mk, mv, p);
   return (int)cudaGetLastError();
 }
 
@@ -341,5 +392,5 @@ MMB_API int mmb_fmha_prefill(const MmbFmhaPrefillParams* pp, cudaStream_t stream
     return (int)cudaErrorInvalidValue;
   // the tensor maps need strides that grow with the dimension: head stride <= token stride
   if (p.q_head_stride > p.q_tok_stride || p.k_head_stride > p.k_tok_stride) return (int)cudaErrorInvalidValue;
-  return p.D == 128 ? mmb::launch_fmha<128>(p, stream) : mmb::launch_fmha<256>(p, stream);
+  return p.D == 128 ? mmb::launch_fmha<128, 128>(p, stream) : mmb::launch_fmha<256, 64>(p, stream);
 }
