@@ -33,7 +33,7 @@ def main():
     lm = MMFP4ForCausalLM.from_config(cfg, device="cuda", seed=0)
     spans = []
     names = ["linear", "bf16_linear", "moe_forward", "moe_router", "rmsnorm", "mla_prep", "rope", "qk_norm_rope_cache", "embedding",
-             "bf16_gemm", "silu_mul", "prefill_attention"]
+             "bf16_gemm", "silu_mul", "prefill_attention", "fmha_prefill"]
     originals = {n: getattr(ops, n) for n in names}
 
     def wrap(name, fn):
