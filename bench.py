@@ -134,7 +134,10 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a rank that fails alone (an exception the others do not see) must not leave the others waiting in a collective for
+        # the library's ten-minute default: collectives give up after three minutes and the error is reported in the line
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     from metal_marlin_b200 import ops
     from metal_marlin_b200.engine.session import DecodeSession, SamplingParams
@@ -304,8 +307,12 @@ def main():
         except Exception as e:
             out["tp"] = {"error": repr(e)[:300]}
     if rank == 0:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
+        if isinstance(out.get("tp"), dict) and "error" in out["tp"]:
+            # the ranks may have left the tensor-parallel section at different points: no further collective, no group teardown
+            sys.stdout.flush()
+            os._exit(0)
         dist.destroy_process_group()
     return 0
 

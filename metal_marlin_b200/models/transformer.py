@@ -387,13 +387,14 @@ class Transformer:
         """``kv_b`` split for the tensor-core prompt path: ``w_k [H * dn, R]`` (contiguous copy, made once per layer) and
         ``w_v [H, dv, R]`` (a strided view of the same matrix, the batched GEMM takes it as it is)."""
         sp = getattr(L, "_kv_b_split_cache", None)
-        if sp is not None and sp[2] != L.kv_b_dense.data_ptr():        # a (sharded) copy of the layer carries another matrix
+        key = (L.kv_b_dense.data_ptr(), tuple(L.kv_b_dense.shape), self.n_heads_local)
+        if sp is not None and sp[2] != key:        # a (sharded) copy of the layer carries another matrix (maybe at the same address)
             sp = None
         if sp is None:
             cfg = self.cfg
             H, dn, dv, R = self.n_heads_local, cfg.qk_nope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
             w = L.kv_b_dense.view(H, dn + dv, R)
-            sp = (w[:, :dn, :].reshape(H * dn, R).contiguous(), w[:, dn:, :], L.kv_b_dense.data_ptr())
+            sp = (w[:, :dn, :].reshape(H * dn, R).contiguous(), w[:, dn:, :], key)
             L._kv_b_split_cache = sp
         return sp[0], sp[1]
 

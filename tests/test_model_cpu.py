@@ -74,3 +74,25 @@ def test_eager_bf16_baseline_tracks_the_model():
     sess.set_state(lg_eager.argmax(-1), [25], bt)
     toks = [int(sess.step()[0]) for _ in range(3)]
     assert all(0 <= t < lm.config.vocab_size for t in toks)
+
+
+def test_kv_b_split_cache_follows_a_sharded_copy_of_the_layer():
+    """The prompt path caches the key / value halves of ``kv_b`` on the layer object; a shallow copy of the layer whose
+    matrix was sliced for tensor parallelism (rank 0's slice starts at the same address) must get its own split."""
+    import copy
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM
+    lm = MMFP4ForCausalLM.from_config("tiny-mla-moe", device="cpu", seed=1)
+    m, cfg = lm.model, lm.config
+    L = m.layers[0]
+    H, dn, dv, R = m.n_heads_local, cfg.qk_nope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+    w_k, w_v = m._kv_b_split(L)
+    assert w_k.shape == (H * dn, R) and w_v.shape == (H, dv, R)
+    S = copy.copy(L)
+    S.kv_b_dense = L.kv_b_dense[: (H // 2) * (dn + dv)].contiguous()
+    assert S.kv_b_dense.data_ptr() == L.kv_b_dense.data_ptr()
+    m2 = copy.copy(m)
+    m2.n_heads_local = H // 2
+    w_k2, w_v2 = m2._kv_b_split(S)
+    assert w_k2.shape == ((H // 2) * dn, R) and w_v2.shape == (H // 2, dv, R)
+    full = L.kv_b_dense.view(H, dn + dv, R)
+    assert torch.equal(w_k2, full[: H // 2, :dn].reshape(-1, R)) and torch.equal(w_v2, full[: H // 2, dn:])
