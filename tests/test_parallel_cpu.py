@@ -113,3 +113,26 @@ def test_ep_pp_cp_on_two_cpu_ranks():
         assert res["ep_fused_cpu"] < 3e-2, res
         assert res["cp"] < 1e-4, res
     assert results[world - 1]["pp"] < 1e-2, results
+
+
+def test_ep_exchange_layout_and_descriptors():
+    """Buffer layout of the expert-parallel exchange: regions do not overlap, every rank's tables point into the peers'
+    buffers at the same offsets, descriptors have the lengths the kernels expect."""
+    from metal_marlin_b200.parallel.ep import EPExchange
+    ep, H, T, k = 4, 64, 6, 2
+    lay = EPExchange.layout(ep, T * k, H)
+    assert EPExchange.OFF_META <= lay["meta"] < lay["recv_x"] < lay["ret_y"] < lay["bytes"]
+    assert lay["recv_x"] - lay["meta"] >= ep * T * k * 8 and lay["ret_y"] - lay["recv_x"] >= ep * T * k * H * 2
+    assert lay["recv_x"] % 256 == 0 and lay["ret_y"] % 256 == 0
+    exs = EPExchange.emulated(ep, H, T, k, "cpu")
+    for r, ex in enumerate(exs):
+        assert ex.rank == r and ex.cap == T * k and ex.recv_x.shape == (ep * T * k, H) and ex.ret_y.shape == (T * k, H)
+        assert [len(d) for d in (ex.desc_dispatch, ex.desc_recv, ex.desc_signal, ex.desc_combine)] == [8, 6, 2, 4]
+        tbl = ex._tbl
+        for d in range(ep):
+            base = exs[d].local.data_ptr()
+            assert int(tbl[0, d]) == base + lay["recv_x"] and int(tbl[1, d]) == base + lay["meta"]
+            assert int(tbl[3, d]) == base + EPExchange.OFF_FLAGS + 4 * r              # dispatch flag [0][r] on rank d
+            assert int(tbl[5, d]) == base + EPExchange.OFF_FLAGS + 4 * (ep + r)       # return flag [1][r] on rank d
+        ex.begin()
+        assert int(ex.step.item()) == 1 and ex.check() == 0
