@@ -99,24 +99,83 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The reference package is Metal-only: its quantized kernels need Apple GPUs and its flagship model class
-    (metal_marlin/models/mmfp4_causal_lm.py) is absent from its own tree, so MMFP4Pipeline.from_pretrained cannot
-    construct the GLM-4.7-Flash model on this platform."""
-    ref_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
-    why = None
+    """Drive the unmodified reference package (installed under baseline/_ref) through its stock loader.
+
+    A random-init checkpoint of the GLM-4.7-Flash architecture family is written in the shared MMFP4 format and handed to
+    the reference's ``metal_marlin.model_utils.load_prequantized_mmfp4_model(path, device="cuda")``.  On a machine without
+    Apple's MPS backend that loader cannot build its quantized layers (``MetalQuantizedLinear.__init__`` calls
+    ``require_mps()``; ``replace_linear_layers`` swallows the error and leaves ``nn.Linear`` modules, so the packed tensors
+    then fail to copy), and ``MMFP4Pipeline.from_pretrained`` imports ``metal_marlin.models.mmfp4_causal_lm``, which the
+    reference tree does not contain.  The exact exception text is reported in the ``unavailable`` line.  If the loader ever
+    succeeds, the same decode steps are timed through the reference model's own forward."""
+    import tempfile
+    root = os.path.dirname(os.path.abspath(__file__))
+    ref_dir = os.path.join(root, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_dir, "metal_marlin")):
-        why = "baseline/_ref is not installed (pip install --no-deps --target baseline/_ref /root/reference)"
-    else:
-        sys.path.insert(0, ref_dir)
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "baseline/_ref is not installed (pip install --no-deps --target baseline/_ref <reference checkout>)"}))
+        return 0
+    why = []
+    model = None
+    with tempfile.TemporaryDirectory() as tmp:
         try:
-            from metal_marlin.inference.mmfp4_pipeline import MMFP4Pipeline as RefPipeline   # the reference's public API
-            # stock entry point of the headline workload; it imports metal_marlin.models.mmfp4_causal_lm first
-            RefPipeline.from_pretrained(os.environ.get("GLM47_MODEL_PATH", "models/GLM-4.7-Flash-MMFP4"))
-            why = "reference pipeline constructed unexpectedly; no CUDA kernels exist in the reference to time"
+            # checkpoint writer only (file format shared with the reference); nothing of this repo runs after this block
+            from metal_marlin_b200.models.config import get_preset
+            from metal_marlin_b200.quant.convert import save_random_checkpoint
+            preset = os.environ.get("MMB200_REF_PRESET", "tiny-mla-moe")
+            save_random_checkpoint(get_preset(preset), tmp, fmt="mmfp4", seed=args.seed)
+            for m in [m for m in sys.modules if m.startswith("metal_marlin_b200")]:
+                del sys.modules[m]
         except Exception as e:
-            why = (f"reference public API fails on this platform: {type(e).__name__}: {str(e)[:160]} "
-                   "(metal_marlin/models is absent from the reference tree; its kernels are Apple-Metal shaders)")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+            print(json.dumps({"impl": "reference", "unavailable": f"could not write the synthetic checkpoint: {e!r}"[:300]}))
+            return 0
+        sys.path.insert(0, ref_dir)
+        import io
+        import contextlib
+        import torch
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        try:
+            with contextlib.redirect_stdout(io.StringIO()):
+                from metal_marlin.inference_metal import MetalQuantizedLinear
+                MetalQuantizedLinear(in_features=256, out_features=256, bits=4, group_size=64, bias=False)
+        except Exception as e:
+            why.append(f"MetalQuantizedLinear: {type(e).__name__}: {' '.join(str(e).split())[:120]}")
+        try:
+            with contextlib.redirect_stdout(io.StringIO()):
+                from metal_marlin.model_utils import load_prequantized_mmfp4_model
+                model, _tok = load_prequantized_mmfp4_model(tmp, device=dev)
+        except Exception as e:
+            why.append(f"load_prequantized_mmfp4_model(device={dev!r}): {type(e).__name__}: {' '.join(str(e).split())[:160]}")
+        try:
+            with contextlib.redirect_stdout(io.StringIO()):
+                from metal_marlin.inference.mmfp4_pipeline import MMFP4Pipeline as RefPipeline
+                RefPipeline.from_pretrained(tmp)
+        except Exception as e:
+            why.append(f"MMFP4Pipeline.from_pretrained: {type(e).__name__}: {' '.join(str(e).split())[:120]}")
+    if model is None or why:
+        print(json.dumps({"impl": "reference", "unavailable": "reference is Apple-Metal only; stock CUDA path fails: " + " | ".join(why)}))
+        return 0
+    # the loader worked: time its own forward, one token per step, batch 1
+    model = model.to(dev).eval()
+    ids = torch.randint(0, model.config.vocab_size, (1, args.prompt_len), device=dev)
+    with torch.no_grad():
+        out = model(ids, use_cache=True)
+        past, tok = out.past_key_values, out.logits[:, -1:].argmax(-1)
+        for _ in range(max(args.warmup, 3)):
+            out = model(tok, past_key_values=past, use_cache=True)
+            past, tok = out.past_key_values, out.logits[:, -1:].argmax(-1)
+        t0 = time.perf_counter()
+        if dev == "cuda":
+            torch.cuda.synchronize()
+        for _ in range(args.steps):
+            out = model(tok, past_key_values=past, use_cache=True)
+            past, tok = out.past_key_values, out.logits[:, -1:].argmax(-1)
+        if dev == "cuda":
+            torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    print(json.dumps({"impl": "reference", "metric": "glm47_flash_mmfp4_decode_tok_s_bs1", "value": 1e3 / ms, "unit": "tok/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                      "config": {"model": os.environ.get("MMB200_REF_PRESET", "tiny-mla-moe"), "note": "reference loader succeeded"}}))
     return 0
 
 

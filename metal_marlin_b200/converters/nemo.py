@@ -6,7 +6,7 @@ under ``model_weights/``); the Megatron layout fuses q/k/v into ``linear_qkv`` (
 undoes both and renames to ``model.layers.N.self_attn.{q,k,v,o}_proj`` / ``mlp.{gate,up,down}_proj`` so every loader and
 quantizer of this package applies.
 
-Parity: reference ``metal_marlin/converters`` NeMo -> PyTorch path (SURVEY component P35).
+Parity: reference ``metal_marlin/converters`` NeMo -> PyTorch path.
 """
 from __future__ import annotations
 

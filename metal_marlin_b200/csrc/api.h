@@ -189,6 +189,7 @@ typedef struct {
   int B, V, hist_len;
   unsigned long long seed, offset;
   const int64_t* offset_dev; // optional device scalar added to offset (lets a captured graph advance the RNG)
+  const int64_t* seed_dev;   // optional per-row seeds [B] on the device (replace `seed`)
 } MmbSampleParams;
 int mmb_sample(const MmbSampleParams* p, cudaStream_t stream);
 int mmb_argmax(const float* logits, int64_t* out, int B, int V, cudaStream_t stream);

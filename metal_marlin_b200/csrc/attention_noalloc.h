@@ -16,6 +16,11 @@
 // that device current) and should therefore come before any stream capture.  The scratch is one array per
 // device: two calls that overlap in time on the same device (different streams or threads) race on it; calls on
 // one stream are ordered and safe.
+//
+// The kernels are launched with the programmatic-dependent-launch attribute and request K tiles before they wait
+// for the preceding kernel of the stream.  Every cached KV row other than the one at position ctx - 1 must
+// therefore be complete in memory before this call is enqueued (the usual case: older rows were written by
+// earlier steps); a caller whose preceding kernel still writes older rows sets MMB200_PDL=0 in the environment.
 #pragma once
 #include <cuda_runtime.h>
 

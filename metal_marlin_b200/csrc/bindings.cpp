@@ -347,6 +347,19 @@ void mla_prep_impl(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, cons
   check(mmb_mla_prep(&p, cur_stream()), "mla_prep");
 }
 
+// Per-device status word for kernels whose op signature carries none (registered once per device from Python).
+int* g_status_word[64] = {nullptr};
+void set_status_word(Tensor status) {
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  const int d = status.device().index();
+  TORCH_CHECK(d >= 0 && d < 64);
+  g_status_word[d] = status.data_ptr<int>();
+}
+inline int* status_word_of(const Tensor& t) {
+  const int d = t.device().index();
+  return (d >= 0 && d < 64) ? g_status_word[d] : nullptr;
+}
+
 void paged_decode_impl(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& block_tables, const Tensor& ctx_lens,
                        Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk, int64_t dv, int64_t block_size, int64_t splits,
                        double scale, int64_t window, const Tensor* k_scale, const OptT* v_scale);
@@ -399,6 +412,7 @@ void paged_decode_impl(const Tensor& q, const Tensor& k_pool, const OptT& v_pool
     if (v_scale != nullptr && v_scale->has_value() && (*v_scale)->defined()) p.v_scale = (*v_scale)->data_ptr<float>();
   }
   TORCH_CHECK(part_o.numel() >= (int64_t)p.B * Hq * splits * dv && part_ml.numel() >= (int64_t)p.B * Hq * splits * 2);
+  p.status = status_word_of(q);
   check(mmb_paged_decode(&p, cur_stream()), "paged_decode");
 }
 
@@ -467,7 +481,7 @@ void moe_select(const Tensor& logits, const OptT& bias, Tensor ids, Tensor weigh
 
 void sample(const Tensor& logits, Tensor out_ids, const OptT& out_logprob, const OptT& temperature, const OptT& top_k,
             const OptT& top_p, const OptT& min_p, const OptT& history, const OptT& rep_penalty, int64_t seed,
-            int64_t offset, const OptT& offset_dev) {
+            int64_t offset, const OptT& offset_dev, const OptT& seed_dev) {
   TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.is_contiguous() && logits.dim() == 2);
   TORCH_CHECK(out_ids.scalar_type() == at::kLong);
   c10::cuda::CUDAGuard guard(logits.device());
@@ -493,6 +507,10 @@ void sample(const Tensor& logits, Tensor out_ids, const OptT& out_logprob, const
   if (offset_dev.has_value() && offset_dev->defined()) {
     TORCH_CHECK(offset_dev->scalar_type() == at::kLong);
     p.offset_dev = offset_dev->data_ptr<int64_t>();
+  }
+  if (seed_dev.has_value() && seed_dev->defined()) {
+    TORCH_CHECK(seed_dev->scalar_type() == at::kLong && seed_dev->numel() >= logits.size(0));
+    p.seed_dev = seed_dev->data_ptr<int64_t>();
   }
   check(mmb_sample(&p, cur_stream()), "sample");
 }
@@ -1098,6 +1116,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("qk_norm_rope_cache", &qk_norm_rope_cache);
   m.def("mla_prep", &mla_prep);
   m.def("paged_decode", &paged_decode);
+  m.def("set_status_word", &set_status_word);
   m.def("decode_merge", &decode_merge);
   m.def("moe_router", &moe_router);
   m.def("moe_select", &moe_select);

@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const MmbSamplePar
   const float min_p = p.min_p ? p.min_p[row] : 0.f;
   const float rp = p.rep_penalty ? p.rep_penalty[row] : 1.f;
   const unsigned long long rng_off = p.offset + (p.offset_dev ? (unsigned long long)(*p.offset_dev) : 0ull);
+  const unsigned long long seed = p.seed_dev ? (unsigned long long)p.seed_dev[row] : p.seed;   // per-row seeds survive graph replays
   const bool use_hist = (p.history != nullptr) && (rp != 1.f) && (p.hist_len > 0);
   if (use_hist) {
     const int words = (p.V + 31) / 32;
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const MmbSamplePar
     gm.i = 0x7fffffff;
     for (int i0 = tid * 4; i0 < p.V; i0 += kSampThreads * 4) {
       const uint4 r = philox4x32(make_uint4((uint32_t)rng_off, (uint32_t)(rng_off >> 32), (uint32_t)row, (uint32_t)(i0 >> 2)),
-                                 make_uint2((uint32_t)p.seed, (uint32_t)(p.seed >> 32)));
+                                 make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
       const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const MmbSamplePar
     float zz = 0.f;
     for (int i = 0; i < n_keep; ++i) zz += __expf(cand_v[i] - vmax);
     const uint4 r = philox4x32(make_uint4((uint32_t)rng_off, (uint32_t)(rng_off >> 32), (uint32_t)row, 0xffffffffu),
-                               make_uint2((uint32_t)p.seed, (uint32_t)(p.seed >> 32)));
+                               make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
     const float target = u01(r.x) * zz;
     float cum = 0.f;
     int pick = n_keep - 1;

@@ -23,6 +23,7 @@ from ..models.transformer import BatchMeta, PagedKVStorage, Transformer
 from .request import GenerationRequest, RequestStatus, RunningRequest, SchedulerOutput
 from .scheduler import BatchScheduler, SchedulerConfig
 from .session import SamplingParams
+from ..parallel.health import raise_for_status
 
 
 @dataclass
@@ -41,28 +42,50 @@ class EngineConfig:
     graph_buckets: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)
 
 
+HISTORY_LEN = 256      # most recent tokens (prompt tail + generated) the repetition penalty looks at
+
+
+def _packed(specs, pin: bool, device=None):
+    """One byte buffer holding several named arrays (16-byte aligned segments), so a whole decode batch crosses PCIe (or is
+    broadcast to tensor-parallel followers) as a single copy.  ``specs``: ``(name, dtype, shape)``.  Returns
+    ``(buffer, {name: view})``."""
+    off, segs = 0, []
+    for name, dt, shape in specs:
+        n = 1
+        for d in shape:
+            n *= d
+        nbytes = n * torch.empty(0, dtype=dt).element_size()
+        segs.append((name, dt, shape, off, nbytes))
+        off += (nbytes + 15) // 16 * 16
+    buf = torch.zeros(off, dtype=torch.uint8, pin_memory=pin) if device is None else torch.zeros(off, dtype=torch.uint8, device=device)
+    return buf, {name: buf[o:o + nb].view(dt).view(*shape) for name, dt, shape, o, nb in segs}
+
+
 class _DecodeBucket:
-    """Static buffers (+ optional CUDA graph) for decode batches padded to ``B`` rows."""
+    """Static buffers (+ optional CUDA graph) for decode batches padded to ``B`` rows.  All per-step inputs live in one
+    packed host buffer and one packed device buffer; the device status word of the bounded in-kernel waits comes back in
+    the same trip as the sampled ids."""
 
     def __init__(self, model: Transformer, kv: PagedKVStorage, B: int, max_blocks: int, use_graph: bool):
         dev = model.device
         self.model, self.kv, self.B, self.dev = model, kv, B, dev
         pin = dev.type == "cuda"
-        self.h_ids = torch.zeros(B, dtype=torch.int64, pin_memory=pin)
-        self.h_pos = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
-        self.h_slots = torch.full((B,), -1, dtype=torch.int64, pin_memory=pin)
-        self.h_ctx = torch.ones(B, dtype=torch.int32, pin_memory=pin)
-        self.h_bt = torch.zeros(B, max_blocks, dtype=torch.int32, pin_memory=pin)
-        self.h_f = torch.zeros(4, B, dtype=torch.float32, pin_memory=pin)      # temperature, top_p, min_p, rep_penalty
-        self.h_topk = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
+        specs = [("ids", torch.int64, (B,)), ("slots", torch.int64, (B,)), ("seeds", torch.int64, (B,)),
+                 ("pos", torch.int32, (B,)), ("ctx", torch.int32, (B,)), ("topk", torch.int32, (B,)),
+                 ("bt", torch.int32, (B, max_blocks)), ("f", torch.float32, (4, B))]     # f: temperature, top_p, min_p, rep_penalty
+        self.h_buf, h = _packed(specs, pin)
+        self.d_buf, d = _packed(specs, False, dev)
+        self.h_ids, self.h_slots, self.h_seeds, self.h_pos, self.h_ctx = h["ids"], h["slots"], h["seeds"], h["pos"], h["ctx"]
+        self.h_topk, self.h_bt, self.h_f = h["topk"], h["bt"], h["f"]
+        self.ids, self.slots, self.seeds, self.pos, self.ctx = d["ids"], d["slots"], d["seeds"], d["pos"], d["ctx"]
+        self.topk, self.bt, self.f = d["topk"], d["bt"], d["f"]
+        self.h_slots.fill_(-1)
+        self.h_ctx.fill_(1)
+        self.h_hist = torch.full((B, HISTORY_LEN), -1, dtype=torch.int64, pin_memory=pin)
+        self.hist = torch.full((B, HISTORY_LEN), -1, dtype=torch.int64, device=dev)
+        self.hist_dirty = False
         self.h_out = torch.zeros(B, dtype=torch.int64, pin_memory=pin)
-        self.ids = torch.zeros(B, dtype=torch.int64, device=dev)
-        self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
-        self.slots = torch.zeros(B, dtype=torch.int64, device=dev)
-        self.ctx = torch.ones(B, dtype=torch.int32, device=dev)
-        self.bt = torch.zeros(B, max_blocks, dtype=torch.int32, device=dev)
-        self.f = torch.zeros(4, B, dtype=torch.float32, device=dev)
-        self.topk = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.h_status = torch.zeros(4, dtype=torch.int32, pin_memory=pin)
         self.out = torch.zeros(B, dtype=torch.int64, device=dev)
         self.step_no = torch.zeros(1, dtype=torch.int64, device=dev)
         cfg = model.cfg
@@ -71,20 +94,33 @@ class _DecodeBucket:
                                          mla_latent=cfg.is_mla and cfg.latent_dim == 576 and getattr(self.kv, "kv_dtype", "bf16") == "bf16")
         self.use_graph = use_graph and dev.type == "cuda"
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.seed = 0
+        self.status = ops.gemm_status(dev)
 
     def _body(self):
         meta = BatchMeta(positions=self.pos, slots=self.slots, block_tables=self.bt, ctx_lens=self.ctx, decode=True,
                          max_ctx=self.max_ctx, splits=self.splits)
-        logits = self.model.forward(self.ids, self.kv, meta)
-        ops.sample(logits, temperature=self.f[0], top_k=self.topk, top_p=self.f[1], min_p=self.f[2], seed=self.seed,
-                   offset_dev=self.step_no, out=self.out)
+        logits = self.model.full_logits(self.model.forward(self.ids, self.kv, meta))
+        ops.sample(logits, temperature=self.f[0], top_k=self.topk, top_p=self.f[1], min_p=self.f[2], history=self.hist,
+                   rep_penalty=self.f[3], seed_dev=self.seeds, offset_dev=self.step_no, out=self.out)
         self.step_no += 1
 
-    def run(self) -> torch.Tensor:
-        for d, h in ((self.ids, self.h_ids), (self.pos, self.h_pos), (self.slots, self.h_slots), (self.ctx, self.h_ctx),
-                     (self.bt, self.h_bt), (self.f, self.h_f), (self.topk, self.h_topk)):
-            d.copy_(h, non_blocking=True)
+    def upload(self, group=None, src: int = 0, leader: bool = True) -> None:
+        """Stage this step's inputs on the device: one copy from pinned memory on the leader; with a process group the
+        packed device buffer is then broadcast so that every tensor-parallel rank replays the same batch."""
+        if leader:
+            self.d_buf.copy_(self.h_buf, non_blocking=True)
+            if self.hist_dirty:
+                self.hist.copy_(self.h_hist, non_blocking=True)
+        if group is not None:
+            import torch.distributed as dist
+            dist.broadcast(self.d_buf, src=src, group=group)
+            flag = torch.tensor([1 if self.hist_dirty else 0], device=self.dev)
+            dist.broadcast(flag, src=src, group=group)
+            if int(flag.item()):
+                dist.broadcast(self.hist, src=src, group=group)
+        self.hist_dirty = False
+
+    def execute(self) -> torch.Tensor:
         if self.use_graph:
             if self.graph is None:
                 s = torch.cuda.Stream(device=self.dev)
@@ -93,16 +129,28 @@ class _DecodeBucket:
                     self._body()
                 torch.cuda.current_stream(self.dev).wait_stream(s)
                 torch.cuda.synchronize(self.dev)
+                self.step_no.zero_()            # the warm-up pass must not advance the random stream
                 self.graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(self.graph):
                     self._body()
+                self.step_no.zero_()
             self.graph.replay()
         else:
             self._body()
         self.h_out.copy_(self.out, non_blocking=True)
+        self.h_status.copy_(self.status, non_blocking=True)
         if self.dev.type == "cuda":
             torch.cuda.current_stream(self.dev).synchronize()
+        code = int(self.h_status[0])
+        if code:
+            self.status.zero_()             # one expiry must not fail every later step
+            self.h_status.zero_()
+            raise_for_status(code)
         return self.h_out
+
+    def run(self) -> torch.Tensor:
+        self.upload()
+        return self.execute()
 
 
 class LLMEngine:
@@ -251,9 +299,11 @@ class LLMEngine:
                 rows.append(j)
                 reqs.append(rr)
         if not rows:
+            self._check_device_status()
             return {}
-        lg = logits[rows].contiguous()
+        lg = self.model.full_logits(logits)[rows].contiguous()
         toks = self._sample(lg, reqs)
+        self._check_device_status()
         return {rr.id: int(t) for rr, t in zip(reqs, toks)}
 
     def _sample(self, logits: torch.Tensor, reqs: List[RunningRequest]) -> List[int]:
@@ -265,8 +315,17 @@ class LLMEngine:
         k = torch.tensor([p.top_k for p in sp], dtype=torch.int32, device=dev)
         tp = torch.tensor([p.top_p for p in sp], dtype=torch.float32, device=dev)
         mp = torch.tensor([p.min_p for p in sp], dtype=torch.float32, device=dev)
-        return ops.sample(logits, temperature=t, top_k=k, top_p=tp, min_p=mp, seed=sp[0].seed,
-                          offset=(1 << 32) + self.iterations).tolist()
+        seeds = torch.tensor([(int(p.seed) * 1000003 + len(r.output_ids)) & 0x7FFFFFFFFFFFFFFF for p, r in zip(sp, reqs)],
+                             dtype=torch.int64, device=dev)
+        hist = rp = None
+        if any(p.repetition_penalty != 1.0 for p in sp):
+            hist = torch.full((len(reqs), HISTORY_LEN), -1, dtype=torch.int64)
+            for i, r in enumerate(reqs):
+                tail = r.all_ids[-HISTORY_LEN:]
+                hist[i, : len(tail)] = torch.tensor(tail, dtype=torch.int64)
+            hist = hist.to(dev)
+            rp = torch.tensor([p.repetition_penalty for p in sp], dtype=torch.float32, device=dev)
+        return ops.sample(logits, temperature=t, top_k=k, top_p=tp, min_p=mp, history=hist, rep_penalty=rp, seed_dev=seeds).tolist()
 
     def _bucket(self, n: int) -> _DecodeBucket:
         B = next((b for b in self.cfg.graph_buckets if b >= n), n)
@@ -287,6 +346,7 @@ class LLMEngine:
         bk.h_f[1].fill_(1.0)
         bk.h_f[3].fill_(1.0)
         bk.h_topk.zero_()
+        bk.h_seeds.zero_()
         for i, rr in enumerate(reqs):
             n = self.cache.table.num_tokens(rr.id)         # includes the slot appended for this step's input
             blocks = self.cache.table.block_table(rr.id)
@@ -298,9 +358,26 @@ class LLMEngine:
             sp = rr.req.sampling
             bk.h_f[0, i], bk.h_f[1, i], bk.h_f[2, i], bk.h_f[3, i] = sp.temperature, sp.top_p, sp.min_p, sp.repetition_penalty
             bk.h_topk[i] = sp.top_k
-            bk.seed = sp.seed
-        out = bk.run()
+            # a row's random stream depends on its own seed and on how many tokens it has produced, not on its batch slot
+            bk.h_seeds[i] = (int(sp.seed) * 1000003 + len(rr.output_ids)) & 0x7FFFFFFFFFFFFFFF
+            if sp.repetition_penalty != 1.0:
+                tail = rr.all_ids[-HISTORY_LEN:]
+                bk.h_hist[i].fill_(-1)
+                bk.h_hist[i, : len(tail)] = torch.tensor(tail, dtype=torch.int64)
+                bk.hist_dirty = True
+        out = self._execute_decode(bk)
         return {rr.id: int(out[i]) for i, rr in enumerate(reqs)}
+
+    def _execute_decode(self, bk: _DecodeBucket) -> torch.Tensor:
+        return bk.run()
+
+    def _check_device_status(self) -> None:
+        """Host read of the device status word after a prompt pass (the pass already synchronised to sample)."""
+        st = ops.gemm_status(self.model.device)
+        code = int(st[0].item())
+        if code:
+            st.zero_()
+            raise_for_status(code)
 
     # ------------------------------------------------------------------ introspection
     def stats(self) -> dict:

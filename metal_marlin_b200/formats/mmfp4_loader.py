@@ -24,7 +24,7 @@ import torch
 
 from .safetensors_io import SafetensorsFile
 
-WEIGHT_SUFFIXES = (".weight", ".qweight", ".packed_weight")
+WEIGHT_SUFFIXES = (".qweight", ".weight", ".packed_weight")      # probe order of the reference loader
 SCALE_SUFFIXES = (".scales", ".weight_scale", ".scales_fp4", ".weight.scales")
 _LAYER_RE = re.compile(r"(?:layers|h|blocks)\.(\d+)\.")
 

@@ -86,10 +86,18 @@ class CheckpointSource:
             w = FP4Weight.from_float(self.loader.load_tensor(name + ".weight").to(self.device), self.cfg.group_size)
         assert (w.out_features, w.in_features) == (out_f, in_f), (name, w.out_features, w.in_features, out_f, in_f)
         w.names = [(name + ".weight", out_f)]
+        # MR-GPTQ checkpoints store the weight in a block-Hadamard-rotated input basis; the op layer rotates the activation
+        w.hadamard_block = self.loader.get_hadamard_block_size(name)
         return w
 
     def linear_cat(self, names, outs, in_f) -> FP4Weight:
-        return FP4Weight.concat_rows([self.linear(n, o, in_f) for n, o in zip(names, outs)])
+        parts = [self.linear(n, o, in_f) for n, o in zip(names, outs)]
+        blocks = {p.hadamard_block for p in parts}
+        if len(blocks) != 1:
+            raise ValueError(f"projections fused over one input must share one rotation, got blocks {sorted(blocks)} for {names}")
+        w = FP4Weight.concat_rows(parts)
+        w.hadamard_block = blocks.pop()
+        return w
 
     def dense(self, name: str, *shape, std=None) -> torch.Tensor:
         t = self.loader.load_tensor(name).to(self.device, torch.bfloat16)
@@ -101,6 +109,21 @@ class CheckpointSource:
 
     def float(self, name: str, *shape, std=None) -> torch.Tensor:
         return self.loader.load_tensor(name).to(self.device, torch.float32)
+
+
+def _unrotate(w: torch.Tensor, block: int) -> torch.Tensor:
+    """Dense copy of a weight stored in the rotated basis: ``W = W_rot . H`` (H block-diagonal, orthonormal, symmetric)."""
+    if not block:
+        return w
+    from ..quant.hadamard import fwht
+    return fwht(w.reshape(w.shape[0], -1, block)).reshape(w.shape)
+
+
+def _bank_block(ws) -> int:
+    blocks = {getattr(w, "hadamard_block", 0) for w in ws}
+    if len(blocks) != 1:
+        raise ValueError(f"the experts of one bank must share one rotation, got blocks {sorted(blocks)}")
+    return blocks.pop()
 
 
 def _expert_names(prefix: str, e: int):
@@ -123,8 +146,9 @@ def build_layer(cfg: ModelConfig, src, i: int) -> LayerWeights:
             L.qa_kva = src.linear_cat([f"{a}.q_proj", f"{a}.kv_a_proj_with_mqa"], [nh * (dn + dr), R + dr], H)
         L.kv_a_norm = src.norm(f"{a}.kv_a_layernorm.weight", R)
         L.kv_b = src.linear(f"{a}.kv_b_proj", nh * (dn + dv), R)
-        L.w_ukT, L.w_uv = absorb_kv_b(L.kv_b, nh, dn, dv, R)
-        L.kv_b_dense = L.kv_b.dequantize(torch.bfloat16).contiguous()      # prefill lifts latent rows to per-head K / V with it
+        hb = getattr(L.kv_b, "hadamard_block", 0)
+        L.w_ukT, L.w_uv = absorb_kv_b(L.kv_b, nh, dn, dv, R, hadamard_block=hb)
+        L.kv_b_dense = _unrotate(L.kv_b.dequantize(torch.float32), hb).to(torch.bfloat16).contiguous()      # prefill lifts latent rows to per-head K / V with it
         L.kv_b = None      # the absorbed copies serve decode
         L.o = src.linear(f"{a}.o_proj", H, nh * dv)
     else:
@@ -166,13 +190,17 @@ def build_layer(cfg: ModelConfig, src, i: int) -> LayerWeights:
                     gu = FP4Weight.concat_rows([FP4Weight.from_codes(gcs[0][sl], gcs[1][sl]),
                                                 FP4Weight.from_codes(ucs[0][sl], ucs[1][sl])])
                     gu.names = (sg.names or []) + (su.names or [])        # calibration: same input as the whole shared MLP
+                    gu.hadamard_block = sg.hadamard_block
                     gus.append(gu)
                     gper = I // sd.group_size
                     dw = FP4Weight.from_codes(sdc[:, sl].contiguous(), sds[:, j * gper:(j + 1) * gper].contiguous())
+                    assert not sd.hadamard_block or I % sd.hadamard_block == 0, "shared-expert width must be a multiple of the rotation block"
+                    dw.hadamard_block = sd.hadamard_block
                     dw.names = sd.names if ns == 1 else None            # a column slice of the shared down matrix has no Hessian of its own
                     dws.append(dw)
             L.gate_up_bank = FP4ExpertBank.from_weights(gus)
             L.down_bank = FP4ExpertBank.from_weights(dws)
+            L.gate_up_bank.hadamard_block, L.down_bank.hadamard_block = _bank_block(gus), _bank_block(dws)
     else:
         I = cfg.intermediate_size
         L.gate_up = src.linear_cat([f"{m}.gate_proj", f"{m}.up_proj"], [I, I], H)

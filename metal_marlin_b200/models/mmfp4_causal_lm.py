@@ -88,6 +88,9 @@ class MMFP4ForCausalLM:
         device = device or ("cuda" if torch.cuda.is_available() else "cpu")
         return cls(build_transformer(cfg, RandomSource(cfg, device, seed)))
 
+    def to(self, device) -> "MMFP4ForCausalLM":
+        return MMFP4ForCausalLM(self.model.to(device))
+
     # ------------------------------------------------------------------ cache helpers
     def new_cache(self, num_blocks: int, block_size: int = 16, kv_dtype: str = "bf16") -> PagedKVStorage:
         return PagedKVStorage(self.config, num_blocks, block_size, self.device, kv_dtype=kv_dtype)

@@ -98,11 +98,15 @@ class LayerWeights:
     down_bank: Optional[FP4ExpertBank] = None
 
 
-def absorb_kv_b(kv_b: FP4Weight, H: int, dn: int, dv: int, R: int) -> Tuple[torch.Tensor, torch.Tensor]:
+def absorb_kv_b(kv_b: FP4Weight, H: int, dn: int, dv: int, R: int, hadamard_block: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
     """Split the dequantized kv_b projection ``[H * (dn + dv), R]`` into ``W_uk^T [H, R, dn]`` and
     ``W_uv [H, dv, R]`` (bf16) for absorbed-MLA decode.  Parity: reference
     ``metal_marlin/paged/mmfp4_paged_adapter.py:236-345``."""
-    w = kv_b.dequantize(torch.float32).view(H, dn + dv, R)
+    w = kv_b.dequantize(torch.float32)
+    if hadamard_block:        # stored in a rotated input basis: W = W_rot . H
+        from ..quant.hadamard import fwht
+        w = fwht(w.reshape(w.shape[0], -1, hadamard_block)).reshape(w.shape)
+    w = w.view(H, dn + dv, R)
     w_uk = w[:, :dn, :]
     return w_uk.transpose(1, 2).contiguous().to(torch.bfloat16), w[:, dn:, :].contiguous().to(torch.bfloat16)
 
@@ -506,6 +510,21 @@ class Transformer:
         if not meta.decode and last_only and meta.cu_seqlens is not None:
             rows = torch.tensor([e - 1 for e in meta.cu_seqlens[1:]], device=h.device, dtype=torch.long)
         return self.logits(h, d, rows)
+
+    def to(self, device) -> "Transformer":
+        """Copy of the model on ``device`` (weights are moved as they are: no re-quantization, no kernel launch)."""
+        import dataclasses
+        device = torch.device(device)
+
+        def mv(v):
+            if isinstance(v, (FP4Weight, FP4ExpertBank, torch.Tensor)):
+                return v.to(device)
+            return v
+        layers = [dataclasses.replace(L, **{f.name: mv(getattr(L, f.name)) for f in dataclasses.fields(L)}) for L in self.layers]
+        head = self.embed.to(device) if self.lm_head is self.embed else self.lm_head.to(device)
+        m = Transformer(self.cfg, layers, self.embed.to(device) if self.lm_head is not self.embed else head, self.final_norm.to(device), head)
+        m.mtp = self.mtp
+        return m
 
     # ------------------------------------------------------------------ accounting
     def weight_bytes(self) -> int:

@@ -76,7 +76,13 @@ def gemm_status(device) -> torch.Tensor:
     key = str(device)
     if key not in _status:
         _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        if torch.device(device).type == "cuda" and native_available():
+            torch.ops.mmb200.set_status_word(_status[key])     # kernels without a status argument report here too
     return _status[key]
+
+
+def clear_status(device) -> None:
+    gemm_status(device).zero_()
 
 
 def check_status(device) -> int:
@@ -129,7 +135,7 @@ def rmsnorm(x, w, eps=1e-6, *, delta=None, resid_out=None, out=None):
 
 
 def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bias=None, out_add=None,
-           out=None, token_tile=0, tpx=None, ag_wait=None):
+           out=None, token_tile=0, tpx=None, ag_wait=None, _rotated=False):
     """``out = epilogue( prologue(x) @ dequant(W)^T )``; prologue = optional residual add + RMSNorm,
     epilogue = optional bias, SwiGLU over the two row halves (``act=1``), residual add.
 
@@ -145,6 +151,17 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
         from . import generic
         return generic.linear(x, W, delta=delta, norm_w=norm_w, eps=eps, resid_out=resid_out, act=act, bias=bias,
                               out_add=out_add, out=out)
+    hb = getattr(W, "hadamard_block", 0)
+    if hb and not _rotated:
+        # weight stored in a block-Hadamard-rotated basis (MR-GPTQ): y = W_rot . H(norm(x + delta)); the add + norm cannot
+        # stay fused in the streaming kernel's prologue because the rotation sits between them and the product
+        assert tpx is None or (delta is None and norm_w is None)
+        xin = x[:, : W.in_features]
+        if delta is not None or norm_w is not None:
+            xin = rmsnorm(x, norm_w, eps, delta=delta, resid_out=resid_out) if norm_w is not None else _add(x, delta, resid_out)
+            xin = xin[:, : W.in_features]
+        xin = hadamard(xin.contiguous(), hb)
+        return linear(xin, W, act=act, bias=bias, out_add=out_add, out=out, token_tile=token_tile, tpx=tpx, _rotated=True)
     if _capture is not None:
         _capture("linear", W, ref.add_norm(x[:, : W.in_features], None if delta is None else delta[:, : W.in_features], norm_w, eps), None)
     if not _use_native(x):
@@ -198,6 +215,13 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
     if out_add is not None:
         out += out_add
     return out
+
+
+def _add(x, delta, resid_out=None):
+    y = (x.to(torch.float32) + delta.to(torch.float32)).to(x.dtype)
+    if resid_out is not None:
+        resid_out.copy_(y)
+    return y
 
 
 def bf16_linear(x, w, *, delta=None, norm_w=None, eps=1e-6, out_dtype=torch.bfloat16, out=None, tpx=None):
@@ -407,6 +431,7 @@ def paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, *, Hq, Hkv, dqk, 
         part_o, part_ml = workspace
     if out is None:
         out = torch.empty(B, Hq, dvo, dtype=torch.bfloat16, device=q.device)
+    gemm_status(q.device)        # registers the device's status word on first use: the kernel's bounded waits report there
     if fp8:
         K.mmb200.paged_decode_fp8(q, k_pool.data, None if v_pool is None else v_pool.data, k_pool.scale,
                                   None if v_pool is None else v_pool.scale, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv,
@@ -512,8 +537,9 @@ def argmax(logits, out=None):
 
 
 def sample(logits, *, temperature=None, top_k=None, top_p=None, min_p=None, history=None, rep_penalty=None, seed=0,
-           offset=0, out=None, out_logprob=None, generator=None, offset_dev=None):
-    """Per-row parameters are tensors on the logits' device (None = feature off)."""
+           offset=0, out=None, out_logprob=None, generator=None, offset_dev=None, seed_dev=None):
+    """Per-row parameters are tensors on the logits' device (None = feature off).  ``seed_dev`` (int64 ``[B]``) gives
+    every row its own Philox key and, being device memory, can change between replays of a captured graph."""
     if not _use_native(logits):
         ids, lp = ref.sample(logits, temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p, history=history,
                              rep_penalty=rep_penalty, generator=generator)
@@ -526,7 +552,7 @@ def sample(logits, *, temperature=None, top_k=None, top_p=None, min_p=None, hist
     if out is None:
         out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
     K.mmb200.sample(logits, out, out_logprob, temperature, top_k, top_p, min_p, history, rep_penalty, int(seed), int(offset),
-                    offset_dev)
+                    offset_dev, seed_dev)
     return out
 
 
@@ -627,6 +653,15 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
         from . import generic
         return generic.moe_forward(x, gate_up, ids, weights, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps,
                                    out_add=out_add)
+    if getattr(gate_up, "hadamard_block", 0) or getattr(down, "hadamard_block", 0):
+        # banks stored in a rotated basis: rotate the (normalised) input once, and the SwiGLU output of every slot
+        xin = rmsnorm(x, norm_w, eps) if norm_w is not None else x
+        if getattr(gate_up, "hadamard_block", 0):
+            xin = hadamard(xin[:, : gate_up.in_features].contiguous(), gate_up.hadamard_block)
+        h = moe_gate_up(xin, gate_up, ids, n_shared=n_shared, shared_base=shared_base)
+        if getattr(down, "hadamard_block", 0):
+            h = hadamard(h.reshape(-1, h.shape[-1])[:, : down.in_features].contiguous(), down.hadamard_block).view(T, -1, down.in_features)
+        return moe_down(h, down, ids, weights, n_shared=n_shared, shared_base=shared_base, out_add=out_add, tpx=tpx)
     if _capture is not None:
         # calibration: expose the inputs of both expert projections with the expert of every (token, slot)
         e_all = ids.long()

@@ -18,9 +18,9 @@ from ..formats import fp4 as fp4fmt
 
 
 class FP4Weight:
-    __slots__ = ("qtile", "stile", "out_features", "in_features", "group_size", "_deq", "names")
+    __slots__ = ("qtile", "stile", "out_features", "in_features", "group_size", "_deq", "names", "hadamard_block")
 
-    def __init__(self, qtile, stile, out_features, in_features, group_size):
+    def __init__(self, qtile, stile, out_features, in_features, group_size, hadamard_block: int = 0):
         self.qtile = qtile
         self.stile = stile
         self.out_features = int(out_features)
@@ -28,6 +28,8 @@ class FP4Weight:
         self.group_size = int(group_size)
         self._deq = None
         self.names = None            # [(checkpoint tensor name, rows)] when loaded from a checkpoint (calibration hooks)
+        # > 0: the matrix is stored in a block-Hadamard-rotated input basis (MR-GPTQ); consumers rotate the activation
+        self.hadamard_block = int(hadamard_block)
 
     # ------------------------------------------------------------------ constructors
     @classmethod
@@ -70,7 +72,8 @@ class FP4Weight:
             assert p.out_features % 16 == 0, "row-concat needs 16-row aligned parts"
         q = torch.cat([p.qtile for p in parts], 0)
         s = torch.cat([p.stile for p in parts], 0)
-        w = cls(q, s, sum(p.out_features for p in parts), p0.in_features, p0.group_size)
+        assert len({p.hadamard_block for p in parts}) == 1, "row-concatenated matrices must share one input rotation"
+        w = cls(q, s, sum(p.out_features for p in parts), p0.in_features, p0.group_size, p0.hadamard_block)
         if all(p.names for p in parts):
             w.names = [n for p in parts for n in p.names]
         return w
@@ -80,15 +83,17 @@ class FP4Weight:
         """Output rows ``[r0, r1)`` (column-parallel shard); bounds must be multiples of 16."""
         assert r0 % 16 == 0 and (r1 % 16 == 0 or r1 == self.out_features)
         return FP4Weight(self.qtile[r0 // 16: (r1 + 15) // 16].contiguous(), self.stile[r0 // 16: (r1 + 15) // 16].contiguous(),
-                         r1 - r0, self.in_features, self.group_size)
+                         r1 - r0, self.in_features, self.group_size, self.hadamard_block)
 
     def slice_cols(self, k0: int, k1: int) -> "FP4Weight":
         """Input columns ``[k0, k1)`` (row-parallel shard); bounds must be multiples of max(64, group size)."""
         unit = max(64, self.group_size)
         assert k0 % unit == 0 and (k1 % unit == 0 or k1 == self.in_features), (k0, k1, unit)
         gs = self.group_size
+        hb = self.hadamard_block
+        assert not hb or (k0 % hb == 0 and (k1 - k0) % hb == 0), "a column shard must not cut a rotation block"
         return FP4Weight(self.qtile[:, k0 // 64: (k1 + 63) // 64].contiguous(),
-                         self.stile[:, k0 // gs: (k1 + gs - 1) // gs].contiguous(), self.out_features, k1 - k0, gs)
+                         self.stile[:, k0 // gs: (k1 + gs - 1) // gs].contiguous(), self.out_features, k1 - k0, gs, hb)
 
     # ------------------------------------------------------------------ views
     @property
@@ -101,7 +106,7 @@ class FP4Weight:
 
     def to(self, device) -> "FP4Weight":
         return FP4Weight(self.qtile.to(device), self.stile.to(device), self.out_features, self.in_features,
-                         self.group_size)
+                         self.group_size, self.hadamard_block)
 
     def codes_scales(self):
         return fp4fmt.from_tile_layout(self.qtile, self.stile, self.out_features, self.in_features, self.group_size)
@@ -121,9 +126,10 @@ class FP4Weight:
 
 class FP4ExpertBank:
     """``E`` (+ shared) expert matrices of identical shape stacked on a leading axis."""
-    __slots__ = ("qtile", "stile", "num_experts", "out_features", "in_features", "group_size", "_deq", "names")
+    __slots__ = ("qtile", "stile", "num_experts", "out_features", "in_features", "group_size", "_deq", "names", "hadamard_block")
 
-    def __init__(self, qtile, stile, out_features, in_features, group_size):
+    def __init__(self, qtile, stile, out_features, in_features, group_size, hadamard_block: int = 0):
+        self.hadamard_block = int(hadamard_block)      # shared input rotation of every expert (0 = none)
         self.qtile = qtile            # [E, N/16, K/64, 32, 4] int32
         self.stile = stile            # [E, N/16, K/gs, 8, 2] fp16
         self.num_experts = qtile.shape[0]
@@ -155,17 +161,25 @@ class FP4ExpertBank:
         """Keep the output-row ranges ``[(r0, r1), ...]`` (multiples of 16) of every expert, concatenated."""
         q = torch.cat([self.qtile[:, r0 // 16: r1 // 16] for r0, r1 in ranges], 1).contiguous()
         s = torch.cat([self.stile[:, r0 // 16: r1 // 16] for r0, r1 in ranges], 1).contiguous()
-        return FP4ExpertBank(q, s, sum(r1 - r0 for r0, r1 in ranges), self.in_features, self.group_size)
+        return FP4ExpertBank(q, s, sum(r1 - r0 for r0, r1 in ranges), self.in_features, self.group_size, self.hadamard_block)
 
     def slice_cols(self, k0: int, k1: int) -> "FP4ExpertBank":
         unit = max(64, self.group_size)
         assert k0 % unit == 0 and (k1 % unit == 0 or k1 == self.in_features), (k0, k1, unit)
         gs = self.group_size
+        hb = self.hadamard_block
+        assert not hb or (k0 % hb == 0 and (k1 - k0) % hb == 0), "a column shard must not cut a rotation block"
         return FP4ExpertBank(self.qtile[:, :, k0 // 64: (k1 + 63) // 64].contiguous(),
-                             self.stile[:, :, k0 // gs: (k1 + gs - 1) // gs].contiguous(), self.out_features, k1 - k0, gs)
+                             self.stile[:, :, k0 // gs: (k1 + gs - 1) // gs].contiguous(), self.out_features, k1 - k0, gs, hb)
+
+    def to(self, device) -> "FP4ExpertBank":
+        b = FP4ExpertBank(self.qtile.to(device), self.stile.to(device), self.out_features, self.in_features, self.group_size,
+                          self.hadamard_block)
+        b.names = self.names
+        return b
 
     def expert(self, e: int) -> FP4Weight:
-        return FP4Weight(self.qtile[e], self.stile[e], self.out_features, self.in_features, self.group_size)
+        return FP4Weight(self.qtile[e], self.stile[e], self.out_features, self.in_features, self.group_size, self.hadamard_block)
 
     def dequantize(self, dtype=torch.float32, cache: bool = False) -> torch.Tensor:
         if self._deq is not None and self._deq.dtype == dtype:

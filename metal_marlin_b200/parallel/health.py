@@ -24,6 +24,54 @@ class PeerFailure(RuntimeError):
         self.ranks, self.reason = ranks, reason
 
 
+class DeviceWaitExpired(RuntimeError):
+    """A bounded device-side wait of a kernel on THIS GPU ran out (no peer is implied): a pipeline barrier of the tensor-core
+    GEMM / attention kernels or of the paged decode kernel."""
+
+    def __init__(self, code: int, what: str):
+        super().__init__(f"device-side wait expired (status {code}: {what})")
+        self.code, self.what = code, what
+
+
+class ExpertCapacityOverflow(RuntimeError):
+    """The expert-parallel receive buffer was too small for the routed rows (status 120): not a peer failure."""
+
+    def __init__(self, code: int = 120):
+        super().__init__("expert-parallel receive buffer overflowed; rows were dropped (status 120)")
+        self.code = code
+
+
+def decode_status(code: int):
+    """Meaning of a device status word: ``(kind, ranks, text)`` with kind in
+    ``"ok" | "peer" | "local" | "capacity"``.  Only three ranges name a rank: 100-109 tensor-parallel source ``code - 100``,
+    121-128 expert-parallel sender ``code - 121``, 140-147 expert-parallel return ``code - 140``."""
+    if code == 0:
+        return "ok", [], "no wait expired"
+    if 100 <= code <= 109:
+        return "peer", [code - 100], f"tensor-parallel partial from rank {code - 100} did not arrive"
+    if 121 <= code <= 128:
+        return "peer", [code - 121], f"expert-parallel rows from rank {code - 121} did not arrive"
+    if 140 <= code <= 147:
+        return "peer", [code - 140], f"expert-parallel results from rank {code - 140} did not arrive"
+    if code == 120:
+        return "capacity", [], "expert-parallel receive buffer overflow"
+    names = {1: "GEMM producer barrier", 2: "GEMM MMA barrier", 3: "GEMM expansion barrier", 4: "GEMM epilogue barrier",
+             42: "attention kernel barrier", 110: "GEMM all-gather tile wait", 200: "paged decode row barrier"}
+    return "local", [], names.get(code, "unknown wait")
+
+
+def raise_for_status(code: int) -> None:
+    """Turn a non-zero status word into the matching exception."""
+    kind, ranks, text = decode_status(code)
+    if kind == "ok":
+        return
+    if kind == "peer":
+        raise PeerFailure(ranks, f"device-side exchange wait expired (status {code}: {text})")
+    if kind == "capacity":
+        raise ExpertCapacityOverflow(code)
+    raise DeviceWaitExpired(code, text)
+
+
 class Heartbeat:
     def __init__(self, store, rank: int, world: int, interval_s: float = 0.2, timeout_s: float = 2.0, prefix: str = "hb",
                  join_timeout_s: float = 60.0):
@@ -111,10 +159,7 @@ class StepGuard:
         out = step_fn()
         self.steps += 1
         if self.ctx is not None:
-            code = self.ctx.check()
-            if code:
-                src = code - 100 if code >= 100 else -1
-                raise PeerFailure([src] if src >= 0 else [], f"device-side exchange wait expired (status {code})")
+            raise_for_status(self.ctx.check())
         return out
 
 

@@ -107,7 +107,7 @@ class TPContext:
         self.flags_off = flags_off
         self.step = torch.zeros(1, dtype=torch.int32, device=device)
         self.counters = torch.zeros(self.n_flag_sites, dtype=torch.int32, device=device)
-        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.status = ops.gemm_status(device)      # one status word per device: the engine reads it back with the sampled ids
         # per site: device arrays of peer addresses (my slot in every peer's buffer, my flag on every peer)
         slots = torch.empty(self.n_flag_sites, tp, dtype=torch.int64)
         flags = torch.empty(self.n_flag_sites, tp, dtype=torch.int64)

@@ -59,7 +59,7 @@ def _copy_aux(src: str, dst: str) -> None:
 
 
 def quantize_named_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], fmt: str, group_size: int,
-                           device: str = "cpu", quantize_fn: Optional[Callable] = None
+                           device: str = "cpu", quantize_fn: Optional[Callable] = None, hadamard_block: int = 0
                            ) -> Iterator[Tuple[str, Dict[str, torch.Tensor], Dict[str, str], Optional[dict]]]:
     """For each input tensor yields (name, tensors-to-write, dtype-overrides, report-entry)."""
     for name, t in tensors:
@@ -68,6 +68,10 @@ def quantize_named_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], fmt: str
             continue
         gs = fp4fmt.pick_group_size(t.shape[1], group_size)
         w = t.to(device=device, dtype=torch.float32)
+        rot = hadamard_block if (hadamard_block and w.shape[1] % hadamard_block == 0) else 0
+        if rot:      # quantize in the rotated input basis (W . H); readers rotate the activation: y = (W H)(H x)
+            from .hadamard import fwht
+            w = fwht(w.reshape(w.shape[0], -1, rot)).reshape(w.shape)
         if quantize_fn is not None:
             codes, scales = quantize_fn(name, w, gs)
         else:
@@ -79,11 +83,14 @@ def quantize_named_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], fmt: str
             packed, sc = fp4fmt.pack_mmfp4(codes, scales)
         # both reference writers key the side tensors off the full tensor name: "<name>.scales", "<name>.group_size"
         out = {name: packed.cpu(), name + ".scales": sc.cpu(), name + ".group_size": torch.tensor([gs], dtype=torch.int32)}
+        if rot:
+            out[name + ".hadamard_block_size"] = torch.tensor([rot], dtype=torch.int32)
         yield name, out, {name: "U32"}, {"name": name, "shape": list(t.shape), "group_size": gs, "rel_rmse": err}
 
 
 def convert_model(model_dir: str, out_dir: str, fmt: str = "marlin_fp4", group_size: int = 128, device: str = "cpu",
-                  shard_bytes: int = 4 << 30, quantize_fn: Optional[Callable] = None, verbose: bool = False) -> dict:
+                  shard_bytes: int = 4 << 30, quantize_fn: Optional[Callable] = None, verbose: bool = False,
+                  hadamard_block: int = 0) -> dict:
     """Stream a float HF checkpoint into a quantized one.  ``fmt``: ``marlin_fp4`` (single
     ``model.safetensors``) or ``mmfp4`` (shards + ``model.safetensors.index.json``)."""
     os.makedirs(out_dir, exist_ok=True)
@@ -104,7 +111,8 @@ def convert_model(model_dir: str, out_dir: str, fmt: str = "marlin_fp4", group_s
         shard_no += 1
 
     n_q = n_total = 0
-    for name, outs, dts, rep in quantize_named_tensors(iter_safetensors_weights(model_dir), fmt, group_size, device, quantize_fn):
+    for name, outs, dts, rep in quantize_named_tensors(iter_safetensors_weights(model_dir), fmt, group_size, device, quantize_fn,
+                                                         hadamard_block):
         n_total += 1
         if rep is not None:
             n_q += 1
@@ -212,12 +220,15 @@ def random_hf_state(cfg, seed: int = 0, std: float = 0.02) -> Dict[str, torch.Te
     return sd
 
 
-def save_random_checkpoint(cfg, out_dir: str, fmt: str = "mmfp4", seed: int = 0, float_dir: Optional[str] = None) -> dict:
-    """Write a random-init float checkpoint (HF names) and quantize it to ``fmt`` in ``out_dir``."""
+def save_random_checkpoint(cfg, out_dir: str, fmt: str = "mmfp4", seed: int = 0, float_dir: Optional[str] = None,
+                           hadamard_block: int = 0) -> dict:
+    """Write a random-init float checkpoint (HF names) and quantize it to ``fmt`` in ``out_dir``.  With
+    ``hadamard_block`` every quantized matrix is stored in the block-Hadamard-rotated input basis (as MR-GPTQ writes
+    them), with a ``<name>.hadamard_block_size`` tensor beside it."""
     float_dir = float_dir or os.path.join(out_dir, "_float")
     os.makedirs(float_dir, exist_ok=True)
     save_file(random_hf_state(cfg, seed), os.path.join(float_dir, "model.safetensors"), metadata={"format": "pt"})
     cfg.save_pretrained(float_dir)
-    info = convert_model(float_dir, out_dir, fmt, cfg.group_size)
+    info = convert_model(float_dir, out_dir, fmt, cfg.group_size, hadamard_block=hadamard_block)
     shutil.rmtree(float_dir, ignore_errors=True)
     return info

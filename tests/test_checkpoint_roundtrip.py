@@ -86,3 +86,32 @@ def test_language_model_prefix_alias(tmp_path):
     convert_model(str(fdir), str(tmp_path / "q"), "mmfp4", 128)
     lm = MMFP4ForCausalLM.from_pretrained(str(tmp_path / "q"), device="cpu")
     assert len(lm.generate([[5, 6, 7]], max_new_tokens=2)[0]) == 2
+
+
+@pytest.mark.parametrize("preset", ["tiny-llama", "tiny-mla-moe"])
+def test_rotated_checkpoint_loads_with_its_rotation(tmp_path, preset):
+    """A checkpoint whose matrices are stored in the block-Hadamard-rotated basis (``<name>.hadamard_block_size`` beside
+    them, as MR-GPTQ writes) must give the logits of the same model stored unrotated, up to 4-bit rounding; ignoring the
+    rotation tensors gives unrelated logits."""
+    import torch
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM
+    from metal_marlin_b200.quant.convert import save_random_checkpoint
+    cfg = get_preset(preset)
+    plain, rotated = str(tmp_path / "plain"), str(tmp_path / "rot")
+    save_random_checkpoint(cfg, plain, seed=5)
+    save_random_checkpoint(cfg, rotated, seed=5, hadamard_block=32)
+    ids = torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(1)).tolist()
+    a = MMFP4ForCausalLM.from_pretrained(plain, device="cpu")
+    b = MMFP4ForCausalLM.from_pretrained(rotated, device="cpu")
+    assert b.model.layers[0].o.hadamard_block == 32 and a.model.layers[0].o.hadamard_block == 0
+    la, lb = a.forward_logits(ids), b.forward_logits(ids)
+    cos = torch.nn.functional.cosine_similarity(la.flatten(), lb.flatten(), dim=0)
+    assert cos > 0.8, cos           # two 4-bit roundings of one random model agree to about 0.9
+    # the same rotated bytes read without their rotation: wrong model
+    for L in b.model.layers:
+        for v in vars(L).values():
+            if hasattr(v, "hadamard_block"):
+                v.hadamard_block = 0
+    lc = b.forward_logits(ids)
+    assert torch.nn.functional.cosine_similarity(la.flatten(), lc.flatten(), dim=0) < 0.5

@@ -225,3 +225,45 @@ def test_engine_survives_preemption_with_identical_output():
                                            use_cuda_graphs=False))
     got = eng.generate(prompts, max_new_tokens=10)
     assert got == want and eng.scheduler.num_preemptions >= 1
+
+
+def test_engine_fails_requests_when_the_device_status_word_is_set():
+    """A bounded in-kernel wait that ran out leaves a code in the device status word; the engine reads the word back with
+    the sampled ids, fails the in-flight requests instead of returning their tokens, and clears the word."""
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.parallel.health import DeviceWaitExpired, PeerFailure
+    lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    eng = LLMEngine(lm.model, EngineConfig(num_kv_blocks=32, max_model_len=64, use_cuda_graphs=False))
+    st = ops.gemm_status(lm.device)
+    eng.add_request(GenerationRequest([1, 2, 3], 4))
+    st[0] = 101                                   # as if the wait on tensor-parallel source 1 had expired
+    with pytest.raises(PeerFailure) as e:
+        eng.step()                                # prompt pass
+    assert e.value.ranks == [1] and int(st[0]) == 0
+    eng.step()                                    # the word was cleared: the next pass runs
+    st[0] = 200                                   # paged-decode barrier: a local wait, no rank named
+    with pytest.raises(DeviceWaitExpired):
+        eng.step()                                # decode pass
+    assert int(st[0]) == 0
+    # background loop: the in-flight request ends FAILED with the reason, the loop keeps serving
+    eng2 = LLMEngine(lm.model, EngineConfig(num_kv_blocks=32, max_model_len=64, use_cuda_graphs=False))
+    st[0] = 3
+    eng2.start()
+    bad = eng2.add_request(GenerationRequest([4, 5, 6], 4))
+    assert bad.done.wait(30) and bad.status is RequestStatus.FAILED and "status 3" in bad.error
+    good = eng2.add_request(GenerationRequest([4, 5, 6], 4))
+    assert good.done.wait(30) and good.status is RequestStatus.FINISHED
+    eng2.stop()
+
+
+def test_engine_applies_repetition_penalty_per_request():
+    """The penalty of each request reaches the sampler together with that request's recent tokens (prompt tail and
+    generated ids): with a very strong penalty nothing already seen is produced again."""
+    lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    eng = LLMEngine(lm.model, EngineConfig(num_kv_blocks=32, max_model_len=128, use_cuda_graphs=False))
+    prompt = list(range(10, 30))
+    plain = eng.add_request(GenerationRequest(list(prompt), 12))
+    pen = eng.add_request(GenerationRequest(list(prompt), 12, SamplingParams(repetition_penalty=1e4)))
+    eng.run_until_done()
+    assert len(set(pen.output_ids)) == len(pen.output_ids) and not set(pen.output_ids) & set(prompt)
+    assert plain.output_ids != pen.output_ids or len(set(plain.output_ids)) == len(plain.output_ids)

@@ -94,3 +94,52 @@ def test_step_guard_reports_device_wait_expiry():
     with pytest.raises(PeerFailure) as e:
         guard.run(lambda: 7)
     assert e.value.ranks == [1] and "status 101" in str(e.value)
+
+
+def test_status_codes_are_decoded_by_range():
+    """Only three code ranges name a peer; everything else is a local wait or the capacity overflow."""
+    from metal_marlin_b200.parallel.health import (DeviceWaitExpired, ExpertCapacityOverflow, decode_status,
+                                                   raise_for_status)
+    assert decode_status(0)[0] == "ok"
+    assert decode_status(103)[:2] == ("peer", [3])
+    assert decode_status(121)[:2] == ("peer", [0]) and decode_status(128)[:2] == ("peer", [7])
+    assert decode_status(145)[:2] == ("peer", [5])
+    for code in (1, 2, 3, 4, 42, 110, 200, 999):
+        assert decode_status(code)[:2] == ("local", []), code
+        with pytest.raises(DeviceWaitExpired):
+            raise_for_status(code)
+    assert decode_status(120)[0] == "capacity"
+    with pytest.raises(ExpertCapacityOverflow):
+        raise_for_status(120)
+    with pytest.raises(PeerFailure) as e:
+        raise_for_status(142)
+    assert e.value.ranks == [2]
+    raise_for_status(0)
+
+
+def test_step_guard_keeps_non_peer_codes_apart():
+    from metal_marlin_b200.parallel.health import DeviceWaitExpired, ExpertCapacityOverflow
+
+    class FakeStore(dict):
+        def set(self, k, v):
+            self[k] = v.encode() if isinstance(v, str) else v
+
+        def get(self, k):
+            return self[k]
+
+    class FakeCtx:
+        code = 0
+
+        def check(self):
+            return self.code
+
+    ctx = FakeCtx()
+    guard = StepGuard(Heartbeat(FakeStore(), 0, 1), ctx)
+    for code, exc in ((110, DeviceWaitExpired), (200, DeviceWaitExpired), (120, ExpertCapacityOverflow)):
+        ctx.code = code
+        with pytest.raises(exc):
+            guard.run(lambda: 1)
+    ctx.code = 125
+    with pytest.raises(PeerFailure) as e:
+        guard.run(lambda: 1)
+    assert e.value.ranks == [4]

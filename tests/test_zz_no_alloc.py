@@ -78,9 +78,15 @@ def test_noalloc_matches_regular_entry_point_twice(case):
     for it in range(2):                            # two calls in a row reuse the same built-in scratch
         q = _bf(len(ctxs), H, dqk, scale=0.3)
         out = torch.full((len(ctxs), H, dvo), float("nan"), dtype=torch.bfloat16, device=dev)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(dev)[0]
+        reserved_before = torch.cuda.memory_reserved(dev)
         rc = _call(lib, q, kp, vp, bt, cl, w_uv, out, H, Hkv, dqk, dv, dvo, bs, splits, scale)
         assert rc == 0, (rc, lib.mmb_paged_attention_noalloc_error())
         torch.cuda.synchronize()
+        if it == 1:     # the first call may make the driver load the module's kernels; the second must not move a byte
+            assert torch.cuda.mem_get_info(dev)[0] >= free_before, "the entry point took device memory"
+        assert torch.cuda.memory_reserved(dev) == reserved_before, "the entry point went through torch's allocator"
         o_reg = ops.paged_attention(q, kp_arg, vp, bt, cl, Hq=H, Hkv=Hkv, dqk=dqk, dv=dv, block_size=bs, scale=scale,
                                     splits=splits, w_uv=w_uv)
         with ops.force_reference():
