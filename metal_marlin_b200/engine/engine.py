@@ -104,20 +104,12 @@ class _DecodeBucket:
                    rep_penalty=self.f[3], seed_dev=self.seeds, offset_dev=self.step_no, out=self.out)
         self.step_no += 1
 
-    def upload(self, group=None, src: int = 0, leader: bool = True) -> None:
-        """Stage this step's inputs on the device: one copy from pinned memory on the leader; with a process group the
-        packed device buffer is then broadcast so that every tensor-parallel rank replays the same batch."""
-        if leader:
-            self.d_buf.copy_(self.h_buf, non_blocking=True)
-            if self.hist_dirty:
-                self.hist.copy_(self.h_hist, non_blocking=True)
-        if group is not None:
-            import torch.distributed as dist
-            dist.broadcast(self.d_buf, src=src, group=group)
-            flag = torch.tensor([1 if self.hist_dirty else 0], device=self.dev)
-            dist.broadcast(flag, src=src, group=group)
-            if int(flag.item()):
-                dist.broadcast(self.hist, src=src, group=group)
+    def upload(self) -> None:
+        """Stage this step's inputs on the device: one copy of the packed buffer (+ the token history when a row uses a
+        repetition penalty)."""
+        self.d_buf.copy_(self.h_buf, non_blocking=True)
+        if self.hist_dirty:
+            self.hist.copy_(self.h_hist, non_blocking=True)
         self.hist_dirty = False
 
     def execute(self) -> torch.Tensor:
@@ -154,9 +146,15 @@ class _DecodeBucket:
 
 
 class LLMEngine:
-    def __init__(self, model: Transformer, config: Optional[EngineConfig] = None):
+    def __init__(self, model: Transformer, config: Optional[EngineConfig] = None, coordinator=None):
+        """``coordinator`` (``engine/distributed.py``): set on the leading rank of a tensor-parallel group; it tells the
+        other ranks which batch to run before this rank launches it, so all shards execute the same passes in step."""
         self.model = model
         self.cfg = config or EngineConfig()
+        self.coordinator = coordinator
+        self.lockstep = None         # set by an expert-parallel group: passes are agreed between the ranks (engine/distributed.py)
+        self._tracked: Dict[str, RunningRequest] = {}
+        self._filler_block: Optional[int] = None
         c = self.cfg
         self.kv = PagedKVStorage(model.cfg, c.num_kv_blocks, c.block_size, model.device, kv_dtype=c.kv_cache_dtype)
         self.cache = PagedKVCache(c.num_kv_blocks, c.block_size, enable_prefix_cache=c.enable_prefix_cache,
@@ -189,8 +187,27 @@ class LLMEngine:
             req.timeout_s = self.cfg.request_timeout_s
         with self._lock:
             rr = self.scheduler.add_request(req)
+            if self.lockstep is not None:
+                self._tracked[rr.id] = rr
         self._wake.set()
         return rr
+
+    def tracked(self) -> List[RunningRequest]:
+        """Requests added since they were last untracked (an expert-parallel group reports their progress to the leader)."""
+        return list(self._tracked.values())
+
+    def untrack(self, request_id: str) -> None:
+        self._tracked.pop(request_id, None)
+
+    def fail_running(self, reason: str) -> None:
+        """Fail every in-flight request (after a step raised) so the engine can carry on with new ones."""
+        self.last_error = reason
+        with self._lock:
+            for rr in list(self.scheduler.running):
+                rr.error = reason
+                self.scheduler.running.remove(rr)
+                self.cache.release(rr.id)
+                rr.transition(RequestStatus.FAILED)
 
     def abort(self, request_id: str) -> bool:
         with self._lock:
@@ -204,13 +221,19 @@ class LLMEngine:
         """One engine iteration.  Returns the requests that finished in it."""
         with self._lock:
             out = self.scheduler.schedule()
-            if out.is_empty:
+            do_prefill, do_decode = bool(out.prefill), bool(out.decode)
+            if self.lockstep is not None:
+                # expert-parallel group: a pass runs on every rank if any rank needs it (a rank without work runs a filler)
+                do_prefill, do_decode, _ = self.lockstep.agree(do_prefill, do_decode)
+            elif out.is_empty:
                 return []
             sampled: Dict[str, int] = {}
-            if out.prefill:
-                sampled.update(self._run_prefill(out))
-            if out.decode:
-                sampled.update(self._run_decode(out.decode))
+            if do_prefill:
+                sampled.update(self._run_prefill(out) if out.prefill else self._filler_prefill())
+            if do_decode:
+                sampled.update(self._run_decode(out.decode) if out.decode else self._filler_decode())
+            if out.is_empty:
+                return []
             finished = self.scheduler.step(out, sampled)
             self.iterations += 1
             self.tokens_generated += len(sampled)
@@ -257,18 +280,11 @@ class LLMEngine:
             try:
                 self.step()
             except Exception as e:      # fail every in-flight request rather than wedging the server
-                self.last_error = repr(e)
-                with self._lock:
-                    for rr in list(self.scheduler.running):
-                        rr.error = repr(e)
-                        self.scheduler.running.remove(rr)
-                        self.cache.release(rr.id)
-                        rr.transition(RequestStatus.FAILED)
+                self.fail_running(repr(e))
 
     # ------------------------------------------------------------------ model execution
-    def _run_prefill(self, out: SchedulerOutput) -> Dict[str, int]:
-        dev = self.model.device
-        bs = self.cfg.block_size
+    def _prefill_arrays(self, out: SchedulerOutput) -> Dict[str, list]:
+        """Host description of a flattened prompt pass (token ids, positions, cache slots, block tables)."""
         ids: List[int] = []
         pos: List[int] = []
         slots: List[int] = []
@@ -277,20 +293,33 @@ class LLMEngine:
         tables = []
         for ch in out.prefill:
             rr = ch.request
-            toks = rr.all_ids[ch.start:ch.start + ch.length]
-            ids.extend(toks)
+            ids.extend(rr.all_ids[ch.start:ch.start + ch.length])
             pos.extend(range(ch.start, ch.start + ch.length))
             slots.extend(self.cache.table.slot_mapping(rr.id, ch.start, ch.length))
             cu.append(cu[-1] + ch.length)
             ctx.append(ch.start + ch.length)
             tables.append(self.cache.table.block_table(rr.id))
         width = max(len(t) for t in tables)
-        bt = torch.tensor([t + [0] * (width - len(t)) for t in tables], dtype=torch.int32, device=dev)
-        meta = BatchMeta(positions=torch.tensor(pos, dtype=torch.int32, device=dev),
-                         slots=torch.tensor(slots, dtype=torch.int64, device=dev), block_tables=bt,
-                         ctx_lens=torch.tensor(ctx, dtype=torch.int32, device=dev), decode=False, cu_seqlens=cu,
-                         ctx_lens_host=ctx)
-        logits = self.model.forward(torch.tensor(ids, dtype=torch.int64, device=dev), self.kv, meta, last_only=True)
+        return {"ids": ids, "pos": pos, "slots": slots, "cu": cu, "ctx": ctx,
+                "tables": [t + [0] * (width - len(t)) for t in tables]}
+
+    def _exec_prefill(self, a: Dict[str, list]) -> torch.Tensor:
+        """Runs the prompt pass described by ``a`` on this rank's model shard; returns the full-vocabulary logits of the
+        last token of every chunk.  Every rank of a tensor-parallel group runs this with the same arrays."""
+        dev = self.model.device
+        meta = BatchMeta(positions=torch.tensor(a["pos"], dtype=torch.int32, device=dev),
+                         slots=torch.tensor(a["slots"], dtype=torch.int64, device=dev),
+                         block_tables=torch.tensor(a["tables"], dtype=torch.int32, device=dev),
+                         ctx_lens=torch.tensor(a["ctx"], dtype=torch.int32, device=dev), decode=False, cu_seqlens=list(a["cu"]),
+                         ctx_lens_host=list(a["ctx"]))
+        logits = self.model.forward(torch.tensor(a["ids"], dtype=torch.int64, device=dev), self.kv, meta, last_only=True)
+        return self.model.full_logits(logits)
+
+    def _run_prefill(self, out: SchedulerOutput) -> Dict[str, int]:
+        arrays = self._prefill_arrays(out)
+        if self.coordinator is not None:
+            self.coordinator.announce_prefill(arrays)
+        logits = self._exec_prefill(arrays)
         # sample a first token only for requests whose prefill completes now and that have no output yet
         rows, reqs = [], []
         for j, ch in enumerate(out.prefill):
@@ -301,8 +330,7 @@ class LLMEngine:
         if not rows:
             self._check_device_status()
             return {}
-        lg = self.model.full_logits(logits)[rows].contiguous()
-        toks = self._sample(lg, reqs)
+        toks = self._sample(logits[rows].contiguous(), reqs)
         self._check_device_status()
         return {rr.id: int(t) for rr, t in zip(reqs, toks)}
 
@@ -368,7 +396,38 @@ class LLMEngine:
         out = self._execute_decode(bk)
         return {rr.id: int(out[i]) for i, rr in enumerate(reqs)}
 
+    # ------------------------------------------------------------------ filler passes (lockstep groups)
+    def _filler_slot(self) -> int:
+        """First slot of a cache block reserved for passes that exist only to keep an expert-parallel group in step."""
+        if self._filler_block is None:
+            self._filler_block = self.cache.alloc.allocate()
+        return self._filler_block * self.cfg.block_size
+
+    def _filler_prefill(self) -> Dict[str, int]:
+        slot = self._filler_slot()
+        self._exec_prefill({"ids": [0], "pos": [0], "slots": [slot], "cu": [0, 1], "ctx": [1], "tables": [[self._filler_block]]})
+        self._check_device_status()
+        return {}
+
+    def _filler_decode(self) -> Dict[str, int]:
+        bk = self._bucket(1)
+        slot = self._filler_slot()
+        bk.h_ids.zero_()
+        bk.h_pos.zero_()
+        bk.h_ctx.fill_(1)
+        bk.h_slots.fill_(slot)
+        bk.h_bt.zero_()
+        bk.h_bt[:, 0] = self._filler_block
+        bk.h_f.zero_()
+        bk.h_f[1].fill_(1.0)
+        bk.h_f[3].fill_(1.0)
+        bk.h_topk.zero_()
+        bk.run()
+        return {}
+
     def _execute_decode(self, bk: _DecodeBucket) -> torch.Tensor:
+        if self.coordinator is not None:
+            self.coordinator.announce_decode(bk)
         return bk.run()
 
     def _check_device_status(self) -> None:

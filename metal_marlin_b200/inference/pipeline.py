@@ -57,29 +57,67 @@ class _IncrementalDecoder:
 
 class MMFP4Pipeline:
     def __init__(self, model: MMFP4ForCausalLM, tokenizer, engine_config: Optional[EngineConfig] = None,
-                 result_cache_size: int = 64):
+                 result_cache_size: int = 64, parallel=None):
+        """``parallel``: an ``engine.distributed.ParallelConfig`` (or a dict ``{"tp": .., "ep": .., "dp": ..}``) in a job
+        started with ``torchrun``: the model is sharded over the ranks, rank 0 drives generation through the same calls
+        as on one GPU and every other rank calls :meth:`serve_forever`."""
         self.model, self.tokenizer = model, tokenizer
         self.config: ModelConfig = model.config
         self.device = model.device
         ec = engine_config or EngineConfig(max_model_len=min(self.config.max_position_embeddings, 8192))
-        self.engine = LLMEngine(model.model, ec)
+        self.parallel = None
+        if parallel is not None and not (isinstance(parallel, dict) and not any(v and v > 1 for v in parallel.values())):
+            from ..engine.distributed import ParallelConfig, build_engine, init_process_group
+            rank, world, dev, ctrl = init_process_group(torch.device(self.device))
+            pc = parallel if isinstance(parallel, ParallelConfig) else ParallelConfig.parse(world=world, **parallel)
+            self.parallel = pc
+            self.rank, self.world = rank, world
+            if pc.mode in ("single", "dp"):
+                self.engine = LLMEngine(model.model, ec)
+            else:
+                self.engine = build_engine(model.model, ec, pc, rank, world, dev, ctrl)
+                model.model = self.engine.model          # the rank's shard; the whole model is released
+        else:
+            self.engine = LLMEngine(model.model, ec)
         self._results: "OrderedDict[tuple, str]" = OrderedDict()
         self._result_cache_size = result_cache_size
         self.speculative = None
         self.stats = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0}
 
     # ------------------------------------------------------------------ construction
+    @staticmethod
+    def _parallel_args(tp, ep, dp, device):
+        """(parallel dict or None, device): in a multi-rank job every rank loads onto its own GPU."""
+        import os
+        if max(tp, ep, dp) <= 1:
+            return None, device
+        if device is None and torch.cuda.is_available():
+            device = f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
+        return {"tp": tp, "ep": ep, "dp": dp}, device
+
     @classmethod
     def from_pretrained(cls, path: str, device: Optional[str] = None, engine_config: Optional[EngineConfig] = None,
-                        **_ignored) -> "MMFP4Pipeline":
+                        tp: int = 1, ep: int = 1, dp: int = 1, **_ignored) -> "MMFP4Pipeline":
+        par, device = cls._parallel_args(tp, ep, dp, device)
         lm = MMFP4ForCausalLM.from_pretrained(path, device)
-        return cls(lm, load_tokenizer(path, lm.config.vocab_size), engine_config)
+        return cls(lm, load_tokenizer(path, lm.config.vocab_size), engine_config, parallel=par)
 
     @classmethod
     def from_config(cls, cfg, device: Optional[str] = None, seed: int = 0,
-                    engine_config: Optional[EngineConfig] = None) -> "MMFP4Pipeline":
+                    engine_config: Optional[EngineConfig] = None, tp: int = 1, ep: int = 1, dp: int = 1) -> "MMFP4Pipeline":
+        par, device = cls._parallel_args(tp, ep, dp, device)
         lm = MMFP4ForCausalLM.from_config(cfg, device, seed)
-        return cls(lm, load_tokenizer(None, lm.config.vocab_size), engine_config)
+        return cls(lm, load_tokenizer(None, lm.config.vocab_size), engine_config, parallel=par)
+
+    @property
+    def is_leader(self) -> bool:
+        """False on the ranks of a multi-GPU job that only execute what rank 0 schedules."""
+        return getattr(self.engine, "is_leader", True)
+
+    def serve_forever(self) -> None:
+        """Ranks other than 0 of a tensor- / expert-parallel job: run the leader's batches until it closes the pipeline."""
+        if hasattr(self.engine, "serve_forever"):
+            self.engine.serve_forever()
 
     # ------------------------------------------------------------------ helpers
     @property

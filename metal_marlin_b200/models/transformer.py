@@ -96,6 +96,10 @@ class LayerWeights:
     router_bias: Optional[torch.Tensor] = None
     gate_up_bank: Optional[FP4ExpertBank] = None
     down_bank: Optional[FP4ExpertBank] = None
+    # expert parallelism inside a tensor-parallel group: this rank's range of whole routed experts (0 = experts are width-sliced)
+    ep_first: int = 0
+    ep_local: int = 0
+    ep_shared_local: int = 0
 
 
 def absorb_kv_b(kv_b: FP4Weight, H: int, dn: int, dv: int, R: int, hadamard_block: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -203,6 +207,7 @@ class Transformer:
         self.mtp = None      # optional multi-token-prediction head (spec/mtp.py)
         # tensor parallelism (parallel/tp.py): a shard keeps only its local heads / vocabulary rows
         self.tp = None
+        self.ep = None       # expert parallelism with replicated attention (parallel/ep.py::EPModelState)
         self.routing_hook = None     # optional callable(layer, expert_ids, router_probs)
         self.n_heads_local = cfg.num_attention_heads
         self.n_kv_heads_local = cfg.num_key_value_heads
@@ -456,6 +461,9 @@ class Transformer:
         if self.tp is not None:
             return new_h, self.tp.moe_row_parallel(new_h, {"norm_w": L.post_norm, "eps": cfg.rms_norm_eps}, L, ids, wts, cfg,
                                                    2 * li + 1)
+        if self.ep is not None:
+            # every rank holds different tokens: rows travel to the ranks that own their experts and come back
+            return new_h, self.ep.forward(li, new_h, ids, wts, norm_w=L.post_norm, eps=cfg.rms_norm_eps)
         out = ops.moe_forward(new_h, L.gate_up_bank, L.down_bank, ids, wts, n_shared=cfg.n_shared_experts,
                               shared_base=cfg.num_experts, norm_w=L.post_norm, eps=cfg.rms_norm_eps)
         return new_h, out

@@ -243,3 +243,75 @@ class EPExchange:
         bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(ep)]
         ptrs = [b.data_ptr() for b in bufs]
         return [cls(r, ep, hidden, max_tokens, topk, bufs[r], ptrs) for r in range(ep)]
+
+
+class EPModelState:
+    """Expert parallelism of a whole model whose attention and dense layers are replicated (every rank serves its own
+    sequences): per MoE layer the rank's routed experts (:class:`ExpertParallelMoE`) plus a local copy of the shared
+    experts, and one :class:`EPExchange` that all layers use in turn.
+
+    ``mode``: ``"fused"`` - dispatch, expert GEMMs and combine inside this library's kernels over peer memory;
+    ``"nccl"`` - the all-to-all baseline (:meth:`ExpertParallelMoE.forward_dispatch`)."""
+
+    def __init__(self, rank: int, ep: int, exchange: Optional[EPExchange], group=None, mode: str = "fused"):
+        self.rank, self.ep, self.exchange, self.group, self.mode = rank, ep, exchange, group, mode
+        self.layers: Dict[int, ExpertParallelMoE] = {}
+        self.shared: Dict[int, Tuple[FP4ExpertBank, FP4ExpertBank]] = {}
+        self.n_shared = 0
+
+    def add_layer(self, li: int, gate_up: FP4ExpertBank, down: FP4ExpertBank, num_routed: int, n_shared: int) -> None:
+        moe = ExpertParallelMoE(gate_up, down, num_routed, 0, self.rank, self.ep, self.group)
+        self.layers[li] = moe
+        self.n_shared = n_shared
+        if n_shared:
+            sel = torch.arange(num_routed, num_routed + n_shared, device=gate_up.qtile.device)
+            pick = lambda b: FP4ExpertBank(b.qtile.index_select(0, sel).contiguous(), b.stile.index_select(0, sel).contiguous(),
+                                           b.out_features, b.in_features, b.group_size)
+            self.shared[li] = (pick(gate_up), pick(down))
+
+    def max_tokens(self) -> int:
+        return self.exchange.cap // max(1, self._topk) if self.exchange is not None else 1 << 30
+
+    _topk = 1
+
+    def forward(self, li: int, x, ids, weights, *, norm_w=None, eps=1e-6):
+        """MoE output for this rank's tokens ``x [T, H]`` (un-normalised residual stream; ``norm_w`` is applied first)."""
+        moe = self.layers[li]
+        add0 = None
+        if li in self.shared:
+            gu, dn = self.shared[li]
+            xin = ops.rmsnorm(x, norm_w, eps) if norm_w is not None else x
+            add0 = ops._shared_experts(xin, gu, dn, self.n_shared, 0)
+        if self.mode == "fused" and self.exchange is not None and x.is_cuda:
+            return moe.forward_fused(self.exchange, x, ids, weights, norm_w=norm_w, eps=eps, add0=add0)
+        out = moe.forward_dispatch(x, ids, weights, norm_w=norm_w, eps=eps)
+        return out if add0 is None else (out.to(torch.float32) + add0.to(torch.float32)).to(out.dtype)
+
+    def check(self) -> int:
+        return self.exchange.check() if self.exchange is not None else 0
+
+
+def shard_transformer_ep(model, rank: int, ep: int, max_tokens: int, group=None, mode: str = "fused"):
+    """The rank's expert-parallel copy of ``model``: attention, dense MLPs, router and shared experts stay whole, the
+    routed experts of every MoE layer are cut to this rank's range, and the model's MoE layers exchange tokens through one
+    :class:`EPExchange` (``max_tokens`` = most tokens a rank brings to one forward pass)."""
+    import copy
+    from ..models.transformer import Transformer
+    cfg = model.cfg
+    dev = model.device
+    ex = None
+    if mode == "fused" and dev.type == "cuda" and ep > 1:
+        ex = EPExchange.create(cfg.hidden_size, max_tokens, cfg.num_experts_per_tok, dev, group)
+    st = EPModelState(rank, ep, ex, group, mode)
+    st._topk = cfg.num_experts_per_tok
+    layers = []
+    for li, L in enumerate(model.layers):
+        S = copy.copy(L)
+        if L.router_w is not None:
+            st.add_layer(li, L.gate_up_bank, L.down_bank, cfg.num_experts, cfg.n_shared_experts)
+            S.gate_up_bank = S.down_bank = None      # only the rank's experts stay resident (inside ``st``)
+        layers.append(S)
+    m = Transformer(cfg, layers, model.embed, model.final_norm, model.lm_head)
+    m.ep = st
+    m.mtp = model.mtp
+    return m

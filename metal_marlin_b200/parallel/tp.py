@@ -271,14 +271,19 @@ class TPContext:
 
     def moe_row_parallel(self, h, x_normed_args, L, ids, wts, cfg, site: int):
         T = ids.shape[0]
+        n_shared, shared_base = cfg.n_shared_experts, cfg.num_experts
+        if getattr(L, "ep_local", 0):
+            # whole experts per rank: experts of other ranks become id -1, which the kernels skip; the partial outputs
+            # of the ranks add up to the full MoE output exactly like the slices of a width-sharded expert
+            from .ep import localize_ids
+            ids = localize_ids(ids, L.ep_first, L.ep_local)
+            n_shared, shared_base = L.ep_shared_local, L.ep_local
         if self.use_fused(T):
-            hmid = ops.moe_gate_up(h, L.gate_up_bank, ids, n_shared=cfg.n_shared_experts, shared_base=cfg.num_experts,
-                                   **x_normed_args)
-            ops.moe_down(hmid, L.down_bank, ids, wts, n_shared=cfg.n_shared_experts, shared_base=cfg.num_experts,
+            hmid = ops.moe_gate_up(h, L.gate_up_bank, ids, n_shared=n_shared, shared_base=shared_base, **x_normed_args)
+            ops.moe_down(hmid, L.down_bank, ids, wts, n_shared=n_shared, shared_base=shared_base,
                          tpx=self._desc("out", site, T), out=self._dummy(T, L.down_bank.out_features))
             return TPPartial(site, T)
-        y = ops.moe_forward(h, L.gate_up_bank, L.down_bank, ids, wts, n_shared=cfg.n_shared_experts,
-                            shared_base=cfg.num_experts, **x_normed_args)
+        y = ops.moe_forward(h, L.gate_up_bank, L.down_bank, ids, wts, n_shared=n_shared, shared_base=shared_base, **x_normed_args)
         return self.all_reduce(y)
 
     def _dummy(self, m: int, n: int) -> torch.Tensor:
@@ -328,8 +333,9 @@ class TPContext:
 # ---------------------------------------------------------------------------------------------
 # sharding
 # ---------------------------------------------------------------------------------------------
-def shard_layer(cfg, L: LayerWeights, rank: int, tp: int) -> Tuple[LayerWeights, dict]:
-    """Returns the rank's shard of one layer and its local dimensions."""
+def shard_layer(cfg, L: LayerWeights, rank: int, tp: int, expert_parallel: bool = False) -> Tuple[LayerWeights, dict]:
+    """Returns the rank's shard of one layer and its local dimensions.  ``expert_parallel``: the routed experts are not
+    sliced; the rank keeps its range of whole experts (and rank 0 the shared experts), see ``parallel/ep.py``."""
     S = copy.copy(L)
     info = {}
     if cfg.is_mla:
@@ -370,7 +376,13 @@ def shard_layer(cfg, L: LayerWeights, rank: int, tp: int) -> Tuple[LayerWeights,
                                     b[(Hq + Hk + k0) * D:(Hq + Hk + k0 + kv_per) * D]]).contiguous()
         S.o = L.o.slice_cols(q0 * D, q1 * D)
         assert g >= 1
-    if L.gate_up_bank is not None:
+    if L.gate_up_bank is not None and expert_parallel:
+        from .ep import shard_bank
+        S.gate_up_bank, first, n_local, n_sh = shard_bank(L.gate_up_bank, cfg.num_experts, cfg.n_shared_experts, rank, tp)
+        S.down_bank = shard_bank(L.down_bank, cfg.num_experts, cfg.n_shared_experts, rank, tp)[0]
+        S.ep_first, S.ep_local, S.ep_shared_local = first, n_local, n_sh
+        info["moe_inter"] = L.gate_up_bank.out_features // 2
+    elif L.gate_up_bank is not None:
         I = L.gate_up_bank.out_features // 2
         unit = max(64, L.down_bank.group_size)
         i0, i1 = even_split(I, tp, unit)[rank]
@@ -388,12 +400,13 @@ def shard_layer(cfg, L: LayerWeights, rank: int, tp: int) -> Tuple[LayerWeights,
     return S, info
 
 
-def shard_transformer(model: Transformer, rank: int, tp: int, ctx: Optional[TPContext] = None) -> Transformer:
+def shard_transformer(model: Transformer, rank: int, tp: int, ctx: Optional[TPContext] = None,
+                      expert_parallel: bool = False) -> Transformer:
     """Build the rank's tensor-parallel shard of ``model`` (weights are sliced, not re-quantized)."""
     cfg = model.cfg
     layers, infos = [], []
     for L in model.layers:
-        S, info = shard_layer(cfg, L, rank, tp)
+        S, info = shard_layer(cfg, L, rank, tp, expert_parallel)
         layers.append(S)
         infos.append(info)
     v0, v1 = even_split(cfg.vocab_size, tp)[rank]

@@ -41,6 +41,10 @@ class EngineConfig:
     preset: Optional[str] = None          # serve a random-init architecture preset (no checkpoint)
     speculative: Optional[str] = None     # "ngram" | "mtp" | path of a draft checkpoint
     num_speculative_tokens: int = 4
+    # multi-GPU (job started with torchrun, one process per GPU): tensor / expert / data parallel degrees
+    tp: int = 1
+    ep: int = 1
+    dp: int = 1
 
 
 def detect_model_format(path: str) -> str:
@@ -77,19 +81,22 @@ class ServingEngine:
                                 max_model_len=config.max_model_len, max_num_seqs=config.max_batch_size,
                                 request_timeout_s=config.request_timeout)
         from ..inference.pipeline import MMFP4Pipeline
+        par = dict(tp=config.tp, ep=config.ep, dp=1)        # data-parallel replicas are whole servers behind serving/router.py
         if self.mock:
             self.model_name = config.model_name or os.environ.get("METAL_MARLIN_MOCK_MODEL_NAME", "mock-model")
             self.pipeline = MMFP4Pipeline.from_config("tiny-llama", device="cpu", engine_config=core)
         elif config.preset:
             self.model_name = config.model_name or config.preset
-            self.pipeline = MMFP4Pipeline.from_config(config.preset, device=config.device, engine_config=core)
+            self.pipeline = MMFP4Pipeline.from_config(config.preset, device=config.device, engine_config=core, **par)
         elif self.model_format == "trellis":
             from ..trellis.lm import TrellisPipeline
             self.model_name = config.model_name or os.path.basename(os.path.normpath(config.model_path))
             self.pipeline = TrellisPipeline.from_pretrained(config.model_path, device=config.device, engine_config=core)
         else:
             self.model_name = config.model_name or os.path.basename(os.path.normpath(config.model_path))
-            self.pipeline = MMFP4Pipeline.from_pretrained(config.model_path, device=config.device, engine_config=core)
+            self.pipeline = MMFP4Pipeline.from_pretrained(config.model_path, device=config.device, engine_config=core, **par)
+        if not self.pipeline.is_leader:
+            return                      # this rank only executes the leader's batches (see run_server)
         if config.speculative:
             self.pipeline.enable_speculative_decoding(config.speculative, config.num_speculative_tokens)
         self.pipeline.engine.start()

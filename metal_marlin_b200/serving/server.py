@@ -133,8 +133,27 @@ async def metrics():
 
 def run_server(config: EngineConfig, host: str = "127.0.0.1", port: int = 8000, metrics_port: Optional[int] = None,
                log_level: str = "info") -> None:
+    import os
+
     import uvicorn
-    configure(config)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if config.dp > 1 and config.tp == 1 and config.ep == 1:
+        # data parallel: every rank is a whole replica with its own server on port + 1 + rank; rank 0 also runs the router
+        if world != config.dp:
+            raise ValueError(f"--dp {config.dp} needs {config.dp} processes (torchrun), the job has {world}")
+        if config.device is None:
+            config.device = f"cuda:{os.environ.get('LOCAL_RANK', '0')}"
+        if rank == 0:
+            from .router import run_router
+            backends = [f"http://{host}:{port + 1 + r}" for r in range(world)]
+            threading.Thread(target=lambda: run_router(backends, host=host, port=port, log_level="warning"), daemon=True).start()
+        port = port + 1 + rank
+    eng = configure(config)
+    if not eng.pipeline.is_leader:
+        try:
+            eng.pipeline.serve_forever()         # tensor / expert parallel: execute what rank 0 schedules
+        finally:
+            return
     if metrics_port:
         mapp = FastAPI()
         mapp.get("/metrics")(metrics)
