@@ -234,8 +234,6 @@ def main():
         state["ctx"] = make_context(cfg, dev, mode="fused")
         state["model"] = shard_transformer(lm.model, rank, world, state["ctx"])
         state["tp"] = True
-        lm.model.layers = []
-        torch.cuda.empty_cache()
 
     if headline_tp:
         to_tensor_parallel()
@@ -244,12 +242,14 @@ def main():
         from metal_marlin_b200.baseline_eager import EagerBF16Model
         eager_model = EagerBF16Model(lm.model)
 
-    def run_config(batch: int, steps: int, warmup: int, e2e: bool):
+    def run_config(batch: int, steps: int, warmup: int, e2e: bool, graph: bool = True, same_batch=None):
         total_len = args.prompt_len + warmup + steps * (2 if e2e else 1) + 8
         nb = (total_len + block_size - 1) // block_size
         kv = lm.new_cache(batch * nb, block_size, kv_dtype=args.kv_dtype)
         use_tp, run_model = state["tp"], state["model"]
-        g = torch.Generator().manual_seed(args.seed + (0 if use_tp else rank))     # tensor-parallel ranks share the batch
+        if same_batch is None:
+            same_batch = use_tp
+        g = torch.Generator().manual_seed(args.seed + (0 if same_batch else rank))     # tensor-parallel ranks share the batch
         prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(batch)]
         bt = torch.arange(batch * nb, dtype=torch.int32).view(batch, nb)
         # one untimed prefill of the first sequence: one-time library / attribute initialisation is not time-to-first-token
@@ -269,14 +269,15 @@ def main():
         torch.cuda.synchronize(dev)
         ttft_ms = ev0.elapsed_time(ev1)
         model = eager_model if eager else run_model
-        sess = DecodeSession(model, kv, batch, nb, max_new_tokens=0, max_ctx=total_len, use_graph=not (eager or args.no_graph))
+        no_graph = eager or args.no_graph or not graph
+        sess = DecodeSession(model, kv, batch, nb, max_new_tokens=0, max_ctx=total_len, use_graph=not no_graph)
         sess.set_sampling([SamplingParams()] * batch)
         first = run_model.greedy(logits) if not eager else logits.argmax(-1)
         sess.set_state(first, [args.prompt_len] * batch, bt)
         l0 = ops.launch_count()
-        sess._step_body() if (eager or args.no_graph) else sess.capture()
-        launches_per_step = (ops.launch_count() - l0) // (1 if (eager or args.no_graph) else 3)
-        if eager or args.no_graph:
+        sess._step_body() if no_graph else sess.capture()
+        launches_per_step = (ops.launch_count() - l0) // (1 if no_graph else 3)
+        if no_graph:
             sess.set_state(first, [args.prompt_len] * batch, bt)
         for _ in range(warmup):
             sess.step()
@@ -345,15 +346,43 @@ def main():
     }
     if use_tp:
         out["config"]["exchange_status"] = state["ctx"].check()
-    if args.extra:
+    n_half, w_half = max(8, args.steps // 2), max(3, args.warmup // 2)
+    if args.extra or world > 1 or args.batch == 1:
+        # batch 32 per replica (decode throughput regime) and its time to first token
         try:
-            r32 = run_config(32, max(8, args.steps // 2), max(3, args.warmup // 2), e2e=False)
+            r32 = run_config(32, n_half, w_half, e2e=False)
             out["extra"] = {"bs32_tok_s": round((1 if state["tp"] else world) * 32 * 1e3 / r32["ms_per_step"], 1),
                             "bs32_ms_per_step": round(r32["ms_per_step"], 4), "bs32_ttft_ms": round(r32["ttft_ms"], 1),
                             "bs32_launches_per_step": r32["launches_per_step"]}
         except Exception as e:      # the headline line must still be printed
             out["extra"] = {"error": repr(e)[:300]}
-    if also_tp:
+    failed_section = False
+    if world > 1 and args.parallelism == "auto" and not eager and cfg.is_moe:
+        # expert parallel with data-parallel attention: every rank serves its own sequences, the MoE layers exchange token
+        # rows with the expert owners - inside this library's kernels over NVLink ("fused"), or through NCCL all-to-all
+        try:
+            from metal_marlin_b200.parallel.ep import shard_transformer_ep
+            ep_out = {"parallelism": f"ep{world} (attention data parallel, experts sharded)", "global_batch": 32 * world,
+                      "prompt_tokens_per_rank": 32 * args.prompt_len}
+            saved = dict(state)
+            for arm in ("fused", "nccl"):
+                state["model"] = shard_transformer_ep(lm.model, rank, world, 8192, mode=arm)
+                state["model"].ep.uniform = True      # every rank brings the same number of tokens to every pass
+                state["tp"] = False
+                re = run_config(32, n_half, w_half, e2e=False, graph=(arm == "fused"), same_batch=False)
+                ep_out[arm] = {"bs32_per_rank_tok_s": round(world * 32 * 1e3 / re["ms_per_step"], 1),
+                               "ms_per_step": round(re["ms_per_step"], 4),
+                               "prefill_tok_s": round(world * 32 * args.prompt_len * 1e3 / re["ttft_ms"], 1),
+                               "prefill_ms": round(re["ttft_ms"], 1), "launches_per_step": re["launches_per_step"],
+                               "exchange_status": state["model"].ep.check()}
+                state["model"] = None
+                torch.cuda.empty_cache()
+            state.update(saved)
+            out["ep"] = ep_out
+        except Exception as e:
+            out["ep"] = {"error": repr(e)[:300]}
+            failed_section = True
+    if also_tp and not failed_section:
         # latency mode on the same GPUs: one stream, every matrix split over the ranks
         try:
             to_tensor_parallel()
@@ -361,14 +390,18 @@ def main():
             out["tp"] = {"parallelism": f"tp{world} (in-kernel NVLink exchange)", "global_batch": args.batch,
                          "ms_per_step": round(rt["ms_per_step"], 4), "tok_s": round(args.batch * 1e3 / rt["ms_per_step"], 2),
                          "ttft_ms": round(rt["ttft_ms"], 2),      # prompt split over the ranks: GEMM -> reduce-scatter -> gather -> GEMM in-kernel
-                         "launches_per_step": rt["launches_per_step"], "exchange_status": state["ctx"].check(), "multimem": bool(getattr(state["ctx"], "use_multimem", False)),
+                         "launches_per_step": rt["launches_per_step"], "multimem": bool(getattr(state["ctx"], "use_multimem", False)),
                          "weights_gb_per_gpu": round(state["model"].weight_bytes() / 1e9, 2)}
+            rt32 = run_config(32, n_half, w_half, e2e=False)
+            out["tp"].update(bs32_tok_s=round(32 * 1e3 / rt32["ms_per_step"], 1), bs32_ms_per_step=round(rt32["ms_per_step"], 4),
+                             bs32_ttft_ms=round(rt32["ttft_ms"], 1), exchange_status=state["ctx"].check())
         except Exception as e:
-            out["tp"] = {"error": repr(e)[:300]}
+            out["tp"] = dict(out.get("tp") or {}, error=repr(e)[:300])
+            failed_section = True
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
-        if isinstance(out.get("tp"), dict) and "error" in out["tp"]:
+        if failed_section:
             # the ranks may have left the tensor-parallel section at different points: no further collective, no group teardown
             sys.stdout.flush()
             os._exit(0)

@@ -113,7 +113,8 @@ extern "C" {
 // MoE dispatch helpers (see moe_dispatch.cu).  ids int32 [n = T * topk]; order / inv int32 [n]; tile arrays int32 [max_tiles].
 int mmb_moe_group(const int* ids, int n, int E, int token_tile, int max_tiles, int* order, int* inv, int* tile_expert, int* tile_row0,
                   int* tile_rows, int* n_tiles, cudaStream_t stream);
-int mmb_moe_gather(const void* x, const int* order, void* xs, int n, int topk, int K, int ldx, cudaStream_t stream);
+// n_dev: optional device int; only the first min(n, *n_dev) rows are gathered (the rest of xs is left as it is)
+int mmb_moe_gather(const void* x, const int* order, void* xs, int n, int topk, int K, int ldx, const int* n_dev, cudaStream_t stream);
 int mmb_moe_combine(const void* y, const int* inv, const void* add0, const void* add1, void* out, int T, int topk, int N, cudaStream_t stream);
 #ifdef __cplusplus
 }
@@ -158,7 +159,8 @@ typedef struct {
   int* tile_expert;
   int* tile_row0;
   int* tile_rows;
-  int* n_tiles;
+  int* n_tiles;                    // [2]: tiles, rows received in all
+  int n_rows_max;                  // length of order / row_dst (0: ep * cap).  More rows than this: status 120, no tile is run
 } MmbEpRecvParams;
 int mmb_ep_recv_group(const MmbEpRecvParams* p, cudaStream_t stream);
 

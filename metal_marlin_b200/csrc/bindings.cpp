@@ -547,14 +547,21 @@ MmbAgWait ag_from(const Tensor& ag) {
   return a;
 }
 
-void fp4_gemm_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status, const Tensor* ag);
+void fp4_gemm_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status, const Tensor* ag,
+                   int act = 0);
 void fp4_gemm(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status) {
   fp4_gemm_impl(x, qw, sc, out, N, gs, status, nullptr);
 }
 void fp4_gemm_ag(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status, const Tensor& ag) {
   fp4_gemm_impl(x, qw, sc, out, N, gs, status, &ag);
 }
-void fp4_gemm_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status, const Tensor* ag) {
+// SwiGLU fused into the epilogue: W holds gate rows [0, N/2) and up rows [N/2, N); out is [M, N/2].
+void fp4_gemm_swiglu(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status) {
+  TORCH_CHECK(N % 128 == 0 && out.size(1) == N / 2, "fused SwiGLU needs N / 2 to be a multiple of 64 and out [M, N / 2]");
+  fp4_gemm_impl(x, qw, sc, out, N, gs, status, nullptr, 1);
+}
+void fp4_gemm_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs, Tensor status, const Tensor* ag,
+                   int act) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && qw.is_contiguous() && sc.is_contiguous());
@@ -573,6 +580,7 @@ void fp4_gemm_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor o
   p.gs_shift = log2i(gs);
   p.status = status.data_ptr<int>();
   if (ag != nullptr) p.ag = ag_from(*ag);
+  p.act = act;
   check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm");
 }
 
@@ -658,7 +666,14 @@ void tp_wait(const Tensor& desc) {
 // Grouped (MoE) GEMM: x rows are sorted by expert; the tile list lives on the device.
 static void fp4_gemm_grouped_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
                                   const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
-                                  int64_t token_tile, const OptT& row_scale, Tensor status, const Tensor* out_rows);
+                                  int64_t token_tile, const OptT& row_scale, Tensor status, const Tensor* out_rows, int act = 0);
+// Grouped GEMM with SwiGLU in the epilogue (gate | up row halves of every expert): out [rows, N / 2].
+void fp4_gemm_grouped_swiglu(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
+                             const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
+                             int64_t token_tile, Tensor status) {
+  TORCH_CHECK(N % 128 == 0 && out.size(1) == N / 2, "fused SwiGLU needs N / 2 to be a multiple of 64 and out [rows, N / 2]");
+  fp4_gemm_grouped_impl(x, qw, sc, out, N, gs, tile_expert, tile_row0, tile_rows, n_tiles, token_tile, c10::nullopt, status, nullptr, 1);
+}
 void fp4_gemm_grouped(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
                       const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
                       int64_t token_tile, const OptT& row_scale, Tensor status) {
@@ -674,7 +689,7 @@ void fp4_gemm_grouped_scatter(const Tensor& x, const Tensor& qw, const Tensor& s
 }
 static void fp4_gemm_grouped_impl(const Tensor& x, const Tensor& qw, const Tensor& sc, Tensor out, int64_t N, int64_t gs,
                                   const Tensor& tile_expert, const Tensor& tile_row0, const Tensor& tile_rows, const Tensor& n_tiles,
-                                  int64_t token_tile, const OptT& row_scale, Tensor status, const Tensor* out_rows) {
+                                  int64_t token_tile, const OptT& row_scale, Tensor status, const Tensor* out_rows, int act) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && qw.dim() == 5 && qw.is_contiguous() &&
@@ -707,6 +722,7 @@ static void fp4_gemm_grouped_impl(const Tensor& x, const Tensor& qw, const Tenso
     p.row_scale = row_scale->data_ptr<float>();
   }
   if (out_rows != nullptr) p.out_rows = reinterpret_cast<const long long*>(out_rows->data_ptr<int64_t>());
+  p.act = act;
   check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm_grouped");
 }
 
@@ -746,8 +762,8 @@ void ep_dispatch(const Tensor& x, const Tensor& ids, const Tensor& desc, int64_t
 void ep_recv_group(const Tensor& desc, int64_t ep, int64_t cap, int64_t H, int64_t E_local, int64_t token_tile, Tensor order, Tensor row_dst,
                    Tensor tile_expert, Tensor tile_row0, Tensor tile_rows, Tensor n_tiles) {
   TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kLong && desc.numel() == 6);
-  TORCH_CHECK(order.is_cuda() && order.scalar_type() == at::kInt && order.numel() == ep * cap && row_dst.scalar_type() == at::kLong &&
-              row_dst.numel() == ep * cap && order.is_contiguous() && row_dst.is_contiguous());
+  TORCH_CHECK(order.is_cuda() && order.scalar_type() == at::kInt && order.numel() <= ep * cap && row_dst.scalar_type() == at::kLong &&
+              row_dst.numel() == order.numel() && order.is_contiguous() && row_dst.is_contiguous() && n_tiles.numel() >= 2);
   TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_row0.scalar_type() == at::kInt && tile_rows.scalar_type() == at::kInt &&
               n_tiles.scalar_type() == at::kInt && tile_row0.numel() == tile_expert.numel() && tile_rows.numel() == tile_expert.numel());
   const int64_t* v = desc.data_ptr<int64_t>();
@@ -771,6 +787,7 @@ void ep_recv_group(const Tensor& desc, int64_t ep, int64_t cap, int64_t H, int64
   p.tile_row0 = tile_row0.data_ptr<int>();
   p.tile_rows = tile_rows.data_ptr<int>();
   p.n_tiles = n_tiles.data_ptr<int>();
+  p.n_rows_max = (int)order.numel();
   check(mmb_ep_recv_group(&p, cur_stream()), "ep_recv_group");
 }
 
@@ -1043,13 +1060,20 @@ void moe_group(const Tensor& ids, int64_t E, int64_t token_tile, Tensor order, T
         "moe_group");
 }
 
-void moe_gather(const Tensor& x, const Tensor& order, Tensor xs, int64_t topk) {
+void moe_gather_impl(const Tensor& x, const Tensor& order, Tensor xs, int64_t topk, const int* n_dev);
+void moe_gather(const Tensor& x, const Tensor& order, Tensor xs, int64_t topk) { moe_gather_impl(x, order, xs, topk, nullptr); }
+// Gathers only the first `n_rows[idx]` rows (a count that lives on the device, e.g. the rows an expert owner received).
+void moe_gather_n(const Tensor& x, const Tensor& order, Tensor xs, int64_t topk, const Tensor& n_rows, int64_t idx) {
+  TORCH_CHECK(n_rows.is_cuda() && n_rows.scalar_type() == at::kInt && idx >= 0 && idx < n_rows.numel());
+  moe_gather_impl(x, order, xs, topk, n_rows.data_ptr<int>() + idx);
+}
+void moe_gather_impl(const Tensor& x, const Tensor& order, Tensor xs, int64_t topk, const int* n_dev) {
   check_bf16(x, "x");
   check_bf16(xs, "xs");
   TORCH_CHECK(x.stride(1) == 1 && xs.is_contiguous() && order.scalar_type() == at::kInt && xs.size(0) == order.numel() && xs.size(1) <= x.size(1));
   c10::cuda::CUDAGuard guard(x.device());
   check(mmb_moe_gather(x.data_ptr(), order.data_ptr<int>(), xs.data_ptr(), (int)order.numel(), (int)topk, (int)xs.size(1), (int)x.stride(0),
-                       cur_stream()),
+                       n_dev, cur_stream()),
         "moe_gather");
 }
 
@@ -1124,6 +1148,8 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("argmax", &argmax);
   m.def("tp_argmax", &tp_argmax);
   m.def("fp4_gemm", &fp4_gemm);
+  m.def("fp4_gemm_swiglu", &fp4_gemm_swiglu);
+  m.def("fp4_gemm_grouped_swiglu", &fp4_gemm_grouped_swiglu);
   m.def("fp4_gemm_rs", &fp4_gemm_rs);
   m.def("tp_rs_finish", &tp_rs_finish);
   m.def("tp_rs_finish_norm", &tp_rs_finish_norm);
@@ -1144,6 +1170,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("ep_combine", &ep_combine);
   m.def("moe_group", &moe_group);
   m.def("moe_gather", &moe_gather);
+  m.def("moe_gather_n", &moe_gather_n);
   m.def("moe_combine", &moe_combine);
   m.def("prefill_attention", &prefill_attention);
   m.def("qk_norm_rope_cache_fp8", &qk_norm_rope_cache_fp8);

@@ -84,9 +84,10 @@ __global__ void __launch_bounds__(1024) ep_recv_group_kernel(MmbEpRecvParams p) 
   __shared__ int off[kEpMaxExperts + 1];
   __shared__ int tbase[kEpMaxExperts + 1];
   __shared__ int scnt[kEpMaxRanks];
+  __shared__ int s_fits;
   pdl_launch_dependents();
   pdl_wait();
-  const int tid = threadIdx.x, E = p.E_local, n = p.ep * p.cap;
+  const int tid = threadIdx.x, E = p.E_local, n = (p.n_rows_max > 0) ? min(p.n_rows_max, p.ep * p.cap) : p.ep * p.cap;
   if (tid < p.ep) {
     int c = 0;
     if (ep_wait_flag(p.flags + tid, *p.step)) c = min(max(__ldcg(p.recv_cnt + tid), 0), p.cap);
@@ -111,9 +112,26 @@ __global__ void __launch_bounds__(1024) ep_recv_group_kernel(MmbEpRecvParams p) 
     }
     off[E] = o;
     tbase[E] = t;
-    *p.n_tiles = min(t, p.max_tiles);
+    // the caller sized the row arrays for a bound on this pass; more rows than that: run nothing and report
+    s_fits = (o <= n) ? 1 : 0;
+    if (!s_fits && p.status) atomicExch(p.status, 120);
+    p.n_tiles[0] = s_fits ? min(t, p.max_tiles) : 0;
+    p.n_tiles[1] = s_fits ? o : 0;        // rows received in all: later kernels sweep these, not the worst-case capacity
   }
   __syncthreads();
+  if (!s_fits) {
+    // clear the tile list and the row tables: no row is scheduled
+    for (int ti = tid; ti < p.max_tiles; ti += 1024) {
+      p.tile_expert[ti] = 0;
+      p.tile_row0[ti] = 0;
+      p.tile_rows[ti] = 0;
+    }
+    for (int i = tid; i < n; i += 1024) {
+      p.order[i] = -1;
+      p.row_dst[i] = 0;
+    }
+    return;
+  }
   for (int e = tid; e < E; e += 1024) {
     const int nt = tbase[e + 1] - tbase[e];
     for (int j = 0; j < nt; ++j) {

@@ -207,8 +207,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       uint4 w0[kRB], w1[kRB];
 #pragma unroll
       for (int j = 0; j < kRB; ++j) {
-        const int rt = (n0 >> 4) + dw0 + j;
-        rt_ok[j] = rt < n_rt;
+        // act == 1 (fused SwiGLU): the CTA's 128 lanes are 64 gate rows (blocks 0..3) and the 64 up rows of the same
+        // output features (blocks 4..7), so both halves of a product meet in one accumulator tile
+        const int blk = dw0 + j;
+        const int rt = p.act ? (((blk & 4) ? (n_rt >> 1) : 0) + (int)blockIdx.x * 4 + (blk & 3)) : ((n0 >> 4) + blk);
+        rt_ok[j] = p.act ? ((int)blockIdx.x * 4 + (blk & 3) < (n_rt >> 1)) : (rt < n_rt);
         wsrc[j] = qw + ((long long)rt * KC) * 32 + lane;
         sc_row[j] = sc + (long long)rt * NG * 8 + g;
         st_row[j] = ((dw0 + j) * 16 + g) * 128;
@@ -300,6 +303,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       const int n = n0 + q * 32 + lane;
       const int ldo = WFMT == 0 ? p.ldo : pb.ldo;
       const int c_first = ((warp - 2) >> 2) * 32; // the warps of a quarter take the 32-column chunks round-robin
+      if (WFMT == 0 && p.act) {
+        // fused SwiGLU: lanes 0..63 hold gate rows, lanes 64..127 the matching up rows.  The four warps that share a
+        // 32-column chunk (one per lane quarter) pair up through shared memory: the up quarters park their values in a
+        // column-major slab of the (now idle) pipeline stages, the gate quarters read them back and store silu(g) * u.
+        // Two slabs per chunk group alternate, so one named barrier per chunk orders both directions.
+        const int grp = (warp - 2) >> 2;                                   // chunk group 0..3
+        float* slab = reinterpret_cast<float*>(tiles) + grp * (2 * 64 * 32);
+        const int half_n = N >> 1;
+        const int no = (int)blockIdx.x * 64 + (q & 1) * 32 + lane;        // output feature of this lane (gate quarters)
+        int it = 0;
+#pragma unroll 1
+        for (int c0 = c_first; c0 < TN; c0 += (kExpandWarps / 4) * 32, ++it) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+          tmem_ld_wait();
+          float* sl = slab + (it & 1) * (64 * 32);
+          if (q >= 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sl[j * 64 + (q & 1) * 32 + lane] = __uint_as_float(v[j]);
+          }
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+          if (q < 2 && no < half_n) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int r = c0 + j;
+              if (r < tok_rows && tok0 + r < M) {
+                const float gv = __uint_as_float(v[j]), uv = sl[j * 64 + (q & 1) * 32 + lane];
+                float f = gv / (1.f + __expf(-gv)) * uv;
+                if (p.row_scale) f *= p.row_scale[tok0 + r];
+                reinterpret_cast<bf16*>(p.out)[(long long)(tok0 + r) * ldo + no] = __float2bfloat16(f);
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c0 = c_first; c0 < TN; c0 += (kExpandWarps / 4) * 32) {
         uint32_t v[32];
@@ -330,6 +368,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             }
           }
         }
+      }
       }
       if (WFMT == 0 && p.out_rows != nullptr) __threadfence_system();     // peer stores ordered before the grid completes
     }
@@ -416,7 +455,9 @@ MMB_API int mmb_fp4_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
   using namespace mmb;
   MmbFp4GemmParams p = *pp;
   if (p.M <= 0 || p.N <= 0) return 0;
-  if (p.K % 64 != 0 || p.Kx % 8 != 0 || p.Kx > p.K || p.act != 0) return (int)cudaErrorInvalidValue;
+  if (p.K % 64 != 0 || p.Kx % 8 != 0 || p.Kx > p.K || (p.act != 0 && p.act != 1)) return (int)cudaErrorInvalidValue;
+  // fused SwiGLU: N counts gate + up rows; every CTA takes 64 output features (needs N / 2 to be a multiple of 64)
+  if (p.act == 1 && ((p.N & 127) != 0 || p.rs_peer_bufs != nullptr || p.out_rows != nullptr)) return (int)cudaErrorInvalidValue;
   const bool grouped = p.tile_expert != nullptr;
   if (p.ag.flags != nullptr && (grouped || p.ag.step == nullptr || p.ag.rows <= 0 || p.ag.tp < 1)) return (int)cudaErrorInvalidValue;
   const int TN = pick_tn(grouped ? (p.token_tile ? p.token_tile : 128) : p.M, p.token_tile);
@@ -424,7 +465,7 @@ MMB_API int mmb_fp4_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
   int e = make_tmap_2d(&mx, p.x, p.Kx, p.M, p.Kx, TN);
   if (e) return e;
   MmbBf16GemmParams pb{};
-  dim3 grid((p.N + kTileRows - 1) / kTileRows, grouped ? p.max_tiles : (p.M + TN - 1) / TN, 1);
+  dim3 grid((p.N + kTileRows - 1) / kTileRows, grouped ? p.max_tiles : (p.M + TN - 1) / TN, 1);     // act == 1: N / 128 CTAs of 64 + 64 rows
   switch (TN) {
     case 32: return launch_gemm<32, 0>(mx, mx, p, pb, grid, stream);
     case 64: return launch_gemm<64, 0>(mx, mx, p, pb, grid, stream);

@@ -74,9 +74,10 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
 
 // xs[pos, :] = x[order[pos] / topk, :] (zero rows for padding); 8 bf16 per thread.
 __global__ void __launch_bounds__(256) moe_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ order, bf16* __restrict__ xs,
-                                                         int n, int topk, int K, int ldx) {
+                                                         int n, int topk, int K, int ldx, const int* __restrict__ n_dev) {
   pdl_launch_dependents();
   pdl_wait();
+  if (n_dev != nullptr) n = min(n, max(*n_dev, 0));      // rows beyond the device-side count are never read by a tile
   const int vec = K / 8;
   for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < (long long)n * vec; i += (long long)gridDim.x * 256) {
     const int pos = (int)(i / vec), c = (int)(i % vec);
@@ -130,12 +131,12 @@ MMB_API int mmb_moe_group(const int* ids, int n, int E, int token_tile, int max_
                      tile_row0, tile_rows, n_tiles);
 }
 
-MMB_API int mmb_moe_gather(const void* x, const int* order, void* xs, int n, int topk, int K, int ldx, cudaStream_t stream) {
+MMB_API int mmb_moe_gather(const void* x, const int* order, void* xs, int n, int topk, int K, int ldx, const int* n_dev, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (K % 8 != 0 || ldx % 8 != 0 || topk < 1) return (int)cudaErrorInvalidValue;
   long long blocks = ((long long)n * (K / 8) + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  return mmb::launch(mmb::moe_gather_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, 1, (const bf16*)x, order, (bf16*)xs, n, topk, K, ldx);
+  return mmb::launch(mmb::moe_gather_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, 1, (const bf16*)x, order, (bf16*)xs, n, topk, K, ldx, n_dev);
 }
 
 MMB_API int mmb_moe_combine(const void* y, const int* inv, const void* add0, const void* add1, void* out, int T, int topk, int N,

@@ -175,10 +175,11 @@ class EPLockstep:
     def __init__(self, ctrl_group):
         self.group = ctrl_group
 
-    def agree(self, prefill: bool, decode: bool, alive: bool = True):
-        f = torch.tensor([int(prefill), int(decode), int(alive)], dtype=torch.int64)
+    def agree(self, prefill_tokens: int, decode_tokens: int):
+        """Largest prompt-pass and decode-pass token counts over the ranks (0: nobody runs that pass)."""
+        f = torch.tensor([int(prefill_tokens), int(decode_tokens)], dtype=torch.int64)
         dist.all_reduce(f, op=dist.ReduceOp.MAX, group=self.group)
-        return bool(f[0]), bool(f[1]), bool(f[2])
+        return int(f[0]), int(f[1])
 
 
 def _req_to_wire(rid: str, req: GenerationRequest) -> dict:

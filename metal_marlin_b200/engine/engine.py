@@ -222,15 +222,25 @@ class LLMEngine:
         with self._lock:
             out = self.scheduler.schedule()
             do_prefill, do_decode = bool(out.prefill), bool(out.decode)
+            n_pre = n_dec = 0
             if self.lockstep is not None:
-                # expert-parallel group: a pass runs on every rank if any rank needs it (a rank without work runs a filler)
-                do_prefill, do_decode, _ = self.lockstep.agree(do_prefill, do_decode)
+                # expert-parallel group: a pass runs on every rank if any rank needs it (a rank without work runs a filler);
+                # the ranks also learn the largest token count of each pass, which bounds the rows an expert owner receives
+                mine_pre = sum(ch.length for ch in out.prefill)
+                mine_dec = self._bucket_size(len(out.decode)) if out.decode else 0
+                n_pre, n_dec = self.lockstep.agree(mine_pre, mine_dec)
+                do_prefill, do_decode = n_pre > 0, n_dec > 0
             elif out.is_empty:
                 return []
             sampled: Dict[str, int] = {}
+            ep = getattr(self.model, "ep", None)
             if do_prefill:
+                if ep is not None:
+                    ep.pass_tokens = n_pre
                 sampled.update(self._run_prefill(out) if out.prefill else self._filler_prefill())
             if do_decode:
+                if ep is not None:
+                    ep.pass_tokens = n_dec
                 sampled.update(self._run_decode(out.decode) if out.decode else self._filler_decode())
             if out.is_empty:
                 return []
@@ -355,12 +365,19 @@ class LLMEngine:
             rp = torch.tensor([p.repetition_penalty for p in sp], dtype=torch.float32, device=dev)
         return ops.sample(logits, temperature=t, top_k=k, top_p=tp, min_p=mp, history=hist, rep_penalty=rp, seed_dev=seeds).tolist()
 
+    def _bucket_size(self, n: int) -> int:
+        return next((b for b in self.cfg.graph_buckets if b >= n), n)
+
     def _bucket(self, n: int) -> _DecodeBucket:
-        B = next((b for b in self.cfg.graph_buckets if b >= n), n)
-        bk = self._buckets.get(B)
+        B = self._bucket_size(n)
+        # an expert-parallel model sizes its expert passes by the group's largest decode batch: a captured step is valid
+        # for that bound only, so it is part of the key
+        ep = getattr(self.model, "ep", None)
+        key = B if ep is None else (B, ep.pass_tokens)
+        bk = self._buckets.get(key)
         if bk is None:
             bk = _DecodeBucket(self.model, self.kv, B, self.max_blocks, self.cfg.use_cuda_graphs)
-            self._buckets[B] = bk
+            self._buckets[key] = bk
         return bk
 
     def _run_decode(self, reqs: List[RunningRequest]) -> Dict[str, int]:

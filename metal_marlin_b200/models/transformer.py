@@ -491,6 +491,12 @@ class Transformer:
 
     def logits(self, h, d, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """fp32 logits of the selected rows (default: all)."""
+        if rows is not None and d is not None and not isinstance(d, torch.Tensor):
+            # a short tensor-parallel pass leaves the last partial sums in the exchange buffers (the head kernel adds them
+            # while it stages its input): run the head on all rows of the pass, then keep the requested ones
+            lg = ops.bf16_linear(h, self.lm_head, norm_w=self.final_norm, eps=self.cfg.rms_norm_eps, out_dtype=torch.float32,
+                                 **self._dargs(d))
+            return lg.index_select(0, rows)
         if rows is not None:
             h = h.index_select(0, rows)
             d = d.index_select(0, rows) if d is not None else None

@@ -203,6 +203,12 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
                 resid_out.copy_(xin)
     elif not xin.is_contiguous() or xin.shape[1] != W.in_features:
         xin = xin[:, : W.in_features].contiguous()
+    if act == 1 and ag_wait is None and W.out_features % 128 == 0 and bias is None:
+        # SwiGLU in the GEMM's epilogue: the gate | up product never goes through memory
+        K.mmb200.fp4_gemm_swiglu(xin, W.qtile, W.stile, out, W.out_features, W.group_size, gemm_status(x.device))
+        if out_add is not None:
+            out += out_add
+        return out
     y = out if act == 0 else torch.empty(M, W.out_features, dtype=torch.bfloat16, device=x.device)
     if ag_wait is not None:
         K.mmb200.fp4_gemm_ag(xin, W.qtile, W.stile, y, W.out_features, W.group_size, gemm_status(x.device), ag_wait.wait)
@@ -701,11 +707,15 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
     K.mmb200.moe_group(ids.reshape(-1).contiguous(), gate_up.num_experts, token_tile, order, inv, t_e, t_r0, t_rows, n_tiles)
     xs = torch.empty(n, gate_up.in_features, dtype=torch.bfloat16, device=dev)
     K.mmb200.moe_gather(xin, order, xs, topk)
-    gu = torch.empty(n, gate_up.out_features, dtype=torch.bfloat16, device=dev)
-    K.mmb200.fp4_gemm_grouped(xs, gate_up.qtile, gate_up.stile, gu, gate_up.out_features, gate_up.group_size,
-                              t_e, t_r0, t_rows, n_tiles, token_tile, None, st)
     h = torch.empty(n, inter, dtype=torch.bfloat16, device=dev)
-    K.mmb200.silu_mul(gu, h)
+    if gate_up.out_features % 128 == 0:
+        K.mmb200.fp4_gemm_grouped_swiglu(xs, gate_up.qtile, gate_up.stile, h, gate_up.out_features, gate_up.group_size,
+                                         t_e, t_r0, t_rows, n_tiles, token_tile, st)
+    else:
+        gu = torch.empty(n, gate_up.out_features, dtype=torch.bfloat16, device=dev)
+        K.mmb200.fp4_gemm_grouped(xs, gate_up.qtile, gate_up.stile, gu, gate_up.out_features, gate_up.group_size,
+                                  t_e, t_r0, t_rows, n_tiles, token_tile, None, st)
+        K.mmb200.silu_mul(gu, h)
     y = torch.empty(n, down.out_features, dtype=torch.bfloat16, device=dev)
     # routing weight of every sorted row (dropped pairs, id < 0, are never read by a tile)
     rs = weights.reshape(-1).to(torch.float32).index_select(0, order.clamp_min(0).long()).contiguous()

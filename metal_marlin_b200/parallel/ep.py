@@ -103,7 +103,7 @@ class ExpertParallelMoE:
 
 
     def forward_fused(self, ex: "EPExchange", x_local, ids_local, weights_local, *, norm_w=None, eps=1e-6, add0=None, add1=None,
-                      token_tile: int = 0):
+                      token_tile: int = 0, rows_bound: int = 0):
         """Same result as :meth:`forward_dispatch` (+ ``add0`` + ``add1``, e.g. the shared expert and the residual input)
         with the dispatch, the expert GEMMs and the combine chained on the device over peer memory."""
         if not (x_local.is_cuda and ops.native_available()):
@@ -113,7 +113,7 @@ class ExpertParallelMoE:
                     out = out + a.to(torch.float32)
             return out.to(torch.bfloat16)
         st = self.fused_dispatch(ex, x_local, ids_local, weights_local, norm_w=norm_w, eps=eps)
-        self.fused_experts(ex, expected_rows=ids_local.numel(), token_tile=token_tile)
+        self.fused_experts(ex, expected_rows=ids_local.numel(), token_tile=token_tile, rows_bound=rows_bound)
         return self.fused_combine(ex, st, add0=add0, add1=add1)
 
     # The three phases of forward_fused, separately callable so that several emulated ranks on one GPU can be stepped phase
@@ -129,12 +129,15 @@ class ExpertParallelMoE:
         ops.K.mmb200.ep_dispatch(xin, ids32, ex.desc_dispatch, per, self.ep, self.rank, ex.cap)
         return ids32, weights_local.to(torch.float32).contiguous()
 
-    def fused_experts(self, ex: "EPExchange", *, expected_rows: int, token_tile: int = 0) -> None:
-        """Phase 2 (expert owner): wait for the senders, group the received rows, run the experts, return the rows."""
+    def fused_experts(self, ex: "EPExchange", *, expected_rows: int, token_tile: int = 0, rows_bound: int = 0) -> None:
+        """Phase 2 (expert owner): wait for the senders, group the received rows, run the experts, return the rows.
+        ``rows_bound``: an upper bound of the (token, slot) rows ONE rank sends in this pass that every rank agrees on
+        (0: the exchange capacity); the work arrays and the launch grids are sized by it, and a pass that receives more
+        rows than ``ep * rows_bound`` runs no tile and raises status 120."""
         K = ops.K.mmb200
         dev = ex.local.device
         gu_b, dn_b = self.gate_up, self.down
-        n = self.ep * ex.cap
+        n = self.ep * (min(ex.cap, rows_bound) if rows_bound > 0 else ex.cap)
         if not token_tile:      # rows arrive from every rank: a local expert expects about expected_rows / n_local of them
             avg = expected_rows / max(1, self.n_local)
             token_tile = 32 if avg <= 24 else (64 if avg <= 48 else (128 if avg <= 160 else 256))
@@ -143,17 +146,21 @@ class ExpertParallelMoE:
         row_dst = torch.empty(n, dtype=torch.int64, device=dev)
         t_e = torch.empty(max_tiles, dtype=torch.int32, device=dev)
         t_r0, t_rows = torch.empty_like(t_e), torch.empty_like(t_e)
-        n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+        n_tiles = torch.empty(2, dtype=torch.int32, device=dev)      # [tiles, rows received]
         K.ep_recv_group(ex.desc_recv, self.ep, ex.cap, dn_b.out_features, max(1, self.n_local), token_tile, order, row_dst, t_e, t_r0,
                         t_rows, n_tiles)
         st = ops.gemm_status(dev)
         xs = torch.empty(n, gu_b.in_features, dtype=torch.bfloat16, device=dev)
-        K.moe_gather(ex.recv_x, order, xs, 1)
-        gu = torch.empty(n, gu_b.out_features, dtype=torch.bfloat16, device=dev)
-        K.fp4_gemm_grouped(xs, gu_b.qtile, gu_b.stile, gu, gu_b.out_features, gu_b.group_size, t_e, t_r0, t_rows, n_tiles, token_tile,
-                           None, st)
+        K.moe_gather_n(ex.recv_x, order, xs, 1, n_tiles, 1)      # only the rows that arrived, not the worst-case capacity
         h = torch.empty(n, gu_b.out_features // 2, dtype=torch.bfloat16, device=dev)
-        K.silu_mul(gu, h)
+        if gu_b.out_features % 128 == 0:       # SwiGLU in the GEMM epilogue: only rows that a tile covers are touched
+            K.fp4_gemm_grouped_swiglu(xs, gu_b.qtile, gu_b.stile, h, gu_b.out_features, gu_b.group_size, t_e, t_r0, t_rows, n_tiles,
+                                      token_tile, st)
+        else:
+            gu = torch.empty(n, gu_b.out_features, dtype=torch.bfloat16, device=dev)
+            K.fp4_gemm_grouped(xs, gu_b.qtile, gu_b.stile, gu, gu_b.out_features, gu_b.group_size, t_e, t_r0, t_rows, n_tiles, token_tile,
+                               None, st)
+            K.silu_mul(gu, h)
         # down projection: every output row goes from the epilogue into its token owner's return buffer
         K.fp4_gemm_grouped_scatter(h, dn_b.qtile, dn_b.stile, ex.ret_y[:1], dn_b.out_features, dn_b.group_size, t_e, t_r0, t_rows,
                                    n_tiles, token_tile, st, row_dst)
@@ -258,6 +265,11 @@ class EPModelState:
         self.layers: Dict[int, ExpertParallelMoE] = {}
         self.shared: Dict[int, Tuple[FP4ExpertBank, FP4ExpertBank]] = {}
         self.n_shared = 0
+        # Most tokens ANY rank brings to the current forward pass, when the ranks know it (an engine group agrees on it every
+        # step; ``uniform`` says every rank brings as many tokens as this one): the expert owners size their work by it
+        # instead of by the exchange capacity.
+        self.pass_tokens = 0
+        self.uniform = False
 
     def add_layer(self, li: int, gate_up: FP4ExpertBank, down: FP4ExpertBank, num_routed: int, n_shared: int) -> None:
         moe = ExpertParallelMoE(gate_up, down, num_routed, 0, self.rank, self.ep, self.group)
@@ -283,7 +295,8 @@ class EPModelState:
             xin = ops.rmsnorm(x, norm_w, eps) if norm_w is not None else x
             add0 = ops._shared_experts(xin, gu, dn, self.n_shared, 0)
         if self.mode == "fused" and self.exchange is not None and x.is_cuda:
-            return moe.forward_fused(self.exchange, x, ids, weights, norm_w=norm_w, eps=eps, add0=add0)
+            bound = ids.shape[0] if self.uniform else self.pass_tokens
+            return moe.forward_fused(self.exchange, x, ids, weights, norm_w=norm_w, eps=eps, add0=add0, rows_bound=bound * ids.shape[1])
         out = moe.forward_dispatch(x, ids, weights, norm_w=norm_w, eps=eps)
         return out if add0 is None else (out.to(torch.float32) + add0.to(torch.float32)).to(out.dtype)
 

@@ -81,7 +81,7 @@ dist.init_process_group("nccl", device_id=dev)
 from metal_marlin_b200 import ops
 from metal_marlin_b200.ops.weights import FP4ExpertBank
 from metal_marlin_b200.parallel.ep import EPExchange, ExpertParallelMoE
-E, topk, H, I, gs, T = 16, 4, 512, 256, 64, 96 + 32 * rank
+E, topk, H, I, gs, T = 16, 4, 512, 256, 64, 96 + 8 * rank
 torch.manual_seed(7)                       # same banks on every rank
 gu = FP4ExpertBank.from_float(torch.randn(E, 2 * I, H, device=dev) * 0.05, gs)
 dn = FP4ExpertBank.from_float(torch.randn(E, H, I, device=dev) * 0.05, gs)
@@ -116,10 +116,11 @@ def _free_port():
     return p
 
 
-def test_fused_expert_parallel_two_gpus(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs at least 2 GPUs")
-    world, port = 2, _free_port()
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_expert_parallel_multi_gpu(world, tmp_path):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    port = _free_port()
     script = tmp_path / "child.py"
     script.write_text(_CHILD)
     procs = []

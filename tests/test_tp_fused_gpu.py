@@ -82,12 +82,12 @@ def _free_port():
     return p
 
 
-@pytest.mark.parametrize("preset", ["tiny-mla-moe"])
-def test_fused_tp_decode_matches_unsharded(preset, tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("preset", ["tiny-mla-moe-h8"])
+def test_fused_tp_decode_matches_unsharded(preset, world, tmp_path):
     n = torch.cuda.device_count()
-    if n < 2:
-        pytest.skip("needs at least 2 GPUs")
-    world = 2
+    if n < world:
+        pytest.skip(f"needs {world} GPUs")
     port = _free_port()
     script = tmp_path / "child.py"
     script.write_text(_CHILD)

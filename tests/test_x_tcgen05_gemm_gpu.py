@@ -105,3 +105,37 @@ def test_prefill_through_tensor_core_path_matches_reference():
         b = prefill(lm.model, lm.new_cache(32, 16), prompts, bt)
     assert ops.check_status(DEV) == 0
     assert float((a - b).abs().max() / b.abs().max()) < 4e-2
+
+
+@pytest.mark.parametrize("M", [33, 64, 130, 257, 1024, 2300])
+@pytest.mark.parametrize("I,K,gs", [(64, 64, 64), (128, 512, 128), (1536, 2048, 128), (320, 768, 64)])
+def test_fp4_gemm_swiglu_epilogue(M, I, K, gs):
+    """SwiGLU fused into the tensor-core GEMM's epilogue (64 gate rows and the 64 matching up rows share one accumulator
+    tile) against the fp32 statement silu(x Wg^T) * (x Wu^T)."""
+    torch.manual_seed(M + I)
+    W = FP4Weight.from_float(torch.randn(2 * I, K, device=DEV) * 0.05, gs)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    y = ops.linear(x, W, act=1)
+    assert ops.check_status(DEV) == 0 and y.shape == (M, I)
+    z = x.float() @ W.dequantize().t()
+    ref = torch.nn.functional.silu(z[:, :I]) * z[:, I:]
+    _check(y, ref, tol=3e-2)
+    assert not torch.isnan(y.float()).any()
+
+
+@pytest.mark.parametrize("T,E,topk,I", [(200, 8, 2, 128), (700, 16, 4, 192), (1500, 64, 4, 1536)])
+def test_moe_grouped_gemm_swiglu_epilogue(T, E, topk, I, monkeypatch):
+    """Grouped expert GEMM with the fused SwiGLU epilogue (ragged expert tiles) against the reference MoE."""
+    torch.manual_seed(T)
+    monkeypatch.setattr(ops, "MOE_GROUPED_GEMV_MAX_T", 0)
+    H = 512
+    gu = FP4ExpertBank.from_float(torch.randn(E, 2 * I, H, device=DEV) * 0.05, 64)
+    dn = FP4ExpertBank.from_float(torch.randn(E, H, I, device=DEV) * 0.05, 64)
+    x = torch.randn(T, H, device=DEV).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, device=DEV)[:topk] for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, topk, device=DEV)
+    y = ops.moe_forward(x, gu, dn, ids, wts)
+    assert ops.check_status(DEV) == 0
+    with ops.force_reference():
+        y_ref = ops.moe_forward(x, gu, dn, ids, wts)
+    _check(y, y_ref, tol=4e-2)
