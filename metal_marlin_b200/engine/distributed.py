@@ -82,7 +82,10 @@ def init_process_group(device: Optional[torch.device] = None, timeout_s: int = 1
             dist.init_process_group("gloo", timeout=to)
     ctrl = None
     if world > 1:
-        ctrl = dist.new_group(backend="gloo") if device.type == "cuda" else dist.group.WORLD
+        # Host-side control messages.  A follower legitimately waits in a broadcast while the leader is idle, so the default
+        # limit is long; MMB200_CTRL_TIMEOUT_S shortens it (tests, or deployments whose leader sends keep-alives).
+        ctl_to = datetime.timedelta(seconds=int(os.environ.get("MMB200_CTRL_TIMEOUT_S", "1800")))
+        ctrl = dist.new_group(backend="gloo", timeout=ctl_to) if device.type == "cuda" else dist.group.WORLD
     return rank, world, device, ctrl
 
 
@@ -396,6 +399,9 @@ class DistributedEngine:
             self.run_until_done()
         for r in rrs:
             r.done.wait()
+        failed = [r.error for r in rrs if getattr(r, "error", None)]
+        if failed:
+            raise RuntimeError(f"{len(failed)} request(s) failed: {failed[0]}")
         return [r.output_ids for r in rrs]
 
     def start(self) -> None:

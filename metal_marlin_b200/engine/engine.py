@@ -93,16 +93,25 @@ class _DecodeBucket:
         self.splits = ops.default_splits(B, 1 if cfg.is_mla else cfg.num_key_value_heads, self.max_ctx,
                                          mla_latent=cfg.is_mla and cfg.latent_dim == 576 and getattr(self.kv, "kv_dtype", "bf16") == "bf16")
         self.use_graph = use_graph and dev.type == "cuda"
+        ep = getattr(model, "ep", None)
+        if ep is not None and ep.mode != "fused":
+            self.use_graph = False       # the all-to-all baseline reads its split sizes on the host: not capturable
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.status = ops.gemm_status(dev)
 
-    def _body(self):
+    def _forward(self):
         meta = BatchMeta(positions=self.pos, slots=self.slots, block_tables=self.bt, ctx_lens=self.ctx, decode=True,
                          max_ctx=self.max_ctx, splits=self.splits)
-        logits = self.model.full_logits(self.model.forward(self.ids, self.kv, meta))
-        ops.sample(logits, temperature=self.f[0], top_k=self.topk, top_p=self.f[1], min_p=self.f[2], history=self.hist,
-                   rep_penalty=self.f[3], seed_dev=self.seeds, offset_dev=self.step_no, out=self.out)
+        self.logits = self.model.forward(self.ids, self.kv, meta)
+
+    def _sample(self):
+        ops.sample(self.model.full_logits(self.logits), temperature=self.f[0], top_k=self.topk, top_p=self.f[1], min_p=self.f[2],
+                   history=self.hist, rep_penalty=self.f[3], seed_dev=self.seeds, offset_dev=self.step_no, out=self.out)
         self.step_no += 1
+
+    def _body(self):
+        self._forward()
+        self._sample()
 
     def upload(self) -> None:
         """Stage this step's inputs on the device: one copy of the packed buffer (+ the token history when a row uses a
@@ -113,6 +122,9 @@ class _DecodeBucket:
         self.hist_dirty = False
 
     def execute(self) -> torch.Tensor:
+        # With a vocabulary-sharded head the sampler needs the logits of all ranks: that gather is a library collective and
+        # stays outside the captured graph (the graph then holds this library's kernels only).
+        split = getattr(self.model, "tp", None) is not None and self.model.tp.tp > 1
         if self.use_graph:
             if self.graph is None:
                 s = torch.cuda.Stream(device=self.dev)
@@ -124,9 +136,11 @@ class _DecodeBucket:
                 self.step_no.zero_()            # the warm-up pass must not advance the random stream
                 self.graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(self.graph):
-                    self._body()
+                    self._forward() if split else self._body()
                 self.step_no.zero_()
             self.graph.replay()
+            if split:
+                self._sample()
         else:
             self._body()
         self.h_out.copy_(self.out, non_blocking=True)
