@@ -1,6 +1,8 @@
 // torch.ops.mmb200.* : thin argument-checking shims over the extern "C" kernel launchers.
 // Every op writes into caller-provided output tensors (no allocation here), runs on the current
 // CUDA stream and is therefore capturable in a CUDA graph.
+#include <cstring>
+
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
@@ -9,6 +11,7 @@
 #include "api.h"
 #include "api_gemm.h"
 #include "api_ext.h"
+#include "api_chain.h"
 
 namespace {
 
@@ -415,6 +418,21 @@ void paged_decode_impl(const Tensor& q, const Tensor& k_pool, const OptT& v_pool
   p.status = status_word_of(q);
   check(mmb_paged_decode(&p, cur_stream()), "paged_decode");
 }
+
+// Decode chain (decode_chain.cu).  `desc` is a CPU byte tensor holding an MmbChainParams exactly as the C ABI lays it out
+// (the Python side builds it with a ctypes mirror of the struct); all pointers in it are device addresses of tensors the
+// caller keeps alive.
+void decode_chain(const Tensor& desc, const Tensor& anchor) {
+  TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kByte && desc.is_contiguous() &&
+                  desc.numel() == (int64_t)sizeof(MmbChainParams),
+              "decode_chain: descriptor has ", desc.numel(), " bytes, the library expects ", sizeof(MmbChainParams));
+  TORCH_CHECK(anchor.is_cuda());
+  c10::cuda::CUDAGuard guard(anchor.device());
+  MmbChainParams p;
+  std::memcpy(&p, desc.data_ptr(), sizeof(p));
+  check(mmb_decode_chain(&p, cur_stream()), "decode_chain");
+}
+int64_t decode_chain_param_bytes() { return (int64_t)sizeof(MmbChainParams); }
 
 void decode_merge(const Tensor& part_o, const Tensor& part_ml, const OptT& w_uv, Tensor out, int64_t B, int64_t Hq,
                   int64_t dv, int64_t dvo, int64_t splits) {
@@ -1140,6 +1158,8 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("qk_norm_rope_cache", &qk_norm_rope_cache);
   m.def("mla_prep", &mla_prep);
   m.def("paged_decode", &paged_decode);
+  m.def("decode_chain", &decode_chain);
+  m.def("decode_chain_param_bytes", &decode_chain_param_bytes);
   m.def("set_status_word", &set_status_word);
   m.def("decode_merge", &decode_merge);
   m.def("moe_router", &moe_router);

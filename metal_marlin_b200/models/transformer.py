@@ -206,6 +206,7 @@ class Transformer:
         self.scale = cfg.softmax_scale()
         self.mtp = None      # optional multi-token-prediction head (spec/mtp.py)
         # tensor parallelism (parallel/tp.py): a shard keeps only its local heads / vocabulary rows
+        self._chain = None   # decode-chain runner (ops/chain.py); False once found unsupported for this model
         self.tp = None
         self.ep = None       # expert parallelism with replicated attention (parallel/ep.py::EPModelState)
         self.routing_hook = None     # optional callable(layer, expert_ids, router_probs)
@@ -468,12 +469,26 @@ class Transformer:
                               shared_base=cfg.num_experts, norm_w=L.post_norm, eps=cfg.rms_norm_eps)
         return new_h, out
 
+    def _use_chain(self, input_ids, kv, meta) -> bool:
+        """Small decode batches of MLA models run the persistent decode-chain kernel (``ops/chain.py``): one launch between
+        two attention calls instead of seven."""
+        from ..ops import chain
+        if self._chain is False or not input_ids.is_cuda or input_ids.shape[0] > chain.MAX_BATCH or self.routing_hook is not None:
+            return False
+        if ops._FORCE_REF or ops._capture is not None or isinstance(kv.k[0], ops.FP8KV) or meta.attn_mask is not None:
+            return False
+        if self._chain is None:
+            self._chain = chain.DecodeChain(self) if (ops.native_available() and chain.model_supported(self)) else False
+        return self._chain is not False
+
     # ------------------------------------------------------------------ full forward
     def forward_hidden(self, input_ids: torch.Tensor, kv: PagedKVStorage, meta: BatchMeta) -> Tuple[torch.Tensor, torch.Tensor]:
         """Runs all layers.  Returns (hidden, pending delta): the final residual add + norm is fused
         into the head projection."""
         if self.tp is not None:
             self.tp.begin_step()          # new exchange epoch: every in-kernel exchange site is used once per forward pass
+        if meta.decode and self._use_chain(input_ids, kv, meta):
+            return self._chain.step(input_ids, kv, meta)
         h = ops.embedding(self.embed, input_ids)
         d = None
         for li, L in enumerate(self.layers):
