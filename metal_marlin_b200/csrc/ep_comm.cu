@@ -26,12 +26,12 @@ namespace mmb {
 constexpr int kEpMaxRanks = 32;
 constexpr int kEpMaxExperts = 1024;
 
-__device__ __forceinline__ bool ep_wait_flag(const unsigned* f, unsigned want) {
+__device__ __forceinline__ bool ep_wait_flag(const unsigned* f, unsigned want, const int* status) {
   if (ld_acquire_sys(f) >= want) return true;
-  const unsigned long long t0 = tp_now_ns();
+  const unsigned long long t0 = tp_now_ns(), lim = wait_limit_ns(status);
   unsigned it = 0;
   while (ld_acquire_sys(f) < want) {
-    if ((++it & 63u) == 0u && tp_now_ns() - t0 > kTpWaitNs) return false;
+    if ((++it & 63u) == 0u && tp_now_ns() - t0 > lim) return false;
   }
   return true;
 }
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(1024) ep_recv_group_kernel(MmbEpRecvParams p) 
   const int tid = threadIdx.x, E = p.E_local, n = (p.n_rows_max > 0) ? min(p.n_rows_max, p.ep * p.cap) : p.ep * p.cap;
   if (tid < p.ep) {
     int c = 0;
-    if (ep_wait_flag(p.flags + tid, *p.step)) c = min(max(__ldcg(p.recv_cnt + tid), 0), p.cap);
+    if (ep_wait_flag(p.flags + tid, *p.step, p.status)) c = min(max(__ldcg(p.recv_cnt + tid), 0), p.cap);
     else if (p.status) atomicExch(p.status, 121 + tid);
     scnt[tid] = c;
   }
@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(MmbEpCombineParams p) {
   pdl_launch_dependents();
   pdl_wait();
   if ((int)threadIdx.x < p.ep) {
-    if (!ep_wait_flag(p.flags + threadIdx.x, *p.step) && p.status) atomicExch(p.status, 140 + (int)threadIdx.x);
+    if (!ep_wait_flag(p.flags + threadIdx.x, *p.step, p.status) && p.status) atomicExch(p.status, 140 + (int)threadIdx.x);
   }
   __syncthreads();
   const int vec = p.N / 8;

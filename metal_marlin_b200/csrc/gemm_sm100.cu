@@ -124,7 +124,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           const unsigned long long t0 = tp_now_ns();
           unsigned spins = 0;
           while (ld_acquire_sys(f) < want) {
-            if ((++spins & 63u) == 0u && tp_now_ns() - t0 > kTpWaitNs) {
+            if ((++spins & 63u) == 0u && tp_now_ns() - t0 > wait_limit_ns(status)) {
               x_ready = false;
               break;
             }

@@ -19,6 +19,16 @@ namespace mmb {
 
 constexpr unsigned long long kTpWaitNs = 1000000000ull;   // 1 s
 
+// Limit of a bounded wait: word 1 of the status array, when positive, gives it in microseconds (a host-side setting for
+// tests and for deployments that want to give up sooner); otherwise one second.
+__device__ __forceinline__ unsigned long long wait_limit_ns(const int* status) {
+  if (status != nullptr) {
+    const int us = *reinterpret_cast<const volatile int*>(status + 1);
+    if (us > 0) return (unsigned long long)us * 1000ull;
+  }
+  return kTpWaitNs;
+}
+
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
   unsigned v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -57,10 +67,10 @@ __device__ __forceinline__ void tp_wait(const TpIn& t) {
     const unsigned want = *t.step;
     const unsigned* f = t.flags + threadIdx.x;
     if (ld_acquire_sys(f) < want) {
-      const unsigned long long t0 = tp_now_ns();
+      const unsigned long long t0 = tp_now_ns(), lim = wait_limit_ns(t.status);
       unsigned it = 0;
       while (ld_acquire_sys(f) < want) {
-        if ((++it & 63u) == 0u && tp_now_ns() - t0 > kTpWaitNs) {
+        if ((++it & 63u) == 0u && tp_now_ns() - t0 > lim) {
           if (t.status) atomicExch(t.status, 100 + (int)threadIdx.x);
           break;
         }

@@ -204,7 +204,7 @@ class EPExchange:
         self.recv_x = local[lay["recv_x"]: lay["recv_x"] + ep * self.cap * hidden * 2].view(torch.bfloat16).view(ep * self.cap, hidden)
         self.ret_y = local[lay["ret_y"]: lay["ret_y"] + self.cap * hidden * 2].view(torch.bfloat16).view(self.cap, hidden)
         self.step = local[self.OFF_STEP: self.OFF_STEP + 4].view(torch.int32)
-        self.status = local[self.OFF_STATUS: self.OFF_STATUS + 4].view(torch.int32)
+        self.status = local[self.OFF_STATUS: self.OFF_STATUS + 8].view(torch.int32)     # [code, wait limit in us (0: one second)]
         tbl = torch.tensor([[p + lay["recv_x"] for p in self.peer_ptrs],
                             [p + lay["meta"] for p in self.peer_ptrs],
                             [p + self.OFF_CNT for p in self.peer_ptrs],
@@ -228,7 +228,11 @@ class EPExchange:
 
     def check(self) -> int:
         """0, or the code of the wait that gave up / the overflow (reads the device: call between steps)."""
-        return int(self.status.item())
+        return int(self.status[0].item())
+
+    def set_wait_limit_us(self, us: int) -> None:
+        """Give up device-side waits of this exchange after ``us`` microseconds (0 restores the one-second default)."""
+        self.status[1] = int(us)
 
     @classmethod
     def create(cls, hidden: int, max_tokens: int, topk: int, device, group=None) -> "EPExchange":

@@ -143,3 +143,72 @@ def test_step_guard_keeps_non_peer_codes_apart():
     with pytest.raises(PeerFailure) as e:
         guard.run(lambda: 1)
     assert e.value.ranks == [4]
+
+
+@pytest.mark.gpu
+def test_bounded_device_waits_run_out_and_report():
+    """The allowed form of a device-side failure test: a flag that nothing sets.  The wait limit is taken from word 1 of
+    the status array (microseconds), the kernels give up after it, leave their code in word 0 and return; the host turns
+    the code into PeerFailure and the context stays usable.  No fault, no trap, no endless loop."""
+    import time
+
+    import torch
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.ops.weights import FP4ExpertBank
+    from metal_marlin_b200.parallel.ep import EPExchange, ExpertParallelMoE
+    from metal_marlin_b200.parallel.health import raise_for_status
+    dev = torch.device("cuda", 0)
+    assert ops.native_available()
+    # ---- tensor-parallel consumer wait: two source flags, step 1, nobody publishes
+    flags = torch.zeros(2, dtype=torch.int32, device=dev)
+    step = torch.ones(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    status[1] = 3000                                            # give up after 3 ms
+    desc = torch.tensor([flags.data_ptr(), step.data_ptr(), status.data_ptr(), 2], dtype=torch.int64)
+    t0 = time.perf_counter()
+    ops.K.mmb200.tp_wait(desc)
+    torch.cuda.synchronize(dev)
+    assert time.perf_counter() - t0 < 0.5                        # far below the one-second default: the setting was honoured
+    code = int(status[0])
+    assert code in (100, 101), code
+
+    class Ctx:
+        def check(self):
+            return code
+
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v.encode() if isinstance(v, str) else v
+
+        def get(self, k):
+            return self[k]
+
+    with pytest.raises(PeerFailure) as e:
+        StepGuard(Heartbeat(Store(), 0, 1), Ctx()).run(lambda: None)
+    assert e.value.ranks == [code - 100]
+    # the wait returns at once when the flags are there
+    status.zero_()
+    flags.fill_(1)
+    ops.K.mmb200.tp_wait(desc)
+    torch.cuda.synchronize(dev)
+    assert int(status[0]) == 0
+    # ---- expert-parallel owner: rank 0 of two emulated ranks waits for senders that never dispatch
+    E, H, I, topk = 4, 256, 128, 2
+    torch.manual_seed(0)
+    gu = FP4ExpertBank.from_float(torch.randn(E, 2 * I, H, device=dev) * 0.05, 64)
+    dn = FP4ExpertBank.from_float(torch.randn(E, H, I, device=dev) * 0.05, 64)
+    exs = EPExchange.emulated(2, H, 16, topk, dev)
+    moe = ExpertParallelMoE(gu, dn, E, 0, 0, 2)
+    exs[0].set_wait_limit_us(3000)
+    exs[0].begin()
+    t0 = time.perf_counter()
+    moe.fused_experts(exs[0], expected_rows=16 * topk)
+    torch.cuda.synchronize(dev)
+    assert time.perf_counter() - t0 < 0.5
+    code = exs[0].check()
+    assert code in (121, 122), code
+    with pytest.raises(PeerFailure) as e:
+        raise_for_status(code)
+    assert e.value.ranks == [code - 121]
+    # the device is still usable
+    assert float(torch.ones(8, device=dev).sum()) == 8.0 and ops.check_status(dev) == 0
