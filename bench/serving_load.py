@@ -1,7 +1,9 @@
 """Serving load test: Poisson arrivals into the continuous-batching engine, synthetic prompts.
 
     python bench/serving_load.py --model glm-4.7-flash --rate 16 --requests 64 --prompt-min 128 --prompt-max 1024 \
-        --out-min 32 --out-max 128
+        --out-min 32 --out-max 128 [--speculative ngram | draft --draft-layers 2 --num-spec 4]
+    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 bench/serving_load.py --model qwen3.5-122b-a10b --tp 8 --ep 8 \
+        --speculative draft --rate 16 --prompt-max 4096 --out-min 64 --out-max 512
 
 Requests are submitted from a driver thread at exponentially distributed intervals while the engine loop (paged KV,
 chunked prefill, CUDA-graph decode buckets, optional speculative decoding in the pipeline layer) runs in its own
@@ -51,13 +53,44 @@ def main():
     ap.add_argument("--kv-blocks", type=int, default=8192)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--device", default=None)
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (under torchrun)")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree (with --tp: whole experts per rank)")
+    ap.add_argument("--speculative", default="none", choices=["none", "ngram", "draft"],
+                    help="draft: a random-init small model of the same vocabulary (--draft-layers)")
+    ap.add_argument("--draft-layers", type=int, default=2)
+    ap.add_argument("--num-spec", type=int, default=4)
     args = ap.parse_args()
-    dev = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
-    lm = MMFP4ForCausalLM.from_config(args.model, device=dev, seed=args.seed)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    ecfg = EngineConfig(num_kv_blocks=args.kv_blocks, block_size=16, max_model_len=args.prompt_max + args.out_max + 16,
+                        max_num_seqs=args.max_seqs, max_num_batched_tokens=4096, max_prefill_tokens=2048, max_chunk=1024,
+                        use_cuda_graphs=torch.cuda.is_available(), request_timeout_s=600.0)
+    if world > 1:
+        from metal_marlin_b200.engine.distributed import ParallelConfig, build_engine, init_process_group
+        rank, world, device, ctrl = init_process_group()
+        dev = str(device)
+        lm = MMFP4ForCausalLM.from_config(args.model, device=dev, seed=args.seed)
+        pc = ParallelConfig.parse(tp=args.tp, ep=args.ep, world=world)
+        eng = build_engine(lm.model, ecfg, pc, rank, world, device, ctrl)
+        core = eng.engine
+    else:
+        rank = 0
+        dev = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        lm = MMFP4ForCausalLM.from_config(args.model, device=dev, seed=args.seed)
+        eng = core = LLMEngine(lm.model, ecfg)
+        pc = None
     cfg = lm.config
-    eng = LLMEngine(lm.model, EngineConfig(num_kv_blocks=args.kv_blocks, block_size=16, max_model_len=args.prompt_max + args.out_max + 16,
-                                           max_num_seqs=args.max_seqs, max_num_batched_tokens=4096, max_prefill_tokens=2048, max_chunk=1024,
-                                           use_cuda_graphs=dev != "cpu", request_timeout_s=600.0))
+    if args.speculative != "none" and rank == 0:
+        draft = "ngram"
+        if args.speculative == "draft":        # small random-init model with the target's vocabulary
+            import copy
+            dcfg = copy.copy(cfg)
+            dcfg.num_hidden_layers = args.draft_layers
+            dcfg.first_k_dense_replace = min(dcfg.first_k_dense_replace, args.draft_layers)
+            draft = MMFP4ForCausalLM.from_config(dcfg, device=dev, seed=args.seed + 1)
+        core.enable_speculative(draft, num_speculative_tokens=args.num_spec)
+    if rank != 0:
+        eng.serve_forever()
+        return
     rng = random.Random(args.seed)
     g = torch.Generator().manual_seed(args.seed)
     # warm-up: compile the graph buckets and the prefill shapes
@@ -90,7 +123,10 @@ def main():
         "prompt_len": [args.prompt_min, args.prompt_max], "output_len": [args.out_min, args.out_max],
         "ttft_ms_p50": round(1e3 * pct(ttft, 0.5), 1) if ttft else None, "ttft_ms_p99": round(1e3 * pct(ttft, 0.99), 1) if ttft else None,
         "latency_ms_p50": round(1e3 * pct(e2e, 0.5), 1) if e2e else None, "latency_ms_p99": round(1e3 * pct(e2e, 0.99), 1) if e2e else None,
-        "output_tok_s": round(out_tokens / max(t_end - t_start, 1e-9), 1), "engine_iterations": eng.iterations, "wall_s": round(t_end - t_start, 2)}))
+        "output_tok_s": round(out_tokens / max(t_end - t_start, 1e-9), 1), "engine_iterations": eng.iterations, "wall_s": round(t_end - t_start, 2),
+        "parallelism": pc.mode if pc is not None else "single", "n_gpus": world, "speculative": args.speculative,
+        "spec_acceptance_rate": round(core.spec_accepted / max(1, core.spec_proposed), 3) if core.spec is not None else None,
+        "exchange_status": eng.check() if hasattr(eng, "check") else 0}))
 
 
 if __name__ == "__main__":

@@ -55,9 +55,15 @@ typedef struct {
   // out_rows[r] instead of out + r * ldo (0 = row not stored).  The addresses may lie in peer memory: the expert
   // outputs go straight from the epilogue into the token owners' return buffers over NVLink.
   const long long* out_rows;
+  // Trellis weights (mmb_trellis_gemm): device table of matrix descriptors (see MmbTrellisMat in api_ext.h, 6 x int64 per
+  // matrix), matrices per expert, and the first matrix of the projection (qw / sc / gs_shift are unused).
+  const long long* tr_desc;
+  int tr_stride, tr_first;
 } MmbFp4GemmParams;
 
 int mmb_fp4_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
+// Same pipeline with trellis weights decoded inside the main loop (2..8 bits per matrix, mixed per expert and matrix).
+int mmb_trellis_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
 
 // out[M, N] = x[M, K] * W[N, K]^T, both bf16 row major (TMA for both operands), fp32 accumulate in TMEM.
 // Batched over `batch` independent problems with element strides (0 = shared operand).

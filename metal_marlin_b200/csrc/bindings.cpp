@@ -744,6 +744,52 @@ static void fp4_gemm_grouped_impl(const Tensor& x, const Tensor& qw, const Tenso
   check(mmb_fp4_gemm(&p, cur_stream()), "fp4_gemm_grouped");
 }
 
+// Trellis weights on the tensor cores (codes decoded inside the GEMM's main loop).  `desc` int64 [n_mats, 6] on the device:
+// codes, scales, su, sv, out | in << 32, bits | group << 32 per matrix.  Dense: n_mats = 1 (or 2 with act = 1: gate, up).
+// Grouped: matrices [expert * stride + first (+ 1 for the up half)], rows of x sorted by expert, tile list on the device.
+void trellis_gemm(const Tensor& x, const Tensor& desc, Tensor out, int64_t N, int64_t K, int64_t act, int64_t first, int64_t stride,
+                  const OptT& tile_expert, const OptT& tile_row0, const OptT& tile_rows, const OptT& n_tiles, int64_t token_tile,
+                  const OptT& row_scale, Tensor status) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && desc.is_cuda() && desc.scalar_type() == at::kLong &&
+              desc.is_contiguous() && desc.dim() == 2 && desc.size(1) == 6);
+  TORCH_CHECK(K % 64 == 0 && x.size(1) == K, "trellis_gemm: the input width must equal K and be a multiple of 64");
+  TORCH_CHECK(act == 0 ? out.size(1) == N : (N % 128 == 0 && out.size(1) == N / 2));
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbFp4GemmParams p{};
+  p.x = x.data_ptr();
+  p.out = out.data_ptr();
+  p.M = (int)x.size(0);
+  p.N = (int)N;
+  p.K = (int)K;
+  p.Kx = (int)K;
+  p.ldo = (int)out.stride(0);
+  p.status = status.data_ptr<int>();
+  p.act = (int)act;
+  p.tr_desc = reinterpret_cast<const long long*>(desc.data_ptr<int64_t>());
+  p.tr_first = (int)first;
+  p.tr_stride = (int)stride;
+  if (tile_expert.has_value() && tile_expert->defined()) {
+    TORCH_CHECK(tile_row0.has_value() && tile_rows.has_value() && n_tiles.has_value());
+    TORCH_CHECK(tile_expert->scalar_type() == at::kInt && tile_row0->scalar_type() == at::kInt && tile_rows->scalar_type() == at::kInt &&
+                n_tiles->scalar_type() == at::kInt);
+    p.tile_expert = tile_expert->data_ptr<int>();
+    p.tile_row0 = tile_row0->data_ptr<int>();
+    p.tile_rows = tile_rows->data_ptr<int>();
+    p.n_tiles = n_tiles->data_ptr<int>();
+    p.max_tiles = (int)tile_expert->numel();
+    p.token_tile = (int)token_tile;
+  } else {
+    TORCH_CHECK(desc.size(0) >= first + (act ? 2 : 1));
+  }
+  if (row_scale.has_value() && row_scale->defined()) {
+    TORCH_CHECK(row_scale->scalar_type() == at::kFloat && row_scale->is_contiguous());
+    p.row_scale = row_scale->data_ptr<float>();
+  }
+  check(mmb_trellis_gemm(&p, cur_stream()), "trellis_gemm");
+}
+
 // ---- expert-parallel exchange (ep_comm.cu).  Descriptors are CPU int64 tensors of device addresses.
 // desc [8] = tables (device arrays of ep pointers) peer_recv_x, peer_recv_meta, peer_recv_cnt, peer_flags; then the local
 // send_cnt, counter, step, status
@@ -1169,6 +1215,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("tp_argmax", &tp_argmax);
   m.def("fp4_gemm", &fp4_gemm);
   m.def("fp4_gemm_swiglu", &fp4_gemm_swiglu);
+  m.def("trellis_gemm", &trellis_gemm);
   m.def("fp4_gemm_grouped_swiglu", &fp4_gemm_grouped_swiglu);
   m.def("fp4_gemm_rs", &fp4_gemm_rs);
   m.def("tp_rs_finish", &tp_rs_finish);

@@ -59,28 +59,30 @@ struct PipeShared {
   int abort_flag;
 };
 
-// WFMT 0: FP4 tile-layout weights expanded by warps 2..5.  WFMT 1: bf16 weights fetched by TMA.
+// WFMT 0: FP4 tile-layout weights expanded by the warps 2..17.  WFMT 1: bf16 weights fetched by TMA.  WFMT 2: trellis weights
+// (16 x 16 tiles of 2..8-bit codes, LSB-first bit stream) decoded by the same warps inside the main loop.
 template <int TN, int WFMT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const MmbFp4GemmParams p, const MmbBf16GemmParams pb) {
   using Cfg = GemmCfg<TN>;
+  constexpr bool QW = WFMT != 1;       // weights are expanded by the warps of this CTA (parameters in `p`)
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   PipeShared* ps = reinterpret_cast<PipeShared*>(tiles + (size_t)Cfg::kStages * Cfg::stage_bytes);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // ---- problem decode
-  const int M = WFMT == 0 ? p.M : pb.M, N = WFMT == 0 ? p.N : pb.N, K = WFMT == 0 ? p.K : pb.K;
-  int* status = WFMT == 0 ? p.status : pb.status;
+  const int M = QW ? p.M : pb.M, N = QW ? p.N : pb.N, K = QW ? p.K : pb.K;
+  int* status = QW ? p.status : pb.status;
   const int n0 = blockIdx.x * kTileRows;
-  const MmbAgWait& ag = WFMT == 0 ? p.ag : pb.ag;
+  const MmbAgWait& ag = QW ? p.ag : pb.ag;
   int tile_y = blockIdx.y;
   if (ag.flags != nullptr)      // all-gather fused into the load of x: start with the token tiles of this rank's own rows
     tile_y = (int)((blockIdx.y + (unsigned)((ag.rank * ag.rows) / TN)) % gridDim.y);
   int tok0 = tile_y * TN, tok_rows = TN, expert = 0;
   const int batch = blockIdx.z;
-  if (WFMT == 0 && p.tile_expert != nullptr) {
+  if (QW && p.tile_expert != nullptr) {
     if ((int)blockIdx.y >= *p.n_tiles) return;
     expert = p.tile_expert[blockIdx.y];
     tok0 = p.tile_row0[blockIdx.y];
@@ -90,7 +92,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
 
   if (tid == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
-      mbar_init(&ps->full_a[s], WFMT == 0 ? kExpandWarps / kExpandSplit : 1);      // the warps of one stage class (see the expansion loop)
+      mbar_init(&ps->full_a[s], QW ? kExpandWarps / kExpandSplit : 1);      // the warps of one stage class (see the expansion loop)
       mbar_init(&ps->full_b[s], 1);
       mbar_init(&ps->empty[s], 1);
     }
@@ -144,7 +146,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
         unsigned char* b_tile = a_tile + Cfg::a_bytes;
-        if (WFMT == 0) {
+        if (QW) {
           mbar_expect_tx(&ps->full_b[s], Cfg::b_bytes);
           tma_load_2d(b_tile, &tmap_x, &ps->full_b[s], i * kBK, tok0);
         } else {
@@ -292,6 +294,107 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&ps->full_a[s]);
       }
+    } else if (WFMT == 2) {
+      // Trellis weights decoded in the main loop.  A 16 x 16 tile is 32 * bits bytes, LSB-first; lane l owns the 8 codes of
+      // output row l / 2, input columns (l % 2) * 8 .. + 7, i.e. bytes [l * bits, (l + 1) * bits) of the tile - and those 8
+      // values are exactly one 16-byte chunk of the swizzled K-major A row, so every lane makes one shared-memory store per
+      // tile.  The four tiles of a k block are contiguous in memory; a lane fetches its bytes with aligned 32-bit loads
+      // (neighbouring lanes read neighbouring words) and funnels them into place.  w = (code - (2^bits - 1) / 2) * sv[o] *
+      // grid * scale[group, o] * su[i], rounded to bf16 once: the same value the stand-alone de-quantization kernel writes.
+      constexpr float kGrid = 1.24371088f;
+      const long long* desc0 = p.tr_desc + (long long)expert * p.tr_stride * 6;
+      const uint8_t* codes[kRB];
+      const float* scl[kRB];
+      const float* su[kRB];
+      float rowf[kRB], halfc[kRB];
+      int bits[kRB], gsz[kRB], outf[kRB], tin[kRB], orow[kRB], st_off[kRB];
+      bool rt_ok[kRB];
+#pragma unroll
+      for (int j = 0; j < kRB; ++j) {
+        const int blk = dw0 + j;
+        const int mat = p.tr_first + ((p.act && (blk & 4)) ? 1 : 0);
+        const long long* d = desc0 + mat * 6;
+        const int rt = p.act ? ((int)blockIdx.x * 4 + (blk & 3)) : ((n0 >> 4) + blk);
+        codes[j] = reinterpret_cast<const uint8_t*>(d[0]);
+        scl[j] = reinterpret_cast<const float*>(d[1]);
+        su[j] = reinterpret_cast<const float*>(d[2]);
+        const float* sv = reinterpret_cast<const float*>(d[3]);
+        outf[j] = (int)(d[4] & 0xffffffffll);
+        const int in_f = (int)(d[4] >> 32);
+        bits[j] = (int)(d[5] & 0xffffffffll);
+        gsz[j] = (int)(d[5] >> 32);
+        tin[j] = (in_f + 15) >> 4;
+        orow[j] = rt * 16 + (lane >> 1);
+        rt_ok[j] = orow[j] < outf[j];
+        rowf[j] = rt_ok[j] ? __ldg(sv + orow[j]) * kGrid : 0.f;
+        halfc[j] = (float)((1 << bits[j]) - 1) * 0.5f;
+        codes[j] += (long long)rt * tin[j] * (32 * bits[j]);          // first tile of this row block
+        const int r = blk * 16 + (lane >> 1);                          // row inside the 128-row A tile
+        st_off[j] = r * 128;
+      }
+      for (int i = kh; i < KB; i += kSplit) {
+        const int s = i % Cfg::kStages;
+        const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
+        // fetch this k block's bytes before waiting for the stage (the loads do not depend on the pipeline)
+        unsigned long long cw[kRB][4];
+        float sc[kRB][4];
+#pragma unroll
+        for (int j = 0; j < kRB; ++j) {
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt) {
+            const int ti = i * 4 + tt;
+            cw[j][tt] = 0ull;
+            sc[j][tt] = 0.f;
+            if (rt_ok[j] && ti < tin[j]) {
+              const uint8_t* tile = codes[j] + (long long)ti * (32 * bits[j]);
+              const int o = lane * bits[j], lo = o & 3;
+              const uint32_t* w = reinterpret_cast<const uint32_t*>(tile + (o - lo));
+              const int need = lo + bits[j];                            // bytes from the first aligned word on
+              const uint32_t w0 = __ldg(w), w1 = need > 4 ? __ldg(w + 1) : 0u, w2 = need > 8 ? __ldg(w + 2) : 0u;
+              unsigned long long v = ((unsigned long long)w1 << 32) | w0;
+              v >>= 8 * lo;
+              if (lo && need > 8) v |= (unsigned long long)w2 << (64 - 8 * lo);
+              cw[j][tt] = v;
+              sc[j][tt] = __ldg(scl[j] + (long long)((ti * 16) / gsz[j]) * outf[j] + orow[j]) * rowf[j];
+            }
+          }
+        }
+        if (!mbar_wait(&ps->empty[s], ph ^ 1u, abort_flag)) {
+          if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 3);
+          ok = false;
+          break;
+        }
+        unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
+#pragma unroll
+        for (int j = 0; j < kRB; ++j) {
+          const unsigned mask = (1u << bits[j]) - 1u;
+          const int r7 = (lane >> 1) & 7;
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt) {
+            const int col0 = (i * 4 + tt) * 16 + (lane & 1) * 8;
+            uint32_t o4[4] = {0u, 0u, 0u, 0u};
+            if (rt_ok[j] && (i * 4 + tt) < tin[j]) {
+              const float4 s0 = __ldg(reinterpret_cast<const float4*>(su[j] + col0));
+              const float4 s1 = __ldg(reinterpret_cast<const float4*>(su[j] + col0 + 4));
+              const float sf[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+              const unsigned long long v = cw[j][tt];
+              float wv[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) wv[e] = ((float)((unsigned)(v >> (e * bits[j])) & mask) - halfc[j]) * sc[j][tt] * sf[e];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const bf162 pr = __floats2bfloat162_rn(wv[2 * e], wv[2 * e + 1]);
+                o4[e] = *reinterpret_cast<const uint32_t*>(&pr);
+              }
+            }
+            const int chunk = tt * 2 + (lane & 1);
+            *reinterpret_cast<uint4*>(a_tile + st_off[j] + ((chunk ^ r7) * 16)) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ps->full_a[s]);
+      }
     }
     // ---- epilogue: TMEM -> registers -> global
     if (ok) ok = mbar_wait(&ps->acc_full, 0u, abort_flag);
@@ -301,9 +404,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       tc_fence_after();
       const int q = warp & 3;                    // TMEM lane quarter this warp may access
       const int n = n0 + q * 32 + lane;
-      const int ldo = WFMT == 0 ? p.ldo : pb.ldo;
+      const int ldo = QW ? p.ldo : pb.ldo;
       const int c_first = ((warp - 2) >> 2) * 32; // the warps of a quarter take the 32-column chunks round-robin
-      if (WFMT == 0 && p.act) {
+      if (QW && p.act) {
         // fused SwiGLU: lanes 0..63 hold gate rows, lanes 64..127 the matching up rows.  The four warps that share a
         // 32-column chunk (one per lane quarter) pair up through shared memory: the up quarters park their values in a
         // column-major slab of the (now idle) pipeline stages, the gate quarters read them back and store silu(g) * u.
@@ -349,15 +452,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             const int r = c0 + j;
             if (r < tok_rows && tok0 + r < M) {
               float f = __uint_as_float(v[j]);
-              if (WFMT == 0 && p.rs_peer_bufs != nullptr) {
+              if (QW && p.rs_peer_bufs != nullptr) {
                 // reduce-scatter epilogue: the partial goes to the rank that owns this token row
                 const int row = tok0 + r, owner = row / p.rs_rows;
                 p.rs_peer_bufs[owner][((long long)p.rs_rank * p.rs_rows + (row - owner * p.rs_rows)) * N + n] = f;
-              } else if (WFMT == 0 && p.out_rows != nullptr) {
+              } else if (QW && p.out_rows != nullptr) {
                 // scatter epilogue: the row's destination (possibly in a peer's memory) comes from a device table
                 bf16* dst = reinterpret_cast<bf16*>(p.out_rows[tok0 + r]);
                 if (dst != nullptr) dst[n] = __float2bfloat16(f);
-              } else if (WFMT == 0) {
+              } else if (QW) {
                 if (p.row_scale) f *= p.row_scale[tok0 + r];
                 reinterpret_cast<bf16*>(p.out)[(long long)(tok0 + r) * ldo + n] = __float2bfloat16(f);
               } else {
@@ -370,10 +473,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
       }
       }
-      if (WFMT == 0 && p.out_rows != nullptr) __threadfence_system();     // peer stores ordered before the grid completes
+      if (QW && p.out_rows != nullptr) __threadfence_system();     // peer stores ordered before the grid completes
     }
   }
-  if (WFMT == 0 && p.rs_peer_bufs != nullptr) {
+  if (QW && p.rs_peer_bufs != nullptr) {
     // all threads: make the peer stores visible system wide, then the last CTA of the grid raises the flags
     TpOut tout;
     tout.peer_slots = nullptr;
@@ -471,6 +574,30 @@ MMB_API int mmb_fp4_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
     case 64: return launch_gemm<64, 0>(mx, mx, p, pb, grid, stream);
     case 128: return launch_gemm<128, 0>(mx, mx, p, pb, grid, stream);
     default: return launch_gemm<256, 0>(mx, mx, p, pb, grid, stream);
+  }
+}
+
+// Trellis weights (WFMT 2): `tr_desc` is a device table of MmbTrellisMat rows (6 x int64 each: codes, scales, su, sv,
+// out | in << 32, bits | group << 32); matrix index = expert * tr_stride + tr_first (+ 1 for the up half with act = 1).
+MMB_API int mmb_trellis_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
+  using namespace mmb;
+  MmbFp4GemmParams p = *pp;
+  if (p.M <= 0 || p.N <= 0) return 0;
+  if (p.tr_desc == nullptr || p.K % 64 != 0 || p.Kx % 8 != 0 || p.Kx > p.K || (p.act != 0 && p.act != 1)) return (int)cudaErrorInvalidValue;
+  if (p.act == 1 && ((p.N & 127) != 0 || p.out_rows != nullptr)) return (int)cudaErrorInvalidValue;
+  if (p.rs_peer_bufs != nullptr || p.ag.flags != nullptr) return (int)cudaErrorInvalidValue;
+  const bool grouped = p.tile_expert != nullptr;
+  const int TN = pick_tn(grouped ? (p.token_tile ? p.token_tile : 128) : p.M, p.token_tile);
+  CUtensorMap mx;
+  int e = make_tmap_2d(&mx, p.x, p.Kx, p.M, p.Kx, TN);
+  if (e) return e;
+  MmbBf16GemmParams pb{};
+  dim3 grid((p.N + kTileRows - 1) / kTileRows, grouped ? p.max_tiles : (p.M + TN - 1) / TN, 1);
+  switch (TN) {
+    case 32: return launch_gemm<32, 2>(mx, mx, p, pb, grid, stream);
+    case 64: return launch_gemm<64, 2>(mx, mx, p, pb, grid, stream);
+    case 128: return launch_gemm<128, 2>(mx, mx, p, pb, grid, stream);
+    default: return launch_gemm<256, 2>(mx, mx, p, pb, grid, stream);
   }
 }
 

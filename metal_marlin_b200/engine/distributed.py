@@ -118,7 +118,7 @@ class TPCoordinator:
     def announce_prefill(self, a: Dict[str, list]) -> None:
         n_seq, width = len(a["ctx"]), len(a["tables"][0])
         flat = a["ids"] + a["pos"] + a["slots"] + a["cu"] + a["ctx"] + [b for t in a["tables"] for b in t]
-        self._header(KIND_PREFILL, len(a["ids"]), n_seq, width)
+        self._header(KIND_PREFILL, len(a["ids"]), n_seq, width, int(a.get("all_rows", 0)))
         dist.broadcast(torch.tensor(flat, dtype=torch.int64), src=self.leader, group=self.group)
 
     def announce_decode(self, bk: _DecodeBucket) -> None:
@@ -157,7 +157,9 @@ def tp_follow(engine: LLMEngine, ctrl_group, leader: int = 0) -> int:
                 T, n_seq, width = int(h[1]), int(h[2]), int(h[3])
                 flat = torch.empty(3 * T + 2 * n_seq + 1 + n_seq * width, dtype=torch.int64)
                 dist.broadcast(flat, src=leader, group=ctrl_group)
-                engine._exec_prefill(unpack_prefill(flat, T, n_seq, width))
+                arrays = unpack_prefill(flat, T, n_seq, width)
+                arrays["all_rows"] = int(h[4])
+                engine._exec_prefill(arrays)
                 engine._check_device_status()
             elif kind == KIND_DECODE:
                 bk = engine._bucket(int(h[1]))

@@ -166,6 +166,9 @@ class LLMEngine:
         self.model = model
         self.cfg = config or EngineConfig()
         self.coordinator = coordinator
+        self.spec = None             # speculative decoding inside the batch loop (enable_speculative)
+        self.spec_proposed = 0
+        self.spec_accepted = 0
         self.lockstep = None         # set by an expert-parallel group: passes are agreed between the ranks (engine/distributed.py)
         self._tracked: Dict[str, RunningRequest] = {}
         self._filler_block: Optional[int] = None
@@ -255,12 +258,15 @@ class LLMEngine:
             if do_decode:
                 if ep is not None:
                     ep.pass_tokens = n_dec
-                sampled.update(self._run_decode(out.decode) if out.decode else self._filler_decode())
+                if self.spec is not None and out.decode and self.lockstep is None:
+                    sampled.update(self._run_decode_speculative(out.decode))
+                else:
+                    sampled.update(self._run_decode(out.decode) if out.decode else self._filler_decode())
             if out.is_empty:
                 return []
             finished = self.scheduler.step(out, sampled)
             self.iterations += 1
-            self.tokens_generated += len(sampled)
+            self.tokens_generated += sum(len(v) if isinstance(v, (list, tuple)) else 1 for v in sampled.values())
             return finished
 
     def run_until_done(self, max_iters: int = 1 << 30) -> None:
@@ -329,14 +335,16 @@ class LLMEngine:
 
     def _exec_prefill(self, a: Dict[str, list]) -> torch.Tensor:
         """Runs the prompt pass described by ``a`` on this rank's model shard; returns the full-vocabulary logits of the
-        last token of every chunk.  Every rank of a tensor-parallel group runs this with the same arrays."""
+        last token of every chunk (of every token when ``a["all_rows"]`` is set: speculative verification).  Every rank of
+        a tensor-parallel group runs this with the same arrays."""
         dev = self.model.device
         meta = BatchMeta(positions=torch.tensor(a["pos"], dtype=torch.int32, device=dev),
                          slots=torch.tensor(a["slots"], dtype=torch.int64, device=dev),
                          block_tables=torch.tensor(a["tables"], dtype=torch.int32, device=dev),
                          ctx_lens=torch.tensor(a["ctx"], dtype=torch.int32, device=dev), decode=False, cu_seqlens=list(a["cu"]),
                          ctx_lens_host=list(a["ctx"]))
-        logits = self.model.forward(torch.tensor(a["ids"], dtype=torch.int64, device=dev), self.kv, meta, last_only=True)
+        logits = self.model.forward(torch.tensor(a["ids"], dtype=torch.int64, device=dev), self.kv, meta,
+                                    last_only=not a.get("all_rows", 0))
         return self.model.full_logits(logits)
 
     def _run_prefill(self, out: SchedulerOutput) -> Dict[str, int]:
@@ -357,6 +365,97 @@ class LLMEngine:
         toks = self._sample(logits[rows].contiguous(), reqs)
         self._check_device_status()
         return {rr.id: int(t) for rr, t in zip(reqs, toks)}
+
+    # ------------------------------------------------------------------ speculative decoding in the batch loop
+    def enable_speculative(self, draft="ngram", num_speculative_tokens: int = 4, adaptive: bool = True, **draft_kw) -> None:
+        """Every decoding request drafts up to ``num_speculative_tokens`` tokens per step (``draft``: ``"ngram"``, a callable
+        ``request -> DraftModel``, or a small causal LM shared by all requests' drafts); one flattened target pass verifies
+        the drafts of the whole batch (k + 1 positions per sequence, paged attention over each sequence's own context),
+        accepted tokens are kept, the cache rows of rejected ones are given back.  Requests that sample with a temperature
+        use rejection sampling against the draft distribution where the draft provides one, else fall back to one token."""
+        from ..spec.adaptive import AdaptiveSpeculationController
+        from ..spec.draft import DraftModel, NGramDraft, SmallModelDraft
+        if draft == "ngram":
+            make = lambda rr: NGramDraft(**draft_kw)
+        elif callable(draft) and not isinstance(draft, DraftModel):
+            make = draft
+        elif isinstance(draft, DraftModel):
+            raise ValueError("pass a factory (request -> DraftModel): drafts keep per-request state")
+        else:        # a small causal LM: every request gets its own draft cache over the shared weights
+            make = lambda rr, lm=draft: SmallModelDraft(lm, max_len=self.cfg.max_model_len, block_size=self.cfg.block_size, **draft_kw)
+        self.spec = {"make": make, "k": int(num_speculative_tokens),
+                     "ctrl": (lambda: AdaptiveSpeculationController(depth=num_speculative_tokens)) if adaptive else None}
+
+    def disable_speculative(self) -> None:
+        self.spec = None
+
+    def _run_decode_speculative(self, reqs: List[RunningRequest]) -> Dict[str, list]:
+        from ..kv.paged import OutOfBlocks
+        bs = self.cfg.block_size
+        plan = []
+        for rr in reqs:
+            if not hasattr(rr, "draft") or rr.draft is None:
+                rr.draft = self.spec["make"](rr)
+                rr.spec_ctrl = self.spec["ctrl"]() if self.spec["ctrl"] else None
+            n = self.cache.table.num_tokens(rr.id)              # includes the slot of this step's input token
+            room = min(rr.req.max_new_tokens - len(rr.output_ids) - 1, self.cfg.max_model_len - n - 1)
+            k = max(0, min(rr.spec_ctrl.depth if rr.spec_ctrl else self.spec["k"], room))
+            sp = rr.req.sampling
+            drafts: List[int] = []
+            if k > 0 and sp.temperature <= 0 and sp.repetition_penalty == 1.0:
+                prop = rr.draft.propose(rr.all_ids, k)
+                drafts = [] if prop.parents is not None else list(prop.tokens)[:k]
+            if drafts:
+                try:
+                    self.cache.append(rr.id, len(drafts))
+                except OutOfBlocks:
+                    drafts = []
+            plan.append((rr, n, drafts))
+        arrays = {"ids": [], "pos": [], "slots": [], "cu": [0], "ctx": [], "tables": [], "all_rows": 1}
+        for rr, n, drafts in plan:
+            t = 1 + len(drafts)
+            arrays["ids"].extend([rr.output_ids[-1]] + drafts)
+            arrays["pos"].extend(range(n - 1, n - 1 + t))
+            arrays["slots"].extend(self.cache.table.slot_mapping(rr.id, n - 1, t))
+            arrays["cu"].append(arrays["cu"][-1] + t)
+            arrays["ctx"].append(n - 1 + t)
+            arrays["tables"].append(self.cache.table.block_table(rr.id))
+        width = max(len(t) for t in arrays["tables"])
+        arrays["tables"] = [t + [0] * (width - len(t)) for t in arrays["tables"]]
+        if self.coordinator is not None:
+            self.coordinator.announce_prefill(arrays)
+        logits = self._exec_prefill(arrays)                      # [sum(k_i + 1), V]
+        self._check_device_status()
+        # requests that sample draw their (single) token from their row; greedy rows are verified against the drafts
+        target = ops.argmax(logits).tolist()
+        out: Dict[str, list] = {}
+        row = 0
+        sampled_rows, sampled_reqs = [], []
+        for rr, n, drafts in plan:
+            t = 1 + len(drafts)
+            if rr.req.sampling.temperature > 0 or rr.req.sampling.repetition_penalty != 1.0:
+                sampled_rows.append(row)
+                sampled_reqs.append(rr)
+                row += t
+                continue
+            a = 0
+            while a < len(drafts) and target[row + a] == drafts[a]:
+                a += 1
+            out[rr.id] = drafts[:a] + [target[row + a]]
+            rr.spec_proposed += len(drafts)
+            rr.spec_accepted += a
+            self.spec_proposed += len(drafts)
+            self.spec_accepted += a
+            if rr.spec_ctrl is not None and drafts:
+                rr.spec_ctrl.update(len(drafts), a)
+            if a < len(drafts):                                  # give back the cache rows of the rejected drafts
+                self.cache.table.truncate(rr.id, n + a)
+            row += t
+        if sampled_rows:
+            toks = self._sample(logits[sampled_rows].contiguous(), sampled_reqs)
+            for rr, tk in zip(sampled_reqs, toks):
+                out[rr.id] = [int(tk)]
+        return out
 
     def _sample(self, logits: torch.Tensor, reqs: List[RunningRequest]) -> List[int]:
         dev = logits.device
@@ -473,4 +572,7 @@ class LLMEngine:
     def stats(self) -> dict:
         s = self.scheduler.stats()
         s.update(iterations=self.iterations, tokens_generated=self.tokens_generated, last_error=self.last_error)
+        if self.spec is not None:
+            s.update(spec_proposed=self.spec_proposed, spec_accepted=self.spec_accepted,
+                     spec_acceptance_rate=self.spec_accepted / max(1, self.spec_proposed))
         return s

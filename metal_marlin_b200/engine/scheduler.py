@@ -207,8 +207,9 @@ class BatchScheduler:
 
     # ------------------------------------------------------------------ after the model ran
     def step(self, out: SchedulerOutput, sampled: Dict[str, int]) -> List[RunningRequest]:
-        """Account for an executed iteration.  ``sampled`` maps request id -> new token for every
-        decode request and for every request whose prefill completed in this iteration."""
+        """Account for an executed iteration.  ``sampled`` maps request id -> new token (or, after a speculative step, the
+        list of tokens the step produced) for every decode request and for every request whose prefill completed in this
+        iteration."""
         finished = []
         for ch in out.prefill:
             rr = ch.request
@@ -220,8 +221,12 @@ class BatchScheduler:
             rr = self.requests[rid]
             if rr.status is not RequestStatus.RUNNING:
                 continue
-            rr.append_token(tok)
-            reason = rr.should_stop()
+            reason = None
+            for t in (tok if isinstance(tok, (list, tuple)) else (tok,)):
+                rr.append_token(t)
+                reason = rr.should_stop()
+                if reason is not None:
+                    break
             if reason is None and rr.req.timeout_s is not None and time.monotonic() - rr.arrival > rr.req.timeout_s:
                 reason = "timeout"
             if reason is not None:

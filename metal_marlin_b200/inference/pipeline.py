@@ -82,6 +82,7 @@ class MMFP4Pipeline:
         self._results: "OrderedDict[tuple, str]" = OrderedDict()
         self._result_cache_size = result_cache_size
         self.speculative = None
+        self._spec_args = None
         self.stats = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0}
 
     # ------------------------------------------------------------------ construction
@@ -289,18 +290,43 @@ class MMFP4Pipeline:
 
     # ------------------------------------------------------------------ speculative decoding
     def enable_speculative_decoding(self, draft="ngram", num_speculative_tokens: int = 4, **kw) -> None:
-        """Attach a draft source.  ``draft``: ``"ngram"``, ``"mtp"``, a small :class:`MMFP4ForCausalLM`, or
-        any object implementing ``spec.draft.DraftModel``."""
-        from ..spec.engine import SpeculativeEngine, make_draft
-        self.speculative = SpeculativeEngine(self.model, make_draft(draft, self.model, **kw),
-                                             num_speculative_tokens=num_speculative_tokens)
+        """Attach a draft source.  ``draft``: ``"ngram"``, ``"mtp"``, ``"eagle"``, the path of a small checkpoint, a small
+        :class:`MMFP4ForCausalLM`, or any object implementing ``spec.draft.DraftModel``.
+
+        N-gram and small-model drafts run inside the continuous-batching engine: every generate / stream / server call
+        then drafts and verifies per step, batched over all running requests.  Drafts that need the target's hidden state
+        (MTP, EAGLE trees) serve :meth:`speculative_generate` (one request at a time)."""
+        from ..spec.draft import DraftModel
+        self._spec_args = (draft, num_speculative_tokens, kw)
+        self.speculative = None
+        core = getattr(self.engine, "engine", self.engine)          # a multi-GPU engine wraps the rank's LLMEngine
+        if isinstance(draft, str) and draft not in ("ngram", "mtp", "eagle"):
+            draft = MMFP4ForCausalLM.from_pretrained(draft, str(self.device))
+            self._spec_args = (draft, num_speculative_tokens, kw)
+        if draft == "ngram" or isinstance(draft, MMFP4ForCausalLM):
+            core.enable_speculative(draft, num_speculative_tokens, **kw)
+            self._results.clear()
+        elif isinstance(draft, DraftModel) or draft in ("mtp", "eagle"):
+            self._ensure_spec_engine()
+
+    def _ensure_spec_engine(self):
+        if self.speculative is None:
+            if getattr(self, "_spec_args", None) is None:
+                raise RuntimeError("call enable_speculative_decoding() first")
+            from ..spec.engine import SpeculativeEngine, make_draft
+            draft, k, kw = self._spec_args
+            self.speculative = SpeculativeEngine(self.model, make_draft(draft, self.model, **kw), num_speculative_tokens=k)
+        return self.speculative
 
     def speculative_generate(self, prompt: str, max_new_tokens: int = 64, temperature: float = 0.0, seed: int = 0):
-        if self.speculative is None:
-            raise RuntimeError("call enable_speculative_decoding() first")
-        ids, stats = self.speculative.generate(self.encode(prompt), max_new_tokens, temperature=temperature, seed=seed,
-                                               eos_ids=self.eos_ids)
+        spec = self._ensure_spec_engine()
+        ids, stats = spec.generate(self.encode(prompt), max_new_tokens, temperature=temperature, seed=seed, eos_ids=self.eos_ids)
         return self.tokenizer.decode([t for t in ids if t not in self.eos_ids], skip_special_tokens=True), stats
+
+    def speculative_stats(self) -> dict:
+        """Acceptance statistics of the in-engine speculative decoding."""
+        st = getattr(self.engine, "engine", self.engine).stats()
+        return {k: st[k] for k in ("spec_proposed", "spec_accepted", "spec_acceptance_rate") if k in st}
 
     # ------------------------------------------------------------------ perplexity
     @torch.no_grad()

@@ -140,9 +140,12 @@ class TrellisLinear:
         self.codes = tw.indices.reshape(-1)[1:].contiguous().to(device)
         self.scales = tw.scales.float().contiguous().to(device)
         self.su, self.sv = su.contiguous().to(device), sv.contiguous().to(device)
+        if self.codes.data_ptr() % 16:       # the code stream starts one byte into its checkpoint tensor: the kernels read aligned words
+            self.codes = self.codes.clone()
         self.bias = None if bias is None else bias.to(device, torch.bfloat16)
         self.device = device
         self._deq = None
+        self._desc = None
 
     @classmethod
     def from_float(cls, w: torch.Tensor, bits: int = 4, group_size: int = 128, device=None):
@@ -157,6 +160,13 @@ class TrellisLinear:
         x2 = x.reshape(-1, shape[-1]).to(torch.bfloat16).contiguous()
         if x2.shape[0] <= DECODE_MAX_M:
             y = ops.trellis_gemv(x2, self.codes, self.scales, self.su, self.sv, self.out_features, self.bits, self.group_size)
+        elif ops.trellis_gemm_ok(x2, self.in_features, self.group_size):
+            # tensor cores: the codes are decoded inside the GEMM's main loop, no bf16 copy of the matrix exists
+            if self._desc is None:
+                self._desc = torch.tensor([ops.trellis_desc_row(self.codes, self.scales, self.su, self.sv, self.out_features,
+                                                                self.in_features, self.bits, self.group_size)],
+                                          dtype=torch.int64).to(x2.device)
+            y = ops.trellis_gemm(x2, self._desc, self.out_features, self.in_features)
         else:
             w = self.dequantize(torch.bfloat16)          # transient: the bf16 copy is not kept between calls
             y = _bf16_matmul(x2, w)

@@ -765,6 +765,32 @@ def trellis_dequant(codes, scales, su, sv, out_f: int, in_f: int, bits: int, gro
     return out
 
 
+def trellis_desc_row(codes, scales, su, sv, out_f: int, in_f: int, bits: int, group_size: int):
+    """One matrix descriptor (six int64) of the trellis kernels: codes, scales, su, sv, out | in << 32, bits | group << 32."""
+    return [codes.data_ptr(), scales.data_ptr(), su.data_ptr(), sv.data_ptr(), out_f | (in_f << 32), bits | (group_size << 32)]
+
+
+def trellis_gemm_ok(x, in_f: int, group_size: int) -> bool:
+    """Whether the tensor-core trellis GEMM (codes decoded inside the main loop) takes this input."""
+    return bool(_use_native(x) and x.dtype == torch.bfloat16 and in_f % 64 == 0 and group_size % 16 == 0 and not NO_TCGEN05)
+
+
+def trellis_gemm(x, desc, N: int, Kin: int, *, act: int = 0, first: int = 0, stride: int = 1, tiles=None, token_tile: int = 0,
+                 row_scale=None, out=None):
+    """``out = x @ W^T`` with trellis weights decoded in the tcgen05 GEMM's main loop (2..8 bits, mixed per matrix).
+    ``desc``: device int64 ``[n_mats, 6]`` (:func:`trellis_desc_row`).  ``act=1``: matrices ``first`` (gate) and
+    ``first + 1`` (up), SwiGLU in the epilogue, ``out [M, N / 2]``.  ``tiles = (tile_expert, tile_row0, tile_rows, n_tiles)``:
+    grouped mode over rows sorted by expert (matrix ``expert * stride + first``)."""
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty(M, N // 2 if act else N, dtype=torch.bfloat16, device=x.device)
+    te = tr0 = trw = nt = None
+    if tiles is not None:
+        te, tr0, trw, nt = tiles
+    K.mmb200.trellis_gemm(x, desc, out, N, Kin, act, first, stride, te, tr0, trw, nt, token_tile, row_scale, gemm_status(x.device))
+    return out
+
+
 def trellis_gemv(x, codes, scales, su, sv, out_f: int, bits: int, group_size: int, out=None):
     """``x [M, in] @ W^T`` for small M straight from the bit stream."""
     in_f = x.shape[1]

@@ -110,6 +110,11 @@ def _trellis_desc(bank: GenericExpertBank, n_routed: int, device):
     return desc
 
 
+def ops_no_tc() -> bool:
+    from . import NO_TCGEN05
+    return NO_TCGEN05
+
+
 def moe_forward(x, bank: GenericExpertBank, ids, weights, *, n_shared=0, shared_base=0, norm_w=None, eps=1e-6, out_add=None):
     """Routed + shared experts on generic (trellis, codebook, dense) weights.  Decode-size batches on trellis banks run the
     routed experts in two launches that read the expert ids from device memory (mixed bits per expert and matrix; no
@@ -129,6 +134,34 @@ def moe_forward(x, bank: GenericExpertBank, ids, weights, *, n_shared=0, shared_
                              weights.to(torch.float32).contiguous(), h, y, H, I)
         acc = y.view(T, topk, H).sum(1)
         return _finish_shared(acc, xin, bank, n_shared, shared_base, out_add)
+    gdesc = _trellis_desc(bank, n_routed, x.device) if (_use_native(x) and x.dtype == torch.bfloat16) else None
+    if gdesc is not None and gdesc[1] % 64 == 0 and gdesc[2] % 64 == 0 and not ops_no_tc():
+        # prompt-size batches: counting sort by expert and a tile list on the device, then two grouped tensor-core GEMMs that
+        # decode the experts' codes (any bit width per expert and matrix) inside their main loops: gate|up with SwiGLU in the
+        # epilogue, down with the routing weight; no host synchronisation, no bf16 copy of an expert
+        from . import trellis_gemm
+        mats, H, I = gdesc
+        topk = ids.shape[1]
+        n = T * topk
+        dev = x.device
+        avg = n / max(1, n_routed)
+        token_tile = 32 if avg <= 24 else (64 if avg <= 48 else (128 if avg <= 160 else 256))
+        max_tiles = (n + token_tile - 1) // token_tile + n_routed
+        order = torch.empty(n, dtype=torch.int32, device=dev)
+        inv = torch.empty(n, dtype=torch.int32, device=dev)
+        t_e = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+        t_r0, t_rows = torch.empty_like(t_e), torch.empty_like(t_e)
+        n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+        K.mmb200.moe_group(ids.to(torch.int32).reshape(-1).contiguous(), n_routed, token_tile, order, inv, t_e, t_r0, t_rows, n_tiles)
+        xs = torch.empty(n, H, dtype=torch.bfloat16, device=dev)
+        K.mmb200.moe_gather(xin if xin.stride(1) == 1 else xin.contiguous(), order, xs, topk)
+        tiles = (t_e, t_r0, t_rows, n_tiles)
+        h = trellis_gemm(xs, mats, 2 * I, H, act=1, first=0, stride=3, tiles=tiles, token_tile=token_tile)
+        rs = weights.reshape(-1).to(torch.float32).index_select(0, order.clamp_min(0).long()).contiguous()
+        y = trellis_gemm(h, mats, H, I, act=0, first=2, stride=3, tiles=tiles, token_tile=token_tile, row_scale=rs)
+        acc = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        K.mmb200.moe_combine(y, inv, None, None, acc, topk)
+        return _finish_shared(acc.to(torch.float32), xin, bank, n_shared, shared_base, out_add)
     acc = torch.zeros(T, bank.down[0].out_features, dtype=torch.float32, device=x.device)
     ids_l = ids.long()
     for e in ids_l.unique().tolist():

@@ -200,5 +200,53 @@ def test_trellis_moe_device_path_matches_host_loop(T, topk, monkeypatch):
     got = generic.moe_forward(x, bank, ids, wts, n_shared=1, shared_base=E, norm_w=nw, out_add=add)
     assert bank._trellis_desc[1] is not None          # the device path was taken
     monkeypatch.setattr(generic, "TRELLIS_MOE_MAX_T", 0)
+    monkeypatch.setattr(generic, "ops_no_tc", lambda: True)          # host loop over experts
     want = generic.moe_forward(x, bank, ids, wts, n_shared=1, shared_base=E, norm_w=nw, out_add=add)
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("M,N,K,gs", [(33, 128, 64, 16), (200, 144, 192, 64), (1030, 768, 2048, 128), (64, 1000, 512, 32)])
+def test_trellis_gemm_decodes_codes_in_the_main_loop(bits, M, N, K, gs):
+    """Tensor-core GEMM on trellis weights (codes unpacked inside the tcgen05 main loop, every bit width, tile-boundary shapes)
+    against x @ dequant(W)^T: the kernel rounds each weight to bf16 exactly like the de-quantization kernel, so only the
+    accumulation order differs."""
+    from metal_marlin_b200.layers import TrellisLinear
+    torch.manual_seed(bits * 100 + M)
+    lin = TrellisLinear.from_float(torch.randn(N, K) * 0.05, bits=bits, group_size=gs, device=DEV)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    assert ops.trellis_gemm_ok(x, K, gs)
+    y = lin(x)
+    assert ops.check_status(DEV) == 0
+    ref = x.float() @ lin.dequantize(torch.float32).t()
+    err = float((y.float() - ref).abs().max() / ref.abs().max())
+    assert err < 1e-2, err
+
+
+@pytest.mark.parametrize("T,topk", [(40, 2), (300, 4), (1500, 3)])
+def test_trellis_moe_grouped_tensor_core_path(T, topk, monkeypatch):
+    """Prompt-size trellis MoE: device-side grouping + two grouped tensor-core GEMMs with mixed bits per expert and matrix
+    (SwiGLU in the first epilogue, routing weight in the second) against the host loop over experts."""
+    from metal_marlin_b200.layers import TrellisLinear
+    from metal_marlin_b200.ops import generic
+    torch.manual_seed(T)
+    E, H, I = 6, 256, 128
+    bits = [2, 3, 4, 5, 6, 8]
+    gus, dws = [], []
+    for e in range(E):
+        g = TrellisLinear.from_float(torch.randn(I, H) * 0.05, bits=bits[e], group_size=64, device=DEV)
+        u = TrellisLinear.from_float(torch.randn(I, H) * 0.05, bits=bits[(e + 1) % E], group_size=64, device=DEV)
+        gus.append(generic.CatWeight([g, u]))
+        dws.append(TrellisLinear.from_float(torch.randn(H, I) * 0.05, bits=bits[(e + 2) % E], group_size=64, device=DEV))
+    bank = generic.GenericExpertBank(gus, dws)
+    x = (torch.randn(T, H, device=DEV) * 0.5).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, device=DEV)[:topk] for _ in range(T)]).to(torch.int32)
+    ids[0, 0] = -1
+    wts = torch.rand(T, topk, device=DEV)
+    launches = ops.launch_count()
+    got = generic.moe_forward(x, bank, ids, wts)
+    assert ops.launch_count() - launches <= 8 and ops.check_status(DEV) == 0      # group, gather, two GEMMs, combine (+ norm)
+    monkeypatch.setattr(generic, "ops_no_tc", lambda: True)
+    want = generic.moe_forward(x, bank, ids, wts)
+    err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
+    assert err < 3e-2, err

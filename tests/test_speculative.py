@@ -111,3 +111,59 @@ def test_pipeline_speculative_api():
     text, stats = pipe.speculative_generate("hello hello hello", max_new_tokens=12)
     assert text == plain and stats.tokens == 12
     pipe.close()
+
+
+@pytest.mark.parametrize("draft_kind", ["ngram", "small"])
+def test_speculative_decoding_inside_the_batch_engine(draft_kind):
+    """Speculative slots in the continuous-batching loop: several concurrent requests draft and verify per step in one
+    flattened target pass; greedy output equals plain decoding token for token, rejected drafts give their cache rows back,
+    and the engine reports acceptance."""
+    from metal_marlin_b200.engine.engine import EngineConfig, LLMEngine
+    from metal_marlin_b200.engine.session import SamplingParams
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM
+    lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    prompts = [[5, 6, 7, 5, 6, 7, 5, 6], list(range(1, 40)), [9, 9, 9, 9], [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5], [7] * 20, [11, 12, 13],
+               list(range(50, 90)), [2, 4, 2, 4, 2, 4]]
+    cfg = EngineConfig(num_kv_blocks=96, block_size=16, max_model_len=128, max_chunk=128, max_prefill_tokens=512, use_cuda_graphs=False)
+    want = LLMEngine(lm.model, cfg).generate(prompts, max_new_tokens=20)
+    eng = LLMEngine(lm.model, cfg)
+    draft = "ngram" if draft_kind == "ngram" else MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    eng.enable_speculative(draft, num_speculative_tokens=4)
+    got = eng.generate(prompts, max_new_tokens=20)
+    assert got == want
+    st = eng.stats()
+    assert st["spec_proposed"] > 0 and 0.0 <= st["spec_acceptance_rate"] <= 1.0
+    if draft_kind == "small":        # the draft IS the target: everything it proposes is accepted, fewer target passes are needed
+        assert st["spec_acceptance_rate"] == 1.0 and eng.iterations < LLMEngine(lm.model, cfg).iterations + 12
+    assert eng.cache.alloc.num_allocated == len(eng.cache.prefix.table)      # rolled-back rows and finished requests freed their blocks
+    # sampled requests ride along (one token per step) beside greedy ones
+    mixed = [eng.add_request(__import__("metal_marlin_b200.engine.request", fromlist=["GenerationRequest"]).GenerationRequest(
+        list(p), 6, SamplingParams(temperature=0.7 if i % 2 else 0.0, seed=i))) for i, p in enumerate(prompts[:4])]
+    eng.run_until_done()
+    assert all(len(r.output_ids) == 6 for r in mixed)
+    assert mixed[0].output_ids == want[0][:6] and mixed[2].output_ids == want[2][:6]
+
+
+def test_server_engine_with_ngram_speculation_batches_concurrent_requests(monkeypatch):
+    """``serve --speculative ngram``: eight concurrent completions go through the continuous-batching engine with
+    speculative slots and return the same greedy text as the plain server engine; the engine reports acceptance."""
+    import asyncio
+
+    from metal_marlin_b200.serving.engine import EngineConfig, ServingEngine
+    from metal_marlin_b200.serving.openai_schemas import CompletionRequest
+    monkeypatch.setenv("METAL_MARLIN_MOCK_MODEL", "1")
+    prompts = [f"repeat after me {i} {i} {i} again {i} {i} {i}" for i in range(8)]
+
+    async def run(engine):
+        reqs = [CompletionRequest(model="mock-model", prompt=p, max_tokens=24, temperature=0.0) for p in prompts]
+        return [r.choices[0].text for r in await asyncio.gather(*[engine.completion(r) for r in reqs])]
+
+    plain = ServingEngine(EngineConfig(max_model_len=512, num_kv_blocks=256, request_timeout=60))
+    want = asyncio.run(run(plain))
+    plain.shutdown()
+    spec = ServingEngine(EngineConfig(max_model_len=512, num_kv_blocks=256, request_timeout=60, speculative="ngram"))
+    got = asyncio.run(run(spec))
+    st = spec.pipeline.speculative_stats()
+    spec.shutdown()
+    assert got == want
+    assert st["spec_proposed"] > 0 and 0.0 <= st["spec_acceptance_rate"] <= 1.0
