@@ -749,7 +749,7 @@ static void fp4_gemm_grouped_impl(const Tensor& x, const Tensor& qw, const Tenso
 // Grouped: matrices [expert * stride + first (+ 1 for the up half)], rows of x sorted by expert, tile list on the device.
 void trellis_gemm(const Tensor& x, const Tensor& desc, Tensor out, int64_t N, int64_t K, int64_t act, int64_t first, int64_t stride,
                   const OptT& tile_expert, const OptT& tile_row0, const OptT& tile_rows, const OptT& n_tiles, int64_t token_tile,
-                  const OptT& row_scale, Tensor status) {
+                  const OptT& row_scale, const OptT& out_rows, Tensor status) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && desc.is_cuda() && desc.scalar_type() == at::kLong &&
@@ -758,6 +758,12 @@ void trellis_gemm(const Tensor& x, const Tensor& desc, Tensor out, int64_t N, in
   TORCH_CHECK(act == 0 ? out.size(1) == N : (N % 128 == 0 && out.size(1) == N / 2));
   c10::cuda::CUDAGuard guard(x.device());
   MmbFp4GemmParams p{};
+  if (out_rows.has_value() && out_rows->defined()) {
+    // scatter epilogue: row r of the result goes to the address out_rows[r] (possibly peer memory); `out` gives the width
+    TORCH_CHECK(out_rows->is_cuda() && out_rows->scalar_type() == at::kLong && out_rows->is_contiguous() && out_rows->numel() >= x.size(0) &&
+                act == 0);
+    p.out_rows = reinterpret_cast<const long long*>(out_rows->data_ptr<int64_t>());
+  }
   p.x = x.data_ptr();
   p.out = out.data_ptr();
   p.M = (int)x.size(0);

@@ -151,6 +151,26 @@ class TrellisLinear:
     def from_float(cls, w: torch.Tensor, bits: int = 4, group_size: int = 128, device=None):
         return cls(trfmt.quantize_trellis(w, bits, group_size), device)
 
+    @classmethod
+    def random(cls, out_f: int, in_f: int, bits: int = 4, group_size: int = 128, device="cpu", seed: int = 0, std: float = 0.02):
+        """Random-init matrix drawn directly in the quantized domain (uniform codes, one scale per group and row sized so
+        that the weights have about ``std`` spread): synthetic benchmark models of tens of billions of parameters are built
+        in seconds, without ever holding a float copy."""
+        self = cls.__new__(cls)
+        dev = torch.device(device)
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.out_features, self.in_features, self.bits, self.group_size = out_f, in_f, bits, group_size
+        n_tiles = ((out_f + 15) // 16) * ((in_f + 15) // 16)
+        self.codes = torch.randint(0, 256, (n_tiles * 32 * bits,), dtype=torch.uint8, device=dev, generator=g)
+        levels = (1 << bits) - 1
+        # uniform codes have a spread of about levels / sqrt(12) grid steps
+        step = std / (max(levels, 1) / 3.4641 * 1.24371088)
+        self.scales = torch.full(((in_f + group_size - 1) // group_size, out_f), step, dtype=torch.float32, device=dev)
+        self.su = (torch.randint(0, 2, (in_f,), device=dev, generator=g).float() * 2 - 1).contiguous()
+        self.sv = (torch.randint(0, 2, (out_f,), device=dev, generator=g).float() * 2 - 1).contiguous()
+        self.bias, self.device, self._deq, self._desc = None, dev, None, None
+        return self
+
     def dequantize(self, dtype=torch.bfloat16) -> torch.Tensor:
         return ops.trellis_dequant(self.codes, self.scales, self.su, self.sv, self.out_features, self.in_features, self.bits,
                                    self.group_size).to(dtype)

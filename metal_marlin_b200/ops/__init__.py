@@ -776,18 +776,19 @@ def trellis_gemm_ok(x, in_f: int, group_size: int) -> bool:
 
 
 def trellis_gemm(x, desc, N: int, Kin: int, *, act: int = 0, first: int = 0, stride: int = 1, tiles=None, token_tile: int = 0,
-                 row_scale=None, out=None):
+                 row_scale=None, out=None, out_rows=None):
     """``out = x @ W^T`` with trellis weights decoded in the tcgen05 GEMM's main loop (2..8 bits, mixed per matrix).
     ``desc``: device int64 ``[n_mats, 6]`` (:func:`trellis_desc_row`).  ``act=1``: matrices ``first`` (gate) and
     ``first + 1`` (up), SwiGLU in the epilogue, ``out [M, N / 2]``.  ``tiles = (tile_expert, tile_row0, tile_rows, n_tiles)``:
-    grouped mode over rows sorted by expert (matrix ``expert * stride + first``)."""
+    grouped mode over rows sorted by expert (matrix ``expert * stride + first``).  ``out_rows`` (device int64 per row): the
+    scatter epilogue of the expert-parallel return path (``out`` then only gives the row width)."""
     M = x.shape[0]
     if out is None:
         out = torch.empty(M, N // 2 if act else N, dtype=torch.bfloat16, device=x.device)
     te = tr0 = trw = nt = None
     if tiles is not None:
         te, tr0, trw, nt = tiles
-    K.mmb200.trellis_gemm(x, desc, out, N, Kin, act, first, stride, te, tr0, trw, nt, token_tile, row_scale, gemm_status(x.device))
+    K.mmb200.trellis_gemm(x, desc, out, N, Kin, act, first, stride, te, tr0, trw, nt, token_tile, row_scale, out_rows, gemm_status(x.device))
     return out
 
 

@@ -57,6 +57,7 @@ class ExpertParallelMoE:
         self.num_routed = num_routed
         self.gate_up, self.first, self.n_local, self.n_shared_local = shard_bank(gate_up, num_routed, n_shared, rank, ep)
         self.down = shard_bank(down, num_routed, n_shared, rank, ep)[0]
+        self.hidden = self.down.out_features
 
     def partial(self, x, ids, weights, *, norm_w=None, eps=1e-6, tpx=None):
         """This rank's share of the expert output for replicated tokens (sum over ranks = full MoE output)."""
@@ -93,11 +94,11 @@ class ExpertParallelMoE:
         # local experts on the received (token, expert) pairs: one slot per row, weight 1 (weights applied at home)
         lid = localize_ids(recv_e.view(-1, 1), self.first, self.n_local)
         ones = torch.ones(recv_x.shape[0], 1, dtype=torch.float32, device=dev)
-        y = ops.moe_forward(recv_x, self.gate_up, self.down, lid, ones) if recv_x.shape[0] else recv_x.new_zeros(0, self.down.out_features)
-        back = torch.empty(send_x.shape[0], self.down.out_features, dtype=y.dtype, device=dev)
+        y = ops.moe_forward(recv_x, self.gate_up, self.down, lid, ones) if recv_x.shape[0] else recv_x.new_zeros(0, self.hidden)
+        back = torch.empty(send_x.shape[0], self.hidden, dtype=y.dtype, device=dev)
         dist.all_to_all_single(back, y.contiguous(), sc, rc, group=self.group)
         w_sorted = weights_local.reshape(-1).index_select(0, order).to(torch.float32)
-        out = torch.zeros(T, self.down.out_features, dtype=torch.float32, device=dev)
+        out = torch.zeros(T, self.hidden, dtype=torch.float32, device=dev)
         out.index_add_(0, tok, back.to(torch.float32) * w_sorted.unsqueeze(-1))
         return out.to(torch.bfloat16)
 
@@ -147,11 +148,20 @@ class ExpertParallelMoE:
         t_e = torch.empty(max_tiles, dtype=torch.int32, device=dev)
         t_r0, t_rows = torch.empty_like(t_e), torch.empty_like(t_e)
         n_tiles = torch.empty(2, dtype=torch.int32, device=dev)      # [tiles, rows received]
-        K.ep_recv_group(ex.desc_recv, self.ep, ex.cap, dn_b.out_features, max(1, self.n_local), token_tile, order, row_dst, t_e, t_r0,
+        K.ep_recv_group(ex.desc_recv, self.ep, ex.cap, self.hidden, max(1, self.n_local), token_tile, order, row_dst, t_e, t_r0,
                         t_rows, n_tiles)
         st = ops.gemm_status(dev)
-        xs = torch.empty(n, gu_b.in_features, dtype=torch.bfloat16, device=dev)
+        xs = torch.empty(n, self.hidden, dtype=torch.bfloat16, device=dev)
         K.moe_gather_n(ex.recv_x, order, xs, 1, n_tiles, 1)      # only the rows that arrived, not the worst-case capacity
+        self._run_local_experts(ex, xs, n, (t_e, t_r0, t_rows, n_tiles), token_tile, row_dst, st)
+        K.ep_signal(ex.desc_signal, self.ep)
+
+    def _run_local_experts(self, ex, xs, n, tiles, token_tile, row_dst, st) -> None:
+        """Gate|up (SwiGLU) and down projection of the sorted rows; the down epilogue stores each row at ``row_dst``."""
+        K = ops.K.mmb200
+        dev = xs.device
+        gu_b, dn_b = self.gate_up, self.down
+        t_e, t_r0, t_rows, n_tiles = tiles
         h = torch.empty(n, gu_b.out_features // 2, dtype=torch.bfloat16, device=dev)
         if gu_b.out_features % 128 == 0:       # SwiGLU in the GEMM epilogue: only rows that a tile covers are touched
             K.fp4_gemm_grouped_swiglu(xs, gu_b.qtile, gu_b.stile, h, gu_b.out_features, gu_b.group_size, t_e, t_r0, t_rows, n_tiles,
@@ -164,15 +174,39 @@ class ExpertParallelMoE:
         # down projection: every output row goes from the epilogue into its token owner's return buffer
         K.fp4_gemm_grouped_scatter(h, dn_b.qtile, dn_b.stile, ex.ret_y[:1], dn_b.out_features, dn_b.group_size, t_e, t_r0, t_rows,
                                    n_tiles, token_tile, st, row_dst)
-        K.ep_signal(ex.desc_signal, self.ep)
 
     def fused_combine(self, ex: "EPExchange", state, *, add0=None, add1=None):
         """Phase 3 (token owner): wait for the owners' returns, routing-weighted sum over the slots (+ adds)."""
         ids32, w32 = state
-        out = torch.empty(ids32.shape[0], self.down.out_features, dtype=torch.bfloat16, device=ids32.device)
+        out = torch.empty(ids32.shape[0], self.hidden, dtype=torch.bfloat16, device=ids32.device)
         ops.K.mmb200.ep_combine(ex.desc_combine, ids32, w32, None if add0 is None else add0.contiguous(),
                                 None if add1 is None else add1.contiguous(), out, self.ep)
         return out
+
+
+class GenericExpertParallelMoE(ExpertParallelMoE):
+    """Expert parallelism over a bank of generic (trellis) experts: the rank keeps its range of the routed experts as they
+    are (mixed bit widths per expert and matrix); the exchanged rows run through the grouped trellis GEMMs, whose codes are
+    decoded inside the tensor-core main loop, with the same scatter epilogue into the token owners' return buffers."""
+
+    def __init__(self, bank, num_routed: int, rank: int, ep: int, group=None):
+        from ..ops.generic import GenericExpertBank, _trellis_desc
+        self.rank, self.ep, self.group, self.num_routed = rank, ep, group, num_routed
+        e0, e1 = expert_range(num_routed, rank, ep)
+        self.first, self.n_local, self.n_shared_local = e0, e1 - e0, 0
+        local = GenericExpertBank(bank.gate_up[e0:e1], bank.down[e0:e1])
+        self.gate_up = self.down = local
+        self.hidden = bank.in_features
+        self.inter = bank.gate_up[0].out_features // 2
+        self._desc_fn = _trellis_desc
+
+    def _run_local_experts(self, ex, xs, n, tiles, token_tile, row_dst, st) -> None:
+        desc = self._desc_fn(self.gate_up, self.n_local, xs.device)
+        if desc is None or self.hidden % 64 or self.inter % 64:
+            raise RuntimeError("the fused expert-parallel path needs uniformly trellis experts with widths that are multiples of 64")
+        mats, H, I = desc
+        h = ops.trellis_gemm(xs, mats, 2 * I, H, act=1, first=0, stride=3, tiles=tiles, token_tile=token_tile)
+        ops.trellis_gemm(h, mats, H, I, act=0, first=2, stride=3, tiles=tiles, token_tile=token_tile, out=ex.ret_y[:1], out_rows=row_dst)
 
 
 class EPExchange:
@@ -275,10 +309,16 @@ class EPModelState:
         self.pass_tokens = 0
         self.uniform = False
 
-    def add_layer(self, li: int, gate_up: FP4ExpertBank, down: FP4ExpertBank, num_routed: int, n_shared: int) -> None:
+    def add_layer(self, li: int, gate_up, down, num_routed: int, n_shared: int) -> None:
+        self.n_shared = n_shared
+        if getattr(gate_up, "is_generic", False):
+            from ..ops.generic import GenericExpertBank
+            self.layers[li] = GenericExpertParallelMoE(gate_up, num_routed, self.rank, self.ep, self.group)
+            if n_shared:
+                self.shared[li] = GenericExpertBank(gate_up.gate_up[num_routed:], gate_up.down[num_routed:])
+            return
         moe = ExpertParallelMoE(gate_up, down, num_routed, 0, self.rank, self.ep, self.group)
         self.layers[li] = moe
-        self.n_shared = n_shared
         if n_shared:
             sel = torch.arange(num_routed, num_routed + n_shared, device=gate_up.qtile.device)
             pick = lambda b: FP4ExpertBank(b.qtile.index_select(0, sel).contiguous(), b.stile.index_select(0, sel).contiguous(),
@@ -295,9 +335,16 @@ class EPModelState:
         moe = self.layers[li]
         add0 = None
         if li in self.shared:
-            gu, dn = self.shared[li]
             xin = ops.rmsnorm(x, norm_w, eps) if norm_w is not None else x
-            add0 = ops._shared_experts(xin, gu, dn, self.n_shared, 0)
+            if isinstance(self.shared[li], tuple):
+                gu, dn = self.shared[li]
+                add0 = ops._shared_experts(xin, gu, dn, self.n_shared, 0)
+            else:      # generic (trellis) shared experts: no routed slot, the bank's experts all act as shared ones
+                from ..ops import generic
+                bank = self.shared[li]
+                none = torch.empty(x.shape[0], 0, dtype=torch.int32, device=x.device)
+                add0 = generic._finish_shared(torch.zeros(x.shape[0], x.shape[1], dtype=torch.float32, device=x.device), xin, bank,
+                                              len(bank.gate_up), 0, None)
         if self.mode == "fused" and self.exchange is not None and x.is_cuda:
             bound = ids.shape[0] if self.uniform else self.pass_tokens
             return moe.forward_fused(self.exchange, x, ids, weights, norm_w=norm_w, eps=eps, add0=add0, rows_bound=bound * ids.shape[1])

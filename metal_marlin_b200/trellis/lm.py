@@ -81,6 +81,60 @@ class TrellisSource:
         return bank, bank
 
 
+class TrellisRandomSource:
+    """Random-init trellis weights of an architecture preset (synthetic benchmarks): attention and dense matrices at
+    ``dense_bits``, expert ``e`` at ``expert_bits[e % len(expert_bits)]`` (mixed precision per expert, as the trellis-v2
+    quantizer assigns it), routers / norms / embeddings in bf16.  Every rank of a multi-GPU job draws the same tensors."""
+
+    def __init__(self, cfg: ModelConfig, device, seed: int = 0, dense_bits: int = 4, expert_bits=(2, 3, 4), group_size: int = 128):
+        self.cfg, self.device, self.seed = cfg, torch.device(device), seed
+        self.dense_bits, self.expert_bits, self.gs = dense_bits, tuple(expert_bits), group_size
+
+    def _seed(self, name: str) -> int:
+        import zlib
+        return (zlib.crc32(name.encode()) + self.seed * 7919) & 0x7FFFFFFF
+
+    def _gs(self, in_f: int) -> int:
+        gs = self.gs
+        while gs > 16 and in_f % gs:
+            gs //= 2
+        return gs
+
+    def has(self, name: str) -> bool:
+        return True
+
+    def linear(self, name: str, out_f: int, in_f: int, bits: Optional[int] = None):
+        return TrellisLinear.random(out_f, in_f, bits or self.dense_bits, self._gs(in_f), self.device, self._seed(name))
+
+    def linear_cat(self, names, outs, in_f):
+        return CatWeight([self.linear(n, o, in_f) for n, o in zip(names, outs)])
+
+    def dense(self, name: str, *shape, std=None) -> torch.Tensor:
+        g = torch.Generator(device=self.device).manual_seed(self._seed(name))
+        return (torch.randn(*shape, device=self.device, generator=g) * (std or 0.02)).to(torch.bfloat16)
+
+    def norm(self, name: str, dim: int) -> torch.Tensor:
+        return torch.ones(dim, dtype=torch.bfloat16, device=self.device)
+
+    def float(self, name: str, *shape, std=None) -> torch.Tensor:
+        g = torch.Generator(device=self.device).manual_seed(self._seed(name))
+        return torch.randn(*shape, device=self.device, generator=g) * (std or 0.02)
+
+    def expert_banks(self, m: str, E: int, I: int, H: int, ns: int):
+        gus, dws = [], []
+        for e in range(E):
+            b = self.expert_bits[e % len(self.expert_bits)]
+            p = f"{m}.experts.{e}"
+            gus.append(CatWeight([self.linear(f"{p}.gate_proj", I, H, b), self.linear(f"{p}.up_proj", I, H, b)]))
+            dws.append(self.linear(f"{p}.down_proj", H, I, b))
+        for j in range(ns):
+            p = f"{m}.shared_experts.{j}"
+            gus.append(CatWeight([self.linear(f"{p}.gate_proj", I, H), self.linear(f"{p}.up_proj", I, H)]))
+            dws.append(self.linear(f"{p}.down_proj", H, I))
+        bank = GenericExpertBank(gus, dws)
+        return bank, bank
+
+
 class _DenseWeight:
     is_generic = True
     names = None
@@ -106,6 +160,15 @@ class TrellisForCausalLM(MMFP4ForCausalLM):
         device = device or ("cuda" if torch.cuda.is_available() else "cpu")
         cfg = ModelConfig.from_pretrained(path)
         return cls(build_transformer(cfg, TrellisSource(cfg, path, device)))
+
+    @classmethod
+    def from_config(cls, cfg, device: Optional[str] = None, seed: int = 0, dense_bits: int = 4, expert_bits=(2, 3, 4)) -> "TrellisForCausalLM":
+        """Random-init trellis model of an architecture preset (see :class:`TrellisRandomSource`)."""
+        from ..models.config import get_preset
+        if isinstance(cfg, str):
+            cfg = get_preset(cfg)
+        device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        return cls(build_transformer(cfg, TrellisRandomSource(cfg, device, seed, dense_bits, expert_bits)))
 
     def generate(self, prompts, max_new_tokens: int = 32, **kw):
         kw.setdefault("use_graph", False)

@@ -100,8 +100,23 @@ for rep in range(3):
     with ops.force_reference():
         ref = ops.moe_forward(x, gu, dn, ids, wts, norm_w=nw, out_add=add).float()
     errs.append([float((out.float() - ref).abs().max() / ref.abs().max()), float((base - ref).abs().max() / ref.abs().max())])
+# the same exchange over trellis experts (mixed 2-8 bits, codes decoded inside the grouped tensor-core GEMMs)
+from metal_marlin_b200.layers import TrellisLinear
+from metal_marlin_b200.ops import generic
+from metal_marlin_b200.parallel.ep import GenericExpertParallelMoE
+bits = [2, 3, 4, 5, 6, 8]
+tg, td = [], []
+for e in range(E):
+    b = bits[e % len(bits)]
+    tg.append(generic.CatWeight([TrellisLinear.random(I, H, b, 64, dev, seed=3 * e, std=0.05), TrellisLinear.random(I, H, b, 64, dev, seed=3 * e + 1, std=0.05)]))
+    td.append(TrellisLinear.random(H, I, b, 64, dev, seed=3 * e + 2, std=0.05))
+tbank = generic.GenericExpertBank(tg, td)
+tmoe = GenericExpertParallelMoE(tbank, E, rank, world)
+out_t = tmoe.forward_fused(ex, x, ids, wts, norm_w=nw, add0=add)
+ref_t = generic.moe_forward(x, tbank, ids, wts, norm_w=nw, out_add=add).float()
+trellis_err = float((out_t.float() - ref_t).abs().max() / ref_t.abs().max())
 torch.cuda.synchronize()
-res = {"rank": rank, "errs": errs, "status": ex.check(), "gemm_status": ops.check_status(dev)}
+res = {"rank": rank, "errs": errs, "trellis_err": trellis_err, "status": ex.check(), "gemm_status": ops.check_status(dev)}
 print("RESULT " + json.dumps(res), flush=True)
 dist.barrier()
 dist.destroy_process_group()
@@ -136,3 +151,4 @@ def test_fused_expert_parallel_multi_gpu(world, tmp_path):
         assert res["status"] == 0 and res["gemm_status"] == 0, res
         for fused_err, nccl_err in res["errs"]:
             assert fused_err < 4e-2 and nccl_err < 4e-2, res
+        assert res["trellis_err"] < 4e-2, res
