@@ -41,6 +41,13 @@ def gated_delta_rule_chunked(q, k, v, g, beta, state: Optional[torch.Tensor] = N
     scale = scale if scale is not None else dk ** -0.5
     S = torch.zeros(B, H, dk, dv, dtype=torch.float32, device=q.device) if state is None else state.clone().float()
     out = torch.empty(B, T, H, dv, dtype=torch.float32, device=q.device)
+    if q.is_cuda and ops.native_available() and not ops._FORCE_REF and dk in (16, 32, 64, 128) and dv <= 1024:
+        # prompt pass on the device in one launch: every value column's state vector lives in registers while the kernel
+        # walks the tokens (csrc/recurrent_scan.cu); the chunk-parallel form below is the CPU / oracle path
+        f = lambda t: t.float().contiguous()
+        S = S.contiguous()
+        ops.K.mmb200.gated_delta_scan(f(q), f(k), f(v), f(g), f(beta), S, out, float(scale))
+        return out.to(v.dtype), S
     for c0 in range(0, T, chunk):
         c1 = min(T, c0 + chunk)
         L = c1 - c0

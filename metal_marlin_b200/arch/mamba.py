@@ -20,6 +20,13 @@ def selective_scan(x, dt, A, Bm, Cm, D=None, state: Optional[torch.Tensor] = Non
     Bsz, T, Di = x.shape
     N = A.shape[1]
     h = torch.zeros(Bsz, Di, N, dtype=torch.float32, device=x.device) if state is None else state.clone().float()
+    if x.is_cuda and ops.native_available() and not ops._FORCE_REF and N in (8, 16, 32, 64, 128):
+        # one launch over all tokens: the per-channel state stays in registers (csrc/recurrent_scan.cu)
+        f = lambda t: t.float().contiguous()
+        y = torch.empty(Bsz, T, Di, dtype=torch.float32, device=x.device)
+        h = h.contiguous()
+        ops.K.mmb200.selective_scan(f(x), f(dt), f(A), f(Bm), f(Cm), None if D is None else f(D), h, y)
+        return y.to(x.dtype), h
     ys = torch.empty(Bsz, T, Di, dtype=torch.float32, device=x.device)
     xf, dtf = x.float(), dt.float()
     for t in range(T):

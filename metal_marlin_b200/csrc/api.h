@@ -86,6 +86,10 @@ int mmb_bf16_gemv(const MmbBf16GemvParams* p, cudaStream_t stream);
 // ----------------------------------------------------------------------------- elementwise
 int mmb_rmsnorm(const void* x, const void* delta, const void* w, void* out, void* resid_out, int rows, int dim,
                 int ldx, int ldo, float eps, cudaStream_t stream);
+// LayerNorm over the last axis (bf16 in / out, fp32 statistics): out = ((x + delta) - mean) * rstd * w + b; w, b, delta and
+// resid_out optional (resid_out receives x + delta).
+int mmb_layernorm(const void* x, const void* delta, const void* w, const void* b, void* out, void* resid_out, int rows, int dim, int ldx,
+                  int ldo, float eps, cudaStream_t stream);
 int mmb_silu_mul(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream);
 int mmb_add(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
 int mmb_embedding(const void* table, const int64_t* ids, void* out, int n, int dim, cudaStream_t stream);

@@ -47,6 +47,12 @@ int mmb_codebook_gemv(const void* x, const uint8_t* codes, const void* scales, c
 // Vision preprocessing: bilinear resize of uint8 HWC images [B, H, W, 3] to [out_h, out_w], per-channel
 // (x / 255 - mean) / std, written either as bf16 CHW [B, 3, out_h, out_w] (patch == 0) or as flattened patches
 // bf16 [B, (out_h / patch) * (out_w / patch), 3 * patch * patch] (channel-major inside a patch).
+// General image preprocessing: crop rectangle, resampling mode (0 bilinear, 1 bicubic, 2 nearest), normalisation, CHW or
+// patch output, patches optionally ordered by merge x merge groups.
+int mmb_vision_preprocess_ex(const uint8_t* images, void* out, int B, int H, int W, int crop_y, int crop_x, int crop_h, int crop_w,
+                             int out_h, int out_w, int patch, int merge, int mode, const float* mean3, const float* std3, cudaStream_t stream);
+// fp32 [B, 3, 2]: mean and standard deviation of pixel / 255 per image and channel.
+int mmb_channel_stats(const uint8_t* images, float* out, int B, int H, int W, cudaStream_t stream);
 int mmb_vision_preprocess(const uint8_t* images, void* out, int B, int H, int W, int out_h, int out_w, int patch,
                           const float* mean3, const float* std3, cudaStream_t stream);
 
@@ -64,6 +70,15 @@ int mmb_gated_delta_step(const void* q, const void* k, const void* v, const floa
                          int B, int H, int dk, int dv, float scale, cudaStream_t stream);
 // Mamba selective scan: x bf16 [B, D], dt fp32 [B, D] (after softplus), A fp32 [D, N] (negative), Bm / Cm fp32 [B, N], optional
 // skip Dskip fp32 [D], state fp32 [B, D, N] updated in place, y bf16 [B, D].
+// Whole-sequence scans (recurrent_scan.cu); every tensor fp32 and contiguous, the state is updated in place.
+//   WKV: r, k [B, T, H, dk], v [B, T, H, dv], u [H, dk], w addressed as w[b * w_bstride + t * w_tstride + h * dk + i]
+//   (v6: per-token decay, strides T * H * dk and H * dk; v5: per-head decay, both strides 0), state [B, H, dk, dv].
+int mmb_wkv(const float* r, const float* k, const float* v, const float* w, const float* u, float* state, float* out, int B, int T,
+            int H, int dk, int dv, long long w_bstride, long long w_tstride, cudaStream_t stream);
+int mmb_gated_delta_scan(const float* q, const float* k, const float* v, const float* g, const float* beta, float* state, float* out,
+                         int B, int T, int H, int dk, int dv, float scale, cudaStream_t stream);
+int mmb_selective_scan(const float* x, const float* dt, const float* A, const float* Bm, const float* Cm, const float* Dskip,
+                       float* state, float* y, int B, int T, int D, int N, cudaStream_t stream);
 int mmb_selective_scan_step(const void* x, const float* dt, const float* A, const float* Bm, const float* Cm, const float* Dskip,
                             float* state, void* y, int B, int D, int N, cudaStream_t stream);
 

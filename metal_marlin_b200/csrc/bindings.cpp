@@ -1013,6 +1013,39 @@ void vision_preprocess(const Tensor& images, Tensor out, int64_t out_h, int64_t 
         "vision_preprocess");
 }
 
+// crop = {y, x, h, w} of the source rectangle; mode 0 bilinear, 1 bicubic, 2 nearest; merge: patch grouping (1 = row major)
+void vision_preprocess_ex(const Tensor& images, Tensor out, std::vector<int64_t> crop, int64_t out_h, int64_t out_w, int64_t patch,
+                          int64_t merge, int64_t mode, std::vector<double> mean, std::vector<double> stdv) {
+  TORCH_CHECK(images.scalar_type() == at::kByte && images.is_contiguous() && images.dim() == 4 && images.size(3) == 3);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && mean.size() == 3 && stdv.size() == 3 && crop.size() == 4);
+  TORCH_CHECK(out.numel() == images.size(0) * 3 * out_h * out_w);
+  const float m[3] = {(float)mean[0], (float)mean[1], (float)mean[2]}, sd[3] = {(float)stdv[0], (float)stdv[1], (float)stdv[2]};
+  c10::cuda::CUDAGuard guard(images.device());
+  check(mmb_vision_preprocess_ex(images.data_ptr<uint8_t>(), out.data_ptr(), (int)images.size(0), (int)images.size(1), (int)images.size(2),
+                                 (int)crop[0], (int)crop[1], (int)crop[2], (int)crop[3], (int)out_h, (int)out_w, (int)patch, (int)merge,
+                                 (int)mode, m, sd, cur_stream()),
+        "vision_preprocess_ex");
+}
+void channel_stats(const Tensor& images, Tensor out) {
+  TORCH_CHECK(images.scalar_type() == at::kByte && images.is_contiguous() && images.dim() == 4 && images.size(3) == 3);
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == images.size(0) * 6);
+  c10::cuda::CUDAGuard guard(images.device());
+  check(mmb_channel_stats(images.data_ptr<uint8_t>(), out.data_ptr<float>(), (int)images.size(0), (int)images.size(1), (int)images.size(2),
+                          cur_stream()),
+        "channel_stats");
+}
+// LayerNorm over the last axis: out = (x - mean) * rstd * w + b (bf16 in / out, fp32 statistics); optional residual `delta`
+// added first (resid_out receives x + delta).
+void layernorm(const Tensor& x, const OptT& delta, const OptT& w, const OptT& b, Tensor out, const OptT& resid_out, double eps) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1 && out.size(0) == x.size(0) && out.size(1) == x.size(1));
+  c10::cuda::CUDAGuard guard(x.device());
+  check(mmb_layernorm(x.data_ptr(), cptr(delta), cptr(w), cptr(b), out.data_ptr(), mptr(resid_out), (int)x.size(0), (int)x.size(1),
+                      (int)x.stride(0), (int)out.stride(0), (float)eps, cur_stream()),
+        "layernorm");
+}
+
 void spec_verify(const Tensor& p_target, const Tensor& p_draft, const Tensor& draft, const Tensor& u, const Tensor& u_res,
                  Tensor out_tokens, Tensor out_accepted) {
   TORCH_CHECK(p_target.scalar_type() == at::kFloat && p_draft.scalar_type() == at::kFloat && p_target.is_contiguous() && p_draft.is_contiguous());
@@ -1040,6 +1073,48 @@ void gated_delta_step(const Tensor& q, const Tensor& k, const Tensor& v, const T
   check(mmb_gated_delta_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr<float>(), beta.data_ptr<float>(), state.data_ptr<float>(),
                              out.data_ptr(), B, H, dk, dv, (float)scale, cur_stream()),
         "gated_delta_step");
+}
+
+static void check_f32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), name, " must be a contiguous CUDA fp32 tensor");
+}
+// r, k [B, T, H, dk], v [B, T, H, dv], w [B, T, H, dk] or [H, dk], u [H, dk], state [B, H, dk, dv] (in place), out [B, T, H, dv]
+void wkv_scan(const Tensor& r, const Tensor& k, const Tensor& v, const Tensor& w, const Tensor& u, Tensor state, Tensor out) {
+  for (const Tensor* t : {&r, &k, &v, &w, &u, (const Tensor*)&state, (const Tensor*)&out}) check_f32(*t, "wkv tensor");
+  TORCH_CHECK(r.dim() == 4 && v.dim() == 4 && state.dim() == 4);
+  const int B = (int)r.size(0), T = (int)r.size(1), H = (int)r.size(2), dk = (int)r.size(3), dv = (int)v.size(3);
+  TORCH_CHECK(state.size(0) == B && state.size(1) == H && state.size(2) == dk && state.size(3) == dv && u.numel() == (int64_t)H * dk);
+  const bool per_token = w.dim() == 4;
+  TORCH_CHECK(per_token ? w.numel() == r.numel() : w.numel() == (int64_t)H * dk);
+  c10::cuda::CUDAGuard guard(r.device());
+  check(mmb_wkv(r.data_ptr<float>(), k.data_ptr<float>(), v.data_ptr<float>(), w.data_ptr<float>(), u.data_ptr<float>(), state.data_ptr<float>(),
+                out.data_ptr<float>(), B, T, H, dk, dv, per_token ? (long long)T * H * dk : 0, per_token ? (long long)H * dk : 0, cur_stream()),
+        "wkv_scan");
+}
+void gated_delta_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, Tensor state, Tensor out,
+                      double scale) {
+  for (const Tensor* t : {&q, &k, &v, &g, &beta, (const Tensor*)&state, (const Tensor*)&out}) check_f32(*t, "gated_delta tensor");
+  const int B = (int)q.size(0), T = (int)q.size(1), H = (int)q.size(2), dk = (int)q.size(3), dv = (int)v.size(3);
+  TORCH_CHECK(state.numel() == (int64_t)B * H * dk * dv && g.numel() == (int64_t)B * T * H && beta.numel() == g.numel());
+  c10::cuda::CUDAGuard guard(q.device());
+  check(mmb_gated_delta_scan(q.data_ptr<float>(), k.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr<float>(), beta.data_ptr<float>(),
+                             state.data_ptr<float>(), out.data_ptr<float>(), B, T, H, dk, dv, (float)scale, cur_stream()),
+        "gated_delta_scan");
+}
+void selective_scan(const Tensor& x, const Tensor& dt, const Tensor& A, const Tensor& Bm, const Tensor& Cm, const OptT& Dskip, Tensor state,
+                    Tensor y) {
+  for (const Tensor* t : {&x, &dt, &A, &Bm, &Cm, (const Tensor*)&state, (const Tensor*)&y}) check_f32(*t, "selective_scan tensor");
+  const int B = (int)x.size(0), T = (int)x.size(1), D = (int)x.size(2), N = (int)A.size(1);
+  TORCH_CHECK(state.numel() == (int64_t)B * D * N && Bm.numel() == (int64_t)B * T * N && Cm.numel() == Bm.numel());
+  const float* dsk = nullptr;
+  if (Dskip.has_value() && Dskip->defined()) {
+    check_f32(*Dskip, "Dskip");
+    dsk = Dskip->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  check(mmb_selective_scan(x.data_ptr<float>(), dt.data_ptr<float>(), A.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(), dsk,
+                           state.data_ptr<float>(), y.data_ptr<float>(), B, T, D, N, cur_stream()),
+        "selective_scan");
 }
 
 void selective_scan_step(const Tensor& x, const Tensor& dt, const Tensor& A, const Tensor& Bm, const Tensor& Cm, const OptT& Dskip,
@@ -1235,6 +1310,9 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("trellis_moe", &trellis_moe);
   m.def("codebook_gemv", &codebook_gemv);
   m.def("vision_preprocess", &vision_preprocess);
+  m.def("vision_preprocess_ex", &vision_preprocess_ex);
+  m.def("channel_stats", &channel_stats);
+  m.def("layernorm", &layernorm);
   m.def("spec_verify", &spec_verify);
   m.def("fp4_gemm_grouped_scatter", &fp4_gemm_grouped_scatter);
   m.def("ep_dispatch", &ep_dispatch);
@@ -1252,4 +1330,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("paged_decode_fp8", &paged_decode_fp8);
   m.def("gated_delta_step", &gated_delta_step);
   m.def("selective_scan_step", &selective_scan_step);
+  m.def("wkv_scan", &wkv_scan);
+  m.def("gated_delta_scan", &gated_delta_scan);
+  m.def("selective_scan", &selective_scan);
 }

@@ -36,6 +36,50 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const bf16* __restrict__ x
   }
 }
 
+// LayerNorm, one CTA per row: the row is read once into registers (8 values per thread and trip), mean and variance come
+// from one pass of sums (fp32), the normalised row is written with 16-byte stores.
+__global__ void __launch_bounds__(256) layernorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, const bf16* __restrict__ w,
+                                                        const bf16* __restrict__ b, bf16* __restrict__ out, bf16* __restrict__ resid_out,
+                                                        int dim, int ldx, int ldo, float eps) {
+  __shared__ float red[32];
+  extern __shared__ float rowbuf[];          // [dim] fp32 copy of the row (rows wider than the register budget)
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long r = blockIdx.x;
+  const bf16* xr = x + r * ldx;
+  float s = 0.f, q = 0.f;
+  for (int k = threadIdx.x * 2; k < dim; k += 512) {
+    float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
+    if (delta != nullptr) {
+      const float2 d = __bfloat1622float2(*reinterpret_cast<const bf162*>(delta + r * ldx + k));
+      const bf162 s2 = __floats2bfloat162_rn(v.x + d.x, v.y + d.y);
+      v = __bfloat1622float2(s2);
+      if (resid_out != nullptr) *reinterpret_cast<bf162*>(resid_out + r * dim + k) = s2;
+    }
+    rowbuf[k] = v.x;
+    rowbuf[k + 1] = v.y;
+    s += v.x + v.y;
+    q = fmaf(v.x, v.x, fmaf(v.y, v.y, q));
+  }
+  const float mean = block_sum(s, red) / (float)dim;
+  const float var = fmaxf(block_sum(q, red) / (float)dim - mean * mean, 0.f);
+  const float rstd = rsqrtf(var + eps);
+  for (int k = threadIdx.x * 2; k < dim; k += 512) {
+    float a = (rowbuf[k] - mean) * rstd, c = (rowbuf[k + 1] - mean) * rstd;
+    if (w != nullptr) {
+      const float2 ww = __bfloat1622float2(*reinterpret_cast<const bf162*>(w + k));
+      a *= ww.x;
+      c *= ww.y;
+    }
+    if (b != nullptr) {
+      const float2 bb = __bfloat1622float2(*reinterpret_cast<const bf162*>(b + k));
+      a += bb.x;
+      c += bb.y;
+    }
+    *reinterpret_cast<bf162*>(out + r * ldo + k) = __floats2bfloat162_rn(a, c);
+  }
+}
+
 __global__ void silu_mul_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int inter) {
   const long long r = blockIdx.x;            // rows on the x axis: prefill row counts exceed the 65535 limit of y
   const int k = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
@@ -261,6 +305,21 @@ MMB_API int mmb_rmsnorm(const void* x, const void* delta, const void* w, void* o
   }
   mmb::rmsnorm_kernel<<<rows, 256, smem, stream>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w, (bf16*)out,
                                                    (bf16*)resid_out, dim, ldx, ldo, eps);
+  return (int)cudaGetLastError();
+}
+
+MMB_API int mmb_layernorm(const void* x, const void* delta, const void* w, const void* b, void* out, void* resid_out, int rows, int dim, int ldx,
+                          int ldo, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dim <= 0 || (dim & 1) || (ldx & 1) || (ldo & 1)) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)dim * 4;
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(mmb::layernorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  mmb::layernorm_kernel<<<rows, 256, smem, stream>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w, (const bf16*)b, (bf16*)out,
+                                                     (bf16*)resid_out, dim, ldx, ldo, eps);
   return (int)cudaGetLastError();
 }
 

@@ -134,6 +134,30 @@ def rmsnorm(x, w, eps=1e-6, *, delta=None, resid_out=None, out=None):
     return out
 
 
+def layernorm(x, w=None, b=None, eps=1e-5, *, delta=None, resid_out=None, out=None):
+    """LayerNorm over the last axis (vision encoders, Mamba / RWKV blocks).  ``x`` of any leading shape; bf16 on CUDA runs the
+    kernel in ``csrc/elementwise.cu``; parity: reference ``src/layernorm.metal:149``."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    if not (_use_native(x2) and x2.dtype == torch.bfloat16 and shape[-1] % 2 == 0 and x2.stride(1) == 1):
+        v = x2.to(torch.float32)
+        if delta is not None:
+            v = (v + delta.reshape(-1, shape[-1]).to(torch.float32)).to(x.dtype).to(torch.float32)
+            if resid_out is not None:
+                resid_out.copy_(v.to(resid_out.dtype).view_as(resid_out))
+        y = torch.nn.functional.layer_norm(v, (shape[-1],), None if w is None else w.float(), None if b is None else b.float(), eps).to(x.dtype)
+        if out is not None:
+            out.copy_(y.view_as(out))
+            return out
+        return y.view(shape)
+    if out is None:
+        out = torch.empty_like(x2)
+    d2 = None if delta is None else delta.reshape(-1, shape[-1]).contiguous()
+    K.mmb200.layernorm(x2 if d2 is None else x2.contiguous(), d2, None if w is None else w.to(torch.bfloat16), None if b is None else b.to(torch.bfloat16),
+                       out.view(-1, shape[-1]), resid_out, eps)
+    return out.view(shape)
+
+
 def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bias=None, out_add=None,
            out=None, token_tile=0, tpx=None, ag_wait=None, _rotated=False):
     """``out = epilogue( prologue(x) @ dequant(W)^T )``; prologue = optional residual add + RMSNorm,
@@ -833,6 +857,36 @@ def vision_preprocess(images, out_h: int, out_w: int, *, patch: int = 0, mean=(0
     shape = (B, 3, out_h, out_w) if patch == 0 else (B, (out_h // patch) * (out_w // patch), 3 * patch * patch)
     out = torch.empty(*shape, dtype=torch.bfloat16, device=images.device)
     K.mmb200.vision_preprocess(images.contiguous(), out, out_h, out_w, patch, [float(m) for m in mean], [float(s) for s in std])
+    return out
+
+
+RESAMPLE_MODES = {"bilinear": 0, "bicubic": 1, "nearest": 2}
+
+
+def vision_preprocess_ex(images, out_h: int, out_w: int, *, crop=None, patch: int = 0, merge: int = 1, resample: str = "bilinear",
+                         mean=(0.48145466, 0.4578275, 0.40821073), std=(0.26862954, 0.26130258, 0.27577711)):
+    """General image preprocessing in one launch: ``crop = (y, x, h, w)`` source rectangle (None = whole image), resampling
+    to ``out_h x out_w`` (bilinear / bicubic / nearest, half-pixel centres), normalisation, CHW pixels or ViT patches
+    (``merge > 1``: patches ordered by merge x merge groups).  Parity: reference ``src/vision_preprocess.metal:214`` (bicubic),
+    ``:761`` (centre crop), ``:1354`` (patch extraction)."""
+    B, H, W, _ = images.shape
+    crop = (0, 0, H, W) if crop is None else tuple(int(c) for c in crop)
+    if not _use_native(images):
+        return ref.vision_preprocess_ex(images, out_h, out_w, crop, patch, merge, resample, mean, std)
+    shape = (B, 3, out_h, out_w) if patch == 0 else (B, (out_h // patch) * (out_w // patch), 3 * patch * patch)
+    out = torch.empty(*shape, dtype=torch.bfloat16, device=images.device)
+    K.mmb200.vision_preprocess_ex(images.contiguous(), out, list(crop), out_h, out_w, patch, merge, RESAMPLE_MODES[resample],
+                                  [float(m) for m in mean], [float(s) for s in std])
+    return out
+
+
+def channel_stats(images):
+    """Per-image, per-channel (mean, std) of ``pixel / 255`` for uint8 ``[B, H, W, 3]`` images: fp32 ``[B, 3, 2]``."""
+    if not _use_native(images):
+        v = images.to(torch.float32) / 255.0
+        return torch.stack([v.mean((1, 2)), v.std((1, 2), unbiased=False)], -1)
+    out = torch.empty(images.shape[0], 3, 2, dtype=torch.float32, device=images.device)
+    K.mmb200.channel_stats(images.contiguous(), out)
     return out
 
 

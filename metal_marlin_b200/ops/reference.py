@@ -348,6 +348,29 @@ def vision_preprocess(images, out_h, out_w, patch, mean, std):
     return x.to(torch.bfloat16)
 
 
+def vision_preprocess_ex(images, out_h, out_w, crop, patch, merge, resample, mean, std):
+    """Crop rectangle -> resample (bilinear / bicubic / nearest, half-pixel centres) -> normalise -> CHW or patches."""
+    y0, x0, ch, cw = crop
+    x = images[:, y0:y0 + ch, x0:x0 + cw].permute(0, 3, 1, 2).to(torch.float32)
+    if resample == "nearest":
+        iy = ((torch.arange(out_h, device=x.device).float() + 0.5) * ch / out_h).floor().long().clamp(0, ch - 1)
+        ix = ((torch.arange(out_w, device=x.device).float() + 0.5) * cw / out_w).floor().long().clamp(0, cw - 1)
+        x = x[:, :, iy][:, :, :, ix]
+    else:
+        x = F.interpolate(x, size=(out_h, out_w), mode=resample, align_corners=False)
+    m = torch.tensor(mean, device=x.device).view(1, 3, 1, 1)
+    s = torch.tensor(std, device=x.device).view(1, 3, 1, 1)
+    x = (x / 255.0 - m) / s
+    if patch:
+        B = x.shape[0]
+        ph, pw = out_h // patch, out_w // patch
+        x = x.view(B, 3, ph, patch, pw, patch).permute(0, 2, 4, 1, 3, 5)           # [B, ph, pw, 3, p, p]
+        if merge > 1:
+            x = x.reshape(B, ph // merge, merge, pw // merge, merge, 3, patch, patch).permute(0, 1, 3, 2, 4, 5, 6, 7)
+        x = x.reshape(B, ph * pw, 3 * patch * patch)
+    return x.to(torch.bfloat16)
+
+
 def spec_verify(p_target, p_draft, draft, u, u_resample):
     B, K1, V = p_target.shape
     K = K1 - 1

@@ -28,6 +28,53 @@ class PreprocessConfig:
     mean: Tuple[float, float, float] = CLIP_MEAN
     std: Tuple[float, float, float] = CLIP_STD
     as_patches: bool = True
+    resample: str = "bilinear"          # "bilinear" | "bicubic" | "nearest"
+    crop: str = "none"                  # "center": largest centred square (CLIP-style resize + centre crop in one pass)
+    merge_size: int = 1                 # > 1: patches ordered by merge x merge groups (Qwen2-VL spatial merge)
+
+
+def center_crop_box(height: int, width: int, aspect: float = 1.0) -> Tuple[int, int, int, int]:
+    """``(y, x, h, w)`` of the largest centred rectangle with the given width / height aspect ratio."""
+    if width / height > aspect:
+        h, w = height, max(1, int(round(height * aspect)))
+    else:
+        h, w = max(1, int(round(width / aspect))), width
+    return (height - h) // 2, (width - w) // 2, h, w
+
+
+def smart_resize(height: int, width: int, factor: int = 28, min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280) -> Tuple[int, int]:
+    """Dynamic resolution of Qwen2-VL style encoders: the size closest to the image whose sides are multiples of ``factor``
+    (patch x merge) and whose area lies in ``[min_pixels, max_pixels]``, keeping the aspect ratio."""
+    import math
+    if max(height, width) / min(height, width) > 200:
+        raise ValueError("aspect ratio above 200")
+    h = max(factor, round(height / factor) * factor)
+    w = max(factor, round(width / factor) * factor)
+    if h * w > max_pixels:
+        beta = math.sqrt(height * width / max_pixels)
+        h = max(factor, math.floor(height / beta / factor) * factor)
+        w = max(factor, math.floor(width / beta / factor) * factor)
+    elif h * w < min_pixels:
+        beta = math.sqrt(min_pixels / (height * width))
+        h = math.ceil(height * beta / factor) * factor
+        w = math.ceil(width * beta / factor) * factor
+    return h, w
+
+
+def preprocess_dynamic(image: torch.Tensor, patch: int = 14, merge: int = 2, resample: str = "bicubic", mean=CLIP_MEAN, std=CLIP_STD,
+                       min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280):
+    """One image of any size -> ``(patches [n, 3 * patch^2] in merge-group order, (grid_h, grid_w))`` at its dynamic
+    resolution (one kernel launch)."""
+    H, W = image.shape[-3], image.shape[-2]
+    oh, ow = smart_resize(H, W, patch * merge, min_pixels, max_pixels)
+    out = ops.vision_preprocess_ex(image.unsqueeze(0) if image.dim() == 3 else image, oh, ow, patch=patch, merge=merge, resample=resample,
+                                   mean=mean, std=std)
+    return out[0], (oh // patch, ow // patch)
+
+
+def channel_statistics(images: torch.Tensor) -> torch.Tensor:
+    """fp32 ``[B, 3, 2]``: per-image, per-channel mean and standard deviation of ``pixel / 255``."""
+    return ops.channel_stats(images if images.dim() == 4 else images.unsqueeze(0))
 
 
 class ImagePreprocessor:
@@ -46,7 +93,11 @@ class ImagePreprocessor:
         if self.device is not None:
             images = images.to(self.device)
         c = self.cfg
-        return ops.vision_preprocess(images.contiguous(), c.image_size, c.image_size, patch=c.patch_size if c.as_patches else 0, mean=c.mean, std=c.std)
+        if c.resample == "bilinear" and c.crop == "none" and c.merge_size == 1:
+            return ops.vision_preprocess(images.contiguous(), c.image_size, c.image_size, patch=c.patch_size if c.as_patches else 0, mean=c.mean, std=c.std)
+        crop = center_crop_box(images.shape[1], images.shape[2]) if c.crop == "center" else None
+        return ops.vision_preprocess_ex(images.contiguous(), c.image_size, c.image_size, crop=crop, patch=c.patch_size if c.as_patches else 0,
+                                        merge=c.merge_size, resample=c.resample, mean=c.mean, std=c.std)
 
     def num_patches(self) -> int:
         return (self.cfg.image_size // self.cfg.patch_size) ** 2

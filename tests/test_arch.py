@@ -96,3 +96,50 @@ def test_recurrent_step_kernels_gpu():
     y_ref, h_ref = arch.selective_scan(x[:, None].float().cpu(), dt[:, None].cpu(), A.cpu(), Bm[:, None].cpu(), Cm[:, None].cpu(), D.cpu(), st0.cpu())
     torch.testing.assert_close(y.float().cpu(), y_ref[:, 0], rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(st.cpu(), h_ref, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.gpu
+def test_sequence_scan_kernels_match_token_loops():
+    """Whole-sequence scan kernels (state in registers, one launch over all tokens) against the PyTorch token loops:
+    RWKV v5 / v6 WKV, Mamba selective scan, gated delta rule; with and without an initial state."""
+    import torch
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.arch import deltanet as dn
+    from metal_marlin_b200.arch import mamba as mb
+    from metal_marlin_b200.arch import rwkv
+    dev = "cuda"
+    torch.manual_seed(0)
+    B, T, H, dk, dv = 2, 37, 3, 64, 64
+    r, k = torch.randn(B, T, H, dk, device=dev) * 0.5, torch.randn(B, T, H, dk, device=dev) * 0.5
+    v = torch.randn(B, T, H, dv, device=dev)
+    w6 = torch.rand(B, T, H, dk, device=dev) * 0.5 + 0.4
+    w5, u = torch.rand(H, dk, device=dev) * 0.5 + 0.4, torch.randn(H, dk, device=dev) * 0.3
+    s0 = torch.randn(B, H, dk, dv, device=dev) * 0.1
+    for fn, w in ((rwkv.wkv6, w6), (rwkv.wkv5, w5)):
+        for st in (None, s0):
+            o, S = fn(r, k, v, w, u, st)
+            with ops.force_reference():
+                o_ref, S_ref = fn(r, k, v, w, u, st)
+            torch.testing.assert_close(o, o_ref, rtol=2e-4, atol=2e-4)
+            torch.testing.assert_close(S, S_ref, rtol=2e-4, atol=2e-4)
+    # selective scan
+    Di, N = 200, 16
+    x, dt = torch.randn(B, T, Di, device=dev), torch.rand(B, T, Di, device=dev) * 0.1
+    A = -torch.rand(Di, N, device=dev)
+    Bm, Cm, D = torch.randn(B, T, N, device=dev), torch.randn(B, T, N, device=dev), torch.randn(Di, device=dev)
+    h0 = torch.randn(B, Di, N, device=dev) * 0.1
+    for st in (None, h0):
+        y, h = mb.selective_scan(x, dt, A, Bm, Cm, D, st)
+        with ops.force_reference():
+            y_ref, h_ref = mb.selective_scan(x, dt, A, Bm, Cm, D, st)
+        torch.testing.assert_close(y, y_ref, rtol=2e-4, atol=2e-4)
+        torch.testing.assert_close(h, h_ref, rtol=2e-4, atol=2e-4)
+    # gated delta rule
+    dk2, dv2 = 64, 128
+    q, kk = torch.randn(B, T, H, dk2, device=dev), dn.l2norm(torch.randn(B, T, H, dk2, device=dev))
+    vv = torch.randn(B, T, H, dv2, device=dev)
+    g, beta = -torch.rand(B, T, H, device=dev) * 0.2, torch.rand(B, T, H, device=dev)
+    o, S = dn.gated_delta_rule_chunked(q, kk, vv, g, beta)
+    o_ref, S_ref = dn.gated_delta_rule_recurrent(q, kk, vv, g, beta)
+    torch.testing.assert_close(o, o_ref, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(S, S_ref, rtol=1e-3, atol=1e-3)

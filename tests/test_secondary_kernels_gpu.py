@@ -250,3 +250,24 @@ def test_trellis_moe_grouped_tensor_core_path(T, topk, monkeypatch):
     want = generic.moe_forward(x, bank, ids, wts)
     err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
     assert err < 3e-2, err
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 64), (37, 1024), (300, 1152), (5, 4096)])
+def test_layernorm_kernel(rows, dim):
+    """LayerNorm kernel (fp32 statistics, optional residual add, weight, bias) against torch.nn.functional.layer_norm."""
+    torch.manual_seed(rows)
+    x = torch.randn(rows, dim, device=DEV).to(torch.bfloat16)
+    d = (torch.randn(rows, dim, device=DEV) * 0.3).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(dim, device=DEV)).to(torch.bfloat16)
+    b = (0.1 * torch.randn(dim, device=DEV)).to(torch.bfloat16)
+    y = ops.layernorm(x, w, b, 1e-5)
+    F = torch.nn.functional
+    ref = F.layer_norm(x.float(), (dim,), w.float(), b.float(), 1e-5)
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    resid = torch.empty_like(x)
+    y2 = ops.layernorm(x, w, None, 1e-5, delta=d, resid_out=resid)
+    s = (x.float() + d.float()).to(torch.bfloat16)
+    assert torch.equal(resid, s)
+    torch.testing.assert_close(y2.float(), F.layer_norm(s.float(), (dim,), w.float(), None, 1e-5), rtol=2e-2, atol=2e-2)
+    y3 = ops.layernorm(x.view(rows, 1, dim))          # no affine, leading shape kept
+    assert y3.shape == (rows, 1, dim)
