@@ -140,7 +140,7 @@ class PatchMergerProjector:
         B, N, C = feats.shape
         h, w = grid_hw
         m = self.merge
-        x = F.layer_norm(feats.to(self.w1.dtype), (C,), self.ln_w, self.ln_b)
+        x = ops.layernorm(feats.to(self.w1.dtype), self.ln_w, self.ln_b)
         x = x.view(B, h // m, m, w // m, m, C).permute(0, 1, 3, 2, 4, 5).reshape(B, (h // m) * (w // m), m * m * C)
         return F.linear(F.gelu(F.linear(x, self.w1, self.b1)), self.w2, self.b2)
 
@@ -157,7 +157,7 @@ class PixelShuffleProjector:
         r = int(round(1 / self.scale))
         x = feats.view(B, s, s, C).view(B, s, s // r, C * r).permute(0, 2, 1, 3).reshape(B, s // r, s // r, C * r * r)
         x = x.permute(0, 2, 1, 3).reshape(B, (s // r) ** 2, C * r * r).to(self.w1.dtype)
-        x = F.layer_norm(x, (x.shape[-1],), self.ln_w, self.ln_b)
+        x = ops.layernorm(x, self.ln_w, self.ln_b)
         return F.linear(F.gelu(F.linear(x, self.w1, self.b1)), self.w2, self.b2)
 
 
