@@ -31,7 +31,9 @@ _reg(".models.config", "ModelConfig", "get_preset")
 _reg(".models.transformer", "Transformer", "PagedKVStorage", "BatchMeta")
 _reg(".engine.session", "DecodeSession", "SamplingParams")
 _reg(".engine.engine", "LLMEngine")
-_reg(".engine.scheduler", "BatchScheduler", "FCFSScheduler", "SchedulerConfig", "PreemptionPolicy")
+_reg(".engine.scheduler", "BatchScheduler", "SchedulerConfig", "PreemptionPolicy", "QueueFullError")
+_reg(".inference.pipelined", "PipelineScheduler", "AsyncPipelineScheduler", "InferenceRequest", "RequestState", "generate_pipelined")
+_reg(".engine.fcfs", "FCFSScheduler", "PrefillStrategy", "InsertionPolicy", "CacheInfo")
 _reg(".engine.request", "GenerationRequest", "RequestStatus", "RunningRequest", "RequestPriority")
 _reg(".sampler", "SamplingConfig", "Sampler", "sample_next_token", MetalSampler="Sampler")
 _reg(".rope", "YaRNConfig", "RotaryEmbedding", "apply_rope", "rope_inv_freq", "yarn_inv_freq")
@@ -75,7 +77,8 @@ _reg(".inference.long_context", "LongContextConfig", "LongContextModel", "Stream
 _reg(".attention", "block_sparse_attention", "sliding_window_attention", "tree_attention", "differential_attention")
 _reg(".arch", "MambaBlock", "MambaConfig", "selective_scan", "gated_delta_rule_chunked", "gated_delta_step", "wkv5", "wkv6", "layout_from_config")
 _reg(".vision", "ImagePreprocessor", "PreprocessConfig", "LlavaProjector", "PatchMergerProjector", "VisionEncoderCache")
-_reg(".hf", "replace_linear_layers", "find_linear_layers", "find_moe_layers", "load_prequantized_mmfp4_model")
+_reg(".hf", "replace_linear_layers", "find_linear_layers", "find_moe_layers", "load_prequantized_mmfp4_model", "replace_moe_layers",
+     "replace_moe_layers_streaming", "quantize_moe_experts", "QuantizedMoEExperts", "QuantizedMoEBlock")
 _reg(".memory", "Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "PinnedPool", "WeightStreamer", "MemoryPressureMonitor")
 _reg(".parallel.tp", "TPContext", "shard_transformer", "make_context")
 _reg(".parallel.mesh", "DeviceMesh", "MeshShape", "plan_mesh")

@@ -4,7 +4,7 @@
 // the token tile is the "B" operand (TN = 32..256 tokens = TMEM columns), so the same kernel serves
 // batch-32 decode (TN = 32) and long prefill (TN = 256) without wasting the M = 128 instruction shape.
 //
-// CTA = 18 warps:
+// CTA = 18 warps (the weight-expanding variants run two such CTAs per SM):
 //   warp 0      TMA producer: x tile [TN x 64] bf16, 128-byte swizzle, one bulk tensor copy per stage
 //               (bf16-weight variant: also the W tile)
 //   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits stages back to the
@@ -21,6 +21,7 @@
 // Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records a code in
 // status[0], skips the remaining work, still frees its TMEM and returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "api_gemm.h"
 #include "common.cuh"
@@ -40,9 +41,12 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int tn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
 }
 
-template <int TN>
+// MINB = 2: two CTAs share an SM (half the pipeline depth each).  The FP4 / trellis main loops are bound by the latency of the
+// expansion warps' round trips, not by the tensor pipe or shared memory, so a second resident CTA fills the idle issue slots
+// and MMA time of the first; both accumulators fit the 512 TMEM columns (2 x 256).
+template <int TN, int MINB>
 struct GemmCfg {
-  static constexpr int kStages = (TN <= 128) ? 6 : 4;
+  static constexpr int kStages = (MINB == 2) ? ((TN == 256) ? 2 : (TN == 128) ? 3 : 4) : ((TN <= 128) ? 6 : 4);
   static constexpr int a_bytes = kTileRows * kBK * 2;      // 16 KB
   static constexpr int b_bytes = TN * kBK * 2;
   static constexpr int stage_bytes = a_bytes + b_bytes;
@@ -61,11 +65,11 @@ struct PipeShared {
 
 // WFMT 0: FP4 tile-layout weights expanded by the warps 2..17.  WFMT 1: bf16 weights fetched by TMA.  WFMT 2: trellis weights
 // (16 x 16 tiles of 2..8-bit codes, LSB-first bit stream) decoded by the same warps inside the main loop.
-template <int TN, int WFMT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int TN, int WFMT, int MINB>
+__global__ void __launch_bounds__(kGemmThreads, MINB)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const MmbFp4GemmParams p, const MmbBf16GemmParams pb) {
-  using Cfg = GemmCfg<TN>;
+  using Cfg = GemmCfg<TN, MINB>;
   constexpr bool QW = WFMT != 1;       // weights are expanded by the warps of this CTA (parameters in `p`)
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -207,6 +211,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       const uint32_t* sc_row[kRB];
       int st_row[kRB];
       uint4 w0[kRB], w1[kRB];
+      uint32_t s0[kRB], s1[kRB];       // groups of 64 and more: the scale words of the next two k blocks of the class, fetched with the weights
 #pragma unroll
       for (int j = 0; j < kRB; ++j) {
         // act == 1 (fused SwiGLU): the CTA's 128 lanes are 64 gate rows (blocks 0..3) and the 64 up rows of the same
@@ -219,6 +224,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         st_row[j] = ((dw0 + j) * 16 + g) * 128;
         w0[j] = (rt_ok[j] && kh < KB) ? ldg_stream(wsrc[j] + (long long)kh * 32) : make_uint4(0, 0, 0, 0);
         w1[j] = (rt_ok[j] && kh + kSplit < KB) ? ldg_stream(wsrc[j] + (long long)(kh + kSplit) * 32) : make_uint4(0, 0, 0, 0);
+        s0[j] = (big_groups && rt_ok[j] && kh < KB) ? __ldg(sc_row[j] + (long long)((kh * kBK) >> p.gs_shift) * 8) : 0u;
+        s1[j] = (big_groups && rt_ok[j] && kh + kSplit < KB) ? __ldg(sc_row[j] + (long long)(((kh + kSplit) * kBK) >> p.gs_shift) * 8) : 0u;
       }
       // store offsets inside a row of the A tile (128-byte swizzle: 16-byte chunk index XOR (row % 8); row % 8 == g)
       int st_col[4][2];
@@ -231,11 +238,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         const int s = i % Cfg::kStages;
         const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
         uint4 wcur[kRB];
+        uint32_t scur[kRB];
 #pragma unroll
         for (int j = 0; j < kRB; ++j) {
           wcur[j] = w0[j];
           w0[j] = w1[j];
           w1[j] = (rt_ok[j] && i + 2 * kSplit < KB) ? ldg_stream(wsrc[j] + (long long)(i + 2 * kSplit) * 32) : make_uint4(0, 0, 0, 0);
+          scur[j] = s0[j];
+          s0[j] = s1[j];
+          s1[j] = (big_groups && rt_ok[j] && i + 2 * kSplit < KB) ? __ldg(sc_row[j] + (long long)(((i + 2 * kSplit) * kBK) >> p.gs_shift) * 8) : 0u;
         }
         if (!mbar_wait(&ps->empty[s], ph ^ 1u, abort_flag)) {
           if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 3);
@@ -253,7 +264,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           bf162 m_lo, m_hi;
           bool fold = true;
           if (big_groups) {
-            const uint32_t sw = rt_ok[j] ? __ldg(sc_row[j] + (long long)((i * kBK) >> p.gs_shift) * 8) : 0u;
+            const uint32_t sw = scur[j];
             const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sw));
             // fold the 2^126 subnormal rescale into the scale when it cannot overflow bf16
             fold = (fabsf(sf.x) < 2.f) && (fabsf(sf.y) < 2.f);
@@ -530,18 +541,38 @@ static int make_tmap_2d(CUtensorMap* map, const void* base, long long cols, long
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int TN, int WFMT>
-static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const MmbFp4GemmParams& p, const MmbBf16GemmParams& pb,
-                       dim3 grid, cudaStream_t stream) {
-  auto kern = gemm_kernel<TN, WFMT>;
+template <int TN, int WFMT, int MINB>
+static int launch_gemm_b(const CUtensorMap& mx, const CUtensorMap& mw, const MmbFp4GemmParams& p, const MmbBf16GemmParams& pb,
+                         dim3 grid, cudaStream_t stream) {
+  auto kern = gemm_kernel<TN, WFMT, MINB>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<TN>::smem_bytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<TN, MINB>::smem_bytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, kGemmThreads, GemmCfg<TN>::smem_bytes, stream>>>(mx, mw, p, pb);
+  kern<<<grid, kGemmThreads, GemmCfg<TN, MINB>::smem_bytes, stream>>>(mx, mw, p, pb);
   return (int)cudaGetLastError();
+}
+
+// CTAs per SM of the weight-expanding variants: 2 unless MMB200_GEMM_CTAS=1 (the bf16 x bf16 variant is fed by TMA alone
+// and keeps the deep single-CTA pipeline).
+static int gemm_ctas_per_sm() {
+  static int v = 0;
+  if (v == 0) {
+    const char* e = getenv("MMB200_GEMM_CTAS");
+    v = (e != nullptr && e[0] == '1') ? 1 : 2;
+  }
+  return v;
+}
+
+template <int TN, int WFMT>
+static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const MmbFp4GemmParams& p, const MmbBf16GemmParams& pb,
+                       dim3 grid, cudaStream_t stream) {
+  if constexpr (WFMT != 1) {
+    if (gemm_ctas_per_sm() == 2) return launch_gemm_b<TN, WFMT, 2>(mx, mw, p, pb, grid, stream);
+  }
+  return launch_gemm_b<TN, WFMT, 1>(mx, mw, p, pb, grid, stream);
 }
 
 static int pick_tn(int M, int forced) {

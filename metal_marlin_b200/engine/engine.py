@@ -40,6 +40,7 @@ class EngineConfig:
     use_cuda_graphs: bool = True
     request_timeout_s: float = 60.0
     graph_buckets: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)
+    scheduler_policy: str = "priority"   # "priority" (continuous batching with priorities) | "fcfs" | "shortest_first" | "longest_first"
 
 
 HISTORY_LEN = 256      # most recent tokens (prompt tail + generated) the repetition penalty looks at
@@ -176,10 +177,14 @@ class LLMEngine:
         self.kv = PagedKVStorage(model.cfg, c.num_kv_blocks, c.block_size, model.device, kv_dtype=c.kv_cache_dtype)
         self.cache = PagedKVCache(c.num_kv_blocks, c.block_size, enable_prefix_cache=c.enable_prefix_cache,
                                   copy_fn=self._copy_block)
-        self.scheduler = BatchScheduler(SchedulerConfig(max_num_seqs=c.max_num_seqs,
-                                                        max_num_batched_tokens=c.max_num_batched_tokens,
-                                                        max_prefill_tokens=c.max_prefill_tokens, block_size=c.block_size,
-                                                        max_chunk=c.max_chunk, max_model_len=c.max_model_len), self.cache)
+        scfg = SchedulerConfig(max_num_seqs=c.max_num_seqs, max_num_batched_tokens=c.max_num_batched_tokens,
+                               max_prefill_tokens=c.max_prefill_tokens, block_size=c.block_size, max_chunk=c.max_chunk,
+                               max_model_len=c.max_model_len)
+        if c.scheduler_policy == "priority":
+            self.scheduler = BatchScheduler(scfg, self.cache)
+        else:
+            from .fcfs import FCFSScheduler, PrefillStrategy
+            self.scheduler = FCFSScheduler(scfg, self.cache, prefill_strategy=PrefillStrategy(c.scheduler_policy))
         self.max_blocks = -(-c.max_model_len // c.block_size)
         self._buckets: Dict[int, _DecodeBucket] = {}
         self._lock = threading.RLock()

@@ -1,5 +1,6 @@
 """Continuous-batching scheduler: per-iteration token budgets, decode-first planning, chunked
-prefill, priorities with starvation promotion, preemption by recompute, FCFS variant.
+prefill, priorities with starvation promotion, preemption by recompute.  The first-come-first-served scheduler with
+prefill strategies and insertion policies builds on it in ``engine/fcfs.py``.
 
 Parity: reference ``metal_marlin/serving/continuous_batch.py``: ``SchedulerConfig`` (max_num_seqs 64,
 max_num_batched_tokens 2048, max_prefill_tokens 1024, chunk 512, starvation 30 s), ``PreemptionPolicy``,
@@ -60,7 +61,7 @@ class BatchScheduler:
 
     # ------------------------------------------------------------------ queue
     def add_request(self, req: GenerationRequest) -> RunningRequest:
-        if len(self._heap) >= self.cfg.max_waiting:
+        if self.num_waiting >= self.cfg.max_waiting:
             raise QueueFullError(f"waiting queue is full ({self.cfg.max_waiting})")
         if len(req.prompt_ids) + req.max_new_tokens > self.cfg.max_model_len:
             raise ValueError("context_length_exceeded")
@@ -72,6 +73,18 @@ class BatchScheduler:
     def _push(self, rr: RunningRequest) -> None:
         pr = 0 if self.cfg.fcfs else -rr.effective_priority
         heapq.heappush(self._heap, (pr, rr.arrival, next(self._seq), rr))
+
+    def _peek_waiting(self) -> Optional[RunningRequest]:
+        """The request admission looks at next (the head of the queue blocks the ones behind it)."""
+        return self._heap[0][3] if self._heap else None
+
+    def _pop_waiting(self, rr: RunningRequest) -> None:
+        assert self._heap[0][3] is rr
+        heapq.heappop(self._heap)
+
+    def _drop_waiting(self, rr: RunningRequest) -> None:
+        self._heap = [e for e in self._heap if e[3] is not rr]
+        heapq.heapify(self._heap)
 
     @property
     def num_waiting(self) -> int:
@@ -88,8 +101,7 @@ class BatchScheduler:
             self.running.remove(rr)
             self.cache.release(rr.id)
         else:
-            self._heap = [e for e in self._heap if e[3] is not rr]
-            heapq.heapify(self._heap)
+            self._drop_waiting(rr)
             if self.cache.table.has(rr.id):
                 self.cache.release(rr.id)
         rr.finish_reason = "abort"
@@ -173,15 +185,17 @@ class BatchScheduler:
             if n > 0:
                 out.prefill.append(PrefillChunk(rr, rr.prefill_progress, n))
                 prefill_budget -= n
-        while self._heap and prefill_budget > 0 and len(self.running) < self.cfg.max_num_seqs:
-            rr = self._heap[0][3]
+        while prefill_budget > 0 and len(self.running) < self.cfg.max_num_seqs:
+            rr = self._peek_waiting()
+            if rr is None:
+                break
             tokens = rr.all_ids[: rr.prefill_target] if rr.output_ids else rr.req.prompt_ids
             if not self.cfg.enable_chunked_prefill and len(tokens) > prefill_budget and out.prefill:
                 break
             # room for the whole context plus the first decode slot
             if not self.cache.can_admit(len(tokens) + 1):
                 break
-            heapq.heappop(self._heap)
+            self._pop_waiting(rr)
             try:
                 cached = self.cache.admit(rr.id, tokens)
             except OutOfBlocks:
@@ -241,11 +255,3 @@ class BatchScheduler:
     def stats(self) -> dict:
         return {"waiting": self.num_waiting, "running": len(self.running), "preemptions": self.num_preemptions,
                 "finished": self.num_finished, "kv": self.cache.stats()}
-
-
-class FCFSScheduler(BatchScheduler):
-    """Strict first-come-first-served variant (no priorities, no starvation promotion)."""
-
-    def __init__(self, config: SchedulerConfig, cache: PagedKVCache):
-        config.fcfs = True
-        super().__init__(config, cache)

@@ -18,7 +18,7 @@ from .transformer import BatchMeta, PagedKVStorage, Transformer
 
 
 def prefill(model: Transformer, kv: PagedKVStorage, seqs: Sequence[Sequence[int]], block_tables: torch.Tensor,
-            start: Optional[Sequence[int]] = None, chunk_tokens: int = 2048, max_batch_tokens: int = 8192) -> torch.Tensor:
+            start: Optional[Sequence[int]] = None, chunk_tokens: int = 4096, max_batch_tokens: int = 32768) -> torch.Tensor:
     """Write the prompts into the paged cache and return fp32 logits of each sequence's last token.
 
     Sequences are processed in chunks of at most ``chunk_tokens`` (chunked prefill); chunks of
