@@ -33,6 +33,9 @@ _reg(".engine.session", "DecodeSession", "SamplingParams")
 _reg(".engine.engine", "LLMEngine")
 _reg(".engine.scheduler", "BatchScheduler", "SchedulerConfig", "PreemptionPolicy", "QueueFullError")
 _reg(".inference.pipelined", "PipelineScheduler", "AsyncPipelineScheduler", "InferenceRequest", "RequestState", "generate_pipelined")
+_reg(".converters.exl3", "detect_exl3_format", "convert_sharded_to_layerwise", "load_exl3_from_hub", "download_exl3_model", "list_exl3_models",
+     "parse_model_card", "exl3_layer_to_marlin", "convert_exl3_to_marlin")
+_reg(".quant.ldlq", "block_ldl", "ldlq_quantize", "compute_group_scales", "quantize_tile_viterbi", "quantize_tile_greedy", "LDLQResult")
 _reg(".engine.fcfs", "FCFSScheduler", "PrefillStrategy", "InsertionPolicy", "CacheInfo")
 _reg(".engine.request", "GenerationRequest", "RequestStatus", "RunningRequest", "RequestPriority")
 _reg(".sampler", "SamplingConfig", "Sampler", "sample_next_token", MetalSampler="Sampler")

@@ -97,15 +97,16 @@ int mmb_embedding(const void* table, const int64_t* ids, void* out, int n, int d
 int mmb_rope(void* q, void* k, const int* positions, const float* inv_freq, int T, int Hq, int Hk, int D,
              int rot_dim, int ldq, int ldk, int interleaved, float mscale, cudaStream_t stream);
 // Per-head RMSNorm (Qwen3 q/k norm) fused with RoPE, then K/V scatter into a paged pool.
-// FP8 variant of the K / V scatter: pools of E4M3 bytes plus one fp32 scale (row amax / 448) per (slot, head).
+// Quantized variant of the K / V scatter: pools of 8- or 4-bit codes plus one fp32 scale per (slot, head); `kv_fmt`: 0 FP8
+// E4M3, 1 INT8, 2 FP4 E2M1, 3 INT4 (kv_quant.cuh; the 4-bit formats hold two values per byte, rows of D / 2 bytes).
 int mmb_qk_norm_rope_cache_fp8(void* q, const void* k, const void* v, const void* qn_w, const void* kn_w, const int* positions,
                                const float* inv_freq, const int64_t* slots, void* k_pool, void* v_pool, float* k_scale,
-                               float* v_scale, int T, int Hq, int Hk, int D, int ldqkv, float eps, int interleaved,
+                               float* v_scale, int T, int Hq, int Hk, int D, int ldqkv, float eps, int interleaved, int kv_fmt,
                                cudaStream_t stream);
 // Paged FP8 rows -> contiguous bf16 rows (prompt passes over a quantized cache): out[cu_k[b] + t, h, :] = pool row of token t
 // of sequence b times its scale.
 int mmb_kv_fp8_gather(const void* pool, const float* scale, const int* block_tables, const int* ctx_lens, const int* cu_k,
-                      void* out, int B, int Hkv, int D, int block_size, int max_blocks, int max_ctx, cudaStream_t stream);
+                      void* out, int B, int Hkv, int D, int block_size, int max_blocks, int max_ctx, int kv_fmt, cudaStream_t stream);
 int mmb_qk_norm_rope_cache(void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
                            const int* positions, const float* inv_freq, const int64_t* slots, void* k_pool,
                            void* v_pool, int T, int Hq, int Hk, int D, int ldqkv, float eps, int interleaved,
@@ -128,7 +129,8 @@ typedef struct {
   float eps, mscale;
   int interleaved;
   int skip_absorb;          // 1: leave q_full[:, :, :R] untouched (prefill uses the non-absorbed form), only RoPE + cache write
-  float* cache_scale;       // FP8 cache: cache holds E4M3 bytes [num_slots, R + dr], cache_scale fp32 [num_slots] the row's scale
+  float* cache_scale;       // quantized cache: cache holds codes [num_slots, (R + dr) or (R + dr) / 2 bytes], cache_scale fp32 [num_slots]
+  int cache_fmt;            // format of a quantized cache (0 FP8 E4M3, 1 INT8, 2 FP4 E2M1, 3 INT4)
 } MmbMlaPrepParams;
 int mmb_mla_prep(const MmbMlaPrepParams* p, cudaStream_t stream);
 
@@ -149,6 +151,7 @@ typedef struct {
   // every (token, head) row; rows are expanded to bf16 in shared memory after they land.  Null scales = bf16 pools.
   const float* k_scale;
   const float* v_scale;
+  int kv_fmt;               // with scales: 0 FP8 E4M3, 1 INT8, 2 FP4 E2M1, 3 INT4 (4-bit rows hold dqk / 2 and dv / 2 bytes)
 } MmbPagedDecodeParams;
 int mmb_paged_decode(const MmbPagedDecodeParams* p, cudaStream_t stream);
 // Merge the split partials; optional per-head up projection W_uv [Hq, dvo, dv] (MLA), output bf16 [B, Hq, dvo or dv].

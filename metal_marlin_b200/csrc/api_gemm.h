@@ -59,11 +59,18 @@ typedef struct {
   // matrix), matrices per expert, and the first matrix of the projection (qw / sc / gs_shift are unused).
   const long long* tr_desc;
   int tr_stride, tr_first;
+  // Codebook weights (mmb_codebook_gemm: INT8 / INT4 / INT2 with or without zero points, FP8, NF4 ...): qw = codes, row major
+  // [N, K * bits / 8], LSB-first along K; sc = fp16 scales [N, K >> gs_shift]; w = (lut[code] - zero) * scale.
+  const void* cb_zeros;     // fp16 [N, K >> gs_shift] or null
+  const float* cb_lut;      // device float [256]
+  int cb_bits;              // 2, 4 or 8
 } MmbFp4GemmParams;
 
 int mmb_fp4_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
 // Same pipeline with trellis weights decoded inside the main loop (2..8 bits per matrix, mixed per expert and matrix).
 int mmb_trellis_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
+// Same pipeline with codebook weights (table look-up, zero point and group scale applied inside the main loop); plain mode only.
+int mmb_codebook_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
 
 // out[M, N] = x[M, K] * W[N, K]^T, both bf16 row major (TMA for both operands), fp32 accumulate in TMEM.
 // Batched over `batch` independent problems with element strides (0 = shared operand).

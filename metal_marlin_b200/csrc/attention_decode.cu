@@ -14,6 +14,7 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "kv_quant.cuh"
 #include "launch.h"
 
 namespace cg = cooperative_groups;
@@ -161,9 +162,16 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const MmbMlaPrepParams p)
         }
         amax = block_max(amax, red);
         if (slot >= 0) {
-          const float sc = amax > 0.f ? amax / 448.f : 1.f, inv = 1.f / sc;
-          unsigned char* dst8 = reinterpret_cast<unsigned char*>(p.cache) + slot * dl;
-          for (int d = tid; d < dl; d += 256) dst8[d] = (unsigned char)__nv_cvt_float_to_fp8(sm[d] * inv, __NV_SATFINITE, __NV_E4M3);
+          const int fmt = p.cache_fmt;
+          const float sc = amax > 0.f ? amax / kvq_range(fmt) : 1.f, inv = 1.f / sc;
+          if (kvq_is4(fmt)) {
+            unsigned char* dst8 = reinterpret_cast<unsigned char*>(p.cache) + slot * (dl / 2);
+            for (int d = tid; d < dl / 2; d += 256)
+              dst8[d] = (unsigned char)(kvq_encode(sm[2 * d] * inv, fmt) | (kvq_encode(sm[2 * d + 1] * inv, fmt) << 4));
+          } else {
+            unsigned char* dst8 = reinterpret_cast<unsigned char*>(p.cache) + slot * dl;
+            for (int d = tid; d < dl; d += 256) dst8[d] = (unsigned char)kvq_encode(sm[d] * inv, fmt);
+          }
           if (tid == 0) p.cache_scale[slot] = sc;
         }
       } else if (slot >= 0) {
@@ -211,19 +219,21 @@ __device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem));
 }
 
-// In-place expansion of a tile of E4M3 rows (D bytes each, sitting in the upper half of bf16 rows of stride RS elements)
-// to bf16 x row scale.  Called by all NT threads of the CTA: every thread first reads its 16-byte pieces, the CTA
-// synchronizes, then the 32-byte results are written (a piece's result overlaps other pieces' source bytes).
-template <int D, int RS, int NT, int TT>
-__device__ __forceinline__ void expand_fp8_rows(bf16* rows, const float* row_scale, int nvalid, int tid) {
-  constexpr int UPR = D / 16;                               // pieces per row
+// In-place expansion of a tile of quantized rows to bf16 x row scale.  BPV = 1: D code bytes sit in the upper half of a bf16
+// row of stride RS elements; BPV = 2 (4-bit codes, two per byte): D / 2 bytes sit in its last quarter.  Called by all NT
+// threads of the CTA: every thread first reads its 16-byte pieces, the CTA synchronizes, then the 32- / 64-byte results are
+// written (a piece's result overlaps other pieces' source bytes).
+template <int D, int RS, int NT, int TT, int BPV>
+__device__ __forceinline__ void expand_fp8_rows(bf16* rows, const float* row_scale, int nvalid, int tid, int fmt) {
+  constexpr int UPR = D / (16 * BPV);                        // pieces per row
   constexpr int PER = (TT * UPR + NT - 1) / NT;              // pieces per thread
+  constexpr int SRC0 = 2 * D - D / BPV;                      // byte offset of the codes inside the row
   uint4 raw[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int u = tid + i * NT, r = u / UPR, c = u - r * UPR;
     raw[i] = make_uint4(0, 0, 0, 0);
-    if (r < nvalid) raw[i] = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(rows + r * RS) + D + c * 16);
+    if (r < nvalid) raw[i] = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(rows + r * RS) + SRC0 + c * 16);
   }
   __syncthreads();
 #pragma unroll
@@ -232,17 +242,30 @@ __device__ __forceinline__ void expand_fp8_rows(bf16* rows, const float* row_sca
     if (r >= nvalid) continue;
     const float sc = row_scale[r];
     const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-    uint32_t o[8];
+    if (BPV == 1) {
+      uint32_t o[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w[e >> 1] >> ((e & 1) * 16)) & 0xffffu), __NV_E4M3);
-      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
-      const bf162 b2 = __floats2bfloat162_rn(f.x * sc, f.y * sc);
-      o[e] = *reinterpret_cast<const uint32_t*>(&b2);
+      for (int e = 0; e < 8; ++e) {
+        const float2 f = kvq_decode8x2(w[e >> 1] >> ((e & 1) * 16), fmt);
+        const bf162 b2 = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        o[e] = *reinterpret_cast<const uint32_t*>(&b2);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(rows + r * RS + c * 16);
+      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    } else {
+      uint4* dst = reinterpret_cast<uint4*>(rows + r * RS + c * 32);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {                       // one 32-bit word = 8 values = one 16-byte result
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const bf162 b2 = __floats2bfloat162_rn(kvq_decode4((w[q4] >> (8 * e)) & 0xfu, fmt) * sc, kvq_decode4((w[q4] >> (8 * e + 4)) & 0xfu, fmt) * sc);
+          o[e] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+        dst[q4] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
     }
-    uint4* dst = reinterpret_cast<uint4*>(rows + r * RS + c * 16);
-    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
   }
   __syncthreads();
 }
@@ -271,7 +294,7 @@ struct DecodeSmem {
 
 // grid (splits, Hkv, B), NW * 32 threads.  FP8: the pools hold E4M3 bytes and a scale per (slot, head); a row's bytes land
 // in the upper half of its bf16 row in shared memory and are expanded in place (all reads, a barrier, all writes).
-template <int DQK, int DV, int MT, bool SHARED_V, int NW, bool FP8, int TT>
+template <int DQK, int DV, int MT, bool SHARED_V, int NW, int FP8, int TT>
 __global__ void __launch_bounds__(NW * 32, (TT == 32) ? 2 : 1) paged_decode_kernel(const MmbPagedDecodeParams p) {
   using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW, TT>;
   constexpr int NT = NW * 32;
@@ -345,18 +368,20 @@ __global__ void __launch_bounds__(NW * 32, (TT == 32) ? 2 : 1) paged_decode_kern
     const int nvalid = min(kTileTok, ctx - tok0);
     bf16* kd = buf ? k_s1 : k_s0;
     bf16* vd = buf ? v_s1 : v_s0;
-    if (tid == 0) mbar_expect_tx(&bar_kv[buf], (uint32_t)nvalid * (uint32_t)((DQK + (SHARED_V ? 0 : DV)) * (FP8 ? 1 : 2)));
+    // FP8 = 0: bf16 rows; 1: one code byte per value; 2: two 4-bit codes per byte
+    if (tid == 0) mbar_expect_tx(&bar_kv[buf], (uint32_t)nvalid * (uint32_t)((DQK + (SHARED_V ? 0 : DV)) * 2 / (FP8 == 0 ? 1 : 2 * FP8)));
     if (tid < nvalid) {
       const int tok = tok0 + tid;
       const long long slot = pow2_blocks ? (((long long)__ldg(bt + (tok >> bs_shift)) << bs_shift) + (tok & (p.block_size - 1)))
                                          : ((long long)__ldg(bt + tok / p.block_size) * p.block_size + (tok % p.block_size));
       if (FP8) {
         const long long row = slot * p.Hkv + hkv;
-        bulk_g2s(reinterpret_cast<unsigned char*>(kd + tid * L::KS) + DQK, reinterpret_cast<const unsigned char*>(p.k_pool) + row * DQK, DQK,
+        constexpr int KB8 = DQK / (FP8 ? FP8 : 1), VB8 = DV / (FP8 ? FP8 : 1);      // code bytes per row
+        bulk_g2s(reinterpret_cast<unsigned char*>(kd + tid * L::KS) + 2 * DQK - KB8, reinterpret_cast<const unsigned char*>(p.k_pool) + row * KB8, KB8,
                  &bar_kv[buf]);
         cp_async_4(&scale_s[buf][0][tid], p.k_scale + row);
         if (!SHARED_V) {
-          bulk_g2s(reinterpret_cast<unsigned char*>(vd + tid * L::VS) + DV, reinterpret_cast<const unsigned char*>(p.v_pool) + row * DV, DV,
+          bulk_g2s(reinterpret_cast<unsigned char*>(vd + tid * L::VS) + 2 * DV - VB8, reinterpret_cast<const unsigned char*>(p.v_pool) + row * VB8, VB8,
                    &bar_kv[buf]);
           cp_async_4(&scale_s[buf][1][tid], p.v_scale + row);
         }
@@ -422,8 +447,8 @@ __global__ void __launch_bounds__(NW * 32, (TT == 32) ? 2 : 1) paged_decode_kern
     const bf16* vt = buf ? v_s1 : v_s0;
     if (FP8) {
       const int nvalid = min(kTileTok, ctx - (lo_al + tile * kTileTok));
-      expand_fp8_rows<DQK, L::KS, NT, TT>(buf ? k_s1 : k_s0, scale_s[buf][0], nvalid, tid);
-      if (!SHARED_V) expand_fp8_rows<DV, L::VS, NT, TT>(buf ? v_s1 : v_s0, scale_s[buf][1], nvalid, tid);
+      expand_fp8_rows<DQK, L::KS, NT, TT, FP8 ? FP8 : 1>(buf ? k_s1 : k_s0, scale_s[buf][0], nvalid, tid, p.kv_fmt);
+      if (!SHARED_V) expand_fp8_rows<DV, L::VS, NT, TT, FP8 ? FP8 : 1>(buf ? v_s1 : v_s0, scale_s[buf][1], nvalid, tid, p.kv_fmt);
     }
 
     // ---- S = Q K^T for this warp's token columns
@@ -785,7 +810,7 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restri
   }
 }
 
-template <int DQK, int DV, int MT, bool SHARED_V, int NW, bool FP8, int TT = 64>
+template <int DQK, int DV, int MT, bool SHARED_V, int NW, int FP8, int TT = 64>
 static int launch_decode_impl(const MmbPagedDecodeParams& p, cudaStream_t stream) {
   using L = DecodeSmem<DQK, DV, MT, SHARED_V, NW, TT>;
   auto kern = paged_decode_kernel<DQK, DV, MT, SHARED_V, NW, FP8, TT>;
@@ -801,10 +826,14 @@ static int launch_decode_impl(const MmbPagedDecodeParams& p, cudaStream_t stream
 template <int DQK, int DV, int MT, bool SHARED_V, int NW>
 static int launch_decode(const MmbPagedDecodeParams& p, cudaStream_t stream) {
   if (p.k_scale != nullptr) {
-    if (!SHARED_V && p.v_scale == nullptr) return (int)cudaErrorInvalidValue;
-    return launch_decode_impl<DQK, DV, MT, SHARED_V, NW, true>(p, stream);
+    if ((!SHARED_V && p.v_scale == nullptr) || p.kv_fmt < 0 || p.kv_fmt > 3) return (int)cudaErrorInvalidValue;
+    if (kvq_is4(p.kv_fmt)) {
+      if constexpr (DQK % 32 == 0 && DV % 32 == 0) return launch_decode_impl<DQK, DV, MT, SHARED_V, NW, 2>(p, stream);
+      return (int)cudaErrorNotSupported;
+    }
+    return launch_decode_impl<DQK, DV, MT, SHARED_V, NW, 1>(p, stream);
   }
-  return launch_decode_impl<DQK, DV, MT, SHARED_V, NW, false>(p, stream);
+  return launch_decode_impl<DQK, DV, MT, SHARED_V, NW, 0>(p, stream);
 }
 
 }  // namespace mmb
@@ -828,7 +857,7 @@ MMB_API int mmb_paged_decode(const MmbPagedDecodeParams* pp, cudaStream_t stream
   const int Gh = p.Hq / p.Hkv;
   const bool shared = (p.v_pool == nullptr);
   if (shared && p.dqk == 576 && p.dv == 512 && Gh <= 23 && (long long)p.B * p.Hkv * p.splits > 148 && p.k_scale == nullptr)
-    return launch_decode_impl<576, 512, 2, true, 8, false, 32>(p, stream);      // more CTAs than SMs: two smaller CTAs per SM
+    return launch_decode_impl<576, 512, 2, true, 8, 0, 32>(p, stream);      // more CTAs than SMs: two smaller CTAs per SM
   if (shared && p.dqk == 576 && p.dv == 512 && Gh <= 32) return launch_decode<576, 512, 2, true, 8>(p, stream);
   if (shared && p.dqk == 96 && p.dv == 64 && Gh <= 16) return launch_decode<96, 64, 1, true, 4>(p, stream);   // tiny MLA (tests)
   if (!shared && p.dqk == 128 && p.dv == 128 && Gh <= 16) return launch_decode<128, 128, 1, false, 8>(p, stream);

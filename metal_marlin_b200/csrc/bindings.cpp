@@ -269,37 +269,39 @@ void qk_norm_rope_cache(Tensor q, const Tensor& k, const Tensor& v, const OptT& 
 
 void qk_norm_rope_cache_fp8(Tensor q, const Tensor& k, const Tensor& v, const OptT& qn_w, const OptT& kn_w, const Tensor& positions,
                             const Tensor& inv_freq, const Tensor& slots, Tensor k_pool, Tensor v_pool, Tensor k_scale, Tensor v_scale,
-                            int64_t Hq, int64_t Hk, int64_t D, double eps, bool interleaved) {
+                            int64_t Hq, int64_t Hk, int64_t D, double eps, bool interleaved, int64_t kv_fmt) {
   check_bf16(q, "q");
   TORCH_CHECK(q.stride(0) == k.stride(0) && q.stride(0) == v.stride(0));
   TORCH_CHECK(positions.scalar_type() == at::kInt && slots.scalar_type() == at::kLong);
+  TORCH_CHECK(k_pool.size(-1) == (kv_fmt >= 2 ? D / 2 : D) && v_pool.size(-1) == k_pool.size(-1), "quantized KV pool row width does not match the format");
   TORCH_CHECK(k_pool.scalar_type() == at::kByte && v_pool.scalar_type() == at::kByte && k_scale.scalar_type() == at::kFloat &&
               v_scale.scalar_type() == at::kFloat && k_pool.is_contiguous() && v_pool.is_contiguous());
   c10::cuda::CUDAGuard guard(q.device());
   check(mmb_qk_norm_rope_cache_fp8(q.data_ptr(), k.data_ptr(), v.data_ptr(), cptr(qn_w), cptr(kn_w), positions.data_ptr<int>(),
                                    inv_freq.data_ptr<float>(), slots.data_ptr<int64_t>(), k_pool.data_ptr(), v_pool.data_ptr(),
                                    k_scale.data_ptr<float>(), v_scale.data_ptr<float>(), (int)positions.numel(), (int)Hq, (int)Hk, (int)D,
-                                   (int)q.stride(0), (float)eps, interleaved ? 1 : 0, cur_stream()),
+                                   (int)q.stride(0), (float)eps, interleaved ? 1 : 0, (int)kv_fmt, cur_stream()),
         "qk_norm_rope_cache_fp8");
 }
 
 // pool uint8 [num_slots, Hkv, D] + scale fp32 [num_slots, Hkv] -> out bf16 [sum ctx, Hkv, D] (rows cu_k[b] .. of sequence b)
 void kv_fp8_gather(const Tensor& pool, const Tensor& scale, const Tensor& block_tables, const Tensor& ctx_lens, const Tensor& cu_k, Tensor out,
-                   int64_t Hkv, int64_t D, int64_t block_size, int64_t max_ctx) {
+                   int64_t Hkv, int64_t D, int64_t block_size, int64_t max_ctx, int64_t kv_fmt) {
   check_bf16(out, "out");
+  TORCH_CHECK(pool.size(-1) == (kv_fmt >= 2 ? D / 2 : D), "quantized KV pool row width does not match the format");
   TORCH_CHECK(pool.scalar_type() == at::kByte && pool.is_contiguous() && scale.scalar_type() == at::kFloat && out.is_contiguous());
   TORCH_CHECK(block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 && block_tables.is_contiguous() &&
               ctx_lens.scalar_type() == at::kInt && cu_k.scalar_type() == at::kInt);
   c10::cuda::CUDAGuard guard(pool.device());
   check(mmb_kv_fp8_gather(pool.data_ptr(), scale.data_ptr<float>(), block_tables.data_ptr<int>(), ctx_lens.data_ptr<int>(),
                           cu_k.data_ptr<int>(), out.data_ptr(), (int)ctx_lens.numel(), (int)Hkv, (int)D, (int)block_size,
-                          (int)block_tables.size(1), (int)max_ctx, cur_stream()),
+                          (int)block_tables.size(1), (int)max_ctx, (int)kv_fmt, cur_stream()),
         "kv_fp8_gather");
 }
 
 void mla_prep_impl(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
                    const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, int64_t H, int64_t dn, int64_t dr,
-                   int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb, Tensor* cache_scale);
+                   int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb, Tensor* cache_scale, int64_t cache_fmt = 0);
 void mla_prep(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
               const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, int64_t H, int64_t dn, int64_t dr,
               int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb) {
@@ -307,18 +309,20 @@ void mla_prep(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Ten
   mla_prep_impl(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps, mscale, interleaved, skip_absorb,
                 nullptr);
 }
-// FP8 latent cache: `cache` uint8 [num_slots, R + dr] (E4M3), `cache_scale` fp32 [num_slots].
+// Quantized latent cache: `cache` uint8 [num_slots, R + dr] (8-bit formats) or [num_slots, (R + dr) / 2] (4-bit), `cache_scale`
+// fp32 [num_slots]; `cache_fmt` as in kv_quant.cuh.
 void mla_prep_fp8(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
                   const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, Tensor cache_scale, int64_t H, int64_t dn,
-                  int64_t dr, int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb) {
+                  int64_t dr, int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb, int64_t cache_fmt) {
   TORCH_CHECK(cache.scalar_type() == at::kByte && cache_scale.scalar_type() == at::kFloat && cache_scale.is_contiguous() &&
-              cache_scale.numel() == cache.size(0));
+              cache_scale.numel() == cache.size(0) && cache_fmt >= 0 && cache_fmt <= 3);
+  TORCH_CHECK(cache.size(-1) == (cache_fmt >= 2 ? (R + dr) / 2 : R + dr), "quantized latent cache row width does not match the format");
   mla_prep_impl(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps, mscale, interleaved, skip_absorb,
-                &cache_scale);
+                &cache_scale, cache_fmt);
 }
 void mla_prep_impl(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, const Tensor& kv_norm_w, const Tensor& positions,
                    const Tensor& inv_freq, const Tensor& slots, Tensor q_full, Tensor cache, int64_t H, int64_t dn, int64_t dr,
-                   int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb, Tensor* cache_scale) {
+                   int64_t R, double eps, double mscale, bool interleaved, bool skip_absorb, Tensor* cache_scale, int64_t cache_fmt) {
   check_bf16(q, "q");
   check_bf16(kva, "kva");
   check_bf16(w_ukT, "w_ukT");
@@ -347,6 +351,7 @@ void mla_prep_impl(const Tensor& q, const Tensor& kva, const Tensor& w_ukT, cons
   p.interleaved = interleaved ? 1 : 0;
   p.skip_absorb = skip_absorb ? 1 : 0;
   p.cache_scale = cache_scale ? cache_scale->data_ptr<float>() : nullptr;
+  p.cache_fmt = (int)cache_fmt;
   check(mmb_mla_prep(&p, cur_stream()), "mla_prep");
 }
 
@@ -365,7 +370,7 @@ inline int* status_word_of(const Tensor& t) {
 
 void paged_decode_impl(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& block_tables, const Tensor& ctx_lens,
                        Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk, int64_t dv, int64_t block_size, int64_t splits,
-                       double scale, int64_t window, const Tensor* k_scale, const OptT* v_scale);
+                       double scale, int64_t window, const Tensor* k_scale, const OptT* v_scale, int64_t kv_fmt = 0);
 void paged_decode(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& block_tables,
                   const Tensor& ctx_lens, Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk, int64_t dv,
                   int64_t block_size, int64_t splits, double scale, int64_t window) {
@@ -376,17 +381,19 @@ void paged_decode(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, con
 // FP8 pools: uint8 (E4M3) K / V pools with fp32 scales [num_slots, Hkv].
 void paged_decode_fp8(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& k_scale, const OptT& v_scale,
                       const Tensor& block_tables, const Tensor& ctx_lens, Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk,
-                      int64_t dv, int64_t block_size, int64_t splits, double scale, int64_t window) {
+                      int64_t dv, int64_t block_size, int64_t splits, double scale, int64_t window, int64_t kv_fmt) {
   TORCH_CHECK(k_pool.scalar_type() == at::kByte && k_scale.scalar_type() == at::kFloat && k_scale.is_contiguous());
-  TORCH_CHECK(dqk % 16 == 0 && dv % 16 == 0, "FP8 rows are copied in 16-byte pieces");
+  TORCH_CHECK(kv_fmt >= 0 && kv_fmt <= 3 && dqk % (kv_fmt >= 2 ? 32 : 16) == 0 && dv % (kv_fmt >= 2 ? 32 : 16) == 0,
+              "quantized rows are copied in 16-byte pieces");
+  TORCH_CHECK(k_pool.size(-1) == (kv_fmt >= 2 ? dqk / 2 : dqk), "quantized KV pool row width does not match the format");
   if (v_pool.has_value() && v_pool->defined())
     TORCH_CHECK(v_pool->scalar_type() == at::kByte && v_scale.has_value() && v_scale->defined() && v_scale->scalar_type() == at::kFloat);
   paged_decode_impl(q, k_pool, v_pool, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv, block_size, splits, scale, window, &k_scale,
-                    &v_scale);
+                    &v_scale, kv_fmt);
 }
 void paged_decode_impl(const Tensor& q, const Tensor& k_pool, const OptT& v_pool, const Tensor& block_tables, const Tensor& ctx_lens,
                        Tensor part_o, Tensor part_ml, int64_t Hq, int64_t Hkv, int64_t dqk, int64_t dv, int64_t block_size, int64_t splits,
-                       double scale, int64_t window, const Tensor* k_scale, const OptT* v_scale) {
+                       double scale, int64_t window, const Tensor* k_scale, const OptT* v_scale, int64_t kv_fmt) {
   check_bf16(q, "q");
   TORCH_CHECK(q.is_contiguous() && k_pool.is_contiguous() && block_tables.is_contiguous() && block_tables.dim() == 2);
   TORCH_CHECK(block_tables.scalar_type() == at::kInt && ctx_lens.scalar_type() == at::kInt);
@@ -412,6 +419,7 @@ void paged_decode_impl(const Tensor& q, const Tensor& k_pool, const OptT& v_pool
   p.window = (int)window;
   if (k_scale != nullptr) {
     p.k_scale = k_scale->data_ptr<float>();
+    p.kv_fmt = (int)kv_fmt;
     if (v_scale != nullptr && v_scale->has_value() && (*v_scale)->defined()) p.v_scale = (*v_scale)->data_ptr<float>();
   }
   TORCH_CHECK(part_o.numel() >= (int64_t)p.B * Hq * splits * dv && part_ml.numel() >= (int64_t)p.B * Hq * splits * 2);
@@ -988,6 +996,41 @@ void trellis_moe(const Tensor& x, const Tensor& mats, const Tensor& ids, const T
         "trellis_moe");
 }
 
+// Codebook weights on the tensor cores for more than 8 rows: look-up, zero point and group scale applied inside the GEMM's
+// main loop (gemm_sm100.cu, weight format 3).
+void codebook_gemm(const Tensor& x, const Tensor& codes, const Tensor& scales, const OptT& zeros, const Tensor& lut, Tensor out,
+                   int64_t in_f, int64_t group_size, int64_t bits, Tensor status) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.size(1) == in_f && out.is_contiguous() && out.size(0) == x.size(0));
+  TORCH_CHECK(codes.is_cuda() && codes.scalar_type() == at::kByte && codes.is_contiguous() && codes.dim() == 2 &&
+              codes.size(1) * 8 == in_f * bits && out.size(1) == codes.size(0));
+  TORCH_CHECK(scales.scalar_type() == at::kHalf && scales.is_contiguous() && lut.scalar_type() == at::kFloat && lut.numel() == 256 && lut.is_cuda());
+  TORCH_CHECK(group_size >= 32 && (group_size & (group_size - 1)) == 0 && in_f % group_size == 0 && in_f % 64 == 0,
+              "codebook_gemm: group size must be a power of two >= 32 dividing the input width (a multiple of 64)");
+  TORCH_CHECK(scales.numel() == codes.size(0) * (in_f / group_size));
+  if (zeros.has_value() && zeros->defined()) TORCH_CHECK(zeros->scalar_type() == at::kHalf && zeros->is_contiguous() && zeros->numel() == scales.numel());
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbFp4GemmParams p{};
+  p.x = x.data_ptr();
+  p.qw = codes.data_ptr();
+  p.sc = scales.data_ptr();
+  p.out = out.data_ptr();
+  p.M = (int)x.size(0);
+  p.N = (int)codes.size(0);
+  p.K = (int)in_f;
+  p.Kx = (int)in_f;
+  p.ldo = (int)out.stride(0);
+  int sh = 0;
+  while ((1ll << sh) < group_size) ++sh;
+  p.gs_shift = sh;
+  p.status = status.data_ptr<int>();
+  p.cb_zeros = cptr(zeros);
+  p.cb_lut = lut.data_ptr<float>();
+  p.cb_bits = (int)bits;
+  check(mmb_codebook_gemm(&p, cur_stream()), "codebook_gemm");
+}
+
 void codebook_gemv(const Tensor& x, const Tensor& codes, const Tensor& scales, const OptT& zeros, const Tensor& lut, Tensor y,
                    int64_t in_f, int64_t group_size, int64_t bits) {
   check_bf16(x, "x");
@@ -1309,6 +1352,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("trellis_gemv", &trellis_gemv);
   m.def("trellis_moe", &trellis_moe);
   m.def("codebook_gemv", &codebook_gemv);
+  m.def("codebook_gemm", &codebook_gemm);
   m.def("vision_preprocess", &vision_preprocess);
   m.def("vision_preprocess_ex", &vision_preprocess_ex);
   m.def("channel_stats", &channel_stats);

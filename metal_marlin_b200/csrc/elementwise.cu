@@ -3,6 +3,7 @@
 // accesses where the row length allows, fp32 math, bf16 storage.
 #include "api.h"
 #include "common.cuh"
+#include "kv_quant.cuh"
 
 namespace mmb {
 
@@ -140,9 +141,14 @@ __global__ void rope_kernel(bf16* __restrict__ q, bf16* __restrict__ k, const in
 
 // Qwen3-style attention prologue: per-head RMSNorm of q and k (optional), RoPE, K/V scatter to a paged
 // pool [num_slots, Hk, D].  grid = (T, Hq + Hk); one warp-sized CTA per (token, head); D <= 256.
-// E4M3 byte of v / scale (saturating).
-__device__ __forceinline__ unsigned char to_e4m3(float v) {
-  return (unsigned char)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+// One quantized row: `vals` (shared memory, D floats) -> codes at `dst` (D bytes, or D / 2 for the 4-bit formats).
+__device__ __forceinline__ void kvq_store_row(unsigned char* dst, const float* vals, float inv, int D, int fmt) {
+  if (kvq_is4(fmt)) {
+    for (int i = threadIdx.x; i < D / 2; i += blockDim.x)
+      dst[i] = (unsigned char)(kvq_encode(vals[2 * i] * inv, fmt) | (kvq_encode(vals[2 * i + 1] * inv, fmt) << 4));
+  } else {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = (unsigned char)kvq_encode(vals[i] * inv, fmt);
+  }
 }
 
 // FP8 cache variant of the kernel below: same prologue; the K row (after norm + RoPE) and the V row are quantized to
@@ -153,7 +159,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_cache_fp8_kernel(bf16* __res
                                                                      const float* __restrict__ inv_freq, const int64_t* __restrict__ slots,
                                                                      unsigned char* __restrict__ k_pool, unsigned char* __restrict__ v_pool,
                                                                      float* __restrict__ k_scale, float* __restrict__ v_scale, int Hq,
-                                                                     int Hk, int D, int ldqkv, float eps, int interleaved) {
+                                                                     int Hk, int D, int ldqkv, float eps, int interleaved, int fmt) {
   __shared__ float red[32];
   __shared__ float vals[256];
   const long long tkn = blockIdx.x;
@@ -199,42 +205,57 @@ __global__ void __launch_bounds__(128) qk_norm_rope_cache_fp8_kernel(bf16* __res
   if (is_q || slot < 0) return;
   const long long row = slot * Hk + (h - Hq);
   amax = block_max(amax, red);
+  const int row_bytes = kvq_is4(fmt) ? D / 2 : D;
+  __syncthreads();       // all rotated values are in `vals`
   {
-    const float sc = amax > 0.f ? amax / 448.f : 1.f, inv = 1.f / sc;
-    unsigned char* kd = k_pool + row * (long long)D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) kd[i] = to_e4m3(vals[i] * inv);
+    const float sc = amax > 0.f ? amax / kvq_range(fmt) : 1.f, inv = 1.f / sc;
+    kvq_store_row(k_pool + row * (long long)row_bytes, vals, inv, D, fmt);
     if (threadIdx.x == 0) k_scale[row] = sc;
   }
   if (v != nullptr) {
     const bf16* vs = v + tkn * ldqkv + (long long)(h - Hq) * D;
     float vmax = 0.f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) vmax = fmaxf(vmax, fabsf(__bfloat162float(vs[i])));
+    __syncthreads();     // the K codes have been read out of `vals`
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      const float x = __bfloat162float(vs[i]);
+      vals[i] = x;
+      vmax = fmaxf(vmax, fabsf(x));
+    }
     vmax = block_max(vmax, red);
-    const float sc = vmax > 0.f ? vmax / 448.f : 1.f, inv = 1.f / sc;
-    unsigned char* vd = v_pool + row * (long long)D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) vd[i] = to_e4m3(__bfloat162float(vs[i]) * inv);
+    const float sc = vmax > 0.f ? vmax / kvq_range(fmt) : 1.f, inv = 1.f / sc;
+    kvq_store_row(v_pool + row * (long long)row_bytes, vals, inv, D, fmt);
     if (threadIdx.x == 0) v_scale[row] = sc;
   }
 }
 
-// Paged FP8 rows to contiguous bf16: grid (max_ctx, Hkv, B), one row per CTA of 64 threads (4 bytes per thread and trip).
+// Paged quantized rows to contiguous bf16: grid (max_ctx, Hkv, B), one row per CTA of 64 threads (4 bytes per thread and trip).
 __global__ void __launch_bounds__(64) kv_fp8_gather_kernel(const unsigned char* __restrict__ pool, const float* __restrict__ scale,
                                                            const int* __restrict__ block_tables, const int* __restrict__ ctx_lens,
                                                            const int* __restrict__ cu_k, bf16* __restrict__ out, int Hkv, int D,
-                                                           int block_size, int max_blocks) {
+                                                           int block_size, int max_blocks, int fmt) {
   const int t = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   if (t >= ctx_lens[b]) return;
   const long long slot = (long long)block_tables[(long long)b * max_blocks + t / block_size] * block_size + t % block_size;
   const long long row = slot * Hkv + h;
   const float sc = scale[row];
-  const unsigned char* src = pool + row * (long long)D;
   bf16* dst = out + ((long long)(cu_k[b] + t) * Hkv + h) * D;
+  if (kvq_is4(fmt)) {
+    const unsigned char* src = pool + row * (long long)(D / 2);
+    for (int i = threadIdx.x * 4; i < D / 2; i += 64 * 4) {      // 4 bytes = 8 values
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(src + i);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        *reinterpret_cast<bf162*>(dst + 2 * i + 2 * e) =
+            __floats2bfloat162_rn(kvq_decode4((w >> (8 * e)) & 0xfu, fmt) * sc, kvq_decode4((w >> (8 * e + 4)) & 0xfu, fmt) * sc);
+    }
+    return;
+  }
+  const unsigned char* src = pool + row * (long long)D;
   for (int i = threadIdx.x * 4; i < D; i += 64 * 4) {
     const uint32_t w = *reinterpret_cast<const uint32_t*>(src + i);
 #pragma unroll
     for (int e = 0; e < 4; e += 2) {
-      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w >> (8 * e)) & 0xffffu), __NV_E4M3);
-      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      const float2 f = kvq_decode8x2(w >> (8 * e), fmt);
       *reinterpret_cast<bf162*>(dst + i + e) = __floats2bfloat162_rn(f.x * sc, f.y * sc);
     }
   }
@@ -368,24 +389,25 @@ MMB_API int mmb_qk_norm_rope_cache(void* q, const void* k, const void* v, const 
 
 MMB_API int mmb_qk_norm_rope_cache_fp8(void* q, const void* k, const void* v, const void* qn_w, const void* kn_w, const int* positions,
                                        const float* inv_freq, const int64_t* slots, void* k_pool, void* v_pool, float* k_scale,
-                                       float* v_scale, int T, int Hq, int Hk, int D, int ldqkv, float eps, int interleaved,
+                                       float* v_scale, int T, int Hq, int Hk, int D, int ldqkv, float eps, int interleaved, int kv_fmt,
                                        cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (D > 256 || D % 4 || k_scale == nullptr || (v != nullptr && v_scale == nullptr)) return (int)cudaErrorInvalidValue;
+  if (D > 256 || D % 8 || k_scale == nullptr || (v != nullptr && v_scale == nullptr) || kv_fmt < 0 || kv_fmt > 3) return (int)cudaErrorInvalidValue;
   dim3 grid(T, Hq + Hk);
   mmb::qk_norm_rope_cache_fp8_kernel<<<grid, 128, 0, stream>>>((bf16*)q, (const bf16*)k, (const bf16*)v, (const bf16*)qn_w,
                                                                (const bf16*)kn_w, positions, inv_freq, slots, (unsigned char*)k_pool,
                                                                (unsigned char*)v_pool, k_scale, v_scale, Hq, Hk, D, ldqkv, eps,
-                                                               interleaved);
+                                                               interleaved, kv_fmt);
   return (int)cudaGetLastError();
 }
 
 MMB_API int mmb_kv_fp8_gather(const void* pool, const float* scale, const int* block_tables, const int* ctx_lens, const int* cu_k,
-                              void* out, int B, int Hkv, int D, int block_size, int max_blocks, int max_ctx, cudaStream_t stream) {
+                              void* out, int B, int Hkv, int D, int block_size, int max_blocks, int max_ctx, int kv_fmt,
+                              cudaStream_t stream) {
   if (B <= 0 || max_ctx <= 0) return 0;
-  if (D % 4 != 0 || Hkv > 65535 || B > 65535) return (int)cudaErrorInvalidValue;
+  if (D % 8 != 0 || Hkv > 65535 || B > 65535 || kv_fmt < 0 || kv_fmt > 3) return (int)cudaErrorInvalidValue;
   dim3 grid(max_ctx, Hkv, B);
   mmb::kv_fp8_gather_kernel<<<grid, 64, 0, stream>>>((const unsigned char*)pool, scale, block_tables, ctx_lens, cu_k, (bf16*)out, Hkv, D,
-                                                     block_size, max_blocks);
+                                                     block_size, max_blocks, kv_fmt);
   return (int)cudaGetLastError();
 }

@@ -63,8 +63,30 @@ struct PipeShared {
   int abort_flag;
 };
 
+// One lane's 32 codes of a codebook row (LSB-first, BITS each) -> four 16-byte chunks of the swizzled K-major A row.
+template <int BITS>
+__device__ __forceinline__ void cb_expand_row(const uint32_t (&words)[8], const float* lut_s, float zp, float sc, unsigned char* dst,
+                                              int half, int r7) {
+  constexpr unsigned cmask = (1u << BITS) - 1u;
+#pragma unroll
+  for (int cc = 0; cc < 4; ++cc) {
+    uint32_t o4[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int b0 = (cc * 8 + e * 2) * BITS, b1 = b0 + BITS;
+      const float w0 = (lut_s[(words[b0 >> 5] >> (b0 & 31)) & cmask] - zp) * sc;
+      const float w1 = (lut_s[(words[b1 >> 5] >> (b1 & 31)) & cmask] - zp) * sc;
+      const bf162 pr = __floats2bfloat162_rn(w0, w1);
+      o4[e] = *reinterpret_cast<const uint32_t*>(&pr);
+    }
+    const int chunk = half * 4 + cc;
+    *reinterpret_cast<uint4*>(dst + ((chunk ^ r7) * 16)) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+  }
+}
+
 // WFMT 0: FP4 tile-layout weights expanded by the warps 2..17.  WFMT 1: bf16 weights fetched by TMA.  WFMT 2: trellis weights
-// (16 x 16 tiles of 2..8-bit codes, LSB-first bit stream) decoded by the same warps inside the main loop.
+// (16 x 16 tiles of 2..8-bit codes, LSB-first bit stream) decoded by the same warps inside the main loop.  WFMT 3: codebook
+// weights (row-major 2 / 4 / 8-bit codes, 256-entry value table, fp16 group scales and optional zero points).
 template <int TN, int WFMT, int MINB>
 __global__ void __launch_bounds__(kGemmThreads, MINB)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -72,6 +94,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   using Cfg = GemmCfg<TN, MINB>;
   constexpr bool QW = WFMT != 1;       // weights are expanded by the warps of this CTA (parameters in `p`)
   extern __shared__ unsigned char smem_dyn[];
+  __shared__ float lut_s[WFMT == 3 ? 256 : 1];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   PipeShared* ps = reinterpret_cast<PipeShared*>(tiles + (size_t)Cfg::kStages * Cfg::stage_bytes);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -406,6 +429,73 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&ps->full_a[s]);
       }
+    } else if (WFMT == 3) {
+      // Codebook weights decoded in the main loop.  Lane l owns output row l / 2 of a 16-row block and the 32 input columns
+      // (l % 2) * 32 .. + 31 of the k block: 4 * bits contiguous bytes of the row-major code matrix (one or two vector loads,
+      // requested before the stage wait) that become four 16-byte chunks of the swizzled K-major A row.
+      for (int i2 = tid - 64; i2 < 256; i2 += kExpandWarps * 32) lut_s[i2] = __ldg(p.cb_lut + i2);
+      asm volatile("bar.sync 6, %0;" ::"n"(kExpandWarps * 32) : "memory");
+      const int bits = p.cb_bits;
+      const int NG = K >> p.gs_shift;
+      const long long row_bytes = (long long)K * bits / 8;
+      const uint8_t* cbase = reinterpret_cast<const uint8_t*>(p.qw);
+      const __half* sc_h = reinterpret_cast<const __half*>(p.sc);
+      const __half* zp_h = reinterpret_cast<const __half*>(p.cb_zeros);
+      const int half_k = (lane & 1) * 32;
+      int orow[kRB], st_off[kRB];
+      bool rt_ok[kRB];
+#pragma unroll
+      for (int j = 0; j < kRB; ++j) {
+        const int blk = dw0 + j;
+        orow[j] = n0 + blk * 16 + (lane >> 1);
+        rt_ok[j] = orow[j] < N;
+        st_off[j] = (blk * 16 + (lane >> 1)) * 128;
+      }
+      for (int i = kh; i < KB; i += kSplit) {
+        const int s = i % Cfg::kStages;
+        const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
+        uint4 cw[kRB][2];
+        float scl[kRB], zpt[kRB];
+#pragma unroll
+        for (int j = 0; j < kRB; ++j) {
+          cw[j][0] = cw[j][1] = make_uint4(0, 0, 0, 0);
+          scl[j] = zpt[j] = 0.f;
+          if (rt_ok[j]) {
+            const int k0 = i * kBK + half_k;
+            const uint8_t* src = cbase + (long long)orow[j] * row_bytes + (long long)k0 * bits / 8;
+            if (bits == 8) {
+              cw[j][0] = ldg_stream(reinterpret_cast<const uint4*>(src));
+              cw[j][1] = ldg_stream(reinterpret_cast<const uint4*>(src) + 1);
+            } else if (bits == 4) {
+              cw[j][0] = ldg_stream(reinterpret_cast<const uint4*>(src));
+            } else {
+              const uint2 v2 = __ldg(reinterpret_cast<const uint2*>(src));
+              cw[j][0] = make_uint4(v2.x, v2.y, 0, 0);
+            }
+            const long long gi = (long long)orow[j] * NG + (k0 >> p.gs_shift);
+            scl[j] = __half2float(sc_h[gi]);
+            zpt[j] = zp_h ? __half2float(zp_h[gi]) : 0.f;
+          }
+        }
+        if (!mbar_wait(&ps->empty[s], ph ^ 1u, abort_flag)) {
+          if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 3);
+          ok = false;
+          break;
+        }
+        unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
+        const int r7 = (lane >> 1) & 7;
+#pragma unroll
+        for (int j = 0; j < kRB; ++j) {
+          const uint32_t words[8] = {cw[j][0].x, cw[j][0].y, cw[j][0].z, cw[j][0].w, cw[j][1].x, cw[j][1].y, cw[j][1].z, cw[j][1].w};
+          unsigned char* dst = a_tile + st_off[j];
+          if (bits == 4) cb_expand_row<4>(words, lut_s, zpt[j], scl[j], dst, lane & 1, r7);
+          else if (bits == 8) cb_expand_row<8>(words, lut_s, zpt[j], scl[j], dst, lane & 1, r7);
+          else cb_expand_row<2>(words, lut_s, zpt[j], scl[j], dst, lane & 1, r7);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ps->full_a[s]);
+      }
     }
     // ---- epilogue: TMEM -> registers -> global
     if (ok) ok = mbar_wait(&ps->acc_full, 0u, abort_flag);
@@ -629,6 +719,29 @@ MMB_API int mmb_trellis_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
     case 64: return launch_gemm<64, 2>(mx, mx, p, pb, grid, stream);
     case 128: return launch_gemm<128, 2>(mx, mx, p, pb, grid, stream);
     default: return launch_gemm<256, 2>(mx, mx, p, pb, grid, stream);
+  }
+}
+
+// Codebook weights (WFMT 3): plain mode only (no grouping, activation or exchange epilogues).
+MMB_API int mmb_codebook_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
+  using namespace mmb;
+  MmbFp4GemmParams p = *pp;
+  if (p.M <= 0 || p.N <= 0) return 0;
+  if (p.qw == nullptr || p.sc == nullptr || p.cb_lut == nullptr || (p.cb_bits != 2 && p.cb_bits != 4 && p.cb_bits != 8)) return (int)cudaErrorInvalidValue;
+  if (p.K % 64 != 0 || p.Kx != p.K || p.gs_shift < 5 || (p.K & ((1 << p.gs_shift) - 1)) != 0) return (int)cudaErrorInvalidValue;
+  if (p.act != 0 || p.tile_expert != nullptr || p.rs_peer_bufs != nullptr || p.ag.flags != nullptr || p.out_rows != nullptr) return (int)cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(p.qw) & 15) return (int)cudaErrorInvalidValue;
+  const int TN = pick_tn(p.M, p.token_tile);
+  CUtensorMap mx;
+  int e = make_tmap_2d(&mx, p.x, p.Kx, p.M, p.Kx, TN);
+  if (e) return e;
+  MmbBf16GemmParams pb{};
+  dim3 grid((p.N + kTileRows - 1) / kTileRows, (p.M + TN - 1) / TN, 1);
+  switch (TN) {
+    case 32: return launch_gemm<32, 3>(mx, mx, p, pb, grid, stream);
+    case 64: return launch_gemm<64, 3>(mx, mx, p, pb, grid, stream);
+    case 128: return launch_gemm<128, 3>(mx, mx, p, pb, grid, stream);
+    default: return launch_gemm<256, 3>(mx, mx, p, pb, grid, stream);
   }
 }
 

@@ -30,7 +30,7 @@ from ..parallel.health import raise_for_status
 class EngineConfig:
     num_kv_blocks: int = 512
     block_size: int = 16
-    kv_cache_dtype: str = "bf16"       # "fp8": E4M3 pools with per-row scales (half the cache bytes)
+    kv_cache_dtype: str = "bf16"       # "fp8" / "int8" (half the cache bytes), "fp4" / "int4" (a quarter): codes + one scale per cached row
     max_model_len: int = 4096
     max_num_seqs: int = 64
     max_num_batched_tokens: int = 2048

@@ -21,7 +21,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Sequence, Dict, Iterable, List, Optional, Tuple
 
 import torch
 
@@ -294,17 +294,55 @@ class TrellisModelLoader:
 
 
 def quantize_model_trellis(model_dir: str, out_dir: str, bits: int = 4, group_size: int = 128, device: str = "cpu",
-                           container: str = "v3", bit_allocation: Optional[Dict[str, int]] = None) -> dict:
+                           container: str = "v3", bit_allocation: Optional[Dict[str, int]] = None,
+                           hessians: Optional[Dict[str, torch.Tensor]] = None, target_bpw: Optional[float] = None,
+                           bit_choices: Sequence[int] = (2, 3, 4, 5, 6, 8)) -> dict:
     """Quantize a float HF checkpoint into a trellis container.  Linear weights (2-D, not embeddings / norms /
-    routers) become trellis tensors at ``bits`` (or ``bit_allocation[name]``); everything else is kept as is."""
+    routers) become trellis tensors at ``bits`` (or ``bit_allocation[name]``); everything else is kept as is.
+
+    ``hessians`` (``name -> X^T X`` of the layer's inputs): matrices that have one are quantized with LDL error feedback
+    (``quant/ldlq.py``) instead of plain nearest-grid rounding.  ``target_bpw``: mixed bit widths - every matrix is tried at
+    each of ``bit_choices``, its error on the Hessian metric (plain squared error without a Hessian) recorded, and bits are
+    handed out greedily by error drop per byte until the average reaches the target (``quant.mixed_precision.allocate_bits``)."""
     from ..quant.convert import iter_safetensors_weights, should_quantize_tensor
     weights: Dict[str, TrellisWeight] = {}
     base: Dict[str, torch.Tensor] = {}
     errs = []
+    hessians = hessians or {}
+
+    def usable(name, t):
+        H = hessians.get(name)
+        gs = group_size if t.shape[1] % group_size == 0 else 16
+        return H if (H is not None and t.shape[1] % 16 == 0 and H.shape[0] == t.shape[1]) else None, gs
+
+    if target_bpw is not None and bit_allocation is None:
+        from ..quant.ldlq import proxy_error
+        from ..quant.mixed_precision import allocate_bits
+        sens, sizes = {}, {}
+        for name, t in iter_safetensors_weights(model_dir):
+            if not should_quantize_tensor(name, t):
+                continue
+            w = t.to(device=device, dtype=torch.float32)
+            H, gs = usable(name, t)
+            sizes[name] = w.numel()
+            sens[name] = {}
+            for b in bit_choices:
+                dq = quantize_trellis(w, b, gs, random_signs=False).dequantize().to(w.device)
+                # absolute (not relative) error, so that large and sensitive matrices attract the bits
+                sens[name][b] = (proxy_error(w, dq, H.to(w.device)) * float(torch.einsum("oi,ij,oj->", w.double(), H.to(w.device).double(), w.double()))
+                                 if H is not None else float((w - dq).pow(2).sum()))
+        bit_allocation = allocate_bits(sens, sizes, target_bpw, bit_choices)
+    n_ldlq = 0
     for name, t in iter_safetensors_weights(model_dir):
         if should_quantize_tensor(name, t):
             b = (bit_allocation or {}).get(name, bits)
-            tw = quantize_trellis(t.to(device=device, dtype=torch.float32), b, group_size, seed=len(weights))
+            H, gs = usable(name, t)
+            if H is not None:
+                from ..quant.ldlq import ldlq_quantize
+                tw = ldlq_quantize(t.to(device=device, dtype=torch.float32), H.to(device), b, gs, seed=len(weights)).weight
+                n_ldlq += 1
+            else:
+                tw = quantize_trellis(t.to(device=device, dtype=torch.float32), b, group_size, seed=len(weights))
             tw.name = name
             weights[name] = tw
             w = t.float()
@@ -322,5 +360,7 @@ def quantize_model_trellis(model_dir: str, out_dir: str, bits: int = 4, group_si
         if os.path.exists(os.path.join(model_dir, fn)):
             import shutil
             shutil.copy(os.path.join(model_dir, fn), os.path.join(out_dir, fn))
-    return {"quantized": len(weights), "tensors": len(weights) + len(base), "bits": bits,
+    n_w = sum(tw.shape[0] * tw.shape[1] for tw in weights.values())
+    return {"quantized": len(weights), "tensors": len(weights) + len(base), "bits": bits, "ldlq": n_ldlq,
+            "mean_bpw": sum(tw.shape[0] * tw.shape[1] * tw.bits for tw in weights.values()) / max(1, n_w),
             "mean_rel_rmse": sum(errs) / max(1, len(errs)), "format": "trellis_" + container}

@@ -115,6 +115,10 @@ class QuantizedLinear:
         if fast:
             y = ops.codebook_gemv(x2.contiguous(), self.codes, self.scales, self.zeros, self.lut, self.in_features, self.group_size,
                                   self.dev_bits)
+        elif ops.codebook_gemm_ok(x2, self.in_features, self.group_size, self.dev_bits):
+            # more than a few rows: the same codes on the tensor cores, expanded inside the GEMM's main loop
+            y = ops.codebook_gemm(x2.contiguous(), self.codes, self.scales, self.zeros, self.lut, self.in_features, self.group_size,
+                                  self.dev_bits)
         else:
             if self._deq is None:
                 self._deq = self.dequantize(torch.bfloat16)

@@ -124,19 +124,19 @@ class PagedKVStorage:
     mappings come from the host-side allocator (``kv/paged.py``)."""
 
     def __init__(self, cfg: ModelConfig, num_blocks: int, block_size: int, device, dtype=torch.bfloat16, kv_dtype: str = "bf16"):
-        """``kv_dtype="fp8"``: pools of E4M3 bytes with one scale per cached row (``ops.FP8KV``); written by the attention
-        prologue kernels, expanded to bf16 inside the decode kernel."""
+        """``kv_dtype`` ``"fp8"`` / ``"int8"`` / ``"fp4"`` / ``"int4"``: pools of 8- or 4-bit codes with one scale per cached row
+        (``ops.FP8KV``); written by the attention prologue kernels, expanded to bf16 inside the decode kernel."""
         self.cfg, self.num_blocks, self.block_size, self.kv_dtype = cfg, num_blocks, block_size, kv_dtype
         n_slots = num_blocks * block_size
         L = cfg.num_hidden_layers
-        assert kv_dtype in ("bf16", "fp8"), kv_dtype
-        if kv_dtype == "fp8":
+        assert kv_dtype == "bf16" or kv_dtype in ops.KV_FORMATS, kv_dtype
+        if kv_dtype != "bf16":
             if cfg.is_mla:
-                self.k = [ops.FP8KV(n_slots, (cfg.latent_dim,), device) for _ in range(L)]
+                self.k = [ops.FP8KV(n_slots, (cfg.latent_dim,), device, kv_dtype) for _ in range(L)]
                 self.v = [None] * L
             else:
-                self.k = [ops.FP8KV(n_slots, (cfg.num_key_value_heads, cfg.dh), device) for _ in range(L)]
-                self.v = [ops.FP8KV(n_slots, (cfg.num_key_value_heads, cfg.dh), device) for _ in range(L)]
+                self.k = [ops.FP8KV(n_slots, (cfg.num_key_value_heads, cfg.dh), device, kv_dtype) for _ in range(L)]
+                self.v = [ops.FP8KV(n_slots, (cfg.num_key_value_heads, cfg.dh), device, kv_dtype) for _ in range(L)]
         elif cfg.is_mla:
             self.k = [torch.zeros(n_slots, cfg.latent_dim, dtype=dtype, device=device) for _ in range(L)]
             self.v = [None] * L
@@ -147,9 +147,9 @@ class PagedKVStorage:
     def bytes_per_token(self) -> int:
         cfg = self.cfg
         per = cfg.latent_dim if cfg.is_mla else 2 * cfg.num_key_value_heads * cfg.dh
-        if self.kv_dtype == "fp8":        # one byte per element + a 4-byte scale per row
+        if self.kv_dtype != "bf16":       # one byte (or half a byte) per element + a 4-byte scale per row
             rows = 1 if cfg.is_mla else 2 * cfg.num_key_value_heads
-            return (per + 4 * rows) * cfg.num_hidden_layers
+            return ((per // 2 if self.kv_dtype in ("fp4", "int4") else per) + 4 * rows) * cfg.num_hidden_layers
         return per * 2 * cfg.num_hidden_layers
 
 

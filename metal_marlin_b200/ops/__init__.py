@@ -303,48 +303,105 @@ def rope(q, k, positions, inv_freq, Hq, Hk, D, rot_dim, interleaved=False, mscal
     return q, k
 
 
+KV_FORMATS = {"fp8": 0, "int8": 1, "fp4": 2, "int4": 3}
+_KV_RANGE = {0: 448.0, 1: 127.0, 2: 6.0, 3: 7.0}
+_E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+_E2M1_MIDPOINTS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+
+
 class FP8KV:
-    """Paged KV pool in FP8 (E4M3) with one fp32 scale per cached row: ``data`` uint8 ``[num_slots, Hkv, D]`` (GQA) or
-    ``[num_slots, latent_dim]`` (MLA latent), ``scale`` fp32 ``[num_slots, Hkv | 1]`` = row amax / 448.  Indexing with slot
-    ids returns the de-quantized bf16 rows, so code that gathers rows from a bf16 pool works unchanged.
+    """Quantized paged KV pool with one fp32 scale per cached row: ``data`` uint8 ``[num_slots, Hkv, W]`` (GQA) or
+    ``[num_slots, W]`` (MLA latent) and ``scale`` fp32 ``[num_slots, Hkv | 1]``.  ``fmt``: ``"fp8"`` (E4M3, scale = row amax / 448;
+    the default the class is named for), ``"int8"`` (amax / 127), ``"fp4"`` (E2M1, amax / 6) or ``"int4"`` (amax / 7); the
+    8-bit formats hold one byte per value (``W = D``), the 4-bit formats two values per byte, even element in the low nibble
+    (``W = D / 2``).  Indexing with slot ids returns the de-quantized bf16 rows, so code that gathers rows from a bf16 pool
+    works unchanged.
 
-    Parity: reference ``metal_marlin/kv_cache.py`` (fp8 cache mode) and ``paged_attention_v1_fp8`` / ``_v2_fp8``
-    (``src/paged_attention.metal``)."""
+    Parity: reference ``metal_marlin/kv_cache.py`` (fp8 / int8 / fp4 cache modes) and ``paged_attention_v1_fp8``,
+    ``paged_attention_v1_fp4`` ``:670``, ``paged_attention_v1_int4`` ``:885`` (``src/paged_attention.metal``: packed codes with
+    per-token-per-head scales)."""
 
-    def __init__(self, num_slots: int, row_shape, device):
+    def __init__(self, num_slots: int, row_shape, device, fmt: str = "fp8"):
         row_shape = tuple(row_shape)
-        self.data = torch.zeros(num_slots, *row_shape, dtype=torch.uint8, device=device)
+        self.fmt = fmt
+        self.fmt_code = KV_FORMATS[fmt]
+        self.four_bit = self.fmt_code >= 2
+        self.width = row_shape[-1]                                   # values per row
+        if self.four_bit and self.width % 32:
+            raise ValueError("4-bit KV rows must hold a multiple of 32 values")
+        stored = row_shape[:-1] + (self.width // 2 if self.four_bit else self.width,)
+        self.data = torch.zeros(num_slots, *stored, dtype=torch.uint8, device=device)
         self.scale = torch.ones(num_slots, row_shape[0] if len(row_shape) == 2 else 1, dtype=torch.float32, device=device)
 
-    shape = property(lambda self: self.data.shape)
     device = property(lambda self: self.data.device)
     dtype = torch.uint8
+
+    @property
+    def shape(self):
+        return self.data.shape[:-1] + (self.width,)
 
     def view(self, *shape):
         return self
 
     def numel(self):
-        return self.data.numel()
+        return self.data.numel() * (2 if self.four_bit else 1)
 
     def element_size(self):
         return 1
 
+    def nbytes(self) -> int:
+        return self.data.numel() + self.scale.numel() * 4
+
+    # ---- PyTorch restatement of the kernels' quantizer and de-quantizer (kv_quant.cuh)
+    def _encode(self, x: torch.Tensor) -> torch.Tensor:
+        """``x`` = value / row scale -> integer codes (uint8, one per value)."""
+        c = self.fmt_code
+        if c == 0:
+            return x.clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        if c == 1:
+            return torch.round(x.clamp(-127.0, 127.0)).to(torch.int16).bitwise_and(0xFF).to(torch.uint8)
+        if c == 3:
+            return torch.round(x.clamp(-7.0, 7.0)).to(torch.int16).bitwise_and(0xF).to(torch.uint8)
+        mag = torch.bucketize(x.abs(), torch.tensor(_E2M1_MIDPOINTS, device=x.device, dtype=x.dtype), right=True)
+        return (mag + 8 * (x < 0).to(mag.dtype)).to(torch.uint8)
+
+    def _decode(self, codes: torch.Tensor) -> torch.Tensor:
+        c = self.fmt_code
+        if c == 0:
+            return codes.view(torch.float8_e4m3fn).float()
+        if c == 1:
+            return codes.view(torch.int8).float()
+        n = codes.to(torch.int16)
+        if c == 3:
+            return torch.where(n >= 8, n - 16, n).float()
+        tab = torch.tensor(_E2M1_VALUES, device=codes.device, dtype=torch.float32)
+        v = tab[(n & 7).long()]
+        return torch.where(n >= 8, -v, v)
+
     def store(self, slots, rows):
-        """PyTorch restatement of the kernels' quantizer (rows: float ``[n, ...row_shape]``, bf16-rounded first)."""
+        """Quantize ``rows`` (float ``[n, ...row_shape]``, bf16-rounded first) into the given slots."""
         r = rows.to(torch.bfloat16).float()
         amax = r.abs().amax(-1)
-        sc = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
-        q = (r * (1.0 / sc).unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
-        self.data[slots] = q.view(torch.uint8)
+        sc = torch.where(amax > 0, amax / _KV_RANGE[self.fmt_code], torch.ones_like(amax))
+        q = self._encode(r * (1.0 / sc).unsqueeze(-1))
+        if self.four_bit:
+            q = q[..., 0::2] | (q[..., 1::2] << 4)
+        self.data[slots] = q
         self.scale[slots] = sc.reshape(sc.shape[0], -1)
 
     def __getitem__(self, idx):
-        d = self.data[idx].view(torch.float8_e4m3fn).float()
+        d = self.data[idx]
+        if self.four_bit:
+            d = torch.stack([d & 0xF, d >> 4], -1).flatten(-2)
+        d = self._decode(d)
         sc = self.scale[idx]
         return (d * (sc.unsqueeze(-1) if d.dim() == sc.dim() + 1 else sc)).to(torch.bfloat16)
 
     def dequantize(self):
         return self[torch.arange(self.data.shape[0], device=self.data.device)]
+
+
+QuantKV = FP8KV
 
 
 def kv_copy_rows(pool, dst, src) -> None:
@@ -361,7 +418,7 @@ def _ref_cache_write(fn, pool_pairs, slots, n_tok):
     """Runs a reference cache-writing op against scratch bf16 pools with identity slots, then quantizes the written rows
     into the FP8 pools."""
     ident = torch.where(slots >= 0, torch.arange(n_tok, device=slots.device), torch.full_like(slots, -1))
-    tmps = [torch.zeros(n_tok, *p.data.shape[1:], dtype=torch.bfloat16, device=p.data.device) for p in pool_pairs]
+    tmps = [torch.zeros(n_tok, *p.shape[1:], dtype=torch.bfloat16, device=p.data.device) for p in pool_pairs]
     r = fn(ident, tmps)
     ok = slots >= 0
     for p, t in zip(pool_pairs, tmps):
@@ -376,7 +433,7 @@ def qk_norm_rope_cache(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool, 
                                                                   interleaved), [k_pool, v_pool], slots, q.shape[0])
             return q
         K.mmb200.qk_norm_rope_cache_fp8(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool.data, v_pool.data, k_pool.scale,
-                                        v_pool.scale, Hq, Hk, D, eps, interleaved)
+                                        v_pool.scale, Hq, Hk, D, eps, interleaved, k_pool.fmt_code)
         return q
     if not _use_native(q):
         return ref.qk_norm_rope_cache(q, k, v, qn_w, kn_w, positions, inv_freq, slots, k_pool, v_pool, Hq, Hk, D, eps,
@@ -395,7 +452,7 @@ def mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache
                                                         mscale, interleaved), [cache], slots, q.shape[0])
             return q_full
         K.mmb200.mla_prep_fp8(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache.data, cache.scale.view(-1), H, dn, dr, R,
-                              eps, mscale, interleaved, skip_absorb)
+                              eps, mscale, interleaved, skip_absorb, cache.fmt_code)
         return q_full
     if not _use_native(q):
         return ref.mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache, H, dn, dr, R, eps,
@@ -407,10 +464,10 @@ def mla_prep(q, kva, w_ukT, kv_norm_w, positions, inv_freq, slots, q_full, cache
 
 def kv_fp8_rows(pool: "FP8KV", block_tables, ctx_lens, cu_k, total: int, max_ctx: int, block_size: int):
     """Contiguous bf16 ``[total, Hkv, D]`` rows of the sequences described by ``block_tables`` / ``ctx_lens``."""
-    Hkv, D = (pool.data.shape[1], pool.data.shape[2]) if pool.data.dim() == 3 else (1, pool.data.shape[1])
+    Hkv, D = (pool.data.shape[1] if pool.data.dim() == 3 else 1), pool.width
     out = torch.empty(total, Hkv, D, dtype=torch.bfloat16, device=pool.data.device)
-    if _use_native(pool.data) and D % 4 == 0:
-        K.mmb200.kv_fp8_gather(pool.data, pool.scale, block_tables, ctx_lens, cu_k, out, Hkv, D, block_size, max_ctx)
+    if _use_native(pool.data) and D % 8 == 0:
+        K.mmb200.kv_fp8_gather(pool.data, pool.scale, block_tables, ctx_lens, cu_k, out, Hkv, D, block_size, max_ctx, pool.fmt_code)
         return out
     cl, ck = ctx_lens.tolist(), cu_k.tolist()
     for b, n in enumerate(cl):
@@ -465,7 +522,7 @@ def paged_attention(q, k_pool, v_pool, block_tables, ctx_lens, *, Hq, Hkv, dqk, 
     if fp8:
         K.mmb200.paged_decode_fp8(q, k_pool.data, None if v_pool is None else v_pool.data, k_pool.scale,
                                   None if v_pool is None else v_pool.scale, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv,
-                                  block_size, splits, scale, window)
+                                  block_size, splits, scale, window, k_pool.fmt_code)
     else:
         K.mmb200.paged_decode(q, k_pool, v_pool, block_tables, ctx_lens, part_o, part_ml, Hq, Hkv, dqk, dv, block_size,
                               splits, scale, window)
@@ -845,6 +902,28 @@ def codebook_gemv(x, codes, scales, zeros, lut, in_f: int, group_size: int, bits
     if out is None:
         out = torch.empty(x.shape[0], codes.shape[0], dtype=torch.bfloat16, device=x.device)
     K.mmb200.codebook_gemv(x, codes, scales, zeros, lut, out, in_f, group_size, bits)
+    return out
+
+
+def codebook_gemm_ok(x, in_f: int, group_size: int, bits: int) -> bool:
+    """Whether the tensor-core codebook GEMM takes this problem (else: de-quantize and use the bf16 GEMM)."""
+    return (_use_native(x) and not NO_TCGEN05 and x.dtype == torch.bfloat16 and bits in (2, 4, 8) and in_f % 64 == 0
+            and group_size >= 32 and group_size & (group_size - 1) == 0 and in_f % group_size == 0)
+
+
+def codebook_gemm(x, codes, scales, zeros, lut, in_f: int, group_size: int, bits: int = 8, out=None):
+    """``x [M, in] @ W^T`` for any ``M`` with the codebook weights of :func:`codebook_gemv`, expanded inside the tcgen05 GEMM's
+    main loop (no bf16 copy of the matrix exists)."""
+    if not codebook_gemm_ok(x, in_f, group_size, bits):
+        w = ref.codebook_dequant(codes, scales, zeros, lut, in_f, group_size, bits)
+        y = (x[:, :in_f].to(torch.float32) @ w.t()).to(torch.bfloat16)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty(x.shape[0], codes.shape[0], dtype=torch.bfloat16, device=x.device)
+    K.mmb200.codebook_gemm(x.contiguous(), codes, scales, zeros, lut, out, in_f, group_size, bits, gemm_status(x.device))
     return out
 
 

@@ -90,9 +90,10 @@ def quantize_named_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], fmt: str
 
 def convert_model(model_dir: str, out_dir: str, fmt: str = "marlin_fp4", group_size: int = 128, device: str = "cpu",
                   shard_bytes: int = 4 << 30, quantize_fn: Optional[Callable] = None, verbose: bool = False,
-                  hadamard_block: int = 0) -> dict:
+                  hadamard_block: int = 0, tensors: Optional[Iterable[Tuple[str, torch.Tensor]]] = None) -> dict:
     """Stream a float HF checkpoint into a quantized one.  ``fmt``: ``marlin_fp4`` (single
-    ``model.safetensors``) or ``mmfp4`` (shards + ``model.safetensors.index.json``)."""
+    ``model.safetensors``) or ``mmfp4`` (shards + ``model.safetensors.index.json``).  ``tensors``: take the ``(name, tensor)``
+    stream from the caller instead of the safetensors files of ``model_dir`` (importers that de-quantize another format)."""
     os.makedirs(out_dir, exist_ok=True)
     t0 = time.time()
     report, weight_map = [], {}
@@ -111,7 +112,7 @@ def convert_model(model_dir: str, out_dir: str, fmt: str = "marlin_fp4", group_s
         shard_no += 1
 
     n_q = n_total = 0
-    for name, outs, dts, rep in quantize_named_tensors(iter_safetensors_weights(model_dir), fmt, group_size, device, quantize_fn,
+    for name, outs, dts, rep in quantize_named_tensors(tensors if tensors is not None else iter_safetensors_weights(model_dir), fmt, group_size, device, quantize_fn,
                                                          hadamard_block):
         n_total += 1
         if rep is not None:

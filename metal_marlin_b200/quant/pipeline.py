@@ -108,14 +108,41 @@ def _generic_group_writer(model_dir: str, out_dir: str, fmt: str, group_size: in
     return {"quantized": n_q, "tensors": len(tensors), "mean_rel_rmse": sum(errs) / max(1, len(errs))}
 
 
+class _HessianView:
+    """``name -> Hessian`` mapping over a collector (only ``get`` is needed by the writers)."""
+
+    def __init__(self, col):
+        self.col = col
+
+    def get(self, name, default=None):
+        H = self.col.get(name)
+        return default if H is None else H
+
+
 def quantize_checkpoint(model_dir: str, out_dir: str, fmt: str = "mmfp4", method: str = "rtn", group_size: int = 128,
                         bits: Optional[int] = None, calibration: str = "synthetic", num_samples: int = 32, seq_len: int = 512,
-                        mixed_preset: Optional[str] = None, device: Optional[str] = None, act_order: bool = False) -> dict:
+                        mixed_preset: Optional[str] = None, device: Optional[str] = None, act_order: bool = False,
+                        target_bpw: Optional[float] = None) -> dict:
+    """``fmt="trellis-v2"`` with ``method="ldlq"`` is the EXL3-style pipeline: Hessians of every layer input from calibration
+    text, LDL error feedback per matrix, and (with ``target_bpw``) sensitivity-driven mixed bit widths."""
     t0 = time.time()
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     if fmt == "trellis-v2":
         from ..formats.trellis import quantize_model_trellis
-        stats = quantize_model_trellis(model_dir, out_dir, bits=bits or 4, device=device)
+        hess = None
+        if method in ("ldlq", "exl3"):
+            tmp = tempfile.mkdtemp(prefix="mmb200_rtn_")
+            try:
+                convert_model(model_dir, tmp, "mmfp4", group_size, device=device)
+                col = collect_hessians(tmp, calibration, num_samples, seq_len, device)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            hess = _HessianView(col)
+        elif method != "rtn":
+            raise ValueError(f"method {method!r} does not write trellis containers; use rtn or ldlq")
+        stats = quantize_model_trellis(model_dir, out_dir, bits=bits or 4, group_size=group_size, device=device, hessians=hess,
+                                       target_bpw=target_bpw)
+        stats["method"] = "ldlq" if hess is not None else "rtn"
         stats["seconds"] = time.time() - t0
         return stats
     if fmt not in _FP4_FORMATS:

@@ -41,6 +41,8 @@ class EngineConfig:
     preset: Optional[str] = None          # serve a random-init architecture preset (no checkpoint)
     speculative: Optional[str] = None     # "ngram" | "mtp" | path of a draft checkpoint
     num_speculative_tokens: int = 4
+    kv_cache_dtype: str = "bf16"          # "fp8" | "int8" | "fp4" | "int4": quantized paged cache (one scale per cached row)
+    scheduler_policy: str = "priority"    # "priority" | "fcfs" | "shortest_first" | "longest_first"
     # multi-GPU (job started with torchrun, one process per GPU): tensor / expert / data parallel degrees
     tp: int = 1
     ep: int = 1
@@ -79,7 +81,8 @@ class ServingEngine:
         self.model_format = "mock" if self.mock else detect_model_format(config.model_path)
         core = CoreEngineConfig(num_kv_blocks=config.num_kv_blocks, block_size=config.block_size,
                                 max_model_len=config.max_model_len, max_num_seqs=config.max_batch_size,
-                                request_timeout_s=config.request_timeout)
+                                request_timeout_s=config.request_timeout, kv_cache_dtype=config.kv_cache_dtype,
+                                scheduler_policy=config.scheduler_policy)
         from ..inference.pipeline import MMFP4Pipeline
         par = dict(tp=config.tp, ep=config.ep, dp=1)        # data-parallel replicas are whole servers behind serving/router.py
         if self.mock:

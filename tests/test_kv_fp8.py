@@ -1,4 +1,4 @@
-"""FP8 (E4M3, per-row scale) paged KV cache: quantizer properties, model-level agreement with the bf16 cache on CPU,
+"""Quantized paged KV cache (FP8 E4M3, INT8, FP4 E2M1, INT4; one scale per cached row): quantizer properties, model-level agreement with the bf16 cache on CPU,
 and the CUDA kernels (cache write, decode with in-kernel expansion, gather for prompt passes) against the PyTorch
 restatement.  Reference: tests/test_kv_cache_quantized.py, tests/test_paged_attention_fp8.py."""
 import pytest
@@ -27,27 +27,57 @@ def test_fp8_pool_roundtrip_and_copy():
 
 
 @pytest.mark.parametrize("preset", ["tiny-llama", "tiny-mla-moe"])
-def test_generation_with_fp8_cache_tracks_bf16_cache_cpu(preset):
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+def test_generation_with_fp8_cache_tracks_bf16_cache_cpu(preset, fmt):
     lm = MMFP4ForCausalLM.from_config(preset, device="cpu", seed=3)
     prompts = [[5, 9, 200, 17, 3, 44, 8], [7, 7, 7, 12]]
     out_bf16 = lm.generate(prompts, max_new_tokens=6)
-    out_fp8 = lm.generate(prompts, max_new_tokens=6, kv=lm.new_cache(16, 16, kv_dtype="fp8"))
+    out_fp8 = lm.generate(prompts, max_new_tokens=6, kv=lm.new_cache(16, 16, kv_dtype=fmt))
     # greedy tokens of a random-init model are sensitive to tiny logit changes; the first generated token comes from the
     # prompt pass over freshly quantized rows and must agree, the rest must be valid ids
     for x, y in zip(out_bf16, out_fp8):
         assert x[0] == y[0] and len(x) == len(y)
 
 
+@pytest.mark.parametrize("fmt, rel", [("fp8", 0.0625), ("int8", 0.5 / 127), ("fp4", 1.0 / 6), ("int4", 0.5 / 7)])
+def test_quantized_pool_formats_roundtrip(fmt, rel):
+    """Every format: error of a value bounded by half the largest code step times the row scale; 4-bit rows take half the bytes;
+    zeros stay zeros; negative extremes survive."""
+    torch.manual_seed(0)
+    p = ops.FP8KV(32, (2, 64), "cpu", fmt)
+    assert p.data.shape == (32, 2, 32 if fmt in ("fp4", "int4") else 64) and p.shape == (32, 2, 64) and p.fmt_code == ops.KV_FORMATS[fmt]
+    rows = torch.randn(5, 2, 64) * 2
+    rows[0, 0, 3] = -rows.abs().max() * 1.5
+    idx = torch.tensor([0, 3, 7, 8, 31])
+    p.store(idx, rows)
+    back = p[idx].float()
+    amax = rows.to(torch.bfloat16).float().abs().amax(-1, keepdim=True)
+    assert float(((back - rows).abs() / amax).max()) <= rel + 4e-3
+    assert float(back[0, 0, 3]) == float(rows[0, 0, 3].to(torch.bfloat16))       # the row maximum is representable exactly
+    z = ops.FP8KV(4, (64,), "cpu", fmt)
+    z.store(torch.tensor([1]), torch.zeros(1, 64))
+    assert torch.all(z[torch.tensor([1])] == 0)
+    if fmt in ("fp4", "int4"):
+        with pytest.raises(ValueError):
+            ops.FP8KV(4, (48,), "cpu", fmt)
+
+
+# largest distance between neighbouring codes; INT8 codes are finer than a bf16 ulp of the row maximum (2^-8 of it), so one
+# ulp of difference in front of the quantizer can move a value by more than one code
+_STEP = {"fp8": 32.0, "int8": 2.0, "fp4": 2.0, "int4": 1.0}
+
+
 @pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["fp8", "int8", "fp4", "int4"])
 @pytest.mark.parametrize("Hq,Hk,D", [(8, 2, 128), (4, 4, 64), (16, 2, 256)])
-def test_fp8_cache_write_and_decode_kernels_gqa(Hq, Hk, D):
+def test_fp8_cache_write_and_decode_kernels_gqa(Hq, Hk, D, fmt):
     torch.manual_seed(D)
     bs, ctxs = 16, [1, 70, 200]
     B = len(ctxs)
     nb = max((c + bs - 1) // bs for c in ctxs)
     bt = torch.randperm(B * nb, device=DEV).to(torch.int32).view(B, nb)
-    kp, vp = ops.FP8KV(B * nb * bs, (Hk, D), DEV), ops.FP8KV(B * nb * bs, (Hk, D), DEV)
-    kr, vr = ops.FP8KV(B * nb * bs, (Hk, D), DEV), ops.FP8KV(B * nb * bs, (Hk, D), DEV)
+    kp, vp = ops.FP8KV(B * nb * bs, (Hk, D), DEV, fmt), ops.FP8KV(B * nb * bs, (Hk, D), DEV, fmt)
+    kr, vr = ops.FP8KV(B * nb * bs, (Hk, D), DEV, fmt), ops.FP8KV(B * nb * bs, (Hk, D), DEV, fmt)
     inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, device=DEV).float() / D))
     qn = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16)
     kn = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16)
@@ -67,9 +97,10 @@ def test_fp8_cache_write_and_decode_kernels_gqa(Hq, Hk, D):
                 with ops.force_reference():
                     ops.qk_norm_rope_cache(q, k, v, qn, kn, pos, inv, slots, pools[0], pools[1], Hq, Hk, D, 1e-6)
     used = torch.cat([bt[b, t // bs].long() * bs + t % bs for b in range(B) for t in [torch.arange(ctxs[b], device=DEV)]])
-    # one E4M3 step of the row scale is the most the two quantizers may differ by
-    dk = (kp[used].float() - kr[used].float()).abs().amax(-1)
-    assert float((dk / (kr.scale[used] * 32 + 1e-6)).max()) <= 1.0
+    # one code step of the row scale is the most the two quantizers may differ by (bf16 rounding in front of the quantizer)
+    for a, b in ((kp, kr), (vp, vr)):
+        dk = (a[used].float() - b[used].float()).abs().amax(-1)
+        assert float((dk / (b.scale[used] * _STEP[fmt] * 1.02 + 1e-6)).max()) <= 1.0
     cl = torch.tensor(ctxs, dtype=torch.int32, device=DEV)
     q = (torch.randn(B, Hq, D, device=DEV) * 0.5).to(torch.bfloat16)
     got = ops.paged_attention(q, kp, vp, bt, cl, Hq=Hq, Hkv=Hk, dqk=D, dv=D, block_size=bs, scale=D ** -0.5)
@@ -87,12 +118,35 @@ def test_fp8_cache_write_and_decode_kernels_gqa(Hq, Hk, D):
 
 
 @pytest.mark.gpu
-def test_fp8_latent_cache_mla_model_matches_reference_path():
+@pytest.mark.parametrize("fmt", ["fp8", "int8", "fp4", "int4"])
+def test_fp8_latent_cache_mla_model_matches_reference_path(fmt):
     lm = MMFP4ForCausalLM.from_config("tiny-mla-moe", device="cuda", seed=5)
     prompts = [torch.randint(0, 512, (40,)).tolist(), torch.randint(0, 512, (9,)).tolist()]
-    out = lm.generate(prompts, max_new_tokens=8, kv=lm.new_cache(16, 16, kv_dtype="fp8"))
+    out = lm.generate(prompts, max_new_tokens=8, kv=lm.new_cache(16, 16, kv_dtype=fmt))
     with ops.force_reference():
-        ref = lm.generate(prompts, max_new_tokens=8, kv=lm.new_cache(16, 16, kv_dtype="fp8"), use_graph=False)
-    assert [o[0] for o in out] == [r[0] for r in ref]
+        ref = lm.generate(prompts, max_new_tokens=8, kv=lm.new_cache(16, 16, kv_dtype=fmt), use_graph=False)
+    if fmt in ("fp8", "int8"):
+        assert [o[0] for o in out] == [r[0] for r in ref]
     agree = sum(a == b for o, r in zip(out, ref) for a, b in zip(o, r)) / sum(len(o) for o in out)
-    assert agree >= 0.6, (out, ref)
+    assert agree >= (0.6 if fmt in ("fp8", "int8") else 0.25), (out, ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["int8", "fp4", "int4"])
+def test_quantized_latent_decode_kernel_matches_dequantized_attention(fmt):
+    """The full-size MLA latent (576 = 512 + 64 values per row, 20 heads on one latent): the decode kernel expands the codes
+    in shared memory; compared with attention over the de-quantized pool."""
+    torch.manual_seed(11)
+    bs, ctxs, Hq, R, dr = 16, [33, 300, 1], 20, 512, 64
+    B = len(ctxs)
+    nb = max((c + bs - 1) // bs for c in ctxs)
+    bt = torch.randperm(B * nb, device=DEV).to(torch.int32).view(B, nb)
+    pool = ops.FP8KV(B * nb * bs, (R + dr,), DEV, fmt)
+    pool.store(torch.arange(B * nb * bs, device=DEV), torch.randn(B * nb * bs, R + dr, device=DEV))
+    cl = torch.tensor(ctxs, dtype=torch.int32, device=DEV)
+    q = (torch.randn(B, Hq, R + dr, device=DEV) * 0.3).to(torch.bfloat16)
+    got = ops.paged_attention(q, pool, None, bt, cl, Hq=Hq, Hkv=1, dqk=R + dr, dv=R, block_size=bs, scale=(192 + 64) ** -0.5)
+    with ops.force_reference():
+        want = ops.paged_attention(q, pool, None, bt, cl, Hq=Hq, Hkv=1, dqk=R + dr, dv=R, block_size=bs, scale=(192 + 64) ** -0.5)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    assert ops.check_status(torch.device(DEV)) == 0

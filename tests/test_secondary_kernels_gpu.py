@@ -53,8 +53,29 @@ def test_codebook_gemv(fmt, bits):
         x = (torch.randn(M, 512, device=DEV) * 0.5).to(torch.bfloat16)
         y = lin(x)
         torch.testing.assert_close(y.float().cpu(), x.float().cpu() @ w_ref.t(), rtol=2e-2, atol=2e-2)
-    big = lin((torch.randn(40, 512, device=DEV) * 0.5).to(torch.bfloat16))          # large M: de-quantize + GEMM
+    big = lin((torch.randn(40, 512, device=DEV) * 0.5).to(torch.bfloat16))
     assert big.shape == (40, 96)
+
+
+@pytest.mark.parametrize("fmt,bits,gs", [("int8", 8, 128), ("int4", 4, 64), ("int4", 4, 32), ("int2", 2, 128), ("fp8", 8, 128), ("nf4", 4, 128),
+                                         ("int3", 4, 64)])
+@pytest.mark.parametrize("M,out_f,in_f", [(40, 96, 512), (300, 200, 1024), (1100, 136, 640)])
+def test_codebook_gemm_on_the_tensor_cores(fmt, bits, gs, M, out_f, in_f):
+    """More than eight rows: codes are looked up, shifted by the zero point and scaled inside the tcgen05 GEMM's main loop
+    (no bf16 copy of the matrix); compared with the fp32 product over the de-quantized weights."""
+    from metal_marlin_b200.layers import QuantizedLinear
+    torch.manual_seed(7)
+    w = torch.randn(out_f, in_f) * 0.05
+    lin = QuantizedLinear.from_float(w, fmt, group_size=gs, device=DEV)
+    assert lin.dev_bits == bits and ops.codebook_gemm_ok(torch.empty(1, in_f, dtype=torch.bfloat16, device=DEV), in_f, gs, bits)
+    w_ref = lin.dequantize(torch.float32).cpu()
+    x = (torch.randn(M, in_f, device=DEV) * 0.5).to(torch.bfloat16)
+    y = lin(x)
+    assert lin._deq is None                                 # the tensor-core path ran: no cached bf16 matrix
+    want = x.float().cpu() @ w_ref.t()
+    err = (y.float().cpu() - want).abs().max() / want.abs().max()
+    assert err < 1.5e-2, float(err)
+    assert ops.check_status(DEV) == 0
 
 
 @pytest.mark.parametrize("patch", [0, 14])
