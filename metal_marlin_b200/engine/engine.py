@@ -152,7 +152,11 @@ class _DecodeBucket:
         if code:
             self.status.zero_()             # one expiry must not fail every later step
             self.h_status.zero_()
-            raise_for_status(code)
+            ep = getattr(self.model, "ep", None)
+            if code == 120 and ep is not None and getattr(ep, "capacity_policy", "error") == "drop":
+                ep.overflow_steps += 1      # token dropping was asked for: the step stands without the rows that did not fit
+            else:
+                raise_for_status(code)
         return self.h_out
 
     def run(self) -> torch.Tensor:
@@ -571,6 +575,10 @@ class LLMEngine:
         code = int(st[0].item())
         if code:
             st.zero_()
+            ep = getattr(self.model, "ep", None)
+            if code == 120 and ep is not None and getattr(ep, "capacity_policy", "error") == "drop":
+                ep.overflow_steps += 1       # token dropping was asked for: the step stands without the rows that did not fit
+                return
             raise_for_status(code)
 
     # ------------------------------------------------------------------ introspection

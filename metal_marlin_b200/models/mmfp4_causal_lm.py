@@ -78,7 +78,13 @@ class MMFP4ForCausalLM:
     def from_pretrained(cls, path: str, device: Optional[str] = None) -> "MMFP4ForCausalLM":
         device = device or ("cuda" if torch.cuda.is_available() else "cpu")
         cfg = ModelConfig.from_pretrained(path)
-        return cls(build_transformer(cfg, CheckpointSource(cfg, path, device)))
+        src = CheckpointSource(cfg, path, device)
+        lm = cls(build_transformer(cfg, src))
+        # multi-token-prediction modules stored after the decoder stack become the model's draft head
+        # (reference: metal_marlin/model_utils.py:416 _load_mtp_head_from_checkpoint)
+        from ..spec.draft import MTPHead
+        lm.model.mtp = MTPHead.from_checkpoint(lm.model, src.loader)
+        return lm
 
     @classmethod
     def from_config(cls, cfg, device: Optional[str] = None, seed: int = 0) -> "MMFP4ForCausalLM":

@@ -308,6 +308,11 @@ class EPModelState:
         # instead of by the exchange capacity.
         self.pass_tokens = 0
         self.uniform = False
+        # What a receive-buffer overflow (device status 120: a rank was sent more rows than its region holds; the rows beyond it
+        # are not computed) means to the engine: "error" fails the step's requests, "drop" accepts the loss of those expert
+        # contributions (token dropping, as a capacity factor below the worst case implies) and counts the steps it happened in.
+        self.capacity_policy = "error"
+        self.overflow_steps = 0
 
     def add_layer(self, li: int, gate_up, down, num_routed: int, n_shared: int) -> None:
         self.n_shared = n_shared

@@ -20,7 +20,7 @@ import torch
 from ..formats import fp4 as fp4fmt
 from ..formats.safetensors_io import SafetensorsFile, save_file
 
-SKIP_PATTERNS = ("embed", "norm", "lm_head", "output", "bias")
+SKIP_PATTERNS = ("embed", "norm", "lm_head", "shared_head.head", "output", "bias")      # vocabulary heads (also those of MTP modules) stay bf16
 COPY_FILES = ("config.json", "tokenizer.json", "tokenizer_config.json", "tokenizer.model", "special_tokens_map.json",
               "generation_config.json", "vocab.json", "merges.txt", "chat_template.jinja")
 

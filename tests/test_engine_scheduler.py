@@ -245,6 +245,23 @@ def test_engine_fails_requests_when_the_device_status_word_is_set():
     with pytest.raises(DeviceWaitExpired):
         eng.step()                                # decode pass
     assert int(st[0]) == 0
+    # expert-parallel receive-buffer overflow (120): fails the step unless the model asked for token dropping
+    from metal_marlin_b200.parallel.health import ExpertCapacityOverflow
+    st[0] = 120
+    with pytest.raises(ExpertCapacityOverflow):
+        eng.step()
+
+    class _EP:
+        capacity_policy, overflow_steps, mode, pass_tokens = "drop", 0, "nccl", 0
+    lm.model.ep = _EP()
+    try:
+        eng3 = LLMEngine(lm.model, EngineConfig(num_kv_blocks=32, max_model_len=64, use_cuda_graphs=False))
+        eng3.cache, eng3.kv = eng.cache, eng.kv
+        st[0] = 120
+        eng3._check_device_status()               # tolerated, counted, cleared
+        assert lm.model.ep.overflow_steps == 1 and int(st[0]) == 0
+    finally:
+        lm.model.ep = None
     # background loop: the in-flight request ends FAILED with the reason, the loop keeps serving
     eng2 = LLMEngine(lm.model, EngineConfig(num_kv_blocks=32, max_model_len=64, use_cuda_graphs=False))
     st[0] = 3

@@ -80,6 +80,23 @@ def _worker(rank, world, port, q):
         outs = pipeline_prefill(stage, [(torch.tensor(toks), kv, meta, None)])
         if stage.is_last:
             res["pp"] = float((outs[0] - ref_logits).abs().max() / ref_logits.abs().max())
+        # several micro-batches (different sequences) with overlapped hand-overs: receives posted ahead, sends in the background;
+        # the same answer as with blocking hand-overs, micro-batch by micro-batch
+        seqs = [list(range(3 + i, 12 + 2 * i)) for i in range(4)]
+        def mbs():
+            out = []
+            for s_ in seqs:
+                kv_i = lm.new_cache(2, 16)
+                p_i = torch.arange(len(s_), dtype=torch.int32)
+                out.append((torch.tensor(s_), kv_i, BatchMeta(positions=p_i, slots=p_i.long(), block_tables=torch.arange(2, dtype=torch.int32).view(1, 2),
+                                                              ctx_lens=torch.tensor([len(s_)], dtype=torch.int32), decode=False,
+                                                              cu_seqlens=[0, len(s_)], ctx_lens_host=[len(s_)]), None))
+            return out
+        a = pipeline_prefill(stage, mbs(), overlap=True, max_inflight_sends=1)
+        b = pipeline_prefill(stage, mbs(), overlap=False)
+        if stage.is_last:
+            res["pp_overlap"] = max(float((x - y).abs().max()) for x, y in zip(a, b))
+            res["pp_multi"] = max(float((x - lm.forward_logits(s_)).abs().max() / x.abs().max()) for x, s_ in zip(a, seqs))
         # ring attention vs dense causal attention
         torch.manual_seed(2)
         S = 8
@@ -113,6 +130,7 @@ def test_ep_pp_cp_on_two_cpu_ranks():
         assert res["ep_fused_cpu"] < 3e-2, res
         assert res["cp"] < 1e-4, res
     assert results[world - 1]["pp"] < 1e-2, results
+    assert results[world - 1]["pp_overlap"] == 0.0 and results[world - 1]["pp_multi"] < 1e-2, results
 
 
 def test_ep_exchange_layout_and_descriptors():

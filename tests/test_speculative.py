@@ -168,3 +168,67 @@ def test_server_engine_with_ngram_speculation_batches_concurrent_requests(monkey
     spec.shutdown()
     assert got == want
     assert st["spec_proposed"] > 0 and 0.0 <= st["spec_acceptance_rate"] <= 1.0
+
+
+def test_mtp_and_eagle_heads_load_from_checkpoints(tmp_path):
+    """Draft heads come from checkpoint tensors when the checkpoint has them: GLM-style per-depth vocabulary heads and
+    DeepSeek-style fusion projections after the decoder stack become ``model.mtp``; an EAGLE head file gives the tree draft."""
+    import os
+
+    from metal_marlin_b200.formats.safetensors_io import load_file, save_file
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.quant.convert import convert_model, random_hf_state
+    cfg = get_preset("tiny-llama")
+    cfg.num_nextn_predict_layers = 2
+    H, V, L = cfg.hidden_size, cfg.vocab_size, cfg.num_hidden_layers
+    sd = random_hf_state(cfg, seed=2)
+    g = torch.Generator().manual_seed(9)
+    head0 = (torch.randn(V, H, generator=g) * 0.02).to(torch.bfloat16)
+    sd[f"model.layers.{L}.shared_head.head.weight"] = head0                       # GLM style: a head per depth
+    sd[f"model.layers.{L + 1}.shared_head.head.weight"] = (torch.randn(H, V, generator=g) * 0.02).to(torch.bfloat16)   # stored transposed
+    sd[f"model.layers.{L + 1}.eh_proj.weight"] = (torch.randn(H, 2 * H, generator=g) * 0.02).to(torch.bfloat16)        # DeepSeek style
+    sd[f"model.layers.{L + 1}.enorm.weight"] = torch.ones(H, dtype=torch.bfloat16)
+    sd[f"model.layers.{L + 1}.hnorm.weight"] = torch.ones(H, dtype=torch.bfloat16)
+    fdir, qdir = str(tmp_path / "f"), str(tmp_path / "q")
+    os.makedirs(fdir)
+    save_file(sd, os.path.join(fdir, "model.safetensors"), metadata={"format": "pt"})
+    cfg.save_pretrained(fdir)
+    convert_model(fdir, qdir, "mmfp4", 64)
+    lm2 = MMFP4ForCausalLM.from_pretrained(qdir, device="cpu")
+    mtp = lm2.model.mtp
+    assert mtp is not None and mtp.source == "checkpoint" and mtp.depth == 2
+    assert torch.equal(mtp.heads[0].cpu(), head0) and mtp.proj[0] is None and mtp.proj[1] is not None and mtp.heads[1].shape == (V, H)
+    hidden = torch.randn(H)
+    toks = mtp.draft(hidden, 5, 4)
+    want0 = int(torch.nn.functional.linear(hidden.to(torch.bfloat16).float().unsqueeze(0), head0.float()).argmax())
+    assert len(toks) == 2 and toks[0] == want0
+    # the loaded head drives the MTP draft of the speculative engine; output equals plain greedy decoding
+    prompt = [5, 9, 2, 7, 5, 9, 2, 7]
+    want = lm2.generate([prompt], max_new_tokens=12)[0]
+    got, _ = SpeculativeEngine(lm2, MTPDraft(lm2.model, depth=2), num_speculative_tokens=2, max_len=128).generate(prompt, 12)
+    assert got == want and MTPDraft(lm2.model).head is mtp
+    # a checkpoint without such tensors leaves the model without a head
+    sd_plain = {k: v for k, v in sd.items() if f"layers.{L}." not in k and f"layers.{L + 1}." not in k}
+    f2, q2 = str(tmp_path / "f2"), str(tmp_path / "q2")
+    os.makedirs(f2)
+    save_file(sd_plain, os.path.join(f2, "model.safetensors"), metadata={"format": "pt"})
+    cfg.save_pretrained(f2)
+    convert_model(f2, q2, "mmfp4", 64)
+    assert MMFP4ForCausalLM.from_pretrained(q2, device="cpu").model.mtp is None
+    # EAGLE: published layout (fc.weight shared by all depths) and the per-depth layout the class saves
+    eg = str(tmp_path / "eagle.safetensors")
+    save_file({"fc.weight": (torch.randn(H, 2 * H, generator=g) * 0.02).to(torch.bfloat16), "fc.bias": torch.zeros(H)}, eg)
+    dr = EagleDraft.from_checkpoint(lm2.model, eg, width=2, depth=2)
+    assert dr.head.source == "checkpoint" and dr.head.proj[0] is dr.head.proj[0] and dr.head.heads[0] is None
+    out = dr.propose(prompt, 2, hidden=hidden)
+    assert len(out.tokens) >= 2 and out.parents[:2] == [-1, -1]
+    got, _ = SpeculativeEngine(lm2, dr, num_speculative_tokens=2, max_len=128).generate(prompt, 12)
+    assert got == want
+    eg2 = str(tmp_path / "eagle2.safetensors")
+    dr.save(eg2)
+    assert set(load_file(eg2)) == {"proj.0.weight", "proj.1.weight"}
+    dr2 = EagleDraft.from_checkpoint(lm2.model, eg2, width=2, depth=2)
+    assert torch.equal(dr2.head.proj[1], dr.head.proj[1])
+    save_file({"unrelated": torch.zeros(2)}, str(tmp_path / "no.safetensors"))
+    with pytest.raises(ValueError):
+        EagleDraft.from_checkpoint(lm2.model, str(tmp_path / "no.safetensors"))
