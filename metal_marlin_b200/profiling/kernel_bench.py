@@ -3,6 +3,7 @@
 
     python -m metal_marlin_b200.profiling.kernel_bench --op all --iters 20
     python -m metal_marlin_b200.profiling.kernel_bench --op moe_gate_up --iters 3 --warmup 1      # small: for ncu
+    python -m metal_marlin_b200.profiling.kernel_bench --op gemm_32768x2048x5120,bf16gemm_32768x2048x5120,cublas_32768x2048x5120
 
 Every op is timed with CUDA events on the launching stream after warm-up, with a write of a 256 MB buffer
 between iterations so the 126 MB L2 is cold, and reported with its algorithmic bytes and the fraction of the
@@ -154,6 +155,22 @@ def main():
         ops.GROUPED_GEMV_TUNE[:] = [int(v) for v in args.grouped_tune.split(",")]
     cases = build_cases(dev, args.batch, args.ctx, variants=max(1, args.chain))
     names = list(cases) if args.op == "all" else args.op.split(",")
+    for n in names:
+        # gemm_<tokens>x<out>x<in>, bf16gemm_... (both operands by TMA) and cublas_... (torch.matmul) for any shape
+        kind, _, dims = n.partition("_")
+        if n not in cases and kind in ("gemm", "bf16gemm", "cublas") and dims.count("x") == 2:
+            M, N, Kd = (int(v) for v in dims.split("x"))
+            xq = (torch.randn(M, Kd, device=dev) * 0.5).to(torch.bfloat16)
+            wf = torch.randn(N, Kd, device=dev) * 0.02
+            if kind == "gemm":
+                wq = FP4Weight.from_float(wf, 128)
+                cases[n] = (lambda i=0, xq=xq, wq=wq: ops.linear(xq, wq), 2.0 * M * N * Kd)
+            elif kind == "bf16gemm":
+                wb = wf.to(torch.bfloat16)
+                cases[n] = (lambda i=0, xq=xq, wb=wb: ops.bf16_gemm(xq, wb), 2.0 * M * N * Kd)
+            else:
+                wt = wf.to(torch.bfloat16).t()
+                cases[n] = (lambda i=0, xq=xq, wt=wt: torch.matmul(xq, wt), 2.0 * M * N * Kd)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     peak = _peak_gbs()
     out = {}
@@ -201,7 +218,7 @@ def main():
             ts.append(e0.elapsed_time(e1) * 1e3)
         ts.sort()
         med = ts[len(ts) // 2]
-        if n.startswith("gemm_"):
+        if n.split("_")[0] in ("gemm", "bf16gemm", "cublas"):
             out[n] = {"us": round(med, 2), "tflops": round(nbytes / med / 1e6, 1)}
         else:
             gbs = nbytes / med / 1e3
