@@ -391,6 +391,7 @@ def main():
                          "ms_per_step": round(rt["ms_per_step"], 4), "tok_s": round(args.batch * 1e3 / rt["ms_per_step"], 2),
                          "ttft_ms": round(rt["ttft_ms"], 2),      # prompt split over the ranks: GEMM -> reduce-scatter -> gather -> GEMM in-kernel
                          "launches_per_step": rt["launches_per_step"], "multimem": bool(getattr(state["ctx"], "use_multimem", False)),
+                         "symmetric_memory": getattr(getattr(state["ctx"], "buf", None), "backend", None),
                          "weights_gb_per_gpu": round(state["model"].weight_bytes() / 1e9, 2)}
             rt32 = run_config(32, n_half, w_half, e2e=False)
             out["tp"].update(bs32_tok_s=round(32 * 1e3 / rt32["ms_per_step"], 1), bs32_ms_per_step=round(rt32["ms_per_step"], 4),

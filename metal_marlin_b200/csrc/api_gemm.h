@@ -111,6 +111,19 @@ typedef struct {
   float eps;
 } MmbRsFinishParams;
 int mmb_tp_rs_finish(const MmbRsFinishParams* p, cudaStream_t stream);
+// In-switch all-reduce of a symmetric fp32 buffer (tp_allreduce.cu): `mc` is the buffer's address through the NVSwitch
+// multicast mapping, `peer_flags[r]` the base of rank r's flag words (arrive[tp] then done[tp]), `local_flags` this rank's.
+typedef struct {
+  float* mc;
+  unsigned* const* peer_flags;      // device array [tp]
+  const unsigned* local_flags;      // local [2 * tp]
+  unsigned* step;                   // local device word, advanced by the kernel
+  unsigned* counter;                // local CTA completion counter (0 before and after)
+  int* status;
+  long long n;                      // fp32 elements (multiple of 4)
+  int tp, rank;
+} MmbMcAllReduceParams;
+int mmb_mc_all_reduce(const MmbMcAllReduceParams* p, cudaStream_t stream);
 // Wait (bounded) until all tp ranks published `step` in `flags`; on expiry writes a code to `status`.
 int mmb_tp_wait(const unsigned* flags, const unsigned* step, int* status, int tp, cudaStream_t stream);
 

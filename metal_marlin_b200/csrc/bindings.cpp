@@ -12,6 +12,7 @@
 #include "api_gemm.h"
 #include "api_ext.h"
 #include "api_chain.h"
+#include "api_vmm.h"
 
 namespace {
 
@@ -1312,6 +1313,58 @@ void fmha_prefill(const Tensor& q, const Tensor& k, const Tensor& vt, Tensor out
   check(mmb_fmha_prefill(&p, cur_stream()), "fmha_prefill");
 }
 
+// In-switch all-reduce of the first `n` fp32 elements of a symmetric buffer.  desc (CPU int64 [6]): multicast address of the
+// data, device table of the peers' flag bases, local flags, step word, counter, status word.
+void mc_all_reduce(const Tensor& desc, int64_t n, int64_t tp, int64_t rank, const Tensor& anchor) {
+  TORCH_CHECK(!desc.is_cuda() && desc.scalar_type() == at::kLong && desc.numel() == 6 && anchor.is_cuda());
+  const int64_t* v = desc.data_ptr<int64_t>();
+  c10::cuda::CUDAGuard guard(anchor.device());
+  MmbMcAllReduceParams p{};
+  p.mc = reinterpret_cast<float*>(v[0]);
+  p.peer_flags = reinterpret_cast<unsigned* const*>(v[1]);
+  p.local_flags = reinterpret_cast<const unsigned*>(v[2]);
+  p.step = reinterpret_cast<unsigned*>(v[3]);
+  p.counter = reinterpret_cast<unsigned*>(v[4]);
+  p.status = reinterpret_cast<int*>(v[5]);
+  p.n = n;
+  p.tp = (int)tp;
+  p.rank = (int)rank;
+  check(mmb_mc_all_reduce(&p, cur_stream()), "mc_all_reduce");
+}
+
+// ---- symmetric-memory allocator (symm_vmm.cpp): thin pass-throughs; ids and file descriptors are plain integers
+int64_t vmm_available() { return mmb_vmm_available(); }
+int64_t vmm_create(int64_t dev, int64_t bytes) { return mmb_vmm_create((int)dev, bytes); }
+int64_t vmm_export_fd(int64_t id) { return mmb_vmm_export_fd(id); }
+int64_t vmm_import_fd(int64_t fd, int64_t bytes, int64_t dev) { return mmb_vmm_import_fd((int)fd, bytes, (int)dev); }
+int64_t vmm_ptr(int64_t id) { return mmb_vmm_ptr(id); }
+int64_t vmm_size(int64_t id) { return mmb_vmm_size(id); }
+int64_t vmm_free(int64_t id) { return mmb_vmm_free(id); }
+int64_t mc_create(int64_t n_dev, int64_t bytes) { return mmb_mc_create((int)n_dev, bytes); }
+int64_t mc_export_fd(int64_t id) { return mmb_mc_export_fd(id); }
+int64_t mc_import_fd(int64_t fd, int64_t n_dev, int64_t bytes) { return mmb_mc_import_fd((int)fd, (int)n_dev, bytes); }
+int64_t mc_add_device(int64_t mc, int64_t dev) { return mmb_mc_add_device(mc, (int)dev); }
+int64_t mc_bind(int64_t mc, int64_t mem) { return mmb_mc_bind(mc, mem); }
+int64_t mc_map(int64_t mc, int64_t dev) { return mmb_mc_map(mc, (int)dev); }
+int64_t mc_unbind(int64_t mc, int64_t dev, int64_t mem) { return mmb_mc_unbind(mc, (int)dev, mem); }
+void vmm_close_fd(int64_t fd) { mmb_close_fd((int)fd); }
+// Device-to-device copy between raw addresses (a mapped peer allocation and a local tensor) on the current stream of `dev`,
+// the device the mappings were made for.
+void vmm_copy(int64_t dst, int64_t src, int64_t nbytes, int64_t dev) {
+  TORCH_CHECK(dst != 0 && src != 0 && nbytes > 0);
+  c10::cuda::CUDAGuard guard((c10::DeviceIndex)dev);
+  check((int)cudaMemcpyAsync(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), (size_t)nbytes, cudaMemcpyDeviceToDevice,
+                             cur_stream()),
+        "vmm_copy");
+}
+// uint8 tensor over a mapped allocation (the allocation outlives the tensor: it is freed explicitly by id)
+Tensor vmm_tensor(int64_t id, int64_t nbytes, int64_t dev) {
+  const int64_t p = mmb_vmm_ptr(id);
+  TORCH_CHECK(p != 0 && nbytes > 0 && nbytes <= mmb_vmm_size(id), "vmm_tensor: unknown allocation or size out of range");
+  return torch::from_blob(reinterpret_cast<void*>(p), {nbytes}, [](void*) {},
+                          torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, (int)dev));
+}
+
 TORCH_LIBRARY(mmb200, m) {
   m.def("fmha_prefill", &fmha_prefill);
   m.def("fp4_gemm_grouped", &fp4_gemm_grouped);
@@ -1323,6 +1376,24 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("rmsnorm", &rmsnorm);
   m.def("silu_mul", &silu_mul);
   m.def("add", &add);
+  m.def("mc_all_reduce", &mc_all_reduce);
+  m.def("vmm_available", &vmm_available);
+  m.def("vmm_create", &vmm_create);
+  m.def("vmm_export_fd", &vmm_export_fd);
+  m.def("vmm_import_fd", &vmm_import_fd);
+  m.def("vmm_ptr", &vmm_ptr);
+  m.def("vmm_size", &vmm_size);
+  m.def("vmm_free", &vmm_free);
+  m.def("vmm_tensor", &vmm_tensor);
+  m.def("vmm_copy", &vmm_copy);
+  m.def("vmm_close_fd", &vmm_close_fd);
+  m.def("mc_create", &mc_create);
+  m.def("mc_export_fd", &mc_export_fd);
+  m.def("mc_import_fd", &mc_import_fd);
+  m.def("mc_add_device", &mc_add_device);
+  m.def("mc_bind", &mc_bind);
+  m.def("mc_map", &mc_map);
+  m.def("mc_unbind", &mc_unbind);
   m.def("embedding", &embedding);
   m.def("rope", &rope);
   m.def("qk_norm_rope_cache", &qk_norm_rope_cache);

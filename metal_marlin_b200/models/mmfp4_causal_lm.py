@@ -27,6 +27,15 @@ def prefill(model: Transformer, kv: PagedKVStorage, seqs: Sequence[Sequence[int]
     dev = model.device
     bs = kv.block_size
     B = len(seqs)
+    # parallel models bound a pass: the expert-parallel exchange by its receive regions, the tensor-parallel prompt path by
+    # the size of its reduce-scatter / gather buffers
+    ep, tp = getattr(model, "ep", None), getattr(model, "tp", None)
+    if ep is not None:
+        max_batch_tokens = min(max_batch_tokens, ep.max_tokens())
+    if tp is not None and getattr(tp, "tp", 1) > 1:
+        from ..parallel.tp import FUSED_GEMM_MAX_TOKENS
+        max_batch_tokens = min(max_batch_tokens, FUSED_GEMM_MAX_TOKENS)
+    chunk_tokens = min(chunk_tokens, max_batch_tokens)
     done = list(start) if start is not None else [0] * B
     last_logits = None       # [B, vocab] (or the rank's vocabulary shard under tensor parallelism)
     pending = [b for b in range(B) if done[b] < len(seqs[b])]

@@ -3,10 +3,16 @@
 One allocation per rank with the same layout on every rank; after the rendezvous every rank knows the
 device address of every peer's copy, so kernels can store into / load from peer memory directly.
 
-Primary path: ``torch.distributed._symmetric_memory`` (CUDA VMM allocations exported to the peers of the
-process group; where the fabric supports it the allocation is also bound to an NVSwitch multicast object, whose address
-``multicast_ptr`` lets a kernel reach all ranks' copies with one ``multimem`` store).  Fallback: CUDA IPC
-handles of a regular torch allocation exchanged through the process group.
+Backends (``MMB200_SYMM_BACKEND`` = ``vmm`` | ``torch`` | ``ipc``; default: ``vmm``, then ``torch``, then ``ipc`` when the
+one before raises):
+
+* ``vmm``: this library's own allocator (``csrc/symm_vmm.cpp``): a physical allocation created with the CUDA virtual-memory
+  API, exported as a file descriptor, passed to the peers over Unix sockets (``SCM_RIGHTS``), imported and mapped by each of
+  them; bound to an NVSwitch multicast object created by rank 0 (unless ``MMB200_SYMM_MULTICAST=0`` or NVLS is switched
+  off with ``NCCL_NVLS_ENABLE=0``), whose mapping is the ``multimem`` address of all copies.  No private PyTorch API is
+  involved.
+* ``torch``: ``torch.distributed._symmetric_memory`` (the same mechanism inside PyTorch; multicast where the fabric has it).
+* ``ipc``: CUDA IPC handles of a regular torch allocation exchanged through the process group (no multicast).
 
 Parity: nothing comparable exists in the reference (its "collectives" are numpy concatenations inside one
 process, ``metal_marlin/distributed/tensor_parallel.py:142-276``); this module is the communication runtime
@@ -34,13 +40,26 @@ class SymmetricBuffer:
         self.multicast_ptr = 0
         self._peer_tensors: List[torch.Tensor] = []
         err = None
-        try:
-            self._init_symm_mem()
-            self.backend = "symmetric_memory"
-        except Exception as e:      # fall back to classic IPC peer mappings
-            err = e
-            self._init_ipc()
-            self.backend = "cuda_ipc"
+        import os
+        want = os.environ.get("MMB200_SYMM_BACKEND", "")
+        mc = os.environ.get("MMB200_SYMM_MULTICAST", "1") != "0" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
+        order = {"vmm": ["vmm"], "torch": ["torch", "ipc"], "ipc": ["ipc"]}.get(want, ["vmm", "torch", "ipc"])
+        for i, be in enumerate(order):
+            try:
+                if be == "vmm":
+                    self._init_vmm(mc)              # without multicast on the fabric: peer pointers only (multicast_ptr 0)
+                    self.backend = "vmm"
+                elif be == "torch":
+                    self._init_symm_mem()
+                    self.backend = "symmetric_memory"
+                else:
+                    self._init_ipc()
+                    self.backend = "cuda_ipc"
+                break
+            except Exception as e:
+                err = e
+                if i == len(order) - 1:
+                    raise
         self.init_error = repr(err) if err else None
         self.local.zero_()
         torch.cuda.synchronize(device)
@@ -58,6 +77,21 @@ class SymmetricBuffer:
         # a multimem store there lands in every rank's copy
         self.multicast_ptr = int(getattr(hdl, "multicast_ptr", 0) or 0)
         assert len(self.peer_ptrs) == self.world and self.peer_ptrs[self.rank] == t.data_ptr()
+
+    def _init_vmm(self, multicast: bool) -> None:
+        from .vmm import VmmExchange
+        self._vmm = VmmExchange(self.nbytes, self.device, self.group, multicast=multicast)
+        self.local = self._vmm.local
+        self.peer_ptrs = list(self._vmm.peer_ptrs)
+        self.multicast_ptr = self._vmm.multicast_ptr
+        self.nbytes = self._vmm.nbytes
+
+    def close(self) -> None:
+        """Unmap and release what the own allocator holds (the other backends free with their tensors)."""
+        v = getattr(self, "_vmm", None)
+        if v is not None:
+            v.close()
+            self._vmm = None
 
     def _init_ipc(self) -> None:
         t = torch.empty(self.nbytes, dtype=torch.uint8, device=self.device)

@@ -302,12 +302,45 @@ class TPContext:
             return {"delta": self.finish_plain(d)}
         return {"delta": d}
 
+    AR_MAX_ELEMS = 8192 * 4096          # fp32 elements of the in-switch all-reduce buffer (128 MiB per rank)
+
+    def _ar_buffers(self):
+        """Symmetric fp32 buffer + flag words of the in-switch all-reduce (``csrc/tp_allreduce.cu``), created on first use;
+        ``None`` when the allocation has no NVSwitch multicast mapping (the collective library is used then)."""
+        ar = getattr(self, "_ar", None)
+        if ar is None:
+            ar = False
+            if self.fused_ok and self.use_multimem and self.tp > 1 and os.environ.get("MMB_TP_MC_ALLREDUCE", "1") != "0":
+                nbytes = self.AR_MAX_ELEMS * 4
+                buf = SymmetricBuffer(nbytes + 256, self.device, self.group)
+                if buf.multicast_ptr:
+                    flags_off = nbytes
+                    table = torch.tensor([buf.peer_addr(r, flags_off) for r in range(self.tp)], dtype=torch.int64).to(self.device)
+                    step = torch.zeros(1, dtype=torch.int32, device=self.device)
+                    counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+                    desc = torch.tensor([buf.multicast_ptr, table.data_ptr(), buf.local.data_ptr() + flags_off, step.data_ptr(),
+                                         counter.data_ptr(), self.status.data_ptr()], dtype=torch.int64)
+                    ar = {"buf": buf, "data": buf.view(0, (self.AR_MAX_ELEMS,), torch.float32), "table": table, "step": step,
+                          "counter": counter, "desc": desc}
+            self._ar = ar
+        return ar or None
+
     def all_reduce(self, y: torch.Tensor) -> torch.Tensor:
-        if self.tp > 1:
-            yf = y.to(torch.float32)
-            dist.all_reduce(yf, group=self.group)
-            return yf.to(y.dtype)
-        return y
+        """Sum of ``y`` over the tensor-parallel ranks.  With NVSwitch multicast: one kernel of this library
+        (``multimem.ld_reduce`` + ``multimem.st`` on a symmetric fp32 copy, bounded flag waits, no collective call);
+        otherwise ``torch.distributed.all_reduce``."""
+        if self.tp <= 1:
+            return y
+        n = y.numel()
+        ar = self._ar_buffers() if (y.is_cuda and n % 4 == 0 and n <= self.AR_MAX_ELEMS) else None
+        if ar is not None:
+            data = ar["data"][:n].view(y.shape)
+            data.copy_(y)                                                   # cast to fp32 into this rank's symmetric copy
+            ops.K.mmb200.mc_all_reduce(ar["desc"], n, self.tp, self.rank, data)
+            return data.to(y.dtype)
+        yf = y.to(torch.float32)
+        dist.all_reduce(yf, group=self.group)
+        return yf.to(y.dtype)
 
     def greedy(self, logits_local: torch.Tensor, vocab_offset: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Global arg-max of vocabulary-sharded logits."""

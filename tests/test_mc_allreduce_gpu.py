@@ -1,0 +1,102 @@
+"""In-switch all-reduce (``multimem.ld_reduce`` + ``multimem.st`` in one kernel, ``csrc/tp_allreduce.cu``) against the
+collective library, on PyTorch's symmetric memory and on this library's own allocator with its own multicast object.
+Runs as child processes, one per GPU; skipped with fewer than two GPUs or without NVSwitch multicast."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+_CHILD = r"""
+import os, sys, json, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["MMB_REPO"])
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from metal_marlin_b200 import ops
+from metal_marlin_b200.parallel.tp import TPContext
+ctx = TPContext(rank, world, dev, n_sites=1, hidden=256, max_tokens=8)
+res = {"backend": ctx.buf.backend, "multimem": bool(ctx.use_multimem)}
+if ctx._ar_buffers() is None:
+    res["skipped"] = "no multicast mapping"
+else:
+    errs, same = [], []
+    torch.manual_seed(100 + rank)
+    for shape in [(8, 512), (300, 2048), (4096, 2048), (1, 4)]:
+        for rep in range(3):                       # repeated calls: the step words of the ranks stay in lock step
+            y = (torch.randn(*shape, device=dev) * 0.5).to(torch.bfloat16)
+            got = ctx.all_reduce(y)
+            ref = y.to(torch.float32)
+            dist.all_reduce(ref)
+            errs.append(float((got.float() - ref).abs().max() / ref.abs().max().clamp_min(1e-6)))
+            # every rank holds the same bits
+            chk = got.float().sum().reshape(1).clone()
+            lo, hi = chk.clone(), chk.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            same.append(bool(lo.item() == hi.item()))
+    res["max_err"] = max(errs); res["identical_on_all_ranks"] = all(same)
+    # device-side timing of a prompt-size all-reduce (4096 x 2048), both ways
+    y = (torch.randn(4096, 2048, device=dev) * 0.5).to(torch.bfloat16)
+    def timed(fn, n=10):
+        for _ in range(3): fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n): fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return round(float(t.item()), 1)
+    def nccl():
+        f = y.to(torch.float32); dist.all_reduce(f); return f.to(torch.bfloat16)
+    res["us_in_switch"] = timed(lambda: ctx.all_reduce(y)); res["us_nccl"] = timed(nccl)
+    res["status"] = ops.check_status(dev)
+if rank == 0:
+    print("RESULT " + json.dumps(res), flush=True)
+dist.barrier()
+torch.cuda.synchronize()
+ar = getattr(ctx, "_ar", None)
+if ar:
+    ar["buf"].close()          # own allocator: unbind / unmap in lock step before any rank leaves
+ctx.buf.close()
+dist.barrier()
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.parametrize("backend", ["torch", "vmm"])
+def test_in_switch_all_reduce_matches_the_collective(tmp_path, backend):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, MMB_REPO=repo, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), MMB200_SYMM_BACKEND=backend, MMB200_SYMM_MULTICAST="1", MMB200_SOCKET_DIR=str(tmp_path))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    from conftest import collect_children
+    outs = collect_children(procs, 150)
+    assert any(l.startswith("RESULT ") for l in outs[0].splitlines()), outs
+    res = json.loads(next(l for l in outs[0].splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    print(res)
+    out_dir = os.path.join(repo, "gpurun_out")
+    if os.path.isdir(out_dir):
+        with open(os.path.join(out_dir, f"mc_allreduce_{backend}.json"), "w") as f:
+            json.dump(res, f)
+    if "skipped" in res:
+        pytest.skip(res["skipped"])
+    assert res["max_err"] < 1e-2 and res["identical_on_all_ranks"] and res["status"] == 0, res
+    assert res["backend"] == ("vmm" if backend == "vmm" else res["backend"])
