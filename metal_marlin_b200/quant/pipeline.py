@@ -179,20 +179,32 @@ def quantize_checkpoint(model_dir: str, out_dir: str, fmt: str = "mmfp4", method
     state = state or gptq_mod.ResumableState(out_dir)
     info = {"with_hessian": 0, "rtn_fallback": 0, "rotated": 0}
 
+    if method == "awq":
+        # whole-checkpoint AWQ: one scale per (RMSNorm -> projections) group, folded into the projections' input channels
+        # and out of the norm's weight, so the result is an ordinary weights-only checkpoint
+        from ..formats.safetensors_io import SafetensorsFile
+        where = {}
+        for fn in sorted(os.listdir(model_dir)):
+            if fn.endswith(".safetensors"):
+                with SafetensorsFile(os.path.join(model_dir, fn)) as sf:
+                    for k in sf.keys():
+                        where[k] = os.path.join(model_dir, fn)
+
+        def get_w(n):
+            with SafetensorsFile(where[n]) as sf:
+                return sf.get_tensor(n).to(torch.float32)
+
+        plan = awq_mod.awq_plan(where.keys(), get_w, lambda n: getattr(col, "inputs", {}).get(n), "fp4", group_size)
+        stats = convert_model(model_dir, out_dir, ck_fmt, group_size, device=device,
+                              tensors=awq_mod.apply_awq_plan(iter_safetensors_weights(model_dir), plan))
+        stats.update(method="awq", awq_groups=len(plan), awq_scaled_tensors=sum(len(g["consumers"]) for g in plan.values()),
+                     awq_mean_gain=(sum(g["mse_rtn"] / max(g["mse"], 1e-30) for g in plan.values()) / max(1, len(plan))),
+                     calibration_tokens=sum(col.n.values()) // max(1, len(col.n)))
+        return stats
+
     def qfn(name, w, gs):
         gs = fp4fmt.pick_group_size(w.shape[1], gs_for(name, gs))
         H = col.get(name)
-        if method == "awq":
-            x = getattr(col, "inputs", {}).get(name)
-            if x is None:
-                info["rtn_fallback"] += 1
-                return fp4fmt.quantize_codes(w, gs)
-            # the per-channel scale must be folded into the producer of the activation, which a weights-only
-            # checkpoint cannot express; AWQ is therefore applied as a clipping / scale search that keeps the layer
-            # input unchanged: pick the rescaled quantization, then map it back to the original channel scaling
-            q, s, st = awq_mod.awq_quantize(w, x.to(w.device), "fp4", gs)
-            info["with_hessian"] += 1
-            return fp4fmt.quantize_codes(q.dequantize(torch.float32) / s, gs)
         if H is None:
             info["rtn_fallback"] += 1
             return fp4fmt.quantize_codes(w, gs)

@@ -42,7 +42,12 @@ def test_calibrated_quantization_writes_a_loadable_checkpoint(float_ckpt, tmp_pa
     cfg, d = float_ckpt
     out = str(tmp_path / method)
     st = quantize_checkpoint(d, out, fmt="mmfp4", method=method, group_size=64, num_samples=2, seq_len=24, device="cpu")
-    assert st["method"] == method and st["with_hessian"] > 0 and st["quantized"] == st["with_hessian"] + st["rtn_fallback"]
+    assert st["method"] == method
+    if method == "awq":        # one scale per (norm -> projections) group, folded into the weights and out of the norm
+        assert st["awq_groups"] >= 2 * cfg.num_hidden_layers and st["awq_scaled_tensors"] >= 4 * cfg.num_hidden_layers
+        assert st["awq_mean_gain"] >= 1.0
+    else:
+        assert st["with_hessian"] > 0 and st["quantized"] == st["with_hessian"] + st["rtn_fallback"]
     from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM
     lm = MMFP4ForCausalLM.from_pretrained(out, device="cpu")
     assert torch.isfinite(lm.forward_logits(list(range(5, 21)))).all()

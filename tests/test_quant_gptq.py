@@ -98,3 +98,45 @@ def test_mixed_precision_presets_and_bit_allocation():
     alloc = mixed_precision.allocate_bits(sens, {"a": 100, "b": 100}, target_bpw=4.0, choices=(2, 4, 8))
     assert alloc == {"a": 4, "b": 4} or alloc == {"a": 4, "b": 2}
     assert mixed_precision.allocate_bits(sens, {"a": 100, "b": 100}, target_bpw=3.0, choices=(2, 4, 8)) == {"a": 4, "b": 2}
+
+
+def test_awq_plan_folds_the_scale_into_the_norm_and_keeps_the_function():
+    """Whole-checkpoint AWQ on one synthetic layer: projections behind a norm share a scale vector; after applying the plan the
+    float function is unchanged (norm / s, weights * s, router compensated) and the quantized layer output is closer to the
+    float one than round-to-nearest when a few input channels dominate."""
+    torch.manual_seed(0)
+    H, I, E = 128, 192, 4
+    p = "model.layers.0."
+    sd = {p + "input_layernorm.weight": 1 + 0.1 * torch.randn(H), p + "post_attention_layernorm.weight": 1 + 0.1 * torch.randn(H),
+          p + "self_attn.q_proj.weight": torch.randn(H, H) * 0.05, p + "self_attn.k_proj.weight": torch.randn(64, H) * 0.05,
+          p + "self_attn.v_proj.weight": torch.randn(64, H) * 0.05, p + "self_attn.o_proj.weight": torch.randn(H, H) * 0.05,
+          p + "mlp.gate.weight": torch.randn(E, H) * 0.05, "model.norm.weight": torch.ones(H)}
+    for e in range(E):
+        sd[p + f"mlp.experts.{e}.gate_proj.weight"] = torch.randn(I, H) * 0.05
+        sd[p + f"mlp.experts.{e}.up_proj.weight"] = torch.randn(I, H) * 0.05
+        sd[p + f"mlp.experts.{e}.down_proj.weight"] = torch.randn(H, I) * 0.05
+    X = torch.randn(400, H)
+    X[:, :6] *= 12.0                                     # salient channels
+    inputs = {n: X for n in sd if n.endswith(("q_proj.weight", "k_proj.weight", "v_proj.weight", "gate_proj.weight", "up_proj.weight"))}
+    plan = awq.awq_plan(sd.keys(), lambda n: sd[n], lambda n: inputs.get(n), "int4", 64, n_grid=10)
+    assert set(plan) == {p + "input_layernorm.weight", p + "post_attention_layernorm.weight"}
+    g = plan[p + "post_attention_layernorm.weight"]
+    assert len(g["consumers"]) == 2 * E and g["compensate"] == [p + "mlp.gate.weight"] and g["alpha"] > 0 and g["mse"] < 0.7 * g["mse_rtn"]
+    new = dict(awq.apply_awq_plan(sd.items(), plan))
+    assert set(new) == set(sd) and torch.equal(new[p + "self_attn.o_proj.weight"], sd[p + "self_attn.o_proj.weight"])
+
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    x = torch.randn(8, H)
+    for norm, mats in ((p + "input_layernorm.weight", [p + "self_attn.q_proj.weight", p + "self_attn.v_proj.weight"]),
+                       (p + "post_attention_layernorm.weight", [p + "mlp.gate.weight", p + "mlp.experts.2.up_proj.weight"])):
+        for m in mats:
+            torch.testing.assert_close(rms(x, new[norm]) @ new[m].t(), rms(x, sd[norm]) @ sd[m].t(), rtol=1e-4, atol=1e-4)
+    # quantized: the scaled weights reproduce the float projection better on the salient data
+    from metal_marlin_b200.quant.rtn import quantize
+    n, m = p + "post_attention_layernorm.weight", p + "mlp.experts.1.gate_proj.weight"
+    ref = X @ sd[m].t()
+    e_rtn = ((X @ quantize(sd[m], "int4", 64).dequantize(torch.float32).t()) - ref).pow(2).mean()
+    s = plan[n]["scale"]
+    e_awq = (((X / s) @ quantize(new[m], "int4", 64).dequantize(torch.float32).t()) - ref).pow(2).mean()
+    assert e_awq < 0.8 * e_rtn
