@@ -42,7 +42,7 @@ _reg(".sampler", "SamplingConfig", "Sampler", "sample_next_token", MetalSampler=
 _reg(".rope", "YaRNConfig", "RotaryEmbedding", "apply_rope", "rope_inv_freq", "yarn_inv_freq")
 _reg(".kv.contiguous", "KVCache", "KVCacheTorch", "MLAKVCache", "PersistentKVCache", "CacheConfig", "quantize_kv", "dequantize_kv")
 _reg(".kv.paged", "BlockAllocator", "MultimodalBlockAllocator", "PageTable", "PrefixCache", "PagedKVCache")
-_reg(".layers", "MMFP4Linear", "QuantizedLinear", "TrellisLinear", "HadamardLinear")
+_reg(".layers", "MMFP4Linear", "QuantizedLinear", "TrellisLinear", "HadamardLinear", "Sparse24Linear")
 _reg(".ops.weights", "FP4Weight", "FP4ExpertBank")
 _reg(".trellis", "TrellisForCausalLM", "TrellisGenerator", "TrellisModelConfig", "GenerationConfig")
 _reg(".formats.mmfp4_loader", "MMFP4ModelLoader")

@@ -64,6 +64,11 @@ typedef struct {
   const void* cb_zeros;     // fp16 [N, K >> gs_shift] or null
   const float* cb_lut;      // device float [256]
   int cb_bits;              // 2, 4 or 8
+  // 2:4 sparse FP4 weights (mmb_sparse24_gemm): of every 4 consecutive input columns 2 are stored.  qw = E2M1 codes of the
+  // kept values, row major [N, K / 4] bytes (two codes per byte, low nibble first); sp_meta = [N, K / 8] bytes, one nibble
+  // per group of 4 columns (low nibble first): bits 0-1 position of the first kept value, bits 2-3 of the second; sc = fp16
+  // scales [N, K >> gs_shift] over the dense columns.
+  const void* sp_meta;
 } MmbFp4GemmParams;
 
 int mmb_fp4_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
@@ -71,6 +76,9 @@ int mmb_fp4_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
 int mmb_trellis_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
 // Same pipeline with codebook weights (table look-up, zero point and group scale applied inside the main loop); plain mode only.
 int mmb_codebook_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
+// Same pipeline with 2:4 sparse FP4 weights: the kept values are scattered to their columns (zeros elsewhere) inside the main
+// loop, so the matrix is read at 0.375 bytes per dense weight and no dense copy exists; plain mode only.
+int mmb_sparse24_gemm(const MmbFp4GemmParams* p, cudaStream_t stream);
 
 // out[M, N] = x[M, K] * W[N, K]^T, both bf16 row major (TMA for both operands), fp32 accumulate in TMEM.
 // Batched over `batch` independent problems with element strides (0 = shared operand).

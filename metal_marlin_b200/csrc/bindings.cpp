@@ -1032,6 +1032,38 @@ void codebook_gemm(const Tensor& x, const Tensor& codes, const Tensor& scales, c
   check(mmb_codebook_gemm(&p, cur_stream()), "codebook_gemm");
 }
 
+// 2:4 sparse FP4 weights on the tensor cores (gemm_sm100.cu, weight format 4): codes uint8 [N, K / 4], meta uint8 [N, K / 8],
+// scales fp16 [N, K / group].
+void sparse24_gemm(const Tensor& x, const Tensor& codes, const Tensor& meta, const Tensor& scales, Tensor out, int64_t in_f,
+                   int64_t group_size, Tensor status) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.size(1) == in_f && out.is_contiguous() && out.size(0) == x.size(0));
+  TORCH_CHECK(codes.is_cuda() && codes.scalar_type() == at::kByte && codes.is_contiguous() && codes.dim() == 2 && codes.size(1) * 4 == in_f &&
+              out.size(1) == codes.size(0));
+  TORCH_CHECK(meta.is_cuda() && meta.scalar_type() == at::kByte && meta.is_contiguous() && meta.size(0) == codes.size(0) && meta.size(1) * 8 == in_f);
+  TORCH_CHECK(scales.scalar_type() == at::kHalf && scales.is_contiguous() && scales.numel() == codes.size(0) * (in_f / group_size));
+  TORCH_CHECK(group_size >= 32 && (group_size & (group_size - 1)) == 0 && in_f % group_size == 0 && in_f % 64 == 0,
+              "sparse24_gemm: group size must be a power of two >= 32 dividing the input width (a multiple of 64)");
+  c10::cuda::CUDAGuard guard(x.device());
+  MmbFp4GemmParams p{};
+  p.x = x.data_ptr();
+  p.qw = codes.data_ptr();
+  p.sp_meta = meta.data_ptr();
+  p.sc = scales.data_ptr();
+  p.out = out.data_ptr();
+  p.M = (int)x.size(0);
+  p.N = (int)codes.size(0);
+  p.K = (int)in_f;
+  p.Kx = (int)in_f;
+  p.ldo = (int)out.stride(0);
+  int sh = 0;
+  while ((1ll << sh) < group_size) ++sh;
+  p.gs_shift = sh;
+  p.status = status.data_ptr<int>();
+  check(mmb_sparse24_gemm(&p, cur_stream()), "sparse24_gemm");
+}
+
 void codebook_gemv(const Tensor& x, const Tensor& codes, const Tensor& scales, const OptT& zeros, const Tensor& lut, Tensor y,
                    int64_t in_f, int64_t group_size, int64_t bits) {
   check_bf16(x, "x");
@@ -1424,6 +1456,7 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("trellis_moe", &trellis_moe);
   m.def("codebook_gemv", &codebook_gemv);
   m.def("codebook_gemm", &codebook_gemm);
+  m.def("sparse24_gemm", &sparse24_gemm);
   m.def("vision_preprocess", &vision_preprocess);
   m.def("vision_preprocess_ex", &vision_preprocess_ex);
   m.def("channel_stats", &channel_stats);

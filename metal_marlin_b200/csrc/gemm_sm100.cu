@@ -86,7 +86,8 @@ __device__ __forceinline__ void cb_expand_row(const uint32_t (&words)[8], const 
 
 // WFMT 0: FP4 tile-layout weights expanded by the warps 2..17.  WFMT 1: bf16 weights fetched by TMA.  WFMT 2: trellis weights
 // (16 x 16 tiles of 2..8-bit codes, LSB-first bit stream) decoded by the same warps inside the main loop.  WFMT 3: codebook
-// weights (row-major 2 / 4 / 8-bit codes, 256-entry value table, fp16 group scales and optional zero points).
+// weights (row-major 2 / 4 / 8-bit codes, 256-entry value table, fp16 group scales and optional zero points).  WFMT 4: 2:4
+// sparse FP4 weights (two kept E2M1 values + a 4-bit position word per group of four columns), scattered to a dense tile.
 template <int TN, int WFMT, int MINB>
 __global__ void __launch_bounds__(kGemmThreads, MINB)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -94,7 +95,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   using Cfg = GemmCfg<TN, MINB>;
   constexpr bool QW = WFMT != 1;       // weights are expanded by the warps of this CTA (parameters in `p`)
   extern __shared__ unsigned char smem_dyn[];
-  __shared__ float lut_s[WFMT == 3 ? 256 : 1];
+  __shared__ float lut_s[WFMT == 3 ? 256 : (WFMT == 4 ? 16 : 1)];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   PipeShared* ps = reinterpret_cast<PipeShared*>(tiles + (size_t)Cfg::kStages * Cfg::stage_bytes);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -496,6 +497,83 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&ps->full_a[s]);
       }
+    } else if (WFMT == 4) {
+      // 2:4 sparse FP4.  Lane l owns output row l / 2 of a 16-row block and the 32 dense columns (l % 2) * 32 .. + 31 of the
+      // k block: 8 groups of four = 8 bytes of kept codes + 4 bytes of positions (both requested before the stage wait),
+      // scattered into four 16-byte chunks of the swizzled K-major A row.
+      if (tid - 64 < 16) {
+        const int c = tid - 64, m = c & 7, e = m >> 1, f = m & 1;
+        const float mag = e == 0 ? 0.5f * (float)f : (1.f + 0.5f * (float)f) * (float)(1 << (e - 1));
+        lut_s[c] = (c & 8) ? -mag : mag;
+      }
+      asm volatile("bar.sync 6, %0;" ::"n"(kExpandWarps * 32) : "memory");
+      const int NG = K >> p.gs_shift;
+      const uint8_t* cbase = reinterpret_cast<const uint8_t*>(p.qw);
+      const uint8_t* mbase = reinterpret_cast<const uint8_t*>(p.sp_meta);
+      const __half* sc_h = reinterpret_cast<const __half*>(p.sc);
+      const int half_k = (lane & 1) * 32;
+      int orow[kRB], st_off[kRB];
+      bool rt_ok[kRB];
+#pragma unroll
+      for (int j = 0; j < kRB; ++j) {
+        const int blk = dw0 + j;
+        orow[j] = n0 + blk * 16 + (lane >> 1);
+        rt_ok[j] = orow[j] < N;
+        st_off[j] = (blk * 16 + (lane >> 1)) * 128;
+      }
+      for (int i = kh; i < KB; i += kSplit) {
+        const int s = i % Cfg::kStages;
+        const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
+        uint2 cw[kRB];
+        uint32_t mw[kRB];
+        float scl[kRB];
+#pragma unroll
+        for (int j = 0; j < kRB; ++j) {
+          cw[j] = make_uint2(0, 0);
+          mw[j] = 0u;
+          scl[j] = 0.f;
+          if (rt_ok[j]) {
+            const int k0 = i * kBK + half_k;
+            cw[j] = __ldg(reinterpret_cast<const uint2*>(cbase + (long long)orow[j] * (K >> 2) + (k0 >> 2)));
+            mw[j] = __ldg(reinterpret_cast<const uint32_t*>(mbase + (long long)orow[j] * (K >> 3) + (k0 >> 3)));
+            scl[j] = __half2float(sc_h[(long long)orow[j] * NG + (k0 >> p.gs_shift)]);
+          }
+        }
+        if (!mbar_wait(&ps->empty[s], ph ^ 1u, abort_flag)) {
+          if (atomicExch(&ps->abort_flag, 1) == 0 && status) atomicExch(status, 3);
+          ok = false;
+          break;
+        }
+        unsigned char* a_tile = tiles + (size_t)s * Cfg::stage_bytes;
+        const int r7 = (lane >> 1) & 7;
+#pragma unroll
+        for (int j = 0; j < kRB; ++j) {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {                     // chunk cc = groups 2 cc and 2 cc + 1
+            uint32_t o4[4];
+#pragma unroll
+            for (int g2 = 0; g2 < 2; ++g2) {
+              const int g = cc * 2 + g2;
+              const uint32_t word = g < 4 ? cw[j].x : cw[j].y;
+              const uint32_t pair = (word >> ((g & 3) * 8)) & 0xffu;
+              const uint32_t m4 = (mw[j] >> (g * 4)) & 0xfu;
+              const int i0 = (int)(m4 & 3u), i1 = (int)(m4 >> 2);
+              const float a = lut_s[pair & 0xfu] * scl[j], b = lut_s[pair >> 4] * scl[j];
+              float v[4];
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) v[q4] = (q4 == i0 ? a : 0.f) + (q4 == i1 ? b : 0.f);
+              const bf162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+              o4[g2 * 2] = *reinterpret_cast<const uint32_t*>(&p0);
+              o4[g2 * 2 + 1] = *reinterpret_cast<const uint32_t*>(&p1);
+            }
+            const int chunk = (lane & 1) * 4 + cc;
+            *reinterpret_cast<uint4*>(a_tile + st_off[j] + ((chunk ^ r7) * 16)) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ps->full_a[s]);
+      }
     }
     // ---- epilogue: TMEM -> registers -> global
     if (ok) ok = mbar_wait(&ps->acc_full, 0u, abort_flag);
@@ -742,6 +820,29 @@ MMB_API int mmb_codebook_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
     case 64: return launch_gemm<64, 3>(mx, mx, p, pb, grid, stream);
     case 128: return launch_gemm<128, 3>(mx, mx, p, pb, grid, stream);
     default: return launch_gemm<256, 3>(mx, mx, p, pb, grid, stream);
+  }
+}
+
+// 2:4 sparse FP4 weights (WFMT 4): plain mode only.
+MMB_API int mmb_sparse24_gemm(const MmbFp4GemmParams* pp, cudaStream_t stream) {
+  using namespace mmb;
+  MmbFp4GemmParams p = *pp;
+  if (p.M <= 0 || p.N <= 0) return 0;
+  if (p.qw == nullptr || p.sc == nullptr || p.sp_meta == nullptr) return (int)cudaErrorInvalidValue;
+  if (p.K % 64 != 0 || p.Kx != p.K || p.gs_shift < 5 || (p.K & ((1 << p.gs_shift) - 1)) != 0) return (int)cudaErrorInvalidValue;
+  if (p.act != 0 || p.tile_expert != nullptr || p.rs_peer_bufs != nullptr || p.ag.flags != nullptr || p.out_rows != nullptr) return (int)cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(p.qw) & 7) || (reinterpret_cast<uintptr_t>(p.sp_meta) & 3)) return (int)cudaErrorInvalidValue;
+  const int TN = pick_tn(p.M, p.token_tile);
+  CUtensorMap mx;
+  int e = make_tmap_2d(&mx, p.x, p.Kx, p.M, p.Kx, TN);
+  if (e) return e;
+  MmbBf16GemmParams pb{};
+  dim3 grid((p.N + kTileRows - 1) / kTileRows, (p.M + TN - 1) / TN, 1);
+  switch (TN) {
+    case 32: return launch_gemm<32, 4>(mx, mx, p, pb, grid, stream);
+    case 64: return launch_gemm<64, 4>(mx, mx, p, pb, grid, stream);
+    case 128: return launch_gemm<128, 4>(mx, mx, p, pb, grid, stream);
+    default: return launch_gemm<256, 4>(mx, mx, p, pb, grid, stream);
   }
 }
 

@@ -1,3 +1,3 @@
-from .linear import HadamardLinear, MMFP4Linear, QuantizedLinear, TrellisLinear
+from .linear import HadamardLinear, MMFP4Linear, QuantizedLinear, Sparse24Linear, TrellisLinear
 
-__all__ = ["HadamardLinear", "MMFP4Linear", "QuantizedLinear", "TrellisLinear"]
+__all__ = ["HadamardLinear", "MMFP4Linear", "QuantizedLinear", "Sparse24Linear", "TrellisLinear"]

@@ -130,6 +130,65 @@ class QuantizedLinear:
     forward = __call__
 
 
+class Sparse24Linear:
+    """2:4 structured-sparse FP4 linear: of every four consecutive input columns the two of largest magnitude are kept,
+    quantized to E2M1 with one fp16 scale per ``group_size`` dense columns, and stored with a 4-bit position word per group -
+    0.375 bytes per dense weight (FP4 dense: 0.5).  The product runs on the tensor-core GEMM, which scatters the kept values
+    into a dense tile inside its main loop (``csrc/gemm_sm100.cu``, weight format 4); no dense copy of the matrix exists.
+
+    Parity: reference ``src/sparse_gemm.metal:334`` (``marlin_gemm_sparse_fp4``: compressed FP4 values + 2-bit position
+    metadata, dense tile rebuilt by the loader), ``src/sparse.metal:630``, ``metal_marlin/prune_weights.py`` (magnitude 2:4)."""
+    is_generic = True
+    names = None
+
+    def __init__(self, codes, meta, scales, out_features: int, in_features: int, group_size: int, bias=None):
+        self.codes, self.meta, self.scales = codes, meta, scales
+        self.out_features, self.in_features, self.group_size = out_features, in_features, group_size
+        self.bias = bias
+
+    @staticmethod
+    def prune(w: torch.Tensor):
+        """``(kept values [out, in / 4, 2], positions [out, in / 4, 2] ascending)`` of the magnitude 2:4 pattern."""
+        out_f, in_f = w.shape
+        g = w.reshape(out_f, in_f // 4, 4)
+        pos = g.abs().topk(2, -1).indices.sort(-1).values
+        return g.gather(-1, pos), pos
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor, group_size: int = 128, bias=None, device=None):
+        from ..formats import fp4 as fp4fmt
+        out_f, in_f = w.shape
+        if in_f % 64 or in_f % group_size or group_size < 32 or group_size & (group_size - 1):
+            raise ValueError("in_features must be a multiple of 64 and of the group size (a power of two >= 32)")
+        device = torch.device(device) if device is not None else w.device
+        vals, pos = cls.prune(w.to(torch.float32))
+        # the kept values of a dense group of `group_size` columns are `group_size / 2` consecutive compact columns
+        codes, scales = fp4fmt.quantize_codes(vals.reshape(out_f, in_f // 2), group_size // 2)
+        c = codes.view(out_f, in_f // 4, 2)
+        packed = (c[..., 0] | (c[..., 1] << 4)).to(torch.uint8)
+        nib = (pos[..., 0] | (pos[..., 1] << 2)).to(torch.uint8).view(out_f, in_f // 8, 2)
+        meta = (nib[..., 0] | (nib[..., 1] << 4)).to(torch.uint8)
+        b = None if bias is None else bias.to(device, torch.bfloat16)
+        return cls(packed.contiguous().to(device), meta.contiguous().to(device), scales.contiguous().to(device), out_f, in_f, group_size, b)
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        from ..ops import reference as ref
+        return ref.sparse24_dequant(self.codes, self.meta, self.scales, self.in_features, self.group_size).to(dtype)
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.meta.numel() + self.scales.numel() * 2
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).to(torch.bfloat16)
+        y = ops.sparse24_gemm(x2, self.codes, self.meta, self.scales, self.in_features, self.group_size)
+        if self.bias is not None:
+            y = y + self.bias
+        return y.view(*shape[:-1], self.out_features)
+
+    forward = __call__
+
+
 class TrellisLinear:
     is_generic = True
     names = None

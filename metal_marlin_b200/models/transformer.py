@@ -279,6 +279,24 @@ class Transformer:
             slots = meta.cached(("slots", 0, n_ctx), _slots)
             ops.fmha_prefill(q, kv.k[li].view(-1, Hk, D)[slots], kv.v[li].view(-1, Hk, D)[slots], out.view(-1, Hq, D), self.scale)
             return out
+        n_seq = len(meta.cu_seqlens) - 1
+        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and n_seq > 1 and not cfg.sliding_window
+                and not isinstance(kv.k[li], ops.FP8KV) and q.stride(2) == 1
+                and all(ops.fmha_ok(meta.cu_seqlens[b + 1] - meta.cu_seqlens[b], int(meta.ctx_lens_host[b]), D, D, q.device)
+                        for b in range(n_seq))):
+            # several long sequences: the tcgen05 attention kernel sequence by sequence (a launch per sequence costs
+            # microseconds against the milliseconds of a prompt-size attention; the mma.sync kernel below is 4-5 x slower)
+            for b in range(n_seq):
+                s0, e0 = meta.cu_seqlens[b], meta.cu_seqlens[b + 1]
+                n_ctx = int(meta.ctx_lens_host[b])
+
+                def _slots(b=b, n_ctx=n_ctx):
+                    tok = torch.arange(n_ctx, device=q.device)
+                    return meta.block_tables[b, tok // bs].long() * bs + tok % bs
+                slots = meta.cached(("slots", b, n_ctx), _slots)
+                ops.fmha_prefill(q[s0:e0], kv.k[li].view(-1, Hk, D)[slots], kv.v[li].view(-1, Hk, D)[slots],
+                                 out[s0:e0].view(-1, Hq, D), self.scale)
+            return out
         if meta.attn_mask is None and q.dtype == torch.bfloat16:
             # one launch for all sequences: keys are read from the paged pool through the block table
             cu_q = meta.dev_ints("cu_q", meta.cu_seqlens, q.device)

@@ -927,6 +927,24 @@ def codebook_gemm(x, codes, scales, zeros, lut, in_f: int, group_size: int, bits
     return out
 
 
+def sparse24_gemm(x, codes, meta, scales, in_f: int, group_size: int, out=None):
+    """``x [M, in] @ W^T`` with 2:4 sparse FP4 weights (``layers.Sparse24Linear``): the kept values are scattered to their
+    columns inside the tcgen05 GEMM's main loop.  Off the GPU: the product over the de-quantized dense matrix."""
+    ok = (_use_native(x) and not NO_TCGEN05 and x.dtype == torch.bfloat16 and in_f % 64 == 0 and group_size >= 32
+          and group_size & (group_size - 1) == 0 and in_f % group_size == 0)
+    if not ok:
+        w = ref.sparse24_dequant(codes, meta, scales, in_f, group_size)
+        y = (x[:, :in_f].to(torch.float32) @ w.t()).to(torch.bfloat16)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty(x.shape[0], codes.shape[0], dtype=torch.bfloat16, device=x.device)
+    K.mmb200.sparse24_gemm(x.contiguous(), codes, meta, scales, out, in_f, group_size, gemm_status(x.device))
+    return out
+
+
 def vision_preprocess(images, out_h: int, out_w: int, *, patch: int = 0, mean=(0.48145466, 0.4578275, 0.40821073),
                       std=(0.26862954, 0.26130258, 0.27577711)):
     """uint8 ``[B, H, W, 3]`` -> bf16 ``[B, 3, out_h, out_w]`` (``patch == 0``) or patches ``[B, n, 3 * patch^2]``."""

@@ -446,3 +446,21 @@ def prefill_attention(q, k, v, cu_q, cu_k, block_tables, ctx_lens, block_size, s
         pr = torch.where(ok.any(-1, keepdim=True), pr, torch.zeros_like(pr))       # rows that see nothing give zeros
         out[s:e] = (pr @ vf).transpose(0, 1).to(out.dtype)
     return out
+
+
+def sparse24_dequant(codes, meta, scales, in_f: int, group_size: int) -> torch.Tensor:
+    """Dense fp32 ``[out, in]`` matrix of a 2:4 sparse FP4 weight: ``codes uint8 [out, in / 4]`` (two E2M1 codes per byte, low
+    nibble first: the kept values of one group of four columns), ``meta uint8 [out, in / 8]`` (one nibble per group, low nibble
+    first: bits 0-1 column of the first kept value, bits 2-3 of the second), ``scales fp16 [out, in / group_size]``."""
+    from .._compat import get_e2m1_torch_table
+    out_f = codes.shape[0]
+    tab = get_e2m1_torch_table(codes.device, torch.float32)
+    c = codes.long()
+    vals = torch.stack([tab[c & 15], tab[c >> 4]], -1)                       # [out, in / 4, 2]
+    m = meta.long()
+    nib = torch.stack([m & 15, m >> 4], -1).reshape(out_f, in_f // 4)          # [out, groups]
+    pos = torch.stack([nib & 3, nib >> 2], -1)                                  # [out, groups, 2]
+    dense = torch.zeros(out_f, in_f // 4, 4, dtype=torch.float32, device=codes.device)
+    dense.scatter_(2, pos, vals)
+    dense = dense.view(out_f, in_f)
+    return dense * scales.to(torch.float32).repeat_interleave(group_size, 1)

@@ -112,3 +112,35 @@ def test_gqa_prompt_pass_with_tensor_core_attention_matches_reference():
         b = prefill(lm.model, lm.new_cache(48, 16), prompts, bt)
     assert ops.check_status(torch.device(DEV)) == 0
     assert float((a - b).abs().max() / b.abs().max()) < 4e-2
+
+
+def test_gqa_batch_of_long_prompts_runs_the_tensor_core_attention_per_sequence():
+    """Several long prompts in one pass: the tcgen05 kernel is launched once per sequence and layer (not the mma.sync kernel for
+    the whole batch); a short prompt in the batch sends the pass back to the batched kernel."""
+    import dataclasses
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM, prefill
+    cfg = dataclasses.replace(get_preset("tiny-qwen3-moe"), head_dim=128, num_attention_heads=4, num_key_value_heads=2, hidden_size=512)
+    lm = MMFP4ForCausalLM.from_config(cfg, device="cuda", seed=4)
+    prompts = [torch.randint(0, 512, (n,)).tolist() for n in (600, 257, 431)]
+    bt = torch.arange(3 * 48, dtype=torch.int32).view(3, 48)
+    calls = {"n": 0}
+    real = ops.fmha_prefill
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+    ops.fmha_prefill = counting
+    try:
+        a = prefill(lm.model, lm.new_cache(3 * 48, 16), prompts, bt)
+        assert calls["n"] == 3 * cfg.num_hidden_layers
+        calls["n"] = 0
+        mixed = prefill(lm.model, lm.new_cache(3 * 48, 16), prompts[:2] + [[5, 6, 7]], bt)
+        assert calls["n"] == 0 and torch.isfinite(mixed).all()
+    finally:
+        ops.fmha_prefill = real
+    with ops.force_reference():
+        b = prefill(lm.model, lm.new_cache(3 * 48, 16), prompts, bt)
+    assert ops.check_status(torch.device(DEV)) == 0
+    assert float((a - b).abs().max() / b.abs().max()) < 4e-2
