@@ -25,7 +25,8 @@ def _reg(module: str, *names: str, **aliases: str) -> None:
 
 _reg("._compat", "E2M1_VALUES", "NF4_VALUES")
 _reg(".dtypes", "DTypeConfig", "get_dtype_config", "to_torch_dtype")
-_reg(".inference.pipeline", "MMFP4Pipeline", "StreamingOutput", MarlinPipeline="MMFP4Pipeline")
+_reg(".inference.pipeline", "MMFP4Pipeline", "MarlinPipeline", "StreamingOutput")
+_reg(".models.mmfp4_causal_lm", MetalMarlinModel="MMFP4ForCausalLM")
 _reg(".models.mmfp4_causal_lm", "MMFP4ForCausalLM", "prefill")
 _reg(".models.config", "ModelConfig", "get_preset")
 _reg(".models.transformer", "Transformer", "PagedKVStorage", "BatchMeta")

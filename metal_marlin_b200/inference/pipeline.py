@@ -344,4 +344,30 @@ class MMFP4Pipeline:
 
 
 # the dense marlin_fp4 pipeline of the reference is the same object here
-MarlinPipeline = MMFP4Pipeline
+class MarlinPipeline(MMFP4Pipeline):
+    """The generic pipeline surface over the same engine: ``from_pretrained(path, quant_type=...)`` for dense ``marlin_fp4`` /
+    MMFP4 checkpoints, ``__call__``, ``stream_generate`` / ``generate_stream`` (text chunks), ``generate_batch``, ``chat`` and
+    ``info()``.  Parity: reference ``metal_marlin/inference/pipeline.py:835`` (``MarlinPipeline``), ``:901`` (``__call__``),
+    ``:918`` (``stream_generate``), ``:932`` (``info``), ``metal_marlin/inference/pipeline_v2.py`` (``TransformersMarlinPipeline``)."""
+
+    @classmethod
+    def from_pretrained(cls, path: str, quant_type: str = "fp4", device: Optional[str] = None, **kw):
+        if quant_type not in ("fp4", "mmfp4", "marlin_fp4"):
+            import warnings
+            warnings.warn(f"quant_type={quant_type!r}: checkpoints are read in the format they were written in", UserWarning, stacklevel=2)
+        return super().from_pretrained(path, device=device, **kw)
+
+    def stream_generate(self, prompt: str, max_tokens: int = 64, **kw) -> Iterator[str]:
+        for chunk in self.stream(prompt, max_new_tokens=max_tokens, **kw):
+            if chunk.text:
+                yield chunk.text
+
+    generate_stream = stream_generate
+
+    def info(self) -> Dict[str, object]:
+        cfg = self.config
+        m = self.model.model
+        return {"model_type": cfg.model_type, "num_layers": cfg.num_hidden_layers, "hidden_size": cfg.hidden_size,
+                "vocab_size": cfg.vocab_size, "num_attention_heads": cfg.num_attention_heads, "num_experts": getattr(cfg, "num_experts", 0) or 0,
+                "attention": "mla" if cfg.is_mla else "gqa", "quant_format": getattr(cfg, "quant_format", "mmfp4"), "group_size": cfg.group_size,
+                "weight_bytes": int(m.weight_bytes()), "device": str(self.device), "max_model_len": self.engine.cfg.max_model_len}

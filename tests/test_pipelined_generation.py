@@ -64,3 +64,19 @@ def test_prompt_passes_overlap_decode_steps_on_the_gpu():
     assert sched.overlap
     agree = sum(res[r][0, len(p):].tolist() == w for r, p, w in zip(rids, prompts, want))
     assert agree >= 3                     # batch-4 and batch-1 decode kernels may differ in the last bit of a near-tie
+
+
+def test_generic_pipeline_surface():
+    """``MarlinPipeline``: call, text-chunk streaming, batch generation and model info over the same engine."""
+    import metal_marlin_b200 as mm
+    pipe = mm.MarlinPipeline.from_config("tiny-llama", device="cpu")
+    try:
+        text = pipe("hello world", max_new_tokens=6)
+        chunks = list(pipe.stream_generate("hello world", max_tokens=6))
+        assert "".join(chunks) == text and list(pipe.generate_stream("hello world", max_tokens=6)) == chunks
+        assert pipe.generate_batch(["hello world", "b"], 6)[0] == text
+        info = pipe.info()
+        assert info["num_layers"] == 2 and info["attention"] == "gqa" and info["weight_bytes"] > 0 and info["device"] == "cpu"
+        assert isinstance(pipe, mm.MMFP4Pipeline) and mm.MetalMarlinModel is mm.MMFP4ForCausalLM
+    finally:
+        pipe.close()
