@@ -128,12 +128,15 @@ class _DecodeBucket:
         split = getattr(self.model, "tp", None) is not None and self.model.tp.tp > 1
         if self.use_graph:
             if self.graph is None:
+                rec = self.kv.snapshot_recurrent() if hasattr(self.kv, "snapshot_recurrent") else None
                 s = torch.cuda.Stream(device=self.dev)
                 s.wait_stream(torch.cuda.current_stream(self.dev))
                 with torch.cuda.stream(s):
                     self._body()
                 torch.cuda.current_stream(self.dev).wait_stream(s)
                 torch.cuda.synchronize(self.dev)
+                if rec is not None:
+                    self.kv.restore_recurrent(rec)      # the warm-up pass advanced the recurrent states
                 self.step_no.zero_()            # the warm-up pass must not advance the random stream
                 self.graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(self.graph):
@@ -178,6 +181,12 @@ class LLMEngine:
         self._tracked: Dict[str, RunningRequest] = {}
         self._filler_block: Optional[int] = None
         c = self.cfg
+        self.recurrent = bool(getattr(model.cfg, "has_linear_layers", False))
+        if self.recurrent and c.enable_prefix_cache:
+            # the recurrent state of a sequence is addressed by its first cache block and cannot be shared or truncated:
+            # no prefix sharing (and no speculative roll-back, see enable_speculative) for hybrid stacks
+            import dataclasses
+            c = self.cfg = dataclasses.replace(c, enable_prefix_cache=False)
         self.kv = PagedKVStorage(model.cfg, c.num_kv_blocks, c.block_size, model.device, kv_dtype=c.kv_cache_dtype)
         self.cache = PagedKVCache(c.num_kv_blocks, c.block_size, enable_prefix_cache=c.enable_prefix_cache,
                                   copy_fn=self._copy_block)
@@ -382,6 +391,9 @@ class LLMEngine:
         the drafts of the whole batch (k + 1 positions per sequence, paged attention over each sequence's own context),
         accepted tokens are kept, the cache rows of rejected ones are given back.  Requests that sample with a temperature
         use rejection sampling against the draft distribution where the draft provides one, else fall back to one token."""
+        if getattr(self, "recurrent", False):
+            raise ValueError("speculative decoding needs a cache that can be rolled back; recurrent (linear attention) layers keep a state "
+                             "that cannot")
         from ..spec.adaptive import AdaptiveSpeculationController
         from ..spec.draft import DraftModel, NGramDraft, SmallModelDraft
         if draft == "ngram":

@@ -132,6 +132,7 @@ class DecodeSession:
         if self.device.type != "cuda":
             return
         saved = [t.clone() for t in (self.ids, self.positions, self.slots, self.ctx_lens, self.step_idx, self.history)]
+        rec = self.kv.snapshot_recurrent() if hasattr(self.kv, "snapshot_recurrent") else None
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
@@ -141,6 +142,8 @@ class DecodeSession:
         torch.cuda.synchronize(self.device)
         for dst, src in zip((self.ids, self.positions, self.slots, self.ctx_lens, self.step_idx, self.history), saved):
             dst.copy_(src)
+        if rec is not None:
+            self.kv.restore_recurrent(rec)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             self._step_body()

@@ -136,7 +136,25 @@ def build_layer(cfg: ModelConfig, src, i: int) -> LayerWeights:
     L = LayerWeights(input_norm=src.norm(f"{p}.input_layernorm.weight", H),
                      post_norm=src.norm(f"{p}.post_attention_layernorm.weight", H))
     a = f"{p}.self_attn"
-    if cfg.is_mla:
+    if cfg.layer_is_linear(i):
+        la = f"{p}.linear_attn"
+        Hk, Hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        kd, vd = Hk * dk, Hv * dv
+        if (2 * Hv) % 16 or kd % 16 or vd % 16:
+            raise ValueError("linear attention: 2 x value heads and the key / value widths must be multiples of 16 (weight tile rows)")
+        if isinstance(src, RandomSource) or src.has(f"{la}.in_proj_q.weight"):
+            L.lin_in = src.linear_cat([f"{la}.in_proj_q", f"{la}.in_proj_k", f"{la}.in_proj_v", f"{la}.in_proj_z", f"{la}.in_proj_ba"],
+                                      [kd, kd, vd, vd, 2 * Hv], H)
+        else:
+            raise ValueError(f"{la}: the checkpoint must store the input projection as in_proj_q / _k / _v / _z / _ba (rows in that "
+                             "order); interleaved in_proj_qkvz tensors are split by the converter")
+        L.lin_conv = src.float(f"{la}.conv1d.weight", 2 * kd + vd, cfg.linear_conv_kernel_dim, std=0.2).to(torch.float32) \
+            .reshape(2 * kd + vd, cfg.linear_conv_kernel_dim).contiguous()          # checkpoints hold [C, 1, K]
+        L.lin_dt_bias = src.float(f"{la}.dt_bias", Hv, std=0.5).to(torch.float32)
+        L.lin_A_log = src.float(f"{la}.A_log", Hv, std=0.5).to(torch.float32)
+        L.lin_norm = src.norm(f"{la}.norm.weight", dv)
+        L.lin_out = src.linear(f"{la}.out_proj", H, vd)
+    elif cfg.is_mla:
         nh, dn, dr, dv, R = cfg.num_attention_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         if cfg.q_lora_rank:
             L.qa_kva = src.linear_cat([f"{a}.q_a_proj", f"{a}.kv_a_proj_with_mqa"], [cfg.q_lora_rank, R + dr], H)

@@ -96,6 +96,14 @@ class LayerWeights:
     router_bias: Optional[torch.Tensor] = None
     gate_up_bank: Optional[FP4ExpertBank] = None
     down_bank: Optional[FP4ExpertBank] = None
+    # Gated DeltaNet (linear attention) mixer of hybrid stacks: in_proj rows [q | k | v | z | b | a], depthwise causal conv over
+    # [q | k | v] (weights [C, K]), per-value-head decay parameters, gated RMSNorm weight [dv], out_proj
+    lin_in: Optional[FP4Weight] = None
+    lin_conv: Optional[torch.Tensor] = None
+    lin_dt_bias: Optional[torch.Tensor] = None
+    lin_A_log: Optional[torch.Tensor] = None
+    lin_norm: Optional[torch.Tensor] = None
+    lin_out: Optional[FP4Weight] = None
     # expert parallelism inside a tensor-parallel group: this rank's range of whole routed experts (0 = experts are width-sliced)
     ep_first: int = 0
     ep_local: int = 0
@@ -130,6 +138,18 @@ class PagedKVStorage:
         n_slots = num_blocks * block_size
         L = cfg.num_hidden_layers
         assert kv_dtype == "bf16" or kv_dtype in ops.KV_FORMATS, kv_dtype
+        # hybrid stacks: recurrent (Gated DeltaNet) layers keep, per sequence, a convolution window and a state matrix instead
+        # of cached keys.  The pools run parallel to the block pool and are addressed by the FIRST block of a sequence's block
+        # table (unique among live sequences as long as blocks are not shared, which is why prefix sharing is off for them).
+        self.rec = [None] * L
+        if cfg.has_linear_layers:
+            kd, vd = cfg.linear_num_key_heads * cfg.linear_key_head_dim, cfg.linear_num_value_heads * cfg.linear_value_head_dim
+            for i in range(L):
+                if cfg.layer_is_linear(i):
+                    # one entry more than blocks: rows of a padded decode batch (slot -1) park their state there
+                    self.rec[i] = (torch.zeros(num_blocks + 1, 2 * kd + vd, cfg.linear_conv_kernel_dim - 1, dtype=torch.float32, device=device),
+                                   torch.zeros(num_blocks + 1, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim,
+                                               dtype=torch.float32, device=device))
         if kv_dtype != "bf16":
             if cfg.is_mla:
                 self.k = [ops.FP8KV(n_slots, (cfg.latent_dim,), device, kv_dtype) for _ in range(L)]
@@ -141,8 +161,25 @@ class PagedKVStorage:
             self.k = [torch.zeros(n_slots, cfg.latent_dim, dtype=dtype, device=device) for _ in range(L)]
             self.v = [None] * L
         else:
-            self.k = [torch.zeros(n_slots, cfg.num_key_value_heads, cfg.dh, dtype=dtype, device=device) for _ in range(L)]
-            self.v = [torch.zeros(n_slots, cfg.num_key_value_heads, cfg.dh, dtype=dtype, device=device) for _ in range(L)]
+            lin = [cfg.layer_is_linear(i) for i in range(L)]
+            self.k = [None if lin[i] else torch.zeros(n_slots, cfg.num_key_value_heads, cfg.dh, dtype=dtype, device=device) for i in range(L)]
+            self.v = [None if lin[i] else torch.zeros(n_slots, cfg.num_key_value_heads, cfg.dh, dtype=dtype, device=device) for i in range(L)]
+
+    def snapshot_recurrent(self):
+        """Copies of the recurrent-state pools (``None`` for a pure attention model).  A warm-up pass in front of a graph
+        capture advances them - unlike cache rows, which a repeated pass rewrites with the same values - so the capture code
+        restores them afterwards."""
+        if not any(r is not None for r in self.rec):
+            return None
+        return [None if r is None else (r[0].clone(), r[1].clone()) for r in self.rec]
+
+    def restore_recurrent(self, snap) -> None:
+        if snap is None:
+            return
+        for r, s in zip(self.rec, snap):
+            if r is not None:
+                r[0].copy_(s[0])
+                r[1].copy_(s[1])
 
     def bytes_per_token(self) -> int:
         cfg = self.cfg
@@ -339,6 +376,70 @@ class Transformer:
             out[s:e] = o.squeeze(0).transpose(0, 1).reshape(t, Hq * D)
         return out
 
+    def _attn_deltanet(self, L: LayerWeights, li: int, h, d, kv: PagedKVStorage, meta: BatchMeta):
+        """Gated DeltaNet mixer (linear attention with the gated delta rule): ``in_proj -> causal depthwise conv + SiLU on
+        [q | k | v] -> L2-normalised q, k -> S <- S exp(g) + k ((v - S^T k) beta)^T, o = S^T q -> RMSNorm(o) * silu(z) ->
+        out_proj``.  The convolution window and the state matrix of every sequence live in ``kv.rec[li]`` at the index of
+        the sequence's first cache block.  Prompt passes run the sequence-scan kernel per sequence (carrying the state from
+        earlier chunks), decode steps the single-step kernel on the batch.  Parity: reference
+        ``metal_marlin/kernels/qwen36_27b.py`` / ``src/qwen36_27b_decode.metal`` (DeltaNet decode path) and the DeltaNet
+        fields of ``metal_marlin/trellis/config.py:75``."""
+        from ..arch.deltanet import gated_delta_rule_chunked, gated_delta_step, l2norm
+        cfg = self.cfg
+        Hk, Hv, dk, dv, Kc = (cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim,
+                              cfg.linear_conv_kernel_dim)
+        kd, vd = Hk * dk, Hv * dv
+        T = h.shape[0]
+        proj, h = self._norm_linear(h, d, L.lin_in, L.input_norm)
+        pf = proj.to(torch.float32)
+        qkv, z, b, a = pf[:, : 2 * kd + vd], pf[:, 2 * kd + vd: 2 * kd + 2 * vd], pf[:, 2 * kd + 2 * vd: 2 * kd + 2 * vd + Hv], pf[:, 2 * kd + 2 * vd + Hv:]
+        beta = torch.sigmoid(b)
+        g = -torch.exp(L.lin_A_log.float()) * F.softplus(a + L.lin_dt_bias.float())
+        conv_pool, state_pool = kv.rec[li]
+        w = L.lin_conv.float()                                     # [C, Kc]
+        first = meta.block_tables[:, 0].long()                     # pool index of every sequence
+        if meta.decode:                                            # padding rows of a bucketed batch must not touch a live state
+            first = torch.where(meta.slots >= 0, first, torch.full_like(first, conv_pool.shape[0] - 1))
+        rep = Hv // Hk
+
+        def heads(x_conv):
+            q = l2norm(x_conv[..., :kd].reshape(*x_conv.shape[:-1], Hk, dk))
+            k = l2norm(x_conv[..., kd: 2 * kd].reshape(*x_conv.shape[:-1], Hk, dk))
+            v = x_conv[..., 2 * kd:].reshape(*x_conv.shape[:-1], Hv, dv)
+            if rep > 1:
+                q, k = q.repeat_interleave(rep, -2), k.repeat_interleave(rep, -2)
+            return q, k, v
+
+        if meta.decode:
+            win = torch.cat([conv_pool.index_select(0, first), qkv.unsqueeze(-1)], -1)            # [B, C, Kc]
+            xc = F.silu((win * w).sum(-1))
+            conv_pool.index_copy_(0, first, win[..., 1:].contiguous())
+            q, k, v = heads(xc)
+            S = state_pool.index_select(0, first)
+            o = gated_delta_step(q, k, v, g, beta, S, scale=dk ** -0.5).to(torch.float32)           # [B, Hv, dv]
+            state_pool.index_copy_(0, first, S)
+        else:
+            o = torch.empty(T, Hv, dv, dtype=torch.float32, device=h.device)
+            for bi in range(len(meta.cu_seqlens) - 1):
+                s0, e0 = meta.cu_seqlens[bi], meta.cu_seqlens[bi + 1]
+                t = e0 - s0
+                idx = first[bi: bi + 1]
+                fresh = int(meta.ctx_lens_host[bi]) == t                                            # the sequence starts in this pass
+                hist = torch.zeros(1, 2 * kd + vd, Kc - 1, device=h.device) if fresh else conv_pool.index_select(0, idx)
+                xin = torch.cat([hist[0], qkv[s0:e0].t()], -1)                                      # [C, Kc - 1 + t]
+                xc = F.silu(F.conv1d(xin.unsqueeze(0), w.unsqueeze(1), groups=w.shape[0])[0].t())   # [t, C]
+                conv_pool.index_copy_(0, idx, xin[:, -(Kc - 1):].unsqueeze(0).contiguous())
+                q, k, v = heads(xc)
+                S0 = None if fresh else state_pool.index_select(0, idx)
+                os_, S = gated_delta_rule_chunked(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), g[s0:e0].unsqueeze(0), beta[s0:e0].unsqueeze(0),
+                                                  S0, scale=dk ** -0.5)
+                o[s0:e0] = os_[0].float()
+                state_pool.index_copy_(0, idx, S.float())
+        # gated RMSNorm per value head, then the output projection (the result is the pending residual delta)
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * L.lin_norm.float()
+        o = (o * F.silu(z.reshape(T, Hv, dv))).reshape(T, vd).to(torch.bfloat16)
+        return h, ops.linear(o, L.lin_out)
+
     def _attn_mla(self, L: LayerWeights, li: int, h, d, kv: PagedKVStorage, meta: BatchMeta):
         cfg = self.cfg
         H, dn, dr, dv, R = self.n_heads_local, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
@@ -510,7 +611,9 @@ class Transformer:
         h = ops.embedding(self.embed, input_ids)
         d = None
         for li, L in enumerate(self.layers):
-            if self.cfg.is_mla:
+            if L.lin_in is not None:
+                h, d = self._attn_deltanet(L, li, h, d, kv, meta)
+            elif self.cfg.is_mla:
                 h, d = self._attn_mla(L, li, h, d, kv, meta)
             else:
                 h, d = self._attn_gqa(L, li, h, d, kv, meta)

@@ -437,6 +437,8 @@ def shard_transformer(model: Transformer, rank: int, tp: int, ctx: Optional[TPCo
                       expert_parallel: bool = False) -> Transformer:
     """Build the rank's tensor-parallel shard of ``model`` (weights are sliced, not re-quantized)."""
     cfg = model.cfg
+    if getattr(cfg, "has_linear_layers", False):
+        raise NotImplementedError("tensor parallelism over Gated DeltaNet layers is not implemented (serve hybrid stacks with --dp)")
     layers, infos = [], []
     for L in model.layers:
         S, info = shard_layer(cfg, L, rank, tp, expert_parallel)

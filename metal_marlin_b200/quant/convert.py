@@ -177,7 +177,17 @@ def random_hf_state(cfg, seed: int = 0, std: float = 0.02) -> Dict[str, torch.Te
         sd[f"{p}.input_layernorm.weight"] = n(H)
         sd[f"{p}.post_attention_layernorm.weight"] = n(H)
         a = f"{p}.self_attn"
-        if cfg.is_mla:
+        if cfg.layer_is_linear(i):
+            la = f"{p}.linear_attn"
+            kd, vd, Hv = cfg.linear_num_key_heads * cfg.linear_key_head_dim, cfg.linear_num_value_heads * cfg.linear_value_head_dim, cfg.linear_num_value_heads
+            for nm, rows in (("in_proj_q", kd), ("in_proj_k", kd), ("in_proj_v", vd), ("in_proj_z", vd), ("in_proj_ba", 2 * Hv)):
+                sd[f"{la}.{nm}.weight"] = w(rows, H)
+            sd[f"{la}.conv1d.weight"] = (torch.randn(2 * kd + vd, 1, cfg.linear_conv_kernel_dim, generator=g) * 0.2).to(torch.bfloat16)
+            sd[f"{la}.dt_bias"] = torch.randn(Hv, generator=g) * 0.5
+            sd[f"{la}.A_log"] = torch.randn(Hv, generator=g) * 0.5
+            sd[f"{la}.norm.weight"] = n(cfg.linear_value_head_dim)
+            sd[f"{la}.out_proj.weight"] = w(H, vd)
+        elif cfg.is_mla:
             nh, dn, dr, dv, R = cfg.num_attention_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
             if cfg.q_lora_rank:
                 sd[f"{a}.q_a_proj.weight"] = w(cfg.q_lora_rank, H)
