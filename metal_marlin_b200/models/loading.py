@@ -136,7 +136,21 @@ def build_layer(cfg: ModelConfig, src, i: int) -> LayerWeights:
     L = LayerWeights(input_norm=src.norm(f"{p}.input_layernorm.weight", H),
                      post_norm=src.norm(f"{p}.post_attention_layernorm.weight", H))
     a = f"{p}.self_attn"
-    if cfg.layer_is_linear(i):
+    if cfg.layer_is_mamba(i):
+        mm = f"{p}.mamba"
+        Di, N, r = cfg.mamba_d_inner, cfg.mamba_d_state, cfg.mamba_rank
+        if Di % 16 or (r + 2 * N) % 16:
+            raise ValueError("mamba: the inner width and dt_rank + 2 * d_state must be multiples of 16 (weight tile rows)")
+        L.mamba_in = src.linear(f"{mm}.in_proj", 2 * Di, H)
+        L.mamba_conv = src.float(f"{mm}.conv1d.weight", Di, cfg.mamba_d_conv, std=0.2).to(torch.float32).reshape(Di, cfg.mamba_d_conv).contiguous()
+        L.mamba_conv_b = src.float(f"{mm}.conv1d.bias", Di, std=0.05).to(torch.float32)
+        L.mamba_x = src.linear(f"{mm}.x_proj", r + 2 * N, Di)
+        L.mamba_dt = src.float(f"{mm}.dt_proj.weight", Di, r, std=0.1).to(torch.float32)
+        L.mamba_dt_b = src.float(f"{mm}.dt_proj.bias", Di, std=0.5).to(torch.float32)
+        L.mamba_A_log = src.float(f"{mm}.A_log", Di, N, std=0.5).to(torch.float32)
+        L.mamba_D = src.float(f"{mm}.D", Di, std=0.5).to(torch.float32)
+        L.mamba_out = src.linear(f"{mm}.out_proj", H, Di)
+    elif cfg.layer_is_linear(i):
         la = f"{p}.linear_attn"
         Hk, Hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
         kd, vd = Hk * dk, Hv * dv

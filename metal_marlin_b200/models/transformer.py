@@ -104,6 +104,17 @@ class LayerWeights:
     lin_A_log: Optional[torch.Tensor] = None
     lin_norm: Optional[torch.Tensor] = None
     lin_out: Optional[FP4Weight] = None
+    # Mamba mixer of Jamba / Zamba style stacks: in_proj rows [x | z] (2 Di), depthwise causal conv [Di, K] + bias, x_proj rows
+    # [dt (rank) | B (N) | C (N)], dt_proj [Di, rank] + bias, A_log [Di, N], D [Di], out_proj [H, Di]
+    mamba_in: Optional[FP4Weight] = None
+    mamba_conv: Optional[torch.Tensor] = None
+    mamba_conv_b: Optional[torch.Tensor] = None
+    mamba_x: Optional[FP4Weight] = None
+    mamba_dt: Optional[torch.Tensor] = None
+    mamba_dt_b: Optional[torch.Tensor] = None
+    mamba_A_log: Optional[torch.Tensor] = None
+    mamba_D: Optional[torch.Tensor] = None
+    mamba_out: Optional[FP4Weight] = None
     # expert parallelism inside a tensor-parallel group: this rank's range of whole routed experts (0 = experts are width-sliced)
     ep_first: int = 0
     ep_local: int = 0
@@ -145,6 +156,9 @@ class PagedKVStorage:
         if cfg.has_linear_layers:
             kd, vd = cfg.linear_num_key_heads * cfg.linear_key_head_dim, cfg.linear_num_value_heads * cfg.linear_value_head_dim
             for i in range(L):
+                if cfg.layer_is_mamba(i):
+                    self.rec[i] = (torch.zeros(num_blocks + 1, cfg.mamba_d_inner, cfg.mamba_d_conv - 1, dtype=torch.float32, device=device),
+                                   torch.zeros(num_blocks + 1, cfg.mamba_d_inner, cfg.mamba_d_state, dtype=torch.float32, device=device))
                 if cfg.layer_is_linear(i):
                     # one entry more than blocks: rows of a padded decode batch (slot -1) park their state there
                     self.rec[i] = (torch.zeros(num_blocks + 1, 2 * kd + vd, cfg.linear_conv_kernel_dim - 1, dtype=torch.float32, device=device),
@@ -161,7 +175,7 @@ class PagedKVStorage:
             self.k = [torch.zeros(n_slots, cfg.latent_dim, dtype=dtype, device=device) for _ in range(L)]
             self.v = [None] * L
         else:
-            lin = [cfg.layer_is_linear(i) for i in range(L)]
+            lin = [cfg.layer_is_recurrent(i) for i in range(L)]
             self.k = [None if lin[i] else torch.zeros(n_slots, cfg.num_key_value_heads, cfg.dh, dtype=dtype, device=device) for i in range(L)]
             self.v = [None if lin[i] else torch.zeros(n_slots, cfg.num_key_value_heads, cfg.dh, dtype=dtype, device=device) for i in range(L)]
 
@@ -440,6 +454,58 @@ class Transformer:
         o = (o * F.silu(z.reshape(T, Hv, dv))).reshape(T, vd).to(torch.bfloat16)
         return h, ops.linear(o, L.lin_out)
 
+    def _attn_mamba(self, L: LayerWeights, li: int, h, d, kv: PagedKVStorage, meta: BatchMeta):
+        """Mamba mixer (selective state space): ``in_proj -> [x | z]``, causal depthwise conv + SiLU on x, ``x_proj -> dt, B, C``,
+        ``h_t = exp(dt_t A) h_{t-1} + dt_t B_t x_t``, ``y_t = C_t h_t + D x_t``, ``y * silu(z) -> out_proj``.  Convolution window and
+        state per sequence live in ``kv.rec[li]`` like the DeltaNet state; prompt passes run the selective-scan kernel per
+        sequence, decode steps the single-step kernel.  Parity: reference ``metal_marlin/architectures/mamba.py``,
+        ``src/mamba_ssm.metal:204``."""
+        from ..arch.mamba import selective_scan, selective_scan_step
+        cfg = self.cfg
+        Di, N, r, Kc = cfg.mamba_d_inner, cfg.mamba_d_state, cfg.mamba_rank, cfg.mamba_d_conv
+        T = h.shape[0]
+        xz, h = self._norm_linear(h, d, L.mamba_in, L.input_norm)
+        xz = xz.to(torch.float32)
+        x, z = xz[:, :Di], xz[:, Di:]
+        conv_pool, state_pool = kv.rec[li]
+        w, wb = L.mamba_conv.float(), L.mamba_conv_b.float()
+        A = -torch.exp(L.mamba_A_log.float())
+        first = meta.block_tables[:, 0].long()
+        if meta.decode:
+            first = torch.where(meta.slots >= 0, first, torch.full_like(first, conv_pool.shape[0] - 1))
+
+        def ssm_inputs(xc):
+            proj = ops.linear(xc.to(torch.bfloat16).contiguous(), L.mamba_x).to(torch.float32)
+            dt = F.softplus(proj[:, :r] @ L.mamba_dt.float().t() + L.mamba_dt_b.float())
+            return dt, proj[:, r: r + N], proj[:, r + N: r + 2 * N]
+
+        if meta.decode:
+            win = torch.cat([conv_pool.index_select(0, first), x.unsqueeze(-1)], -1)              # [B, Di, Kc]
+            xc = F.silu((win * w).sum(-1) + wb)
+            conv_pool.index_copy_(0, first, win[..., 1:].contiguous())
+            dt, Bm, Cm = ssm_inputs(xc)
+            S = state_pool.index_select(0, first)
+            y = selective_scan_step(xc, dt, A, Bm, Cm, L.mamba_D.float(), S).to(torch.float32)
+            state_pool.index_copy_(0, first, S)
+        else:
+            y = torch.empty(T, Di, dtype=torch.float32, device=h.device)
+            for bi in range(len(meta.cu_seqlens) - 1):
+                s0, e0 = meta.cu_seqlens[bi], meta.cu_seqlens[bi + 1]
+                t = e0 - s0
+                idx = first[bi: bi + 1]
+                fresh = int(meta.ctx_lens_host[bi]) == t
+                hist = torch.zeros(1, Di, Kc - 1, device=h.device) if fresh else conv_pool.index_select(0, idx)
+                xin = torch.cat([hist[0], x[s0:e0].t()], -1)
+                xc = F.silu(F.conv1d(xin.unsqueeze(0), w.unsqueeze(1), wb, groups=Di)[0].t())          # [t, Di]
+                conv_pool.index_copy_(0, idx, xin[:, -(Kc - 1):].unsqueeze(0).contiguous())
+                dt, Bm, Cm = ssm_inputs(xc)
+                S0 = None if fresh else state_pool.index_select(0, idx)
+                ys, S = selective_scan(xc.unsqueeze(0), dt.unsqueeze(0), A, Bm.unsqueeze(0), Cm.unsqueeze(0), L.mamba_D.float(), S0)
+                y[s0:e0] = ys[0].float()
+                state_pool.index_copy_(0, idx, S.float())
+        y = (y * F.silu(z)).to(torch.bfloat16)
+        return h, ops.linear(y, L.mamba_out)
+
     def _attn_mla(self, L: LayerWeights, li: int, h, d, kv: PagedKVStorage, meta: BatchMeta):
         cfg = self.cfg
         H, dn, dr, dv, R = self.n_heads_local, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
@@ -613,6 +679,8 @@ class Transformer:
         for li, L in enumerate(self.layers):
             if L.lin_in is not None:
                 h, d = self._attn_deltanet(L, li, h, d, kv, meta)
+            elif L.mamba_in is not None:
+                h, d = self._attn_mamba(L, li, h, d, kv, meta)
             elif self.cfg.is_mla:
                 h, d = self._attn_mla(L, li, h, d, kv, meta)
             else:

@@ -20,7 +20,7 @@ import torch
 from ..formats import fp4 as fp4fmt
 from ..formats.safetensors_io import SafetensorsFile, save_file
 
-SKIP_PATTERNS = ("embed", "norm", "lm_head", "shared_head.head", "output", "bias")      # vocabulary heads (also those of MTP modules) stay bf16
+SKIP_PATTERNS = ("embed", "norm", "lm_head", "shared_head.head", "output", "bias", "dt_proj", "a_log")      # vocabulary heads (also those of MTP modules) stay bf16
 COPY_FILES = ("config.json", "tokenizer.json", "tokenizer_config.json", "tokenizer.model", "special_tokens_map.json",
               "generation_config.json", "vocab.json", "merges.txt", "chat_template.jinja")
 
@@ -177,7 +177,19 @@ def random_hf_state(cfg, seed: int = 0, std: float = 0.02) -> Dict[str, torch.Te
         sd[f"{p}.input_layernorm.weight"] = n(H)
         sd[f"{p}.post_attention_layernorm.weight"] = n(H)
         a = f"{p}.self_attn"
-        if cfg.layer_is_linear(i):
+        if cfg.layer_is_mamba(i):
+            mm = f"{p}.mamba"
+            Di, N, r = cfg.mamba_d_inner, cfg.mamba_d_state, cfg.mamba_rank
+            sd[f"{mm}.in_proj.weight"] = w(2 * Di, H)
+            sd[f"{mm}.conv1d.weight"] = (torch.randn(Di, 1, cfg.mamba_d_conv, generator=g) * 0.2).to(torch.bfloat16)
+            sd[f"{mm}.conv1d.bias"] = torch.randn(Di, generator=g) * 0.05
+            sd[f"{mm}.x_proj.weight"] = w(r + 2 * N, Di)
+            sd[f"{mm}.dt_proj.weight"] = torch.randn(Di, r, generator=g) * 0.1
+            sd[f"{mm}.dt_proj.bias"] = torch.randn(Di, generator=g) * 0.5
+            sd[f"{mm}.A_log"] = torch.randn(Di, N, generator=g) * 0.5
+            sd[f"{mm}.D"] = torch.randn(Di, generator=g) * 0.5
+            sd[f"{mm}.out_proj.weight"] = w(H, Di)
+        elif cfg.layer_is_linear(i):
             la = f"{p}.linear_attn"
             kd, vd, Hv = cfg.linear_num_key_heads * cfg.linear_key_head_dim, cfg.linear_num_value_heads * cfg.linear_value_head_dim, cfg.linear_num_value_heads
             for nm, rows in (("in_proj_q", kd), ("in_proj_k", kd), ("in_proj_v", vd), ("in_proj_z", vd), ("in_proj_ba", 2 * Hv)):
