@@ -182,6 +182,9 @@ def reference_arm(args):
 def main():
     args = _args()
     if args.impl == "reference":
+        # the reference is a single-device program: under a multi-rank launch only rank 0 runs it and prints the line
+        if int(os.environ.get("RANK", "0")) != 0:
+            return 0
         return reference_arm(args)
 
     import torch

@@ -12,6 +12,20 @@ extern "C" {
 // row of x bf16 [rows, dim]; out may alias x.
 int mmb_hadamard(const void* x, void* out, int rows, int dim, int block, cudaStream_t stream);
 
+// GPTQ over one lazy block of columns [i1, i1 + B), B <= 128: for every row and every column in order, quantize
+// W[r, c] to grid[k] * col_scale[r, c] (nearest grid value, ties to the lower one; grid sorted, 2..256 values), store it in
+// Q, store err = (w - q) / Hinv[c, c] in E [out_f, B] and subtract err * Hinv[c, c'] from the later columns c' of the
+// block.  W, Q, col_scale fp32 with row stride ldw; Hinv fp32 upper Cholesky factor of the inverse Hessian, row stride ldh;
+// err_rows fp32 [out_f] accumulates the squared quantization error of each row.  Plain fp32 roundings, no fused
+// multiply-add, so the result equals the PyTorch loop bit for bit.
+int mmb_gptq_block(float* W, float* Q, float* E, const float* Hinv, const float* col_scale, const float* grid,
+                   float* err_rows, int n_grid, int out_f, long ldw, long ldh, int i1, int B, cudaStream_t stream);
+// Round-to-nearest E2M1 quantization of w [out_f, in_f] (fp32, or bf16 when w_is_bf16) with one fp16 scale = absmax / 6
+// per group of group_size (8..128, a power of two) input columns, packed eight codes per word along the input axis:
+// packed uint32 [out_f, in_f / 8], scales fp16 [out_f, in_f / group_size].
+int mmb_fp4_quantize_pack(const void* w, int w_is_bf16, uint32_t* packed, void* scales, long out_f, int in_f, int group_size,
+                          cudaStream_t stream);
+
 // Trellis weights.  `codes`: the 16x16-tile bit stream without its header byte ([tiles_out][tiles_in][32 * bits]
 // bytes, codes LSB first, code index local_out * 16 + local_in); scales fp32 [n_groups, out]; su fp32 [in];
 // sv fp32 [out].  W[o, i] = (code - (2^bits - 1) / 2) * 1.24371088 * scales[i / gs, o] * sv[o] * su[i].
@@ -214,6 +228,7 @@ typedef struct {
   int t, n, n_pad, Hq, Hk, D;
   long long q_tok_stride, q_head_stride, k_tok_stride, k_head_stride, o_tok_stride, o_head_stride;
   float scale;
+  int window;             // 0 = none; > 0: query position x sees the keys (x - window, x]
   int* status;            // device int: 31..36 after a bounded wait expired (producer, mma, softmax stages)
 } MmbFmhaPrefillParams;
 int mmb_fmha_prefill(const MmbFmhaPrefillParams* p, cudaStream_t stream);

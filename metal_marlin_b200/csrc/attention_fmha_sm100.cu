@@ -1,4 +1,4 @@
-// Causal prefill attention on the tcgen05 tensor cores.
+// Causal prefill attention (optionally with a sliding window) on the tcgen05 tensor cores.
 //
 // One CTA owns 128 query rows of one head and walks the keys in tiles of KT (64 at head size 256, 128 at head size 128):
 //   warp 0      TMA producer: Q once, then per tile the K rows [KT keys x D] and the V^T block [D x KT keys] into a
@@ -77,7 +77,11 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;       // all heads' tiles with the most keys start first
   const int q0 = qt * 128, h = blockIdx.x, hk = h / (p.Hq / p.Hk);
   const int q_off = p.n - p.t;
-  const int nt = (q_off + min(q0 + 127, p.t - 1)) / KT + 1;    // key tiles this query tile can see
+  // sliding window: a query at position x sees the keys (x - window, x]; tiles wholly in front of the first row's window
+  // are never loaded, and tile numbers below count from the first visited tile j0
+  const int win = p.window;
+  const int j0 = win > 0 ? max(0, q_off + q0 - win + 1) / KT : 0;
+  const int nt = (q_off + min(q0 + 127, p.t - 1)) / KT + 1 - j0;    // key tiles this query tile can see
   int* status = p.status;
   if ((smem_u32(smem_fm) & 1023u) != 0u) {      // no room for alignment slack: refuse rather than mis-address the tiles
     if (tid == 0 && status) atomicExch(status, 42);
@@ -126,14 +130,14 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
         mbar_expect_tx(&sh->k_full[s], Cfg::k_bytes);
         for (int kb = 0; kb < Cfg::KB; ++kb)
-          tma_load_3d(Ks + s * Cfg::k_bytes + kb * Cfg::k_blk, &tm_k, &sh->k_full[s], kb * 64, hk, j * KT);
+          tma_load_3d(Ks + s * Cfg::k_bytes + kb * Cfg::k_blk, &tm_k, &sh->k_full[s], kb * 64, hk, (j0 + j) * KT);
         if (j >= 2 && !mbar_wait(&sh->pv_done[s], ph(j - 2), abort_flag)) {     // V stage read by PV(j-2)
           fail(32);
           break;
         }
         mbar_expect_tx(&sh->v_full[s], Cfg::v_bytes);
         for (int kb = 0; kb < Cfg::NKB; ++kb)
-          tma_load_3d(Vs + s * Cfg::v_bytes + kb * Cfg::v_blk, &tm_v, &sh->v_full[s], j * KT + kb * 64, 0, hk);
+          tma_load_3d(Vs + s * Cfg::v_bytes + kb * Cfg::v_blk, &tm_v, &sh->v_full[s], (j0 + j) * KT + kb * 64, 0, hk);
       }
     }
   } else if (warp == 1) {
@@ -212,8 +216,8 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
       for (int cc = 0; cc < NC; ++cc) tmem_ld32(ts + (uint32_t)(cc * 32), v[cc]);
       tmem_ld_wait();
-      const int key0 = j * KT;
-      const bool need_mask = (key0 + KT - 1 > q_off + q0) || (key0 + KT > p.n);
+      const int key0 = (j0 + j) * KT;
+      const bool need_mask = (key0 + KT - 1 > q_off + q0) || (key0 + KT > p.n) || (win > 0 && key0 <= q_off + q0 + 127 - win);
       float mt = -INFINITY;
 #pragma unroll
       for (int cc = 0; cc < NC; ++cc)
@@ -222,7 +226,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           float x = __uint_as_float(v[cc][i]) * c;
           if (need_mask) {
             const int key = key0 + half * HC + cc * 32 + i;
-            if (key > my_pos || key >= p.n) x = -INFINITY;
+            if (key > my_pos || key >= p.n || (win > 0 && key <= my_pos - win)) x = -INFINITY;
           }
           v[cc][i] = __float_as_uint(x);
           mt = fmaxf(mt, x);
@@ -386,7 +390,7 @@ static int launch_fmha(const MmbFmhaPrefillParams& p, cudaStream_t stream) {
 MMB_API int mmb_fmha_prefill(const MmbFmhaPrefillParams* pp, cudaStream_t stream) {
   const MmbFmhaPrefillParams& p = *pp;
   if (p.t <= 0) return 0;
-  if (p.n < p.t || p.n_pad < p.n || p.n_pad % 8 != 0 || p.Hk < 1 || p.Hq % p.Hk != 0 || (p.D != 128 && p.D != 256)) return (int)cudaErrorInvalidValue;
+  if (p.window < 0 || p.n < p.t || p.n_pad < p.n || p.n_pad % 8 != 0 || p.Hk < 1 || p.Hq % p.Hk != 0 || (p.D != 128 && p.D != 256)) return (int)cudaErrorInvalidValue;
   if (p.q_tok_stride % 8 || p.q_head_stride % 8 || p.k_tok_stride % 8 || p.k_head_stride % 8 || p.o_tok_stride % 8 || p.o_head_stride % 8 ||
       (reinterpret_cast<uintptr_t>(p.out) & 15))
     return (int)cudaErrorInvalidValue;

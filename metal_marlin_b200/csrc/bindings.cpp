@@ -947,6 +947,33 @@ void hadamard(const Tensor& x, Tensor out, int64_t block) {
   check(mmb_hadamard(x.data_ptr(), out.data_ptr(), (int)(x.numel() / dim), dim, (int)block, cur_stream()), "hadamard");
 }
 
+void gptq_block(Tensor W, Tensor Q, Tensor E, const Tensor& Hinv, const Tensor& col_scale, const Tensor& grid, Tensor err_rows,
+                int64_t i1, int64_t B) {
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&W, &Q, &E, &Hinv, &col_scale, &grid, &err_rows})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat, "gptq_block: fp32 CUDA tensors expected");
+  TORCH_CHECK(W.dim() == 2 && W.stride(1) == 1 && Q.sizes() == W.sizes() && Q.stride(1) == 1 && Q.stride(0) == W.stride(0));
+  TORCH_CHECK(col_scale.sizes() == W.sizes() && col_scale.stride(1) == 1 && col_scale.stride(0) == W.stride(0));
+  TORCH_CHECK(Hinv.dim() == 2 && Hinv.stride(1) == 1 && Hinv.size(0) == W.size(1) && Hinv.size(1) == W.size(1));
+  TORCH_CHECK(i1 >= 0 && B >= 1 && i1 + B <= W.size(1));
+  TORCH_CHECK(E.is_contiguous() && E.size(0) == W.size(0) && E.size(1) == B && grid.is_contiguous());
+  TORCH_CHECK(err_rows.is_contiguous() && err_rows.numel() == W.size(0));
+  c10::cuda::CUDAGuard guard(W.device());
+  check(mmb_gptq_block(W.data_ptr<float>(), Q.data_ptr<float>(), E.data_ptr<float>(), Hinv.data_ptr<float>(),
+                       col_scale.data_ptr<float>(), grid.data_ptr<float>(), err_rows.data_ptr<float>(), (int)grid.numel(),
+                       (int)W.size(0), (long)W.stride(0), (long)Hinv.stride(0), (int)i1, (int)B, cur_stream()), "gptq_block");
+}
+
+void fp4_quantize_pack(const Tensor& w, Tensor packed, Tensor scales, int64_t group_size) {
+  TORCH_CHECK(w.is_cuda() && w.dim() == 2 && w.is_contiguous(), "fp4_quantize_pack: contiguous 2-D CUDA weight expected");
+  TORCH_CHECK(w.scalar_type() == at::kFloat || w.scalar_type() == at::kBFloat16, "fp4_quantize_pack: fp32 or bf16 weight");
+  TORCH_CHECK(w.size(1) % group_size == 0 && w.size(1) % 8 == 0);
+  TORCH_CHECK(packed.is_contiguous() && packed.scalar_type() == at::kInt && packed.numel() == w.numel() / 8);
+  TORCH_CHECK(scales.is_contiguous() && scales.scalar_type() == at::kHalf && scales.numel() == w.numel() / group_size);
+  c10::cuda::CUDAGuard guard(w.device());
+  check(mmb_fp4_quantize_pack(w.data_ptr(), w.scalar_type() == at::kBFloat16, (uint32_t*)packed.data_ptr(), scales.data_ptr(),
+                              (long)w.size(0), (int)w.size(1), (int)group_size, cur_stream()), "fp4_quantize_pack");
+}
+
 void trellis_dequant(const Tensor& codes, const Tensor& scales, const Tensor& su, const Tensor& sv, Tensor out, int64_t bits,
                      int64_t group_size) {
   TORCH_CHECK(codes.scalar_type() == at::kByte && codes.is_contiguous() && scales.scalar_type() == at::kFloat && scales.is_contiguous());
@@ -1312,7 +1339,8 @@ void moe_combine(const Tensor& y, const Tensor& inv, const OptT& add0, const Opt
 
 // Causal prefill attention of one sequence on the tcgen05 path.  q [t, Hq, D], k [n, Hk, D] (last dim contiguous),
 // vt [Hk, D, n_pad] contiguous, out [t, Hq, D]; status: device int tensor (first word receives a code after a timeout).
-void fmha_prefill(const Tensor& q, const Tensor& k, const Tensor& vt, Tensor out, int64_t n, double scale, Tensor status) {
+void fmha_prefill(const Tensor& q, const Tensor& k, const Tensor& vt, Tensor out, int64_t n, double scale, Tensor status,
+                  int64_t window) {
   check_bf16(q, "q");
   check_bf16(k, "k");
   check_bf16(vt, "vt");
@@ -1341,6 +1369,7 @@ void fmha_prefill(const Tensor& q, const Tensor& k, const Tensor& vt, Tensor out
   p.o_tok_stride = out.stride(0);
   p.o_head_stride = out.stride(1);
   p.scale = (float)scale;
+  p.window = (int)window;
   p.status = status.data_ptr<int>();
   check(mmb_fmha_prefill(&p, cur_stream()), "fmha_prefill");
 }
@@ -1451,6 +1480,8 @@ TORCH_LIBRARY(mmb200, m) {
   m.def("bf16_gemm_ag", &bf16_gemm_ag);
   m.def("tp_wait", &tp_wait);
   m.def("hadamard", &hadamard);
+  m.def("gptq_block", &gptq_block);
+  m.def("fp4_quantize_pack", &fp4_quantize_pack);
   m.def("trellis_dequant", &trellis_dequant);
   m.def("trellis_gemv", &trellis_gemv);
   m.def("trellis_moe", &trellis_moe);

@@ -134,6 +134,10 @@ def unpack_marlin_fp4(packed: torch.Tensor, scales: torch.Tensor) -> Tuple[torch
 def quantize_fp4(w: torch.Tensor, group_size: int = 128, layout: str = "marlin_fp4"):
     """One-call RTN quantizer returning tensors in a checkpoint layout."""
     gs = pick_group_size(w.shape[1], group_size)
+    if w.is_cuda and w.dim() == 2 and layout in ("marlin_fp4", "mmfp4"):
+        from .. import ops                      # one fused quantize + pack launch on the GPU, same bits
+        packed, scales = ops.fp4_quantize_pack(w, gs)
+        return (packed, scales, gs) if layout == "mmfp4" else (packed.t().contiguous(), scales.t().contiguous(), gs)
     codes, scales = quantize_codes(w, gs)
     if layout == "marlin_fp4":
         return (*pack_marlin_fp4(codes, scales), gs)

@@ -318,20 +318,28 @@ class Transformer:
         Hq, Hk, D = self.n_heads_local, self.n_kv_heads_local, cfg.dh
         out = torch.empty(q.shape[0], Hq * D, dtype=torch.bfloat16, device=q.device)
         bs = kv.block_size
-        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and len(meta.cu_seqlens) == 2 and not cfg.sliding_window
+        win = int(cfg.sliding_window or 0)
+
+        def _first_key(t, n_ctx):
+            # with a sliding window only the keys the chunk's first query can still see are gathered
+            return max(0, n_ctx - t - win + 1) if win else 0
+
+        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and len(meta.cu_seqlens) == 2
                 and not isinstance(kv.k[li], ops.FP8KV) and q.stride(2) == 1
                 and ops.fmha_ok(q.shape[0], int(meta.ctx_lens_host[0]), D, D, q.device)):
             # one long sequence: its cache rows (this chunk included) gathered once, then the tcgen05 attention kernel
             n_ctx = int(meta.ctx_lens_host[0])
+            lo = _first_key(q.shape[0], n_ctx)
 
-            def _slots(n_ctx=n_ctx):
-                tok = torch.arange(n_ctx, device=q.device)
+            def _slots(n_ctx=n_ctx, lo=lo):
+                tok = torch.arange(lo, n_ctx, device=q.device)
                 return meta.block_tables[0, tok // bs].long() * bs + tok % bs
-            slots = meta.cached(("slots", 0, n_ctx), _slots)
-            ops.fmha_prefill(q, kv.k[li].view(-1, Hk, D)[slots], kv.v[li].view(-1, Hk, D)[slots], out.view(-1, Hq, D), self.scale)
+            slots = meta.cached(("slots", 0, lo, n_ctx), _slots)
+            ops.fmha_prefill(q, kv.k[li].view(-1, Hk, D)[slots], kv.v[li].view(-1, Hk, D)[slots], out.view(-1, Hq, D), self.scale,
+                             window=win)
             return out
         n_seq = len(meta.cu_seqlens) - 1
-        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and n_seq > 1 and not cfg.sliding_window
+        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and n_seq > 1
                 and not isinstance(kv.k[li], ops.FP8KV) and q.stride(2) == 1
                 and all(ops.fmha_ok(meta.cu_seqlens[b + 1] - meta.cu_seqlens[b], int(meta.ctx_lens_host[b]), D, D, q.device)
                         for b in range(n_seq))):
@@ -340,13 +348,14 @@ class Transformer:
             for b in range(n_seq):
                 s0, e0 = meta.cu_seqlens[b], meta.cu_seqlens[b + 1]
                 n_ctx = int(meta.ctx_lens_host[b])
+                lo = _first_key(e0 - s0, n_ctx)
 
-                def _slots(b=b, n_ctx=n_ctx):
-                    tok = torch.arange(n_ctx, device=q.device)
+                def _slots(b=b, n_ctx=n_ctx, lo=lo):
+                    tok = torch.arange(lo, n_ctx, device=q.device)
                     return meta.block_tables[b, tok // bs].long() * bs + tok % bs
-                slots = meta.cached(("slots", b, n_ctx), _slots)
+                slots = meta.cached(("slots", b, lo, n_ctx), _slots)
                 ops.fmha_prefill(q[s0:e0], kv.k[li].view(-1, Hk, D)[slots], kv.v[li].view(-1, Hk, D)[slots],
-                                 out[s0:e0].view(-1, Hq, D), self.scale)
+                                 out[s0:e0].view(-1, Hq, D), self.scale, window=win)
             return out
         if meta.attn_mask is None and q.dtype == torch.bfloat16:
             # one launch for all sequences: keys are read from the paged pool through the block table

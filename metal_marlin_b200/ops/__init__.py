@@ -24,8 +24,10 @@ _native_ok = False
 GEMV_MAX_M = 32          # dense projections: at or below this many tokens the weight-streaming GEMV path is used
 GEMV_FUSED_PROLOGUE_MAX_M = 8   # ... with the residual add + RMSNorm fused into its staging up to this many tokens
 ROUTER_GEMM_MIN_T = 64   # above this many tokens the gate logits come from the bf16 tcgen05 GEMM
-MOE_GEMV_MAX_T = 16      # MoE: per-(token, slot) streaming up to this many tokens
+MOE_GEMV_MAX_T = 8       # MoE: per-(token, slot) streaming up to this many tokens (measured: the expert-sorted kernel wins from 9)
 MOE_GROUPED_GEMV_MAX_T = 128   # ... expert-sorted 8-row tiles on the streaming kernel up to here, grouped tcgen05 GEMMs above
+GEMV_LIMITS = {}         # (out_features, in_features) -> tuned GEMV_MAX_M of that shape (installed by autotune.apply_config)
+MOE_TOKEN_TILES = []     # sorted (tokens, token tile): tuned tile of the grouped GEMM, nearest measured token count wins
 GROUPED_GEMV_TUNE = [0, 0, 0, 0]   # (wpt, units per item) of the gate-up and the down launch; 0 = launcher's choice
 # Diagnostic switch: route every shape through the weight-streaming kernels (no tcgen05 GEMM).
 NO_TCGEN05 = os.environ.get("MMB200_NO_TCGEN05", "0") == "1"
@@ -158,6 +160,10 @@ def layernorm(x, w=None, b=None, eps=1e-5, *, delta=None, resid_out=None, out=No
     return out.view(shape)
 
 
+def _gemv_limit(W) -> int:
+    return GEMV_LIMITS.get((W.out_features, W.in_features), GEMV_MAX_M) if GEMV_LIMITS else GEMV_MAX_M
+
+
 def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bias=None, out_add=None,
            out=None, token_tile=0, tpx=None, ag_wait=None, _rotated=False):
     """``out = epilogue( prologue(x) @ dequant(W)^T )``; prologue = optional residual add + RMSNorm,
@@ -167,7 +173,7 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
     waits per token tile for the owners of the rows (an object with ``.wait`` descriptor and ``.ensure()``)."""
     if ag_wait is not None:
         direct = (delta is None and norm_w is None and _use_native(x) and not getattr(W, "is_generic", False) and _capture is None
-                  and x.shape[0] > GEMV_MAX_M and not NO_TCGEN05 and x.is_contiguous() and x.shape[1] == W.in_features)
+                  and x.shape[0] > _gemv_limit(W) and not NO_TCGEN05 and x.is_contiguous() and x.shape[1] == W.in_features)
         if not direct:
             ag_wait.ensure()
             ag_wait = None
@@ -195,7 +201,7 @@ def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None
     n_out = W.out_features // 2 if act == 1 else W.out_features
     if out is None:
         out = torch.empty(M, n_out, dtype=torch.bfloat16, device=x.device)
-    if M <= GEMV_MAX_M or NO_TCGEN05:
+    if M <= _gemv_limit(W) or tpx is not None or NO_TCGEN05:      # the in-kernel exchange exists on the streaming kernel only
         if M > GEMV_FUSED_PROLOGUE_MAX_M and tpx is None and delta is not None:
             # every CTA of the streaming kernel stages all its token rows: with many rows the residual add (+ norm, + the
             # residual write) is cheaper done once in its own launch than repeated by every CTA; a norm alone stays fused
@@ -772,6 +778,8 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
         return _moe_forward_grouped_gemv(xin, gate_up, down, ids, weights, n_shared, shared_base, out_add)
     st = gemm_status(x.device)
     E_routed = gate_up.num_experts - n_shared
+    if not token_tile and MOE_TOKEN_TILES:      # tuned on this GPU: the tile measured best at the nearest token count
+        token_tile = min(MOE_TOKEN_TILES, key=lambda e: abs(e[0] - T))[1]
     if not token_tile:      # smallest MMA N tile that holds the average expert load
         avg = T * topk / max(1, E_routed)
         token_tile = 32 if avg <= 24 else (64 if avg <= 48 else (128 if avg <= 160 else 256))
@@ -813,6 +821,38 @@ def moe_forward(x, gate_up: FP4ExpertBank, down: FP4ExpertBank, ids, weights, *,
 # secondary kernels: Hadamard rotation, trellis weights, codebook (INT4 / INT8 / FP8 / NF4 ...) GEMV, vision
 # preprocessing, speculative verification
 # ----------------------------------------------------------------------------------------------------------------
+def gptq_block(W, Q, Hinv, col_scale, grid, err_rows, i1: int, i2: int):
+    """The column-serial part of GPTQ over the lazy block ``[i1, i2)`` (at most 128 columns) as one launch, a warp per
+    weight row: writes the quantized columns into ``Q``, adds each row's squared error to ``err_rows`` and returns the
+    scaled errors ``E [out, i2 - i1]`` for the update of the columns behind the block.  All tensors fp32 on one CUDA device;
+    ``W`` (updated in place), ``Q`` and ``col_scale`` share a row stride.  Bit-identical to the PyTorch loop in
+    ``quant.gptq.gptq_quantize`` (plain fp32 roundings).  Parity: reference ``src/cholesky.metal`` (``gptq_update_weights``)."""
+    E = torch.empty(W.shape[0], i2 - i1, dtype=torch.float32, device=W.device)
+    K.mmb200.gptq_block(W, Q, E, Hinv, col_scale, grid, err_rows, i1, i2 - i1)
+    return E
+
+
+def gptq_block_ok(W, block: int, n_grid: int) -> bool:
+    return _use_native(W) and W.dtype == torch.float32 and 1 <= block <= 128 and 2 <= n_grid <= 256
+
+
+def fp4_quantize_pack(w, group_size: int = 128):
+    """Round-to-nearest E2M1 quantization and packing of ``w [out, in]`` (fp32 or bf16) in one pass: returns ``(packed int32
+    [out, in / 8], scales fp16 [out, in / group_size])``, the row-packed checkpoint layout.  Equal bit for bit to
+    ``formats.fp4.quantize_codes`` followed by ``pack_mmfp4``, which is what runs on the CPU.  Parity: reference
+    ``metal_marlin/fp4_metal.py``."""
+    lanes = group_size // 8
+    if not (_use_native(w) and w.dtype in (torch.float32, torch.bfloat16) and 8 <= group_size <= 128 and lanes & (lanes - 1) == 0
+            and group_size % 8 == 0):
+        from ..formats import fp4 as fp4fmt
+        return fp4fmt.pack_mmfp4(*fp4fmt.quantize_codes(w, group_size))
+    w = w.detach().contiguous()
+    packed = torch.empty(w.shape[0], w.shape[1] // 8, dtype=torch.int32, device=w.device)
+    scales = torch.empty(w.shape[0], w.shape[1] // group_size, dtype=torch.float16, device=w.device)
+    K.mmb200.fp4_quantize_pack(w, packed, scales, group_size)
+    return packed, scales
+
+
 def hadamard(x, block: int = 128, out=None):
     """Orthonormal block Walsh-Hadamard transform along the last axis (bf16 on CUDA; any float dtype on CPU)."""
     if not _use_native(x) or x.dtype != torch.bfloat16:
@@ -1012,9 +1052,10 @@ def fmha_ok(t: int, n: int, D: int, Dv: int, device) -> bool:
                 and torch.device(device).type == "cuda" and native_available() and not _FORCE_REF)
 
 
-def fmha_prefill(q, k, v, out, scale, vt=None):
+def fmha_prefill(q, k, v, out, scale, vt=None, window=0):
     """Causal attention of ONE sequence on the tcgen05 kernel (``csrc/attention_fmha_sm100.cu``): ``q [t, Hq, D]`` are the last
-    ``t`` positions of the keys ``k, v [n, Hk, D]``; ``D`` 128 or 256.  The kernel takes V transposed per head, ``vt [Hk, D,
+    ``t`` positions of the keys ``k, v [n, Hk, D]``; ``D`` 128 or 256.  With ``window > 0`` a query sees only the last
+    ``window`` keys up to its own position, and key tiles in front of a query tile's window are skipped.  The kernel takes V transposed per head, ``vt [Hk, D,
     n_pad]`` with ``n_pad % 8 == 0`` and zeros behind column ``n`` (the B operand of its P V MMA is K-major like every other
     operand); callers that can produce it directly (a GEMM with swapped operands) pass ``vt``, else it is built here with
     one strided copy of ``v``."""
@@ -1026,7 +1067,7 @@ def fmha_prefill(q, k, v, out, scale, vt=None):
         vt[:, :, :n].copy_(v.permute(1, 2, 0))
         if n_pad > n:
             vt[:, :, n:].zero_()
-    K.mmb200.fmha_prefill(q, k, vt, out, n, float(scale), gemm_status(q.device))
+    K.mmb200.fmha_prefill(q, k, vt, out, n, float(scale), gemm_status(q.device), int(window or 0))
     return out
 
 
@@ -1056,13 +1097,18 @@ def prefill_attention(q, k, v, cu_q, *, cu_k=None, block_tables=None, ctx_lens=N
     if max_q is None and (block_mask is not None or (_use_native(q) and D in PREFILL_ATTN_DIMS)):
         max_q = int((cu_q[1:] - cu_q[:-1]).max())
     if (FMHA_TCGEN05 and _use_native(q) and not NO_TCGEN05 and D in (128, 256) and q.dtype == torch.bfloat16 and cu_k is not None
-            and cu_q.numel() == 2 and causal and not window and not sinks and tree_mask is None and block_mask is None
+            and cu_q.numel() == 2 and causal and not sinks and tree_mask is None and block_mask is None
             and T >= FMHA_MIN_T and k.shape[-1] == D and v.shape[-1] == D and k.shape[0] >= T and q.stride(2) == 1
             and k.stride(2) == 1 and out.stride(2) == 1 and k.stride(1) <= k.stride(0) and q.stride(1) <= q.stride(0)):
-        return fmha_prefill(q, k, v, out, scale)
+        return fmha_prefill(q, k, v, out, scale, window=window)
     if _use_native(q) and D in PREFILL_ATTN_DIMS and q.dtype == torch.bfloat16 and k.shape[-1] == D and v.shape[-1] == D:
         K.mmb200.prefill_attention(q, k, v, out, cu_q, cu_k, block_tables, ctx_lens, block_size, max_q, scale, window, causal,
                                    int(sinks), tree_mask, block_mask)
         return out
     return ref.prefill_attention(q, k, v, cu_q, cu_k, block_tables, ctx_lens, block_size, scale, window, causal, out,
                                  sinks=sinks, tree_mask=tree_mask, block_mask=block_mask)
+
+
+if os.environ.get("MMB200_TUNING_FILE"):      # a table written by `metal-marlin autotune` replaces the built-in thresholds
+    from ..autotune import load_config as _load_tuning
+    _load_tuning()

@@ -51,7 +51,7 @@ def main():
             ts.append(a.elapsed_time(b) * 1e3)
         return sorted(ts)[len(ts) // 2]
 
-    us = timed(lambda: ops.K.mmb200.fmha_prefill(q, k, vt, out, t, D ** -0.5, st))
+    us = timed(lambda: ops.K.mmb200.fmha_prefill(q, k, vt, out, t, D ** -0.5, st, 0))
     flops = 4.0 * t * t / 2 * H * D
     res = {"bench": "fmha_prefill", "tokens": t, "heads": H, "kv_heads": Hk, "dim": D, "tcgen05_us": round(us, 1),
            "tcgen05_tflops": round(flops / us / 1e6, 1), "status": int(st[0]),

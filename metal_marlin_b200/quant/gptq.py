@@ -3,9 +3,11 @@
 Parity: reference ``metal_marlin/gptq.py`` / ``gptq_fp4.py`` / ``gptq_accelerated.py`` (column-wise quantization
 with Cholesky-inverse Hessian updates, damping, block size 128, act-order) and ``metal_marlin/mr_gptq.py``
 (``:68`` config, ``:164`` Hessian handling, ``:400`` block-Hadamard rotation, ``:620`` kurtosis gating, ``:686``
-per-layer loop, ``:974`` stacked-expert tensors, ``:2420`` resumable state).  Everything is torch linear algebra
-and runs on whatever device the tensors are on (GPU for real models); the output is codes + group scales in
-the same form the round-to-nearest quantizers produce, so the packers and checkpoint writers are shared.
+per-layer loop, ``:974`` stacked-expert tensors, ``:2420`` resumable state).  The Hessian factorisations and the
+between-block updates are torch linear algebra on whatever device the tensors are on; on a GPU the column-serial loop
+inside a block is one launch of ``csrc/quantizer.cu`` (a warp per weight row, bit-identical to the loop written here).
+The output is codes + group scales in the same form the round-to-nearest quantizers produce, so the packers and
+checkpoint writers are shared.
 """
 from __future__ import annotations
 
@@ -80,6 +82,16 @@ def gptq_quantize(w: torch.Tensor, H: torch.Tensor, cfg: Optional[GPTQConfig] = 
     Hinv = torch.linalg.cholesky(torch.cholesky_inverse(L), upper=True)
     Q = torch.zeros_like(W)
     err_total = 0.0
+    from .. import ops
+    if ops.gptq_block_ok(W, cfg.block_size, grid.numel()):
+        # on the GPU the column loop of a block is one kernel launch (a warp per row), same roundings as the loop below
+        col_scale, Hrows = col_scale.contiguous(), Hinv.contiguous()     # the kernel reads rows of the factor
+        err_rows = torch.zeros(out_f, dtype=torch.float32, device=dev)
+        for i1 in range(0, in_f, cfg.block_size):
+            i2 = min(i1 + cfg.block_size, in_f)
+            E1 = ops.gptq_block(W, Q, Hrows, col_scale, grid, err_rows, i1, i2)
+            W[:, i2:] -= E1 @ Hinv[i1:i2, i2:]
+        return Q[:, inv_perm], scales, {"sq_err": float(err_rows.sum()), "act_order": cfg.act_order, "group_size": gs}
     for i1 in range(0, in_f, cfg.block_size):
         i2 = min(i1 + cfg.block_size, in_f)
         W1 = W[:, i1:i2].clone()
@@ -90,10 +102,11 @@ def gptq_quantize(w: torch.Tensor, H: torch.Tensor, cfg: Optional[GPTQConfig] = 
             s = col_scale[:, i1 + i]
             q = _nearest(wcol / s, grid) * s
             Q[:, i1 + i] = q
-            e = (wcol - q) / Hi[i, i]
+            d = wcol - q                  # taken before the update below, which also rewrites column i (wcol is a view)
+            e = d / Hi[i, i]
+            err_total += float((d ** 2).sum())
             W1[:, i:] -= e.unsqueeze(1) * Hi[i, i:].unsqueeze(0)
             E1[:, i] = e
-            err_total += float(((wcol - q) ** 2).sum())
         W[:, i2:] -= E1 @ Hinv[i1:i2, i2:]
     Q = Q[:, inv_perm]
     return Q, scales, {"sq_err": err_total, "act_order": cfg.act_order, "group_size": gs}

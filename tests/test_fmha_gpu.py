@@ -9,14 +9,17 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _ref(q, k, v, scale):
+def _ref(q, k, v, scale, window=0):
     t, Hq, D = q.shape
     n, Hk, _ = k.shape
     g = Hq // Hk
     qf, kf, vf = q.float(), k.float().repeat_interleave(g, 1), v.float().repeat_interleave(g, 1)
     s = torch.einsum("thd,nhd->htn", qf, kf) * scale
     pos = torch.arange(n - t, n, device=q.device).view(1, t, 1)
-    s = s.masked_fill(torch.arange(n, device=q.device).view(1, 1, n) > pos, float("-inf"))
+    keys = torch.arange(n, device=q.device).view(1, 1, n)
+    s = s.masked_fill(keys > pos, float("-inf"))
+    if window:
+        s = s.masked_fill(keys <= pos - window, float("-inf"))
     return torch.einsum("htn,nhd->thd", torch.softmax(s, -1), vf)
 
 
@@ -39,6 +42,31 @@ def test_fmha_prefill_matches_reference(t, n, Hq, Hk, D, boost):
     ref = _ref(q, k, v, scale)
     err = float((out.float() - ref).abs().max() / ref.abs().max())
     assert err < 2e-2, err
+
+
+@pytest.mark.parametrize("t,n,Hq,Hk,D,window", [(1024, 1024, 4, 2, 128, 64), (1024, 1536, 4, 2, 128, 300), (700, 900, 2, 2, 256, 100),
+                                                (512, 2048, 2, 1, 256, 1000), (640, 640, 2, 2, 128, 4096), (384, 1200, 4, 4, 128, 1)])
+def test_fmha_prefill_sliding_window(t, n, Hq, Hk, D, window):
+    """Windows shorter than a key tile (a row's first visited tile can be wholly outside its window), longer than the
+    context (no effect), and in between (leading key tiles are skipped)."""
+    from metal_marlin_b200 import ops
+    torch.manual_seed(t + n + window)
+    q = torch.randn(t, Hq, D, device=DEV).to(torch.bfloat16)
+    k = torch.randn(n, Hk, D, device=DEV).to(torch.bfloat16)
+    v = torch.randn(n, Hk, D, device=DEV).to(torch.bfloat16)
+    out = torch.empty(t, Hq, D, dtype=torch.bfloat16, device=DEV)
+    scale = D ** -0.5
+    ops.fmha_prefill(q, k, v, out, scale, window=window)
+    torch.cuda.synchronize()
+    assert ops.check_status(torch.device(DEV)) == 0
+    ref = _ref(q, k, v, scale, window)
+    err = float((out.float() - ref).abs().max() / ref.abs().max())
+    assert err < 2e-2, err
+    # the general entry point routes a windowed single sequence to the same kernel
+    cu_q = torch.tensor([0, t], dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    o2 = ops.prefill_attention(q, k, v, cu_q, cu_k=cu_k, max_q=t, window=window)
+    assert float((o2.float() - ref).abs().max() / ref.abs().max()) < 2e-2
 
 
 def test_prefill_attention_routes_single_sequences_to_the_tensor_core_kernel():
@@ -144,3 +172,40 @@ def test_gqa_batch_of_long_prompts_runs_the_tensor_core_attention_per_sequence()
         b = prefill(lm.model, lm.new_cache(3 * 48, 16), prompts, bt)
     assert ops.check_status(torch.device(DEV)) == 0
     assert float((a - b).abs().max() / b.abs().max()) < 4e-2
+
+
+def test_sliding_window_model_prompts_take_the_tensor_core_kernel():
+    """A grouped-query model with a 200-token window: a 700-token prompt, then a 300-token continuation over the cached
+    keys (only the keys inside the chunk's window are gathered), against the PyTorch restatement of every op."""
+    import dataclasses
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM, prefill
+    cfg = dataclasses.replace(get_preset("tiny-llama"), hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                              sliding_window=200)
+    lm = MMFP4ForCausalLM.from_config(cfg, device="cuda", seed=5)
+    g = torch.Generator().manual_seed(9)
+    seq = torch.randint(0, cfg.vocab_size, (1000,), generator=g).tolist()
+    bt = torch.arange(64, dtype=torch.int32).view(1, 64)
+    calls = {"n": 0}
+    real = ops.fmha_prefill
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        assert k.get("window") == 200
+        return real(*a, **k)
+    ops.fmha_prefill = counting
+    try:
+        kv = lm.new_cache(64, 16)
+        prefill(lm.model, kv, [seq[:700]], bt)
+        a = prefill(lm.model, kv, [seq], bt, start=[700])
+    finally:
+        ops.fmha_prefill = real
+    assert calls["n"] == 2 * cfg.num_hidden_layers
+    assert ops.check_status(torch.device(DEV)) == 0
+    with ops.force_reference():
+        kv = lm.new_cache(64, 16)
+        prefill(lm.model, kv, [seq[:700]], bt)
+        b = prefill(lm.model, kv, [seq], bt, start=[700])
+    err = float((a - b).abs().max() / b.abs().max())
+    assert err < 5e-2, err
