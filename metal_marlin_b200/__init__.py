@@ -34,6 +34,11 @@ _reg(".engine.session", "DecodeSession", "SamplingParams")
 _reg(".engine.engine", "LLMEngine")
 _reg(".engine.scheduler", "BatchScheduler", "SchedulerConfig", "PreemptionPolicy", "QueueFullError")
 _reg(".inference.pipelined", "PipelineScheduler", "AsyncPipelineScheduler", "InferenceRequest", "RequestState", "generate_pipelined")
+_reg(".inference.prefill", "PrefillConfig", "PrefillStats", "chunked_prefill", "parallel_kv_write", "flash_prefill_attention",
+     "SpeculativePrefillConfig", "speculative_prefill", "pick_chunk_size")
+_reg(".inference.decode", "DecodeConfig", "DecodePerfStats", "DecodeState", "persistent_decode_step", "select_decode_kernel",
+     "quantized_kv_attention", "quantize_kv_cache")
+_reg(".autotune", "KernelAutoTuner", "TunedConfig", "OnlineAdapter", "get_optimal_config")
 _reg(".converters.exl3", "detect_exl3_format", "convert_sharded_to_layerwise", "load_exl3_from_hub", "download_exl3_model", "list_exl3_models",
      "parse_model_card", "exl3_layer_to_marlin", "convert_exl3_to_marlin")
 _reg(".quant.ldlq", "block_ldl", "ldlq_quantize", "compute_group_scales", "quantize_tile_viterbi", "quantize_tile_greedy", "LDLQResult")
