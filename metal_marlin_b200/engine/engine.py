@@ -41,6 +41,8 @@ class EngineConfig:
     request_timeout_s: float = 60.0
     graph_buckets: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)
     scheduler_policy: str = "priority"   # "priority" (continuous batching with priorities) | "fcfs" | "shortest_first" | "longest_first"
+    preemption_mode: str = "recompute"   # "swap": a preempted sequence keeps its cache rows in pinned host memory and resumes from them
+    swap_space_blocks: int = 0           # host blocks for swapped sequences (0 with "swap": as many as ``num_kv_blocks``)
 
 
 HISTORY_LEN = 256      # most recent tokens (prompt tail + generated) the repetition penalty looks at
@@ -190,9 +192,15 @@ class LLMEngine:
         self.kv = PagedKVStorage(model.cfg, c.num_kv_blocks, c.block_size, model.device, kv_dtype=c.kv_cache_dtype)
         self.cache = PagedKVCache(c.num_kv_blocks, c.block_size, enable_prefix_cache=c.enable_prefix_cache,
                                   copy_fn=self._copy_block)
+        # swapping moves cache rows only: the recurrent state of a hybrid stack is addressed by a sequence's first block, and
+        # the shards of a tensor-parallel group would each have to repeat the moves, so both fall back to recompute
+        swap = c.preemption_mode == "swap" and not self.recurrent and coordinator is None
+        self.swap_blocks = (c.swap_space_blocks or c.num_kv_blocks) if swap else 0
+        self._swap_pools = None
         scfg = SchedulerConfig(max_num_seqs=c.max_num_seqs, max_num_batched_tokens=c.max_num_batched_tokens,
                                max_prefill_tokens=c.max_prefill_tokens, block_size=c.block_size, max_chunk=c.max_chunk,
-                               max_model_len=c.max_model_len)
+                               max_model_len=c.max_model_len, preemption_mode="swap" if swap else "recompute",
+                               swap_space_blocks=self.swap_blocks)
         if c.scheduler_policy == "priority":
             self.scheduler = BatchScheduler(scfg, self.cache)
         else:
@@ -215,6 +223,42 @@ class LLMEngine:
             for t in pool:
                 if t is not None:
                     ops.kv_copy_rows(t, slice(dst * bs, (dst + 1) * bs), slice(src * bs, (src + 1) * bs))
+
+    def _host_pools(self):
+        """Host mirrors of the cache pools (``swap_blocks`` blocks each, pinned on a CUDA engine), created at the first swap."""
+        if self._swap_pools is None:
+            n = self.swap_blocks * self.cfg.block_size
+            pin = self.model.device.type == "cuda"
+
+            def host(t):
+                return torch.zeros(n, *t.shape[1:], dtype=t.dtype, pin_memory=pin)
+            pools = []
+            for group in (self.kv.k, self.kv.v):
+                for t in group:
+                    if t is None:
+                        continue
+                    pools.extend((d, host(d)) for d in ([t.data, t.scale] if isinstance(t, ops.FP8KV) else [t]))
+            self._swap_pools = pools
+        return self._swap_pools
+
+    def _apply_swaps(self, out: SchedulerOutput) -> None:
+        """Carry out the block moves the scheduler planned: all moves to the host first (their device blocks may be handed
+        to another sequence in this very iteration, and to a sequence swapped in below), then the moves back."""
+        bs = self.cfg.block_size
+        dev = self.model.device
+        ar = torch.arange(bs)
+
+        def rows(blocks):
+            return (torch.tensor(blocks, dtype=torch.int64).unsqueeze(1) * bs + ar).reshape(-1)
+        pools = self._host_pools()
+        for _rr, dev_blocks, host_blocks in out.swap_out:
+            d, h = rows(dev_blocks).to(dev), rows(host_blocks)
+            for dev_t, host_t in pools:
+                host_t[h] = dev_t[d].to("cpu")
+        for _rr, host_blocks, dev_blocks in out.swap_in:
+            d, h = rows(dev_blocks).to(dev), rows(host_blocks)
+            for dev_t, host_t in pools:
+                dev_t[d] = host_t[h].to(dev, non_blocking=False)
 
     # ------------------------------------------------------------------ public API
     def add_request(self, req: GenerationRequest) -> RunningRequest:
@@ -256,6 +300,8 @@ class LLMEngine:
         """One engine iteration.  Returns the requests that finished in it."""
         with self._lock:
             out = self.scheduler.schedule()
+            if out.swap_out or out.swap_in:
+                self._apply_swaps(out)
             do_prefill, do_decode = bool(out.prefill), bool(out.decode)
             n_pre = n_dec = 0
             if self.lockstep is not None:

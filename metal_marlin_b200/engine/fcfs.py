@@ -83,7 +83,7 @@ class FCFSScheduler(BatchScheduler):
         return len(self.running)
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.swapped or self.running)
+        return bool(self.waiting or self.swapped or self.running or self.swapped_out)
 
     has_pending_work = property(has_work)
 

@@ -21,6 +21,7 @@ class RequestStatus(enum.Enum):
     PREFILLING = "prefilling"
     RUNNING = "running"
     PREEMPTED = "preempted"
+    SWAPPED = "swapped"          # preempted with its cache rows parked in host memory (resumes without recomputing)
     FINISHED = "finished"
     ABORTED = "aborted"
     FAILED = "failed"
@@ -30,7 +31,9 @@ _LEGAL = {
     RequestStatus.WAITING: {RequestStatus.PREFILLING, RequestStatus.ABORTED, RequestStatus.FAILED},
     RequestStatus.PREFILLING: {RequestStatus.RUNNING, RequestStatus.PREEMPTED, RequestStatus.FINISHED,
                                RequestStatus.ABORTED, RequestStatus.FAILED},
-    RequestStatus.RUNNING: {RequestStatus.FINISHED, RequestStatus.PREEMPTED, RequestStatus.ABORTED, RequestStatus.FAILED},
+    RequestStatus.RUNNING: {RequestStatus.FINISHED, RequestStatus.PREEMPTED, RequestStatus.SWAPPED, RequestStatus.ABORTED,
+                            RequestStatus.FAILED},
+    RequestStatus.SWAPPED: {RequestStatus.RUNNING, RequestStatus.ABORTED, RequestStatus.FAILED},
     RequestStatus.PREEMPTED: {RequestStatus.PREFILLING, RequestStatus.WAITING, RequestStatus.ABORTED, RequestStatus.FAILED},
     RequestStatus.FINISHED: set(), RequestStatus.ABORTED: set(), RequestStatus.FAILED: set(),
 }
@@ -87,6 +90,8 @@ class RunningRequest:
     done: threading.Event = field(default_factory=threading.Event)
     spec_accepted: int = 0
     spec_proposed: int = 0
+    swap_host_blocks: Optional[List[int]] = None     # host blocks holding the cache rows while the request is SWAPPED
+    swap_tokens: int = 0                             # rows those blocks hold
 
     def __post_init__(self):
         self.effective_priority = int(self.req.priority)
@@ -153,6 +158,10 @@ class SchedulerOutput:
     prefill: List[PrefillChunk] = field(default_factory=list)
     decode: List[RunningRequest] = field(default_factory=list)
     preempted: List[RunningRequest] = field(default_factory=list)
+    # cache blocks to move before the model runs, in this order: (request, device blocks, host blocks) out, then
+    # (request, host blocks, device blocks) in
+    swap_out: List[tuple] = field(default_factory=list)
+    swap_in: List[tuple] = field(default_factory=list)
 
     @property
     def num_tokens(self) -> int:

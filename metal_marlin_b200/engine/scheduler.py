@@ -1,5 +1,6 @@
 """Continuous-batching scheduler: per-iteration token budgets, decode-first planning, chunked
-prefill, priorities with starvation promotion, preemption by recompute.  The first-come-first-served scheduler with
+prefill, priorities with starvation promotion, preemption by recompute or by swapping the victim's cache blocks to host
+memory (``preemption_mode="swap"``: the scheduler plans the block moves, the engine copies).  The first-come-first-served scheduler with
 prefill strategies and insertion policies builds on it in ``engine/fcfs.py``.
 
 Parity: reference ``metal_marlin/serving/continuous_batch.py``: ``SchedulerConfig`` (max_num_seqs 64,
@@ -47,6 +48,8 @@ class SchedulerConfig:
     max_waiting: int = 4096
     max_model_len: int = 1 << 20
     fcfs: bool = False                     # ignore priorities: strict arrival order
+    preemption_mode: str = "recompute"     # "swap": a fully prefilled victim keeps its cache rows in host blocks
+    swap_space_blocks: int = 0             # host blocks available to swapped sequences
 
 
 class BatchScheduler:
@@ -58,6 +61,9 @@ class BatchScheduler:
         self.requests: Dict[str, RunningRequest] = {}
         self.num_preemptions = 0
         self.num_finished = 0
+        self.swapped_out: List[RunningRequest] = []          # sequences whose cache rows sit in host blocks, oldest first
+        self._host_free: List[int] = list(range(config.swap_space_blocks if config.preemption_mode == "swap" else 0))
+        self.num_swaps = 0
 
     # ------------------------------------------------------------------ queue
     def add_request(self, req: GenerationRequest) -> RunningRequest:
@@ -91,7 +97,7 @@ class BatchScheduler:
         return len(self._heap)
 
     def has_work(self) -> bool:
-        return bool(self._heap or self.running)
+        return bool(self._heap or self.running or self.swapped_out)
 
     def abort(self, request_id: str) -> bool:
         rr = self.requests.get(request_id)
@@ -100,6 +106,10 @@ class BatchScheduler:
         if rr in self.running:
             self.running.remove(rr)
             self.cache.release(rr.id)
+        elif rr in self.swapped_out:
+            self.swapped_out.remove(rr)
+            self._host_free.extend(rr.swap_host_blocks)
+            rr.swap_host_blocks = None
         else:
             self._drop_waiting(rr)
             if self.cache.table.has(rr.id):
@@ -135,8 +145,27 @@ class BatchScheduler:
             return min(cands, key=lambda r: r.arrival)
         return min(cands, key=lambda r: (r.effective_priority, -r.arrival))
 
-    def _preempt(self, rr: RunningRequest) -> None:
-        """Free the sequence's KV and queue it again; its cache is recomputed on resume."""
+    def _preempt(self, rr: RunningRequest, out: Optional[SchedulerOutput] = None) -> None:
+        """Free the sequence's KV and queue it again; its cache is recomputed on resume.  In swap mode a fully prefilled
+        sequence instead has its blocks copied to host blocks (planned in ``out.swap_out``) and resumes from them."""
+        if (out is not None and self.cfg.preemption_mode == "swap" and rr.status is RequestStatus.RUNNING
+                and not any(rr is e[0] for e in out.swap_in)):
+            # rows worth keeping: every token but the newest, whose row the next decode step writes (a slot this iteration
+            # may already have reserved for it is dropped with the rest of the table)
+            n_tok = len(rr.all_ids) - 1
+            blocks = list(self.cache.table.block_table(rr.id))[: -(-n_tok // self.cfg.block_size)]
+            if len(blocks) <= len(self._host_free):
+                host = [self._host_free.pop() for _ in blocks]
+                rr.swap_host_blocks, rr.swap_tokens = host, n_tok
+                out.swap_out.append((rr, blocks, host))
+                self.running.remove(rr)
+                self.cache.release(rr.id)
+                rr.num_preemptions += 1
+                self.num_preemptions += 1
+                self.num_swaps += 1
+                rr.transition(RequestStatus.SWAPPED)
+                self.swapped_out.append(rr)
+                return
         self.running.remove(rr)
         self.cache.release(rr.id)
         rr.prefill_progress = 0
@@ -170,7 +199,7 @@ class BatchScheduler:
                     if victim in out.decode:
                         out.decode.remove(victim)
                         budget += 1
-                    self._preempt(victim)
+                    self._preempt(victim, out)
                     if victim is rr:
                         break
             if rr in self.running:
@@ -185,7 +214,23 @@ class BatchScheduler:
             if n > 0:
                 out.prefill.append(PrefillChunk(rr, rr.prefill_progress, n))
                 prefill_budget -= n
-        while prefill_budget > 0 and len(self.running) < self.cfg.max_num_seqs:
+        # swapped sequences come back before anything new is admitted (and hold admissions back while they cannot)
+        while self.swapped_out and len(self.running) < self.cfg.max_num_seqs:
+            rr = self.swapped_out[0]
+            if any(rr is e[0] for e in out.swap_out) or not self.cache.can_admit(rr.swap_tokens + 1):
+                break
+            try:
+                self.cache.table.add_sequence(rr.id, rr.swap_tokens)
+            except OutOfBlocks:
+                self.cache.table.seqs.pop(rr.id, None)
+                break
+            self.swapped_out.pop(0)
+            out.swap_in.append((rr, rr.swap_host_blocks, list(self.cache.table.block_table(rr.id))))
+            self._host_free.extend(rr.swap_host_blocks)
+            rr.swap_host_blocks = None
+            rr.transition(RequestStatus.RUNNING)
+            self.running.append(rr)
+        while not self.swapped_out and prefill_budget > 0 and len(self.running) < self.cfg.max_num_seqs:
             rr = self._peek_waiting()
             if rr is None:
                 break
@@ -253,5 +298,6 @@ class BatchScheduler:
         return finished
 
     def stats(self) -> dict:
-        return {"waiting": self.num_waiting, "running": len(self.running), "preemptions": self.num_preemptions,
+        return {"waiting": self.num_waiting, "running": len(self.running), "swapped_out": len(self.swapped_out),
+                "swaps": self.num_swaps, "preemptions": self.num_preemptions,
                 "finished": self.num_finished, "kv": self.cache.stats()}

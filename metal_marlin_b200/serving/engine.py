@@ -43,6 +43,8 @@ class EngineConfig:
     num_speculative_tokens: int = 4
     kv_cache_dtype: str = "bf16"          # "fp8" | "int8" | "fp4" | "int4": quantized paged cache (one scale per cached row)
     scheduler_policy: str = "priority"    # "priority" | "fcfs" | "shortest_first" | "longest_first"
+    preemption_mode: str = "recompute"    # "swap": preempted sequences park their cache rows in pinned host memory
+    swap_space_blocks: int = 0
     # multi-GPU (job started with torchrun, one process per GPU): tensor / expert / data parallel degrees
     tp: int = 1
     ep: int = 1
@@ -82,7 +84,8 @@ class ServingEngine:
         core = CoreEngineConfig(num_kv_blocks=config.num_kv_blocks, block_size=config.block_size,
                                 max_model_len=config.max_model_len, max_num_seqs=config.max_batch_size,
                                 request_timeout_s=config.request_timeout, kv_cache_dtype=config.kv_cache_dtype,
-                                scheduler_policy=config.scheduler_policy)
+                                scheduler_policy=config.scheduler_policy, preemption_mode=config.preemption_mode,
+                                swap_space_blocks=config.swap_space_blocks)
         from ..inference.pipeline import MMFP4Pipeline
         par = dict(tp=config.tp, ep=config.ep, dp=1)        # data-parallel replicas are whole servers behind serving/router.py
         if self.mock:

@@ -284,3 +284,59 @@ def test_engine_applies_repetition_penalty_per_request():
     eng.run_until_done()
     assert len(set(pen.output_ids)) == len(pen.output_ids) and not set(pen.output_ids) & set(prompt)
     assert plain.output_ids != pen.output_ids or len(set(plain.output_ids)) == len(plain.output_ids)
+
+
+def test_preemption_by_swap_plans_block_moves_and_resumes_without_recompute():
+    s = _sched(blocks=4, preemption_policy=PreemptionPolicy.LOWEST_PRIORITY, preemption_mode="swap", swap_space_blocks=4)
+    a = s.add_request(GenerationRequest(list(range(7)), 8, priority=RequestPriority.HIGH))
+    b = s.add_request(GenerationRequest(list(range(7)), 8, priority=RequestPriority.LOW))
+    _drive(s, s.schedule())
+    _drive(s, s.schedule())
+    o = s.schedule()                                     # each needs a third block: the low-priority one goes to the host
+    assert b.status is RequestStatus.SWAPPED and b in o.preempted and s.swapped_out == [b] and b.prefill_progress == 7
+    (rr, dev_blocks, host_blocks), = o.swap_out
+    assert rr is b and len(dev_blocks) == len(host_blocks) == 2 and b.swap_tokens == len(b.all_ids) - 1 == 8
+    assert a in o.decode and s.num_swaps == 1 and len(s._host_free) == 2
+    _drive(s, o)
+    c = s.add_request(GenerationRequest(list(range(3)), 2, priority=RequestPriority.REALTIME))
+    while a.status is not RequestStatus.FINISHED:
+        o = s.schedule()
+        assert not o.swap_in and c.status is RequestStatus.WAITING       # nothing new is admitted past a swapped sequence
+        _drive(s, o)
+    o = s.schedule()
+    (rr, host_back, dev_new), = o.swap_in
+    assert rr is b and host_back == host_blocks and len(dev_new) == 2 and b.status is RequestStatus.RUNNING
+    assert s.cache.table.num_tokens(b.id) == 8 and len(s._host_free) == 4
+    _drive(s, o)
+    while s.has_work():
+        _drive(s, s.schedule())
+    assert len(b.output_ids) == 8 and c.status is RequestStatus.FINISHED and s.cache.alloc.num_free == 4
+    # a swapped request can be aborted: its host blocks return
+    s2 = _sched(blocks=4, preemption_mode="swap", swap_space_blocks=2)
+    x = s2.add_request(GenerationRequest(list(range(7)), 8, priority=RequestPriority.HIGH))
+    y = s2.add_request(GenerationRequest(list(range(7)), 8, priority=RequestPriority.LOW))
+    for _ in range(3):
+        _drive(s2, s2.schedule())
+    assert y.status is RequestStatus.SWAPPED and s2.abort(y.id) and len(s2._host_free) == 2 and not s2.swapped_out
+    # without host room the victim is recomputed as before
+    s3 = _sched(blocks=4, preemption_mode="swap", swap_space_blocks=1)
+    s3.add_request(GenerationRequest(list(range(7)), 8, priority=RequestPriority.HIGH))
+    z = s3.add_request(GenerationRequest(list(range(7)), 8, priority=RequestPriority.LOW))
+    for _ in range(3):
+        _drive(s3, s3.schedule())
+    assert z.status is RequestStatus.PREEMPTED and z.prefill_progress == 0
+
+
+@pytest.mark.parametrize("kv_dtype", ["bf16", "fp8"])
+def test_engine_swap_preemption_keeps_the_output(kv_dtype):
+    lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    prompts = [list(range(1, 30)), list(range(40, 70))]
+    base = LLMEngine(lm.model, EngineConfig(num_kv_blocks=16, block_size=16, max_model_len=64, enable_prefix_cache=False,
+                                            use_cuda_graphs=False, kv_cache_dtype=kv_dtype))
+    want = base.generate(prompts, max_new_tokens=10)
+    eng = LLMEngine(lm.model, EngineConfig(num_kv_blocks=5, block_size=16, max_model_len=64, enable_prefix_cache=False,
+                                           use_cuda_graphs=False, kv_cache_dtype=kv_dtype, preemption_mode="swap"))
+    got = eng.generate(prompts, max_new_tokens=10)
+    st = eng.scheduler.stats()
+    assert got == want and st["swaps"] >= 1 and st["swapped_out"] == 0
+    assert len(eng.scheduler._host_free) == eng.swap_blocks == 5
