@@ -6,8 +6,10 @@ from .capacity import (CapacityAnalyzer, CapacityStats, DynamicCapacity, Dynamic
                        count_expert_assignments)
 from .load_balancing import ExpertLoadTracker, LoadBalancingConfig, gate_entropy, load_balance_loss
 from .prefetch import ExpertPrefetcher, PrefetchConfig, PrefetchStrategy
+from .router_int8 import Int8Router, Int8RouterLinear, RouterQuantConfig, measure_quantization_error, quantize_router_weights
 
 __all__ = ["CapacityAnalyzer", "CapacityStats", "DynamicCapacity", "DynamicCapacityConfig", "OverflowInfo", "OverflowPolicy",
            "analyze_overflow_rate", "apply_overflow_policy", "auto_tune_capacity", "compute_expert_capacity", "count_expert_assignments",
            "ExpertLoadTracker", "LoadBalancingConfig", "gate_entropy", "load_balance_loss", "ExpertPrefetcher", "PrefetchConfig",
-           "PrefetchStrategy"]
+           "PrefetchStrategy", "Int8Router", "Int8RouterLinear", "RouterQuantConfig", "measure_quantization_error",
+           "quantize_router_weights"]

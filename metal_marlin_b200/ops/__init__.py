@@ -585,6 +585,24 @@ def moe_router(x, w, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, bias=
     return ids, weights
 
 
+def moe_select(logits, *, bias=None, topk=4, scoring=0, renorm=True, routed_scale=1.0, n_group=1, topk_group=1, counts=None):
+    """Expert choice from gate logits fp32 ``[T, E]`` (softmax or sigmoid scoring, optional group-limited top-k, optional
+    renormalisation): ``(ids int32 [T, topk], weights fp32 [T, topk])``; ``counts`` int32 ``[E]`` accumulates the load.  One
+    warp per token on the GPU.  The logits may come from any gate: bf16 GEMM, INT8 router (``moe/router_int8.py``)."""
+    if not _use_native(logits):
+        ids, wts = ref.moe_select(logits, bias=bias, topk=topk, scoring=scoring, renorm=renorm, routed_scale=routed_scale,
+                                  n_group=n_group, topk_group=topk_group)
+        if counts is not None:
+            counts += torch.bincount(ids.reshape(-1).long(), minlength=counts.numel()).to(counts.dtype)
+        return ids, wts
+    T = logits.shape[0]
+    ids = torch.empty(T, topk, dtype=torch.int32, device=logits.device)
+    weights = torch.empty(T, topk, dtype=torch.float32, device=logits.device)
+    K.mmb200.moe_select(logits.to(torch.float32).contiguous(), bias, ids, weights, counts, topk, scoring, renorm, routed_scale,
+                        n_group, topk_group)
+    return ids, weights
+
+
 def moe_gate_up(x, bank: FP4ExpertBank, ids, *, n_shared=0, shared_base=0, norm_w=None, eps=1e-6, out=None):
     if not _use_native(x):
         return ref.moe_gate_up(x, bank, ids, n_shared=n_shared, shared_base=shared_base, norm_w=norm_w, eps=eps, out=out)

@@ -202,6 +202,14 @@ def moe_router(x, w, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, bias=
                routed_scale=1.0, n_group=1, topk_group=1) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     xin = add_norm(x, delta, norm_w, eps, resid_out)
     logits = xin @ w.to(torch.float32).t()
+    ids, wts = moe_select(logits, bias=bias, topk=topk, scoring=scoring, renorm=renorm, routed_scale=routed_scale, n_group=n_group,
+                          topk_group=topk_group)
+    return ids, wts, logits
+
+
+def moe_select(logits, *, bias=None, topk=4, scoring=0, renorm=True, routed_scale=1.0, n_group=1, topk_group=1):
+    """Scores, (grouped) top-k and weights from fp32 gate logits ``[T, E]``."""
+    logits = logits.to(torch.float32)
     if scoring == 0:
         scores = torch.softmax(logits, dim=-1)
         choice = scores
@@ -220,7 +228,7 @@ def moe_router(x, w, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, bias=
     if renorm:
         wts = wts / (wts.sum(-1, keepdim=True) + 1e-20)
     wts = wts * routed_scale
-    return ids.to(torch.int32), wts.to(torch.float32), logits
+    return ids.to(torch.int32), wts.to(torch.float32)
 
 
 def moe_gate_up(x, bank, ids, *, n_shared=0, shared_base=0, norm_w=None, eps=1e-6, out=None):

@@ -113,3 +113,37 @@ def test_prefetcher_predicts_and_loads_in_the_background(strategy):
     assert pf.get_stats()["failures"] == 1 and not pf.is_loaded(1, 5)
     assert pf.step(1, []) == []
     pf.stop()
+
+
+def test_int8_router_matches_the_float_router():
+    import torch
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.moe.router_int8 import (Int8Router, Int8RouterLinear, measure_quantization_error,
+                                                   quantize_router_weights)
+    torch.manual_seed(0)
+    E, H, T = 64, 256, 200
+    w = torch.randn(E, H) * 0.02
+    x = torch.randn(T, H)
+    q, s = quantize_router_weights(w)
+    assert q.dtype == torch.int8 and s.shape == (E,) and int(q.abs().max()) == 127
+    err = measure_quantization_error(w, x=x, topk=4)
+    assert err["relative_error"] < 0.01 and err["topk_agreement"] > 0.9
+    gate = Int8RouterLinear.from_weight(w)
+    assert float((gate.dequantize(torch.float32) - q.float() * s.unsqueeze(1)).abs().max()) < 1e-3 * float(w.abs().max())
+    lg = gate(x.bfloat16()).float()
+    ref_lg = x.bfloat16().float() @ gate.dequantize(torch.float32).t()
+    assert float((lg - ref_lg).abs().max()) < 0.02 * float(ref_lg.abs().max())
+    # softmax top-4 with renormalisation and sigmoid + bias with group-limited choice: same experts as the float gate on
+    # the de-quantized matrix except where two logits tie within bf16 rounding
+    for kw in ({"topk": 4}, {"topk": 4, "scoring": 1, "n_group": 8, "topk_group": 4, "bias": torch.randn(E) * 0.01, "routed_scale": 1.8}):
+        r = Int8Router(gate, **kw)
+        ids, wts = r(x.bfloat16())
+        ids2, wts2 = ops.moe_router(x.bfloat16().float(), gate.dequantize(torch.float32), **kw)
+        same = (ids.sort(-1).values == ids2.sort(-1).values).all(-1)
+        assert float(same.float().mean()) > 0.9 and ids.dtype == torch.int32
+        a = torch.zeros(T, E).scatter_(1, ids.long(), wts)
+        b = torch.zeros(T, E).scatter_(1, ids2.long(), wts2)
+        assert float((a[same] - b[same]).abs().max()) < 0.02 * float(b.abs().max())
+    counts = torch.zeros(E, dtype=torch.int32)
+    Int8Router.from_weight(w, topk=2)(x.bfloat16(), counts=counts)
+    assert int(counts.sum()) == 2 * T and r.num_experts == E and r.hidden_dim == H

@@ -292,3 +292,28 @@ def test_layernorm_kernel(rows, dim):
     torch.testing.assert_close(y2.float(), F.layer_norm(s.float(), (dim,), w.float(), None, 1e-5), rtol=2e-2, atol=2e-2)
     y3 = ops.layernorm(x.view(rows, 1, dim))          # no affine, leading shape kept
     assert y3.shape == (rows, 1, dim)
+
+
+@pytest.mark.parametrize("T", [4, 100])
+def test_int8_router_on_the_quantized_kernels(T):
+    """Decode batches take the int8 weight-streaming kernel, larger ones the tensor-core GEMM that expands the codes in its
+    main loop (one scale per expert row: a 2048-wide group); selection by the one-warp-per-token kernel."""
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.moe.router_int8 import Int8Router
+    torch.manual_seed(T)
+    E, H = 64, 2048
+    w = torch.randn(E, H) * 0.02
+    x = torch.randn(T, H).to(torch.bfloat16)
+    kw = {"topk": 4, "scoring": 1, "n_group": 8, "topk_group": 4, "bias": torch.randn(E) * 0.01, "routed_scale": 1.8}
+    r = Int8Router.from_weight(w.cuda(), **{**kw, "bias": kw["bias"].cuda()})
+    counts = torch.zeros(E, dtype=torch.int32, device="cuda")
+    ids, wts = r(x.cuda(), counts=counts)
+    lg = r.logits(x.cuda()).cpu()
+    wq = r.gate.dequantize(torch.float32).cpu()
+    ref_lg = x.float() @ wq.t()
+    assert float((lg - ref_lg).abs().max()) < 0.02 * float(ref_lg.abs().max())
+    ids2, wts2 = ops.moe_select(lg, **kw)                   # the PyTorch selection on the same logits
+    assert torch.equal(ids.cpu().sort(-1).values, ids2.sort(-1).values)
+    a = torch.zeros(T, E).scatter_(1, ids.cpu().long(), wts.cpu())
+    b = torch.zeros(T, E).scatter_(1, ids2.long(), wts2)
+    assert float((a - b).abs().max()) < 1e-4 and int(counts.sum()) == 4 * T
