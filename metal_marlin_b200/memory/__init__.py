@@ -10,7 +10,8 @@ request path calls ``cudaMalloc``.
 from .arena import Arena, BumpAllocator, WorkspaceBuffer
 from .expert_cache import ExpertCache
 from .pressure import MemoryPressureMonitor, PressureLevel
+from .pools import BufferPool, BufferPoolStats, RingBuffer, TransferStream, get_ring_buffer, reset_ring_buffer
 from .streaming import PinnedPool, WeightStreamer
 
 __all__ = ["Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "MemoryPressureMonitor", "PressureLevel", "PinnedPool",
-           "WeightStreamer"]
+           "WeightStreamer", "BufferPool", "BufferPoolStats", "RingBuffer", "TransferStream", "get_ring_buffer", "reset_ring_buffer"]
