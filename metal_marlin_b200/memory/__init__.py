@@ -8,10 +8,10 @@ allocator bookkeeping is native (``csrc/runtime.cpp``); tensors handed out are v
 request path calls ``cudaMalloc``.
 """
 from .arena import Arena, BumpAllocator, WorkspaceBuffer
-from .expert_cache import ExpertCache
+from .expert_cache import ExpertCache, TileCoordinator
 from .pressure import MemoryPressureMonitor, PressureLevel
 from .pools import BufferPool, BufferPoolStats, RingBuffer, TransferStream, get_ring_buffer, reset_ring_buffer
 from .streaming import PinnedPool, WeightStreamer
 
-__all__ = ["Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "MemoryPressureMonitor", "PressureLevel", "PinnedPool",
+__all__ = ["Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "TileCoordinator", "MemoryPressureMonitor", "PressureLevel", "PinnedPool",
            "WeightStreamer", "BufferPool", "BufferPoolStats", "RingBuffer", "TransferStream", "get_ring_buffer", "reset_ring_buffer"]

@@ -52,3 +52,48 @@ class ExpertCache:
 
     def __len__(self) -> int:
         return len(self._d)
+
+
+class TileCoordinator:
+    """Tile arithmetic over one expert matrix ``[out_features, in_features]``: linear tile index <-> (row tile, column
+    tile) <-> element ranges, in the device layout of the FP4 weights by default (16 output rows x 64 input columns per
+    tile, ``qtile[out / 16, in / 64, 32, 4]``), so partial-expert prefetch and cache code can name the bytes of a tile.
+    Parity: reference ``metal_marlin/expert_cache.py:628`` (``TileCoordinator``)."""
+
+    def __init__(self, weight_shape: Tuple[int, int], tile_shape: Tuple[int, int] = (16, 64)):
+        self.weight_shape, self.tile_shape = tuple(weight_shape), tuple(tile_shape)
+        self.num_row_tiles = -(-weight_shape[0] // tile_shape[0])
+        self.num_col_tiles = -(-weight_shape[1] // tile_shape[1])
+        self.num_tiles = self.num_row_tiles * self.num_col_tiles
+
+    def tile_to_coords(self, tile_idx: int) -> Tuple[int, int]:
+        if not 0 <= tile_idx < self.num_tiles:
+            raise IndexError(tile_idx)
+        return divmod(tile_idx, self.num_col_tiles)
+
+    def coords_to_tile(self, row_tile: int, col_tile: int) -> int:
+        if not (0 <= row_tile < self.num_row_tiles and 0 <= col_tile < self.num_col_tiles):
+            raise IndexError((row_tile, col_tile))
+        return row_tile * self.num_col_tiles + col_tile
+
+    def tile_bounds(self, tile_idx: int) -> Tuple[slice, slice]:
+        """Element ranges ``(rows, cols)`` of a tile, clipped at the matrix edge."""
+        r, c = self.tile_to_coords(tile_idx)
+        th, tw = self.tile_shape
+        return (slice(r * th, min((r + 1) * th, self.weight_shape[0])), slice(c * tw, min((c + 1) * tw, self.weight_shape[1])))
+
+    def tiles_for_rows(self, row0: int, row1: int) -> List[int]:
+        """Tiles that hold any of the output rows ``[row0, row1)`` (a row-sharded or partially fetched expert)."""
+        th = self.tile_shape[0]
+        return [self.coords_to_tile(r, c) for r in range(row0 // th, -(-row1 // th)) for c in range(self.num_col_tiles)]
+
+    def tile_nbytes(self, bits: int = 4) -> int:
+        return self.tile_shape[0] * self.tile_shape[1] * bits // 8
+
+    def byte_offset(self, tile_idx: int, bits: int = 4) -> int:
+        """Offset of a tile inside a matrix stored tile after tile (row tiles outermost)."""
+        return tile_idx * self.tile_nbytes(bits)
+
+    def iter_tiles(self):
+        for i in range(self.num_tiles):
+            yield (i, *self.tile_to_coords(i))

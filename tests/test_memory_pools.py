@@ -46,3 +46,23 @@ def test_transfer_stream_cpu_passthrough_and_ring_buffer():
     get_ring_buffer("cpu").alloc((8,), torch.uint8)
     reset_ring_buffer("cpu")
     assert get_ring_buffer("cpu").used == 0
+
+
+def test_tile_coordinator_matches_the_fp4_tile_layout():
+    from metal_marlin_b200.formats import fp4 as fp4fmt
+    from metal_marlin_b200.memory import TileCoordinator
+    tc = TileCoordinator((40, 200))
+    assert (tc.num_row_tiles, tc.num_col_tiles, tc.num_tiles) == (3, 4, 12)
+    assert tc.tile_to_coords(5) == (1, 1) and tc.coords_to_tile(2, 3) == 11
+    rows, cols = tc.tile_bounds(11)
+    assert (rows.start, rows.stop, cols.start, cols.stop) == (32, 40, 192, 200)
+    assert tc.tiles_for_rows(16, 33) == [4, 5, 6, 7, 8, 9, 10, 11] and tc.tile_nbytes() == 512 and tc.byte_offset(3) == 1536
+    assert [t[0] for t in tc.iter_tiles()] == list(range(12))
+    # the same grid as the device layout of a quantized matrix
+    codes, scales = fp4fmt.quantize_codes(torch.randn(48, 256), 64)
+    qtile, _stile, _gs = fp4fmt.to_tile_layout(codes, scales)
+    full = TileCoordinator((48, 256))
+    assert qtile.shape[:2] == (full.num_row_tiles, full.num_col_tiles) and qtile[0, 0].numel() * 4 == full.tile_nbytes()
+    import pytest
+    with pytest.raises(IndexError):
+        tc.tile_to_coords(12)

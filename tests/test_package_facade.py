@@ -10,5 +10,5 @@ def test_all_exports_resolve():
         except Exception as e:      # noqa: BLE001 - the test reports every failing name at once
             missing.append((name, repr(e)[:120]))
     assert not missing, missing
-    assert mm.MarlinPipeline is mm.MMFP4Pipeline and mm.KVCacheTorch is mm.KVCache
+    assert issubclass(mm.MarlinPipeline, mm.MMFP4Pipeline) and mm.KVCacheTorch is mm.KVCache
     assert len(mm.__all__) > 150 and "TrellisForCausalLM" in dir(mm)
