@@ -124,7 +124,8 @@ def test_speculative_decoding_inside_the_batch_engine(draft_kind):
     lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
     prompts = [[5, 6, 7, 5, 6, 7, 5, 6], list(range(1, 40)), [9, 9, 9, 9], [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5], [7] * 20, [11, 12, 13],
                list(range(50, 90)), [2, 4, 2, 4, 2, 4]]
-    cfg = EngineConfig(num_kv_blocks=96, block_size=16, max_model_len=128, max_chunk=128, max_prefill_tokens=512, use_cuda_graphs=False)
+    cfg = EngineConfig(num_kv_blocks=96, block_size=16, max_model_len=128, max_chunk=128, max_prefill_tokens=512, use_cuda_graphs=False,
+                       request_timeout_s=900.0)      # a loaded test machine must not turn into a 'timeout' finish reason
     want = LLMEngine(lm.model, cfg).generate(prompts, max_new_tokens=20)
     eng = LLMEngine(lm.model, cfg)
     draft = "ngram" if draft_kind == "ngram" else MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
