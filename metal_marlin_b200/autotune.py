@@ -142,11 +142,11 @@ class KernelAutoTuner:
             t_stream, t_gemm = [], []
             for m in self.batch_sizes:
                 x = torch.randn(m, in_f, device=self.device).to(torch.bfloat16)
-                with override(GEMV_MAX_M=_BIG, GEMV_LIMITS={}):
+                with override(GEMV_MAX_M=_BIG, GEMV_LIMITS={}, GEMV_BIG_WEIGHT=_BIG * _BIG):
                     a = self._time(lambda: ops.linear(x, W))
                 b = float("inf")
                 if m >= self.min_tc:
-                    with override(GEMV_MAX_M=0, GEMV_LIMITS={}):
+                    with override(GEMV_MAX_M=0, GEMV_LIMITS={}, GEMV_BIG_WEIGHT=_BIG * _BIG):
                         b = self._time(lambda: ops.linear(x, W))
                 t_stream.append(a)
                 t_gemm.append(b)
@@ -281,7 +281,9 @@ def load_config(path: Optional[str] = None, apply: bool = True) -> Optional[Tune
 def get_optimal_config(tokens: int, out_features: int, in_features: int) -> Dict[str, object]:
     """Which kernel a dense FP4 projection of this shape takes for ``tokens`` rows under the installed table."""
     from . import ops
-    lim = ops.GEMV_LIMITS.get((out_features, in_features), ops.GEMV_MAX_M)
+    lim = ops.GEMV_LIMITS.get((out_features, in_features))
+    if lim is None:
+        lim = min(ops.GEMV_MAX_M, ops.GEMV_BIG_MAX_M) if out_features * in_features >= ops.GEMV_BIG_WEIGHT else ops.GEMV_MAX_M
     return {"kernel": "fp4_gemv" if tokens <= lim else "fp4_gemm_tcgen05", "limit": lim,
             "tuned": (out_features, in_features) in ops.GEMV_LIMITS}
 

@@ -114,7 +114,8 @@ def persistent_decode_step(state: DecodeState, timed: bool = False) -> torch.Ten
 
 def select_decode_kernel(M: int, N: int, K: int) -> str:
     """Name of the kernel an FP4 projection ``[M, K] x [N, K]^T`` takes under the installed thresholds."""
-    lim = ops.GEMV_LIMITS.get((N, K), ops.GEMV_MAX_M) if ops.GEMV_LIMITS else ops.GEMV_MAX_M
+    from ..autotune import get_optimal_config
+    lim = get_optimal_config(M, N, K)["limit"]
     if M > lim and not ops.NO_TCGEN05:
         return "fp4_gemm_tcgen05"
     if M <= ops.GEMV_FUSED_PROLOGUE_MAX_M:

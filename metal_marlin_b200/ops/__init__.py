@@ -160,8 +160,18 @@ def layernorm(x, w=None, b=None, eps=1e-5, *, delta=None, resid_out=None, out=No
     return out.view(shape)
 
 
+GEMV_BIG_WEIGHT = 24_000_000     # weights of this many elements or more leave the streaming kernel at GEMV_BIG_MAX_M tokens already
+GEMV_BIG_MAX_M = 24              # (measured in whole Qwen3-4B steps: the tcgen05 GEMM wins at 32 tokens, 3942 vs 3584 tok/s, and loses at 24)
+
+
 def _gemv_limit(W) -> int:
-    return GEMV_LIMITS.get((W.out_features, W.in_features), GEMV_MAX_M) if GEMV_LIMITS else GEMV_MAX_M
+    if GEMV_LIMITS:
+        lim = GEMV_LIMITS.get((W.out_features, W.in_features))
+        if lim is not None:
+            return lim
+    if W.out_features * W.in_features >= GEMV_BIG_WEIGHT:
+        return min(GEMV_MAX_M, GEMV_BIG_MAX_M)
+    return GEMV_MAX_M
 
 
 def linear(x, W: FP4Weight, *, delta=None, norm_w=None, eps=1e-6, resid_out=None, act=0, bias=None, out_add=None,
