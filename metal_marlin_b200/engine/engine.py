@@ -43,9 +43,54 @@ class EngineConfig:
     scheduler_policy: str = "priority"   # "priority" (continuous batching with priorities) | "fcfs" | "shortest_first" | "longest_first"
     preemption_mode: str = "recompute"   # "swap": a preempted sequence keeps its cache rows in pinned host memory and resumes from them
     swap_space_blocks: int = 0           # host blocks for swapped sequences (0 with "swap": as many as ``num_kv_blocks``)
+    adaptive_prefill_budget: bool = False   # shrink the prompt-token budget under memory pressure / after an out-of-memory error, regrow later
 
 
 HISTORY_LEN = 256      # most recent tokens (prompt tail + generated) the repetition penalty looks at
+
+
+class PrefillBudget:
+    """Memory-aware prompt-token budget of an engine: the scheduler's ``max_prefill_tokens`` is halved when the device is
+    critically full or a prompt pass ran out of memory (never below ``floor``), held under a warning level, and grown by a
+    quarter per quiet iteration back to the configured value.  Activations of a prompt pass scale with its token count, so this
+    is the batch-size knob that matters once the cache itself is a fixed pool.
+
+    Parity: reference ``metal_marlin/inference/mmfp4_pipeline.py:2735`` (``_dynamic_batch``: halve on pressure, recover
+    gradually) and ``metal_marlin/memory/memory_pressure.py``."""
+
+    def __init__(self, scheduler_cfg, monitor=None, floor: int = 128):
+        from ..memory.pressure import MemoryPressureMonitor
+        self.cfg = scheduler_cfg
+        self.ceiling = scheduler_cfg.max_prefill_tokens
+        self.floor = min(floor, self.ceiling)
+        self.monitor = monitor or MemoryPressureMonitor()
+        self.shrinks = self.ooms = 0
+
+    @property
+    def value(self) -> int:
+        return self.cfg.max_prefill_tokens
+
+    def _set(self, v: int) -> int:
+        self.cfg.max_prefill_tokens = max(self.floor, min(self.ceiling, int(v)))
+        return self.cfg.max_prefill_tokens
+
+    def before_iteration(self) -> int:
+        from ..memory.pressure import PressureLevel
+        level = self.monitor.check()
+        if level is PressureLevel.CRITICAL:
+            if self.value > self.floor:
+                self.shrinks += 1
+            return self._set(self.value // 2)
+        if level is PressureLevel.NORMAL and self.value < self.ceiling:
+            return self._set(self.value + max(16, self.value // 4))
+        return self.value
+
+    def on_oom(self) -> int:
+        self.ooms += 1
+        return self._set(self.value // 2)
+
+    def stats(self) -> dict:
+        return {"max_prefill_tokens": self.value, "configured": self.ceiling, "shrinks": self.shrinks, "ooms": self.ooms}
 
 
 def _packed(specs, pin: bool, device=None):
@@ -206,6 +251,7 @@ class LLMEngine:
         else:
             from .fcfs import FCFSScheduler, PrefillStrategy
             self.scheduler = FCFSScheduler(scfg, self.cache, prefill_strategy=PrefillStrategy(c.scheduler_policy))
+        self.prefill_budget = PrefillBudget(self.scheduler.cfg) if c.adaptive_prefill_budget and coordinator is None else None
         self.max_blocks = -(-c.max_model_len // c.block_size)
         self._buckets: Dict[int, _DecodeBucket] = {}
         self._lock = threading.RLock()
@@ -299,6 +345,8 @@ class LLMEngine:
     def step(self) -> List[RunningRequest]:
         """One engine iteration.  Returns the requests that finished in it."""
         with self._lock:
+            if self.prefill_budget is not None and self.lockstep is None:
+                self.prefill_budget.before_iteration()
             out = self.scheduler.schedule()
             if out.swap_out or out.swap_in:
                 self._apply_swaps(out)
@@ -415,7 +463,20 @@ class LLMEngine:
         arrays = self._prefill_arrays(out)
         if self.coordinator is not None:
             self.coordinator.announce_prefill(arrays)
-        logits = self._exec_prefill(arrays)
+        if self.prefill_budget is not None and self.lockstep is None:
+            try:
+                logits = self._exec_prefill(arrays)
+            except torch.cuda.OutOfMemoryError:
+                # the pass did not fit: give the allocator's cache back, halve the budget and plan these chunks again (their
+                # progress is only recorded after a pass, so dropping them from this iteration's plan is the whole roll-back)
+                torch.cuda.empty_cache()
+                if sum(ch.length for ch in out.prefill) <= self.prefill_budget.floor:
+                    raise
+                self.prefill_budget.on_oom()
+                out.prefill.clear()
+                return {}
+        else:
+            logits = self._exec_prefill(arrays)
         # sample a first token only for requests whose prefill completes now and that have no output yet
         rows, reqs = [], []
         for j, ch in enumerate(out.prefill):
@@ -643,6 +704,8 @@ class LLMEngine:
     def stats(self) -> dict:
         s = self.scheduler.stats()
         s.update(iterations=self.iterations, tokens_generated=self.tokens_generated, last_error=self.last_error)
+        if self.prefill_budget is not None:
+            s["prefill_budget"] = self.prefill_budget.stats()
         if self.spec is not None:
             s.update(spec_proposed=self.spec_proposed, spec_accepted=self.spec_accepted,
                      spec_acceptance_rate=self.spec_accepted / max(1, self.spec_proposed))

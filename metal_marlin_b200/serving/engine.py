@@ -45,6 +45,7 @@ class EngineConfig:
     scheduler_policy: str = "priority"    # "priority" | "fcfs" | "shortest_first" | "longest_first"
     preemption_mode: str = "recompute"    # "swap": preempted sequences park their cache rows in pinned host memory
     swap_space_blocks: int = 0
+    adaptive_prefill_budget: bool = True   # shrink the prompt-token budget under memory pressure or after an out-of-memory error
     # multi-GPU (job started with torchrun, one process per GPU): tensor / expert / data parallel degrees
     tp: int = 1
     ep: int = 1
@@ -85,7 +86,8 @@ class ServingEngine:
                                 max_model_len=config.max_model_len, max_num_seqs=config.max_batch_size,
                                 request_timeout_s=config.request_timeout, kv_cache_dtype=config.kv_cache_dtype,
                                 scheduler_policy=config.scheduler_policy, preemption_mode=config.preemption_mode,
-                                swap_space_blocks=config.swap_space_blocks)
+                                swap_space_blocks=config.swap_space_blocks,
+                                adaptive_prefill_budget=config.adaptive_prefill_budget)
         from ..inference.pipeline import MMFP4Pipeline
         par = dict(tp=config.tp, ep=config.ep, dp=1)        # data-parallel replicas are whole servers behind serving/router.py
         if self.mock:

@@ -340,3 +340,48 @@ def test_engine_swap_preemption_keeps_the_output(kv_dtype):
     st = eng.scheduler.stats()
     assert got == want and st["swaps"] >= 1 and st["swapped_out"] == 0
     assert len(eng.scheduler._host_free) == eng.swap_blocks == 5
+
+
+def test_prefill_budget_follows_memory_pressure_and_recovers_from_oom():
+    import torch
+    from metal_marlin_b200.engine.engine import PrefillBudget
+    from metal_marlin_b200.memory.pressure import MemoryPressureMonitor
+    free = {"v": 50}
+    mon = MemoryPressureMonitor(probe=lambda: (free["v"], 100))
+    cfg = SchedulerConfig(max_prefill_tokens=1024)
+    b = PrefillBudget(cfg, mon, floor=128)
+    assert b.before_iteration() == 1024
+    free["v"] = 3                                    # 97 % used: critical
+    assert b.before_iteration() == 512 and b.before_iteration() == 256 and cfg.max_prefill_tokens == 256
+    free["v"] = 10                                   # warning: hold
+    assert b.before_iteration() == 256
+    free["v"] = 60                                   # normal: grow by a quarter per iteration up to the configured value
+    assert b.before_iteration() == 320 and b.before_iteration() == 400
+    for _ in range(10):
+        b.before_iteration()
+    assert b.value == 1024 and b.shrinks == 2
+    assert b.on_oom() == 512 and b.stats()["ooms"] == 1
+    for _ in range(5):
+        b.on_oom()
+    assert b.value == 128                            # never below the floor
+
+    # an engine whose prompt pass runs out of memory once: the chunks are planned again under half the budget
+    lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    prompts = [list(range(1, 60)), list(range(70, 100))]
+    want = [lm.generate([p], max_new_tokens=6)[0] for p in prompts]
+    eng = LLMEngine(lm.model, EngineConfig(num_kv_blocks=32, block_size=16, max_model_len=128, use_cuda_graphs=False,
+                                           max_prefill_tokens=256, max_chunk=256, adaptive_prefill_budget=True))
+    eng.prefill_budget.monitor = MemoryPressureMonitor(probe=lambda: (60, 100))
+    eng.prefill_budget.floor = 16
+    real, calls = eng._exec_prefill, {"n": 0, "sizes": []}
+
+    def flaky(a):
+        calls["n"] += 1
+        calls["sizes"].append(len(a["ids"]))
+        if calls["n"] == 1:
+            raise torch.cuda.OutOfMemoryError("simulated")
+        return real(a)
+    eng._exec_prefill = flaky
+    got = eng.generate(prompts, max_new_tokens=6)
+    assert got == want and eng.stats()["prefill_budget"]["ooms"] == 1
+    assert calls["sizes"][0] == 89 and calls["sizes"][1] <= 128
