@@ -50,21 +50,31 @@ HISTORY_LEN = 256      # most recent tokens (prompt tail + generated) the repeti
 
 
 class PrefillBudget:
-    """Memory-aware prompt-token budget of an engine: the scheduler's ``max_prefill_tokens`` is halved when the device is
-    critically full or a prompt pass ran out of memory (never below ``floor``), held under a warning level, and grown by a
-    quarter per quiet iteration back to the configured value.  Activations of a prompt pass scale with its token count, so this
-    is the batch-size knob that matters once the cache itself is a fixed pool.
+    """Memory-aware prompt-token budget of an engine.  Before every iteration the free device memory (what the driver
+    reports plus what the caching allocator holds unused) is compared with the transient memory a prompt pass of the
+    current budget needs: below 1.25 x the need the scheduler's ``max_prefill_tokens`` is halved (never below ``floor``),
+    above 2 x the need of a budget a quarter larger it grows back toward the configured value.  A prompt pass that still
+    runs out of memory halves it at once and its chunks are planned again.  Activations of a prompt pass scale with its token
+    count, so this is the batch-size knob that matters once the cache itself is a fixed pool; a device that is simply full of
+    pre-allocated pools is not pressure by this measure.
 
-    Parity: reference ``metal_marlin/inference/mmfp4_pipeline.py:2735`` (``_dynamic_batch``: halve on pressure, recover
-    gradually) and ``metal_marlin/memory/memory_pressure.py``."""
+    Parity: reference ``metal_marlin/inference/mmfp4_pipeline.py:2735`` (``_dynamic_batch``: shrink on pressure, recover
+    gradually, per-request memory estimate) and ``metal_marlin/memory/memory_pressure.py``."""
 
-    def __init__(self, scheduler_cfg, monitor=None, floor: int = 128):
-        from ..memory.pressure import MemoryPressureMonitor
+    def __init__(self, scheduler_cfg, need_fn, free_fn=None, floor: int = 128):
         self.cfg = scheduler_cfg
         self.ceiling = scheduler_cfg.max_prefill_tokens
         self.floor = min(floor, self.ceiling)
-        self.monitor = monitor or MemoryPressureMonitor()
+        self.need_fn = need_fn                       # tokens -> bytes a prompt pass of that many tokens allocates
+        self.free_fn = free_fn or self._device_free
         self.shrinks = self.ooms = 0
+
+    @staticmethod
+    def _device_free() -> int:
+        if not torch.cuda.is_available():
+            return 1 << 62
+        free, _total = torch.cuda.mem_get_info()
+        return free + torch.cuda.memory_reserved() - torch.cuda.memory_allocated()
 
     @property
     def value(self) -> int:
@@ -75,14 +85,15 @@ class PrefillBudget:
         return self.cfg.max_prefill_tokens
 
     def before_iteration(self) -> int:
-        from ..memory.pressure import PressureLevel
-        level = self.monitor.check()
-        if level is PressureLevel.CRITICAL:
+        free = self.free_fn()
+        if free < 1.25 * self.need_fn(self.value):
             if self.value > self.floor:
                 self.shrinks += 1
             return self._set(self.value // 2)
-        if level is PressureLevel.NORMAL and self.value < self.ceiling:
-            return self._set(self.value + max(16, self.value // 4))
+        if self.value < self.ceiling:
+            grown = min(self.ceiling, self.value + max(16, self.value // 4))
+            if free > 2.0 * self.need_fn(grown):
+                return self._set(grown)
         return self.value
 
     def on_oom(self) -> int:
@@ -251,7 +262,10 @@ class LLMEngine:
         else:
             from .fcfs import FCFSScheduler, PrefillStrategy
             self.scheduler = FCFSScheduler(scfg, self.cache, prefill_strategy=PrefillStrategy(c.scheduler_policy))
-        self.prefill_budget = PrefillBudget(self.scheduler.cfg) if c.adaptive_prefill_budget and coordinator is None else None
+        self.prefill_budget = None
+        if c.adaptive_prefill_budget and coordinator is None:
+            from ..inference.prefill import estimate_chunk_bytes
+            self.prefill_budget = PrefillBudget(self.scheduler.cfg, lambda n: estimate_chunk_bytes(model.cfg, n, c.max_model_len))
         self.max_blocks = -(-c.max_model_len // c.block_size)
         self._buckets: Dict[int, _DecodeBucket] = {}
         self._lock = threading.RLock()

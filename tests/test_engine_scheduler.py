@@ -345,18 +345,16 @@ def test_engine_swap_preemption_keeps_the_output(kv_dtype):
 def test_prefill_budget_follows_memory_pressure_and_recovers_from_oom():
     import torch
     from metal_marlin_b200.engine.engine import PrefillBudget
-    from metal_marlin_b200.memory.pressure import MemoryPressureMonitor
-    free = {"v": 50}
-    mon = MemoryPressureMonitor(probe=lambda: (free["v"], 100))
+    free = {"v": 10_000_000}
     cfg = SchedulerConfig(max_prefill_tokens=1024)
-    b = PrefillBudget(cfg, mon, floor=128)
-    assert b.before_iteration() == 1024
-    free["v"] = 3                                    # 97 % used: critical
+    b = PrefillBudget(cfg, need_fn=lambda n: n * 1000, free_fn=lambda: free["v"], floor=128)
+    assert b.before_iteration() == 1024               # 10 MB free, 1 MB needed
+    free["v"] = 500_000                               # less than 1.25 x the need of 1024 and of 512 tokens, enough for 256
     assert b.before_iteration() == 512 and b.before_iteration() == 256 and cfg.max_prefill_tokens == 256
-    free["v"] = 10                                   # warning: hold
-    assert b.before_iteration() == 256
-    free["v"] = 60                                   # normal: grow by a quarter per iteration up to the configured value
-    assert b.before_iteration() == 320 and b.before_iteration() == 400
+    assert b.before_iteration() == 256                # 320 tokens would need 2 x 320 kB: no room to grow
+    free["v"] = 900_000                               # room for 320 (640 kB x ... ) and 400, not for 500
+    assert b.before_iteration() == 320 and b.before_iteration() == 400 and b.before_iteration() == 400
+    free["v"] = 10_000_000
     for _ in range(10):
         b.before_iteration()
     assert b.value == 1024 and b.shrinks == 2
@@ -371,7 +369,7 @@ def test_prefill_budget_follows_memory_pressure_and_recovers_from_oom():
     want = [lm.generate([p], max_new_tokens=6)[0] for p in prompts]
     eng = LLMEngine(lm.model, EngineConfig(num_kv_blocks=32, block_size=16, max_model_len=128, use_cuda_graphs=False,
                                            max_prefill_tokens=256, max_chunk=256, adaptive_prefill_budget=True))
-    eng.prefill_budget.monitor = MemoryPressureMonitor(probe=lambda: (60, 100))
+    assert eng.prefill_budget.need_fn(256) > eng.prefill_budget.need_fn(128) > 0
     eng.prefill_budget.floor = 16
     real, calls = eng._exec_prefill, {"n": 0, "sizes": []}
 
