@@ -359,8 +359,9 @@ class LLMEngine:
     def step(self) -> List[RunningRequest]:
         """One engine iteration.  Returns the requests that finished in it."""
         with self._lock:
-            if self.prefill_budget is not None and self.lockstep is None:
-                self.prefill_budget.before_iteration()
+            if self.prefill_budget is not None and self.lockstep is None and (
+                    self.scheduler.num_waiting or any(r.status is RequestStatus.PREFILLING for r in self.scheduler.running)):
+                self.prefill_budget.before_iteration()          # only iterations that can schedule prompt tokens pay the query
             out = self.scheduler.schedule()
             if out.swap_out or out.swap_in:
                 self._apply_swaps(out)
