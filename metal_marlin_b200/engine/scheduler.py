@@ -50,6 +50,7 @@ class SchedulerConfig:
     fcfs: bool = False                     # ignore priorities: strict arrival order
     preemption_mode: str = "recompute"     # "swap": a fully prefilled victim keeps its cache rows in host blocks
     swap_space_blocks: int = 0             # host blocks available to swapped sequences
+    proactive_evict_above: float = 0.9     # cached prefix blocks are released while more than this share of the pool is in use
 
 
 class BatchScheduler:
@@ -179,6 +180,8 @@ class BatchScheduler:
     def schedule(self) -> SchedulerOutput:
         out = SchedulerOutput()
         self._check_starvation()
+        if self.cache.prefix is not None and self.cfg.proactive_evict_above < 1.0:
+            self.cache.prefix.proactive_evict(self.cfg.proactive_evict_above)
         budget = self.cfg.max_num_batched_tokens
         # phase 1: every fully prefilled running sequence decodes one token; grow its KV by one slot
         order = sorted(self.running, key=lambda r: (-r.effective_priority, r.arrival))

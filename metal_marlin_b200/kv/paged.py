@@ -255,6 +255,8 @@ class EvictionPolicy(enum.Enum):
     LRU = "lru"
     LFU = "lfu"
     WEIGHTED = "weighted"    # age / (1 + hits)
+    FIFO = "fifo"            # oldest insertion first
+    ADAPTIVE = "adaptive"    # recency when the cache rarely hits, frequency when it hits often (weights follow the hit rate)
 
 
 def hash_tokens(tokens: Sequence[int], parent: str = "") -> str:
@@ -336,12 +338,35 @@ class PrefixCache:
             key = next(iter(self.table))
         elif self.policy is EvictionPolicy.LFU:
             key = min(self.table, key=lambda k: (self.table[k].hits, self.table[k].last_used))
+        elif self.policy is EvictionPolicy.FIFO:
+            key = min(self.table, key=lambda k: self.table[k].created)
+        elif self.policy is EvictionPolicy.ADAPTIVE:
+            rate = self.hits / max(1, self.hits + self.misses)
+            oldest = max(now - cb.last_used for cb in self.table.values()) or 1.0
+            most = max(cb.hits for cb in self.table.values()) or 1
+            key = max(self.table, key=lambda k: (1.0 - rate) * (now - self.table[k].last_used) / oldest
+                      - rate * self.table[k].hits / most)
         else:
             key = max(self.table, key=lambda k: (now - self.table[k].last_used) / (1 + self.table[k].hits))
         cb = self.table.pop(key)
         self.alloc.free(cb.block)
         self.evictions += 1
         return True
+
+    def evict_batch(self, n: int) -> int:
+        """Evict up to ``n`` cached blocks in one go; returns how many went."""
+        done = 0
+        while done < n and self.evict_one():
+            done += 1
+        return done
+
+    def proactive_evict(self, pressure: float = 0.9) -> int:
+        """While more than ``pressure`` of the allocator's blocks are in use, release cached blocks (the ones no sequence
+        holds any more become free), so that admissions do not have to evict one block at a time under load."""
+        n = 0
+        while self.alloc.usage() > pressure and self.evict_one():
+            n += 1
+        return n
 
     def evict_until(self, n_free: int) -> int:
         """Evict cached blocks until the allocator has ``n_free`` free blocks (or the cache is empty)."""

@@ -383,3 +383,42 @@ def test_prefill_budget_follows_memory_pressure_and_recovers_from_oom():
     got = eng.generate(prompts, max_new_tokens=6)
     assert got == want and eng.stats()["prefill_budget"]["ooms"] == 1
     assert calls["sizes"][0] == 89 and calls["sizes"][1] <= 128
+
+
+def test_prefix_cache_fifo_adaptive_and_proactive_eviction():
+    from metal_marlin_b200.kv.paged import BlockAllocator, EvictionPolicy, PrefixCache
+    al = BlockAllocator(16, 4)
+    pc = PrefixCache(al, max_blocks=8, policy=EvictionPolicy.FIFO)
+    seqs = [[i] * 4 for i in range(4)]
+    blocks = []
+    for t in seqs:
+        b = al.allocate()
+        blocks.append(b)
+        pc.insert(t, [b])
+        al.free(b)                       # only the cache holds the block now
+    for b in pc.match(seqs[0]):          # a hit does not save the oldest entry under FIFO
+        al.free(b)
+    assert pc.evict_one() and not pc.match(seqs[0]) and al.ref_count(blocks[0]) == 0
+    assert pc.evict_batch(2) == 2 and len(pc.table) == 1
+    # adaptive: with a high hit rate the never-hit entry goes although it is the most recent one
+    al2 = BlockAllocator(16, 4)
+    ad = PrefixCache(al2, max_blocks=8, policy=EvictionPolicy.ADAPTIVE)
+    for t in seqs[:3]:
+        b = al2.allocate()
+        ad.insert(t, [b])
+        al2.free(b)
+    for _ in range(5):
+        for t in seqs[:2]:
+            for b in ad.match(t):
+                al2.free(b)
+    assert ad.evict_one() and ad.match(seqs[0]) and ad.match(seqs[1])
+    assert len(ad.table) == 2
+    # proactive eviction: above 75 % usage cached blocks are released until usage is back under it
+    al3 = BlockAllocator(8, 4)
+    pe = PrefixCache(al3, max_blocks=8)
+    held = [al3.allocate() for _ in range(3)]
+    for i in range(4):
+        b = al3.allocate()
+        pe.insert([100 + i] * 4, [b])
+        al3.free(b)
+    assert al3.usage() == 7 / 8 and pe.proactive_evict(0.75) == 1 and al3.usage() == 6 / 8 and len(held) == 3
