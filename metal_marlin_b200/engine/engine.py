@@ -359,6 +359,8 @@ class LLMEngine:
     def step(self) -> List[RunningRequest]:
         """One engine iteration.  Returns the requests that finished in it."""
         with self._lock:
+            if self.iterations % 64 == 63 and not self.recurrent and self.coordinator is None and self.lockstep is None:
+                self.cache.compact()         # packs the blocks in use when the free space has crumbled (rarely true)
             if self.prefill_budget is not None and self.lockstep is None and (
                     self.scheduler.num_waiting or any(r.status is RequestStatus.PREFILLING for r in self.scheduler.running)):
                 self.prefill_budget.before_iteration()          # only iterations that can schedule prompt tokens pay the query

@@ -125,6 +125,31 @@ class BlockAllocator:
     def usage(self) -> float:
         return self.num_allocated / max(1, self.num_blocks)
 
+    def needs_compaction(self, max_fragmentation: float = 0.75, max_runs: int = 32) -> bool:
+        """The free space is split so badly that contiguous requests suffer (parity: the reference compacts above a
+        fragmentation of 0.75 or more than 32 free runs)."""
+        return self.fragmentation() > max_fragmentation or len(self.free_runs()) > max_runs
+
+    def compaction_plan(self) -> List[Tuple[int, int]]:
+        """Moves ``(src, dst)`` that pack the allocated blocks into the lowest ids: the highest allocated block goes into
+        the lowest hole until no hole lies below an allocated block.  Apply with :meth:`apply_moves`."""
+        holes = sorted(self._free_set)
+        used = sorted((b for b in range(self.num_blocks) if self._ref[b] > 0), reverse=True)
+        moves = []
+        for src, dst in zip(used, holes):
+            if dst >= src:
+                break
+            moves.append((src, dst))
+        return moves
+
+    def apply_moves(self, moves: Sequence[Tuple[int, int]]) -> None:
+        """Book-keeping of a compaction: reference counts follow the blocks, the free list is rebuilt."""
+        for src, dst in moves:
+            assert self._ref[dst] == 0 and self._ref[src] > 0
+            self._ref[dst], self._ref[src] = self._ref[src], 0
+        self._free = [b for b in range(self.num_blocks - 1, -1, -1) if self._ref[b] == 0]
+        self._free_set = set(self._free)
+
 
 class MultimodalBlockAllocator(BlockAllocator):
     """Block allocator with a reserved region for vision-encoder tokens (image blocks are
@@ -429,6 +454,28 @@ class PagedKVCache:
 
     def release(self, sid) -> None:
         self.table.remove(sid)
+
+    def compact(self, copy_fn=None, force: bool = False) -> int:
+        """Pack the blocks in use into the lowest ids when the allocator asks for it (or ``force``): every moved block is
+        copied with ``copy_fn(src, dst)`` (default: the cache's own copy function) and every page table and prefix-cache
+        entry that named it is rewritten.  Returns the number of blocks moved.  Call between iterations only."""
+        if not force and not self.alloc.needs_compaction():
+            return 0
+        moves = self.alloc.compaction_plan()
+        if not moves:
+            return 0
+        copy_fn = copy_fn or self.copy_fn
+        remap = dict(moves)
+        for src, dst in moves:
+            if copy_fn is not None:
+                copy_fn(src, dst)
+        self.alloc.apply_moves(moves)
+        for ent in self.table.seqs.values():
+            ent.blocks[:] = [remap.get(b, b) for b in ent.blocks]
+        if self.prefix is not None:
+            for cb in self.prefix.table.values():
+                cb.block = remap.get(cb.block, cb.block)
+        return len(moves)
 
     def stats(self) -> dict:
         s = {"blocks": self.alloc.num_blocks, "free": self.alloc.num_free, "usage": self.alloc.usage(),

@@ -422,3 +422,33 @@ def test_prefix_cache_fifo_adaptive_and_proactive_eviction():
         pe.insert([100 + i] * 4, [b])
         al3.free(b)
     assert al3.usage() == 7 / 8 and pe.proactive_evict(0.75) == 1 and al3.usage() == 6 / 8 and len(held) == 3
+
+
+def test_block_compaction_rewrites_tables_and_prefix_entries():
+    moved = []
+    cache = PagedKVCache(12, 4, enable_prefix_cache=True, copy_fn=lambda s, d: moved.append((s, d)))
+    toks = {sid: [ord(sid) * 10 + i for i in range(8)] for sid in "abcdef"}
+    for sid, t in toks.items():
+        cache.admit(sid, t)
+        cache.publish(sid, t)
+    for sid in "ace":                         # every other sequence leaves: holes between the survivors...
+        cache.release(sid)
+    cache.prefix.evict_until(12)              # ...once the cache's own references to their blocks are gone too
+    before = {sid: list(cache.table.block_table(sid)) for sid in "bdf"}
+    assert cache.alloc.fragmentation() > 0 and not cache.alloc.needs_compaction()
+    assert cache.compact() == 0               # below the thresholds nothing moves
+    n = cache.compact(force=True)
+    assert n == len(moved) > 0
+    after = {sid: list(cache.table.block_table(sid)) for sid in "bdf"}
+    remap = dict(moved)
+    assert all(after[s] == [remap.get(b, b) for b in before[s]] for s in "bdf")
+    used = sorted(b for bl in after.values() for b in bl)
+    assert used == list(range(len(used))) and cache.alloc.fragmentation() == 0.0
+    assert cache.alloc.num_free == 12 - len(used) and all(cache.alloc.ref_count(b) >= 1 for b in used)
+    # allocation still works and hands out the packed free ids
+    assert cache.alloc.allocate_contiguous(4) == list(range(len(used), len(used) + 4))
+    al = PagedKVCache(64, 1, enable_prefix_cache=False).alloc
+    ids = al.allocate_many(64)
+    for b in ids[::2]:
+        al.free(b)
+    assert al.needs_compaction(max_runs=16)   # 32 one-block holes
