@@ -324,23 +324,28 @@ class Transformer:
             # with a sliding window only the keys the chunk's first query can still see are gathered
             return max(0, n_ctx - t - win + 1) if win else 0
 
-        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and len(meta.cu_seqlens) == 2
-                and not isinstance(kv.k[li], ops.FP8KV) and q.stride(2) == 1
+        def _rows(pool, b, lo, n_ctx):
+            """bf16 rows ``[n_ctx - lo, Hk, D]`` of sequence ``b``'s cached keys or values (quantized pools are expanded by
+            their gather kernel, with the window's leading rows cut off afterwards)."""
+            if isinstance(pool, ops.FP8KV):
+                cu_k = meta.cached(("cu_k1", n_ctx), lambda: torch.tensor([0, n_ctx], dtype=torch.int32, device=q.device))
+                return ops.kv_fp8_rows(pool, meta.block_tables[b:b + 1], meta.ctx_lens[b:b + 1], cu_k, n_ctx, n_ctx, bs)[lo:]
+
+            def _slots():
+                tok = torch.arange(lo, n_ctx, device=q.device)
+                return meta.block_tables[b, tok // bs].long() * bs + tok % bs
+            return pool.view(-1, Hk, D)[meta.cached(("slots", b, lo, n_ctx), _slots)]
+
+        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and len(meta.cu_seqlens) == 2 and q.stride(2) == 1
                 and ops.fmha_ok(q.shape[0], int(meta.ctx_lens_host[0]), D, D, q.device)):
             # one long sequence: its cache rows (this chunk included) gathered once, then the tcgen05 attention kernel
             n_ctx = int(meta.ctx_lens_host[0])
             lo = _first_key(q.shape[0], n_ctx)
-
-            def _slots(n_ctx=n_ctx, lo=lo):
-                tok = torch.arange(lo, n_ctx, device=q.device)
-                return meta.block_tables[0, tok // bs].long() * bs + tok % bs
-            slots = meta.cached(("slots", 0, lo, n_ctx), _slots)
-            ops.fmha_prefill(q, kv.k[li].view(-1, Hk, D)[slots], kv.v[li].view(-1, Hk, D)[slots], out.view(-1, Hq, D), self.scale,
+            ops.fmha_prefill(q, _rows(kv.k[li], 0, lo, n_ctx), _rows(kv.v[li], 0, lo, n_ctx), out.view(-1, Hq, D), self.scale,
                              window=win)
             return out
         n_seq = len(meta.cu_seqlens) - 1
-        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and n_seq > 1
-                and not isinstance(kv.k[li], ops.FP8KV) and q.stride(2) == 1
+        if (meta.attn_mask is None and q.dtype == torch.bfloat16 and n_seq > 1 and q.stride(2) == 1
                 and all(ops.fmha_ok(meta.cu_seqlens[b + 1] - meta.cu_seqlens[b], int(meta.ctx_lens_host[b]), D, D, q.device)
                         for b in range(n_seq))):
             # several long sequences: the tcgen05 attention kernel sequence by sequence (a launch per sequence costs
@@ -349,12 +354,7 @@ class Transformer:
                 s0, e0 = meta.cu_seqlens[b], meta.cu_seqlens[b + 1]
                 n_ctx = int(meta.ctx_lens_host[b])
                 lo = _first_key(e0 - s0, n_ctx)
-
-                def _slots(b=b, n_ctx=n_ctx, lo=lo):
-                    tok = torch.arange(lo, n_ctx, device=q.device)
-                    return meta.block_tables[b, tok // bs].long() * bs + tok % bs
-                slots = meta.cached(("slots", b, lo, n_ctx), _slots)
-                ops.fmha_prefill(q[s0:e0], kv.k[li].view(-1, Hk, D)[slots], kv.v[li].view(-1, Hk, D)[slots],
+                ops.fmha_prefill(q[s0:e0], _rows(kv.k[li], b, lo, n_ctx), _rows(kv.v[li], b, lo, n_ctx),
                                  out[s0:e0].view(-1, Hq, D), self.scale, window=win)
             return out
         if meta.attn_mask is None and q.dtype == torch.bfloat16:

@@ -209,3 +209,40 @@ def test_sliding_window_model_prompts_take_the_tensor_core_kernel():
         b = prefill(lm.model, kv, [seq], bt, start=[700])
     err = float((a - b).abs().max() / b.abs().max())
     assert err < 5e-2, err
+
+
+@pytest.mark.parametrize("kv_dtype,window", [("fp8", 0), ("int8", 200), ("fp4", 0)])
+def test_quantized_cache_prompts_take_the_tensor_core_kernel(kv_dtype, window):
+    """Grouped-query model over a quantized paged cache: the rows of a sequence are expanded by the cache's gather kernel
+    and the prompt attention runs on the tcgen05 kernel (first pass and a chunk over cached keys, optionally windowed)."""
+    import dataclasses
+    from metal_marlin_b200 import ops
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM, prefill
+    cfg = dataclasses.replace(get_preset("tiny-llama"), hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                              sliding_window=window)
+    lm = MMFP4ForCausalLM.from_config(cfg, device="cuda", seed=6)
+    g = torch.Generator().manual_seed(10)
+    seqs = [torch.randint(0, cfg.vocab_size, (900,), generator=g).tolist(), torch.randint(0, cfg.vocab_size, (860,), generator=g).tolist()]
+    bt = torch.arange(2 * 64, dtype=torch.int32).view(2, 64)
+    calls = {"n": 0}
+    real = ops.fmha_prefill
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+    ops.fmha_prefill = counting
+    try:
+        kv = lm.new_cache(128, 16, kv_dtype=kv_dtype)
+        prefill(lm.model, kv, [s[:600] for s in seqs], bt)
+        a = prefill(lm.model, kv, seqs, bt, start=[600, 600])
+    finally:
+        ops.fmha_prefill = real
+    assert calls["n"] == 2 * 2 * cfg.num_hidden_layers          # two passes x two sequences x layers
+    assert ops.check_status(torch.device(DEV)) == 0
+    with ops.force_reference():
+        kv = lm.new_cache(128, 16, kv_dtype=kv_dtype)
+        prefill(lm.model, kv, [s[:600] for s in seqs], bt)
+        b = prefill(lm.model, kv, seqs, bt, start=[600, 600])
+    err = float((a - b).abs().max() / b.abs().max())
+    assert err < (0.25 if kv_dtype == "fp4" else 8e-2), err
