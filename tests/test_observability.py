@@ -74,3 +74,38 @@ def test_nan_guard_and_checkpoint_utils(tmp_path):
     assert "model.language_model.layers.0.w" in rem and "lm_head.weight" in rem
     assert set(filter_weights(sd, include=r"layers\.[01]\.")) == {"model.layers.0.w", "model.layers.1.w"}
     assert "lm_head.weight" not in filter_weights(sd, exclude="lm_head")
+
+
+def test_server_monitor_parses_and_renders_metrics():
+    from metal_marlin_b200.serving import monitor as mon
+    text = """# HELP metal_marlin_requests_total Total requests
+# TYPE metal_marlin_requests_total counter
+metal_marlin_requests_total 12
+metal_marlin_active_requests 3
+metal_marlin_latency_ms{quantile="0.5"} 41.5
+metal_marlin_latency_ms{quantile="0.95"} 90.25
+metal_marlin_latency_ms{quantile="0.99"} 120
+metal_marlin_tokens_total{type="prompt"} 1000
+metal_marlin_tokens_total{type="completion"} 400
+metal_marlin_queue_depth 2
+metal_marlin_gpu_memory_mb 20480.0
+metal_marlin_throughput_tok_sec 133.700
+moe_tokens_processed_total 5000
+garbage line
+"""
+    m = mon.parse_metrics(text)
+    assert m["metal_marlin_requests_total"] == 12 and m['metal_marlin_latency_ms{quantile="0.95"}'] == 90.25 and len(m) == 11
+    later = dict(m)
+    later["metal_marlin_requests_total"] = 16
+    later['metal_marlin_tokens_total{type="completion"}'] = 700
+    table = mon.render(later, m, 2.0, {"status": "ok"})
+    assert "status" in table and "ok" in table and "16 / 3" in table and "1000 / 700" in table
+    assert "41.5 / 90.2 / 120.0" in table and "2.00" in table and "150.0" in table and "5000 / 0" in table
+    lines = []
+    rc = mon.run("http://x", once=True, out=lines.append, fetch_fn=lambda url: (m, {"status": "ok"}))
+    assert rc == 0 and len(lines) == 1 and "requests total / active" in lines[0]
+
+    def failing(url):
+        raise OSError("connection refused")
+    assert mon.run("http://x", once=True, out=lines.append, fetch_fn=failing) == 1 and "connection refused" in lines[-1]
+    assert mon.run("http://x", interval=0.0, polls=2, out=lines.append, fetch_fn=lambda url: (later, {})) == 0
