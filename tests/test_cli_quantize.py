@@ -79,3 +79,19 @@ def test_cli_end_to_end(float_ckpt, tmp_path):
     res = r.invoke(cli, ["serve"])
     assert res.exit_code != 0 and "model path" in res.output
     assert r.invoke(cli, ["--help"]).exit_code == 0
+
+
+def test_serve_profiles_set_family_defaults(monkeypatch):
+    import metal_marlin_b200.serving.server as srv
+    seen = {}
+    monkeypatch.setattr(srv, "run_server", lambda cfg, host, port, metrics_port: seen.update(cfg=cfg, port=port))
+    monkeypatch.setenv("GLM47_PORT", "8123")
+    r = CliRunner().invoke(cli, ["serve", "--profile", "glm47", "--batch-size", "24"])
+    assert r.exit_code == 0, r.output
+    cfg = seen["cfg"]
+    assert (cfg.preset, cfg.num_kv_blocks, cfg.block_size, cfg.max_batch_size, cfg.max_model_len) == ("glm-4.7-flash", 4096, 16, 24, 8192)
+    assert seen["port"] == 8123
+    monkeypatch.setenv("GLM47_MODEL_PATH", "/models/glm")
+    r = CliRunner().invoke(cli, ["serve", "--profile", "glm47", "--port", "9000", "--num-kv-blocks", "1024"])
+    assert r.exit_code == 0 and seen["cfg"].model_path == "/models/glm" and seen["cfg"].preset is None
+    assert seen["port"] == 9000 and seen["cfg"].num_kv_blocks == 1024 and seen["cfg"].max_batch_size == 32
