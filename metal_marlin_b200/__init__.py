@@ -100,6 +100,36 @@ _reg(".utils", "NaNGuard", "LazyCheckpoint", "load_checkpoint", "save_checkpoint
 _reg(".baseline_eager", "EagerBF16Model")
 
 
+# the reference facade's remaining names (packers, FP8 / Hadamard helpers, MoE dispatch bookkeeping, GEMM / attention entry points,
+# RoPE helpers, precision configs, ONNX / vision helpers, memory and dispatch objects) on this engine
+_reg(".compat_api",
+     "AWQResult", "AdaptiveQuantResult", "AdaptiveQuantizer", "AsyncTransferHandle", "AsyncTransferManager",
+     "BatchDispatchContext", "CacheConfigTorch", "CppDispatchInfo", "ExpertManagerCpp", "FP4GPTQQuantizer",
+     "FP4Metal", "FP8_E4M3_MAX", "FP8_E4M3_VALUES", "FP8_E5M2_MAX", "FP8_E5M2_VALUES", "FastInferenceContext",
+     "GPTQMetal", "GPTQQuantizer", "HAS_MPS", "HAS_PYOBJC_METAL", "HadamardMetadata", "HadamardMetal", "HeapAllocation",
+     "HeapAllocatorMetrics", "HeapBufferPool", "HessianManager", "InternVLProjector", "LLaVAProjector", "LayerBudget",
+     "LayerPrecisionSelector", "LayerQuantConfig", "LayerSensitivity", "MLAAttentionCpp", "MRGPTQQuantizer",
+     "MarlinAttention", "MarlinLinear", "MetalHeapAllocator", "MetalQuantizedLinear", "MetalQuantizedMoE", "MixedPrecisionConfig",
+     "MoEDispatchInfo", "MoEPrecisionConfig", "ModelBudgetAllocation", "ONNXGraphInfo", "PipelinedLayerDispatcher",
+     "Precision", "QuantizationFormat", "QuantizationReport", "Qwen2VLProjector", "RoPE", "VisionProjector",
+     "VisionProjectorConfig", "YaRNRoPE", "apply_hadamard_rotation", "awq_dequantize", "awq_quantize_model",
+     "compute_activation_stats", "compute_expert_load", "compute_fp8_e4m3_values", "compute_fp8_e5m2_values",
+     "compute_hessian_metal", "compute_load_balancing_loss", "compute_moe_expert_sensitivity", "compute_salient_scaling",
+     "compute_yarn_cos_sin_cache", "compute_yarn_inv_freq", "create_causal_mask", "create_expert_manager", "create_rope_from_config",
+     "create_sliding_window_mask", "dequant_fp8_e4m3", "dequant_fp8_e5m2", "dequantize_fp4_metal", "dequantize_fp8_e4m3",
+     "dequantize_fp8_e5m2", "dequantize_kv_cache_fp8", "dequantize_kv_cache_fp8_e5m2", "dequantize_mmfp4", "detect_projector_type",
+     "dispatch_batched_gemm_variable_seq", "dispatch_grouped_attention_variable_seq", "expert_gather", "expert_manager_available",
+     "expert_scatter_add", "extract_onnx_weights", "fast_dispatch_available", "find_salient_weights", "flash_attention_metal",
+     "fused_moe_forward", "gather_for_experts", "generate", "generate_batch", "generate_stream", "get_fast_context",
+     "get_onnx_config", "get_parent_module", "get_yarn_mscale", "group_tokens_by_expert", "group_tokens_by_expert_full",
+     "hadamard_transform_metal", "inverse_hadamard_rotation", "list_onnx_tensors", "marlin_gemm_fp4", "marlin_gemm_int4",
+     "mla_cpp_available", "mmfp4_fused_qkv", "mmfp4_gemm", "normalize_onnx_name", "pack_fp4_weights", "pack_fp4_weights_cpu",
+     "pack_fp8_weights", "pack_int4_weights", "pack_nf4_weights", "parse_onnx_graph_full", "quantize_fp4_metal",
+     "quantize_kv_cache_fp8", "quantize_kv_cache_fp8_e5m2", "quantize_linear_layer", "quantize_to_fp8", "quantize_to_fp8_e4m3",
+     "quantize_to_fp8_e5m2", "quantize_to_int4", "quantize_to_nf4", "scaled_dot_product_attention_metal", "scatter_expert_outputs",
+     "sliding_window_attention_metal", "unpack_fp4_weights")
+
+
 def __getattr__(name: str):
     try:
         module, attr = _EXPORTS[name]
