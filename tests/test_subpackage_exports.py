@@ -1,0 +1,61 @@
+"""Sub-package surfaces under the reference's names: speculative decoding and evaluation helpers.  Parity: reference
+``metal_marlin/speculative/__init__.py`` and ``metal_marlin/eval/__init__.py`` exports."""
+import numpy as np
+import pytest
+import torch
+
+
+def test_speculative_package_surface():
+    from metal_marlin_b200 import spec
+    for n in ("AcceptanceResult", "AcceptanceStats", "DraftOutput", "EagleHead", "EagleTreeVerifyResult", "GenerationStats",
+              "MMFP4DraftModel", "MMFP4DraftModelWithTarget", "SpeculativeConfig", "StepResult", "TreeDraftOutput", "VerifyResult",
+              "compute_acceptance_probabilities", "create_acceptance_report", "estimate_optimal_speculation_length", "verify_eagle_tree",
+              "SpeculativeEngine", "NGramDraft", "verify_speculative"):
+        assert hasattr(spec, n), n
+    p = torch.tensor([[0.5, 0.5], [0.9, 0.1]])
+    q = torch.tensor([[0.25, 0.75], [0.9, 0.1]])
+    acc = spec.compute_acceptance_probabilities(p, q, [0, 1])
+    assert torch.allclose(acc, torch.tensor([1.0, 1.0])) and float(spec.compute_acceptance_probabilities(p, q, [1, 0])[0]) == pytest.approx(2 / 3)
+    assert spec.estimate_optimal_speculation_length(0.0) == 1
+    assert spec.estimate_optimal_speculation_length(0.9, 0.05) > spec.estimate_optimal_speculation_length(0.5, 0.05) >= 1
+    assert spec.estimate_optimal_speculation_length(0.9, 0.5) <= spec.estimate_optimal_speculation_length(0.9, 0.05)
+    # tree: root -> a(0) -> b(1); root -> c(2).  The target wants token 7 then 9.
+    V = 12
+    root = torch.zeros(V)
+    root[7] = 5
+    nodes = torch.zeros(3, V)
+    nodes[0, 9] = 5
+    nodes[1, 3] = 5
+    r = spec.verify_eagle_tree(root, nodes, tokens=[7, 9, 4], parents=[-1, 0, -1])
+    assert r.accepted_path == [0, 1] and r.tokens == [7, 9, 3] and r.num_accepted == 2
+    tr = spec.TokenAcceptanceTracker()
+    tr.record([1, 2, 3, 4], 3)
+    tr.record([1, 2, 3, 4], 1)
+    rep = spec.create_acceptance_report(tr)
+    assert rep["proposed"] == 8 and rep["accepted"] == 4 and rep["position_rates"][0] == 1.0 and rep["suggested_length"] >= 1
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM
+    lm = MMFP4ForCausalLM.from_config("tiny-llama", device="cpu", seed=0)
+    eng = spec.SpeculativeConfig(draft="ngram", num_speculative_tokens=3).build(lm)
+    assert isinstance(eng, spec.SpeculativeEngine) and isinstance(eng.draft, spec.NGramDraft)
+
+
+def test_eval_package_surface():
+    from metal_marlin_b200 import eval as ev
+    x = np.random.RandomState(0).randn(5, 7)
+    assert np.allclose(ev.softmax(x).sum(-1), 1) and np.allclose(np.exp(ev.log_softmax(x)), ev.softmax(x))
+    logits = torch.zeros(4, 10)
+    assert ev.compute_perplexity_from_logits(logits, torch.tensor([1, 2, 3, 4])) == pytest.approx(10.0)
+    kl = ev.compute_kl_divergence(torch.randn(6, 9), torch.randn(6, 9))
+    same = ev.compute_kl_divergence(logits, logits)
+    assert kl.kl_mean > 0 and kl.num_tokens == 6 and same.kl_mean == pytest.approx(0.0) and same.top1_agreement == 1.0
+    assert ev.compute_kl_divergence_np(logits, logits) == pytest.approx(0.0)
+    corpus = ev.load_wikitext2(None, max_tokens=300, vocab_size=50)
+    assert len(corpus) == 300 and max(corpus) < 50
+
+    def uniform(ids):
+        return torch.zeros(len(ids), 50)
+    assert ev.compute_perplexity_sliding_window(uniform, corpus, 64, 32) == pytest.approx(50.0, rel=1e-3)
+    assert ev.compute_perplexity_wikitext(uniform, None, 64, 32, max_tokens=200, vocab_size=50) == pytest.approx(50.0, rel=1e-3)
+    r = ev.evaluate_kl_divergence(uniform, uniform, corpus[:100], 64)
+    assert r.kl_mean == pytest.approx(0.0, abs=1e-9)
+    assert ev.load_tokenizer(None, 100) is not None
