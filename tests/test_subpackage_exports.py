@@ -59,3 +59,47 @@ def test_eval_package_surface():
     r = ev.evaluate_kl_divergence(uniform, uniform, corpus[:100], 64)
     assert r.kl_mean == pytest.approx(0.0, abs=1e-9)
     assert ev.load_tokenizer(None, 100) is not None
+
+
+def test_utils_package_surface(tmp_path):
+    from metal_marlin_b200 import utils as u
+    assert u.calculate_matmul_flops(4, 8, 16) == 2 * 4 * 8 * 16 and u.calculate_matmul_flops(4, 8, 16, quantized=True) > 1024
+    full = u.calculate_attention_flops(1, 128, 8, 64)
+    assert u.calculate_attention_flops(1, 128, 8, 64, causal=True) < full and full == 4 * 8 * 128 * 128 * 64 + 5 * 8 * 128 * 128
+    assert u.calculate_ffn_flops(1, 10, 64, 256, gated=True) > u.calculate_ffn_flops(1, 10, 64, 256)
+    assert u.calculate_layernorm_flops(2, 3, 4) == 120 and u.calculate_embedding_flops(1, 1, 10, 10) == 0
+    c = u.profile_model_flops(1, 512, 4, 1024, 8, 4096, vocab_size=32000)
+    s = c.summary()
+    assert s["layers"] == 5 and 0.5 < s["matmul_fraction"] < 1 and c.total_flops == sum(l.total_flops for l in c.layers)
+    mem = u.get_system_memory()
+    det = u.get_system_memory_detailed()
+    assert mem.total_ram_gb > 0 and det.available_ram_gb <= det.total_ram_gb and u.get_metal_memory_pressure() in ("normal", "warn", "critical")
+    assert isinstance(u.should_reduce_allocation(), bool)
+    assert u.estimate_tensor_memory((4, 8), np.float16) == 64 and u.estimate_tensor_memory((4, 8), torch.bfloat16) == 64
+    assert u.compute_optimal_batch_size([(1024, 1024)], 1.0, np.float16, 0.5) == 256
+    assert u.round_up(13, 8) == 16
+    a, orig = u.pad_numpy_2d(np.ones((3, 5)), rows_multiple=4, cols_multiple=8)
+    t, orig_t = u.pad_torch_2d(torch.ones(3, 5), rows_multiple=4, cols_multiple=8, value=2.0)
+    assert a.shape == (4, 8) and orig == (3, 5) and t.shape == (4, 8) and float(t[3, 7]) == 2.0 and orig_t == (3, 5)
+    from metal_marlin_b200.formats.safetensors_io import save_file
+    f1, f2 = str(tmp_path / "a.safetensors"), str(tmp_path / "b.safetensors")
+    save_file({"x": torch.ones(64, 64), "y": torch.zeros(64, 64)}, f1)
+    save_file({"z": torch.full((64, 64), 3.0)}, f2)
+    pf = u.AdaptivePrefetcher([f1, f2], budget_bytes=64 * 64 * 4 + 8)
+    got = list(pf)
+    assert [sorted(b) for b in got] == [["x"], ["y"], ["z"]] and float(got[2]["z"][0, 0]) == 3.0 and len(pf.meta) == 3
+    u.clear_profiles()
+    u.enable_profiling()
+    try:
+        @u.profile_kernel("unit")
+        def work():
+            return sum(range(1000))
+        assert work() == 499500 and work() == 499500 and u.is_profiling_enabled()
+        st = u.get_profile_stats("unit")
+        assert st.count == 2 and st.total_ms >= 0 and len(u.get_profile_records("unit")) == 2 and "unit" in u.get_all_profile_stats()
+        lines = []
+        u.print_profile_summary(lines.append)
+        assert any("unit" in l for l in lines)
+    finally:
+        u.disable_profiling()
+        u.clear_profiles()
