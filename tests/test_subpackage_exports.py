@@ -103,3 +103,60 @@ def test_utils_package_surface(tmp_path):
     finally:
         u.disable_profiling()
         u.clear_profiles()
+
+
+def test_kv_package_surface():
+    from metal_marlin_b200 import kv
+    for n in ("BlockState", "CacheStats", "EvictionPolicy", "KVBlock", "KVBlockConfig", "MLABlock", "MLABlockAllocator", "MLACacheConfig",
+              "ParityValidator", "paged_attention", "paged_attention_v1", "mla_attention", "write_kv_to_blocks", "validate_paged_v1_parity",
+              "run_comprehensive_parity_suite", "compare_memory_usage", "PrefixMatch", "CachedBlock", "CacheMetrics", "QuantizedKVCache",
+              "compress_kv", "decompress_kv", "hash_prefix", "hash_tokens", "PagedKVCache", "RadixPrefixCache", "KVCache", "MLAKVCache"):
+        assert hasattr(kv, n), n
+    res = kv.run_comprehensive_parity_suite("cpu")
+    assert len(res) == 4 and all(r.passed for r in res), [r.max_abs_error for r in res]
+    assert kv.ParityValidator(kv.ParityConfig(seq_len=20)).run().passed
+    al = kv.BlockAllocator(4, 16)
+    b = al.allocate()
+    assert kv.KVBlock.of(al, b).state is kv.BlockState.ALLOCATED and kv.KVBlock.of(al, 3).state is kv.BlockState.FREE
+    al.incref(b)
+    assert kv.KVBlock.of(al, b).state is kv.BlockState.SHARED
+    cfg = kv.KVBlockConfig(16, 8, 128, "bf16")
+    assert cfg.bytes_per_token == 2 * 8 * 128 * 2 and cfg.bytes_per_block == 16 * cfg.bytes_per_token
+    assert kv.KVBlockConfig(16, 8, 128, "fp8").bytes_per_token == 2 * (8 * 128 + 32)
+    assert kv.MLACacheConfig().bytes_per_token == 576 * 2
+    m = kv.compare_memory_usage([100, 700, 30], 4096, cfg)
+    assert m["blocks"] == 7 + 44 + 2 and 0.9 < m["savings"] < 1.0 and 0 < m["internal_fragmentation"] < 0.1
+    cache = kv.PagedKVCache(8, 4)
+    cache.admit("a", list(range(10)))
+    st = kv.CacheStats.of(cache)
+    assert st.blocks == 8 and st.free == 5 and st.sequences == 1
+    q = kv.QuantizedKVCache(2, 1, 2, 64, 32, dtype="fp8")
+    k, v = torch.randn(1, 2, 5, 64), torch.randn(1, 2, 5, 64)
+    ka, va = q.update(0, k, v)
+    assert ka.shape[-2] == 5 and float((ka.float() - k).abs().max()) < 0.1 * float(k.abs().max())
+    stored, sc = kv.compress_kv(k, "int8")
+    assert float((kv.decompress_kv(stored, sc, "int8", torch.float32) - k).abs().max()) < 0.05 * float(k.abs().max())
+    assert kv.hash_prefix([1, 2, 3]) == kv.hash_tokens([1, 2, 3])
+
+
+def test_parallel_package_surface_single_process():
+    from metal_marlin_b200 import parallel as par
+    for n in par.__all__:
+        assert getattr(par, n) is not None, n
+    t = torch.arange(24.0).view(4, 6)
+    assert torch.equal(par.shard_tensor(t, 1, 1, 2), t[:, 3:]) and par.shard_tensor(t, 0, 0, 4).shape == (1, 6)
+    assert par.ShardSpec(0, 1, 2, unit=16).bounds(96) == (48, 96)
+    x = torch.ones(3)
+    assert par.all_reduce(x.clone()).tolist() == [1, 1, 1] and par.all_gather(x) is x and par.broadcast(x) is x and par.scatter(x) is x
+    w, inp = torch.randn(8, 12), torch.randn(5, 12)
+    ref = inp @ w.t()
+    cols = [par.TensorParallelLinear(w, par.ParallelMode.COLUMN, r, 2, gather_output=False)(inp) for r in range(2)]
+    assert torch.allclose(torch.cat(cols, -1), ref, atol=1e-5)
+    rows = [par.TensorParallelLinear(w, par.ParallelMode.ROW, r, 2)(inp) for r in range(2)]
+    assert torch.allclose(rows[0] + rows[1], ref, atol=1e-5)
+    q = par.TensorParallelLinear(torch.randn(64, 256) * 0.1, par.ParallelMode.COLUMN, 1, 2, gather_output=False, quantize=True, group_size=64)
+    assert q(torch.randn(3, 256)).shape == (3, 32)
+    pp = par.PipelineParallel(10, par.PipelineConfig(num_stages=3), rank=1)
+    assert len(pp.stages) == 3 and pp.stage_of(0) == 0 and pp.stage_of(9) == 2 and list(pp.my_layers) == list(range(*pp.stages[1]))
+    devs = par.Device.discover()
+    assert devs and devs[0].torch_device.type in ("cpu", "cuda")
