@@ -2,7 +2,16 @@ from .deltanet import gated_delta_rule_chunked, gated_delta_rule_recurrent, gate
 from .hybrid import LayerSpec, jamba_layout, kv_layers, layout_from_config, qwen35_layout, zamba_layout
 from .mamba import MambaBlock, MambaConfig, mamba2_scan, selective_scan, selective_scan_step
 from .rwkv import wkv5, wkv6
+from .blocks import (AttentionLayerConfig, DifferentialAttention, DifferentialAttentionConfig, DifferentialMarlinAttention,
+                     HybridArchitectureConfig, HybridBlock, HybridLayerConfig, HybridLayerType, HybridModel, HybridModelBuilder,
+                     LayerProtocol, LayerState, MambaLayerConfig, MambaState, MarlinMambaBlock, RWKVBlock, RWKVChannelMixing,
+                     RWKVLayerState, RWKVTimeMixing, SelectiveScanConfig, StateType, build_hybrid_config,
+                     parse_diff_transformer_config, rwkv_wkv_batched, rwkv_wkv_single_token)
 
 __all__ = ["gated_delta_rule_chunked", "gated_delta_rule_recurrent", "gated_delta_step", "l2norm", "LayerSpec", "jamba_layout", "kv_layers",
            "layout_from_config", "qwen35_layout", "zamba_layout", "MambaBlock", "MambaConfig", "mamba2_scan", "selective_scan",
-           "selective_scan_step", "wkv5", "wkv6"]
+           "selective_scan_step", "wkv5", "wkv6", "AttentionLayerConfig", "DifferentialAttention", "DifferentialAttentionConfig",
+           "DifferentialMarlinAttention", "HybridArchitectureConfig", "HybridBlock", "HybridLayerConfig", "HybridLayerType", "HybridModel",
+           "HybridModelBuilder", "LayerProtocol", "LayerState", "MambaLayerConfig", "MambaState", "MarlinMambaBlock", "RWKVBlock",
+           "RWKVChannelMixing", "RWKVLayerState", "RWKVTimeMixing", "SelectiveScanConfig", "StateType", "build_hybrid_config",
+           "parse_diff_transformer_config", "rwkv_wkv_batched", "rwkv_wkv_single_token"]

@@ -160,3 +160,41 @@ def test_parallel_package_surface_single_process():
     assert len(pp.stages) == 3 and pp.stage_of(0) == 0 and pp.stage_of(9) == 2 and list(pp.my_layers) == list(range(*pp.stages[1]))
     devs = par.Device.discover()
     assert devs and devs[0].torch_device.type in ("cpu", "cuda")
+
+
+def test_arch_blocks_carry_state_across_calls():
+    from metal_marlin_b200 import arch
+    torch.manual_seed(0)
+    B, T, d, H = 2, 9, 64, 4
+    x = torch.randn(B, T, d)
+    # RWKV: one pass equals a prompt pass plus single-token steps with the carried state
+    blk = arch.RWKVBlock.random(d, H, seed=1)
+    full, _ = blk(x)
+    y1, st = blk(x[:, :5])
+    outs = [y1]
+    for t in range(5, T):
+        yt, st = blk(x[:, t:t + 1], st)
+        outs.append(yt)
+    assert torch.allclose(torch.cat(outs, 1), full, atol=1e-4) and st.wkv.shape == (B, H, d // H, d // H)
+    r, k, v = (torch.randn(B, H, 16) for _ in range(3))
+    w, u = torch.rand(B, H, 16), torch.randn(H, 16)
+    o, s = arch.rwkv_wkv_single_token(r, k, v, w, u, torch.zeros(B, H, 16, 16))
+    ob, sb = arch.rwkv_wkv_batched(r[:, None], k[:, None], v[:, None], w[:, None], u)
+    assert torch.allclose(o, ob[:, 0], atol=1e-5) and torch.allclose(s, sb, atol=1e-5)
+    # differential attention: shape, causality
+    da = arch.DifferentialAttention.random(arch.parse_diff_transformer_config({"hidden_size": d, "num_attention_heads": 4}, layer_idx=2))
+    ya = da(x)
+    x2 = x.clone()
+    x2[:, -1] += 1.0
+    assert ya.shape == x.shape and torch.allclose(da(x2)[:, :-1], ya[:, :-1], atol=1e-5) and 0.2 < da.cfg.lambda_init < 0.8
+    # hybrid stacks: pieces with carried states equal one pass, for every family
+    for kind, kw in (("jamba", {"attn_period": 2, "attn_offset": 1}), ("rwkv", {}), ("mamba", {}), ("attention", {}), ("zamba", {"shared_every": 2})):
+        cfg = arch.build_hybrid_config(kind, d, 4, num_heads=H, **kw)
+        model = arch.HybridModelBuilder(cfg).build(seed=3)
+        whole, states = model(x)
+        a, st = model(x[:, :4])
+        b, st = model(x[:, 4:], st)
+        assert torch.allclose(torch.cat([a, b], 1), whole, atol=2e-4), kind
+        assert len(states) == 4 and len(model.state_types()) == 4
+    assert arch.StateType.KV_CACHE in arch.HybridModelBuilder(arch.build_hybrid_config("jamba", d, 4, H, attn_period=2, attn_offset=1)).build().state_types()
+    assert arch.MarlinMambaBlock is arch.MambaBlock and arch.MambaLayerConfig is arch.MambaConfig
