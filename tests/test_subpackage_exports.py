@@ -198,3 +198,29 @@ def test_arch_blocks_carry_state_across_calls():
         assert len(states) == 4 and len(model.state_types()) == 4
     assert arch.StateType.KV_CACHE in arch.HybridModelBuilder(arch.build_hybrid_config("jamba", d, 4, H, attn_period=2, attn_offset=1)).build().state_types()
     assert arch.MarlinMambaBlock is arch.MambaBlock and arch.MambaLayerConfig is arch.MambaConfig
+
+
+def test_inference_and_serving_package_surfaces():
+    from metal_marlin_b200 import inference as inf
+    from metal_marlin_b200 import serving as srv
+    for n in inf.__all__:
+        assert getattr(inf, n) is not None, n
+    for n in srv.__all__:
+        assert getattr(srv, n) is not None, n
+    assert inf.get_device("cpu") == "cpu" and inf.get_device() in ("cpu",) or inf.get_device().startswith("cuda")
+    from metal_marlin_b200.compat_api import pack_fp4_weights
+    w = torch.randn(128, 24) * 0.1
+    p, s, _m = pack_fp4_weights(w, 64, output_backend="torch")
+    d = inf.dequantize_fp4_torch(p, s)
+    assert d.shape == (128, 24) and float((d - w).abs().max()) < 0.26 * float(w.abs().max())
+    hid = torch.randn(2, 3, 16)
+    r = inf.batched_kv_projection(hid, torch.randn(8, 16), torch.randn(8, 16), 2, 4)
+    assert r.keys.shape == (2, 3, 2, 4) and r.values.shape == (2, 3, 2, 4) and r.num_tokens == 6
+    pipe = inf.MMFP4Pipeline.from_config("tiny-llama", device="cpu")
+    info = inf.ModelInfo.of(pipe)
+    assert info.num_layers == 2 and info.attention == "gqa" and isinstance(inf.chat(pipe, [{"role": "user", "content": "hi"}], max_new_tokens=2), str)
+    from metal_marlin_b200.kv import PagedKVCache
+    c = PagedKVCache(8, 4)
+    c.admit("s", list(range(6)))
+    reg = srv.KVRegion.of(c, "s")
+    assert reg.num_tokens == 6 and len(reg.blocks) == 2 and len(reg.slots()) == 6 and srv.KVCacheManager is PagedKVCache
