@@ -224,3 +224,54 @@ def test_inference_and_serving_package_surfaces():
     c.admit("s", list(range(6)))
     reg = srv.KVRegion.of(c, "s")
     assert reg.num_tokens == 6 and len(reg.blocks) == 2 and len(reg.slots()) == 6 and srv.KVCacheManager is PagedKVCache
+
+
+def test_layer_objects_moe_mla_mixed_precision():
+    from metal_marlin_b200 import layers
+    torch.manual_seed(0)
+    E, H, I, T, k = 8, 128, 64, 6, 2
+    router = torch.randn(E, H) * 0.1
+    gate, up, down = torch.randn(E, I, H) * 0.1, torch.randn(E, I, H) * 0.1, torch.randn(E, H, I) * 0.1
+    shared = (torch.randn(1, I, H) * 0.1, torch.randn(1, I, H) * 0.1, torch.randn(1, H, I) * 0.1)
+    moe = layers.MMFP4MoE.from_float(router, gate, up, down, top_k=k, shared=shared, group_size=64)
+    x = torch.randn(T, H)
+    y = moe(x)
+    ids, wts = moe.route(x.bfloat16())
+    gu, dn = moe.gate_up.dequantize(torch.float32), moe.down.dequantize(torch.float32)
+
+    def expert(e, v):
+        h = gu[e] @ v
+        return dn[e] @ (F_silu(h[:I]) * h[I:])
+    F_silu = torch.nn.functional.silu
+    xb = x.bfloat16().float()
+    ref = torch.stack([sum(float(wts[t, j]) * expert(int(ids[t, j]), xb[t]) for j in range(k)) + expert(E, xb[t]) for t in range(T)])
+    assert y.shape == x.shape and float((y - ref).abs().max()) < 0.05 * float(ref.abs().max()) + 1e-3
+    assert layers.MMFP4FusedMoE is layers.MMFP4MoE and layers.MMFP4MTPHead is layers.GLMMTPHead
+    # MLA: a prompt pass plus single-token steps over the latent cache equals one pass over the whole sequence
+    mla = layers.MMFP4MLA.from_float(hidden=128, num_heads=4, q_lora_rank=64, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16,
+                                     v_head_dim=32, seed=1)
+    xs = torch.randn(2, 7, 128)
+    whole = mla(xs)
+    cache = mla.new_cache(batch=2, max_seq_len=16)
+    parts = [mla(xs[:, :4], cache=cache)] + [mla(xs[:, t:t + 1], cache=cache) for t in range(4, 7)]
+    assert whole.shape == xs.shape and cache.seq_len == 7
+    assert float((torch.cat(parts, 1) - whole).abs().max()) < 0.03 * float(whole.abs().max()) + 1e-3
+    x2 = xs.clone()
+    x2[:, -1] += 1
+    assert torch.allclose(mla(x2)[:, :-1], whole[:, :-1], atol=1e-3)          # causal
+    # precision policy picks the storage
+    w = torch.randn(64, 128) * 0.1
+    for prec, tol in (("fp4", 0.3), ("int8", 0.03), ("bf16", 0.02)):
+        lin = layers.MixedPrecisionLinear(w, prec, 64)
+        out = lin(x[:, :128])
+        assert float((out - x[:, :128] @ w.t()).abs().max()) < tol * float((x[:, :128] @ w.t()).abs().max()) + 1e-2, prec
+    assert layers.MixedPrecisionLinear.for_tensor("model.layers.0.input_layernorm.weight", w).format == "keep"
+    assert layers.MixedPrecisionLinear.for_tensor("model.layers.0.self_attn.q_proj.weight", w, "quality").format == "int8"
+    # vectorised verification: a draft equal to the target's arg-max with one-hot distributions is accepted whole
+    V, K = 11, 3
+    tgt = torch.zeros(1, K + 1, V)
+    tgt[0, torch.arange(K + 1), torch.tensor([1, 2, 3, 4])] = 1.0
+    dr = torch.zeros(1, K, V)
+    dr[0, torch.arange(K), torch.tensor([1, 2, 3])] = 1.0
+    toks, acc = layers.verify_kernel(tgt, dr, torch.tensor([[1, 2, 3]]), generator=torch.Generator().manual_seed(0))
+    assert int(acc[0]) == 3 and toks[0].tolist() == [1, 2, 3, 4]
