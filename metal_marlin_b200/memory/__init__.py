@@ -9,9 +9,13 @@ request path calls ``cudaMalloc``.
 """
 from .arena import Arena, BumpAllocator, WorkspaceBuffer
 from .expert_cache import ExpertCache, TileCoordinator
+from .model_memory import (CompactionConfig, CompactionStats, CUDAPinnedPool, ExpertMetadata, LayerMetadata, MemoryCompactor, MemoryStats,
+                           MLACompressionRatio, MMAPWeightConfig, MMAPWeightManager, MMAPWeightStats, MMFP4MemoryManager, PooledBuffer)
 from .pressure import MemoryPressureMonitor, PressureLevel
 from .pools import BufferPool, BufferPoolStats, RingBuffer, TransferStream, get_ring_buffer, reset_ring_buffer
 from .streaming import PinnedPool, WeightStreamer
 
 __all__ = ["Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "TileCoordinator", "MemoryPressureMonitor", "PressureLevel", "PinnedPool",
-           "WeightStreamer", "BufferPool", "BufferPoolStats", "RingBuffer", "TransferStream", "get_ring_buffer", "reset_ring_buffer"]
+           "WeightStreamer", "BufferPool", "BufferPoolStats", "RingBuffer", "TransferStream", "get_ring_buffer", "reset_ring_buffer", "CompactionConfig",
+           "CompactionStats", "CUDAPinnedPool", "ExpertMetadata", "LayerMetadata", "MemoryCompactor", "MemoryStats", "MLACompressionRatio",
+           "MMAPWeightConfig", "MMAPWeightManager", "MMAPWeightStats", "MMFP4MemoryManager", "PooledBuffer"]

@@ -275,3 +275,51 @@ def test_layer_objects_moe_mla_mixed_precision():
     dr[0, torch.arange(K), torch.tensor([1, 2, 3])] = 1.0
     toks, acc = layers.verify_kernel(tgt, dr, torch.tensor([[1, 2, 3]]), generator=torch.Generator().manual_seed(0))
     assert int(acc[0]) == 3 and toks[0].tolist() == [1, 2, 3, 4]
+
+
+def test_moe_and_memory_package_surfaces(tmp_path):
+    from metal_marlin_b200 import layers, memory, moe
+    from metal_marlin_b200.models.config import get_preset
+    ids = torch.tensor([[0, 3], [3, 1], [2, 0], [3, 2]], dtype=torch.int32)
+    res = moe.GPUExpertGrouping(4, token_tile=2).group(ids)
+    assert int(res.num_tiles) >= 4 and torch.equal(res.order.long()[res.inverse.long()], torch.arange(8))
+    order, offsets, inv = moe.group_tokens_by_expert_auto(ids, 4)
+    assert offsets.tolist() == [0, 2, 3, 5, 8] and moe.group_tokens_by_expert_full_gpu(ids, 4).num_tokens == 4
+    torch.manual_seed(0)
+    lay = layers.MMFP4MoE.from_float(torch.randn(4, 64) * 0.1, torch.randn(4, 64, 64) * 0.1, torch.randn(4, 64, 64) * 0.1,
+                                     torch.randn(4, 64, 64) * 0.1, top_k=2, group_size=64)
+    disp = moe.MoEDispatcher(lay)
+    x = torch.randn(5, 64)
+    assert torch.allclose(disp(x), lay(x), atol=1e-5) and int(disp.tracker.counts.sum()) == 10 and moe.FusedMoEDispatcher is moe.MoEDispatcher
+    # memory planning for the GLM-4.7-Flash configuration
+    cfg = get_preset("glm-4.7-flash")
+    mgr = memory.MMFP4MemoryManager(cfg, limit_bytes=180 << 30)
+    plan = mgr.plan()
+    st = plan["stats"]
+    assert plan["fits_entirely"] and 12e9 < st.weight_bytes + st.resident_expert_bytes < 22e9 and st.kv_tokens_that_fit > 1_000_000
+    small = memory.MMFP4MemoryManager(cfg, limit_bytes=8 << 30).plan()
+    assert not small["fits_entirely"] and small["stats"].offloaded_expert_bytes > 0 and any(not e.resident for e in small["experts"])
+    r = memory.MLACompressionRatio.of(cfg)
+    assert r.latent_bytes_per_token == 576 * 2 and r.ratio > 15
+    assert mgr.kv_bytes_per_token() == 576 * 2 * cfg.num_hidden_layers
+    # compaction wrapper and memory-mapped weights
+    arena = memory.Arena(4096, "cpu", alignment=64)
+    a, b, c = (arena.alloc((512,), torch.uint8) for _ in range(3))
+    c.fill_(7)
+    off_c = arena.offset_of(c)
+    arena.free(a)
+    arena.free(b)
+    moved = {}
+    comp = memory.MemoryCompactor(arena, memory.CompactionConfig(0.0, 0.0), on_moved=lambda o, n: moved.update({o: n}))
+    assert comp.maybe_compact(force=True) >= 1 and moved[off_c] < off_c and comp.stats.runs == 1
+    from metal_marlin_b200.formats.safetensors_io import save_file
+    d = tmp_path / "ck"
+    d.mkdir()
+    save_file({"model.layers.0.w": torch.ones(4, 4), "model.layers.1.w": torch.zeros(2, 2), "model.norm.weight": torch.ones(4)}, str(d / "model.safetensors"))
+    mm = memory.MMAPWeightManager(str(d))
+    assert sorted(mm.names())[0] == "model.layers.0.w" and float(mm.get("model.layers.0.w").sum()) == 16 and list(mm.layer(1)) == ["model.layers.1.w"]
+    assert mm.stats.loads == 2 and mm.stats.bytes_loaded == 64 + 16 and memory.CUDAPinnedPool is memory.PinnedPool
+    mm.close()
+    pb = memory.PooledBuffer(torch.empty(8))
+    pb.touch()
+    assert pb.use_count == 1
