@@ -323,3 +323,61 @@ def test_moe_and_memory_package_surfaces(tmp_path):
     pb = memory.PooledBuffer(torch.empty(8))
     pb.touch()
     assert pb.use_count == 1
+
+
+def test_trellis_package_surface():
+    from metal_marlin_b200 import trellis as tr
+    for n in tr.__all__:
+        assert getattr(tr, n) is not None, n
+    torch.manual_seed(0)
+    codes = torch.randint(0, 8, (32, 48), dtype=torch.uint8)
+    blob = tr.pack_indices(codes, 3)
+    assert blob.numel() == tr.compute_packed_size(32, 48, 3) and int(blob[0]) == 3
+    assert torch.equal(tr.unpack_indices(blob, 32, 48), codes) and torch.equal(tr.unpack_trellis_indices(tr.pack_trellis_indices(codes, 3), 32, 48), codes)
+    assert 3.5 < tr.compute_compression_ratio(4096, 4096, 4) < 4.0 and tr.compute_compression_ratio(4096, 4096, 2) > 7
+    w = torch.randn(64, 128) * 0.05
+    lin = tr.TrellisLinear.from_float(w, 4, 64)
+    deq = tr.dequantize_trellis_weight(lin, torch.float32)
+    assert float((deq - w).abs().max()) < 0.25 * float(w.abs().max())
+    again = tr.dispatch_trellis_dequant(lin.codes, lin.scales, lin.su, lin.sv, 64, 128, 4, 64).float()
+    assert torch.allclose(again, deq, atol=1e-2)
+    x = torch.randn(3, 128)
+    assert float((tr.dispatch_gemm_trellis_auto(x, lin).float() - x.bfloat16().float() @ deq.t()).abs().max()) < 0.05
+    assert torch.equal(tr.dispatch_sign_flips(torch.ones(2, 4), torch.tensor([1.0, -1, 1, -1])), torch.tensor([[1.0, -1, 1, -1]] * 2))
+    # dense MLP and a mixed-bit MoE MLP against their de-quantized restatement
+    H, I, E = 128, 64, 4
+    mk = lambda bits, seed: tr.TrellisDenseMLP.from_float(*(torch.randn(*s, generator=torch.Generator().manual_seed(seed + i)) * 0.1
+                                                          for i, s in enumerate(((I, H), (I, H), (H, I)))), bits=bits, group_size=64)
+    mlp = mk(4, 0)
+
+    def ref_mlp(m, v):
+        g, u, d = (t.dequantize(torch.float32) for t in (m.gate, m.up, m.down))
+        return (torch.nn.functional.silu(v @ g.t()) * (v @ u.t())) @ d.t()
+    xb = x.bfloat16().float()
+    assert float((mlp(x).float() - ref_mlp(mlp, xb)).abs().max()) < 0.05 * float(ref_mlp(mlp, xb).abs().max()) + 1e-3
+    experts = [mk(b, 10 * e) for e, b in enumerate((2, 3, 4, 4))]
+    moe = tr.TrellisMoEMLP(torch.randn(E, H) * 0.1, experts, tr.MoEConfig(E, 2, H, I, num_shared_experts=1), shared=[mk(4, 99)])
+    tr.reset_mixed_bpw_stats()
+    y = tr.dispatch_mixed_bpw_moe(x, moe)
+    ids, wts = moe.route(x.bfloat16())
+    ref = torch.stack([sum(float(wts[t, j]) * ref_mlp(experts[int(ids[t, j])], xb[t:t + 1])[0] for j in range(2)) + ref_mlp(moe.shared[0], xb[t:t + 1])[0]
+                       for t in range(3)])
+    assert float((y.float() - ref).abs().max()) < 0.06 * float(ref.abs().max()) + 1e-3
+    st = tr.get_mixed_bpw_stats()
+    assert st["calls"] == 1 and st["tokens"] == 3 and sum(st["by_bits"].values()) == 6
+    # MLA attention over trellis projections, inside a decoder layer, with the compressed latent cache
+    cfg = tr.TrellisMLAConfig(H, 4, 64, 64, 32, 16, 32)
+    g = torch.Generator().manual_seed(5)
+    rn = lambda *s: torch.randn(*s, generator=g) * 0.05
+    state = {"q_a_proj": rn(64, H), "q_a_layernorm": torch.ones(64), "q_b_proj": rn(4 * 48, 64), "kv_a_proj_with_mqa": rn(64 + 16, H),
+             "kv_a_layernorm": torch.ones(64), "kv_b_proj": rn(4 * 64, 64), "o_proj": rn(H, 4 * 32)}
+    attn = tr.TrellisMLAttention(cfg, tr.create_mla_projections(cfg, state, bits=4, group_size=32))
+    layer = tr.TrellisDecoderLayer(attn, mlp, torch.ones(H), torch.ones(H))
+    xs = torch.randn(1, 6, H)
+    whole = layer(xs)
+    cache = tr.CompressedKVCache(1, 64, 16, 1, 16, dtype="bf16")
+    parts = torch.cat([layer(xs[:, :4], cache=cache), layer(xs[:, 4:5], cache=cache), layer(xs[:, 5:], cache=cache)], 1)
+    assert float((parts - whole).abs().max()) < 0.03 * float(whole.abs().max()) + 1e-3 and cache.seq_len == 6
+    with pytest.raises(ValueError):
+        tr.TrellisMLAttention(cfg, {"kv_a": None})
+    assert tr.MixedBPWAutoTuner.__name__ == "KernelAutoTuner" and tr.TrellisModelWrapper is tr.TrellisForCausalLM
