@@ -1,5 +1,7 @@
 """Sub-package surfaces under the reference's names: speculative decoding and evaluation helpers.  Parity: reference
 ``metal_marlin/speculative/__init__.py`` and ``metal_marlin/eval/__init__.py`` exports."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -381,3 +383,100 @@ def test_trellis_package_surface():
     with pytest.raises(ValueError):
         tr.TrellisMLAttention(cfg, {"kv_a": None})
     assert tr.MixedBPWAutoTuner.__name__ == "KernelAutoTuner" and tr.TrellisModelWrapper is tr.TrellisForCausalLM
+
+
+# ------------------------------------------------------------------------------------------------ quantization / calibration names
+REFERENCE_QUANTIZATION = [
+    "BartowskiCalibration", "CalibrationBatch", "CalibrationDataset", "CalibrationHooks", "CalibrationStreamer", "EXL3QuantResult",
+    "EXL3Quantizer", "EXL3QuantizerPipeline", "GQACalibrationHooks", "LayerInfo", "LayerStreamer", "LayerWeights", "StreamingHessianCollector",
+    "StreamingQuantizer", "TrellisCodebook", "TrellisTile", "analyze_layer_sensitivity", "blockwise_hadamard", "collect_all_hessians_streaming",
+    "collect_layer_hessian", "compute_model_sensitivity_profile", "compute_quantization_error", "compute_tile_scales", "copy_non_linear_tensors",
+    "ldl_solve", "ldlq_quantize_layer", "ldlq_quantize_layer_core", "load_sensitivity_profile", "pack_indices", "preprocess_hessian_exl3",
+    "quantize_model_exl3", "quantize_model_streaming", "quantize_tiles_parallel", "recommend_quantization", "rotate_weights_exl3", "save_exl3_layer",
+    "save_sensitivity_profile", "sensitivity_to_config", "tensor_core_perm", "tensor_core_perm_i", "unrotate_weights_exl3",
+]
+
+
+def test_quant_package_names_resolve():
+    import metal_marlin_b200.quant as q
+    for n in REFERENCE_QUANTIZATION + ["gptq_quantize", "mr_gptq_quantize", "ldlq_quantize", "quantize_checkpoint", "allocate_bits", "convert_model"]:
+        assert getattr(q, n) is not None, n
+    assert set(REFERENCE_QUANTIZATION) <= set(q.__all__)
+
+
+def test_exl3_pieces_numerics(tmp_path):
+    import metal_marlin_b200.quant as q
+    torch.manual_seed(0)
+    w = torch.randn(64, 256)
+    x = torch.randn(512, 256)
+    H = q.preprocess_hessian_exl3(q.collect_layer_hessian(x), damp=0.01)
+    assert torch.allclose(H, H.t()) and torch.linalg.eigvalsh(H.double()).min() > 0
+    # rotation is an orthonormal involution and keeps w @ x^T when x is rotated too
+    wr = q.rotate_weights_exl3(w, 128)
+    assert torch.allclose(q.unrotate_weights_exl3(wr, 128), w, atol=1e-4)
+    assert torch.allclose(wr @ q.blockwise_hadamard(x, 128).t(), w @ x.t(), atol=1e-2)
+    L, D = q.ldl_solve(H.double(), 16)
+    assert L.shape == H.shape
+    r4 = q.EXL3Quantizer(bits=4).quantize_layer(w, H)
+    r2 = q.EXL3Quantizer(bits=2).quantize_layer(w, H)
+    assert r4.bits == 4 and r4.dequantized.shape == w.shape and r4.proxy_error < r2.proxy_error
+    err = q.compute_quantization_error(w, r4.dequantized, H)
+    assert err["relative"] < 0.2 and err["proxy"] > 0
+    # fragment-order permutation and its inverse
+    p, pi = q.tensor_core_perm(), q.tensor_core_perm_i()
+    assert sorted(p.tolist()) == list(range(256)) and torch.equal(p[pi], torch.arange(256))
+    tile = torch.arange(256.).reshape(16, 16)
+    assert torch.equal(q.apply_tensor_core_perm_i(q.apply_tensor_core_perm(tile)), tile)
+    cb = q.TrellisCodebook(3)
+    codes = cb.encode(cb.values + 1e-4)
+    assert codes.tolist() == list(range(8)) and torch.equal(cb.decode(codes), cb.values)
+    d = q.save_exl3_layer({"model.layers.0.mlp.up_proj.weight": r4.weight}, str(tmp_path), 0)
+    assert os.path.isfile(os.path.join(d, "index.json")) and os.path.isfile(os.path.join(d, "tensor_0000.safetensors"))
+
+
+def test_sensitivity_profile_roundtrip_and_recommendation(tmp_path):
+    import metal_marlin_b200.quant as q
+    torch.manual_seed(1)
+    tensors = {"a": torch.randn(32, 128), "b": torch.randn(32, 128) * torch.linspace(0.1, 8, 128)}
+    prof = q.compute_model_sensitivity_profile(tensors, bit_choices=(2, 3, 4, 6))
+    for v in prof.values():
+        e = v["error_by_bits"]
+        assert e[2] > e[3] > e[4] > e[6]
+    path = str(tmp_path / "p" / "profile.json")
+    q.save_sensitivity_profile(prof, path)
+    assert q.load_sensitivity_profile(path) == prof
+    rec = q.recommend_quantization(prof, target_bpw=3.5)
+    assert set(rec) == {"a", "b"} and sum(rec.values()) / 2 <= 3.5 + 1e-6
+    cfg = q.sensitivity_to_config(prof, 3.5)
+    assert cfg["a"]["format"] == "trellis" and cfg["a"]["bits"] == rec["a"]
+
+
+def test_layer_streamer_calibration_hooks_and_streaming_quantizer(tmp_path):
+    import metal_marlin_b200.quant as q
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM
+    from metal_marlin_b200.formats.safetensors_io import save_file
+    from metal_marlin_b200.models.config import get_preset
+    cfg = get_preset("tiny-llama")
+    src = str(tmp_path / "hf")
+    os.makedirs(src)
+    save_file(q.random_hf_state(cfg, 0), os.path.join(src, "model.safetensors"), metadata={"format": "pt"})
+    cfg.save_pretrained(src)
+    st = q.LayerStreamer(src)
+    infos = st.layer_infos()
+    assert len(infos) >= 1 and infos[0].nbytes > 0
+    layers = list(st)
+    assert [l.index for l in layers] == list(range(len(infos))) and set(layers[0].tensors) == set(infos[0].tensor_names)
+    assert any("embed" in k for k in st.non_layer_tensors())
+    res = q.quantize_model_streaming(src, str(tmp_path / "q"), fmt="mmfp4", method="rtn")
+    assert res.layers == len(infos) and res.tensors > 0
+    n = q.copy_non_linear_tensors(str(tmp_path / "q"), str(tmp_path / "base.safetensors"))
+    assert n > 0
+    lm = MMFP4ForCausalLM.from_pretrained(str(tmp_path / "q"), "cpu")
+    ds = q.CalibrationDataset("synthetic", vocab_size=lm.config.vocab_size, num_samples=2, seq_len=16)
+    batches = list(q.CalibrationStreamer(ds, batch_size=2))
+    assert len(batches) == 1 and batches[0].input_ids.shape == (2, 16)
+    with q.CalibrationHooks() as h:
+        with torch.no_grad():
+            lm.forward_logits(ds[0])
+    names = h.collector.names()
+    assert any(n.endswith("q_proj.weight") for n in names) and h.collector.n[names[0]] == 16
