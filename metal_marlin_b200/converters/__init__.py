@@ -1,6 +1,8 @@
 """Checkpoint importers / converters: GGUF (de-quantize + re-quantize), PyTorch ``.bin`` / ``.pt`` state dicts, HF
 safetensors, GPTQ (AutoGPTQ-style int4), EXL3-style trellis tensors and ONNX graphs (``onnx.py``: own protobuf reader,
-graph summary, executor with quantized MatMul / Gemm), plus the mixed-format packer.
+graph summary, executor with quantized MatMul / Gemm), plus the mixed-format packer; weight-name mapping of other decoder
+families (``name_mapping.py``), activation statistics (``activation_stats.py``), the quantize-with-report driver
+(``quantize_report.py``) and the quantized custom operators for ONNX graphs (``custom_ops.py``).
 
 Parity: reference ``metal_marlin/converters/*``, ``gguf_to_marlin.py``, ``hf_exl3_loader.py``,
 ``quantization/exl3_to_marlin.py``, ``packing/mixed_format.py`` and the ``convert`` command (``cli.py:307-345``).
@@ -111,4 +113,31 @@ def convert_checkpoint(src: str, dst: str, from_format: str = "auto", to_format:
             shutil.rmtree(stage, ignore_errors=True)
 
 
-__all__ = ["convert_checkpoint", "detect_format", "gguf", "onnx", "dequantize_gptq_int4", "import_gptq_state", "MixedFormatPack"]
+# the reference's ``converters`` package names, resolved on first use
+_LAZY = {
+    ".activation_stats": ["CalibrationCollector", "CalibrationDataset", "CalibrationStats", "compute_scales"],
+    ".quantize_report": ["LayerReport", "QuantizationReport", "quantize_model"],
+    ".custom_ops": ["MarlinFlashAttentionOp", "MarlinQuantizedLinearOp", "MarlinQuantizedMatMulOp", "MarlinSession", "create_session",
+                    "export_with_marlin_ops"],
+    ".name_mapping": ["Rule", "detect_model_type", "estimate_memory", "get_supported_architectures", "load_and_quantize", "load_config",
+                      "load_mapped_safetensors", "map_weight_names", "register_architecture"],
+    ".nemo": ["convert_nemo_to_pytorch", "load_nemo"],
+    ".onnx": ["ONNXExecutor", "ONNXGraph", "ONNXOp", "load_onnx", "save_onnx"],
+}
+_WHERE = {n: m for m, names in _LAZY.items() for n in names}
+
+
+def __getattr__(name: str):
+    import importlib
+    if name == "load_onnx_model":
+        return importlib.import_module(".onnx", __package__).load_onnx
+    if name in ("onnx", "nemo", "qmi4", "exl3"):
+        return importlib.import_module("." + name, __package__)
+    mod = _WHERE.get(name)
+    if mod is None:
+        raise AttributeError(name)
+    return getattr(importlib.import_module(mod, __package__), name)
+
+
+__all__ = sorted(["convert_checkpoint", "detect_format", "gguf", "onnx", "dequantize_gptq_int4", "import_gptq_state", "MixedFormatPack",
+                  "load_onnx_model"] + list(_WHERE))

@@ -107,3 +107,49 @@ def load_nemo(path: str) -> Tuple[Dict[str, torch.Tensor], Dict]:
     hf = hf_config_from_nemo(cfg)
     return convert_state_dict(sd, hf["num_attention_heads"], hf["num_key_value_heads"], hf["head_dim"],
                               gated_mlp=str(cfg.get("activation", "fast-swiglu")).endswith("glu")), hf
+
+
+def convert_nemo_to_pytorch(nemo_path: str, output_path: str, *, extract_config_only: bool = False, config_output: Optional[str] = None,
+                            use_safetensors: bool = True) -> Dict:
+    """A ``.nemo`` archive to a standard checkpoint: Hugging Face tensor names in ``output_path`` (``.safetensors``, or a
+    ``torch.save`` file when ``use_safetensors`` is off or the name ends in ``.pt`` / ``.bin``; a directory gets ``model.safetensors`` and
+    ``config.json``).  ``config_output`` also writes the derived configuration as JSON; ``extract_config_only`` stops after that.
+    Returns ``{"config", "num_tensors", "num_parameters", "output"}`` (reference ``converters/nemo_to_pytorch.py:173``)."""
+    import json
+    import os
+    nemo_path, output_path = str(nemo_path), str(output_path)
+    if not os.path.isfile(nemo_path):
+        raise FileNotFoundError(f"NeMo file not found: {nemo_path}")
+    if not nemo_path.endswith(".nemo"):
+        raise ValueError(f"expected a .nemo archive, got {nemo_path}")
+    if extract_config_only:
+        with tarfile.open(nemo_path) as tf:
+            raw = next((yaml.safe_load(tf.extractfile(m).read()) or {} for m in tf.getmembers() if m.name.split("/")[-1] == "model_config.yaml"), None)
+        if raw is None:
+            raise FileNotFoundError(f"{nemo_path}: no model_config.yaml inside the archive")
+        sd, hf = {}, hf_config_from_nemo(raw)
+    else:
+        sd, hf = load_nemo(nemo_path)
+    if config_output:
+        os.makedirs(os.path.dirname(os.path.abspath(config_output)), exist_ok=True)
+        with open(config_output, "w") as f:
+            json.dump(hf, f, indent=1)
+    info = {"config": hf, "num_tensors": len(sd), "num_parameters": int(sum(t.numel() for t in sd.values())), "output": None}
+    if extract_config_only:
+        return info
+    as_dir = os.path.isdir(output_path) or not os.path.splitext(output_path)[1]
+    if as_dir:
+        os.makedirs(output_path, exist_ok=True)
+        with open(os.path.join(output_path, "config.json"), "w") as f:
+            json.dump(hf, f, indent=1)
+        target = os.path.join(output_path, "model.safetensors" if use_safetensors else "pytorch_model.bin")
+    else:
+        os.makedirs(os.path.dirname(os.path.abspath(output_path)), exist_ok=True)
+        target = output_path
+    if use_safetensors and target.endswith(".safetensors"):
+        from ..formats.safetensors_io import save_file
+        save_file({k: v.contiguous() for k, v in sd.items()}, target, metadata={"format": "pt"})
+    else:
+        torch.save(sd, target)
+    info["output"] = target
+    return info

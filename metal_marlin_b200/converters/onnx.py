@@ -167,6 +167,7 @@ class ONNXOp:
     inputs: List[str]
     outputs: List[str]
     attrs: Dict[str, Any] = field(default_factory=dict)
+    domain: str = ""               # operator set the node belongs to ("" = the standard ONNX set)
 
 
 ONNXNode = ONNXOp
@@ -183,7 +184,7 @@ class ONNXGraph:
 
 
 def _parse_node(buf: memoryview) -> ONNXOp:
-    ins, outs, attrs, name, op = [], [], {}, "", ""
+    ins, outs, attrs, name, op, domain = [], [], {}, "", "", ""
     for fno, _, v in _fields(buf):
         if fno == 1:
             ins.append(bytes(v).decode())
@@ -196,7 +197,9 @@ def _parse_node(buf: memoryview) -> ONNXOp:
         elif fno == 5:
             k, a = _parse_attribute(v)
             attrs[k] = a
-    return ONNXOp(name or (outs[0] if outs else op), op, ins, outs, attrs)
+        elif fno == 7:
+            domain = bytes(v).decode()
+    return ONNXOp(name or (outs[0] if outs else op), op, ins, outs, attrs, domain)
 
 
 def _value_info_name(buf: memoryview) -> str:
@@ -213,10 +216,15 @@ def load_onnx(path_or_bytes: Union[str, Path, bytes]) -> ONNXGraph:
     for fno, _, v in _fields(memoryview(data)):
         if fno == 7:
             graph_buf = v
-        elif fno == 8:        # opset_import: OperatorSetIdProto {domain = 1, version = 2}
+        elif fno == 8:        # opset_import: OperatorSetIdProto {domain = 1, version = 2}; custom domains carry their own versions
+            dom, ver = "", 0
             for f2, _, v2 in _fields(v):
-                if f2 == 2:
-                    opset = max(opset, int(v2))
+                if f2 == 1:
+                    dom = bytes(v2).decode()
+                elif f2 == 2:
+                    ver = int(v2)
+            if dom in ("", "ai.onnx"):
+                opset = max(opset, ver)
     if graph_buf is None:
         raise ValueError("not an ONNX ModelProto: no graph")
     nodes, inits, ins, outs, gname = [], {}, [], [], ""
@@ -273,6 +281,8 @@ def save_onnx(graph: ONNXGraph, path: Optional[Union[str, Path]] = None) -> byte
         nb = b"".join(_w_field(1, _LEN, i.encode()) for i in n.inputs) + b"".join(_w_field(2, _LEN, o.encode()) for o in n.outputs)
         nb += _w_field(3, _LEN, n.name.encode()) + _w_field(4, _LEN, n.op_type.encode())
         nb += b"".join(_w_field(5, _LEN, _attr_proto(k, v)) for k, v in n.attrs.items())
+        if n.domain:
+            nb += _w_field(7, _LEN, n.domain.encode())
         g += _w_field(1, _LEN, nb)
     g += _w_field(2, _LEN, (graph.name or "graph").encode())
     for k, arr in graph.initializers.items():
@@ -282,6 +292,8 @@ def save_onnx(graph: ONNXGraph, path: Optional[Union[str, Path]] = None) -> byte
     for o in graph.outputs:
         g += _w_field(12, _LEN, _w_field(1, _LEN, o.encode()))
     model = _w_field(1, _VARINT, 8) + _w_field(7, _LEN, g) + _w_field(8, _LEN, _w_field(2, _VARINT, graph.opset or 17))
+    for dom in sorted({n.domain for n in graph.nodes if n.domain}):
+        model += _w_field(8, _LEN, _w_field(1, _LEN, dom.encode()) + _w_field(2, _VARINT, 1))
     if path is not None:
         Path(path).write_bytes(model)
     return model

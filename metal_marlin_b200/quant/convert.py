@@ -59,11 +59,11 @@ def _copy_aux(src: str, dst: str) -> None:
 
 
 def quantize_named_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], fmt: str, group_size: int,
-                           device: str = "cpu", quantize_fn: Optional[Callable] = None, hadamard_block: int = 0
-                           ) -> Iterator[Tuple[str, Dict[str, torch.Tensor], Dict[str, str], Optional[dict]]]:
+                           device: str = "cpu", quantize_fn: Optional[Callable] = None, hadamard_block: int = 0,
+                           extra_skip: Iterable[str] = ()) -> Iterator[Tuple[str, Dict[str, torch.Tensor], Dict[str, str], Optional[dict]]]:
     """For each input tensor yields (name, tensors-to-write, dtype-overrides, report-entry)."""
     for name, t in tensors:
-        if not should_quantize_tensor(name, t):
+        if not should_quantize_tensor(name, t, extra_skip):
             yield name, {name: t}, {}, None
             continue
         gs = fp4fmt.pick_group_size(t.shape[1], group_size)
@@ -90,10 +90,12 @@ def quantize_named_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], fmt: str
 
 def convert_model(model_dir: str, out_dir: str, fmt: str = "marlin_fp4", group_size: int = 128, device: str = "cpu",
                   shard_bytes: int = 4 << 30, quantize_fn: Optional[Callable] = None, verbose: bool = False,
-                  hadamard_block: int = 0, tensors: Optional[Iterable[Tuple[str, torch.Tensor]]] = None) -> dict:
+                  hadamard_block: int = 0, tensors: Optional[Iterable[Tuple[str, torch.Tensor]]] = None,
+                  extra_skip: Iterable[str] = ()) -> dict:
     """Stream a float HF checkpoint into a quantized one.  ``fmt``: ``marlin_fp4`` (single
     ``model.safetensors``) or ``mmfp4`` (shards + ``model.safetensors.index.json``).  ``tensors``: take the ``(name, tensor)``
-    stream from the caller instead of the safetensors files of ``model_dir`` (importers that de-quantize another format)."""
+    stream from the caller instead of the safetensors files of ``model_dir`` (importers that de-quantize another format);
+    ``extra_skip``: lower-case name fragments of further tensors to keep unquantized."""
     os.makedirs(out_dir, exist_ok=True)
     t0 = time.time()
     report, weight_map = [], {}
@@ -113,7 +115,7 @@ def convert_model(model_dir: str, out_dir: str, fmt: str = "marlin_fp4", group_s
 
     n_q = n_total = 0
     for name, outs, dts, rep in quantize_named_tensors(tensors if tensors is not None else iter_safetensors_weights(model_dir), fmt, group_size, device, quantize_fn,
-                                                         hadamard_block):
+                                                         hadamard_block, tuple(extra_skip)):
         n_total += 1
         if rep is not None:
             n_q += 1

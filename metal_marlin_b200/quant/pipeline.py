@@ -40,7 +40,11 @@ def collect_hessians(model_dir_fp4: str, calibration: str = "synthetic", num_sam
         tok = load_tokenizer(model_dir_fp4)
     except Exception:
         tok = None
-    seqs = load_calibration_tokens(calibration, tok, lm.config.vocab_size, num_samples, min(seq_len, lm.config.max_position_embeddings))
+    max_len = min(seq_len, lm.config.max_position_embeddings)
+    if isinstance(calibration, str):
+        seqs = load_calibration_tokens(calibration, tok, lm.config.vocab_size, num_samples, max_len)
+    else:            # token sequences from the caller (lists or tensors of ids)
+        seqs = [[int(t) for t in torch.as_tensor(s).reshape(-1)[:max_len]] for s in calibration][:num_samples]
     col = HessianCollector()
     col.inputs: Dict[str, torch.Tensor] = {}
 
