@@ -229,4 +229,32 @@ class VisionEncoderCache:
 
 
 __all__ = ["PreprocessConfig", "ImagePreprocessor", "dynamic_tiles", "LlavaProjector", "PatchMergerProjector", "PixelShuffleProjector",
-           "PerceiverResampler", "merge_image_tokens", "VisionQuantConfig", "VisionEncoderCache", "CLIP_MEAN", "CLIP_STD"]
+           "PerceiverResampler", "merge_image_tokens", "VisionQuantConfig", "VisionEncoderCache", "CLIP_MEAN", "CLIP_STD",
+           "LLaVAProjector", "Qwen2VLProjector", "InternVLProjector", "VisionProjector", "VisionProjectorConfig", "detect_projector_type", "VisionMetal",
+           "VisionDevice", "preprocess_for_vit", "VisionCalibrationConfig", "VisionCalibrationDataset", "build_vision_calibration_dataset",
+           "collect_vision_calibration_stats", "analyze_vision_encoder_sensitivity", "build_vision_precision_map", "build_vlm_precision_map",
+           "pack_vlm_mixed_format", "VisionLayerType", "VisionLayerSensitivity", "SensitivityReport", "classify_vision_layer"]
+
+
+# ------------------------------------------------------------------------------------------------ the reference's names
+LLaVAProjector = LlavaProjector
+Qwen2VLProjector = PatchMergerProjector
+InternVLProjector = PixelShuffleProjector
+
+_LAZY = {
+    "VisionProjector": ("..compat_api", "VisionProjector"), "VisionProjectorConfig": ("..compat_api", "VisionProjectorConfig"),
+    "detect_projector_type": ("..compat_api", "detect_projector_type"),
+    "VisionMetal": (".device_ops", "VisionMetal"), "VisionDevice": (".device_ops", "VisionDevice"), "preprocess_for_vit": (".device_ops", "preprocess_for_vit"),
+    **{n: (".calibration", n) for n in (
+        "VisionCalibrationConfig", "VisionCalibrationDataset", "build_vision_calibration_dataset", "collect_vision_calibration_stats",
+        "analyze_vision_encoder_sensitivity", "build_vision_precision_map", "build_vlm_precision_map", "pack_vlm_mixed_format", "VisionLayerType",
+        "VisionLayerSensitivity", "SensitivityReport", "classify_vision_layer")},
+}
+
+
+def __getattr__(name: str):
+    if name in _LAZY:
+        import importlib
+        mod, attr = _LAZY[name]
+        return getattr(importlib.import_module(mod, __package__), attr)
+    raise AttributeError(name)
