@@ -10,6 +10,8 @@ from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Protocol, Sequence, Tuple
 
 _LAZY = {
+    "GenerationConfig": ("..trellis", "GenerationConfig"), "MetalMarlinModel": ("..models.mmfp4_causal_lm", "MMFP4ForCausalLM"),
+    "ModelConfig": ("..models.config", "ModelConfig"),
     "MMFP4Pipeline": (".pipeline", "MMFP4Pipeline"), "MarlinPipeline": (".pipeline", "MarlinPipeline"),
     "TransformersMarlinPipeline": (".pipeline", "MarlinPipeline"), "StreamingOutput": (".pipeline", "StreamingOutput"),
     "PipelineScheduler": (".pipelined", "PipelineScheduler"), "AsyncPipelineScheduler": (".pipelined", "AsyncPipelineScheduler"),

@@ -85,3 +85,13 @@ FusedMoEDispatcher = MoEDispatcher
 __all__ += ["GPUGroupingResult", "GPUExpertGrouping", "TopKExpertGrouping", "group_tokens_by_expert_gpu", "group_tokens_by_expert_fast",
             "group_tokens_by_expert_gpu_optimized", "group_tokens_by_expert_auto", "group_tokens_by_expert_full_gpu", "MoEDispatcher",
             "FusedMoEDispatcher", "MoEDispatchInfo", "group_tokens_by_expert", "group_tokens_by_expert_full"]
+
+
+def __getattr__(name: str):
+    if name in ("compute_expert_load", "compute_load_balancing_loss", "gather_for_experts", "scatter_expert_outputs"):
+        from .. import compat_api
+        return getattr(compat_api, name)
+    raise AttributeError(name)
+
+
+__all__ += ["compute_expert_load", "compute_load_balancing_loss", "gather_for_experts", "scatter_expert_outputs"]

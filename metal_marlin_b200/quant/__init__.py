@@ -26,8 +26,11 @@ _MODULES = {
                  "compute_tile_scales", "copy_non_linear_tensors", "ldl_solve", "ldlq_quantize_layer", "ldlq_quantize_layer_core",
                  "load_sensitivity_profile", "preprocess_hessian_exl3", "quantize_model_exl3", "quantize_model_streaming",
                  "quantize_tiles_parallel", "recommend_quantization", "rotate_weights_exl3", "save_exl3_layer", "save_sensitivity_profile",
-                 "sensitivity_to_config", "tensor_core_perm", "tensor_core_perm_i", "unrotate_weights_exl3"],
+                 "sensitivity_to_config", "tensor_core_perm", "tensor_core_perm_i", "unrotate_weights_exl3", "quantize_tile_viterbi",
+                 "write_exl3_config", "HessianManager"],
 }
+# adaptive-precision planning objects live with the facade's mixed-precision classes
+_COMPAT = ("AdaptiveQuantizer", "AdaptiveQuantResult", "LayerBudget", "ModelBudgetAllocation", "LayerSensitivity", "compute_moe_expert_sensitivity")
 _WHERE = {name: mod for mod, names in _MODULES.items() for name in names}
 
 
@@ -35,10 +38,13 @@ def __getattr__(name: str):
     if name == "pack_indices":
         from ..formats.trellis import pack_codes
         return pack_codes
+    if name in _COMPAT:
+        from .. import compat_api
+        return getattr(compat_api, name)
     mod = _WHERE.get(name)
     if mod is None:
         raise AttributeError(name)
     return getattr(importlib.import_module(mod, __package__), name)
 
 
-__all__ = sorted(list(_WHERE) + ["pack_indices"])
+__all__ = sorted(list(_WHERE) + ["pack_indices"] + list(_COMPAT))

@@ -424,3 +424,125 @@ def recommend_quantization(profile: Dict[str, Dict], target_bpw: float = 4.0) ->
 def sensitivity_to_config(profile: Dict[str, Dict], target_bpw: float = 4.0, group_size: int = 128) -> Dict[str, Dict]:
     """``{tensor name: {"bits", "group_size", "format"}}`` for the quantization driver (``bit_allocation`` of the trellis writer)."""
     return {k: {"bits": b, "group_size": group_size, "format": "trellis"} for k, b in recommend_quantization(profile, target_bpw).items()}
+
+
+# ------------------------------------------------------------------------------------------------ trellis search, config, Hessian manager
+def quantize_tile_viterbi(tile: torch.Tensor, codebook: TrellisCodebook, scale: float, transition_penalty: float = 0.0
+                          ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Minimum-cost path through the level trellis of a tile (flattened row by row): cost ``sum_i (x_i / scale - g[s_i])^2 +
+    transition_penalty * sum_i |s_i - s_{i-1}|``.  With no transition penalty every element takes its nearest level; a positive one
+    trades a little error for smoother index sequences.  Returns ``(indices uint8 [n], de-quantized tile)``.
+    Reference ``quantization/viterbi_quant.py:91``."""
+    g = codebook.values.to(torch.float64)
+    x = tile.reshape(-1).to(torch.float64) / float(scale)
+    n, S = x.numel(), g.numel()
+    local = (x[:, None] - g[None, :]) ** 2                                        # [n, S]
+    if transition_penalty <= 0.0:
+        idx = local.argmin(1)
+    else:
+        states = torch.arange(S, dtype=torch.float64)
+        trans = transition_penalty * (states[:, None] - states[None, :]).abs()   # [prev, cur]
+        cost = local[0].clone()
+        back = torch.zeros(n, S, dtype=torch.long)
+        for i in range(1, n):
+            total = cost[:, None] + trans
+            cost, back[i] = total.min(0)
+            cost = cost + local[i]
+        idx = torch.empty(n, dtype=torch.long)
+        idx[-1] = int(cost.argmin())
+        for i in range(n - 1, 0, -1):
+            idx[i - 1] = back[i, idx[i]]
+    deq = (g[idx] * float(scale)).to(tile.dtype).reshape(tile.shape)
+    return idx.to(torch.uint8), deq
+
+
+def write_exl3_config(output_path: str, bits: int, group_size: int, results: Sequence[EXL3QuantResult]) -> str:
+    """``quantization_config.json`` in ``output_path``: method, bit width, group size, and the summary of the layer results."""
+    os.makedirs(str(output_path), exist_ok=True)
+    n = max(1, len(results))
+    cfg = {"quantization_config": {"quant_method": "exl3", "bits": int(bits), "group_size": int(group_size), "format": f"exl3_{int(bits)}bit",
+                                   "symmetric": True, "desc_act": False},
+           "quantization_stats": {"layers_quantized": len(results), "avg_reconstruction_mse": sum(float(r.mse) for r in results) / n,
+                                  "avg_proxy_error": sum(float(r.proxy_error) for r in results) / n,
+                                  "bits_histogram": {str(b): sum(1 for r in results if r.bits == b) for b in sorted({r.bits for r in results})}}}
+    path = os.path.join(str(output_path), "quantization_config.json")
+    with open(path, "w") as f:
+        json.dump(cfg, f, indent=1)
+    return path
+
+
+class HessianManager:
+    """Named Hessian accumulators with explicit registration: ``register_layer(name, in_features)``, ``accumulate_layer(name, x)``,
+    ``get_hessian(name, damp)`` (mean of ``x x^T`` plus ``damp * mean(diag)`` on the diagonal).  ``attach(module)`` registers every
+    ``nn.Linear`` below a module and hooks its input.  Reference ``calibration/hessian_collector.py:218``."""
+
+    def __init__(self, default_damp: float = 0.01):
+        self.default_damp = default_damp
+        self._dims: Dict[str, int] = {}
+        self._col = HessianCollector()
+        self._handles: list = []
+
+    def register_layer(self, name: str, in_features: int) -> None:
+        if name in self._dims and self._dims[name] != in_features:
+            raise ValueError(f"{name} is registered with {self._dims[name]} input features")
+        self._dims[name] = int(in_features)
+
+    def unregister_layer(self, name: str) -> None:
+        self._dims.pop(name, None)
+        self.reset_layer(name)
+
+    def accumulate_layer(self, name: str, x) -> None:
+        if name not in self._dims:
+            raise KeyError(f"layer {name!r} is not registered")
+        x = torch.as_tensor(x)
+        if x.shape[-1] != self._dims[name]:
+            raise ValueError(f"{name}: activations have {x.shape[-1]} features, registered {self._dims[name]}")
+        self._col.add(name, x)
+
+    def get_hessian(self, name: str, damp: Optional[float] = None) -> torch.Tensor:
+        if name not in self._dims:
+            raise KeyError(f"layer {name!r} is not registered")
+        H = self._col.get(name)
+        if H is None:
+            H = torch.zeros(self._dims[name], self._dims[name])
+        damp = self.default_damp if damp is None else damp
+        level = torch.diag(H).mean() if float(torch.diag(H).mean()) > 0 else torch.tensor(1.0)
+        return H + torch.eye(H.shape[0], device=H.device) * damp * level
+
+    def get_all_hessians(self, damp: Optional[float] = None) -> Dict[str, torch.Tensor]:
+        return {n: self.get_hessian(n, damp) for n in self._dims}
+
+    def get_sample_counts(self) -> Dict[str, int]:
+        return {n: int(self._col.n.get(n, 0)) for n in self._dims}
+
+    def reset_layer(self, name: str) -> None:
+        self._col.H.pop(name, None)
+        self._col.n.pop(name, None)
+
+    def reset_all(self) -> None:
+        self._col.H.clear()
+        self._col.n.clear()
+
+    def attach(self, module, prefix: str = "") -> int:
+        import torch.nn as nn
+        count = 0
+        for name, m in module.named_modules():
+            if isinstance(m, nn.Linear):
+                full = f"{prefix}{name}"
+                self.register_layer(full, m.in_features)
+                self._handles.append(m.register_forward_pre_hook(lambda _m, args, _n=full: self.accumulate_layer(_n, args[0].detach())))
+                count += 1
+        return count
+
+    def remove_hooks(self) -> None:
+        for h in self._handles:
+            h.remove()
+        self._handles = []
+
+    @property
+    def layer_names(self) -> List[str]:
+        return list(self._dims)
+
+    @property
+    def num_layers(self) -> int:
+        return len(self._dims)

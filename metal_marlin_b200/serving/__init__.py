@@ -9,6 +9,9 @@ from dataclasses import dataclass
 from typing import List
 
 _LAZY = {
+    "SchedulerConfig": ("..engine.scheduler", "SchedulerConfig"), "ContinuousSchedulerConfig": ("..engine.scheduler", "SchedulerConfig"),
+    "PreemptionPolicy": ("..engine.scheduler", "PreemptionPolicy"), "RequestPriority": ("..engine.request", "RequestPriority"),
+    "RequestState": ("..engine.request", "RunningRequest"), "ModelConfig": ("..models.config", "ModelConfig"),
     "ServingEngine": (".engine", "ServingEngine"), "EngineConfig": (".engine", "EngineConfig"), "run_server": (".server", "run_server"),
     "app": (".server", "app"), "configure": (".server", "configure"), "MetricsCollector": (".metrics", "MetricsCollector"),
     "MoEMetrics": (".metrics", "MoEMetrics"), "PerplexityTracker": (".metrics", "PerplexityTracker"),
@@ -45,4 +48,19 @@ class KVRegion:
         return [self.blocks[t // self.block_size] * self.block_size + t % self.block_size for t in range(self.num_tokens)]
 
 
-__all__ = sorted(list(_LAZY) + ["KVRegion"])
+def _kv_sharing(server=None, enable_prefix_caching: bool = True, cache=None):
+    """A prompt-sharing manager over a paged cache: ``cache`` when given, else the cache of ``server`` (a serving engine), else a
+    small cache of its own (stand-alone bookkeeping).  Reference ``serving/mmfp4_server.py:410``."""
+    from ..kv.paged import PagedKVCache
+    from .batching import KVCacheSharing
+    if cache is None and server is not None:
+        for holder in (server, getattr(server, "engine", None), getattr(getattr(server, "engine", None), "engine", None)):
+            if isinstance(getattr(holder, "cache", None), PagedKVCache):
+                cache = holder.cache
+                break
+    if cache is None:
+        cache = PagedKVCache(num_blocks=64, block_size=16, enable_prefix_cache=enable_prefix_caching)
+    return KVCacheSharing(cache)
+
+
+__all__ = sorted(list(_LAZY) + ["KVRegion", "_kv_sharing"])

@@ -16,6 +16,9 @@ TrellisModelWrapper = TrellisForCausalLM
 
 
 def __getattr__(name: str):
+    if name in ("TrellisWeight", "TrellisModelLoader"):
+        from ..formats import trellis as fmt
+        return getattr(fmt, name)
     if name in ("MixedBPWAutoTuner", "AutotuneConfig", "KernelConfig", "BenchmarkResult", "TrellisModel"):
         if name == "TrellisModel":                      # the decoder under the wrapper
             from ..models.transformer import Transformer
@@ -26,7 +29,7 @@ def __getattr__(name: str):
     raise AttributeError(name)
 
 
-__all__ = ["GenerationConfig", "TrellisGenerator", "TrellisForCausalLM", "TrellisModelConfig", "TrellisLinear", "TrellisModelWrapper",
+__all__ = ["TrellisWeight", "TrellisModelLoader", "GenerationConfig", "TrellisGenerator", "TrellisForCausalLM", "TrellisModelConfig", "TrellisLinear", "TrellisModelWrapper",
            "TrellisModel", "MixedBPWAutoTuner", "AutotuneConfig", "KernelConfig", "BenchmarkResult", "GLM4_TOKENIZER_ID", "CausalLMOutput",
            "CompressedKVCache", "MixedBPWMoEDispatcher", "MoEConfig", "TrellisDecoderLayer", "TrellisDenseMLP", "TrellisExpert",
            "TrellisKVCache", "TrellisMLAConfig", "TrellisMLAttention", "TrellisMoELayer", "TrellisMoEMLP", "compute_compression_ratio",

@@ -480,3 +480,78 @@ def test_layer_streamer_calibration_hooks_and_streaming_quantizer(tmp_path):
             lm.forward_logits(ds[0])
     names = h.collector.names()
     assert any(n.endswith("q_proj.weight") for n in names) and h.collector.n[names[0]] == 16
+
+
+def test_viterbi_tile_search_is_optimal():
+    import itertools
+    import metal_marlin_b200.quant as q
+    cb = q.TrellisCodebook(2)
+    torch.manual_seed(3)
+    x = torch.randn(6)
+    g = cb.values.double()
+    for lam in (0.0, 0.4, 2.0):
+        idx, deq = q.quantize_tile_viterbi(x, cb, 0.9, transition_penalty=lam)
+        cost = lambda s: float(((x.double() / 0.9 - g[list(s)]) ** 2).sum()) + lam * sum(abs(a - b) for a, b in zip(s, s[1:]))   # noqa: E731
+        best = min(itertools.product(range(4), repeat=6), key=cost)
+        assert abs(cost(tuple(idx.tolist())) - cost(best)) < 1e-9
+        assert torch.allclose(deq, (g[idx.long()] * 0.9).float())
+    assert torch.equal(q.quantize_tile_viterbi(x, cb, 0.9)[0], cb.encode(x / 0.9))
+
+
+def test_exl3_config_and_hessian_manager(tmp_path):
+    import json
+    import torch.nn as nn
+    import metal_marlin_b200.quant as q
+    torch.manual_seed(0)
+    res = [q.EXL3Quantizer(bits=b).quantize_layer(torch.randn(32, 128), None) for b in (3, 4, 4)]
+    path = q.write_exl3_config(str(tmp_path / "out"), 4, 128, res)
+    with open(path) as f:
+        cfg = json.load(f)
+    assert cfg["quantization_config"]["format"] == "exl3_4bit" and cfg["quantization_stats"]["layers_quantized"] == 3
+    assert cfg["quantization_stats"]["bits_histogram"] == {"3": 1, "4": 2} and cfg["quantization_stats"]["avg_reconstruction_mse"] > 0
+    hm = q.HessianManager(default_damp=0.1)
+    hm.register_layer("a", 8)
+    x = torch.randn(20, 8)
+    hm.accumulate_layer("a", x[:12])
+    hm.accumulate_layer("a", x[12:].numpy())
+    H = x.t() @ x / 20
+    assert torch.allclose(hm.get_hessian("a", damp=0.0), H, atol=1e-5) and hm.get_sample_counts() == {"a": 20}
+    assert torch.allclose(hm.get_hessian("a"), H + torch.eye(8) * 0.1 * torch.diag(H).mean(), atol=1e-5)
+    with pytest.raises(KeyError):
+        hm.accumulate_layer("b", x)
+    with pytest.raises(ValueError):
+        hm.accumulate_layer("a", torch.randn(3, 7))
+    hm.reset_layer("a")
+    assert hm.get_sample_counts() == {"a": 0} and torch.allclose(hm.get_hessian("a"), torch.eye(8) * 0.1)
+    model = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 4))
+    assert hm.attach(model, prefix="m.") == 2 and hm.num_layers == 3 and "m.2" in hm.layer_names
+    model(x)
+    hm.remove_hooks()
+    model(x)
+    assert hm.get_sample_counts()["m.0"] == 20 and set(hm.get_all_hessians()) == {"a", "m.0", "m.2"}
+    hm.unregister_layer("a")
+    hm.reset_all()
+    assert hm.layer_names == ["m.0", "m.2"] and hm.get_sample_counts()["m.2"] == 0
+
+
+def test_remaining_reference_subpackage_names():
+    import importlib
+    want = {"layers": ["MarlinLinear"], "inference": ["GenerationConfig", "MetalMarlinModel", "ModelConfig"],
+            "quant": ["write_exl3_config", "quantize_tile_viterbi", "AdaptiveQuantizer", "AdaptiveQuantResult", "LayerBudget", "ModelBudgetAllocation",
+                      "compute_moe_expert_sensitivity", "HessianManager", "LayerSensitivity"],
+            "moe": ["compute_expert_load", "compute_load_balancing_loss", "gather_for_experts", "scatter_expert_outputs"],
+            "trellis": ["TrellisWeight", "TrellisModelLoader"],
+            "serving": ["SchedulerConfig", "ContinuousSchedulerConfig", "PreemptionPolicy", "RequestPriority", "RequestState", "ModelConfig", "_kv_sharing"]}
+    for pkg, names in want.items():
+        mod = importlib.import_module("metal_marlin_b200." + pkg)
+        for n in names:
+            assert getattr(mod, n) is not None, (pkg, n)
+            assert n in mod.__all__, (pkg, n)
+    import metal_marlin_b200.serving as s
+    sharing = s._kv_sharing()
+    assert sharing.create_region("a", [1, 2, 3, 4, 5]).num_tokens == 5 and sharing.attach("b", [1, 2, 3, 4, 5]) is not None
+    from metal_marlin_b200.kv.paged import PagedKVCache
+
+    class Holder:
+        cache = PagedKVCache(8, 16)
+    assert s._kv_sharing(Holder()).cache is Holder.cache
