@@ -394,7 +394,7 @@ def profile_model(lm, token_sequences: Sequence[Sequence[int]], profiler: Option
     cfg = lm.config
     moe_layers: Dict[int, int] = {}
     if profiler is None:
-        n_moe = sum(1 for i in range(cfg.num_hidden_layers) if cfg.is_moe_layer(i)) if hasattr(cfg, "is_moe_layer") else cfg.num_hidden_layers
+        n_moe = sum(1 for i in range(cfg.num_hidden_layers) if cfg.layer_is_moe(i))
         profiler = MoERoutingProfiler(cfg.num_experts, max(1, n_moe), cfg.num_experts_per_tok)
 
     seen = [0]                                      # MoE layers met so far in the current pass

@@ -15,3 +15,13 @@ __all__ = ["gated_delta_rule_chunked", "gated_delta_rule_recurrent", "gated_delt
            "HybridModelBuilder", "LayerProtocol", "LayerState", "MambaLayerConfig", "MambaState", "MarlinMambaBlock", "RWKVBlock",
            "RWKVChannelMixing", "RWKVLayerState", "RWKVTimeMixing", "SelectiveScanConfig", "StateType", "build_hybrid_config",
            "parse_diff_transformer_config", "rwkv_wkv_batched", "rwkv_wkv_single_token"]
+
+
+def __getattr__(name: str):
+    if name == "create_causal_mask":                 # the differential-attention module of the reference re-exports the mask helper
+        from ..compat_api import create_causal_mask
+        return create_causal_mask
+    raise AttributeError(name)
+
+
+__all__ += ["create_causal_mask"]

@@ -1241,3 +1241,87 @@ class MLAAttentionCpp:
     def decode(self, q_lat: torch.Tensor, latent_pool, block_tables: torch.Tensor, ctx_lens: torch.Tensor, scale: float) -> torch.Tensor:
         return ops.paged_attention(q_lat, latent_pool, None, block_tables, ctx_lens, Hq=self.H, Hkv=1, dqk=self.R + self.dr, dv=self.R,
                                    block_size=self.block_size, scale=scale)
+
+
+# ------------------------------------------------------------------------------------------------ GEMM operation objects
+class GemmFp4:
+    """``forward(x [..., K], packed_weight [K / 8, N], scales [K / group, N]) -> [..., N]`` on the FP4 GEMM / GEMV kernels
+    (reference ``ops/gemm_fp4.py:20``).  Device weights are cached per packed tensor, so repeated calls with the same weight do
+    not rebuild the tile layout."""
+
+    def __init__(self, library: Any = None, cache_size: int = 64):
+        self._cache: Dict[Tuple[int, int], Any] = {}
+        self._cache_size = cache_size
+
+    def _weight(self, packed: torch.Tensor, scales: torch.Tensor, device):
+        from .ops.weights import FP4Weight
+        key = (packed.data_ptr(), scales.data_ptr())
+        hit = self._cache.get(key)
+        if hit is not None and hit[0] is packed:
+            return hit[1]
+        W = FP4Weight.from_marlin_fp4(packed.to(torch.int32), scales, device)
+        if len(self._cache) >= self._cache_size:
+            self._cache.pop(next(iter(self._cache)))
+        self._cache[key] = (packed, W)
+        return W
+
+    def forward(self, x: torch.Tensor, packed_weight: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+        W = self._weight(packed_weight, scales, x.device)
+        y = ops.linear(x.reshape(-1, x.shape[-1]).to(torch.bfloat16), W)
+        return y.to(x.dtype if x.is_floating_point() else torch.bfloat16).reshape(*x.shape[:-1], -1)
+
+    __call__ = forward
+
+
+def pack_int8_weights(weights: torch.Tensor) -> torch.Tensor:
+    """``[K, N]`` weights in ``[-1, 1]`` -> int8 codes ``round(w * 127)`` packed four to a word along K: ``[ceil(K / 4), N]`` (int32
+    holding the uint32 bit pattern; byte ``i`` of a word is row ``4 r + i``).  Reference ``ops/gemm_int8.py:165``."""
+    q = torch.clamp(torch.round(weights.float() * 127.0), -128, 127).to(torch.int32)
+    K, N = q.shape
+    pad = (-K) % 4
+    if pad:
+        q = torch.cat([q, torch.zeros(pad, N, dtype=torch.int32, device=q.device)])
+    b = (q & 0xFF).view(-1, 4, N).to(torch.int64)
+    word = b[:, 0] | (b[:, 1] << 8) | (b[:, 2] << 16) | (b[:, 3] << 24)
+    return torch.where(word >= 2 ** 31, word - 2 ** 32, word).to(torch.int32)
+
+
+def unpack_int8_weights(packed: torch.Tensor, K: Optional[int] = None) -> torch.Tensor:
+    """Inverse of :func:`pack_int8_weights`: signed int8 values ``[K, N]``."""
+    w = packed.to(torch.int64) & 0xFFFFFFFF
+    b = torch.stack([(w >> s) & 0xFF for s in (0, 8, 16, 24)], 1).reshape(-1, packed.shape[-1])
+    q = torch.where(b >= 128, b - 256, b).to(torch.int8)
+    return q[:K] if K is not None else q
+
+
+class GemmInt8:
+    """W8A16: ``forward(activations [M, K], weights [K / 4, N] packed int8, scales [K / group, N], zeros) -> [M, N]`` with
+    ``w = (q - zero) * scale`` (reference ``ops/gemm_int8.py:35``), on the code-table GEMM / GEMV kernels."""
+
+    def __init__(self, device: Optional[str] = None):
+        self.device = device
+        self._cache: Dict[int, Any] = {}
+
+    def _linear(self, weights, scales, zeros, group_size: int, K: int, device):
+        hit = self._cache.get(weights.data_ptr())
+        if hit is not None and hit[0] is weights:
+            return hit[1]
+        from .layers import QuantizedLinear
+        from .quant.rtn import QuantizedTensor
+        q = unpack_int8_weights(weights, K)                                   # [K, N]
+        codes = (q.to(torch.int16) + 128).to(torch.uint8).t().contiguous()    # [N, K]
+        z = torch.zeros_like(scales) if zeros is None else zeros
+        qt = QuantizedTensor(codes, scales.t().contiguous().to(torch.float16), (z.t().contiguous().float() + 128.0).to(torch.float16), "int8",
+                             group_size, 8)
+        lin = QuantizedLinear(qt, None, device)
+        self._cache = {weights.data_ptr(): (weights, lin)} if len(self._cache) > 32 else {**self._cache, weights.data_ptr(): (weights, lin)}
+        return lin
+
+    def forward(self, activations: torch.Tensor, weights: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor] = None,
+                group_size: int = 128) -> torch.Tensor:
+        x = activations.reshape(-1, activations.shape[-1])
+        lin = self._linear(weights, scales, zeros, group_size, x.shape[-1], self.device or x.device)
+        y = lin(x.to(torch.bfloat16) if x.device.type == "cuda" else x)
+        return y.to(activations.dtype).reshape(*activations.shape[:-1], -1)
+
+    __call__ = forward

@@ -285,3 +285,13 @@ def compare_memory_usage(seq_lens: Sequence[int], max_seq_len: int, block_config
 
 __all__ = [n for n in dir() if not n.startswith("_") and n not in ("annotations", "enum", "dataclass", "field", "torch", "Dict", "List",
                                                                      "Optional", "Sequence", "Tuple")]
+
+
+def __getattr__(name: str):
+    if name == "VisionEncoderCache":                 # content-addressed cache of encoded images (kept with the vision front end)
+        from ..vision import VisionEncoderCache
+        return VisionEncoderCache
+    raise AttributeError(name)
+
+
+__all__ += ["VisionEncoderCache"]

@@ -1140,3 +1140,14 @@ def prefill_attention(q, k, v, cu_q, *, cu_k=None, block_tables=None, ctx_lens=N
 if os.environ.get("MMB200_TUNING_FILE"):      # a table written by `metal-marlin autotune` replaces the built-in thresholds
     from ..autotune import load_config as _load_tuning
     _load_tuning()
+
+
+def __getattr__(name: str):
+    # operation objects of the reference's ``ops`` package (GEMM classes, int8 packer, quantized linear module)
+    if name in ("GemmFp4", "GemmInt8", "pack_int8_weights", "unpack_int8_weights"):
+        from .. import compat_api
+        return getattr(compat_api, name)
+    if name == "MetalQuantizedLinear":
+        from ..hf import QuantizedLinearModule
+        return QuantizedLinearModule
+    raise AttributeError(name)

@@ -168,3 +168,8 @@ def profile_kernel(name: Optional[str] = None):
 
 def profile_records() -> Dict[str, List[float]]:
     return _global_timer.records
+
+
+def get_timer() -> KernelTimer:
+    """The process-wide timer behind ``profile_kernel`` (reference ``profiling/kernel_timer.py:62``)."""
+    return _global_timer

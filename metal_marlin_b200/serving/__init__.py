@@ -9,6 +9,8 @@ from dataclasses import dataclass
 from typing import List
 
 _LAZY = {
+    "ServingCppDispatcher": (".native_dispatch", "ServingCppDispatcher"), "ServingCppEngineWrapper": (".native_dispatch", "ServingCppEngineWrapper"),
+    "create_serving_cpp_dispatcher": (".native_dispatch", "create_serving_cpp_dispatcher"), "DispatchHandle": (".native_dispatch", "DispatchHandle"),
     "SchedulerConfig": ("..engine.scheduler", "SchedulerConfig"), "ContinuousSchedulerConfig": ("..engine.scheduler", "SchedulerConfig"),
     "PreemptionPolicy": ("..engine.scheduler", "PreemptionPolicy"), "RequestPriority": ("..engine.request", "RequestPriority"),
     "RequestState": ("..engine.request", "RunningRequest"), "ModelConfig": ("..models.config", "ModelConfig"),

@@ -336,18 +336,7 @@ def build_vlm_precision_map(weights: Dict[str, Any], vision_config: Any = None, 
 def pack_vlm_mixed_format(weights: Dict[str, Any], precision_map: Dict[str, Tuple[Any, int]], output_path: str):
     """Quantize every tensor to its mapped precision into one mixed-format file; tensors without an entry (vectors) are kept in
     16 bits.  Returns the pack."""
-    from ..converters.mixed_format import MixedFormatPack
-    pack = MixedFormatPack()
-    for name, w in weights.items():
-        t = torch.as_tensor(np.asarray(w)) if not isinstance(w, torch.Tensor) else w
-        prec, gs = precision_map.get(name, (None, 0))
-        fmt = getattr(prec, "value", prec) or "bf16"
-        if fmt in ("bf16", "fp16") or t.dim() != 2 or t.shape[1] % 8:
-            pack.add(name, t.to(torch.bfloat16) if t.is_floating_point() else t, "keep")
-            continue
-        gs = gs or 128
-        while t.shape[1] % gs:
-            gs //= 2
-        pack.add(name, t, fmt, gs)
+    from ..converters.mixed_format import build_mixed_pack
+    pack = build_mixed_pack(weights, precision_map)
     pack.save(output_path)
     return pack

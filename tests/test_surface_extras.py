@@ -1,0 +1,240 @@
+"""FLOP calculator, GEMM operation objects, mixed-format model packing, visualization, native dispatch wrapper and the
+graph-captured decoder layer."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+
+# ------------------------------------------------------------------------------------------------ FLOPs
+def test_flops_calculator():
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.utils import (LayerFLOPsCalculator, calculate_layer_flops, estimate_marlin_linear_flops, profile_model_layers)
+    assert estimate_marlin_linear_flops(64, 32, 2, 3, quantized=False, include_bias=False) == 2 * 6 * 64 * 32
+    assert estimate_marlin_linear_flops(64, 32, 2, 3, quantized=False, include_bias=True) == 2 * 6 * 64 * 32 + 6 * 32
+    assert estimate_marlin_linear_flops(64, 32, 1, 300, quantized=True, include_bias=False) == 2 * 300 * 64 * 32 + 3 * 64 * 32
+    assert calculate_layer_flops("linear", in_features=64, out_features=32, batch_size=2, seq_len=3, quantized=False) == 2 * 6 * 64 * 32
+    assert calculate_layer_flops("attention", batch_size=1, seq_len=8, num_heads=2, head_dim=4) == 4 * 2 * 64 * 4 + 5 * 2 * 64
+    assert calculate_layer_flops("layernorm", batch_size=2, seq_len=4, hidden_dim=16) == 5 * 8 * 16 and calculate_layer_flops("embedding") == 0
+    with pytest.raises(ValueError):
+        calculate_layer_flops("conv3d")
+    model = nn.Sequential(nn.Embedding(10, 16), nn.Linear(16, 32), nn.LayerNorm(32), nn.Linear(32, 8, bias=False))
+    calc = profile_model_layers(model, batch_size=2, seq_len=5, quantized=False)
+    assert [r.module_type for r in calc.get_results()] == ["Embedding", "Linear", "LayerNorm", "Linear"]
+    assert calc.get_layer("1").flops == 2 * 10 * 16 * 32 + 10 * 32 and calc.get_layer("3").flops == 2 * 10 * 32 * 8
+    assert calc.total_params == sum(p.numel() for p in model.parameters()) and calc.total_tflops == calc.total_flops / 1e12
+    assert calc.add_module("x", nn.ReLU()) is None and "GFLOP" in calc.summary_text(2)
+    r = LayerFLOPsCalculator().add_module("lin", nn.Linear(8, 4), input_shape=(3, 7, 8))
+    assert r.flops == 2 * 21 * 8 * 4 + 21 * 4 and r.gflops == r.flops / 1e9
+    from metal_marlin_b200.layers import MMFP4Linear
+    q = LayerFLOPsCalculator(1, 1).add_module("q", MMFP4Linear.from_float(torch.randn(32, 128), group_size=64, device="cpu"))
+    assert q.metadata["quantized"] and q.flops == 2 * 128 * 32 + 128 * 32
+    cfg = get_preset("glm-4.7-flash")
+    c = profile_model_layers(cfg, 1, 1, quantized=False)
+    active = cfg.param_count()["active"]
+    assert 0.98 < c.total_flops / (2 * active) < 1.05                      # decode FLOPs are twice the active parameters plus a little
+    assert c.get_layer("layers.0.mlp") is not None and c.get_layer("layers.1.moe.routed").metadata["experts_per_token"] == cfg.num_experts_per_tok
+    calc.clear()
+    assert calc.total_flops == 0
+
+
+# ------------------------------------------------------------------------------------------------ GEMM objects
+def test_gemm_operation_objects():
+    import metal_marlin_b200.ops as ops
+    from metal_marlin_b200.compat_api import pack_fp4_weights, unpack_fp4_weights
+    torch.manual_seed(0)
+    w = torch.rand(256, 64) * 2 - 1
+    p = ops.pack_int8_weights(w)
+    q = ops.unpack_int8_weights(p, 256)
+    assert p.shape == (64, 64) and p.dtype == torch.int32 and torch.equal(q.float(), torch.clamp(torch.round(w * 127), -128, 127))
+    assert ops.pack_int8_weights(w[:254]).shape == (64, 64) and torch.equal(ops.unpack_int8_weights(ops.pack_int8_weights(w[:254]), 254), q[:254])
+    scales = torch.full((4, 64), 1 / 127.0)
+    x = torch.randn(5, 256)
+    g8 = ops.GemmInt8()
+    ref = x @ (q.float() / 127)
+    assert float((g8(x, p, scales, None, 64) - ref).norm() / ref.norm()) < 5e-3
+    zeros = torch.full((4, 64), 3.0)
+    ref_z = x @ ((q.float() - 3) / 127)
+    assert float((ops.GemmInt8().forward(x, p, scales, zeros, 64) - ref_z).norm() / ref_z.norm()) < 5e-3
+    W = torch.randn(128, 32) * 0.1
+    pk, sc, meta = pack_fp4_weights(W.numpy(), 64, output_backend="torch")
+    g4 = ops.GemmFp4()
+    x4 = torch.randn(2, 3, 128)
+    y = g4(x4, pk, sc, 64)
+    ref4 = x4 @ torch.from_numpy(unpack_fp4_weights(pk.numpy(), sc.numpy(), meta).astype(np.float32))
+    assert y.shape == (2, 3, 32) and float((y - ref4).norm() / ref4.norm()) < 0.02
+    g4(x4, pk, sc, 64)
+    assert len(g4._cache) == 1                                              # the device weight of a packed tensor is built once
+    assert ops.MetalQuantizedLinear is not None
+    with pytest.raises(AttributeError):
+        ops.no_such_name
+
+
+# ------------------------------------------------------------------------------------------------ mixed-format model
+def test_mixed_format_model_roundtrip(tmp_path):
+    import metal_marlin_b200.converters as conv
+    from metal_marlin_b200.compat_api import Precision
+    torch.manual_seed(0)
+    weights = {"a.weight": torch.randn(32, 128), "b.weight": torch.randn(16, 96).numpy(), "norm.weight": torch.ones(128), "c.weight": torch.randn(8, 64)}
+    pmap = {"a.weight": (Precision.FP4, 64), "b.weight": (Precision.INT8, 64), "c.weight": (Precision.BF16, 0)}
+    out = str(tmp_path / "m" / "model.safetensors")
+    h = conv.pack_mixed_format_model(weights, pmap, out)
+    assert h.layer_formats["a.weight"] == "fp4" and h.layer_group_sizes["b.weight"] == 32 and h.layer_formats["norm.weight"] == "bf16"
+    assert h.total_params == 32 * 128 + 16 * 96 + 128 + 8 * 64 and h.quantized_params == 32 * 128 + 16 * 96 and 4 < h.average_bits < 8
+    assert "x fp4" in h.summary() and conv.MixedFormatHeader.from_json(h.to_json()) == h
+    tensors, h2 = conv.load_mixed_format_model(out)
+    assert h2 == h and "a.weight.scales" in tensors and tensors["c.weight"].dtype == torch.bfloat16
+    assert h2.get_format("a.weight.scales") == "fp4" and h2.get_group_size("a.weight") == 64 and h2.get_format("zzz") is None
+    assert conv.get_layer_precision(h2, "b.weight") == (Precision.INT8, 32) and conv.get_layer_precision(h2, "zzz") == (Precision.FP16, 0)
+    back = conv.MixedFormatPack.load(out)
+    assert float((back.dequantize("a.weight") - weights["a.weight"]).norm() / weights["a.weight"].norm()) < 0.15
+    other = str(tmp_path / "m" / "second.safetensors")
+    conv.pack_mixed_format_model({"d.weight": torch.randn(8, 64)}, {"d.weight": (Precision.INT4, 32)}, other)
+    hm = conv.merge_mixed_format_models([out, other], str(tmp_path / "m" / "merged.safetensors"))
+    assert set(hm.layer_formats) == set(h.layer_formats) | {"d.weight"} and hm.total_params == h.total_params + 8 * 64
+    with pytest.raises(ValueError):
+        conv.merge_mixed_format_models([out, out], str(tmp_path / "m" / "dup.safetensors"))
+    with pytest.raises(FileNotFoundError):
+        conv.load_mixed_format_model(str(tmp_path / "none.safetensors"))
+    from metal_marlin_b200.formats.safetensors_io import save_file
+    plain = str(tmp_path / "plain.safetensors")
+    save_file({"x": torch.zeros(2)}, plain)
+    with pytest.raises(ValueError):
+        conv.load_mixed_format_model(plain)
+
+
+# ------------------------------------------------------------------------------------------------ visualization
+def test_error_metrics_and_analyzer():
+    from metal_marlin_b200.visualization import ErrorAnalyzer, ErrorMetrics
+    torch.manual_seed(0)
+    o = torch.randn(64, 64)
+    q = o + 0.01 * torch.randn(64, 64)
+    m = ErrorMetrics.from_tensors(o, q.numpy(), bits_per_weight=4.25)
+    e = (q - o).double()
+    assert m.mse == pytest.approx(float(e.pow(2).mean())) and m.rmse == pytest.approx(math.sqrt(m.mse)) and m.mae == pytest.approx(float(e.abs().mean()))
+    assert m.snr == pytest.approx(10 * math.log10(float(o.double().pow(2).mean()) / m.mse)) and m.psnr > m.snr
+    assert m.cosine_similarity > 0.999 and m.correlation > 0.999 and m.compression_ratio == pytest.approx(16 / 4.25) and abs(m.quantization_kurtosis) < 0.5
+    assert 0 < m.outlier_ratio < 0.2 and set(m.to_dict()) >= {"mse", "psnr", "outlier_ratio"}
+    same = ErrorMetrics.from_tensors(o, o)
+    assert same.mse == 0 and same.snr == float("inf") and same.cosine_similarity == pytest.approx(1.0)
+    with pytest.raises(ValueError):
+        ErrorMetrics.from_tensors(o, o[:3])
+    an = ErrorAnalyzer()
+    for i, noise in enumerate((0.01, 0.05, 0.02)):
+        an.add_layer_metrics(f"l{i}", "fp4", ErrorMetrics.from_tensors(o, o + noise * torch.randn(64, 64), 4.25))
+        an.add_layer_metrics(f"l{i}", "int8", ErrorMetrics.from_tensors(o, o + noise / 10 * torch.randn(64, 64), 8.25))
+    assert an.formats() == ["fp4", "int8"] and set(an.get_layer_comparison("l1")) == {"fp4", "int8"} and an.get_layer_comparison("zz") is None
+    s = an.get_format_summary("fp4")
+    assert s["num_layers"] == 3 and s["max_rmse"] == pytest.approx(an.layer_metrics["l1"]["fp4"].rmse) and an.get_format_summary("nf4") == {}
+    assert an.get_best_format_per_layer("rmse")["l0"][0] == "int8" and an.get_best_format_per_layer("snr")["l0"][0] == "int8"
+    assert [l for l, _ in an.identify_problematic_layers("fp4")] == ["l1", "l2", "l0"] and an.identify_problematic_layers("fp4", threshold_rmse=0.03, top_k=5)[0][0] == "l1"
+    assert len(an.identify_problematic_layers("fp4", threshold_rmse=0.03)) == 1 and set(an.to_dict()) == {"layers", "formats"}
+
+
+def test_weight_visualizer_and_plots(tmp_path):
+    from metal_marlin_b200.formats.safetensors_io import save_file
+    from metal_marlin_b200.visualization import (WeightVisualizer, plot_error_distribution, plot_error_heatmap, plot_layer_errors, plot_weight_comparison)
+    torch.manual_seed(0)
+    ws = {f"model.layers.{i}.mlp.up_proj.weight": torch.randn(64, 128) * (0.02 * (i + 1)) for i in range(4)}
+    ws["model.norm.weight"] = torch.ones(128)
+    ws["model.layers.0.idx"] = torch.zeros(4, 4, dtype=torch.int32)
+    f = str(tmp_path / "model.safetensors")
+    save_file(ws, f)
+    viz = WeightVisualizer.from_safetensors(f, group_size=64)
+    assert len(viz.layer_names()) == 4 and len(WeightVisualizer.from_safetensors(str(tmp_path), max_tensors=2).layer_names()) == 2
+    assert WeightVisualizer.from_safetensors(f, name_filter="layers.3").layer_names() == ["model.layers.3.mlp.up_proj.weight"]
+    name = "model.layers.1.mlp.up_proj.weight"
+    m4, m8 = viz.compare_quantization(name, "fp4"), viz.compare_quantization(name, "int8")
+    assert m8.rmse < m4.rmse and m4.bits_per_weight == 4.25 and 15 < m4.snr < 25
+    assert set(viz.compare_formats(name, ("int4", "nf4"))) == {"int4", "nf4"}
+    with pytest.raises(KeyError):
+        viz.compare_quantization("nope", "fp4")
+    with pytest.raises(ValueError):
+        viz.compare_quantization(name, "fp5")
+    rep = viz.generate_error_report(str(tmp_path / "rep"), ("fp4", "int8"), plots_for_worst=1)
+    files = set(os.listdir(tmp_path / "rep"))
+    assert {"error_report.json", "layer_errors_fp4.png", "layer_errors_int8.png", "heatmap_model_layers_3_mlp_up_proj_weight_fp4.png",
+            "compare_model_layers_3_mlp_up_proj_weight_fp4.png"} <= files
+    assert json.load(open(tmp_path / "rep" / "error_report.json"))["problematic_layers"]["fp4"][0][0] == "model.layers.3.mlp.up_proj.weight"
+    assert rep["formats"]["int8"]["mean_snr"] > rep["formats"]["fp4"]["mean_snr"] and rep["best_format_per_layer"][name]["format"] == "int8"
+    o = ws[name]
+    q = viz.quantize(name, "fp4")
+    hm = plot_error_heatmap(o, q, str(tmp_path / "p" / "h.png"), title="t")
+    assert hm.shape == (64 + 16, 128, 3) and hm.dtype == np.uint8 and os.path.getsize(tmp_path / "p" / "h.png") > 0
+    big = plot_error_heatmap(torch.randn(300, 1000), torch.randn(300, 1000), max_side=100)
+    assert big.shape[0] <= 100 and big.shape[1] <= 100
+    exact = plot_error_heatmap(o, o)
+    assert (exact == 255).all()                                             # zero error is white
+    cmp_img = plot_weight_comparison(o, q)
+    assert cmp_img.shape == (64 + 16, 3 * 128 + 12, 3)
+    d1 = plot_error_distribution(q - o, title="fp4")
+    d2 = plot_error_distribution({"fp4": q - o, "int8": viz.quantize(name, "int8") - o}, str(tmp_path / "p" / "d.png"), log=False)
+    assert d1.shape == d2.shape == (360, 640, 3) and (d1 != 255).any() and (d2 != 255).any()
+    bars = plot_layer_errors({f"l{i}": float(i) for i in range(10)}, highlight_top=2)
+    assert bars.shape == (360, 800, 3) and ((bars == np.array([210, 60, 50])).all(-1)).any() and ((bars == np.array([40, 90, 200])).all(-1)).any()
+    assert plot_layer_errors({}).shape == (360, 800, 3)
+    assert viz.plot_error_distribution(name, ("fp4", "int4")).shape == (360, 640, 3)
+
+
+# ------------------------------------------------------------------------------------------------ dispatch wrapper, traced layer
+def test_native_dispatch_wrapper_on_cpu():
+    from metal_marlin_b200.serving import ServingCppDispatcher, ServingCppEngineWrapper, create_serving_cpp_dispatcher
+    d = ServingCppDispatcher("cpu")
+    assert d.available is False and create_serving_cpp_dispatcher("cpu") is None
+    with pytest.raises(RuntimeError):
+        d.dispatch_sync("rmsnorm", torch.zeros(1))
+    assert d.dispatch_sync(lambda a, b=1: a + b, 2, b=3) == 5
+    h = d.dispatch_async(torch.add, torch.ones(2), torch.ones(2))
+    assert d.is_complete(h) and torch.equal(d.wait(h), torch.full((2,), 2.0))
+    m = d.get_metrics()
+    assert m["sync_dispatches"] == 1 and m["async_dispatches"] == 1 and m["total_dispatches"] == 2 and m["waits"] == 1 and m["avg_host_launch_us"] > 0
+    d.reset_metrics()
+    assert d.get_metrics()["total_dispatches"] == 0
+    w = ServingCppEngineWrapper(dispatcher=d)
+    assert w.available is False and w.dispatch_for_decode(lambda: 7) == 7 and w.wait(w.dispatch_for_prefill(lambda: 8)) == 8
+    assert w.get_metrics()["decode_calls"] == 1 and w.get_metrics()["prefill_calls"] == 1
+
+
+def test_traced_decoder_layer_eager_path():
+    from metal_marlin_b200.engine.traced import TracedDecoderLayer
+    lin = nn.Linear(16, 16)
+    calls = []
+
+    def layer(h, scale=None):
+        calls.append(1)
+        return (lin(h) * scale, None)
+    s = torch.tensor(2.0)
+    t = TracedDecoderLayer(layer, batch_size=2, seq_len=3, hidden_size=16, dtype=torch.float32, device="cpu")
+    x = torch.randn(2, 3, 16)
+    y = t(x, scale=s)
+    assert torch.allclose(y, lin(x) * 2) and t.shape == (2, 3, 16) and t.replays == 0
+    s.fill_(3.0)                                                            # tensors bound at compile are read at call time
+    assert torch.allclose(t(x, scale=s), lin(x) * 3)
+    with pytest.raises(ValueError):
+        t(torch.randn(1, 3, 16))
+    with pytest.raises(ValueError):
+        t(x, scale=torch.tensor(1.0))
+
+
+@pytest.mark.gpu
+def test_traced_decoder_layer_graph_replay_gpu():
+    from metal_marlin_b200.engine.traced import TracedDecoderLayer
+    from metal_marlin_b200.serving import ServingCppDispatcher
+    torch.manual_seed(0)
+    lin = nn.Linear(64, 64).cuda().bfloat16()
+    t = TracedDecoderLayer(lambda h: torch.nn.functional.silu(lin(h)) + h, 1, 4, 64)
+    for _ in range(3):
+        x = torch.randn(1, 4, 64, device="cuda", dtype=torch.bfloat16)
+        ref = torch.nn.functional.silu(lin(x)) + x
+        assert torch.allclose(t(x).float(), ref.float(), atol=2e-2)
+    assert t.replays == 3
+    d = ServingCppDispatcher()
+    assert d.available
+    x = torch.randn(8, 64, device="cuda", dtype=torch.bfloat16)
+    h = d.dispatch_async(torch.add, x, x)
+    assert torch.equal(d.wait(h), x + x) and d.is_complete(h)
+    assert torch.equal(d.dispatch_sync(torch.mul, x, 2), x * 2)
