@@ -90,3 +90,56 @@ def test_directory_import_manifest_and_coverage(tmp_path):
         qmi4.ArtifactManifest([qmi4.Int4TensorArtifact("mlp_up", 0, "q", "s", "z", 8, 8, 32)]).validate(SHAPES)
     with pytest.raises(ValueError):          # the same (layer, role) twice
         qmi4.ArtifactManifest([arts[0], arts[0]]).validate(SHAPES)
+
+
+def test_artifact_parity_validation(tmp_path):
+    """Kernel-path output of the INT4 layers against the float64 oracle over the packed words (reference
+    ``tests/test_qwen36_27b_validation.py``: projection, MLP, full-attention, linear-block and LM-head parity)."""
+    from metal_marlin_b200.converters import qmi4_validation as val
+    assert val.sample_columns(5, 8) == (0, 1, 2, 3, 4)
+    cols = val.sample_columns(1000, 16)
+    assert len(cols) <= 16 and cols[0] == 0 and cols[-1] == 999 and 500 in cols and list(cols) == sorted(set(cols))
+    with pytest.raises(ValueError):
+        val.sample_columns(10, 0)
+    t = _tensor("mlp_up", seed=3)
+    x = torch.randn(t.in_features, generator=torch.Generator().manual_seed(1))
+    want = (t.dequantize().double() @ x.double())
+    assert torch.allclose(val.oracle_columns(x, t, (0, 7, t.out_features - 1)), want[[0, 7, t.out_features - 1]], atol=1e-9)
+
+    src = str(tmp_path / "proto")
+    os.makedirs(src)
+    legacy = {v: k for k, v in qmi4.LEGACY_NAMES.items() if k != "beta"}
+    for role in qmi4.REQUIRED_ROLES:
+        qmi4.write_qmi4_tensor(os.path.join(src, legacy[role] + ".qmi4"), _tensor(role, seed=len(role)))
+    out = str(tmp_path / "artifact")
+    qmi4.import_qmi4_directory(src, out, layer_index=None, shapes=SHAPES)
+    mlp = val.validate_mlp(out, None, max_columns=16, device="cpu", shapes=SHAPES)
+    assert [r.role for r in mlp.results] == ["mlp_gate", "mlp_up", "mlp_down"] and mlp.norms["intermediate"] > 0
+    mlp.assert_within(atol=8e-3, rtol=2e-2)
+    att = val.validate_full_attention(out, None, max_columns=16, device="cpu", shapes=SHAPES, kv_heads=CFG.num_key_value_heads)
+    assert set(att.by_role()) == set(qmi4.FULL_ATTENTION_ROLES)
+    att.assert_within(atol=8e-3, rtol=2e-2)
+    lin = val.validate_linear_block(out, None, max_columns=16, device="cpu", shapes=SHAPES)
+    assert set(lin.by_role()) == set(qmi4.LINEAR_ATTENTION_ROLES)
+    lin.assert_within(atol=8e-3, rtol=2e-2)
+    head = val.validate_lm_head(out, max_columns=32, device="cpu", shapes=SHAPES)
+    head.assert_within(atol=8e-3, rtol=2e-2)
+    proj = val.validate_projections(out, None, roles=("linear_attn_q", "full_attn_k"), device="cpu", shapes=SHAPES)
+    assert len(proj.results) == 2 and proj.max_abs_error < 8e-3 and proj.max_rel_error >= 0
+    everything = val.validate_all(out, linear_layer=None, attention_layer=None, device="cpu", shapes=SHAPES)
+    assert set(everything) == {"linear_block", "full_attention", "lm_head"}          # the MLP scan covers numbered layers only
+    # a corrupted artifact is caught: flip the scales of one tensor on disk
+    m = qmi4.read_manifest(os.path.join(out, "manifest.json"), SHAPES)
+    art = m.index()[(None, "mlp_down")]
+    good = val._Layer(out, None, "cpu", SHAPES)
+    bad_t = good.tensors["mlp_down"]
+    xin = torch.randn(bad_t.in_features, generator=torch.Generator().manual_seed(2))
+    y = good.run("mlp_down", xin)
+    broken = dataclasses.replace(bad_t, scales=bad_t.scales * 1.5)
+    res = val.compare("mlp_down", xin, broken, y, 16)
+    bv = val.BlockValidation(out, "mlp", [res])
+    with pytest.raises(AssertionError):
+        bv.assert_within(atol=8e-3, rtol=2e-2)
+    with pytest.raises(KeyError):
+        val.validate_mlp(out, 5, device="cpu", shapes=SHAPES)
+    assert art.role == "mlp_down"
