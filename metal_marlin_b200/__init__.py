@@ -24,6 +24,13 @@ def _reg(module: str, *names: str, **aliases: str) -> None:
 
 
 _reg("._compat", "E2M1_VALUES", "NF4_VALUES")
+_reg(".compat_api", "silu_metal", "gelu_metal", "relu_metal", "swiglu_fused_metal", "geglu_fused_metal", "GemmFp4", "GemmInt8", "pack_int8_weights",
+     "unpack_int8_weights")
+_reg(".memory.pools", "TransientBuffer", "TransientBufferCPP", "get_transient_buffer_cpp", "reset_transient_buffer_cpp", "transient_buffer_cpp_stats")
+_reg(".converters.activation_stats", "CalibrationDatasetLoader", "compute_activation_ranges", "ranges_to_scales", "save_ranges", "load_ranges")
+_reg(".models.qwen36_profile", "Qwen36ModelProfile", "QWEN36_27B_PROFILE", "profile_from_hf_config", "load_profile_from_config_file",
+     "shape_contract_payload", "is_qwen36_27b_profile", "is_qwen36_27b_config", "validate_supported_profile")
+_reg(".analysis.moe_routing", "MoERoutingProfiler", "simulate_routing_for_model", "analyze_routing_from_file")
 _reg(".dtypes", "DTypeConfig", "get_dtype_config", "to_torch_dtype")
 _reg(".inference.pipeline", "MMFP4Pipeline", "MarlinPipeline", "StreamingOutput")
 _reg(".models.mmfp4_causal_lm", MetalMarlinModel="MMFP4ForCausalLM")

@@ -1325,3 +1325,32 @@ class GemmInt8:
         return y.to(activations.dtype).reshape(*activations.shape[:-1], -1)
 
     __call__ = forward
+
+
+# ------------------------------------------------------------------------------------------------ activation functions
+def silu_metal(x: torch.Tensor) -> torch.Tensor:
+    return torch.nn.functional.silu(x)
+
+
+def gelu_metal(x: torch.Tensor) -> torch.Tensor:
+    return torch.nn.functional.gelu(x)
+
+
+def relu_metal(x: torch.Tensor) -> torch.Tensor:
+    return torch.relu(x)
+
+
+def swiglu_fused_metal(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up``; bf16 CUDA tensors go through the fused kernel (one read of each input, one write)."""
+    if gate.shape != up.shape:
+        raise ValueError(f"gate {tuple(gate.shape)} and up {tuple(up.shape)} differ in shape")
+    if gate.is_cuda and gate.dtype == torch.bfloat16 and gate.dim() >= 1 and gate.shape[-1] % 8 == 0:
+        gu = torch.cat([gate.reshape(-1, gate.shape[-1]), up.reshape(-1, up.shape[-1])], -1)
+        return ops.silu_mul(gu).reshape(gate.shape)
+    return torch.nn.functional.silu(gate) * up
+
+
+def geglu_fused_metal(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    if gate.shape != up.shape:
+        raise ValueError(f"gate {tuple(gate.shape)} and up {tuple(up.shape)} differ in shape")
+    return torch.nn.functional.gelu(gate) * up

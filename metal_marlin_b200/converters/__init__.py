@@ -115,7 +115,8 @@ def convert_checkpoint(src: str, dst: str, from_format: str = "auto", to_format:
 
 # the reference's ``converters`` package names, resolved on first use
 _LAZY = {
-    ".activation_stats": ["CalibrationCollector", "CalibrationDataset", "CalibrationStats", "compute_scales"],
+    ".activation_stats": ["CalibrationCollector", "CalibrationDataset", "CalibrationStats", "compute_scales", "CalibrationDatasetLoader",
+                          "compute_activation_ranges", "ranges_to_scales", "save_ranges", "load_ranges"],
     ".quantize_report": ["LayerReport", "QuantizationReport", "quantize_model"],
     ".custom_ops": ["MarlinFlashAttentionOp", "MarlinQuantizedLinearOp", "MarlinQuantizedMatMulOp", "MarlinSession", "create_session",
                     "export_with_marlin_ops"],

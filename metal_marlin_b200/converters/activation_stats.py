@@ -229,3 +229,107 @@ def compute_scales(stats: Dict[str, CalibrationStats], quant_type: str = "fp4", 
         else:
             raise ValueError(f"quant_type must be 'fp4', 'int4_sym' or 'int4_asym', got {quant_type!r}")
     return out
+
+
+# ------------------------------------------------------------------------------------------------ activation ranges of a whole model
+class CalibrationDatasetLoader:
+    """Named loaders (reference ``calibration_utils.py:138``): ``v3`` is the multi-domain text set (local file, see
+    ``CalibrationDataset.bartowski_v3``), ``from_file`` any text file."""
+
+    @classmethod
+    def v3(cls, max_samples: Optional[int] = None, cache_dir: Optional[str] = None, force_download: bool = False, min_sample_length: int = 100
+           ) -> CalibrationDataset:
+        if force_download:
+            raise RuntimeError("there is no download path in this build: place calibration_datav3.txt in the calibration directory")
+        ds = CalibrationDataset.bartowski_v3(None, cache_dir)
+        ds.samples = [s for s in ds.samples if len(s) >= min_sample_length][: max_samples]
+        return ds
+
+    @classmethod
+    def from_file(cls, path: str, max_samples: Optional[int] = None, min_sample_length: int = 1) -> CalibrationDataset:
+        return CalibrationDataset.from_file(path, max_samples, min_sample_length)
+
+
+def compute_activation_ranges(model, calibration, layers: Optional[Sequence[str]] = None, batch_size: int = 1, max_seq_len: int = 2048,
+                              tokenizer=None, verbose: bool = False) -> Dict[str, Tuple[float, float]]:
+    """``{layer name: (min, max)}`` of the inputs of a model's linear layers over a calibration set.
+
+    ``model``: a ``torch.nn.Module`` (hooks on its ``nn.Linear`` modules; ``calibration`` is then an iterable of input tensors, or a
+    ``CalibrationDataset`` with a ``tokenizer``) or an engine model with ``forward_logits`` (statistics per checkpoint tensor name
+    through the operator capture hook; ``calibration``: token-id sequences, or texts with a ``tokenizer``).
+    Reference ``calibration_utils.py:318``."""
+    def token_seqs():
+        for item in calibration:
+            if isinstance(item, str):
+                if tokenizer is None:
+                    raise ValueError("text calibration samples need a tokenizer")
+                ids = tokenizer.encode(item) if hasattr(tokenizer, "encode") else tokenizer(item)["input_ids"]
+                yield [int(t) for t in ids][:max_seq_len]
+            else:
+                yield item
+
+    ranges: Dict[str, Tuple[float, float]] = {}
+
+    def note(name: str, x: torch.Tensor):
+        lo, hi = float(x.min()), float(x.max())
+        old = ranges.get(name)
+        ranges[name] = (lo, hi) if old is None else (min(old[0], lo), max(old[1], hi))
+
+    if isinstance(model, nn.Module):
+        col = CalibrationCollector(model, layers, method="histogram", num_bins=256)
+        with torch.no_grad():
+            for item in token_seqs():
+                t = torch.as_tensor(item)
+                if t.dtype in (torch.int32, torch.int64) and t.dim() == 1:
+                    t = t[:max_seq_len].unsqueeze(0)
+                model(t)
+        col.remove_hooks()
+        return {k: (float(s.min_val), float(s.max_val)) for k, s in col.stats.items()}
+    from .. import ops
+
+    def hook(kind, W, x, ids):
+        names = getattr(W, "names", None)
+        if kind != "linear" or not names:
+            return
+        for name, _rows in names:
+            if layers is None or any(name.startswith(p) or p in name for p in layers):
+                note(name, x)
+
+    ops.set_capture(hook)
+    try:
+        with torch.no_grad():
+            for i, seq in enumerate(token_seqs()):
+                model.forward_logits([int(t) for t in torch.as_tensor(seq).reshape(-1)[:max_seq_len]])
+                if verbose:
+                    print(f"calibration sample {i + 1}: {len(ranges)} layers tracked")
+    finally:
+        ops.set_capture(None)
+    return ranges
+
+
+def ranges_to_scales(ranges: Dict[str, Tuple[float, float]], quant_type: str = "fp4") -> Dict[str, float]:
+    """One scale per layer from its ``(min, max)``: ``absmax / 6`` (``fp4``), ``/ 7`` (``int4_sym``), ``/ 127`` (``int8_sym``), ``(max - min) / 15``
+    (``int4_asym``)."""
+    div = {"fp4": 6.0, "int4_sym": 7.0, "int8_sym": 127.0}
+    out = {}
+    for name, (lo, hi) in ranges.items():
+        if quant_type in div:
+            out[name] = max(abs(lo), abs(hi)) / div[quant_type] or 1e-8
+        elif quant_type == "int4_asym":
+            out[name] = (hi - lo) / 15.0 or 1e-8
+        else:
+            raise ValueError(f"quant_type must be one of fp4, int4_sym, int4_asym, int8_sym; got {quant_type!r}")
+    return out
+
+
+def save_ranges(ranges: Dict[str, Tuple[float, float]], path: str) -> None:
+    import json
+    os.makedirs(os.path.dirname(os.path.abspath(str(path))), exist_ok=True)
+    with open(path, "w") as f:
+        json.dump({k: [float(a), float(b)] for k, (a, b) in ranges.items()}, f, indent=1)
+
+
+def load_ranges(path: str) -> Dict[str, Tuple[float, float]]:
+    import json
+    with open(path) as f:
+        return {k: (float(v[0]), float(v[1])) for k, v in json.load(f).items()}

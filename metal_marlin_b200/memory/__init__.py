@@ -12,10 +12,12 @@ from .expert_cache import ExpertCache, TileCoordinator
 from .model_memory import (CompactionConfig, CompactionStats, CUDAPinnedPool, ExpertMetadata, LayerMetadata, MemoryCompactor, MemoryStats,
                            MLACompressionRatio, MMAPWeightConfig, MMAPWeightManager, MMAPWeightStats, MMFP4MemoryManager, PooledBuffer)
 from .pressure import MemoryPressureMonitor, PressureLevel
-from .pools import BufferPool, BufferPoolStats, RingBuffer, TransferStream, get_ring_buffer, reset_ring_buffer
+from .pools import (BufferPool, BufferPoolStats, RingBuffer, TransferStream, TransientBuffer, TransientBufferCPP, get_ring_buffer,
+                    get_transient_buffer_cpp, reset_ring_buffer, reset_transient_buffer_cpp, transient_buffer_cpp_stats)
 from .streaming import PinnedPool, WeightStreamer
 
 __all__ = ["Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "TileCoordinator", "MemoryPressureMonitor", "PressureLevel", "PinnedPool",
            "WeightStreamer", "BufferPool", "BufferPoolStats", "RingBuffer", "TransferStream", "get_ring_buffer", "reset_ring_buffer", "CompactionConfig",
            "CompactionStats", "CUDAPinnedPool", "ExpertMetadata", "LayerMetadata", "MemoryCompactor", "MemoryStats", "MLACompressionRatio",
-           "MMAPWeightConfig", "MMAPWeightManager", "MMAPWeightStats", "MMFP4MemoryManager", "PooledBuffer"]
+           "MMAPWeightConfig", "MMAPWeightManager", "MMAPWeightStats", "MMFP4MemoryManager", "PooledBuffer", "TransientBuffer", "TransientBufferCPP",
+           "get_transient_buffer_cpp", "reset_transient_buffer_cpp", "transient_buffer_cpp_stats"]

@@ -211,3 +211,90 @@ def reset_ring_buffer(device="cpu") -> None:
     r = _rings.get(str(torch.device(device)))
     if r is not None:
         r.reset()
+
+
+# ------------------------------------------------------------------------------------------------ transient (per-pass) buffer
+class TransientBuffer:
+    """Per-pass scratch over one slab: ``allocate(size) -> (slab, offset)`` (256-byte aligned), ``tensor(shape, dtype)`` for a view,
+    ``reset()`` in O(1) at the start of a pass; one shared instance per device through ``get_for_device``.  Reference
+    ``transient_buffer_cpp.py:59`` (``TransientBufferCPP``: ``allocate`` / ``allocate_bytes`` / ``reset`` / ``capacity`` / ``used`` / ``available`` /
+    ``utilization`` / ``stats`` / ``get_for_device`` / ``reset_global``)."""
+    _instances: dict = {}
+
+    def __init__(self, device=None, capacity: int = 100 * 1024 * 1024):
+        from .arena import BumpAllocator
+        dev = torch.device(device) if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        self._bump = BumpAllocator(int(capacity), dev)
+        self._device, self._resets, self._allocs = dev, 0, 0
+
+    def reset(self) -> None:
+        self._bump.reset()
+        self._resets += 1
+
+    def allocate(self, size: int):
+        t = self._bump.alloc((int(size),), torch.uint8)
+        self._allocs += 1
+        return self._bump.slab, t.data_ptr() - self._bump.slab.data_ptr()
+
+    allocate_bytes = allocate
+
+    def tensor(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        self._allocs += 1
+        return self._bump.alloc(tuple(shape), dtype)
+
+    @property
+    def capacity(self) -> int:
+        return self._bump.slab.numel()
+
+    @property
+    def used(self) -> int:
+        return self._bump.cursor
+
+    @property
+    def available(self) -> int:
+        return self.capacity - self.used
+
+    @property
+    def utilization(self) -> float:
+        return self.used / self.capacity if self.capacity else 0.0
+
+    @property
+    def is_cpp_backend(self) -> bool:
+        return False                         # a cursor over one tensor: there is nothing for native code to add
+
+    def stats(self) -> dict:
+        return {"capacity": self.capacity, "used": self.used, "available": self.available, "utilization": self.utilization,
+                "high_water": self._bump.high_water, "allocations": self._allocs, "resets": self._resets, "device": str(self._device)}
+
+    @classmethod
+    def get_for_device(cls, device=None, capacity: int = 100 * 1024 * 1024) -> "TransientBuffer":
+        key = str(torch.device(device) if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu"))
+        inst = cls._instances.get(key)
+        if inst is None or inst.capacity < capacity:
+            inst = cls._instances[key] = cls(key, capacity)
+        return inst
+
+    @classmethod
+    def reset_global(cls) -> None:
+        cls._instances.clear()
+
+    @classmethod
+    def is_available(cls) -> bool:
+        return True
+
+
+TransientBufferCPP = TransientBuffer
+
+
+def get_transient_buffer_cpp(device=None, capacity: int = 100 * 1024 * 1024) -> TransientBuffer:
+    return TransientBuffer.get_for_device(device, capacity)
+
+
+def reset_transient_buffer_cpp() -> None:
+    TransientBuffer.reset_global()
+
+
+def transient_buffer_cpp_stats(device=None):
+    key = str(torch.device(device) if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu"))
+    inst = TransientBuffer._instances.get(key)
+    return inst.stats() if inst is not None else None

@@ -238,3 +238,83 @@ def test_traced_decoder_layer_graph_replay_gpu():
     h = d.dispatch_async(torch.add, x, x)
     assert torch.equal(d.wait(h), x + x) and d.is_complete(h)
     assert torch.equal(d.dispatch_sync(torch.mul, x, 2), x * 2)
+
+
+# ------------------------------------------------------------------------------------------------ transient buffer, ranges, activations
+def test_transient_buffer():
+    from metal_marlin_b200.memory import TransientBufferCPP, get_transient_buffer_cpp, reset_transient_buffer_cpp, transient_buffer_cpp_stats
+    reset_transient_buffer_cpp()
+    assert transient_buffer_cpp_stats("cpu") is None
+    buf = get_transient_buffer_cpp("cpu", 4096)
+    assert buf is get_transient_buffer_cpp("cpu", 1024) and TransientBufferCPP.is_available() and not buf.is_cpp_backend
+    slab, off0 = buf.allocate(100)
+    _, off1 = buf.allocate_bytes(10)
+    assert off0 == 0 and off1 == 256 and slab.numel() == 4096 and buf.used == 266 and buf.available == 4096 - 266
+    t = buf.tensor((4, 8), torch.float32)
+    t.fill_(1.5)
+    assert t.data_ptr() == slab.data_ptr() + 512 and buf.utilization == pytest.approx((512 + 128) / 4096)
+    with pytest.raises(MemoryError):
+        buf.allocate(4096)
+    buf.reset()
+    assert buf.used == 0 and buf.stats()["resets"] == 1 and buf.stats()["high_water"] == 640 and buf.stats()["allocations"] == 3
+    assert get_transient_buffer_cpp("cpu", 8192) is not buf and transient_buffer_cpp_stats("cpu")["capacity"] == 8192
+    reset_transient_buffer_cpp()
+
+
+def test_activation_ranges_and_scales(tmp_path):
+    import metal_marlin_b200 as mm
+    from metal_marlin_b200.converters import CalibrationDatasetLoader
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 4))
+    xs = [torch.randn(5, 8) * (i + 1) for i in range(3)]
+    r = mm.compute_activation_ranges(model, xs)
+    allx = torch.cat(xs)
+    assert r["0"] == (pytest.approx(float(allx.min())), pytest.approx(float(allx.max()))) and r["2"][0] >= 0
+    assert set(mm.compute_activation_ranges(model, xs, layers=["2"])) == {"2"}
+    s = mm.ranges_to_scales({"a": (-3.0, 6.0), "b": (-1.0, 0.5)}, "fp4")
+    assert s == {"a": 1.0, "b": pytest.approx(1 / 6)} and mm.ranges_to_scales({"a": (-3.0, 6.0)}, "int4_asym")["a"] == pytest.approx(0.6)
+    assert mm.ranges_to_scales({"a": (-3.0, 6.0)}, "int8_sym")["a"] == pytest.approx(6 / 127) and mm.ranges_to_scales({"a": (0.0, 0.0)}, "int4_sym")["a"] > 0
+    with pytest.raises(ValueError):
+        mm.ranges_to_scales({"a": (0, 1)}, "fp3")
+    p = str(tmp_path / "r" / "ranges.json")
+    mm.save_ranges(r, p)
+    assert mm.load_ranges(p) == {k: (float(a), float(b)) for k, (a, b) in r.items()}
+    # an engine model: ranges per checkpoint tensor through the capture hook
+    from metal_marlin_b200.formats.safetensors_io import save_file
+    from metal_marlin_b200.models.config import get_preset
+    from metal_marlin_b200.models.mmfp4_causal_lm import MMFP4ForCausalLM
+    import metal_marlin_b200.quant as q
+    cfg = get_preset("tiny-llama")
+    d = str(tmp_path / "ck")
+    q.save_random_checkpoint(cfg, d, seed=0)
+    lm = MMFP4ForCausalLM.from_pretrained(d, "cpu")
+    er = mm.compute_activation_ranges(lm, [[1, 2, 3, 4, 5], [7, 8, 9]])
+    assert any(k.endswith("q_proj.weight") for k in er) and all(lo <= hi for lo, hi in er.values())
+    assert set(mm.compute_activation_ranges(lm, [[1, 2, 3]], layers=["down_proj"])) == {k for k in er if "down_proj" in k}
+    with pytest.raises(ValueError):
+        mm.compute_activation_ranges(lm, ["some text"])
+    f = tmp_path / "calib.txt"
+    f.write_text("x" * 120 + "\n\n" + "short\n\n" + "y" * 150)
+    assert len(CalibrationDatasetLoader.from_file(str(f), min_sample_length=100)) == 2
+    (tmp_path / "calibration_datav3.txt").write_text("x" * 120 + "\n\n" + "a sample of middling size\n\n" + "y" * 150)
+    assert len(CalibrationDatasetLoader.v3(cache_dir=str(tmp_path))) == 2 and len(CalibrationDatasetLoader.v3(max_samples=1, cache_dir=str(tmp_path))) == 1
+    with pytest.raises(RuntimeError):
+        CalibrationDatasetLoader.v3(force_download=True)
+
+
+def test_activation_functions():
+    import metal_marlin_b200 as mm
+    g, u = torch.randn(3, 16), torch.randn(3, 16)
+    assert torch.allclose(mm.swiglu_fused_metal(g, u), torch.nn.functional.silu(g) * u) and torch.allclose(mm.geglu_fused_metal(g, u), torch.nn.functional.gelu(g) * u)
+    assert torch.equal(mm.relu_metal(g), torch.relu(g)) and torch.allclose(mm.silu_metal(g), torch.nn.functional.silu(g)) and torch.allclose(mm.gelu_metal(g), torch.nn.functional.gelu(g))
+    with pytest.raises(ValueError):
+        mm.swiglu_fused_metal(g, u[:2])
+
+
+@pytest.mark.gpu
+def test_swiglu_fused_kernel_gpu():
+    import metal_marlin_b200 as mm
+    torch.manual_seed(0)
+    g, u = (torch.randn(2, 5, 256, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    ref = torch.nn.functional.silu(g.float()) * u.float()
+    assert torch.allclose(mm.swiglu_fused_metal(g, u).float(), ref, atol=3e-2, rtol=2e-2)
