@@ -30,6 +30,12 @@ _reg(".memory.pools", "TransientBuffer", "TransientBufferCPP", "get_transient_bu
 _reg(".converters.activation_stats", "CalibrationDatasetLoader", "compute_activation_ranges", "ranges_to_scales", "save_ranges", "load_ranges")
 _reg(".models.qwen36_profile", "Qwen36ModelProfile", "QWEN36_27B_PROFILE", "profile_from_hf_config", "load_profile_from_config_file",
      "shape_contract_payload", "is_qwen36_27b_profile", "is_qwen36_27b_config", "validate_supported_profile")
+_reg(".utils.memory", "pad_to_multiple", "unpad")
+_reg(".converters.torch_compat", "export_for_pytorch", "import_from_pytorch")
+_reg(".memory.expert_cache", "ExpertWeightStreamer")
+_reg(".moe.fast_router", "MoERouterCpp", "RouterBatchOutput")
+_reg(".trellis.lm", TrellisConfig="TrellisModelConfig")
+_reg(".compat_api", "cholesky_decompose")
 _reg(".analysis.moe_routing", "MoERoutingProfiler", "simulate_routing_for_model", "analyze_routing_from_file")
 _reg(".dtypes", "DTypeConfig", "get_dtype_config", "to_torch_dtype")
 _reg(".inference.pipeline", "MMFP4Pipeline", "MarlinPipeline", "StreamingOutput")

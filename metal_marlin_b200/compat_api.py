@@ -1354,3 +1354,14 @@ def geglu_fused_metal(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     if gate.shape != up.shape:
         raise ValueError(f"gate {tuple(gate.shape)} and up {tuple(up.shape)} differ in shape")
     return torch.nn.functional.gelu(gate) * up
+
+
+def cholesky_decompose(H, regularization: float = 1e-6) -> np.ndarray:
+    """Lower Cholesky factor of ``H + regularization * mean(diag) * I`` in float64 (damping grows tenfold until the factorisation
+    succeeds).  Reference ``gptq_metal.py:1120``."""
+    from .quant.psd import damp_until_cholesky
+    Ht = torch.as_tensor(np.asarray(H) if not isinstance(H, torch.Tensor) else H).double()
+    Hd, _L32, lam = damp_until_cholesky(Ht, regularization)
+    if lam == lam:                       # a plain damping worked: redo the factorisation in float64 on the undamaged input
+        Hd = Ht + lam * torch.eye(Ht.shape[-1], dtype=torch.float64, device=Ht.device)
+    return torch.linalg.cholesky(Hd.double()).cpu().numpy().astype(np.float64)

@@ -123,6 +123,7 @@ _LAZY = {
     ".name_mapping": ["Rule", "detect_model_type", "estimate_memory", "get_supported_architectures", "load_and_quantize", "load_config",
                       "load_mapped_safetensors", "map_weight_names", "register_architecture"],
     ".nemo": ["convert_nemo_to_pytorch", "load_nemo"],
+    ".torch_compat": ["export_for_pytorch", "import_from_pytorch"],
     ".mixed_format": ["MixedFormatHeader", "pack_mixed_format_model", "load_mixed_format_model", "get_layer_precision", "merge_mixed_format_models",
                       "build_mixed_pack"],
     ".onnx": ["ONNXExecutor", "ONNXGraph", "ONNXOp", "load_onnx", "save_onnx"],

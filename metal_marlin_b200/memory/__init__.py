@@ -8,7 +8,7 @@ allocator bookkeeping is native (``csrc/runtime.cpp``); tensors handed out are v
 request path calls ``cudaMalloc``.
 """
 from .arena import Arena, BumpAllocator, WorkspaceBuffer
-from .expert_cache import ExpertCache, TileCoordinator
+from .expert_cache import ExpertCache, ExpertWeightStreamer, TileCoordinator
 from .model_memory import (CompactionConfig, CompactionStats, CUDAPinnedPool, ExpertMetadata, LayerMetadata, MemoryCompactor, MemoryStats,
                            MLACompressionRatio, MMAPWeightConfig, MMAPWeightManager, MMAPWeightStats, MMFP4MemoryManager, PooledBuffer)
 from .pressure import MemoryPressureMonitor, PressureLevel
@@ -16,7 +16,7 @@ from .pools import (BufferPool, BufferPoolStats, RingBuffer, TransferStream, Tra
                     get_transient_buffer_cpp, reset_ring_buffer, reset_transient_buffer_cpp, transient_buffer_cpp_stats)
 from .streaming import PinnedPool, WeightStreamer
 
-__all__ = ["Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "TileCoordinator", "MemoryPressureMonitor", "PressureLevel", "PinnedPool",
+__all__ = ["Arena", "BumpAllocator", "WorkspaceBuffer", "ExpertCache", "ExpertWeightStreamer", "TileCoordinator", "MemoryPressureMonitor", "PressureLevel", "PinnedPool",
            "WeightStreamer", "BufferPool", "BufferPoolStats", "RingBuffer", "TransferStream", "get_ring_buffer", "reset_ring_buffer", "CompactionConfig",
            "CompactionStats", "CUDAPinnedPool", "ExpertMetadata", "LayerMetadata", "MemoryCompactor", "MemoryStats", "MLACompressionRatio",
            "MMAPWeightConfig", "MMAPWeightManager", "MMAPWeightStats", "MMFP4MemoryManager", "PooledBuffer", "TransientBuffer", "TransientBufferCPP",

@@ -97,3 +97,69 @@ class TileCoordinator:
     def iter_tiles(self):
         for i in range(self.num_tiles):
             yield (i, *self.tile_to_coords(i))
+
+
+class ExpertWeightStreamer:
+    """Device residency of routed experts under a budget: ``get_expert_weights(e)`` returns the resident copy, loading it on a
+    miss (``loader(e)`` brings the expert's tensors to the device; without a loader a record ``{"expert_idx", "resident"}`` stands
+    in, which is enough for the bookkeeping and for tests); eviction takes, among the least recently used half, the expert
+    with the fewest accesses, and halves its count so that a formerly hot expert can cool down; ``predicted_experts`` ranks
+    the non-resident experts of the recent routing history for prefetching.  Reference ``expert_weight_streaming.py:22``."""
+
+    def __init__(self, num_experts: int = 256, gpu_cache_size: int = 64, loader: Optional[Callable[[int], object]] = None,
+                 on_evict: Optional[Callable[[int, object], None]] = None, history: int = 1024):
+        import collections
+        self.num_experts, self.gpu_cache_size = num_experts, gpu_cache_size
+        self.loader, self.on_evict = loader, on_evict
+        self.gpu_cache: "OrderedDict[int, object]" = OrderedDict()
+        self.access_counts: Dict[int, int] = collections.defaultdict(int)
+        self._history = collections.deque(maxlen=history)
+        self.hits = self.misses = self.evictions = 0
+
+    def _load(self, e: int) -> None:
+        self.gpu_cache[e] = self.loader(e) if self.loader is not None else {"expert_idx": e, "resident": True}
+        self.evict_cold()
+
+    def prefetch_experts(self, expert_indices) -> int:
+        n = 0
+        for e in expert_indices:
+            if 0 <= e < self.num_experts and e not in self.gpu_cache:
+                self._load(int(e))
+                n += 1
+        return n
+
+    def get_expert_weights(self, expert_idx: int):
+        if not 0 <= expert_idx < self.num_experts:
+            raise ValueError(f"expert_idx {expert_idx} out of range [0, {self.num_experts})")
+        self.access_counts[expert_idx] += 1
+        self._history.append(expert_idx)
+        if expert_idx in self.gpu_cache:
+            self.hits += 1
+            self.gpu_cache.move_to_end(expert_idx)
+            return self.gpu_cache[expert_idx]
+        self.misses += 1
+        self._load(expert_idx)
+        return self.gpu_cache[expert_idx]
+
+    def evict_cold(self) -> None:
+        while len(self.gpu_cache) > self.gpu_cache_size:
+            order = list(self.gpu_cache)
+            newest = order[-1]
+            pool = [e for e in order[: max(1, len(order) // 2)] if e != newest] or order[:1]
+            victim = min(pool, key=lambda e: self.access_counts[e])
+            obj = self.gpu_cache.pop(victim)
+            self.access_counts[victim] //= 2
+            self.evictions += 1
+            if self.on_evict is not None:
+                self.on_evict(victim, obj)
+
+    def predicted_experts(self, top_k: int = 8, window: int = 256) -> List[int]:
+        freq: Dict[int, int] = {}
+        for e in list(self._history)[-window:]:
+            if e not in self.gpu_cache:
+                freq[e] = freq.get(e, 0) + 1
+        return sorted(freq, key=lambda e: (-freq[e], e))[:top_k]
+
+    def hit_rate(self) -> float:
+        n = self.hits + self.misses
+        return self.hits / n if n else 0.0

@@ -88,10 +88,13 @@ __all__ += ["GPUGroupingResult", "GPUExpertGrouping", "TopKExpertGrouping", "gro
 
 
 def __getattr__(name: str):
+    if name in ("MoERouterCpp", "RouterBatchOutput"):
+        from . import fast_router
+        return getattr(fast_router, name)
     if name in ("compute_expert_load", "compute_load_balancing_loss", "gather_for_experts", "scatter_expert_outputs"):
         from .. import compat_api
         return getattr(compat_api, name)
     raise AttributeError(name)
 
 
-__all__ += ["compute_expert_load", "compute_load_balancing_loss", "gather_for_experts", "scatter_expert_outputs"]
+__all__ += ["MoERouterCpp", "RouterBatchOutput", "compute_expert_load", "compute_load_balancing_loss", "gather_for_experts", "scatter_expert_outputs"]

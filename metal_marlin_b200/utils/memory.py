@@ -191,3 +191,25 @@ class AdaptivePrefetcher:
                 th = threading.Thread(target=work, args=(i + 1,))
                 th.start()
             yield cur
+
+
+def pad_to_multiple(tensor, dim: int, multiple: int = 8):
+    """Zero-pad ``tensor`` along ``dim`` up to the next multiple: ``(padded, pad_size)`` (the tensor itself and 0 when it fits)."""
+    import torch
+    if multiple <= 0:
+        raise ValueError(f"multiple must be > 0, got {multiple}")
+    d = dim % tensor.dim()
+    pad = (-tensor.size(d)) % multiple
+    if pad == 0:
+        return tensor, 0
+    shape = list(tensor.shape)
+    shape[d] = pad
+    return torch.cat([tensor, torch.zeros(shape, dtype=tensor.dtype, device=tensor.device)], d), pad
+
+
+def unpad(tensor, dim: int, pad_size: int):
+    """Undo :func:`pad_to_multiple`."""
+    if pad_size == 0:
+        return tensor
+    d = dim % tensor.dim()
+    return tensor.narrow(d, 0, tensor.size(d) - pad_size)

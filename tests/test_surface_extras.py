@@ -318,3 +318,107 @@ def test_swiglu_fused_kernel_gpu():
     g, u = (torch.randn(2, 5, 256, device="cuda", dtype=torch.bfloat16) for _ in range(2))
     ref = torch.nn.functional.silu(g.float()) * u.float()
     assert torch.allclose(mm.swiglu_fused_metal(g, u).float(), ref, atol=3e-2, rtol=2e-2)
+
+
+# ------------------------------------------------------------------------------------------------ streamer, packings, padding, router
+def test_expert_weight_streamer():
+    from metal_marlin_b200.memory import ExpertWeightStreamer
+    loaded, evicted = [], []
+    s = ExpertWeightStreamer(num_experts=16, gpu_cache_size=3, loader=lambda e: loaded.append(e) or {"w": torch.full((2,), float(e))},
+                             on_evict=lambda e, o: evicted.append(e))
+    for e in (0, 1, 0, 0, 2):
+        s.get_expert_weights(e)
+    assert list(s.gpu_cache) == [1, 0, 2] and s.hits == 2 and s.misses == 3 and loaded == [0, 1, 2]
+    s.get_expert_weights(3)                       # over budget: among the older half {1}, the coldest goes
+    assert evicted == [1] and 1 not in s.gpu_cache and s.evictions == 1 and s.access_counts[1] == 0
+    assert float(s.get_expert_weights(3)["w"][0]) == 3.0 and s.hit_rate() == pytest.approx(3 / 7)
+    for e in (5, 5, 5, 6):                         # each load evicts again; what is not resident and recurs is predicted
+        s.get_expert_weights(e)
+    pred = s.predicted_experts(4)
+    assert all(p not in s.gpu_cache for p in pred) and len(s.gpu_cache) == 3
+    assert s.prefetch_experts([9, 99, 9]) == 1 and 9 in s.gpu_cache
+    with pytest.raises(ValueError):
+        s.get_expert_weights(16)
+    plain = ExpertWeightStreamer(4, 2)
+    assert plain.get_expert_weights(1) == {"expert_idx": 1, "resident": True}
+
+
+def test_marlin_gptq_packing_round_trip():
+    import metal_marlin_b200 as mm
+    from metal_marlin_b200.converters import torch_compat as tc
+    rs = np.random.RandomState(0)
+    K, N, gs = 64, 24, 32
+    codes = rs.randint(0, 16, (K, N)).astype(np.uint8)
+    marlin = tc.pack_along_n(codes)
+    assert marlin.shape == (K, N // 8) and marlin.dtype == np.uint32 and np.array_equal(tc.unpack_along_n(marlin, N), codes)
+    assert int(marlin[3, 1]) == sum(int(codes[3, 8 + i]) << (4 * i) for i in range(8))
+    scales = rs.rand(K // gs, N).astype(np.float32)
+    sd = mm.export_for_pytorch(marlin, scales, {"in_features": K, "out_features": N, "group_size": gs})
+    assert sd["qweight"].shape == (K // 8, N) and sd["qweight"].dtype == np.int32 and np.array_equal(tc.unpack_along_k(sd["qweight"]), codes)
+    assert int(sd["qweight"].view(np.uint32)[2, 5]) == sum(int(codes[16 + i, 5]) << (4 * i) for i in range(8))
+    assert sd["g_idx"].tolist() == [i // gs for i in range(K)] and sd["bits"].tolist() == [4] and sd["scales"].dtype == np.float16
+    back, sc, g = mm.import_from_pytorch(sd)
+    assert np.array_equal(back, marlin) and g == gs and np.array_equal(sc, scales.astype(np.float16))
+    del sd["group_size"]
+    assert mm.import_from_pytorch(sd)[2] == gs                                 # inferred from the shapes
+    with pytest.raises(ValueError):
+        mm.export_for_pytorch(marlin, scales, {"in_features": K, "out_features": N + 8, "group_size": gs})
+    with pytest.raises(ValueError):
+        tc.pack_along_n(codes[:, :5])
+
+
+def test_padding_cholesky_and_aliases():
+    import metal_marlin_b200 as mm
+    x = torch.arange(15.).reshape(3, 5)
+    p, n = mm.pad_to_multiple(x, -1, 4)
+    assert p.shape == (3, 8) and n == 3 and torch.equal(p[:, :5], x) and (p[:, 5:] == 0).all() and torch.equal(mm.unpad(p, 1, n), x)
+    same, z = mm.pad_to_multiple(x, 0, 3)
+    assert same is x and z == 0 and mm.unpad(x, 0, 0) is x
+    with pytest.raises(ValueError):
+        mm.pad_to_multiple(x, 0, 0)
+    rs = np.random.RandomState(0)
+    A = rs.randn(12, 6)
+    H = A.T @ A
+    L = mm.cholesky_decompose(H, 1e-6)
+    assert L.dtype == np.float64 and np.allclose(np.tril(L), L) and np.allclose(L @ L.T, H + 1e-6 * np.trace(H) / 6 * np.eye(6), atol=1e-5)
+    assert np.isfinite(mm.cholesky_decompose(np.ones((4, 4)), 1e-6)).all()       # singular input: damping takes care of it
+    from metal_marlin_b200.trellis import TrellisModelConfig
+    assert mm.TrellisConfig is TrellisModelConfig
+
+
+def test_fast_router_and_hot_pairs():
+    from metal_marlin_b200.moe import MoERouterCpp
+    torch.manual_seed(0)
+    E, H, K = 8, 32, 2
+    w = torch.randn(E, H)
+    r = MoERouterCpp(E, H, K, max_batch_tokens=64, hot_pair_cache_capacity=2, hot_pair_threshold=3, device="cpu")
+    assert (r.num_experts, r.hidden_dim, r.top_k, r.hot_pair_count) == (E, H, K, 0)
+    x = torch.randn(10, H)
+    out = r.route_batch(x, w.numpy())
+    p = torch.softmax(x @ w.t(), -1)
+    wt, ids = p.topk(K, -1)
+    assert torch.equal(out.expert_ids.long(), ids) and torch.allclose(out.expert_weights, wt / wt.sum(-1, keepdim=True), atol=1e-5)
+    assert out.num_tokens == 10 and out.top_k == 2
+    bias = torch.zeros(E)
+    bias[5] = 50.0
+    assert (r.route_batch(x, w, bias.numpy()).expert_ids[:, 0] == 5).all()
+    bits = x.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)       # raw bf16 patterns, as the reference passes them
+    ob = r.route_batch(bits, w)
+    assert torch.equal(ob.expert_ids.long(), torch.softmax(x.to(torch.bfloat16).float() @ w.t(), -1).topk(K, -1).indices)
+    with pytest.raises(TypeError):
+        r.route_batch(x.numpy(), w)
+    with pytest.raises(ValueError):
+        r.route_batch(torch.randn(65, H), w)
+    with pytest.raises(ValueError):
+        MoERouterCpp(4, 8, 5)
+    # a token repeated makes its leading pair hot after `threshold` sightings; the cache holds `capacity` pairs
+    r.reset_hot_pair_cache()
+    one = x[:1].repeat(5, 1)
+    o1 = r.route_batch(one, w)
+    pair = tuple(sorted(o1.expert_ids[0].tolist()))
+    assert o1.hot_pairs == [pair] and o1.hot_pair_hits == 2 and r.hot_pair_count == 1
+    for i in (1, 2, 3):
+        r.route_batch(x[i:i + 1].repeat(3, 1), w)
+    assert r.hot_pair_count <= 2
+    r.reset_hot_pair_cache()
+    assert r.hot_pair_count == 0
