@@ -35,7 +35,8 @@ _reg(".converters.torch_compat", "export_for_pytorch", "import_from_pytorch")
 _reg(".memory.expert_cache", "ExpertWeightStreamer")
 _reg(".moe.fast_router", "MoERouterCpp", "RouterBatchOutput")
 _reg(".trellis.lm", TrellisConfig="TrellisModelConfig")
-_reg(".compat_api", "cholesky_decompose")
+_reg(".compat_api", "cholesky_decompose", "is_expert_buffer_pool_available", "initialize_expert_buffer_pool", "get_expert_buffer_pool",
+     "allocate_expert_weight_buffer", "clear_expert_buffer_pool")
 _reg(".analysis.moe_routing", "MoERoutingProfiler", "simulate_routing_for_model", "analyze_routing_from_file")
 _reg(".dtypes", "DTypeConfig", "get_dtype_config", "to_torch_dtype")
 _reg(".inference.pipeline", "MMFP4Pipeline", "MarlinPipeline", "StreamingOutput")

@@ -1365,3 +1365,41 @@ def cholesky_decompose(H, regularization: float = 1e-6) -> np.ndarray:
     if lam == lam:                       # a plain damping worked: redo the factorisation in float64 on the undamaged input
         Hd = Ht + lam * torch.eye(Ht.shape[-1], dtype=torch.float64, device=Ht.device)
     return torch.linalg.cholesky(Hd.double()).cpu().numpy().astype(np.float64)
+
+
+# ------------------------------------------------------------------------------------------------ expert weight buffer pool
+_EXPERT_POOL: Dict[str, Any] = {"arena": None}
+
+
+def is_expert_buffer_pool_available() -> bool:
+    return _EXPERT_POOL["arena"] is not None
+
+
+def initialize_expert_buffer_pool(device=None, heap_size: int = 1 << 30) -> bool:
+    """One arena (best fit with coalescing, in the native runtime) that expert weight buffers are carved from, so that
+    bringing an expert in does not call the device allocator.  ``device``: a torch device or name (the reference passes a
+    device pointer; on this platform the slab is an ordinary tensor).  Returns True when a pool exists afterwards.
+    Reference ``expert_manager_cpp.py:91``."""
+    from .memory import Arena
+    if _EXPERT_POOL["arena"] is None:
+        dev = torch.device(device) if device is not None and not isinstance(device, int) else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        _EXPERT_POOL["arena"] = Arena(int(heap_size), dev)
+    return True
+
+
+def get_expert_buffer_pool():
+    return _EXPERT_POOL["arena"]
+
+
+def allocate_expert_weight_buffer(size: int) -> torch.Tensor:
+    """``size`` bytes from the pool as a ``uint8`` tensor (``arena.free(t)`` returns it)."""
+    if _EXPERT_POOL["arena"] is None:
+        raise RuntimeError("the expert buffer pool is not initialised (call initialize_expert_buffer_pool first)")
+    return _EXPERT_POOL["arena"].alloc((int(size),), torch.uint8, tag="expert")
+
+
+def clear_expert_buffer_pool() -> None:
+    a = _EXPERT_POOL["arena"]
+    _EXPERT_POOL["arena"] = None
+    if a is not None and hasattr(a, "close"):
+        a.close()

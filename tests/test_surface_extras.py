@@ -422,3 +422,21 @@ def test_fast_router_and_hot_pairs():
     assert r.hot_pair_count <= 2
     r.reset_hot_pair_cache()
     assert r.hot_pair_count == 0
+
+
+def test_expert_buffer_pool():
+    import metal_marlin_b200 as mm
+    mm.clear_expert_buffer_pool()
+    assert not mm.is_expert_buffer_pool_available() and mm.get_expert_buffer_pool() is None
+    with pytest.raises(RuntimeError):
+        mm.allocate_expert_weight_buffer(64)
+    assert mm.initialize_expert_buffer_pool("cpu", heap_size=1 << 16) and mm.is_expert_buffer_pool_available()
+    pool = mm.get_expert_buffer_pool()
+    a, b = mm.allocate_expert_weight_buffer(1000), mm.allocate_expert_weight_buffer(3000)
+    assert a.dtype == torch.uint8 and a.numel() == 1000 and pool.offset_of(b) >= 1000 and pool.stats()["used"] >= 4000
+    pool.free(a)
+    c = mm.allocate_expert_weight_buffer(900)
+    assert pool.offset_of(c) == 0                                            # best fit reuses the freed block
+    assert mm.initialize_expert_buffer_pool("cpu") and mm.get_expert_buffer_pool() is pool      # a second call keeps the pool
+    mm.clear_expert_buffer_pool()
+    assert not mm.is_expert_buffer_pool_available()
