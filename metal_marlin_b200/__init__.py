@@ -33,6 +33,7 @@ _reg(".models.qwen36_profile", "Qwen36ModelProfile", "QWEN36_27B_PROFILE", "prof
 _reg(".utils.memory", "pad_to_multiple", "unpad")
 _reg(".converters.torch_compat", "export_for_pytorch", "import_from_pytorch")
 _reg(".memory.expert_cache", "ExpertWeightStreamer")
+_reg(".attention", "BlockSparseMask", "block_sparse_attention_metal")
 _reg(".moe.fast_router", "MoERouterCpp", "RouterBatchOutput")
 _reg(".trellis.lm", TrellisConfig="TrellisModelConfig")
 _reg(".compat_api", "cholesky_decompose", "is_expert_buffer_pool_available", "initialize_expert_buffer_pool", "get_expert_buffer_pool",

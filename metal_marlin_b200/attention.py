@@ -101,6 +101,126 @@ def sliding_window_attention(q, k, v, window: int, global_tokens: int = 0, scale
     return F.scaled_dot_product_attention(q, k, v, attn_mask=m, scale=scale)
 
 
+# ------------------------------------------------------------------------------------------ block-sparse mask object
+class BlockSparseMask:
+    """Which (query block, key block) pairs are computed, stored as bit sets: ``mask_bits [num_q_blocks, ceil(num_k_blocks / 64)]``
+    int64 words (the bit pattern of unsigned 64-bit words: bit ``j % 64`` of word ``j // 64`` in row ``i`` says that query block ``i``
+    attends to key block ``j``).  Factories for the usual patterns; ``dense()`` gives the boolean block matrix the attention
+    entry points take.  Reference ``attention.py:40`` (``BlockSparseMask``: ``create_sliding_window`` / ``create_bigbird`` /
+    ``create_longformer`` / ``from_dense_mask``)."""
+
+    def __init__(self, mask_bits: torch.Tensor, block_q: int, block_k: int, num_q_blocks: int, num_k_blocks: int, seq_q: int, seq_k: int):
+        self.mask_bits, self.block_q, self.block_k = mask_bits, block_q, block_k
+        self.num_q_blocks, self.num_k_blocks, self.seq_q, self.seq_k = num_q_blocks, num_k_blocks, seq_q, seq_k
+
+    @classmethod
+    def from_block_matrix(cls, blocks: torch.Tensor, block_q: int, block_k: int, seq_q: int, seq_k: int, device=None) -> "BlockSparseMask":
+        b = blocks.bool().cpu()
+        nq, nk = b.shape
+        words = (nk + 63) // 64
+        pad = torch.zeros(nq, words * 64, dtype=torch.int64)
+        pad[:, :nk] = b.long()
+        shifts = torch.arange(64, dtype=torch.int64)
+        lo = (pad.view(nq, words, 64)[..., :63] << shifts[:63]).sum(-1)
+        top = pad.view(nq, words, 64)[..., 63]
+        bits = lo | torch.where(top > 0, torch.tensor(-2 ** 63, dtype=torch.int64), torch.tensor(0, dtype=torch.int64))
+        return cls(bits.to(device) if device is not None else bits, block_q, block_k, nq, nk, seq_q, seq_k)
+
+    def dense(self) -> torch.Tensor:
+        """bool ``[num_q_blocks, num_k_blocks]``."""
+        w = self.mask_bits.cpu()
+        shifts = torch.arange(64, dtype=torch.int64)
+        bits = ((w.unsqueeze(-1) >> shifts) & 1).bool().reshape(self.num_q_blocks, -1)
+        return bits[:, : self.num_k_blocks]
+
+    def is_active(self, q_block: int, k_block: int) -> bool:
+        return bool((int(self.mask_bits[q_block, k_block // 64]) >> (k_block % 64)) & 1)
+
+    @property
+    def density(self) -> float:
+        return float(self.dense().float().mean())
+
+    def element_mask(self, causal: bool = False) -> torch.Tensor:
+        """bool ``[seq_q, seq_k]`` (queries are the last positions of the keys for the causal rule)."""
+        m = self.dense().repeat_interleave(self.block_q, 0).repeat_interleave(self.block_k, 1)[: self.seq_q, : self.seq_k]
+        if causal:
+            qpos = torch.arange(self.seq_q).unsqueeze(1) + (self.seq_k - self.seq_q)
+            m = m & (torch.arange(self.seq_k).unsqueeze(0) <= qpos)
+        return m
+
+    @staticmethod
+    def _blocks(seq_len: int, block_size: int) -> int:
+        return (seq_len + block_size - 1) // block_size
+
+    @classmethod
+    def create_sliding_window(cls, seq_len: int, window_size: int, block_size: int = 64, device=None) -> "BlockSparseMask":
+        """Causal sliding window: query block ``i`` sees the key blocks that hold any position within ``window_size`` before its
+        last query, up to itself."""
+        n = cls._blocks(seq_len, block_size)
+        qi = torch.arange(n)
+        q_end = torch.clamp((qi + 1) * block_size, max=seq_len)
+        first = torch.clamp(q_end - window_size, min=0) // block_size
+        kj = torch.arange(n).unsqueeze(0)
+        return cls.from_block_matrix((kj >= first.unsqueeze(1)) & (kj <= qi.unsqueeze(1)), block_size, block_size, seq_len, seq_len, device)
+
+    @classmethod
+    def create_bigbird(cls, seq_len: int, num_random_blocks: int = 3, num_global_blocks: int = 2, window_size: int = 256, block_size: int = 64,
+                       device=None, seed: int = 42) -> "BlockSparseMask":
+        """Local window (both directions) + the first ``num_global_blocks`` blocks seen by and seeing everything + ``num_random_blocks``
+        further key blocks visible to every query (drawn once with ``seed``)."""
+        n = cls._blocks(seq_len, block_size)
+        w = max(1, window_size // block_size)
+        idx = torch.arange(n)
+        m = (idx.unsqueeze(0) - idx.unsqueeze(1)).abs() <= w // 2 if w > 1 else torch.eye(n, dtype=torch.bool)
+        g = min(num_global_blocks, n)
+        m[:, :g] = True
+        m[:g, :] = True
+        if num_random_blocks > 0 and n > g:
+            gen = torch.Generator().manual_seed(seed)
+            m[:, torch.randperm(n - g, generator=gen)[:num_random_blocks] + g] = True
+        return cls.from_block_matrix(m, block_size, block_size, seq_len, seq_len, device)
+
+    @classmethod
+    def create_longformer(cls, seq_len: int, window_size: int = 512, global_token_indices: Sequence[int] = (0,), block_size: int = 64, device=None
+                          ) -> "BlockSparseMask":
+        """Symmetric local window + global tokens (their blocks attend everywhere and are attended from everywhere)."""
+        n = cls._blocks(seq_len, block_size)
+        idx = torch.arange(n)
+        half = max(0, (window_size // 2 + block_size - 1) // block_size)
+        m = (idx.unsqueeze(0) - idx.unsqueeze(1)).abs() <= half
+        for t in global_token_indices:
+            if 0 <= t < seq_len:
+                m[t // block_size, :] = True
+                m[:, t // block_size] = True
+        return cls.from_block_matrix(m, block_size, block_size, seq_len, seq_len, device)
+
+    @classmethod
+    def from_dense_mask(cls, mask: torch.Tensor, block_q: int = 64, block_k: int = 64, device=None) -> "BlockSparseMask":
+        """From an element mask ``[seq_q, seq_k]`` (bool: True = attend; float: finite = attend): a block is active when any of
+        its elements is."""
+        keep = mask.bool() if mask.dtype == torch.bool else torch.isfinite(mask) & (mask > -1e30)
+        sq, sk = keep.shape
+        nq, nk = (sq + block_q - 1) // block_q, (sk + block_k - 1) // block_k
+        pad = torch.zeros(nq * block_q, nk * block_k, dtype=torch.bool)
+        pad[:sq, :sk] = keep.cpu()
+        return cls.from_block_matrix(pad.view(nq, block_q, nk, block_k).any(3).any(1), block_q, block_k, sq, sk, device)
+
+
+def block_sparse_attention_metal(q, k, v, block_sparse_mask: BlockSparseMask, scale: Optional[float] = None, causal: bool = False):
+    """``q [B, H, Sq, D]``, ``k / v [B, Hk, Sk, D]`` restricted to the active blocks of the mask (and to the causal triangle with
+    ``causal``).  Square problems with one block size go to :func:`block_sparse_attention` (the prefill kernel skips empty key
+    tiles on a GPU); others use the element mask.  Reference ``attention.py:900``."""
+    m = block_sparse_mask
+    if q.shape[2] != m.seq_q or k.shape[2] != m.seq_k:
+        raise ValueError(f"sequence length mismatch: q={q.shape[2]}, k={k.shape[2]}, mask=({m.seq_q}, {m.seq_k})")
+    if m.seq_q == m.seq_k and m.block_q == m.block_k and q.shape[1] == k.shape[1]:
+        return block_sparse_attention(q, k, v, m.dense(), m.block_q, causal, scale)
+    el = m.element_mask(causal).to(q.device)
+    if k.shape[1] != q.shape[1]:
+        k, v = k.repeat_interleave(q.shape[1] // k.shape[1], 1), v.repeat_interleave(q.shape[1] // v.shape[1], 1)
+    return F.scaled_dot_product_attention(q, k, v, attn_mask=el, scale=scale)
+
+
 # ------------------------------------------------------------------------------------------ tree attention
 def tree_mask_from_parents(parents: Sequence[int]) -> torch.Tensor:
     """``parents[i]`` is the index of node i's parent (-1 = child of the last committed token).  Node i may attend

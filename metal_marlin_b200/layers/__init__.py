@@ -1,4 +1,5 @@
 from .linear import HadamardLinear, MMFP4Linear, QuantizedLinear, Sparse24Linear, TrellisLinear
+from .lora import LoRAMixin, apply_lora
 from .blocks import MMFP4FusedMoE, MMFP4MLA, MMFP4MoE, MixedPrecisionLinear, verify_kernel
 
 
@@ -13,4 +14,4 @@ def __getattr__(name: str):
 
 
 __all__ = ["HadamardLinear", "MMFP4Linear", "QuantizedLinear", "Sparse24Linear", "TrellisLinear", "MMFP4FusedMoE", "MMFP4MLA", "MMFP4MoE",
-           "MixedPrecisionLinear", "verify_kernel", "MMFP4MTPHead", "GLMMTPHead", "MarlinLinear"]
+           "MixedPrecisionLinear", "verify_kernel", "LoRAMixin", "apply_lora", "MMFP4MTPHead", "GLMMTPHead", "MarlinLinear"]

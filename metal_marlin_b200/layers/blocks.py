@@ -18,6 +18,7 @@ import torch.nn.functional as F
 from .. import ops
 from ..ops.weights import FP4ExpertBank
 from .linear import MMFP4Linear, QuantizedLinear
+from .lora import LoRAMixin
 
 
 class MMFP4MoE:
@@ -143,7 +144,7 @@ class MMFP4MLA:
     forward = __call__
 
 
-class MixedPrecisionLinear:
+class MixedPrecisionLinear(LoRAMixin):
     """A linear layer whose storage follows a precision policy: ``fp4`` -> :class:`MMFP4Linear`, other quantized formats ->
     :class:`QuantizedLinear`, 16-bit formats stay a plain matrix."""
 

@@ -21,6 +21,7 @@ from .. import ops
 from ..formats import trellis as trfmt
 from ..ops.weights import FP4Weight
 from ..quant import rtn
+from .lora import LoRAMixin
 
 DECODE_MAX_M = 8
 
@@ -34,7 +35,7 @@ def _bf16_matmul(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return (x2.float() @ w.float().t()).to(torch.bfloat16)
 
 
-class MMFP4Linear:
+class MMFP4Linear(LoRAMixin):
     def __init__(self, weight: FP4Weight, bias: Optional[torch.Tensor] = None, activation: Optional[str] = None):
         self.weight, self.bias, self.activation = weight, bias, activation
         self.in_features, self.out_features = weight.in_features, weight.out_features
@@ -77,7 +78,7 @@ def _lut_for(fmt: str, device) -> torch.Tensor:
     return lut.to(device)
 
 
-class QuantizedLinear:
+class QuantizedLinear(LoRAMixin):
     """Group-quantized linear for the non-FP4 formats."""
     is_generic = True
     names = None
@@ -130,7 +131,7 @@ class QuantizedLinear:
     forward = __call__
 
 
-class Sparse24Linear:
+class Sparse24Linear(LoRAMixin):
     """2:4 structured-sparse FP4 linear: of every four consecutive input columns the two of largest magnitude are kept,
     quantized to E2M1 with one fp16 scale per ``group_size`` dense columns, and stored with a 4-bit position word per group -
     0.375 bytes per dense weight (FP4 dense: 0.5).  The product runs on the tensor-core GEMM, which scatters the kept values
@@ -189,7 +190,7 @@ class Sparse24Linear:
     forward = __call__
 
 
-class TrellisLinear:
+class TrellisLinear(LoRAMixin):
     is_generic = True
     names = None
 
@@ -263,7 +264,7 @@ class TrellisLinear:
         return self.codes.numel() + 4 * (self.scales.numel() + self.su.numel() + self.sv.numel())
 
 
-class HadamardLinear:
+class HadamardLinear(LoRAMixin):
     """``y = inner(block_hadamard(x))`` for a weight stored in the rotated basis."""
     is_generic = True
     names = None

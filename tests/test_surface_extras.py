@@ -440,3 +440,86 @@ def test_expert_buffer_pool():
     assert mm.initialize_expert_buffer_pool("cpu") and mm.get_expert_buffer_pool() is pool      # a second call keeps the pool
     mm.clear_expert_buffer_pool()
     assert not mm.is_expert_buffer_pool_available()
+
+
+def test_block_sparse_mask_object():
+    import metal_marlin_b200 as mm
+    from metal_marlin_b200.attention import BlockSparseMask, block_sparse_attention_metal
+    m = BlockSparseMask.create_sliding_window(seq_len=1000, window_size=200, block_size=64)
+    assert m.num_q_blocks == m.num_k_blocks == 16 and m.mask_bits.shape == (16, 1) and m.mask_bits.dtype == torch.int64
+    d = m.dense()
+    for i in range(16):
+        first = max(0, min((i + 1) * 64, 1000) - 200) // 64
+        assert d[i].tolist() == [first <= j <= i for j in range(16)]
+    assert m.is_active(5, 5) and m.is_active(5, 2) and not m.is_active(5, 1) and not m.is_active(5, 6) and 0 < m.density < 0.35
+    wide = BlockSparseMask.create_sliding_window(seq_len=64 * 130, window_size=64 * 130, block_size=64)      # more than one 64-bit word, bit 63 in use
+    assert wide.mask_bits.shape == (130, 3) and wide.is_active(129, 63) and wide.is_active(129, 64) and wide.is_active(129, 129) and not wide.is_active(3, 64)
+    assert torch.equal(wide.dense(), torch.tril(torch.ones(130, 130, dtype=torch.bool)))
+    bb = BlockSparseMask.create_bigbird(512, num_random_blocks=1, num_global_blocks=1, window_size=128, block_size=64)
+    db = bb.dense()
+    assert db[:, 0].all() and db[0, :].all() and db.diagonal().all() and db.sum(1).min() >= 3
+    assert torch.equal(db, BlockSparseMask.create_bigbird(512, 1, 1, 128, 64).dense())                      # the random blocks are seeded
+    lf = BlockSparseMask.create_longformer(512, window_size=128, global_token_indices=(0, 300), block_size=64).dense()
+    assert lf[4, :].all() and lf[:, 4].all() and lf[7, 6] and not lf[7, 2]
+    el = torch.zeros(100, 150, dtype=torch.bool)
+    el[10, 140] = True
+    fd = BlockSparseMask.from_dense_mask(el, 32, 64)
+    assert (fd.num_q_blocks, fd.num_k_blocks) == (4, 3) and fd.dense().nonzero().tolist() == [[0, 2]]
+    add = torch.full((64, 64), float("-inf"))
+    add[:, :32] = 0
+    assert BlockSparseMask.from_dense_mask(add, 32, 32).dense().tolist() == [[True, False], [True, False]]
+    # attention through the mask matches the element-mask oracle
+    torch.manual_seed(0)
+    S = 256
+    q, k, v = (torch.randn(1, 2, S, 32) for _ in range(3))
+    sm = BlockSparseMask.create_sliding_window(S, 96, 64)
+    out = mm.block_sparse_attention_metal(q, k, v, sm, causal=True)
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=sm.element_mask(causal=True))
+    assert torch.allclose(out, ref, atol=1e-5)
+    rect = BlockSparseMask.from_dense_mask(torch.ones(64, 128, dtype=torch.bool), 32, 64)
+    o2 = block_sparse_attention_metal(q[:, :, :64], k[:, :1, :128], v[:, :1, :128], rect)
+    r2 = torch.nn.functional.scaled_dot_product_attention(q[:, :, :64], k[:, :1, :128].expand(-1, 2, -1, -1), v[:, :1, :128].expand(-1, 2, -1, -1))
+    assert torch.allclose(o2, r2, atol=1e-5)
+    with pytest.raises(ValueError):
+        block_sparse_attention_metal(q[:, :, :100], k, v, sm)
+
+
+def test_batch_aware_lora_dispatch():
+    """Reference ``tests/test_batch_aware_lora.py``: per-row adapters over a quantized base, ``-1`` = no adapter."""
+    from metal_marlin_b200.layers import MMFP4Linear, MixedPrecisionLinear, QuantizedLinear, apply_lora
+    torch.manual_seed(0)
+    in_f, out_f, rank = 64, 16, 4
+    lin = MMFP4Linear.from_float(torch.randn(out_f, in_f), group_size=32, device="cpu")
+    x = torch.randn(4, in_f)
+    u, v = torch.randn(2, in_f, rank), torch.randn(2, rank, out_f)
+    idx = torch.tensor([0, 1, -1, 0])
+    base = lin(x).float()
+    out = lin.batch_aware_dispatch(x, u, v, idx).float()
+    want = base.clone()
+    for t, a in enumerate(idx.tolist()):
+        if a >= 0:
+            want[t] += (x[t] @ u[a]) @ v[a]
+    assert torch.allclose(out, want, atol=0.15, rtol=1e-2) and torch.allclose(out[2], base[2])      # bf16 outputs: one rounding of the sum
+    assert not torch.allclose(out[0], base[0])
+    assert torch.equal(lin.batch_aware_dispatch(x).float(), base)
+    # lists of adapters with different ranks, a scaling factor, and one index per sequence of a [batch, seq, in] input
+    ul, vl = [torch.randn(in_f, 2), torch.randn(in_f, 6)], [torch.randn(2, out_f), torch.randn(6, out_f)]
+    x3 = torch.randn(2, 3, in_f)
+    q8 = QuantizedLinear.from_float(torch.randn(out_f, in_f), "int8", 32, device="cpu")
+    o3 = q8.batch_aware_dispatch(x3, ul, vl, torch.tensor([1, 0]), scaling=0.5).float()
+    w3 = q8(x3).float()
+    w3[0] += 0.5 * (x3[0] @ ul[1]) @ vl[1]
+    w3[1] += 0.5 * (x3[1] @ ul[0]) @ vl[0]
+    assert o3.shape == (2, 3, out_f) and torch.allclose(o3, w3, atol=0.15, rtol=1e-2)
+    mp = MixedPrecisionLinear(torch.randn(out_f, 128), "bf16", device="cpu")
+    xb = torch.randn(4, 128, dtype=torch.bfloat16)
+    ub, vb = torch.randn(2, 128, rank, dtype=torch.bfloat16), torch.randn(2, rank, out_f, dtype=torch.bfloat16)
+    ob = mp.batch_aware_dispatch(xb, ub, vb, torch.tensor([0, -1, 1, 0]))
+    assert ob.shape == (4, out_f) and torch.allclose(ob[1].float(), mp(xb)[1].float()) and not torch.allclose(ob[2].float(), mp(xb)[2].float())
+    acc = torch.zeros(3, out_f)
+    apply_lora(acc, torch.ones(3, in_f), u, v, torch.tensor([1, 1, 1]))
+    assert torch.allclose(acc[0], torch.ones(in_f) @ u[1] @ v[1], atol=1e-4) and torch.equal(acc[0], acc[2])
+    with pytest.raises(ValueError):
+        apply_lora(acc, torch.ones(3, in_f), u, v, torch.tensor([0, 2, 0]))
+    with pytest.raises(ValueError):
+        apply_lora(acc, torch.ones(3, in_f), u, v, torch.tensor([0, 1]))
