@@ -16,6 +16,13 @@ TrellisModelWrapper = TrellisForCausalLM
 
 
 def __getattr__(name: str):
+    if name in ("MixedKernelSelector", "KernelABTester", "KernelFeedback", "ExpertSelectionCache", "ExpertMemoryPool", "select_intelligent_kernel",
+                "get_kernel_for_batch_size"):
+        from . import kernel_selection
+        return getattr(kernel_selection, name)
+    if name in ("create_mock_trellis_linear", "create_mock_dense_mlp", "create_mock_moe_mlp", "create_mini_config", "create_mini_model"):
+        from . import testing
+        return getattr(testing, name)
     if name in ("TrellisWeight", "TrellisModelLoader"):
         from ..formats import trellis as fmt
         return getattr(fmt, name)
@@ -29,7 +36,9 @@ def __getattr__(name: str):
     raise AttributeError(name)
 
 
-__all__ = ["TrellisWeight", "TrellisModelLoader", "GenerationConfig", "TrellisGenerator", "TrellisForCausalLM", "TrellisModelConfig", "TrellisLinear", "TrellisModelWrapper",
+__all__ = ["MixedKernelSelector", "KernelABTester", "KernelFeedback", "ExpertSelectionCache", "ExpertMemoryPool", "select_intelligent_kernel",
+           "get_kernel_for_batch_size", "create_mock_trellis_linear", "create_mock_dense_mlp", "create_mock_moe_mlp", "create_mini_config",
+           "create_mini_model", "TrellisWeight", "TrellisModelLoader", "GenerationConfig", "TrellisGenerator", "TrellisForCausalLM", "TrellisModelConfig", "TrellisLinear", "TrellisModelWrapper",
            "TrellisModel", "MixedBPWAutoTuner", "AutotuneConfig", "KernelConfig", "BenchmarkResult", "GLM4_TOKENIZER_ID", "CausalLMOutput",
            "CompressedKVCache", "MixedBPWMoEDispatcher", "MoEConfig", "TrellisDecoderLayer", "TrellisDenseMLP", "TrellisExpert",
            "TrellisKVCache", "TrellisMLAConfig", "TrellisMLAttention", "TrellisMoELayer", "TrellisMoEMLP", "compute_compression_ratio",
