@@ -10,6 +10,7 @@ from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Protocol, Sequence, Tuple
 
 _LAZY = {
+    "_fused_sampling": (".generate_loop", "_fused_sampling"), "_optimized_generate": (".generate_loop", "_optimized_generate"),
     "GenerationConfig": ("..trellis", "GenerationConfig"), "MetalMarlinModel": ("..models.mmfp4_causal_lm", "MMFP4ForCausalLM"),
     "ModelConfig": ("..models.config", "ModelConfig"),
     "MMFP4Pipeline": (".pipeline", "MMFP4Pipeline"), "MarlinPipeline": (".pipeline", "MarlinPipeline"),

@@ -133,3 +133,47 @@ def test_quantized_kv_attention_contiguous_layout(fmt, tol):
         p = torch.softmax(torch.einsum("hqd,hnd->hqn", q[b].float(), kk) * D ** -0.5, -1)
         ref[b] = p @ vv
     assert float((out - ref).abs().max()) < tol * float(ref.abs().max()) + 0.02
+
+
+def test_fused_sampling_and_allocation_free_generate_loop():
+    """Reference ``tests/test_fused_sampling_optimized.py`` / ``test_optimized_generate.py``."""
+    import types
+    import torch
+    from metal_marlin_b200.inference import _fused_sampling, _optimized_generate
+    p = torch.tensor([[0.1, 0.6, 0.3], [0.7, 0.2, 0.1]])
+    assert _fused_sampling(p, temperature=0.0).tolist() == [[1], [0]]
+    out = torch.zeros(2, 1, dtype=torch.int64)
+    assert _fused_sampling(p, temperature=1.0, top_k=1, out=out) is out and out.tolist() == [[1], [0]]
+    draws = torch.cat([_fused_sampling(p[:1], temperature=1.0, top_p=0.5, seed=3) for _ in range(60)])
+    assert set(draws.reshape(-1).tolist()) == {1}                                       # the nucleus of 0.5 holds one token
+    two = torch.cat([_fused_sampling(p[:1], temperature=1.0, top_p=0.65, seed=4) for _ in range(200)])
+    assert set(two.reshape(-1).tolist()) == {1, 2}                                      # 0.6 < 0.65: the next token joins the nucleus
+    wide = torch.cat([_fused_sampling(p[:1], temperature=1.0, top_p=1.0, seed=5) for _ in range(200)]).reshape(-1)
+    assert set(wide.tolist()) == {0, 1, 2} and (wide == 1).sum() > (wide == 0).sum()
+
+    V = 11
+
+    class Toy:
+        """Next token = (last token + 1) mod V; with a cache it must be fed one token at a time."""
+        def __init__(self, cache=True):
+            self.cache, self.calls = cache, []
+
+        def __call__(self, input_ids=None, past_key_values=None, use_cache=True, attention_mask=None):
+            self.calls.append((tuple(input_ids.shape), None if attention_mask is None else attention_mask.shape[1]))
+            logits = torch.full((*input_ids.shape, V), -10.0)
+            logits.scatter_(2, ((input_ids + 1) % V).unsqueeze(-1), 10.0)
+            past = (0 if past_key_values is None else past_key_values) + input_ids.shape[1] if self.cache else None
+            return types.SimpleNamespace(logits=logits, past_key_values=past)
+    ids = torch.tensor([[3, 4], [8, 9]])
+    m = Toy()
+    seq, past = _optimized_generate(m, ids, 4, temperature=0.0, return_past_key_values=True, attention_mask=torch.ones_like(ids))
+    assert seq.tolist() == [[3, 4, 5, 6, 7, 8], [8, 9, 10, 0, 1, 2]] and past == 5
+    assert [c[0] for c in m.calls] == [(2, 2), (2, 1), (2, 1), (2, 1)] and [c[1] for c in m.calls] == [2, 3, 4, 5]
+    nocache = Toy(cache=False)
+    assert _optimized_generate(nocache, ids, 2, temperature=0.0).tolist() == [[3, 4, 5, 6], [8, 9, 10, 0]] and nocache.calls[1][0] == (2, 3)
+    stop = _optimized_generate(Toy(), ids, 6, temperature=0.0, eos_token_id=6, pad_token_id=99)
+    assert stop[0].tolist()[:4] == [3, 4, 5, 6] and (stop[0, 4:] == 99).all() and stop.shape[1] == 8      # row 1 never stops: the loop runs on
+    both = _optimized_generate(Toy(), torch.tensor([[4], [4]]), 6, temperature=0.0, eos_token_id=6)
+    assert both.tolist() == [[4, 5, 6], [4, 5, 6]]                                     # every row done: early exit
+    sampled = _optimized_generate(Toy(), ids, 3, temperature=0.7, top_p=0.9, top_k=3, seed=1)
+    assert sampled.tolist() == [[3, 4, 5, 6, 7], [8, 9, 10, 0, 1]]                      # the peaked toy distribution leaves one choice
