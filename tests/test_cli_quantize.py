@@ -95,3 +95,25 @@ def test_serve_profiles_set_family_defaults(monkeypatch):
     r = CliRunner().invoke(cli, ["serve", "--profile", "glm47", "--port", "9000", "--num-kv-blocks", "1024"])
     assert r.exit_code == 0 and seen["cfg"].model_path == "/models/glm" and seen["cfg"].preset is None
     assert seen["port"] == 9000 and seen["cfg"].num_kv_blocks == 1024 and seen["cfg"].max_batch_size == 32
+
+
+def test_analysis_commands(tmp_path):
+    import json
+    import torch
+    from metal_marlin_b200.formats.safetensors_io import save_file
+    r = CliRunner()
+    out = r.invoke(cli, ["analyze-routing", "--simulate", "mixtral", "--samples", "64", "--output-dir", str(tmp_path / "routing")])
+    assert out.exit_code == 0, out.output
+    assert "MoE routing: 32 layers x 8 experts" in out.output and (tmp_path / "routing" / "routing_report.json").is_file()
+    assert r.invoke(cli, ["analyze-routing"]).exit_code != 0 and r.invoke(cli, ["analyze-routing", "--log", "x.jsonl"]).exit_code != 0
+    torch.manual_seed(0)
+    f = str(tmp_path / "w.safetensors")
+    save_file({"a.weight": torch.randn(32, 128) * 0.05, "b.weight": torch.randn(16, 64) * 0.05, "n.weight": torch.ones(64)}, f)
+    out = r.invoke(cli, ["error-report", f, "-o", str(tmp_path / "err"), "--formats", "fp4,int8", "--group-size", "64"])
+    assert out.exit_code == 0, out.output
+    assert "fp4: 2 matrices" in out.output and "int8: 2 matrices" in out.output
+    rep = json.load(open(tmp_path / "err" / "error_report.json"))
+    assert set(rep["layers"]) == {"a.weight", "b.weight"}
+    out = r.invoke(cli, ["flops", "--preset", "glm-4.7-flash", "--top", "3"])
+    assert out.exit_code == 0 and "lm_head" in out.output and "TFLOP" in out.output
+    assert r.invoke(cli, ["flops"]).exit_code != 0
